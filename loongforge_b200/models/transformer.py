@@ -1,0 +1,294 @@
+"""Decoder building blocks on a packed-token layout.
+
+Activations are ``[T, hidden]`` (T = all tokens of the micro-batch, sequence boundaries in
+``cu_seqlens``); under sequence parallelism the tensors between blocks are ``[T/tp, hidden]``.
+Module and parameter names reproduce Megatron's so that ``state_dict`` keys equal the
+reference's checkpoint keys (configs/models/llama3/ckpt_convert/llama3_convert.yaml:43-70):
+``self_attention.linear_qkv.{layer_norm_weight,weight,bias}``, ``self_attention.linear_proj``,
+``mlp.linear_fc1.{layer_norm_weight,weight}``, ``mlp.linear_fc2``, ``pre_mlp_layernorm``,
+``input_layernorm``, ``self_attention.{q,k}_layernorm``.
+
+The packed QKV weight uses Megatron's per-group row order ``[q_0..q_{r-1}, k, v]``
+(tools/convert_checkpoint/huggingface/util/hf_attn_converter.py:62-78) and FC1 is
+``[gate; up]`` (tools/convert_checkpoint/huggingface/huggingface_base.py:495-524).
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.utils.checkpoint
+
+from ..ops import functional as OF
+from ..parallel import layers as PL
+from ..parallel import state as ps
+from .config import TransformerConfig
+
+
+@dataclasses.dataclass
+class PackedSeqParams:
+    """Sequence boundaries of a packed ("thd") micro-batch."""
+    cu_seqlens: Optional[torch.Tensor] = None  # int32 [num_seqs + 1]
+    max_seqlen: Optional[int] = None
+
+
+@dataclasses.dataclass
+class RotaryInputs:
+    freqs: torch.Tensor  # fp32 [P, rot_dim/2] angle table, or per-token angles [T, rot_dim/2]
+    pos_ids: Optional[torch.Tensor] = None  # int32 [T] rows of `freqs`; None = row t
+    mscale: float = 1.0
+
+
+class Norm(nn.Module):
+    def __init__(self, hidden: int, cfg: TransformerConfig, device=None, sequence_parallel: bool = False):
+        super().__init__()
+        self.kind = cfg.normalization
+        self.eps = cfg.layernorm_epsilon
+        self.offset = 1.0 if cfg.layernorm_zero_centered_gamma else 0.0
+        init = 0.0 if cfg.layernorm_zero_centered_gamma else 1.0
+        self.weight = nn.Parameter(torch.full((hidden,), init, dtype=cfg.params_dtype, device=device))
+        PL.mark_tp(self.weight, None, sequence_parallel=sequence_parallel)
+        if self.kind == "LayerNorm":
+            self.bias = nn.Parameter(torch.zeros(hidden, dtype=cfg.params_dtype, device=device))
+            PL.mark_tp(self.bias, None, sequence_parallel=sequence_parallel)
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, x):
+        return apply_norm(x, self.weight, self.bias, self.kind, self.eps, self.offset)
+
+
+def apply_norm(x, weight, bias, kind, eps, offset=0.0):
+    if kind == "RMSNorm":
+        return OF.rmsnorm(x, weight, eps, offset)
+    w = weight + offset if offset else weight
+    return torch.nn.functional.layer_norm(x, (x.shape[-1],), w.to(x.dtype), bias.to(x.dtype) if bias is not None else None, eps)
+
+
+class LayerNormColumnParallelLinear(PL.ColumnParallelLinear):
+    """Norm fused in front of a column-parallel linear (norm runs on the sequence shard,
+    before the all-gather). Parameter names: ``layer_norm_weight`` / ``layer_norm_bias``."""
+
+    def __init__(self, in_features, out_features, cfg: TransformerConfig, **kw):
+        super().__init__(in_features, out_features, **kw)
+        dev = self.weight.device
+        init = 0.0 if cfg.layernorm_zero_centered_gamma else 1.0
+        self.layer_norm_weight = nn.Parameter(torch.full((in_features,), init, dtype=cfg.params_dtype, device=dev))
+        PL.mark_tp(self.layer_norm_weight, None, sequence_parallel=self.sequence_parallel)
+        if cfg.normalization == "LayerNorm":
+            self.layer_norm_bias = nn.Parameter(torch.zeros(in_features, dtype=cfg.params_dtype, device=dev))
+            PL.mark_tp(self.layer_norm_bias, None, sequence_parallel=self.sequence_parallel)
+        else:
+            self.register_parameter("layer_norm_bias", None)
+        self._norm = (cfg.normalization, cfg.layernorm_epsilon, 1.0 if cfg.layernorm_zero_centered_gamma else 0.0)
+
+    def forward(self, x):
+        kind, eps, off = self._norm
+        return super().forward(apply_norm(x, self.layer_norm_weight, self.layer_norm_bias, kind, eps, off))
+
+
+def _act(name: str):
+    import torch.nn.functional as F
+    return {"gelu": F.gelu, "relu": F.relu, "silu": F.silu,
+            "quick_gelu": lambda x: x * torch.sigmoid(1.702 * x),
+            "gelu_tanh": lambda x: F.gelu(x, approximate="tanh")}[name]
+
+
+class MLP(nn.Module):
+    def __init__(self, cfg: TransformerConfig, key: str, *, ffn_hidden: Optional[int] = None, fused_norm: bool = True,
+                 device=None, parallel_state=None, is_expert: bool = False, sequence_parallel: Optional[bool] = None):
+        super().__init__()
+        f = ffn_hidden or cfg.ffn_hidden_size
+        sp = cfg.sequence_parallel if sequence_parallel is None else sequence_parallel
+        glu = cfg.gated_linear_unit
+        common = dict(init_std=cfg.init_method_std, sequence_parallel=sp, params_dtype=cfg.params_dtype,
+                      device=device, parallel_state=parallel_state, tp_comm_overlap=cfg.tp_comm_overlap,
+                      is_expert=is_expert)
+        fc1_kw = dict(bias=cfg.add_bias_linear, key=key + ".linear_fc1", stride=2 if glu else 1, **common)
+        if fused_norm:
+            self.linear_fc1 = LayerNormColumnParallelLinear(cfg.hidden_size, f * (2 if glu else 1), cfg, **fc1_kw)
+        else:
+            self.linear_fc1 = PL.ColumnParallelLinear(cfg.hidden_size, f * (2 if glu else 1), **fc1_kw)
+        out_std = cfg.init_method_std / math.sqrt(2.0 * cfg.num_layers)
+        common["init_std"] = out_std
+        self.linear_fc2 = PL.RowParallelLinear(f, cfg.hidden_size, bias=cfg.add_bias_linear, key=key + ".linear_fc2",
+                                               **common)
+        self.glu = glu
+        self.act_name = cfg.activation
+
+    def forward(self, x, residual=None):
+        h = self.linear_fc1(x)
+        if self.glu and self.act_name == "swiglu":
+            h = OF.swiglu(h)
+        elif self.glu:
+            g, u = h.chunk(2, dim=-1)
+            h = _act("gelu" if self.act_name == "geglu" else self.act_name)(g) * u
+        else:
+            h = _act(self.act_name)(h)
+        return self.linear_fc2(h, residual)
+
+
+class SelfAttention(nn.Module):
+    """GQA self attention with a packed QKV projection, optional per-head QK RMSNorm (Qwen3),
+    RoPE / M-RoPE applied in place on the packed buffer, and packed-sequence attention."""
+
+    def __init__(self, cfg: TransformerConfig, key: str, *, fused_norm: bool = True, device=None, parallel_state=None):
+        super().__init__()
+        st = ps.get_state(parallel_state)
+        tp = st.dims.tp
+        self.cfg = cfg
+        self.d = cfg.kv_channels
+        self.nq, self.ng = cfg.num_attention_heads, cfg.num_query_groups
+        assert self.ng % tp == 0 and self.nq % self.ng == 0, "kv groups must divide by TP"
+        self.r = self.nq // self.ng
+        self.ng_local = self.ng // tp
+        self.nq_local = self.nq // tp
+        qkv_out = (self.nq + 2 * self.ng) * self.d
+        common = dict(sequence_parallel=cfg.sequence_parallel, params_dtype=cfg.params_dtype, device=device,
+                      parallel_state=parallel_state, tp_comm_overlap=cfg.tp_comm_overlap)
+        kw = dict(bias=cfg.add_bias_linear or cfg.add_qkv_bias, init_std=cfg.init_method_std,
+                  key=key + ".linear_qkv", **common)
+        if fused_norm:
+            self.linear_qkv = LayerNormColumnParallelLinear(cfg.hidden_size, qkv_out, cfg, **kw)
+        else:
+            self.linear_qkv = PL.ColumnParallelLinear(cfg.hidden_size, qkv_out, **kw)
+        if cfg.qk_layernorm:
+            self.q_layernorm = Norm(self.d, cfg, device=device)
+            self.k_layernorm = Norm(self.d, cfg, device=device)
+        else:
+            self.q_layernorm = self.k_layernorm = None
+        self.linear_proj = PL.RowParallelLinear(self.nq * self.d, cfg.hidden_size, bias=cfg.add_bias_linear,
+                                                init_std=cfg.init_method_std / math.sqrt(2.0 * cfg.num_layers),
+                                                key=key + ".linear_proj", **common)
+        self.scale = cfg.attention_softmax_scale or 1.0 / math.sqrt(self.d)
+        self.rot_dim = int(self.d * cfg.rotary_percent)
+
+    def forward(self, x, rotary: Optional[RotaryInputs], packed: Optional[PackedSeqParams], residual=None):
+        cfg = self.cfg
+        qkv = self.linear_qkv(x)  # [T, ng_local * (r + 2) * d]
+        T = qkv.shape[0]
+        g, r, d = self.ng_local, self.r, self.d
+        cu = packed.cu_seqlens if packed is not None else None
+        if self.q_layernorm is None:
+            if rotary is not None:
+                qkv = self._rope_packed(qkv, rotary)
+            pk4 = qkv.view(T, g, r + 2, d)
+            q = pk4[:, :, :r].reshape(T, g * r, d)
+            k = pk4[:, :, r]
+            v = pk4[:, :, r + 1]
+        else:
+            pk4 = qkv.view(T, g, r + 2, d)
+            q = self.q_layernorm(pk4[:, :, :r].reshape(T, g * r, d))
+            k = self.k_layernorm(pk4[:, :, r].contiguous())
+            v = pk4[:, :, r + 1]
+            if rotary is not None:
+                q = self._rope(q, rotary)
+                k = self._rope(k, rotary)
+        o = core_attention(q, k, v, causal=cfg.causal, scale=self.scale, cu_seqlens=cu, cfg=cfg)
+        return self.linear_proj(o.reshape(T, g * r * d), residual)
+
+    def _rope_kw(self, rotary):
+        cfg = self.cfg
+        return dict(pos_ids=rotary.pos_ids, rot_dim=self.rot_dim, interleaved=cfg.rotary_interleaved,
+                    mscale=rotary.mscale)
+
+    def _rope(self, t, rotary):
+        if rotary.freqs.dim() == 3:  # M-RoPE: per-token angles already mixed from the t/h/w streams
+            return OF.rope(t, rotary.freqs[:, 0], rot_dim=self.rot_dim, interleaved=False, mscale=rotary.mscale)
+        return OF.rope(t, rotary.freqs, **self._rope_kw(rotary))
+
+    def _rope_packed(self, pk, rotary):
+        f = rotary.freqs[:, 0] if rotary.freqs.dim() == 3 else rotary.freqs
+        kw = self._rope_kw(rotary)
+        if rotary.freqs.dim() == 3:
+            kw.update(pos_ids=None, interleaved=False)
+        return OF.rope(pk, f, group=self.r + 2, rope_in_group=self.r + 1, inplace=True, head_dim=self.d, **kw)
+
+
+def core_attention(q, k, v, *, causal, scale, cu_seqlens, cfg: Optional[TransformerConfig] = None):
+    """Attention over packed tokens; context parallelism is applied here when enabled."""
+    st = ps.get_state()
+    if st.dims.cp > 1:
+        from ..parallel import context_parallel as CP
+        return CP.ring_attention(q, k, v, causal=causal, scale=scale, cu_seqlens=cu_seqlens)
+    return OF.attention(q, k, v, causal=causal, scale=scale, cu_seqlens=cu_seqlens)
+
+
+class TransformerLayer(nn.Module):
+    """Pre-norm decoder layer: x + Attn(LN(x)), then x + MLP(LN(x)). The residual adds are
+    folded into the output-projection / FC2 epilogues."""
+
+    def __init__(self, cfg: TransformerConfig, layer_number: int, *, device=None, parallel_state=None):
+        super().__init__()
+        self.cfg = cfg
+        self.layer_number = layer_number  # 0-based global index
+        key = f"decoder.layers.{layer_number}"
+        self.is_moe = cfg.is_moe_layer(layer_number)
+        if cfg.multi_latent_attention:
+            from .mla import MLASelfAttention
+            self.input_layernorm = Norm(cfg.hidden_size, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
+            self.self_attention = MLASelfAttention(cfg, key + ".self_attention", layer_number, device=device,
+                                                   parallel_state=parallel_state)
+        else:
+            self.input_layernorm = None
+            self.self_attention = SelfAttention(cfg, key + ".self_attention", device=device,
+                                                parallel_state=parallel_state)
+        if self.is_moe:
+            from .moe import MoELayer
+            self.pre_mlp_layernorm = Norm(cfg.hidden_size, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
+            self.mlp = MoELayer(cfg, key + ".mlp", layer_number, device=device, parallel_state=parallel_state)
+        elif cfg.multi_latent_attention:
+            self.pre_mlp_layernorm = Norm(cfg.hidden_size, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
+            self.mlp = MLP(cfg, key + ".mlp", fused_norm=False, device=device, parallel_state=parallel_state)
+        else:
+            self.pre_mlp_layernorm = None
+            self.mlp = MLP(cfg, key + ".mlp", device=device, parallel_state=parallel_state)
+
+    def forward(self, x, rotary=None, packed=None):
+        h = self.input_layernorm(x) if self.input_layernorm is not None else x
+        x = self.self_attention(h, rotary, packed, residual=x)
+        h = self.pre_mlp_layernorm(x) if self.pre_mlp_layernorm is not None else x
+        if self.is_moe:
+            return x + self.mlp(h)
+        return self.mlp(h, residual=x)
+
+
+class TransformerBlock(nn.Module):
+    """The layers owned by this pipeline stage (+ final norm on the last stage), with
+    full / uniform / block activation recomputation
+    (loongforge/models/foundation/language_transformer_block.py:230-245,449-503)."""
+
+    def __init__(self, cfg: TransformerConfig, layer_numbers, *, post_process: bool = True, device=None,
+                 parallel_state=None):
+        super().__init__()
+        self.cfg = cfg
+        self.layers = nn.ModuleList([TransformerLayer(cfg, n, device=device, parallel_state=parallel_state)
+                                     for n in layer_numbers])
+        self.layer_numbers = list(layer_numbers)
+        self.final_layernorm = Norm(cfg.hidden_size, cfg, device=device,
+                                    sequence_parallel=cfg.sequence_parallel) if post_process else None
+        self.deepstack_hook = None  # callable(layer_idx, hidden) -> hidden, used by Qwen3-VL
+
+    def _run(self, layer, x, rotary, packed):
+        return layer(x, rotary, packed)
+
+    def forward(self, x, rotary=None, packed=None):
+        cfg = self.cfg
+        n = len(self.layers)
+        rec = cfg.recompute_granularity == "full" and torch.is_grad_enabled()
+        rec_n = cfg.recompute_num_layers if cfg.recompute_num_layers is not None else n
+        method = cfg.recompute_method or "block"
+        for i, layer in enumerate(self.layers):
+            do_rec = rec and ((method == "block" and i < rec_n) or method == "uniform")
+            if do_rec:
+                x = torch.utils.checkpoint.checkpoint(self._run, layer, x, rotary, packed, use_reentrant=False)
+            else:
+                x = layer(x, rotary, packed)
+            if self.deepstack_hook is not None:
+                x = self.deepstack_hook(self.layer_numbers[i], x)
+        if self.final_layernorm is not None:
+            x = self.final_layernorm(x)
+        return x

@@ -1,0 +1,407 @@
+// Torch bindings of the sm_100a kernels. Every function runs on the current CUDA
+// stream, checks shapes/dtypes/alignment on the host, and counts the kernels it
+// launches (`launch_count`) so that benchmarks can report how many of this
+// library's kernels ran inside a timed region.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cstdint>
+#include "elementwise.h"
+#include "gemm_sm100.h"
+#ifdef LF_HAVE_ATTN
+#include "attention_sm100.h"
+#endif
+#ifdef LF_HAVE_PEER
+#include "peer_gemm.h"
+#endif
+
+namespace {
+
+int64_t g_launches = 0;
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check_bf16_cuda(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bf16");
+}
+
+// D = op(A) * op(B) [+ bias] [+ residual]; see gemm_sm100.h for operand layouts.
+at::Tensor gemm(const at::Tensor& A, const at::Tensor& B, c10::optional<at::Tensor> D_, bool a_mn_major,
+                bool b_mn_major, int64_t out_mode, c10::optional<at::Tensor> bias,
+                c10::optional<at::Tensor> residual, double alpha, const at::Tensor& status, int64_t max_ctas) {
+  check_bf16_cuda(A, "A");
+  check_bf16_cuda(B, "B");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2, "gemm operands must be 2-D");
+  TORCH_CHECK(A.stride(1) == 1 && B.stride(1) == 1, "gemm operands must be row-major (unit inner stride)");
+  c10::cuda::CUDAGuard guard(A.device());
+  const int64_t M = a_mn_major ? A.size(1) : A.size(0);
+  const int64_t K = a_mn_major ? A.size(0) : A.size(1);
+  const int64_t N = b_mn_major ? B.size(1) : B.size(0);
+  const int64_t Kb = b_mn_major ? B.size(0) : B.size(1);
+  TORCH_CHECK(K == Kb, "gemm contraction mismatch: ", K, " vs ", Kb);
+  at::Tensor D;
+  if (D_.has_value()) {
+    D = *D_;
+    TORCH_CHECK(D.dim() == 2 && D.size(0) == M && D.size(1) == N && D.stride(1) == 1, "bad output shape");
+    TORCH_CHECK(D.scalar_type() == (out_mode == 0 ? at::kBFloat16 : at::kFloat), "bad output dtype");
+  } else {
+    TORCH_CHECK(out_mode != 2, "accumulate mode needs an output tensor");
+    D = at::empty({M, N}, A.options().dtype(out_mode == 0 ? at::kBFloat16 : at::kFloat));
+  }
+  lf::GemmArgs g;
+  g.A = A.data_ptr();
+  g.B = B.data_ptr();
+  g.D = D.data_ptr();
+  g.lda = A.stride(0);
+  g.ldb = B.stride(0);
+  g.ldd = D.stride(0);
+  g.M = static_cast<int>(M);
+  g.N = static_cast<int>(N);
+  g.K = static_cast<int>(K);
+  g.a_mn_major = a_mn_major;
+  g.b_mn_major = b_mn_major;
+  g.out_mode = static_cast<int>(out_mode);
+  if (bias.has_value()) {
+    check_bf16_cuda(*bias, "bias");
+    TORCH_CHECK(bias->numel() == N && bias->is_contiguous(), "bad bias");
+    g.bias = bias->data_ptr();
+  }
+  if (residual.has_value()) {
+    check_bf16_cuda(*residual, "residual");
+    TORCH_CHECK(out_mode == 0 && residual->dim() == 2 && residual->size(0) == M && residual->size(1) == N &&
+                    residual->stride(1) == 1,
+                "bad residual");
+    g.residual = residual->data_ptr();
+    g.ldr = residual->stride(0);
+  }
+  g.alpha = static_cast<float>(alpha);
+  g.status = status.data_ptr<int>();
+  g.max_ctas = static_cast<int>(max_ctas);
+  const int rc = lf::gemm_bf16(g, cur_stream());
+  TORCH_CHECK(rc == 0, "lf::gemm_bf16 failed with code ", rc, " (M=", M, " N=", N, " K=", K,
+              "); leading dimensions must be multiples of 8 and bases 16-byte aligned");
+  ++g_launches;
+  return D;
+}
+
+std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, double eps, double w_offset) {
+  check_bf16_cuda(x, "x");
+  check_bf16_cuda(w, "w");
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous());
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t H = x.size(-1);
+  TORCH_CHECK(H % 8 == 0 && w.numel() == H, "rmsnorm: H must be a multiple of 8");
+  const int64_t T = x.numel() / H;
+  at::Tensor y = at::empty_like(x);
+  at::Tensor rstd = at::empty({T}, x.options().dtype(at::kFloat));
+  lf::rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), T, static_cast<int>(H), H, H,
+                  static_cast<float>(eps), static_cast<float>(w_offset), cur_stream());
+  ++g_launches;
+  return {y, rstd};
+}
+
+std::vector<at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w,
+                                    const at::Tensor& rstd, c10::optional<at::Tensor> dres, double w_offset) {
+  check_bf16_cuda(dy, "dy");
+  check_bf16_cuda(x, "x");
+  TORCH_CHECK(dy.is_contiguous() && x.is_contiguous() && w.is_contiguous());
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t H = x.size(-1);
+  TORCH_CHECK(H % 8 == 0 && H <= 8192, "rmsnorm_bwd: H must be a multiple of 8 and <= 8192");
+  const int64_t T = x.numel() / H;
+  at::Tensor dx = at::empty_like(x);
+  const int grid = lf::rmsnorm_bwd_grid(T);
+  at::Tensor partial = at::empty({grid, H}, x.options().dtype(at::kFloat));
+  at::Tensor dw = at::empty({H}, x.options().dtype(at::kFloat));
+  const void* dres_p = nullptr;
+  if (dres.has_value()) {
+    check_bf16_cuda(*dres, "dres");
+    TORCH_CHECK(dres->is_contiguous() && dres->numel() == x.numel());
+    dres_p = dres->data_ptr();
+  }
+  lf::rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dres_p, dx.data_ptr(),
+                  partial.data_ptr<float>(), dw.data_ptr<float>(), nullptr, 0, T, static_cast<int>(H),
+                  static_cast<float>(w_offset), cur_stream());
+  g_launches += 2;
+  return {dx, dw};
+}
+
+// In-place rotary embedding on a [T, heads, D] view (strides in elements).
+void rope_(at::Tensor x, const at::Tensor& freqs, c10::optional<at::Tensor> pos_ids, int64_t T, int64_t heads,
+           int64_t D, int64_t rot_dim, int64_t rot_offset, int64_t t_stride, int64_t h_stride, int64_t group,
+           int64_t rope_in_group, bool interleaved, double mscale, double sign) {
+  check_bf16_cuda(x, "x");
+  TORCH_CHECK(freqs.is_cuda() && freqs.scalar_type() == at::kFloat && freqs.is_contiguous());
+  TORCH_CHECK(freqs.size(-1) == rot_dim / 2, "freqs last dim must be rot_dim/2");
+  TORCH_CHECK(rot_offset + rot_dim <= D);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int* pid = nullptr;
+  if (pos_ids.has_value()) {
+    TORCH_CHECK(pos_ids->scalar_type() == at::kInt && pos_ids->is_contiguous() && pos_ids->numel() == T);
+    pid = pos_ids->data_ptr<int>();
+  } else {
+    TORCH_CHECK(freqs.numel() / (rot_dim / 2) >= T, "freqs has fewer rows than tokens");
+  }
+  lf::rope_inplace(x.data_ptr(), freqs.data_ptr<float>(), pid, static_cast<int>(T), static_cast<int>(heads),
+                   static_cast<int>(D), static_cast<int>(rot_dim), static_cast<int>(rot_offset), t_stride, h_stride,
+                   static_cast<int>(group), static_cast<int>(rope_in_group), interleaved ? 1 : 0,
+                   static_cast<float>(mscale), static_cast<float>(sign), cur_stream());
+  ++g_launches;
+}
+
+at::Tensor swiglu_fwd(const at::Tensor& in) {
+  check_bf16_cuda(in, "in");
+  TORCH_CHECK(in.is_contiguous());
+  c10::cuda::CUDAGuard guard(in.device());
+  const int64_t F2 = in.size(-1);
+  TORCH_CHECK(F2 % 16 == 0, "swiglu: 2F must be a multiple of 16");
+  const int64_t F = F2 / 2;
+  const int64_t T = in.numel() / F2;
+  auto sizes = in.sizes().vec();
+  sizes.back() = F;
+  at::Tensor out = at::empty(sizes, in.options());
+  lf::swiglu_fwd(in.data_ptr(), out.data_ptr(), T, static_cast<int>(F), cur_stream());
+  ++g_launches;
+  return out;
+}
+
+at::Tensor swiglu_bwd(const at::Tensor& dout, const at::Tensor& in) {
+  check_bf16_cuda(dout, "dout");
+  check_bf16_cuda(in, "in");
+  TORCH_CHECK(in.is_contiguous() && dout.is_contiguous());
+  c10::cuda::CUDAGuard guard(in.device());
+  const int64_t F2 = in.size(-1);
+  const int64_t F = F2 / 2;
+  const int64_t T = in.numel() / F2;
+  TORCH_CHECK(dout.numel() == T * F);
+  at::Tensor din = at::empty_like(in);
+  lf::swiglu_bwd(dout.data_ptr(), in.data_ptr(), din.data_ptr(), T, static_cast<int>(F), cur_stream());
+  ++g_launches;
+  return din;
+}
+
+std::vector<at::Tensor> ce_stats(const at::Tensor& logits, const at::Tensor& labels, int64_t vocab_start,
+                                 int64_t valid_v) {
+  check_bf16_cuda(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && logits.size(1) % 8 == 0 && logits.stride(0) % 8 == 0);
+  TORCH_CHECK(labels.scalar_type() == at::kLong && labels.is_contiguous() && labels.numel() == logits.size(0));
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t T = logits.size(0);
+  auto fo = logits.options().dtype(at::kFloat);
+  at::Tensor mx = at::empty({T}, fo), sm = at::empty({T}, fo), tg = at::empty({T}, fo);
+  lf::ce_stats(logits.data_ptr(), labels.data_ptr<int64_t>() ? reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()) : nullptr,
+               mx.data_ptr<float>(), sm.data_ptr<float>(), tg.data_ptr<float>(), T, static_cast<int>(logits.size(1)),
+               logits.stride(0), static_cast<int>(vocab_start), static_cast<int>(valid_v), cur_stream());
+  ++g_launches;
+  return {mx, sm, tg};
+}
+
+void ce_dlogits_(at::Tensor logits, const at::Tensor& labels, const at::Tensor& gmax, const at::Tensor& gsum,
+                 const at::Tensor& row_scale, int64_t vocab_start, int64_t valid_v) {
+  check_bf16_cuda(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && logits.size(1) % 8 == 0 && logits.stride(0) % 8 == 0);
+  TORCH_CHECK(gmax.scalar_type() == at::kFloat && gsum.scalar_type() == at::kFloat &&
+              row_scale.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t T = logits.size(0);
+  lf::ce_dlogits(logits.data_ptr(), reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()),
+                 gmax.data_ptr<float>(), gsum.data_ptr<float>(), row_scale.data_ptr<float>(), T,
+                 static_cast<int>(logits.size(1)), logits.stride(0), static_cast<int>(vocab_start),
+                 static_cast<int>(valid_v), cur_stream());
+  ++g_launches;
+}
+
+void adam_step_(at::Tensor master, const at::Tensor& grad, at::Tensor m, at::Tensor v,
+                c10::optional<at::Tensor> model_out, double lr, double beta1, double beta2, double eps, double wd,
+                int64_t step, double grad_scale) {
+  TORCH_CHECK(master.is_cuda() && master.scalar_type() == at::kFloat && master.is_contiguous());
+  TORCH_CHECK(grad.is_contiguous() && m.is_contiguous() && v.is_contiguous());
+  const int64_t n = master.numel();
+  TORCH_CHECK(grad.numel() == n && m.numel() == n && v.numel() == n);
+  TORCH_CHECK(m.scalar_type() == v.scalar_type());
+  c10::cuda::CUDAGuard guard(master.device());
+  const bool gb = grad.scalar_type() == at::kBFloat16;
+  TORCH_CHECK(gb || grad.scalar_type() == at::kFloat);
+  const bool mb = m.scalar_type() == at::kBFloat16;
+  TORCH_CHECK(mb || m.scalar_type() == at::kFloat);
+  void* mo = nullptr;
+  if (model_out.has_value()) {
+    check_bf16_cuda(*model_out, "model_out");
+    TORCH_CHECK(model_out->is_contiguous() && model_out->numel() == n);
+    mo = model_out->data_ptr();
+  }
+  const float bc1 = 1.f - static_cast<float>(std::pow(beta1, static_cast<double>(step)));
+  const float bc2 = 1.f - static_cast<float>(std::pow(beta2, static_cast<double>(step)));
+  lf::adam_step(master.data_ptr<float>(), grad.data_ptr(), gb, m.data_ptr(), v.data_ptr(), mb, mo, n,
+                static_cast<float>(lr), static_cast<float>(beta1), static_cast<float>(beta2),
+                static_cast<float>(eps), static_cast<float>(wd), bc1, bc2, static_cast<float>(grad_scale),
+                cur_stream());
+  ++g_launches;
+}
+
+void sumsq_(const at::Tensor& x, at::Tensor out) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && out.scalar_type() == at::kFloat && out.numel() == 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  const bool b = x.scalar_type() == at::kBFloat16;
+  TORCH_CHECK(b || x.scalar_type() == at::kFloat);
+  lf::sumsq(x.data_ptr(), b, x.numel(), out.data_ptr<float>(), cur_stream());
+  ++g_launches;
+}
+
+#ifdef LF_HAVE_ATTN
+// ------------------------------------------------------------------ attention
+std::vector<at::Tensor> attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                 c10::optional<at::Tensor> cu_seqlens, double scale, bool causal,
+                                 const at::Tensor& status) {
+  // q [T, Hq, D], k/v [T, Hkv, D]; last dim contiguous, arbitrary token/head strides.
+  check_bf16_cuda(q, "q");
+  check_bf16_cuda(k, "k");
+  check_bf16_cuda(v, "v");
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3);
+  TORCH_CHECK(q.stride(2) == 1 && k.stride(2) == 1 && v.stride(2) == 1);
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t T = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1);
+  at::Tensor o = at::empty({T, Hq, D}, q.options());
+  at::Tensor lse = at::empty({Hq, T}, q.options().dtype(at::kFloat));
+  lf::AttnArgs a;
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.o = o.data_ptr();
+  a.lse = lse.data_ptr<float>();
+  a.T = static_cast<int>(T); a.Hq = static_cast<int>(Hq); a.Hkv = static_cast<int>(Hkv); a.D = static_cast<int>(D);
+  a.q_ts = q.stride(0); a.q_hs = q.stride(1);
+  a.k_ts = k.stride(0); a.k_hs = k.stride(1);
+  a.v_ts = v.stride(0); a.v_hs = v.stride(1);
+  a.o_ts = o.stride(0); a.o_hs = o.stride(1);
+  a.scale = static_cast<float>(scale);
+  a.causal = causal;
+  a.status = status.data_ptr<int>();
+  if (cu_seqlens.has_value()) {
+    TORCH_CHECK(cu_seqlens->scalar_type() == at::kInt && cu_seqlens->is_contiguous());
+    a.cu_seqlens = cu_seqlens->data_ptr<int>();
+    a.num_seqs = static_cast<int>(cu_seqlens->numel() - 1);
+  }
+  const int rc = lf::attn_fwd(a, cur_stream());
+  TORCH_CHECK(rc == 0, "lf::attn_fwd failed with code ", rc);
+  ++g_launches;
+  return {o, lse};
+}
+
+std::vector<at::Tensor> attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k,
+                                 const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
+                                 c10::optional<at::Tensor> cu_seqlens, double scale, bool causal,
+                                 const at::Tensor& status) {
+  check_bf16_cuda(dout, "dout");
+  TORCH_CHECK(dout.stride(2) == 1 && o.stride(2) == 1);
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t T = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1);
+  at::Tensor dq = at::empty({T, Hq, D}, q.options());
+  at::Tensor dk = at::empty({T, Hkv, D}, q.options());
+  at::Tensor dv = at::empty({T, Hkv, D}, q.options());
+  at::Tensor delta = at::empty({Hq, T}, q.options().dtype(at::kFloat));
+  lf::AttnArgs a;
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.o = const_cast<void*>(o.data_ptr());
+  a.lse = const_cast<float*>(lse.data_ptr<float>());
+  a.dout = dout.data_ptr(); a.dq = dq.data_ptr(); a.dk = dk.data_ptr(); a.dv = dv.data_ptr();
+  a.delta = delta.data_ptr<float>();
+  a.T = static_cast<int>(T); a.Hq = static_cast<int>(Hq); a.Hkv = static_cast<int>(Hkv); a.D = static_cast<int>(D);
+  a.q_ts = q.stride(0); a.q_hs = q.stride(1);
+  a.k_ts = k.stride(0); a.k_hs = k.stride(1);
+  a.v_ts = v.stride(0); a.v_hs = v.stride(1);
+  a.o_ts = o.stride(0); a.o_hs = o.stride(1);
+  a.do_ts = dout.stride(0); a.do_hs = dout.stride(1);
+  a.scale = static_cast<float>(scale);
+  a.causal = causal;
+  a.status = status.data_ptr<int>();
+  if (cu_seqlens.has_value()) {
+    a.cu_seqlens = cu_seqlens->data_ptr<int>();
+    a.num_seqs = static_cast<int>(cu_seqlens->numel() - 1);
+  }
+  const int rc = lf::attn_bwd(a, cur_stream());
+  TORCH_CHECK(rc == 0, "lf::attn_bwd failed with code ", rc);
+  g_launches += 3;
+  return {dq, dk, dv};
+}
+
+#endif  // LF_HAVE_ATTN
+
+#ifdef LF_HAVE_PEER
+// ------------------------------------------------------------------ fused TP GEMMs over peer memory
+at::Tensor ag_gemm(const at::Tensor& x_local, const at::Tensor& peer_ptrs, int64_t rank, int64_t world,
+                   const at::Tensor& W, const at::Tensor& x_full, const at::Tensor& flags_ptrs, int64_t epoch,
+                   c10::optional<at::Tensor> bias, const at::Tensor& status) {
+  c10::cuda::CUDAGuard guard(W.device());
+  lf::AgGemmArgs a;
+  a.peer_x = reinterpret_cast<const void* const*>(peer_ptrs.data_ptr<int64_t>());
+  a.peer_flags = reinterpret_cast<int* const*>(flags_ptrs.data_ptr<int64_t>());
+  a.rank = static_cast<int>(rank);
+  a.world = static_cast<int>(world);
+  a.rows_per_rank = static_cast<int>(x_local.size(0));
+  a.K = static_cast<int>(x_local.size(1));
+  a.N = static_cast<int>(W.size(0));
+  a.W = W.data_ptr();
+  a.x_full = x_full.data_ptr();
+  a.epoch = static_cast<int>(epoch);
+  a.bias = bias.has_value() ? bias->data_ptr() : nullptr;
+  a.status = status.data_ptr<int>();
+  at::Tensor out = at::empty({x_local.size(0) * world, W.size(0)}, W.options());
+  a.out = out.data_ptr();
+  const int rc = lf::ag_gemm(a, cur_stream());
+  TORCH_CHECK(rc == 0, "lf::ag_gemm failed with code ", rc);
+  g_launches += 2;
+  return out;
+}
+
+at::Tensor gemm_rs(const at::Tensor& x, const at::Tensor& W, const at::Tensor& partial_ptrs,
+                   const at::Tensor& flags_ptrs, int64_t rank, int64_t world, int64_t epoch,
+                   c10::optional<at::Tensor> residual, const at::Tensor& status) {
+  c10::cuda::CUDAGuard guard(W.device());
+  lf::GemmRsArgs a;
+  a.x = x.data_ptr();
+  a.W = W.data_ptr();
+  a.M = static_cast<int>(x.size(0));
+  a.K = static_cast<int>(x.size(1));
+  a.N = static_cast<int>(W.size(0));
+  a.peer_partial = reinterpret_cast<void* const*>(partial_ptrs.data_ptr<int64_t>());
+  a.peer_flags = reinterpret_cast<int* const*>(flags_ptrs.data_ptr<int64_t>());
+  a.rank = static_cast<int>(rank);
+  a.world = static_cast<int>(world);
+  a.epoch = static_cast<int>(epoch);
+  a.residual = residual.has_value() ? residual->data_ptr() : nullptr;
+  a.status = status.data_ptr<int>();
+  at::Tensor out = at::empty({x.size(0) / world, W.size(0)}, W.options());
+  a.out = out.data_ptr();
+  const int rc = lf::gemm_rs(a, cur_stream());
+  TORCH_CHECK(rc == 0, "lf::gemm_rs failed with code ", rc);
+  g_launches += 2;
+  return out;
+}
+
+#endif  // LF_HAVE_PEER
+
+int64_t launch_count() { return g_launches; }
+void reset_launch_count() { g_launches = 0; }
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rope_", &rope_);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("ce_stats", &ce_stats);
+  m.def("ce_dlogits_", &ce_dlogits_);
+  m.def("adam_step_", &adam_step_);
+  m.def("sumsq_", &sumsq_);
+#ifdef LF_HAVE_ATTN
+  m.def("attn_fwd", &attn_fwd);
+  m.def("attn_bwd", &attn_bwd);
+#endif
+#ifdef LF_HAVE_PEER
+  m.def("ag_gemm", &ag_gemm);
+  m.def("gemm_rs", &gemm_rs);
+#endif
+  m.def("launch_count", &launch_count);
+  m.def("reset_launch_count", &reset_launch_count);
+}

@@ -1,0 +1,28 @@
+// Host launchers of the bandwidth-bound kernels in elementwise.cu (raw pointers + stream).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace lf {
+
+void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long T, int H, long long x_stride,
+                 long long y_stride, float eps, float w_offset, cudaStream_t s);
+// Number of CTAs (= rows of the fp32 `dw_partial[grid, H]` scratch) the backward uses for T rows.
+int rmsnorm_bwd_grid(long long T);
+void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                 float* dw_partial, float* dw_f32, void* dw_bf16, int accumulate, long long T, int H, float w_offset,
+                 cudaStream_t s);
+void rope_inplace(void* x, const float* freqs, const int* pos_ids, int T, int heads, int D, int rot_dim,
+                  int rot_offset, long long t_stride, long long h_stride, int group, int rope_in_group,
+                  int interleaved, float mscale, float sign, cudaStream_t s);
+void swiglu_fwd(const void* in, void* out, long long T, int F, cudaStream_t s);
+void swiglu_bwd(const void* dout, const void* in, void* din, long long T, int F, cudaStream_t s);
+void ce_stats(const void* logits, const long long* labels, float* row_max, float* row_sum, float* tgt, long long T,
+              int V, long long ld, int vocab_start, int valid_v, cudaStream_t s);
+void ce_dlogits(void* logits, const long long* labels, const float* gmax, const float* gsum, const float* row_scale,
+                long long T, int V, long long ld, int vocab_start, int valid_v, cudaStream_t s);
+void adam_step(float* master, const void* grad, int grad_is_bf16, void* m, void* v, int moments_bf16,
+               void* model_out, long long n, float lr, float beta1, float beta2, float eps, float wd, float bc1,
+               float bc2, float grad_scale, cudaStream_t s);
+void sumsq(const void* x, int is_bf16, long long n, float* out, cudaStream_t s);
+
+}  // namespace lf

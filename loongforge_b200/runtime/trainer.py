@@ -1,0 +1,323 @@
+"""Training runtime: model/optimizer set-up, the train step, the logging line and the loop.
+
+Counterpart of the reference's ``pretrain()`` / ``setup_model_and_optimizer()`` / ``train_step()``
+/ ``training_log()`` (loongforge/train/training_utils.py:345,1030,1471,2001,2431). The public
+entry points are ``Trainer`` (programmatic) and ``loongforge_b200.train`` (CLI).
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+import os
+import time
+from typing import Callable, Dict, Iterator, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..models.config import TransformerConfig
+from ..models.gpt import GPTModel, pipeline_layer_split
+from ..models.transformer import PackedSeqParams
+from ..optim.lr_scheduler import OptimizerParamScheduler
+from ..parallel import state as ps
+from ..parallel.ddp import DDPConfig, DistributedDataParallel
+from ..parallel.dist_optimizer import DistributedOptimizer, OptimizerConfig
+from ..parallel.state import ParallelDims
+from . import schedules
+from .microbatches import MicrobatchCalculator
+from .timers import Timers
+
+
+@dataclasses.dataclass
+class TrainConfig:
+    micro_batch_size: int = 1
+    global_batch_size: int = 8
+    seq_length: int = 128
+    train_iters: int = 20
+    lr: float = 1e-4
+    min_lr: float = 0.0
+    lr_decay_style: str = "constant"
+    lr_warmup_iters: int = 0
+    lr_decay_iters: Optional[int] = None
+    weight_decay: float = 0.0
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.999
+    adam_eps: float = 1e-8
+    clip_grad: float = 1.0
+    bf16: bool = False
+    seed: int = 1234
+    log_interval: int = 1
+    save: Optional[str] = None
+    load: Optional[str] = None
+    save_interval: Optional[int] = None
+    ckpt_format: str = "torch_dist"
+    use_distributed_optimizer: bool = True
+    overlap_grad_reduce: bool = True
+    overlap_param_gather: bool = False
+    grad_reduce_in_fp32: bool = True
+    exp_avg_dtype: torch.dtype = torch.float32
+    exp_avg_sq_dtype: torch.dtype = torch.float32
+    ddp_bucket_size: Optional[int] = None
+    calculate_per_token_loss: bool = False
+    custom_pipeline_layers: Optional[List[int]] = None
+    training_phase: str = "pretrain"
+    log_throughput: bool = True
+    check_for_nan_in_loss: bool = True
+    exit_on_nan: bool = False
+
+
+def _device_for_rank() -> torch.device:
+    if torch.cuda.is_available():
+        local = int(os.environ.get("LOCAL_RANK", 0))
+        torch.cuda.set_device(local)
+        return torch.device("cuda", local)
+    return torch.device("cpu")
+
+
+def init_distributed(backend: Optional[str] = None, timeout_s: int = 1800) -> torch.device:
+    """torchrun-style rendezvous (RANK / WORLD_SIZE / MASTER_*); also accepts OpenMPI variables
+    as the reference does (loongforge/train/parser.py:101-106)."""
+    dev = _device_for_rank()
+    if "RANK" not in os.environ and "OMPI_COMM_WORLD_RANK" in os.environ:
+        os.environ["RANK"] = os.environ["OMPI_COMM_WORLD_RANK"]
+        os.environ["WORLD_SIZE"] = os.environ["OMPI_COMM_WORLD_SIZE"]
+        os.environ.setdefault("LOCAL_RANK", os.environ.get("OMPI_COMM_WORLD_LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1 and not dist.is_initialized():
+        import datetime
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        be = backend or ("nccl" if dev.type == "cuda" else "gloo")
+        kw = {}
+        if be == "nccl":
+            kw["device_id"] = dev
+        dist.init_process_group(be, timeout=datetime.timedelta(seconds=timeout_s), **kw)
+    return dev
+
+
+class Trainer:
+    """Owns model chunks, DDP wrappers, optimizer, scheduler and the step function."""
+
+    def __init__(self, model_cfg: TransformerConfig, train_cfg: TrainConfig, dims: Optional[ParallelDims] = None,
+                 *, device: Optional[torch.device] = None, model_provider: Optional[Callable] = None,
+                 forward_step: Optional[Callable] = None):
+        self.mcfg, self.tcfg = model_cfg, train_cfg
+        self.device = device or _device_for_rank()
+        dims = dims or ParallelDims()
+        if not ps.model_parallel_is_initialized():
+            ps.initialize_model_parallel(dims, gloo_groups=False)
+        self.st = ps.get_state()
+        self.world = self.st.world_size
+        self.dp = self.st.dp_size
+        self.timers = Timers()
+        if train_cfg.bf16:
+            model_cfg.params_dtype = torch.bfloat16
+        torch.manual_seed(train_cfg.seed + 100 * self.st.pp_rank + 2718 * self.st.tp_rank)
+        from ..parallel.layers import set_init_seed
+        set_init_seed(train_cfg.seed)
+        self.mb_calc = MicrobatchCalculator(train_cfg.global_batch_size, train_cfg.micro_batch_size, self.dp)
+        self.model_provider = model_provider or self._default_model_provider
+        self.forward_step = forward_step or self._default_forward_step
+        self.models = self._build_models()
+        self.optimizer = self._build_optimizer()
+        self.scheduler = OptimizerParamScheduler(
+            self.optimizer, max_lr=train_cfg.lr, min_lr=train_cfg.min_lr, warmup_steps=train_cfg.lr_warmup_iters,
+            decay_steps=train_cfg.lr_decay_iters or train_cfg.train_iters, decay_style=train_cfg.lr_decay_style)
+        self.iteration = 0
+        self.consumed_samples = 0
+        self.num_flops_so_far = 0.0
+        self._skipped = 0
+        self._nan = 0
+
+    # ------------------------------------------------------------------ construction
+    def _default_model_provider(self, pre_process, post_process, layer_numbers):
+        return GPTModel(self.mcfg, pre_process=pre_process, post_process=post_process, layer_numbers=layer_numbers,
+                        device=self.device)
+
+    def _build_models(self) -> List[DistributedDataParallel]:
+        st = self.st
+        pp, vpp = st.dims.pp, st.dims.vpp or 1
+        splits = pipeline_layer_split(self.mcfg.num_layers, pp * vpp, self.tcfg.custom_pipeline_layers)
+        chunks = []
+        for v in range(vpp):
+            virt = v * pp + st.pp_rank
+            module = self.model_provider(virt == 0, virt == pp * vpp - 1, splits[virt])
+            ddp_cfg = DDPConfig(grad_reduce_in_fp32=self.tcfg.grad_reduce_in_fp32,
+                                overlap_grad_reduce=self.tcfg.overlap_grad_reduce,
+                                use_distributed_optimizer=self.tcfg.use_distributed_optimizer,
+                                bucket_size=self.tcfg.ddp_bucket_size or max(40_000_000, 1_000_000 * self.dp))
+            # bucketing only helps the chunk whose backward runs last (reference: training_utils.py:987-988)
+            chunks.append(DistributedDataParallel(module, ddp_cfg, disable_bucketing=v > 0))
+        for c in chunks:
+            c.broadcast_params()
+        return chunks
+
+    def _build_optimizer(self) -> DistributedOptimizer:
+        t = self.tcfg
+        ocfg = OptimizerConfig(lr=t.lr, min_lr=t.min_lr, weight_decay=t.weight_decay, adam_beta1=t.adam_beta1,
+                               adam_beta2=t.adam_beta2, adam_eps=t.adam_eps, clip_grad=t.clip_grad,
+                               exp_avg_dtype=t.exp_avg_dtype, exp_avg_sq_dtype=t.exp_avg_sq_dtype,
+                               overlap_param_gather=t.overlap_param_gather)
+        return DistributedOptimizer(self.models, ocfg)
+
+    # ------------------------------------------------------------------ default LLM pretrain step
+    def get_batch(self, data_iterator) -> Dict[str, torch.Tensor]:
+        """Pull one micro-batch, move it to the device (H2D from pinned memory) and flatten to the
+        packed-token layout. On pipeline-middle stages only position ids are needed."""
+        batch = next(data_iterator)
+        out = {}
+        for k, v in batch.items():
+            out[k] = v.to(self.device, non_blocking=True) if isinstance(v, torch.Tensor) else v
+        return out
+
+    def _default_forward_step(self, data_iterator, model):
+        t = self.tcfg
+        b = self.get_batch(data_iterator)
+        tokens = b["tokens"].reshape(-1)
+        labels = b["labels"].reshape(-1)
+        mask = b["loss_mask"].reshape(-1)
+        pos = b["position_ids"].reshape(-1)
+        bs = b["tokens"].shape[0]
+        packed = None
+        if bs > 1 or "cu_seqlens" in b:
+            cu = b.get("cu_seqlens")
+            if cu is None:
+                cu = torch.arange(0, (bs + 1) * t.seq_length, t.seq_length, dtype=torch.int32, device=self.device)
+            packed = PackedSeqParams(cu_seqlens=cu, max_seqlen=t.seq_length)
+        n_valid = b.get("num_valid_tokens")
+        if n_valid is None:
+            n_valid = int(mask.numel())
+        nmb = self.mb_calc.num_microbatches
+        scale = 1.0 / (max(n_valid, 1) * nmb)
+        out = model(tokens, pos, labels=labels, loss_mask=mask, packed=packed, loss_scale=scale)
+
+        def loss_func(losses):
+            loss = (losses * mask.float()).sum() * scale
+            return loss, {"lm loss": loss.detach() * nmb, "num_tokens": n_valid}
+
+        return out, loss_func
+
+    # ------------------------------------------------------------------ step
+    def train_step(self, data_iterator) -> Dict[str, float]:
+        """zero grads -> forward/backward over the micro-batches -> optimizer step -> reduce metrics."""
+        t = self.tcfg
+        for m in self.models:
+            m.train()
+        self.optimizer.zero_grad()
+        fb = schedules.get_forward_backward_func()
+        T = t.seq_length * t.micro_batch_size
+        sp_div = self.st.dims.tp if self.mcfg.sequence_parallel else 1
+        reports = fb(forward_step_func=self.forward_step, data_iterator=data_iterator,
+                     model=self.models if len(self.models) > 1 else self.models[0],
+                     num_microbatches=self.mb_calc.num_microbatches,
+                     tensor_shape=(T // sp_div // self.st.dims.cp, self.mcfg.hidden_size),
+                     dtype=self.mcfg.params_dtype)
+        self._allreduce_sequence_parallel_grads()
+        ok, grad_norm, _ = self.optimizer.step()
+        if ok:
+            self.scheduler.step(1)
+            skipped = 0
+        else:
+            skipped = 1
+        self.iteration += 1
+        self.consumed_samples += t.global_batch_size
+        metrics: Dict[str, float] = {"grad_norm": grad_norm, "skipped": skipped}
+        # loss: average over micro-batches, then over the data-parallel group (last stage only)
+        if reports:
+            keys = [k for k in reports[0] if k != "num_tokens"]
+            vals = torch.stack([torch.stack([r[k].float() for r in reports]).mean() for k in keys])
+            if self.st.size("dp_cp") > 1:
+                dist.all_reduce(vals, group=self.st.group("dp_cp"))
+                vals /= self.st.size("dp_cp")
+            for k, v in zip(keys, vals.tolist()):
+                metrics[k] = v
+        return metrics
+
+    def _allreduce_sequence_parallel_grads(self):
+        """Norm weights etc. see only a sequence shard per TP rank: sum their grads over TP."""
+        st = self.st
+        if st.dims.tp == 1 or not self.mcfg.sequence_parallel:
+            return
+        grads = []
+        for m in self.models:
+            for p in m.module.parameters():
+                if getattr(p, "sequence_parallel", False) and p.requires_grad:
+                    grads.append(p.main_grad)
+        if not grads:
+            return
+        flat = torch.cat([g.reshape(-1) for g in grads])
+        dist.all_reduce(flat, group=st.group("tp"))
+        off = 0
+        for g in grads:
+            n = g.numel()
+            g.copy_(flat[off:off + n].view_as(g))
+            off += n
+
+    # ------------------------------------------------------------------ logging
+    def flops_per_step(self) -> float:
+        return self.mcfg.flops_per_token(self.tcfg.seq_length) * self.tcfg.seq_length * self.tcfg.global_batch_size
+
+    def format_log(self, metrics: Dict[str, float], elapsed_ms: float, peak_tflops: Optional[float] = None) -> str:
+        """The reference's log line (loongforge/train/training_utils.py:2278-2394), parsed by
+        tests/llm_vlm/tools/log2json.py:19-29."""
+        t = self.tcfg
+        tokens = t.seq_length * t.global_batch_size
+        tps = tokens / (elapsed_ms / 1e3) / self.world
+        s = " [%s] iteration %8d/%8d |" % (time.strftime("%Y-%m-%d %H:%M:%S"), self.iteration, t.train_iters)
+        s += " consumed samples: %12d |" % self.consumed_samples
+        s += " elapsed time per iteration (ms): %.1f |" % elapsed_ms
+        s += " throughput (token/sec/GPU): %.1f |" % tps
+        if t.log_throughput:
+            tf = self.flops_per_step() / (elapsed_ms / 1e3) / 1e12 / self.world
+            s += " flop throughput (TFLOP/sec/GPU): %.1f |" % tf
+        s += " learning rate: %.6E |" % self.optimizer.param_groups[0]["lr"]
+        s += " global batch size: %5d |" % t.global_batch_size
+        for k, v in metrics.items():
+            if k in ("grad_norm", "skipped"):
+                continue
+            s += " %s: %.6E |" % (k, v)
+        s += " loss scale: %.1f |" % 1.0
+        s += " grad norm: %.6f |" % metrics.get("grad_norm", float("nan"))
+        s += " number of skipped iterations: %3d |" % metrics.get("skipped", 0)
+        s += " number of nan iterations: %3d |" % 0
+        if self.device.type == "cuda":
+            s += " mem-allocated-bytes-avg(MB): %.1f |" % (torch.cuda.memory_allocated() / 2 ** 20)
+            s += " mem-max-allocated-bytes-avg(MB): %.1f |" % (torch.cuda.max_memory_allocated() / 2 ** 20)
+        return s
+
+    # ------------------------------------------------------------------ loop
+    def train(self, data_iterator, *, on_log: Optional[Callable[[str], None]] = None) -> List[Dict[str, float]]:
+        t = self.tcfg
+        history = []
+        is_log_rank = (not dist.is_initialized()) or dist.get_rank() == dist.get_world_size() - 1
+        while self.iteration < t.train_iters:
+            t0 = self._now()
+            metrics = self.train_step(data_iterator)
+            elapsed_ms = (self._now() - t0) * 1e3
+            self.num_flops_so_far += self.flops_per_step()
+            history.append(metrics)
+            if t.check_for_nan_in_loss and "lm loss" in metrics and not math.isfinite(metrics["lm loss"]):
+                self._nan += 1
+                if t.exit_on_nan:
+                    raise RuntimeError(f"non-finite loss at iteration {self.iteration}")
+            if self.iteration % t.log_interval == 0:
+                line = self.format_log(metrics, elapsed_ms)
+                if is_log_rank:
+                    (on_log or print)(line)
+            if t.save and t.save_interval and self.iteration % t.save_interval == 0:
+                self.save_checkpoint(t.save)
+        return history
+
+    def _now(self):
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        return time.perf_counter()
+
+    # ------------------------------------------------------------------ checkpoints
+    def save_checkpoint(self, path: str):
+        from ..ckpt import checkpointing
+        checkpointing.save_checkpoint(path, self)
+
+    def load_checkpoint(self, path: str, **kw):
+        from ..ckpt import checkpointing
+        return checkpointing.load_checkpoint(path, self, **kw)

@@ -1,0 +1,175 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ext():
+    from loongforge_b200.ops import _ext
+
+    return _ext
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (384, 136, 200), (128, 128, 64), (1000, 776, 520)])
+def test_gemm_layouts(a_mn, b_mn, M, N, K):
+    from loongforge_b200.ops import functional as OF
+
+    torch.manual_seed(0)
+    dev = "cuda"
+    A = torch.randn((K, M) if a_mn else (M, K), device=dev).bfloat16()
+    B = torch.randn((K, N) if b_mn else (N, K), device=dev).bfloat16()
+    D = OF.gemm(A, B, a_mn_major=a_mn, b_mn_major=b_mn)
+    _ext().check_status()
+    Af = A.float().t() if a_mn else A.float()
+    Bf = B.float() if b_mn else B.float().t()
+    ref = Af @ Bf
+    assert D.shape == (M, N)
+    assert _rel_err(D, ref) < 1e-2, f"rel err {_rel_err(D, ref)}"
+
+
+def test_gemm_big_and_epilogues():
+    from loongforge_b200.ops import functional as OF
+
+    torch.manual_seed(1)
+    dev = "cuda"
+    M, N, K = 2048, 1536, 4096
+    A = torch.randn(M, K, device=dev).bfloat16()
+    B = torch.randn(N, K, device=dev).bfloat16() * 0.05
+    bias = torch.randn(N, device=dev).bfloat16()
+    res = torch.randn(M, N, device=dev).bfloat16()
+    ref = A.float() @ B.float().t()
+    D = OF.gemm(A, B, bias=bias, residual=res)
+    assert _rel_err(D, ref + bias.float() + res.float()) < 1e-2
+    acc = torch.ones(M, N, device=dev, dtype=torch.float32)
+    OF.gemm(A, B, out=acc, out_mode=2)
+    assert _rel_err(acc, ref + 1.0) < 2e-3
+    D32 = OF.gemm(A, B, out_mode=1, alpha=0.5)
+    assert _rel_err(D32, 0.5 * ref) < 2e-3
+    _ext().check_status()
+
+
+def test_linear_autograd_matches_torch():
+    from loongforge_b200.ops import functional as OF
+
+    torch.manual_seed(2)
+    dev = "cuda"
+    x = torch.randn(512, 1024, device=dev).bfloat16().requires_grad_()
+    w = (torch.randn(768, 1024, device=dev) * 0.05).bfloat16().requires_grad_()
+    y = OF.linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    yr = xr @ wr.t()
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("T,H", [(64, 4096), (300, 1280), (17, 8192), (128, 128)])
+def test_rmsnorm(T, H):
+    from loongforge_b200.ops import functional as OF
+
+    torch.manual_seed(3)
+    x = torch.randn(T, H, device="cuda").bfloat16().requires_grad_()
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16().requires_grad_()
+    y = OF.rmsnorm(x, w, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_rope_packed(interleaved):
+    from loongforge_b200.ops import functional as OF
+
+    torch.manual_seed(4)
+    T, g, r, d = 96, 2, 4, 128
+    x = torch.randn(T, g * (r + 2) * d, device="cuda").bfloat16()
+    freqs = OF.rope_freqs(torch.arange(T, device="cuda"), d, 10000.0)
+    xa = x.clone().requires_grad_()
+    y = OF.rope(xa * 1.0, freqs, group=r + 2, rope_in_group=r + 1, interleaved=interleaved, head_dim=d, inplace=True)
+    grad = torch.randn_like(y)
+    y.backward(grad)
+    xc = x.cpu().float().requires_grad_()
+    yr = OF.rope(xc, freqs.cpu(), group=r + 2, rope_in_group=r + 1, interleaved=interleaved, head_dim=d)
+    yr.backward(grad.cpu().float())
+    assert _rel_err(y.cpu(), yr) < 1e-2
+    assert _rel_err(xa.grad.cpu(), xc.grad) < 1e-2
+
+
+def test_swiglu():
+    from loongforge_b200.ops import functional as OF
+
+    torch.manual_seed(5)
+    x = torch.randn(200, 2 * 1376, device="cuda").bfloat16().requires_grad_()
+    y = OF.swiglu(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    a, b = xr.chunk(2, -1)
+    yr = torch.nn.functional.silu(a) * b
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+
+
+def test_linear_cross_entropy():
+    from loongforge_b200.ops import functional as OF
+
+    torch.manual_seed(6)
+    T, H, V = 700, 512, 4096
+    h = torch.randn(T, H, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(V, H, device="cuda") * 0.05).bfloat16().requires_grad_()
+    labels = torch.randint(0, V - 100, (T,), device="cuda")
+    mask = (torch.rand(T, device="cuda") > 0.2).float()
+    losses = OF.linear_cross_entropy(h, w, labels, mask, valid_vocab=V - 100, chunk_tokens=256)
+    c = 1.0 / mask.sum()
+    (losses * mask).sum().mul(c).backward()
+    hr = h.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    logits = (hr @ wr.t())[:, : V - 100]
+    lr = torch.nn.functional.cross_entropy(logits, labels, reduction="none")
+    (lr * mask).sum().mul(c).backward()
+    assert _rel_err(losses, lr) < 2e-2
+    assert _rel_err(h.grad, hr.grad) < 3e-2
+    assert _rel_err(w.grad, wr.grad) < 3e-2
+
+
+@pytest.mark.parametrize("gdt,mdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+def test_adam(gdt, mdt):
+    from loongforge_b200.ops import functional as OF
+
+    torch.manual_seed(7)
+    n = 100_003
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda").to(gdt)
+    m = torch.zeros(n, device="cuda", dtype=mdt)
+    v = torch.zeros(n, device="cuda", dtype=mdt)
+    out = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    pr, mr, vr = p.cpu().clone(), m.cpu().clone(), v.cpu().clone()
+    for step in (1, 2):
+        OF.adam_step(p, g, m, v, out, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step,
+                     grad_scale=0.5)
+        OF.adam_step(pr, g.cpu(), mr, vr, None, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
+                     step=step, grad_scale=0.5)
+    assert _rel_err(p.cpu(), pr) < (1e-5 if mdt == torch.float32 else 1e-3)
+    assert _rel_err(out.cpu(), pr) < 1e-2
+    ss = OF.sum_of_squares(g)
+    assert abs(ss.item() - g.float().pow(2).sum().item()) / ss.item() < 1e-3
