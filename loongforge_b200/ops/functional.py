@@ -104,6 +104,8 @@ class _LinearFn(torch.autograd.Function):
         ctx.has_bias = bias is not None
         ctx.has_res = residual is not None
         ctx.in_shape = shp
+        if len(shp) == 2:
+            return y  # not a view: callers may rotate it in place (RoPE on the packed QKV)
         return y.reshape(*shp[:-1], weight.shape[0])
 
     @staticmethod
