@@ -175,6 +175,10 @@ class SelfAttention(nn.Module):
         if self.q_layernorm is None:
             if rotary is not None:
                 qkv = self._rope_packed(qkv, rotary)
+            if ps.get_state().dims.cp == 1 and OF.attention_packed_supported(qkv, d):
+                # tcgen05 attention reads q/k/v straight out of the packed GEMM output
+                o = OF.attention_packed(qkv, g, r, causal=cfg.causal, scale=self.scale, cu_seqlens=cu)
+                return self.linear_proj(o.view(T, g * r * d), residual)
             pk4 = qkv.view(T, g, r + 2, d)
             q = pk4[:, :, :r].reshape(T, g * r, d)
             k = pk4[:, :, r]

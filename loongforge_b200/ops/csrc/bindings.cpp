@@ -251,75 +251,79 @@ void sumsq_(const at::Tensor& x, at::Tensor out) {
 
 #ifdef LF_HAVE_ATTN
 // ------------------------------------------------------------------ attention
-std::vector<at::Tensor> attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
-                                 c10::optional<at::Tensor> cu_seqlens, double scale, bool causal,
-                                 const at::Tensor& status) {
-  // q [T, Hq, D], k/v [T, Hkv, D]; last dim contiguous, arbitrary token/head strides.
+// q: [T, G, R, 128] (any token/group/head strides, e.g. a view into a packed QKV buffer),
+// k, v: [T, G, 128] views. Returns o [T, G*R, 128] and lse [G*R, T].
+void fill_attn_common(lf::AttnArgs& a, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                      const c10::optional<at::Tensor>& cu_seqlens, double scale, bool causal,
+                      const at::Tensor& status) {
   check_bf16_cuda(q, "q");
   check_bf16_cuda(k, "k");
   check_bf16_cuda(v, "v");
-  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3);
-  TORCH_CHECK(q.stride(2) == 1 && k.stride(2) == 1 && v.stride(2) == 1);
-  c10::cuda::CUDAGuard guard(q.device());
-  const int64_t T = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1);
-  at::Tensor o = at::empty({T, Hq, D}, q.options());
-  at::Tensor lse = at::empty({Hq, T}, q.options().dtype(at::kFloat));
-  lf::AttnArgs a;
-  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.o = o.data_ptr();
-  a.lse = lse.data_ptr<float>();
-  a.T = static_cast<int>(T); a.Hq = static_cast<int>(Hq); a.Hkv = static_cast<int>(Hkv); a.D = static_cast<int>(D);
-  a.q_ts = q.stride(0); a.q_hs = q.stride(1);
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 3 && v.dim() == 3, "q must be [T,G,R,128], k/v [T,G,128]");
+  TORCH_CHECK(q.size(3) == 128 && k.size(2) == 128 && v.size(2) == 128, "head dim must be 128");
+  TORCH_CHECK(q.stride(3) == 1 && k.stride(2) == 1 && v.stride(2) == 1);
+  TORCH_CHECK(k.size(1) == q.size(1) && v.size(1) == q.size(1) && k.size(0) == q.size(0));
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr();
+  a.T = static_cast<int>(q.size(0));
+  a.Hkv = static_cast<int>(q.size(1));
+  a.Hq = static_cast<int>(q.size(1) * q.size(2));
+  a.q_ts = q.stride(0); a.q_gs = q.stride(1); a.q_hs = q.stride(2);
   a.k_ts = k.stride(0); a.k_hs = k.stride(1);
   a.v_ts = v.stride(0); a.v_hs = v.stride(1);
-  a.o_ts = o.stride(0); a.o_hs = o.stride(1);
   a.scale = static_cast<float>(scale);
   a.causal = causal;
   a.status = status.data_ptr<int>();
   if (cu_seqlens.has_value()) {
-    TORCH_CHECK(cu_seqlens->scalar_type() == at::kInt && cu_seqlens->is_contiguous());
+    TORCH_CHECK(cu_seqlens->is_cuda() && cu_seqlens->scalar_type() == at::kInt && cu_seqlens->is_contiguous());
     a.cu_seqlens = cu_seqlens->data_ptr<int>();
     a.num_seqs = static_cast<int>(cu_seqlens->numel() - 1);
   }
+}
+
+std::vector<at::Tensor> attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                 c10::optional<at::Tensor> cu_seqlens, double scale, bool causal,
+                                 const at::Tensor& status) {
+  c10::cuda::CUDAGuard guard(q.device());
+  lf::AttnArgs a;
+  fill_attn_common(a, q, k, v, cu_seqlens, scale, causal, status);
+  at::Tensor o = at::empty({a.T, a.Hq, 128}, q.options());
+  at::Tensor lse = at::empty({a.Hq, a.T}, q.options().dtype(at::kFloat));
+  a.o = o.data_ptr();
+  a.o_ts = o.stride(0); a.o_hs = o.stride(1);
+  a.lse = lse.data_ptr<float>();
   const int rc = lf::attn_fwd(a, cur_stream());
   TORCH_CHECK(rc == 0, "lf::attn_fwd failed with code ", rc);
   ++g_launches;
   return {o, lse};
 }
 
-std::vector<at::Tensor> attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k,
-                                 const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
-                                 c10::optional<at::Tensor> cu_seqlens, double scale, bool causal,
-                                 const at::Tensor& status) {
-  check_bf16_cuda(dout, "dout");
-  TORCH_CHECK(dout.stride(2) == 1 && o.stride(2) == 1);
+// dq/dk/dv are OUTPUT views (same shapes as q/k/v), typically into one packed gradient buffer.
+void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+              const at::Tensor& o, const at::Tensor& lse, at::Tensor dq, at::Tensor dk, at::Tensor dv,
+              c10::optional<at::Tensor> cu_seqlens, double scale, bool causal, const at::Tensor& status) {
   c10::cuda::CUDAGuard guard(q.device());
-  const int64_t T = q.size(0), Hq = q.size(1), D = q.size(2), Hkv = k.size(1);
-  at::Tensor dq = at::empty({T, Hq, D}, q.options());
-  at::Tensor dk = at::empty({T, Hkv, D}, q.options());
-  at::Tensor dv = at::empty({T, Hkv, D}, q.options());
-  at::Tensor delta = at::empty({Hq, T}, q.options().dtype(at::kFloat));
   lf::AttnArgs a;
-  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.o = const_cast<void*>(o.data_ptr());
-  a.lse = const_cast<float*>(lse.data_ptr<float>());
-  a.dout = dout.data_ptr(); a.dq = dq.data_ptr(); a.dk = dk.data_ptr(); a.dv = dv.data_ptr();
-  a.delta = delta.data_ptr<float>();
-  a.T = static_cast<int>(T); a.Hq = static_cast<int>(Hq); a.Hkv = static_cast<int>(Hkv); a.D = static_cast<int>(D);
-  a.q_ts = q.stride(0); a.q_hs = q.stride(1);
-  a.k_ts = k.stride(0); a.k_hs = k.stride(1);
-  a.v_ts = v.stride(0); a.v_hs = v.stride(1);
+  fill_attn_common(a, q, k, v, cu_seqlens, scale, causal, status);
+  check_bf16_cuda(dout, "dout");
+  check_bf16_cuda(o, "o");
+  TORCH_CHECK(dout.dim() == 3 && dout.stride(2) == 1 && o.stride(2) == 1 && dout.size(1) == a.Hq);
+  TORCH_CHECK(dq.sizes() == q.sizes() && dk.sizes() == k.sizes() && dv.sizes() == v.sizes());
+  TORCH_CHECK(dq.stride(3) == 1 && dk.stride(2) == 1 && dv.stride(2) == 1);
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous());
+  at::Tensor delta = at::empty({a.Hq, a.T}, q.options().dtype(at::kFloat));
+  a.o = const_cast<void*>(o.data_ptr());
   a.o_ts = o.stride(0); a.o_hs = o.stride(1);
+  a.lse = const_cast<float*>(lse.data_ptr<float>());
+  a.dout = dout.data_ptr();
   a.do_ts = dout.stride(0); a.do_hs = dout.stride(1);
-  a.scale = static_cast<float>(scale);
-  a.causal = causal;
-  a.status = status.data_ptr<int>();
-  if (cu_seqlens.has_value()) {
-    a.cu_seqlens = cu_seqlens->data_ptr<int>();
-    a.num_seqs = static_cast<int>(cu_seqlens->numel() - 1);
-  }
+  a.dq = dq.data_ptr(); a.dk = dk.data_ptr(); a.dv = dv.data_ptr();
+  a.dq_ts = dq.stride(0); a.dq_gs = dq.stride(1); a.dq_hs = dq.stride(2);
+  a.dk_ts = dk.stride(0); a.dk_hs = dk.stride(1);
+  a.dv_ts = dv.stride(0); a.dv_hs = dv.stride(1);
+  a.delta = delta.data_ptr<float>();
   const int rc = lf::attn_bwd(a, cur_stream());
   TORCH_CHECK(rc == 0, "lf::attn_bwd failed with code ", rc);
   g_launches += 3;
-  return {dq, dk, dv};
 }
 
 #endif  // LF_HAVE_ATTN

@@ -336,26 +336,62 @@ def attention_ref(q, k, v, causal=True, scale=None, cu_seqlens=None):
 
 
 class _AttnFn(torch.autograd.Function):
+    """q [T, Hq, 128], k/v [T, Hkv, 128] (strided views allowed) -> o [T, Hq, 128]."""
+
     @staticmethod
     def forward(ctx, q, k, v, cu_seqlens, scale, causal):
-        o, lse = _C().attn_fwd(q, k, v, cu_seqlens, scale, causal, _ext.status_tensor(q.device))
-        ctx.save_for_backward(q, k, v, o, lse, cu_seqlens) if cu_seqlens is not None else ctx.save_for_backward(
-            q, k, v, o, lse)
-        ctx.has_cu = cu_seqlens is not None
+        Hkv = k.shape[1]
+        q4 = q.unflatten(1, (Hkv, q.shape[1] // Hkv))
+        o, lse = _C().attn_fwd(q4, k, v, cu_seqlens, scale, causal, _ext.status_tensor(q.device))
+        ctx.save_for_backward(q, k, v, o, lse, *([cu_seqlens] if cu_seqlens is not None else []))
         ctx.scale, ctx.causal = scale, causal
         return o
 
     @staticmethod
     def backward(ctx, do):
-        if ctx.has_cu:
-            q, k, v, o, lse, cu = ctx.saved_tensors
-        else:
-            q, k, v, o, lse = ctx.saved_tensors
-            cu = None
-        if do.stride(2) != 1:
+        q, k, v, o, lse, *rest = ctx.saved_tensors
+        cu = rest[0] if rest else None
+        if do.stride(2) != 1 or do.stride(1) % 8 or do.stride(0) % 8:
             do = do.contiguous()
-        dq, dk, dv = _C().attn_bwd(do, q, k, v, o, lse, cu, ctx.scale, ctx.causal, _ext.status_tensor(q.device))
+        Hkv = k.shape[1]
+        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+        R = q.shape[1] // Hkv
+        _C().attn_bwd(do, q.unflatten(1, (Hkv, R)), k, v, o, lse, dq.unflatten(1, (Hkv, R)), dk, dv, cu, ctx.scale,
+                      ctx.causal, _ext.status_tensor(q.device))
         return dq, dk, dv, None, None, None
+
+
+class _AttnPackedFn(torch.autograd.Function):
+    """Attention straight on the packed QKV GEMM output ``[T, G*(R+2)*128]`` (Megatron's per-group
+    ``[q_0..q_{R-1}, k, v]`` order): no split copies forward, and the backward kernels write dq,
+    dk, dv into ONE packed gradient buffer that feeds the QKV dgrad/wgrad GEMMs directly."""
+
+    @staticmethod
+    def forward(ctx, qkv, G, R, cu_seqlens, scale, causal):
+        T = qkv.shape[0]
+        pk = qkv.view(T, G, R + 2, 128)
+        o, lse = _C().attn_fwd(pk[:, :, :R], pk[:, :, R], pk[:, :, R + 1], cu_seqlens, scale, causal,
+                               _ext.status_tensor(qkv.device))
+        ctx.save_for_backward(qkv, o, lse, *([cu_seqlens] if cu_seqlens is not None else []))
+        ctx.cfg = (G, R, scale, causal)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, o, lse, *rest = ctx.saved_tensors
+        cu = rest[0] if rest else None
+        G, R, scale, causal = ctx.cfg
+        T = qkv.shape[0]
+        if do.stride(2) != 1 or do.stride(1) % 8 or do.stride(0) % 8:
+            do = do.contiguous()
+        pk = qkv.view(T, G, R + 2, 128)
+        dqkv = torch.empty_like(qkv)
+        dpk = dqkv.view(T, G, R + 2, 128)
+        _C().attn_bwd(do, pk[:, :, :R], pk[:, :, R], pk[:, :, R + 1], o, lse, dpk[:, :, :R], dpk[:, :, R],
+                      dpk[:, :, R + 1], cu, scale, causal, _ext.status_tensor(qkv.device))
+        return dqkv, None, None, None, None, None
 
 
 _ATTN_IMPL = {"impl": "auto"}
@@ -373,6 +409,20 @@ def native_attention_supported(q, k, v) -> bool:
             and q.shape[-1] == 128 and v.shape[-1] == 128)
 
 
+def attention_packed_supported(qkv: torch.Tensor, head_dim: int) -> bool:
+    m = _ext.get()
+    return (_ATTN_IMPL["impl"] != "sdpa" and m is not None and hasattr(m, "attn_fwd") and qkv.is_cuda
+            and qkv.dtype == torch.bfloat16 and head_dim == 128 and qkv.dim() == 2 and qkv.is_contiguous())
+
+
+def attention_packed(qkv: torch.Tensor, groups: int, q_per_group: int, *, causal: bool = True,
+                     scale: Optional[float] = None, cu_seqlens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention on a packed ``[T, G*(R+2)*128]`` QKV buffer -> ``[T, G*R, 128]``."""
+    scale = 1.0 / math.sqrt(128) if scale is None else scale
+    cu = cu_seqlens.to(torch.int32).contiguous() if cu_seqlens is not None else None
+    return _AttnPackedFn.apply(qkv, groups, q_per_group, cu, scale, causal)
+
+
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = True,
               scale: Optional[float] = None, cu_seqlens: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Softmax attention over packed tokens. q [T, Hq, D], k/v [T, Hkv, D] -> [T, Hq, Dv]."""
@@ -381,6 +431,11 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
     impl = _ATTN_IMPL["impl"]
     if q.is_cuda and impl != "sdpa" and native_attention_supported(q, k, v):
         cu = cu_seqlens.to(torch.int32).contiguous() if cu_seqlens is not None else None
+
+        def ok(t):
+            return t.stride(2) == 1 and t.stride(1) % 8 == 0 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
+
+        q, k, v = (t if ok(t) else t.contiguous() for t in (q, k, v))
         return _AttnFn.apply(q, k, v, cu, scale, causal)
     if impl == "native" and q.is_cuda:
         raise RuntimeError("native attention requested but not available for this shape")
