@@ -27,7 +27,8 @@
 
 namespace lf {
 
-static constexpr int AT_THREADS = 192;
+static constexpr int AT_THREADS = 192;      // forward: 2 control warps + 4 softmax warps
+static constexpr int AT_BWD_THREADS = 320;  // backward: 2 control warps + 8 math warps (2 per TMEM lane quarter)
 static constexpr int TILE_BYTES = 128 * 128 * 2;  // 32 KB
 static constexpr int BOX_BYTES = 128 * 64 * 2;    // 16 KB
 static constexpr float LOG2E = 1.4426950408889634f;
@@ -124,17 +125,23 @@ struct SharedCtl {
 };
 
 // =========================================================================== forward
-// smem: Q tile | K[2] | V[2] | P tile | control
+// smem: Q tile | K[2] | V[2] | P[2] | control
 struct FwdSmem {
   static constexpr int Q = 0;
   static constexpr int K = TILE_BYTES;
   static constexpr int V = 3 * TILE_BYTES;
   static constexpr int P = 5 * TILE_BYTES;
-  static constexpr int CTL = 6 * TILE_BYTES;
-  static constexpr int BYTES = 6 * TILE_BYTES + 256 + 1024;
+  static constexpr int CTL = 7 * TILE_BYTES;
+  static constexpr int BYTES = 7 * TILE_BYTES + 256 + 1024;
 };
-enum { F_Q = 0, F_KV_FULL = 1, F_KV_EMPTY = 3, F_S_FULL = 5, F_P_FULL = 7, F_O_DONE = 8 };
+enum { F_Q = 0, F_KV_FULL = 1, F_KV_EMPTY = 3, F_S_FULL = 5, F_P_FULL = 7, F_P_EMPTY = 9, F_O_DONE = 11 };
 
+// Pipeline per kv block j (S and P are double buffered, index j & 1):
+//   MMA warp : S[j+1] = Q K[j+1]^T is issued BEFORE waiting for P[j], so the tensor core computes
+//              the next scores while the softmax warps work on block j; then O += P[j] V[j].
+//   softmax  : reads S[j] once into registers, row max, (rare) lazy rescale of O, exponentials ->
+//              P[j] in shared memory; it only waits for P[j-2]'s consumer, never for O += P[j-1] V[j-1],
+//              unless a rescale is needed.
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                 const __grid_constant__ CUtensorMap tv, const AttnParams p) {
@@ -160,8 +167,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       mbar_init(&bars[F_KV_FULL + s], 1);
       mbar_init(&bars[F_KV_EMPTY + s], 1);
       mbar_init(&bars[F_S_FULL + s], 1);
+      mbar_init(&bars[F_P_FULL + s], 4);
+      mbar_init(&bars[F_P_EMPTY + s], 1);
     }
-    mbar_init(&bars[F_P_FULL], 4);
     mbar_init(&bars[F_O_DONE], 1);
     ctl->abort_flag = 0;
     fence_mbar_init();
@@ -208,11 +216,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           mma_tile<false, false>(tmem_s0 + s1 * 128, sq, smem_u32(smem + FwdSmem::K + s1 * TILE_BYTES), false);
           tc_commit(&bars[F_S_FULL + s1]);
         }
-        ok = mbar_wait(&bars[F_P_FULL], j & 1, abort_flag);
+        ok = mbar_wait(&bars[F_P_FULL + s], (j >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
-        mma_tile<false, true>(tmem_o, sp, smem_u32(smem + FwdSmem::V + s * TILE_BYTES), j > 0);
+        mma_tile<false, true>(tmem_o, sp + s * TILE_BYTES, smem_u32(smem + FwdSmem::V + s * TILE_BYTES), j > 0);
         tc_commit(&bars[F_KV_EMPTY + s]);
+        tc_commit(&bars[F_P_EMPTY + s]);
         tc_commit(&bars[F_O_DONE]);
       }
       if (!ok) atomicCAS(p.status, 0, LF_ERR_WAIT_FULL);
@@ -228,44 +237,50 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int s = j & 1;
-      ok = mbar_wait(&bars[F_S_FULL + s], (j >> 1) & 1, abort_flag);
+      ok = mbar_wait_warp(&bars[F_S_FULL + s], (j >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t ts = tmem_s0 + s * 128 + lane_off;
       const int kv0 = j * 128;
+      // the whole score row of this thread in registers: one TMEM pass
+      uint32_t r0[32], r1[32], r2[32], r3[32];
+      tmem_ld_32x32b_x32(ts, r0);
+      tmem_ld_32x32b_x32(ts + 32, r1);
+      tmem_ld_32x32b_x32(ts + 64, r2);
+      tmem_ld_32x32b_x32(ts + 96, r3);
+      tmem_ld_wait();
       const bool need_mask = (kv0 + 128 > seq_len) || (p.causal && kv0 + 127 > q0);
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(ts + c0, r);
-        tmem_ld_wait();
+      if (need_mask) {
+        const int lim = min(seq_len, p.causal ? qi + 1 : seq_len) - kv0;  // columns [0, lim) stay
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(r[i]);
-          if (need_mask) {
-            const int kj = kv0 + c0 + i;
-            if (kj >= seq_len || (p.causal && kj > qi)) x = -INFINITY;
-          }
-          mx = fmaxf(mx, x);
+          if (i >= lim) r0[i] = 0xff800000u;
+          if (i + 32 >= lim) r1[i] = 0xff800000u;
+          if (i + 64 >= lim) r2[i] = 0xff800000u;
+          if (i + 96 >= lim) r3[i] = 0xff800000u;
         }
       }
-      mx *= p.scale_log2;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        mx0 = fmaxf(mx0, __uint_as_float(r0[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(r1[i]));
+        mx2 = fmaxf(mx2, __uint_as_float(r2[i]));
+        mx3 = fmaxf(mx3, __uint_as_float(r3[i]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
       // Lazy rescale: keep the old reference unless the maximum grew by more than 2^8; then all
       // exponentials stay below 256 and the accumulated O / l remain consistent with m_ref.
       float m_new = m_ref;
       if (mx > m_ref + 8.f || m_ref == -INFINITY) m_new = fmaxf(mx, m_ref);
       const bool rescale = (m_new != m_ref) && (j > 0);
       const unsigned any = __ballot_sync(0xffffffffu, rescale);
-      // P of the previous block must have been consumed, and O complete, before touching either
-      if (j > 0) {
-        ok = mbar_wait(&bars[F_O_DONE], (j - 1) & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after_sync();
-      }
       const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
       if (any) {
+        // O must be complete (O += P[j-1] V[j-1] retired) before its rows are rescaled
+        ok = mbar_wait_warp(&bars[F_O_DONE], (j - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
 #pragma unroll 1
         for (int c0 = 0; c0 < 128; c0 += 16) {
           uint32_t r[16];
@@ -279,34 +294,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       }
       l_sum *= alpha;
       m_ref = m_new;
-      // pass 2: probabilities -> shared memory (bf16), row sum
-      const float mref_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(ts + c0, r);
-        tmem_ld_wait();
+      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+      // P[s] was last read by O += P[j-2] V[j-2]
+      ok = mbar_wait_warp(&bars[F_P_EMPTY + s], ((j >> 1) & 1) ^ 1, abort_flag);
+      if (!ok) break;
+      uint8_t* ptile = smem + FwdSmem::P + s * TILE_BYTES;
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      {
         float pv[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(r[i]) * p.scale_log2 - mref_safe;
-          if (need_mask) {
-            const int kj = kv0 + c0 + i;
-            if (kj >= seq_len || (p.causal && kj > qi)) x = -INFINITY;
-          }
-          const float e = exp2f(x);
-          pv[i] = e;
-          l_sum += e;
-        }
-        store_row_chunk(smem + FwdSmem::P, row, c0, pv);
+        for (int i = 0; i < 32; ++i) { pv[i] = exp2f(fmaf(__uint_as_float(r0[i]), p.scale_log2, neg_m)); l0 += pv[i]; }
+        store_row_chunk(ptile, row, 0, pv);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { pv[i] = exp2f(fmaf(__uint_as_float(r1[i]), p.scale_log2, neg_m)); l1 += pv[i]; }
+        store_row_chunk(ptile, row, 32, pv);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { pv[i] = exp2f(fmaf(__uint_as_float(r2[i]), p.scale_log2, neg_m)); l2 += pv[i]; }
+        store_row_chunk(ptile, row, 64, pv);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { pv[i] = exp2f(fmaf(__uint_as_float(r3[i]), p.scale_log2, neg_m)); l3 += pv[i]; }
+        store_row_chunk(ptile, row, 96, pv);
       }
+      l_sum += (l0 + l1) + (l2 + l3);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[F_P_FULL]);
+      if (lane == 0) mbar_arrive(&bars[F_P_FULL + s]);
     }
     // ---------------------------------------------------------------- epilogue
-    if (ok && n_kv > 0) ok = mbar_wait(&bars[F_O_DONE], (n_kv - 1) & 1, abort_flag);
+    if (ok && n_kv > 0) ok = mbar_wait_warp(&bars[F_O_DONE], (n_kv - 1) & 1, abort_flag);
     if (!ok) {
       if (lane == 0) atomicCAS(p.status, 0, LF_ERR_WAIT_TMEM_FULL);
     } else {
@@ -368,15 +384,39 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const 
 }
 
 // =========================================================================== backward: dK, dV
-// One CTA per (kv block, kv head); loops over the R query heads of the group and over the
-// query blocks that attend to this kv block. smem: K | V | Q | dO | P | dS | control.
+// One CTA per (64-row kv block, kv head); loops over the R query heads of the group and over the
+// 128-row query blocks that attend to this kv block. Per iteration (all on tcgen05, N = 64):
+//   S  = Q K^T, dP = dO V^T                      [128 q x 64 kv] fp32 in TMEM (double buffered)
+//   P  = exp2(S*scale*log2e - lse), dS = P (dP - delta) scale   -> bf16 tiles in shared memory (x2)
+//   dV^T += dO^T P,  dK^T += Q^T dS              [128 d x 64 kv] fp32 in TMEM
+// The transposed accumulators keep M = 128 for every MMA; Q, dO, P and dS tiles are read MN-major
+// where the contraction runs over their rows, so nothing is transposed in memory. Q/dO, S/dP and
+// P/dS are all double buffered: TMA, the score MMAs of iteration it+1 and the gradient MMAs of
+// iteration it overlap the math warps' work on iteration it.
 struct BkvSmem {
-  static constexpr int K = 0, V = TILE_BYTES, Q = 2 * TILE_BYTES, DO = 3 * TILE_BYTES, P = 4 * TILE_BYTES,
-                       DS = 5 * TILE_BYTES, CTL = 6 * TILE_BYTES, BYTES = 6 * TILE_BYTES + 256 + 1024;
+  static constexpr int KVB = 64 * 128 * 2;  // 16 KB: [64 kv rows x 128 d]
+  static constexpr int PB = 128 * 64 * 2;   // 16 KB: [128 q rows x 64 kv]
+  static constexpr int K = 0, V = KVB, Q = 2 * KVB, DO = Q + 2 * TILE_BYTES, P = DO + 2 * TILE_BYTES, DS = P + 2 * PB,
+                       CTL = DS + 2 * PB, BYTES = CTL + 256 + 1024;
 };
-enum { B_KV = 0, B_QDO_FULL = 1, B_QDO_EMPTY = 2, B_S_FULL = 3, B_PDS_FULL = 4, B_ACC_DONE = 5 };
+enum { B_KV = 0, B_QDO_FULL = 1, B_QDO_EMPTY = 3, B_S_FULL = 5, B_PDS_FULL = 7, B_PDS_EMPTY = 9, B_ACC_DONE = 11 };
 
-__global__ void __launch_bounds__(AT_THREADS, 1)
+// 128 x 64 x 128 product. A: two-box tile [128 x 128] (K-major: rows = M) or MN-major (rows = contraction).
+// B (N = 64): K-major [64 rows x 128 contraction] as two 8 KB boxes, or MN-major [128 contraction rows x 64].
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ void mma_tile_n64(uint32_t tmem_d, uint32_t a_base, uint32_t b_base, bool accumulate) {
+  constexpr uint32_t idesc = make_idesc(1, 1, A_MN, B_MN, 128, 64);
+#pragma unroll
+  for (int kk = 0; kk < 8; ++kk) {
+    const uint64_t da = A_MN ? make_smem_desc_sw128(a_base + kk * 2048, BOX_BYTES, 1024)
+                             : make_smem_desc_sw128(a_base + (kk >> 2) * BOX_BYTES + (kk & 3) * 32, 16, 1024);
+    const uint64_t db = B_MN ? make_smem_desc_sw128(b_base + kk * 2048, 16, 1024)
+                             : make_smem_desc_sw128(b_base + (kk >> 2) * (64 * 128) + (kk & 3) * 32, 16, 1024);
+    tc_mma_f16_ss(tmem_d, da, db, idesc, (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+
+__global__ void __launch_bounds__(AT_BWD_THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                      const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
                      const AttnParams p) {
@@ -388,19 +428,24 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = blockIdx.y;
 
-  int seq_start, seq_len, kb;
-  if (!locate_block(blockIdx.x, p.cu_seqlens, p.num_seqs, p.T, seq_start, seq_len, kb)) return;
-  const int kv0 = kb * 128;
+  // kv blocks are 64 rows: locate by 128-row block, then take the half
+  int seq_start, seq_len, kb128;
+  if (!locate_block(blockIdx.x >> 1, p.cu_seqlens, p.num_seqs, p.T, seq_start, seq_len, kb128)) return;
+  const int kv0 = kb128 * 128 + (blockIdx.x & 1) * 64;
+  if (kv0 >= seq_len) return;
   const int n_qb_total = (seq_len + 127) >> 7;
-  const int qb_first = p.causal ? kb : 0;
+  const int qb_first = p.causal ? kb128 : 0;
   const int n_iter = (n_qb_total - qb_first) * p.R;  // iteration it -> head it % R, q block qb_first + it / R
 
   if (threadIdx.x == 0) {
     mbar_init(&bars[B_KV], 1);
-    mbar_init(&bars[B_QDO_FULL], 1);
-    mbar_init(&bars[B_QDO_EMPTY], 1);
-    mbar_init(&bars[B_S_FULL], 1);
-    mbar_init(&bars[B_PDS_FULL], 4);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars[B_QDO_FULL + s], 1);
+      mbar_init(&bars[B_QDO_EMPTY + s], 1);
+      mbar_init(&bars[B_S_FULL + s], 1);
+      mbar_init(&bars[B_PDS_FULL + s], 8);
+      mbar_init(&bars[B_PDS_EMPTY + s], 1);
+    }
     mbar_init(&bars[B_ACC_DONE], 1);
     ctl->abort_flag = 0;
     fence_mbar_init();
@@ -410,22 +455,25 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = ctl->tmem_slot;
-  const uint32_t t_s = tmem, t_dp = tmem + 128, t_dv = tmem + 256, t_dk = tmem + 384;
+  const uint32_t t_s = tmem, t_dp = tmem + 128, t_dv = tmem + 256, t_dk = tmem + 320;  // S[2], dP[2] 64 cols each
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(&bars[B_KV], 2 * TILE_BYTES);
-      load_tile_kv(smem + BkvSmem::K, &tk, &bars[B_KV], g, seq_start + kv0);
-      load_tile_kv(smem + BkvSmem::V, &tv, &bars[B_KV], g, seq_start + kv0);
+      mbar_arrive_expect_tx(&bars[B_KV], 2 * BkvSmem::KVB);
+      for (int b = 0; b < 2; ++b) {
+        tma_load_3d(smem + BkvSmem::K + b * (64 * 128), &tk, &bars[B_KV], b * 64, g, seq_start + kv0);
+        tma_load_3d(smem + BkvSmem::V + b * (64 * 128), &tv, &bars[B_KV], b * 64, g, seq_start + kv0);
+      }
       for (int it = 0; it < n_iter; ++it) {
-        if (!mbar_wait(&bars[B_QDO_EMPTY], (it & 1) ^ 1, abort_flag)) {
+        const int s = it & 1;
+        if (!mbar_wait(&bars[B_QDO_EMPTY + s], ((it >> 1) & 1) ^ 1, abort_flag)) {
           atomicCAS(p.status, 0, LF_ERR_WAIT_EMPTY);
           break;
         }
         const int jh = it % p.R, qb = qb_first + it / p.R;
-        mbar_arrive_expect_tx(&bars[B_QDO_FULL], 2 * TILE_BYTES);
-        load_tile_q(smem + BkvSmem::Q, &tq, &bars[B_QDO_FULL], jh, g, seq_start + qb * 128);
-        load_tile_q(smem + BkvSmem::DO, &tdo, &bars[B_QDO_FULL], jh, g, seq_start + qb * 128);
+        mbar_arrive_expect_tx(&bars[B_QDO_FULL + s], 2 * TILE_BYTES);
+        load_tile_q(smem + BkvSmem::Q + s * TILE_BYTES, &tq, &bars[B_QDO_FULL + s], jh, g, seq_start + qb * 128);
+        load_tile_q(smem + BkvSmem::DO + s * TILE_BYTES, &tdo, &bars[B_QDO_FULL + s], jh, g, seq_start + qb * 128);
       }
     }
   } else if (warp == 1) {
@@ -434,103 +482,101 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       const uint32_t sq = smem_u32(smem + BkvSmem::Q), sdo = smem_u32(smem + BkvSmem::DO);
       const uint32_t sp = smem_u32(smem + BkvSmem::P), sds = smem_u32(smem + BkvSmem::DS);
       bool ok = mbar_wait(&bars[B_KV], 0, abort_flag);
+      if (ok) ok = mbar_wait(&bars[B_QDO_FULL + 0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        mma_tile_n64<false, false>(t_s, sq, sk, false);    // S[0]  = Q K^T
+        mma_tile_n64<false, false>(t_dp, sdo, sv, false);  // dP[0] = dO V^T
+        tc_commit(&bars[B_S_FULL + 0]);
+      }
       for (int it = 0; it < n_iter && ok; ++it) {
-        ok = mbar_wait(&bars[B_QDO_FULL], it & 1, abort_flag);
+        const int s = it & 1;
+        if (it + 1 < n_iter) {
+          const int s1 = (it + 1) & 1;
+          ok = mbar_wait(&bars[B_QDO_FULL + s1], ((it + 1) >> 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          mma_tile_n64<false, false>(t_s + s1 * 64, sq + s1 * TILE_BYTES, sk, false);
+          mma_tile_n64<false, false>(t_dp + s1 * 64, sdo + s1 * TILE_BYTES, sv, false);
+          tc_commit(&bars[B_S_FULL + s1]);
+        }
+        ok = mbar_wait(&bars[B_PDS_FULL + s], (it >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
-        mma_tile<false, false>(t_s, sq, sk, false);    // S  = Q K^T
-        mma_tile<false, false>(t_dp, sdo, sv, false);  // dP = dO V^T
-        tc_commit(&bars[B_S_FULL]);
-        ok = mbar_wait(&bars[B_PDS_FULL], it & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after_sync();
-        mma_tile<true, true>(t_dv, sp, sdo, it > 0);   // dV += P^T dO
-        mma_tile<true, true>(t_dk, sds, sq, it > 0);   // dK += dS^T Q
-        tc_commit(&bars[B_QDO_EMPTY]);
-        tc_commit(&bars[B_ACC_DONE]);
+        mma_tile_n64<true, true>(t_dv, sdo + s * TILE_BYTES, sp + s * BkvSmem::PB, it > 0);  // dV^T += dO^T P
+        mma_tile_n64<true, true>(t_dk, sq + s * TILE_BYTES, sds + s * BkvSmem::PB, it > 0);  // dK^T += Q^T dS
+        tc_commit(&bars[B_QDO_EMPTY + s]);
+        tc_commit(&bars[B_PDS_EMPTY + s]);
+        if (it == n_iter - 1) tc_commit(&bars[B_ACC_DONE]);
       }
       if (!ok) atomicCAS(p.status, 0, LF_ERR_WAIT_FULL);
     }
   } else {
+    // two warps share each TMEM lane quarter; each takes 32 of the 64 tile columns
     const int quarter = warp & 3;
+    const int cbeg = ((warp - 2) >> 2) * 32;
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
+      const int s = it & 1;
       const int jh = it % p.R, qb = qb_first + it / p.R;
       const int head = g * p.R + jh;
       const int qi = qb * 128 + row;  // this thread's query row
       const bool q_valid = qi < seq_len;
       const long long tok = seq_start + qi;
-      const float lse2 = q_valid ? p.lse[static_cast<long long>(head) * p.T + tok] * LOG2E : 0.f;
+      const float neg_lse2 = q_valid ? -p.lse[static_cast<long long>(head) * p.T + tok] * LOG2E : 0.f;
       const float dlt = q_valid ? p.delta[static_cast<long long>(head) * p.T + tok] : 0.f;
-      ok = mbar_wait(&bars[B_S_FULL], it & 1, abort_flag);
+      // columns [0, lim) of this row are kept (sequence end, causal diagonal, invalid query row)
+      const int lim = q_valid ? (min(seq_len, p.causal ? qi + 1 : seq_len) - kv0) : 0;
+      ok = mbar_wait_warp(&bars[B_S_FULL + s], (it >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
-      // P and dS tiles of the previous iteration must have been consumed by the MMAs
-      if (it > 0) {
-        ok = mbar_wait(&bars[B_ACC_DONE], (it - 1) & 1, abort_flag);
-        if (!ok) break;
-      }
-#pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
-        uint32_t rs[32], rd[32];
-        tmem_ld_32x32b_x32(t_s + lane_off + c0, rs);
-        tmem_ld_32x32b_x32(t_dp + lane_off + c0, rd);
-        tmem_ld_wait();
-        float pv[32], ds[32];
+      uint32_t rs[32], rd[32];
+      tmem_ld_32x32b_x32(t_s + s * 64 + lane_off + cbeg, rs);
+      tmem_ld_32x32b_x32(t_dp + s * 64 + lane_off + cbeg, rd);
+      tmem_ld_wait();
+      float pv[32], ds[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kj = kv0 + c0 + i;
-          const bool keep = q_valid && kj < seq_len && (!p.causal || kj <= qi);
-          const float pr = keep ? exp2f(__uint_as_float(rs[i]) * p.scale_log2 - lse2) : 0.f;
-          pv[i] = pr;
-          ds[i] = pr * (__uint_as_float(rd[i]) - dlt) * p.scale;
-        }
-        store_row_chunk(smem + BkvSmem::P, row, c0, pv);
-        store_row_chunk(smem + BkvSmem::DS, row, c0, ds);
+      for (int i = 0; i < 32; ++i) {
+        float pr = exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, neg_lse2));
+        if (cbeg + i >= lim) pr = 0.f;
+        pv[i] = pr;
+        ds[i] = pr * (__uint_as_float(rd[i]) - dlt) * p.scale;
       }
+      // P[s] / dS[s] were last read by the gradient MMAs of iteration it - 2
+      ok = mbar_wait_warp(&bars[B_PDS_EMPTY + s], ((it >> 1) & 1) ^ 1, abort_flag);
+      if (!ok) break;
+      store_row_chunk(smem + BkvSmem::P + s * BkvSmem::PB, row, cbeg, pv);
+      store_row_chunk(smem + BkvSmem::DS + s * BkvSmem::PB, row, cbeg, ds);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[B_PDS_FULL]);
+      if (lane == 0) mbar_arrive(&bars[B_PDS_FULL + s]);
     }
-    if (ok && n_iter > 0) ok = mbar_wait(&bars[B_ACC_DONE], (n_iter - 1) & 1, abort_flag);
+    if (ok && n_iter > 0) ok = mbar_wait_warp(&bars[B_ACC_DONE], 0, abort_flag);
     if (!ok) {
       if (lane == 0) atomicCAS(p.status, 0, LF_ERR_WAIT_TMEM_FULL);
     } else {
+      // accumulators are transposed: TMEM lane = head-dim index d, column = kv row
       tc_fence_after_sync();
-      const int kj = kv0 + row;
-      const bool valid = kj < seq_len;
-      const long long tok = seq_start + kj;
-      __nv_bfloat16* dvrow = p.dv + tok * p.dv_ts + static_cast<long long>(g) * p.dv_hs;
-      __nv_bfloat16* dkrow = p.dk + tok * p.dk_ts + static_cast<long long>(g) * p.dk_hs;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
-        uint32_t a[32], b[32];
-        if (n_iter > 0) {
-          tmem_ld_32x32b_x32(t_dv + lane_off + c0, a);
-          tmem_ld_32x32b_x32(t_dk + lane_off + c0, b);
-          tmem_ld_wait();
-        } else {
+      uint32_t a[32], b[32];
+      if (n_iter > 0) {
+        tmem_ld_32x32b_x32(t_dv + lane_off + cbeg, a);
+        tmem_ld_32x32b_x32(t_dk + lane_off + cbeg, b);
+        tmem_ld_wait();
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) a[i] = b[i] = 0u;
-        }
-        if (valid) {
+        for (int i = 0; i < 32; ++i) a[i] = b[i] = 0u;
+      }
+      const int d = row;
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 q;
-            q.x = pack_bf16x2(__uint_as_float(a[i]), __uint_as_float(a[i + 1]));
-            q.y = pack_bf16x2(__uint_as_float(a[i + 2]), __uint_as_float(a[i + 3]));
-            q.z = pack_bf16x2(__uint_as_float(a[i + 4]), __uint_as_float(a[i + 5]));
-            q.w = pack_bf16x2(__uint_as_float(a[i + 6]), __uint_as_float(a[i + 7]));
-            *reinterpret_cast<uint4*>(dvrow + c0 + i) = q;
-            q.x = pack_bf16x2(__uint_as_float(b[i]), __uint_as_float(b[i + 1]));
-            q.y = pack_bf16x2(__uint_as_float(b[i + 2]), __uint_as_float(b[i + 3]));
-            q.z = pack_bf16x2(__uint_as_float(b[i + 4]), __uint_as_float(b[i + 5]));
-            q.w = pack_bf16x2(__uint_as_float(b[i + 6]), __uint_as_float(b[i + 7]));
-            *reinterpret_cast<uint4*>(dkrow + c0 + i) = q;
-          }
+      for (int i = 0; i < 32; ++i) {
+        const int kj = kv0 + cbeg + i;
+        if (kj < seq_len) {
+          const long long tok = seq_start + kj;
+          p.dv[tok * p.dv_ts + static_cast<long long>(g) * p.dv_hs + d] = __float2bfloat16(__uint_as_float(a[i]));
+          p.dk[tok * p.dk_ts + static_cast<long long>(g) * p.dk_hs + d] = __float2bfloat16(__uint_as_float(b[i]));
         }
       }
     }
@@ -544,14 +590,18 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
 }
 
 // =========================================================================== backward: dQ
-// One CTA per (q block, q head); loops over kv blocks. smem: Q | dO | K | V | dS | control.
+// One CTA per (q block, q head); loops over kv blocks j.
+// smem: Q | dO | K[2] | V[2] | dS | control.   TMEM: S[2] | dP | dQ.
+// MMA issue order keeps the tensor core busy while the math warps work on block j:
+//   S[j+1] (and S[j+2]) are computed ahead into the spare S buffer, dP[j+1] is issued as soon as
+//   the math warps have drained dP[j], and dQ += dS[j] K[j] runs under the math of block j+1.
 struct BqSmem {
-  static constexpr int Q = 0, DO = TILE_BYTES, K = 2 * TILE_BYTES, V = 3 * TILE_BYTES, DS = 4 * TILE_BYTES,
-                       CTL = 5 * TILE_BYTES, BYTES = 5 * TILE_BYTES + 256 + 1024;
+  static constexpr int Q = 0, DO = TILE_BYTES, K = 2 * TILE_BYTES, V = 4 * TILE_BYTES, DS = 6 * TILE_BYTES,
+                       CTL = 7 * TILE_BYTES, BYTES = 7 * TILE_BYTES + 256 + 1024;
 };
-enum { Q_QDO = 0, Q_KV_FULL = 1, Q_KV_EMPTY = 2, Q_S_FULL = 3, Q_DS_FULL = 4, Q_ACC_DONE = 5 };
+enum { Q_QDO = 0, Q_KV_FULL = 1, Q_KV_EMPTY = 3, Q_S_FULL = 5, Q_DS_FULL = 6, Q_ACC_DONE = 7 };
 
-__global__ void __launch_bounds__(AT_THREADS, 1)
+__global__ void __launch_bounds__(AT_BWD_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                    const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
                    const AttnParams p) {
@@ -571,10 +621,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
 
   if (threadIdx.x == 0) {
     mbar_init(&bars[Q_QDO], 1);
-    mbar_init(&bars[Q_KV_FULL], 1);
-    mbar_init(&bars[Q_KV_EMPTY], 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars[Q_KV_FULL + s], 1);
+      mbar_init(&bars[Q_KV_EMPTY + s], 1);
+    }
     mbar_init(&bars[Q_S_FULL], 1);
-    mbar_init(&bars[Q_DS_FULL], 4);
+    mbar_init(&bars[Q_DS_FULL], 8);
     mbar_init(&bars[Q_ACC_DONE], 1);
     ctl->abort_flag = 0;
     fence_mbar_init();
@@ -584,7 +636,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = ctl->tmem_slot;
-  const uint32_t t_s = tmem, t_dp = tmem + 128, t_dq = tmem + 256;
+  const uint32_t t_s0 = tmem, t_dp = tmem + 256, t_dq = tmem + 384;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -592,13 +644,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       load_tile_q(smem + BqSmem::Q, &tq, &bars[Q_QDO], jh, g, seq_start + q0);
       load_tile_q(smem + BqSmem::DO, &tdo, &bars[Q_QDO], jh, g, seq_start + q0);
       for (int j = 0; j < n_kv; ++j) {
-        if (!mbar_wait(&bars[Q_KV_EMPTY], (j & 1) ^ 1, abort_flag)) {
+        const int s = j & 1;
+        if (!mbar_wait(&bars[Q_KV_EMPTY + s], ((j >> 1) & 1) ^ 1, abort_flag)) {
           atomicCAS(p.status, 0, LF_ERR_WAIT_EMPTY);
           break;
         }
-        mbar_arrive_expect_tx(&bars[Q_KV_FULL], 2 * TILE_BYTES);
-        load_tile_kv(smem + BqSmem::K, &tk, &bars[Q_KV_FULL], g, seq_start + j * 128);
-        load_tile_kv(smem + BqSmem::V, &tv, &bars[Q_KV_FULL], g, seq_start + j * 128);
+        mbar_arrive_expect_tx(&bars[Q_KV_FULL + s], 2 * TILE_BYTES);
+        load_tile_kv(smem + BqSmem::K + s * TILE_BYTES, &tk, &bars[Q_KV_FULL + s], g, seq_start + j * 128);
+        load_tile_kv(smem + BqSmem::V + s * TILE_BYTES, &tv, &bars[Q_KV_FULL + s], g, seq_start + j * 128);
       }
     }
   } else if (warp == 1) {
@@ -607,24 +660,44 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       const uint32_t sk = smem_u32(smem + BqSmem::K), sv = smem_u32(smem + BqSmem::V);
       const uint32_t sds = smem_u32(smem + BqSmem::DS);
       bool ok = mbar_wait(&bars[Q_QDO], 0, abort_flag);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        ok = mbar_wait(&bars[Q_KV_FULL], j & 1, abort_flag);
-        if (!ok) break;
+      if (ok) ok = mbar_wait(&bars[Q_KV_FULL + 0], 0, abort_flag);
+      if (ok) {
         tc_fence_after_sync();
-        mma_tile<false, false>(t_s, sq, sk, false);
-        mma_tile<false, false>(t_dp, sdo, sv, false);
+        mma_tile<false, false>(t_s0, sq, sk, false);    // S[0]
+        mma_tile<false, false>(t_dp, sdo, sv, false);   // dP[0]
         tc_commit(&bars[Q_S_FULL]);
-        ok = mbar_wait(&bars[Q_DS_FULL], j & 1, abort_flag);
+        if (n_kv > 1) {
+          ok = mbar_wait(&bars[Q_KV_FULL + 1], 0, abort_flag);
+          if (ok) {
+            tc_fence_after_sync();
+            mma_tile<false, false>(t_s0 + 128, sq, sk + TILE_BYTES, false);  // S[1]
+          }
+        }
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1;
+        ok = mbar_wait(&bars[Q_DS_FULL], j & 1, abort_flag);  // math of block j done: dS[j] ready, dP free
         if (!ok) break;
         tc_fence_after_sync();
-        mma_tile<false, true>(t_dq, sds, sk, j > 0);  // dQ += dS K
-        tc_commit(&bars[Q_KV_EMPTY]);
+        if (j + 1 < n_kv) {
+          mma_tile<false, false>(t_dp, sdo, sv + ((j + 1) & 1) * TILE_BYTES, false);  // dP[j+1]
+          tc_commit(&bars[Q_S_FULL]);                                                  // S[j+1], dP[j+1] ready
+        }
+        mma_tile<false, true>(t_dq, sds, sk + s * TILE_BYTES, j > 0);  // dQ += dS[j] K[j]
+        tc_commit(&bars[Q_KV_EMPTY + s]);
         tc_commit(&bars[Q_ACC_DONE]);
+        if (j + 2 < n_kv) {
+          ok = mbar_wait(&bars[Q_KV_FULL + s], ((j + 2) >> 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          mma_tile<false, false>(t_s0 + s * 128, sq, sk + s * TILE_BYTES, false);  // S[j+2]
+        }
       }
       if (!ok) atomicCAS(p.status, 0, LF_ERR_WAIT_FULL);
     }
   } else {
     const int quarter = warp & 3;
+    const int cbeg = ((warp - 2) >> 2) * 64;
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const int qi = q0 + row;
@@ -632,45 +705,51 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     const long long tok = seq_start + qi;
     const float lse2 = q_valid ? p.lse[static_cast<long long>(head) * p.T + tok] * LOG2E : 0.f;
     const float dlt = q_valid ? p.delta[static_cast<long long>(head) * p.T + tok] : 0.f;
+    const float neg_lse2 = -lse2;
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int kv0 = j * 128;
-      ok = mbar_wait(&bars[Q_S_FULL], j & 1, abort_flag);
+      ok = mbar_wait_warp(&bars[Q_S_FULL], j & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
+      const int lim = q_valid ? (min(seq_len, p.causal ? qi + 1 : seq_len) - kv0) : 0;
+      const uint32_t t_s = t_s0 + (j & 1) * 128;
+      uint32_t rs0[32], rd0[32], rs1[32], rd1[32];
+      tmem_ld_32x32b_x32(t_s + lane_off + cbeg, rs0);
+      tmem_ld_32x32b_x32(t_dp + lane_off + cbeg, rd0);
+      tmem_ld_32x32b_x32(t_s + lane_off + cbeg + 32, rs1);
+      tmem_ld_32x32b_x32(t_dp + lane_off + cbeg + 32, rd1);
+      tmem_ld_wait();
+      float ds0[32], ds1[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float pr = exp2f(fmaf(__uint_as_float(rs0[i]), p.scale_log2, neg_lse2));
+        if (cbeg + i >= lim) pr = 0.f;
+        ds0[i] = pr * (__uint_as_float(rd0[i]) - dlt) * p.scale;
+        float pr1 = exp2f(fmaf(__uint_as_float(rs1[i]), p.scale_log2, neg_lse2));
+        if (cbeg + 32 + i >= lim) pr1 = 0.f;
+        ds1[i] = pr1 * (__uint_as_float(rd1[i]) - dlt) * p.scale;
+      }
+      // the dS tile is single buffered: dQ += dS[j-1] K[j-1] must have retired
       if (j > 0) {
-        ok = mbar_wait(&bars[Q_ACC_DONE], (j - 1) & 1, abort_flag);
+        ok = mbar_wait_warp(&bars[Q_ACC_DONE], (j - 1) & 1, abort_flag);
         if (!ok) break;
       }
-#pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
-        uint32_t rs[32], rd[32];
-        tmem_ld_32x32b_x32(t_s + lane_off + c0, rs);
-        tmem_ld_32x32b_x32(t_dp + lane_off + c0, rd);
-        tmem_ld_wait();
-        float ds[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kj = kv0 + c0 + i;
-          const bool keep = q_valid && kj < seq_len && (!p.causal || kj <= qi);
-          const float pr = keep ? exp2f(__uint_as_float(rs[i]) * p.scale_log2 - lse2) : 0.f;
-          ds[i] = pr * (__uint_as_float(rd[i]) - dlt) * p.scale;
-        }
-        store_row_chunk(smem + BqSmem::DS, row, c0, ds);
-      }
+      store_row_chunk(smem + BqSmem::DS, row, cbeg, ds0);
+      store_row_chunk(smem + BqSmem::DS, row, cbeg + 32, ds1);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars[Q_DS_FULL]);
     }
-    if (ok && n_kv > 0) ok = mbar_wait(&bars[Q_ACC_DONE], (n_kv - 1) & 1, abort_flag);
+    if (ok && n_kv > 0) ok = mbar_wait_warp(&bars[Q_ACC_DONE], (n_kv - 1) & 1, abort_flag);
     if (!ok) {
       if (lane == 0) atomicCAS(p.status, 0, LF_ERR_WAIT_TMEM_FULL);
     } else {
       tc_fence_after_sync();
       __nv_bfloat16* dqrow = p.dq + tok * p.dq_ts + static_cast<long long>(g) * p.dq_gs + jh * p.dq_hs;
 #pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
+      for (int c0 = cbeg; c0 < cbeg + 64; c0 += 32) {
         uint32_t a[32];
         tmem_ld_32x32b_x32(t_dq + lane_off + c0, a);
         tmem_ld_wait();
@@ -738,14 +817,15 @@ static int make_map_q(CUtensorMap* m, const void* ptr, int T, int groups, int R,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -3;
 }
 // 3-D map (d, head, token) with box (64, 1, 128).
-static int make_map_kv(CUtensorMap* m, const void* ptr, int T, int heads, long long ts, long long hs) {
+static int make_map_kv(CUtensorMap* m, const void* ptr, int T, int heads, long long ts, long long hs,
+                       int box_rows = 128) {
   EncodeTiledFn fn = attn_encode_fn();
   if (!fn) return -1;
   if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (ts % 8) || (hs % 8)) return -2;
   cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(T)};
   cuuint64_t strides[2] = {static_cast<cuuint64_t>(hs) * 2, static_cast<cuuint64_t>(ts) * 2};
   if (heads == 1) strides[0] = 256;
-  cuuint32_t box[3] = {64, 1, 128};
+  cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(box_rows)};
   cuuint32_t es[3] = {1, 1, 1};
   return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -811,11 +891,13 @@ int attn_bwd(const AttnArgs& a, cudaStream_t stream) {
   if ((a.do_ts % 8) || (a.do_hs % 8) || (a.dq_ts % 8) || (a.dq_gs % 8) || (a.dq_hs % 8) || (a.dk_ts % 8) ||
       (a.dk_hs % 8) || (a.dv_ts % 8) || (a.dv_hs % 8))
     return -2;
-  CUtensorMap tq, tk, tv, tdo;
+  CUtensorMap tq, tk, tv, tdo, tk64, tv64;
   int rc;
   if ((rc = make_map_q(&tq, a.q, a.T, a.Hkv, R, a.q_ts, a.q_gs, a.q_hs))) return rc;
   if ((rc = make_map_kv(&tk, a.k, a.T, a.Hkv, a.k_ts, a.k_hs))) return rc;
   if ((rc = make_map_kv(&tv, a.v, a.T, a.Hkv, a.v_ts, a.v_hs))) return rc;
+  if ((rc = make_map_kv(&tk64, a.k, a.T, a.Hkv, a.k_ts, a.k_hs, 64))) return rc;
+  if ((rc = make_map_kv(&tv64, a.v, a.T, a.Hkv, a.v_ts, a.v_hs, 64))) return rc;
   // dO is [T, Hq, 128]: group stride R * head stride
   if ((rc = make_map_q(&tdo, a.dout, a.T, a.Hkv, R, a.do_ts, a.do_hs * R, a.do_hs))) return rc;
   LF_DBG("maps encoded");
@@ -835,11 +917,11 @@ int attn_bwd(const AttnArgs& a, cudaStream_t stream) {
       static_cast<const __nv_bfloat16*>(a.dout), static_cast<const __nv_bfloat16*>(a.o), a.delta, a.T, a.Hq, a.do_ts,
       a.do_hs, a.o_ts, a.o_hs);
   LF_DBG("delta launched");
-  dim3 grid_kv(max_blocks(a), a.Hkv);
-  attn_bwd_dkdv_kernel<<<grid_kv, AT_THREADS, BkvSmem::BYTES, stream>>>(tq, tk, tv, tdo, p);
+  dim3 grid_kv(2 * max_blocks(a), a.Hkv);
+  attn_bwd_dkdv_kernel<<<grid_kv, AT_BWD_THREADS, BkvSmem::BYTES, stream>>>(tq, tk64, tv64, tdo, p);
   LF_DBG("dkdv launched");
   dim3 grid_q(max_blocks(a), a.Hq);
-  attn_bwd_dq_kernel<<<grid_q, AT_THREADS, BqSmem::BYTES, stream>>>(tq, tk, tv, tdo, p);
+  attn_bwd_dq_kernel<<<grid_q, AT_BWD_THREADS, BqSmem::BYTES, stream>>>(tq, tk, tv, tdo, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

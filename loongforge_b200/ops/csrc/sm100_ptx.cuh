@@ -89,6 +89,42 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Warp-collective bounded wait for warps that share an SM sub-partition with busy math warps:
+// only lane 0 polls, with the NON-blocking test_wait and a short sleep between polls, so that a
+// waiting warp neither floods shared memory nor sits inside a blocking instruction.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  int ok = 1;
+  if (lane_id() == 0) {
+    if (!mbar_test_wait(bar, parity)) {
+      const long long t0 = clock64();
+      uint32_t spins = 0;
+      while (!mbar_test_wait(bar, parity)) {
+        __nanosleep(20);
+        if ((++spins & 0xff) == 0) {
+          if (*abort_flag || clock64() - t0 > LF_WAIT_BUDGET_CYCLES) {
+            *abort_flag = 1;
+            ok = 0;
+            break;
+          }
+        }
+      }
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
+}
+
 // ---------------------------------------------------------------- TMA (tiled bulk tensor copies)
 // The innermost coordinate times the element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int32_t x,
