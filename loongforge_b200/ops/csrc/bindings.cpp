@@ -330,53 +330,96 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
 
 #ifdef LF_HAVE_PEER
 // ------------------------------------------------------------------ fused TP GEMMs over peer memory
-at::Tensor ag_gemm(const at::Tensor& x_local, const at::Tensor& peer_ptrs, int64_t rank, int64_t world,
-                   const at::Tensor& W, const at::Tensor& x_full, const at::Tensor& flags_ptrs, int64_t epoch,
-                   c10::optional<at::Tensor> bias, const at::Tensor& status) {
-  c10::cuda::CUDAGuard guard(W.device());
+// Peer pointers are plain integers (device virtual addresses obtained from the symmetric-memory
+// rendezvous); index r is rank r of the tensor-parallel group.
+at::Tensor ag_gemm(std::vector<int64_t> peer_x, std::vector<int64_t> peer_sync, at::Tensor x_full,
+                   at::Tensor chunk_flags, const at::Tensor& B, bool b_mn_major, c10::optional<at::Tensor> bias,
+                   int64_t rank, int64_t rows_per_rank, int64_t epoch, int64_t copy_ctas, const at::Tensor& status) {
+  check_bf16_cuda(B, "B");
+  check_bf16_cuda(x_full, "x_full");
+  TORCH_CHECK(B.dim() == 2 && B.stride(1) == 1 && x_full.dim() == 2 && x_full.is_contiguous());
+  TORCH_CHECK(chunk_flags.scalar_type() == at::kInt && chunk_flags.is_contiguous());
+  c10::cuda::CUDAGuard guard(B.device());
+  const int64_t world = static_cast<int64_t>(peer_x.size());
+  TORCH_CHECK(world >= 1 && world <= lf::kMaxPeers && static_cast<int64_t>(peer_sync.size()) == world);
+  const int64_t K = x_full.size(1);
+  const int64_t N = b_mn_major ? B.size(1) : B.size(0);
+  TORCH_CHECK((b_mn_major ? B.size(0) : B.size(1)) == K, "contraction mismatch");
+  TORCH_CHECK(x_full.size(0) == rows_per_rank * world && chunk_flags.numel() >= x_full.size(0) / 128);
   lf::AgGemmArgs a;
-  a.peer_x = reinterpret_cast<const void* const*>(peer_ptrs.data_ptr<int64_t>());
-  a.peer_flags = reinterpret_cast<int* const*>(flags_ptrs.data_ptr<int64_t>());
+  for (int64_t r = 0; r < world; ++r) {
+    a.peer_x[r] = reinterpret_cast<const void*>(peer_x[r]);
+    a.peer_sync[r] = reinterpret_cast<int*>(peer_sync[r]);
+  }
+  a.x_full = x_full.data_ptr();
+  a.chunk_flags = chunk_flags.data_ptr<int>();
+  a.B = B.data_ptr();
+  a.ldb = B.stride(0);
+  a.b_mn_major = b_mn_major;
+  at::Tensor out = at::empty({x_full.size(0), N}, B.options());
+  a.out = out.data_ptr();
+  a.ldo = N;
+  if (bias.has_value()) {
+    check_bf16_cuda(*bias, "bias");
+    TORCH_CHECK(bias->numel() == N && bias->is_contiguous());
+    a.bias = bias->data_ptr();
+  }
   a.rank = static_cast<int>(rank);
   a.world = static_cast<int>(world);
-  a.rows_per_rank = static_cast<int>(x_local.size(0));
-  a.K = static_cast<int>(x_local.size(1));
-  a.N = static_cast<int>(W.size(0));
-  a.W = W.data_ptr();
-  a.x_full = x_full.data_ptr();
+  a.rows_per_rank = static_cast<int>(rows_per_rank);
+  a.K = static_cast<int>(K);
+  a.N = static_cast<int>(N);
   a.epoch = static_cast<int>(epoch);
-  a.bias = bias.has_value() ? bias->data_ptr() : nullptr;
+  a.copy_ctas = static_cast<int>(copy_ctas);
   a.status = status.data_ptr<int>();
-  at::Tensor out = at::empty({x_local.size(0) * world, W.size(0)}, W.options());
-  a.out = out.data_ptr();
   const int rc = lf::ag_gemm(a, cur_stream());
   TORCH_CHECK(rc == 0, "lf::ag_gemm failed with code ", rc);
-  g_launches += 2;
+  ++g_launches;
   return out;
 }
 
-at::Tensor gemm_rs(const at::Tensor& x, const at::Tensor& W, const at::Tensor& partial_ptrs,
-                   const at::Tensor& flags_ptrs, int64_t rank, int64_t world, int64_t epoch,
-                   c10::optional<at::Tensor> residual, const at::Tensor& status) {
-  c10::cuda::CUDAGuard guard(W.device());
+at::Tensor gemm_rs(const at::Tensor& A, const at::Tensor& B, bool b_mn_major, std::vector<int64_t> peer_recv,
+                   std::vector<int64_t> peer_tile_flags, c10::optional<at::Tensor> residual, int64_t rank,
+                   int64_t call_index, const at::Tensor& status) {
+  check_bf16_cuda(A, "A");
+  check_bf16_cuda(B, "B");
+  TORCH_CHECK(A.dim() == 2 && A.stride(1) == 1 && B.dim() == 2 && B.stride(1) == 1);
+  c10::cuda::CUDAGuard guard(B.device());
+  const int64_t world = static_cast<int64_t>(peer_recv.size());
+  TORCH_CHECK(world >= 1 && world <= lf::kMaxPeers && static_cast<int64_t>(peer_tile_flags.size()) == world);
+  const int64_t T = A.size(0), K = A.size(1);
+  const int64_t N = b_mn_major ? B.size(1) : B.size(0);
+  TORCH_CHECK((b_mn_major ? B.size(0) : B.size(1)) == K, "contraction mismatch");
   lf::GemmRsArgs a;
-  a.x = x.data_ptr();
-  a.W = W.data_ptr();
-  a.M = static_cast<int>(x.size(0));
-  a.K = static_cast<int>(x.size(1));
-  a.N = static_cast<int>(W.size(0));
-  a.peer_partial = reinterpret_cast<void* const*>(partial_ptrs.data_ptr<int64_t>());
-  a.peer_flags = reinterpret_cast<int* const*>(flags_ptrs.data_ptr<int64_t>());
+  a.A = A.data_ptr();
+  a.lda = A.stride(0);
+  a.B = B.data_ptr();
+  a.ldb = B.stride(0);
+  a.b_mn_major = b_mn_major;
+  for (int64_t r = 0; r < world; ++r) {
+    a.peer_recv[r] = reinterpret_cast<void*>(peer_recv[r]);
+    a.peer_tile_flags[r] = reinterpret_cast<int*>(peer_tile_flags[r]);
+  }
+  at::Tensor out = at::empty({T / world, N}, B.options());
+  a.out = out.data_ptr();
+  a.ldo = N;
+  if (residual.has_value()) {
+    check_bf16_cuda(*residual, "residual");
+    TORCH_CHECK(residual->dim() == 2 && residual->size(0) == T / world && residual->size(1) == N &&
+                residual->stride(1) == 1);
+    a.residual = residual->data_ptr();
+    a.ldr = residual->stride(0);
+  }
   a.rank = static_cast<int>(rank);
   a.world = static_cast<int>(world);
-  a.epoch = static_cast<int>(epoch);
-  a.residual = residual.has_value() ? residual->data_ptr() : nullptr;
+  a.T = static_cast<int>(T);
+  a.K = static_cast<int>(K);
+  a.N = static_cast<int>(N);
+  a.call_index = static_cast<int>(call_index);
   a.status = status.data_ptr<int>();
-  at::Tensor out = at::empty({x.size(0) / world, W.size(0)}, W.options());
-  a.out = out.data_ptr();
   const int rc = lf::gemm_rs(a, cur_stream());
   TORCH_CHECK(rc == 0, "lf::gemm_rs failed with code ", rc);
-  g_launches += 2;
+  ++g_launches;
   return out;
 }
 
