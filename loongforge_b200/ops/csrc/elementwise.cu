@@ -498,3 +498,43 @@ void sumsq(const void* x, int is_bf16, long long n, float* out, cudaStream_t s) 
 }
 
 }  // namespace lf
+
+// ============================================================================ allocation-free RMSNorm backward
+// See rmsnorm_bwd_noalloc.h. The per-CTA partial weight gradients go to a scratch array that is
+// part of the library image instead of a per-call allocation.
+#include "rmsnorm_bwd_noalloc.h"
+
+static __device__ __align__(256) float g_rmsnorm_noalloc_scratch[LF_RMSNORM_NOALLOC_MAX_CTAS * LF_RMSNORM_NOALLOC_MAX_H];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_scratch_dev_ptr[kMaxDevices] = {};  // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" int lf_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                                      float* dw, long long T, int H, float w_offset, cudaStream_t stream) {
+  if (H <= 0 || H > LF_RMSNORM_NOALLOC_MAX_H || (H % 8) != 0 || T < 0) return LF_NOALLOC_ERR_TOO_LARGE;
+  if (T == 0) return LF_NOALLOC_OK;
+  const void* ptrs[6] = {dy, x, w, rstd, dx, dw};
+  for (const void* p : ptrs)
+    if (p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) != 0) return LF_NOALLOC_ERR_BAD_POINTER;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return LF_NOALLOC_ERR_CUDA;
+  float* scratch = g_scratch_dev_ptr[dev];
+  if (scratch == nullptr) {
+    // One-time set-up for this device (it is current): in host code the array's name is only a
+    // stand-in for the symbol, so ask the runtime for its address in device memory.
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_rmsnorm_noalloc_scratch) != cudaSuccess || p == nullptr) return LF_NOALLOC_ERR_CUDA;
+    scratch = static_cast<float*>(p);
+    g_scratch_dev_ptr[dev] = scratch;
+  }
+  const int grid = static_cast<int>(T < LF_RMSNORM_NOALLOC_MAX_CTAS ? T : LF_RMSNORM_NOALLOC_MAX_CTAS);
+  // Every CTA writes its full row [0, H) of the scratch and the column sum reads exactly rows
+  // [0, grid) x [0, H): stale contents of earlier calls are never read, so no clearing is needed.
+  lf::rmsnorm_bwd_kernel<<<grid, lf::NORM_THREADS, 0, stream>>>(
+      static_cast<const lf::bf16*>(dy), static_cast<const lf::bf16*>(x), static_cast<const lf::bf16*>(w), rstd,
+      nullptr, static_cast<lf::bf16*>(dx), scratch, static_cast<int>(T), H, w_offset);
+  lf::colsum_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(scratch, grid, H, dw, nullptr, 0);
+  return cudaGetLastError() == cudaSuccess ? LF_NOALLOC_OK : LF_NOALLOC_ERR_CUDA;
+}
