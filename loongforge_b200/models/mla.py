@@ -1,0 +1,205 @@
+"""Multi-latent attention (DeepSeek-V2/V3) and its sparse variant with the lightning indexer (V3.2).
+
+Counterpart of the reference's ``MLASelfAttentionFused`` / ``DSAIndexerFused`` / ``DSAttentionFused``
+(loongforge/models/common/experimental_attention_variant/multi_latent_attention.py:66-1338,
+dsa_fused.py:111-971). Parameter names follow the converter map
+(configs/models/deepseek3/ckpt_convert/deepseek_v3_2_convert.yaml:70-150):
+``linear_q_down_proj``, ``q_layernorm``, ``linear_q_up_proj``, ``linear_kv_down_proj``,
+``kv_layernorm``, ``linear_kv_up_proj``, ``linear_proj`` and
+``core_attention.indexer.{linear_wq_b,linear_wk,k_norm,linear_weights_proj}``.
+
+Dense MLA materialises per-head K/V from the latent (192-dim keys, 128-dim values). DSA runs the
+ABSORBED form: queries are projected into the 512-dim latent space with W_uk, attention runs
+against the shared ``[kv_c | k_pe]`` (576-dim) rows selected by the indexer, and the 512-dim result
+is projected with W_uv. Down projections are replicated across TP ranks; heads are TP-sharded.
+Under context parallelism the compressed KV (576 values per token) is all-gathered, which is cheap
+for MLA, and each rank attends from its own query chunk.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from ..ops import dsa_ops
+from ..ops import functional as OF
+from ..parallel import layers as PL
+from ..parallel import mappings as M
+from ..parallel import state as ps
+from .config import TransformerConfig
+from .moe import AuxLossScaler, track_aux_loss
+
+
+class _ReplicatedLinear(nn.Module):
+    """[out, in] weight held by every TP rank (TP-duplicated down projections)."""
+
+    def __init__(self, in_f, out_f, key, cfg, device=None, bias=False):
+        super().__init__()
+        w = PL.init_full_then_slice(key + ".weight", (out_f, in_f), cfg.init_method_std, partition_dim=None, rank=0,
+                                    world=1, device=device or "cpu", dtype=cfg.params_dtype)
+        self.weight = nn.Parameter(w)
+        PL.mark_tp(self.weight, None, sequence_parallel=cfg.sequence_parallel)
+        if bias:
+            self.bias = nn.Parameter(torch.zeros(out_f, dtype=cfg.params_dtype, device=device))
+            PL.mark_tp(self.bias, None, sequence_parallel=cfg.sequence_parallel)
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, x):
+        return OF.linear(x, self.weight, self.bias)
+
+
+def _rope_pe(t: torch.Tensor, rotary, interleaved: bool = True) -> torch.Tensor:
+    """RoPE on a [T, heads, d_pe] tensor (DeepSeek stores the rotary pairs interleaved)."""
+    return OF.rope(t, rotary.freqs, pos_ids=rotary.pos_ids, interleaved=interleaved, mscale=1.0)
+
+
+class DSAIndexer(nn.Module):
+    def __init__(self, cfg: TransformerConfig, key: str, device=None):
+        super().__init__()
+        self.cfg = cfg
+        self.nh, self.d = cfg.dsa_indexer_n_heads, cfg.dsa_indexer_head_dim
+        q_in = cfg.q_lora_rank or cfg.hidden_size
+        self.linear_wq_b = _ReplicatedLinear(q_in, self.nh * self.d, key + ".linear_wq_b", cfg, device)
+        self.linear_wk = _ReplicatedLinear(cfg.hidden_size, self.d, key + ".linear_wk", cfg, device)
+        self.k_norm = nn.LayerNorm(self.d, eps=1e-6, device=device, dtype=cfg.params_dtype)
+        self.linear_weights_proj = _ReplicatedLinear(cfg.hidden_size, self.nh, key + ".linear_weights_proj", cfg, device)
+        self.rope_dim = cfg.qk_pos_emb_head_dim
+        self.softmax_scale = self.d ** -0.5
+
+    def project(self, x, q_c, rotary):
+        """x [T, h], q_c [T, q_lora] (both detached by the caller) -> q [T, Hi, D], k [T, D], w [T, Hi]."""
+        T = x.shape[0]
+        q = self.linear_wq_b(q_c).view(T, self.nh, self.d)
+        k = self.k_norm(self.linear_wk(x))
+        # rotary part comes FIRST in the indexer's head layout (non-interleaved halves)
+        q = OF.rope(q, rotary.freqs, pos_ids=rotary.pos_ids, rot_dim=self.rope_dim, rot_offset=0, interleaved=False)
+        k = OF.rope(k.view(T, 1, self.d), rotary.freqs, pos_ids=rotary.pos_ids, rot_dim=self.rope_dim, rot_offset=0,
+                    interleaved=False).view(T, self.d)
+        q = dsa_ops.hadamard_transform(q)
+        k = dsa_ops.hadamard_transform(k)
+        w = self.linear_weights_proj(x).float() * (self.nh ** -0.5) * self.softmax_scale
+        return q, k, w
+
+
+class MLASelfAttention(nn.Module):
+    def __init__(self, cfg: TransformerConfig, key: str, layer_number: int, *, device=None, parallel_state=None):
+        super().__init__()
+        self.cfg, self.layer_number, self.state_name = cfg, layer_number, parallel_state
+        st = ps.get_state(parallel_state)
+        tp = st.dims.tp
+        nh = cfg.num_attention_heads
+        assert nh % tp == 0
+        self.nh_local = nh // tp
+        self.dn, self.dr, self.dv, self.dc = cfg.qk_head_dim, cfg.qk_pos_emb_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
+        qd = self.dn + self.dr
+        common = dict(init_std=cfg.init_method_std, params_dtype=cfg.params_dtype, device=device,
+                      parallel_state=parallel_state)
+        if cfg.q_lora_rank:
+            self.linear_q_down_proj = _ReplicatedLinear(cfg.hidden_size, cfg.q_lora_rank, key + ".linear_q_down_proj",
+                                                        cfg, device)
+            from .transformer import Norm
+            self.q_layernorm = Norm(cfg.q_lora_rank, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
+            self.linear_q_up_proj = PL.ColumnParallelLinear(cfg.q_lora_rank, nh * qd, key=key + ".linear_q_up_proj",
+                                                            **common)
+        else:
+            self.linear_q_proj = PL.ColumnParallelLinear(cfg.hidden_size, nh * qd, key=key + ".linear_q_proj", **common)
+        self.linear_kv_down_proj = _ReplicatedLinear(cfg.hidden_size, self.dc + self.dr, key + ".linear_kv_down_proj",
+                                                     cfg, device)
+        from .transformer import Norm
+        self.kv_layernorm = Norm(self.dc, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
+        self.linear_kv_up_proj = PL.ColumnParallelLinear(self.dc, nh * (self.dn + self.dv),
+                                                         key=key + ".linear_kv_up_proj", **common)
+        common["init_std"] = cfg.init_method_std / math.sqrt(2.0 * cfg.num_layers)
+        self.linear_proj = PL.RowParallelLinear(nh * self.dv, cfg.hidden_size, key=key + ".linear_proj",
+                                                sequence_parallel=cfg.sequence_parallel, **common)
+        if cfg.use_dsa:
+            self.core_attention = nn.Module()
+            self.core_attention.indexer = DSAIndexer(cfg, key + ".core_attention.indexer", device)
+        self.mscale = 1.0  # set from the rotary inputs (YaRN)
+
+    def _softmax_scale(self, rotary) -> float:
+        m = rotary.mscale if rotary is not None else 1.0
+        return (m * m) / math.sqrt(self.dn + self.dr)
+
+    def forward(self, x, rotary, packed, residual=None):
+        cfg = self.cfg
+        st = ps.get_state(self.state_name)
+        g_tp = st.group("tp")
+        if cfg.sequence_parallel and st.dims.tp > 1:
+            x = M.gather_from_sequence_parallel_region(x, g_tp, True)
+        T = x.shape[0]
+        H = self.nh_local
+        # ---- latents
+        if cfg.q_lora_rank:
+            q_c = self.q_layernorm(self.linear_q_down_proj(x))
+            q = self.linear_q_up_proj(q_c)
+        else:
+            q_c = x
+            q = self.linear_q_proj(x)
+        q = q.view(T, H, self.dn + self.dr)
+        kv = self.linear_kv_down_proj(x)
+        kv_c = self.kv_layernorm(kv[:, : self.dc].contiguous())
+        k_pe = kv[:, self.dc:].contiguous().view(T, 1, self.dr)
+        q_nope, q_pe = q[..., : self.dn], q[..., self.dn:]
+        if rotary is not None:
+            q_pe = _rope_pe(q_pe.contiguous(), rotary)
+            k_pe = _rope_pe(k_pe, rotary)
+        scale = self._softmax_scale(rotary)
+        cu = packed.cu_seqlens if packed is not None else None
+        w_up = self.linear_kv_up_proj.weight.view(H, self.dn + self.dv, self.dc)
+        if not cfg.use_dsa:
+            kvu = self.linear_kv_up_proj(kv_c).view(T, H, self.dn + self.dv)
+            k = torch.cat([kvu[..., : self.dn], k_pe.expand(T, H, self.dr)], dim=-1)
+            v = kvu[..., self.dn:]
+            qq = torch.cat([q_nope, q_pe], dim=-1)
+            o = OF.attention(qq.contiguous(), k.contiguous(), v.contiguous(), causal=True, scale=scale, cu_seqlens=cu)
+        else:
+            o = self._dsa(x, q_c, q_nope, q_pe, kv_c, k_pe, w_up, rotary, cu, scale)
+        return self.linear_proj(o.reshape(T, H * self.dv), residual)
+
+    # ------------------------------------------------------------------ sparse path
+    def _dsa(self, x, q_c, q_nope, q_pe, kv_c, k_pe, w_up, rotary, cu, scale):
+        cfg = self.cfg
+        st = ps.get_state(self.state_name)
+        T, H = q_nope.shape[0], self.nh_local
+        w_uk, w_uv = w_up[:, : self.dn, :], w_up[:, self.dn:, :]  # [H, dn, dc], [H, dv, dc]
+        # absorbed query: q_nope @ W_uk -> latent space; key = [kv_c | k_pe] shared by all heads
+        q_abs = torch.einsum("thd,hdc->thc", q_nope, w_uk.to(q_nope.dtype))
+        query = torch.cat([q_abs, q_pe], dim=-1)  # [T, H, dc + dr]
+        key = torch.cat([kv_c, k_pe.view(T, self.dr)], dim=-1)  # [T, dc + dr]
+        pos = rotary.pos_ids.long() if (rotary is not None and rotary.pos_ids is not None) else torch.arange(T, device=x.device)
+        seg = None
+        if cu is not None:
+            seg = torch.bucketize(torch.arange(T, device=x.device), cu[1:].long().to(x.device), right=True)
+        key_all, pos_k, seg_k = key, pos, seg
+        if st.dims.cp > 1:
+            g = st.group("cp")
+            key_all = M.gather_from_sequence_parallel_region(key, g, True)
+            pos_k = M._all_gather_dim0(pos, g)
+            seg_k = M._all_gather_dim0(seg, g) if seg is not None else None
+        idxr = self.core_attention.indexer
+        qi, ki, wi = idxr.project(x.detach(), q_c.detach(), rotary)
+        ki_all = M._all_gather_dim0(ki, st.group("cp")) if st.dims.cp > 1 else ki
+        with torch.no_grad():
+            qq, _ = dsa_ops.quant_fp8_rowwise_pow2(qi) if cfg.fp8 else (qi, None)
+            kq, _ = dsa_ops.quant_fp8_rowwise_pow2(ki_all) if cfg.fp8 else (ki_all, None)
+            indices, _ = dsa_ops.indexer_topk(qq, kq, wi, cfg.dsa_indexer_topk, pos, pos_k, seg, seg_k)
+        want_loss = self.training and cfg.dsa_indexer_loss_coeff > 0
+        out = dsa_ops.sparse_mla_attention(query, key_all, indices, scale, d_v=self.dc,
+                                           return_head_mean_probs=want_loss)
+        if want_loss:
+            o_c, pmean = out
+            # index scores at the selected slots, differentiable w.r.t. the indexer weights only
+            kg = ki_all[indices.clamp_min(0)]
+            sc = (torch.relu(torch.einsum("mhd,mkd->mhk", qi.float(), kg.float())) * wi.unsqueeze(-1)).sum(1)
+            loss = dsa_ops.indexer_kl_loss(sc, pmean, indices, cfg.dsa_indexer_loss_coeff)
+            if st.dims.tp > 1:
+                loss = M.reduce_from_tensor_model_parallel_region(loss, st.group("tp")) / st.dims.tp
+            track_aux_loss("indexer_loss", loss / cfg.dsa_indexer_loss_coeff, self.layer_number, cfg.num_layers)
+            o_c = AuxLossScaler.apply(o_c, loss)
+        else:
+            o_c = out
+        return torch.einsum("thc,hvc->thv", o_c, w_uv.to(o_c.dtype))

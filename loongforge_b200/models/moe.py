@@ -1,0 +1,256 @@
+"""Mixture-of-experts layer: router, all-to-all token dispatcher over the expert-parallel group,
+grouped expert MLP, optional shared expert.
+
+Counterpart of Megatron's ``MoELayer`` / ``TopKRouter`` / ``MoEAlltoAllTokenDispatcher`` /
+``TEGroupedMLP`` that the reference wires in its specs
+(loongforge/models/foundation/qwen3/qwen_layer_spec.py:30-69,
+loongforge/models/foundation/deepseek/deepseek_layer_spec.py:153-205); routing semantics follow the
+in-tree copy of the routing function (loongforge/models/foundation/ernie4_5_vl/ernie_router.py:32-140).
+Parameter names: ``router.weight``, ``router.expert_bias``, ``experts.linear_fc{1,2}.weight{e}``
+(grouped-GEMM naming, configs/models/qwen3/ckpt_convert/qwen3_moe_convert.yaml:47-82),
+``shared_experts.linear_fc{1,2}.weight``.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..ops import functional as OF
+from ..ops import moe_ops
+from ..parallel import layers as PL
+from ..parallel import mappings as M
+from ..parallel import state as ps
+from .config import TransformerConfig
+
+# Aux-loss values of the current step, keyed by name; the trainer logs and clears them
+# (reference: MoE aux-loss tracker, loongforge/train/training_utils.py:2203-2242).
+AUX_LOSS_TRACKER = {}
+
+
+def track_aux_loss(name: str, value: torch.Tensor, layer: int, num_layers: int):
+    t = AUX_LOSS_TRACKER.get(name)
+    if t is None:
+        t = torch.zeros(num_layers, dtype=torch.float32, device=value.device)
+        AUX_LOSS_TRACKER[name] = t
+    t[layer] += value.detach().float()
+
+
+class AuxLossScaler(torch.autograd.Function):
+    """Attach an auxiliary loss to an activation: identity forward, and backward adds the aux
+    loss's gradient with weight ``scale`` (set to the main loss scale by the trainer)."""
+
+    scale = 1.0
+
+    @staticmethod
+    def forward(ctx, x, aux):
+        ctx.save_for_backward(aux)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        (aux,) = ctx.saved_tensors
+        return g, torch.full_like(aux, AuxLossScaler.scale)
+
+
+class TopKRouter(nn.Module):
+    def __init__(self, cfg: TransformerConfig, key: str, layer_number: int, device=None):
+        super().__init__()
+        self.cfg, self.layer_number = cfg, layer_number
+        E = cfg.num_moe_experts
+        w = PL.init_full_then_slice(key + ".weight", (E, cfg.hidden_size), cfg.init_method_std, partition_dim=None,
+                                    rank=0, world=1, device=device or "cpu", dtype=torch.float32)
+        self.weight = nn.Parameter(w)  # router runs in fp32
+        PL.mark_tp(self.weight, None, sequence_parallel=cfg.sequence_parallel)
+        if cfg.moe_router_enable_expert_bias:
+            self.register_buffer("expert_bias", torch.zeros(E, dtype=torch.float32, device=device))
+            self.register_buffer("local_tokens_per_expert", torch.zeros(E, dtype=torch.float32, device=device),
+                                 persistent=False)
+        else:
+            self.expert_bias = None
+
+    def forward(self, x: torch.Tensor, seq_lens: Optional[List[int]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """x [T, H] -> (probs [T, E] fp32 (zero outside the top-k), routing_map [T, E] bool)."""
+        cfg = self.cfg
+        logits = torch.nn.functional.linear(x.float(), self.weight.float())
+        if cfg.moe_z_loss_coeff:
+            z = torch.logsumexp(logits, dim=-1).square().mean() * cfg.moe_z_loss_coeff
+            track_aux_loss("z_loss", z / cfg.moe_z_loss_coeff, self.layer_number, cfg.num_layers)
+            logits = AuxLossScaler.apply(logits, z)
+        probs, routing_map, scores_for_aux = moe_ops.topk_routing(
+            logits, cfg.moe_router_topk, score_function=cfg.moe_router_score_function,
+            pre_softmax=cfg.moe_router_pre_softmax, expert_bias=self.expert_bias,
+            num_groups=cfg.moe_router_num_groups, group_topk=cfg.moe_router_group_topk,
+            scaling_factor=cfg.moe_router_topk_scaling_factor)
+        if self.expert_bias is not None and self.training:
+            with torch.no_grad():
+                self.local_tokens_per_expert += routing_map.sum(0).float()
+        if self.training and cfg.moe_aux_loss_coeff and cfg.moe_router_load_balancing_type != "none":
+            kind = cfg.moe_router_load_balancing_type
+            if kind == "seq_aux_loss" and seq_lens is not None:
+                aux = moe_ops.seq_aux_loss(scores_for_aux, routing_map, cfg.moe_router_topk, seq_lens,
+                                           cfg.moe_aux_loss_coeff)
+            else:
+                aux = moe_ops.switch_aux_loss(scores_for_aux, routing_map.sum(0), cfg.moe_router_topk,
+                                              cfg.moe_aux_loss_coeff)
+            track_aux_loss("load_balancing_loss", aux / cfg.moe_aux_loss_coeff, self.layer_number, cfg.num_layers)
+            probs = AuxLossScaler.apply(probs, aux)
+        return probs, routing_map
+
+    @torch.no_grad()
+    def update_expert_bias(self, group=None):
+        """Aux-loss-free balancing: raise the bias of under-loaded experts, lower over-loaded ones
+        (reference call site: loongforge/train/training_utils.py:2203-2226)."""
+        if self.expert_bias is None:
+            return
+        cnt = self.local_tokens_per_expert.clone()
+        if group is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(cnt, group=group)
+        self.expert_bias += torch.sign(cnt.mean() - cnt) * self.cfg.moe_router_bias_update_rate
+        self.local_tokens_per_expert.zero_()
+
+
+class GroupedLinear(nn.Module):
+    """E_local independent [out, in] weights named ``weight0..weight{E-1}``; applies each to its
+    contiguous slice of a token list sorted by expert."""
+
+    def __init__(self, num_local: int, first_global: int, in_f: int, out_f: int, key: str, std: float,
+                 cfg: TransformerConfig, device=None, stride: int = 1):
+        super().__init__()
+        self.num_local = num_local
+        for e in range(num_local):
+            w = PL.init_full_then_slice(f"{key}.weight{first_global + e}", (out_f, in_f), std, partition_dim=None,
+                                        rank=0, world=1, device=device or "cpu", dtype=cfg.params_dtype)
+            p = nn.Parameter(w)
+            PL.mark_tp(p, None)
+            p.is_expert = True
+            p.partition_stride = stride
+            self.register_parameter(f"weight{e}", p)
+
+    def weights(self):
+        return [getattr(self, f"weight{e}") for e in range(self.num_local)]
+
+    def forward(self, x: torch.Tensor, tokens_per_expert: List[int]) -> torch.Tensor:
+        return moe_ops.grouped_linear(x, self.weights(), tokens_per_expert)
+
+
+class GroupedMLP(nn.Module):
+    def __init__(self, cfg: TransformerConfig, key: str, num_local: int, first_global: int, device=None):
+        super().__init__()
+        f = cfg.moe_ffn_hidden_size
+        glu = cfg.gated_linear_unit
+        self.linear_fc1 = GroupedLinear(num_local, first_global, cfg.hidden_size, f * (2 if glu else 1),
+                                        key + ".linear_fc1", cfg.init_method_std, cfg, device, stride=2 if glu else 1)
+        self.linear_fc2 = GroupedLinear(num_local, first_global, f, cfg.hidden_size, key + ".linear_fc2",
+                                        cfg.init_method_std / math.sqrt(2.0 * cfg.num_layers), cfg, device)
+        self.glu = glu
+        self.act = cfg.activation
+
+    def forward(self, x, tokens_per_expert):
+        h = self.linear_fc1(x, tokens_per_expert)
+        if self.glu and self.act == "swiglu":
+            h = OF.swiglu(h)
+        elif self.glu:
+            g, u = h.chunk(2, -1)
+            h = torch.nn.functional.gelu(g) * u
+        else:
+            h = torch.nn.functional.gelu(h)
+        return self.linear_fc2(h, tokens_per_expert)
+
+
+class AlltoAllDispatcher:
+    """permute -> all-to-all(v) over EP -> sort by local expert; and the exact inverse.
+    Splits are exchanged on the host (one small all_to_all of counts), as Megatron's
+    alltoall dispatcher does."""
+
+    def __init__(self, num_experts: int, state_name=None):
+        st = ps.get_state(state_name)
+        self.ep, self.ep_rank, self.group = st.dims.ep, st.ep_rank, st.group("ep")
+        self.E = num_experts
+        self.E_local = num_experts // self.ep
+
+    def dispatch(self, x, probs, routing_map):
+        T, H = x.shape
+        # (expert, token) pairs in expert-major order
+        emap = routing_map.t().contiguous()
+        expert_idx, token_idx = emap.nonzero(as_tuple=True)
+        self.token_idx = token_idx
+        self.sel_probs = probs.t()[expert_idx, token_idx]
+        self.T = T
+        permuted = x.index_select(0, token_idx)
+        counts = emap.sum(1)  # tokens per global expert (local tokens)
+        if self.ep == 1:
+            self.tpe = counts.tolist()
+            return permuted, self.tpe
+        # counts matrix: what every EP rank sends to each of my local experts
+        send_counts = counts.view(self.ep, self.E_local)
+        recv_counts = torch.empty_like(send_counts)
+        if send_counts.is_cuda:
+            dist.all_to_all_single(recv_counts, send_counts.contiguous(), group=self.group)
+        else:
+            M.all_to_all_single(recv_counts, send_counts.contiguous(), None, None, self.group)
+        self.in_splits = send_counts.sum(1).tolist()
+        rc = recv_counts.cpu()
+        self.out_splits = rc.sum(1).tolist()
+        recv = M.all_to_all(permuted, self.group, self.out_splits, self.in_splits)
+        # received order is [src rank][local expert]; experts need [local expert][src rank]
+        chunk_sizes = rc.reshape(-1).tolist()
+        order = [s * self.E_local + e for e in range(self.E_local) for s in range(self.ep)]
+        self.chunk_sizes, self.order = chunk_sizes, order
+        chunks = recv.split(chunk_sizes, 0)
+        sorted_tokens = torch.cat([chunks[i] for i in order], 0) if len(chunks) > 1 else recv
+        self.tpe = rc.sum(0).tolist()
+        return sorted_tokens, self.tpe
+
+    def combine(self, y):
+        if self.ep > 1:
+            sizes_sorted = [self.chunk_sizes[i] for i in self.order]
+            chunks = y.split(sizes_sorted, 0)
+            inv = [0] * len(self.order)
+            for pos, i in enumerate(self.order):
+                inv[i] = pos
+            y = torch.cat([chunks[inv[i]] for i in range(len(self.order))], 0) if len(chunks) > 1 else y
+            y = M.all_to_all(y, self.group, self.in_splits, self.out_splits)
+        y = y * self.sel_probs.to(y.dtype).unsqueeze(-1)
+        out = torch.zeros(self.T, y.shape[1], dtype=y.dtype, device=y.device)
+        return out.index_add(0, self.token_idx, y)
+
+
+class MoELayer(nn.Module):
+    def __init__(self, cfg: TransformerConfig, key: str, layer_number: int, *, device=None, parallel_state=None):
+        super().__init__()
+        self.cfg, self.layer_number, self.state_name = cfg, layer_number, parallel_state
+        st = ps.get_state(parallel_state)
+        E, ep = cfg.num_moe_experts, st.dims.ep
+        assert E % ep == 0, "num_moe_experts must divide by expert parallel size"
+        self.E_local = E // ep
+        self.router = TopKRouter(cfg, key + ".router", layer_number, device=device)
+        self.experts = GroupedMLP(cfg, key + ".experts", self.E_local, st.ep_rank * self.E_local, device=device)
+        if cfg.moe_shared_expert_intermediate_size:
+            from .transformer import MLP
+            self.shared_experts = MLP(cfg, key + ".shared_experts", ffn_hidden=cfg.moe_shared_expert_intermediate_size,
+                                      fused_norm=False, device=device, parallel_state=parallel_state,
+                                      sequence_parallel=False)
+        else:
+            self.shared_experts = None
+        self.dispatcher = AlltoAllDispatcher(E, parallel_state)
+
+    def forward(self, x: torch.Tensor, seq_lens=None) -> torch.Tensor:
+        probs, routing_map = self.router(x, seq_lens)
+        tokens, tpe = self.dispatcher.dispatch(x, probs, routing_map)
+        y = self.experts(tokens, tpe)
+        out = self.dispatcher.combine(y)
+        if self.shared_experts is not None:
+            st = ps.get_state(self.state_name)
+            if st.dims.tp > 1:
+                # shared expert is tensor parallel over the full token set of the TP group
+                g = st.group("tp")
+                xs = M.gather_from_sequence_parallel_region(x, g, False) if self.cfg.sequence_parallel else x
+                ys = self.shared_experts(xs)
+                out = out + (M.scatter_to_sequence_parallel_region(ys, g) if self.cfg.sequence_parallel else ys)
+            else:
+                out = out + self.shared_experts(x)
+        return out

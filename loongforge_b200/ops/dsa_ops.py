@@ -1,0 +1,110 @@
+"""DeepSeek sparse attention (DSA) math: lightning indexer, top-k selection, top-k sparse MLA
+attention on the absorbed (compressed-KV) form, and the indexer KL loss.
+
+The formulas are those of the reference's torch oracles: indexer logits
+``sum_h w[m,h] * relu(q[m,h,:] . k[n,:])`` (ops/tilelang_ops/lightning_indexer.py:12-32), sparse
+attention over gathered KV rows with ``d_v = 512`` of the 576-dim key
+(ops/tilelang_ops/sparse_mla_fwd.py:218-265), and the KL between the head-averaged attention
+distribution over the selected tokens and the softmax of the index scores
+(loongforge/models/common/experimental_attention_variant/dsa_fused.py:924-956). Query rows are
+processed in blocks so that no ``[s_q, s_k]`` matrix larger than a block is ever alive.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+
+def hadamard_transform(x: torch.Tensor) -> torch.Tensor:
+    """x @ H_n / sqrt(n) on the last dim (n a power of two), fast Walsh-Hadamard butterflies."""
+    n = x.shape[-1]
+    assert n & (n - 1) == 0
+    y = x.float().reshape(-1, n)
+    h = 1
+    while h < n:
+        y = y.view(-1, n // (2 * h), 2, h)
+        a, b = y[:, :, 0, :], y[:, :, 1, :]
+        y = torch.stack([a + b, a - b], dim=2).reshape(-1, n)
+        h *= 2
+    return (y / math.sqrt(n)).reshape(x.shape).to(x.dtype)
+
+
+def quant_fp8_rowwise_pow2(x: torch.Tensor, block: int = 128, eps: float = 1e-12):
+    """1 x `block` e4m3 quantisation with power-of-two scales (emulated; returns dequantised values
+    and scales), as the indexer inputs are quantised in the reference (dsa_fused_kernels.py:2308-2315)."""
+    shp = x.shape
+    xb = x.float().reshape(-1, shp[-1] // block, block)
+    amax = xb.abs().amax(-1, keepdim=True).clamp_min(eps)
+    scale = torch.exp2(torch.ceil(torch.log2(amax / 448.0)))
+    q = (xb / scale).to(torch.float8_e4m3fn).float()
+    return (q * scale).reshape(shp), scale.reshape(*shp[:-1], shp[-1] // block)
+
+
+def indexer_logits_block(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """q [m, Hi, D], k [n, D], w [m, Hi] -> logits [m, n] = sum_h w * relu(q . k)."""
+    s = torch.einsum("mhd,nd->mhn", q.float(), k.float())
+    return (torch.relu(s) * w.float().unsqueeze(-1)).sum(1)
+
+
+def indexer_topk(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, topk: int, q_pos: torch.Tensor,
+                 k_pos: torch.Tensor, seg_q: Optional[torch.Tensor] = None, seg_k: Optional[torch.Tensor] = None,
+                 block: int = 1024) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Causal top-k key indices per query. Returns (indices [m, topk] int64 with -1 padding,
+    scores [m, topk] fp32 with -inf padding). `q_pos` / `k_pos` are global positions; `seg_*`
+    optional packed-sequence ids."""
+    m, n = q.shape[0], k.shape[0]
+    kk = min(topk, n)
+    idx_out = torch.full((m, topk), -1, dtype=torch.int64, device=q.device)
+    sc_out = torch.full((m, topk), float("-inf"), dtype=torch.float32, device=q.device)
+    for s in range(0, m, block):
+        e = min(m, s + block)
+        lg = indexer_logits_block(q[s:e], k, w[s:e])
+        mask = k_pos[None, :] <= q_pos[s:e, None]
+        if seg_q is not None:
+            mask &= seg_q[s:e, None] == seg_k[None, :]
+        lg = lg.masked_fill(~mask, float("-inf"))
+        v, i = lg.topk(kk, dim=-1)
+        i = torch.where(torch.isinf(v), torch.full_like(i, -1), i)
+        idx_out[s:e, :kk] = i
+        sc_out[s:e, :kk] = v
+    return idx_out, sc_out
+
+
+def sparse_mla_attention(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, scale: float, d_v: int = 512,
+                         block: int = 256, return_head_mean_probs: bool = False):
+    """q [m, H, Dk], kv [n, Dk] (shared by all heads), indices [m, K] (-1 = empty).
+    Returns o [m, H, d_v] (and the head-averaged attention distribution over the K slots)."""
+    m, H, Dk = q.shape
+    outs, pmeans = [], []
+    for s in range(0, m, block):
+        e = min(m, s + block)
+        idx = indices[s:e]
+        valid = idx >= 0
+        g = kv[idx.clamp_min(0)]  # [b, K, Dk]
+        sc = torch.einsum("bhd,bkd->bhk", q[s:e].float(), g.float()) * scale
+        sc = sc.masked_fill(~valid[:, None, :], float("-inf"))
+        p = torch.softmax(sc, dim=-1)
+        p = torch.nan_to_num(p)
+        outs.append(torch.einsum("bhk,bkd->bhd", p, g[..., :d_v].float()).to(q.dtype))
+        if return_head_mean_probs:
+            pmeans.append(p.mean(1))
+    o = torch.cat(outs, 0)
+    if return_head_mean_probs:
+        return o, torch.cat(pmeans, 0)
+    return o
+
+
+def indexer_kl_loss(index_scores: torch.Tensor, attn_probs_head_mean: torch.Tensor, indices: torch.Tensor,
+                    coeff: float) -> torch.Tensor:
+    """KL( attention distribution || softmax(index scores) ) over the selected slots, summed over
+    slots and queries, divided by the number of queries, times `coeff`. The attention side is a
+    constant target (detached)."""
+    valid = indices >= 0
+    tgt = attn_probs_head_mean.detach().float()
+    logq = torch.log_softmax(index_scores.float().masked_fill(~valid, float("-inf")), dim=-1)
+    logq = torch.where(valid, logq, torch.zeros_like(logq))
+    logp = torch.where(tgt > 0, torch.log(tgt.clamp_min(1e-30)), torch.zeros_like(tgt))
+    kl = (tgt * (logp - logq) * valid).sum()
+    return kl / max(index_scores.shape[0], 1) * coeff
