@@ -49,8 +49,13 @@ class ParamAndGradBuffer:
     """Flat storage for a set of parameters that share dtype and data-parallel group."""
 
     def __init__(self, params: List[nn.Parameter], named: Dict[nn.Parameter, str], cfg: DDPConfig, dp_group,
-                 dp_size: int, dp_rank: int, param_dtype: torch.dtype, grad_dtype: torch.dtype):
+                 dp_size: int, dp_rank: int, param_dtype: torch.dtype, grad_dtype: torch.dtype,
+                 grad_scale: Optional[float] = None):
         self.cfg, self.dp_group, self.dp_size, self.dp_rank = cfg, dp_group, dp_size, dp_rank
+        # Gradients are AVERAGED over the full data-parallel size. Expert parameters are reduced over
+        # the (smaller) expert-data-parallel group but already hold the token contributions of all
+        # expert-parallel ranks, so they are scaled by 1/dp as well, not 1/edp.
+        self.grad_scale = (1.0 / dp_size) if grad_scale is None else grad_scale
         self.param_dtype, self.grad_dtype = param_dtype, grad_dtype
         self.params = list(reversed(params))  # roughly backward order
         self.named = named
@@ -124,7 +129,7 @@ class DistributedDataParallel(nn.Module):
             for dt, ps_ in by_dtype.items():
                 gdt = torch.float32 if self.cfg.grad_reduce_in_fp32 else dt
                 store.append(ParamAndGradBuffer(ps_, named, self.cfg, st.group(kind), st.size(kind),
-                                                st.rank_in(kind), dt, gdt))
+                                                st.rank_in(kind), dt, gdt, grad_scale=1.0 / st.size("dp_cp")))
         self._all_buffers = self.buffers + self.expert_buffers
         self.is_last_microbatch = True
         self._comm_stream = None
@@ -164,12 +169,14 @@ class DistributedDataParallel(nn.Module):
 
     # ------------------------------------------------------------------ communication
     def _start_bucket(self, buf: ParamAndGradBuffer, b: Bucket, async_op: bool = True):
+        g = buf.grad_data[b.start:b.end]
+        scale = buf.grad_scale
         if buf.dp_size == 1:
+            if scale != 1.0:
+                g.mul_(scale)
             b.handle = True
             return
-        g = buf.grad_data[b.start:b.end]
-        scale = 1.0 / buf.dp_size
-        use_avg = self.cfg.average_in_collective and g.is_cuda
+        use_avg = self.cfg.average_in_collective and g.is_cuda and abs(scale * buf.dp_size - 1.0) < 1e-12
         if not use_avg:
             g.mul_(scale)
         op = dist.ReduceOp.AVG if use_avg else dist.ReduceOp.SUM

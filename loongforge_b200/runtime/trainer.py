@@ -173,6 +173,10 @@ class Trainer:
     def _default_forward_step(self, data_iterator, model):
         t = self.tcfg
         b = self.get_batch(data_iterator)
+        cp = self.st.dims.cp
+        if cp > 1:
+            from ..parallel.context_parallel import get_batch_on_this_cp_rank
+            b = get_batch_on_this_cp_rank(b, cp, self.st.cp_rank)
         tokens = b["tokens"].reshape(-1)
         labels = b["labels"].reshape(-1)
         mask = b["loss_mask"].reshape(-1)
@@ -182,13 +186,16 @@ class Trainer:
         if bs > 1 or "cu_seqlens" in b:
             cu = b.get("cu_seqlens")
             if cu is None:
-                cu = torch.arange(0, (bs + 1) * t.seq_length, t.seq_length, dtype=torch.int32, device=self.device)
-            packed = PackedSeqParams(cu_seqlens=cu, max_seqlen=t.seq_length)
+                sl = t.seq_length // cp
+                cu = torch.arange(0, (bs + 1) * sl, sl, dtype=torch.int32, device=self.device)
+            packed = PackedSeqParams(cu_seqlens=cu, max_seqlen=t.seq_length // cp)
         n_valid = b.get("num_valid_tokens")
         if n_valid is None:
-            n_valid = int(mask.numel())
+            n_valid = int(mask.numel()) * cp
         nmb = self.mb_calc.num_microbatches
-        scale = 1.0 / (max(n_valid, 1) * nmb)
+        # each context-parallel rank sums its own tokens; gradients are averaged over dp x cp, so the
+        # factor cp turns that average into (sum over cp, mean over dp)
+        scale = float(cp) / (max(n_valid, 1) * nmb)
         out = model(tokens, pos, labels=labels, loss_mask=mask, packed=packed, loss_scale=scale)
 
         def loss_func(losses):
