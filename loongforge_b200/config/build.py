@@ -1,0 +1,168 @@
+"""Turn (CLI args, model YAML) into the three config objects the runtime uses, with validation.
+
+Mirrors the reference's flow: model name -> YAML (loongforge/utils/config_map.py:439-460), YAML keys
+copied onto the args / config dataclass (loongforge/train/validators.py:79-122), Megatron-style
+consistency checks (validators.py:140-620). YAML keys use the reference's spelling; the table
+below maps the ones whose name differs from ``TransformerConfig``.
+"""
+from __future__ import annotations
+
+import dataclasses
+import os
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+
+from ..models.config import TransformerConfig
+from ..models.registry import get_model_config, list_models
+from ..parallel.state import ParallelDims
+from ..runtime.trainer import TrainConfig
+from . import yaml_compose
+
+REPO_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+CONFIG_DIR = os.path.join(REPO_ROOT, "configs", "models")
+
+# model name -> yaml path relative to configs/models (names follow the reference's --model-name values)
+MODEL_YAML = {
+    "llama3-8b": "llama3/llama3_8b.yaml",
+    "llama3-70b": "llama3/llama3_70b.yaml",
+    "llama2-7b": "llama2/llama2_7b.yaml",
+    "qwen2.5-7b": "qwen2.5/qwen2_5_7b.yaml",
+    "qwen3-8b": "qwen3/qwen3_8b.yaml",
+    "qwen3-14b": "qwen3/qwen3_14b.yaml",
+    "qwen3-30b-a3b": "qwen3/qwen3_30b_a3b.yaml",
+    "deepseek-v2-lite": "deepseek2/deepseek_v2_lite.yaml",
+    "deepseek-v3": "deepseek3/deepseek_v3.yaml",
+    "deepseek-v3.2": "deepseek3/deepseek_v3_2.yaml",
+    "qwen2.5-vl-7b": "qwen2.5vl/qwen2_5_vl_7b.yaml",
+}
+
+_YAML_ALIASES = {"norm_epsilon": "layernorm_epsilon", "num_experts": "num_moe_experts",
+                 "rotary_emb_base": "rotary_base", "activation_func": "activation"}
+_FIELDS = {f.name for f in dataclasses.fields(TransformerConfig)}
+
+
+def family_of(model_type: Optional[str]) -> str:
+    mt = (model_type or "llama").lower()
+    for fam in ("deepseek", "qwen3", "qwen2", "llama", "glm", "internlm", "minimax", "mimo", "ernie"):
+        if mt.startswith(fam) or fam in mt:
+            return fam
+    return mt
+
+
+def transformer_config_from_yaml(node: Dict[str, Any], base: Optional[TransformerConfig] = None) -> TransformerConfig:
+    """One model section of a YAML file -> TransformerConfig (unknown keys are kept in ``.extra``)."""
+    kw: Dict[str, Any] = dataclasses.asdict(base) if base is not None else {}
+    extra: Dict[str, Any] = {}
+    for k, v in node.items():
+        k2 = _YAML_ALIASES.get(k, k)
+        if k2 == "swiglu":
+            if v:
+                kw["activation"], kw["gated_linear_unit"] = "swiglu", True
+        elif k2 == "group_query_attention":
+            extra[k] = v
+        elif k2 == "model_type":
+            kw["model_family"] = family_of(v)
+            extra[k] = v
+        elif k2 == "moe_layer_freq" and isinstance(v, str):
+            kw[k2] = yaml_compose._moe_freq(v)
+        elif k2 in _FIELDS:
+            kw[k2] = v
+        else:
+            extra[k] = v
+    if extra.get("group_query_attention") is False:
+        kw["num_query_groups"] = None
+    if isinstance(kw.get("params_dtype"), str):
+        kw["params_dtype"] = getattr(torch, kw["params_dtype"].replace("torch.", ""))
+    cfg = TransformerConfig(**kw)
+    cfg.extra = extra
+    return cfg
+
+
+def load_model_yaml(args, overrides: List[str]) -> Optional[dict]:
+    path = args.config_file
+    if path is None and args.model_name:
+        rel = MODEL_YAML.get(args.model_name.lower().replace("_", "-"))
+        if rel and os.path.isfile(os.path.join(CONFIG_DIR, rel)):
+            path = os.path.join(CONFIG_DIR, rel)
+    if path is None:
+        return None
+    os.environ.setdefault("LOONGFORGE_PATH", REPO_ROOT)
+    return yaml_compose.compose(path, overrides)
+
+
+_ARG_TO_CFG = {
+    "num_layers": "num_layers", "hidden_size": "hidden_size", "ffn_hidden_size": "ffn_hidden_size",
+    "num_attention_heads": "num_attention_heads", "num_query_groups": "num_query_groups",
+    "kv_channels": "kv_channels", "max_position_embeddings": "max_position_embeddings",
+    "position_embedding_type": "position_embedding_type", "rotary_base": "rotary_base",
+    "rotary_percent": "rotary_percent", "rotary_scaling_factor": "rotary_scaling_factor",
+    "normalization": "normalization", "norm_epsilon": "layernorm_epsilon", "init_method_std": "init_method_std",
+    "vocab_size": "vocab_size", "num_experts": "num_moe_experts", "moe_router_topk": "moe_router_topk",
+    "moe_ffn_hidden_size": "moe_ffn_hidden_size",
+    "moe_shared_expert_intermediate_size": "moe_shared_expert_intermediate_size",
+    "moe_router_score_function": "moe_router_score_function",
+    "moe_router_bias_update_rate": "moe_router_bias_update_rate", "moe_router_num_groups": "moe_router_num_groups",
+    "moe_router_group_topk": "moe_router_group_topk",
+    "moe_router_topk_scaling_factor": "moe_router_topk_scaling_factor",
+    "moe_router_load_balancing_type": "moe_router_load_balancing_type", "moe_aux_loss_coeff": "moe_aux_loss_coeff",
+    "moe_z_loss_coeff": "moe_z_loss_coeff", "mtp_num_layers": "mtp_num_layers",
+    "mtp_loss_scaling_factor": "mtp_loss_scaling_factor", "recompute_granularity": "recompute_granularity",
+    "recompute_method": "recompute_method", "recompute_num_layers": "recompute_num_layers",
+}
+_FLAG_TO_CFG = {"swiglu": ("activation", "swiglu"), "add_qkv_bias": ("add_qkv_bias", True),
+                "qk_layernorm": ("qk_layernorm", True), "disable_bias_linear": ("add_bias_linear", False),
+                "untie_embeddings_and_output_weights": ("untie_embeddings_and_output_weights", True),
+                "moe_router_pre_softmax": ("moe_router_pre_softmax", True),
+                "moe_router_enable_expert_bias": ("moe_router_enable_expert_bias", True),
+                "multi_latent_attention": ("multi_latent_attention", True), "use_dsa_fused": ("use_dsa", True),
+                "sequence_parallel": ("sequence_parallel", True), "tp_comm_overlap": ("tp_comm_overlap", True)}
+
+
+def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[TransformerConfig, TrainConfig, ParallelDims, dict]:
+    """(model config, train config, parallel dims, raw yaml). Raises ValueError on inconsistent input."""
+    overrides = overrides or []
+    raw = load_model_yaml(args, overrides) or {}
+    node = raw.get("model", raw) if isinstance(raw, dict) else {}
+    lm_node = node.get("foundation", node) if isinstance(node, dict) else {}
+    base = None
+    if args.model_name and args.model_name.lower().replace("_", "-") in list_models():
+        base = get_model_config(args.model_name)
+    if lm_node:
+        cfg = transformer_config_from_yaml({k: v for k, v in lm_node.items() if not isinstance(v, dict)}, base)
+    elif base is not None:
+        cfg = base
+    else:
+        cfg = TransformerConfig()
+    for a, c in _ARG_TO_CFG.items():
+        v = getattr(args, a, None)
+        if v is not None:
+            setattr(cfg, c, v)
+    for a, (c, val) in _FLAG_TO_CFG.items():
+        if getattr(args, a, False):
+            setattr(cfg, c, val)
+    if isinstance(getattr(args, "moe_layer_freq", None), str):
+        cfg.moe_layer_freq = yaml_compose._moe_freq(args.moe_layer_freq)
+    if cfg.fp8 is None and args.fp8_format:
+        cfg.fp8 = "blockwise" if (args.fp8_recipe or "blockwise") == "blockwise" else args.fp8_recipe
+    cfg.__post_init__()
+    dims = ParallelDims(tp=args.tensor_model_parallel_size, pp=args.pipeline_model_parallel_size,
+                        cp=args.context_parallel_size, ep=args.expert_model_parallel_size,
+                        etp=args.expert_tensor_parallel_size, vpp=args.num_virtual_stages_per_pipeline_rank)
+    dt = {"fp32": torch.float32, "bf16": torch.bfloat16}
+    custom_layers = [int(x) for x in args.custom_pipeline_layers.split(",")] if args.custom_pipeline_layers else None
+    tc = TrainConfig(
+        micro_batch_size=args.micro_batch_size, global_batch_size=args.global_batch_size or args.micro_batch_size,
+        seq_length=args.seq_length or cfg.max_position_embeddings, train_iters=args.train_iters or 0, lr=args.lr,
+        min_lr=args.min_lr, lr_decay_style=args.lr_decay_style, lr_warmup_iters=args.lr_warmup_iters,
+        lr_decay_iters=args.lr_decay_iters, weight_decay=args.weight_decay, adam_beta1=args.adam_beta1,
+        adam_beta2=args.adam_beta2, adam_eps=args.adam_eps, clip_grad=args.clip_grad, bf16=args.bf16, seed=args.seed,
+        log_interval=args.log_interval, save=args.save, load=args.load, save_interval=args.save_interval,
+        ckpt_format="torch_dist" if args.ckpt_format in ("torch_dist", "torch_dcp") else args.ckpt_format,
+        use_distributed_optimizer=args.use_distributed_optimizer, overlap_grad_reduce=args.overlap_grad_reduce,
+        overlap_param_gather=args.overlap_param_gather, exp_avg_dtype=dt[args.exp_avg_dtype],
+        exp_avg_sq_dtype=dt[args.exp_avg_sq_dtype], calculate_per_token_loss=args.calculate_per_token_loss,
+        custom_pipeline_layers=custom_layers, training_phase=args.training_phase, log_throughput=True)
+    from .validators import validate
+    validate(args, cfg, tc, dims)
+    return cfg, tc, dims, raw

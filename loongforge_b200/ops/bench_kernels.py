@@ -1,0 +1,108 @@
+"""Micro-benchmarks of the native kernels (CUDA-event timing, warm-up, L2-exceeding inputs).
+
+    python -m loongforge_b200.ops.bench_kernels gemm [--m 8192 --n 4096 --k 4096] [--iters 20]
+    python -m loongforge_b200.ops.bench_kernels attention [--t 8192 --groups 8 --rep 4]
+    python -m loongforge_b200.ops.bench_kernels norm [--t 8192 --h 4096]
+
+Each sub-command prints one JSON line; `--once` runs a single un-timed invocation (for profilers).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+
+from . import _ext
+from . import functional as OF
+
+
+def _time(fn, iters, warm=5):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attention", "norm"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--t", type=int, default=8192)
+    ap.add_argument("--h", type=int, default=4096)
+    ap.add_argument("--groups", type=int, default=8)
+    ap.add_argument("--rep", type=int, default=4)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--once", action="store_true")
+    a = ap.parse_args()
+    _ext.require()
+    dev = "cuda"
+    torch.manual_seed(0)
+    out = {"what": a.what}
+    if a.what == "gemm":
+        A = torch.randn(a.m, a.k, device=dev).bfloat16()
+        B = torch.randn(a.n, a.k, device=dev).bfloat16()
+        dY = torch.randn(a.m, a.n, device=dev).bfloat16()
+        mg = torch.zeros(a.n, a.k, device=dev)
+        fns = {"fwd_nt": lambda: OF.gemm(A, B), "dgrad_nn": lambda: OF.gemm(dY, B, b_mn_major=True),
+               "wgrad_tn_acc": lambda: OF.gemm(dY, A, a_mn_major=True, b_mn_major=True, out=mg, out_mode=2)}
+        if a.once:
+            for f in fns.values():
+                f()
+        else:
+            fl = 2.0 * a.m * a.n * a.k / 1e9
+            for k_, f in fns.items():
+                out[k_ + "_tflops"] = fl / _time(f, a.iters)
+            out["cublas_fwd_tflops"] = fl / _time(lambda: A @ B.t(), a.iters)
+        out.update(m=a.m, n=a.n, k=a.k)
+    elif a.what == "attention":
+        G, R, T = a.groups, a.rep, a.t
+        qkv = torch.randn(T, G * (R + 2) * 128, device=dev).bfloat16().requires_grad_()
+        o = OF.attention_packed(qkv, G, R)
+        do = torch.randn_like(o)
+
+        def fb():
+            oo = OF.attention_packed(qkv, G, R)
+            oo.backward(do)
+            qkv.grad = None
+
+        if a.once:
+            fb()
+        else:
+            fl = 4.0 * T * T * 128 * G * R / 2 / 1e9
+            tf = _time(lambda: OF.attention_packed(qkv.detach(), G, R), a.iters)
+            tfb = _time(fb, a.iters)
+            out.update(fwd_ms=tf, fwd_tflops=fl / tf, bwd_ms=tfb - tf, bwd_tflops=2.5 * fl / (tfb - tf))
+        out.update(t=T, q_heads=G * R, kv_heads=G)
+    else:
+        x = torch.randn(a.t, a.h, device=dev).bfloat16().requires_grad_()
+        w = torch.ones(a.h, device=dev).bfloat16().requires_grad_()
+        g = torch.randn(a.t, a.h, device=dev).bfloat16()
+
+        def fb():
+            y = OF.rmsnorm(x, w, 1e-5)
+            y.backward(g)
+            x.grad = None
+            w.grad = None
+
+        if a.once:
+            fb()
+        else:
+            ms = _time(fb, a.iters)
+            out.update(fwd_bwd_ms=ms, gbytes_per_s=a.t * a.h * 2 * 5 / ms / 1e6)
+    torch.cuda.synchronize()
+    _ext.check_status()
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,46 @@
+"""(model family, training phase) -> trainer factory registry
+(loongforge/train/trainer_builder.py:13-91)."""
+from __future__ import annotations
+
+from typing import Callable, Dict, Tuple
+
+_REGISTRY: Dict[Tuple[str, str], Callable] = {}
+LLM_FAMILIES = ("llama", "qwen2", "qwen3", "deepseek", "glm", "internlm", "minimax", "mimo", "qwen")
+VLM_FAMILIES = ("qwen2_5_vl", "qwen2_vl", "qwen3_vl", "internvl", "llava_ov", "ernie4_5_vl")
+
+
+def register_model_trainer(families, phase: str):
+    fams = [families] if isinstance(families, str) else list(families)
+
+    def deco(fn):
+        for f in fams:
+            _REGISTRY[(f, phase)] = fn
+        return fn
+    return deco
+
+
+def build_model_trainer(family: str, phase: str, **kw):
+    fn = _REGISTRY.get((family, phase))
+    if fn is None:
+        raise KeyError(f"no trainer registered for family {family!r}, phase {phase!r}; "
+                       f"known: {sorted(_REGISTRY)}")
+    return fn(**kw)
+
+
+@register_model_trainer(LLM_FAMILIES, "pretrain")
+def _llm_pretrain(model_cfg, train_cfg, dims, **kw):
+    from .trainer import Trainer
+    return Trainer(model_cfg, train_cfg, dims, **kw)
+
+
+@register_model_trainer(LLM_FAMILIES, "sft")
+def _llm_sft(model_cfg, train_cfg, dims, **kw):
+    from .sft import SFTTrainer
+    return SFTTrainer(model_cfg, train_cfg, dims, **kw)
+
+
+@register_model_trainer(VLM_FAMILIES, "pretrain")
+@register_model_trainer(VLM_FAMILIES, "sft")
+def _vlm(model_cfg, train_cfg, dims, **kw):
+    from .vlm import VLMTrainer
+    return VLMTrainer(model_cfg, train_cfg, dims, **kw)

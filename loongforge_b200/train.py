@@ -1,0 +1,57 @@
+"""Training entry point: ``torchrun ... -m loongforge_b200.train <flags> [yaml overrides]``
+(same role and flag spelling as the reference's loongforge/train.py:17-27)."""
+from __future__ import annotations
+
+import sys
+from typing import List, Optional
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    import torch.distributed as dist
+
+    from .config.arguments import parse_args
+    from .config.build import build_configs
+    from .data.synthetic import synthetic_batch_iterator
+    from .runtime.trainer import init_distributed
+    from .runtime.trainer_builder import build_model_trainer
+
+    args, overrides = parse_args(argv)
+    device = init_distributed(backend=args.distributed_backend if args.distributed_backend == "gloo" else None,
+                              timeout_s=args.distributed_timeout_minutes * 60)
+    model_cfg, train_cfg, dims, raw = build_configs(args, overrides)
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    if rank == 0:
+        print("------------------------ arguments ------------------------", flush=True)
+        for k, v in sorted(vars(args).items()):
+            print(f"  {k} {'.' * max(1, 48 - len(k))} {v}", flush=True)
+        print("-------------------- end of arguments ---------------------", flush=True)
+    if args.cp_comm_type not in ("auto", None):
+        from .parallel.context_parallel import set_cp_comm_type
+        set_cp_comm_type(args.cp_comm_type if args.cp_comm_type in ("p2p", "allgather", "a2a") else "auto")
+    if args.attention_backend in ("native", "sdpa"):
+        from .ops.functional import set_attention_impl
+        set_attention_impl(args.attention_backend)
+    node = raw.get("model", raw) if isinstance(raw, dict) else {}
+    family = (node.get("model_type") if isinstance(node, dict) and "foundation" in node else None) or model_cfg.model_family
+    trainer = build_model_trainer(family, train_cfg.training_phase, model_cfg=model_cfg, train_cfg=train_cfg,
+                                  dims=dims, device=device)
+    if train_cfg.load:
+        trainer.load_checkpoint(train_cfg.load, load_optim=not args.no_load_optim and not args.finetune,
+                                load_rng=not args.no_load_rng and not args.finetune)
+    data_iter = trainer.build_data_iterator(args) if hasattr(trainer, "build_data_iterator") else None
+    if data_iter is None:
+        st = trainer.st
+        data_iter = synthetic_batch_iterator(model_cfg.vocab_size, train_cfg.seq_length, train_cfg.micro_batch_size,
+                                             dp_rank=st.dp_rank, dp_size=st.dp_size, seed=train_cfg.seed,
+                                             start_sample=trainer.consumed_samples)
+    trainer.train(data_iter)
+    if train_cfg.save:
+        trainer.save_checkpoint(train_cfg.save)
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

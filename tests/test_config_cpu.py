@@ -1,0 +1,62 @@
+"""CLI parsing, YAML composition (defaults lists, resolvers, overrides) and validation."""
+import os
+import textwrap
+
+import pytest
+
+
+def test_yaml_compose_defaults_resolvers_overrides(tmp_path, monkeypatch):
+    from loongforge_b200.config import yaml_compose as yc
+
+    (tmp_path / "enc").mkdir()
+    (tmp_path / "enc" / "vit.yaml").write_text("hidden_size: 64\nactivation_func: ${act:silu}\n")
+    (tmp_path / "lm.yaml").write_text("num_layers: 2\nfreq: ${moe_freq:[0]*1+[1]*3}\n")
+    (tmp_path / "top.yaml").write_text(textwrap.dedent("""
+        defaults:
+          - enc@model.image_encoder: vit
+          - .@model.foundation: lm
+          - _self_
+        model:
+          root: ${oc.env:MY_ROOT,/x}/cfg
+          foundation:
+            num_layers: 4
+          ref: ${model.foundation.num_layers}
+    """))
+    monkeypatch.delenv("MY_ROOT", raising=False)
+    cfg = yc.compose(str(tmp_path / "top.yaml"), ["model.foundation.num_layers=6", "+model.image_encoder.freeze=true",
+                                                  "~model.image_encoder.activation_func"])
+    assert cfg["model"]["foundation"]["num_layers"] == 6 and cfg["model"]["ref"] == 6
+    assert cfg["model"]["foundation"]["freq"] == [0, 1, 1, 1]
+    assert cfg["model"]["image_encoder"] == {"hidden_size": 64, "freeze": True}
+    assert cfg["model"]["root"] == "/x/cfg"
+    with pytest.raises(KeyError):
+        yc.compose(str(tmp_path / "top.yaml"), ["model.nope=1"])
+
+
+def test_cli_to_configs(monkeypatch):
+    from loongforge_b200.config.arguments import parse_args
+    from loongforge_b200.config.build import build_configs
+
+    monkeypatch.setenv("WORLD_SIZE", "8")
+    args, ov = parse_args(["--model-name", "llama3-8b", "--tensor-model-parallel-size", "2", "--sequence-parallel",
+                           "--tp-comm-overlap", "--use-distributed-optimizer", "--seq-length", "8192",
+                           "--micro-batch-size", "1", "--global-batch-size", "128", "--bf16", "--train-iters", "10"])
+    cfg, tc, dims, _ = build_configs(args, ov)
+    assert (cfg.num_layers, cfg.hidden_size, cfg.num_query_groups, cfg.ffn_hidden_size) == (32, 4096, 8, 14336)
+    assert cfg.sequence_parallel and cfg.tp_comm_overlap and dims.tp == 2 and tc.global_batch_size == 128
+    with pytest.raises(SystemExit):
+        parse_args(["--model-name", "llama3-8b", "--no-such-flag"])
+    args, ov = parse_args(["--model-name", "llama3-8b", "--global-batch-size", "3", "--seq-length", "128"])
+    with pytest.raises(ValueError):
+        build_configs(args, ov)
+
+
+def test_registry_presets_cover_baseline_configs():
+    from loongforge_b200.models.registry import get_model_config
+
+    q = get_model_config("qwen3-30b-a3b")
+    assert (q.num_moe_experts, q.moe_router_topk, q.moe_ffn_hidden_size, q.qk_layernorm) == (128, 8, 768, True)
+    d = get_model_config("deepseek-v3.2-slice")
+    assert d.use_dsa and d.num_layers == 4 and d.moe_layer_freq == [0, 1, 1, 1] and d.fp8 == "blockwise"
+    n = get_model_config("llama3-8b").num_parameters()
+    assert 7.9e9 < n < 8.2e9
