@@ -372,7 +372,10 @@ def load_checkpoint(root: str, trainer, *, load_optim: bool = True, load_rng: bo
                 p.data[sl].copy_(b)
     if load_optim and same_mp:
         for k, piece, kind, buf in opt_targets:
-            piece[kind].copy_(buf)
+            if kind == "master":
+                piece["set_master"](buf)
+            else:
+                piece[kind].copy_(buf)
         trainer.optimizer.load_state_dict(common["optimizer"])
         trainer.scheduler.load_state_dict(common["opt_param_scheduler"])
     else:
@@ -411,7 +414,8 @@ def save_legacy(root: str, trainer, *, release: bool = False) -> str:
     # optimizer shards of every data-parallel rank
     od = os.path.join(d, f"distrib_optim_dp{st.rank_in('dp_cp'):03d}.pt")
     os.makedirs(d, exist_ok=True)
-    torch.save({n: [{k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in pc.items()} for pc in pcs]
+    torch.save({n: [{k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in pc.items() if k != "set_master"}
+                    for pc in pcs]
                 for n, pcs in trainer.optimizer.sharded_state().items()}, od)
     if dist.is_initialized():
         dist.barrier()
@@ -435,7 +439,8 @@ def load_legacy(root: str, trainer, it: int, release: bool, *, load_optim: bool 
         cur = trainer.optimizer.sharded_state()
         for name, pieces in cur.items():
             for pc, sv in zip(pieces, saved.get(name, [])):
-                for kind in ("master", "exp_avg", "exp_avg_sq"):
+                pc["set_master"](sv["master"])
+                for kind in ("exp_avg", "exp_avg_sq"):
                     pc[kind].copy_(sv[kind])
         trainer.optimizer.load_state_dict(sd["optimizer"])
         trainer.scheduler.load_state_dict(sd["opt_param_scheduler"])

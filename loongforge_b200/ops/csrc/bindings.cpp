@@ -240,6 +240,46 @@ void adam_step_(at::Tensor master, const at::Tensor& grad, at::Tensor m, at::Ten
   ++g_launches;
 }
 
+void adam_step_remainder_(at::Tensor w, at::Tensor lo, const at::Tensor& grad, at::Tensor m, at::Tensor v, double lr,
+                          double beta1, double beta2, double eps, double wd, int64_t step, double grad_scale) {
+  check_bf16_cuda(w, "w");
+  TORCH_CHECK(lo.is_cuda() && lo.scalar_type() == at::kShort && w.is_contiguous() && lo.is_contiguous());
+  const int64_t n = w.numel();
+  TORCH_CHECK(lo.numel() == n && grad.numel() == n && m.numel() == n && v.numel() == n);
+  TORCH_CHECK(grad.is_contiguous() && m.is_contiguous() && v.is_contiguous() && m.scalar_type() == v.scalar_type());
+  c10::cuda::CUDAGuard guard(w.device());
+  const bool gb = grad.scalar_type() == at::kBFloat16;
+  TORCH_CHECK(gb || grad.scalar_type() == at::kFloat);
+  const bool mb = m.scalar_type() == at::kBFloat16;
+  TORCH_CHECK(mb || m.scalar_type() == at::kFloat);
+  const float bc1 = 1.f - static_cast<float>(std::pow(beta1, static_cast<double>(step)));
+  const float bc2 = 1.f - static_cast<float>(std::pow(beta2, static_cast<double>(step)));
+  lf::adam_step_remainder(w.data_ptr(), lo.data_ptr(), grad.data_ptr(), gb, m.data_ptr(), v.data_ptr(), mb, n,
+                          static_cast<float>(lr), static_cast<float>(beta1), static_cast<float>(beta2),
+                          static_cast<float>(eps), static_cast<float>(wd), bc1, bc2, static_cast<float>(grad_scale),
+                          cur_stream());
+  ++g_launches;
+}
+
+void master_split_(const at::Tensor& master, at::Tensor w, at::Tensor lo, bool write_w) {
+  TORCH_CHECK(master.is_cuda() && master.scalar_type() == at::kFloat && master.is_contiguous());
+  check_bf16_cuda(w, "w");
+  TORCH_CHECK(lo.scalar_type() == at::kShort && w.numel() == master.numel() && lo.numel() == master.numel());
+  c10::cuda::CUDAGuard guard(w.device());
+  lf::master_split(master.data_ptr<float>(), w.data_ptr(), lo.data_ptr(), master.numel(), write_w, cur_stream());
+  ++g_launches;
+}
+
+at::Tensor master_join(const at::Tensor& w, const at::Tensor& lo) {
+  check_bf16_cuda(w, "w");
+  TORCH_CHECK(lo.scalar_type() == at::kShort && lo.numel() == w.numel() && w.is_contiguous() && lo.is_contiguous());
+  c10::cuda::CUDAGuard guard(w.device());
+  at::Tensor out = at::empty({w.numel()}, w.options().dtype(at::kFloat));
+  lf::master_join(w.data_ptr(), lo.data_ptr(), out.data_ptr<float>(), w.numel(), cur_stream());
+  ++g_launches;
+  return out;
+}
+
 void sumsq_(const at::Tensor& x, at::Tensor out) {
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && out.scalar_type() == at::kFloat && out.numel() == 1);
   c10::cuda::CUDAGuard guard(x.device());
@@ -441,6 +481,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ce_dlogits_", &ce_dlogits_);
   m.def("adam_step_", &adam_step_);
   m.def("sumsq_", &sumsq_);
+  m.def("adam_step_remainder_", &adam_step_remainder_);
+  m.def("master_split_", &master_split_);
+  m.def("master_join", &master_join);
 #ifdef LF_HAVE_ATTN
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);

@@ -381,6 +381,61 @@ __global__ void adam_kernel(float* __restrict__ master, const GT* __restrict__ g
   }
 }
 
+// AdamW with the fp32 master weight stored as (bf16 model weight, int16 remainder):
+//   master_bits = (bf16_bits << 16) + remainder,  bf16 = round-to-nearest-even(master)
+// The pair is an exact fp32 value, so the update is bit-identical to the fp32-master kernel while
+// the optimizer keeps 2 instead of 4 extra bytes per parameter.
+__device__ __forceinline__ float master_from_parts(bf16 w, short lo) {
+  const unsigned hi = static_cast<unsigned>(__bfloat16_as_ushort(w)) << 16;
+  return __uint_as_float(hi + static_cast<unsigned>(static_cast<int>(lo)));
+}
+__device__ __forceinline__ void master_to_parts(float p, bf16& w, short& lo) {
+  w = __float2bfloat16_rn(p);
+  const unsigned hi = static_cast<unsigned>(__bfloat16_as_ushort(w)) << 16;
+  lo = static_cast<short>(static_cast<int>(__float_as_uint(p) - hi));
+}
+template <typename GT, typename MT>
+__global__ void adam_remainder_kernel(bf16* __restrict__ w, short* __restrict__ lo, const GT* __restrict__ grad,
+                                      MT* __restrict__ m, MT* __restrict__ v, long long n, float lr, float beta1,
+                                      float beta2, float eps, float wd, float bc1, float bc2, float grad_scale) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float g = static_cast<float>(grad[i]) * grad_scale;
+    float mi = static_cast<float>(m[i]);
+    float vi = static_cast<float>(v[i]);
+    mi = beta1 * mi + (1.f - beta1) * g;
+    vi = beta2 * vi + (1.f - beta2) * g * g;
+    float p = master_from_parts(w[i], lo[i]);
+    const float upd = (mi / bc1) / (sqrtf(vi / bc2) + eps) + wd * p;
+    p -= lr * upd;
+    bf16 wn;
+    short ln;
+    master_to_parts(p, wn, ln);
+    w[i] = wn;
+    lo[i] = ln;
+    m[i] = static_cast<MT>(mi);
+    v[i] = static_cast<MT>(vi);
+  }
+}
+// remainder <-> fp32 master conversion (checkpointing, initialisation)
+__global__ void master_split_kernel(const float* __restrict__ master, bf16* __restrict__ w, short* __restrict__ lo,
+                                    long long n, int write_w) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    bf16 wn;
+    short ln;
+    master_to_parts(master[i], wn, ln);
+    if (write_w) w[i] = wn;
+    lo[i] = ln;
+  }
+}
+__global__ void master_join_kernel(const bf16* __restrict__ w, const short* __restrict__ lo, float* __restrict__ master,
+                                   long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    master[i] = master_from_parts(w[i], lo[i]);
+}
+
 // sum of squares of a flat buffer into a single fp32 (atomic add of block partials)
 template <typename T>
 __global__ void sumsq_kernel(const T* __restrict__ x, long long n, float* __restrict__ out) {
@@ -486,6 +541,44 @@ void adam_step(float* master, const void* grad, int grad_is_bf16, void* m, void*
                                                      static_cast<float*>(v), mo, n, lr, beta1, beta2, eps, wd, bc1,
                                                      bc2, grad_scale);
   }
+}
+
+void adam_step_remainder(void* w, void* lo, const void* grad, int grad_is_bf16, void* m, void* v, int moments_bf16,
+                         long long n, float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
+                         float grad_scale, cudaStream_t s) {
+  if (n == 0) return;
+  const int grid = grid_for(n, 256, 148 * 16);
+  bf16* wp = static_cast<bf16*>(w);
+  short* lp = static_cast<short*>(lo);
+  if (grad_is_bf16) {
+    if (moments_bf16)
+      adam_remainder_kernel<bf16, bf16><<<grid, 256, 0, s>>>(wp, lp, static_cast<const bf16*>(grad), static_cast<bf16*>(m),
+                                                             static_cast<bf16*>(v), n, lr, beta1, beta2, eps, wd, bc1,
+                                                             bc2, grad_scale);
+    else
+      adam_remainder_kernel<bf16, float><<<grid, 256, 0, s>>>(wp, lp, static_cast<const bf16*>(grad),
+                                                              static_cast<float*>(m), static_cast<float*>(v), n, lr,
+                                                              beta1, beta2, eps, wd, bc1, bc2, grad_scale);
+  } else {
+    if (moments_bf16)
+      adam_remainder_kernel<float, bf16><<<grid, 256, 0, s>>>(wp, lp, static_cast<const float*>(grad),
+                                                              static_cast<bf16*>(m), static_cast<bf16*>(v), n, lr,
+                                                              beta1, beta2, eps, wd, bc1, bc2, grad_scale);
+    else
+      adam_remainder_kernel<float, float><<<grid, 256, 0, s>>>(wp, lp, static_cast<const float*>(grad),
+                                                               static_cast<float*>(m), static_cast<float*>(v), n, lr,
+                                                               beta1, beta2, eps, wd, bc1, bc2, grad_scale);
+  }
+}
+void master_split(const float* master, void* w, void* lo, long long n, int write_w, cudaStream_t s) {
+  if (n == 0) return;
+  master_split_kernel<<<grid_for(n, 256, 148 * 16), 256, 0, s>>>(master, static_cast<bf16*>(w), static_cast<short*>(lo),
+                                                                 n, write_w);
+}
+void master_join(const void* w, const void* lo, float* master, long long n, cudaStream_t s) {
+  if (n == 0) return;
+  master_join_kernel<<<grid_for(n, 256, 148 * 16), 256, 0, s>>>(static_cast<const bf16*>(w),
+                                                                static_cast<const short*>(lo), master, n);
 }
 
 void sumsq(const void* x, int is_bf16, long long n, float* out, cudaStream_t s) {

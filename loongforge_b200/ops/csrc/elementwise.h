@@ -23,6 +23,11 @@ void ce_dlogits(void* logits, const long long* labels, const float* gmax, const 
 void adam_step(float* master, const void* grad, int grad_is_bf16, void* m, void* v, int moments_bf16,
                void* model_out, long long n, float lr, float beta1, float beta2, float eps, float wd, float bc1,
                float bc2, float grad_scale, cudaStream_t s);
+void adam_step_remainder(void* w, void* lo, const void* grad, int grad_is_bf16, void* m, void* v, int moments_bf16,
+                         long long n, float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
+                         float grad_scale, cudaStream_t s);
+void master_split(const float* master, void* w, void* lo, long long n, int write_w, cudaStream_t s);
+void master_join(const void* w, const void* lo, float* master, long long n, cudaStream_t s);
 void sumsq(const void* x, int is_bf16, long long n, float* out, cudaStream_t s);
 
 }  // namespace lf

@@ -629,3 +629,39 @@ def sum_of_squares(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch
     else:
         out.add_(x.float().pow(2).sum())
     return out
+
+
+# ----------------------------------------------------------------------------- fp32 master as (bf16, int16 remainder)
+
+
+def master_join(w: torch.Tensor, lo: torch.Tensor) -> torch.Tensor:
+    """Exact fp32 master weights from the bf16 weights and their int16 remainders."""
+    if w.is_cuda:
+        return _C().master_join(w.contiguous(), lo.contiguous())
+    bits = (w.contiguous().view(torch.int16).to(torch.int32) << 16) + lo.to(torch.int32)
+    return bits.view(torch.float32)
+
+
+def master_split(master: torch.Tensor, w: torch.Tensor, lo: torch.Tensor, write_w: bool = True) -> None:
+    """Split fp32 `master` into round-to-nearest bf16 `w` (optional) and the int16 remainder `lo`."""
+    if master.is_cuda:
+        _C().master_split_(master.contiguous(), w, lo, write_w)
+        return
+    wb = master.to(torch.bfloat16)
+    hi = wb.view(torch.int16).to(torch.int32) << 16
+    lo.copy_((master.contiguous().view(torch.int32) - hi).to(torch.int16))
+    if write_w:
+        w.copy_(wb)
+
+
+def adam_step_remainder(w, lo, grad, exp_avg, exp_avg_sq, *, lr, beta1, beta2, eps, weight_decay, step,
+                        grad_scale=1.0):
+    """AdamW where the fp32 master weight is the exact pair (bf16 `w`, int16 `lo`); updates both in place."""
+    if w.is_cuda:
+        _C().adam_step_remainder_(w, lo, grad, exp_avg, exp_avg_sq, lr, beta1, beta2, eps, weight_decay, step,
+                                  grad_scale)
+        return
+    master = master_join(w, lo).clone()
+    adam_step(master, grad, exp_avg, exp_avg_sq, None, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
+              weight_decay=weight_decay, step=step, grad_scale=grad_scale)
+    master_split(master, w, lo, True)

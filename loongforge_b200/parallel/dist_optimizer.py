@@ -37,6 +37,9 @@ class OptimizerConfig:
     exp_avg_dtype: torch.dtype = torch.float32
     exp_avg_sq_dtype: torch.dtype = torch.float32
     overlap_param_gather: bool = False
+    # keep the fp32 master of bf16 parameters as (bf16 weight in the parameter buffer, int16 remainder):
+    # exact, and 2 bytes per parameter less optimizer memory
+    master_as_remainder: bool = False
     no_weight_decay_cond: Optional[object] = None  # callable(name, param) -> bool
 
 
@@ -47,7 +50,12 @@ class _ShardState:
         self.buf, self.bucket, self.start, self.end = buf, b, s, e
         dev = buf.param_data.device
         n = e - s
-        self.master = buf.param_data[s:e].float().clone()
+        self.remainder = cfg.master_as_remainder and buf.param_data.dtype == torch.bfloat16
+        if self.remainder:
+            self.lo = torch.zeros(n, dtype=torch.int16, device=dev)  # master == bf16 weight exactly at start
+            self._master = None
+        else:
+            self._master = buf.param_data[s:e].float().clone()
         self.exp_avg = torch.zeros(n, dtype=cfg.exp_avg_dtype, device=dev)
         self.exp_avg_sq = torch.zeros(n, dtype=cfg.exp_avg_sq_dtype, device=dev)
         # segments: (lo, hi, weight_decay_on, tp_duplicated, name)
@@ -63,6 +71,20 @@ class _ShardState:
             dup = not getattr(p, "tensor_model_parallel", False)
             self.segments.append((lo - s, hi - s, not no_wd, dup, name, p, ps_))
         self.segments.sort(key=lambda t: t[0])
+
+    @property
+    def master(self) -> torch.Tensor:
+        """fp32 master weights of the shard (materialised on demand in remainder mode)."""
+        if self.remainder:
+            return OF.master_join(self.buf.param_data[self.start:self.end], self.lo)
+        return self._master
+
+    def set_master(self, lo: int, hi: int, values: torch.Tensor) -> None:
+        if self.remainder:
+            w = self.buf.param_data[self.start + lo:self.start + hi]
+            OF.master_split(values.float().contiguous().to(w.device), w, self.lo[lo:hi], True)
+        else:
+            self._master[lo:hi].copy_(values)
 
 
 class DistributedOptimizer:
@@ -91,7 +113,7 @@ class DistributedOptimizer:
     def grad_norm(self) -> torch.Tensor:
         """Global L2 norm of all gradients (each logical element counted once)."""
         st = self.state
-        dev = self.shards[0].master.device
+        dev = self.shards[0].exp_avg.device
         total = torch.zeros(1, dtype=torch.float32, device=dev)
         for sh in self.shards:
             g = sh.buf.grad_data[sh.start:sh.end]
@@ -152,6 +174,12 @@ class DistributedOptimizer:
                 else:
                     runs.append([lo, hi, use_wd])
             for lo, hi, use_wd in runs:
+                if sh.remainder:
+                    OF.adam_step_remainder(out[lo:hi], sh.lo[lo:hi], g[lo:hi], sh.exp_avg[lo:hi],
+                                           sh.exp_avg_sq[lo:hi], lr=lr, beta1=cfg.adam_beta1, beta2=cfg.adam_beta2,
+                                           eps=cfg.adam_eps, weight_decay=wd if use_wd else 0.0,
+                                           step=self.step_count, grad_scale=clip)
+                    continue
                 OF.adam_step(sh.master[lo:hi], g[lo:hi], sh.exp_avg[lo:hi], sh.exp_avg_sq[lo:hi],
                              out_arg[lo:hi] if out_arg is not None else None, lr=lr, beta1=cfg.adam_beta1,
                              beta2=cfg.adam_beta2, eps=cfg.adam_eps, weight_decay=wd if use_wd else 0.0,
@@ -183,7 +211,10 @@ class DistributedOptimizer:
     def reload_model_params(self):
         """Refresh fp32 masters from the (possibly just loaded) model weights."""
         for sh in self.shards:
-            sh.master.copy_(sh.buf.param_data[sh.start:sh.end].float())
+            if sh.remainder:
+                sh.lo.zero_()
+            else:
+                sh._master.copy_(sh.buf.param_data[sh.start:sh.end].float())
 
     # ------------------------------------------------------------------ checkpoint state
     def sharded_state(self) -> Dict[str, Dict[str, torch.Tensor]]:
@@ -198,7 +229,8 @@ class DistributedOptimizer:
                 off = sh.start + lo - pstart
                 out.setdefault(name, []).append({
                     "offset": off, "numel": hi - lo, "param_numel": p.numel(),
-                    "master": sh.master[lo:hi], "exp_avg": sh.exp_avg[lo:hi], "exp_avg_sq": sh.exp_avg_sq[lo:hi]})
+                    "master": sh.master[lo:hi], "exp_avg": sh.exp_avg[lo:hi], "exp_avg_sq": sh.exp_avg_sq[lo:hi],
+                    "set_master": (lambda v, sh=sh, lo=lo, hi=hi: sh.set_master(lo, hi, v))})
         return out
 
     def state_dict(self):
@@ -217,6 +249,6 @@ class DistributedOptimizer:
                 if src is None:
                     continue
                 off = sh.start + lo - pstart
-                sh.master[lo:hi].copy_(src["master"][off:off + hi - lo])
+                sh.set_master(lo, hi, src["master"][off:off + hi - lo])
                 sh.exp_avg[lo:hi].copy_(src["exp_avg"][off:off + hi - lo])
                 sh.exp_avg_sq[lo:hi].copy_(src["exp_avg_sq"][off:off + hi - lo])

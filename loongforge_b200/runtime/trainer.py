@@ -57,6 +57,7 @@ class TrainConfig:
     grad_reduce_in_fp32: bool = True
     exp_avg_dtype: torch.dtype = torch.float32
     exp_avg_sq_dtype: torch.dtype = torch.float32
+    master_as_remainder: bool = False
     ddp_bucket_size: Optional[int] = None
     calculate_per_token_loss: bool = False
     custom_pipeline_layers: Optional[List[int]] = None
@@ -157,7 +158,8 @@ class Trainer:
         ocfg = OptimizerConfig(lr=t.lr, min_lr=t.min_lr, weight_decay=t.weight_decay, adam_beta1=t.adam_beta1,
                                adam_beta2=t.adam_beta2, adam_eps=t.adam_eps, clip_grad=t.clip_grad,
                                exp_avg_dtype=t.exp_avg_dtype, exp_avg_sq_dtype=t.exp_avg_sq_dtype,
-                               overlap_param_gather=t.overlap_param_gather)
+                               overlap_param_gather=t.overlap_param_gather,
+                               master_as_remainder=t.master_as_remainder)
         return DistributedOptimizer(self.models, ocfg)
 
     # ------------------------------------------------------------------ default LLM pretrain step

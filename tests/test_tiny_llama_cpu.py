@@ -133,3 +133,24 @@ def test_model_matches_independent_reference():
     assert abs(loss.item() - ref.item()) < 1e-4
     for n, p in model.named_parameters():
         assert torch.allclose(g_ours[n], p.grad, atol=2e-5, rtol=1e-3), n
+
+
+def test_master_remainder_is_exact_fp32():
+    """(bf16, int16 remainder) reproduces the fp32 master bit for bit, and AdamW on it equals AdamW on fp32."""
+    from loongforge_b200.ops import functional as OF
+
+    torch.manual_seed(0)
+    master = torch.randn(10001) * torch.logspace(-6, 3, 10001)
+    w = torch.empty(10001, dtype=torch.bfloat16)
+    lo = torch.empty(10001, dtype=torch.int16)
+    OF.master_split(master, w, lo)
+    assert torch.equal(OF.master_join(w, lo), master)
+    assert torch.equal(w, master.to(torch.bfloat16))
+    g = torch.randn(10001)
+    m1, v1 = torch.zeros(10001), torch.zeros(10001)
+    m2, v2 = torch.zeros(10001), torch.zeros(10001)
+    ref = master.clone()
+    for step in (1, 2, 3):
+        OF.adam_step(ref, g, m1, v1, None, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
+        OF.adam_step_remainder(w, lo, g, m2, v2, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
+    assert torch.equal(OF.master_join(w, lo), ref)
