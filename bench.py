@@ -49,6 +49,9 @@ def parse():
     ap.add_argument("--attention", default="auto", choices=["auto", "native", "sdpa"])
     ap.add_argument("--recompute", default="auto", choices=["auto", "none", "full"])
     ap.add_argument("--no-tp-overlap", action="store_true")
+    ap.add_argument("--recompute-layers", type=int, default=None, help="with --recompute full: first K layers only")
+    ap.add_argument("--fp32-master-copy", action="store_true",
+                    help="keep a separate fp32 master tensor instead of the exact (bf16, int16 remainder) pair")
     return ap.parse_args()
 
 
@@ -158,10 +161,13 @@ def main():
         recompute = "full" if world == 1 else "none"
     if recompute == "full":
         cfg.recompute_granularity, cfg.recompute_method = "full", "uniform"
+        if args.recompute_layers is not None:
+            cfg.recompute_method, cfg.recompute_num_layers = "block", args.recompute_layers
     gbs = args.seqs_per_gpu * world
     tc = TrainConfig(micro_batch_size=1, global_batch_size=gbs, seq_length=args.seq_len,
                      train_iters=10 ** 9, lr=3e-4, weight_decay=0.1, adam_beta2=0.95, clip_grad=1.0, bf16=True,
-                     use_distributed_optimizer=True, overlap_grad_reduce=True)
+                     use_distributed_optimizer=True, overlap_grad_reduce=True,
+                     master_as_remainder=not args.fp32_master_copy)
     trainer = Trainer(cfg, tc, ParallelDims(tp=tp), device=dev)
     st = trainer.st
     host_iter = synthetic_batch_iterator(cfg.vocab_size, tc.seq_length, 1, dp_rank=st.dp_rank, dp_size=st.dp_size,
@@ -252,6 +258,8 @@ def main():
                 "l2_policy": "inputs larger than L2: 16 GB of weights + activations stream every step",
                 "baseline_number": "3550 tok/s/GPU (reference CI, 8 x BZZ chip, seq 4096, TP2 PP2 CP2)",
                 "last_loss": last_loss,
+                "fp32_master": "separate fp32 tensor" if args.fp32_master_copy else "exact (bf16, int16 remainder) pair",
+                "max_memory_allocated_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
             },
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -1,0 +1,153 @@
+"""Vision-language composition: vision encoder -> projector -> language model, with
+heterogeneous parallelism between the components.
+
+Counterpart of the reference's ``OmniCombinationModel`` / ``OmniEncoderModel``
+(loongforge/models/omni_models/omni_combination_model.py:191-597,
+omni_encoder_model.py:66-218,386-397). The encoder and projector live in their own named parallel
+state (``image_encoder``, typically TP=1) while the language model uses the default state (e.g.
+TP2 + sequence parallel, PP2); entering the encoder switches the current state and leaving
+restores it. With ``encoder_hetero_dp`` the ranks of one language-model TP group split the images
+of the micro-batch among themselves (the encoder runs data parallel over the TP group) and
+all-gather the projected embeddings, instead of every rank encoding every image. The encoder
+exists only on the first pipeline stage. Image embeddings replace the ``image_token_id`` slots of
+the text embedding sequence (masked scatter) before the sequence is scattered for sequence
+parallelism.
+"""
+from __future__ import annotations
+
+import contextlib
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..parallel import mappings as M
+from ..parallel import state as ps
+from .config import TransformerConfig
+from .gpt import GPTModel
+from .vision import MLPAdapter, VisionModel
+
+ENCODER_STATE = "image_encoder"
+IGNORE_INDEX = -100
+
+
+@contextlib.contextmanager
+def parallel_state(name: Optional[str]):
+    if name is None or name not in ps._STATES:
+        yield
+        return
+    prev = ps.change_parallel_state(name)
+    try:
+        yield
+    finally:
+        ps.change_parallel_state(prev)
+
+
+class _GatherVarRows(torch.autograd.Function):
+    """All-gather of row blocks with different row counts per rank (backward: take own slice)."""
+
+    @staticmethod
+    def forward(ctx, x, counts, group):
+        ctx.group, ctx.counts = group, counts
+        r = dist.get_rank(group)
+        mx = max(counts)
+        pad = torch.zeros(mx, x.shape[1], dtype=x.dtype, device=x.device)
+        pad[: x.shape[0]] = x
+        outs = [torch.empty_like(pad) for _ in counts]
+        dist.all_gather(outs, pad, group=group)
+        ctx.rank = r
+        return torch.cat([o[:c] for o, c in zip(outs, counts)], 0)
+
+    @staticmethod
+    def backward(ctx, g):
+        start = sum(ctx.counts[: ctx.rank])
+        # every rank consumed the full gathered tensor identically: sum the replicas' gradients
+        g = g.contiguous()
+        dist.all_reduce(g, group=ctx.group)
+        return g[start:start + ctx.counts[ctx.rank]] / dist.get_world_size(ctx.group), None, None
+
+
+class OmniCombinationModel(nn.Module):
+    def __init__(self, lm_cfg: TransformerConfig, vit_cfg: Optional[TransformerConfig], *, image_token_id: int,
+                 pre_process: bool = True, post_process: bool = True, layer_numbers=None, device=None,
+                 encoder_hetero_dp: bool = False, freeze_encoder: bool = False, projector_activation: str = "gelu"):
+        super().__init__()
+        self.cfg = lm_cfg
+        self.image_token_id = image_token_id
+        self.pre_process, self.post_process = pre_process, post_process
+        self.encoder_hetero_dp = encoder_hetero_dp
+        self.foundation_model = GPTModel(lm_cfg, pre_process=pre_process, post_process=post_process,
+                                         layer_numbers=layer_numbers, device=device)
+        self.has_encoder = pre_process and vit_cfg is not None
+        if self.has_encoder:
+            enc_state = ENCODER_STATE if ENCODER_STATE in ps._STATES else None
+            self.encoder_state = enc_state
+            with parallel_state(enc_state):
+                self.encoder_model = nn.Module()
+                self.encoder_model.image_encoder = VisionModel(vit_cfg, device=device, parallel_state=enc_state)
+                self.encoder_model.image_projector = MLPAdapter(vit_cfg, lm_cfg.hidden_size, device=device,
+                                                                activation=projector_activation)
+            if freeze_encoder:
+                for p in self.encoder_model.image_encoder.parameters():
+                    p.requires_grad_(False)
+
+    # pipeline plumbing is delegated to the language model
+    @property
+    def decoder(self):
+        return self.foundation_model.decoder
+
+    def set_input_tensor(self, t):
+        self.foundation_model.set_input_tensor(t)
+
+    def encode_images(self, pixels: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
+        """[n_patches, patch_dim] -> [n_merged_tokens, lm_hidden]."""
+        st = ps.get_state()
+        tp, g = st.dims.tp, st.group("tp")
+        n_img = grid_thw.shape[0]
+        split = self.encoder_hetero_dp and tp > 1 and n_img >= tp
+        if split:
+            per = [(n_img + tp - 1 - r) // tp for r in range(tp)]
+            starts = [sum(per[:r]) for r in range(tp)]
+            patches = (grid_thw[:, 0] * grid_thw[:, 1] * grid_thw[:, 2]).tolist()
+            i0, i1 = starts[st.tp_rank], starts[st.tp_rank] + per[st.tp_rank]
+            p0, p1 = sum(patches[:i0]), sum(patches[:i1])
+            pixels, my_grid = pixels[p0:p1], grid_thw[i0:i1]
+        else:
+            my_grid = grid_thw
+        with parallel_state(self.encoder_state):
+            h, widx = self.encoder_model.image_encoder(pixels, my_grid)
+            emb = self.encoder_model.image_projector(h, widx)
+        if split:
+            unit = self.encoder_model.image_projector.unit
+            counts = [sum(patches[starts[r]:starts[r] + per[r]]) // unit for r in range(tp)]
+            emb = _GatherVarRows.apply(emb, counts, g)
+        return emb
+
+    def forward(self, tokens, position_ids, *, pixels=None, grid_thw=None, labels=None, loss_mask=None, packed=None,
+                loss_scale=None):
+        lm = self.foundation_model
+        decoder_input = None
+        if self.pre_process:
+            st = ps.get_state()
+            sp = self.cfg.sequence_parallel and st.dims.tp > 1
+            if sp:
+                # full-sequence text embeddings (all-reduce), merged with the image tokens, then scattered
+                emb_mod = lm.embedding.word_embeddings
+                was = emb_mod.sequence_parallel
+                emb_mod.sequence_parallel = False
+                try:
+                    x = lm.embed(tokens)
+                finally:
+                    emb_mod.sequence_parallel = was
+            else:
+                x = lm.embed(tokens)
+            if self.has_encoder and pixels is not None and pixels.numel() > 0:
+                img = self.encode_images(pixels, grid_thw).to(x.dtype)
+                mask = tokens == self.image_token_id
+                x = x.masked_scatter(mask.unsqueeze(-1), img)
+            if sp:
+                x = M.scatter_to_sequence_parallel_region(x, st.group("tp"))
+            decoder_input = x
+        return lm(tokens, position_ids, labels=labels, loss_mask=loss_mask, packed=packed,
+                  decoder_input=decoder_input, loss_scale=loss_scale)

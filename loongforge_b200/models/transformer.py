@@ -87,6 +87,10 @@ class LayerNormColumnParallelLinear(PL.ColumnParallelLinear):
 
     def forward(self, x):
         kind, eps, off = self._norm
+        if (self.tp == 1 and kind == "RMSNorm" and not self.gather_output
+                and OF.norm_linear_supported(x, self.layer_norm_weight, self.weight)):
+            # single-GPU tensor layout: fused block that does not store the normalised activations
+            return OF.norm_linear(x, self.layer_norm_weight, self.weight, self.bias, eps, off)
         return super().forward(apply_norm(x, self.layer_norm_weight, self.layer_norm_bias, kind, eps, off))
 
 
@@ -121,6 +125,9 @@ class MLP(nn.Module):
 
     def forward(self, x, residual=None):
         h = self.linear_fc1(x)
+        if (self.glu and self.act_name == "swiglu" and self.linear_fc2.tp == 1 and self.linear_fc2.bias is None
+                and OF.swiglu_linear_supported(h, self.linear_fc2.weight)):
+            return OF.swiglu_linear(h, self.linear_fc2.weight, residual)
         if self.glu and self.act_name == "swiglu":
             h = OF.swiglu(h)
         elif self.glu:

@@ -445,6 +445,20 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
             q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None],
             is_causal=causal, scale=scale, enable_gqa=Hq != Hkv)
         return o[0].transpose(0, 1).contiguous()
+    if q.is_cuda:
+        # library fallback for head dims the tcgen05 kernel does not cover (e.g. ViT d=80):
+        # block-diagonal (+ causal) mask from the sequence boundaries
+        T = q.shape[0]
+        idx = torch.arange(T, device=q.device)
+        seg = torch.bucketize(idx, cu_seqlens[1:].to(q.device), right=True)
+        mask = seg[:, None] == seg[None, :]
+        if causal:
+            mask &= idx[None, :] <= idx[:, None]
+        Hq, Hkv = q.shape[1], k.shape[1]
+        o = F.scaled_dot_product_attention(
+            q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None], attn_mask=mask[None, None],
+            scale=scale, enable_gqa=Hq != Hkv)
+        return o[0].transpose(0, 1).contiguous()
     return attention_ref(q, k, v, causal, scale, cu_seqlens)
 
 
@@ -665,3 +679,74 @@ def adam_step_remainder(w, lo, grad, exp_avg, exp_avg_sq, *, lr, beta1, beta2, e
     adam_step(master, grad, exp_avg, exp_avg_sq, None, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
               weight_decay=weight_decay, step=step, grad_scale=grad_scale)
     master_split(master, w, lo, True)
+
+
+# ----------------------------------------------------------------------------- memory-lean fused blocks
+
+
+class _NormLinearFn(torch.autograd.Function):
+    """y = RMSNorm(x; g) @ W^T (+ bias). Only x and rstd are kept; the normalised activations are
+    recomputed in backward (one bandwidth-bound pass) instead of being stored."""
+
+    @staticmethod
+    def forward(ctx, x, ln_w, weight, bias, eps, w_offset):
+        xn, rstd = _C().rmsnorm_fwd(x, ln_w, eps, w_offset)
+        y = gemm(xn, weight, bias=bias)
+        ctx.save_for_backward(x, ln_w, rstd, weight)
+        ctx.cfg = (eps, w_offset, bias is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, ln_w, rstd, weight = ctx.saved_tensors
+        eps, w_offset, has_bias = ctx.cfg
+        dy = dy.contiguous()
+        xn, _ = _C().rmsnorm_fwd(x, ln_w, eps, w_offset)
+        dw = _wgrad(dy, xn, weight) if ctx.needs_input_grad[2] else None
+        del xn
+        dxn = gemm(dy, weight, b_mn_major=True)
+        dx, dg = _C().rmsnorm_bwd(dxn, x, ln_w, rstd, None, w_offset)
+        db = dy.float().sum(0).to(dy.dtype) if has_bias else None
+        return dx, dg.to(ln_w.dtype), dw, db, None, None
+
+
+def norm_linear_supported(x, ln_w, weight) -> bool:
+    H = x.shape[-1]
+    return (x.is_cuda and x.dim() == 2 and x.dtype == torch.bfloat16 and ln_w.dtype == torch.bfloat16
+            and H % 8 == 0 and H <= 8192 and weight.shape[0] % 8 == 0 and _ld_ok(weight))
+
+
+def norm_linear(x, ln_w, weight, bias=None, eps=1e-5, w_offset=0.0):
+    return _NormLinearFn.apply(x.contiguous(), ln_w, weight, bias, eps, w_offset)
+
+
+class _SwiGLULinearFn(torch.autograd.Function):
+    """y = swiglu(h) @ W^T (+ residual). Keeps only h ([T, 2F]); silu(gate)*up is recomputed in backward."""
+
+    @staticmethod
+    def forward(ctx, h, weight, residual):
+        a = _C().swiglu_fwd(h)
+        y = gemm(a, weight, residual=residual)
+        ctx.save_for_backward(h, weight)
+        ctx.has_res = residual is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        h, weight = ctx.saved_tensors
+        dy = dy.contiguous()
+        a = _C().swiglu_fwd(h)
+        dw = _wgrad(dy, a, weight) if ctx.needs_input_grad[1] else None
+        del a
+        da = gemm(dy, weight, b_mn_major=True)
+        dh = _C().swiglu_bwd(da, h)
+        return dh, dw, (dy if ctx.has_res else None)
+
+
+def swiglu_linear_supported(h, weight) -> bool:
+    return (h.is_cuda and h.dim() == 2 and h.dtype == torch.bfloat16 and h.shape[-1] % 16 == 0
+            and weight.shape[0] % 8 == 0 and _ld_ok(weight) and h.is_contiguous())
+
+
+def swiglu_linear(h, weight, residual=None):
+    return _SwiGLULinearFn.apply(h, weight, residual)
