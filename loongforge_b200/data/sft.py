@@ -1,0 +1,73 @@
+"""Supervised fine-tuning datasets: jsonl/json files in alpaca / sharegpt / openai formats, blended
+by weight, tokenised with a chat template, optionally packed
+(loongforge/data/sft_dataset.py, sft_data_collator.py, blended_hf_dataset_builder.py)."""
+from __future__ import annotations
+
+import json
+import random
+from typing import Dict, Iterator, List, Optional, Sequence
+
+import torch
+
+from .chat_template import encode_chat, to_messages
+from .packing import collate_packed, pack_first_fit_decreasing
+
+
+def load_records(path: str) -> List[dict]:
+    with open(path) as f:
+        head = f.read(1)
+        f.seek(0)
+        if head == "[":
+            return json.load(f)
+        return [json.loads(line) for line in f if line.strip()]
+
+
+class SFTDataset:
+    def __init__(self, paths: Sequence[str], tokenizer, template: str = "chatml", max_len: int = 2048,
+                 weights: Optional[Sequence[float]] = None, fmt: str = "auto", train_on_prompt: bool = False,
+                 seed: int = 1234):
+        self.tokenizer, self.template, self.max_len = tokenizer, template, max_len
+        self.train_on_prompt, self.fmt = train_on_prompt, fmt
+        sets = [load_records(p) for p in paths]
+        if weights is None:
+            self.records = [r for s in sets for r in s]
+        else:  # blend: sample each source proportionally to its weight
+            rng = random.Random(seed)
+            total = sum(len(s) for s in sets)
+            wsum = float(sum(weights))
+            self.records = []
+            for s, w in zip(sets, weights):
+                n = max(1, round(total * w / wsum))
+                self.records.extend(rng.choices(s, k=n) if n > len(s) else rng.sample(s, n))
+            rng.shuffle(self.records)
+
+    def __len__(self):
+        return len(self.records)
+
+    def __getitem__(self, i):
+        return encode_chat(self.tokenizer, to_messages(self.records[i], self.fmt), self.template,
+                           self.train_on_prompt, self.max_len)
+
+
+def sft_batch_iterator(ds: SFTDataset, seq_length: int, *, packing: bool = True, dp_rank: int = 0, dp_size: int = 1,
+                       seed: int = 1234, pad_id: int = 0, start_sample: int = 0,
+                       pad_to_multiple: int = 1) -> Iterator[Dict[str, torch.Tensor]]:
+    """Infinite iterator of micro-batches of ONE packed row of `seq_length` tokens (or one padded
+    sample when packing is off). Epochs are reshuffled deterministically; rank r takes every
+    dp_size-th bin."""
+    epoch, consumed = 0, start_sample
+    while True:
+        rng = random.Random(seed + epoch)
+        order = list(range(len(ds)))
+        rng.shuffle(order)
+        samples = [ds[i] for i in order]
+        if packing:
+            bins = pack_first_fit_decreasing([len(s[0]) for s in samples], seq_length)
+        else:
+            bins = [[i] for i in range(len(samples))]
+        for b in range(dp_rank, len(bins) - (len(bins) % dp_size if len(bins) >= dp_size else 0), dp_size):
+            if consumed > 0:
+                consumed -= 1
+                continue
+            yield collate_packed([samples[i] for i in bins[b]], seq_length, pad_id, pad_to_multiple)
+        epoch += 1

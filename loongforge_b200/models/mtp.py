@@ -1,0 +1,81 @@
+"""Multi-token prediction (DeepSeek-V3 style): extra depth-k modules that predict token t+1+k from
+the main model's hidden state at t and the embedding of token t+k.
+
+Counterpart of Megatron's ``MultiTokenPredictionBlock`` as used by the reference
+(loongforge/models/foundation/base/base_gpt_model.py:34-41,650-664,782-794) with the checkpoint
+names ``mtp.layers.{k}.{enorm,hnorm,eh_proj,transformer_layer.*,final_layernorm}``
+(configs/models/deepseek3/ckpt_convert/deepseek_v3_2_convert.yaml:70-150). The MTP loss is scaled by
+``mtp_loss_scaling_factor / mtp_num_layers`` and attached to the main loss through the same
+autograd scaler as the MoE auxiliary losses. This implementation requires the MTP block to live
+on the last pipeline stage together with a copy of the embedding when pipeline parallelism is on
+(single-stage models share the embedding module directly).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from ..ops import functional as OF
+from ..parallel import layers as PL
+from ..parallel import state as ps
+from .config import TransformerConfig
+from .moe import AuxLossScaler, track_aux_loss
+from .transformer import Norm, TransformerLayer
+
+
+class MTPLayer(nn.Module):
+    def __init__(self, cfg: TransformerConfig, k: int, device=None, parallel_state=None):
+        super().__init__()
+        self.enorm = Norm(cfg.hidden_size, cfg, device=device)
+        self.hnorm = Norm(cfg.hidden_size, cfg, device=device)
+        self.eh_proj = PL.ColumnParallelLinear(2 * cfg.hidden_size, cfg.hidden_size, gather_output=True,
+                                               init_std=cfg.init_method_std, key=f"mtp.layers.{k}.eh_proj",
+                                               params_dtype=cfg.params_dtype, device=device,
+                                               parallel_state=parallel_state)
+        self.transformer_layer = TransformerLayer(cfg, cfg.num_layers - 1, device=device, parallel_state=parallel_state)
+        self.final_layernorm = Norm(cfg.hidden_size, cfg, device=device)
+
+    def forward(self, hidden, emb_next, rotary, packed):
+        x = self.eh_proj(torch.cat([self.enorm(emb_next), self.hnorm(hidden)], dim=-1))
+        x = self.transformer_layer(x, rotary, packed)
+        return self.final_layernorm(x)
+
+
+class MultiTokenPredictionBlock(nn.Module):
+    def __init__(self, cfg: TransformerConfig, device=None, parallel_state=None):
+        super().__init__()
+        assert not cfg.sequence_parallel, "MTP with sequence parallelism is not supported"
+        self.cfg = cfg
+        self.layers = nn.ModuleList([MTPLayer(cfg, k, device, parallel_state) for k in range(cfg.mtp_num_layers)])
+
+    def attach(self, model, hidden, losses, labels, loss_mask, loss_scale, *, tokens, position_ids, rotary, packed):
+        """Adds the MTP losses to the autograd graph of `losses` and returns `losses`."""
+        cfg = self.cfg
+        st = ps.get_state(model.state_name)
+        T = tokens.shape[0]
+        h = hidden
+        tok, lab = tokens, labels
+        mask = loss_mask.float() if loss_mask is not None else torch.ones(T, device=tokens.device)
+        w = model.shared_embedding_weight()
+        per = cfg.padded_vocab_size // st.dims.tp
+        v0 = st.tp_rank * per
+        valid = max(0, min(per, cfg.vocab_size - v0))
+        total = losses.new_zeros(())
+        for k, layer in enumerate(self.layers):
+            # shift left by one: position t now sees token t+1+k and predicts label t+1+k
+            tok = torch.cat([tok[1:], tok[-1:]])
+            lab = torch.cat([lab[1:], lab[-1:]])
+            mask = torch.cat([mask[1:], mask.new_zeros(1)])
+            if packed is not None and packed.cu_seqlens is not None:
+                ends = (packed.cu_seqlens[1:].long() - 1).clamp_min(0)
+                mask = mask.clone()
+                mask[ends] = 0  # never predict across a packed-sequence boundary
+            emb = model.embed(tok)
+            h = layer(h, emb, rotary, packed)
+            l_k = OF.linear_cross_entropy(h, w, lab, mask, vocab_start=v0, valid_vocab=valid,
+                                          tp_group=st.group("tp") if st.dims.tp > 1 else None,
+                                          chunk_tokens=cfg.cross_entropy_chunk_tokens)
+            mtp_loss = (l_k * mask).sum() / mask.sum().clamp_min(1)
+            track_aux_loss("mtp_loss", mtp_loss, k, max(cfg.mtp_num_layers, 1))
+            total = total + mtp_loss * (cfg.mtp_loss_scaling_factor / cfg.mtp_num_layers)
+        return AuxLossScaler.apply(losses, total)

@@ -1,0 +1,113 @@
+"""Vision-language trainer (pre-training and SFT): builds the ViT + projector + LLM composition with
+a separate parallel state for the encoder, feeds packed text + image batches, computes the loss on
+text positions only (loongforge/train/pretrain/pretrain_vlm.py:78-521, loongforge/train/sft/sft_vlm.py)."""
+from __future__ import annotations
+
+from typing import Dict, Iterator, Optional
+
+import torch
+
+from ..data.position_ids import mrope_ids
+from ..models.config import TransformerConfig
+from ..models.omni import ENCODER_STATE, OmniCombinationModel
+from ..models.registry import get_model_config
+from ..models.transformer import PackedSeqParams
+from ..parallel import state as ps
+from ..parallel.state import ParallelDims
+from .trainer import Trainer
+
+
+def synthetic_vlm_iterator(vocab_size: int, seq_length: int, *, images_per_sample: int = 4, image_size: int = 448,
+                           patch: int = 14, temporal_patch: int = 2, merge: int = 2, channels: int = 3,
+                           image_token_id: Optional[int] = None, dp_rank: int = 0, dp_size: int = 1, seed: int = 1234,
+                           pin_memory: Optional[bool] = None) -> Iterator[Dict[str, torch.Tensor]]:
+    """Packed samples: `images_per_sample` synthetic images (pixels ~ N(0,1), already patchified to
+    ``[n_patches, C*t*p*p]``) whose merged tokens are interleaved with uniform random text tokens up
+    to `seq_length`; labels are -100 (masked) on image positions."""
+    image_token_id = vocab_size - 1 if image_token_id is None else image_token_id
+    g = image_size // patch
+    tokens_per_image = (g // merge) ** 2
+    n_patch = g * g
+    pin = torch.cuda.is_available() if pin_memory is None else pin_memory
+    step = 0
+    text_total = seq_length - images_per_sample * tokens_per_image
+    assert text_total > images_per_sample, "sequence too short for the images"
+    while True:
+        gen = torch.Generator()
+        gen.manual_seed(seed * 7919 + step * dp_size + dp_rank)
+        toks = torch.randint(0, vocab_size - 1, (seq_length + 1,), generator=gen)
+        seg = text_total // (images_per_sample + 1)
+        pos = 0
+        tokens = toks[:-1].clone()
+        for i in range(images_per_sample):
+            pos += seg
+            tokens[pos:pos + tokens_per_image] = image_token_id
+            pos += tokens_per_image
+        labels = toks[1:].clone()
+        # no loss where the INPUT or the TARGET is an image placeholder
+        is_img = tokens == image_token_id
+        nxt_img = torch.cat([is_img[1:], is_img.new_zeros(1)])
+        mask = (~is_img & ~nxt_img).float()
+        pixels = torch.randn(images_per_sample * n_patch, channels * temporal_patch * patch * patch, generator=gen)
+        grid = torch.tensor([[1, g, g]] * images_per_sample)
+        batch = {"tokens": tokens.unsqueeze(0), "labels": labels.unsqueeze(0), "loss_mask": mask.unsqueeze(0),
+                 "position_ids": mrope_ids(tokens, grid, image_token_id, merge).unsqueeze(1),  # [3, 1, T]
+                 "pixels": pixels, "grid_thw": grid}
+        if pin:
+            batch = {k: v.pin_memory() for k, v in batch.items()}
+        batch["num_valid_tokens"] = int(mask.sum().item())
+        yield batch
+        step += 1
+
+
+class VLMTrainer(Trainer):
+    def __init__(self, model_cfg: TransformerConfig, train_cfg, dims: Optional[ParallelDims] = None, *,
+                 vit_cfg: Optional[TransformerConfig] = None, encoder_tp: int = 1, encoder_hetero_dp: bool = False,
+                 image_token_id: Optional[int] = None, encoder_recompute: bool = True, **kw):
+        self.vit_cfg = vit_cfg or get_model_config("qwen2.5-vit")
+        if encoder_recompute:
+            self.vit_cfg.recompute_granularity = "full"
+        self.encoder_hetero_dp = encoder_hetero_dp
+        self.image_token_id = model_cfg.vocab_size - 1 if image_token_id is None else image_token_id
+        dims = dims or ParallelDims()
+        if not ps.model_parallel_is_initialized():
+            ps.initialize_model_parallel(dims)
+            # the encoder gets its own tensor-parallel degree (must divide the decoder's)
+            ps.create_parallel_state(ENCODER_STATE, ParallelDims(tp=encoder_tp, pp=dims.pp, cp=dims.cp))
+        if train_cfg.bf16:
+            self.vit_cfg.params_dtype = torch.bfloat16
+        super().__init__(model_cfg, train_cfg, dims, **kw)
+
+    def _default_model_provider(self, pre_process, post_process, layer_numbers):
+        return OmniCombinationModel(self.mcfg, self.vit_cfg if pre_process else None, image_token_id=self.image_token_id,
+                                    pre_process=pre_process, post_process=post_process, layer_numbers=layer_numbers,
+                                    device=self.device, encoder_hetero_dp=self.encoder_hetero_dp)
+
+    def build_data_iterator(self, args=None):
+        st = self.st
+        v = self.vit_cfg
+        return synthetic_vlm_iterator(self.mcfg.vocab_size, self.tcfg.seq_length, patch=v.patch_size,
+                                      temporal_patch=v.temporal_patch_size, merge=v.spatial_merge_size,
+                                      channels=v.in_channels, image_token_id=self.image_token_id, dp_rank=st.dp_rank,
+                                      dp_size=st.dp_size, seed=self.tcfg.seed)
+
+    def _default_forward_step(self, data_iterator, model):
+        b = self.get_batch(data_iterator)
+        tokens = b["tokens"].reshape(-1)
+        labels = b["labels"].reshape(-1)
+        mask = b["loss_mask"].reshape(-1)
+        pos = b["position_ids"].reshape(3, -1)
+        nmb = self.mb_calc.num_microbatches
+        n_valid = max(int(b.get("num_valid_tokens", mask.numel())), 1)
+        scale = 1.0 / (n_valid * nmb)
+        packed = PackedSeqParams(cu_seqlens=b["cu_seqlens"]) if "cu_seqlens" in b else None
+        first = self.st.is_first_stage
+        out = model(tokens, pos, pixels=b["pixels"].to(self.mcfg.params_dtype) if first else None,
+                    grid_thw=b["grid_thw"] if first else None, labels=labels, loss_mask=mask, packed=packed,
+                    loss_scale=scale)
+
+        def loss_func(losses):
+            loss = (losses * mask.float()).sum() * scale
+            return loss, {"lm loss": loss.detach() * nmb, "num_tokens": n_valid}
+
+        return out, loss_func

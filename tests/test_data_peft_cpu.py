@@ -1,0 +1,115 @@
+"""Data pipeline (chat templates, packing, indexed datasets), tokenizer, LoRA and the VLM trainer on CPU."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+
+def test_chat_template_masks_only_assistant_tokens():
+    from loongforge_b200.data.chat_template import encode_chat, to_messages
+    from loongforge_b200.tokenizer.tokenizer import ByteTokenizer
+
+    tok = ByteTokenizer(["<|im_start|>", "<|im_end|>"])
+    msgs = to_messages({"instruction": "Add", "input": "1+1", "output": "2"})
+    ids, labels = encode_chat(tok, msgs, "chatml")
+    assert len(ids) == len(labels)
+    tgt = [i for i, l in zip(ids, labels) if l != -100]
+    assert tok.detokenize(tgt) == "2<|im_end|>\n"
+    assert tok.detokenize(ids).startswith("<|im_start|>user\nAdd\n1+1<|im_end|>")
+    sg = to_messages({"conversations": [{"from": "human", "value": "hi"}, {"from": "gpt", "value": "yo"}]})
+    assert [m["role"] for m in sg] == ["user", "assistant"]
+
+
+def test_packing_and_lpt():
+    from loongforge_b200.data.packing import collate_packed, lpt_partition, pack_first_fit_decreasing
+
+    lens = [900, 300, 700, 120, 60, 1000, 40]
+    bins = pack_first_fit_decreasing(lens, 1024)
+    assert sorted(i for b in bins for i in b) == list(range(len(lens)))
+    assert all(sum(min(lens[i], 1024) for i in b) <= 1024 for b in bins)
+    groups = lpt_partition([5, 3, 3, 2, 2, 1], 2)
+    loads = [sum([5, 3, 3, 2, 2, 1][i] for i in g) for g in groups]
+    assert abs(loads[0] - loads[1]) <= 1
+    b = collate_packed([([1, 2, 3, 4], [-100, -100, 3, 4]), ([5, 6, 7], [-100, 6, 7])], 16)
+    assert b["tokens"].shape == (1, 16) and b["cu_seqlens"].tolist() == [0, 4, 7, 16]
+    assert b["position_ids"][0, :7].tolist() == [0, 1, 2, 3, 0, 1, 2]
+    assert b["loss_mask"][0, :7].tolist() == [0, 1, 1, 0, 1, 1, 0] and b["num_valid_tokens"] == 4
+
+
+def test_indexed_dataset_roundtrip(tmp_path):
+    from loongforge_b200.data.indexed_dataset import GPTDataset, IndexedDataset, IndexedDatasetWriter
+
+    w = IndexedDatasetWriter(str(tmp_path / "corpus"), np.int32)
+    docs = [list(range(10)), list(range(100, 137)), [7, 8, 9, 1]]
+    for d in docs:
+        w.add_document(d)
+    w.finalize()
+    ds = IndexedDataset(str(tmp_path / "corpus"))
+    assert len(ds) == 3 and [ds[i].tolist() for i in range(3)] == docs and ds.num_tokens == 51
+    g = GPTDataset(ds, seq_length=8, num_samples=5, seed=1)
+    s = g[0]
+    assert s["tokens"].shape == (8,) and torch.equal(s["tokens"][1:], s["labels"][:-1])
+
+
+def test_lora_trains_only_adapters_and_merges():
+    from loongforge_b200.models.gpt import GPTModel
+    from loongforge_b200.models.peft import adapter_state_dict, apply_lora, merge_lora
+    from loongforge_b200.models.registry import get_model_config
+
+    torch.manual_seed(0)
+    m = GPTModel(get_model_config("tiny-llama"))
+    T = 32
+    tok = torch.randint(0, 32000, (T,))
+    base = m(tok, torch.arange(T))
+    names = apply_lora(m, rank=4, alpha=8, canonical=True)
+    assert len(names) == 8
+    assert torch.allclose(m(tok, torch.arange(T)), base, atol=1e-5)  # B starts at zero
+    trainable = [n for n, p in m.named_parameters() if p.requires_grad]
+    assert trainable and all("lora_" in n for n in trainable)
+    for n, p in m.named_parameters():
+        if "lora_B" in n:
+            torch.nn.init.normal_(p, std=0.02)
+    tuned = m(tok, torch.arange(T))
+    assert len(adapter_state_dict(m)) == 16
+    assert merge_lora(m) == 8
+    assert torch.allclose(m(tok, torch.arange(T)), tuned, atol=1e-4)
+
+
+def test_sft_trainer_with_packed_data(tmp_path):
+    from loongforge_b200.data.sft import SFTDataset, sft_batch_iterator
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.runtime.sft import SFTTrainer
+    from loongforge_b200.runtime.trainer import TrainConfig
+    from loongforge_b200.tokenizer.tokenizer import ByteTokenizer
+
+    p = tmp_path / "d.jsonl"
+    with open(p, "w") as f:
+        for i in range(40):
+            f.write(json.dumps({"instruction": f"say {i}", "output": "ok " * (i % 7 + 1)}) + "\n")
+    tok = ByteTokenizer(["<|im_start|>", "<|im_end|>"])
+    ds = SFTDataset([str(p)], tok, max_len=128)
+    it = sft_batch_iterator(ds, 128, packing=True, pad_id=tok.pad)
+    cfg = get_model_config("tiny-llama", vocab_size=tok.vocab_size, make_vocab_size_divisible_by=8)
+    tr = SFTTrainer(cfg, TrainConfig(micro_batch_size=1, global_batch_size=2, seq_length=128, train_iters=4, lr=2e-3,
+                                     training_phase="sft", log_interval=100), lora=dict(rank=4, alpha=8))
+    losses = [tr.train_step(it)["lm loss"] for _ in range(6)]
+    assert losses[-1] < losses[0]
+
+
+def test_vlm_trainer_loss_on_text_only():
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.runtime.trainer import TrainConfig
+    from loongforge_b200.runtime.vlm import VLMTrainer, synthetic_vlm_iterator
+
+    lm = get_model_config("tiny-llama", position_embedding_type="mrope", mrope_section=[8, 12, 12])
+    vit = get_model_config("tiny-vit")
+    tr = VLMTrainer(lm, TrainConfig(micro_batch_size=1, global_batch_size=1, seq_length=128, train_iters=2, lr=1e-3,
+                                    log_interval=100), vit_cfg=vit)
+    it = synthetic_vlm_iterator(lm.vocab_size, 128, images_per_sample=2, image_size=112, pin_memory=False)
+    b = next(it)
+    assert b["pixels"].shape == (2 * 64, 3 * 2 * 14 * 14) and (b["tokens"] == lm.vocab_size - 1).sum() == 2 * 16
+    assert float((b["loss_mask"][0][b["tokens"][0] == lm.vocab_size - 1]).sum()) == 0.0
+    m = tr.train_step(it)
+    assert np.isfinite(m["lm loss"]) and m["grad_norm"] > 0
