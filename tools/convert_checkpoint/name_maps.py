@@ -1,0 +1,187 @@
+"""Hugging Face <-> Megatron-core parameter mapping for decoder-only language models.
+
+The reference drives its converter with per-family YAML name maps
+(configs/models/*/ckpt_convert/*.yaml; e.g. llama3_convert.yaml:17-70) and a two-step pipeline
+HF -> "common" -> mcore (tools/convert_checkpoint/module_convertor/model.py:250-383). Here the common
+form is simply the UNSHARDED Megatron state dict; one table describes a family:
+
+  * plain renames (embedding, norms, proj, fc2, router, lm head),
+  * packed QKV: per KV group rows ``[q_0 .. q_{r-1}, k, v]`` (hf_attn_converter.py:62-78),
+  * SwiGLU FC1 = ``cat([gate, up])`` (huggingface_base.py:495-524),
+  * MoE experts as ``experts.linear_fc{1,2}.weight{e}`` (mcore_moe.py:60-74).
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Dict, List, Optional
+
+import torch
+
+
+@dataclasses.dataclass
+class FamilyMap:
+    name: str
+    qkv_bias: bool = False
+    qk_norm: bool = False
+    moe: bool = False
+    hf_prefix: str = "model."
+    hf_layers: str = "model.layers.{i}."
+    expert_tpl: str = "mlp.experts.{e}."
+    router: str = "mlp.gate.weight"
+    shared_expert: Optional[str] = None  # e.g. "mlp.shared_experts."
+
+
+FAMILIES: Dict[str, FamilyMap] = {
+    "llama": FamilyMap("llama"),
+    "llama2": FamilyMap("llama2"),
+    "llama3": FamilyMap("llama3"),
+    "internlm": FamilyMap("internlm"),
+    "qwen2": FamilyMap("qwen2", qkv_bias=True),
+    "qwen2.5": FamilyMap("qwen2.5", qkv_bias=True),
+    "qwen3": FamilyMap("qwen3", qk_norm=True),
+    "qwen3_moe": FamilyMap("qwen3_moe", qk_norm=True, moe=True),
+}
+
+
+def pack_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, num_groups: int) -> torch.Tensor:
+    """[nq*d, ...], [ng*d, ...], [ng*d, ...] -> Megatron packed [(nq + 2 ng) * d, ...] per-group order."""
+    tail = q.shape[1:]
+    d = k.shape[0] // num_groups
+    r = q.shape[0] // k.shape[0]
+    qg = q.reshape(num_groups, r * d, *tail)
+    kg = k.reshape(num_groups, d, *tail)
+    vg = v.reshape(num_groups, d, *tail)
+    return torch.cat([qg, kg, vg], dim=1).reshape(-1, *tail)
+
+
+def unpack_qkv(w: torch.Tensor, num_heads: int, num_groups: int):
+    tail = w.shape[1:]
+    d = w.shape[0] // (num_heads + 2 * num_groups)
+    r = num_heads // num_groups
+    g = w.reshape(num_groups, (r + 2) * d, *tail)
+    q = g[:, : r * d].reshape(-1, *tail)
+    k = g[:, r * d:(r + 1) * d].reshape(-1, *tail)
+    v = g[:, (r + 1) * d:].reshape(-1, *tail)
+    return q.contiguous(), k.contiguous(), v.contiguous()
+
+
+def pad_vocab(w: torch.Tensor, padded: int) -> torch.Tensor:
+    """Pad the vocabulary dimension by repeating the last row (tools/convert_checkpoint/utils/utils.py:71-98)."""
+    if w.shape[0] >= padded:
+        return w
+    return torch.cat([w, w[-1:].expand(padded - w.shape[0], -1)], 0).contiguous()
+
+
+def hf_to_mcore(hf: Dict[str, torch.Tensor], fam: FamilyMap, *, num_layers: int, num_heads: int, num_groups: int,
+                padded_vocab: Optional[int] = None, num_experts: Optional[int] = None,
+                tie_embeddings: bool = False) -> Dict[str, torch.Tensor]:
+    out: Dict[str, torch.Tensor] = {}
+    emb = hf[fam.hf_prefix + "embed_tokens.weight"]
+    out["embedding.word_embeddings.weight"] = pad_vocab(emb, padded_vocab or emb.shape[0])
+    for i in range(num_layers):
+        h = fam.hf_layers.format(i=i)
+        m = f"decoder.layers.{i}."
+        out[m + "self_attention.linear_qkv.layer_norm_weight"] = hf[h + "input_layernorm.weight"]
+        out[m + "self_attention.linear_qkv.weight"] = pack_qkv(hf[h + "self_attn.q_proj.weight"],
+                                                               hf[h + "self_attn.k_proj.weight"],
+                                                               hf[h + "self_attn.v_proj.weight"], num_groups)
+        if fam.qkv_bias:
+            out[m + "self_attention.linear_qkv.bias"] = pack_qkv(hf[h + "self_attn.q_proj.bias"],
+                                                                 hf[h + "self_attn.k_proj.bias"],
+                                                                 hf[h + "self_attn.v_proj.bias"], num_groups)
+        if fam.qk_norm:
+            out[m + "self_attention.q_layernorm.weight"] = hf[h + "self_attn.q_norm.weight"]
+            out[m + "self_attention.k_layernorm.weight"] = hf[h + "self_attn.k_norm.weight"]
+        out[m + "self_attention.linear_proj.weight"] = hf[h + "self_attn.o_proj.weight"]
+        post = hf[h + "post_attention_layernorm.weight"]
+        if fam.moe and (h + fam.router) in hf:
+            out[m + "pre_mlp_layernorm.weight"] = post
+            out[m + "mlp.router.weight"] = hf[h + fam.router]
+            for e in range(num_experts):
+                p = h + fam.expert_tpl.format(e=e)
+                out[m + f"mlp.experts.linear_fc1.weight{e}"] = torch.cat([hf[p + "gate_proj.weight"],
+                                                                          hf[p + "up_proj.weight"]], 0)
+                out[m + f"mlp.experts.linear_fc2.weight{e}"] = hf[p + "down_proj.weight"]
+        else:
+            out[m + "mlp.linear_fc1.layer_norm_weight"] = post
+            out[m + "mlp.linear_fc1.weight"] = torch.cat([hf[h + "mlp.gate_proj.weight"], hf[h + "mlp.up_proj.weight"]], 0)
+            out[m + "mlp.linear_fc2.weight"] = hf[h + "mlp.down_proj.weight"]
+    out["decoder.final_layernorm.weight"] = hf[fam.hf_prefix + "norm.weight"]
+    if not tie_embeddings:
+        head = hf.get("lm_head.weight", emb)
+        out["output_layer.weight"] = pad_vocab(head, padded_vocab or head.shape[0])
+    return out
+
+
+def mcore_to_hf(mc: Dict[str, torch.Tensor], fam: FamilyMap, *, num_layers: int, num_heads: int, num_groups: int,
+                vocab_size: Optional[int] = None, num_experts: Optional[int] = None,
+                tie_embeddings: bool = False) -> Dict[str, torch.Tensor]:
+    out: Dict[str, torch.Tensor] = {}
+
+    def strip(w):
+        return w[:vocab_size].contiguous() if vocab_size else w
+
+    out[fam.hf_prefix + "embed_tokens.weight"] = strip(mc["embedding.word_embeddings.weight"])
+    for i in range(num_layers):
+        h = fam.hf_layers.format(i=i)
+        m = f"decoder.layers.{i}."
+        out[h + "input_layernorm.weight"] = mc[m + "self_attention.linear_qkv.layer_norm_weight"]
+        q, k, v = unpack_qkv(mc[m + "self_attention.linear_qkv.weight"], num_heads, num_groups)
+        out[h + "self_attn.q_proj.weight"], out[h + "self_attn.k_proj.weight"], out[h + "self_attn.v_proj.weight"] = q, k, v
+        if fam.qkv_bias:
+            qb, kb, vb = unpack_qkv(mc[m + "self_attention.linear_qkv.bias"], num_heads, num_groups)
+            out[h + "self_attn.q_proj.bias"], out[h + "self_attn.k_proj.bias"], out[h + "self_attn.v_proj.bias"] = qb, kb, vb
+        if fam.qk_norm:
+            out[h + "self_attn.q_norm.weight"] = mc[m + "self_attention.q_layernorm.weight"]
+            out[h + "self_attn.k_norm.weight"] = mc[m + "self_attention.k_layernorm.weight"]
+        out[h + "self_attn.o_proj.weight"] = mc[m + "self_attention.linear_proj.weight"]
+        if (m + "mlp.router.weight") in mc:
+            out[h + "post_attention_layernorm.weight"] = mc[m + "pre_mlp_layernorm.weight"]
+            out[h + fam.router] = mc[m + "mlp.router.weight"]
+            for e in range(num_experts):
+                p = h + fam.expert_tpl.format(e=e)
+                g, u = mc[m + f"mlp.experts.linear_fc1.weight{e}"].chunk(2, 0)
+                out[p + "gate_proj.weight"], out[p + "up_proj.weight"] = g.contiguous(), u.contiguous()
+                out[p + "down_proj.weight"] = mc[m + f"mlp.experts.linear_fc2.weight{e}"]
+        else:
+            out[h + "post_attention_layernorm.weight"] = mc[m + "mlp.linear_fc1.layer_norm_weight"]
+            g, u = mc[m + "mlp.linear_fc1.weight"].chunk(2, 0)
+            out[h + "mlp.gate_proj.weight"], out[h + "mlp.up_proj.weight"] = g.contiguous(), u.contiguous()
+            out[h + "mlp.down_proj.weight"] = mc[m + "mlp.linear_fc2.weight"]
+    out[fam.hf_prefix + "norm.weight"] = mc["decoder.final_layernorm.weight"]
+    if not tie_embeddings and "output_layer.weight" in mc:
+        out["lm_head.weight"] = strip(mc["output_layer.weight"])
+    return out
+
+
+# ---- tensor / pipeline / expert sharding of the unsharded Megatron dict -----------------------
+def tp_rule(key: str):
+    """(partition_dim, stride) of a Megatron key, or None when replicated."""
+    if key.endswith(("linear_qkv.weight", "linear_qkv.bias", "embedding.word_embeddings.weight", "output_layer.weight")):
+        return 0, 1
+    if key.endswith(("linear_fc1.weight", "linear_fc1.bias")) and ".experts." not in key:
+        return 0, 2
+    if key.endswith(("linear_proj.weight", "linear_fc2.weight")) and ".experts." not in key:
+        return 1, 1
+    return None
+
+
+def shard_tp(key: str, w: torch.Tensor, rank: int, tp: int) -> torch.Tensor:
+    rule = tp_rule(key)
+    if rule is None or tp == 1:
+        return w
+    dim, stride = rule
+    if stride == 1:
+        return w.chunk(tp, dim)[rank].contiguous()
+    return torch.cat([b.chunk(tp, dim)[rank] for b in w.chunk(stride, dim)], dim).contiguous()
+
+
+def merge_tp(key: str, shards: List[torch.Tensor]) -> torch.Tensor:
+    rule = tp_rule(key)
+    if rule is None or len(shards) == 1:
+        return shards[0]
+    dim, stride = rule
+    if stride == 1:
+        return torch.cat(shards, dim)
+    blocks = [s.chunk(stride, dim) for s in shards]
+    return torch.cat([torch.cat([b[j] for b in blocks], dim) for j in range(stride)], dim)
