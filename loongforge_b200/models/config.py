@@ -73,7 +73,8 @@ class TransformerConfig:
     moe_router_load_balancing_type: str = "aux_loss"  # aux_loss | seq_aux_loss | none
     moe_aux_loss_coeff: float = 0.0
     moe_z_loss_coeff: Optional[float] = None
-    moe_token_dispatcher_type: str = "alltoall"
+    moe_token_dispatcher_type: str = "alltoall"  # alltoall (NCCL) | peer (NVLink peer-memory kernels, CUDA only)
+    moe_peer_capacity_factor: float = 2.0  # receive-buffer rows per rank = factor * local tokens * top-k
     moe_grouped_gemm: bool = True
     moe_expert_capacity_factor: Optional[float] = None
     # ---- MLA / DSA

@@ -149,7 +149,9 @@ class GroupedMLP(nn.Module):
         self.glu = glu
         self.act = cfg.activation
 
-    def forward(self, x, tokens_per_expert):
+    def forward(self, x, tokens_per_expert, row_probs=None):
+        """``row_probs`` [rows]: router probability of each received row, multiplied in before FC2
+        (dispatchers that sum expert outputs unweighted pass it; Megatron's weighted-SwiGLU form)."""
         h = self.linear_fc1(x, tokens_per_expert)
         if self.glu and self.act == "swiglu":
             h = OF.swiglu(h)
@@ -158,6 +160,8 @@ class GroupedMLP(nn.Module):
             h = torch.nn.functional.gelu(g) * u
         else:
             h = torch.nn.functional.gelu(h)
+        if row_probs is not None:
+            h = h * row_probs.unsqueeze(-1).to(h.dtype)
         return self.linear_fc2(h, tokens_per_expert)
 
 
@@ -237,12 +241,23 @@ class MoELayer(nn.Module):
         else:
             self.shared_experts = None
         self.dispatcher = AlltoAllDispatcher(E, parallel_state)
+        self.peer_dispatcher = None
+        if cfg.moe_token_dispatcher_type == "peer":
+            from ..parallel.moe_peer import PeerDispatcher
+            self.peer_dispatcher = PeerDispatcher(E, cfg.hidden_size, ep, st.ep_rank, st.group("ep") if ep > 1 else None,
+                                                  cfg.moe_peer_capacity_factor)
 
     def forward(self, x: torch.Tensor, seq_lens=None) -> torch.Tensor:
         probs, routing_map = self.router(x, seq_lens)
-        tokens, tpe = self.dispatcher.dispatch(x, probs, routing_map)
-        y = self.experts(tokens, tpe)
-        out = self.dispatcher.combine(y)
+        if self.peer_dispatcher is not None and x.is_cuda and x.dtype == torch.bfloat16:
+            # indices of the k selected experts of every token (order within a token is irrelevant)
+            topk_idx = routing_map.to(torch.float16).topk(self.cfg.moe_router_topk, dim=1).indices
+            tokens, tpe, row_probs = self.peer_dispatcher.dispatch(x, probs, topk_idx)
+            out = self.peer_dispatcher.combine(self.experts(tokens, tpe, row_probs))
+        else:
+            tokens, tpe = self.dispatcher.dispatch(x, probs, routing_map)
+            y = self.experts(tokens, tpe)
+            out = self.dispatcher.combine(y)
         if self.shared_experts is not None:
             st = ps.get_state(self.state_name)
             if st.dims.tp > 1:

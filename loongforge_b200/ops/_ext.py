@@ -40,6 +40,10 @@ def _sources() -> tuple[list[str], list[str]]:
         defs.append("-DLF_HAVE_ATTN")
     if os.path.exists(os.path.join(_CSRC, "peer_gemm.cu")):
         defs.append("-DLF_HAVE_PEER")
+    if os.path.exists(os.path.join(_CSRC, "moe_peer.cu")):
+        defs.append("-DLF_HAVE_MOE_PEER")
+    if os.path.exists(os.path.join(_CSRC, "grouped_gemm_sm100.cu")):
+        defs.append("-DLF_HAVE_GROUPED")
     return srcs, defs
 
 
@@ -155,6 +159,7 @@ STATUS_NAMES = {
     4: "MMA warp timed out waiting for a drained accumulator",
     5: "timed out waiting for a flag written by a peer GPU",
     6: "bad argument detected on the device",
+    7: "an index read from device memory was out of range (access skipped)",
 }
 
 

@@ -5,6 +5,7 @@
 #include <torch/extension.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <algorithm>
 #include <cstdint>
 #include "elementwise.h"
 #include "gemm_sm100.h"
@@ -13,6 +14,12 @@
 #endif
 #ifdef LF_HAVE_PEER
 #include "peer_gemm.h"
+#endif
+#ifdef LF_HAVE_GROUPED
+#include "grouped_gemm_sm100.h"
+#endif
+#ifdef LF_HAVE_MOE_PEER
+#include "moe_peer.h"
 #endif
 
 namespace {
@@ -465,6 +472,229 @@ at::Tensor gemm_rs(const at::Tensor& A, const at::Tensor& B, bool b_mn_major, st
 
 #endif  // LF_HAVE_PEER
 
+// ------------------------------------------------------------------ MoE router
+// Returns (probs [T,E] f32, routing_map [T,E] bool, aux_scores [T,E] f32, topk_idx [T,k] i32, counts [E] i32).
+std::vector<at::Tensor> router_fwd(const at::Tensor& logits, c10::optional<at::Tensor> bias, int64_t k, int64_t score,
+                                   int64_t num_groups, int64_t group_topk, double scale) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous());
+  TORCH_CHECK(logits.scalar_type() == at::kFloat || logits.scalar_type() == at::kBFloat16);
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t T = logits.size(0), E = logits.size(1);
+  auto f32 = logits.options().dtype(at::kFloat);
+  at::Tensor probs = at::empty({T, E}, f32), aux = at::empty({T, E}, f32);
+  at::Tensor map = at::empty({T, E}, logits.options().dtype(at::kBool));
+  at::Tensor idx = at::empty({T, k}, logits.options().dtype(at::kInt));
+  at::Tensor counts = at::zeros({E}, logits.options().dtype(at::kInt));
+  lf::RouterArgs a;
+  a.logits = logits.data_ptr();
+  a.logits_bf16 = logits.scalar_type() == at::kBFloat16;
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->scalar_type() == at::kFloat && bias->is_contiguous() && bias->numel() == E);
+    a.bias = bias->data_ptr<float>();
+  }
+  a.probs = probs.data_ptr<float>();
+  a.map = reinterpret_cast<unsigned char*>(map.data_ptr());
+  a.aux = aux.data_ptr<float>();
+  a.topk_idx = idx.data_ptr<int>();
+  a.counts = counts.data_ptr<int>();
+  a.T = static_cast<int>(T); a.E = static_cast<int>(E); a.k = static_cast<int>(k); a.score = static_cast<int>(score);
+  a.num_groups = static_cast<int>(num_groups); a.group_topk = static_cast<int>(group_topk);
+  a.scale = static_cast<float>(scale);
+  const int rc = lf::router_fwd(a, cur_stream());
+  TORCH_CHECK(rc == 0, "router_fwd: unsupported shape (code ", rc, ")");
+  ++g_launches;
+  return {probs, map, aux, idx, counts};
+}
+
+at::Tensor router_bwd(const at::Tensor& logits, const at::Tensor& map, const at::Tensor& dprobs,
+                      c10::optional<at::Tensor> daux, int64_t k, int64_t score, double scale) {
+  TORCH_CHECK(logits.is_cuda() && logits.is_contiguous() && map.is_contiguous() && dprobs.is_contiguous());
+  TORCH_CHECK(dprobs.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(logits.device());
+  at::Tensor dl = at::empty(logits.sizes(), logits.options().dtype(at::kFloat));
+  lf::RouterArgs a;
+  a.logits = logits.data_ptr();
+  a.logits_bf16 = logits.scalar_type() == at::kBFloat16;
+  a.map = reinterpret_cast<unsigned char*>(map.data_ptr());
+  a.dprobs = dprobs.data_ptr<float>();
+  if (daux.has_value()) {
+    TORCH_CHECK(daux->scalar_type() == at::kFloat && daux->is_contiguous());
+    a.daux = daux->data_ptr<float>();
+  }
+  a.dlogits = dl.data_ptr<float>();
+  a.T = static_cast<int>(logits.size(0)); a.E = static_cast<int>(logits.size(1));
+  a.k = static_cast<int>(k); a.score = static_cast<int>(score); a.scale = static_cast<float>(scale);
+  const int rc = lf::router_bwd(a, cur_stream());
+  TORCH_CHECK(rc == 0, "router_bwd: unsupported shape (code ", rc, ")");
+  ++g_launches;
+  return dl;
+}
+
+#ifdef LF_HAVE_GROUPED
+// ------------------------------------------------------------------ grouped (per-expert) GEMM
+// Rows of `A` (and `X`) are sorted by expert; expert e owns `tpe[e]` consecutive rows.
+//   mode 0 forward: outs[0][rows_e, N] = A[rows_e, K] * weights[e][N, K]^T
+//   mode 1 dgrad  : outs[0][rows_e, K] = A[rows_e, N] * weights[e][N, K]
+//   mode 2 wgrad  : outs[e][N, K] (=|+=) A[rows_e, N]^T * X[rows_e, K]     (weights unused)
+// One launch for all experts; descriptors are built on the host and copied with the stream.
+void grouped_gemm(const at::Tensor& A, c10::optional<at::Tensor> X_, std::vector<at::Tensor> weights,
+                  std::vector<at::Tensor> outs, std::vector<int64_t> tpe, int64_t mode, int64_t out_mode,
+                  const at::Tensor& status) {
+  check_bf16_cuda(A, "A");
+  TORCH_CHECK(A.dim() == 2 && A.stride(1) == 1);
+  c10::cuda::CUDAGuard guard(A.device());
+  const int64_t E = static_cast<int64_t>(tpe.size());
+  TORCH_CHECK(E > 0);
+  const bool a_mn = mode == 2, b_mn = mode != 0;
+  const char* a_ptr = static_cast<const char*>(A.data_ptr());
+  const int64_t lda = A.stride(0);
+  at::Tensor X;
+  if (mode == 2) {
+    TORCH_CHECK(X_.has_value());
+    X = *X_;
+    check_bf16_cuda(X, "X");
+    TORCH_CHECK(X.dim() == 2 && X.stride(1) == 1 && X.size(0) == A.size(0));
+    TORCH_CHECK(static_cast<int64_t>(outs.size()) == E);
+  } else {
+    TORCH_CHECK(static_cast<int64_t>(weights.size()) == E && outs.size() == 1);
+    TORCH_CHECK(outs[0].dim() == 2 && outs[0].stride(1) == 1 && outs[0].size(0) == A.size(0));
+  }
+  auto host_opts = at::TensorOptions().dtype(at::kByte).pinned_memory(true);
+  at::Tensor desc_h = at::empty({E * static_cast<int64_t>(sizeof(lf::GroupDesc))}, host_opts);
+  auto* descs = reinterpret_cast<lf::GroupDesc*>(desc_h.data_ptr());
+  std::vector<int> order;
+  int64_t num_tiles = 0, row = 0;
+  std::vector<int> tiles_of(E, 0);
+  for (int64_t e = 0; e < E; ++e) {
+    const int64_t n = tpe[e];
+    int rc = 0;
+    if (mode == 0 || mode == 1) {
+      const at::Tensor& w = weights[e];
+      check_bf16_cuda(w, "weight");
+      TORCH_CHECK(w.dim() == 2 && w.stride(1) == 1);
+      const int64_t Nout = mode == 0 ? w.size(0) : w.size(1);
+      const int64_t Kc = mode == 0 ? w.size(1) : w.size(0);
+      TORCH_CHECK(A.size(1) == Kc && outs[0].size(1) == Nout, "grouped_gemm shape mismatch");
+      char* d_ptr = static_cast<char*>(outs[0].data_ptr()) + row * outs[0].stride(0) * outs[0].element_size();
+      rc = lf::grouped_gemm_fill_desc(&descs[e], a_ptr + row * lda * 2, lda, w.data_ptr(), w.stride(0), d_ptr,
+                                      outs[0].stride(0), static_cast<int>(n), static_cast<int>(Nout),
+                                      static_cast<int>(Kc), a_mn, b_mn, static_cast<int>(out_mode));
+      tiles_of[e] = n > 0 ? lf::grouped_gemm_tiles_for(static_cast<int>(n), static_cast<int>(Nout)) : 0;
+    } else {
+      const at::Tensor& d = outs[e];
+      TORCH_CHECK(d.is_cuda() && d.dim() == 2 && d.stride(1) == 1 && d.size(0) == A.size(1) && d.size(1) == X.size(1));
+      TORCH_CHECK(out_mode == 0 ? d.scalar_type() == at::kBFloat16 : d.scalar_type() == at::kFloat);
+      rc = lf::grouped_gemm_fill_desc(&descs[e], a_ptr + row * lda * 2, lda,
+                                      static_cast<const char*>(X.data_ptr()) + row * X.stride(0) * 2, X.stride(0),
+                                      d.data_ptr(), d.stride(0), static_cast<int>(A.size(1)),
+                                      static_cast<int>(X.size(1)), static_cast<int>(n), a_mn, b_mn,
+                                      static_cast<int>(out_mode));
+      tiles_of[e] = n > 0 ? lf::grouped_gemm_tiles_for(static_cast<int>(A.size(1)), static_cast<int>(X.size(1))) : 0;
+    }
+    TORCH_CHECK(rc == 0, "grouped_gemm descriptor for expert ", e, " failed with code ", rc);
+    num_tiles += tiles_of[e];
+    order.push_back(static_cast<int>(e));
+    row += n;
+  }
+  TORCH_CHECK(row == A.size(0), "tokens_per_expert sums to ", row, ", expected ", A.size(0));
+  if (num_tiles == 0) return;
+  // longest contraction first: with a static round-robin walk this keeps the tail short in wgrad
+  if (mode == 2) std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return tpe[a] > tpe[b]; });
+  at::Tensor tiles_h = at::empty({num_tiles * 2}, at::TensorOptions().dtype(at::kInt).pinned_memory(true));
+  int* tp = tiles_h.data_ptr<int>();
+  for (int e : order)
+    for (int t = 0; t < tiles_of[e]; ++t) {
+      *tp++ = e;
+      *tp++ = t;
+    }
+  at::Tensor desc_d = desc_h.to(A.device(), /*non_blocking=*/true);
+  at::Tensor tiles_d = tiles_h.to(A.device(), /*non_blocking=*/true);
+  const int rc = lf::grouped_gemm_launch(reinterpret_cast<const lf::GroupDesc*>(desc_d.data_ptr()), tiles_d.data_ptr(),
+                                         static_cast<int>(num_tiles), a_mn, b_mn, status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "grouped_gemm launch failed with code ", rc);
+  ++g_launches;
+}
+#endif  // LF_HAVE_GROUPED
+
+#ifdef LF_HAVE_MOE_PEER
+// ------------------------------------------------------------------ expert-parallel exchange over peer memory
+// Peer pointers are device virtual addresses from the symmetric-memory rendezvous (index = EP rank).
+static lf::MoePeerBufs moe_bufs(const std::vector<int64_t>& buf, const std::vector<int64_t>& scal,
+                                const std::vector<int64_t>& flags, int64_t rank, int64_t cap_rows) {
+  const int64_t world = static_cast<int64_t>(buf.size());
+  TORCH_CHECK(world >= 1 && world <= lf::kMoeMaxPeers && scal.size() == buf.size() && flags.size() == buf.size());
+  lf::MoePeerBufs b;
+  for (int64_t r = 0; r < world; ++r) {
+    b.buf[r] = reinterpret_cast<void*>(buf[r]);
+    b.scal[r] = reinterpret_cast<float*>(scal[r]);
+    b.flags[r] = reinterpret_cast<int*>(flags[r]);
+  }
+  b.rank = static_cast<int>(rank);
+  b.world = static_cast<int>(world);
+  b.cap_rows = static_cast<int>(cap_rows);
+  return b;
+}
+
+void moe_push(std::vector<int64_t> buf, std::vector<int64_t> scal, std::vector<int64_t> flags, int64_t rank,
+              int64_t cap_rows, const at::Tensor& x, const at::Tensor& pair_token, const at::Tensor& pair_row,
+              const at::Tensor& pair_dst, c10::optional<at::Tensor> pair_scal, const at::Tensor& done_counter,
+              int64_t kind, int64_t epoch, const at::Tensor& status) {
+  check_bf16_cuda(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1);
+  TORCH_CHECK(pair_token.scalar_type() == at::kInt && pair_row.scalar_type() == at::kInt &&
+              pair_dst.scalar_type() == at::kInt);
+  TORCH_CHECK(pair_token.is_contiguous() && pair_row.is_contiguous() && pair_dst.is_contiguous());
+  c10::cuda::CUDAGuard guard(x.device());
+  const float* ps = nullptr;
+  if (pair_scal.has_value()) {
+    TORCH_CHECK(pair_scal->scalar_type() == at::kFloat && pair_scal->is_contiguous() &&
+                pair_scal->numel() == pair_token.numel());
+    ps = pair_scal->data_ptr<float>();
+  }
+  const int rc = lf::moe_push(moe_bufs(buf, scal, flags, rank, cap_rows), x.data_ptr(), x.stride(0),
+                              static_cast<int>(x.size(1)), pair_token.data_ptr<int>(), pair_row.data_ptr<int>(),
+                              pair_dst.data_ptr<int>(), ps, static_cast<int>(pair_token.numel()),
+                              done_counter.data_ptr<int>(), static_cast<int>(kind), static_cast<int>(epoch),
+                              status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "moe_push failed with code ", rc);
+  ++g_launches;
+}
+
+// Returns (out [T, H] bf16, slot_scal [T, k] f32 or empty).
+std::vector<at::Tensor> moe_pull(std::vector<int64_t> buf, std::vector<int64_t> scal, std::vector<int64_t> flags,
+                                 int64_t rank, int64_t cap_rows, int64_t T, int64_t k, int64_t H,
+                                 const at::Tensor& slot_pair, const at::Tensor& pair_row, const at::Tensor& pair_dst,
+                                 bool with_scal, const at::Tensor& status) {
+  TORCH_CHECK(slot_pair.scalar_type() == at::kInt && slot_pair.is_contiguous() && slot_pair.numel() == T * k);
+  TORCH_CHECK(pair_row.scalar_type() == at::kInt && pair_dst.scalar_type() == at::kInt);
+  c10::cuda::CUDAGuard guard(slot_pair.device());
+  at::Tensor out = at::empty({T, H}, slot_pair.options().dtype(at::kBFloat16));
+  at::Tensor sc = with_scal ? at::empty({T, k}, slot_pair.options().dtype(at::kFloat))
+                            : at::empty({0}, slot_pair.options().dtype(at::kFloat));
+  const int rc = lf::moe_pull(moe_bufs(buf, scal, flags, rank, cap_rows), out.data_ptr(), H, static_cast<int>(H),
+                              static_cast<int>(T), static_cast<int>(k), slot_pair.data_ptr<int>(),
+                              pair_row.data_ptr<int>(), pair_dst.data_ptr<int>(),
+                              with_scal ? sc.data_ptr<float>() : nullptr, status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "moe_pull failed with code ", rc);
+  ++g_launches;
+  return {out, sc};
+}
+
+void moe_signal(std::vector<int64_t> buf, std::vector<int64_t> scal, std::vector<int64_t> flags, int64_t rank,
+                int64_t kind, int64_t epoch) {
+  TORCH_CHECK(lf::moe_signal(moe_bufs(buf, scal, flags, rank, 0), static_cast<int>(kind), static_cast<int>(epoch),
+                             cur_stream()) == 0);
+  ++g_launches;
+}
+
+void moe_wait(std::vector<int64_t> buf, std::vector<int64_t> scal, std::vector<int64_t> flags, int64_t rank,
+              int64_t kind, int64_t epoch, const at::Tensor& status) {
+  TORCH_CHECK(lf::moe_wait(moe_bufs(buf, scal, flags, rank, 0), static_cast<int>(kind), static_cast<int>(epoch),
+                           status.data_ptr<int>(), cur_stream()) == 0);
+  ++g_launches;
+}
+#endif  // LF_HAVE_MOE_PEER
+
 int64_t launch_count() { return g_launches; }
 void reset_launch_count() { g_launches = 0; }
 
@@ -492,6 +722,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ag_gemm", &ag_gemm);
   m.def("gemm_rs", &gemm_rs);
 #endif
+#ifdef LF_HAVE_GROUPED
+  m.def("grouped_gemm", &grouped_gemm);
+#endif
+#ifdef LF_HAVE_MOE_PEER
+  m.def("moe_push", &moe_push);
+  m.def("moe_pull", &moe_pull);
+  m.def("moe_signal", &moe_signal);
+  m.def("moe_wait", &moe_wait);
+#endif
+  m.def("router_fwd", &router_fwd);
+  m.def("router_bwd", &router_bwd);
   m.def("launch_count", &launch_count);
   m.def("reset_launch_count", &reset_launch_count);
 }

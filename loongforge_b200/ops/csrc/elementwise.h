@@ -30,4 +30,24 @@ void master_split(const float* master, void* w, void* lo, long long n, int write
 void master_join(const void* w, const void* lo, float* master, long long n, cudaStream_t s);
 void sumsq(const void* x, int is_bf16, long long n, float* out, cudaStream_t s);
 
+// MoE router (router.cu). score: 0 softmax over the selected k, 1 softmax over all experts then top-k, 2 sigmoid.
+struct RouterArgs {
+  const void* logits = nullptr;  // [T, E] fp32 or bf16
+  int logits_bf16 = 0;
+  const float* bias = nullptr;   // [E], selection only
+  float* probs = nullptr;        // [T, E], zero off the top-k
+  unsigned char* map = nullptr;  // [T, E] 0/1
+  float* aux = nullptr;          // [T, E] scores for the load-balancing loss
+  int* topk_idx = nullptr;       // [T, k]
+  int* counts = nullptr;         // [E] += tokens routed to each expert (optional)
+  const float* dprobs = nullptr; // backward inputs / output
+  const float* daux = nullptr;
+  float* dlogits = nullptr;
+  int T = 0, E = 0, k = 0, score = 0, num_groups = 0, group_topk = 0;
+  float scale = 1.f;
+};
+// 0 on success; negative when E > 512, k > 32, or the group shape is unsupported (callers fall back).
+int router_fwd(const RouterArgs& a, cudaStream_t s);
+int router_bwd(const RouterArgs& a, cudaStream_t s);
+
 }  // namespace lf

@@ -23,6 +23,7 @@ enum : int {
   LF_ERR_WAIT_TMEM_EMPTY = 4, // MMA warp gave up waiting for a drained accumulator
   LF_ERR_WAIT_PEER = 5,       // gave up waiting for a flag written by another GPU
   LF_ERR_BAD_ARG = 6,
+  LF_ERR_BAD_INDEX = 7,       // an index read from device memory was out of range; the access was skipped
 };
 
 // About one second at ~2 GHz. A healthy pipeline stage completes in microseconds.
@@ -134,6 +135,12 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
           smem_u32(smem_dst)),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
+}
+// Makes a tensor map that lives in global memory (and may have been rewritten since this SM last used
+// that address) visible to the TMA unit before the first copy through it.
+__device__ __forceinline__ void tmap_acquire(const CUtensorMap* map) {
+  asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(map))
+               : "memory");
 }
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int32_t x,
                                             int32_t y, int32_t z) {

@@ -81,6 +81,14 @@ def gemm(
     return d
 
 
+def grouped_gemm(a: torch.Tensor, x: Optional[torch.Tensor], weights, outs, tokens_per_expert, *, mode: int,
+                 out_mode: int = 0) -> None:
+    """One grouped tcgen05 launch over all experts (csrc/grouped_gemm_sm100.h): mode 0 forward,
+    1 dgrad, 2 wgrad (``outs`` = one [N, K] tensor per expert; ``out_mode`` 2 accumulates in fp32)."""
+    _C().grouped_gemm(a, x, list(weights), list(outs), [int(n) for n in tokens_per_expert], mode, out_mode,
+                      _ext.status_tensor(a.device))
+
+
 def _ld_ok(*ts: torch.Tensor) -> bool:
     for t in ts:
         if t.stride(-1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:

@@ -27,10 +27,51 @@ def group_limited_topk(scores: torch.Tensor, topk: int, num_groups: int, group_t
     return masked.topk(topk, dim=-1)
 
 
+_SCORE_CODE = {("softmax", False): 0, ("softmax", True): 1, ("sigmoid", False): 2, ("sigmoid", True): 2}
+
+
+class _RouterFn(torch.autograd.Function):
+    """Score + (group-limited) top-k + dense outputs in one launch (csrc/router.cu)."""
+
+    @staticmethod
+    def forward(ctx, logits, bias, topk, code, num_groups, group_topk, scale):
+        from . import _ext
+
+        logits = logits.contiguous()
+        probs, rmap, aux, idx, counts = _ext.require().router_fwd(logits, bias, topk, code, num_groups, group_topk, scale)
+        ctx.save_for_backward(logits, rmap)
+        ctx.cfg = (topk, code, scale)
+        ctx.mark_non_differentiable(rmap, idx, counts)
+        return probs, rmap, aux, idx, counts
+
+    @staticmethod
+    def backward(ctx, dprobs, _dmap, daux, _didx, _dcounts):
+        from . import _ext
+
+        logits, rmap = ctx.saved_tensors
+        topk, code, scale = ctx.cfg
+        dl = _ext.require().router_bwd(logits, rmap, dprobs.float().contiguous(),
+                                       None if daux is None else daux.float().contiguous(), topk, code, scale)
+        return dl.to(logits.dtype), None, None, None, None, None, None
+
+
+def _router_native_ok(logits, topk, num_groups) -> bool:
+    return (logits.is_cuda and logits.dtype in (torch.float32, torch.bfloat16) and logits.shape[1] <= 512
+            and topk <= 32 and (not num_groups or (num_groups <= 32 and logits.shape[1] % num_groups == 0)))
+
+
 def topk_routing(logits: torch.Tensor, topk: int, *, score_function: str = "softmax", pre_softmax: bool = False,
                  expert_bias: Optional[torch.Tensor] = None, num_groups: Optional[int] = None,
                  group_topk: Optional[int] = None, scaling_factor: Optional[float] = None):
     """Returns (probs [T, E], routing_map [T, E] bool, scores used by the aux loss [T, E])."""
+    if score_function not in ("softmax", "sigmoid"):
+        raise ValueError(f"unknown router score function {score_function}")
+    if _router_native_ok(logits, topk, num_groups):
+        bias = None if expert_bias is None else expert_bias.detach().float().contiguous()
+        probs, rmap, aux, _, _ = _RouterFn.apply(logits, bias, topk, _SCORE_CODE[(score_function, bool(pre_softmax))],
+                                                 int(num_groups or 0), int(group_topk or 0),
+                                                 float(scaling_factor) if scaling_factor else 1.0)
+        return probs, rmap, aux
     T, E = logits.shape
 
     def select(s):
@@ -83,22 +124,34 @@ def seq_aux_loss(scores, routing_map, topk: int, seq_lens: Sequence[int], coeff:
     return total / max(len(seq_lens), 1)
 
 
+def _native_grouped(x: torch.Tensor, weights) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and weights[0].shape[0] % 8 == 0
+            and weights[0].shape[1] % 8 == 0)
+
+
 class _GroupedLinearFn(torch.autograd.Function):
     """y[rows of expert e] = x[rows of e] @ W_e^T for tokens sorted by expert (variable rows per
-    expert). Forward, dgrad and wgrad each run one tcgen05 GEMM per non-empty expert on views of the
-    sorted buffers; wgrad accumulates into ``main_grad`` when present."""
+    expert). On the GPU forward, dgrad and wgrad are ONE grouped tcgen05 launch each (per-expert TMA
+    descriptors, ragged rows exact); wgrad accumulates into ``main_grad`` when present. Elsewhere the
+    same math runs as one GEMM per non-empty expert."""
 
     @staticmethod
     def forward(ctx, x, tokens_per_expert, *weights):
         N = weights[0].shape[0]
         y = torch.empty(x.shape[0], N, dtype=x.dtype, device=x.device)
-        s = 0
-        for w, n in zip(weights, tokens_per_expert):
-            if n > 0:
-                OF.gemm(x[s:s + n], w, out=y[s:s + n])
-            s += n
+        tpe = [int(n) for n in tokens_per_expert]
+        ctx.native = _native_grouped(x, weights)
+        if ctx.native:
+            x = x.contiguous()
+            OF.grouped_gemm(x, None, list(weights), [y], tpe, mode=0)
+        else:
+            s = 0
+            for w, n in zip(weights, tpe):
+                if n > 0:
+                    OF.gemm(x[s:s + n], w, out=y[s:s + n])
+                s += n
         ctx.save_for_backward(x, *weights)
-        ctx.tpe = list(tokens_per_expert)
+        ctx.tpe = tpe
         return y
 
     @staticmethod
@@ -107,6 +160,20 @@ class _GroupedLinearFn(torch.autograd.Function):
         dy = dy.contiguous()
         dx = torch.empty_like(x)
         grads = []
+        if ctx.native:
+            OF.grouped_gemm(dy, None, weights, [dx], ctx.tpe, mode=1)
+            fused = all(getattr(w, "main_grad", None) is not None for w in weights)
+            if fused:
+                OF.grouped_gemm(dy, x, [], [w.main_grad for w in weights], ctx.tpe, mode=2, out_mode=2)
+                for w in weights:
+                    hook = getattr(w, "grad_ready", None)
+                    if hook is not None:
+                        hook()
+                grads = [None] * len(weights)
+            else:
+                grads = [torch.zeros_like(w) if n == 0 else torch.empty_like(w) for w, n in zip(weights, ctx.tpe)]
+                OF.grouped_gemm(dy, x, [], grads, ctx.tpe, mode=2, out_mode=0)
+            return (dx, None, *grads)
         s = 0
         for w, n in zip(weights, ctx.tpe):
             if n > 0:
