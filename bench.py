@@ -46,6 +46,10 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=8192)
     ap.add_argument("--seqs-per-gpu", type=int, default=16)
     ap.add_argument("--layers", type=int, default=32, help="debug only; anything but 32 is not the named config")
+    ap.add_argument("--model", default="llama3-8b", help="registry preset; anything but llama3-8b is a side benchmark")
+    ap.add_argument("--tp", type=int, default=None)
+    ap.add_argument("--ep", type=int, default=1)
+    ap.add_argument("--moe-dispatcher", default="peer", choices=["peer", "alltoall"])
     ap.add_argument("--attention", default="auto", choices=["auto", "native", "sdpa"])
     ap.add_argument("--recompute", default="auto", choices=["auto", "none", "full"])
     ap.add_argument("--no-tp-overlap", action="store_true")
@@ -148,10 +152,14 @@ def main():
     _ext.require()
     OF.set_attention_impl(args.attention)
 
-    tp = 2 if world >= 2 else 1
+    flagship = args.model == "llama3-8b"
+    tp = args.tp if args.tp is not None else (2 if world >= 2 and flagship else 1)
     dp = world // tp
-    cfg = get_model_config("llama3-8b")
-    cfg.num_layers = args.layers
+    cfg = get_model_config(args.model)
+    if flagship or args.layers != 32:
+        cfg.num_layers = args.layers
+    if cfg.num_moe_experts:
+        cfg.moe_token_dispatcher_type = args.moe_dispatcher
     cfg.sequence_parallel = tp > 1
     cfg.tp_comm_overlap = tp > 1 and not args.no_tp_overlap
     # One GPU holds all 8 B parameters with exact fp32 master weights (bf16 + int16 remainder), fp32
@@ -170,7 +178,7 @@ def main():
                      train_iters=10 ** 9, lr=3e-4, weight_decay=0.1, adam_beta2=0.95, clip_grad=1.0, bf16=True,
                      use_distributed_optimizer=True, overlap_grad_reduce=True,
                      master_as_remainder=not args.fp32_master_copy)
-    trainer = Trainer(cfg, tc, ParallelDims(tp=tp), device=dev)
+    trainer = Trainer(cfg, tc, ParallelDims(tp=tp, ep=args.ep), device=dev)
     st = trainer.st
     host_iter = synthetic_batch_iterator(cfg.vocab_size, tc.seq_length, 1, dp_rank=st.dp_rank, dp_size=st.dp_size,
                                          pin_memory=True)
@@ -244,13 +252,15 @@ def main():
     tflops_gpu = flops / (ms_per_step / 1e3) / 1e12 / world
     if rank == 0:
         out = {
-            "metric": "tokens/sec (whole job) on Llama-3-8B pretrain; per-GPU and MFU in config",
+            "metric": ("tokens/sec (whole job) on Llama-3-8B pretrain; per-GPU and MFU in config" if flagship else
+                       f"tokens/sec (whole job) on {args.model} pretrain (side benchmark)"),
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": (value / world) / REF_PUBLISHED_TOK_S_GPU,
+            "vs_baseline": (value / world) / REF_PUBLISHED_TOK_S_GPU if flagship else None,
             "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights", "impl": "ours",
             "config": {
-                "model": f"llama3-8b ({cfg.num_layers} layers, h4096, 32q/8kv, ffn14336, vocab128256)",
+                "model": (f"llama3-8b ({cfg.num_layers} layers, h4096, 32q/8kv, ffn14336, vocab128256)" if flagship else
+                          f"{args.model} ({cfg.num_layers} layers, ep{args.ep}, dispatcher {args.moe_dispatcher})"),
                 "global_batch": gbs, "seq_len": tc.seq_length, "micro_batch": 1,
                 "parallelism": (f"tp{tp}+sp" if tp > 1 else "tp1") + f" dp{dp} distributed-optimizer",
                 "recompute": recompute, "attention_impl": args.attention,

@@ -437,6 +437,99 @@ __global__ void master_join_kernel(const bf16* __restrict__ w, const short* __re
 }
 
 // sum of squares of a flat buffer into a single fp32 (atomic add of block partials)
+// ---- small rows (H = 64 / 128 / 256, e.g. per-head QK norm): one WARP per row, VPL elements per lane.
+template <int VPL>
+struct alignas(2 * VPL) BfVec {
+  bf16 v[VPL];
+};
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
+                        float* __restrict__ rstd, long long T, long long x_stride, long long y_stride, float eps,
+                        float w_offset) {
+  using V = BfVec<VPL>;
+  const int lane = threadIdx.x & 31;
+  const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const V wv = reinterpret_cast<const V*>(w)[lane];
+  for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < T;
+       row += warps) {
+    const V xv = reinterpret_cast<const V*>(x + row * x_stride)[lane];
+    float f[VPL], ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      f[j] = __bfloat162float(xv.v[j]);
+      ss += f[j] * f[j];
+    }
+    ss = warp_sum_f(ss);
+    const float r = rsqrtf(ss / static_cast<float>(32 * VPL) + eps);
+    if (lane == 0 && rstd != nullptr) rstd[row] = r;
+    V o;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) o.v[j] = __float2bfloat16_rn(f[j] * r * (__bfloat162float(wv.v[j]) + w_offset));
+    reinterpret_cast<V*>(y + row * y_stride)[lane] = o;
+  }
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_warp_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                        const float* __restrict__ rstd, const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                        float* __restrict__ dw_partial, long long T, float w_offset) {
+  using V = BfVec<VPL>;
+  constexpr int H = 32 * VPL;
+  __shared__ float sh[8][H];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const long long warps = static_cast<long long>(gridDim.x) * 8;
+  const V wv = reinterpret_cast<const V*>(w)[lane];
+  float fw[VPL], dwacc[VPL];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    fw[j] = __bfloat162float(wv.v[j]) + w_offset;
+    dwacc[j] = 0.f;
+  }
+  for (long long row = static_cast<long long>(blockIdx.x) * 8 + wid; row < T; row += warps) {
+    const V xv = reinterpret_cast<const V*>(x + row * H)[lane];
+    const V gv = reinterpret_cast<const V*>(dy + row * H)[lane];
+    const float r = rstd[row];
+    float fx[VPL], fg[VPL], dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      fx[j] = __bfloat162float(xv.v[j]);
+      fg[j] = __bfloat162float(gv.v[j]);
+      dot += fg[j] * fw[j] * fx[j];
+      dwacc[j] += fg[j] * fx[j] * r;
+    }
+    dot = warp_sum_f(dot);
+    const float c = dot * r * r * r / static_cast<float>(H);
+    V o;
+    if (dres != nullptr) {
+      const V rv = reinterpret_cast<const V*>(dres + row * H)[lane];
+#pragma unroll
+      for (int j = 0; j < VPL; ++j)
+        o.v[j] = __float2bfloat16_rn(r * fg[j] * fw[j] - c * fx[j] + __bfloat162float(rv.v[j]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) o.v[j] = __float2bfloat16_rn(r * fg[j] * fw[j] - c * fx[j]);
+    }
+    reinterpret_cast<V*>(dx + row * H)[lane] = o;
+  }
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) sh[wid][lane * VPL + j] = dwacc[j];
+  __syncthreads();
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) s += sh[q][h];
+    dw_partial[static_cast<long long>(blockIdx.x) * H + h] = s;
+  }
+}
+
 template <typename T>
 __global__ void sumsq_kernel(const T* __restrict__ x, long long n, float* __restrict__ out) {
   __shared__ float sh[32];
@@ -461,6 +554,19 @@ static inline int grid_for(long long work, int threads, int cap = 148 * 8) {
 void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long T, int H, long long x_stride,
                  long long y_stride, float eps, float w_offset, cudaStream_t s) {
   if (T == 0) return;
+  if ((H == 64 || H == 128 || H == 256) && x_stride % 8 == 0 && y_stride % 8 == 0) {
+    const bf16* xp = static_cast<const bf16*>(x);
+    const bf16* wp = static_cast<const bf16*>(w);
+    bf16* yp = static_cast<bf16*>(y);
+    const int grid = grid_for(T, 8, 148 * 8);
+    if (H == 64)
+      rmsnorm_fwd_warp_kernel<2><<<grid, 256, 0, s>>>(xp, wp, yp, rstd, T, x_stride, y_stride, eps, w_offset);
+    else if (H == 128)
+      rmsnorm_fwd_warp_kernel<4><<<grid, 256, 0, s>>>(xp, wp, yp, rstd, T, x_stride, y_stride, eps, w_offset);
+    else
+      rmsnorm_fwd_warp_kernel<8><<<grid, 256, 0, s>>>(xp, wp, yp, rstd, T, x_stride, y_stride, eps, w_offset);
+    return;
+  }
   rmsnorm_fwd_kernel<<<static_cast<unsigned>(T), NORM_THREADS, 0, s>>>(
       static_cast<const bf16*>(x), static_cast<const bf16*>(w), static_cast<bf16*>(y), rstd, H, x_stride, y_stride,
       eps, w_offset);
@@ -473,6 +579,20 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
                  cudaStream_t s) {
   if (T == 0) return;
   const int grid = rmsnorm_bwd_grid(T);
+  if (H == 64 || H == 128 || H == 256) {
+    const bf16 *gp = static_cast<const bf16*>(dy), *xp = static_cast<const bf16*>(x), *wp = static_cast<const bf16*>(w);
+    const bf16* rp = static_cast<const bf16*>(dres);
+    bf16* op = static_cast<bf16*>(dx);
+    if (H == 64)
+      rmsnorm_bwd_warp_kernel<2><<<grid, 256, 0, s>>>(gp, xp, wp, rstd, rp, op, dw_partial, T, w_offset);
+    else if (H == 128)
+      rmsnorm_bwd_warp_kernel<4><<<grid, 256, 0, s>>>(gp, xp, wp, rstd, rp, op, dw_partial, T, w_offset);
+    else
+      rmsnorm_bwd_warp_kernel<8><<<grid, 256, 0, s>>>(gp, xp, wp, rstd, rp, op, dw_partial, T, w_offset);
+    colsum_partials_kernel<<<(H + 255) / 256, 256, 0, s>>>(dw_partial, grid, H, dw_f32, static_cast<bf16*>(dw_bf16),
+                                                           accumulate);
+    return;
+  }
   rmsnorm_bwd_kernel<<<grid, NORM_THREADS, 0, s>>>(static_cast<const bf16*>(dy), static_cast<const bf16*>(x),
                                                    static_cast<const bf16*>(w), rstd, static_cast<const bf16*>(dres),
                                                    static_cast<bf16*>(dx), dw_partial, static_cast<int>(T), H,

@@ -76,7 +76,7 @@ def test_linear_autograd_matches_torch():
     assert _rel_err(w.grad, wr.grad) < 1e-2
 
 
-@pytest.mark.parametrize("T,H", [(64, 4096), (300, 1280), (17, 8192), (128, 128)])
+@pytest.mark.parametrize("T,H", [(64, 4096), (300, 1280), (17, 8192), (128, 128), (5000, 64), (9001, 128), (777, 256)])
 def test_rmsnorm(T, H):
     from loongforge_b200.ops import functional as OF
 
