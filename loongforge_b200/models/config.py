@@ -89,6 +89,15 @@ class TransformerConfig:
     dsa_indexer_head_dim: int = 128
     dsa_indexer_topk: int = 2048
     dsa_indexer_loss_coeff: float = 0.0
+    # ---- hybrid attention (Qwen3-Next / Qwen3.5): per-layer "full_attention" | "linear_attention"
+    layer_types: Optional[List[str]] = None
+    full_attention_interval: Optional[int] = None  # every n-th layer is full attention when layer_types is unset
+    attention_output_gate: bool = False
+    linear_conv_kernel_dim: int = 4
+    linear_key_head_dim: int = 128
+    linear_value_head_dim: int = 128
+    linear_num_key_heads: int = 16
+    linear_num_value_heads: int = 32
     # ---- MTP
     mtp_num_layers: int = 0
     mtp_loss_scaling_factor: float = 0.1
@@ -131,6 +140,13 @@ class TransformerConfig:
             self.moe_ffn_hidden_size = self.ffn_hidden_size
 
     # helpers ---------------------------------------------------------------------
+    def layer_type(self, layer_idx: int) -> str:
+        if self.layer_types is not None:
+            return self.layer_types[layer_idx]
+        if self.full_attention_interval:
+            return "full_attention" if (layer_idx + 1) % self.full_attention_interval == 0 else "linear_attention"
+        return "full_attention"
+
     def pad_vocab(self, tp: int) -> int:
         mult = self.make_vocab_size_divisible_by * tp
         self.padded_vocab_size = ((self.vocab_size + mult - 1) // mult) * mult

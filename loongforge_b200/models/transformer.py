@@ -243,6 +243,16 @@ class TransformerLayer(nn.Module):
             self.input_layernorm = Norm(cfg.hidden_size, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
             self.self_attention = MLASelfAttention(cfg, key + ".self_attention", layer_number, device=device,
                                                    parallel_state=parallel_state)
+        elif cfg.layer_type(layer_number) == "linear_attention":
+            from .hybrid import GatedDeltaNet
+            self.input_layernorm = Norm(cfg.hidden_size, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
+            self.self_attention = GatedDeltaNet(cfg, key + ".self_attention", device=device,
+                                                parallel_state=parallel_state)
+        elif cfg.attention_output_gate:
+            from .hybrid import GatedAttention
+            self.input_layernorm = Norm(cfg.hidden_size, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
+            self.self_attention = GatedAttention(cfg, key + ".self_attention", device=device,
+                                                 parallel_state=parallel_state)
         else:
             self.input_layernorm = None
             self.self_attention = SelfAttention(cfg, key + ".self_attention", device=device,
