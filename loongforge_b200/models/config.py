@@ -98,6 +98,17 @@ class TransformerConfig:
     linear_value_head_dim: int = 128
     linear_num_key_heads: int = 16
     linear_num_value_heads: int = 32
+    # ---- DeepSeek-V4: compressed sparse attention, hyper-connections, hash-routed first MoE layers
+    csa_compress_ratios: Optional[List[int]] = None  # per layer: 0 (window only) or the tokens folded per entry
+    csa_window_size: int = 128
+    enable_hyper_connections: bool = False
+    num_residual_streams: int = 4
+    mhc_sinkhorn_iterations: int = 20
+    mhc_init_gating_factor: float = 1e-2
+    moe_n_hash_layers: int = 0  # the first n MoE layers pick experts by a hash of the token id
+    swiglu_limit: Optional[float] = None
+    # ---- MiniMax: QK RMSNorm over the whole projection (all heads) instead of per head
+    qk_layernorm_full: bool = False
     # ---- MTP
     mtp_num_layers: int = 0
     mtp_loss_scaling_factor: float = 0.1

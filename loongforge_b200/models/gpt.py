@@ -141,7 +141,7 @@ class GPTModel(nn.Module):
                 self.mtp = MultiTokenPredictionBlock(cfg, device=device, parallel_state=parallel_state)
             else:
                 self.mtp = None
-        rot_dim = cfg.qk_pos_emb_head_dim if cfg.multi_latent_attention else int(cfg.kv_channels * cfg.rotary_percent)
+        rot_dim = cfg.qk_pos_emb_head_dim if (cfg.multi_latent_attention or cfg.csa_compress_ratios is not None) else int(cfg.kv_channels * cfg.rotary_percent)
         self.rotary = RotaryEmbedding(cfg, rot_dim) if cfg.position_embedding_type in ("rope", "yarn", "mrope") else None
         self.input_tensor = None  # set by the pipeline schedule on non-first stages
 
@@ -187,6 +187,9 @@ class GPTModel(nn.Module):
             x = self.input_tensor
         n_tok = position_ids.shape[-1]
         rotary = self.build_rotary(position_ids, n_tok, x.device)
+        if cfg.moe_n_hash_layers:
+            from .moe import set_current_token_ids
+            set_current_token_ids(tokens)
         x = self.decoder(x, rotary, packed)
         if not self.post_process:
             return x

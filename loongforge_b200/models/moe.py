@@ -56,10 +56,19 @@ class AuxLossScaler(torch.autograd.Function):
         return g, torch.full_like(aux, AuxLossScaler.scale)
 
 
+_CURRENT_TOKEN_IDS = {"ids": None}
+
+
+def set_current_token_ids(ids: Optional[torch.Tensor]) -> None:
+    """Token ids of the micro-batch in flight, for hash-routed MoE layers (set by the language model)."""
+    _CURRENT_TOKEN_IDS["ids"] = ids
+
+
 class TopKRouter(nn.Module):
     def __init__(self, cfg: TransformerConfig, key: str, layer_number: int, device=None):
         super().__init__()
         self.cfg, self.layer_number = cfg, layer_number
+        self.moe_index = sum(1 for i in range(layer_number) if cfg.is_moe_layer(i))  # 0-based among MoE layers
         E = cfg.num_moe_experts
         w = PL.init_full_then_slice(key + ".weight", (E, cfg.hidden_size), cfg.init_method_std, partition_dim=None,
                                     rank=0, world=1, device=device or "cpu", dtype=torch.float32)
@@ -80,6 +89,17 @@ class TopKRouter(nn.Module):
             z = torch.logsumexp(logits, dim=-1).square().mean() * cfg.moe_z_loss_coeff
             track_aux_loss("z_loss", z / cfg.moe_z_loss_coeff, self.layer_number, cfg.num_layers)
             logits = AuxLossScaler.apply(logits, z)
+        ids = _CURRENT_TOKEN_IDS["ids"]
+        if self.moe_index < cfg.moe_n_hash_layers and ids is not None and ids.numel() == logits.shape[0]:
+            # experts are fixed by the token id; the gate only weights them (scores normalised over the k picks)
+            idx = moe_ops.hash_routing(ids, cfg.num_moe_experts, cfg.moe_router_topk)
+            s = torch.sqrt(torch.nn.functional.softplus(logits)) if cfg.moe_router_score_function == "sqrtsoftplus" \
+                else (torch.sigmoid(logits) if cfg.moe_router_score_function == "sigmoid" else logits.softmax(-1))
+            vals = s.gather(1, idx)
+            vals = vals / (vals.sum(-1, keepdim=True) + 1e-20) * (cfg.moe_router_topk_scaling_factor or 1.0)
+            probs = torch.zeros_like(s).scatter(1, idx, vals)
+            routing_map = torch.zeros_like(s, dtype=torch.bool).scatter(1, idx, True)
+            return probs, routing_map
         probs, routing_map, scores_for_aux = moe_ops.topk_routing(
             logits, cfg.moe_router_topk, score_function=cfg.moe_router_score_function,
             pre_softmax=cfg.moe_router_pre_softmax, expert_bias=self.expert_bias,

@@ -238,7 +238,12 @@ class TransformerLayer(nn.Module):
         self.layer_number = layer_number  # 0-based global index
         key = f"decoder.layers.{layer_number}"
         self.is_moe = cfg.is_moe_layer(layer_number)
-        if cfg.multi_latent_attention:
+        if cfg.csa_compress_ratios is not None:
+            from .csa import CompressedSparseAttention
+            self.input_layernorm = Norm(cfg.hidden_size, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
+            self.self_attention = CompressedSparseAttention(cfg, key + ".self_attention", layer_number, device=device,
+                                                            parallel_state=parallel_state)
+        elif cfg.multi_latent_attention:
             from .mla import MLASelfAttention
             self.input_layernorm = Norm(cfg.hidden_size, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
             self.self_attention = MLASelfAttention(cfg, key + ".self_attention", layer_number, device=device,
@@ -261,14 +266,32 @@ class TransformerLayer(nn.Module):
             from .moe import MoELayer
             self.pre_mlp_layernorm = Norm(cfg.hidden_size, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
             self.mlp = MoELayer(cfg, key + ".mlp", layer_number, device=device, parallel_state=parallel_state)
-        elif cfg.multi_latent_attention:
+        elif cfg.multi_latent_attention or cfg.csa_compress_ratios is not None:
             self.pre_mlp_layernorm = Norm(cfg.hidden_size, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
             self.mlp = MLP(cfg, key + ".mlp", fused_norm=False, device=device, parallel_state=parallel_state)
         else:
             self.pre_mlp_layernorm = None
             self.mlp = MLP(cfg, key + ".mlp", device=device, parallel_state=parallel_state)
+        if cfg.enable_hyper_connections:
+            from .hyper_connections import HyperConnection
+            assert self.input_layernorm is not None and self.pre_mlp_layernorm is not None, \
+                "hyper-connections need the un-fused norm layout"
+            hc = dict(n=cfg.num_residual_streams, sinkhorn_iters=cfg.mhc_sinkhorn_iterations,
+                      gate_init=cfg.mhc_init_gating_factor, eps=cfg.layernorm_epsilon, device=device,
+                      sequence_parallel=cfg.sequence_parallel)
+            self.hc_attention = HyperConnection(cfg.hidden_size, key=key + ".hc_attention", **hc)
+            self.hc_mlp = HyperConnection(cfg.hidden_size, key=key + ".hc_mlp", **hc)
+
+    def _forward_hyper(self, xs, rotary, packed):
+        """xs [T, n, C]: both sub-layers read one mixed vector and write back into all streams."""
+        h, maps = self.hc_attention.read(xs)
+        xs = self.hc_attention.write(xs, self.self_attention(self.input_layernorm(h), rotary, packed), maps)
+        h, maps = self.hc_mlp.read(xs)
+        return self.hc_mlp.write(xs, self.mlp(self.pre_mlp_layernorm(h)), maps)
 
     def forward(self, x, rotary=None, packed=None):
+        if self.cfg.enable_hyper_connections:
+            return self._forward_hyper(x, rotary, packed)
         h = self.input_layernorm(x) if self.input_layernorm is not None else x
         x = self.self_attention(h, rotary, packed, residual=x)
         h = self.pre_mlp_layernorm(x) if self.pre_mlp_layernorm is not None else x
@@ -292,6 +315,13 @@ class TransformerBlock(nn.Module):
         self.final_layernorm = Norm(cfg.hidden_size, cfg, device=device,
                                     sequence_parallel=cfg.sequence_parallel) if post_process else None
         self.deepstack_hook = None  # callable(layer_idx, hidden) -> hidden, used by Qwen3-VL
+        self.pre_process = True  # set False by pipeline stages that receive hidden states
+        if cfg.enable_hyper_connections and post_process:
+            from .hyper_connections import HyperHead
+            self.head_hyper_connection = HyperHead(cfg.hidden_size, cfg.num_residual_streams,
+                                                   cfg.mhc_init_gating_factor, cfg.layernorm_epsilon,
+                                                   "decoder.head_hyper_connection", device=device,
+                                                   sequence_parallel=cfg.sequence_parallel)
 
     def _run(self, layer, x, rotary, packed):
         return layer(x, rotary, packed)
@@ -302,6 +332,12 @@ class TransformerBlock(nn.Module):
         rec = cfg.recompute_granularity == "full" and torch.is_grad_enabled()
         rec_n = cfg.recompute_num_layers if cfg.recompute_num_layers is not None else n
         method = cfg.recompute_method or "block"
+        hyper = cfg.enable_hyper_connections
+        if hyper:
+            # streams travel between pipeline stages flattened as [T, n * C]; the first stage replicates the embedding
+            ns = cfg.num_residual_streams
+            x = x.unsqueeze(1).expand(-1, ns, -1).contiguous() if x.shape[-1] == cfg.hidden_size else \
+                x.view(x.shape[0], ns, cfg.hidden_size)
         for i, layer in enumerate(self.layers):
             do_rec = rec and ((method == "block" and i < rec_n) or method == "uniform")
             if do_rec:
@@ -310,6 +346,8 @@ class TransformerBlock(nn.Module):
                 x = layer(x, rotary, packed)
             if self.deepstack_hook is not None:
                 x = self.deepstack_hook(self.layer_numbers[i], x)
+        if hyper:
+            x = self.head_hyper_connection(x) if self.final_layernorm is not None else x.reshape(x.shape[0], -1)
         if self.final_layernorm is not None:
             x = self.final_layernorm(x)
         return x

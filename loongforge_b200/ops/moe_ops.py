@@ -64,9 +64,9 @@ def topk_routing(logits: torch.Tensor, topk: int, *, score_function: str = "soft
                  expert_bias: Optional[torch.Tensor] = None, num_groups: Optional[int] = None,
                  group_topk: Optional[int] = None, scaling_factor: Optional[float] = None):
     """Returns (probs [T, E], routing_map [T, E] bool, scores used by the aux loss [T, E])."""
-    if score_function not in ("softmax", "sigmoid"):
+    if score_function not in ("softmax", "sigmoid", "sqrtsoftplus"):
         raise ValueError(f"unknown router score function {score_function}")
-    if _router_native_ok(logits, topk, num_groups):
+    if score_function != "sqrtsoftplus" and _router_native_ok(logits, topk, num_groups):
         bias = None if expert_bias is None else expert_bias.detach().float().contiguous()
         probs, rmap, aux, _, _ = _RouterFn.apply(logits, bias, topk, _SCORE_CODE[(score_function, bool(pre_softmax))],
                                                  int(num_groups or 0), int(group_topk or 0),
@@ -90,8 +90,10 @@ def topk_routing(logits: torch.Tensor, topk: int, *, score_function: str = "soft
             v, idx = select(sel)
             vals = torch.softmax(logits.gather(1, idx), dim=-1, dtype=torch.float32)
         aux_scores = full
-    elif score_function == "sigmoid":
-        s = torch.sigmoid(logits.float())
+    elif score_function in ("sigmoid", "sqrtsoftplus"):
+        # sqrtsoftplus (DeepSeek-V4): s = sqrt(softplus(logit)); selection, normalisation and aux scores as for sigmoid
+        s = torch.sigmoid(logits.float()) if score_function == "sigmoid" else \
+            torch.sqrt(torch.nn.functional.softplus(logits.float()))
         sel = s + expert_bias if expert_bias is not None else s
         _, idx = select(sel)
         vals = s.gather(1, idx)
@@ -105,6 +107,18 @@ def topk_routing(logits: torch.Tensor, topk: int, *, score_function: str = "soft
     probs = torch.zeros(T, E, dtype=torch.float32, device=logits.device).scatter(1, idx, vals)
     routing_map = torch.zeros(T, E, dtype=torch.bool, device=logits.device).scatter(1, idx, True)
     return probs, routing_map, aux_scores
+
+
+def hash_routing(token_ids: torch.Tensor, num_experts: int, topk: int) -> torch.Tensor:
+    """Static routing of DeepSeek-V4's first MoE layers: expert j of token t is a fixed hash of its id.
+    Returns [T, topk] distinct expert indices (Knuth multiplicative hash for the first, odd stride after)."""
+    t = token_ids.long()
+    first = (t * 2654435761 % 4294967296) % num_experts
+    stride = 2 * ((t * 40503 % 65536) % max(num_experts // 2, 1)) + 1  # odd
+    if num_experts & (num_experts - 1):  # not a power of two: fall back to consecutive experts (always distinct)
+        stride = torch.ones_like(stride)
+    j = torch.arange(topk, device=t.device)
+    return (first.unsqueeze(1) + stride.unsqueeze(1) * j) % num_experts
 
 
 def switch_aux_loss(scores: torch.Tensor, tokens_per_expert: torch.Tensor, topk: int, coeff: float) -> torch.Tensor:

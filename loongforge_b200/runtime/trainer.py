@@ -219,7 +219,8 @@ class Trainer:
         reports = fb(forward_step_func=self.forward_step, data_iterator=data_iterator,
                      model=self.models if len(self.models) > 1 else self.models[0],
                      num_microbatches=self.mb_calc.num_microbatches,
-                     tensor_shape=(T // sp_div // self.st.dims.cp, self.mcfg.hidden_size),
+                     tensor_shape=(T // sp_div // self.st.dims.cp, self.mcfg.hidden_size *
+                                   (self.mcfg.num_residual_streams if self.mcfg.enable_hyper_connections else 1)),
                      dtype=self.mcfg.params_dtype)
         self._allreduce_sequence_parallel_grads()
         ok, grad_norm, _ = self.optimizer.step()
