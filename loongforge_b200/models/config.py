@@ -112,6 +112,7 @@ class TransformerConfig:
     # ---- MTP
     mtp_num_layers: int = 0
     mtp_loss_scaling_factor: float = 0.1
+    mtp_hidden_first: bool = False  # MiMo: eh_proj input is [hidden, embedding] instead of [embedding, hidden]
     # ---- precision
     params_dtype: torch.dtype = torch.float32
     fp8: Optional[str] = None  # None | "blockwise"

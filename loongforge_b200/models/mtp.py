@@ -26,6 +26,7 @@ from .transformer import Norm, TransformerLayer
 class MTPLayer(nn.Module):
     def __init__(self, cfg: TransformerConfig, k: int, device=None, parallel_state=None):
         super().__init__()
+        self.cfg = cfg
         self.enorm = Norm(cfg.hidden_size, cfg, device=device)
         self.hnorm = Norm(cfg.hidden_size, cfg, device=device)
         self.eh_proj = PL.ColumnParallelLinear(2 * cfg.hidden_size, cfg.hidden_size, gather_output=True,
@@ -36,7 +37,10 @@ class MTPLayer(nn.Module):
         self.final_layernorm = Norm(cfg.hidden_size, cfg, device=device)
 
     def forward(self, hidden, emb_next, rotary, packed):
-        x = self.eh_proj(torch.cat([self.enorm(emb_next), self.hnorm(hidden)], dim=-1))
+        parts = [self.enorm(emb_next), self.hnorm(hidden)]
+        if self.cfg.mtp_hidden_first:  # MiMo concatenates [hidden, embedding]
+            parts.reverse()
+        x = self.eh_proj(torch.cat(parts, dim=-1))
         x = self.transformer_layer(x, rotary, packed)
         return self.final_layernorm(x)
 

@@ -61,6 +61,28 @@ class Norm(nn.Module):
         return apply_norm(x, self.weight, self.bias, self.kind, self.eps, self.offset)
 
 
+class TPRMSNorm(nn.Module):
+    """RMSNorm over a feature dimension that is SHARDED across tensor-parallel ranks: each rank holds its
+    slice of the features and of the weight; the sum of squares is all-reduced over the TP group
+    (MiniMax full-width QK norm, loongforge/models/foundation/minimax/attention.py:143,170,230-239;
+    InternViT's TP-aware norm, loongforge/models/encoder/internvl_vision_models/intern_vision_attention.py:116)."""
+
+    def __init__(self, full_dim: int, cfg: TransformerConfig, key: str, device=None, parallel_state=None):
+        super().__init__()
+        st = ps.get_state(parallel_state)
+        self.state_name, self.full_dim, self.eps = parallel_state, full_dim, cfg.layernorm_epsilon
+        self.weight = nn.Parameter(torch.ones(full_dim // st.dims.tp, device=device, dtype=cfg.params_dtype))
+        PL.mark_tp(self.weight, 0 if st.dims.tp > 1 else None)
+
+    def forward(self, x):
+        st = ps.get_state(self.state_name)
+        ss = x.float().pow(2).sum(-1, keepdim=True)
+        if st.dims.tp > 1:
+            from ..parallel import mappings as M
+            ss = M.reduce_from_tensor_model_parallel_region(ss, st.group("tp"))
+        return (x.float() * torch.rsqrt(ss / self.full_dim + self.eps) * self.weight.float()).to(x.dtype)
+
+
 def apply_norm(x, weight, bias, kind, eps, offset=0.0):
     if kind == "RMSNorm":
         return OF.rmsnorm(x, weight, eps, offset)
@@ -162,7 +184,13 @@ class SelfAttention(nn.Module):
             self.linear_qkv = LayerNormColumnParallelLinear(cfg.hidden_size, qkv_out, cfg, **kw)
         else:
             self.linear_qkv = PL.ColumnParallelLinear(cfg.hidden_size, qkv_out, **kw)
-        if cfg.qk_layernorm:
+        if cfg.qk_layernorm_full:
+            # MiniMax: one RMSNorm over ALL heads of q (and of k); under TP the statistic is all-reduced
+            self.q_layernorm = TPRMSNorm(self.nq * self.d, cfg, key + ".q_layernorm", device=device,
+                                         parallel_state=parallel_state)
+            self.k_layernorm = TPRMSNorm(self.ng * self.d, cfg, key + ".k_layernorm", device=device,
+                                         parallel_state=parallel_state)
+        elif cfg.qk_layernorm:
             self.q_layernorm = Norm(self.d, cfg, device=device)
             self.k_layernorm = Norm(self.d, cfg, device=device)
         else:
@@ -192,8 +220,12 @@ class SelfAttention(nn.Module):
             v = pk4[:, :, r + 1]
         else:
             pk4 = qkv.view(T, g, r + 2, d)
-            q = self.q_layernorm(pk4[:, :, :r].reshape(T, g * r, d))
-            k = self.k_layernorm(pk4[:, :, r].contiguous())
+            if cfg.qk_layernorm_full:
+                q = self.q_layernorm(pk4[:, :, :r].reshape(T, g * r * d)).view(T, g * r, d)
+                k = self.k_layernorm(pk4[:, :, r].reshape(T, g * d)).view(T, g, d)
+            else:
+                q = self.q_layernorm(pk4[:, :, :r].reshape(T, g * r, d))
+                k = self.k_layernorm(pk4[:, :, r].contiguous())
             v = pk4[:, :, r + 1]
             if rotary is not None:
                 q = self._rope(q, rotary)

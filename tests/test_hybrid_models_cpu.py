@@ -85,3 +85,40 @@ def test_tiny_qwen3_next_trains():
         losses.append(loss.item())
     assert all(p.grad is not None for p in model.parameters())
     assert losses[-1] < losses[0] - 0.3, losses
+
+
+def _train_tiny(name, steps=6):
+    from loongforge_b200.models.registry import build_model, get_model_config
+    from loongforge_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(ps.ParallelDims())
+    cfg = get_model_config(name)
+    torch.manual_seed(0)
+    model = build_model(cfg)
+    model.train()
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3)
+    T = 48
+    tokens = torch.randint(0, cfg.vocab_size, (T,))
+    labels, pos = torch.roll(tokens, -1), torch.arange(T)
+    losses = []
+    for _ in range(steps):
+        loss = model(tokens, pos, labels=labels, loss_mask=torch.ones(T)).mean()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    return model, losses
+
+
+def test_tiny_minimax_full_width_qk_norm_trains():
+    model, losses = _train_tiny("tiny-minimax")
+    att = model.decoder.layers[0].self_attention
+    assert att.q_layernorm.weight.numel() == 4 * 16 and att.k_layernorm.weight.numel() == 2 * 16
+    assert losses[-1] < losses[0]
+
+
+def test_tiny_mimo_mtp_hidden_first_trains():
+    model, losses = _train_tiny("tiny-mimo")
+    assert model.mtp is not None and model.cfg.mtp_hidden_first
+    assert losses[-1] < losses[0]
