@@ -107,6 +107,11 @@ class TransformerConfig:
     mhc_init_gating_factor: float = 1e-2
     moe_n_hash_layers: int = 0  # the first n MoE layers pick experts by a hash of the token id
     swiglu_limit: Optional[float] = None
+    # ---- ERNIE-4.5-VL: modality-routed expert sets and 3-D rotary layout
+    moe_multi_type: bool = False
+    moe_vision_num_experts: Optional[int] = None
+    moe_vision_ffn_hidden_size: Optional[int] = None
+    rope_3d_freq_allocation: int = 0  # > 0: the last n rotary frequencies follow the temporal position
     # ---- MiniMax: QK RMSNorm over the whole projection (all heads) instead of per head
     qk_layernorm_full: bool = False
     # ---- MTP

@@ -158,6 +158,10 @@ class GPTModel(nn.Module):
     def build_rotary(self, position_ids: torch.Tensor, n_tokens: int, device) -> Optional[RotaryInputs]:
         if self.rotary is None:
             return None
+        if self.cfg.rope_3d_freq_allocation and position_ids.dim() == 2:
+            from .ernie import ernie_3d_angles
+            return ernie_3d_angles(position_ids, self.rotary.rot_dim, self.cfg.rotary_base,
+                                   self.cfg.rope_3d_freq_allocation)
         if self.cfg.position_embedding_type == "mrope" or position_ids.dim() == 2 and position_ids.shape[0] == 3:
             return self.rotary.mrope(position_ids)
         n_pos = max(self.cfg.max_position_embeddings, n_tokens)
@@ -173,7 +177,7 @@ class GPTModel(nn.Module):
     def forward(self, tokens: Optional[torch.Tensor], position_ids: torch.Tensor, *,
                 labels: Optional[torch.Tensor] = None, loss_mask: Optional[torch.Tensor] = None,
                 packed: Optional[PackedSeqParams] = None, decoder_input: Optional[torch.Tensor] = None,
-                loss_scale: Optional[float] = None):
+                loss_scale: Optional[float] = None, token_type: Optional[torch.Tensor] = None):
         """tokens / labels / loss_mask are flat ``[T]``; position_ids ``[T]`` or ``[3, T]`` (M-RoPE).
 
         Returns per-token losses ``[T]`` when `labels` is given on the last stage, logits
@@ -187,6 +191,10 @@ class GPTModel(nn.Module):
             x = self.input_tensor
         n_tok = position_ids.shape[-1]
         rotary = self.build_rotary(position_ids, n_tok, x.device)
+        if cfg.moe_multi_type:
+            for layer in self.decoder.layers:
+                if hasattr(layer.mlp, "set_token_type"):
+                    layer.mlp.set_token_type(token_type)
         if cfg.moe_n_hash_layers:
             from .moe import set_current_token_ids
             set_current_token_ids(tokens)

@@ -296,6 +296,8 @@ class TransformerLayer(nn.Module):
                                                 parallel_state=parallel_state)
         if self.is_moe:
             from .moe import MoELayer
+            if cfg.moe_multi_type:
+                from .ernie import MultiTypeMoELayer as MoELayer  # noqa: N811
             self.pre_mlp_layernorm = Norm(cfg.hidden_size, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
             self.mlp = MoELayer(cfg, key + ".mlp", layer_number, device=device, parallel_state=parallel_state)
         elif cfg.multi_latent_attention or cfg.csa_compress_ratios is not None:

@@ -126,9 +126,8 @@ class RoutePlan:
         host = torch.cat([blocks[ep_rank].sum(-1), flat_blocks.sum(1).max().view(1)]).tolist()  # one D2H
         self.tokens_per_expert: List[int] = [int(v) for v in host[:El]]
         self.rows = sum(self.tokens_per_expert)
-        if int(host[-1]) > cap_rows:
-            raise RuntimeError(f"expert-parallel receive buffer holds {cap_rows} rows but a rank receives "
-                               f"{int(host[-1])}; raise moe_peer_capacity_factor")
+        # most rows any rank of the group receives; identical on every rank, so all ranks grow their buffers together
+        self.max_rows = int(host[-1])
         j = torch.arange(T * k, device=dev)
         self.pair_token = (perm // k).int()
         self.pair_row = (base[sorted_e] + (j - start[sorted_e])).int()
@@ -221,6 +220,10 @@ class PeerDispatcher:
         cap = max(int(T * k * self.capacity_factor), 128)
         self.ex = PeerExchange.get(self.group, x.device, self.H, cap)
         self.plan = RoutePlan(topk_idx, self.E, self.ep, self.ep_rank, self.group, self.ex.cap)
+        if self.plan.max_rows > self.ex.cap:
+            # routing is more skewed than the capacity factor assumed: every rank sees the same maximum (it comes from
+            # the all-gathered counts), so all of them re-allocate the symmetric buffers at this same call
+            self.ex = PeerExchange.get(self.group, x.device, self.H, int(self.plan.max_rows * 1.25) + 128)
         pair_probs = probs[self.plan.pair_token.long(), self.plan.pair_expert]
         tokens, row_probs = _Dispatch.apply(x, pair_probs, self.ex, self.plan)
         return tokens, self.plan.tokens_per_expert, row_probs

@@ -122,3 +122,41 @@ def test_tiny_mimo_mtp_hidden_first_trains():
     model, losses = _train_tiny("tiny-mimo")
     assert model.mtp is not None and model.cfg.mtp_hidden_first
     assert losses[-1] < losses[0]
+
+
+def test_ernie_3d_rotary_layout():
+    from loongforge_b200.models.ernie import ernie_3d_angles
+
+    pos = torch.tensor([[5, 5], [1, 2], [3, 4]])  # t, h, w for two tokens
+    r = ernie_3d_angles(pos, 16, 10000.0, 2)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, 16, 2).float() / 16))
+    expect0 = torch.tensor([1, 3, 1, 3, 1, 3, 5, 5]).float() * inv  # h, w alternate; last two follow t
+    assert torch.allclose(r.freqs[0], expect0)
+    assert torch.allclose(r.freqs[1], torch.tensor([2, 4, 2, 4, 2, 4, 5, 5]).float() * inv)
+
+
+def test_tiny_ernie_vl_routes_by_modality():
+    from loongforge_b200.models.registry import build_model, get_model_config
+    from loongforge_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(ps.ParallelDims())
+    cfg = get_model_config("tiny-ernie-vl")
+    torch.manual_seed(0)
+    model = build_model(cfg)
+    T = 24
+    tokens = torch.randint(0, cfg.vocab_size, (T,))
+    pos3 = torch.stack([torch.arange(T)] * 3)
+    tt = torch.zeros(T, dtype=torch.long)
+    tt[8:16] = 1
+    loss = model(tokens, pos3, labels=torch.roll(tokens, -1), loss_mask=torch.ones(T), token_type=tt).mean()
+    loss.backward()
+    moe = model.decoder.layers[1].mlp
+    assert moe.text.experts.linear_fc1.weights()[0].shape[0] == 2 * 32
+    assert moe.vision.experts.linear_fc1.weights()[0].shape[0] == 2 * 16
+    assert all(p.grad is not None for p in model.parameters())
+    # text-only batch: vision experts receive no tokens but the step still runs
+    model.zero_grad()
+    model(tokens, pos3, labels=torch.roll(tokens, -1), loss_mask=torch.ones(T), token_type=torch.zeros(T, dtype=torch.long)).mean().backward()
+    g = moe.vision.experts.linear_fc1.weights()[0].grad
+    assert g is None or float(g.abs().sum()) == 0.0

@@ -31,7 +31,9 @@ def _compare_layers(dev, ep, seed_shift=0, steps=3):
               ffn_hidden_size=512, vocab_size=1024, num_moe_experts=8, moe_router_topk=2, moe_ffn_hidden_size=256,
               moe_aux_loss_coeff=0.0, params_dtype=torch.bfloat16)
     ref = MoELayer(TransformerConfig(**kw), "decoder.layers.0.mlp", 0, device=dev)
-    peer = MoELayer(TransformerConfig(moe_token_dispatcher_type="peer", **kw), "decoder.layers.0.mlp", 0, device=dev)
+    # a capacity factor this small forces the receive buffers to be re-allocated when routing is skewed
+    peer = MoELayer(TransformerConfig(moe_token_dispatcher_type="peer", moe_peer_capacity_factor=0.55, **kw),
+                    "decoder.layers.0.mlp", 0, device=dev)
     peer.load_state_dict(ref.state_dict())
     errs = {}
     for step in range(steps):

@@ -1,0 +1,81 @@
+"""Vision encoder families and projectors: shapes, gradient flow, and the distinctive option of each."""
+import pytest
+import torch
+
+from loongforge_b200.models.config import TransformerConfig
+from loongforge_b200.models import vision_zoo as VZ
+from loongforge_b200.parallel import state as ps
+
+
+def _cfg(**kw):
+    base = dict(num_layers=2, hidden_size=64, num_attention_heads=4, kv_channels=16, ffn_hidden_size=128, vocab_size=0,
+                normalization="LayerNorm", activation="gelu", gated_linear_unit=False, add_bias_linear=True,
+                add_qkv_bias=True, layernorm_epsilon=1e-6, causal=False, patch_size=14, temporal_patch_size=1,
+                spatial_merge_size=2, position_embedding_type="rope")
+    base.update(kw)
+    return TransformerConfig(**base)
+
+
+@pytest.fixture(autouse=True)
+def _state():
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(ps.ParallelDims())
+    yield
+
+
+GRID = torch.tensor([[1, 4, 6], [2, 2, 4]])
+N_PATCH = 1 * 4 * 6 + 2 * 2 * 4
+
+
+def _pixels(cfg):
+    return torch.randn(N_PATCH, cfg.in_channels * cfg.temporal_patch_size * cfg.patch_size ** 2)
+
+
+@pytest.mark.parametrize("family", sorted(VZ.VISION_FAMILIES))
+def test_family_forward_backward(family):
+    cfg = _cfg(qk_layernorm_full=(family == "intern_vit"))
+    torch.manual_seed(0)
+    opts, adapter_cls = VZ.VISION_FAMILIES[family]
+    over = {"deepstack_indexes": (0, 1)} if family == "qwen3_vl_vit" else {}
+    if opts.get("pos_table_side"):
+        over["pos_table_side"] = 8
+    vit = VZ.build_vision_encoder(family, cfg, **over)
+    x, taps = vit(_pixels(cfg), GRID)
+    n_tok = N_PATCH + (3 if family == "intern_vit" else 0)  # one class token per frame
+    assert x.shape == (n_tok, 64)
+    out = x
+    if adapter_cls is not None:
+        ad = adapter_cls(cfg, 96)
+        out = ad(x, GRID)
+        units = 1 * 2 * 3 + 2 * 1 * 2
+        expect = units if family != "ernie_vit" else 1 * 2 * 3 + 1 * 1 * 2  # temporal fold of 2 (single frame repeated)
+        assert out.shape == (expect, 96), out.shape
+    if family == "qwen3_vl_vit":
+        assert len(taps) == 2
+        feats = VZ.DeepStackMergers(cfg, 96, 2)(taps, GRID)
+        assert all(f.shape == (10, 96) for f in feats)
+        out = out.sum() + sum(f.sum() for f in feats)
+    out.sum().backward()
+    assert all(p.grad is not None for p in vit.parameters())
+
+
+def test_interpolated_position_table_matches_table_at_native_size():
+    table = torch.randn(16, 8)
+    e = VZ.interpolate_pos_table(table, 4, torch.tensor([[2, 4, 4]]))
+    assert torch.allclose(e[:16], table, atol=1e-6) and torch.allclose(e[16:], table, atol=1e-6)
+
+
+def test_layer_scale_zero_is_identity():
+    cfg = _cfg()
+    layer = VZ.LayerScaleLayer(cfg, 0, init_scale=0.0)
+    x = torch.randn(10, 64)
+    packed = VZ.PackedSeqParams(torch.tensor([0, 10], dtype=torch.int32), 10)
+    assert torch.equal(layer(x, None, packed), x)
+
+
+def test_deepstack_hook_adds_only_at_image_tokens():
+    hidden = torch.zeros(6, 4)
+    mask = torch.tensor([False, True, True, False, False, True])
+    hook = VZ.make_deepstack_hook([torch.ones(3, 4), 2 * torch.ones(3, 4)], mask)
+    assert hook(0, hidden)[mask].eq(1).all() and hook(0, hidden)[~mask].eq(0).all()
+    assert hook(1, hidden)[mask].eq(2).all() and torch.equal(hook(2, hidden), hidden)
