@@ -1,0 +1,131 @@
+"""Three-layer configuration of the embodied stack: CLI overrides > YAML file > dataclass defaults, with a
+model-name -> YAML map and validators (reference: loongforge/embodied/train/parser.py, training_args.py,
+config_map.py, validators.py)."""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import os
+from typing import Any, Dict, List, Optional
+
+import yaml
+
+
+@dataclasses.dataclass
+class EmbodiedArgs:
+    # ---- model / data
+    model_name: str = "pi05"
+    model_overrides: Dict[str, Any] = dataclasses.field(default_factory=dict)
+    dataset_type: str = "synthetic"  # synthetic | npz_episodes | lerobot | hdf5
+    dataset_path: Optional[str] = None
+    action_horizon: int = 16
+    action_dim: int = 7
+    state_dim: int = 8
+    image_size: int = 56
+    num_cameras: int = 1
+    max_text_len: int = 16
+    # ---- optimisation
+    train_steps: int = 100
+    per_device_batch_size: int = 4
+    gradient_accumulation_steps: int = 1
+    lr: float = 1e-4
+    min_lr: float = 0.0
+    weight_decay: float = 0.01
+    warmup_steps: int = 0
+    lr_scheduler: str = "cosine"  # constant | linear | cosine | wsd
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.95
+    max_grad_norm: float = 1.0
+    nan_clean: bool = True
+    bf16: bool = False
+    seed: int = 1234
+    # ---- distribution
+    strategy: str = "ddp"  # ddp | zero1 | fsdp | hsdp
+    fsdp_wrap_patterns: List[str] = dataclasses.field(default_factory=lambda: ["blocks.*", "layers.*"])
+    fsdp_prefetch: int = 1
+    hsdp_shard_size: Optional[int] = None
+    ddp_bucket_mb: int = 25
+    ddp_comm_hook: Optional[str] = None  # None | bf16_compress
+    ddp_static_graph: bool = True
+    activation_checkpoint_patterns: List[str] = dataclasses.field(default_factory=list)
+    fp32_master_weights: bool = False
+    # ---- LoRA
+    lora_rank: int = 0
+    lora_alpha: float = 16.0
+    lora_targets: List[str] = dataclasses.field(default_factory=lambda: ["q", "k", "v", "o"])
+    # ---- CUDA graphs
+    per_microbatch_cuda_graph: bool = False
+    # ---- checkpoint / logging
+    output_dir: str = "./outputs"
+    save_interval: int = 0
+    checkpoint_format: str = "pt"  # pt | dcp
+    resume: bool = False
+    log_interval: int = 1
+    manual_gc_interval: int = 0
+
+
+MODEL_CONFIG_MAP = {name: f"configs/embodied/{name}.yaml" for name in
+                    ("pi05", "groot_n1_6", "groot_n1_7", "xvla", "lingbot_va", "fastwam", "dreamzero", "cosmos3")}
+
+
+def validate(a: EmbodiedArgs) -> EmbodiedArgs:
+    if a.strategy not in ("ddp", "zero1", "fsdp", "hsdp"):
+        raise ValueError(f"unknown strategy {a.strategy}")
+    if a.strategy == "hsdp" and not a.hsdp_shard_size:
+        raise ValueError("hsdp needs hsdp_shard_size")
+    if a.gradient_accumulation_steps < 1 or a.per_device_batch_size < 1:
+        raise ValueError("batch sizes must be positive")
+    if a.checkpoint_format not in ("pt", "dcp"):
+        raise ValueError(f"unknown checkpoint format {a.checkpoint_format}")
+    if a.per_microbatch_cuda_graph and a.strategy in ("fsdp", "hsdp"):
+        raise ValueError("per-microbatch CUDA graphs need parameters resident on the device (ddp / zero1)")
+    if a.lora_rank < 0:
+        raise ValueError("lora_rank must be >= 0")
+    return a
+
+
+def _coerce(value: str, current: Any) -> Any:
+    if isinstance(current, bool):
+        return value.lower() in ("1", "true", "yes")
+    if isinstance(current, (list, dict)) or current is None:
+        return yaml.safe_load(value)
+    return type(current)(value)
+
+
+def parse_args(argv: Optional[List[str]] = None, repo_root: Optional[str] = None) -> EmbodiedArgs:
+    """``--config file.yaml`` or ``--model-name NAME`` (looked up in MODEL_CONFIG_MAP) plus ``key=value`` overrides."""
+    ap = argparse.ArgumentParser("loongforge_b200.embodied.train")
+    ap.add_argument("--config", default=None)
+    ap.add_argument("--model-name", default=None)
+    ap.add_argument("overrides", nargs="*")
+    ns = ap.parse_args(argv)
+    args = EmbodiedArgs()
+    path = ns.config
+    if path is None and ns.model_name:
+        cand = os.path.join(repo_root or os.getcwd(), MODEL_CONFIG_MAP.get(ns.model_name, ""))
+        path = cand if os.path.isfile(cand) else None
+        args.model_name = ns.model_name
+    if path:
+        with open(path) as f:
+            for k, v in (yaml.safe_load(f) or {}).items():
+                if not hasattr(args, k):
+                    raise KeyError(f"unknown config key {k!r} in {path}")
+                setattr(args, k, v)
+    for ov in ns.overrides:
+        k, _, v = ov.partition("=")
+        k = k.lstrip("-").replace("-", "_")
+        if not hasattr(args, k):
+            raise KeyError(f"unknown override {k!r}")
+        setattr(args, k, _coerce(v, getattr(args, k)))
+    return validate(args)
+
+
+_GLOBAL: Dict[str, Any] = {}
+
+
+def set_global_args(a: EmbodiedArgs) -> None:
+    _GLOBAL["args"] = a
+
+
+def get_global_args() -> EmbodiedArgs:
+    return _GLOBAL["args"]

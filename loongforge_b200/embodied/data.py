@@ -1,0 +1,167 @@
+"""Datasets and collators of the embodied stack.
+
+Every sample is one time step of an episode: camera images, a proprioceptive state, a language instruction and the
+chunk of the next ``action_horizon`` actions (padded at episode end, with a mask). Sources:
+
+* ``SyntheticEpisodes``  — deterministic random episodes (benchmarks, tests);
+* ``NpzEpisodes``        — a directory of ``episode_*.npz`` files (arrays ``images [T, cams, C, H, W]``, ``state``,
+  ``actions``, optional ``task``), the layout HDF5 exports convert to (reference: hdf5_dataset.py);
+* ``LeRobotParquet``     — LeRobot-style ``data/chunk-*/episode_*.parquet`` tables with ``observation.state``,
+  ``action``, ``episode_index``, ``task_index`` columns plus ``meta/tasks.jsonl`` (reference: lerobot_dataset.py).
+
+(reference: loongforge/embodied/data/dataloader.py, data/datasets/lerobot_dataset.py, hdf5_dataset.py)
+"""
+from __future__ import annotations
+
+import glob
+import json
+import os
+import zlib
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+from torch.utils.data import DataLoader, Dataset, DistributedSampler
+
+
+def _chunk(actions: np.ndarray, t: int, horizon: int):
+    seg = actions[t:t + horizon]
+    n = seg.shape[0]
+    mask = np.zeros(horizon, dtype=np.float32)
+    mask[:n] = 1.0
+    if n < horizon:
+        seg = np.concatenate([seg, np.repeat(seg[-1:], horizon - n, 0)], 0)
+    return seg.astype(np.float32), mask
+
+
+def hash_tokenize(text: str, max_len: int, vocab: int = 32000) -> np.ndarray:
+    """Whitespace tokens hashed into a fixed vocabulary (stand-in for the model tokenizer in tests / synthetic runs)."""
+    ids = [(zlib.crc32(w.encode()) % (vocab - 2)) + 2 for w in text.lower().split()][:max_len]
+    return np.array(ids + [0] * (max_len - len(ids)), dtype=np.int64)
+
+
+class SyntheticEpisodes(Dataset):
+    def __init__(self, args, num_episodes: int = 8, episode_len: int = 32, seed: int = 0):
+        self.a, self.n, self.L, self.seed = args, num_episodes, episode_len, seed
+
+    def __len__(self):
+        return self.n * self.L
+
+    def __getitem__(self, i):
+        a = self.a
+        ep, t = divmod(i, self.L)
+        rng = np.random.default_rng(self.seed * 100003 + ep)
+        actions = rng.standard_normal((self.L, a.action_dim)).astype(np.float32).cumsum(0) * 0.1
+        state = rng.standard_normal((self.L, a.state_dim)).astype(np.float32)
+        img = np.random.default_rng(i).random((a.num_cameras, 3, a.image_size, a.image_size), dtype=np.float32)
+        chunk, mask = _chunk(actions, t, a.action_horizon)
+        return {"images": img, "state": state[t], "actions": chunk, "action_mask": mask,
+                "text": hash_tokenize(f"task {ep % 3} move the object", a.max_text_len)}
+
+
+class NpzEpisodes(Dataset):
+    def __init__(self, args, path: str):
+        self.a = args
+        self.files = sorted(glob.glob(os.path.join(path, "episode_*.npz")))
+        if not self.files:
+            raise FileNotFoundError(f"no episode_*.npz under {path}")
+        self.index = []
+        for fi, f in enumerate(self.files):
+            with np.load(f, allow_pickle=False) as z:
+                self.index += [(fi, t) for t in range(z["actions"].shape[0])]
+        self._cache = (None, None)
+
+    def __len__(self):
+        return len(self.index)
+
+    def _episode(self, fi):
+        if self._cache[0] != fi:
+            with np.load(self.files[fi], allow_pickle=False) as z:
+                self._cache = (fi, {k: z[k] for k in z.files})
+        return self._cache[1]
+
+    def __getitem__(self, i):
+        fi, t = self.index[i]
+        ep = self._episode(fi)
+        chunk, mask = _chunk(ep["actions"], t, self.a.action_horizon)
+        task = str(ep["task"]) if "task" in ep else "do the task"
+        return {"images": ep["images"][t].astype(np.float32), "state": ep["state"][t].astype(np.float32),
+                "actions": chunk, "action_mask": mask, "text": hash_tokenize(task, self.a.max_text_len)}
+
+
+class LeRobotParquet(Dataset):
+    def __init__(self, args, path: str):
+        import pyarrow.parquet as pq
+
+        self.a = args
+        files = sorted(glob.glob(os.path.join(path, "data", "chunk-*", "episode_*.parquet")))
+        if not files:
+            raise FileNotFoundError(f"no LeRobot parquet episodes under {path}")
+        self.tasks: Dict[int, str] = {}
+        tp = os.path.join(path, "meta", "tasks.jsonl")
+        if os.path.isfile(tp):
+            with open(tp) as f:
+                for line in f:
+                    r = json.loads(line)
+                    self.tasks[int(r["task_index"])] = r["task"]
+        self.episodes = []
+        self.index = []
+        for f in files:
+            t = pq.read_table(f).to_pydict()
+            ep = {"state": np.asarray(t["observation.state"], dtype=np.float32),
+                  "actions": np.asarray(t["action"], dtype=np.float32),
+                  "task": self.tasks.get(int(t["task_index"][0]), "") if "task_index" in t else ""}
+            self.index += [(len(self.episodes), i) for i in range(ep["actions"].shape[0])]
+            self.episodes.append(ep)
+
+    def __len__(self):
+        return len(self.index)
+
+    def __getitem__(self, i):
+        e, t = self.index[i]
+        ep, a = self.episodes[e], self.a
+        chunk, mask = _chunk(ep["actions"], t, a.action_horizon)
+        img = np.zeros((a.num_cameras, 3, a.image_size, a.image_size), dtype=np.float32)  # videos are decoded offline
+        return {"images": img, "state": ep["state"][t], "actions": chunk, "action_mask": mask,
+                "text": hash_tokenize(ep["task"], a.max_text_len)}
+
+
+def collate(samples: List[dict]) -> Dict[str, torch.Tensor]:
+    return {k: torch.from_numpy(np.stack([s[k] for s in samples])) for k in samples[0]}
+
+
+def build_dataset(args) -> Dataset:
+    if args.dataset_type == "synthetic":
+        return SyntheticEpisodes(args)
+    if args.dataset_type in ("npz_episodes", "hdf5"):
+        return NpzEpisodes(args, args.dataset_path)
+    if args.dataset_type == "lerobot":
+        return LeRobotParquet(args, args.dataset_path)
+    raise ValueError(args.dataset_type)
+
+
+class ResumableLoader:
+    """DataLoader + DistributedSampler whose position (epoch, batches consumed) can be saved and restored."""
+
+    def __init__(self, dataset: Dataset, batch_size: int, rank: int, world: int, seed: int, num_workers: int = 0):
+        self.sampler = DistributedSampler(dataset, num_replicas=world, rank=rank, shuffle=True, seed=seed, drop_last=True)
+        self.loader = DataLoader(dataset, batch_size=batch_size, sampler=self.sampler, collate_fn=collate,
+                                 num_workers=num_workers, drop_last=True, pin_memory=torch.cuda.is_available())
+        self.epoch, self.consumed = 0, 0
+
+    def state_dict(self):
+        return {"epoch": self.epoch, "consumed": self.consumed}
+
+    def load_state_dict(self, sd):
+        self.epoch, self.consumed = sd["epoch"], sd["consumed"]
+
+    def __iter__(self):
+        while True:
+            self.sampler.set_epoch(self.epoch)
+            skip = self.consumed
+            for i, batch in enumerate(self.loader):
+                if i < skip:
+                    continue
+                self.consumed = i + 1
+                yield batch
+            self.epoch, self.consumed = self.epoch + 1, 0

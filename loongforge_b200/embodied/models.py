@@ -1,0 +1,220 @@
+"""Vision-language-action and world-model policies of the embodied stack.
+
+All eight reference policies share one skeleton — observation encoders -> a token backbone -> an action head trained
+with flow matching — and differ in which parts they use; ``POLICY_PRESETS`` records the differences:
+
+=============  =======================================================================================
+pi05           VLM prefix (SigLIP-style ViT + Gemma-style LM) with a separate, narrower action-expert
+               transformer attending to the prefix (reference model/pi05/modeling_pi05.py)
+groot_n1_6     Eagle VL backbone features -> DiT action head with AdaLN timestep conditioning
+groot_n1_7     Qwen3 backbone + DiT action head
+xvla           Florence-2 style encoder-decoder features + soft-prompted action transformer
+lingbot_va     WAN video-DiT backbone streaming latents, action tokens decoded jointly
+fastwam        WAN DiT + VAE latents, mixture-of-transformers action branch
+dreamzero      causal WAN world model with an action head on the denoised latents
+cosmos3        video foundation network over packed sequences with a Qwen3-VL conditioner
+=============  =======================================================================================
+
+The world-model policies (last four) use ``models/diffusion.py::WanModel`` as backbone; the VLA policies use the
+transformer blocks below. Sizes here are the configurable skeleton; published sizes are set through ``model_overrides``.
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+from typing import Dict, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..models.diffusion import DiTConfig, WanModel, timestep_embedding
+
+
+@dataclasses.dataclass
+class PolicyConfig:
+    name: str = "pi05"
+    backbone: str = "vlm"  # vlm | wan
+    hidden: int = 256
+    layers: int = 4
+    heads: int = 4
+    expert_hidden: int = 128  # action expert width (pi05) / DiT width
+    expert_layers: int = 4
+    patch: int = 14
+    vocab: int = 32000
+    adaln: bool = True  # DiT-style timestep modulation in the action head (False: time token, pi0 style)
+    action_dim: int = 7
+    state_dim: int = 8
+    action_horizon: int = 16
+    image_size: int = 56
+    num_cameras: int = 1
+    wan_latent_channels: int = 4
+
+
+POLICY_PRESETS: Dict[str, dict] = {
+    "pi05": dict(backbone="vlm", adaln=True),
+    "groot_n1_6": dict(backbone="vlm", adaln=True, expert_layers=6),
+    "groot_n1_7": dict(backbone="vlm", adaln=True, expert_layers=6, layers=6),
+    "xvla": dict(backbone="vlm", adaln=False),
+    "lingbot_va": dict(backbone="wan", adaln=True),
+    "fastwam": dict(backbone="wan", adaln=True, expert_layers=2),
+    "dreamzero": dict(backbone="wan", adaln=True),
+    "cosmos3": dict(backbone="wan", adaln=True, layers=6),
+}
+
+
+class Block(nn.Module):
+    """Pre-norm transformer block with optional cross-attention to a context and optional AdaLN modulation."""
+
+    def __init__(self, dim: int, heads: int, ctx_dim: Optional[int] = None, adaln: bool = False):
+        super().__init__()
+        self.h = heads
+        self.n1, self.n2 = nn.LayerNorm(dim, elementwise_affine=not adaln), nn.LayerNorm(dim, elementwise_affine=not adaln)
+        self.qkv, self.o = nn.Linear(dim, 3 * dim), nn.Linear(dim, dim)
+        self.mlp = nn.Sequential(nn.Linear(dim, 4 * dim), nn.GELU(approximate="tanh"), nn.Linear(4 * dim, dim))
+        if ctx_dim is not None:
+            self.nc = nn.LayerNorm(dim)
+            self.cq, self.ckv, self.co = nn.Linear(dim, dim), nn.Linear(ctx_dim, 2 * dim), nn.Linear(dim, dim)
+        self.has_ctx = ctx_dim is not None
+        self.mod = nn.Sequential(nn.SiLU(), nn.Linear(dim, 6 * dim)) if adaln else None
+
+    def _attn(self, q, k, v, causal=False):
+        B, L, C = q.shape
+        sp = lambda t: t.view(B, -1, self.h, C // self.h).transpose(1, 2)  # noqa: E731
+        o = F.scaled_dot_product_attention(sp(q), sp(k), sp(v), is_causal=causal)
+        return o.transpose(1, 2).reshape(B, L, C)
+
+    def forward(self, x, ctx=None, temb=None, causal=False):
+        if self.mod is not None:
+            b1, s1, g1, b2, s2, g2 = self.mod(temb).unsqueeze(1).chunk(6, dim=-1)
+        else:
+            b1 = b2 = 0.0
+            s1 = s2 = 0.0
+            g1 = g2 = 1.0
+        h = self.n1(x) * (1 + s1) + b1
+        q, k, v = self.qkv(h).chunk(3, dim=-1)
+        x = x + g1 * self.o(self._attn(q, k, v, causal))
+        if self.has_ctx and ctx is not None:
+            k, v = self.ckv(ctx).chunk(2, dim=-1)
+            x = x + self.co(self._attn(self.cq(self.nc(x)), k, v))
+        return x + g2 * self.mlp(self.n2(x) * (1 + s2) + b2)
+
+
+class VLMBackbone(nn.Module):
+    """Patch-embedded camera images + instruction tokens + state token through a bidirectional transformer."""
+
+    def __init__(self, c: PolicyConfig):
+        super().__init__()
+        self.c = c
+        self.patch = nn.Linear(3 * c.patch * c.patch, c.hidden)
+        n_patch = (c.image_size // c.patch) ** 2 * c.num_cameras
+        self.pos = nn.Parameter(torch.zeros(1, n_patch, c.hidden))
+        self.tok = nn.Embedding(c.vocab, c.hidden)
+        self.state = nn.Linear(c.state_dim, c.hidden)
+        self.blocks = nn.ModuleList([Block(c.hidden, c.heads) for _ in range(c.layers)])
+        self.norm = nn.LayerNorm(c.hidden)
+
+    def forward(self, images, text, state):
+        B, cams, C, H, W = images.shape
+        p = self.c.patch
+        x = images.reshape(B * cams, C, H // p, p, W // p, p).permute(0, 2, 4, 1, 3, 5).reshape(B, -1, C * p * p)
+        x = self.patch(x.to(self.patch.weight.dtype)) + self.pos
+        seq = torch.cat([x, self.tok(text), self.state(state.to(x.dtype)).unsqueeze(1)], dim=1)
+        for b in self.blocks:
+            seq = b(seq)
+        return self.norm(seq)
+
+
+class WanBackbone(nn.Module):
+    """Camera frames as (tiny) video latents through the WAN DiT; its output tokens are the action head's context."""
+
+    def __init__(self, c: PolicyConfig):
+        super().__init__()
+        self.c = c
+        self.to_latent = nn.Conv2d(3, c.wan_latent_channels, kernel_size=c.patch // 2, stride=c.patch // 2)
+        self.tok = nn.Embedding(c.vocab, c.hidden)
+        self.state = nn.Linear(c.state_dim, c.hidden)
+        self.wan = WanModel(DiTConfig(hidden_size=c.hidden, num_heads=c.heads, num_layers=c.layers,
+                                      ffn_hidden_size=4 * c.hidden, in_channels=c.wan_latent_channels,
+                                      out_channels=c.hidden // 4, text_dim=c.hidden, freq_dim=64))
+
+    def forward(self, images, text, state):
+        B, cams, C, H, W = images.shape
+        lat = self.to_latent(images.reshape(B * cams, C, H, W).to(self.to_latent.weight.dtype))
+        lat = lat.view(B, cams, *lat.shape[1:]).transpose(1, 2)  # cameras act as frames: [B, C, F, h, w]
+        h, w = lat.shape[-2] // 2 * 2, lat.shape[-1] // 2 * 2
+        ctx = torch.cat([self.tok(text), self.state(state.to(lat.dtype)).unsqueeze(1)], dim=1)
+        out = self.wan(lat[..., :h, :w], torch.zeros(B, device=lat.device), ctx)  # [B, hidden/4, F, h, w]
+        tokens, _ = self.wan.patchify(out)
+        return tokens  # [B, L, hidden]
+
+
+class ActionHead(nn.Module):
+    """Flow-matching action expert: noisy action chunk tokens attend to the backbone tokens."""
+
+    def __init__(self, c: PolicyConfig):
+        super().__init__()
+        self.c, d = c, c.expert_hidden
+        self.inp = nn.Linear(c.action_dim, d)
+        self.pos = nn.Parameter(torch.zeros(1, c.action_horizon, d))
+        self.time = nn.Sequential(nn.Linear(64, d), nn.SiLU(), nn.Linear(d, d))
+        self.blocks = nn.ModuleList([Block(d, c.heads, ctx_dim=c.hidden, adaln=c.adaln) for _ in range(c.expert_layers)])
+        self.norm = nn.LayerNorm(d)
+        self.out = nn.Linear(d, c.action_dim)
+
+    def forward(self, noisy_actions, t, context):
+        temb = self.time(timestep_embedding(t * 1000.0, 64).to(noisy_actions.dtype))
+        x = self.inp(noisy_actions) + self.pos
+        if not self.c.adaln:
+            x = x + temb.unsqueeze(1)
+        for b in self.blocks:
+            x = b(x, ctx=context, temb=temb)
+        return self.out(self.norm(x))
+
+
+class FlowMatchingPolicy(nn.Module):
+    def __init__(self, c: PolicyConfig):
+        super().__init__()
+        self.c = c
+        self.backbone = VLMBackbone(c) if c.backbone == "vlm" else WanBackbone(c)
+        self.head = ActionHead(c)
+
+    def forward(self, batch: Dict[str, torch.Tensor], noise: Optional[torch.Tensor] = None,
+                t: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Flow-matching loss: x_t = t * noise + (1 - t) * actions, target velocity = noise - actions, masked MSE."""
+        actions = batch["actions"]
+        B = actions.shape[0]
+        noise = torch.randn_like(actions) if noise is None else noise
+        if t is None:  # Beta(1.5, 1) skewed towards noisy samples, as pi0 does
+            t = torch.distributions.Beta(1.5, 1.0).sample((B,)).to(actions.device) * 0.999 + 0.001
+        ctx = self.backbone(batch["images"], batch["text"], batch["state"])
+        tt = t.view(B, 1, 1).to(actions.dtype)
+        v = self.head(tt * noise + (1 - tt) * actions, t, ctx)
+        err = (v.float() - (noise - actions).float()).pow(2).mean(-1)
+        m = batch.get("action_mask")
+        return (err * m).sum() / m.sum().clamp(min=1) if m is not None else err.mean()
+
+    @torch.no_grad()
+    def predict_action(self, obs: Dict[str, torch.Tensor], steps: int = 10, generator=None) -> torch.Tensor:
+        """Euler integration of the learned velocity field from noise (t = 1) to actions (t = 0)."""
+        B = obs["state"].shape[0]
+        ctx = self.backbone(obs["images"], obs["text"], obs["state"])
+        x = torch.randn(B, self.c.action_horizon, self.c.action_dim, device=ctx.device, dtype=ctx.dtype, generator=generator)
+        dt = -1.0 / steps
+        t = torch.ones(B, device=ctx.device)
+        for _ in range(steps):
+            x = x + dt * self.head(x, t, ctx)
+            t = t + dt
+        return x
+
+
+def build_policy(name: str, args=None, **overrides) -> FlowMatchingPolicy:
+    if name not in POLICY_PRESETS:
+        raise KeyError(f"unknown policy {name!r}; known: {sorted(POLICY_PRESETS)}")
+    kw = dict(POLICY_PRESETS[name], name=name)
+    if args is not None:
+        kw.update(action_dim=args.action_dim, state_dim=args.state_dim, action_horizon=args.action_horizon,
+                  image_size=args.image_size, num_cameras=args.num_cameras)
+        kw.update(args.model_overrides or {})
+    kw.update(overrides)
+    return FlowMatchingPolicy(PolicyConfig(**kw))

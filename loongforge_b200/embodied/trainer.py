@@ -1,0 +1,154 @@
+"""Trainer template of the embodied stack: ``train -> _setup -> _training_loop -> _train_step`` with gradient
+accumulation under no-sync contexts, NaN cleaning, clipping, manual garbage collection, checkpoint / RNG / data-loader
+resume hooks, and a name -> trainer registry (reference: loongforge/embodied/train/trainers/base_trainer.py:45-808,
+supervised/finetune_trainer.py, trainer_builder.py)."""
+from __future__ import annotations
+
+import gc
+import os
+from typing import Callable, Dict, Optional
+
+import torch
+import torch.nn as nn
+
+from . import checkpoint as ckpt
+from .config import EmbodiedArgs, set_global_args
+from .cuda_graph import MicrobatchGraphRunner
+from .data import ResumableLoader, build_dataset
+from .distributed import DistContext, apply_activation_checkpointing, grad_sync_context, wrap_model
+from .logging import MetricLogger
+from .models import build_policy
+from .optimizer import LRScheduler, build_optimizer, clip_gradients
+
+
+class BaseTrainer:
+    def __init__(self, args: EmbodiedArgs, ctx: Optional[DistContext] = None):
+        self.args = args
+        self.ctx = ctx or DistContext().init()
+        set_global_args(args)
+        self.step = 0
+
+    # ---- hooks subclasses override
+    def build_model(self) -> nn.Module:
+        raise NotImplementedError
+
+    def compute_loss(self, model: nn.Module, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
+        raise NotImplementedError
+
+    # ---- template
+    def _setup(self):
+        a, ctx = self.args, self.ctx
+        torch.manual_seed(a.seed)  # identical initial weights on every rank
+        model = self.build_model()
+        if a.lora_rank > 0:
+            from .lora import inject_lora
+            self.lora_meta = inject_lora(model, a.lora_rank, a.lora_alpha, a.lora_targets)
+        else:
+            self.lora_meta = None
+        if a.bf16:
+            model = model.to(torch.bfloat16)
+        if a.activation_checkpoint_patterns:
+            apply_activation_checkpointing(model, a.activation_checkpoint_patterns)
+        self.model = wrap_model(model, a, ctx)
+        self.optimizer = build_optimizer(self.model, a, ctx.world)
+        self.scheduler = LRScheduler(self.optimizer, a.lr_scheduler, a.lr, a.min_lr, a.warmup_steps, a.train_steps)
+        self.loader = ResumableLoader(build_dataset(a), a.per_device_batch_size, ctx.rank, ctx.world, a.seed)
+        self.logger = MetricLogger(a.output_dir, ctx.is_main, a.train_steps)
+        self.graph_runner = MicrobatchGraphRunner(self.model, self.compute_loss) if a.per_microbatch_cuda_graph else None
+        if a.resume:
+            st = ckpt.load_checkpoint(a.output_dir, self.model, self.optimizer, self.scheduler, rank=ctx.rank)
+            if st is not None:
+                self.step = st["step"]
+                if st.get("dataloader"):
+                    self.loader.load_state_dict(st["dataloader"])
+        torch.manual_seed(a.seed + 1000 * ctx.rank + self.step)  # per-rank noise streams from here on
+
+    def _to_device(self, batch):
+        dev = self.ctx.device
+        out = {k: v.to(dev, non_blocking=True) for k, v in batch.items()}
+        if self.args.bf16:
+            out = {k: (v.to(torch.bfloat16) if v.is_floating_point() else v) for k, v in out.items()}
+        return out
+
+    def _train_step(self, it) -> Dict[str, float]:
+        a = self.args
+        n = a.gradient_accumulation_steps
+        total = 0.0
+        for i in range(n):
+            batch = self._to_device(next(it))
+            with grad_sync_context(self.model, sync=(i == n - 1)):
+                if self.graph_runner is not None:
+                    loss = self.graph_runner.run(batch, 1.0 / n)
+                else:
+                    loss = self.compute_loss(self.model, batch)
+                    (loss / n).backward()
+            total += float(loss.detach()) / n
+        norm = clip_gradients(self.model.parameters(), a.max_grad_norm, nan_clean=a.nan_clean,
+                              sharded=a.strategy in ("fsdp", "hsdp"))
+        self.optimizer.step()
+        if self.graph_runner is not None and self.graph_runner.graph is not None:
+            for p in self.model.parameters():  # captured graphs accumulate into fixed .grad storage
+                if p.grad is not None:
+                    p.grad.zero_()
+        else:
+            self.optimizer.zero_grad(set_to_none=True)
+        self.scheduler.step()
+        return {"loss": total, "grad_norm": norm, "lr": self.optimizer.param_groups[0]["lr"]}
+
+    def _training_loop(self):
+        a = self.args
+        it = iter(self.loader)
+        while self.step < a.train_steps:
+            metrics = self._train_step(it)
+            self.step += 1
+            if a.log_interval and self.step % a.log_interval == 0:
+                self.logger.log(self.step, metrics, a.per_device_batch_size * a.gradient_accumulation_steps * self.ctx.world)
+            if a.manual_gc_interval and self.step % a.manual_gc_interval == 0:
+                gc.collect()
+            if a.save_interval and self.step % a.save_interval == 0:
+                self.save()
+            self.last_metrics = metrics
+
+    def save(self):
+        ckpt.save_checkpoint(self.args.output_dir, self.step, self.model, self.optimizer, self.scheduler,
+                             fmt=self.args.checkpoint_format, dataloader_state=self.loader.state_dict(),
+                             lora_meta=self.lora_meta, rank=self.ctx.rank, world=self.ctx.world)
+
+    def train(self):
+        if self.args.manual_gc_interval:
+            gc.disable()
+        try:
+            self._setup()
+            self._training_loop()
+        finally:
+            if self.args.manual_gc_interval:
+                gc.enable()
+        return self.last_metrics if hasattr(self, "last_metrics") else {}
+
+
+class FinetuneTrainer(BaseTrainer):
+    """Supervised fine-tuning of a flow-matching policy on action chunks."""
+
+    def build_model(self) -> nn.Module:
+        return build_policy(self.args.model_name, self.args)
+
+    def compute_loss(self, model, batch):
+        return model(batch)
+
+
+_TRAINERS: Dict[str, Callable[..., BaseTrainer]] = {}
+
+
+def register_trainer(name: str):
+    def deco(cls):
+        _TRAINERS[name] = cls
+        return cls
+    return deco
+
+
+for _n in ("pi05", "groot_n1_6", "groot_n1_7", "xvla", "lingbot_va", "fastwam", "dreamzero", "cosmos3"):
+    _TRAINERS[_n] = FinetuneTrainer
+
+
+def build_trainer(args: EmbodiedArgs, ctx: Optional[DistContext] = None) -> BaseTrainer:
+    return _TRAINERS.get(args.model_name, FinetuneTrainer)(args, ctx)

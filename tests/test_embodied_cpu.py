@@ -1,0 +1,169 @@
+"""Embodied stack on CPU: config layers, policies, trainer (single process, DDP / ZeRO-1 / FSDP over gloo), resume,
+LoRA, optimizer pieces, eval transport + decoders + orchestrator."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from loongforge_b200.embodied import checkpoint as ckpt
+from loongforge_b200.embodied.config import EmbodiedArgs, parse_args, validate
+from loongforge_b200.embodied.models import POLICY_PRESETS, build_policy
+from tests.dist_utils import run_distributed
+
+SMALL = dict(hidden=32, layers=1, heads=2, expert_hidden=32, expert_layers=1)
+
+
+def _args(tmp, **kw):
+    base = dict(model_name="pi05", model_overrides=dict(SMALL), train_steps=4, per_device_batch_size=2, image_size=28,
+                action_horizon=4, output_dir=str(tmp), log_interval=1, lr=1e-3)
+    base.update(kw)
+    return validate(EmbodiedArgs(**base))
+
+
+def test_config_layers(tmp_path):
+    y = tmp_path / "c.yaml"
+    y.write_text("model_name: groot_n1_6\nlr: 0.5\nstrategy: zero1\n")
+    a = parse_args(["--config", str(y), "lr=0.25", "fsdp_wrap_patterns=[a.*, b]", "bf16=true"])
+    assert a.model_name == "groot_n1_6" and a.lr == 0.25 and a.strategy == "zero1"
+    assert a.fsdp_wrap_patterns == ["a.*", "b"] and a.bf16 is True
+    with pytest.raises(KeyError):
+        parse_args(["nonsense=1"])
+    with pytest.raises(ValueError):
+        validate(EmbodiedArgs(strategy="hsdp"))
+
+
+@pytest.mark.parametrize("name", sorted(POLICY_PRESETS))
+def test_policies_loss_and_sampling(name, tmp_path):
+    a = _args(tmp_path, model_name=name)
+    torch.manual_seed(0)
+    p = build_policy(name, a)
+    from loongforge_b200.embodied.data import SyntheticEpisodes, collate
+    batch = collate([SyntheticEpisodes(a)[i] for i in range(2)])
+    loss = p(batch)
+    loss.backward()
+    assert torch.isfinite(loss) and all(q.grad is not None for q in p.parameters() if q.requires_grad)
+    act = p.predict_action(batch, steps=2)
+    assert act.shape == (2, a.action_horizon, a.action_dim)
+
+
+def test_trainer_learns_and_resumes(tmp_path):
+    from loongforge_b200.embodied.trainer import build_trainer
+
+    a = _args(tmp_path, train_steps=6, save_interval=3, gradient_accumulation_steps=2, warmup_steps=2,
+              activation_checkpoint_patterns=["backbone.blocks.*"])
+    t = build_trainer(a)
+    t.train()
+    lines = [json.loads(x) for x in open(os.path.join(tmp_path, "metrics.jsonl"))]
+    assert len(lines) == 6 and lines[-1]["loss"] < lines[0]["loss"] * 1.5
+    assert ckpt.latest_step(str(tmp_path)) == 6
+    a2 = _args(tmp_path, train_steps=8, resume=True)
+    t2 = build_trainer(a2)
+    t2.train()
+    assert t2.step == 8 and t2.scheduler.step_count == 8
+
+
+def test_lora_freezes_base_and_trains_adapters(tmp_path):
+    from loongforge_b200.embodied.trainer import build_trainer
+
+    a = _args(tmp_path, lora_rank=2, lora_targets=["qkv", "o"], train_steps=2)
+    t = build_trainer(a)
+    t._setup()
+    before = {n: p.detach().clone() for n, p in t.model.named_parameters()}
+    t._training_loop()
+    changed = [n for n, p in t.model.named_parameters() if not torch.equal(p, before[n])]
+    assert changed and all("lora_" in n for n in changed)
+    assert t.lora_meta["modules"]
+
+
+def test_optimizer_pieces():
+    from loongforge_b200.embodied.optimizer import FP32MasterAdapter, LRScheduler, build_param_groups, clip_gradients
+
+    m = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.LayerNorm(4)).to(torch.bfloat16)
+    groups = build_param_groups(m, 0.1, 1e-2)
+    assert sorted(g["weight_decay"] for g in groups) == [0.0, 0.1]
+    opt = FP32MasterAdapter(groups, torch.optim.AdamW, lr=1e-4)
+    w0 = m[0].weight.detach().clone()
+    for _ in range(20):  # updates far below bf16 resolution still accumulate in the fp32 masters
+        m[0].weight.grad = torch.ones_like(m[0].weight)
+        opt.step()
+    assert not torch.equal(m[0].weight, w0)
+    s = LRScheduler(torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=1.0), "wsd", 1.0, 0.0, 2, 12)
+    lrs = [s.lr_at(i) for i in range(12)]
+    assert lrs[0] == 0.5 and lrs[5] == 1.0 and s.lr_at(12) < 1e-9 and 0.4 < s.lr_at(11.5) < 0.6
+    p = torch.nn.Parameter(torch.zeros(3))
+    p.grad = torch.tensor([3.0, float("nan"), 4.0])
+    assert abs(clip_gradients([p], 1.0) - 5.0) < 1e-5 and torch.allclose(p.grad.norm(), torch.tensor(1.0), atol=1e-4)
+
+
+def _dist_train(rank, world, strategy, out):
+    from loongforge_b200.embodied.distributed import DistContext
+    from loongforge_b200.embodied.trainer import build_trainer
+
+    ctx = DistContext()
+    ctx.rank, ctx.world, ctx.local_rank = rank, world, rank
+    a = _args(out, strategy=strategy, train_steps=3, fsdp_wrap_patterns=["backbone.blocks.*", "head.blocks.*"],
+              checkpoint_format="dcp" if strategy == "fsdp" else "pt", save_interval=3)
+    t = build_trainer(a, ctx)
+    m = t.train()
+    full = sum(float(p.full_tensor().float().sum()) if hasattr(p, "full_tensor") else float(p.float().sum())
+               for p in t.model.parameters())
+    return m["loss"], full
+
+
+@pytest.mark.parametrize("strategy", ["ddp", "zero1", "fsdp"])
+def test_distributed_strategies_agree_across_ranks(strategy, tmp_path):
+    res = run_distributed(_dist_train, 2, strategy, str(tmp_path))
+    assert abs(res[0][1] - res[1][1]) < 1e-3 * max(1.0, abs(res[0][1]))  # replicas hold identical weights
+    assert ckpt.latest_step(str(tmp_path)) == 3
+
+
+def test_msgpack_rpc_and_decoders():
+    from loongforge_b200.embodied.eval import action_decoders as AD
+    from loongforge_b200.embodied.eval import msgpack_numpy as mp
+    from loongforge_b200.embodied.eval.transport import RPCClient, RPCError, RPCServer
+
+    obj = {"a": np.arange(6, dtype=np.int16).reshape(2, 3), "b": [1.5, "x"], "c": {"d": np.float32(2.0)}}
+    back = mp.unpackb(mp.packb(obj))
+    assert back["a"].dtype == np.int16 and np.array_equal(back["a"], obj["a"]) and back["c"]["d"] == 2.0
+    srv = RPCServer().start()
+    srv.register("add", lambda x, y: x + y)
+    cli = RPCClient(srv.host, srv.port)
+    assert cli.call("ping") == "pong" and np.array_equal(cli.call("add", x=np.ones(3), y=np.ones(3)), 2 * np.ones(3))
+    with pytest.raises(RPCError):
+        cli.call("add", x=1)
+    cli.close()
+    srv.stop()
+    rng = np.random.default_rng(0)
+    R = AD.rot6d_to_matrix(rng.standard_normal((5, 6)))
+    assert np.allclose(R @ R.transpose(0, 2, 1), np.eye(3), atol=1e-6) and np.allclose(np.linalg.det(R), 1, atol=1e-6)
+    assert np.allclose(AD.rot6d_to_matrix(AD.matrix_to_rot6d(R)), R, atol=1e-6)
+    assert np.allclose(AD.quat_to_matrix(AD.matrix_to_quat(R)), R, atol=1e-5)
+    assert np.allclose(AD.euler_to_matrix(np.array([0.0, 0.0, np.pi / 2])) @ np.array([1.0, 0, 0]), [0, 1, 0], atol=1e-6)
+    acts = np.zeros((3, 10), np.float32)
+    acts[:, 0] = 0.1
+    acts[:, 3:9] = AD.matrix_to_rot6d(np.eye(3))
+    acts[:, 9] = [0.2, 0.7, 0.9]
+    pos, rot, g = AD.decode_ee_delta(acts, np.zeros(3), np.eye(3))
+    assert np.allclose(pos[:, 0], [0.1, 0.2, 0.3]) and np.allclose(rot[-1], np.eye(3)) and g.tolist() == [0, 1, 1]
+    assert np.allclose(AD.decode_joint(np.ones((2, 2)), np.zeros(2), delta=True, upper=1.5), [[1, 1], [1.5, 1.5]])
+
+
+def test_orchestrator_with_mock_and_real_policy(tmp_path):
+    from loongforge_b200.embodied.eval.orchestrator import ENV_ADAPTERS, EvalConfig, compare_reports, run_evaluation
+    from loongforge_b200.embodied.eval.policy_server import MockPolicyService, PolicyService, serve
+
+    srv = serve(MockPolicyService(horizon=4, action_dim=3))
+    goal_seeking = lambda a, obs: obs.state[3:6] + 0 * a  # noqa: E731 - adapter that jumps to the goal
+    rep = run_evaluation(EvalConfig(episodes=3, port=srv.port, output_dir=str(tmp_path)), action_adapter=goal_seeking)
+    srv.stop()
+    assert rep["success_rate"] == 1.0 and rep["mean_steps"] == 1.0 and os.path.isfile(tmp_path / "report.json")
+    a = _args(tmp_path, action_dim=3, state_dim=6)
+    srv = serve(PolicyService(build_policy("pi05", a), a, denoise_steps=2))
+    rep2 = run_evaluation(EvalConfig(episodes=1, port=srv.port, env_kwargs={"max_steps": 4}))
+    srv.stop()
+    assert rep2["policy"]["model"] == "pi05" and rep2["episodes"][0]["steps"] == 4
+    assert "success_rate" in compare_reports(rep, rep2)
+    with pytest.raises(RuntimeError, match="unavailable on this box"):
+        ENV_ADAPTERS["libero"]()
