@@ -49,7 +49,7 @@ def parse():
     ap.add_argument("--model", default="llama3-8b", help="registry preset; anything but llama3-8b is a side benchmark")
     ap.add_argument("--tp", type=int, default=None)
     ap.add_argument("--ep", type=int, default=1)
-    ap.add_argument("--moe-dispatcher", default="peer", choices=["peer", "alltoall"])
+    ap.add_argument("--moe-dispatcher", default="alltoall", choices=["peer", "alltoall"])
     ap.add_argument("--attention", default="auto", choices=["auto", "native", "sdpa"])
     ap.add_argument("--recompute", default="auto", choices=["auto", "none", "full"])
     ap.add_argument("--no-tp-overlap", action="store_true")

@@ -1,0 +1,173 @@
+"""Multimodal sample encoding, online packing and sequence padding for VLM training.
+
+A raw sample is ``{"images": [uint8 HWC arrays], "conversation": [{"role", "content"}]}`` where the user content
+carries ``<image>`` markers. Task encoders turn it into model inputs: pixel patches (flattened
+``C x t x p x p``), ``grid_thw``, token ids with every marker expanded to ``n_patches / merge^2`` image tokens,
+labels masked outside assistant turns. The online packer fills fixed-length buffers greedily (first-fit-decreasing)
+and emits ``cu_seqlens``; sequences are padded to the multiple that TP / CP / FP8 need (reference:
+loongforge/data/multimodal/** task encoders, online packer, dataloader_provider.py:36-185)."""
+from __future__ import annotations
+
+import dataclasses
+import math
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+IGNORE = -100
+
+
+@dataclasses.dataclass
+class VisionPreprocess:
+    patch_size: int = 14
+    temporal_patch_size: int = 2
+    merge_size: int = 2
+    min_pixels: int = 56 * 56
+    max_pixels: int = 14 * 14 * 4 * 1280
+    mean: Sequence[float] = (0.48145466, 0.4578275, 0.40821073)
+    std: Sequence[float] = (0.26862954, 0.26130258, 0.27577711)
+
+    def smart_resize(self, h: int, w: int):
+        """Round both sides to a multiple of patch * merge, keeping the area within [min_pixels, max_pixels]."""
+        f = self.patch_size * self.merge_size
+        hb, wb = max(f, round(h / f) * f), max(f, round(w / f) * f)
+        if hb * wb > self.max_pixels:
+            beta = math.sqrt(h * w / self.max_pixels)
+            hb, wb = max(f, math.floor(h / beta / f) * f), max(f, math.floor(w / beta / f) * f)
+        elif hb * wb < self.min_pixels:
+            beta = math.sqrt(self.min_pixels / (h * w))
+            hb, wb = math.ceil(h * beta / f) * f, math.ceil(w * beta / f) * f
+        return hb, wb
+
+    def __call__(self, image: np.ndarray):
+        """uint8 [H, W, 3] -> (patches [n, C*t*p*p] fp32, grid (t, h, w)). A still image is repeated over the
+        temporal patch."""
+        H, W = image.shape[:2]
+        hb, wb = self.smart_resize(H, W)
+        ys = (np.arange(hb) * H / hb).astype(int)
+        xs = (np.arange(wb) * W / wb).astype(int)
+        img = image[ys][:, xs].astype(np.float32) / 255.0
+        img = (img - np.asarray(self.mean, np.float32)) / np.asarray(self.std, np.float32)
+        chw = np.repeat(img.transpose(2, 0, 1)[None], self.temporal_patch_size, 0)  # [t, C, H, W]
+        p, m = self.patch_size, self.merge_size
+        gh, gw = hb // p, wb // p
+        x = chw.reshape(1, self.temporal_patch_size, 3, gh // m, m, p, gw // m, m, p)
+        # patches ordered in merge units: (grid_t, gh/m, gw/m, m, m) x (C, t, p, p)
+        x = x.transpose(0, 3, 6, 4, 7, 2, 1, 5, 8).reshape(gh * gw, 3 * self.temporal_patch_size * p * p)
+        return x, (1, gh, gw)
+
+
+class VLMTaskEncoder:
+    """Conversation + images -> tokens / labels / pixels. ``tokenize(text) -> List[int]``."""
+
+    def __init__(self, tokenize, image_token_id: int, vision: Optional[VisionPreprocess] = None,
+                 image_marker: str = "<image>", roles=("user", "assistant"), eos_id: Optional[int] = None):
+        self.tok, self.img_id, self.vision = tokenize, image_token_id, vision or VisionPreprocess()
+        self.marker, self.roles, self.eos = image_marker, roles, eos_id
+
+    def encode(self, sample: Dict) -> Dict[str, torch.Tensor]:
+        images = list(sample.get("images", []))
+        pix, grids, ids, labels = [], [], [], []
+        k = 0
+        for turn in sample["conversation"]:
+            parts = turn["content"].split(self.marker)
+            t_ids: List[int] = []
+            for j, part in enumerate(parts):
+                if part:
+                    t_ids += self.tok(part)
+                if j < len(parts) - 1:
+                    p, g = self.vision(images[k])
+                    k += 1
+                    pix.append(p)
+                    grids.append(g)
+                    t_ids += [self.img_id] * (p.shape[0] // self.vision.merge_size ** 2)
+            if turn["role"] == self.roles[1]:
+                if self.eos is not None:
+                    t_ids.append(self.eos)
+                labels += t_ids
+            else:
+                labels += [IGNORE] * len(t_ids)
+            ids += t_ids
+        if k != len(images):
+            raise ValueError(f"{len(images)} images but {k} markers")
+        tokens = torch.tensor(ids, dtype=torch.long)
+        lab = torch.tensor(labels[1:] + [IGNORE], dtype=torch.long)  # next-token targets
+        return {"tokens": tokens, "labels": lab.clamp(min=0), "loss_mask": (lab != IGNORE).float(),
+                "pixels": torch.from_numpy(np.concatenate(pix)) if pix else torch.zeros(0, 0),
+                "grid_thw": torch.tensor(grids, dtype=torch.long).view(-1, 3)}
+
+
+TASK_ENCODERS = {"qwen2_vl": VLMTaskEncoder, "qwen3_vl": VLMTaskEncoder, "internvl": VLMTaskEncoder,
+                 "llava_ov": VLMTaskEncoder, "ernie_vl": VLMTaskEncoder, "kimi_vl": VLMTaskEncoder,
+                 "minicpm_v": VLMTaskEncoder}
+
+
+def pad_to_multiple(n: int, tp: int = 1, cp: int = 1, sequence_parallel: bool = False, fp8: bool = False) -> int:
+    """Sequence lengths must divide by 2*cp (load-balanced CP chunks), by tp under sequence parallelism and by 16 for
+    FP8 GEMM rows."""
+    m = 1
+    if cp > 1:
+        m = math.lcm(m, 2 * cp)
+    if sequence_parallel and tp > 1:
+        m = math.lcm(m, tp * (2 * cp if cp > 1 else 1))
+    if fp8:
+        m = math.lcm(m, 16)
+    return (n + m - 1) // m * m
+
+
+class OnlinePacker:
+    """Buffers encoded samples and emits packs of at most `seq_len` tokens (first-fit decreasing over the buffer)."""
+
+    def __init__(self, seq_len: int, buffer_size: int = 64, pad_id: int = 0, **pad_kw):
+        self.L, self.buf_size, self.pad_id, self.pad_kw = seq_len, buffer_size, pad_id, pad_kw
+        self.buf: List[Dict[str, torch.Tensor]] = []
+
+    def add(self, sample: Dict[str, torch.Tensor]) -> List[Dict[str, torch.Tensor]]:
+        if sample["tokens"].numel() > self.L:
+            return []  # over-long samples are dropped, as the reference's packer does
+        self.buf.append(sample)
+        return self._emit() if len(self.buf) >= self.buf_size else []
+
+    def flush(self) -> List[Dict[str, torch.Tensor]]:
+        out = []
+        while self.buf:
+            out += self._emit(force=True)
+        return out
+
+    def _emit(self, force: bool = False) -> List[Dict[str, torch.Tensor]]:
+        self.buf.sort(key=lambda s: -s["tokens"].numel())
+        bins: List[List[Dict]] = []
+        room: List[int] = []
+        for s in self.buf:
+            n = s["tokens"].numel()
+            for i, r in enumerate(room):
+                if n <= r:
+                    bins[i].append(s)
+                    room[i] -= n
+                    break
+            else:
+                bins.append([s])
+                room.append(self.L - n)
+        # keep the emptiest bin in the buffer (it may still fill up) unless flushing
+        keep = [] if force or len(bins) == 1 else [max(range(len(bins)), key=lambda i: room[i])]
+        self.buf = [s for i in keep for s in bins[i]]
+        return [self._pack(b) for i, b in enumerate(bins) if i not in keep]
+
+    def _pack(self, samples: List[Dict[str, torch.Tensor]]) -> Dict[str, torch.Tensor]:
+        lens = [s["tokens"].numel() for s in samples]
+        total = pad_to_multiple(sum(lens), **self.pad_kw)
+        pad = total - sum(lens)
+        cat = lambda k, fill, dt: torch.cat([s[k] for s in samples] + [torch.full((pad,), fill, dtype=dt)])  # noqa: E731
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        if pad:
+            cu.append(total)  # padding forms its own (masked) sequence so attention never crosses into it
+        pix = [s["pixels"] for s in samples if s["pixels"].numel()]
+        return {"tokens": cat("tokens", self.pad_id, torch.long), "labels": cat("labels", 0, torch.long),
+                "loss_mask": cat("loss_mask", 0.0, torch.float32),
+                "position_ids": torch.cat([torch.arange(n) for n in lens] + [torch.arange(pad)]),
+                "cu_seqlens": torch.tensor(cu, dtype=torch.int32),
+                "pixels": torch.cat(pix) if pix else torch.zeros(0, 0),
+                "grid_thw": torch.cat([s["grid_thw"] for s in samples]) if pix else torch.zeros(0, 3, dtype=torch.long)}

@@ -1,0 +1,99 @@
+"""FP8 (e4m3) block quantisation used by the DSA indexer and the blockwise-FP8 linear path: activations in 1 x 128
+tiles, weights in 128 x 128 blocks, optional power-of-two scales, optional transposed copy for the wgrad GEMM
+(reference kernels: loongforge/models/common/experimental_attention_variant/dsa_fused_kernels.py per-token-group
+quantiser; TransformerEngine blockwise FP8 recipe).
+
+The CUDA kernels live in ``csrc/quant.cu``; the functions here dispatch to them on the GPU and otherwise compute the
+same numbers with PyTorch ops (also the oracle of the kernel tests)."""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+E4M3_MAX = 448.0
+
+
+def _scale(amax: torch.Tensor, pow2: bool) -> torch.Tensor:
+    s = amax.clamp(min=1e-12) / E4M3_MAX
+    if pow2:
+        s = torch.exp2(torch.ceil(torch.log2(s)))
+    return s
+
+
+def quantize_1x128_ref(x: torch.Tensor, pow2: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """x [M, K] (K % 128 == 0) -> (q float8_e4m3fn [M, K], scales fp32 [M, K/128]); x ~= q * scale."""
+    M, K = x.shape
+    xb = x.float().view(M, K // 128, 128)
+    s = _scale(xb.abs().amax(-1), pow2)
+    q = (xb / s.unsqueeze(-1)).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    return q.view(M, K), s
+
+
+def quantize_128x128_ref(w: torch.Tensor, pow2: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """w [N, K] (both % 128 == 0) -> (q [N, K] e4m3, scales [N/128, K/128])."""
+    N, K = w.shape
+    wb = w.float().view(N // 128, 128, K // 128, 128)
+    s = _scale(wb.abs().amax(dim=(1, 3)), pow2)
+    q = (wb / s[:, None, :, None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    return q.view(N, K), s
+
+
+def dequantize_1x128(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+    M, K = q.shape
+    return (q.float().view(M, K // 128, 128) * s.unsqueeze(-1)).view(M, K)
+
+
+def dequantize_128x128(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+    N, K = q.shape
+    return (q.float().view(N // 128, 128, K // 128, 128) * s[:, None, :, None]).view(N, K)
+
+
+def _native(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
+
+
+def quantize_1x128(x: torch.Tensor, pow2: bool = False, transpose: bool = False):
+    """Returns (q, scales) or, with ``transpose``, (q, scales, q_t [K, M], scales_t [K, M/128]) where the transposed
+    copy is quantised along M (what the wgrad GEMM contracts over)."""
+    if _native(x) and x.shape[1] % 128 == 0:
+        from . import _ext
+        C = _ext.require()
+        if hasattr(C, "quant_1x128"):
+            q, s = C.quant_1x128(x, pow2)
+            if not transpose:
+                return q, s
+            qt, st = C.quant_1x128(x.t().contiguous(), pow2) if x.shape[0] % 128 == 0 else quantize_1x128_ref(x.t(), pow2)
+            return q, s, qt, st
+    q, s = quantize_1x128_ref(x, pow2)
+    if not transpose:
+        return q, s
+    qt, st = quantize_1x128_ref(x.t().contiguous(), pow2)
+    return q, s, qt, st
+
+
+def quantize_128x128(w: torch.Tensor, pow2: bool = False):
+    if _native(w) and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0:
+        from . import _ext
+        C = _ext.require()
+        if hasattr(C, "quant_128x128"):
+            return C.quant_128x128(w, pow2)
+    return quantize_128x128_ref(w, pow2)
+
+
+def fp8_blockwise_linear_ref(x: torch.Tensor, w: torch.Tensor, pow2: bool = False) -> torch.Tensor:
+    """y = x @ w^T computed from the block-quantised operands (fp32 accumulate), bf16 out: the oracle of the FP8 GEMM."""
+    qx, sx = quantize_1x128_ref(x, pow2)
+    qw, sw = quantize_128x128_ref(w, pow2)
+    return (dequantize_1x128(qx, sx) @ dequantize_128x128(qw, sw).t()).to(x.dtype)
+
+
+def fp8_blockwise_linear(x: torch.Tensor, w: torch.Tensor, pow2: bool = False) -> torch.Tensor:
+    if _native(x) and _native(w) and x.shape[1] % 128 == 0 and w.shape[0] % 128 == 0:
+        from . import _ext
+        C = _ext.require()
+        if hasattr(C, "gemm_fp8_blockwise"):
+            qx, sx = quantize_1x128(x, pow2)
+            qw, sw = quantize_128x128(w, pow2)
+            return C.gemm_fp8_blockwise(qx, sx, qw, sw, _ext.status_tensor(x.device))
+    return fp8_blockwise_linear_ref(x, w, pow2)

@@ -193,8 +193,11 @@ def _gloo_a2a(outs, ins, group):
         if peer == me:
             outs[me].copy_(ins[me])
             continue
-        reqs.append(dist.isend(ins[peer], ranks[peer], group=group))
-        reqs.append(dist.irecv(outs[peer], ranks[peer], group=group))
+        # zero-size point-to-point transfers never complete on gloo; both sides know the sizes and skip them
+        if ins[peer].numel() > 0:
+            reqs.append(dist.isend(ins[peer], ranks[peer], group=group))
+        if outs[peer].numel() > 0:
+            reqs.append(dist.irecv(outs[peer], ranks[peer], group=group))
     for r in reqs:
         r.wait()
 
