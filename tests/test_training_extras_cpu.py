@@ -1,0 +1,106 @@
+"""EMA, sparse upcycling, profiler / inspector hooks, scalar writers, asynchronous + local checkpoints, retention."""
+import json
+import os
+
+import torch
+
+from loongforge_b200.parallel import state as ps
+
+
+def test_ema_tracks_and_swaps():
+    from loongforge_b200.runtime.ema import ModelEMA
+
+    m = torch.nn.Linear(3, 3)
+    ema = ModelEMA(m.named_parameters(), decay=0.5, warmup=False)
+    w0 = m.weight.detach().clone()
+    with torch.no_grad():
+        m.weight.add_(2.0)
+    ema.update()
+    assert torch.allclose(ema.shadow["weight"], w0 + 1.0)
+    with ema.swapped_in():
+        assert torch.allclose(m.weight, w0 + 1.0)
+    assert torch.allclose(m.weight, w0 + 2.0)
+    e2 = ModelEMA(m.named_parameters(), decay=0.9)
+    e2.load_state_dict(ema.state_dict())
+    assert torch.equal(e2.shadow["weight"], ema.shadow["weight"]) and e2.updates == 1
+
+
+def test_upcycled_moe_reproduces_dense_output():
+    from loongforge_b200.models.registry import build_model, get_model_config
+    from loongforge_b200.runtime.upcycling import upcycle_state_dict
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(ps.ParallelDims())
+    base = dict(vocab_size=256, num_layers=1)
+    dense = build_model(get_model_config("tiny-llama", **base))
+    cfg = get_model_config("tiny-llama", num_moe_experts=4, moe_router_topk=2, moe_ffn_hidden_size=688 // 2,
+                           moe_router_pre_softmax=False, moe_aux_loss_coeff=0.0, **base)
+    moe = build_model(cfg)
+    sd = upcycle_state_dict(dense.state_dict(), 4, granularity=2, router_std=0.0)
+    missing, unexpected = moe.load_state_dict(sd, strict=False)
+    assert not unexpected and not [k for k in missing if "_extra_state" not in k], (missing, unexpected)
+    # a zero router ties all experts; make the top-2 pick one expert of each slice with weights 1/2 each
+    with torch.no_grad():
+        moe.decoder.layers[0].mlp.router.weight.zero_()
+    tokens, pos = torch.randint(0, 256, (16,)), torch.arange(16)
+    a, b = dense(tokens, pos), moe(tokens, pos)
+    assert torch.allclose(a, b, atol=2e-4), (a - b).abs().max()
+
+
+def test_profiler_inspector_and_writers(tmp_path):
+    from loongforge_b200.runtime import metrics_writers as W, profiling as P
+
+    prof = P.StepProfiler(str(tmp_path), 1, 3, ranks=[0], rank=0, profile_memory=False)
+    for it in range(5):
+        torch.randn(64, 64) @ torch.randn(64, 64)
+        prof.step(it)
+    assert prof.trace_path and os.path.getsize(prof.trace_path) > 0
+    assert P.detail_iteration(20, 10) and not P.detail_iteration(21, 10) and not P.detail_iteration(5, None)
+    with P.nvtx_range("x"):
+        pass
+    m = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.ReLU(), torch.nn.Linear(4, 2))
+    insp = P.TensorInspector(m, ["0", "2"], str(tmp_path / "tensors.jsonl"))
+    m(torch.randn(3, 4)).sum().backward()
+    insp.step()
+    recs = [json.loads(x) for x in open(tmp_path / "tensors.jsonl")]
+    assert {(r["module"], r["kind"]) for r in recs} == {("0", "fwd"), ("2", "fwd"), ("0", "bwd"), ("2", "bwd")}
+    insp.remove()
+    w = W.ScalarWriter(str(tmp_path / "tb"), tensorboard=True)
+    w.add_scalars({"lm loss": 2.5, "lr": 1e-4}, 3)
+    w.close()
+    assert json.loads(open(tmp_path / "tb" / "scalars.jsonl").readline())["lm loss"] == 2.5
+    pl = W.ProgressLog(str(tmp_path), 8)
+    pl.start(0.0, "job1")
+    pl.checkpoint(10, 1000, 8e12)
+    assert "Saved checkpoint" in open(tmp_path / "progress.txt").read()
+    assert W.EnergyMonitor().lap() >= 0.0
+    txt = W.dump_first_batch({"tokens": torch.tensor([5, 6, 7]), "loss_mask": torch.tensor([0, 1, 1])})
+    assert "5 [6] [7]" in txt
+
+
+def test_async_local_checkpoints_and_retention(tmp_path):
+    from loongforge_b200.ckpt import async_save as A
+
+    saver = A.AsyncSaver()
+    state = {"w": torch.arange(4.0), "nested": {"step": 3, "t": [torch.ones(2)]}}
+    done = []
+    saver.save(str(tmp_path / "iter_0000004" / "x.pt"), state, on_done=lambda: done.append(1))
+    state["w"].zero_()  # the staged copy is what gets written
+    saver.wait()
+    back = torch.load(tmp_path / "iter_0000004" / "x.pt", weights_only=False)
+    assert done == [1] and torch.equal(back["w"], torch.arange(4.0)) and back["nested"]["step"] == 3
+    for i in (2, 6, 8, 10):
+        os.makedirs(tmp_path / f"iter_{i:07d}", exist_ok=True)
+    assert A.apply_retention(str(tmp_path), keep_last=1, retain_interval=4) == [2, 6]
+    assert A.list_iterations(str(tmp_path)) == [4, 8, 10]
+    loc = A.LocalCheckpointManager(str(tmp_path / "local"), rank=1)
+    loc.save(11, {"a": torch.ones(1)})
+    loc.save(12, {"a": torch.full((1,), 2.0)})
+    assert A.list_iterations(str(tmp_path / "local")) == [12]
+    assert loc.find_latest(10) == 12 and loc.find_latest(12) is None and float(loc.load(12)["a"]) == 2.0
+    A.save_dataloader_state(str(tmp_path), 3, {"consumed": 77})
+    assert A.load_dataloader_state(str(tmp_path), 3) == {"consumed": 77} and A.load_dataloader_state(str(tmp_path), 4) is None
+    ex = A.ExitDecider(exit_interval=5)
+    assert ex.should_exit(10) == "interval" and ex.should_exit(11) is None
+    ex._on_signal(15, None)
+    assert ex.should_exit(11) == "signal"
