@@ -1,0 +1,121 @@
+"""ChunkPipe: a long sequence is cut into chunks that run through the layers one after another, each chunk attending to
+the cached keys / values of the chunks before it; activations of only ONE chunk are alive at a time.
+
+Forward pass (no autograd): chunk c computes its K/V per layer, appends them to the caches, produces its loss.
+Backward pass, chunks in REVERSE order: chunk c is recomputed with autograd against the caches of chunks < c (leaf
+tensors), its loss is back-propagated together with the gradient that later chunks deposited on ITS keys / values,
+and the gradient it produces for earlier chunks' K/V is accumulated into their cache gradients — the cross-chunk
+gradient accumulation of the reference (loongforge/train/training_utils.py:1696-1706 micro-batch x chunk counting,
+chunk-aware RoPE offsets and recompute in base_gpt_model.py / language_transformer_block.py).
+
+``ChunkedAttentionLayer`` is the protocol a layer must follow (``forward(x, past_kv, offset) -> (y, (k, v))``);
+``CausalSelfAttentionBlock`` is a reference layer used by the tests and by small models."""
+from __future__ import annotations
+
+import math
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+KV = Tuple[torch.Tensor, torch.Tensor]
+
+
+class CausalSelfAttentionBlock(nn.Module):
+    """Pre-norm attention + MLP block over ``[T, C]`` tokens with an optional key/value prefix."""
+
+    def __init__(self, dim: int, heads: int, rope_theta: float = 10000.0):
+        super().__init__()
+        self.h, self.d = heads, dim // heads
+        self.n1, self.n2 = nn.LayerNorm(dim), nn.LayerNorm(dim)
+        self.qkv, self.o = nn.Linear(dim, 3 * dim), nn.Linear(dim, dim)
+        self.mlp = nn.Sequential(nn.Linear(dim, 4 * dim), nn.GELU(), nn.Linear(4 * dim, dim))
+        self.theta = rope_theta
+
+    def _rope(self, x, offset):
+        T = x.shape[0]
+        inv = 1.0 / (self.theta ** (torch.arange(0, self.d, 2, dtype=torch.float32) / self.d))
+        ang = torch.outer(torch.arange(offset, offset + T, dtype=torch.float32), inv)
+        cos, sin = ang.cos()[:, None], ang.sin()[:, None]
+        a, b = x[..., :self.d // 2], x[..., self.d // 2:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin], -1)
+
+    def forward(self, x: torch.Tensor, past: Optional[KV] = None, offset: int = 0):
+        T = x.shape[0]
+        q, k, v = self.qkv(self.n1(x)).view(T, 3, self.h, self.d).unbind(1)
+        q, k = self._rope(q, offset), self._rope(k, offset)
+        if past is not None:
+            kk, vv = torch.cat([past[0], k], 0), torch.cat([past[1], v], 0)
+        else:
+            kk, vv = k, v
+        P = kk.shape[0] - T
+        mask = torch.ones(T, P + T, dtype=torch.bool).tril(P)  # token i sees the whole prefix and itself
+        o = F.scaled_dot_product_attention(q.transpose(0, 1), kk.transpose(0, 1), vv.transpose(0, 1), attn_mask=mask)
+        x = x + self.o(o.transpose(0, 1).reshape(T, -1))
+        return x + self.mlp(self.n2(x)), (k, v)
+
+
+def chunk_bounds(seq_len: int, num_chunks: int) -> List[Tuple[int, int]]:
+    size = math.ceil(seq_len / num_chunks)
+    return [(s, min(s + size, seq_len)) for s in range(0, seq_len, size)]
+
+
+def chunkpipe_forward_backward(layers: Sequence[nn.Module], embed: Callable[[torch.Tensor], torch.Tensor],
+                               loss_fn: Callable[[torch.Tensor, int, int], torch.Tensor], tokens: torch.Tensor,
+                               num_chunks: int) -> float:
+    """Accumulates parameter gradients of ``sum_c loss_fn(hidden_c, start_c, end_c)`` and returns the loss value.
+    Peak activation memory is that of one chunk plus the K/V caches."""
+    bounds = chunk_bounds(tokens.shape[0], num_chunks)
+    L = len(layers)
+    caches: List[List[KV]] = [[] for _ in range(L)]  # caches[l][c] = (k, v) of chunk c at layer l
+    total = 0.0
+    with torch.no_grad():
+        for (s, e) in bounds:
+            x = embed(tokens[s:e])
+            for l, layer in enumerate(layers):
+                past = (torch.cat([kv[0] for kv in caches[l]]), torch.cat([kv[1] for kv in caches[l]])) if caches[l] else None
+                x, kv = layer(x, past, s)
+                caches[l].append(kv)
+            total += float(loss_fn(x, s, e))
+    grads: List[List[Optional[KV]]] = [[None] * len(bounds) for _ in range(L)]  # gradient deposited on chunk c's K/V
+    for c in range(len(bounds) - 1, -1, -1):
+        s, e = bounds[c]
+        leaves: List[Optional[KV]] = []
+        x = embed(tokens[s:e])
+        own: List[KV] = []
+        for l, layer in enumerate(layers):
+            if c > 0:
+                pk = torch.cat([caches[l][j][0] for j in range(c)]).requires_grad_(True)
+                pv = torch.cat([caches[l][j][1] for j in range(c)]).requires_grad_(True)
+                leaves.append((pk, pv))
+                x, kv = layer(x, (pk, pv), s)
+            else:
+                leaves.append(None)
+                x, kv = layer(x, None, s)
+            own.append(kv)
+        outs, outg = [loss_fn(x, s, e)], [None]
+        for l in range(L):
+            if grads[l][c] is not None:  # what later chunks want from this chunk's keys / values
+                outs += [own[l][0], own[l][1]]
+                outg += [grads[l][c][0], grads[l][c][1]]
+        torch.autograd.backward(outs, outg)
+        for l in range(L):
+            if leaves[l] is None:
+                continue
+            gk, gv = leaves[l][0].grad, leaves[l][1].grad
+            off = 0
+            for j in range(c):
+                n = caches[l][j][0].shape[0]
+                piece = (gk[off:off + n], gv[off:off + n])
+                grads[l][j] = piece if grads[l][j] is None else (grads[l][j][0] + piece[0], grads[l][j][1] + piece[1])
+                off += n
+        for l in range(L):
+            caches[l][c] = (caches[l][c][0], caches[l][c][1])  # keep for earlier chunks' recomputation
+            grads[l][c] = None
+    return total
+
+
+def num_microbatches_with_chunks(num_microbatches: int, num_chunks: int) -> int:
+    """The pipeline schedule sees every chunk as a micro-batch of its own."""
+    return num_microbatches * num_chunks

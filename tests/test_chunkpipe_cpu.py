@@ -1,0 +1,64 @@
+"""ChunkPipe gradients equal those of the un-chunked sequence; balanced group sampler and savable iterators."""
+import torch
+
+from loongforge_b200.runtime import chunkpipe as CP
+
+
+def _grads(model_parts):
+    return [p.grad.clone() for m in model_parts for p in m.parameters()]
+
+
+def test_chunkpipe_matches_full_sequence():
+    torch.manual_seed(0)
+    dim, T, V = 32, 50, 64
+    layers = torch.nn.ModuleList([CP.CausalSelfAttentionBlock(dim, 4) for _ in range(3)])
+    emb, head = torch.nn.Embedding(V, dim), torch.nn.Linear(dim, V)
+    tokens = torch.randint(0, V, (T,))
+    labels = torch.roll(tokens, -1)
+
+    def loss_fn(h, s, e):
+        return torch.nn.functional.cross_entropy(head(h), labels[s:e], reduction="sum") / T
+
+    x = emb(tokens)
+    for layer in layers:
+        x, _ = layer(x, None, 0)
+    ref = loss_fn(x, 0, T)
+    ref.backward()
+    want = _grads([layers, emb, head])
+    for m in (layers, emb, head):
+        m.zero_grad()
+    got_loss = CP.chunkpipe_forward_backward(layers, emb, loss_fn, tokens, num_chunks=4)
+    assert abs(got_loss - float(ref)) < 1e-4
+    for a, b in zip(_grads([layers, emb, head]), want):
+        assert torch.allclose(a, b, atol=2e-5, rtol=1e-4), (a - b).abs().max()
+    assert CP.chunk_bounds(50, 4) == [(0, 13), (13, 26), (26, 39), (39, 50)]
+    assert CP.num_microbatches_with_chunks(8, 4) == 32
+
+
+def test_balanced_group_sampler_and_savable_iterator():
+    from loongforge_b200.data.samplers import BalancedGroupSampler, SavableCyclicIterator
+
+    lengths = [4000, 100, 200, 3900, 150, 50, 3000, 2900] * 4
+    samplers = [BalancedGroupSampler(lengths, 8, 2, r, capacity=4096, seed=1) for r in range(2)]
+    its = [iter(s) for s in samplers]
+    for _ in range(3):
+        shares = [next(it) for it in its]
+        flat = [[i for p in sh for i in p] for sh in shares]
+        assert len(set(flat[0]) | set(flat[1])) == 8 and not set(flat[0]) & set(flat[1])
+        cost = [sum(lengths[i] ** 2 for i in f) for f in flat]
+        assert max(cost) / (sum(cost) / 2) < 1.25
+        for sh in shares:
+            assert all(sum(min(lengths[i], 4096) for i in p) <= 4096 for p in sh)
+    sd = samplers[0].state_dict()
+    nxt = next(its[0])
+    s2 = BalancedGroupSampler(lengths, 8, 2, 0, capacity=4096, seed=1)
+    s2.load_state_dict(sd)
+    assert next(iter(s2)) == nxt
+    it = SavableCyclicIterator(list(range(5)), seed=3)
+    first = [next(it) for _ in range(7)]
+    assert sorted(first[:5]) == [0, 1, 2, 3, 4]
+    sd = it.state_dict()
+    a = [next(it) for _ in range(4)]
+    it2 = SavableCyclicIterator(list(range(5)), seed=3)
+    it2.load_state_dict(sd)
+    assert [next(it2) for _ in range(4)] == a
