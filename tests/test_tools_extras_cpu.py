@@ -1,0 +1,97 @@
+"""Converter formats (FP8 block, INT4 compressed-tensors, MXFP4), merge tools, SFT pre-tokenisation, offline packing,
+WebDataset shards."""
+import json
+import os
+
+import torch
+
+
+def test_fp8_block_format_roundtrip_with_ragged_edges():
+    from tools.convert_checkpoint import quant_formats as Q
+
+    torch.manual_seed(0)
+    w = torch.randn(200, 300) * 3
+    q, s = Q.fp8_block_quantize(w)
+    assert q.dtype == torch.float8_e4m3fn and s.shape == (2, 3)
+    back = Q.fp8_block_dequantize(q, s, dtype=torch.float32)
+    assert ((back - w).abs() / w.abs().max()).max() < 0.04
+    sd = {"a.weight": w, "model.norm.weight": torch.ones(300), "embed.weight": torch.randn(10, 4)}
+    qsd = Q.quantize_fp8_state_dict(sd)
+    assert "a.weight_scale_inv" in qsd and qsd["embed.weight"].dtype == torch.float32
+    dsd = Q.dequantize_fp8_state_dict(qsd, dtype=torch.float32)
+    assert set(dsd) == set(sd) and torch.allclose(dsd["a.weight"], back)
+
+
+def test_int4_and_mxfp4():
+    from tools.convert_checkpoint import quant_formats as Q
+
+    torch.manual_seed(1)
+    w = torch.randn(16, 256)
+    for sym in (True, False):
+        p, s, z = Q.int4_pack(w, 128, symmetric=sym)
+        assert p.dtype == torch.int32 and p.shape == (16, 32) and s.shape == (16, 2) and (z is None) == sym
+        back = Q.int4_unpack(p, s, z, 128, dtype=torch.float32)
+        assert (back - w).abs().max() <= s.max() * 0.51 + 1e-6
+    exact = torch.tensor([[0.5, -6.0, 3.0, 1.5] * 8]) * 4.0  # representable values with a shared exponent
+    b, e = Q.mxfp4_quantize(exact)
+    assert b.shape == (1, 1, 16) and e.shape == (1, 1)
+    assert torch.equal(Q.mxfp4_dequantize(b, e, torch.float32), exact)
+    r = torch.randn(4, 64)
+    rb = Q.mxfp4_dequantize(*Q.mxfp4_quantize(r), torch.float32)
+    assert ((rb - r).abs() / r.abs().amax(-1, keepdim=True)).max() < 0.26
+
+
+def test_merge_tools():
+    from tools.convert_checkpoint import merge_tools as M
+
+    base = {"l.q_proj.weight": torch.zeros(4, 6), "other": torch.ones(1)}
+    A, B = torch.randn(2, 6), torch.randn(4, 2)
+    lora = {"base_model.model.l.q_proj.lora_A.default.weight": A, "base_model.model.l.q_proj.lora_B.default.weight": B}
+    out = M.merge_lora_state_dict(base, lora, alpha=4, rank=2)
+    assert torch.allclose(out["l.q_proj.weight"], 2.0 * B @ A) and torch.equal(out["other"], base["other"])
+    vlm = M.merge_vlm_state_dicts({"a": torch.ones(1)}, {"b": torch.ones(1)}, {"c": torch.ones(1)})
+    assert set(vlm) == {"foundation_model.a", "encoder_model.image_encoder.b", "encoder_model.image_projector.c"}
+    s0 = {"x.experts.linear_fc1.weight0": torch.zeros(1), "x.experts.linear_fc1.weight1": torch.ones(1), "r": torch.ones(2)}
+    s1 = {"x.experts.linear_fc1.weight0": torch.full((1,), 2.0), "x.experts.linear_fc1.weight1": torch.full((1,), 3.0),
+          "r": torch.ones(2)}
+    m = M.merge_expert_shards([s0, s1])
+    assert [float(m[f"x.experts.linear_fc1.weight{i}"]) for i in range(4)] == [0, 1, 2, 3]
+
+
+def test_sft_pretokenise_then_offline_packing(tmp_path):
+    from tools.data_preprocess import offline_packing, preprocess_sft_data
+
+    recs = [{"instruction": "say " + "x" * n, "output": "ok"} for n in (5, 50, 500, 20, 200, 3000)]
+    src = tmp_path / "sft.jsonl"
+    src.write_text("\n".join(json.dumps(r) for r in recs))
+    kept, dropped = preprocess_sft_data.main(["--input", str(src), "--output-prefix", str(tmp_path / "tok"),
+                                              "--max-length", "1000", "--shard-size", "3"])
+    assert (kept, dropped) == (5, 1)
+    idx = json.load(open(tmp_path / "tok_index.json"))
+    assert idx["shards"] == 2 and len(idx["lengths"]) == 5
+    first = json.loads(open(tmp_path / "tok_00000.jsonl").readline())
+    assert len(first["input_ids"]) == len(first["labels"]) and -100 in first["labels"]
+    packs = offline_packing.main(["--index", str(tmp_path / "tok_index.json"), "--seq-length", "1000", "--output",
+                                  str(tmp_path / "packs.json")])
+    flat = sorted(i for p in packs for i in p)
+    assert flat == [0, 1, 2, 3, 4]
+    assert all(sum(idx["lengths"][i] for i in p) <= 1000 for p in packs) and len(packs) <= 3
+    big = offline_packing.pack_with_buckets([700, 600, 300, 400, 100, 900, 50, 50], 1000, 64)
+    assert sorted(i for p in big for i in p) == list(range(8)) and len(big) <= 4
+
+
+def test_webdataset_shards(tmp_path):
+    from tools.data_preprocess import vlm_to_webdataset as W
+
+    (tmp_path / "img").mkdir()
+    for i in range(3):
+        (tmp_path / "img" / f"{i}.jpg").write_bytes(bytes([i]) * 10)
+    recs = [{"image": f"{i}.jpg", "conversations": [{"from": "human", "value": "<image> hi"}]} for i in range(3)]
+    recs.append({"image": ["0.jpg", "1.jpg"], "conversations": []})
+    index = W.write_shards(recs, str(tmp_path / "wds"), str(tmp_path / "img"), samples_per_shard=3)
+    assert index["total"] == 4 and [s["count"] for s in index["shards"]] == [3, 1]
+    groups = list(W.read_shard(str(tmp_path / "wds" / "shard-000000.tar")))
+    assert len(groups) == 3 and groups[1][1]["jpg"] == bytes([1]) * 10
+    assert json.loads(groups[0][1]["json"])["num_images"] == 1
+    multi = list(W.read_shard(str(tmp_path / "wds" / "shard-000001.tar")))[0][1]
+    assert set(multi) == {"0.jpg", "1.jpg", "json"}
