@@ -71,7 +71,8 @@ class _GatherVarRows(torch.autograd.Function):
 class OmniCombinationModel(nn.Module):
     def __init__(self, lm_cfg: TransformerConfig, vit_cfg: Optional[TransformerConfig], *, image_token_id: int,
                  pre_process: bool = True, post_process: bool = True, layer_numbers=None, device=None,
-                 encoder_hetero_dp: bool = False, freeze_encoder: bool = False, projector_activation: str = "gelu"):
+                 encoder_hetero_dp: bool = False, freeze_encoder: bool = False, projector_activation: str = "gelu",
+                 vision_family: str = "qwen2_vit", vision_options: Optional[dict] = None):
         super().__init__()
         self.cfg = lm_cfg
         self.image_token_id = image_token_id
@@ -83,11 +84,26 @@ class OmniCombinationModel(nn.Module):
         if self.has_encoder:
             enc_state = ENCODER_STATE if ENCODER_STATE in ps._STATES else None
             self.encoder_state = enc_state
+            self.vision_family = vision_family
             with parallel_state(enc_state):
                 self.encoder_model = nn.Module()
-                self.encoder_model.image_encoder = VisionModel(vit_cfg, device=device, parallel_state=enc_state)
-                self.encoder_model.image_projector = MLPAdapter(vit_cfg, lm_cfg.hidden_size, device=device,
-                                                                activation=projector_activation)
+                if vision_family == "qwen2_vit":
+                    self.encoder_model.image_encoder = VisionModel(vit_cfg, device=device, parallel_state=enc_state)
+                    self.encoder_model.image_projector = MLPAdapter(vit_cfg, lm_cfg.hidden_size, device=device,
+                                                                    activation=projector_activation)
+                else:
+                    # the other encoder families: one configurable ViT + the family's projector (models/vision_zoo.py)
+                    from . import vision_zoo as VZ
+                    opts, adapter_cls = VZ.VISION_FAMILIES[vision_family]
+                    opts = {**opts, **(vision_options or {})}
+                    self.encoder_model.image_encoder = VZ.GenericViT(vit_cfg, device=device, parallel_state=enc_state,
+                                                                     **opts)
+                    self.encoder_model.image_projector = (adapter_cls or VZ.PatchMergerAdapter)(
+                        vit_cfg, lm_cfg.hidden_size, device=device)
+                    n_taps = len(opts.get("deepstack_indexes", ()))
+                    if n_taps:
+                        self.encoder_model.deepstack_mergers = VZ.DeepStackMergers(vit_cfg, lm_cfg.hidden_size, n_taps,
+                                                                                   device=device)
             if freeze_encoder:
                 for p in self.encoder_model.image_encoder.parameters():
                     p.requires_grad_(False)
@@ -115,10 +131,18 @@ class OmniCombinationModel(nn.Module):
             pixels, my_grid = pixels[p0:p1], grid_thw[i0:i1]
         else:
             my_grid = grid_thw
+        self._deepstack = None
         with parallel_state(self.encoder_state):
-            h, widx = self.encoder_model.image_encoder(pixels, my_grid)
-            emb = self.encoder_model.image_projector(h, widx)
+            if self.vision_family == "qwen2_vit":
+                h, widx = self.encoder_model.image_encoder(pixels, my_grid)
+                emb = self.encoder_model.image_projector(h, widx)
+            else:
+                h, taps = self.encoder_model.image_encoder(pixels, my_grid)
+                emb = self.encoder_model.image_projector(h, my_grid)
+                if taps and hasattr(self.encoder_model, "deepstack_mergers"):
+                    self._deepstack = self.encoder_model.deepstack_mergers(taps, my_grid)
         if split:
+            assert self.vision_family == "qwen2_vit", "encoder hetero-DP is implemented for the Qwen2-VL encoder"
             unit = self.encoder_model.image_projector.unit
             counts = [sum(patches[starts[r]:starts[r] + per[r]]) // unit for r in range(tp)]
             emb = _GatherVarRows.apply(emb, counts, g)
@@ -146,6 +170,12 @@ class OmniCombinationModel(nn.Module):
                 img = self.encode_images(pixels, grid_thw).to(x.dtype)
                 mask = tokens == self.image_token_id
                 x = x.masked_scatter(mask.unsqueeze(-1), img)
+                if getattr(self, "_deepstack", None):
+                    from .vision_zoo import make_deepstack_hook
+                    assert not sp, "DeepStack injection expects un-scattered hidden states"
+                    self.decoder.deepstack_hook = make_deepstack_hook(self._deepstack, mask)
+                else:
+                    self.decoder.deepstack_hook = None
             if sp:
                 x = M.scatter_to_sequence_parallel_region(x, st.group("tp"))
             decoder_input = x

@@ -113,3 +113,25 @@ def test_vlm_trainer_loss_on_text_only():
     assert float((b["loss_mask"][0][b["tokens"][0] == lm.vocab_size - 1]).sum()) == 0.0
     m = tr.train_step(it)
     assert np.isfinite(m["lm loss"]) and m["grad_norm"] > 0
+
+
+def test_internvl_tiling_and_ernie_positions():
+    import torch
+    from loongforge_b200.runtime import sft_families as F
+
+    assert F.internvl_tile_grid(448, 448) == (1, 1)
+    assert F.internvl_tile_grid(1792, 448, max_tiles=6) == (4, 1)
+    assert F.internvl_tile_grid(896, 1344, max_tiles=6) == (2, 3)
+    assert F.internvl_num_tiles(448, 448) == 1 and F.internvl_num_tiles(896, 1344, max_tiles=6) == 7
+    ids, tiles = F.internvl_expand_image_tokens([1, 9, 2], [(896, 448)], image_marker_id=9, img_start_id=5,
+                                                img_context_id=6, img_end_id=7, tokens_per_tile=4, max_tiles=4)
+    assert tiles == [3] and ids == [1, 5] + [6] * 12 + [7, 2]
+    b = F.internvl_batch([{"input_ids": [1, 2, 3], "labels": [-100, 2, 3], "pixel_tiles": torch.zeros(2, 3, 448, 448)},
+                          {"input_ids": [4, 5], "labels": [-100, 5], "pixel_tiles": None}])
+    assert b["cu_seqlens"].tolist() == [0, 3, 5] and b["loss_mask"].tolist() == [1, 1, 0, 1, 0]
+    assert b["pixel_tiles"].shape[0] == 2
+    tok = torch.tensor([3, 4, 8, 8, 8, 8, 8, 8, 5])
+    tt, pos = F.ernie_token_types_and_positions(tok, 8, [(2, 3)])
+    assert tt.tolist() == [0, 0, 1, 1, 1, 1, 1, 1, 0]
+    assert pos[0].tolist() == [0, 1, 2, 2, 2, 2, 2, 2, 5]
+    assert pos[1].tolist() == [0, 1, 2, 2, 2, 3, 3, 3, 5] and pos[2].tolist() == [0, 1, 2, 3, 4, 2, 3, 4, 5]

@@ -79,3 +79,29 @@ def test_deepstack_hook_adds_only_at_image_tokens():
     hook = VZ.make_deepstack_hook([torch.ones(3, 4), 2 * torch.ones(3, 4)], mask)
     assert hook(0, hidden)[mask].eq(1).all() and hook(0, hidden)[~mask].eq(0).all()
     assert hook(1, hidden)[mask].eq(2).all() and torch.equal(hook(2, hidden), hidden)
+
+
+@pytest.mark.parametrize("family", ["qwen3_vl_vit", "intern_vit", "moon_vit"])
+def test_omni_model_with_zoo_encoders(family):
+    """Composed VLM: image tokens replaced by projected features (+ DeepStack taps added in the first LLM layers)."""
+    from loongforge_b200.models.omni import OmniCombinationModel
+    from loongforge_b200.models.registry import get_model_config
+
+    lm = get_model_config("tiny-llama", vocab_size=300, num_layers=3)
+    vit = _cfg(qk_layernorm_full=(family == "intern_vit"))
+    over = {"pos_table_side": 8}
+    if family == "qwen3_vl_vit":
+        over["deepstack_indexes"] = (0, 1)
+    torch.manual_seed(0)
+    m = OmniCombinationModel(lm, vit, image_token_id=299, vision_family=family, vision_options=over)
+    n_img_tok = 1 * 2 * 3 + 2 * 1 * 2
+    tokens = torch.cat([torch.randint(0, 298, (5,)), torch.full((n_img_tok,), 299), torch.randint(0, 298, (7,))])
+    T = tokens.numel()
+    loss = m(tokens, torch.arange(T), pixels=_pixels(vit), grid_thw=GRID, labels=torch.roll(tokens, -1),
+             loss_mask=torch.ones(T)).mean()
+    loss.backward()
+    assert torch.isfinite(loss)
+    missing = [n for n, p in m.named_parameters() if p.grad is None]
+    assert not missing, missing
+    if family == "qwen3_vl_vit":
+        assert m.decoder.deepstack_hook is not None
