@@ -138,14 +138,20 @@ class GroupedLinear(nn.Module):
     contiguous slice of a token list sorted by expert."""
 
     def __init__(self, num_local: int, first_global: int, in_f: int, out_f: int, key: str, std: float,
-                 cfg: TransformerConfig, device=None, stride: int = 1):
+                 cfg: TransformerConfig, device=None, stride: int = 1, etp_dim: Optional[int] = None,
+                 etp_rank: int = 0, etp_size: int = 1):
+        """``etp_dim``: dimension along which every expert weight is sharded over the expert-tensor-parallel group
+        (0 for FC1, column parallel with `stride` blocks; 1 for FC2, row parallel); None = not sharded."""
         super().__init__()
         self.num_local = num_local
+        shard = etp_dim if etp_size > 1 else None
         for e in range(num_local):
-            w = PL.init_full_then_slice(f"{key}.weight{first_global + e}", (out_f, in_f), std, partition_dim=None,
-                                        rank=0, world=1, device=device or "cpu", dtype=cfg.params_dtype)
+            w = PL.init_full_then_slice(f"{key}.weight{first_global + e}", (out_f, in_f), std, partition_dim=shard,
+                                        rank=etp_rank if shard is not None else 0,
+                                        world=etp_size if shard is not None else 1, device=device or "cpu",
+                                        dtype=cfg.params_dtype, stride=stride if shard == 0 else 1)
             p = nn.Parameter(w)
-            PL.mark_tp(p, None)
+            PL.mark_tp(p, shard, stride=stride if shard == 0 else 1)
             p.is_expert = True
             p.partition_stride = stride
             self.register_parameter(f"weight{e}", p)
@@ -158,14 +164,19 @@ class GroupedLinear(nn.Module):
 
 
 class GroupedMLP(nn.Module):
-    def __init__(self, cfg: TransformerConfig, key: str, num_local: int, first_global: int, device=None):
+    def __init__(self, cfg: TransformerConfig, key: str, num_local: int, first_global: int, device=None,
+                 etp_rank: int = 0, etp_size: int = 1):
         super().__init__()
         f = cfg.moe_ffn_hidden_size
         glu = cfg.gated_linear_unit
+        assert f % etp_size == 0, "moe_ffn_hidden_size must divide by the expert tensor parallel size"
+        etp = dict(etp_rank=etp_rank, etp_size=etp_size)
         self.linear_fc1 = GroupedLinear(num_local, first_global, cfg.hidden_size, f * (2 if glu else 1),
-                                        key + ".linear_fc1", cfg.init_method_std, cfg, device, stride=2 if glu else 1)
+                                        key + ".linear_fc1", cfg.init_method_std, cfg, device, stride=2 if glu else 1,
+                                        etp_dim=0, **etp)
         self.linear_fc2 = GroupedLinear(num_local, first_global, f, cfg.hidden_size, key + ".linear_fc2",
-                                        cfg.init_method_std / math.sqrt(2.0 * cfg.num_layers), cfg, device)
+                                        cfg.init_method_std / math.sqrt(2.0 * cfg.num_layers), cfg, device,
+                                        etp_dim=1, **etp)
         self.glu = glu
         self.act = cfg.activation
 
@@ -252,7 +263,9 @@ class MoELayer(nn.Module):
         assert E % ep == 0, "num_moe_experts must divide by expert parallel size"
         self.E_local = E // ep
         self.router = TopKRouter(cfg, key + ".router", layer_number, device=device)
-        self.experts = GroupedMLP(cfg, key + ".experts", self.E_local, st.ep_rank * self.E_local, device=device)
+        self.etp = st.dims.etp
+        self.experts = GroupedMLP(cfg, key + ".experts", self.E_local, st.ep_rank * self.E_local, device=device,
+                                  etp_rank=st.etp_rank, etp_size=st.dims.etp)
         if cfg.moe_shared_expert_intermediate_size:
             from .transformer import MLP
             self.shared_experts = MLP(cfg, key + ".shared_experts", ffn_hidden=cfg.moe_shared_expert_intermediate_size,
@@ -267,9 +280,23 @@ class MoELayer(nn.Module):
             self.peer_dispatcher = PeerDispatcher(E, cfg.hidden_size, ep, st.ep_rank, st.group("ep") if ep > 1 else None,
                                                   cfg.moe_peer_capacity_factor)
 
+    def _forward_etp(self, x, probs, routing_map):
+        """Expert tensor parallelism: the ranks of an ETP group hold slices of every expert's FFN width. They first
+        share their tokens (all-gather), run the same dispatch, compute partial FC2 sums with their slices, and
+        reduce-scatter the combined output back to each rank's own tokens."""
+        g = ps.get_state(self.state_name).group("etp")
+        xf = M.gather_from_sequence_parallel_region(x, g, False)
+        pf = M.gather_from_sequence_parallel_region(probs, g, False)
+        mf = M.gather_from_sequence_parallel_region(routing_map.to(torch.uint8), g, False).bool()
+        tokens, tpe = self.dispatcher.dispatch(xf, pf, mf)
+        out = self.dispatcher.combine(self.experts(tokens, tpe))
+        return M.reduce_scatter_to_sequence_parallel_region(out, g)
+
     def forward(self, x: torch.Tensor, seq_lens=None) -> torch.Tensor:
         probs, routing_map = self.router(x, seq_lens)
-        if self.peer_dispatcher is not None and x.is_cuda and x.dtype == torch.bfloat16:
+        if self.etp > 1:
+            out = self._forward_etp(x, probs, routing_map)
+        elif self.peer_dispatcher is not None and x.is_cuda and x.dtype == torch.bfloat16:
             # indices of the k selected experts of every token (order within a token is irrelevant)
             topk_idx = routing_map.to(torch.float16).topk(self.cfg.moe_router_topk, dim=1).indices
             tokens, tpe, row_probs = self.peer_dispatcher.dispatch(x, probs, topk_idx)

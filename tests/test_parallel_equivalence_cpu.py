@@ -58,6 +58,14 @@ def test_moe_expert_parallel_matches_single_process():
     _check(ref, res, lambda r: True, tol=5e-4)
 
 
+def test_moe_expert_tensor_parallel_matches_single_process():
+    """Experts sliced over the expert-tensor-parallel group (= the TP ranks), tokens sequence parallel."""
+    ov = {"moe_aux_loss_coeff": 0.0}
+    ref = _single("tiny-qwen3-moe", 3, ov)
+    res = run_distributed(_run, 2, "tiny-qwen3-moe", {"tp": 2, "etp": 2}, 3, ov)
+    _check(ref, res, lambda r: True, tol=5e-4)
+
+
 def _run_cp(rank, world, comm):
     from loongforge_b200.parallel import context_parallel as CP
 
