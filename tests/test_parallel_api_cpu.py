@@ -99,3 +99,38 @@ def test_fsdp2_wrapping_shards_and_matches_dp_average():
     res = run_distributed(_fsdp, 2)
     for local_rows, rows, err, n in res:
         assert local_rows == rows // 2 and err < 1e-5 and n > 10
+
+
+def _hetero(rank, world):
+    import torch.distributed as dist
+    from loongforge_b200.runtime.hetero_dp import FullHeteroEncoderRunner, owner_of, rounds
+
+    torch.manual_seed(0)
+    enc = torch.nn.Linear(6, 4)
+    inputs = [torch.randn(3 + i, 6) for i in range(5)]  # 5 micro-batches, identical on both ranks
+    calls = []
+
+    def encode(x):
+        calls.append(x.shape[0])
+        return enc(x)
+
+    runner = FullHeteroEncoderRunner(dist.group.WORLD, encode)
+    embs = runner.encode_all(inputs)
+    # the "language model": both ranks compute the same loss; only rank 0 contributes its gradient
+    loss = sum((e * (i + 1)).sum() for i, e in enumerate(embs))
+    loss.backward()
+    runner.backward(contributes=(rank == 0))
+    g = enc.weight.grad.clone()
+    dist.all_reduce(g)  # owners hold disjoint parts of the encoder gradient: DP all-reduce completes it
+    ref = torch.nn.Linear(6, 4)
+    ref.load_state_dict(enc.state_dict())
+    sum((ref(x) * (i + 1)).sum() for i, x in enumerate(inputs)).backward()
+    assert owner_of(3, 2) == 1 and rounds(5, 2) == 3
+    return calls, float((g - ref.weight.grad).abs().max()), [tuple(e.shape) for e in embs]
+
+
+def test_full_hetero_encoder_runner():
+    res = run_distributed(_hetero, 2)
+    assert res[0][0] == [3, 5, 7] and res[1][0] == [4, 6]  # each rank encoded only its own micro-batches
+    for calls, err, shapes in res:
+        assert err < 1e-5 and shapes == [(3, 4), (4, 4), (5, 4), (6, 4), (7, 4)]
