@@ -23,18 +23,31 @@ REPO_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__fi
 CONFIG_DIR = os.path.join(REPO_ROOT, "configs", "models")
 
 # model name -> yaml path relative to configs/models (names follow the reference's --model-name values)
+def _scan_model_yaml() -> Dict[str, str]:
+    """Every ``configs/models/<dir>/<file>.yaml`` whose first line is ``# <model-name> (...)`` registers that name."""
+    out: Dict[str, str] = {}
+    if not os.path.isdir(CONFIG_DIR):
+        return out
+    for d in sorted(os.listdir(CONFIG_DIR)):
+        sub = os.path.join(CONFIG_DIR, d)
+        if not os.path.isdir(sub):
+            continue
+        for f in sorted(os.listdir(sub)):
+            if f.endswith(".yaml"):
+                with open(os.path.join(sub, f)) as fh:
+                    first = fh.readline()
+                if first.startswith("# ") and "(" in first:
+                    out[first[2:first.index("(")].strip().lower()] = f"{d}/{f}"
+    return out
+
+
 MODEL_YAML = {
     "llama3-8b": "llama3/llama3_8b.yaml",
-    "llama3-70b": "llama3/llama3_70b.yaml",
-    "llama2-7b": "llama2/llama2_7b.yaml",
     "qwen2.5-7b": "qwen2.5/qwen2_5_7b.yaml",
-    "qwen3-8b": "qwen3/qwen3_8b.yaml",
-    "qwen3-14b": "qwen3/qwen3_14b.yaml",
     "qwen3-30b-a3b": "qwen3/qwen3_30b_a3b.yaml",
-    "deepseek-v2-lite": "deepseek2/deepseek_v2_lite.yaml",
-    "deepseek-v3": "deepseek3/deepseek_v3.yaml",
     "deepseek-v3.2": "deepseek3/deepseek_v3_2.yaml",
     "qwen2.5-vl-7b": "qwen2.5vl/qwen2_5_vl_7b.yaml",
+    **_scan_model_yaml(),
 }
 
 _YAML_ALIASES = {"norm_epsilon": "layernorm_epsilon", "num_experts": "num_moe_experts",

@@ -881,10 +881,7 @@ int attn_fwd(const AttnArgs& a, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
-#define LF_DBG(msg) do { if (getenv("LF_DEBUG")) { fprintf(stderr, "[lf::attn_bwd] %s\n", msg); fflush(stderr); } } while (0)
-
 int attn_bwd(const AttnArgs& a, cudaStream_t stream) {
-  LF_DBG("enter");
   if (a.T == 0) return 0;
   if (a.Hq % a.Hkv) return -2;
   const int R = a.Hq / a.Hkv;
@@ -900,7 +897,6 @@ int attn_bwd(const AttnArgs& a, cudaStream_t stream) {
   if ((rc = make_map_kv(&tv64, a.v, a.T, a.Hkv, a.v_ts, a.v_hs, 64))) return rc;
   // dO is [T, Hq, 128]: group stride R * head stride
   if ((rc = make_map_q(&tdo, a.dout, a.T, a.Hkv, R, a.do_ts, a.do_hs * R, a.do_hs))) return rc;
-  LF_DBG("maps encoded");
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BkvSmem::BYTES) !=
@@ -910,16 +906,13 @@ int attn_bwd(const AttnArgs& a, cudaStream_t stream) {
       return -4;
     attr = true;
   }
-  LF_DBG("attributes set");
   const AttnParams p = make_params(a);
   const long long warps = static_cast<long long>(a.T) * a.Hq;
   attn_delta_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(a.dout), static_cast<const __nv_bfloat16*>(a.o), a.delta, a.T, a.Hq, a.do_ts,
       a.do_hs, a.o_ts, a.o_hs);
-  LF_DBG("delta launched");
   dim3 grid_kv(2 * max_blocks(a), a.Hkv);
   attn_bwd_dkdv_kernel<<<grid_kv, AT_BWD_THREADS, BkvSmem::BYTES, stream>>>(tq, tk64, tv64, tdo, p);
-  LF_DBG("dkdv launched");
   dim3 grid_q(max_blocks(a), a.Hq);
   attn_bwd_dq_kernel<<<grid_q, AT_BWD_THREADS, BqSmem::BYTES, stream>>>(tq, tk, tv, tdo, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
