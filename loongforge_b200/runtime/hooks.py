@@ -1,0 +1,141 @@
+"""Per-step hooks of the training loop, built from the command-line flags: EMA (``--ema-decay``), profiler
+(``--profile --profile-step-start/end --profile-ranks``), allocator history (``--record-memory-history``), tensor
+inspector (``--enable-log-tensor --log-tensor-name-pattern``), scalar sinks (``--tensorboard-dir --wandb-project``),
+manual garbage collection (``--manual-gc --manual-gc-interval``), checkpoint retention and exit decisions
+(``--exit-interval --exit-duration-in-mins``, SIGTERM). The reference interleaves the same features in its train loop
+(loongforge/train/training_utils.py:2431-2975)."""
+from __future__ import annotations
+
+import gc
+from typing import List, Optional
+
+import torch.distributed as dist
+
+
+class TrainHook:
+    def on_step_end(self, trainer, metrics, elapsed_ms) -> Optional[str]:
+        """Return a non-empty reason string to request checkpoint-and-exit."""
+        return None
+
+    def on_train_end(self, trainer) -> None:
+        pass
+
+
+class EMAHook(TrainHook):
+    def __init__(self, trainer, decay: float):
+        from .ema import ModelEMA
+        named = [(f"{i}.{n}", p) for i, m in enumerate(trainer.models) for n, p in m.named_parameters()]
+        self.ema = ModelEMA(named, decay)
+
+    def on_step_end(self, trainer, metrics, elapsed_ms):
+        self.ema.update()
+
+    def on_train_end(self, trainer):
+        if trainer.tcfg.save:
+            rank = dist.get_rank() if dist.is_initialized() else 0
+            self.ema.save(trainer.tcfg.save, trainer.iteration, f"_rank{rank:05d}")
+
+
+class ProfilerHook(TrainHook):
+    def __init__(self, out_dir, start, end, ranks, rank):
+        from .profiling import StepProfiler
+        self.prof = StepProfiler(out_dir, start, end, ranks, rank)
+
+    def on_step_end(self, trainer, metrics, elapsed_ms):
+        self.prof.step(trainer.iteration)
+
+
+class MemoryHistoryHook(TrainHook):
+    def __init__(self, out_dir, rank, every: int = 0):
+        from .profiling import MemoryHistory
+        self.mh, self.every = MemoryHistory(out_dir, rank), every
+
+    def on_step_end(self, trainer, metrics, elapsed_ms):
+        if self.every and trainer.iteration % self.every == 0:
+            self.mh.dump(f"it{trainer.iteration}")
+
+
+class TensorInspectorHook(TrainHook):
+    def __init__(self, trainer, patterns, out_path, rank):
+        from .profiling import TensorInspector
+        self.insp = [TensorInspector(m, patterns, out_path, rank=rank) for m in trainer.models]
+
+    def on_step_end(self, trainer, metrics, elapsed_ms):
+        for i in self.insp:
+            i.step()
+
+    def on_train_end(self, trainer):
+        for i in self.insp:
+            i.remove()
+
+
+class ScalarHook(TrainHook):
+    def __init__(self, out_dir, wandb_project, enabled):
+        from .metrics_writers import ScalarWriter
+        self.w = ScalarWriter(out_dir, wandb_project=wandb_project, enabled=enabled)
+
+    def on_step_end(self, trainer, metrics, elapsed_ms):
+        sc = {k: v for k, v in metrics.items() if isinstance(v, (int, float))}
+        sc["iteration-time-ms"] = elapsed_ms
+        self.w.add_scalars(sc, trainer.iteration)
+
+    def on_train_end(self, trainer):
+        self.w.close()
+
+
+class ManualGCHook(TrainHook):
+    def __init__(self, interval: int):
+        self.interval = max(int(interval), 1)
+        gc.disable()
+
+    def on_step_end(self, trainer, metrics, elapsed_ms):
+        if trainer.iteration % self.interval == 0:
+            gc.collect()
+
+    def on_train_end(self, trainer):
+        gc.enable()
+
+
+class ExitHook(TrainHook):
+    def __init__(self, duration_min, interval, signals: bool):
+        from ..ckpt.async_save import ExitDecider
+        self.d = ExitDecider(duration_min, interval, install_signal_handlers=signals)
+
+    def on_step_end(self, trainer, metrics, elapsed_ms):
+        return self.d.should_exit(trainer.iteration)
+
+
+class RetentionHook(TrainHook):
+    def __init__(self, keep_last: int, retain_interval):
+        self.keep, self.retain = keep_last, retain_interval
+
+    def on_step_end(self, trainer, metrics, elapsed_ms):
+        t = trainer.tcfg
+        is_main = (not dist.is_initialized()) or dist.get_rank() == 0
+        if is_main and t.save and t.save_interval and trainer.iteration % t.save_interval == 0:
+            from ..ckpt.async_save import apply_retention
+            apply_retention(t.save, self.keep, self.retain)
+
+
+def build_hooks(args, trainer) -> List[TrainHook]:
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    out = getattr(args, "tensorboard_dir", None) or (trainer.tcfg.save or ".")
+    hooks: List[TrainHook] = []
+    if getattr(args, "ema_decay", None):
+        hooks.append(EMAHook(trainer, args.ema_decay))
+    if getattr(args, "profile", False) or getattr(args, "use_pytorch_profiler", False):
+        hooks.append(ProfilerHook(out, args.profile_step_start, args.profile_step_end, args.profile_ranks, rank))
+    if getattr(args, "record_memory_history", False):
+        hooks.append(MemoryHistoryHook(out, rank))
+    if getattr(args, "enable_log_tensor", False):
+        pats = args.log_tensor_name_pattern or ["*"]
+        pats = [pats] if isinstance(pats, str) else list(pats)
+        hooks.append(TensorInspectorHook(trainer, pats, f"{out}/tensors_rank{rank}.jsonl", rank))
+    if getattr(args, "tensorboard_dir", None) or getattr(args, "wandb_project", None):
+        hooks.append(ScalarHook(out, getattr(args, "wandb_project", None), enabled=(rank == world - 1)))
+    if getattr(args, "manual_gc", False):
+        hooks.append(ManualGCHook(getattr(args, "manual_gc_interval", 0) or 1))
+    if getattr(args, "exit_interval", None) or getattr(args, "exit_duration_in_mins", None):
+        hooks.append(ExitHook(getattr(args, "exit_duration_in_mins", None), getattr(args, "exit_interval", None), False))
+    return hooks

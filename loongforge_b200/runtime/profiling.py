@@ -96,7 +96,8 @@ class TensorInspector:
         self.handles = []
         self.records: List[dict] = []
         for name, mod in model.named_modules():
-            if name and any(fnmatch.fnmatch(name, p) for p in patterns):
+            # wrappers (DDP, pipeline chunks) prefix the qualified name: a pattern also matches as a suffix
+            if name and any(fnmatch.fnmatch(name, p) or fnmatch.fnmatch(name, "*." + p) for p in patterns):
                 self.handles.append(mod.register_forward_hook(self._hook(name, "fwd")))
                 if backward:
                     self.handles.append(mod.register_full_backward_hook(self._bhook(name)))

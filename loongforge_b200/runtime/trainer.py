@@ -316,6 +316,16 @@ class Trainer:
                     (on_log or print)(line)
             if t.save and t.save_interval and self.iteration % t.save_interval == 0:
                 self.save_checkpoint(t.save)
+            stop = None
+            for h in getattr(self, "hooks", ()):
+                stop = h.on_step_end(self, metrics, elapsed_ms) or stop
+            if stop:
+                # a hook asked for checkpoint-and-exit (signal, time limit, exit interval)
+                if t.save:
+                    self.save_checkpoint(t.save)
+                break
+        for h in getattr(self, "hooks", ()):
+            h.on_train_end(self)
         return history
 
     def _now(self):

@@ -44,6 +44,8 @@ def main(argv: Optional[List[str]] = None) -> int:
         data_iter = synthetic_batch_iterator(model_cfg.vocab_size, train_cfg.seq_length, train_cfg.micro_batch_size,
                                              dp_rank=st.dp_rank, dp_size=st.dp_size, seed=train_cfg.seed,
                                              start_sample=trainer.consumed_samples)
+    from .runtime.hooks import build_hooks
+    trainer.hooks = build_hooks(args, trainer)
     trainer.train(data_iter)
     if train_cfg.save:
         trainer.save_checkpoint(train_cfg.save)

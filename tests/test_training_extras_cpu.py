@@ -104,3 +104,26 @@ def test_async_local_checkpoints_and_retention(tmp_path):
     assert ex.should_exit(10) == "interval" and ex.should_exit(11) is None
     ex._on_signal(15, None)
     assert ex.should_exit(11) == "signal"
+
+
+def test_cli_hooks_end_to_end(tmp_path):
+    """Flags -> hooks: EMA checkpoint, scalar file, profiler trace, tensor log, exit-interval checkpoint."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "run"
+    cmd = [sys.executable, "-m", "loongforge_b200.train", "--model-name", "tiny-llama", "--seq-length", "64",
+           "--micro-batch-size", "2", "--global-batch-size", "4", "--train-iters", "6", "--lr", "1e-3", "--ema-decay", "0.99",
+           "--tensorboard-dir", str(out), "--profile", "--profile-step-start", "2", "--profile-step-end", "4",
+           "--enable-log-tensor", "--log-tensor-name-pattern", "decoder.layers.0.mlp", "--manual-gc",
+           "--exit-interval", "5", "--save", str(out / "ck")]
+    p = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=600,
+                       env=dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=root))
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert "iteration        5/" in p.stdout and "iteration        6/" not in p.stdout  # left at the exit interval
+    assert (out / "ck" / "iter_0000005").is_dir() and (out / "ck" / "save_ema" / "iter_0000005").is_dir()
+    assert len(open(out / "scalars.jsonl").readlines()) == 5
+    assert (out / "trace_rank0_it2-4.json").is_file()
+    recs = [json.loads(x) for x in open(out / "tensors_rank0.jsonl")]
+    assert recs and all(r["module"].endswith("decoder.layers.0.mlp") for r in recs)
