@@ -187,8 +187,10 @@ def _gather_obj(obj):
     return out
 
 
-def build_save_state(trainer) -> Dict[str, object]:
+def build_save_state(trainer, stage: bool = False) -> Dict[str, object]:
+    """``stage``: every tensor is a private host copy, so the state stays valid while training goes on (asynchronous save)."""
     st = trainer.st
+    own = (lambda t: t.to("cpu", copy=True)) if stage else (lambda t: t.contiguous())
     rank = dist.get_rank()
     tp, tpr = st.dims.tp, st.tp_rank
     # ---- who owns what (model replicas: the first data-parallel rank writes)
@@ -205,7 +207,7 @@ def build_save_state(trainer) -> Dict[str, object]:
         if not writer or (dup and (st.etp_rank if is_expert else tpr) != 0):
             continue
         data = p.detach()
-        local_tensors[key] = [(off, data[sl].contiguous()) for off, sl in pieces]
+        local_tensors[key] = [(off, own(data[sl])) for off, sl in pieces]
         local_desc.append((key, gshape, [(off, list(t.shape)) for off, t in local_tensors[key]]))
     # ---- optimizer: flat chunks per (param, model-parallel coordinate)
     opt_local: Dict[str, List[Tuple[List[int], torch.Tensor]]] = {}
@@ -229,7 +231,7 @@ def build_save_state(trainer) -> Dict[str, object]:
         for piece in pieces:
             for kind in ("master", "exp_avg", "exp_avg_sq"):
                 k = f"optimizer.state.{kind}.{key_of.get(name, name)}.{coord}"
-                t = piece[kind].detach().contiguous()
+                t = own(piece[kind].detach())
                 opt_local.setdefault(k, []).append(([piece["offset"]], t))
                 gshapes[k] = [piece["param_numel"]]
     for k, lst in opt_local.items():
@@ -293,25 +295,60 @@ def common_state(trainer) -> dict:
 
 
 # ----------------------------------------------------------------------------- save / load (torch_dist)
-def save_checkpoint(root: str, trainer, *, fmt: Optional[str] = None, release: bool = False) -> str:
+def finalize_async_save(trainer) -> None:
+    """Waits for the checkpoint write started by an asynchronous save and only then publishes it in the tracker
+    file, so that a crash during the write never leaves the tracker pointing at a partial checkpoint."""
+    pending = getattr(trainer, "_pending_save", None)
+    if pending is None:
+        return
+    fut, root, iteration, release = pending
+    fut.result()
+    trainer._pending_save = None
+    if dist.get_world_size() > 1:
+        dist.barrier()
+    if dist.get_rank() == 0:
+        write_tracker(root, iteration, release)
+    if dist.get_world_size() > 1:
+        dist.barrier()
+
+
+def save_checkpoint(root: str, trainer, *, fmt: Optional[str] = None, release: bool = False,
+                    async_save: Optional[bool] = None) -> str:
     fmt = fmt or trainer.tcfg.ckpt_format
     if fmt == "torch":
         return save_legacy(root, trainer, release=release)
     _ensure_pg()
+    finalize_async_save(trainer)  # at most one write in flight
+    if async_save is None:
+        async_save = bool(getattr(trainer.tcfg, "async_save", False))
     d = iteration_dir(root, trainer.iteration, release)
     rank = dist.get_rank()
     if rank == 0:
         os.makedirs(d, exist_ok=True)
     if dist.get_world_size() > 1:
         dist.barrier()
-    state = build_save_state(trainer)
-    dcp.save(state, checkpoint_id=d)
+    state = build_save_state(trainer, stage=async_save)
+    fut = None
+    if async_save:
+        # the write (and its metadata collectives) runs on a worker thread over a process group of its own, so it
+        # cannot interleave with the training collectives; the tensors were copied to host memory above
+        import concurrent.futures
+        if getattr(trainer, "_ckpt_pg", None) is None:
+            trainer._ckpt_pg = dist.new_group(backend="gloo")
+            trainer._ckpt_pool = concurrent.futures.ThreadPoolExecutor(max_workers=1)
+        fut = trainer._ckpt_pool.submit(dcp.save, state, checkpoint_id=d, process_group=trainer._ckpt_pg)
+    else:
+        dcp.save(state, checkpoint_id=d)
     if rank == 0:
         torch.save(common_state(trainer), os.path.join(d, "common.pt"))
         with open(os.path.join(d, "metadata.json"), "w") as f:
             json.dump({"sharded_backend": "torch_dist", "sharded_backend_version": 1, "common_backend": "torch",
                        "common_backend_version": 1}, f)
-        write_tracker(root, trainer.iteration, release)
+        if fut is None:
+            write_tracker(root, trainer.iteration, release)
+    if fut is not None:
+        trainer._pending_save = (fut, root, trainer.iteration, release)
+        return d
     if dist.get_world_size() > 1:
         dist.barrier()
     return d

@@ -172,6 +172,7 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
         adam_beta2=args.adam_beta2, adam_eps=args.adam_eps, clip_grad=args.clip_grad, bf16=args.bf16, seed=args.seed,
         log_interval=args.log_interval, save=args.save, load=args.load, save_interval=args.save_interval,
         ckpt_format="torch_dist" if args.ckpt_format in ("torch_dist", "torch_dcp") else args.ckpt_format,
+        async_save=bool(getattr(args, "async_save", False)),
         use_distributed_optimizer=args.use_distributed_optimizer, overlap_grad_reduce=args.overlap_grad_reduce,
         overlap_param_gather=args.overlap_param_gather, exp_avg_dtype=dt[args.exp_avg_dtype],
         exp_avg_sq_dtype=dt[args.exp_avg_sq_dtype], calculate_per_token_loss=args.calculate_per_token_loss,

@@ -65,6 +65,7 @@ class TrainConfig:
     log_throughput: bool = True
     check_for_nan_in_loss: bool = True
     exit_on_nan: bool = False
+    async_save: bool = False
 
 
 def _device_for_rank() -> torch.device:
@@ -326,6 +327,9 @@ class Trainer:
                 break
         for h in getattr(self, "hooks", ()):
             h.on_train_end(self)
+        if getattr(self, "_pending_save", None) is not None:
+            from ..ckpt import checkpointing
+            checkpointing.finalize_async_save(self)
         return history
 
     def _now(self):

@@ -154,3 +154,33 @@ def test_master_remainder_is_exact_fp32():
         OF.adam_step(ref, g, m1, v1, None, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
         OF.adam_step_remainder(w, lo, g, m2, v2, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
     assert torch.equal(OF.master_join(w, lo), ref)
+
+
+def _async_worker(rank, world, tmp):
+    from loongforge_b200.ckpt import checkpointing
+    from loongforge_b200.data.synthetic import synthetic_batch_iterator
+    from loongforge_b200.parallel import state as ps
+
+    tr = _make_trainer(world, async_save=True)
+    st = tr.st
+    it = synthetic_batch_iterator(32000, 128, 2, dp_rank=st.dp_rank, dp_size=st.dp_size, seed=7, pin_memory=False)
+    for _ in range(3):
+        tr.train_step(it)
+    tr.save_checkpoint(tmp)
+    tracker_before = os.path.exists(os.path.join(tmp, "latest_checkpointed_iteration.txt"))
+    nxt = tr.train_step(it)["lm loss"]  # training continues while the write is in flight
+    checkpointing.finalize_async_save(tr)
+    tracker_after = open(os.path.join(tmp, "latest_checkpointed_iteration.txt")).read().strip()
+    ps.destroy_model_parallel()
+    tr2 = _make_trainer(world)
+    assert tr2.load_checkpoint(tmp) == 3
+    it2 = synthetic_batch_iterator(32000, 128, 2, dp_rank=st.dp_rank, dp_size=st.dp_size, seed=7, pin_memory=False,
+                                   start_sample=tr2.consumed_samples)
+    return tracker_before, tracker_after, nxt, tr2.train_step(it2)["lm loss"]
+
+
+def test_async_save_publishes_tracker_after_the_write():
+    with tempfile.TemporaryDirectory() as tmp:
+        for before, after, nxt, again in run_distributed(_async_worker, 2, tmp):
+            assert before is False and after == "3"
+            assert nxt == again  # the checkpoint holds the state at save time, not the later step's
