@@ -69,7 +69,9 @@ def _add_moe_args(p):
     g.add_argument("--moe-z-loss-coeff", type=float, default=None)
     g.add_argument("--moe-grouped-gemm", action="store_true")
     g.add_argument("--moe-permute-fusion", action="store_true")
-    g.add_argument("--moe-token-dispatcher-type", type=str, default="alltoall", choices=["alltoall", "allgather", "flex"])
+    g.add_argument("--moe-token-dispatcher-type", type=str, default="alltoall",
+                   choices=["alltoall", "allgather", "flex", "peer"],
+                   help="peer: dispatch / combine kernels over NVLink peer memory (CUDA only)")
     g.add_argument("--moe-enable-deepep", action="store_true")
     g.add_argument("--overlap-moe-expert-parallel-comm", action="store_true")
     g.add_argument("--delay-wgrad-compute", action="store_true")

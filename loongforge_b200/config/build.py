@@ -120,7 +120,8 @@ _ARG_TO_CFG = {
     "moe_router_topk_scaling_factor": "moe_router_topk_scaling_factor",
     "moe_router_load_balancing_type": "moe_router_load_balancing_type", "moe_aux_loss_coeff": "moe_aux_loss_coeff",
     "moe_z_loss_coeff": "moe_z_loss_coeff", "mtp_num_layers": "mtp_num_layers",
-    "mtp_loss_scaling_factor": "mtp_loss_scaling_factor", "recompute_granularity": "recompute_granularity",
+    "mtp_loss_scaling_factor": "mtp_loss_scaling_factor", "moe_token_dispatcher_type": "moe_token_dispatcher_type",
+    "recompute_granularity": "recompute_granularity",
     "recompute_method": "recompute_method", "recompute_num_layers": "recompute_num_layers",
 }
 _FLAG_TO_CFG = {"swiglu": ("activation", "swiglu"), "add_qkv_bias": ("add_qkv_bias", True),
