@@ -40,6 +40,10 @@ def _sources() -> tuple[list[str], list[str]]:
         defs.append("-DLF_HAVE_ATTN")
     if os.path.exists(os.path.join(_CSRC, "peer_gemm.cu")):
         defs.append("-DLF_HAVE_PEER")
+    if os.path.exists(os.path.join(_CSRC, "peer_optim.cu")):
+        defs.append("-DLF_HAVE_PEER_OPTIM")
+    if os.path.exists(os.path.join(_CSRC, "fp8_sm100.cu")):
+        defs.append("-DLF_HAVE_FP8")
     if os.path.exists(os.path.join(_CSRC, "moe_peer.cu")):
         defs.append("-DLF_HAVE_MOE_PEER")
     if os.path.exists(os.path.join(_CSRC, "grouped_gemm_sm100.cu")):

@@ -6,6 +6,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <algorithm>
+#include <cmath>
 #include <cstdint>
 #include "elementwise.h"
 #include "gemm_sm100.h"
@@ -20,6 +21,12 @@
 #endif
 #ifdef LF_HAVE_MOE_PEER
 #include "moe_peer.h"
+#endif
+#ifdef LF_HAVE_FP8
+#include "fp8_sm100.h"
+#endif
+#ifdef LF_HAVE_PEER_OPTIM
+#include "peer_optim.h"
 #endif
 
 namespace {
@@ -695,6 +702,110 @@ void moe_wait(std::vector<int64_t> buf, std::vector<int64_t> scal, std::vector<i
 }
 #endif  // LF_HAVE_MOE_PEER
 
+#ifdef LF_HAVE_FP8
+// ------------------------------------------------------------------ FP8 block quantisers + blockwise GEMM
+std::vector<at::Tensor> quant_1x128(const at::Tensor& x, bool pow2) {
+  check_bf16_cuda(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && x.size(1) % 128 == 0, "quant_1x128 wants contiguous [M, 128k]");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor q = at::empty(x.sizes(), x.options().dtype(at::kFloat8_e4m3fn));
+  at::Tensor s = at::empty({x.size(0), x.size(1) / 128}, x.options().dtype(at::kFloat));
+  TORCH_CHECK(lf::quant_1x128(x.data_ptr(), q.data_ptr(), s.data_ptr<float>(), x.size(0), static_cast<int>(x.size(1)),
+                              pow2, cur_stream()) == 0);
+  ++g_launches;
+  return {q, s};
+}
+
+std::vector<at::Tensor> quant_128x128(const at::Tensor& w, bool pow2) {
+  check_bf16_cuda(w, "w");
+  TORCH_CHECK(w.dim() == 2 && w.is_contiguous() && w.size(0) % 128 == 0 && w.size(1) % 128 == 0);
+  c10::cuda::CUDAGuard guard(w.device());
+  at::Tensor q = at::empty(w.sizes(), w.options().dtype(at::kFloat8_e4m3fn));
+  at::Tensor s = at::empty({w.size(0) / 128, w.size(1) / 128}, w.options().dtype(at::kFloat));
+  TORCH_CHECK(lf::quant_128x128(w.data_ptr(), q.data_ptr(), s.data_ptr<float>(), static_cast<int>(w.size(0)),
+                                static_cast<int>(w.size(1)), pow2, cur_stream()) == 0);
+  ++g_launches;
+  return {q, s};
+}
+
+at::Tensor gemm_fp8_blockwise(const at::Tensor& aq, const at::Tensor& sa, const at::Tensor& bq, const at::Tensor& sb,
+                              const at::Tensor& status) {
+  TORCH_CHECK(aq.is_cuda() && aq.scalar_type() == at::kFloat8_e4m3fn && bq.scalar_type() == at::kFloat8_e4m3fn);
+  TORCH_CHECK(aq.dim() == 2 && bq.dim() == 2 && aq.is_contiguous() && bq.is_contiguous() && aq.size(1) == bq.size(1));
+  TORCH_CHECK(sa.scalar_type() == at::kFloat && sb.scalar_type() == at::kFloat && sa.is_contiguous() && sb.is_contiguous());
+  const int64_t M = aq.size(0), K = aq.size(1), N = bq.size(0);
+  TORCH_CHECK(sa.size(0) == M && sa.size(1) == K / 128 && sb.size(0) == N / 128 && sb.size(1) == K / 128);
+  c10::cuda::CUDAGuard guard(aq.device());
+  at::Tensor d = at::empty({M, N}, aq.options().dtype(at::kBFloat16));
+  const int rc = lf::gemm_fp8_blockwise(aq.data_ptr(), sa.data_ptr<float>(), bq.data_ptr(), sb.data_ptr<float>(),
+                                        d.data_ptr(), N, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K),
+                                        status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "gemm_fp8_blockwise failed with code ", rc);
+  ++g_launches;
+  return d;
+}
+#endif  // LF_HAVE_FP8
+
+#ifdef LF_HAVE_PEER_OPTIM
+// ------------------------------------------------------------------ data-parallel optimizer over peer memory
+static lf::PeerTable peer_table(const std::vector<int64_t>& ptrs, int64_t rank) {
+  TORCH_CHECK(!ptrs.empty() && static_cast<int>(ptrs.size()) <= lf::kOptMaxPeers);
+  lf::PeerTable t;
+  for (size_t r = 0; r < ptrs.size(); ++r) t.ptr[r] = reinterpret_cast<void*>(ptrs[r]);
+  t.world = static_cast<int>(ptrs.size());
+  t.rank = static_cast<int>(rank);
+  return t;
+}
+
+// grads: base pointers of the symmetric fp32 gradient buffer on every DP rank. The reduced shard replaces
+// [start, start + n) of this rank's buffer; `sumsq` (fp32[1]) receives += its squared norm when given.
+void grad_pull_reduce(std::vector<int64_t> grads, int64_t rank, int64_t start, int64_t n, double scale,
+                      c10::optional<at::Tensor> sumsq) {
+  float* ss = nullptr;
+  if (sumsq.has_value()) {
+    TORCH_CHECK(sumsq->is_cuda() && sumsq->scalar_type() == at::kFloat);
+    ss = sumsq->data_ptr<float>();
+  }
+  // the kernel needs a valid accumulator address: without one the partial goes to a scratch word
+  static thread_local at::Tensor scratch;
+  if (ss == nullptr) {
+    if (!scratch.defined()) scratch = at::zeros({1}, at::TensorOptions().dtype(at::kFloat).device(at::kCUDA));
+    ss = scratch.data_ptr<float>();
+  }
+  TORCH_CHECK(lf::grad_pull_reduce(peer_table(grads, rank), start, n, static_cast<float>(scale), ss, cur_stream()) == 0,
+              "grad_pull_reduce: start and n must be multiples of 4");
+  ++g_launches;
+}
+
+void adam_push(std::vector<int64_t> params, int64_t rank, int64_t start, at::Tensor lo, const at::Tensor& grad,
+               at::Tensor m, at::Tensor v, double lr, double beta1, double beta2, double eps, double wd, int64_t step,
+               double grad_scale) {
+  TORCH_CHECK(lo.is_cuda() && lo.scalar_type() == at::kShort && grad.scalar_type() == at::kFloat &&
+              m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
+  TORCH_CHECK(lo.is_contiguous() && grad.is_contiguous() && m.is_contiguous() && v.is_contiguous());
+  const int64_t n = lo.numel();
+  TORCH_CHECK(grad.numel() == n && m.numel() == n && v.numel() == n);
+  const float bc1 = 1.f - static_cast<float>(std::pow(beta1, static_cast<double>(step)));
+  const float bc2 = 1.f - static_cast<float>(std::pow(beta2, static_cast<double>(step)));
+  TORCH_CHECK(lf::adam_push(peer_table(params, rank), start, n, lo.data_ptr<int16_t>(), grad.data_ptr<float>(),
+                            m.data_ptr<float>(), v.data_ptr<float>(), static_cast<float>(lr), static_cast<float>(beta1),
+                            static_cast<float>(beta2), static_cast<float>(eps), static_cast<float>(wd), bc1, bc2,
+                            static_cast<float>(grad_scale), cur_stream()) == 0,
+              "adam_push: start and n must be even");
+  ++g_launches;
+}
+
+void peer_signal(std::vector<int64_t> flags, int64_t rank, int64_t epoch) {
+  TORCH_CHECK(lf::peer_signal(peer_table(flags, rank), static_cast<int>(epoch), cur_stream()) == 0);
+  ++g_launches;
+}
+
+void peer_wait(std::vector<int64_t> flags, int64_t rank, int64_t epoch, const at::Tensor& status) {
+  TORCH_CHECK(lf::peer_wait(peer_table(flags, rank), static_cast<int>(epoch), status.data_ptr<int>(), cur_stream()) == 0);
+  ++g_launches;
+}
+#endif  // LF_HAVE_PEER_OPTIM
+
 int64_t launch_count() { return g_launches; }
 void reset_launch_count() { g_launches = 0; }
 
@@ -730,6 +841,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_pull", &moe_pull);
   m.def("moe_signal", &moe_signal);
   m.def("moe_wait", &moe_wait);
+#endif
+#ifdef LF_HAVE_FP8
+  m.def("quant_1x128", &quant_1x128);
+  m.def("quant_128x128", &quant_128x128);
+  m.def("gemm_fp8_blockwise", &gemm_fp8_blockwise);
+#endif
+#ifdef LF_HAVE_PEER_OPTIM
+  m.def("grad_pull_reduce", &grad_pull_reduce);
+  m.def("adam_push", &adam_push);
+  m.def("peer_signal", &peer_signal);
+  m.def("peer_wait", &peer_wait);
 #endif
   m.def("router_fwd", &router_fwd);
   m.def("router_bwd", &router_bwd);

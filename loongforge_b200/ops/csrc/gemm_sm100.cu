@@ -338,6 +338,21 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* ptr, long long rows, long lo
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
+int make_tmap_u8_2d(CUtensorMap* map, const void* ptr, long long rows, long long cols, long long ld, int box_rows,
+                    int box_cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld & 15) != 0) return -2;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
 static int g_num_sms = 0;
 
 template <int BN, bool A_MN, bool B_MN>

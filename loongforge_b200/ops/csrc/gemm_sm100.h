@@ -29,5 +29,8 @@ int gemm_bf16(const GemmArgs& args, cudaStream_t stream);
 
 int make_tmap_bf16_2d(CUtensorMap* map, const void* ptr, long long rows, long long cols, long long ld,
                       int box_rows, int box_cols);
+// Same for 1-byte elements (fp8): `cols`, `ld` and `box_cols` in bytes; box_cols = 128 (one swizzle row).
+int make_tmap_u8_2d(CUtensorMap* map, const void* ptr, long long rows, long long cols, long long ld, int box_rows,
+                    int box_cols);
 
 }  // namespace lf

@@ -49,8 +49,17 @@ def dequantize_128x128(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
     return (q.float().view(N // 128, 128, K // 128, 128) * s[:, None, :, None]).view(N, K)
 
 
+_NATIVE = {"on": False}
+
+
+def enable_native(flag: bool = True) -> None:
+    """Route CUDA bf16 inputs to the kernels of ``csrc/fp8_sm100.cu``. Off by default: until their numerics tests
+    have run on a GPU the PyTorch formulation stays the production path."""
+    _NATIVE["on"] = bool(flag)
+
+
 def _native(x: torch.Tensor) -> bool:
-    return x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
+    return _NATIVE["on"] and x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
 
 
 def quantize_1x128(x: torch.Tensor, pow2: bool = False, transpose: bool = False):

@@ -32,6 +32,9 @@ class DDPConfig:
     average_in_collective: bool = False
     check_for_nan_in_grad: bool = False
     align_elems: int = 128
+    # parameter / gradient buffers in symmetric (peer-mappable) memory and NO NCCL gradient reduce-scatter: the
+    # distributed optimizer then reduces by peer loads and all-gathers by peer stores inside its own kernels
+    peer_optimizer: bool = False
 
 
 @dataclasses.dataclass
@@ -88,8 +91,21 @@ class ParamAndGradBuffer:
                 close()
         close()
         self.numel = off
-        self.param_data = torch.zeros(self.numel, dtype=param_dtype, device=device)
-        self.grad_data = torch.zeros(self.numel, dtype=grad_dtype, device=device)
+        self.symmetric = None
+        if cfg.peer_optimizer and dp_size > 1 and torch.device(device).type == "cuda":
+            # one symmetric allocation: [params | grads | 2 x int[8] arrival flags]
+            from .fused_tp import _SymmetricBlock
+            pb = (self.numel * torch.empty(0, dtype=param_dtype).element_size() + 255) // 256 * 256
+            gb = (self.numel * torch.empty(0, dtype=grad_dtype).element_size() + 255) // 256 * 256
+            blk = _SymmetricBlock(pb + gb + 256, dp_group, device)
+            self.symmetric = {"block": blk, "param_off": 0, "grad_off": pb, "flag_off": pb + gb, "epoch": 0}
+            self.param_data = blk.local_view(0, self.numel * torch.empty(0, dtype=param_dtype).element_size(),
+                                             param_dtype, (self.numel,))
+            self.grad_data = blk.local_view(pb, self.numel * torch.empty(0, dtype=grad_dtype).element_size(),
+                                            grad_dtype, (self.numel,))
+        else:
+            self.param_data = torch.zeros(self.numel, dtype=param_dtype, device=device)
+            self.grad_data = torch.zeros(self.numel, dtype=grad_dtype, device=device)
         for p in self.params:
             s, e, _ = self.param_index[p]
             self.param_data[s:e].view(p.shape).copy_(p.data)
@@ -171,6 +187,9 @@ class DistributedDataParallel(nn.Module):
     def _start_bucket(self, buf: ParamAndGradBuffer, b: Bucket, async_op: bool = True):
         g = buf.grad_data[b.start:b.end]
         scale = buf.grad_scale
+        if buf.symmetric is not None:
+            b.handle = True  # reduced (and scaled) by the optimizer's pull kernel at step time
+            return
         if buf.dp_size == 1:
             if scale != 1.0:
                 g.mul_(scale)

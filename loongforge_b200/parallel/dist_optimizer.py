@@ -146,11 +146,55 @@ class DistributedOptimizer:
         return "all_reduce over WORLD is exact because every element is counted on exactly one rank"
 
     # ------------------------------------------------------------------ step
+    # ------------------------------------------------------------------ fused step over peer memory
+    def _peer_buffers(self):
+        return [sh for sh in self.shards if getattr(sh.buf, "symmetric", None) is not None]
+
+    def _peer_barrier(self, buf) -> None:
+        """All ranks of the buffer's DP group reach this point (device-side epoch flags, bounded wait)."""
+        from ..ops import _ext
+        sym = buf.symmetric
+        sym["epoch"] += 1
+        C = _ext.require()
+        flags = sym["block"].peer_ptrs(sym["flag_off"])
+        C.peer_signal(flags, buf.dp_rank, sym["epoch"])
+        C.peer_wait(flags, buf.dp_rank, sym["epoch"], _ext.status_tensor(buf.param_data.device))
+
+    def _peer_reduce_grads(self) -> None:
+        """Gradient reduce-scatter by peer loads (csrc/peer_optim.cu): after a barrier (every rank finished its
+        backward) each rank pulls and sums its shard of every bucket from all DP peers, scaled by 1/dp."""
+        from ..ops import _ext
+        C = _ext.require()
+        done = set()
+        for sh in self._peer_buffers():
+            if id(sh.buf) not in done:
+                self._peer_barrier(sh.buf)
+                done.add(id(sh.buf))
+            sym = sh.buf.symmetric
+            C.grad_pull_reduce(sym["block"].peer_ptrs(sym["grad_off"]), sh.buf.dp_rank, sh.start, sh.end - sh.start,
+                               sh.buf.grad_scale, None)
+
+    def _peer_adam_and_gather(self, sh, lo: int, hi: int, lr, wd, clip) -> None:
+        """AdamW on [lo, hi) of the shard + parameter all-gather by peer stores, one kernel."""
+        from ..ops import _ext
+        cfg = self.cfg
+        sym = sh.buf.symmetric
+        _ext.require().adam_push(sym["block"].peer_ptrs(sym["param_off"]), sh.buf.dp_rank, sh.start + lo,
+                                 sh.lo[lo:hi], sh.buf.grad_data[sh.start + lo:sh.start + hi], sh.exp_avg[lo:hi],
+                                 sh.exp_avg_sq[lo:hi], lr, cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps, wd,
+                                 self.step_count, clip)
+
+    def _peer_ok(self, sh) -> bool:
+        return (getattr(sh.buf, "symmetric", None) is not None and sh.remainder and self.sharded
+                and sh.buf.grad_data.dtype == torch.float32 and sh.exp_avg.dtype == torch.float32
+                and sh.exp_avg_sq.dtype == torch.float32)
+
     def step(self) -> tuple:
         """Finish grad sync, clip, Adam on the shards, refresh the bf16 parameters.
         Returns (update_successful, grad_norm, num_zeros)."""
         for m in self.models:
             m.finish_grad_sync()
+        self._peer_reduce_grads()
         cfg = self.cfg
         norm = self.grad_norm()
         norm_val = float(norm.item())
@@ -174,6 +218,9 @@ class DistributedOptimizer:
                 else:
                     runs.append([lo, hi, use_wd])
             for lo, hi, use_wd in runs:
+                if self._peer_ok(sh):
+                    self._peer_adam_and_gather(sh, lo, hi, lr, wd if use_wd else 0.0, clip)
+                    continue
                 if sh.remainder:
                     OF.adam_step_remainder(out[lo:hi], sh.lo[lo:hi], g[lo:hi], sh.exp_avg[lo:hi],
                                            sh.exp_avg_sq[lo:hi], lr=lr, beta1=cfg.adam_beta1, beta2=cfg.adam_beta2,
@@ -187,6 +234,11 @@ class DistributedOptimizer:
                 if out_arg is None:
                     out[lo:hi].copy_(sh.master[lo:hi])
         self._gather_params()
+        done = set()
+        for sh in self._peer_buffers():  # pushes landed everywhere; gradients may be zeroed for the next step
+            if id(sh.buf) not in done:
+                self._peer_barrier(sh.buf)
+                done.add(id(sh.buf))
         return True, norm_val, None
 
     def _gather_params(self):
@@ -194,7 +246,7 @@ class DistributedOptimizer:
             return
         for sh in self.shards:
             buf, b = sh.buf, sh.bucket
-            if buf.dp_size == 1:
+            if buf.dp_size == 1 or self._peer_ok(sh):
                 continue
             full = buf.param_data[b.start:b.end]
             mine = buf.param_data[sh.start:sh.end]

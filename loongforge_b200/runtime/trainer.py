@@ -66,6 +66,7 @@ class TrainConfig:
     check_for_nan_in_loss: bool = True
     exit_on_nan: bool = False
     async_save: bool = False
+    peer_optimizer: bool = False  # grad reduce-scatter / param all-gather inside the optimizer kernels (peer memory)
 
 
 def _device_for_rank() -> torch.device:
@@ -147,6 +148,7 @@ class Trainer:
             ddp_cfg = DDPConfig(grad_reduce_in_fp32=self.tcfg.grad_reduce_in_fp32,
                                 overlap_grad_reduce=self.tcfg.overlap_grad_reduce,
                                 use_distributed_optimizer=self.tcfg.use_distributed_optimizer,
+                                peer_optimizer=self.tcfg.peer_optimizer,
                                 bucket_size=self.tcfg.ddp_bucket_size or max(40_000_000, 1_000_000 * self.dp))
             # bucketing only helps the chunk whose backward runs last (reference: training_utils.py:987-988)
             chunks.append(DistributedDataParallel(module, ddp_cfg, disable_bucketing=v > 0))
