@@ -30,7 +30,29 @@ TOLERANCE = {"lm_loss": 0.02, "grad_norm": 0.02, "elapsed_time_ms": 0.05, "throu
 TIMING_KEYS = ("elapsed_time_ms", "throughput")
 
 
+def run_embodied_scenario(sc: dict, timeout: float = 900.0) -> List[dict]:
+    """Embodied scenarios run ``loongforge_b200.embodied.train`` and are read back from its ``metrics.jsonl``
+    (reference: tests/embodied/execution/metrics.py:6-24)."""
+    import tempfile
+
+    with tempfile.TemporaryDirectory() as out:
+        cmd = [sys.executable, "-m", "loongforge_b200.embodied.train"] + [str(a) for a in sc["args"]] + [f"output_dir={out}"]
+        env = dict(os.environ, CUDA_VISIBLE_DEVICES=os.environ.get("CUDA_VISIBLE_DEVICES", ""), PYTHONPATH=ROOT)
+        p = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=timeout)
+        if p.returncode != 0:
+            raise RuntimeError(f"scenario {sc['name']} exited with {p.returncode}:\n{p.stdout[-2000:]}\n{p.stderr[-2000:]}")
+        recs = []
+        with open(os.path.join(out, "metrics.jsonl")) as f:
+            for line in f:
+                r = json.loads(line)
+                recs.append({"iteration": r["step"], "lm_loss": r["loss"], "grad_norm": r["grad_norm"],
+                             "elapsed_time_ms": r["elapsed_ms"], "throughput": r["samples_per_sec"]})
+        return recs
+
+
 def run_scenario_command(sc: dict, timeout: float = 900.0) -> List[dict]:
+    if sc.get("stack") == "embodied":
+        return run_embodied_scenario(sc, timeout)
     sys.path.insert(0, ROOT)
     from tools.log2json import parse
 

@@ -95,3 +95,17 @@ def test_webdataset_shards(tmp_path):
     assert json.loads(groups[0][1]["json"])["num_images"] == 1
     multi = list(W.read_shard(str(tmp_path / "wds" / "shard-000001.tar")))[0][1]
     assert set(multi) == {"0.jpg", "1.jpg", "json"}
+
+
+def test_layer_benchmark_exports_policy(tmp_path):
+    from loongforge_b200.runtime.fp8_policy import FP8Policy
+    from tools import benchmark_parallel_layers as B
+
+    shapes = B.layer_shapes(__import__("loongforge_b200.models.registry", fromlist=["x"]).get_model_config("llama3-8b"), 2)
+    assert shapes["linear_qkv"] == (4096, 3072) and shapes["linear_fc1"] == (4096, 14336) and shapes["linear_fc2"] == (7168, 4096)
+    rows = B.run("tiny-llama", 1, [16, 32], warmup=1, iters=1)
+    assert {r["kind"] for r in rows} == {"linear_qkv", "linear_proj", "linear_fc1", "linear_fc2"} and len(rows) == 8
+    assert all(r["bf16_ms"] > 0 for r in rows)
+    out = tmp_path / "policy.json"
+    B.main(["--model-name", "tiny-llama", "--tokens", "16", "--out", str(out)])
+    FP8Policy.from_json(str(out))
