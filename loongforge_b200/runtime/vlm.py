@@ -63,8 +63,14 @@ def synthetic_vlm_iterator(vocab_size: int, seq_length: int, *, images_per_sampl
 class VLMTrainer(Trainer):
     def __init__(self, model_cfg: TransformerConfig, train_cfg, dims: Optional[ParallelDims] = None, *,
                  vit_cfg: Optional[TransformerConfig] = None, encoder_tp: int = 1, encoder_hetero_dp: bool = False,
-                 image_token_id: Optional[int] = None, encoder_recompute: bool = True, **kw):
+                 image_token_id: Optional[int] = None, encoder_recompute: bool = True,
+                 vision_family: str = "qwen2_vit", vision_options: Optional[dict] = None, freeze_encoder: bool = False,
+                 images_per_sample: int = 4, image_size: int = 448, **kw):
+        """``vision_family``: ``qwen2_vit`` (Qwen2/2.5-VL encoder) or a key of ``models.vision_zoo.VISION_FAMILIES``
+        (Qwen3-VL, InternViT, RICE, Moon, ERNIE, MiniCPM-V encoders with their projectors)."""
         self.vit_cfg = vit_cfg or get_model_config("qwen2.5-vit")
+        self.vision_family, self.vision_options, self.freeze_encoder = vision_family, vision_options, freeze_encoder
+        self.images_per_sample, self.image_size = images_per_sample, image_size
         if encoder_recompute:
             self.vit_cfg.recompute_granularity = "full"
         self.encoder_hetero_dp = encoder_hetero_dp
@@ -81,7 +87,9 @@ class VLMTrainer(Trainer):
     def _default_model_provider(self, pre_process, post_process, layer_numbers):
         return OmniCombinationModel(self.mcfg, self.vit_cfg if pre_process else None, image_token_id=self.image_token_id,
                                     pre_process=pre_process, post_process=post_process, layer_numbers=layer_numbers,
-                                    device=self.device, encoder_hetero_dp=self.encoder_hetero_dp)
+                                    device=self.device, encoder_hetero_dp=self.encoder_hetero_dp,
+                                    vision_family=self.vision_family, vision_options=self.vision_options,
+                                    freeze_encoder=self.freeze_encoder)
 
     def build_data_iterator(self, args=None):
         st = self.st
@@ -89,7 +97,8 @@ class VLMTrainer(Trainer):
         return synthetic_vlm_iterator(self.mcfg.vocab_size, self.tcfg.seq_length, patch=v.patch_size,
                                       temporal_patch=v.temporal_patch_size, merge=v.spatial_merge_size,
                                       channels=v.in_channels, image_token_id=self.image_token_id, dp_rank=st.dp_rank,
-                                      dp_size=st.dp_size, seed=self.tcfg.seed)
+                                      dp_size=st.dp_size, seed=self.tcfg.seed, images_per_sample=self.images_per_sample,
+                                      image_size=self.image_size)
 
     def _default_forward_step(self, data_iterator, model):
         b = self.get_batch(data_iterator)

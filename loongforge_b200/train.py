@@ -33,8 +33,24 @@ def main(argv: Optional[List[str]] = None) -> int:
         set_attention_impl(args.attention_backend)
     node = raw.get("model", raw) if isinstance(raw, dict) else {}
     family = (node.get("model_type") if isinstance(node, dict) and "foundation" in node else None) or model_cfg.model_family
+    extra = {}
+    enc = node.get("image_encoder") if isinstance(node, dict) else None
+    if isinstance(enc, dict):
+        # VLM YAML: the encoder section becomes its own config; its model_type selects the encoder family
+        from .config.build import transformer_config_from_yaml
+        from .models.vision_zoo import VISION_FAMILIES
+        vt = str(enc.get("model_type", "qwen2_5_vit"))
+        extra["vit_cfg"] = transformer_config_from_yaml({k: v for k, v in enc.items() if not isinstance(v, dict)
+                                                          and k not in ("freeze", "vision_options")})
+        extra["vision_family"] = vt if vt in VISION_FAMILIES else "qwen2_vit"
+        extra["vision_options"] = enc.get("vision_options")
+        extra["freeze_encoder"] = bool(enc.get("freeze", False))
+        extra["encoder_tp"] = int(getattr(args, "encoder_tensor_model_parallel_size", None) or 1)
+        extra["encoder_hetero_dp"] = bool(getattr(args, "enable_encoder_hetero_dp", False))
+        if getattr(args, "image_resolution", None):
+            extra["image_size"] = int(args.image_resolution)
     trainer = build_model_trainer(family, train_cfg.training_phase, model_cfg=model_cfg, train_cfg=train_cfg,
-                                  dims=dims, device=device)
+                                  dims=dims, device=device, **extra)
     if train_cfg.load:
         trainer.load_checkpoint(train_cfg.load, load_optim=not args.no_load_optim and not args.finetune,
                                 load_rng=not args.no_load_rng and not args.finetune)

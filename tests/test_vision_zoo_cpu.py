@@ -105,3 +105,52 @@ def test_omni_model_with_zoo_encoders(family):
     assert not missing, missing
     if family == "qwen3_vl_vit":
         assert m.decoder.deepstack_hook is not None
+
+
+def test_vlm_cli_with_internvit_yaml(tmp_path):
+    """A composed VLM YAML whose encoder section names a zoo family trains through the CLI."""
+    import subprocess
+    import sys
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    y = tmp_path / "tiny_internvl.yaml"
+    y.write_text("""
+model:
+  model_type: internvl
+  image_encoder:
+    model_type: intern_vit
+    num_layers: 2
+    hidden_size: 64
+    kv_channels: 16
+    ffn_hidden_size: 128
+    num_attention_heads: 4
+    num_query_groups: 4
+    patch_size: 14
+    temporal_patch_size: 1
+    spatial_merge_size: 2
+    normalization: LayerNorm
+    activation: gelu
+    gated_linear_unit: false
+    add_bias_linear: true
+    add_qkv_bias: true
+    causal: false
+    vocab_size: 0
+    qk_layernorm_full: true
+    vision_options: {pos_table_side: 4}
+  foundation:
+    model_type: llama
+    num_layers: 2
+    hidden_size: 64
+    num_attention_heads: 4
+    num_query_groups: 2
+    ffn_hidden_size: 128
+    vocab_size: 512
+""")
+    cmd = [sys.executable, "-m", "loongforge_b200.train", "--config-file", str(y), "--seq-length", "64",
+           "--micro-batch-size", "1", "--global-batch-size", "2", "--train-iters", "3", "--lr", "1e-3",
+           "--image-resolution", "56", "--log-interval", "1"]
+    p = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=600,
+                       env=dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=root))
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
+    assert "iteration        3/" in p.stdout and "lm loss" in p.stdout
