@@ -74,7 +74,9 @@ class TransformerConfig:
     moe_aux_loss_coeff: float = 0.0
     moe_z_loss_coeff: Optional[float] = None
     moe_token_dispatcher_type: str = "alltoall"  # alltoall (NCCL) | peer (NVLink peer-memory kernels, CUDA only)
-    moe_peer_capacity_factor: float = 2.0  # receive-buffer rows per rank = factor * local tokens * top-k
+    # receive-buffer rows per rank = factor * local tokens * top-k; routing of an untrained router is easily 2-3x
+    # skewed, and growing the buffers later costs a collective re-allocation
+    moe_peer_capacity_factor: float = 4.0
     moe_grouped_gemm: bool = True
     moe_expert_capacity_factor: Optional[float] = None
     # ---- MLA / DSA

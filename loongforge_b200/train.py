@@ -16,6 +16,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     from .runtime.trainer_builder import build_model_trainer
 
     args, overrides = parse_args(argv)
+    from .config.validators import apply_aliases, unwired_flag_notes
+    apply_aliases(args)
     device = init_distributed(backend=args.distributed_backend if args.distributed_backend == "gloo" else None,
                               timeout_s=args.distributed_timeout_minutes * 60)
     model_cfg, train_cfg, dims, raw = build_configs(args, overrides)
@@ -25,6 +27,8 @@ def main(argv: Optional[List[str]] = None) -> int:
         for k, v in sorted(vars(args).items()):
             print(f"  {k} {'.' * max(1, 48 - len(k))} {v}", flush=True)
         print("-------------------- end of arguments ---------------------", flush=True)
+        for note in unwired_flag_notes(args):
+            print(f"WARNING: {note}", flush=True)
     if args.cp_comm_type not in ("auto", None):
         from .parallel.context_parallel import set_cp_comm_type
         set_cp_comm_type(args.cp_comm_type if args.cp_comm_type in ("p2p", "allgather", "a2a") else "auto")
