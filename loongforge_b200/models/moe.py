@@ -179,12 +179,16 @@ class GroupedMLP(nn.Module):
                                         etp_dim=1, **etp)
         self.glu = glu
         self.act = cfg.activation
+        self.swiglu_limit = cfg.swiglu_limit
 
     def forward(self, x, tokens_per_expert, row_probs=None):
         """``row_probs`` [rows]: router probability of each received row, multiplied in before FC2
         (dispatchers that sum expert outputs unweighted pass it; Megatron's weighted-SwiGLU form)."""
         h = self.linear_fc1(x, tokens_per_expert)
-        if self.glu and self.act == "swiglu":
+        if self.glu and self.act == "swiglu" and self.swiglu_limit:
+            from .transformer import clamped_swiglu
+            h = clamped_swiglu(h, self.swiglu_limit)
+        elif self.glu and self.act == "swiglu":
             h = OF.swiglu(h)
         elif self.glu:
             g, u = h.chunk(2, -1)

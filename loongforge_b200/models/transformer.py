@@ -123,6 +123,13 @@ def _act(name: str):
             "gelu_tanh": lambda x: F.gelu(x, approximate="tanh")}[name]
 
 
+def clamped_swiglu(h: torch.Tensor, limit: float) -> torch.Tensor:
+    """SwiGLU with bounded pre-activations (DeepSeek-V4 ``swiglu_limit``): gate clamped from above, the linear branch
+    to [-limit, limit], so that a few huge activations cannot dominate the product."""
+    g, u = h.chunk(2, dim=-1)
+    return torch.nn.functional.silu(g.clamp(max=limit)) * u.clamp(min=-limit, max=limit)
+
+
 class MLP(nn.Module):
     def __init__(self, cfg: TransformerConfig, key: str, *, ffn_hidden: Optional[int] = None, fused_norm: bool = True,
                  device=None, parallel_state=None, is_expert: bool = False, sequence_parallel: Optional[bool] = None):
@@ -144,9 +151,12 @@ class MLP(nn.Module):
                                                **common)
         self.glu = glu
         self.act_name = cfg.activation
+        self.swiglu_limit = cfg.swiglu_limit
 
     def forward(self, x, residual=None):
         h = self.linear_fc1(x)
+        if self.glu and self.act_name == "swiglu" and self.swiglu_limit:
+            return self.linear_fc2(clamped_swiglu(h, self.swiglu_limit), residual)
         if (self.glu and self.act_name == "swiglu" and self.linear_fc2.tp == 1 and self.linear_fc2.bias is None
                 and OF.swiglu_linear_supported(h, self.linear_fc2.weight)):
             return OF.swiglu_linear(h, self.linear_fc2.weight, residual)

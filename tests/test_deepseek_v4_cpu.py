@@ -89,3 +89,12 @@ def test_tiny_deepseek_v4_trains():
     missing = [n for n, p in model.named_parameters() if p.grad is None]
     assert all(".indexer." in n for n in missing), missing  # the selection itself is not differentiable
     assert losses[-1] < losses[0] - 0.3, losses
+
+
+def test_clamped_swiglu():
+    from loongforge_b200.models.transformer import clamped_swiglu
+
+    h = torch.tensor([[20.0, -3.0, 50.0, -50.0]])  # gate = [20, -3], up = [50, -50]
+    out = clamped_swiglu(h, 10.0)
+    assert torch.allclose(out, torch.stack([torch.nn.functional.silu(torch.tensor(10.0)) * 10.0,
+                                            torch.nn.functional.silu(torch.tensor(-3.0)) * -10.0]).view(1, 2))
