@@ -33,7 +33,9 @@ def _time(fn, iters, warm=5):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "norm"])
+    ap.add_argument("what", choices=["gemm", "attention", "norm", "grouped", "router", "fp8"])
+    ap.add_argument("--experts", type=int, default=16)
+    ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -83,6 +85,59 @@ def main():
             tfb = _time(fb, a.iters)
             out.update(fwd_ms=tf, fwd_tflops=fl / tf, bwd_ms=tfb - tf, bwd_tflops=2.5 * fl / (tfb - tf))
         out.update(t=T, q_heads=G * R, kv_heads=G)
+    elif a.what == "grouped":
+        # E experts with m / E rows each (ragged by +-25 %), weights [n, k]: forward, dgrad, wgrad (fp32 accumulate)
+        E = a.experts
+        gen = torch.Generator().manual_seed(0)
+        base = a.m // E
+        tpe = [max(1, int(base * (0.75 + 0.5 * float(torch.rand(1, generator=gen))))) for _ in range(E)]
+        T = sum(tpe)
+        X = torch.randn(T, a.k, device=dev).bfloat16()
+        dY = torch.randn(T, a.n, device=dev).bfloat16()
+        Y, dX = torch.empty(T, a.n, device=dev).bfloat16(), torch.empty(T, a.k, device=dev).bfloat16()
+        W = [(torch.randn(a.n, a.k, device=dev) * 0.02).bfloat16() for _ in range(E)]
+        MG = [torch.zeros(a.n, a.k, device=dev) for _ in range(E)]
+        fns = {"fwd": lambda: OF.grouped_gemm(X, None, W, [Y], tpe, mode=0),
+               "dgrad": lambda: OF.grouped_gemm(dY, None, W, [dX], tpe, mode=1),
+               "wgrad_acc": lambda: OF.grouped_gemm(dY, X, [], MG, tpe, mode=2, out_mode=2)}
+        if a.once:
+            for f in fns.values():
+                f()
+        else:
+            fl = 2.0 * T * a.n * a.k / 1e9
+            for k_, f in fns.items():
+                out[k_ + "_tflops"] = fl / _time(f, a.iters)
+        out.update(experts=E, rows=T, n=a.n, k=a.k)
+    elif a.what == "router":
+        from . import moe_ops
+        logits = torch.randn(a.t, a.experts, device=dev)
+        f = lambda: moe_ops.topk_routing(logits, a.topk)  # noqa: E731
+        if a.once:
+            f()
+        else:
+            ms = _time(f, a.iters)
+            out.update(ms=ms, gbytes_per_s=a.t * a.experts * (4 + 4 + 4 + 1) / ms / 1e6)
+        out.update(t=a.t, experts=a.experts, topk=a.topk)
+    elif a.what == "fp8":
+        from . import quant as Q
+        Q.enable_native(True)
+        x = torch.randn(a.m, a.k, device=dev).bfloat16()
+        w = (torch.randn(a.n, a.k, device=dev) * 0.02).bfloat16()
+        qx, sx = Q.quantize_1x128(x)
+        qw, sw = Q.quantize_128x128(w)
+        C = _ext.require()
+        st = _ext.status_tensor(x.device)
+        fns = {"quant_1x128": lambda: Q.quantize_1x128(x), "quant_128x128": lambda: Q.quantize_128x128(w),
+               "gemm": lambda: C.gemm_fp8_blockwise(qx, sx, qw, sw, st)}
+        if a.once:
+            for f in fns.values():
+                f()
+        else:
+            out["quant_1x128_gbytes_per_s"] = a.m * a.k * 3 / _time(fns["quant_1x128"], a.iters) / 1e6
+            out["quant_128x128_gbytes_per_s"] = a.n * a.k * 3 / _time(fns["quant_128x128"], a.iters) / 1e6
+            out["gemm_tflops"] = 2.0 * a.m * a.n * a.k / 1e9 / _time(fns["gemm"], a.iters)
+            out["bf16_gemm_tflops"] = 2.0 * a.m * a.n * a.k / 1e9 / _time(lambda: OF.gemm(x, w), a.iters)
+        out.update(m=a.m, n=a.n, k=a.k)
     else:
         x = torch.randn(a.t, a.h, device=dev).bfloat16().requires_grad_()
         w = torch.ones(a.h, device=dev).bfloat16().requires_grad_()
