@@ -207,5 +207,8 @@ class CompressedSparseAttention(nn.Module):
             if sel.shape[1] > 0:
                 idx = torch.cat([idx, torch.where(sel >= 0, sel + T, sel)], dim=1)
                 kv_all = torch.cat([kv, entries], 0)
-        o = sparse_mqa_attention_with_sink(q, kv_all, idx, self.attn_sink, self.scale)
+        from ..ops.blockwise import blockwise_apply
+        scale = self.scale
+        o = blockwise_apply(lambda qb, ib, kvv, sk: sparse_mqa_attention_with_sink(qb, kvv, ib, sk, scale),
+                            [q, idx], [kv_all, self.attn_sink], block=256)
         return self.linear_proj(o.reshape(T, self.nq_l * self.d), residual)

@@ -193,8 +193,7 @@ class MLASelfAttention(nn.Module):
         if want_loss:
             o_c, pmean = out
             # index scores at the selected slots, differentiable w.r.t. the indexer weights only
-            kg = ki_all[indices.clamp_min(0)]
-            sc = (torch.relu(torch.einsum("mhd,mkd->mhk", qi.float(), kg.float())) * wi.unsqueeze(-1)).sum(1)
+            sc = dsa_ops.indexer_scores_at(qi, wi, ki_all, indices)
             loss = dsa_ops.indexer_kl_loss(sc, pmean, indices, cfg.dsa_indexer_loss_coeff)
             if st.dims.tp > 1:
                 loss = M.reduce_from_tensor_model_parallel_region(loss, st.group("tp")) / st.dims.tp

@@ -72,28 +72,45 @@ def indexer_topk(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, topk: int, q
     return idx_out, sc_out
 
 
+def _sparse_mla_block(q, idx, kv, scale: float, d_v: int, with_probs: bool):
+    """One query block: returns o flattened to [b, H*d_v], with the head-mean probabilities [b, K] appended."""
+    valid = idx >= 0
+    g = kv[idx.clamp_min(0)]  # [b, K, Dk]
+    sc = torch.einsum("bhd,bkd->bhk", q.float(), g.float()) * scale
+    sc = sc.masked_fill(~valid[:, None, :], float("-inf"))
+    p = torch.nan_to_num(torch.softmax(sc, dim=-1))
+    o = torch.einsum("bhk,bkd->bhd", p, g[..., :d_v].float()).to(q.dtype).flatten(1)
+    return torch.cat([o, p.mean(1).to(o.dtype)], dim=-1) if with_probs else o
+
+
 def sparse_mla_attention(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, scale: float, d_v: int = 512,
                          block: int = 256, return_head_mean_probs: bool = False):
     """q [m, H, Dk], kv [n, Dk] (shared by all heads), indices [m, K] (-1 = empty).
-    Returns o [m, H, d_v] (and the head-averaged attention distribution over the K slots)."""
-    m, H, Dk = q.shape
-    outs, pmeans = [], []
-    for s in range(0, m, block):
-        e = min(m, s + block)
-        idx = indices[s:e]
-        valid = idx >= 0
-        g = kv[idx.clamp_min(0)]  # [b, K, Dk]
-        sc = torch.einsum("bhd,bkd->bhk", q[s:e].float(), g.float()) * scale
-        sc = sc.masked_fill(~valid[:, None, :], float("-inf"))
-        p = torch.softmax(sc, dim=-1)
-        p = torch.nan_to_num(p)
-        outs.append(torch.einsum("bhk,bkd->bhd", p, g[..., :d_v].float()).to(q.dtype))
-        if return_head_mean_probs:
-            pmeans.append(p.mean(1))
-    o = torch.cat(outs, 0)
+    Returns o [m, H, d_v] (and the head-averaged attention distribution over the K slots, a constant target).
+    Query blocks are recomputed in backward (``ops/blockwise.py``), so the gathered keys of only one block are alive."""
+    from .blockwise import blockwise_apply
+
+    m, H, _ = q.shape
+    K = indices.shape[1]
+    fn = lambda qb, ib, kvv: _sparse_mla_block(qb, ib, kvv, scale, d_v, return_head_mean_probs)  # noqa: E731
+    out = blockwise_apply(fn, [q, indices], [kv], block)
+    o = out[:, :H * d_v].reshape(m, H, d_v)
     if return_head_mean_probs:
-        return o, torch.cat(pmeans, 0)
+        return o, out[:, H * d_v:H * d_v + K].detach().float()
     return o
+
+
+def indexer_scores_at(qi: torch.Tensor, wi: torch.Tensor, ki: torch.Tensor, indices: torch.Tensor,
+                      block: int = 256) -> torch.Tensor:
+    """Index scores ``sum_h w * relu(q_h . k)`` at the selected slots only: [m, K] fp32, differentiable w.r.t. the
+    indexer projections, evaluated in recomputed query blocks."""
+    from .blockwise import blockwise_apply
+
+    def fn(qb, wb, ib, kk):
+        kg = kk[ib.clamp_min(0)]
+        return (torch.relu(torch.einsum("mhd,mkd->mhk", qb.float(), kg.float())) * wb.float().unsqueeze(-1)).sum(1)
+
+    return blockwise_apply(fn, [qi, wi, indices], [ki], block)
 
 
 def indexer_kl_loss(index_scores: torch.Tensor, attn_probs_head_mean: torch.Tensor, indices: torch.Tensor,

@@ -98,3 +98,24 @@ def test_clamped_swiglu():
     out = clamped_swiglu(h, 10.0)
     assert torch.allclose(out, torch.stack([torch.nn.functional.silu(torch.tensor(10.0)) * 10.0,
                                             torch.nn.functional.silu(torch.tensor(-3.0)) * -10.0]).view(1, 2))
+
+
+def test_blockwise_apply_matches_plain_autograd():
+    from loongforge_b200.models.csa import sparse_mqa_attention_with_sink
+    from loongforge_b200.ops.blockwise import blockwise_apply
+
+    torch.manual_seed(0)
+    T, H, d, K = 37, 3, 8, 6
+    q = torch.randn(T, H, d, requires_grad=True)
+    kv = torch.randn(T, d, requires_grad=True)
+    sink = torch.randn(H, requires_grad=True)
+    idx = torch.randint(-1, T, (T, K))
+    ref = sparse_mqa_attention_with_sink(q, kv, idx, sink, 0.3)
+    w = torch.randn_like(ref)
+    g_ref = torch.autograd.grad((ref * w).sum(), [q, kv, sink])
+    out = blockwise_apply(lambda qb, ib, kvv, sk: sparse_mqa_attention_with_sink(qb, kvv, ib, sk, 0.3), [q, idx],
+                          [kv, sink], block=8)
+    g = torch.autograd.grad((out * w).sum(), [q, kv, sink])
+    assert torch.allclose(out, ref, atol=1e-6)
+    for a, b in zip(g, g_ref):
+        assert torch.allclose(a, b, atol=1e-5), (a - b).abs().max()

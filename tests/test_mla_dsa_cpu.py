@@ -1,0 +1,70 @@
+"""Multi-latent attention with the sparse-attention indexer (DeepSeek-V3.2 path) on CPU."""
+import torch
+
+
+def test_sparse_mla_with_all_keys_selected_is_dense_causal_attention():
+    from loongforge_b200.ops import dsa_ops
+
+    torch.manual_seed(0)
+    T, H, Dk, dv = 20, 3, 24, 16
+    q = torch.randn(T, H, Dk, requires_grad=True)
+    kv = torch.randn(T, Dk, requires_grad=True)
+    idx = torch.arange(T).unsqueeze(0).expand(T, T).clone()
+    idx[torch.triu(torch.ones(T, T, dtype=torch.bool), 1)] = -1  # causal: keys after the query are empty slots
+    o, pmean = dsa_ops.sparse_mla_attention(q, kv, idx, 0.2, d_v=dv, block=7, return_head_mean_probs=True)
+    s = torch.einsum("thd,sd->ths", q, kv) * 0.2
+    s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1).unsqueeze(1), float("-inf"))
+    p = s.softmax(-1)
+    ref = torch.einsum("ths,sd->thd", p, kv[:, :dv])
+    assert torch.allclose(o, ref, atol=1e-5) and torch.allclose(pmean, p.mean(1), atol=1e-6)
+    w = torch.randn_like(ref)
+    ga = torch.autograd.grad((o * w).sum(), [q, kv])
+    gb = torch.autograd.grad((ref * w).sum(), [q, kv])
+    for a, b in zip(ga, gb):
+        assert torch.allclose(a, b, atol=1e-5)
+
+
+def test_indexer_topk_is_causal_and_picks_best():
+    from loongforge_b200.ops import dsa_ops
+
+    torch.manual_seed(1)
+    T, Hi, D, k = 30, 2, 8, 4
+    q, kk, w = torch.randn(T, Hi, D), torch.randn(T, D), torch.rand(T, Hi)
+    pos = torch.arange(T)
+    idx, sc = dsa_ops.indexer_topk(q, kk, w, k, pos, pos, block=11)
+    full = dsa_ops.indexer_logits_block(q, kk, w).masked_fill(pos[None, :] > pos[:, None], float("-inf"))
+    for t in range(T):
+        sel = [i for i in idx[t].tolist() if i >= 0]
+        assert all(i <= t for i in sel) and len(sel) == min(k, t + 1)
+        assert set(sel) == set(full[t].topk(len(sel)).indices.tolist())
+    at = dsa_ops.indexer_scores_at(q, w, kk, idx, block=9)
+    assert torch.allclose(at[idx >= 0], sc[idx >= 0], atol=1e-5)
+
+
+def test_tiny_deepseek_v32_trains_with_indexer_loss():
+    from loongforge_b200.models.registry import build_model, get_model_config
+    from loongforge_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(ps.ParallelDims())
+    cfg = get_model_config("tiny-deepseek")
+    assert cfg.use_dsa and cfg.multi_latent_attention and cfg.dsa_indexer_loss_coeff > 0
+    torch.manual_seed(0)
+    model = build_model(cfg)
+    model.train()
+    opt = torch.optim.AdamW(model.parameters(), lr=2e-3)
+    T = 48
+    tokens = torch.randint(0, cfg.vocab_size, (T,))
+    labels, pos = torch.roll(tokens, -1), torch.arange(T)
+    losses = []
+    for _ in range(8):
+        loss = model(tokens, pos, labels=labels, loss_mask=torch.ones(T)).mean()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    idx_params = [n for n, p in model.named_parameters() if ".indexer." in n]
+    assert idx_params and all(p.grad is not None and float(p.grad.abs().sum()) > 0
+                              for n, p in model.named_parameters() if ".indexer." in n)  # trained by the KL loss
+    assert all(p.grad is not None for p in model.parameters())
+    assert losses[-1] < losses[0] - 0.2, losses
