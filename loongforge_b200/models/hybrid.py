@@ -45,6 +45,9 @@ class GatedAttention(nn.Module):
                                                    key=key + ".linear_qgkv", **common)
         self.q_layernorm = Norm(self.d, cfg, device=device)
         self.k_layernorm = Norm(self.d, cfg, device=device)
+        if tp > 1:
+            PL.mark_tp_partial_grad(self.q_layernorm)
+            PL.mark_tp_partial_grad(self.k_layernorm)
         self.linear_proj = PL.RowParallelLinear(self.nq * self.d, cfg.hidden_size, bias=False,
                                                 init_std=cfg.init_method_std / math.sqrt(2.0 * cfg.num_layers),
                                                 key=key + ".linear_proj", **common)
@@ -106,17 +109,26 @@ class GatedDeltaNet(nn.Module):
                                                     init_std=cfg.init_method_std, key=key + ".in_proj_qkvz", **common)
         self.in_proj_ba = PL.ColumnParallelLinear(cfg.hidden_size, self.hk * 2 * self.ratio, bias=False,
                                                   init_std=cfg.init_method_std, key=key + ".in_proj_ba", **common)
-        conv_dim = self.hk_l * (2 * self.dk + self.ratio * self.dv)
-        g = torch.Generator().manual_seed((zlib.crc32((key + ".conv1d").encode()) + st.tp_rank) & 0x7FFFFFFF)
-        self.conv_weight = nn.Parameter((torch.rand(conv_dim, self.K, generator=g) * 2 - 1).mul_(self.K ** -0.5)
-                                        .to(device=device, dtype=cfg.params_dtype))
+        # The FULL parameters are drawn from a seed that depends only on the key, then sliced to this rank's heads, so
+        # that every tensor-parallel layout starts from the same model. Conv channels are laid out type-major
+        # [q heads | k heads | v heads]; a rank keeps its head range of each type.
+        g = torch.Generator().manual_seed(zlib.crc32((key + ".conv1d").encode()) & 0x7FFFFFFF)
+        full_conv = (torch.rand(self.hk * (2 * self.dk + self.ratio * self.dv), self.K, generator=g) * 2 - 1) * self.K ** -0.5
+        qf, kf, vf = full_conv.split([self.hk * self.dk, self.hk * self.dk, self.hv * self.dv], dim=0)
+        r0 = st.tp_rank
+        local = torch.cat([qf.view(self.hk, self.dk, -1)[r0 * self.hk_l:(r0 + 1) * self.hk_l].reshape(-1, self.K),
+                           kf.view(self.hk, self.dk, -1)[r0 * self.hk_l:(r0 + 1) * self.hk_l].reshape(-1, self.K),
+                           vf.view(self.hv, self.dv, -1)[r0 * self.hv_l:(r0 + 1) * self.hv_l].reshape(-1, self.K)], 0)
+        self.conv_weight = nn.Parameter(local.to(device=device, dtype=cfg.params_dtype))
         self.dt_bias = nn.Parameter(torch.ones(self.hv_l, device=device))
-        A = torch.empty(self.hv_l).uniform_(1e-3, 16.0, generator=g)
+        A = torch.empty(self.hv).uniform_(1e-3, 16.0, generator=g)[r0 * self.hv_l:(r0 + 1) * self.hv_l]
         self.A_log = nn.Parameter(torch.log(A).to(device=device))
         for p in (self.conv_weight, self.dt_bias, self.A_log):
             PL.mark_tp(p, 0 if tp > 1 else None)
         self.out_norm = GatedRMSNorm(self.dv, cfg.layernorm_epsilon, device=device)
-        PL.mark_tp(self.out_norm.weight, None, sequence_parallel=cfg.sequence_parallel)
+        PL.mark_tp(self.out_norm.weight, None)
+        if tp > 1:
+            PL.mark_tp_partial_grad(self.out_norm)
         self.out_proj = PL.RowParallelLinear(self.hv * self.dv, cfg.hidden_size, bias=False,
                                              init_std=cfg.init_method_std / math.sqrt(2.0 * cfg.num_layers),
                                              key=key + ".out_proj", **common)

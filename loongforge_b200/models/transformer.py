@@ -203,6 +203,9 @@ class SelfAttention(nn.Module):
         elif cfg.qk_layernorm:
             self.q_layernorm = Norm(self.d, cfg, device=device)
             self.k_layernorm = Norm(self.d, cfg, device=device)
+            if tp > 1:
+                PL.mark_tp_partial_grad(self.q_layernorm)
+                PL.mark_tp_partial_grad(self.k_layernorm)
         else:
             self.q_layernorm = self.k_layernorm = None
         self.linear_proj = PL.RowParallelLinear(self.nq * self.d, cfg.hidden_size, bias=cfg.add_bias_linear,

@@ -117,7 +117,11 @@ class DistributedOptimizer:
         total = torch.zeros(1, dtype=torch.float32, device=dev)
         for sh in self.shards:
             g = sh.buf.grad_data[sh.start:sh.end]
-            is_expert_buf = sh.buf.dp_group is st.group("edp") and st.dims.ep > 1
+            # expert buffers are reduced over the expert-data-parallel group, which contains the TP ranks whenever experts
+            # are replicated over them (ep * etp < tp * cp * dp): with a sharded optimizer every rank of that group
+            # holds a DISJOINT piece, so all of them count, whatever their TP rank
+            is_expert_buf = (sh.buf.dp_group is st.group("edp") and sh.buf.dp_group is not st.group("dp_cp")
+                             and (st.dims.ep > 1 or (self.sharded and sh.buf.dp_size > 1)))
             # merge adjacent segments that are counted with the same multiplicity
             runs = []
             for lo, hi, _, dup, *_ in sh.segments:

@@ -67,6 +67,13 @@ def mark_tp(param: torch.Tensor, partition_dim: Optional[int], stride: int = 1, 
     return param
 
 
+def mark_tp_partial_grad(module: nn.Module) -> None:
+    """Parameters of `module` are replicated over the TP group but applied to THIS rank's heads only, so each rank
+    holds a partial gradient that the trainer sums over the TP group."""
+    for p in module.parameters():
+        p.tp_partial_grad = True
+
+
 class ColumnParallelLinear(nn.Module):
     """Y = X W^T with W sharded on the output dim. With sequence parallelism the input is
     ``[T/tp, in]`` and is all-gathered along tokens first (backward: reduce-scatter of dX)."""

@@ -247,14 +247,18 @@ class Trainer:
         return metrics
 
     def _allreduce_sequence_parallel_grads(self):
-        """Norm weights etc. see only a sequence shard per TP rank: sum their grads over TP."""
+        """Replicated parameters whose gradient is only a PARTIAL sum on each TP rank are summed over the TP group:
+        norm weights that see a sequence shard (sequence parallelism), and per-head norm weights applied to this
+        rank's heads only (``tp_partial_grad``: QK layernorm, gated-delta-net output norm)."""
         st = self.st
-        if st.dims.tp == 1 or not self.mcfg.sequence_parallel:
+        if st.dims.tp == 1:
             return
+        sp = self.mcfg.sequence_parallel
         grads = []
         for m in self.models:
             for p in m.module.parameters():
-                if getattr(p, "sequence_parallel", False) and p.requires_grad:
+                if p.requires_grad and ((sp and getattr(p, "sequence_parallel", False))
+                                        or getattr(p, "tp_partial_grad", False)):
                     grads.append(p.main_grad)
         if not grads:
             return

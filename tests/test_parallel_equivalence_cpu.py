@@ -66,6 +66,18 @@ def test_moe_expert_tensor_parallel_matches_single_process():
     _check(ref, res, lambda r: True, tol=5e-4)
 
 
+@pytest.mark.parametrize("model,dims", [("tiny-qwen3-next", {"tp": 2}), ("tiny-deepseek", {"tp": 2}),
+                                        ("tiny-deepseek-v4", {"pp": 3})])
+def test_newer_families_match_single_process(model, dims):
+    """Hybrid linear attention under TP+SP, MLA + DSA under TP+SP, hyper-connection streams across pipeline stages."""
+    ov = {"moe_aux_loss_coeff": 0.0} if model != "tiny-deepseek-v4" else {}
+    world = dims.get("tp", 1) * dims.get("pp", 1)
+    ref = _single(model, 2, ov)
+    res = run_distributed(_run, world, model, dict(dims), 2, ov)
+    pp = dims.get("pp", 1)
+    _check(ref, res, lambda r: r // (world // pp) == pp - 1, tol=1e-3)
+
+
 def _run_cp(rank, world, comm):
     from loongforge_b200.parallel import context_parallel as CP
 
