@@ -208,6 +208,7 @@ class GPTModel(nn.Module):
         cfg = self.cfg
         st = ps.get_state(self.state_name)
         g = st.group("tp")
+        hidden_local = hidden  # what the MTP layers continue from: the sequence shard under sequence parallelism
         if cfg.sequence_parallel and st.dims.tp > 1:
             hidden = M.gather_from_sequence_parallel_region(hidden, g, True)
         elif st.dims.tp > 1:
@@ -222,5 +223,5 @@ class GPTModel(nn.Module):
                                          tp_group=g if st.dims.tp > 1 else None,
                                          chunk_tokens=cfg.cross_entropy_chunk_tokens, fused_scale=loss_scale)
         if self.mtp is not None and self.training:
-            losses = self.mtp.attach(self, hidden, losses, labels, loss_mask, loss_scale, **mtp_kw)
+            losses = self.mtp.attach(self, hidden_local, losses, labels, loss_mask, loss_scale, **mtp_kw)
         return losses

@@ -12,6 +12,8 @@ on the last pipeline stage together with a copy of the embedding when pipeline p
 """
 from __future__ import annotations
 
+import copy
+
 import torch
 import torch.nn as nn
 
@@ -27,20 +29,27 @@ class MTPLayer(nn.Module):
     def __init__(self, cfg: TransformerConfig, k: int, device=None, parallel_state=None):
         super().__init__()
         self.cfg = cfg
-        self.enorm = Norm(cfg.hidden_size, cfg, device=device)
-        self.hnorm = Norm(cfg.hidden_size, cfg, device=device)
+        sp = cfg.sequence_parallel
+        self.state_name = parallel_state
+        self.enorm = Norm(cfg.hidden_size, cfg, device=device, sequence_parallel=sp)
+        self.hnorm = Norm(cfg.hidden_size, cfg, device=device, sequence_parallel=sp)
         self.eh_proj = PL.ColumnParallelLinear(2 * cfg.hidden_size, cfg.hidden_size, gather_output=True,
                                                init_std=cfg.init_method_std, key=f"mtp.layers.{k}.eh_proj",
                                                params_dtype=cfg.params_dtype, device=device,
-                                               parallel_state=parallel_state)
+                                               parallel_state=parallel_state, sequence_parallel=sp)
         self.transformer_layer = TransformerLayer(cfg, cfg.num_layers - 1, device=device, parallel_state=parallel_state)
-        self.final_layernorm = Norm(cfg.hidden_size, cfg, device=device)
+        self.final_layernorm = Norm(cfg.hidden_size, cfg, device=device, sequence_parallel=sp)
 
     def forward(self, hidden, emb_next, rotary, packed):
+        """hidden / emb_next are sequence shards ``[T/tp, H]`` under sequence parallelism (full otherwise)."""
         parts = [self.enorm(emb_next), self.hnorm(hidden)]
         if self.cfg.mtp_hidden_first:  # MiMo concatenates [hidden, embedding]
             parts.reverse()
-        x = self.eh_proj(torch.cat(parts, dim=-1))
+        x = self.eh_proj(torch.cat(parts, dim=-1))  # all-gathers tokens, gathers features: [T, H] on every rank
+        st = ps.get_state(self.state_name)
+        if self.cfg.sequence_parallel and st.dims.tp > 1:
+            from ..parallel import mappings as M
+            x = M.scatter_to_sequence_parallel_region(x, st.group("tp"))
         x = self.transformer_layer(x, rotary, packed)
         return self.final_layernorm(x)
 
@@ -48,9 +57,10 @@ class MTPLayer(nn.Module):
 class MultiTokenPredictionBlock(nn.Module):
     def __init__(self, cfg: TransformerConfig, device=None, parallel_state=None):
         super().__init__()
-        assert not cfg.sequence_parallel, "MTP with sequence parallelism is not supported"
         self.cfg = cfg
-        self.layers = nn.ModuleList([MTPLayer(cfg, k, device, parallel_state) for k in range(cfg.mtp_num_layers)])
+        lcfg = copy.copy(cfg)
+        lcfg.tp_comm_overlap = False  # the fused TP kernels are sized for the trunk's shapes
+        self.layers = nn.ModuleList([MTPLayer(lcfg, k, device, parallel_state) for k in range(cfg.mtp_num_layers)])
 
     def attach(self, model, hidden, losses, labels, loss_mask, loss_scale, *, tokens, position_ids, rotary, packed):
         """Adds the MTP losses to the autograd graph of `losses` and returns `losses`."""
@@ -58,6 +68,8 @@ class MultiTokenPredictionBlock(nn.Module):
         st = ps.get_state(model.state_name)
         T = tokens.shape[0]
         h = hidden
+        sp = cfg.sequence_parallel and st.dims.tp > 1
+        g = st.group("tp")
         tok, lab = tokens, labels
         mask = loss_mask.float() if loss_mask is not None else torch.ones(T, device=tokens.device)
         w = model.shared_embedding_weight()
@@ -74,9 +86,13 @@ class MultiTokenPredictionBlock(nn.Module):
                 ends = (packed.cu_seqlens[1:].long() - 1).clamp_min(0)
                 mask = mask.clone()
                 mask[ends] = 0  # never predict across a packed-sequence boundary
-            emb = model.embed(tok)
+            emb = model.embed(tok)  # a sequence shard under sequence parallelism
             h = layer(h, emb, rotary, packed)
-            l_k = OF.linear_cross_entropy(h, w, lab, mask, vocab_start=v0, valid_vocab=valid,
+            # the vocab-parallel loss needs the full sequence and sums partial hidden-state gradients over TP
+            from ..parallel import mappings as M
+            h_full = M.gather_from_sequence_parallel_region(h, g, True) if sp else (
+                M.copy_to_tensor_model_parallel_region(h, g) if st.dims.tp > 1 else h)
+            l_k = OF.linear_cross_entropy(h_full, w, lab, mask, vocab_start=v0, valid_vocab=valid,
                                           tp_group=st.group("tp") if st.dims.tp > 1 else None,
                                           chunk_tokens=cfg.cross_entropy_chunk_tokens)
             mtp_loss = (l_k * mask).sum() / mask.sum().clamp_min(1)

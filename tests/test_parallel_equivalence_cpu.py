@@ -67,7 +67,8 @@ def test_moe_expert_tensor_parallel_matches_single_process():
 
 
 @pytest.mark.parametrize("model,dims", [("tiny-qwen3-next", {"tp": 2}), ("tiny-deepseek", {"tp": 2}),
-                                        ("tiny-deepseek-v4", {"pp": 3})])
+                                        ("tiny-deepseek-v4", {"pp": 3}), ("tiny-qwen3-moe", {"tp": 2}),
+                                        ("tiny-minimax", {"tp": 2}), ("tiny-minimax", {"tp": 2, "sp": False})])
 def test_newer_families_match_single_process(model, dims):
     """Hybrid linear attention under TP+SP, MLA + DSA under TP+SP, hyper-connection streams across pipeline stages."""
     ov = {"moe_aux_loss_coeff": 0.0} if model != "tiny-deepseek-v4" else {}
