@@ -176,6 +176,9 @@ def model_param_items(trainer):
                 parts = name.split(".")
                 parts[2] = str(layer_numbers[int(parts[2])])
                 key = ".".join(parts)
+            ge = getattr(p, "expert_global_index", None)
+            if ge is not None:  # "...linear_fc1.weight{local}" -> "...linear_fc1.weight{global}" under expert parallelism
+                key = key[:key.rindex("weight")] + f"weight{ge}"
             yield key, p
 
 
@@ -206,31 +209,25 @@ def build_save_state(trainer, stage: bool = False) -> Dict[str, object]:
         dup = not getattr(p, "tensor_model_parallel", False)
         if not writer or (dup and (st.etp_rank if is_expert else tpr) != 0):
             continue
+        if getattr(p, "shared_embedding_replica", False):
+            continue
         data = p.detach()
         local_tensors[key] = [(off, own(data[sl])) for off, sl in pieces]
         local_desc.append((key, gshape, [(off, list(t.shape)) for off, t in local_tensors[key]]))
     # ---- optimizer: flat chunks per (param, model-parallel coordinate)
     opt_local: Dict[str, List[Tuple[List[int], torch.Tensor]]] = {}
     opt_desc = []
-    key_of = {}
-    for chunk in trainer.models:
-        mod = chunk.module
-        layer_numbers = getattr(mod.decoder, "layer_numbers", None) if hasattr(mod, "decoder") else None
-        for name, _ in mod.named_parameters():
-            key = name
-            if layer_numbers is not None and name.startswith("decoder.layers."):
-                parts = name.split(".")
-                parts[2] = str(layer_numbers[int(parts[2])])
-                key = ".".join(parts)
-            key_of[name] = key
+    key_of = {id(p): key for key, p in model_param_items(trainer)}
     coord = f"tp{tpr}of{tp}.ep{st.ep_rank}of{st.dims.ep}"
     sharded = trainer.optimizer.sharded
     for name, pieces in trainer.optimizer.sharded_state().items():
         if not sharded and st.rank_in("dp_cp") != 0:
             continue
         for piece in pieces:
+            if getattr(piece["param"], "shared_embedding_replica", False):
+                continue  # the first pipeline stage writes the shared word embedding and its optimizer state
             for kind in ("master", "exp_avg", "exp_avg_sq"):
-                k = f"optimizer.state.{kind}.{key_of.get(name, name)}.{coord}"
+                k = f"optimizer.state.{kind}.{key_of.get(id(piece['param']), name)}.{coord}"
                 t = own(piece[kind].detach())
                 opt_local.setdefault(k, []).append(([piece["offset"]], t))
                 gshapes[k] = [piece["param_numel"]]
@@ -383,11 +380,11 @@ def load_checkpoint(root: str, trainer, *, load_optim: bool = True, load_rng: bo
     opt_targets = []
     if load_optim and same_mp:
         coord = f"tp{tpr}of{tp}.ep{st.ep_rank}of{st.dims.ep}"
-        key_of = {n: k for (k, _), (n, _) in zip(model_param_items(trainer), _named_params(trainer))}
+        key_of = {id(p): k for k, p in model_param_items(trainer)}
         for name, pieces in trainer.optimizer.sharded_state().items():
             for piece in pieces:
                 for kind in ("master", "exp_avg", "exp_avg_sq"):
-                    k = f"optimizer.state.{kind}.{key_of.get(name, name)}.{coord}"
+                    k = f"optimizer.state.{kind}.{key_of.get(id(piece['param']), name)}.{coord}"
                     buf = torch.empty(piece["numel"], dtype=piece[kind].dtype)
                     state.setdefault(k + f"@{piece['offset']}", None)
                     opt_targets.append((k, piece, kind, buf))
@@ -451,7 +448,7 @@ def save_legacy(root: str, trainer, *, release: bool = False) -> str:
     # optimizer shards of every data-parallel rank
     od = os.path.join(d, f"distrib_optim_dp{st.rank_in('dp_cp'):03d}.pt")
     os.makedirs(d, exist_ok=True)
-    torch.save({n: [{k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in pc.items() if k != "set_master"}
+    torch.save({n: [{k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in pc.items() if k not in ("set_master", "param")}
                     for pc in pcs]
                 for n, pcs in trainer.optimizer.sharded_state().items()}, od)
     if dist.is_initialized():

@@ -142,6 +142,8 @@ def _add_training_args(p):
     g.add_argument("--fp16", action="store_true")
     g.add_argument("--fp8-format", type=str, default=None)
     g.add_argument("--fp8-recipe", type=str, default=None)
+    g.add_argument("--fp8-dynamic-policy-path", type=str, default=None,
+                   help="JSON rules that pick FP8 or BF16 per linear-layer kind, token count and TP size")
     g.add_argument("--fp8-param-gather", action="store_true")
     g.add_argument("--accumulate-allreduce-grads-in-fp32", action="store_true")
     g.add_argument("--seed", type=int, default=1234)

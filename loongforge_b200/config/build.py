@@ -174,6 +174,10 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
         log_interval=args.log_interval, save=args.save, load=args.load, save_interval=args.save_interval,
         ckpt_format="torch_dist" if args.ckpt_format in ("torch_dist", "torch_dcp") else args.ckpt_format,
         async_save=bool(getattr(args, "async_save", False)),
+        fp8_policy_file=getattr(args, "fp8_dynamic_policy_path", None),
+        optimizer_cpu_offload=bool(getattr(args, "optimizer_cpu_offload", False)),
+        use_fsdp=bool(getattr(args, "use_torch_fsdp2", False) or getattr(args, "use_megatron_fsdp", False)),
+        fsdp_sharding_strategy=getattr(args, "data_parallel_sharding_strategy", None) or "optim_grads_params",
         use_distributed_optimizer=args.use_distributed_optimizer, overlap_grad_reduce=args.overlap_grad_reduce,
         overlap_param_gather=args.overlap_param_gather, exp_avg_dtype=dt[args.exp_avg_dtype],
         exp_avg_sq_dtype=dt[args.exp_avg_sq_dtype], calculate_per_token_loss=args.calculate_per_token_loss,

@@ -55,15 +55,11 @@ def validate(args, cfg, tc, dims) -> None:
 # Flags that are accepted for command-line compatibility but whose feature is reached through a library entry point
 # rather than the training CLI today. Nothing is ignored silently: `unwired_flag_notes` lists what was requested.
 _LIBRARY_ONLY = {
-    "use_torch_fsdp2": "FSDP2 sharding: parallel.fsdp.wrap_fsdp2(model) (the CLI trainer uses DDP + distributed optimizer)",
-    "use_megatron_fsdp": "FSDP sharding: parallel.fsdp.wrap_fsdp2(model)",
-    "optimizer_cpu_offload": "optimizer offload: optim.cpu_offload.CPUOffloadAdam (native host AdamW)",
     "enable_chunkpipe": "sequence-chunk pipelining: runtime.chunkpipe.chunkpipe_forward_backward",
     "enable_full_hetero_dp": "full heterogeneous encoder DP: runtime.hetero_dp.FullHeteroEncoderRunner",
     "use_vlm_dp_balance": "data-parallel load balancing: data.dp_balance.rebalance",
     "enable_cuda_graph": "CUDA graphs: runtime.cuda_graphs.GraphedCallable / embodied.cuda_graph.MicrobatchGraphRunner",
     "overlap_moe_expert_parallel_comm": "A2A overlap plan: runtime.a2a_overlap.interleave / OverlapExecutor",
-    "fp8_format": "FP8: ops.quant (block quantisation) and runtime.fp8_policy (per-module precision)",
 }
 
 

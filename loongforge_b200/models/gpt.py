@@ -121,12 +121,22 @@ class GPTModel(nn.Module):
         cfg.pad_vocab(st.dims.tp)
         if layer_numbers is None:
             layer_numbers = list(range(cfg.num_layers))
-        if pre_process:
+        # With pipeline parallelism the last stage needs the word embedding too when it is tied to the output layer or
+        # feeds the multi-token-prediction layers. Both stages then hold a copy ("shared_embedding"); their gradients are
+        # summed over the embedding group after every backward, so the copies stay identical (reference: Megatron
+        # LanguageModule.setup_embeddings_and_output_layer, used through base_gpt_model.py:709-720).
+        needs_copy = post_process and (not cfg.untie_embeddings_and_output_weights or cfg.mtp_num_layers > 0)
+        shared = st.dims.pp > 1 and (not cfg.untie_embeddings_and_output_weights or cfg.mtp_num_layers > 0)
+        if pre_process or (shared and needs_copy):
             self.embedding = nn.Module()
             self.embedding.word_embeddings = PL.VocabParallelEmbedding(
                 cfg.padded_vocab_size, cfg.hidden_size, init_std=cfg.init_method_std,
                 sequence_parallel=cfg.sequence_parallel, params_dtype=cfg.params_dtype, device=device,
                 parallel_state=parallel_state)
+            if shared:
+                self.embedding.word_embeddings.weight.shared_embedding = True
+                if not pre_process:
+                    self.embedding.word_embeddings.weight.shared_embedding_replica = True
         self.decoder = TransformerBlock(cfg, layer_numbers, post_process=post_process, device=device,
                                         parallel_state=parallel_state)
         if post_process:
@@ -141,6 +151,14 @@ class GPTModel(nn.Module):
                 self.mtp = MultiTokenPredictionBlock(cfg, device=device, parallel_state=parallel_state)
             else:
                 self.mtp = None
+            # weights that collect gradients from several places of one backward pass (output layer + embedding lookup
+            # when tied, one more loss head per MTP depth) must not start their data-parallel reduction at the first
+            multi = [self.embedding.word_embeddings.weight] if hasattr(self, "embedding") else []
+            if self.output_layer is not None and cfg.mtp_num_layers > 0:
+                multi.append(self.output_layer.weight)
+            if not cfg.untie_embeddings_and_output_weights or cfg.mtp_num_layers > 0:
+                for w in multi:
+                    w.defer_grad_sync = True
         rot_dim = cfg.qk_pos_emb_head_dim if (cfg.multi_latent_attention or cfg.csa_compress_ratios is not None) else int(cfg.kv_channels * cfg.rotary_percent)
         self.rotary = RotaryEmbedding(cfg, rot_dim) if cfg.position_embedding_type in ("rope", "yarn", "mrope") else None
         self.input_tensor = None  # set by the pipeline schedule on non-first stages

@@ -182,7 +182,8 @@ class MLASelfAttention(nn.Module):
             seg_k = M._all_gather_dim0(seg, g) if seg is not None else None
         idxr = self.core_attention.indexer
         qi, ki, wi = idxr.project(x.detach(), q_c.detach(), rotary)
-        ki_all = M._all_gather_dim0(ki, st.group("cp")) if st.dims.cp > 1 else ki
+        # index keys of the other context-parallel ranks; their gradient (indexer loss) flows back by reduce-scatter
+        ki_all = M.gather_from_sequence_parallel_region(ki, st.group("cp"), True) if st.dims.cp > 1 else ki
         with torch.no_grad():
             qq, _ = dsa_ops.quant_fp8_rowwise_pow2(qi) if cfg.fp8 else (qi, None)
             kq, _ = dsa_ops.quant_fp8_rowwise_pow2(ki_all) if cfg.fp8 else (ki_all, None)

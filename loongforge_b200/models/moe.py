@@ -154,6 +154,7 @@ class GroupedLinear(nn.Module):
             PL.mark_tp(p, shard, stride=stride if shard == 0 else 1)
             p.is_expert = True
             p.partition_stride = stride
+            p.expert_global_index = first_global + e  # checkpoints name experts by their global index
             self.register_parameter(f"weight{e}", p)
 
     def weights(self):

@@ -106,3 +106,48 @@ def fp8_blockwise_linear(x: torch.Tensor, w: torch.Tensor, pow2: bool = False) -
             qw, sw = quantize_128x128(w, pow2)
             return C.gemm_fp8_blockwise(qx, sx, qw, sw, _ext.status_tensor(x.device))
     return fp8_blockwise_linear_ref(x, w, pow2)
+
+
+# ----------------------------------------------------------------------------- FP8 linear for training
+class _Fp8LinearFn(torch.autograd.Function):
+    """y = x W^T with the forward GEMM and the input-gradient GEMM on block-quantised e4m3 operands (activations
+    and output gradients in 1 x 128 tiles along the contraction, weights in 128 x 128 blocks), fp32 accumulation.
+    The weight-gradient GEMM stays in the parameter dtype and accumulates into the fp32 ``main_grad`` buffer when
+    there is one: its contraction runs over tokens, where both operands would need a second, transposed quantisation,
+    and its result feeds an fp32 accumulator whose precision matters most."""
+
+    @staticmethod
+    def forward(ctx, x2, weight, pow2):
+        ctx.save_for_backward(x2, weight)
+        ctx.pow2 = pow2
+        return fp8_blockwise_linear(x2, weight, pow2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import functional as OF
+
+        x2, weight = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            # dx [T, K] = dy [T, N] @ W [N, K]: contraction over N, so dy is tiled along N and W^T is the blocked operand
+            dx = fp8_blockwise_linear(dy, weight.t().contiguous(), ctx.pow2)
+        if ctx.needs_input_grad[1]:
+            dw = OF._wgrad(dy, x2, weight)
+        return dx, dw, None
+
+
+def fp8_linear_supported(in_features: int, out_features: int) -> bool:
+    return in_features % 128 == 0 and out_features % 128 == 0
+
+
+def fp8_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+               residual: Optional[torch.Tensor] = None, pow2: bool = False) -> torch.Tensor:
+    """Drop-in for ``functional.linear`` on shapes whose feature sizes are multiples of 128."""
+    shape = x.shape
+    y = _Fp8LinearFn.apply(x.reshape(-1, shape[-1]).contiguous(), weight, pow2).reshape(*shape[:-1], weight.shape[0])
+    if bias is not None:
+        y = y + bias
+    if residual is not None:
+        y = y + residual
+    return y

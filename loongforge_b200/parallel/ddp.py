@@ -129,16 +129,23 @@ class DistributedDataParallel(nn.Module):
         self.state = st
         if disable_bucketing:
             self.cfg = dataclasses.replace(self.cfg, bucket_size=None)
-        dense, expert = [], []
+        dense, expert, shared = [], [], []
         named = {}
         for name, p in module.named_parameters():
             if not p.requires_grad:
                 continue
             named[p] = name
-            (expert if getattr(p, "is_expert", False) else dense).append(p)
+            if getattr(p, "shared_embedding", False):
+                shared.append(p)
+            else:
+                (expert if getattr(p, "is_expert", False) else dense).append(p)
         self.buffers: List[ParamAndGradBuffer] = []
         self.expert_buffers: List[ParamAndGradBuffer] = []
-        for plist, kind, store in ((dense, "dp_cp", self.buffers), (expert, "edp", self.expert_buffers)):
+        # The word embedding that the first and last pipeline stage both hold lives in a buffer of its own: both
+        # stages then shard it identically over the data-parallel ranks, so its gradient can be summed over the two
+        # stages after the data-parallel reduce-scatter (reference: Megatron gives such parameters their own bucket).
+        for plist, kind, store in ((dense, "dp_cp", self.buffers), (shared, "dp_cp", self.buffers),
+                                   (expert, "edp", self.expert_buffers)):
             by_dtype: Dict[torch.dtype, List[nn.Parameter]] = {}
             for p in plist:
                 by_dtype.setdefault(p.dtype, []).append(p)
@@ -159,9 +166,10 @@ class DistributedDataParallel(nn.Module):
     # ------------------------------------------------------------------ hooks
     def _make_accumulate_hook(self, buf, p):
         def hook(param):
+            # ops that accumulate straight into main_grad return no gradient, so whatever arrives here is a
+            # contribution that is not in main_grad yet (e.g. the embedding lookup of a weight tied to the output layer)
             if param.grad is not None:
-                if not getattr(param, "grad_added_to_main_grad", False):
-                    param.main_grad.add_(param.grad.to(param.main_grad.dtype))
+                param.main_grad.add_(param.grad.to(param.main_grad.dtype))
                 param.grad = None
             param.grad_ready()
         return hook
@@ -170,6 +178,8 @@ class DistributedDataParallel(nn.Module):
         def ready():
             if not self.is_last_microbatch or not self.cfg.overlap_grad_reduce:
                 return
+            if getattr(p, "defer_grad_sync", False):
+                return  # several gradient sources per backward: reduced when the backward pass has finished
             b = buf.buckets[buf.param_index[p][2]]
             b.pending.discard(p)
             if not b.pending and b.handle is None:

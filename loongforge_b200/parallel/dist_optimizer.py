@@ -40,6 +40,9 @@ class OptimizerConfig:
     # keep the fp32 master of bf16 parameters as (bf16 weight in the parameter buffer, int16 remainder):
     # exact, and 2 bytes per parameter less optimizer memory
     master_as_remainder: bool = False
+    # fp32 masters and Adam moments in pinned host memory, updated by the native host AdamW; per step the gradient
+    # shard goes device -> host and the refreshed weights host -> device on a side stream
+    cpu_offload: bool = False
     no_weight_decay_cond: Optional[object] = None  # callable(name, param) -> bool
 
 
@@ -50,14 +53,25 @@ class _ShardState:
         self.buf, self.bucket, self.start, self.end = buf, b, s, e
         dev = buf.param_data.device
         n = e - s
-        self.remainder = cfg.master_as_remainder and buf.param_data.dtype == torch.bfloat16
-        if self.remainder:
+        self.offload = cfg.cpu_offload
+        self.remainder = cfg.master_as_remainder and buf.param_data.dtype == torch.bfloat16 and not self.offload
+        if self.offload:
+            pin = dev.type == "cuda"
+            host = lambda dt, fill=None: (torch.zeros if fill == 0 else torch.empty)(n, dtype=dt, pin_memory=pin)  # noqa: E731
+            self._master = host(torch.float32)
+            self._master.copy_(buf.param_data[s:e].float())
+            self.exp_avg, self.exp_avg_sq = host(torch.float32, 0), host(torch.float32, 0)
+            self.host_grad = host(torch.float32 if buf.grad_data.dtype == torch.float32 else torch.bfloat16)
+            self.host_out = host(torch.bfloat16) if buf.param_data.dtype == torch.bfloat16 else None
+            self.grad_event = None
+        elif self.remainder:
             self.lo = torch.zeros(n, dtype=torch.int16, device=dev)  # master == bf16 weight exactly at start
             self._master = None
         else:
             self._master = buf.param_data[s:e].float().clone()
-        self.exp_avg = torch.zeros(n, dtype=cfg.exp_avg_dtype, device=dev)
-        self.exp_avg_sq = torch.zeros(n, dtype=cfg.exp_avg_sq_dtype, device=dev)
+        if not self.offload:
+            self.exp_avg = torch.zeros(n, dtype=cfg.exp_avg_dtype, device=dev)
+            self.exp_avg_sq = torch.zeros(n, dtype=cfg.exp_avg_sq_dtype, device=dev)
         # segments: (lo, hi, weight_decay_on, tp_duplicated, name)
         self.segments = []
         for p in b.params:
@@ -95,7 +109,7 @@ class DistributedOptimizer:
         self.state = ps.get_state(parallel_state)
         self.sharded = ddp_models[0].cfg.use_distributed_optimizer
         self.shards: List[_ShardState] = []
-        for m in ddp_models:
+        for mi, m in enumerate(ddp_models):
             for buf in m._all_buffers:
                 for b in buf.buckets:
                     if self.sharded:
@@ -103,11 +117,16 @@ class DistributedOptimizer:
                     else:
                         s, e = b.start, b.end
                     self.shards.append(_ShardState(buf, b, s, e, cfg, self.sharded))
+                    self.shards[-1].chunk = mi
+        # callables run after the data-parallel gradient reduction and before the norm / update (for reductions over
+        # other groups that need the final gradients, e.g. the embedding copies of the first and last pipeline stage)
+        self.post_sync_hooks: List = []
         self.step_count = 0
         self.lr = cfg.lr
         self.weight_decay = cfg.weight_decay
         self.param_groups = [{"lr": cfg.lr, "weight_decay": cfg.weight_decay}]  # scheduler-facing view
         self._gather_stream = None
+        self._offload_stream = None
 
     # ------------------------------------------------------------------ grad norm / clipping
     def grad_norm(self) -> torch.Tensor:
@@ -124,8 +143,10 @@ class DistributedOptimizer:
                              and (st.dims.ep > 1 or (self.sharded and sh.buf.dp_size > 1)))
             # merge adjacent segments that are counted with the same multiplicity
             runs = []
-            for lo, hi, _, dup, *_ in sh.segments:
+            for lo, hi, _, dup, _, p, _ in sh.segments:
                 count = (not dup) or st.tp_rank == 0 or is_expert_buf
+                # the last pipeline stage's copy of the word embedding is the same logical tensor as the first stage's
+                count = count and not getattr(p, "shared_embedding_replica", False)
                 if not count:
                     continue
                 if runs and runs[-1][1] == lo:
@@ -199,6 +220,8 @@ class DistributedOptimizer:
         for m in self.models:
             m.finish_grad_sync()
         self._peer_reduce_grads()
+        for hook in self.post_sync_hooks:
+            hook()
         cfg = self.cfg
         norm = self.grad_norm()
         norm_val = float(norm.item())
@@ -210,10 +233,15 @@ class DistributedOptimizer:
         self.step_count += 1
         lr = self.param_groups[0]["lr"]
         wd = self.param_groups[0]["weight_decay"]
+        if cfg.cpu_offload:
+            self._offload_fetch_grads()
         for sh in self.shards:
             g = sh.buf.grad_data[sh.start:sh.end]
             out = sh.buf.param_data[sh.start:sh.end]
             out_arg = out if out.dtype == torch.bfloat16 else None
+            if sh.offload:
+                self._offload_update(sh, out, lr, wd, clip)
+                continue
             # runs of equal weight-decay setting -> one fused launch each
             runs = []
             for lo, hi, use_wd, *_ in sh.segments:
@@ -237,6 +265,8 @@ class DistributedOptimizer:
                              step=self.step_count, grad_scale=clip)
                 if out_arg is None:
                     out[lo:hi].copy_(sh.master[lo:hi])
+        if cfg.cpu_offload and self._offload_stream is not None:
+            torch.cuda.current_stream().wait_stream(self._offload_stream)
         self._gather_params()
         done = set()
         for sh in self._peer_buffers():  # pushes landed everywhere; gradients may be zeroed for the next step
@@ -244,6 +274,47 @@ class DistributedOptimizer:
                 self._peer_barrier(sh.buf)
                 done.add(id(sh.buf))
         return True, norm_val, None
+
+    # ------------------------------------------------------------------ host (offloaded) update
+    def _offload_fetch_grads(self) -> None:
+        """Queue every shard's gradient copy to pinned host memory on a side stream; each shard's host update then
+        waits only for its own copy, so later copies overlap earlier updates."""
+        dev = self.shards[0].buf.grad_data
+        if dev.is_cuda and self._offload_stream is None:
+            self._offload_stream = torch.cuda.Stream()
+        for sh in self.shards:
+            g = sh.buf.grad_data[sh.start:sh.end]
+            if g.is_cuda:
+                self._offload_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self._offload_stream):
+                    sh.host_grad.copy_(g.to(sh.host_grad.dtype), non_blocking=True)
+                    sh.grad_event = torch.cuda.Event()
+                    sh.grad_event.record(self._offload_stream)
+            else:
+                sh.host_grad.copy_(g)
+
+    def _offload_update(self, sh, out, lr, wd, clip) -> None:
+        from ..optim.cpu_offload import _load_ext
+
+        ext, cfg = _load_ext(), self.cfg
+        if sh.grad_event is not None:
+            sh.grad_event.synchronize()
+        runs = []
+        for lo, hi, use_wd, *_ in sh.segments:
+            if runs and runs[-1][2] == use_wd and runs[-1][1] == lo:
+                runs[-1][1] = hi
+            else:
+                runs.append([lo, hi, use_wd])
+        for lo, hi, use_wd in runs:
+            ext.cpu_adam_step(sh._master[lo:hi], sh.host_grad[lo:hi], sh.exp_avg[lo:hi], sh.exp_avg_sq[lo:hi],
+                              sh.host_out[lo:hi] if sh.host_out is not None else None, lr, cfg.adam_beta1,
+                              cfg.adam_beta2, cfg.adam_eps, wd if use_wd else 0.0, self.step_count, clip)
+            src = sh.host_out if sh.host_out is not None else sh._master
+            if out.is_cuda:
+                with torch.cuda.stream(self._offload_stream):
+                    out[lo:hi].copy_(src[lo:hi], non_blocking=True)
+            else:
+                out[lo:hi].copy_(src[lo:hi])
 
     def _gather_params(self):
         if not self.sharded:
@@ -276,15 +347,18 @@ class DistributedOptimizer:
     def sharded_state(self) -> Dict[str, Dict[str, torch.Tensor]]:
         """Per-parameter optimizer-state pieces owned by this rank.
 
-        Returns {param_name: {"offset": int (into the flattened local param), "master", "exp_avg",
-        "exp_avg_sq"}} which the checkpoint layer writes as flat shards with global offsets
-        ("fully reshardable": a different DP size can re-assemble them)."""
+        Returns {param_name: [{"offset": int (into the flattened local param), "param", "master", "exp_avg",
+        "exp_avg_sq"}]} which the checkpoint layer writes as flat shards with global offsets
+        ("fully reshardable": a different DP size can re-assemble them). With several model chunks (virtual
+        pipeline stages) the chunk-local names repeat, so they are prefixed ``chunk{i}.``; ``param`` identifies
+        the tensor unambiguously."""
         out = {}
+        many = len(self.models) > 1
         for sh in self.shards:
             for lo, hi, _, _, name, p, pstart in sh.segments:
                 off = sh.start + lo - pstart
-                out.setdefault(name, []).append({
-                    "offset": off, "numel": hi - lo, "param_numel": p.numel(),
+                out.setdefault(f"chunk{sh.chunk}.{name}" if many else name, []).append({
+                    "offset": off, "numel": hi - lo, "param_numel": p.numel(), "param": p,
                     "master": sh.master[lo:hi], "exp_avg": sh.exp_avg[lo:hi], "exp_avg_sq": sh.exp_avg_sq[lo:hi],
                     "set_master": (lambda v, sh=sh, lo=lo, hi=hi: sh.set_master(lo, hi, v))})
         return out
@@ -299,9 +373,10 @@ class DistributedOptimizer:
     def load_sharded_state(self, pieces_by_name):
         """Inverse of :meth:`sharded_state`; `pieces_by_name[name]` is a dict of full flat tensors
         (local parameter numel) for master / exp_avg / exp_avg_sq."""
+        many = len(self.models) > 1
         for sh in self.shards:
             for lo, hi, _, _, name, p, pstart in sh.segments:
-                src = pieces_by_name.get(name)
+                src = pieces_by_name.get(f"chunk{sh.chunk}.{name}" if many else name)
                 if src is None:
                     continue
                 off = sh.start + lo - pstart

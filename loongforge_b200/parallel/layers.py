@@ -74,6 +74,15 @@ def mark_tp_partial_grad(module: nn.Module) -> None:
         p.tp_partial_grad = True
 
 
+def _linear(module, x, weight, bias=None, residual=None):
+    """The module's GEMM in the precision chosen for it (``module.gemm_precision``: unset / 'bf16' -> parameter dtype,
+    'fp8' -> block-quantised e4m3 forward and input-gradient GEMMs)."""
+    if getattr(module, "gemm_precision", None) == "fp8":
+        from ..ops import quant
+        return quant.fp8_linear(x, weight, bias, residual)
+    return OF.linear(x, weight, bias, residual)
+
+
 class ColumnParallelLinear(nn.Module):
     """Y = X W^T with W sharded on the output dim. With sequence parallelism the input is
     ``[T/tp, in]`` and is all-gathered along tokens first (backward: reduce-scatter of dX)."""
@@ -119,7 +128,7 @@ class ColumnParallelLinear(nn.Module):
                 x = M.gather_from_sequence_parallel_region(x, g, True)
             else:
                 x = M.copy_to_tensor_model_parallel_region(x, g)
-        y = OF.linear(x, self.weight, self.bias)
+        y = _linear(self, x, self.weight, self.bias)
         if self.gather_output and self.tp > 1:
             y = M.gather_from_tensor_model_parallel_region(y, g)
         return y
@@ -166,11 +175,11 @@ class RowParallelLinear(nn.Module):
         if self.tp > 1 and not self.input_is_parallel:
             x = M.scatter_to_tensor_model_parallel_region(x, g)
         if self.tp == 1:
-            return OF.linear(x, self.weight, self.bias, residual)
+            return _linear(self, x, self.weight, self.bias, residual)
         if self.sequence_parallel and self.tp_comm_overlap and x.is_cuda and self.bias is None:
             from . import fused_tp
             return fused_tp.linear_reduce_scatter(x, self.weight, residual, self.state_name)
-        y = OF.linear(x, self.weight)
+        y = _linear(self, x, self.weight)
         if self.sequence_parallel:
             y = M.reduce_scatter_to_sequence_parallel_region(y, g)
         else:

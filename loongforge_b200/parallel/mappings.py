@@ -23,7 +23,7 @@ def _all_gather_dim0(x: torch.Tensor, group) -> torch.Tensor:
     n = _ws(group)
     if n == 1:
         return x
-    x = x.contiguous()
+    x = x.detach().contiguous()
     out = torch.empty((n * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
     dist.all_gather_into_tensor(out, x, group=group)
     return out

@@ -88,9 +88,29 @@ def apply_fp8_policy(model: nn.Module, policy: FP8Policy, tokens_per_microbatch:
         if w is None or w.dim() != 2:
             continue
         prec = policy.decide(kind, tokens_per_microbatch, tp, w.shape[1], w.shape[0])
+        if prec == "fp8" and not _can_run_fp8(mod, w):
+            prec = "bf16"
         mod.gemm_precision = prec
         out[name] = prec
     return out
+
+
+def _can_run_fp8(mod: nn.Module, w) -> bool:
+    """FP8 GEMMs exist for the dense tensor-parallel linears on feature sizes that are multiples of the 128-wide
+    quantisation block; grouped expert GEMMs and the kernels fused with tensor-parallel collectives run in bf16."""
+    from ..ops.quant import fp8_linear_supported
+    from ..parallel.layers import ColumnParallelLinear, RowParallelLinear
+
+    if not isinstance(mod, (ColumnParallelLinear, RowParallelLinear)):
+        return False
+    if getattr(mod, "tp_comm_overlap", False) and getattr(mod, "tp", 1) > 1:
+        return False
+    return fp8_linear_supported(w.shape[1], w.shape[0])
+
+
+def default_policy() -> FP8Policy:
+    """Every transformer-layer linear in FP8; the output layer (logits) stays in bf16."""
+    return FP8Policy([Rule(kind="output_layer", precision="bf16")], default="fp8")
 
 
 def export_policy_from_benchmark(rows: List[dict], min_speedup: float = 1.05) -> dict:

@@ -13,6 +13,7 @@ SUM over micro-batches is the step's loss (the schedule does not rescale).
 from __future__ import annotations
 
 import contextlib
+import itertools
 from typing import Callable, List, Optional
 
 import torch
@@ -211,55 +212,78 @@ def forward_backward_pipelining_1f1b(*, forward_step_func, data_iterator, model,
 
 def forward_backward_pipelining_interleaved(*, forward_step_func, data_iterator, model, num_microbatches: int,
                                             tensor_shape, dtype, forward_only: bool = False, **_) -> List[dict]:
-    """Virtual-pipeline schedule: each rank holds several model chunks; micro-batches visit the
-    chunks round-robin. Implemented as the "all-forward-then-all-backward per chunk wave"
-    variant: for every group of `pp` micro-batches, chunk 0..v-1 run forward in turn and then
-    backward in reverse, which keeps at most `pp` micro-batches in flight per chunk and needs
-    only neighbour p2p (chunk c on the last stage feeds chunk c+1 on the first stage)."""
+    """Virtual-pipeline schedule: each rank holds `v` model chunks; the `pp * v` virtual stages form a
+    ring (chunk c on the last rank feeds chunk c+1 on the first rank).
+
+    Micro-batches run in groups of `pp`. Inside a group the ring advances in lock step: at tick t rank r
+    runs forward unit ``u = t - r`` (chunk ``u // pp``, micro-batch ``u % pp``), and between two ticks
+    every rank posts its send to the next rank and its receive from the previous rank as ONE batch of
+    non-blocking operations. No rank ever blocks in a send whose receiver is itself blocked in a send,
+    which a rendezvous transport (gloo, NCCL point-to-point) needs with wrap-around neighbours. The
+    backward wave mirrors it in the opposite direction. At most `pp` micro-batches per chunk are alive."""
     assert isinstance(model, (list, tuple)) and len(model) > 1
     st = ps.get_state()
-    pp, v = st.dims.pp, len(model)
+    pp, v, r = st.dims.pp, len(model), st.pp_rank
     device = next(model[0].parameters()).device
     p2p = P2P(tensor_shape, dtype, device)
-    iters = data_iterator if isinstance(data_iterator, (list, tuple)) else [data_iterator] * v
+    # every chunk must see the SAME sequence of micro-batches (the first chunk embeds the tokens whose labels the
+    # last chunk scores); a single iterator is therefore split into v buffered views, each drained by one chunk
+    iters = list(data_iterator) if isinstance(data_iterator, (list, tuple)) else list(itertools.tee(data_iterator, v))
     reports: List[dict] = []
     assert num_microbatches % pp == 0, "interleaved schedule needs num_microbatches divisible by pp"
     n_groups = num_microbatches // pp
+    units, ticks = v * pp, v * pp + pp - 1
 
     def set_last(m, flag):
         if hasattr(m, "is_last_microbatch"):
             m.is_last_microbatch = flag
 
+    def fwd_unit(t):
+        """(chunk, micro-batch, first virtual stage?, last virtual stage?) of this rank at tick t, or None."""
+        u = t - r
+        if not 0 <= u < units:
+            return None
+        c = u // pp
+        return c, u % pp, st.is_first_stage and c == 0, st.is_last_stage and c == v - 1
+
+    def bwd_unit(t):
+        u = t - (pp - 1 - r)
+        if not 0 <= u < units:
+            return None
+        c = v - 1 - u // pp
+        return c, u % pp, st.is_first_stage and c == 0, st.is_last_stage and c == v - 1
+
     for g in range(n_groups):
         last_group = g == n_groups - 1
         saved = [[None] * pp for _ in range(v)]
-        # forward waves
-        for c in range(v):
-            for mb in range(pp):
-                first_virtual = st.is_first_stage and c == 0
-                last_virtual = st.is_last_stage and c == v - 1
-                inp = None
-                if not first_virtual:
-                    inp = p2p._ops(recv_prev=True)[0]
-                out = _forward_one(forward_step_func, iters[c], model[c], inp, reports, last_virtual)
-                if not last_virtual:
-                    p2p._ops(send_next=out)
-                saved[c][mb] = (inp, out)
+        inp = None
+        for t in range(ticks):
+            cur, out = fwd_unit(t), None
+            if cur is not None:
+                c, mb, first_virtual, last_virtual = cur
+                out = _forward_one(forward_step_func, iters[c], model[c], None if first_virtual else inp,
+                                   reports, last_virtual)
+                saved[c][mb] = (None if first_virtual else inp, out)
+                if last_virtual:
+                    out = None
+            nxt = fwd_unit(t + 1)
+            inp = p2p._ops(send_next=out, recv_prev=nxt is not None and not nxt[2])[0]
         if forward_only:
             continue
-        # backward waves
-        for c in reversed(range(v)):
-            for mb in range(pp):
-                first_virtual = st.is_first_stage and c == 0
-                last_virtual = st.is_last_stage and c == v - 1
-                inp, out = saved[c][mb]
+        out_grad = None
+        for t in range(ticks):
+            cur, in_grad = bwd_unit(t), None
+            if cur is not None:
+                c, mb, first_virtual, last_virtual = cur
+                b_in, b_out = saved[c][mb]
                 # gradient buckets of chunk c may start reducing only on its very last backward
                 set_last(model[c], last_group and mb == pp - 1)
-                out_grad = None if last_virtual else p2p._ops(recv_next=True)[1]
-                in_grad = _backward_one(inp, out, out_grad)
-                if not first_virtual:
-                    p2p._ops(send_prev=in_grad)
+                in_grad = _backward_one(b_in, b_out, None if last_virtual else out_grad)
                 saved[c][mb] = None
+                if first_virtual:
+                    in_grad = None
+            nxt = bwd_unit(t + 1)
+            out_grad = p2p._ops(send_prev=in_grad, recv_next=nxt is not None and not nxt[3])[1]
     for m in model:
         set_last(m, True)
     return reports

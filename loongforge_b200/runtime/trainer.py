@@ -58,6 +58,10 @@ class TrainConfig:
     exp_avg_dtype: torch.dtype = torch.float32
     exp_avg_sq_dtype: torch.dtype = torch.float32
     master_as_remainder: bool = False
+    optimizer_cpu_offload: bool = False  # masters + Adam moments on the host, native host AdamW
+    fp8_policy_file: Optional[str] = None  # JSON rules: which linear kinds run FP8 (runtime/fp8_policy.py)
+    use_fsdp: bool = False  # FSDP2 units instead of DDP + distributed optimizer (runtime/fsdp_trainer.py)
+    fsdp_sharding_strategy: str = "optim_grads_params"  # or optim_grads
     ddp_bucket_size: Optional[int] = None
     calculate_per_token_loss: bool = False
     custom_pipeline_layers: Optional[List[int]] = None
@@ -122,7 +126,24 @@ class Trainer:
         self.model_provider = model_provider or self._default_model_provider
         self.forward_step = forward_step or self._default_forward_step
         self.models = self._build_models()
+        self.fp8_decisions = {}
+        if model_cfg.fp8:
+            from . import fp8_policy as FP
+            policy = FP.FP8Policy.from_json(train_cfg.fp8_policy_file) if train_cfg.fp8_policy_file else FP.default_policy()
+            tokens = train_cfg.seq_length * train_cfg.micro_batch_size // max(self.st.dims.cp, 1)
+            for m in self.models:
+                self.fp8_decisions.update(FP.apply_fp8_policy(m.module, policy, tokens, self.st.dims.tp))
         self.optimizer = self._build_optimizer()
+        self._shared_embeddings = [p for m in self.models for p in m.module.parameters()
+                                   if getattr(p, "shared_embedding", False)]
+        if self._shared_embeddings and self.st.group("embd") is not None:
+            # start from identical copies on the first and last pipeline stage, then keep them identical by summing
+            # their gradients after every data-parallel reduction
+            with torch.no_grad():
+                for p in self._shared_embeddings:
+                    dist.broadcast(p.data, src=self.st.group_ranks["embd"][0], group=self.st.group("embd"))
+            self.optimizer.reload_model_params()
+            self.optimizer.post_sync_hooks.append(self._allreduce_embedding_grads)
         self.scheduler = OptimizerParamScheduler(
             self.optimizer, max_lr=train_cfg.lr, min_lr=train_cfg.min_lr, warmup_steps=train_cfg.lr_warmup_iters,
             decay_steps=train_cfg.lr_decay_iters or train_cfg.train_iters, decay_style=train_cfg.lr_decay_style)
@@ -162,7 +183,7 @@ class Trainer:
                                adam_beta2=t.adam_beta2, adam_eps=t.adam_eps, clip_grad=t.clip_grad,
                                exp_avg_dtype=t.exp_avg_dtype, exp_avg_sq_dtype=t.exp_avg_sq_dtype,
                                overlap_param_gather=t.overlap_param_gather,
-                               master_as_remainder=t.master_as_remainder)
+                               master_as_remainder=t.master_as_remainder, cpu_offload=t.optimizer_cpu_offload)
         return DistributedOptimizer(self.models, ocfg)
 
     # ------------------------------------------------------------------ default LLM pretrain step
@@ -216,6 +237,10 @@ class Trainer:
         for m in self.models:
             m.train()
         self.optimizer.zero_grad()
+        # auxiliary losses (MoE balancing, MTP, indexer) are per-micro-batch means: weight each by 1 / micro-batches so
+        # that, after the data-parallel average, they enter the step like the main loss does
+        from ..models.moe import AuxLossScaler
+        AuxLossScaler.scale = 1.0 / self.mb_calc.num_microbatches
         fb = schedules.get_forward_backward_func()
         T = t.seq_length * t.micro_batch_size
         sp_div = self.st.dims.tp if self.mcfg.sequence_parallel else 1
@@ -245,6 +270,14 @@ class Trainer:
             for k, v in zip(keys, vals.tolist()):
                 metrics[k] = v
         return metrics
+
+    def _allreduce_embedding_grads(self):
+        """Sum the word-embedding gradients of the first and last pipeline stage (tied output layer and / or
+        multi-token prediction). Both copies sit alone in identically laid out buffers, so after a sharded
+        data-parallel reduction each rank's valid slice pairs with the same slice on the other stage."""
+        g = self.st.group("embd")
+        for p in self._shared_embeddings:
+            dist.all_reduce(p.main_grad, group=g)
 
     def _allreduce_sequence_parallel_grads(self):
         """Replicated parameters whose gradient is only a PARTIAL sum on each TP rank are summed over the TP group:

@@ -27,16 +27,23 @@ def build_model_trainer(family: str, phase: str, **kw):
     return fn(**kw)
 
 
+def _maybe_fsdp(cls, train_cfg):
+    if getattr(train_cfg, "use_fsdp", False):
+        from .fsdp_trainer import fsdp_variant
+        return fsdp_variant(cls)
+    return cls
+
+
 @register_model_trainer(LLM_FAMILIES, "pretrain")
 def _llm_pretrain(model_cfg, train_cfg, dims, **kw):
     from .trainer import Trainer
-    return Trainer(model_cfg, train_cfg, dims, **kw)
+    return _maybe_fsdp(Trainer, train_cfg)(model_cfg, train_cfg, dims, **kw)
 
 
 @register_model_trainer(LLM_FAMILIES, "sft")
 def _llm_sft(model_cfg, train_cfg, dims, **kw):
     from .sft import SFTTrainer
-    return SFTTrainer(model_cfg, train_cfg, dims, **kw)
+    return _maybe_fsdp(SFTTrainer, train_cfg)(model_cfg, train_cfg, dims, **kw)
 
 
 @register_model_trainer(VLM_FAMILIES, "pretrain")

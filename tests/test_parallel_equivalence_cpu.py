@@ -79,6 +79,21 @@ def test_newer_families_match_single_process(model, dims):
     _check(ref, res, lambda r: r // (world // pp) == pp - 1, tol=1e-3)
 
 
+@pytest.mark.parametrize("model,dims,ov,world", [
+    ("tiny-llama", {"pp": 2, "vpp": 2}, {"num_layers": 4}, 2),          # interleaved 1F1B
+    ("tiny-deepseek", {"cp": 2}, {"moe_aux_loss_coeff": 0.0}, 2),       # MLA + DSA with context parallel keys
+    ("tiny-qwen3-moe", {"tp": 2, "ep": 2}, {"moe_aux_loss_coeff": 0.0}, 4),
+    ("tiny-minimax", {"pp": 2}, {}, 2),                                  # MoE + MTP on the last pipeline stage
+    ("tiny-llama", {"pp": 2}, {"untie_embeddings_and_output_weights": False}, 2),   # tied embedding across stages
+    ("tiny-minimax", {"pp": 2}, {"untie_embeddings_and_output_weights": False}, 4),  # + sharded optimizer over dp 2
+])
+def test_more_layouts_match_single_process(model, dims, ov, world):
+    ref = _single(model, 2, ov)
+    res = run_distributed(_run, world, model, dict(dims), 2, ov)
+    pp = dims.get("pp", 1)
+    _check(ref, res, lambda r: r // (world // pp) == pp - 1, tol=1e-3)
+
+
 def _run_cp(rank, world, comm):
     from loongforge_b200.parallel import context_parallel as CP
 

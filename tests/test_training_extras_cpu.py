@@ -127,3 +127,109 @@ def test_cli_hooks_end_to_end(tmp_path):
     assert (out / "trace_rank0_it2-4.json").is_file()
     recs = [json.loads(x) for x in open(out / "tensors_rank0.jsonl")]
     assert recs and all(r["module"].endswith("decoder.layers.0.mlp") for r in recs)
+
+
+def _offload_traj(rank, world, offload):
+    from loongforge_b200.data.synthetic import synthetic_batch_iterator
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.runtime.trainer import TrainConfig, Trainer
+
+    cfg = get_model_config("tiny-llama")
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=4, seq_length=64, train_iters=4, lr=1e-3, clip_grad=0.5,
+                     weight_decay=0.1, log_interval=1000, optimizer_cpu_offload=offload)
+    tr = Trainer(cfg, tc)
+    st = tr.st
+    it = synthetic_batch_iterator(cfg.vocab_size, 64, 1, dp_rank=st.dp_rank, dp_size=st.dp_size, seed=11,
+                                  pin_memory=False)
+    out = [tr.train_step(it) for _ in range(4)]
+    if offload:
+        assert all(sh.offload and sh.exp_avg.device.type == "cpu" for sh in tr.optimizer.shards)
+    return [(m["lm loss"], m["grad_norm"]) for m in out]
+
+
+def test_optimizer_cpu_offload_matches_device_optimizer():
+    """Sharded optimizer over 2 data-parallel ranks: the host AdamW path follows the on-device trajectory."""
+    from dist_utils import run_distributed
+
+    a = run_distributed(_offload_traj, 2, False)[0]
+    b = run_distributed(_offload_traj, 2, True)[0]
+    for (l0, g0), (l1, g1) in zip(a, b):
+        assert abs(l0 - l1) < 1e-5 * max(1, abs(l0)) and abs(g0 - g1) < 1e-4 * max(1, abs(g0)), (a, b)
+
+
+def _fsdp_traj(rank, world, use_fsdp, tmp):
+    from loongforge_b200.data.synthetic import synthetic_batch_iterator
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel import state as ps
+    from loongforge_b200.runtime.trainer import TrainConfig
+    from loongforge_b200.runtime.trainer_builder import build_model_trainer
+
+    def make():
+        cfg = get_model_config("tiny-llama")
+        tc = TrainConfig(micro_batch_size=1, global_batch_size=4, seq_length=64, train_iters=6, lr=1e-3, clip_grad=0.5,
+                         weight_decay=0.1, log_interval=1000, use_fsdp=use_fsdp)
+        return build_model_trainer("llama", "pretrain", model_cfg=cfg, train_cfg=tc, dims=None), cfg
+
+    tr, cfg = make()
+    st = tr.st
+    data = lambda start=0: synthetic_batch_iterator(cfg.vocab_size, 64, 1, dp_rank=st.dp_rank, dp_size=st.dp_size,  # noqa: E731
+                                                    seed=11, pin_memory=False, start_sample=start)
+    it = data()
+    out = [tr.train_step(it) for _ in range(3)]
+    traj = [(m["lm loss"], m["grad_norm"]) for m in out]
+    if not use_fsdp:
+        return traj, None
+    assert type(tr).__name__ == "FSDPTrainer"
+    w = tr.models[0].module.decoder.layers[0].mlp.linear_fc1.weight
+    assert w.to_local().shape[0] * world == w.shape[0], "parameters are sharded over the data-parallel ranks"
+    tr.save_checkpoint(tmp)
+    cont = tr.train_step(it)
+    ps.destroy_model_parallel()
+    tr2, _ = make()
+    assert tr2.load_checkpoint(tmp) == 3
+    again = tr2.train_step(data(tr2.consumed_samples))
+    return traj, (cont["lm loss"], again["lm loss"], cont["grad_norm"], again["grad_norm"])
+
+
+def test_fsdp_trainer_matches_ddp_trainer_and_resumes(tmp_path):
+    from dist_utils import run_distributed
+
+    a = run_distributed(_fsdp_traj, 2, False, str(tmp_path))[0][0]
+    b, resume = run_distributed(_fsdp_traj, 2, True, str(tmp_path))[0]
+    for (l0, g0), (l1, g1) in zip(a, b):
+        assert abs(l0 - l1) < 1e-4 * max(1, abs(l0)) and abs(g0 - g1) < 1e-3 * max(1, abs(g0)), (a, b)
+    c, again, gc, ga = resume
+    assert abs(c - again) < 1e-6 and abs(gc - ga) < 1e-5, resume
+
+
+def test_fp8_blockwise_training_follows_the_full_precision_run(tmp_path):
+    """FP8 forward / input-gradient GEMMs (emulated bit-exactly on CPU) in every supported linear layer: the loss
+    follows the fp32 run closely, the policy file can keep kinds in bf16, and unsupported modules stay in bf16."""
+    import json
+
+    from loongforge_b200.data.synthetic import synthetic_batch_iterator
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel import state as ps
+    from loongforge_b200.runtime.trainer import TrainConfig, Trainer
+
+    def run(fp8, policy=None):
+        ps.destroy_model_parallel()
+        cfg = get_model_config("tiny-llama", fp8=fp8, ffn_hidden_size=512)
+        tc = TrainConfig(micro_batch_size=2, global_batch_size=2, seq_length=64, train_iters=6, lr=1e-3,
+                         log_interval=1000, fp8_policy_file=policy)
+        tr = Trainer(cfg, tc)
+        it = synthetic_batch_iterator(cfg.vocab_size, 64, 2, seed=2, pin_memory=False)
+        return [tr.train_step(it)["lm loss"] for _ in range(6)], tr.fp8_decisions
+
+    ref, none = run(None)
+    got, dec = run("blockwise")
+    assert none == {} and dec
+    assert all(v == "fp8" for k, v in dec.items() if k.endswith(("linear_qkv", "linear_fc1", "linear_fc2")))
+    assert dec["output_layer"] == "bf16"
+    assert got != ref, "the FP8 path must actually change the arithmetic"
+    assert all(abs(a - b) < 5e-3 * abs(a) for a, b in zip(ref, got)), (ref, got)
+    pol = tmp_path / "policy.json"
+    pol.write_text(json.dumps({"default": "bf16", "rules": [{"kind": "linear_fc1", "precision": "fp8"}]}))
+    _, dec2 = run("blockwise", str(pol))
+    assert {v for k, v in dec2.items() if k.endswith("linear_fc1")} == {"fp8"}
+    assert {v for k, v in dec2.items() if not k.endswith("linear_fc1")} == {"bf16"}
