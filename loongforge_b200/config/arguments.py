@@ -87,6 +87,8 @@ def _add_parallel_args(p):
     g.add_argument("--pipeline-model-parallel-layout", type=str, default=None)
     g.add_argument("--custom-pipeline-layers", type=str, default=None)
     g.add_argument("--custom-pipeline-recompute-layers", type=str, default=None)
+    g.add_argument("--custom-virtual-pipeline-layers", type=str, default=None,
+                   help="layers per virtual stage: every pipeline rank's chunk 0, then every rank's chunk 1, ...")
     g.add_argument("--context-parallel-size", type=int, default=1)
     g.add_argument("--cp-comm-type", type=str, default="auto")
     g.add_argument("--context-parallel-ulysses-degree", type=int, default=None)

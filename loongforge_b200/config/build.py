@@ -164,7 +164,16 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
                         cp=args.context_parallel_size, ep=args.expert_model_parallel_size,
                         etp=args.expert_tensor_parallel_size, vpp=args.num_virtual_stages_per_pipeline_rank)
     dt = {"fp32": torch.float32, "bf16": torch.bfloat16}
-    custom_layers = [int(x) for x in args.custom_pipeline_layers.split(",")] if args.custom_pipeline_layers else None
+    from ..parallel.pipeline_layout import resolve_stage_layers
+    _ints = lambda v: [int(x) for x in v.split(",") if x.strip()] if v else None  # noqa: E731
+    custom_layers = resolve_stage_layers(
+        cfg.num_layers, dims.pp, dims.vpp or 1, layout=getattr(args, "pipeline_model_parallel_layout", None),
+        custom_pipeline_layers=_ints(args.custom_pipeline_layers),
+        custom_virtual_pipeline_layers=_ints(getattr(args, "custom_virtual_pipeline_layers", None)),
+        mtp_num_layers=cfg.mtp_num_layers)
+    recompute_layers = _ints(getattr(args, "custom_pipeline_recompute_layers", None))
+    if recompute_layers is not None and len(recompute_layers) != dims.pp:
+        raise ValueError("--custom-pipeline-recompute-layers needs one count per pipeline stage")
     tc = TrainConfig(
         micro_batch_size=args.micro_batch_size, global_batch_size=args.global_batch_size or args.micro_batch_size,
         seq_length=args.seq_length or cfg.max_position_embeddings, train_iters=args.train_iters or 0, lr=args.lr,
@@ -175,13 +184,15 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
         ckpt_format="torch_dist" if args.ckpt_format in ("torch_dist", "torch_dcp") else args.ckpt_format,
         async_save=bool(getattr(args, "async_save", False)),
         fp8_policy_file=getattr(args, "fp8_dynamic_policy_path", None),
+        chunkpipe_chunks=(max(1, args.seq_length // int(args.chunksize))
+                          if getattr(args, "enable_chunkpipe", False) and getattr(args, "chunksize", None) else 0),
         optimizer_cpu_offload=bool(getattr(args, "optimizer_cpu_offload", False)),
         use_fsdp=bool(getattr(args, "use_torch_fsdp2", False) or getattr(args, "use_megatron_fsdp", False)),
         fsdp_sharding_strategy=getattr(args, "data_parallel_sharding_strategy", None) or "optim_grads_params",
         use_distributed_optimizer=args.use_distributed_optimizer, overlap_grad_reduce=args.overlap_grad_reduce,
         overlap_param_gather=args.overlap_param_gather, exp_avg_dtype=dt[args.exp_avg_dtype],
         exp_avg_sq_dtype=dt[args.exp_avg_sq_dtype], calculate_per_token_loss=args.calculate_per_token_loss,
-        custom_pipeline_layers=custom_layers, training_phase=args.training_phase, log_throughput=True)
+        custom_pipeline_layers=custom_layers, custom_pipeline_recompute_layers=recompute_layers, training_phase=args.training_phase, log_throughput=True)
     from .validators import validate
     validate(args, cfg, tc, dims)
     return cfg, tc, dims, raw

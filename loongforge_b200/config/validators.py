@@ -55,7 +55,6 @@ def validate(args, cfg, tc, dims) -> None:
 # Flags that are accepted for command-line compatibility but whose feature is reached through a library entry point
 # rather than the training CLI today. Nothing is ignored silently: `unwired_flag_notes` lists what was requested.
 _LIBRARY_ONLY = {
-    "enable_chunkpipe": "sequence-chunk pipelining: runtime.chunkpipe.chunkpipe_forward_backward",
     "enable_full_hetero_dp": "full heterogeneous encoder DP: runtime.hetero_dp.FullHeteroEncoderRunner",
     "use_vlm_dp_balance": "data-parallel load balancing: data.dp_balance.rebalance",
     "enable_cuda_graph": "CUDA graphs: runtime.cuda_graphs.GraphedCallable / embodied.cuda_graph.MicrobatchGraphRunner",

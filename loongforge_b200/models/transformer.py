@@ -223,7 +223,7 @@ class SelfAttention(nn.Module):
         if self.q_layernorm is None:
             if rotary is not None:
                 qkv = self._rope_packed(qkv, rotary)
-            if ps.get_state().dims.cp == 1 and OF.attention_packed_supported(qkv, d):
+            if ps.get_state().dims.cp == 1 and not CHUNK_PREFIX["active"] and OF.attention_packed_supported(qkv, d):
                 # tcgen05 attention reads q/k/v straight out of the packed GEMM output
                 o = OF.attention_packed(qkv, g, r, causal=cfg.causal, scale=self.scale, cu_seqlens=cu)
                 return self.linear_proj(o.view(T, g * r * d), residual)
@@ -264,9 +264,23 @@ class SelfAttention(nn.Module):
         return OF.rope(pk, f, group=self.r + 2, rope_in_group=self.r + 1, inplace=True, head_dim=self.d, **kw)
 
 
+# Sequence-chunk pipelining (runtime/chunkpipe.py): while "active", every attention call sees the keys / values of
+# the sequence's earlier chunks as a prefix ("past") and publishes its own keys / values ("out").
+CHUNK_PREFIX = {"active": False, "past": None, "out": None}
+
+
 def core_attention(q, k, v, *, causal, scale, cu_seqlens, cfg: Optional[TransformerConfig] = None):
     """Attention over packed tokens; context parallelism is applied here when enabled."""
     st = ps.get_state()
+    if CHUNK_PREFIX["active"]:
+        from ..parallel.context_parallel import _masked_attention
+        assert cu_seqlens is None and st.dims.cp == 1, "chunk pipelining runs one unpacked sequence per micro-batch"
+        past, T = CHUNK_PREFIX["past"], q.shape[0]
+        CHUNK_PREFIX["out"] = (k, v)
+        kk, vv = (torch.cat([past[0], k]), torch.cat([past[1], v])) if past is not None else (k, v)
+        P = kk.shape[0] - T
+        pos = torch.arange(P + T, device=q.device)
+        return _masked_attention(q, kk, vv, pos[P:], pos, scale, causal)
     if st.dims.cp > 1:
         from ..parallel import context_parallel as CP
         return CP.ring_attention(q, k, v, causal=causal, scale=scale, cu_seqlens=cu_seqlens)

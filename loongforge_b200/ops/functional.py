@@ -611,6 +611,10 @@ def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: tor
     reduces it in its own backward.
     """
     valid_v = weight.shape[0] if valid_vocab is None else valid_vocab
+    if not torch.is_grad_enabled():
+        # the gradients are computed in the forward pass: make sure an evaluation-only call computes (and accumulates
+        # into main_grad) none
+        hidden, weight = hidden.detach(), weight.detach()
     return _LinearCEFn.apply(hidden, weight, labels, loss_mask, vocab_start, valid_v, tp_group, chunk_tokens,
                              fused_scale)
 

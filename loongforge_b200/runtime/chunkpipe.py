@@ -119,3 +119,45 @@ def chunkpipe_forward_backward(layers: Sequence[nn.Module], embed: Callable[[tor
 def num_microbatches_with_chunks(num_microbatches: int, num_chunks: int) -> int:
     """The pipeline schedule sees every chunk as a micro-batch of its own."""
     return num_microbatches * num_chunks
+
+
+# ----------------------------------------------------------------------------- GPT models
+def gpt_chunkpipe_step(model: nn.Module, tokens: torch.Tensor, position_ids: torch.Tensor, labels: torch.Tensor,
+                       loss_mask: torch.Tensor, num_chunks: int, loss_scale: float) -> torch.Tensor:
+    """One micro-batch (ONE sequence, flat ``[T]`` tensors) of a single-stage GPT model through the chunk pipeline:
+    accumulates the gradients of ``loss_scale * sum(loss * mask)`` and returns that loss value. Attention layers
+    take the earlier chunks' keys / values through ``models.transformer.CHUNK_PREFIX``; every other sub-layer (norms,
+    dense and MoE MLPs, the fused linear + cross-entropy head) is token-local and runs on the chunk alone."""
+    from ..models import transformer as TF
+
+    cfg = model.cfg
+    assert model.pre_process and model.post_process, "chunk pipelining needs the whole model on this rank"
+    assert not (cfg.multi_latent_attention or cfg.enable_hyper_connections or cfg.csa_compress_ratios
+                or cfg.layer_types or cfg.full_attention_interval or cfg.mtp_num_layers), \
+        "chunk pipelining covers softmax-attention GPT layers"
+    dev = tokens.device
+    mask_f = loss_mask.float()
+
+    class _Layer:
+        def __init__(self, layer):
+            self.layer = layer
+
+        def __call__(self, x, past, offset):
+            T = x.shape[0]
+            rotary = model.build_rotary(position_ids[..., offset:offset + T], position_ids.shape[-1], dev)
+            TF.CHUNK_PREFIX.update(active=True, past=past, out=None)
+            try:
+                y = self.layer(x, rotary, None)
+                return y, TF.CHUNK_PREFIX["out"]
+            finally:
+                TF.CHUNK_PREFIX.update(active=False, past=None, out=None)
+
+    def loss_fn(hidden, s, e):
+        if model.decoder.final_layernorm is not None:
+            hidden = model.decoder.final_layernorm(hidden)
+        losses = model.postprocess(hidden, labels[s:e], loss_mask[s:e], loss_scale)
+        return (losses * mask_f[s:e]).sum() * loss_scale
+
+    total = chunkpipe_forward_backward([_Layer(l) for l in model.decoder.layers], model.embed, loss_fn, tokens,
+                                       num_chunks)
+    return torch.tensor(total, device=dev)

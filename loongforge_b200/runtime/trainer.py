@@ -6,6 +6,7 @@ entry points are ``Trainer`` (programmatic) and ``loongforge_b200.train`` (CLI).
 """
 from __future__ import annotations
 
+import copy
 import dataclasses
 import math
 import os
@@ -60,11 +61,13 @@ class TrainConfig:
     master_as_remainder: bool = False
     optimizer_cpu_offload: bool = False  # masters + Adam moments on the host, native host AdamW
     fp8_policy_file: Optional[str] = None  # JSON rules: which linear kinds run FP8 (runtime/fp8_policy.py)
+    chunkpipe_chunks: int = 0  # > 1: every sequence runs as that many chunks (runtime/chunkpipe.py)
     use_fsdp: bool = False  # FSDP2 units instead of DDP + distributed optimizer (runtime/fsdp_trainer.py)
     fsdp_sharding_strategy: str = "optim_grads_params"  # or optim_grads
     ddp_bucket_size: Optional[int] = None
     calculate_per_token_loss: bool = False
     custom_pipeline_layers: Optional[List[int]] = None
+    custom_pipeline_recompute_layers: Optional[List[int]] = None  # recomputed layers per pipeline stage
     training_phase: str = "pretrain"
     log_throughput: bool = True
     check_for_nan_in_loss: bool = True
@@ -161,7 +164,18 @@ class Trainer:
     def _build_models(self) -> List[DistributedDataParallel]:
         st = self.st
         pp, vpp = st.dims.pp, st.dims.vpp or 1
-        splits = pipeline_layer_split(self.mcfg.num_layers, pp * vpp, self.tcfg.custom_pipeline_layers)
+        custom = self.tcfg.custom_pipeline_layers
+        if custom and len(custom) == pp and vpp > 1:  # counts per pipeline rank -> per virtual stage
+            from ..parallel.pipeline_layout import split_rank_layers_over_virtual_stages
+            custom = split_rank_layers_over_virtual_stages(custom, vpp)
+        splits = pipeline_layer_split(self.mcfg.num_layers, pp * vpp, custom)
+        rec = self.tcfg.custom_pipeline_recompute_layers
+        if rec:
+            # per-stage number of recomputed layers (stages near the pipeline's start hold more activations in flight)
+            self.mcfg = copy.copy(self.mcfg)
+            self.mcfg.recompute_granularity = "full"
+            self.mcfg.recompute_method = self.mcfg.recompute_method or "block"
+            self.mcfg.recompute_num_layers = rec[st.pp_rank]
         chunks = []
         for v in range(vpp):
             virt = v * pp + st.pp_rank
@@ -244,12 +258,15 @@ class Trainer:
         fb = schedules.get_forward_backward_func()
         T = t.seq_length * t.micro_batch_size
         sp_div = self.st.dims.tp if self.mcfg.sequence_parallel else 1
-        reports = fb(forward_step_func=self.forward_step, data_iterator=data_iterator,
-                     model=self.models if len(self.models) > 1 else self.models[0],
-                     num_microbatches=self.mb_calc.num_microbatches,
-                     tensor_shape=(T // sp_div // self.st.dims.cp, self.mcfg.hidden_size *
-                                   (self.mcfg.num_residual_streams if self.mcfg.enable_hyper_connections else 1)),
-                     dtype=self.mcfg.params_dtype)
+        if t.chunkpipe_chunks and t.chunkpipe_chunks > 1:
+            reports = self._chunkpipe_microbatches(data_iterator)
+        else:
+            reports = fb(forward_step_func=self.forward_step, data_iterator=data_iterator,
+                         model=self.models if len(self.models) > 1 else self.models[0],
+                         num_microbatches=self.mb_calc.num_microbatches,
+                         tensor_shape=(T // sp_div // self.st.dims.cp, self.mcfg.hidden_size *
+                                       (self.mcfg.num_residual_streams if self.mcfg.enable_hyper_connections else 1)),
+                         dtype=self.mcfg.params_dtype)
         self._allreduce_sequence_parallel_grads()
         ok, grad_norm, _ = self.optimizer.step()
         if ok:
@@ -270,6 +287,30 @@ class Trainer:
             for k, v in zip(keys, vals.tolist()):
                 metrics[k] = v
         return metrics
+
+    def _chunkpipe_microbatches(self, data_iterator) -> List[dict]:
+        """Sequence-chunk pipelining instead of whole-sequence micro-batches: each sequence is cut into
+        ``chunkpipe_chunks`` chunks whose activations live one at a time (long-context training on one stage).
+        Gradient reduction starts only after the last chunk of the last micro-batch (every chunk's backward adds to
+        every parameter), i.e. in the optimizer's ``finish_grad_sync``."""
+        from .chunkpipe import gpt_chunkpipe_step
+
+        t, st = self.tcfg, self.st
+        if st.dims.pp > 1 or st.dims.cp > 1 or st.dims.tp > 1 or t.micro_batch_size != 1:
+            raise ValueError("chunk pipelining needs pp = cp = tp = 1 and micro batch size 1")
+        model = self.models[0]
+        nmb = self.mb_calc.num_microbatches
+        reports = []
+        with model.no_sync():
+            for _ in range(nmb):
+                b = self.get_batch(data_iterator)
+                mask = b["loss_mask"].reshape(-1)
+                n_valid = b.get("num_valid_tokens") or int(mask.numel())
+                scale = 1.0 / (max(n_valid, 1) * nmb)
+                loss = gpt_chunkpipe_step(model.module, b["tokens"].reshape(-1), b["position_ids"].reshape(-1),
+                                          b["labels"].reshape(-1), mask, t.chunkpipe_chunks, scale)
+                reports.append({"lm loss": loss * nmb, "num_tokens": n_valid})
+        return reports
 
     def _allreduce_embedding_grads(self):
         """Sum the word-embedding gradients of the first and last pipeline stage (tied output layer and / or
