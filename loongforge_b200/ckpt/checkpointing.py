@@ -93,6 +93,16 @@ def _props(t: torch.Tensor) -> TensorProperties:
                             memory_format=torch.contiguous_format, pin_memory=False)
 
 
+def _param_tp(p: torch.Tensor, st) -> Tuple[int, int]:
+    """(rank, size) of the tensor-parallel sharding of THIS parameter: the owning module's own degree when it recorded
+    one (expert tensor parallelism, encoders with their own TP degree), else the job's main TP."""
+    if hasattr(p, "tp_shards"):
+        return p.tp_shard_rank, p.tp_shards
+    if getattr(p, "is_expert", False):
+        return st.etp_rank, st.dims.etp
+    return st.tp_rank, st.dims.tp
+
+
 def param_global_layout(p: torch.Tensor, tp_rank: int, tp_size: int):
     """[(global_offsets, local_slice)] pieces of parameter `p` in its unsharded tensor, and the global shape."""
     shape = list(p.shape)
@@ -204,10 +214,12 @@ def build_save_state(trainer, stage: bool = False) -> Dict[str, object]:
     for key, p in model_param_items(trainer):
         is_expert = getattr(p, "is_expert", False)
         writer = (st.edp_rank == 0) if is_expert else dp_writer
-        pieces, gshape = param_global_layout(p, st.etp_rank if is_expert else tpr, st.dims.etp if is_expert else tp)
+        p_rank, p_size = _param_tp(p, st)
+        pieces, gshape = param_global_layout(p, p_rank, p_size)
         gshapes[key] = gshape
         dup = not getattr(p, "tensor_model_parallel", False)
-        if not writer or (dup and (st.etp_rank if is_expert else tpr) != 0):
+        # replicas beyond the tensor's own sharding degree do not write (a TP-1 encoder beside a TP-2 decoder)
+        if not writer or (st.etp_rank if is_expert else tpr) >= (1 if dup else p_size):
             continue
         if getattr(p, "shared_embedding_replica", False):
             continue
@@ -373,7 +385,7 @@ def load_checkpoint(root: str, trainer, *, load_optim: bool = True, load_rng: bo
     targets = []
     for key, p in model_param_items(trainer):
         is_expert = getattr(p, "is_expert", False)
-        pieces, gshape = param_global_layout(p, st.etp_rank if is_expert else tpr, st.dims.etp if is_expert else tp)
+        pieces, gshape = param_global_layout(p, *_param_tp(p, st))
         bufs = [(off, torch.empty_like(p.detach()[sl], device="cpu").contiguous()) for off, sl in pieces]
         state[key] = make_sharded(bufs, gshape, rank)
         targets.append((p, pieces, bufs))

@@ -186,6 +186,7 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
         fp8_policy_file=getattr(args, "fp8_dynamic_policy_path", None),
         chunkpipe_chunks=(max(1, args.seq_length // int(args.chunksize))
                           if getattr(args, "enable_chunkpipe", False) and getattr(args, "chunksize", None) else 0),
+        dp_balance=bool(getattr(args, "use_vlm_dp_balance", False)),
         optimizer_cpu_offload=bool(getattr(args, "optimizer_cpu_offload", False)),
         use_fsdp=bool(getattr(args, "use_torch_fsdp2", False) or getattr(args, "use_megatron_fsdp", False)),
         fsdp_sharding_strategy=getattr(args, "data_parallel_sharding_strategy", None) or "optim_grads_params",

@@ -55,8 +55,6 @@ def validate(args, cfg, tc, dims) -> None:
 # Flags that are accepted for command-line compatibility but whose feature is reached through a library entry point
 # rather than the training CLI today. Nothing is ignored silently: `unwired_flag_notes` lists what was requested.
 _LIBRARY_ONLY = {
-    "enable_full_hetero_dp": "full heterogeneous encoder DP: runtime.hetero_dp.FullHeteroEncoderRunner",
-    "use_vlm_dp_balance": "data-parallel load balancing: data.dp_balance.rebalance",
     "enable_cuda_graph": "CUDA graphs: runtime.cuda_graphs.GraphedCallable / embodied.cuda_graph.MicrobatchGraphRunner",
     "overlap_moe_expert_parallel_comm": "A2A overlap plan: runtime.a2a_overlap.interleave / OverlapExecutor",
 }

@@ -36,16 +36,19 @@ class CostModel:
         return self.coef
 
 
-def solve_assignment(lengths_per_rank: Sequence[Sequence[int]], model: CostModel) -> List[List[Tuple[int, int]]]:
+def solve_assignment(lengths_per_rank: Sequence[Sequence[int]], model: CostModel,
+                     capacity: int = 0) -> List[List[Tuple[int, int]]]:
     """-> for every destination rank the list of (source rank, index in source) it should process. Deterministic, so
-    every rank computes the same plan from the same gathered lengths."""
+    every rank computes the same plan from the same gathered lengths. ``capacity`` > 0 caps the number of items per
+    rank (whole micro-batches are moved and every rank must keep the same micro-batch count)."""
     world = len(lengths_per_rank)
     items = [(float(model.cost([n])[0]), r, i) for r, ls in enumerate(lengths_per_rank) for i, n in enumerate(ls)]
     items.sort(key=lambda t: (-t[0], t[1], t[2]))
     load = [0.0] * world
     plan: List[List[Tuple[int, int]]] = [[] for _ in range(world)]
     for c, r, i in items:
-        d = min(range(world), key=lambda k: (load[k], k))
+        open_ranks = [k for k in range(world) if not capacity or len(plan[k]) < capacity]
+        d = min(open_ranks, key=lambda k: (load[k], k))
         plan[d].append((r, i))
         load[d] += c
     for p in plan:
@@ -89,3 +92,101 @@ def balance_vit_images(patch_counts_per_rank: Sequence[Sequence[int]]) -> List[L
     """Encoder-level balance: images are spread so that every rank encodes a similar number of patches (cost linear in
     patches for windowed attention)."""
     return solve_assignment(patch_counts_per_rank, CostModel(0.0, 1.0, 0.0))
+
+
+# ----------------------------------------------------------------------------- whole micro-batches
+class BalancedMicrobatchIterator:
+    """Wraps a rank's micro-batch iterator: once per step (every ``num_microbatches`` pulls) the data-parallel ranks
+    publish the token counts of their micro-batches, solve one assignment with the same micro-batch count per rank,
+    and trade whole micro-batches so that the most expensive ones do not pile up on one rank (reference hook:
+    loongforge/data/dp_balance/train_hooks.py:117-181; plan and exchange: rebalance/balance.py:275-737).
+
+    A micro-batch is a dict of tensors (any shapes; e.g. tokens / labels / loss_mask / position_ids / cu_seqlens, pixel
+    patches and their grids for VLMs) plus plain Python values, which travel with it. Integer and boolean tensors move
+    as one int64 payload, floating tensors as one float32 payload: two variable-size all-to-alls per step. The
+    micro-batch SET of the step is unchanged, so the step's loss and gradients are those of the unbalanced run."""
+
+    def __init__(self, iterator, num_microbatches: int, group=None, model: CostModel = None, length_key: str = "tokens"):
+        self.it, self.nmb, self.group = iterator, num_microbatches, group
+        self.model = model or CostModel()
+        self.length_key = length_key
+        self.buffer: List[dict] = []
+        self.last_imbalance = (1.0, 1.0)  # (before, after) of the latest step
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        if not self.buffer:
+            self.buffer = self._exchange([next(self.it) for _ in range(self.nmb)])
+        return self.buffer.pop(0)
+
+    # -- (de)serialisation of one micro-batch
+    @staticmethod
+    def _pack(b: dict):
+        meta, ints, floats, plain = [], [], [], {}
+        for k, v in b.items():
+            if not torch.is_tensor(v):
+                plain[k] = v
+                continue
+            is_f = v.is_floating_point()
+            meta.append((k, str(v.dtype).replace("torch.", ""), tuple(v.shape), is_f))
+            (floats if is_f else ints).append(v.detach().reshape(-1).to("cpu", torch.float32 if is_f else torch.int64))
+        cat = lambda xs, dt: torch.cat(xs) if xs else torch.empty(0, dtype=dt)  # noqa: E731
+        return meta, plain, cat(ints, torch.int64), cat(floats, torch.float32)
+
+    @staticmethod
+    def _unpack(meta, plain, ints: torch.Tensor, floats: torch.Tensor) -> dict:
+        out, oi, of = dict(plain), 0, 0
+        for k, dt, shape, is_f in meta:
+            n = 1
+            for d in shape:
+                n *= d
+            if is_f:
+                out[k], of = floats[of:of + n].view(shape).to(getattr(torch, dt)), of + n
+            else:
+                out[k], oi = ints[oi:oi + n].view(shape).to(getattr(torch, dt)), oi + n
+        return out
+
+    def _exchange(self, batches: List[dict]) -> List[dict]:
+        g = self.group
+        if not dist.is_initialized() or dist.get_world_size(g) == 1:
+            return batches
+        from ..parallel.mappings import all_to_all_single
+
+        g = g if g is not None else dist.group.WORLD
+        world, rank = dist.get_world_size(g), dist.get_rank(g)
+        packed = [self._pack(b) for b in batches]
+        mine = [(int(b[self.length_key].numel()), m, pl, int(i.numel()), int(f.numel()))
+                for b, (m, pl, i, f) in zip(batches, packed)]
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine, group=g)
+        lengths = [[it[0] for it in r] for r in gathered]
+        plan = solve_assignment(lengths, self.model, capacity=self.nmb)
+        after = [[lengths[r][i] for (r, i) in plan[d]] for d in range(world)]
+        self.last_imbalance = (imbalance(lengths, self.model), imbalance(after, self.model))
+        send = [[i for (r, i) in plan[d] if r == rank] for d in range(world)]
+        recv = [[(r, i) for (r, i) in plan[rank] if r == src] for src in range(world)]
+        payloads = []
+        for which, dt in ((2, torch.int64), (3, torch.float32)):
+            ins = [torch.cat([packed[i][which] for i in idx]) if idx else torch.empty(0, dtype=dt) for idx in send]
+            out_sizes = [sum(gathered[r][i][which + 1] for (r, i) in pairs) for pairs in recv]
+            flat = torch.empty(sum(out_sizes), dtype=dt)
+            dev = _comm_device(g)
+            src = torch.cat(ins).to(dev)
+            dst = flat.to(dev)
+            all_to_all_single(dst, src, out_sizes, [int(c.numel()) for c in ins], g)
+            payloads.append(dst.cpu())
+        out, oi, of = [], 0, 0
+        for pairs in recv:
+            for (r, i) in pairs:
+                _, meta, plain, ni, nf = gathered[r][i]
+                out.append(self._unpack(meta, plain, payloads[0][oi:oi + ni], payloads[1][of:of + nf]))
+                oi, of = oi + ni, of + nf
+        return out
+
+
+def _comm_device(group) -> torch.device:
+    """Tensors of a collective must live where the group's backend works: the GPU for NCCL, the host for gloo."""
+    backend = dist.get_backend(group)
+    return torch.device("cuda", torch.cuda.current_device()) if "nccl" in str(backend) else torch.device("cpu")

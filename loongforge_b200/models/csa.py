@@ -76,7 +76,8 @@ class Compressor(nn.Module):
         self.score_weight = nn.Parameter(w)
         self.pos_bias = nn.Parameter(torch.zeros(ratio, device=device, dtype=torch.float32))
         for p in (self.score_weight, self.pos_bias):
-            PL.mark_tp(p, None, sequence_parallel=cfg.sequence_parallel)
+            PL.mark_tp(p, None)
+            p.tp_partial_grad = True  # entries feed this rank's heads only
 
     def forward(self, x: torch.Tensor, kv: torch.Tensor, cu_seqlens) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """x [T, hidden], kv [T, dim] -> (entries [M, dim], last token index of each entry [M], sequence
@@ -159,9 +160,11 @@ class CompressedSparseAttention(nn.Module):
         self.linear_kv = nn.Parameter(PL.init_full_then_slice(key + ".linear_kv_proj.weight", (self.d, cfg.hidden_size),
                                                               cfg.init_method_std, **rep))
         for p in (self.linear_q_down, self.linear_kv):
-            PL.mark_tp(p, None, sequence_parallel=cfg.sequence_parallel)
-        self.q_layernorm = Norm(qr, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
-        self.kv_layernorm = Norm(self.d, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
+            PL.mark_tp(p, None)
+        self.q_layernorm = Norm(qr, cfg, device=device)
+        self.kv_layernorm = Norm(self.d, cfg, device=device)
+        for p in (self.linear_q_down, self.linear_kv, *self.q_layernorm.parameters(), *self.kv_layernorm.parameters()):
+            p.tp_partial_grad = True  # whole-sequence input, this rank's heads downstream
         self.linear_q_up = PL.ColumnParallelLinear(qr, self.nq * self.d, bias=False, init_std=cfg.init_method_std,
                                                    key=key + ".linear_q_up_proj", **{**common, "sequence_parallel": False})
         self.linear_proj = PL.RowParallelLinear(self.nq * self.d, cfg.hidden_size, bias=False,
@@ -186,12 +189,18 @@ class CompressedSparseAttention(nn.Module):
 
         cfg = self.cfg
         st = ps.get_state()
-        if cfg.sequence_parallel and st.dims.tp > 1:
-            x = M.gather_from_sequence_parallel_region(x, st.group("tp"), True)
+        # Every rank works on the WHOLE sequence with its own heads: the shared projections (q down, kv, compressor)
+        # are replicated and each rank's gradient for them, and for x, is the partial sum over its heads. The region
+        # mapping below sums the x gradients over the TP ranks in backward; the trainer sums the parameter gradients.
+        if st.dims.tp > 1:
+            x = M.gather_from_sequence_parallel_region(x, st.group("tp"), True) if cfg.sequence_parallel \
+                else M.copy_to_tensor_model_parallel_region(x, st.group("tp"))
         T = x.shape[0]
         cu = packed.cu_seqlens if packed is not None else None
         ql = self.q_layernorm(F.linear(x, self.linear_q_down))
-        q = self.linear_q_up(ql).view(T, self.nq_l, self.d)
+        # column-parallel weight applied WITHOUT the module's own input mapping: its backward all-reduce would hand
+        # every rank the full gradient of ql, which the sums above would then count once per rank
+        q = OF.linear(ql, self.linear_q_up.weight).view(T, self.nq_l, self.d)
         kv = self.kv_layernorm(F.linear(x, self.linear_kv))
         q = self._rope(q, rotary)
         kv = self._rope(kv.unsqueeze(1), rotary).squeeze(1)

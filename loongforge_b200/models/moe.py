@@ -69,6 +69,9 @@ class TopKRouter(nn.Module):
         super().__init__()
         self.cfg, self.layer_number = cfg, layer_number
         self.moe_index = sum(1 for i in range(layer_number) if cfg.is_moe_layer(i))  # 0-based among MoE layers
+        # None: the router sees a sequence shard exactly when sequence parallelism is on; the MoE layer sets True when it
+        # shards the tokens over the TP ranks itself (tensor parallelism without sequence parallelism)
+        self.tokens_sharded_over_tp: Optional[bool] = None
         E = cfg.num_moe_experts
         w = PL.init_full_then_slice(key + ".weight", (E, cfg.hidden_size), cfg.init_method_std, partition_dim=None,
                                     rank=0, world=1, device=device or "cpu", dtype=torch.float32)
@@ -85,12 +88,23 @@ class TopKRouter(nn.Module):
         """x [T, H] -> (probs [T, E] fp32 (zero outside the top-k), routing_map [T, E] bool)."""
         cfg = self.cfg
         logits = torch.nn.functional.linear(x.float(), self.weight.float())
+        # Under sequence parallelism this rank routes a SHARD of the micro-batch's tokens and the router weight's
+        # gradient is summed over the TP ranks afterwards: every rank therefore contributes its share of the
+        # whole-micro-batch auxiliary losses (reference: Megatron reduces the aux-loss statistics over the tp-cp group).
+        st = ps.get_state()
+        sharded = cfg.sequence_parallel if self.tokens_sharded_over_tp is None else self.tokens_sharded_over_tp
+        sp_group = st.group("tp") if (sharded and st.dims.tp > 1 and dist.is_initialized()) else None
+        sp_n = st.dims.tp if sp_group is not None else 1
         if cfg.moe_z_loss_coeff:
-            z = torch.logsumexp(logits, dim=-1).square().mean() * cfg.moe_z_loss_coeff
-            track_aux_loss("z_loss", z / cfg.moe_z_loss_coeff, self.layer_number, cfg.num_layers)
+            z = torch.logsumexp(logits, dim=-1).square().mean() * (cfg.moe_z_loss_coeff / sp_n)
+            track_aux_loss("z_loss", self._whole(z, sp_group) / cfg.moe_z_loss_coeff, self.layer_number, cfg.num_layers)
             logits = AuxLossScaler.apply(logits, z)
         ids = _CURRENT_TOKEN_IDS["ids"]
-        if self.moe_index < cfg.moe_n_hash_layers and ids is not None and ids.numel() == logits.shape[0]:
+        if self.moe_index < cfg.moe_n_hash_layers and ids is not None:
+            if sp_n > 1 and ids.numel() == logits.shape[0] * sp_n:  # this rank's sequence shard of the token ids
+                ids = ids[st.tp_rank * logits.shape[0]:(st.tp_rank + 1) * logits.shape[0]]
+            if ids.numel() != logits.shape[0]:
+                raise RuntimeError(f"hash routing got {ids.numel()} token ids for {logits.shape[0]} routed tokens")
             # experts are fixed by the token id; the gate only weights them (scores normalised over the k picks)
             idx = moe_ops.hash_routing(ids, cfg.num_moe_experts, cfg.moe_router_topk)
             s = torch.sqrt(torch.nn.functional.softplus(logits)) if cfg.moe_router_score_function == "sqrtsoftplus" \
@@ -114,11 +128,26 @@ class TopKRouter(nn.Module):
                 aux = moe_ops.seq_aux_loss(scores_for_aux, routing_map, cfg.moe_router_topk, seq_lens,
                                            cfg.moe_aux_loss_coeff)
             else:
-                aux = moe_ops.switch_aux_loss(scores_for_aux, routing_map.sum(0), cfg.moe_router_topk,
-                                              cfg.moe_aux_loss_coeff)
-            track_aux_loss("load_balancing_loss", aux / cfg.moe_aux_loss_coeff, self.layer_number, cfg.num_layers)
+                tpe = routing_map.sum(0)
+                if sp_group is not None:
+                    # f_e over ALL tokens of the micro-batch, P_e from the local shard: the ranks' losses add up to the
+                    # loss of the whole micro-batch (1 / T^2 with the global T)
+                    tpe = tpe.float()
+                    dist.all_reduce(tpe, group=sp_group)
+                aux = moe_ops.switch_aux_loss(scores_for_aux, tpe, cfg.moe_router_topk, cfg.moe_aux_loss_coeff) \
+                    / (sp_n * sp_n)
+            track_aux_loss("load_balancing_loss", self._whole(aux, sp_group) / cfg.moe_aux_loss_coeff, self.layer_number,
+                           cfg.num_layers)
             probs = AuxLossScaler.apply(probs, aux)
         return probs, routing_map
+
+    @staticmethod
+    def _whole(value: torch.Tensor, group) -> torch.Tensor:
+        """Detached value summed over the sequence-parallel ranks (for logging)."""
+        v = value.detach().clone()
+        if group is not None:
+            dist.all_reduce(v, group=group)
+        return v
 
     @torch.no_grad()
     def update_expert_bias(self, group=None):
@@ -268,6 +297,9 @@ class MoELayer(nn.Module):
         assert E % ep == 0, "num_moe_experts must divide by expert parallel size"
         self.E_local = E // ep
         self.router = TopKRouter(cfg, key + ".router", layer_number, device=device)
+        if st.dims.tp > 1:
+            # the router always sees a token shard under TP (see forward): its gradient is a partial sum on every rank
+            self.router.weight.tp_partial_grad = True
         self.etp = st.dims.etp
         self.experts = GroupedMLP(cfg, key + ".experts", self.E_local, st.ep_rank * self.E_local, device=device,
                                   etp_rank=st.etp_rank, etp_size=st.dims.etp)
@@ -290,14 +322,25 @@ class MoELayer(nn.Module):
         share their tokens (all-gather), run the same dispatch, compute partial FC2 sums with their slices, and
         reduce-scatter the combined output back to each rank's own tokens."""
         g = ps.get_state(self.state_name).group("etp")
-        xf = M.gather_from_sequence_parallel_region(x, g, False)
-        pf = M.gather_from_sequence_parallel_region(probs, g, False)
+        # each rank back-propagates only through ITS slices of the expert weights, so the gradients of the gathered
+        # tokens and probabilities are partial sums: reduce-scatter them in backward
+        xf = M.gather_from_sequence_parallel_region(x, g, True)
+        pf = M.gather_from_sequence_parallel_region(probs, g, True)
         mf = M.gather_from_sequence_parallel_region(routing_map.to(torch.uint8), g, False).bool()
         tokens, tpe = self.dispatcher.dispatch(xf, pf, mf)
         out = self.dispatcher.combine(self.experts(tokens, tpe))
         return M.reduce_scatter_to_sequence_parallel_region(out, g)
 
     def forward(self, x: torch.Tensor, seq_lens=None) -> torch.Tensor:
+        st = ps.get_state(self.state_name)
+        # Experts are replicated over the TP ranks (or sliced over them, ETP) and their gradients are summed over those
+        # ranks, so every rank must route a DIFFERENT part of the tokens. Sequence parallelism delivers shards already;
+        # without it the layer shards its input here and gathers its output.
+        local_shard = st.dims.tp > 1 and not self.cfg.sequence_parallel
+        x_full = x
+        if local_shard:
+            self.router.tokens_sharded_over_tp = True
+            x = M.scatter_to_sequence_parallel_region(x, st.group("tp"))
         probs, routing_map = self.router(x, seq_lens)
         if self.etp > 1:
             out = self._forward_etp(x, probs, routing_map)
@@ -310,12 +353,13 @@ class MoELayer(nn.Module):
             tokens, tpe = self.dispatcher.dispatch(x, probs, routing_map)
             y = self.experts(tokens, tpe)
             out = self.dispatcher.combine(y)
+        if local_shard:
+            out = M.gather_from_sequence_parallel_region(out, st.group("tp"), False)
         if self.shared_experts is not None:
-            st = ps.get_state(self.state_name)
             if st.dims.tp > 1:
                 # shared expert is tensor parallel over the full token set of the TP group
                 g = st.group("tp")
-                xs = M.gather_from_sequence_parallel_region(x, g, False) if self.cfg.sequence_parallel else x
+                xs = M.gather_from_sequence_parallel_region(x, g, False) if self.cfg.sequence_parallel else x_full
                 ys = self.shared_experts(xs)
                 out = out + (M.scatter_to_sequence_parallel_region(ys, g) if self.cfg.sequence_parallel else ys)
             else:

@@ -68,10 +68,24 @@ class _GatherVarRows(torch.autograd.Function):
         return g[start:start + ctx.counts[ctx.rank]] / dist.get_world_size(ctx.group), None, None
 
 
+class _ScaleGrad(torch.autograd.Function):
+    """Identity whose backward multiplies the gradient by a constant."""
+
+    @staticmethod
+    def forward(ctx, x, scale):
+        ctx.scale = scale
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g * ctx.scale, None
+
+
 class OmniCombinationModel(nn.Module):
     def __init__(self, lm_cfg: TransformerConfig, vit_cfg: Optional[TransformerConfig], *, image_token_id: int,
                  pre_process: bool = True, post_process: bool = True, layer_numbers=None, device=None,
                  encoder_hetero_dp: bool = False, freeze_encoder: bool = False, projector_activation: str = "gelu",
+                 full_hetero_dp: bool = False,
                  vision_family: str = "qwen2_vit", vision_options: Optional[dict] = None):
         super().__init__()
         self.cfg = lm_cfg
@@ -81,7 +95,10 @@ class OmniCombinationModel(nn.Module):
         self.foundation_model = GPTModel(lm_cfg, pre_process=pre_process, post_process=post_process,
                                          layer_numbers=layer_numbers, device=device)
         self.has_encoder = pre_process and vit_cfg is not None
-        if self.has_encoder:
+        # full heterogeneous DP: EVERY rank of the model-parallel group holds the encoder (later pipeline stages as
+        # replicas of the first stage's copy) and encodes its share of the step's micro-batches
+        self.full_hetero_dp = full_hetero_dp and vit_cfg is not None
+        if self.has_encoder or self.full_hetero_dp:
             enc_state = ENCODER_STATE if ENCODER_STATE in ps._STATES else None
             self.encoder_state = enc_state
             self.vision_family = vision_family
@@ -107,6 +124,19 @@ class OmniCombinationModel(nn.Module):
             if freeze_encoder:
                 for p in self.encoder_model.image_encoder.parameters():
                     p.requires_grad_(False)
+            if self.full_hetero_dp:
+                for p in self.encoder_model.parameters():
+                    # summed over the model-parallel group after the data-parallel reduction; kept in a buffer of its own
+                    # so that every rank shards it identically
+                    p.mp_shared = True
+                    p.defer_grad_sync = True  # one encoder backward per owned micro-batch, all after the pipeline
+                    if not pre_process:
+                        p.shared_embedding_replica = True  # written to checkpoints and counted by the first stage only
+            if encoder_hetero_dp and ps.get_state().dims.tp > 1:
+                # every rank of the TP group encodes different images: its encoder gradients are partial sums, which the
+                # trainer adds up over the TP group (the encoder's data-parallel degree includes the decoder's TP ranks)
+                for p in self.encoder_model.parameters():
+                    p.tp_partial_grad = True
 
     # pipeline plumbing is delegated to the language model
     @property
@@ -141,6 +171,10 @@ class OmniCombinationModel(nn.Module):
                 emb = self.encoder_model.image_projector(h, my_grid)
                 if taps and hasattr(self.encoder_model, "deepstack_mergers"):
                     self._deepstack = self.encoder_model.deepstack_mergers(taps, my_grid)
+        if self.encoder_hetero_dp and tp > 1 and not split:
+            # too few images to split: every rank encoded all of them, and the gradients will still be summed over the
+            # TP group, so each rank passes back 1 / tp of its (identical) gradient
+            emb = _ScaleGrad.apply(emb, 1.0 / tp)
         if split:
             assert self.vision_family == "qwen2_vit", "encoder hetero-DP is implemented for the Qwen2-VL encoder"
             unit = self.encoder_model.image_projector.unit
@@ -149,7 +183,9 @@ class OmniCombinationModel(nn.Module):
         return emb
 
     def forward(self, tokens, position_ids, *, pixels=None, grid_thw=None, labels=None, loss_mask=None, packed=None,
-                loss_scale=None):
+                loss_scale=None, image_embeds=None):
+        """``image_embeds``: projected image tokens computed ahead of the pipeline (full heterogeneous DP); the encoder
+        is then not run here."""
         lm = self.foundation_model
         decoder_input = None
         if self.pre_process:
@@ -166,7 +202,11 @@ class OmniCombinationModel(nn.Module):
                     emb_mod.sequence_parallel = was
             else:
                 x = lm.embed(tokens)
-            if self.has_encoder and pixels is not None and pixels.numel() > 0:
+            if image_embeds is not None:
+                mask = tokens == self.image_token_id
+                x = x.masked_scatter(mask.unsqueeze(-1), image_embeds.to(x.dtype))
+                self.decoder.deepstack_hook = None
+            elif self.has_encoder and pixels is not None and pixels.numel() > 0:
                 img = self.encode_images(pixels, grid_thw).to(x.dtype)
                 mask = tokens == self.image_token_id
                 x = x.masked_scatter(mask.unsqueeze(-1), img)

@@ -79,7 +79,8 @@ class TPRMSNorm(nn.Module):
         ss = x.float().pow(2).sum(-1, keepdim=True)
         if st.dims.tp > 1:
             from ..parallel import mappings as M
-            ss = M.reduce_from_tensor_model_parallel_region(ss, st.group("tp"))
+            # every rank normalises its own feature slice with the SHARED statistic: gradients flow back from all ranks
+            ss = M.all_reduce_forward_and_backward(ss, st.group("tp"))
         return (x.float() * torch.rsqrt(ss / self.full_dim + self.eps) * self.weight.float()).to(x.dtype)
 
 

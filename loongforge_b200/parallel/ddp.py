@@ -129,7 +129,7 @@ class DistributedDataParallel(nn.Module):
         self.state = st
         if disable_bucketing:
             self.cfg = dataclasses.replace(self.cfg, bucket_size=None)
-        dense, expert, shared = [], [], []
+        dense, expert, shared, mp_shared = [], [], [], []
         named = {}
         for name, p in module.named_parameters():
             if not p.requires_grad:
@@ -137,6 +137,8 @@ class DistributedDataParallel(nn.Module):
             named[p] = name
             if getattr(p, "shared_embedding", False):
                 shared.append(p)
+            elif getattr(p, "mp_shared", False):
+                mp_shared.append(p)  # replicated over the whole model-parallel group (vision encoder, full hetero-DP)
             else:
                 (expert if getattr(p, "is_expert", False) else dense).append(p)
         self.buffers: List[ParamAndGradBuffer] = []
@@ -145,7 +147,7 @@ class DistributedDataParallel(nn.Module):
         # stages then shard it identically over the data-parallel ranks, so its gradient can be summed over the two
         # stages after the data-parallel reduce-scatter (reference: Megatron gives such parameters their own bucket).
         for plist, kind, store in ((dense, "dp_cp", self.buffers), (shared, "dp_cp", self.buffers),
-                                   (expert, "edp", self.expert_buffers)):
+                                   (mp_shared, "dp_cp", self.buffers), (expert, "edp", self.expert_buffers)):
             by_dtype: Dict[torch.dtype, List[nn.Parameter]] = {}
             for p in plist:
                 by_dtype.setdefault(p.dtype, []).append(p)

@@ -144,7 +144,10 @@ class DistributedOptimizer:
             # merge adjacent segments that are counted with the same multiplicity
             runs = []
             for lo, hi, _, dup, _, p, _ in sh.segments:
-                count = (not dup) or st.tp_rank == 0 or is_expert_buf
+                # a tensor sharded `tp_shards` ways (1 = replicated) lives on that many consecutive TP ranks and is
+                # repeated on the others (modules built for a parallel state with a smaller TP degree)
+                copies_from = 1 if dup else getattr(p, "tp_shards", st.dims.tp)
+                count = st.tp_rank < copies_from or is_expert_buf
                 # the last pipeline stage's copy of the word embedding is the same logical tensor as the first stage's
                 count = count and not getattr(p, "shared_embedding_replica", False)
                 if not count:

@@ -58,9 +58,17 @@ def init_full_then_slice(key: str, full_shape, std: float, *, partition_dim: Opt
     return torch.cat([b.chunk(world, dim=partition_dim)[rank] for b in blocks], dim=partition_dim).contiguous().to(dtype)
 
 
-def mark_tp(param: torch.Tensor, partition_dim: Optional[int], stride: int = 1, sequence_parallel: bool = False):
-    """Attributes consumed by checkpointing, grad-norm and the SP gradient all-reduce."""
+def mark_tp(param: torch.Tensor, partition_dim: Optional[int], stride: int = 1, sequence_parallel: bool = False,
+            shards: Optional[int] = None, shard_rank: int = 0):
+    """Attributes consumed by checkpointing, grad-norm and the SP gradient all-reduce.
+
+    ``shards`` / ``shard_rank``: tensor-parallel size and rank of the parallel state the OWNING module was built for.
+    A module of a state with a smaller TP degree than the job's main state (a vision encoder with TP 1 beside a
+    decoder with TP 2) is replicated over the main TP group: checkpoints then write it once with its own sharding,
+    and the gradient norm counts it once."""
     param.tensor_model_parallel = partition_dim is not None
+    if shards is not None:
+        param.tp_shards, param.tp_shard_rank = shards, shard_rank
     param.partition_dim = -1 if partition_dim is None else partition_dim
     param.partition_stride = stride
     param.sequence_parallel = sequence_parallel
@@ -107,10 +115,10 @@ class ColumnParallelLinear(nn.Module):
         w = init_full_then_slice(key + ".weight", (out_features, in_features), init_std, partition_dim=0,
                                  rank=self.tp_rank, world=self.tp, device=device, dtype=params_dtype, stride=stride)
         self.weight = nn.Parameter(w)
-        mark_tp(self.weight, 0, stride)
+        mark_tp(self.weight, 0, stride, shards=self.tp, shard_rank=self.tp_rank)
         if bias:
             self.bias = nn.Parameter(torch.zeros(self.out_local, dtype=params_dtype, device=device))
-            mark_tp(self.bias, 0, stride)
+            mark_tp(self.bias, 0, stride, shards=self.tp, shard_rank=self.tp_rank)
         else:
             self.register_parameter("bias", None)
 
@@ -158,7 +166,7 @@ class RowParallelLinear(nn.Module):
         w = init_full_then_slice(key + ".weight", (out_features, in_features), init_std, partition_dim=1,
                                  rank=self.tp_rank, world=self.tp, device=device, dtype=params_dtype)
         self.weight = nn.Parameter(w)
-        mark_tp(self.weight, 1)
+        mark_tp(self.weight, 1, shards=self.tp, shard_rank=self.tp_rank)
         if bias:
             self.bias = nn.Parameter(torch.zeros(out_features, dtype=params_dtype, device=device))
             mark_tp(self.bias, None, sequence_parallel=self.sequence_parallel)
@@ -212,7 +220,7 @@ class VocabParallelEmbedding(nn.Module):
         w = init_full_then_slice(key + ".weight", (num_embeddings, embedding_dim), init_std, partition_dim=0,
                                  rank=self.tp_rank, world=self.tp, device=device, dtype=params_dtype)
         self.weight = nn.Parameter(w)
-        mark_tp(self.weight, 0)
+        mark_tp(self.weight, 0, shards=self.tp, shard_rank=self.tp_rank)
 
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
         g = ps.get_state(self.state_name).group("tp")

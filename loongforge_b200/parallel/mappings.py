@@ -89,6 +89,27 @@ class _ReduceFromTP(torch.autograd.Function):
         return g, None
 
 
+class _AllReduceBoth(torch.autograd.Function):
+    """Sum over the group in forward AND backward: for a statistic (e.g. a sum of squares over a sharded feature
+    dimension) that every rank then uses in its OWN, different downstream computation, so each rank's input receives
+    gradient from every rank's output."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        if _ws(group) > 1:
+            x = x.contiguous().clone()
+            dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        if _ws(ctx.group) > 1:
+            g = g.contiguous().clone()
+            dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
 class _ScatterToSP(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
@@ -205,6 +226,7 @@ def _gloo_a2a(outs, ins, group):
 # public API (names follow Megatron's tensor_parallel.mappings) ------------------------------
 def copy_to_tensor_model_parallel_region(x, group): return _CopyToTP.apply(x, group)
 def reduce_from_tensor_model_parallel_region(x, group): return _ReduceFromTP.apply(x, group)
+def all_reduce_forward_and_backward(x, group): return _AllReduceBoth.apply(x, group)
 def scatter_to_sequence_parallel_region(x, group): return _ScatterToSP.apply(x, group)
 def gather_from_sequence_parallel_region(x, group, tensor_parallel_output_grad: bool = True):
     return _GatherFromSP.apply(x, group, tensor_parallel_output_grad)

@@ -38,6 +38,7 @@ class FullHeteroEncoderRunner:
         self.ranks = dist.get_process_group_ranks(group) if self.world > 1 else [0]
         self._own: dict = {}      # microbatch -> embedding with autograd graph (owner only)
         self._leaves: List[torch.Tensor] = []
+        self._parked: dict = {}    # microbatch -> host handle of an offloaded embedding
 
     def encode_all(self, inputs: Sequence[object]) -> List[torch.Tensor]:
         self._own.clear()
@@ -64,8 +65,19 @@ class FullHeteroEncoderRunner:
                 buf = mine.detach().clone() if mine is not None else torch.empty(rows, cols, dtype=dtype, device=dev)
                 dist.broadcast(buf, src, group=self.group)
                 leaf = buf.requires_grad_(True)
+            if self.offloader is not None:
+                # park the embedding in pinned host memory until its micro-batch enters the pipeline (`leaf(i)`)
+                self._parked[i] = self.offloader.offload(leaf.detach())
+                leaf = None
             self._leaves.append(leaf)
         return self._leaves
+
+    def leaf(self, i: int) -> torch.Tensor:
+        """The embedding of micro-batch i as a leaf tensor that collects ``.grad``; brings it back from host memory
+        first when an offloader is in use."""
+        if self._leaves[i] is None:
+            self._leaves[i] = self.offloader.reload(self._parked.pop(i)).detach().clone().requires_grad_(True)
+        return self._leaves[i]
 
     @staticmethod
     def _device_hint(inputs):
@@ -79,7 +91,8 @@ class FullHeteroEncoderRunner:
     def backward(self, contributes: bool = True) -> None:
         """Every rank calls this once after the pipeline backward. Ranks with ``contributes=False`` (replicas that hold a
         duplicate of the same gradient, or stages that never used the embeddings) send zeros."""
-        for i, leaf in enumerate(self._leaves):
+        for i in range(len(self._leaves)):
+            leaf = self.leaf(i)
             g = leaf.grad if (contributes and leaf.grad is not None) else torch.zeros_like(leaf)
             if self.world > 1:
                 g = g.contiguous()

@@ -61,6 +61,7 @@ class TrainConfig:
     master_as_remainder: bool = False
     optimizer_cpu_offload: bool = False  # masters + Adam moments on the host, native host AdamW
     fp8_policy_file: Optional[str] = None  # JSON rules: which linear kinds run FP8 (runtime/fp8_policy.py)
+    dp_balance: bool = False  # trade whole micro-batches between DP ranks by modelled cost (data/dp_balance.py)
     chunkpipe_chunks: int = 0  # > 1: every sequence runs as that many chunks (runtime/chunkpipe.py)
     use_fsdp: bool = False  # FSDP2 units instead of DDP + distributed optimizer (runtime/fsdp_trainer.py)
     fsdp_sharding_strategy: str = "optim_grads_params"  # or optim_grads
@@ -251,6 +252,8 @@ class Trainer:
         for m in self.models:
             m.train()
         self.optimizer.zero_grad()
+        if t.dp_balance and self.st.dp_size > 1 and not getattr(self, "_already_balanced", False):
+            data_iterator = self._balanced(data_iterator)
         # auxiliary losses (MoE balancing, MTP, indexer) are per-micro-batch means: weight each by 1 / micro-batches so
         # that, after the data-parallel average, they enter the step like the main loss does
         from ..models.moe import AuxLossScaler
@@ -287,6 +290,16 @@ class Trainer:
             for k, v in zip(keys, vals.tolist()):
                 metrics[k] = v
         return metrics
+
+    def _balanced(self, data_iterator):
+        """One balancing wrapper per source iterator (it buffers the step's micro-batches)."""
+        cache = self.__dict__.setdefault("_balanced_iterators", {})
+        w = cache.get(id(data_iterator))
+        if w is None:
+            from ..data.dp_balance import BalancedMicrobatchIterator
+            w = cache[id(data_iterator)] = BalancedMicrobatchIterator(
+                data_iterator, self.mb_calc.num_microbatches, self.st.group("dp"))
+        return w
 
     def _chunkpipe_microbatches(self, data_iterator) -> List[dict]:
         """Sequence-chunk pipelining instead of whole-sequence micro-batches: each sequence is cut into

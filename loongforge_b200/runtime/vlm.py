@@ -6,6 +6,7 @@ from __future__ import annotations
 from typing import Dict, Iterator, Optional
 
 import torch
+import torch.distributed as dist
 
 from ..data.position_ids import mrope_ids
 from ..models.config import TransformerConfig
@@ -65,7 +66,8 @@ class VLMTrainer(Trainer):
                  vit_cfg: Optional[TransformerConfig] = None, encoder_tp: int = 1, encoder_hetero_dp: bool = False,
                  image_token_id: Optional[int] = None, encoder_recompute: bool = True,
                  vision_family: str = "qwen2_vit", vision_options: Optional[dict] = None, freeze_encoder: bool = False,
-                 images_per_sample: int = 4, image_size: int = 448, **kw):
+                 images_per_sample: int = 4, image_size: int = 448, full_hetero_dp: bool = False,
+                 full_hetero_cpu_offload: bool = False, **kw):
         """``vision_family``: ``qwen2_vit`` (Qwen2/2.5-VL encoder) or a key of ``models.vision_zoo.VISION_FAMILIES``
         (Qwen3-VL, InternViT, RICE, Moon, ERNIE, MiniCPM-V encoders with their projectors)."""
         self.vit_cfg = vit_cfg or get_model_config("qwen2.5-vit")
@@ -74,6 +76,9 @@ class VLMTrainer(Trainer):
         if encoder_recompute:
             self.vit_cfg.recompute_granularity = "full"
         self.encoder_hetero_dp = encoder_hetero_dp
+        self.full_hetero_dp, self.full_hetero_cpu_offload = full_hetero_dp, full_hetero_cpu_offload
+        if full_hetero_dp and ((dims and dims.cp > 1) or encoder_tp != 1 or encoder_hetero_dp):
+            raise ValueError("full heterogeneous DP needs cp = 1 and encoder TP 1, and replaces encoder hetero-DP")
         self.image_token_id = model_cfg.vocab_size - 1 if image_token_id is None else image_token_id
         dims = dims or ParallelDims()
         if not ps.model_parallel_is_initialized():
@@ -83,9 +88,20 @@ class VLMTrainer(Trainer):
         if train_cfg.bf16:
             self.vit_cfg.params_dtype = torch.bfloat16
         super().__init__(model_cfg, train_cfg, dims, **kw)
+        self._mp_shared = [p for m in self.models for p in m.module.parameters() if getattr(p, "mp_shared", False)]
+        if self._mp_shared and self.st.group("mp") is not None:
+            self.optimizer.post_sync_hooks.append(self._allreduce_mp_shared_grads)
+
+    def _allreduce_mp_shared_grads(self):
+        """Full hetero-DP: every rank of the model-parallel group back-propagated the encoder for ITS micro-batches;
+        the sum over the group is the gradient of the step."""
+        g = self.st.group("mp")
+        for p in self._mp_shared:
+            dist.all_reduce(p.main_grad, group=g)
 
     def _default_model_provider(self, pre_process, post_process, layer_numbers):
-        return OmniCombinationModel(self.mcfg, self.vit_cfg if pre_process else None, image_token_id=self.image_token_id,
+        return OmniCombinationModel(self.mcfg, self.vit_cfg if (pre_process or self.full_hetero_dp) else None,
+                                    full_hetero_dp=self.full_hetero_dp, image_token_id=self.image_token_id,
                                     pre_process=pre_process, post_process=post_process, layer_numbers=layer_numbers,
                                     device=self.device, encoder_hetero_dp=self.encoder_hetero_dp,
                                     vision_family=self.vision_family, vision_options=self.vision_options,
@@ -111,12 +127,65 @@ class VLMTrainer(Trainer):
         scale = 1.0 / (n_valid * nmb)
         packed = PackedSeqParams(cu_seqlens=b["cu_seqlens"]) if "cu_seqlens" in b else None
         first = self.st.is_first_stage
-        out = model(tokens, pos, pixels=b["pixels"].to(self.mcfg.params_dtype) if first else None,
+        embeds = b.get("image_embeds")
+        out = model(tokens, pos, pixels=b["pixels"].to(self.mcfg.params_dtype) if (first and embeds is None) else None,
                     grid_thw=b["grid_thw"] if first else None, labels=labels, loss_mask=mask, packed=packed,
-                    loss_scale=scale)
+                    loss_scale=scale, **({"image_embeds": embeds} if (first and embeds is not None) else {}))
 
         def loss_func(losses):
             loss = (losses * mask.float()).sum() * scale
             return loss, {"lm loss": loss.detach() * nmb, "num_tokens": n_valid}
 
         return out, loss_func
+
+    # ------------------------------------------------------------------ full heterogeneous DP
+    def train_step(self, data_iterator):
+        if not self.full_hetero_dp:
+            return super().train_step(data_iterator)
+        return self._train_step_full_hetero(data_iterator)
+
+    def _train_step_full_hetero(self, data_iterator):
+        """All encoder rounds run BEFORE the pipeline: the ranks of the model-parallel group (TP x PP, which all see the
+        same micro-batches) each encode the micro-batches they own and broadcast the embeddings; the pipeline then runs
+        on precomputed embeddings; afterwards the embedding gradients return to their owners, which run the encoder
+        backward. The encoder's gradients are summed over the model-parallel group in the optimizer's post-sync hook
+        (reference: loongforge/train/training_utils.py:1484-1677,1720-1841)."""
+        from .hetero_dp import FullHeteroEncoderRunner
+
+        st = self.st
+        nmb = self.mb_calc.num_microbatches
+        if self.tcfg.dp_balance and st.dp_size > 1:
+            data_iterator = self._balanced(data_iterator)
+        batches = [self.get_batch(data_iterator) for _ in range(nmb)]
+        module = self.models[0].module
+        dt = self.mcfg.params_dtype
+
+        def encode(inp):
+            pixels, grid = inp
+            return module.encode_images(pixels.to(dt), grid)
+
+        offloader = None
+        if self.full_hetero_cpu_offload:
+            from .offload import AsyncCPUOffloader
+            offloader = AsyncCPUOffloader()
+        runner = FullHeteroEncoderRunner(st.group("mp"), encode, offloader=offloader)
+        runner.encode_all([(b["pixels"], b["grid_thw"]) for b in batches])
+
+        def feed():
+            for i, b in enumerate(batches):
+                b["image_embeds"] = runner.leaf(i)  # reloaded from host memory here when offloading
+                yield b
+
+        self._hetero_runner, self._already_balanced = runner, True
+        try:
+            return super().train_step(feed())
+        finally:
+            self._hetero_runner, self._already_balanced = None, False
+
+    def _allreduce_sequence_parallel_grads(self):
+        # runs right after the pipeline's backward and before the optimizer: the point where the embedding gradients go
+        # back to the ranks that encoded them (the first stage's first TP rank holds the complete gradient)
+        runner = getattr(self, "_hetero_runner", None)
+        if runner is not None:
+            runner.backward(contributes=self.st.is_first_stage and self.st.tp_rank == 0)
+        super()._allreduce_sequence_parallel_grads()

@@ -51,6 +51,8 @@ def main(argv: Optional[List[str]] = None) -> int:
         extra["freeze_encoder"] = bool(enc.get("freeze", False))
         extra["encoder_tp"] = int(getattr(args, "encoder_tensor_model_parallel_size", None) or 1)
         extra["encoder_hetero_dp"] = bool(getattr(args, "enable_encoder_hetero_dp", False))
+        extra["full_hetero_dp"] = bool(getattr(args, "enable_full_hetero_dp", False))
+        extra["full_hetero_cpu_offload"] = bool(getattr(args, "full_hetero_dp_cpu_offload", False))
         if getattr(args, "image_resolution", None):
             extra["image_size"] = int(args.image_resolution)
     trainer = build_model_trainer(family, train_cfg.training_phase, model_cfg=model_cfg, train_cfg=train_cfg,

@@ -82,3 +82,4 @@ def test_every_model_yaml_builds_the_registered_preset():
             assert getattr(cfg, f.name) == getattr(ref, f.name), (name, f.name)
         checked += 1
     assert checked >= 20
+

@@ -38,7 +38,7 @@ def _check(ref, res, have_loss, tol=2e-4):
         for (l0, g0), (l1, g1) in zip(ref, got):
             if have_loss(r):
                 assert l1 is not None and abs(l0 - l1) < tol * max(1, abs(l0)), (r, l0, l1)
-            assert abs(g0 - g1) < 5e-3 * max(1, abs(g0)), (r, g0, g1)
+            assert abs(g0 - g1) < 5e-4 * max(1, abs(g0)), (r, g0, g1)
 
 
 @pytest.mark.parametrize("dims,world", [({"tp": 2}, 2), ({"tp": 2, "sp": False}, 2), ({"pp": 2}, 2),
@@ -68,7 +68,8 @@ def test_moe_expert_tensor_parallel_matches_single_process():
 
 @pytest.mark.parametrize("model,dims", [("tiny-qwen3-next", {"tp": 2}), ("tiny-deepseek", {"tp": 2}),
                                         ("tiny-deepseek-v4", {"pp": 3}), ("tiny-qwen3-moe", {"tp": 2}),
-                                        ("tiny-minimax", {"tp": 2}), ("tiny-minimax", {"tp": 2, "sp": False})])
+                                        ("tiny-minimax", {"tp": 2}), ("tiny-minimax", {"tp": 2, "sp": False}),
+                                        ("tiny-deepseek-v4", {"tp": 2}), ("tiny-mimo", {"pp": 2})])
 def test_newer_families_match_single_process(model, dims):
     """Hybrid linear attention under TP+SP, MLA + DSA under TP+SP, hyper-connection streams across pipeline stages."""
     ov = {"moe_aux_loss_coeff": 0.0} if model != "tiny-deepseek-v4" else {}
@@ -84,6 +85,8 @@ def test_newer_families_match_single_process(model, dims):
     ("tiny-deepseek", {"cp": 2}, {"moe_aux_loss_coeff": 0.0}, 2),       # MLA + DSA with context parallel keys
     ("tiny-qwen3-moe", {"tp": 2, "ep": 2}, {"moe_aux_loss_coeff": 0.0}, 4),
     ("tiny-minimax", {"pp": 2}, {}, 2),                                  # MoE + MTP on the last pipeline stage
+    ("tiny-qwen3-moe", {"tp": 2}, {"moe_z_loss_coeff": 1e-3}, 2),        # aux + z loss over sequence shards
+    ("tiny-qwen3-moe", {"tp": 2, "sp": False}, {"moe_z_loss_coeff": 1e-3}, 2),   # MoE shards its tokens itself
     ("tiny-llama", {"pp": 2}, {"untie_embeddings_and_output_weights": False}, 2),   # tied embedding across stages
     ("tiny-minimax", {"pp": 2}, {"untie_embeddings_and_output_weights": False}, 4),  # + sharded optimizer over dp 2
 ])

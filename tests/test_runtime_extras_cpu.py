@@ -26,7 +26,7 @@ def test_fp8_policy_rules_and_export():
     from loongforge_b200.parallel import state as ps
     ps.destroy_model_parallel()
     ps.initialize_model_parallel(ps.ParallelDims())
-    dec = P.apply_fp8_policy(build_model(get_model_config("tiny-llama")), pol, 8192, 1)
+    dec = P.apply_fp8_policy(build_model(get_model_config("tiny-llama", ffn_hidden_size=512)), pol, 8192, 1)
     assert dec["decoder.layers.0.mlp.linear_fc1"] == "fp8" and dec["decoder.layers.0.self_attention.linear_qkv"] == "bf16"
 
 

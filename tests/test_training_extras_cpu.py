@@ -233,3 +233,47 @@ def test_fp8_blockwise_training_follows_the_full_precision_run(tmp_path):
     _, dec2 = run("blockwise", str(pol))
     assert {v for k, v in dec2.items() if k.endswith("linear_fc1")} == {"fp8"}
     assert {v for k, v in dec2.items() if not k.endswith("linear_fc1")} == {"bf16"}
+
+
+def _balance_run(rank, world, balance):
+    import torch
+
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.runtime.trainer import TrainConfig, Trainer
+
+    cfg = get_model_config("tiny-llama")
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=8, seq_length=256, train_iters=2, lr=1e-3, clip_grad=1.0,
+                     log_interval=1000, dp_balance=balance)
+    tr = Trainer(cfg, tc)
+    # rank 0 always draws the long sequences, rank 1 the short ones: the worst case for lock-step data parallelism
+    lens = [256, 224, 192, 160] if tr.st.dp_rank == 0 else [32, 48, 64, 16]
+
+    def it():
+        g = torch.Generator().manual_seed(100 + tr.st.dp_rank)
+        while True:
+            for T in lens:
+                tok = torch.randint(0, cfg.vocab_size, (1, T + 1), generator=g)
+                yield {"tokens": tok[:, :-1], "labels": tok[:, 1:], "loss_mask": torch.ones(1, T),
+                       "position_ids": torch.arange(T)[None], "tag": (tr.st.dp_rank, T)}
+
+    seen = []
+    orig = tr.get_batch
+    tr.get_batch = lambda di: (lambda b: (seen.append(b["tag"]), b)[1])(orig(di))
+    out = [tr.train_step(it_) for it_ in [it()] * 1 for _ in range(2)]
+    w = tr.__dict__.get("_balanced_iterators")
+    imb = next(iter(w.values())).last_imbalance if w else None
+    return [(m["lm loss"], m["grad_norm"]) for m in out], seen, imb
+
+
+def test_dp_balance_moves_microbatches_without_changing_the_step():
+    from dist_utils import run_distributed
+
+    plain = run_distributed(_balance_run, 2, False)
+    bal = run_distributed(_balance_run, 2, True)
+    for (l0, g0), (l1, g1) in zip(plain[0][0], bal[0][0]):
+        assert abs(l0 - l1) < 1e-5 * abs(l0) and abs(g0 - g1) < 1e-4 * max(1, g0), (plain[0][0], bal[0][0])
+    (_, seen0, imb0), (_, seen1, imb1) = bal
+    assert imb0 == imb1 and imb0[1] < imb0[0] and imb0[1] < 1.2, imb0
+    assert len(seen0) == len(seen1) == 8, "every rank keeps its micro-batch count"
+    assert {r for r, _ in seen0} == {0, 1}, "rank 0 now also processes micro-batches that rank 1 loaded"
+    assert sorted(seen0[:4] + seen1[:4]) == sorted(plain[0][1][:4] + plain[1][1][:4]), "the step's batch set is unchanged"

@@ -1,0 +1,48 @@
+"""The vision-language trainer under tensor / pipeline parallelism and encoder heterogeneous data parallelism must
+follow the single-process trajectory (same data, same seed)."""
+import pytest
+
+from dist_utils import run_distributed
+
+
+def _run(rank, world, dims_kw, vlm_kw, steps=2):
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel.state import ParallelDims
+    from loongforge_b200.runtime.trainer import TrainConfig
+    from loongforge_b200.runtime.vlm import VLMTrainer, synthetic_vlm_iterator
+
+    lm = get_model_config("tiny-llama", position_embedding_type="mrope", mrope_section=[8, 12, 12])
+    if dims_kw.get("tp", 1) > 1:
+        lm.sequence_parallel = True
+    vit = get_model_config("tiny-vit")
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=4, seq_length=128, train_iters=steps, lr=1e-3, clip_grad=1.0,
+                     log_interval=1000)
+    tr = VLMTrainer(lm, tc, ParallelDims(**dims_kw), vit_cfg=vit, images_per_sample=2, image_size=112, **vlm_kw)
+    st = tr.st
+    it = synthetic_vlm_iterator(lm.vocab_size, 128, images_per_sample=2, image_size=112, pin_memory=False,
+                                dp_rank=st.dp_rank, dp_size=st.dp_size, seed=9)
+    out = []
+    for _ in range(steps):
+        m = tr.train_step(it)
+        out.append((m.get("lm loss"), m["grad_norm"]))
+    return out
+
+
+@pytest.mark.parametrize("dims,vlm_kw,world", [
+    ({"tp": 2}, {}, 2),                                   # decoder TP 2 + SP, encoder TP 1 (replicated on both ranks)
+    ({"tp": 2}, {"encoder_tp": 2}, 2),                    # encoder sharded like the decoder
+    ({"tp": 2}, {"encoder_hetero_dp": True}, 2),          # each TP rank encodes a different micro-batch
+    ({"pp": 2}, {}, 2),                                   # encoder on the first stage only
+    ({}, {}, 2),                                          # data parallel
+    ({"tp": 2}, {"full_hetero_dp": True}, 2),             # encoder data parallel over the TP group, ahead of the step
+    ({"pp": 2}, {"full_hetero_dp": True}, 2),             # ... over the pipeline stages (replica on the last stage)
+    ({"tp": 2, "pp": 2}, {"full_hetero_dp": True, "full_hetero_cpu_offload": True}, 4),
+])
+def test_vlm_layouts_match_single_process(dims, vlm_kw, world):
+    ref = run_distributed(_run, 1, {}, {})[0]
+    res = run_distributed(_run, world, dict(dims), dict(vlm_kw))
+    got = [r for r in res if r[0][0] is not None][-1]
+    for (l0, g0), (l1, g1) in zip(ref, got):
+        assert abs(l0 - l1) < 2e-4 * abs(l0) and abs(g0 - g1) < 1e-3 * max(1, g0), (ref, got)
+    for r in res:  # every rank reports the same global gradient norm
+        assert all(abs(a[1] - b[1]) < 1e-5 * max(1, b[1]) for a, b in zip(r, got)), res
