@@ -170,10 +170,16 @@ class MLASelfAttention(nn.Module):
         q_abs = torch.einsum("thd,hdc->thc", q_nope, w_uk.to(q_nope.dtype))
         query = torch.cat([q_abs, q_pe], dim=-1)  # [T, H, dc + dr]
         key = torch.cat([kv_c, k_pe.view(T, self.dr)], dim=-1)  # [T, dc + dr]
-        pos = rotary.pos_ids.long() if (rotary is not None and rotary.pos_ids is not None) else torch.arange(T, device=x.device)
-        seg = None
-        if cu is not None:
-            seg = torch.bucketize(torch.arange(T, device=x.device), cu[1:].long().to(x.device), right=True)
+        if st.dims.cp > 1:
+            # this rank holds two chunks of the packed row: causal order and sequence membership follow the ROW position
+            from ..parallel.context_parallel import _positions
+            pos, seg = _positions(T, st.dims.cp, st.cp_rank, x.device, cu)
+        else:
+            pos = rotary.pos_ids.long() if (rotary is not None and rotary.pos_ids is not None) \
+                else torch.arange(T, device=x.device)
+            seg = None
+            if cu is not None:
+                seg = torch.bucketize(torch.arange(T, device=x.device), cu[1:].long().to(x.device), right=True)
         key_all, pos_k, seg_k = key, pos, seg
         if st.dims.cp > 1:
             g = st.group("cp")

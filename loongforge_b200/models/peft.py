@@ -39,12 +39,23 @@ class LoRALinear(nn.Module):
         # splits: output row counts of the logical matrices inside a fused weight (canonical LoRA)
         self.splits = splits or [out_local]
         n = len(self.splits)
-        a = torch.empty(n * rank, in_local, dtype=torch.float32)
-        nn.init.kaiming_uniform_(a, a=math.sqrt(5))
-        self.lora_A = nn.Parameter(a.to(device=dev, dtype=dt))
+        tp, tp_rank = getattr(base, "tp", 1) or 1, getattr(base, "tp_rank", 0)
+        in_full = in_local * tp if self.is_row else in_local
+        # A is drawn for the FULL input width from a seed that depends only on the layer's layout-independent name, then
+        # sliced: the adapters (and the run) do not depend on the TP / PP layout. Variance 1 / (3 fan_in), that of the
+        # usual Kaiming-uniform adapter init.
+        a = PL.init_full_then_slice(getattr(base, "init_key", key) + ".lora_A", (n * rank, in_full),
+                                    1.0 / math.sqrt(3.0 * in_full), partition_dim=1 if self.is_row else None,
+                                    rank=tp_rank, world=tp, device=dev, dtype=dt)
+        self.lora_A = nn.Parameter(a)
         self.lora_B = nn.Parameter(torch.zeros(out_local, rank, dtype=dt, device=dev))
-        PL.mark_tp(self.lora_A, 1 if self.is_row else None)
-        PL.mark_tp(self.lora_B, None if self.is_row else 0)
+        PL.mark_tp(self.lora_A, 1 if self.is_row else None, shards=tp, shard_rank=tp_rank)
+        PL.mark_tp(self.lora_B, None if self.is_row else 0, shards=tp, shard_rank=tp_rank)
+        if tp > 1:
+            # the replicated factor sits next to a sharded one, so each rank computes only a partial gradient for it
+            # (column parallel: A sees the gradient of the local output slice; row parallel: B sees the local partial
+            # sum of A's output): summed over the TP group by the trainer
+            (self.lora_B if self.is_row else self.lora_A).tp_partial_grad = True
         for p in base.parameters():
             p.requires_grad_(False)
 

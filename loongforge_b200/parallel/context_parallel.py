@@ -84,14 +84,14 @@ def _masked_attention(q, k, v, q_pos, k_pos, scale, causal, seg_q=None, seg_k=No
 
 
 def _positions(T_local: int, cp: int, rank: int, device, cu_seqlens=None):
-    """Global positions of this rank's tokens when every sequence of the micro-batch has the same
-    length (tokens of a sequence are laid out chunk r then chunk 2cp-1-r)."""
+    """Row positions of this rank's tokens (the packed row is cut into 2*cp chunks; rank r holds chunks r and
+    2cp-1-r, see `get_batch_on_this_cp_rank`) and, for packed rows, the index of the sequence each token belongs to.
+    Row order is causal order inside every sequence, so masks built from (position, sequence) are exact for
+    sequences of any lengths; only the ROW length has to divide by 2*cp."""
+    pos = cp_chunk_indices(T_local * cp, cp, rank, device)
     if cu_seqlens is None:
-        return cp_chunk_indices(T_local * cp, cp, rank, device), None
-    n_seq = cu_seqlens.numel() - 1
-    per = T_local // n_seq
-    pos = cp_chunk_indices(per * cp, cp, rank, device).repeat(n_seq)
-    seg = torch.arange(n_seq, device=device).repeat_interleave(per)
+        return pos, None
+    seg = torch.bucketize(pos, cu_seqlens[1:].to(device=device, dtype=pos.dtype), right=True)
     return pos, seg
 
 

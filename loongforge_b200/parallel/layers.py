@@ -102,6 +102,7 @@ class ColumnParallelLinear(nn.Module):
         super().__init__()
         st = ps.get_state(parallel_state)
         self.state_name = parallel_state
+        self.init_key = key  # layout-independent name of this layer (global layer index), also seeds adapters
         self.tp = st.dims.etp if is_expert else st.dims.tp
         self.tp_rank = st.etp_rank if is_expert else st.tp_rank
         self.group_kind = "etp" if is_expert else "tp"
@@ -153,6 +154,7 @@ class RowParallelLinear(nn.Module):
         super().__init__()
         st = ps.get_state(parallel_state)
         self.state_name = parallel_state
+        self.init_key = key  # layout-independent name of this layer (global layer index), also seeds adapters
         self.tp = st.dims.etp if is_expert else st.dims.tp
         self.tp_rank = st.etp_rank if is_expert else st.tp_rank
         self.group_kind = "etp" if is_expert else "tp"
@@ -209,6 +211,7 @@ class VocabParallelEmbedding(nn.Module):
         super().__init__()
         st = ps.get_state(parallel_state)
         self.state_name = parallel_state
+        self.init_key = key  # layout-independent name of this layer (global layer index), also seeds adapters
         self.tp, self.tp_rank = st.dims.tp, st.tp_rank
         assert num_embeddings % self.tp == 0
         self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim

@@ -30,8 +30,7 @@ class SFTTrainer(Trainer):
         tok = build_tokenizer(args.tokenizer_type, args.hf_tokenizer_path, use_fast=args.use_fast_tokenizer)
         ds = SFTDataset(args.sft_dataset, tok, template=args.chat_template or "chatml", max_len=self.tcfg.seq_length,
                         train_on_prompt=args.train_on_prompt, seed=self.tcfg.seed)
-        pad_mult = self.st.dims.tp * 2 * self.st.dims.cp if self.mcfg.sequence_parallel or self.st.dims.cp > 1 else 1
         return sft_batch_iterator(ds, self.tcfg.seq_length, packing=args.packing_sft_data, dp_rank=self.st.dp_rank,
                                   dp_size=self.st.dp_size, seed=self.tcfg.seed, pad_id=tok.pad,
                                   start_sample=self.consumed_samples // max(self.st.dp_size, 1),
-                                  pad_to_multiple=max(pad_mult, 1) * 0 + 1)
+                                  pad_to_multiple=1)  # rows are padded to seq_length, which the parallel sizes divide

@@ -3,6 +3,11 @@ import sys
 
 import pytest
 
+if os.environ.get("PYTEST_XDIST_WORKER"):
+    # several worker processes share the cores: keep each one's math library from spawning a thread per core
+    os.environ.setdefault("OMP_NUM_THREADS", "2")
+    os.environ.setdefault("MKL_NUM_THREADS", "2")
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
