@@ -142,6 +142,9 @@ class CompressedSparseAttention(nn.Module):
     def __init__(self, cfg: TransformerConfig, key: str, layer_number: int, *, device=None, parallel_state=None):
         super().__init__()
         st = ps.get_state(parallel_state)
+        if st.dims.cp > 1:
+            # window and compressed entries of a query reach into the previous rank's tokens
+            raise NotImplementedError("compressed sparse attention does not support context parallelism")
         tp = st.dims.tp
         self.cfg = cfg
         self.ratio = (cfg.csa_compress_ratios or [0] * (layer_number + 1))[layer_number]

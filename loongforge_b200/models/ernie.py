@@ -17,6 +17,7 @@ from typing import Optional
 import torch
 import torch.nn as nn
 
+from ..parallel import state as ps
 from .config import TransformerConfig
 from .moe import MoELayer
 from .transformer import RotaryInputs
@@ -52,12 +53,19 @@ class MultiTypeMoELayer(nn.Module):
         else:
             self.shared_experts = None
         self.token_type: Optional[torch.Tensor] = None  # [T] set per micro-batch by the model wrapper
+        self.cfg, self.state_name = cfg, parallel_state
 
     def set_token_type(self, token_type: Optional[torch.Tensor]):
         self.token_type = token_type
 
     def forward(self, x: torch.Tensor, seq_lens=None) -> torch.Tensor:
+        from ..parallel import mappings as M
+
+        st = ps.get_state(self.state_name)
+        sp = self.cfg.sequence_parallel and st.dims.tp > 1
         tt = self.token_type
+        if tt is not None and sp and tt.numel() == x.shape[0] * st.dims.tp:
+            tt = tt[st.tp_rank * x.shape[0]:(st.tp_rank + 1) * x.shape[0]]  # this rank's sequence shard
         if tt is None:
             out = self.text(x, seq_lens)
         else:
@@ -68,5 +76,11 @@ class MultiTypeMoELayer(nn.Module):
             out = out.index_add(0, ti, self.text(x.index_select(0, ti)))
             out = out.index_add(0, vi, self.vision(x.index_select(0, vi)))
         if self.shared_experts is not None:
-            out = out + self.shared_experts(x)
+            if sp:
+                # the shared expert is tensor parallel over the WHOLE token set of the TP group
+                g = st.group("tp")
+                ys = self.shared_experts(M.gather_from_sequence_parallel_region(x, g, False))
+                out = out + M.scatter_to_sequence_parallel_region(ys, g)
+            else:
+                out = out + self.shared_experts(x)
         return out

@@ -195,7 +195,8 @@ class GPTModel(nn.Module):
     def forward(self, tokens: Optional[torch.Tensor], position_ids: torch.Tensor, *,
                 labels: Optional[torch.Tensor] = None, loss_mask: Optional[torch.Tensor] = None,
                 packed: Optional[PackedSeqParams] = None, decoder_input: Optional[torch.Tensor] = None,
-                loss_scale: Optional[float] = None, token_type: Optional[torch.Tensor] = None):
+                loss_scale: Optional[float] = None, token_type: Optional[torch.Tensor] = None,
+                full_batch: Optional[dict] = None):
         """tokens / labels / loss_mask are flat ``[T]``; position_ids ``[T]`` or ``[3, T]`` (M-RoPE).
 
         Returns per-token losses ``[T]`` when `labels` is given on the last stage, logits
@@ -220,7 +221,7 @@ class GPTModel(nn.Module):
         if not self.post_process:
             return x
         return self.postprocess(x, labels, loss_mask, loss_scale, tokens=tokens, position_ids=position_ids,
-                                rotary=rotary, packed=packed)
+                                rotary=rotary, packed=packed, full_batch=full_batch)
 
     def postprocess(self, hidden, labels, loss_mask, loss_scale, **mtp_kw):
         cfg = self.cfg

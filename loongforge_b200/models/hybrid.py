@@ -93,6 +93,10 @@ class GatedDeltaNet(nn.Module):
     def __init__(self, cfg: TransformerConfig, key: str, *, device=None, parallel_state=None):
         super().__init__()
         st = ps.get_state(parallel_state)
+        if st.dims.cp > 1:
+            # the recurrent state of a sequence would have to travel from one context-parallel rank to the next
+            raise NotImplementedError("gated delta-net (linear attention) layers do not support context parallelism; "
+                                      "use tensor / sequence parallelism for long sequences")
         tp = st.dims.tp
         self.cfg = cfg
         self.dk, self.dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim

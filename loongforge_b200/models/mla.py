@@ -149,13 +149,16 @@ class MLASelfAttention(nn.Module):
             k_pe = _rope_pe(k_pe, rotary)
         scale = self._softmax_scale(rotary)
         cu = packed.cu_seqlens if packed is not None else None
+        self._row_length = packed.row_length if packed is not None else None
         w_up = self.linear_kv_up_proj.weight.view(H, self.dn + self.dv, self.dc)
         if not cfg.use_dsa:
             kvu = self.linear_kv_up_proj(kv_c).view(T, H, self.dn + self.dv)
             k = torch.cat([kvu[..., : self.dn], k_pe.expand(T, H, self.dr)], dim=-1)
             v = kvu[..., self.dn:]
             qq = torch.cat([q_nope, q_pe], dim=-1)
-            o = OF.attention(qq.contiguous(), k.contiguous(), v.contiguous(), causal=True, scale=scale, cu_seqlens=cu)
+            from .transformer import core_attention  # ring / all-gather attention under context parallelism
+            o = core_attention(qq.contiguous(), k.contiguous(), v.contiguous(), causal=True, scale=scale, cu_seqlens=cu,
+                               cfg=cfg, row_length=packed.row_length if packed is not None else None)
         else:
             o = self._dsa(x, q_c, q_nope, q_pe, kv_c, k_pe, w_up, rotary, cu, scale)
         return self.linear_proj(o.reshape(T, H * self.dv), residual)
@@ -173,7 +176,7 @@ class MLASelfAttention(nn.Module):
         if st.dims.cp > 1:
             # this rank holds two chunks of the packed row: causal order and sequence membership follow the ROW position
             from ..parallel.context_parallel import _positions
-            pos, seg = _positions(T, st.dims.cp, st.cp_rank, x.device, cu)
+            pos, seg = _positions(T, st.dims.cp, st.cp_rank, x.device, cu, self._row_length)
         else:
             pos = rotary.pos_ids.long() if (rotary is not None and rotary.pos_ids is not None) \
                 else torch.arange(T, device=x.device)

@@ -62,8 +62,13 @@ class MultiTokenPredictionBlock(nn.Module):
         lcfg.tp_comm_overlap = False  # the fused TP kernels are sized for the trunk's shapes
         self.layers = nn.ModuleList([MTPLayer(lcfg, k, device, parallel_state) for k in range(cfg.mtp_num_layers)])
 
-    def attach(self, model, hidden, losses, labels, loss_mask, loss_scale, *, tokens, position_ids, rotary, packed):
-        """Adds the MTP losses to the autograd graph of `losses` and returns `losses`."""
+    def attach(self, model, hidden, losses, labels, loss_mask, loss_scale, *, tokens, position_ids, rotary, packed,
+               full_batch=None):
+        """Adds the MTP losses to the autograd graph of `losses` and returns `losses`.
+
+        ``full_batch`` (context parallelism): flat ``tokens`` / ``labels`` / ``loss_mask`` of the micro-batch BEFORE it
+        was cut into this rank's chunks. The token that follows the last position of a chunk lives on another rank, so
+        the shifts run on the full rows and this rank's positions are selected afterwards."""
         cfg = self.cfg
         st = ps.get_state(model.state_name)
         T = tokens.shape[0]
@@ -72,6 +77,13 @@ class MultiTokenPredictionBlock(nn.Module):
         g = st.group("tp")
         tok, lab = tokens, labels
         mask = loss_mask.float() if loss_mask is not None else torch.ones(T, device=tokens.device)
+        local_idx = None
+        if full_batch is not None and st.dims.cp > 1:
+            from ..parallel.context_parallel import _positions
+            local_idx, _ = _positions(T, st.dims.cp, st.cp_rank, tokens.device, None,
+                                      packed.row_length if packed is not None else None)
+            tok, lab = full_batch["tokens"].reshape(-1), full_batch["labels"].reshape(-1)
+            mask = full_batch["loss_mask"].reshape(-1).float()
         w = model.shared_embedding_weight()
         per = cfg.padded_vocab_size // st.dims.tp
         v0 = st.tp_rank * per
@@ -86,16 +98,22 @@ class MultiTokenPredictionBlock(nn.Module):
                 ends = (packed.cu_seqlens[1:].long() - 1).clamp_min(0)
                 mask = mask.clone()
                 mask[ends] = 0  # never predict across a packed-sequence boundary
-            emb = model.embed(tok)  # a sequence shard under sequence parallelism
+            tok_k, lab_k, mask_k, denom = tok, lab, mask, mask.sum().clamp_min(1)
+            if local_idx is not None:
+                # this rank's positions of the shifted full rows; the mean runs over the whole micro-batch: gradients are
+                # averaged over the context-parallel ranks, hence the factor cp
+                tok_k, lab_k, mask_k = tok[local_idx], lab[local_idx], mask[local_idx]
+                denom = denom / st.dims.cp
+            emb = model.embed(tok_k)  # a sequence shard under sequence parallelism
             h = layer(h, emb, rotary, packed)
             # the vocab-parallel loss needs the full sequence and sums partial hidden-state gradients over TP
             from ..parallel import mappings as M
             h_full = M.gather_from_sequence_parallel_region(h, g, True) if sp else (
                 M.copy_to_tensor_model_parallel_region(h, g) if st.dims.tp > 1 else h)
-            l_k = OF.linear_cross_entropy(h_full, w, lab, mask, vocab_start=v0, valid_vocab=valid,
+            l_k = OF.linear_cross_entropy(h_full, w, lab_k, mask_k, vocab_start=v0, valid_vocab=valid,
                                           tp_group=st.group("tp") if st.dims.tp > 1 else None,
                                           chunk_tokens=cfg.cross_entropy_chunk_tokens)
-            mtp_loss = (l_k * mask).sum() / mask.sum().clamp_min(1)
+            mtp_loss = (l_k * mask_k).sum() / denom
             track_aux_loss("mtp_loss", mtp_loss, k, max(cfg.mtp_num_layers, 1))
             total = total + mtp_loss * (cfg.mtp_loss_scaling_factor / cfg.mtp_num_layers)
         return AuxLossScaler.apply(losses, total)

@@ -33,6 +33,9 @@ class PackedSeqParams:
     """Sequence boundaries of a packed ("thd") micro-batch."""
     cu_seqlens: Optional[torch.Tensor] = None  # int32 [num_seqs + 1]
     max_seqlen: Optional[int] = None
+    # Context parallelism cuts every ROW of the micro-batch into 2*cp chunks; with several rows per micro-batch this is
+    # the full (unsliced) row length, and `cu_seqlens` are offsets in the concatenation of the full rows. None = one row.
+    row_length: Optional[int] = None
 
 
 @dataclasses.dataclass
@@ -244,7 +247,8 @@ class SelfAttention(nn.Module):
             if rotary is not None:
                 q = self._rope(q, rotary)
                 k = self._rope(k, rotary)
-        o = core_attention(q, k, v, causal=cfg.causal, scale=self.scale, cu_seqlens=cu, cfg=cfg)
+        o = core_attention(q, k, v, causal=cfg.causal, scale=self.scale, cu_seqlens=cu, cfg=cfg,
+                           row_length=packed.row_length if packed is not None else None)
         return self.linear_proj(o.reshape(T, g * r * d), residual)
 
     def _rope_kw(self, rotary):
@@ -270,7 +274,8 @@ class SelfAttention(nn.Module):
 CHUNK_PREFIX = {"active": False, "past": None, "out": None}
 
 
-def core_attention(q, k, v, *, causal, scale, cu_seqlens, cfg: Optional[TransformerConfig] = None):
+def core_attention(q, k, v, *, causal, scale, cu_seqlens, cfg: Optional[TransformerConfig] = None,
+                   row_length: Optional[int] = None):
     """Attention over packed tokens; context parallelism is applied here when enabled."""
     st = ps.get_state()
     if CHUNK_PREFIX["active"]:
@@ -284,7 +289,7 @@ def core_attention(q, k, v, *, causal, scale, cu_seqlens, cfg: Optional[Transfor
         return _masked_attention(q, kk, vv, pos[P:], pos, scale, causal)
     if st.dims.cp > 1:
         from ..parallel import context_parallel as CP
-        return CP.ring_attention(q, k, v, causal=causal, scale=scale, cu_seqlens=cu_seqlens)
+        return CP.ring_attention(q, k, v, causal=causal, scale=scale, cu_seqlens=cu_seqlens, row_length=row_length)
     return OF.attention(q, k, v, causal=causal, scale=scale, cu_seqlens=cu_seqlens)
 
 

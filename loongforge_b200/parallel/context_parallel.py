@@ -83,19 +83,25 @@ def _masked_attention(q, k, v, q_pos, k_pos, scale, causal, seg_q=None, seg_k=No
     return o.to(q.dtype)
 
 
-def _positions(T_local: int, cp: int, rank: int, device, cu_seqlens=None):
-    """Row positions of this rank's tokens (the packed row is cut into 2*cp chunks; rank r holds chunks r and
-    2cp-1-r, see `get_batch_on_this_cp_rank`) and, for packed rows, the index of the sequence each token belongs to.
-    Row order is causal order inside every sequence, so masks built from (position, sequence) are exact for
-    sequences of any lengths; only the ROW length has to divide by 2*cp."""
-    pos = cp_chunk_indices(T_local * cp, cp, rank, device)
+def _positions(T_local: int, cp: int, rank: int, device, cu_seqlens=None, row_length: Optional[int] = None):
+    """Positions of this rank's tokens in the concatenation of the micro-batch's full rows (every row is cut into
+    2*cp chunks; rank r holds chunks r and 2cp-1-r of EACH row, see `get_batch_on_this_cp_rank`) and, for packed
+    rows, the index of the sequence each token belongs to. That order is causal order inside every sequence, so masks
+    built from (position, sequence) are exact for sequences of any lengths; only the row length has to divide by 2*cp."""
+    total = T_local * cp
+    row = row_length or total
+    one = cp_chunk_indices(row, cp, rank, device)
+    n_rows = total // row
+    pos = one if n_rows == 1 else (one[None, :] + torch.arange(n_rows, device=device)[:, None] * row).reshape(-1)
     if cu_seqlens is None:
-        return pos, None
+        if n_rows == 1:
+            return pos, None
+        return pos, torch.div(pos, row, rounding_mode="floor")
     seg = torch.bucketize(pos, cu_seqlens[1:].to(device=device, dtype=pos.dtype), right=True)
     return pos, seg
 
 
-def ring_attention(q, k, v, *, causal=True, scale=None, cu_seqlens=None):
+def ring_attention(q, k, v, *, causal=True, scale=None, cu_seqlens=None, row_length: Optional[int] = None):
     """Attention for sequence-sharded q/k/v ``[T/cp, H, D]`` (load-balanced chunks)."""
     st = ps.get_state()
     cp, rank, g = st.dims.cp, st.cp_rank, st.group("cp")
@@ -103,10 +109,10 @@ def ring_attention(q, k, v, *, causal=True, scale=None, cu_seqlens=None):
     kind = _CFG["comm_type"]
     Hq, Hkv = q.shape[1], k.shape[1]
     if kind == "auto":
-        kind = "a2a" if (Hq % cp == 0 and Hkv % cp == 0 and cu_seqlens is None) else "allgather"
+        kind = "a2a" if (Hq % cp == 0 and Hkv % cp == 0 and cu_seqlens is None and row_length is None) else "allgather"
     if kind == "a2a":
         return _ulysses(q, k, v, causal, scale, cp, rank, g)
-    pos, seg = _positions(q.shape[0], cp, rank, q.device, cu_seqlens)
+    pos, seg = _positions(q.shape[0], cp, rank, q.device, cu_seqlens, row_length)
     if kind == "allgather":
         k_all = M.gather_from_sequence_parallel_region(k, g, True)
         v_all = M.gather_from_sequence_parallel_region(v, g, True)

@@ -215,8 +215,12 @@ class Trainer:
         t = self.tcfg
         b = self.get_batch(data_iterator)
         cp = self.st.dims.cp
+        extra = {}
         if cp > 1:
             from ..parallel.context_parallel import get_batch_on_this_cp_rank
+            if self.mcfg.mtp_num_layers > 0 and self.st.is_last_stage:
+                # multi-token prediction shifts tokens across the chunk boundaries of the context-parallel slice
+                extra["full_batch"] = {k: b[k] for k in ("tokens", "labels", "loss_mask")}
             b = get_batch_on_this_cp_rank(b, cp, self.st.cp_rank)
         tokens = b["tokens"].reshape(-1)
         labels = b["labels"].reshape(-1)
@@ -226,10 +230,12 @@ class Trainer:
         packed = None
         if bs > 1 or "cu_seqlens" in b:
             cu = b.get("cu_seqlens")
+            full_len = b["tokens"].shape[1] * cp  # row length before the context-parallel slice
             if cu is None:
-                sl = t.seq_length // cp
-                cu = torch.arange(0, (bs + 1) * sl, sl, dtype=torch.int32, device=self.device)
-            packed = PackedSeqParams(cu_seqlens=cu, max_seqlen=t.seq_length // cp)
+                # one sequence per row; under context parallelism boundaries are offsets in the FULL rows
+                cu = torch.arange(0, (bs + 1) * full_len, full_len, dtype=torch.int32, device=self.device)
+            packed = PackedSeqParams(cu_seqlens=cu, max_seqlen=full_len,
+                                     row_length=full_len if (cp > 1 and bs > 1) else None)
         n_valid = b.get("num_valid_tokens")
         if n_valid is None:
             n_valid = int(mask.numel()) * cp
@@ -237,7 +243,7 @@ class Trainer:
         # each context-parallel rank sums its own tokens; gradients are averaged over dp x cp, so the
         # factor cp turns that average into (sum over cp, mean over dp)
         scale = float(cp) / (max(n_valid, 1) * nmb)
-        out = model(tokens, pos, labels=labels, loss_mask=mask, packed=packed, loss_scale=scale)
+        out = model(tokens, pos, labels=labels, loss_mask=mask, packed=packed, loss_scale=scale, **extra)
 
         def loss_func(losses):
             loss = (losses * mask.float()).sum() * scale

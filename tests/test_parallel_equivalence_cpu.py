@@ -6,7 +6,7 @@ import torch
 from dist_utils import run_distributed
 
 
-def _run(rank, world, model_name, dims_kw, steps, overrides, gbs=4):
+def _run(rank, world, model_name, dims_kw, steps, overrides, gbs=4, mbs=1):
     from loongforge_b200.data.synthetic import synthetic_batch_iterator
     from loongforge_b200.models.registry import get_model_config
     from loongforge_b200.parallel.state import ParallelDims
@@ -16,11 +16,11 @@ def _run(rank, world, model_name, dims_kw, steps, overrides, gbs=4):
     if dims_kw.get("tp", 1) > 1:
         cfg.sequence_parallel = dims_kw.pop("sp", True)
     dims_kw.pop("sp", None)
-    tc = TrainConfig(micro_batch_size=1, global_batch_size=gbs, seq_length=64, train_iters=steps, lr=1e-3,
+    tc = TrainConfig(micro_batch_size=mbs, global_batch_size=gbs, seq_length=64, train_iters=steps, lr=1e-3,
                      clip_grad=1.0, log_interval=1000)
     tr = Trainer(cfg, tc, ParallelDims(**dims_kw))
     st = tr.st
-    it = synthetic_batch_iterator(cfg.vocab_size, 64, 1, dp_rank=st.dp_rank, dp_size=st.dp_size, seed=3,
+    it = synthetic_batch_iterator(cfg.vocab_size, 64, mbs, dp_rank=st.dp_rank, dp_size=st.dp_size, seed=3,
                                   pin_memory=False)
     out = []
     for _ in range(steps):
@@ -29,8 +29,8 @@ def _run(rank, world, model_name, dims_kw, steps, overrides, gbs=4):
     return out
 
 
-def _single(model_name, steps, overrides, gbs=4):
-    return run_distributed(_run, 1, model_name, {}, steps, overrides, gbs)[0]
+def _single(model_name, steps, overrides, gbs=4, mbs=1):
+    return run_distributed(_run, 1, model_name, {}, steps, overrides, gbs, mbs)[0]
 
 
 def _check(ref, res, have_loss, tol=2e-4):
@@ -95,6 +95,19 @@ def test_more_layouts_match_single_process(model, dims, ov, world):
     res = run_distributed(_run, world, model, dict(dims), 2, ov)
     pp = dims.get("pp", 1)
     _check(ref, res, lambda r: r // (world // pp) == pp - 1, tol=1e-3)
+
+
+@pytest.mark.parametrize("model,dims,ov,world", [
+    ("tiny-minimax", {"cp": 2}, {}, 2),                      # MTP shifts across context-parallel chunk boundaries
+    ("tiny-deepseek", {"cp": 2}, {"use_dsa": False}, 2),     # dense MLA through ring attention
+    ("tiny-llama", {"tp": 2, "cp": 2}, {}, 4),
+    ("tiny-ernie-vl", {"tp": 2}, {}, 2),                     # shared expert over the gathered sequence
+])
+def test_two_rows_per_microbatch_match_single_process(model, dims, ov, world):
+    """Micro-batches of two rows: context parallelism slices every row separately."""
+    ref = _single(model, 2, ov, mbs=2)
+    res = run_distributed(_run, world, model, dict(dims), 2, ov, 4, 2)
+    _check(ref, res, lambda r: True, tol=1e-3)
 
 
 def _run_cp(rank, world, comm):
