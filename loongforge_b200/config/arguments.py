@@ -162,7 +162,9 @@ def _add_training_args(p):
     g.add_argument("--iterations-to-skip", type=int, nargs="*", default=[])
     g.add_argument("--error-injection-rate", type=int, default=0)
     g.add_argument("--error-injection-type", type=str, default="transient_error")
-    g.add_argument("--rerun-mode", type=str, default="disabled")
+    g.add_argument("--rerun-mode", type=str, default="disabled",
+                   choices=["disabled", "validate_results", "report_stats"])
+    g.add_argument("--check-weight-hash-across-dp-replicas-interval", type=int, default=None)
     g.add_argument("--manual-gc", action="store_true")
     g.add_argument("--manual-gc-interval", type=int, default=0)
     g.add_argument("--ema-decay", type=float, default=None)
@@ -234,6 +236,8 @@ def _add_ckpt_logging_args(p):
     g.add_argument("--enable-log-tensor", action="store_true")
     g.add_argument("--log-tensor-name-pattern", type=str, default=None)
     g.add_argument("--log-straggler", action="store_true")
+    g.add_argument("--heartbeat-timeout-s", type=float, default=None,
+                   help="report ranks whose per-step heartbeat in the job store stopped for this long; checkpoint and exit")
 
 
 def _add_peft_args(p):

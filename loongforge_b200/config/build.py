@@ -186,6 +186,11 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
         fp8_policy_file=getattr(args, "fp8_dynamic_policy_path", None),
         chunkpipe_chunks=(max(1, args.seq_length // int(args.chunksize))
                           if getattr(args, "enable_chunkpipe", False) and getattr(args, "chunksize", None) else 0),
+        rerun_mode=getattr(args, "rerun_mode", "disabled") or "disabled",
+        error_injection_rate=int(getattr(args, "error_injection_rate", 0) or 0),
+        error_injection_type=getattr(args, "error_injection_type", "transient_error"),
+        iterations_to_skip=list(getattr(args, "iterations_to_skip", []) or []),
+        check_weight_hash_interval=int(getattr(args, "check_weight_hash_across_dp_replicas_interval", 0) or 0),
         dp_balance=bool(getattr(args, "use_vlm_dp_balance", False)),
         optimizer_cpu_offload=bool(getattr(args, "optimizer_cpu_offload", False)),
         use_fsdp=bool(getattr(args, "use_torch_fsdp2", False) or getattr(args, "use_megatron_fsdp", False)),

@@ -7,6 +7,8 @@ The CUDA kernels live in ``csrc/quant.cu``; the functions here dispatch to them 
 same numbers with PyTorch ops (also the oracle of the kernel tests)."""
 from __future__ import annotations
 
+import dataclasses
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -14,27 +16,71 @@ import torch
 E4M3_MAX = 448.0
 
 
-def _scale(amax: torch.Tensor, pow2: bool) -> torch.Tensor:
-    s = amax.clamp(min=1e-12) / E4M3_MAX
+@dataclasses.dataclass
+class QParams:
+    power_2_scale: bool = False
+    amax_epsilon: float = 0.0  # floor of the block maximum before the scale is derived
+
+
+@dataclasses.dataclass
+class BlockScalingRecipe:
+    """Per-tensor-class settings of the blockwise FP8 linear: forward input (1 x 128 tiles), forward weight
+    (128 x 128 blocks) and backward output gradient (1 x 128 tiles). Defaults come from the environment variables the
+    reference's TransformerEngine patch introduces (patches/.../common/recipe/__init__.py.patch:9-31):
+    ``NVTE_FP8_BLOCK_SCALING_FP32_SCALES`` (1 = plain fp32 scales, else powers of two), overridden per class by
+    ``NVTE_FP8_BLOCK_SCALING_{FWD_INP,FWD_WEIGHT,BWD_GRAD}_POWER2`` and floored by
+    ``FP8_QUANT_{FWD_INP,FWD_WEIGHT,BWD_GRAD}_AMAX_EPS``."""
+    fwd_inp: QParams = dataclasses.field(default_factory=QParams)
+    fwd_weight: QParams = dataclasses.field(default_factory=QParams)
+    bwd_grad: QParams = dataclasses.field(default_factory=QParams)
+
+    @staticmethod
+    def from_env(env=None) -> "BlockScalingRecipe":
+        env = os.environ if env is None else env
+        f32 = env.get("NVTE_FP8_BLOCK_SCALING_FP32_SCALES", "0") == "1"
+
+        def one(tag: str) -> QParams:
+            v = env.get(f"NVTE_FP8_BLOCK_SCALING_{tag}_POWER2")
+            return QParams((v == "1") if v is not None else (not f32), float(env.get(f"FP8_QUANT_{tag}_AMAX_EPS", "0.0")))
+
+        return BlockScalingRecipe(one("FWD_INP"), one("FWD_WEIGHT"), one("BWD_GRAD"))
+
+
+_RECIPE = {"r": None}
+
+
+def get_recipe() -> BlockScalingRecipe:
+    if _RECIPE["r"] is None:
+        _RECIPE["r"] = BlockScalingRecipe.from_env()
+    return _RECIPE["r"]
+
+
+def set_recipe(r: Optional[BlockScalingRecipe]) -> None:
+    """None re-reads the environment on the next use."""
+    _RECIPE["r"] = r
+
+
+def _scale(amax: torch.Tensor, pow2: bool, eps: float = 0.0) -> torch.Tensor:
+    s = amax.clamp(min=max(eps, 1e-12)) / E4M3_MAX
     if pow2:
         s = torch.exp2(torch.ceil(torch.log2(s)))
     return s
 
 
-def quantize_1x128_ref(x: torch.Tensor, pow2: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+def quantize_1x128_ref(x: torch.Tensor, pow2: bool = False, eps: float = 0.0) -> Tuple[torch.Tensor, torch.Tensor]:
     """x [M, K] (K % 128 == 0) -> (q float8_e4m3fn [M, K], scales fp32 [M, K/128]); x ~= q * scale."""
     M, K = x.shape
     xb = x.float().view(M, K // 128, 128)
-    s = _scale(xb.abs().amax(-1), pow2)
+    s = _scale(xb.abs().amax(-1), pow2, eps)
     q = (xb / s.unsqueeze(-1)).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
     return q.view(M, K), s
 
 
-def quantize_128x128_ref(w: torch.Tensor, pow2: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+def quantize_128x128_ref(w: torch.Tensor, pow2: bool = False, eps: float = 0.0) -> Tuple[torch.Tensor, torch.Tensor]:
     """w [N, K] (both % 128 == 0) -> (q [N, K] e4m3, scales [N/128, K/128])."""
     N, K = w.shape
     wb = w.float().view(N // 128, 128, K // 128, 128)
-    s = _scale(wb.abs().amax(dim=(1, 3)), pow2)
+    s = _scale(wb.abs().amax(dim=(1, 3)), pow2, eps)
     q = (wb / s[:, None, :, None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
     return q.view(N, K), s
 
@@ -119,8 +165,9 @@ class _Fp8LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x2, weight, pow2):
         ctx.save_for_backward(x2, weight)
-        ctx.pow2 = pow2
-        return fp8_blockwise_linear(x2, weight, pow2)
+        r = get_recipe()
+        ctx.recipe = r
+        return _recipe_linear(x2, weight, r.fwd_inp, r.fwd_weight, pow2)
 
     @staticmethod
     def backward(ctx, dy):
@@ -131,10 +178,22 @@ class _Fp8LinearFn(torch.autograd.Function):
         dx = dw = None
         if ctx.needs_input_grad[0]:
             # dx [T, K] = dy [T, N] @ W [N, K]: contraction over N, so dy is tiled along N and W^T is the blocked operand
-            dx = fp8_blockwise_linear(dy, weight.t().contiguous(), ctx.pow2)
+            dx = _recipe_linear(dy, weight.t().contiguous(), ctx.recipe.bwd_grad, ctx.recipe.fwd_weight, None)
         if ctx.needs_input_grad[1]:
             dw = OF._wgrad(dy, x2, weight)
         return dx, dw, None
+
+
+def _recipe_linear(a: torch.Tensor, b: torch.Tensor, qa: QParams, qb: QParams, pow2_override) -> torch.Tensor:
+    """a [M, K] (1 x 128 tiles) times b [N, K] (128 x 128 blocks) under the recipe's per-class settings. The native
+    kernels implement the zero-epsilon case with one pow-2 switch; other settings use the PyTorch formulation."""
+    pa = qa.power_2_scale if pow2_override is None else (pow2_override or qa.power_2_scale)
+    pb = qb.power_2_scale if pow2_override is None else (pow2_override or qb.power_2_scale)
+    if pa == pb and qa.amax_epsilon == 0.0 and qb.amax_epsilon == 0.0:
+        return fp8_blockwise_linear(a, b, pa)
+    qx, sx = quantize_1x128_ref(a, pa, qa.amax_epsilon)
+    qw, sw = quantize_128x128_ref(b, pb, qb.amax_epsilon)
+    return (dequantize_1x128(qx, sx) @ dequantize_128x128(qw, sw).t()).to(a.dtype)
 
 
 def fp8_linear_supported(in_features: int, out_features: int) -> bool:

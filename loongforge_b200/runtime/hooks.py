@@ -117,6 +117,43 @@ class RetentionHook(TrainHook):
             apply_retention(t.save, self.keep, self.retain)
 
 
+class StragglerHook(TrainHook):
+    """Per-rank step times exchanged every ``log_interval`` steps; ranks slower than the threshold x median are
+    reported on the logging rank (``--log-straggler``, reference: loongforge/train/training_utils.py:162,2549-2560)."""
+
+    def __init__(self, trainer, threshold: float = 1.3, sink=print):
+        from .resilience import StragglerDetector
+        self.det = StragglerDetector(None, threshold)
+        self.sink, self.every = sink, max(1, trainer.tcfg.log_interval)
+        self.reports: List[dict] = []
+
+    def on_step_end(self, trainer, metrics, elapsed_ms):
+        self.det.times.append(elapsed_ms / 1e3)
+        if trainer.iteration % self.every == 0:
+            rep = self.det.report()
+            self.reports.append(rep)
+            is_main = (not dist.is_initialized()) or dist.get_rank() == 0
+            if rep["stragglers"] and is_main:
+                self.sink(f" [straggler] iteration {trainer.iteration}: ranks {rep['stragglers']} are slower than "
+                          f"{self.det.threshold:.2f} x median step time {rep['median'] * 1e3:.1f} ms")
+
+
+class HeartbeatHook(TrainHook):
+    """Rank liveness through the job's key-value store: every rank bumps its counter after each step; a peer whose
+    counter stopped for ``timeout_s`` is reported BEFORE the next collective would hang on it, and the loop asks for
+    checkpoint-and-exit."""
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 600.0):
+        from .resilience import Heartbeat
+        self.hb = Heartbeat(store, rank, world, timeout_s)
+        self.dead: List[int] = []
+
+    def on_step_end(self, trainer, metrics, elapsed_ms):
+        self.hb.beat()
+        self.dead = self.hb.dead_ranks()
+        return f"ranks {self.dead} stopped sending heartbeats" if self.dead else None
+
+
 def build_hooks(args, trainer) -> List[TrainHook]:
     rank = dist.get_rank() if dist.is_initialized() else 0
     world = dist.get_world_size() if dist.is_initialized() else 1
@@ -136,6 +173,11 @@ def build_hooks(args, trainer) -> List[TrainHook]:
         hooks.append(ScalarHook(out, getattr(args, "wandb_project", None), enabled=(rank == world - 1)))
     if getattr(args, "manual_gc", False):
         hooks.append(ManualGCHook(getattr(args, "manual_gc_interval", 0) or 1))
+    if getattr(args, "log_straggler", False):
+        hooks.append(StragglerHook(trainer))
+    if getattr(args, "heartbeat_timeout_s", None) and dist.is_initialized() and world > 1:
+        store = dist.distributed_c10d._get_default_store()
+        hooks.append(HeartbeatHook(store, rank, world, float(args.heartbeat_timeout_s)))
     if getattr(args, "exit_interval", None) or getattr(args, "exit_duration_in_mins", None):
         hooks.append(ExitHook(getattr(args, "exit_duration_in_mins", None), getattr(args, "exit_interval", None), False))
     return hooks

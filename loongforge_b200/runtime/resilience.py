@@ -104,8 +104,10 @@ class ErrorInjector:
         self.rng = random.Random(seed)
         self.sticky = False
 
-    def maybe_corrupt(self, loss: float) -> float:
-        if self.rate <= 0 or self.kind == "correct_result":
+    def maybe_corrupt(self, loss: float, replay: bool = False) -> float:
+        """``replay``: the value comes from the re-run of a step whose first result was rejected; a transient fault
+        does not strike the same step twice."""
+        if self.rate <= 0 or self.kind == "correct_result" or (replay and self.kind == "transient_error"):
             return loss
         if self.kind == "persistent_error" and self.sticky:
             return float("nan")
@@ -163,9 +165,11 @@ class Heartbeat:
         for r in range(self.world):
             if r == self.rank:
                 continue
+            key = f"hb/{r}"
             try:
-                v = int(self.store.get(f"hb/{r}").decode())
-            except Exception:  # noqa: BLE001 - key not written yet
+                # `get` blocks until the key exists: ask first, a rank that never wrote counts as silent
+                v = int(self.store.get(key).decode()) if self.store.check([key]) else -1
+            except Exception:  # noqa: BLE001 - store without `check`, or the key vanished
                 v = -1
             last = self.seen.get(r)
             if last is None or last[0] != v:

@@ -61,6 +61,11 @@ class TrainConfig:
     master_as_remainder: bool = False
     optimizer_cpu_offload: bool = False  # masters + Adam moments on the host, native host AdamW
     fp8_policy_file: Optional[str] = None  # JSON rules: which linear kinds run FP8 (runtime/fp8_policy.py)
+    rerun_mode: str = "disabled"  # disabled | validate_results | report_stats (runtime/resilience.py)
+    error_injection_rate: int = 0  # host-side loss corruption every N steps on average (testing the rerun machine)
+    error_injection_type: str = "transient_error"
+    iterations_to_skip: Optional[List[int]] = None  # their data is consumed, no update happens
+    check_weight_hash_interval: int = 0  # > 0: compare parameter checksums across data-parallel replicas every N steps
     dp_balance: bool = False  # trade whole micro-batches between DP ranks by modelled cost (data/dp_balance.py)
     chunkpipe_chunks: int = 0  # > 1: every sequence runs as that many chunks (runtime/chunkpipe.py)
     use_fsdp: bool = False  # FSDP2 units instead of DDP + distributed optimizer (runtime/fsdp_trainer.py)
@@ -130,6 +135,11 @@ class Trainer:
         self.model_provider = model_provider or self._default_model_provider
         self.forward_step = forward_step or self._default_forward_step
         self.models = self._build_models()
+        from .resilience import ErrorInjector, RerunStateMachine
+        self.rerun = RerunStateMachine(train_cfg.rerun_mode)
+        self.injector = (ErrorInjector(train_cfg.error_injection_rate, train_cfg.error_injection_type, train_cfg.seed)
+                         if train_cfg.error_injection_rate > 0 else None)
+        self.exit_requested: Optional[str] = None
         self.fp8_decisions = {}
         if model_cfg.fp8:
             from . import fp8_policy as FP
@@ -267,17 +277,29 @@ class Trainer:
         fb = schedules.get_forward_backward_func()
         T = t.seq_length * t.micro_batch_size
         sp_div = self.st.dims.tp if self.mcfg.sequence_parallel else 1
-        if t.chunkpipe_chunks and t.chunkpipe_chunks > 1:
-            reports = self._chunkpipe_microbatches(data_iterator)
+        def forward_backward(it):
+            if t.chunkpipe_chunks and t.chunkpipe_chunks > 1:
+                return self._chunkpipe_microbatches(it)
+            return fb(forward_step_func=self.forward_step, data_iterator=it,
+                      model=self.models if len(self.models) > 1 else self.models[0],
+                      num_microbatches=self.mb_calc.num_microbatches,
+                      tensor_shape=(T // sp_div // self.st.dims.cp, self.mcfg.hidden_size *
+                                    (self.mcfg.num_residual_streams if self.mcfg.enable_hyper_connections else 1)),
+                      dtype=self.mcfg.params_dtype)
+
+        skip_update = False
+        if self.rerun.mode == "disabled" and self.injector is None:
+            reports = forward_backward(data_iterator)
         else:
-            reports = fb(forward_step_func=self.forward_step, data_iterator=data_iterator,
-                         model=self.models if len(self.models) > 1 else self.models[0],
-                         num_microbatches=self.mb_calc.num_microbatches,
-                         tensor_shape=(T // sp_div // self.st.dims.cp, self.mcfg.hidden_size *
-                                       (self.mcfg.num_residual_streams if self.mcfg.enable_hyper_connections else 1)),
-                         dtype=self.mcfg.params_dtype)
-        self._allreduce_sequence_parallel_grads()
-        ok, grad_norm, _ = self.optimizer.step()
+            reports, skip_update = self._validated_forward_backward(forward_backward, data_iterator)
+        if skip_update:
+            self.optimizer.zero_grad()
+            for m in self.models:
+                m.finish_grad_sync()  # nothing may stay in flight
+            ok, grad_norm = False, float("nan")
+        else:
+            self._allreduce_sequence_parallel_grads()
+            ok, grad_norm, _ = self.optimizer.step()
         if ok:
             self.scheduler.step(1)
             skipped = 0
@@ -296,6 +318,74 @@ class Trainer:
             for k, v in zip(keys, vals.tolist()):
                 metrics[k] = v
         return metrics
+
+    # ------------------------------------------------------------------ result validation (rerun state machine)
+    def _global_loss(self, reports) -> float:
+        """The step's loss as every rank must see it to take the same decision: mean over the micro-batches of all
+        data-parallel ranks; NaN / Inf anywhere wins."""
+        v = torch.zeros(4, dtype=torch.float64, device=self.device)  # sum, count, any nan, any inf
+        for r in reports:
+            x = float(r["lm loss"]) if "lm loss" in r else None
+            if x is None:
+                continue
+            if math.isnan(x):
+                v[2] += 1
+            elif math.isinf(x):
+                v[3] += 1
+            else:
+                v[0] += x
+                v[1] += 1
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(v)
+        s_, n, nan, inf = v.tolist()
+        if nan:
+            return float("nan")
+        if inf:
+            return float("inf")
+        return s_ / max(n, 1.0)
+
+    def _validated_forward_backward(self, forward_backward, data_iterator):
+        """Forward/backward under the rerun state machine: a NaN / Inf / spiky loss triggers ONE replay of the same
+        micro-batches with the same RNG state before any update is applied. A different result means a transient fault
+        (the step is skipped), the same bad result a persistent one (checkpoint and exit). Returns (reports,
+        skip_update)."""
+        from ..ckpt.checkpointing import get_rng_state, set_rng_state
+
+        replay = _ReplayIterator(data_iterator)
+        rng = get_rng_state()
+        replaying = False
+        while True:
+            reports = forward_backward(replay)
+            loss = self._global_loss(reports)
+            if self.injector is not None:
+                loss = self.injector.maybe_corrupt(loss, replay=replaying)
+            d = self.rerun.validate(loss)
+            if d.action == "rerun":
+                replaying = True
+                self.optimizer.zero_grad()
+                replay.rewind()
+                set_rng_state(rng)
+                continue
+            if d.action == "exit":
+                self.exit_requested = d.reason
+            return reports, d.action in ("skip", "exit")
+
+    def check_weight_hash_across_dp_replicas(self) -> bool:
+        """Data-parallel replicas must hold bit-identical parameters: compares a checksum of every replica's parameter
+        buffers over the data-parallel group (reference: loongforge/train/training_utils.py:2640-2645)."""
+        acc = torch.zeros(1, dtype=torch.int64, device=self.device)
+        for m in self.models:
+            for buf in m._all_buffers:
+                if buf.dp_group is not self.st.group("dp_cp"):
+                    continue  # expert buffers are replicated over a different group
+                bits = buf.param_data.view(torch.int16 if buf.param_data.element_size() == 2 else torch.int32)
+                acc += bits.to(torch.int64).sum()
+        lo, hi = acc.clone(), acc.clone()
+        g = self.st.group("dp_cp")
+        if g is not None:
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=g)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=g)
+        return bool((lo == hi).item())
 
     def _balanced(self, data_iterator):
         """One balancing wrapper per source iterator (it buffers the step's micro-batches)."""
@@ -400,9 +490,20 @@ class Trainer:
         t = self.tcfg
         history = []
         is_log_rank = (not dist.is_initialized()) or dist.get_rank() == dist.get_world_size() - 1
+        skip = set(t.iterations_to_skip or ())
         while self.iteration < t.train_iters:
+            if (self.iteration + 1) in skip:
+                # the iteration's data is consumed so that later iterations see what they would have seen
+                for _ in range(self.mb_calc.num_microbatches):
+                    next(data_iterator)
+                self.iteration += 1
+                self.consumed_samples += t.global_batch_size
+                continue
             t0 = self._now()
             metrics = self.train_step(data_iterator)
+            if t.check_weight_hash_interval and self.iteration % t.check_weight_hash_interval == 0:
+                if not self.check_weight_hash_across_dp_replicas():
+                    raise RuntimeError(f"parameters differ between data-parallel replicas at iteration {self.iteration}")
             elapsed_ms = (self._now() - t0) * 1e3
             self.num_flops_so_far += self.flops_per_step()
             history.append(metrics)
@@ -416,7 +517,7 @@ class Trainer:
                     (on_log or print)(line)
             if t.save and t.save_interval and self.iteration % t.save_interval == 0:
                 self.save_checkpoint(t.save)
-            stop = None
+            stop = self.exit_requested
             for h in getattr(self, "hooks", ()):
                 stop = h.on_step_end(self, metrics, elapsed_ms) or stop
             if stop:
@@ -444,3 +545,25 @@ class Trainer:
     def load_checkpoint(self, path: str, **kw):
         from ..ckpt import checkpointing
         return checkpointing.load_checkpoint(path, self, **kw)
+
+
+class _ReplayIterator:
+    """Remembers what the current step pulled from the data iterator so that the step can be replayed."""
+
+    def __init__(self, it):
+        self.it, self.seen, self.pos = it, [], 0
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        if self.pos < len(self.seen):
+            item = self.seen[self.pos]
+        else:
+            item = next(self.it)
+            self.seen.append(item)
+        self.pos += 1
+        return item
+
+    def rewind(self):
+        self.pos = 0

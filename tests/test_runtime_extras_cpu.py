@@ -167,3 +167,32 @@ def test_diffusion_trainers_reduce_loss():
     q = D.QwenImageModel(cfg)
     qt = QwenImageTrainer(q, torch.optim.AdamW(q.parameters(), lr=2e-3))
     assert np.isfinite(qt.train_step({"latents": torch.randn(2, 4, 4, 4), "text": torch.randn(2, 3, 16)})["loss"])
+
+
+def test_fp8_block_scaling_recipe_from_environment():
+    import torch
+
+    from loongforge_b200.ops import quant as Q
+
+    r = Q.BlockScalingRecipe.from_env({})
+    assert r.fwd_inp.power_2_scale and r.fwd_weight.power_2_scale and r.bwd_grad.power_2_scale
+    r = Q.BlockScalingRecipe.from_env({"NVTE_FP8_BLOCK_SCALING_FP32_SCALES": "1",
+                                       "NVTE_FP8_BLOCK_SCALING_BWD_GRAD_POWER2": "1", "FP8_QUANT_FWD_INP_AMAX_EPS": "1e-3"})
+    assert (r.fwd_inp.power_2_scale, r.fwd_weight.power_2_scale, r.bwd_grad.power_2_scale) == (False, False, True)
+    assert r.fwd_inp.amax_epsilon == 1e-3
+    # power-of-two scales are exact powers of two; the epsilon floors the block maximum
+    x = torch.randn(4, 256) * 1e-6
+    _, s = Q.quantize_1x128_ref(x, pow2=True)
+    assert torch.equal(torch.exp2(torch.round(torch.log2(s))), s)
+    _, s_eps = Q.quantize_1x128_ref(x, pow2=False, eps=1e-3)
+    assert torch.allclose(s_eps, torch.full_like(s_eps, 1e-3 / Q.E4M3_MAX))
+    # the training linear follows the active recipe
+    Q.set_recipe(r)
+    try:
+        xx, w = torch.randn(8, 128, requires_grad=True), torch.randn(128, 128, requires_grad=True)
+        y = Q.fp8_linear(xx, w)
+        y.sum().backward()
+        ref = xx.detach() @ w.detach().t()
+        assert (y - ref).abs().max() / ref.abs().max() < 0.1 and xx.grad is not None and w.grad is not None
+    finally:
+        Q.set_recipe(None)

@@ -277,3 +277,64 @@ def test_dp_balance_moves_microbatches_without_changing_the_step():
     assert len(seen0) == len(seen1) == 8, "every rank keeps its micro-batch count"
     assert {r for r, _ in seen0} == {0, 1}, "rank 0 now also processes micro-batches that rank 1 loaded"
     assert sorted(seen0[:4] + seen1[:4]) == sorted(plain[0][1][:4] + plain[1][1][:4]), "the step's batch set is unchanged"
+
+
+def _resilient(rank, world, kind, rate):
+    from loongforge_b200.data.synthetic import synthetic_batch_iterator
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.runtime.trainer import TrainConfig, Trainer
+
+    cfg = get_model_config("tiny-llama")
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=4, seq_length=64, train_iters=6, lr=1e-3, log_interval=1000,
+                     rerun_mode="validate_results", error_injection_rate=rate, error_injection_type=kind, seed=5,
+                     iterations_to_skip=[2], check_weight_hash_interval=1)
+    tr = Trainer(cfg, tc)
+    st = tr.st
+    pulled = []
+
+    def it():
+        for b in synthetic_batch_iterator(cfg.vocab_size, 64, 1, dp_rank=st.dp_rank, dp_size=st.dp_size, seed=3,
+                                          pin_memory=False):
+            pulled.append(1)
+            yield b
+
+    hist = tr.train(it())
+    return [m["skipped"] for m in hist], tr.rerun.stats, tr.exit_requested, tr.iteration, len(pulled)
+
+
+def test_rerun_machine_error_injection_and_iteration_skipping():
+    from dist_utils import run_distributed
+
+    # transient faults: every corrupted loss is replayed once, comes back clean, and the step is applied
+    skipped, stats, exit_reason, it, pulled = run_distributed(_resilient, 2, "transient_error", 2)[0]
+    assert exit_reason is None and it == 6 and sum(skipped) == 0 and stats["nan"] >= 1 and stats["transient"] == stats["nan"]
+    assert len(skipped) == 5 and pulled == 6 * 2, "iteration 2 trained nothing but consumed its two micro-batches"
+    # a persistent fault reproduces on replay: no update, checkpoint-and-exit requested, the loop stops
+    skipped, stats, exit_reason, it, _ = run_distributed(_resilient, 2, "persistent_error", 1)[0]
+    assert exit_reason and "persistent" in exit_reason and stats["persistent"] == 1 and skipped == [1] and it == 1
+
+
+def test_straggler_and_heartbeat_hooks():
+    import types
+
+    import torch.distributed as dist
+
+    from loongforge_b200.runtime import hooks as H
+
+    tr = types.SimpleNamespace(tcfg=types.SimpleNamespace(log_interval=2), iteration=0)
+    lines = []
+    sh = H.StragglerHook(tr, threshold=1.3, sink=lines.append)
+    for i in range(4):
+        tr.iteration = i + 1
+        sh.on_step_end(tr, {}, 100.0)
+    assert len(sh.reports) == 2 and sh.reports[0]["stragglers"] == [] and not lines
+    store = dist.HashStore()
+    a, b = H.HeartbeatHook(store, 0, 2, timeout_s=5.0), H.HeartbeatHook(store, 1, 2, timeout_s=5.0)
+    assert a.on_step_end(tr, {}, 1.0) is None and b.on_step_end(tr, {}, 1.0) is None
+    # rank 1 stops beating; rank 0 keeps going and notices once the timeout has passed (time is injected, not slept)
+    a.hb.beat()
+    assert a.hb.dead_ranks(now=1000.0) == []          # observes rank 1's first beat
+    assert a.hb.dead_ranks(now=1004.0) == []          # unchanged, but within the timeout
+    assert a.hb.dead_ranks(now=1006.0) == [1]         # unchanged for longer than the timeout
+    b.hb.beat()
+    assert a.hb.dead_ranks(now=1007.0) == []
