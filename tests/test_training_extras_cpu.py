@@ -338,3 +338,31 @@ def test_straggler_and_heartbeat_hooks():
     assert a.hb.dead_ranks(now=1006.0) == [1]         # unchanged for longer than the timeout
     b.hb.beat()
     assert a.hb.dead_ranks(now=1007.0) == []
+
+
+def _leaver(rank, world):
+    """Rank 1 leaves between steps (no collective in flight); rank 0 learns of it from the store, not from a hang."""
+    import time
+
+    import torch.distributed as dist
+
+    from loongforge_b200.runtime.resilience import Heartbeat
+
+    hb = Heartbeat(dist.distributed_c10d._get_default_store(), rank, world, timeout_s=1.0)
+    dist.barrier()
+    for step in range(40):
+        hb.beat()
+        if rank == 1 and step == 2:
+            return "left"
+        dead = hb.dead_ranks()
+        if dead:
+            return ("detected", dead, step)
+        time.sleep(0.2)
+    return "never noticed"
+
+
+def test_rank_that_leaves_is_detected_through_the_store():
+    from dist_utils import run_distributed
+
+    r0, r1 = run_distributed(_leaver, 2)
+    assert r1 == "left" and r0[0] == "detected" and r0[1] == [1] and r0[2] > 2
