@@ -74,6 +74,30 @@ def load_hf_checkpoint_online(trainer, hf_dir: str, family: str = "llama3") -> i
     return n
 
 
+_HF_ARCH = {"llama": ("llama", "LlamaForCausalLM"), "llama2": ("llama", "LlamaForCausalLM"),
+            "llama3": ("llama", "LlamaForCausalLM"), "internlm": ("internlm2", "InternLM2ForCausalLM"),
+            "qwen2": ("qwen2", "Qwen2ForCausalLM"), "qwen2.5": ("qwen2", "Qwen2ForCausalLM"),
+            "qwen3": ("qwen3", "Qwen3ForCausalLM"), "qwen3_moe": ("qwen3_moe", "Qwen3MoeForCausalLM")}
+
+
+def hf_config_from_model(cfg, family: str) -> dict:
+    """``config.json`` contents for the exported weights, derived from the training configuration."""
+    model_type, arch = _HF_ARCH.get(family, ("llama", "LlamaForCausalLM"))
+    out = {
+        "architectures": [arch], "model_type": model_type, "hidden_size": cfg.hidden_size,
+        "intermediate_size": cfg.ffn_hidden_size, "num_hidden_layers": cfg.num_layers,
+        "num_attention_heads": cfg.num_attention_heads, "num_key_value_heads": cfg.num_query_groups,
+        "head_dim": cfg.kv_channels, "vocab_size": cfg.vocab_size, "rms_norm_eps": cfg.layernorm_epsilon,
+        "rope_theta": cfg.rotary_base, "max_position_embeddings": cfg.max_position_embeddings,
+        "tie_word_embeddings": not cfg.untie_embeddings_and_output_weights, "hidden_act": "silu",
+        "attention_bias": bool(cfg.add_qkv_bias), "torch_dtype": str(cfg.params_dtype).replace("torch.", ""),
+    }
+    if cfg.num_moe_experts:
+        out.update(num_experts=cfg.num_moe_experts, num_experts_per_tok=cfg.moe_router_topk,
+                   moe_intermediate_size=cfg.moe_ffn_hidden_size, norm_topk_prob=True)
+    return out
+
+
 def save_hf_checkpoint(trainer, out_dir: str, family: str = "llama3", hf_config: Optional[dict] = None) -> None:
     """Gather the model to rank 0 (TP shards merged, pipeline stages concatenated) and write safetensors."""
     from tools.convert_checkpoint.convert import save_hf
@@ -113,6 +137,6 @@ def save_hf_checkpoint(trainer, out_dir: str, family: str = "llama3", hf_config:
     hf = nm.mcore_to_hf(full, nm.FAMILIES[family], num_layers=cfg.num_layers, num_heads=cfg.num_attention_heads,
                         num_groups=cfg.num_query_groups, vocab_size=cfg.vocab_size, num_experts=cfg.num_moe_experts,
                         tie_embeddings=not cfg.untie_embeddings_and_output_weights)
-    save_hf(hf, out_dir, hf_config)
+    save_hf(hf, out_dir, hf_config or hf_config_from_model(cfg, family))
     if world > 1:
         dist.barrier()

@@ -211,7 +211,8 @@ def _add_ckpt_logging_args(p):
     g.add_argument("--no-save-rng", action="store_true")
     g.add_argument("--finetune", action="store_true")
     g.add_argument("--async-save", action="store_true")
-    g.add_argument("--save-hf", action="store_true")
+    g.add_argument("--save-hf", nargs="?", const="true", default="false", choices=["true", "false"],
+                   help="write Hugging Face weights of the final model (to --save-hf-path or <save>/release_hf_weights)")
     g.add_argument("--save-hf-path", type=str, default=None)
     g.add_argument("--load-hf", action="store_true")
     g.add_argument("--hf-checkpoint-path", type=str, default=None)

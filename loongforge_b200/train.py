@@ -2,6 +2,7 @@
 (same role and flag spelling as the reference's loongforge/train.py:17-27)."""
 from __future__ import annotations
 
+import os
 import sys
 from typing import List, Optional
 
@@ -57,9 +58,7 @@ def main(argv: Optional[List[str]] = None) -> int:
             extra["image_size"] = int(args.image_resolution)
     trainer = build_model_trainer(family, train_cfg.training_phase, model_cfg=model_cfg, train_cfg=train_cfg,
                                   dims=dims, device=device, **extra)
-    if train_cfg.load:
-        trainer.load_checkpoint(train_cfg.load, load_optim=not args.no_load_optim and not args.finetune,
-                                load_rng=not args.no_load_rng and not args.finetune)
+    _load_initial_state(trainer, args, train_cfg, family)
     data_iter = trainer.build_data_iterator(args) if hasattr(trainer, "build_data_iterator") else None
     if data_iter is None:
         st = trainer.st
@@ -71,10 +70,72 @@ def main(argv: Optional[List[str]] = None) -> int:
     trainer.train(data_iter)
     if train_cfg.save:
         trainer.save_checkpoint(train_cfg.save)
+    if _truthy(getattr(args, "save_hf", False)) and trainer.iteration >= train_cfg.train_iters:
+        # Hugging Face weights of the final model (reference: loongforge/train/training_utils.py:622-632)
+        from .ckpt.hf_bridge import save_hf_checkpoint
+        out = args.save_hf_path or (os.path.join(train_cfg.save, "release_hf_weights") if train_cfg.save else None)
+        if out is None:
+            raise ValueError("--save-hf needs --save-hf-path or --save")
+        save_hf_checkpoint(trainer, out, family=_hf_family(family, model_cfg))
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
     return 0
+
+
+def _truthy(v) -> bool:
+    return v is True or str(v).lower() in ("1", "true", "yes")
+
+
+def _hf_family(family: str, cfg) -> str:
+    """Key of the Hugging Face name map (tools/convert_checkpoint/name_maps.py) for a model family."""
+    from tools.convert_checkpoint.name_maps import FAMILIES
+    if family == "qwen3" and cfg.num_moe_experts:
+        return "qwen3_moe"
+    if family in FAMILIES:
+        return family
+    return {"llama": "llama3", "qwen": "qwen2"}.get(family, "llama3")
+
+
+def is_hf_checkpoint(path: Optional[str]) -> bool:
+    return bool(path) and os.path.isfile(os.path.join(path, "config.json")) and any(
+        f.endswith((".safetensors", ".bin")) for f in os.listdir(path))
+
+
+def _load_initial_state(trainer, args, train_cfg, family: str) -> str:
+    """Where training starts from, in the reference's order of precedence (loongforge/train/training_utils.py:1184-1204,
+    loongforge/train/checkpointing.py:1721-1730): a checkpoint of THIS run under ``--load`` (resume: weights, optimizer,
+    RNG, iteration; ``--ckpt-step`` picks the iteration); else Hugging Face weights (``--load`` pointing at an HF
+    directory, or ``--load-hf --hf-checkpoint-path``); else ``--pretrained-checkpoint`` (weights only, iteration 0).
+    ``--finetune`` keeps the weights of whatever was loaded and starts the schedule from iteration 0."""
+    from .ckpt.checkpointing import read_tracker
+
+    hf_dir = args.hf_checkpoint_path if getattr(args, "load_hf", False) else None
+    if hf_dir is None and is_hf_checkpoint(train_cfg.load):
+        hf_dir = train_cfg.load
+    resume_dir = train_cfg.load if (train_cfg.load and hf_dir != train_cfg.load) else None
+    has_own = bool(resume_dir) and os.path.isdir(resume_dir) and (
+        read_tracker(resume_dir)[0] is not None or getattr(args, "ckpt_step", None) is not None)
+    how = "scratch"
+    if has_own:
+        finetune = bool(args.finetune)
+        trainer.load_checkpoint(resume_dir, load_optim=not args.no_load_optim and not finetune,
+                                load_rng=not args.no_load_rng and not finetune,
+                                **({"iteration": args.ckpt_step} if getattr(args, "ckpt_step", None) is not None else {}))
+        how = "resume"
+        if finetune:
+            trainer.iteration, trainer.consumed_samples, trainer.num_flops_so_far = 0, 0, 0.0
+            how = "finetune"
+    elif hf_dir:
+        from .ckpt.hf_bridge import load_hf_checkpoint_online
+        load_hf_checkpoint_online(trainer, hf_dir, family=_hf_family(family, trainer.mcfg))
+        trainer.optimizer.reload_model_params()
+        how = "hf"
+    elif getattr(args, "pretrained_checkpoint", None):
+        trainer.load_checkpoint(args.pretrained_checkpoint, load_optim=False, load_rng=False)
+        trainer.iteration, trainer.consumed_samples, trainer.num_flops_so_far = 0, 0, 0.0
+        how = "pretrained"
+    return how
 
 
 if __name__ == "__main__":

@@ -366,3 +366,37 @@ def test_rank_that_leaves_is_detected_through_the_store():
 
     r0, r1 = run_distributed(_leaver, 2)
     assert r1 == "left" and r0[0] == "detected" and r0[1] == [1] and r0[2] > 2
+
+
+def test_cli_start_state_precedence_and_hf_export(tmp_path):
+    """Run A trains and writes Hugging Face weights; run B starts from those HF weights; run C fine-tunes from A's
+    checkpoint given as --pretrained-checkpoint (iteration restarts at 0); run D resumes A at a chosen step."""
+    import re
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=root)
+    base = [sys.executable, "-m", "loongforge_b200.train", "--model-name", "tiny-llama", "--seq-length", "64",
+            "--micro-batch-size", "2", "--global-batch-size", "2", "--lr", "1e-3", "--log-interval", "1"]
+
+    def run(extra):
+        p = subprocess.run(base + extra, cwd=root, capture_output=True, text=True, timeout=600, env=env)
+        assert p.returncode == 0, p.stderr[-2000:]
+        return [(int(m.group(1)), float(m.group(2))) for m in
+                re.finditer(r"iteration\s+(\d+)/.*?lm loss: ([0-9.E+-]+)", p.stdout)]
+
+    a = run(["--train-iters", "4", "--save", str(tmp_path / "a"), "--save-interval", "2", "--save-hf"])
+    hf = tmp_path / "a" / "release_hf_weights"
+    assert (hf / "config.json").is_file() and any(f.suffix == ".safetensors" for f in hf.iterdir())
+    assert [i for i, _ in a] == [1, 2, 3, 4]
+    fresh = run(["--train-iters", "1"])
+    # B: --load pointing at a Hugging Face directory -> online conversion, iteration 0, trained weights (lower loss)
+    b = run(["--train-iters", "1", "--load", str(hf)])
+    assert b[0][0] == 1 and b[0][1] < fresh[0][1] - 1e-3
+    # C: --pretrained-checkpoint -> weights only, the schedule starts over
+    c = run(["--train-iters", "1", "--pretrained-checkpoint", str(tmp_path / "a")])
+    assert c[0][0] == 1 and abs(c[0][1] - b[0][1]) < 1e-3 * b[0][1]
+    # D: resume at --ckpt-step 2 -> continues with iteration 3 and reproduces run A's iteration 3
+    d = run(["--train-iters", "3", "--load", str(tmp_path / "a"), "--ckpt-step", "2"])
+    assert d[0][0] == 3 and abs(d[0][1] - a[2][1]) < 1e-5 * a[2][1]
