@@ -37,8 +37,8 @@ def _add_model_args(p: argparse.ArgumentParser):
     g.add_argument("--qk-layernorm", action="store_true")
     g.add_argument("--untie-embeddings-and-output-weights", action="store_true")
     g.add_argument("--init-method-std", type=float, default=None)
-    g.add_argument("--attention-dropout", type=float, default=0.0)
-    g.add_argument("--hidden-dropout", type=float, default=0.0)
+    g.add_argument("--attention-dropout", type=float, default=None)
+    g.add_argument("--hidden-dropout", type=float, default=None)
     g.add_argument("--vocab-size", type=int, default=None)
     g.add_argument("--make-vocab-size-divisible-by", type=int, default=128)
     g.add_argument("--attention-backend", type=str, default="auto", choices=["auto", "native", "flash", "fused", "sdpa"])

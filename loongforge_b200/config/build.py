@@ -123,6 +123,7 @@ _ARG_TO_CFG = {
     "mtp_loss_scaling_factor": "mtp_loss_scaling_factor", "moe_token_dispatcher_type": "moe_token_dispatcher_type",
     "recompute_granularity": "recompute_granularity",
     "recompute_method": "recompute_method", "recompute_num_layers": "recompute_num_layers",
+    "attention_dropout": "attention_dropout", "hidden_dropout": "hidden_dropout",
 }
 _FLAG_TO_CFG = {"swiglu": ("activation", "swiglu"), "add_qkv_bias": ("add_qkv_bias", True),
                 "qk_layernorm": ("qk_layernorm", True), "disable_bias_linear": ("add_bias_linear", False),
@@ -130,7 +131,8 @@ _FLAG_TO_CFG = {"swiglu": ("activation", "swiglu"), "add_qkv_bias": ("add_qkv_bi
                 "moe_router_pre_softmax": ("moe_router_pre_softmax", True),
                 "moe_router_enable_expert_bias": ("moe_router_enable_expert_bias", True),
                 "multi_latent_attention": ("multi_latent_attention", True), "use_dsa_fused": ("use_dsa", True),
-                "sequence_parallel": ("sequence_parallel", True), "tp_comm_overlap": ("tp_comm_overlap", True)}
+                "sequence_parallel": ("sequence_parallel", True), "tp_comm_overlap": ("tp_comm_overlap", True),
+                "no_gradient_accumulation_fusion": ("gradient_accumulation_fusion", False)}
 
 
 def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[TransformerConfig, TrainConfig, ParallelDims, dict]:
@@ -160,9 +162,16 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
     if cfg.fp8 is None and args.fp8_format:
         cfg.fp8 = "blockwise" if (args.fp8_recipe or "blockwise") == "blockwise" else args.fp8_recipe
     cfg.__post_init__()
+    vpp = args.num_virtual_stages_per_pipeline_rank
+    per_virtual = getattr(args, "num_layers_per_virtual_pipeline_stage", None)
+    if not vpp and per_virtual:
+        pp_ = args.pipeline_model_parallel_size
+        if cfg.num_layers % (pp_ * per_virtual):
+            raise ValueError("num_layers must divide by pipeline size x layers per virtual stage")
+        vpp = cfg.num_layers // (pp_ * per_virtual)
     dims = ParallelDims(tp=args.tensor_model_parallel_size, pp=args.pipeline_model_parallel_size,
                         cp=args.context_parallel_size, ep=args.expert_model_parallel_size,
-                        etp=args.expert_tensor_parallel_size, vpp=args.num_virtual_stages_per_pipeline_rank)
+                        etp=args.expert_tensor_parallel_size, vpp=vpp)
     dt = {"fp32": torch.float32, "bf16": torch.bfloat16}
     from ..parallel.pipeline_layout import resolve_stage_layers
     _ints = lambda v: [int(x) for x in v.split(",") if x.strip()] if v else None  # noqa: E731
@@ -174,11 +183,20 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
     recompute_layers = _ints(getattr(args, "custom_pipeline_recompute_layers", None))
     if recompute_layers is not None and len(recompute_layers) != dims.pp:
         raise ValueError("--custom-pipeline-recompute-layers needs one count per pipeline stage")
+    gbs = args.global_batch_size or args.micro_batch_size
+    train_iters = args.train_iters or 0
+    if not train_iters and getattr(args, "train_samples", None):
+        train_iters = int(args.train_samples) // gbs  # sample-based length (constant batch size)
+    decay_iters = args.lr_decay_iters
+    warmup_iters = args.lr_warmup_iters
+    if getattr(args, "lr_warmup_fraction", None) is not None:
+        warmup_iters = int(float(args.lr_warmup_fraction) * (decay_iters or train_iters))
     tc = TrainConfig(
-        micro_batch_size=args.micro_batch_size, global_batch_size=args.global_batch_size or args.micro_batch_size,
-        seq_length=args.seq_length or cfg.max_position_embeddings, train_iters=args.train_iters or 0, lr=args.lr,
-        min_lr=args.min_lr, lr_decay_style=args.lr_decay_style, lr_warmup_iters=args.lr_warmup_iters,
-        lr_decay_iters=args.lr_decay_iters, weight_decay=args.weight_decay, adam_beta1=args.adam_beta1,
+        micro_batch_size=args.micro_batch_size, global_batch_size=gbs,
+        seq_length=args.seq_length or cfg.max_position_embeddings, train_iters=train_iters, lr=args.lr,
+        min_lr=args.min_lr, lr_decay_style=args.lr_decay_style, lr_warmup_iters=warmup_iters,
+        lr_decay_iters=decay_iters, rampup_batch_size=getattr(args, "rampup_batch_size", None),
+        grad_reduce_in_fp32=(True if getattr(args, "accumulate_allreduce_grads_in_fp32", False) or args.bf16 else False), weight_decay=args.weight_decay, adam_beta1=args.adam_beta1,
         adam_beta2=args.adam_beta2, adam_eps=args.adam_eps, clip_grad=args.clip_grad, bf16=args.bf16, seed=args.seed,
         log_interval=args.log_interval, save=args.save, load=args.load, save_interval=args.save_interval,
         ckpt_format="torch_dist" if args.ckpt_format in ("torch_dist", "torch_dcp") else args.ckpt_format,
@@ -191,6 +209,7 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
         error_injection_type=getattr(args, "error_injection_type", "transient_error"),
         iterations_to_skip=list(getattr(args, "iterations_to_skip", []) or []),
         check_weight_hash_interval=int(getattr(args, "check_weight_hash_across_dp_replicas_interval", 0) or 0),
+        eval_interval=int(getattr(args, "eval_interval", 0) or 0), eval_iters=int(getattr(args, "eval_iters", 0) or 0),
         dp_balance=bool(getattr(args, "use_vlm_dp_balance", False)),
         optimizer_cpu_offload=bool(getattr(args, "optimizer_cpu_offload", False)),
         use_fsdp=bool(getattr(args, "use_torch_fsdp2", False) or getattr(args, "use_megatron_fsdp", False)),

@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import os
 import struct
-from typing import Dict, Iterator, List, Optional, Sequence
+from typing import Dict, Iterator, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -79,12 +79,17 @@ class GPTDataset:
     with an end-of-document token already inside them)."""
 
     def __init__(self, indexed: IndexedDataset, seq_length: int, num_samples: int, seed: int = 1234,
-                 eod_token: Optional[int] = None, eod_mask_loss: bool = False):
+                 eod_token: Optional[int] = None, eod_mask_loss: bool = False,
+                 doc_range: Optional[Tuple[int, int]] = None):
+        """``doc_range``: half-open range of document indices this split may draw from (train / valid / test)."""
         self.ds, self.seq_length, self.eod, self.eod_mask_loss = indexed, seq_length, eod_token, eod_mask_loss
         rng = np.random.RandomState(seed)
-        tokens_per_epoch = indexed.num_tokens
+        lo, hi = doc_range if doc_range is not None else (0, len(indexed))
+        if hi <= lo:
+            raise ValueError(f"empty document range {doc_range} for a dataset of {len(indexed)} documents")
+        tokens_per_epoch = int(sum(len(indexed[d]) for d in range(lo, hi)))
         epochs = max(1, -(-(num_samples * seq_length + 1) // max(tokens_per_epoch, 1)))
-        docs = np.concatenate([rng.permutation(len(indexed)) for _ in range(epochs)])
+        docs = np.concatenate([lo + rng.permutation(hi - lo) for _ in range(epochs)])
         self.stream = np.concatenate([np.asarray(indexed[d]) for d in docs]).astype(np.int64)
         self.num_samples = min(num_samples, (len(self.stream) - 1) // seq_length)
         self.shuffle = rng.permutation(self.num_samples)
@@ -115,3 +120,81 @@ def gpt_batch_iterator(ds: GPTDataset, micro_batch_size: int, *, dp_rank=0, dp_s
         batch["num_valid_tokens"] = int(batch["loss_mask"].sum().item())
         yield batch
         step += 1
+
+
+def split_document_ranges(num_docs: int, split: str) -> List[Tuple[int, int]]:
+    """``"949,50,1"`` -> [(0, a), (a, b), (b, num_docs)]: train / validation / test document ranges in the ratio
+    given (Megatron's ``--split``)."""
+    w = [float(x) for x in split.replace("/", ",").split(",") if x.strip() != ""]
+    w = (w + [0.0, 0.0, 0.0])[:3]
+    tot = sum(w)
+    if tot <= 0:
+        raise ValueError(f"bad split {split!r}")
+    bounds, acc = [0], 0.0
+    for x in w:
+        acc += x / tot
+        bounds.append(int(round(acc * num_docs)))
+    bounds[-1] = num_docs
+    return [(bounds[i], max(bounds[i], bounds[i + 1])) for i in range(3)]
+
+
+class BlendedDataset:
+    """Weighted mixture of datasets: sample i comes from the dataset whose share of the first i samples lags its
+    weight the most (the deterministic scheme of Megatron's blending indices), so every prefix of the stream has
+    the requested proportions."""
+
+    def __init__(self, datasets: Sequence, weights: Sequence[float], num_samples: int):
+        assert len(datasets) == len(weights) and datasets
+        w = np.asarray(weights, dtype=np.float64)
+        w = w / w.sum()
+        self.datasets = list(datasets)
+        counts = np.zeros(len(w), dtype=np.int64)
+        self.which = np.empty(num_samples, dtype=np.int32)
+        self.index = np.empty(num_samples, dtype=np.int64)
+        for i in range(num_samples):
+            d = int(np.argmax(w * (i + 1) - counts))
+            self.which[i], self.index[i] = d, counts[d]
+            counts[d] += 1
+
+    def __len__(self):
+        return len(self.which)
+
+    def __getitem__(self, i):
+        i = i % len(self.which)
+        return self.datasets[int(self.which[i])][int(self.index[i])]
+
+
+def parse_data_path(data_path: Sequence[str]) -> Tuple[List[float], List[str]]:
+    """``["a"]`` -> ([1.0], ["a"]); ``["0.3", "a", "0.7", "b"]`` -> ([0.3, 0.7], ["a", "b"])."""
+    items = list(data_path)
+    if len(items) == 1:
+        return [1.0], items
+    if len(items) % 2:
+        raise ValueError("--data-path takes one prefix, or weight / prefix pairs")
+    return [float(x) for x in items[0::2]], list(items[1::2])
+
+
+def build_gpt_datasets(data_path: Sequence[str], split: str, seq_length: int, samples: Sequence[int], seed: int = 1234,
+                       eod_token: Optional[int] = None, eod_mask_loss: bool = False):
+    """(train, valid, test) datasets over one or several ``.bin/.idx`` prefixes; a split with no documents or no
+    requested samples is None (reference: Megatron ``BlendedMegatronDatasetBuilder`` as used by
+    loongforge/train/pretrain/pretrain_llm.py:198-229)."""
+    weights, prefixes = parse_data_path(data_path)
+    indexed = [IndexedDataset(p) for p in prefixes]
+    out = []
+    for si in range(3):
+        n = int(samples[si])
+        parts, ws = [], []
+        for w, ds in zip(weights, indexed):
+            lo, hi = split_document_ranges(len(ds), split)[si]
+            if hi > lo and n > 0:
+                share = max(1, int(np.ceil(n * w / sum(weights) * 1.005)) + 1)
+                parts.append(GPTDataset(ds, seq_length, share, seed + si, eod_token, eod_mask_loss, (lo, hi)))
+                ws.append(w)
+        if not parts:
+            out.append(None)
+        elif len(parts) == 1:
+            out.append(parts[0])
+        else:
+            out.append(BlendedDataset(parts, ws, n))
+    return tuple(out)

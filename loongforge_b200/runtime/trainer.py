@@ -39,6 +39,7 @@ class TrainConfig:
     min_lr: float = 0.0
     lr_decay_style: str = "constant"
     lr_warmup_iters: int = 0
+    rampup_batch_size: Optional[List[int]] = None  # (start, increment, ramp samples): global batch size grows to its final value
     lr_decay_iters: Optional[int] = None
     weight_decay: float = 0.0
     adam_beta1: float = 0.9
@@ -61,6 +62,8 @@ class TrainConfig:
     master_as_remainder: bool = False
     optimizer_cpu_offload: bool = False  # masters + Adam moments on the host, native host AdamW
     fp8_policy_file: Optional[str] = None  # JSON rules: which linear kinds run FP8 (runtime/fp8_policy.py)
+    eval_interval: int = 0  # > 0: run `eval_iters` forward-only steps on the validation stream every N iterations
+    eval_iters: int = 0
     rerun_mode: str = "disabled"  # disabled | validate_results | report_stats (runtime/resilience.py)
     error_injection_rate: int = 0  # host-side loss corruption every N steps on average (testing the rerun machine)
     error_injection_type: str = "transient_error"
@@ -131,7 +134,8 @@ class Trainer:
         torch.manual_seed(train_cfg.seed + 100 * self.st.pp_rank + 2718 * self.st.tp_rank)
         from ..parallel.layers import set_init_seed
         set_init_seed(train_cfg.seed)
-        self.mb_calc = MicrobatchCalculator(train_cfg.global_batch_size, train_cfg.micro_batch_size, self.dp)
+        self.mb_calc = MicrobatchCalculator(train_cfg.global_batch_size, train_cfg.micro_batch_size, self.dp,
+                                            rampup=train_cfg.rampup_batch_size)
         self.model_provider = model_provider or self._default_model_provider
         self.forward_step = forward_step or self._default_forward_step
         self.models = self._build_models()
@@ -267,6 +271,7 @@ class Trainer:
         t = self.tcfg
         for m in self.models:
             m.train()
+        self.mb_calc.update(self.consumed_samples)  # batch-size ramp-up: micro-batches per step may grow
         self.optimizer.zero_grad()
         if t.dp_balance and self.st.dp_size > 1 and not getattr(self, "_already_balanced", False):
             data_iterator = self._balanced(data_iterator)
@@ -306,7 +311,7 @@ class Trainer:
         else:
             skipped = 1
         self.iteration += 1
-        self.consumed_samples += t.global_batch_size
+        self.consumed_samples += self.mb_calc.current_gbs
         metrics: Dict[str, float] = {"grad_norm": grad_norm, "skipped": skipped}
         # loss: average over micro-batches, then over the data-parallel group (last stage only)
         if reports:
@@ -318,6 +323,73 @@ class Trainer:
             for k, v in zip(keys, vals.tolist()):
                 metrics[k] = v
         return metrics
+
+    # ------------------------------------------------------------------ data and evaluation
+    def build_data_iterator(self, args):
+        """Training stream from ``--data-path`` (one ``.bin/.idx`` prefix or weight / prefix pairs, split by
+        ``--split``); also prepares ``self.valid_iterator`` when evaluation is requested. None = no data path
+        (the caller falls back to synthetic data)."""
+        if not getattr(args, "data_path", None):
+            return None
+        from ..data.indexed_dataset import build_gpt_datasets, gpt_batch_iterator
+
+        t, st = self.tcfg, self.st
+        n_train = t.train_iters * t.global_batch_size
+        n_eval = (t.train_iters // t.eval_interval + 1) * t.eval_iters * t.global_batch_size if t.eval_interval else 0
+        eod = getattr(args, "eod_token_id", None)
+        train, valid, _ = build_gpt_datasets(args.data_path, getattr(args, "split", "949,50,1") or "949,50,1",
+                                              t.seq_length, (n_train, n_eval, 0), t.seed, eod,
+                                              bool(getattr(args, "eod_mask_loss", False)))
+        if train is None:
+            raise ValueError("the training split of --data-path holds no documents")
+        pin = self.device.type == "cuda"
+        kw = dict(dp_rank=st.dp_rank, dp_size=st.dp_size, pin_memory=pin)
+        self.valid_iterator = gpt_batch_iterator(valid, t.micro_batch_size, **kw) if valid is not None else None
+        return gpt_batch_iterator(train, t.micro_batch_size, start_sample=self.consumed_samples, **kw)
+
+    @torch.no_grad()
+    def evaluate(self, data_iterator, iters: Optional[int] = None) -> Dict[str, float]:
+        """Forward-only passes over `iters` global batches; returns the mean of every reported loss (and its
+        perplexity), averaged over the data-parallel group and made known to every rank."""
+        t = self.tcfg
+        iters = iters or t.eval_iters or 1
+        for m in self.models:
+            m.eval()
+        fb = schedules.get_forward_backward_func()
+        T = t.seq_length * t.micro_batch_size
+        sp_div = self.st.dims.tp if self.mcfg.sequence_parallel else 1
+        sums: Dict[str, float] = {}
+        n = 0
+        for _ in range(iters):
+            reports = fb(forward_step_func=self.forward_step, data_iterator=data_iterator,
+                         model=self.models if len(self.models) > 1 else self.models[0],
+                         num_microbatches=self.mb_calc.num_microbatches, forward_only=True,
+                         tensor_shape=(T // sp_div // self.st.dims.cp, self.mcfg.hidden_size *
+                                       (self.mcfg.num_residual_streams if self.mcfg.enable_hyper_connections else 1)),
+                         dtype=self.mcfg.params_dtype)
+            for r in reports:
+                for k, v in r.items():
+                    if k != "num_tokens":
+                        sums[k] = sums.get(k, 0.0) + float(v)
+                n += 1
+        for m in self.models:
+            m.train()
+        keys = sorted(sums) or ["lm loss"]
+        v = torch.tensor([sums.get(k, 0.0) for k in keys] + [float(n)], dtype=torch.float64, device=self.device)
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(v)  # only the last pipeline stage contributes
+        cnt = max(v[-1].item(), 1.0)
+        out = {k: v[i].item() / cnt for i, k in enumerate(keys)}
+        if "lm loss" in out:
+            out["lm loss PPL"] = math.exp(min(20.0, out["lm loss"]))
+        return out
+
+    def format_eval_log(self, metrics: Dict[str, float], label: str = "validation") -> str:
+        line = f" {label} loss at iteration {self.iteration} |"
+        for k, v in metrics.items():
+            line += (f" {k}: {v:.6E} |" if k.endswith("PPL") else f" {k} value: {v:.6E} |")
+        bar = "-" * (len(line) + 1)
+        return f"{bar}\n{line}\n{bar}"
 
     # ------------------------------------------------------------------ result validation (rerun state machine)
     def _global_loss(self, reports) -> float:
@@ -455,13 +527,13 @@ class Trainer:
 
     # ------------------------------------------------------------------ logging
     def flops_per_step(self) -> float:
-        return self.mcfg.flops_per_token(self.tcfg.seq_length) * self.tcfg.seq_length * self.tcfg.global_batch_size
+        return self.mcfg.flops_per_token(self.tcfg.seq_length) * self.tcfg.seq_length * self.mb_calc.current_gbs
 
     def format_log(self, metrics: Dict[str, float], elapsed_ms: float, peak_tflops: Optional[float] = None) -> str:
         """The reference's log line (loongforge/train/training_utils.py:2278-2394), parsed by
         tests/llm_vlm/tools/log2json.py:19-29."""
         t = self.tcfg
-        tokens = t.seq_length * t.global_batch_size
+        tokens = t.seq_length * self.mb_calc.current_gbs
         tps = tokens / (elapsed_ms / 1e3) / self.world
         s = " [%s] iteration %8d/%8d |" % (time.strftime("%Y-%m-%d %H:%M:%S"), self.iteration, t.train_iters)
         s += " consumed samples: %12d |" % self.consumed_samples
@@ -471,7 +543,7 @@ class Trainer:
             tf = self.flops_per_step() / (elapsed_ms / 1e3) / 1e12 / self.world
             s += " flop throughput (TFLOP/sec/GPU): %.1f |" % tf
         s += " learning rate: %.6E |" % self.optimizer.param_groups[0]["lr"]
-        s += " global batch size: %5d |" % t.global_batch_size
+        s += " global batch size: %5d |" % self.mb_calc.current_gbs
         for k, v in metrics.items():
             if k in ("grad_norm", "skipped"):
                 continue
@@ -494,10 +566,11 @@ class Trainer:
         while self.iteration < t.train_iters:
             if (self.iteration + 1) in skip:
                 # the iteration's data is consumed so that later iterations see what they would have seen
+                self.mb_calc.update(self.consumed_samples)
                 for _ in range(self.mb_calc.num_microbatches):
                     next(data_iterator)
                 self.iteration += 1
-                self.consumed_samples += t.global_batch_size
+                self.consumed_samples += self.mb_calc.current_gbs
                 continue
             t0 = self._now()
             metrics = self.train_step(data_iterator)
@@ -515,6 +588,12 @@ class Trainer:
                 line = self.format_log(metrics, elapsed_ms)
                 if is_log_rank:
                     (on_log or print)(line)
+            if (t.eval_interval and t.eval_iters and self.iteration % t.eval_interval == 0
+                    and getattr(self, "valid_iterator", None) is not None):
+                ev = self.evaluate(self.valid_iterator)
+                self.last_eval = ev
+                if is_log_rank:
+                    (on_log or print)(self.format_eval_log(ev))
             if t.save and t.save_interval and self.iteration % t.save_interval == 0:
                 self.save_checkpoint(t.save)
             stop = self.exit_requested

@@ -67,7 +67,7 @@ class VLMTrainer(Trainer):
                  image_token_id: Optional[int] = None, encoder_recompute: bool = True,
                  vision_family: str = "qwen2_vit", vision_options: Optional[dict] = None, freeze_encoder: bool = False,
                  images_per_sample: int = 4, image_size: int = 448, full_hetero_dp: bool = False,
-                 full_hetero_cpu_offload: bool = False, **kw):
+                 full_hetero_cpu_offload: bool = False, lora: Optional[dict] = None, **kw):
         """``vision_family``: ``qwen2_vit`` (Qwen2/2.5-VL encoder) or a key of ``models.vision_zoo.VISION_FAMILIES``
         (Qwen3-VL, InternViT, RICE, Moon, ERNIE, MiniCPM-V encoders with their projectors)."""
         self.vit_cfg = vit_cfg or get_model_config("qwen2.5-vit")
@@ -76,6 +76,7 @@ class VLMTrainer(Trainer):
         if encoder_recompute:
             self.vit_cfg.recompute_granularity = "full"
         self.encoder_hetero_dp = encoder_hetero_dp
+        self._lora = lora  # adapters on the language model's linears; its base weights are frozen
         self.full_hetero_dp, self.full_hetero_cpu_offload = full_hetero_dp, full_hetero_cpu_offload
         if full_hetero_dp and ((dims and dims.cp > 1) or encoder_tp != 1 or encoder_hetero_dp):
             raise ValueError("full heterogeneous DP needs cp = 1 and encoder TP 1, and replaces encoder hetero-DP")
@@ -100,6 +101,13 @@ class VLMTrainer(Trainer):
             dist.all_reduce(p.main_grad, group=g)
 
     def _default_model_provider(self, pre_process, post_process, layer_numbers):
+        model = self._build_omni(pre_process, post_process, layer_numbers)
+        if self._lora:
+            from ..models.peft import apply_lora
+            apply_lora(model.foundation_model, **self._lora)
+        return model
+
+    def _build_omni(self, pre_process, post_process, layer_numbers):
         return OmniCombinationModel(self.mcfg, self.vit_cfg if (pre_process or self.full_hetero_dp) else None,
                                     full_hetero_dp=self.full_hetero_dp, image_token_id=self.image_token_id,
                                     pre_process=pre_process, post_process=post_process, layer_numbers=layer_numbers,

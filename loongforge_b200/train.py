@@ -56,6 +56,9 @@ def main(argv: Optional[List[str]] = None) -> int:
         extra["full_hetero_cpu_offload"] = bool(getattr(args, "full_hetero_dp_cpu_offload", False))
         if getattr(args, "image_resolution", None):
             extra["image_size"] = int(args.image_resolution)
+    if getattr(args, "peft_type", None) and train_cfg.training_phase == "sft" and "lora" not in extra:
+        extra["lora"] = dict(rank=args.lora_rank, alpha=args.lora_alpha, dropout=args.lora_dropout,
+                             targets=tuple(args.lora_target_modules), canonical=args.peft_type == "canonical_lora")
     trainer = build_model_trainer(family, train_cfg.training_phase, model_cfg=model_cfg, train_cfg=train_cfg,
                                   dims=dims, device=device, **extra)
     _load_initial_state(trainer, args, train_cfg, family)

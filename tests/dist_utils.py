@@ -7,12 +7,27 @@ import traceback
 import torch.multiprocessing as mp
 
 
+_NEXT_PORT = {"n": 0}
+
+
 def _free_port() -> int:
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    p = s.getsockname()[1]
-    s.close()
-    return p
+    """A port nobody listens on. Test workers running side by side (pytest-xdist) draw from disjoint ranges and never
+    hand out the same port twice, so two rendezvous cannot race for one port between probing and binding."""
+    w = os.environ.get("PYTEST_XDIST_WORKER", "gw0")
+    idx = int(w[2:]) if w[2:].isdigit() else 0
+    base = 20000 + (idx % 16) * 2500 + (os.getpid() % 5) * 500
+    for _ in range(500):
+        port = base + _NEXT_PORT["n"] % 500
+        _NEXT_PORT["n"] += 1
+        s = socket.socket()
+        try:
+            s.bind(("127.0.0.1", port))
+            return port
+        except OSError:
+            continue
+        finally:
+            s.close()
+    raise RuntimeError("no free port found")
 
 
 def _worker(rank, world, port, fn, args, q):

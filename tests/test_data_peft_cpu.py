@@ -135,3 +135,37 @@ def test_internvl_tiling_and_ernie_positions():
     assert tt.tolist() == [0, 0, 1, 1, 1, 1, 1, 1, 0]
     assert pos[0].tolist() == [0, 1, 2, 2, 2, 2, 2, 2, 5]
     assert pos[1].tolist() == [0, 1, 2, 2, 2, 3, 3, 3, 5] and pos[2].tolist() == [0, 1, 2, 3, 4, 2, 3, 4, 5]
+
+
+def test_pretrain_data_path_split_blend_and_evaluation(tmp_path):
+    """--data-path (weighted blend of two .bin/.idx prefixes) + --split + --eval-interval through the CLI."""
+    import re
+    import subprocess
+    import sys
+
+    from loongforge_b200.data import indexed_dataset as I
+
+    rng = np.random.RandomState(0)
+    for name, lo in (("a", 0), ("b", 500)):
+        w = I.IndexedDatasetWriter(str(tmp_path / name))
+        for _ in range(40):
+            w.add_document(list(rng.randint(lo, lo + 400, size=rng.randint(50, 200))) + [999])
+        w.finalize()
+    assert I.split_document_ranges(40, "949,50,1") == [(0, 38), (38, 40), (40, 40)]
+    assert I.parse_data_path(["0.25", "x", "0.75", "y"]) == ([0.25, 0.75], ["x", "y"])
+    tr, va, te = I.build_gpt_datasets(["0.25", str(tmp_path / "a"), "0.75", str(tmp_path / "b")], "90,10,0", 32,
+                                      (64, 8, 0))
+    assert te is None and len(tr) == 64 and len(va) == 8
+    from_b = sum(int(tr[i]["tokens"].max() >= 500) for i in range(64))
+    assert 44 <= from_b <= 52, "three quarters of the stream come from the second prefix"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "loongforge_b200.train", "--model-name", "tiny-llama", "--vocab-size", "1024",
+           "--seq-length", "32", "--micro-batch-size", "2", "--global-batch-size", "4", "--train-iters", "4",
+           "--lr", "1e-3", "--log-interval", "1", "--data-path", "0.25", str(tmp_path / "a"), "0.75", str(tmp_path / "b"),
+           "--split", "90,10,0", "--eval-interval", "2", "--eval-iters", "1"]
+    p = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=600,
+                       env=dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=root))
+    assert p.returncode == 0, p.stderr[-2000:]
+    evals = re.findall(r"validation loss at iteration (\d+) \| lm loss value: ([0-9.E+-]+) \| lm loss PPL: ([0-9.E+-]+)",
+                       p.stdout)
+    assert [int(e[0]) for e in evals] == [2, 4] and all(float(e[1]) < 8.0 for e in evals)

@@ -400,3 +400,28 @@ def test_cli_start_state_precedence_and_hf_export(tmp_path):
     # D: resume at --ckpt-step 2 -> continues with iteration 3 and reproduces run A's iteration 3
     d = run(["--train-iters", "3", "--load", str(tmp_path / "a"), "--ckpt-step", "2"])
     assert d[0][0] == 3 and abs(d[0][1] - a[2][1]) < 1e-5 * a[2][1]
+
+
+def test_batch_size_rampup_and_sample_based_flags(monkeypatch):
+    from loongforge_b200.config.arguments import parse_args
+    from loongforge_b200.config.build import build_configs
+    from loongforge_b200.data.synthetic import synthetic_batch_iterator
+    from loongforge_b200.runtime.trainer import Trainer
+
+    monkeypatch.setenv("WORLD_SIZE", "1")
+    args, ov = parse_args(["--model-name", "tiny-llama", "--seq-length", "32", "--micro-batch-size", "1",
+                           "--global-batch-size", "4", "--train-samples", "40", "--rampup-batch-size", "2", "2", "8",
+                           "--lr", "1e-3", "--lr-warmup-fraction", "0.2", "--num-layers-per-virtual-pipeline-stage", "1",
+                           "--accumulate-allreduce-grads-in-fp32", "--attention-dropout", "0.0", "--mock-data"])
+    cfg, tc, dims, _ = build_configs(args, ov)
+    assert tc.train_iters == 10 and tc.lr_warmup_iters == 2 and tc.rampup_batch_size == [2, 2, 8]
+    assert tc.grad_reduce_in_fp32 and dims.vpp == 2 and cfg.attention_dropout == 0.0
+    dims.vpp = None
+    tr = Trainer(cfg, tc, dims)
+    it = synthetic_batch_iterator(cfg.vocab_size, 32, 1, pin_memory=False)
+    sizes = []
+    for _ in range(6):
+        tr.train_step(it)
+        sizes.append(tr.mb_calc.current_gbs)
+    assert sizes == [2, 2, 2, 2, 4, 4] and tr.consumed_samples == 16
+    assert "global batch size:     4" in tr.format_log({"lm loss": 1.0, "grad_norm": 1.0}, 10.0)
