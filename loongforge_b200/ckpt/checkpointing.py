@@ -232,7 +232,8 @@ def build_save_state(trainer, stage: bool = False) -> Dict[str, object]:
     key_of = {id(p): key for key, p in model_param_items(trainer)}
     coord = f"tp{tpr}of{tp}.ep{st.ep_rank}of{st.dims.ep}"
     sharded = trainer.optimizer.sharded
-    for name, pieces in trainer.optimizer.sharded_state().items():
+    save_optim = not getattr(trainer.tcfg, "no_save_optim", False)
+    for name, pieces in (trainer.optimizer.sharded_state().items() if save_optim else ()):
         if not sharded and st.rank_in("dp_cp") != 0:
             continue
         for piece in pieces:
@@ -265,9 +266,10 @@ def build_save_state(trainer, stage: bool = False) -> Dict[str, object]:
                     mine = mine + [([a], torch.zeros(b - a, dtype=(mine[0][1].dtype if mine else torch.float32)))]
         state[key] = make_sharded(mine, gshape, rank, allp)
     # ---- per-rank objects
-    buf = io.BytesIO()
-    torch.save(get_rng_state(), buf)
-    state[f"rng_state/shard_{st.pp_rank}.{st.tp_rank}.{st.rank_in('dp_cp')}"] = buf
+    if not getattr(trainer.tcfg, "no_save_rng", False):
+        buf = io.BytesIO()
+        torch.save(get_rng_state(), buf)
+        state[f"rng_state/shard_{st.pp_rank}.{st.tp_rank}.{st.rank_in('dp_cp')}"] = buf
     return state
 
 

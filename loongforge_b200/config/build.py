@@ -210,6 +210,7 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
         iterations_to_skip=list(getattr(args, "iterations_to_skip", []) or []),
         check_weight_hash_interval=int(getattr(args, "check_weight_hash_across_dp_replicas_interval", 0) or 0),
         eval_interval=int(getattr(args, "eval_interval", 0) or 0), eval_iters=int(getattr(args, "eval_iters", 0) or 0),
+        no_save_optim=bool(getattr(args, "no_save_optim", False)), no_save_rng=bool(getattr(args, "no_save_rng", False)),
         dp_balance=bool(getattr(args, "use_vlm_dp_balance", False)),
         optimizer_cpu_offload=bool(getattr(args, "optimizer_cpu_offload", False)),
         use_fsdp=bool(getattr(args, "use_torch_fsdp2", False) or getattr(args, "use_megatron_fsdp", False)),

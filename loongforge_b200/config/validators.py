@@ -60,8 +60,40 @@ _LIBRARY_ONLY = {
 }
 
 
+# Flags of the reference that configure a library this framework does not contain, or select between alternatives of
+# which only one exists here. They are accepted so that the reference's launch scripts run unchanged; when one is given,
+# the note says what happens instead.
+_ACCEPTED = {
+    "use_dsa_sp_first": "sparse attention runs head-parallel under TP with a replicated indexer; there is no separate sequence-first mode",
+    "absorb_backend": "the MLA absorb products use one einsum formulation",
+    "moe_permute_fusion": "token permutation is always fused into the dispatch path",
+    "delay_wgrad_compute": "weight gradients are computed with their data gradients",
+    "use_precision_aware_optimizer": "moment precision is chosen with --exp-avg-dtype / --exp-avg-sq-dtype",
+    "fp8_param_gather": "parameters are gathered in bf16",
+    "cross_entropy_fusion_impl": "one fused linear + cross-entropy implementation exists",
+    "use_flash_attn": "attention always runs on the in-tree flash kernel on GPUs",
+    "cuda_graph_scope": "graph capture is offered by runtime.cuda_graphs for callables, not selected by scope",
+    "tokenizer_model": "tokenizers load from --hf-tokenizer-path",
+    "sft_dataset_config": "dataset options are given as flags",
+    "sft_data_streaming": "SFT datasets are read eagerly",
+    "dataloader_type": "one cyclic, resumable sampler is used",
+    "num_workers": "batches are assembled in the training process",
+    "variable_seq_lengths": "pipeline stages exchange fixed-shape activations; packed rows are padded to --seq-length",
+    "dist_ckpt_strictness": "unexpected or missing checkpoint keys raise",
+    "log_timers_to_tensorboard": "timers are logged to stdout",
+    "timing_log_level": "all timers are recorded",
+    "detail_log_interval": "one log interval exists",
+    "wandb_exp_name": "the run name is the output directory",
+    "moe_use_upcycling": "dense checkpoints are upcycled offline with runtime.upcycling.upcycle_state_dict",
+}
+
+
 def unwired_flag_notes(args) -> list:
     notes = []
+    for flag, what in _ACCEPTED.items():
+        v = getattr(args, flag, None)
+        if v not in (None, False, 0, "", []):
+            notes.append(f"--{flag.replace('_', '-')} was given: {what}")
     for flag, where in _LIBRARY_ONLY.items():
         v = getattr(args, flag, None)
         if v:

@@ -119,8 +119,10 @@ def pad_to_multiple(n: int, tp: int = 1, cp: int = 1, sequence_parallel: bool = 
 class OnlinePacker:
     """Buffers encoded samples and emits packs of at most `seq_len` tokens (first-fit decreasing over the buffer)."""
 
-    def __init__(self, seq_len: int, buffer_size: int = 64, pad_id: int = 0, **pad_kw):
+    def __init__(self, seq_len: int, buffer_size: int = 64, pad_id: int = 0, pad_to_seq_len: bool = False, **pad_kw):
+        """``pad_to_seq_len``: every pack is padded to exactly `seq_len` tokens (fixed shapes for pipeline stages)."""
         self.L, self.buf_size, self.pad_id, self.pad_kw = seq_len, buffer_size, pad_id, pad_kw
+        self.pad_full = pad_to_seq_len
         self.buf: List[Dict[str, torch.Tensor]] = []
 
     def add(self, sample: Dict[str, torch.Tensor]) -> List[Dict[str, torch.Tensor]]:
@@ -156,7 +158,7 @@ class OnlinePacker:
 
     def _pack(self, samples: List[Dict[str, torch.Tensor]]) -> Dict[str, torch.Tensor]:
         lens = [s["tokens"].numel() for s in samples]
-        total = pad_to_multiple(sum(lens), **self.pad_kw)
+        total = self.L if self.pad_full else pad_to_multiple(sum(lens), **self.pad_kw)
         pad = total - sum(lens)
         cat = lambda k, fill, dt: torch.cat([s[k] for s in samples] + [torch.full((pad,), fill, dtype=dt)])  # noqa: E731
         cu = [0]
@@ -167,7 +169,89 @@ class OnlinePacker:
         pix = [s["pixels"] for s in samples if s["pixels"].numel()]
         return {"tokens": cat("tokens", self.pad_id, torch.long), "labels": cat("labels", 0, torch.long),
                 "loss_mask": cat("loss_mask", 0.0, torch.float32),
-                "position_ids": torch.cat([torch.arange(n) for n in lens] + [torch.arange(pad)]),
+                # per-sequence text positions, or the samples' own 3-row (t, h, w) multimodal positions
+                "position_ids": (torch.cat([s["mrope"] for s in samples] + [torch.arange(pad).expand(3, -1)], dim=1)
+                                 if all("mrope" in s for s in samples)
+                                 else torch.cat([torch.arange(n) for n in lens] + [torch.arange(pad)])),
                 "cu_seqlens": torch.tensor(cu, dtype=torch.int32),
                 "pixels": torch.cat(pix) if pix else torch.zeros(0, 0),
                 "grid_thw": torch.cat([s["grid_thw"] for s in samples]) if pix else torch.zeros(0, 3, dtype=torch.long)}
+
+
+# ----------------------------------------------------------------------------- reading shards, building micro-batches
+def decode_image(data: bytes, ext: str) -> np.ndarray:
+    """Image file bytes -> uint8 HWC array (``.npy`` arrays pass through)."""
+    import io
+
+    if ext.endswith("npy"):
+        return np.load(io.BytesIO(data))
+    from PIL import Image
+    return np.asarray(Image.open(io.BytesIO(data)).convert("RGB"))
+
+
+def webdataset_samples(root: str, *, dp_rank: int = 0, dp_size: int = 1, seed: int = 0, start_sample: int = 0,
+                       epochs: Optional[int] = None):
+    """Raw samples (``{"images": [...], "conversation": [...]}``) from the tar shards under `root` (the layout written
+    by tools/data_preprocess/vlm_to_webdataset.py: ``index.json`` + ``shard-*.tar`` with ``{key}.json`` and
+    ``{key}[.n].{ext}`` members). Shards are visited in a per-epoch shuffled order that all ranks share; rank r keeps
+    every dp_size-th sample. ``start_sample`` skips what an earlier run of this rank consumed."""
+    import json
+    import os
+    import tarfile
+
+    with open(os.path.join(root, "index.json")) as f:
+        shards = [os.path.join(root, sh["name"]) for sh in json.load(f)["shards"]]
+    n, epoch = 0, 0
+    while epochs is None or epoch < epochs:
+        order = np.random.RandomState(seed + epoch).permutation(len(shards))
+        for si in order:
+            cur, group = None, {}
+
+            def emit(group):
+                meta = json.loads(group["json"])
+                imgs = sorted((k for k in group if k != "json"), key=lambda k: (len(k), k))
+                conv = meta.get("conversation") or [
+                    {"role": "user" if c.get("from", c.get("role")) in ("human", "user") else "assistant",
+                     "content": c.get("value", c.get("content", ""))} for c in meta.get("conversations", [])]
+                return {"images": [decode_image(group[k], k) for k in imgs], "conversation": conv}
+
+            with tarfile.open(shards[si]) as tar:
+                for m in tar:
+                    key, _, ext = m.name.partition(".")
+                    if key != cur and cur is not None:
+                        if n % dp_size == dp_rank and n // dp_size >= start_sample:
+                            yield emit(group)
+                        n += 1
+                        group = {}
+                    cur = key
+                    group[ext] = tar.extractfile(m).read()
+                if cur is not None:
+                    if n % dp_size == dp_rank and n // dp_size >= start_sample:
+                        yield emit(group)
+                    n += 1
+        epoch += 1
+
+
+def vlm_batch_iterator(samples, encoder: VLMTaskEncoder, seq_len: int, *, merge_size: int = 2, pad_id: int = 0,
+                       packing: bool = True, buffer_size: int = 16, pin_memory: bool = False):
+    """Raw samples -> micro-batches of the vision-language trainer: one packed row of exactly `seq_len` tokens with
+    ``cu_seqlens``, 3-row multimodal position ids, the row's image patches and grids."""
+    from .position_ids import mrope_ids
+
+    packer = OnlinePacker(seq_len, buffer_size=buffer_size if packing else 1, pad_id=pad_id, pad_to_seq_len=True)
+
+    def batches(packs):
+        for p in packs:
+            b = {"tokens": p["tokens"][None], "labels": p["labels"][None], "loss_mask": p["loss_mask"][None],
+                 "position_ids": p["position_ids"].unsqueeze(1), "cu_seqlens": p["cu_seqlens"],
+                 "pixels": p["pixels"].float(), "grid_thw": p["grid_thw"]}
+            if pin_memory:
+                b = {k: v.pin_memory() for k, v in b.items()}
+            b["num_valid_tokens"] = int(p["loss_mask"].sum().item())
+            yield b
+
+    for raw in samples:
+        enc = encoder.encode(raw)
+        enc["mrope"] = mrope_ids(enc["tokens"], enc["grid_thw"], encoder.img_id, merge_size)
+        yield from batches(packer.add(enc))
+    yield from batches(packer.flush())

@@ -118,6 +118,22 @@ class VLMTrainer(Trainer):
     def build_data_iterator(self, args=None):
         st = self.st
         v = self.vit_cfg
+        paths = getattr(args, "data_path", None) if args is not None else None
+        if paths:
+            # image-text shards (tools/data_preprocess/vlm_to_webdataset.py) -> task encoder -> online packer
+            from ..data.multimodal import VLMTaskEncoder, VisionPreprocess, vlm_batch_iterator, webdataset_samples
+            from ..tokenizer.tokenizer import build_tokenizer
+            tok = build_tokenizer(args.tokenizer_type, args.hf_tokenizer_path, use_fast=args.use_fast_tokenizer)
+            vision = VisionPreprocess(patch_size=v.patch_size, temporal_patch_size=v.temporal_patch_size,
+                                      merge_size=v.spatial_merge_size,
+                                      **{k: getattr(args, k) for k in ("min_pixels", "max_pixels")
+                                         if getattr(args, k, None) is not None})
+            enc = VLMTaskEncoder(lambda text: tok.tokenize(text), self.image_token_id, vision, eos_id=tok.eod)
+            samples = webdataset_samples(paths[-1], dp_rank=st.dp_rank, dp_size=st.dp_size, seed=self.tcfg.seed,
+                                         start_sample=self.consumed_samples // max(st.dp_size, 1))
+            return vlm_batch_iterator(samples, enc, self.tcfg.seq_length, merge_size=v.spatial_merge_size,
+                                      pad_id=tok.pad, packing=bool(getattr(args, "packing_sft_data", True)),
+                                      pin_memory=self.device.type == "cuda")
         return synthetic_vlm_iterator(self.mcfg.vocab_size, self.tcfg.seq_length, patch=v.patch_size,
                                       temporal_patch=v.temporal_patch_size, merge=v.spatial_merge_size,
                                       channels=v.in_channels, image_token_id=self.image_token_id, dp_rank=st.dp_rank,
