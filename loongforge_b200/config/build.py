@@ -132,7 +132,9 @@ _FLAG_TO_CFG = {"swiglu": ("activation", "swiglu"), "add_qkv_bias": ("add_qkv_bi
                 "moe_router_enable_expert_bias": ("moe_router_enable_expert_bias", True),
                 "multi_latent_attention": ("multi_latent_attention", True), "use_dsa_fused": ("use_dsa", True),
                 "sequence_parallel": ("sequence_parallel", True), "tp_comm_overlap": ("tp_comm_overlap", True),
-                "no_gradient_accumulation_fusion": ("gradient_accumulation_fusion", False)}
+                "no_gradient_accumulation_fusion": ("gradient_accumulation_fusion", False),
+                "moe_grouped_gemm": ("moe_grouped_gemm", True),
+                "cross_entropy_loss_fusion": ("cross_entropy_loss_fusion", True)}
 
 
 def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[TransformerConfig, TrainConfig, ParallelDims, dict]:
@@ -211,6 +213,7 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
         check_weight_hash_interval=int(getattr(args, "check_weight_hash_across_dp_replicas_interval", 0) or 0),
         eval_interval=int(getattr(args, "eval_interval", 0) or 0), eval_iters=int(getattr(args, "eval_iters", 0) or 0),
         no_save_optim=bool(getattr(args, "no_save_optim", False)), no_save_rng=bool(getattr(args, "no_save_rng", False)),
+        log_memory_stats=bool(getattr(args, "log_memory_stats", False)),
         dp_balance=bool(getattr(args, "use_vlm_dp_balance", False)),
         optimizer_cpu_offload=bool(getattr(args, "optimizer_cpu_offload", False)),
         use_fsdp=bool(getattr(args, "use_torch_fsdp2", False) or getattr(args, "use_megatron_fsdp", False)),
@@ -218,7 +221,8 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
         use_distributed_optimizer=args.use_distributed_optimizer, overlap_grad_reduce=args.overlap_grad_reduce,
         overlap_param_gather=args.overlap_param_gather, exp_avg_dtype=dt[args.exp_avg_dtype],
         exp_avg_sq_dtype=dt[args.exp_avg_sq_dtype], calculate_per_token_loss=args.calculate_per_token_loss,
-        custom_pipeline_layers=custom_layers, custom_pipeline_recompute_layers=recompute_layers, training_phase=args.training_phase, log_throughput=True)
+        custom_pipeline_layers=custom_layers, custom_pipeline_recompute_layers=recompute_layers, training_phase=args.training_phase,
+        log_throughput=True)  # --log-throughput: the TFLOP/s field is always part of the log line
     from .validators import validate
     validate(args, cfg, tc, dims)
     return cfg, tc, dims, raw

@@ -84,6 +84,9 @@ _ACCEPTED = {
     "timing_log_level": "all timers are recorded",
     "detail_log_interval": "one log interval exists",
     "wandb_exp_name": "the run name is the output directory",
+    "packing_batch_size": "the online packer's buffer holds 16 samples (64 for SFT text)",
+    "frame_num": "video inputs are not decoded by the built-in loaders (image-text shards only)",
+    "fps": "video inputs are not decoded by the built-in loaders (image-text shards only)",
     "moe_use_upcycling": "dense checkpoints are upcycled offline with runtime.upcycling.upcycle_state_dict",
 }
 

@@ -62,6 +62,7 @@ class TrainConfig:
     master_as_remainder: bool = False
     optimizer_cpu_offload: bool = False  # masters + Adam moments on the host, native host AdamW
     fp8_policy_file: Optional[str] = None  # JSON rules: which linear kinds run FP8 (runtime/fp8_policy.py)
+    log_memory_stats: bool = False  # memory fields in the log line also on the host (they are always there on GPUs)
     no_save_optim: bool = False  # checkpoints without optimizer state / RNG state
     no_save_rng: bool = False
     eval_interval: int = 0  # > 0: run `eval_iters` forward-only steps on the validation stream every N iterations
