@@ -234,26 +234,29 @@ class WanModel(nn.Module):
         """latents [B, C, F, H, W], timesteps [B], text_context [B, Lt, text_dim] -> prediction like `latents`."""
         cfg = self.cfg
         tok, grid = self.patchify(latents)
+        angles = rope_3d_angles(grid, cfg.head_dim, cfg.rope_theta, tok.device)
+        if ulysses_group is not None:
+            # Every token-wise computation (patch embedding ... head) runs on THIS rank's tokens only, so each
+            # parameter's gradient is the partial sum over the local tokens and one rule holds for all of them: sum
+            # over the sequence-parallel group.
+            from ..parallel.ulysses import shard_sequence
+            tok = shard_sequence(tok, ulysses_group, dim=1)
+            angles = shard_sequence(angles, ulysses_group, dim=0)  # RoPE is applied to the local tokens
         x = self.patch_embedding(tok.to(cfg.params_dtype))
-        angles = rope_3d_angles(grid, cfg.head_dim, cfg.rope_theta, x.device)
         e0 = self.time_embedding(timestep_embedding(timesteps, cfg.freq_dim).to(cfg.params_dtype))
         e = self.time_projection(e0).view(-1, 6, cfg.hidden_size)
         ctx = self.text_embedding(text_context.to(cfg.params_dtype))
         img = self.img_emb(image_context.to(cfg.params_dtype)) if image_context is not None else None
-        if ulysses_group is not None:
-            from ..parallel.ulysses import shard_sequence
-            x = shard_sequence(x, ulysses_group, dim=1)
-            angles = shard_sequence(angles, ulysses_group, dim=0)  # RoPE is applied to the local tokens
         for blk in self.blocks:
             if self.recompute and torch.is_grad_enabled():
                 x = torch.utils.checkpoint.checkpoint(blk, x, e, angles, ctx, img, ulysses_group, use_reentrant=False)
             else:
                 x = blk(x, e, angles, ctx, img, ulysses_group)
+        b, s = (self.head_modulation.float() + e0.float()[:, None]).unbind(1)
+        x = self.head((self.head_norm(x).float() * (1 + s[:, None]) + b[:, None]).to(x.dtype))
         if ulysses_group is not None:
             from ..parallel.ulysses import gather_sequence
             x = gather_sequence(x, ulysses_group, dim=1)
-        b, s = (self.head_modulation.float() + e0.float()[:, None]).unbind(1)
-        x = self.head((self.head_norm(x).float() * (1 + s[:, None]) + b[:, None]).to(x.dtype))
         return self.unpatchify(x, grid)
 
 

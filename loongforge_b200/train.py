@@ -59,8 +59,18 @@ def main(argv: Optional[List[str]] = None) -> int:
     if getattr(args, "peft_type", None) and train_cfg.training_phase == "sft" and "lora" not in extra:
         extra["lora"] = dict(rank=args.lora_rank, alpha=args.lora_alpha, dropout=args.lora_dropout,
                              targets=tuple(args.lora_target_modules), canonical=args.peft_type == "canonical_lora")
-    trainer = build_model_trainer(family, train_cfg.training_phase, model_cfg=model_cfg, train_cfg=train_cfg,
-                                  dims=dims, device=device, **extra)
+    from .runtime.diffusion_trainer import build_diffusion_trainer, is_diffusion_model
+    if is_diffusion_model(args.model_name):
+        # diffusion transformers (WAN, Qwen-Image): their own model configuration, the common loop around it
+        over = {k: v for k, v in (("num_layers", args.num_layers), ("hidden_size", args.hidden_size),
+                                  ("ffn_hidden_size", args.ffn_hidden_size), ("num_heads", args.num_attention_heads))
+                if v is not None}
+        trainer = build_diffusion_trainer(args.model_name, train_cfg, dims, device=device, dit_overrides=over,
+                                          recompute=args.recompute_granularity == "full")
+        family = trainer.kind
+    else:
+        trainer = build_model_trainer(family, train_cfg.training_phase, model_cfg=model_cfg, train_cfg=train_cfg,
+                                      dims=dims, device=device, **extra)
     _load_initial_state(trainer, args, train_cfg, family)
     data_iter = trainer.build_data_iterator(args) if hasattr(trainer, "build_data_iterator") else None
     if data_iter is None:
