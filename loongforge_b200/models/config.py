@@ -91,6 +91,13 @@ class TransformerConfig:
     dsa_indexer_head_dim: int = 128
     dsa_indexer_topk: int = 2048
     dsa_indexer_loss_coeff: float = 0.0
+    # IndexShare (GLM-5.2): only some layers own an indexer; the others reuse the latest computed top-k indices.
+    # Layers below the offset and every `freq`-th layer from (offset + freq - 1) on compute their own.
+    dsa_indexer_topk_freq: int = 1
+    dsa_indexer_skip_topk_offset: int = 0
+    dsa_indexer_rope_interleaved: bool = False  # GLM-5.x rotates the indexer's rotary part in interleaved pairs
+    dsa_indexer_rotate_activation: bool = True  # Hadamard transform of the indexer q / k (DeepSeek-V3.2: on, GLM-5.x: off)
+    dsa_indexer_k_norm_epsilon: float = 1e-6
     # ---- hybrid attention (Qwen3-Next / Qwen3.5): per-layer "full_attention" | "linear_attention"
     layer_types: Optional[List[str]] = None
     full_attention_interval: Optional[int] = None  # every n-th layer is full attention when layer_types is unset
@@ -170,6 +177,20 @@ class TransformerConfig:
         mult = self.make_vocab_size_divisible_by * tp
         self.padded_vocab_size = ((self.vocab_size + mult - 1) // mult) * mult
         return self.padded_vocab_size
+
+    def dsa_computes_topk(self, layer_idx: int) -> bool:
+        """Does this (0-based) layer own an indexer, or does it reuse another layer's top-k (IndexShare)?"""
+        f, off = self.dsa_indexer_topk_freq, self.dsa_indexer_skip_topk_offset
+        if f <= 1 or layer_idx < off or layer_idx >= self.num_layers:  # MTP layers (>= num_layers) always compute
+            return True
+        return (layer_idx - off + 1) % f == 0
+
+    def dsa_source_layer(self, layer_idx: int) -> int:
+        """The layer whose top-k indices this layer uses (itself when it computes them)."""
+        l = layer_idx
+        while not self.dsa_computes_topk(l):
+            l -= 1
+        return l
 
     def is_moe_layer(self, layer_idx: int) -> bool:
         if self.num_moe_experts is None:

@@ -64,7 +64,7 @@ class DSAIndexer(nn.Module):
         q_in = cfg.q_lora_rank or cfg.hidden_size
         self.linear_wq_b = _ReplicatedLinear(q_in, self.nh * self.d, key + ".linear_wq_b", cfg, device)
         self.linear_wk = _ReplicatedLinear(cfg.hidden_size, self.d, key + ".linear_wk", cfg, device)
-        self.k_norm = nn.LayerNorm(self.d, eps=1e-6, device=device, dtype=cfg.params_dtype)
+        self.k_norm = nn.LayerNorm(self.d, eps=cfg.dsa_indexer_k_norm_epsilon, device=device, dtype=cfg.params_dtype)
         self.linear_weights_proj = _ReplicatedLinear(cfg.hidden_size, self.nh, key + ".linear_weights_proj", cfg, device)
         self.rope_dim = cfg.qk_pos_emb_head_dim
         self.softmax_scale = self.d ** -0.5
@@ -74,12 +74,14 @@ class DSAIndexer(nn.Module):
         T = x.shape[0]
         q = self.linear_wq_b(q_c).view(T, self.nh, self.d)
         k = self.k_norm(self.linear_wk(x))
-        # rotary part comes FIRST in the indexer's head layout (non-interleaved halves)
-        q = OF.rope(q, rotary.freqs, pos_ids=rotary.pos_ids, rot_dim=self.rope_dim, rot_offset=0, interleaved=False)
+        # rotary part comes FIRST in the indexer's head layout (half-split pairs; GLM-5.x: interleaved pairs)
+        il = self.cfg.dsa_indexer_rope_interleaved
+        q = OF.rope(q, rotary.freqs, pos_ids=rotary.pos_ids, rot_dim=self.rope_dim, rot_offset=0, interleaved=il)
         k = OF.rope(k.view(T, 1, self.d), rotary.freqs, pos_ids=rotary.pos_ids, rot_dim=self.rope_dim, rot_offset=0,
-                    interleaved=False).view(T, self.d)
-        q = dsa_ops.hadamard_transform(q)
-        k = dsa_ops.hadamard_transform(k)
+                    interleaved=il).view(T, self.d)
+        if self.cfg.dsa_indexer_rotate_activation:
+            q = dsa_ops.hadamard_transform(q)
+            k = dsa_ops.hadamard_transform(k)
         w = self.linear_weights_proj(x).float() * (self.nh ** -0.5) * self.softmax_scale
         return q, k, w
 
@@ -117,7 +119,12 @@ class MLASelfAttention(nn.Module):
                                                 sequence_parallel=cfg.sequence_parallel, **common)
         if cfg.use_dsa:
             self.core_attention = nn.Module()
-            self.core_attention.indexer = DSAIndexer(cfg, key + ".core_attention.indexer", device)
+            # IndexShare: a layer without an indexer receives the top-k indices of its source layer
+            self.computes_topk = cfg.dsa_computes_topk(layer_number)
+            if self.computes_topk:
+                self.core_attention.indexer = DSAIndexer(cfg, key + ".core_attention.indexer", device)
+            self.last_topk_indices = None  # what this layer selected (or was given) in its latest forward
+            self.shared_topk_indices = None  # set by the layer loop before calling a layer that reuses indices
         self.mscale = 1.0  # set from the rotary inputs (YaRN)
 
     def _softmax_scale(self, rotary) -> float:
@@ -189,15 +196,22 @@ class MLASelfAttention(nn.Module):
             key_all = M.gather_from_sequence_parallel_region(key, g, True)
             pos_k = M._all_gather_dim0(pos, g)
             seg_k = M._all_gather_dim0(seg, g) if seg is not None else None
-        idxr = self.core_attention.indexer
-        qi, ki, wi = idxr.project(x.detach(), q_c.detach(), rotary)
-        # index keys of the other context-parallel ranks; their gradient (indexer loss) flows back by reduce-scatter
-        ki_all = M.gather_from_sequence_parallel_region(ki, st.group("cp"), True) if st.dims.cp > 1 else ki
-        with torch.no_grad():
-            qq, _ = dsa_ops.quant_fp8_rowwise_pow2(qi) if cfg.fp8 else (qi, None)
-            kq, _ = dsa_ops.quant_fp8_rowwise_pow2(ki_all) if cfg.fp8 else (ki_all, None)
-            indices, _ = dsa_ops.indexer_topk(qq, kq, wi, cfg.dsa_indexer_topk, pos, pos_k, seg, seg_k)
-        want_loss = self.training and cfg.dsa_indexer_loss_coeff > 0
+        if self.computes_topk:
+            idxr = self.core_attention.indexer
+            qi, ki, wi = idxr.project(x.detach(), q_c.detach(), rotary)
+            # index keys of the other context-parallel ranks; their gradient (indexer loss) flows back by reduce-scatter
+            ki_all = M.gather_from_sequence_parallel_region(ki, st.group("cp"), True) if st.dims.cp > 1 else ki
+            with torch.no_grad():
+                qq, _ = dsa_ops.quant_fp8_rowwise_pow2(qi) if cfg.fp8 else (qi, None)
+                kq, _ = dsa_ops.quant_fp8_rowwise_pow2(ki_all) if cfg.fp8 else (ki_all, None)
+                indices, _ = dsa_ops.indexer_topk(qq, kq, wi, cfg.dsa_indexer_topk, pos, pos_k, seg, seg_k)
+        else:
+            indices = self.shared_topk_indices
+            if indices is None:
+                raise RuntimeError(f"layer {self.layer_number} reuses top-k indices (IndexShare) but received none; "
+                                   "a pipeline stage must start on a layer that computes them")
+        self.last_topk_indices = indices
+        want_loss = self.training and cfg.dsa_indexer_loss_coeff > 0 and self.computes_topk
         out = dsa_ops.sparse_mla_attention(query, key_all, indices, scale, d_v=self.dc,
                                            return_head_mean_probs=want_loss)
         if want_loss:

@@ -379,6 +379,10 @@ class TransformerBlock(nn.Module):
         self.layers = nn.ModuleList([TransformerLayer(cfg, n, device=device, parallel_state=parallel_state)
                                      for n in layer_numbers])
         self.layer_numbers = list(layer_numbers)
+        if (cfg.use_dsa and cfg.dsa_indexer_topk_freq > 1 and self.layer_numbers
+                and not cfg.dsa_computes_topk(self.layer_numbers[0])):
+            raise ValueError(f"layer {self.layer_numbers[0]} reuses another layer's top-k indices (IndexShare): every "
+                             "pipeline stage must start on a layer that computes them")
         self.final_layernorm = Norm(cfg.hidden_size, cfg, device=device,
                                     sequence_parallel=cfg.sequence_parallel) if post_process else None
         self.deepstack_hook = None  # callable(layer_idx, hidden) -> hidden, used by Qwen3-VL
@@ -390,7 +394,9 @@ class TransformerBlock(nn.Module):
                                                    "decoder.head_hyper_connection", device=device,
                                                    sequence_parallel=cfg.sequence_parallel)
 
-    def _run(self, layer, x, rotary, packed):
+    def _run(self, layer, x, rotary, packed, shared_idx=None):
+        if shared_idx is not None and hasattr(layer.self_attention, "shared_topk_indices"):
+            layer.self_attention.shared_topk_indices = shared_idx  # IndexShare: top-k indices of the source layer
         return layer(x, rotary, packed)
 
     def forward(self, x, rotary=None, packed=None):
@@ -405,12 +411,17 @@ class TransformerBlock(nn.Module):
             ns = cfg.num_residual_streams
             x = x.unsqueeze(1).expand(-1, ns, -1).contiguous() if x.shape[-1] == cfg.hidden_size else \
                 x.view(x.shape[0], ns, cfg.hidden_size)
+        share = cfg.use_dsa and cfg.dsa_indexer_topk_freq > 1
+        shared_idx = None
         for i, layer in enumerate(self.layers):
             do_rec = rec and ((method == "block" and i < rec_n) or method == "uniform")
             if do_rec:
-                x = torch.utils.checkpoint.checkpoint(self._run, layer, x, rotary, packed, use_reentrant=False)
+                # the shared top-k indices are an explicit input, so a recomputed layer sees those of ITS forward
+                x = torch.utils.checkpoint.checkpoint(self._run, layer, x, rotary, packed, shared_idx, use_reentrant=False)
             else:
-                x = layer(x, rotary, packed)
+                x = self._run(layer, x, rotary, packed, shared_idx)
+            if share:
+                shared_idx = getattr(layer.self_attention, "last_topk_indices", shared_idx)
             if self.deepstack_hook is not None:
                 x = self.deepstack_hook(self.layer_numbers[i], x)
         if hyper:

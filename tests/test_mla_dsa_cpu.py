@@ -68,3 +68,40 @@ def test_tiny_deepseek_v32_trains_with_indexer_loss():
                               for n, p in model.named_parameters() if ".indexer." in n)  # trained by the KL loss
     assert all(p.grad is not None for p in model.parameters())
     assert losses[-1] < losses[0] - 0.2, losses
+
+
+def test_index_share_layers_reuse_topk_and_train():
+    """GLM-5.2 IndexShare: with frequency 4 and offset 3 the layers 0, 1, 2, 6, 10, ... own an indexer; the others
+    take the indices of the latest computing layer, also when activations are recomputed."""
+    import torch
+
+    from loongforge_b200.models.config import TransformerConfig
+    from loongforge_b200.models.registry import build_model, get_model_config
+    from loongforge_b200.parallel import state as ps
+
+    c = TransformerConfig(num_layers=78, dsa_indexer_topk_freq=4, dsa_indexer_skip_topk_offset=3)
+    owners = [l for l in range(78) if c.dsa_computes_topk(l)]
+    assert owners[:6] == [0, 1, 2, 6, 10, 14] and owners[-1] == 74 and len(owners) == 21
+    assert [c.dsa_source_layer(l) for l in (3, 5, 6, 9, 77)] == [2, 2, 6, 6, 74]
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(ps.ParallelDims())
+    cfg = get_model_config("tiny-glm")  # 6 layers, frequency 2, offset 1 -> layers 0, 2, 4 compute
+    model = build_model(cfg)
+    has = [hasattr(l.self_attention.core_attention, "indexer") for l in model.decoder.layers]
+    assert has == [True, False, True, False, True, False]
+    T = 48
+    tok = torch.randint(0, cfg.vocab_size, (T,))
+    out = {}
+    for rec in (None, "full"):
+        cfg.recompute_granularity = rec
+        model.zero_grad()
+        model(tok, torch.arange(T), labels=torch.roll(tok, -1), loss_mask=torch.ones(T)).mean().backward()
+        idx = [l.self_attention.last_topk_indices for l in model.decoder.layers]
+        assert torch.equal(idx[1], idx[0]) and torch.equal(idx[3], idx[2]) and not torch.equal(idx[2], idx[0])
+        out[rec] = model.decoder.layers[1].self_attention.linear_proj.weight.grad.clone()
+    assert torch.allclose(out[None], out["full"], atol=1e-6), "recomputation sees the same shared indices"
+    # a pipeline stage may not start on a layer that reuses indices
+    from loongforge_b200.models.gpt import GPTModel
+    import pytest
+    with pytest.raises(ValueError, match="IndexShare"):
+        GPTModel(cfg, pre_process=False, post_process=True, layer_numbers=[3, 4, 5])
