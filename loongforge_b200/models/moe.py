@@ -33,8 +33,12 @@ AUX_LOSS_TRACKER = {}
 
 def track_aux_loss(name: str, value: torch.Tensor, layer: int, num_layers: int):
     t = AUX_LOSS_TRACKER.get(name)
-    if t is None:
-        t = torch.zeros(num_layers, dtype=torch.float32, device=value.device)
+    if t is None or t.numel() < max(num_layers, layer + 1) or t.device != value.device:
+        # first use, or a deeper model than the one tracked before (several models in one process)
+        old = t
+        t = torch.zeros(max(num_layers, layer + 1), dtype=torch.float32, device=value.device)
+        if old is not None and old.device == t.device:
+            t[:old.numel()] = old
         AUX_LOSS_TRACKER[name] = t
     t[layer] += value.detach().float()
 
