@@ -41,6 +41,8 @@ class TransformerConfig:
     rotary_percent: float = 1.0
     rotary_interleaved: bool = False
     rotary_scaling_factor: float = 1.0
+    rotary_dynamic_ntk: bool = False  # enlarge the rotary base for sequences beyond max_position_embeddings
+    rotary_dynamic_ntk_factor: float = 8.0
     mrope_section: Optional[List[int]] = None
     mrope_interleaved: bool = False
     attention_dropout: float = 0.0

@@ -55,18 +55,23 @@ class RotaryEmbedding:
         self.cfg, self.rot_dim = cfg, rot_dim
         self._cache = {}
 
-    def _inv_freq(self, device):
+    def _inv_freq(self, device, n_pos: Optional[int] = None):
         cfg = self.cfg
         if cfg.position_embedding_type == "yarn":
             return yarn_inv_freq(cfg, self.rot_dim, device)
-        inv = 1.0 / (cfg.rotary_base ** (torch.arange(0, self.rot_dim, 2, dtype=torch.float32, device=device)
-                                         / self.rot_dim))
+        base = cfg.rotary_base
+        if cfg.rotary_dynamic_ntk and n_pos is not None and n_pos > cfg.max_position_embeddings:
+            # dynamic NTK: the base grows with the sequence length beyond the trained context (Qwen2 / InternLM,
+            # loongforge/models/foundation/qwen2/qwen_model.py:56-126)
+            f, d = cfg.rotary_dynamic_ntk_factor, self.rot_dim
+            base = base * ((f * n_pos / cfg.max_position_embeddings) - (f - 1)) ** (d / (d - 2))
+        inv = 1.0 / (base ** (torch.arange(0, self.rot_dim, 2, dtype=torch.float32, device=device) / self.rot_dim))
         return inv / cfg.rotary_scaling_factor if cfg.rotary_scaling_factor != 1.0 else inv, 1.0
 
     def table(self, n_pos: int, device) -> RotaryInputs:
         key = (n_pos, str(device))
         if key not in self._cache:
-            inv, mscale = self._inv_freq(device)
+            inv, mscale = self._inv_freq(device, n_pos)
             t = torch.arange(n_pos, dtype=torch.float32, device=device)
             self._cache = {key: (torch.outer(t, inv).contiguous(), mscale)}
         f, m = self._cache[key]

@@ -184,3 +184,17 @@ def test_async_save_publishes_tracker_after_the_write():
         for before, after, nxt, again in run_distributed(_async_worker, 2, tmp):
             assert before is False and after == "3"
             assert nxt == again  # the checkpoint holds the state at save time, not the later step's
+
+
+def test_dynamic_ntk_rotary_base_grows_beyond_the_trained_context():
+    from loongforge_b200.models.config import TransformerConfig
+    from loongforge_b200.models.gpt import RotaryEmbedding
+
+    cfg = TransformerConfig(max_position_embeddings=128, rotary_dynamic_ntk=True, rotary_dynamic_ntk_factor=8.0)
+    rot = RotaryEmbedding(cfg, 64)
+    short, long = rot.table(128, "cpu").freqs, rot.table(512, "cpu").freqs
+    plain = RotaryEmbedding(TransformerConfig(max_position_embeddings=128), 64).table(512, "cpu").freqs
+    assert torch.equal(short, plain[:128]), "within the trained context nothing changes"
+    base = 10000.0 * ((8.0 * 512 / 128) - 7.0) ** (64 / 62)
+    want = torch.outer(torch.arange(512.0), 1.0 / base ** (torch.arange(0, 64, 2).float() / 64))
+    assert torch.allclose(long, want, rtol=1e-5) and not torch.allclose(long, plain)
