@@ -182,10 +182,13 @@ def model_param_items(trainer):
         layer_numbers = getattr(mod.decoder, "layer_numbers", None) if hasattr(mod, "decoder") else None
         for name, p in mod.named_parameters():
             key = name
-            if layer_numbers is not None and name.startswith("decoder.layers."):
-                parts = name.split(".")
-                parts[2] = str(layer_numbers[int(parts[2])])
-                key = ".".join(parts)
+            # stage-local layer index -> global one; the language model may sit under a prefix ("foundation_model."
+            # in vision-language models), the encoder's own "...image_encoder.decoder.layers." is never pipelined
+            at = name.find("decoder.layers.")
+            if layer_numbers is not None and at >= 0 and "encoder" not in name[:at]:
+                head, rest = name[:at + len("decoder.layers.")], name[at + len("decoder.layers."):]
+                idx, _, tail = rest.partition(".")
+                key = f"{head}{layer_numbers[int(idx)]}.{tail}"
             ge = getattr(p, "expert_global_index", None)
             if ge is not None:  # "...linear_fc1.weight{local}" -> "...linear_fc1.weight{global}" under expert parallelism
                 key = key[:key.rindex("weight")] + f"weight{ge}"

@@ -46,3 +46,44 @@ def test_vlm_layouts_match_single_process(dims, vlm_kw, world):
         assert abs(l0 - l1) < 2e-4 * abs(l0) and abs(g0 - g1) < 1e-3 * max(1, g0), (ref, got)
     for r in res:  # every rank reports the same global gradient norm
         assert all(abs(a[1] - b[1]) < 1e-5 * max(1, b[1]) for a, b in zip(r, got)), res
+
+
+def _ckpt_worker(rank, world, tmp, dims_kw, vlm_kw, mode):
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel.state import ParallelDims
+    from loongforge_b200.runtime.trainer import TrainConfig
+    from loongforge_b200.runtime.vlm import VLMTrainer, synthetic_vlm_iterator
+
+    lm = get_model_config("tiny-llama", position_embedding_type="mrope", mrope_section=[8, 12, 12])
+    if dims_kw.get("tp", 1) > 1:
+        lm.sequence_parallel = True
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=4, seq_length=128, train_iters=4, lr=1e-3, clip_grad=1.0,
+                     log_interval=1000)
+    tr = VLMTrainer(lm, tc, ParallelDims(**dims_kw), vit_cfg=get_model_config("tiny-vit"), images_per_sample=2,
+                    image_size=112, **vlm_kw)
+    st = tr.st
+    it = synthetic_vlm_iterator(lm.vocab_size, 128, images_per_sample=2, image_size=112, pin_memory=False,
+                                dp_rank=st.dp_rank, dp_size=st.dp_size, seed=9)
+    if mode == "save":
+        for _ in range(2):
+            tr.train_step(it)
+        tr.save_checkpoint(tmp)
+    else:
+        assert tr.load_checkpoint(tmp) == 2
+        for _ in range(2 * 4 // st.dp_size):
+            next(it)
+    m = tr.train_step(it)
+    return m.get("lm loss"), m["grad_norm"]
+
+
+@pytest.mark.parametrize("save,load", [
+    (({"tp": 2}, {}, 2), ({"pp": 2}, {}, 2)),                                   # encoder TP 1 beside decoder TP 2
+    (({"tp": 2}, {"encoder_tp": 2}, 2), ({}, {}, 1)),
+    (({"pp": 2}, {"full_hetero_dp": True}, 2), ({"tp": 2}, {"encoder_hetero_dp": True}, 2)),  # encoder replica not saved
+])
+def test_vlm_checkpoints_reshard(save, load, tmp_path):
+    a = run_distributed(_ckpt_worker, save[2], str(tmp_path), save[0], save[1], "save")
+    b = run_distributed(_ckpt_worker, load[2], str(tmp_path), load[0], load[1], "load")
+    ga = [x for x in a if x[0] is not None][-1]
+    gb = [x for x in b if x[0] is not None][-1]
+    assert abs(ga[0] - gb[0]) < 1e-4 * abs(ga[0]) and abs(ga[1] - gb[1]) < 1e-3 * max(1, ga[1]), (ga, gb)
