@@ -127,7 +127,9 @@ def gpt_chunkpipe_step(model: nn.Module, tokens: torch.Tensor, position_ids: tor
     """One micro-batch (ONE sequence, flat ``[T]`` tensors) of a single-stage GPT model through the chunk pipeline:
     accumulates the gradients of ``loss_scale * sum(loss * mask)`` and returns that loss value. Attention layers
     take the earlier chunks' keys / values through ``models.transformer.CHUNK_PREFIX``; every other sub-layer (norms,
-    dense and MoE MLPs, the fused linear + cross-entropy head) is token-local and runs on the chunk alone."""
+    dense and MoE MLPs, the fused linear + cross-entropy head) is token-local and runs on the chunk alone. Tensor
+    parallelism (with or without sequence parallelism) needs nothing extra: every rank caches the keys / values of its
+    own heads."""
     from ..models import transformer as TF
 
     cfg = model.cfg
@@ -137,13 +139,19 @@ def gpt_chunkpipe_step(model: nn.Module, tokens: torch.Tensor, position_ids: tor
         "chunk pipelining covers softmax-attention GPT layers"
     dev = tokens.device
     mask_f = loss_mask.float()
+    from ..parallel import state as ps
+    st = ps.get_state(model.state_name)
+    sp_factor = st.dims.tp if (cfg.sequence_parallel and st.dims.tp > 1) else 1
+    bounds = chunk_bounds(tokens.shape[0], num_chunks)
+    if any((e - s) % sp_factor for s, e in bounds):
+        raise ValueError("with sequence parallelism every chunk length must divide by the tensor-parallel size")
 
     class _Layer:
         def __init__(self, layer):
             self.layer = layer
 
         def __call__(self, x, past, offset):
-            T = x.shape[0]
+            T = x.shape[0] * sp_factor  # under sequence parallelism x is this rank's shard of the chunk
             rotary = model.build_rotary(position_ids[..., offset:offset + T], position_ids.shape[-1], dev)
             TF.CHUNK_PREFIX.update(active=True, past=past, out=None)
             try:

@@ -480,8 +480,8 @@ class Trainer:
         from .chunkpipe import gpt_chunkpipe_step
 
         t, st = self.tcfg, self.st
-        if st.dims.pp > 1 or st.dims.cp > 1 or st.dims.tp > 1 or t.micro_batch_size != 1:
-            raise ValueError("chunk pipelining needs pp = cp = tp = 1 and micro batch size 1")
+        if st.dims.pp > 1 or st.dims.cp > 1 or t.micro_batch_size != 1:
+            raise ValueError("chunk pipelining needs pp = cp = 1 and micro batch size 1")
         model = self.models[0]
         nmb = self.mb_calc.num_microbatches
         reports = []

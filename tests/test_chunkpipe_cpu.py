@@ -86,3 +86,28 @@ def test_trainer_with_chunk_pipelining_matches_whole_sequences(model_name):
     ref, got = run(0), run(4)
     for (l0, g0), (l1, g1) in zip(ref, got):
         assert abs(l0 - l1) < 1e-4 * max(1, abs(l0)) and abs(g0 - g1) < 1e-3 * max(1, abs(g0)), (ref, got)
+
+
+def _chunk_tp(rank, world, chunks, dims_kw, sp):
+    from loongforge_b200.data.synthetic import synthetic_batch_iterator
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel.state import ParallelDims
+    from loongforge_b200.runtime.trainer import TrainConfig, Trainer
+
+    cfg = get_model_config("tiny-qwen3-moe", moe_aux_loss_coeff=0.0)
+    cfg.sequence_parallel = sp and dims_kw.get("tp", 1) > 1
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=2, seq_length=64, train_iters=2, lr=1e-3, log_interval=1000,
+                     chunkpipe_chunks=chunks)
+    tr = Trainer(cfg, tc, ParallelDims(**dims_kw))
+    it = synthetic_batch_iterator(cfg.vocab_size, 64, 1, seed=4, pin_memory=False)
+    return [(m["lm loss"], m["grad_norm"]) for m in (tr.train_step(it) for _ in range(2))]
+
+
+@pytest.mark.parametrize("sp", [True, False])
+def test_chunk_pipelining_under_tensor_parallelism(sp):
+    from dist_utils import run_distributed
+
+    ref = run_distributed(_chunk_tp, 1, 0, {}, False)[0]
+    got = run_distributed(_chunk_tp, 2, 4, {"tp": 2}, sp)[0]
+    for (l0, g0), (l1, g1) in zip(ref, got):
+        assert abs(l0 - l1) < 1e-4 * abs(l0) and abs(g0 - g1) < 1e-3 * max(1, g0), (ref, got)
