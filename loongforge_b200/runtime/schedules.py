@@ -212,15 +212,18 @@ def forward_backward_pipelining_1f1b(*, forward_step_func, data_iterator, model,
 
 def forward_backward_pipelining_interleaved(*, forward_step_func, data_iterator, model, num_microbatches: int,
                                             tensor_shape, dtype, forward_only: bool = False, **_) -> List[dict]:
-    """Virtual-pipeline schedule: each rank holds `v` model chunks; the `pp * v` virtual stages form a
-    ring (chunk c on the last rank feeds chunk c+1 on the first rank).
+    """Interleaved 1F1B over virtual pipeline stages: each rank holds `v` model chunks; the `pp * v` virtual stages
+    form a ring (chunk c on the last rank feeds chunk c+1 on the first rank).
 
-    Micro-batches run in groups of `pp`. Inside a group the ring advances in lock step: at tick t rank r
-    runs forward unit ``u = t - r`` (chunk ``u // pp``, micro-batch ``u % pp``), and between two ticks
-    every rank posts its send to the next rank and its receive from the previous rank as ONE batch of
-    non-blocking operations. No rank ever blocks in a send whose receiver is itself blocked in a send,
-    which a rendezvous transport (gloo, NCCL point-to-point) needs with wrap-around neighbours. The
-    backward wave mirrors it in the opposite direction. At most `pp` micro-batches per chunk are alive."""
+    Work is cut into units (chunk, micro-batch). Micro-batches go in groups of `pp`; the FORWARD stream visits, per
+    group, chunk 0 for its pp micro-batches, then chunk 1, ...; the BACKWARD stream visits the same units with the
+    chunks in reverse. Both streams advance in lock step: at tick t rank r runs forward unit ``t - r`` and backward
+    unit ``t - v*pp - (pp-1-r)`` (whichever exist), then posts ALL its sends and receives for the next tick - forward
+    activation to the next rank, gradient to the previous rank, and the matching receives - as one batch of
+    non-blocking operations. No rank ever blocks in a send whose receiver is blocked in a send, which a rendezvous
+    transport (gloo, NCCL point-to-point) needs with wrap-around neighbours. The backward stream starts `v*pp` ticks
+    after the forward stream (when the last rank has finished the first group's last chunk), so a rank holds at most
+    ``v*pp + pp - 1 - 2r`` units' activations, and the pipeline fills and drains once per step, not once per group."""
     assert isinstance(model, (list, tuple)) and len(model) > 1
     st = ps.get_state()
     pp, v, r = st.dims.pp, len(model), st.pp_rank
@@ -231,59 +234,54 @@ def forward_backward_pipelining_interleaved(*, forward_step_func, data_iterator,
     iters = list(data_iterator) if isinstance(data_iterator, (list, tuple)) else list(itertools.tee(data_iterator, v))
     reports: List[dict] = []
     assert num_microbatches % pp == 0, "interleaved schedule needs num_microbatches divisible by pp"
-    n_groups = num_microbatches // pp
-    units, ticks = v * pp, v * pp + pp - 1
+    total, group = num_microbatches * v, v * pp
+    t0 = group  # delay of the backward stream
+    ticks = total + pp - 1 if forward_only else total + t0 + pp - 1
 
     def set_last(m, flag):
         if hasattr(m, "is_last_microbatch"):
             m.is_last_microbatch = flag
 
-    def fwd_unit(t):
-        """(chunk, micro-batch, first virtual stage?, last virtual stage?) of this rank at tick t, or None."""
-        u = t - r
-        if not 0 <= u < units:
+    def unit(u, backward):
+        """(chunk, micro-batch, first virtual stage?, last virtual stage?) of stream position u, or None."""
+        if not 0 <= u < total:
             return None
-        c = u // pp
-        return c, u % pp, st.is_first_stage and c == 0, st.is_last_stage and c == v - 1
+        g, rem = divmod(u, group)
+        c, m = divmod(rem, pp)
+        if backward:
+            c = v - 1 - c
+        return c, g * pp + m, st.is_first_stage and c == 0, st.is_last_stage and c == v - 1
 
-    def bwd_unit(t):
-        u = t - (pp - 1 - r)
-        if not 0 <= u < units:
-            return None
-        c = v - 1 - u // pp
-        return c, u % pp, st.is_first_stage and c == 0, st.is_last_stage and c == v - 1
-
-    for g in range(n_groups):
-        last_group = g == n_groups - 1
-        saved = [[None] * pp for _ in range(v)]
-        inp = None
-        for t in range(ticks):
-            cur, out = fwd_unit(t), None
-            if cur is not None:
-                c, mb, first_virtual, last_virtual = cur
-                out = _forward_one(forward_step_func, iters[c], model[c], None if first_virtual else inp,
-                                   reports, last_virtual)
-                saved[c][mb] = (None if first_virtual else inp, out)
-                if last_virtual:
-                    out = None
-            nxt = fwd_unit(t + 1)
-            inp = p2p._ops(send_next=out, recv_prev=nxt is not None and not nxt[2])[0]
-        if forward_only:
-            continue
-        out_grad = None
-        for t in range(ticks):
-            cur, in_grad = bwd_unit(t), None
-            if cur is not None:
-                c, mb, first_virtual, last_virtual = cur
-                b_in, b_out = saved[c][mb]
-                # gradient buckets of chunk c may start reducing only on its very last backward
-                set_last(model[c], last_group and mb == pp - 1)
-                in_grad = _backward_one(b_in, b_out, None if last_virtual else out_grad)
-                saved[c][mb] = None
-                if first_virtual:
-                    in_grad = None
-            nxt = bwd_unit(t + 1)
-            out_grad = p2p._ops(send_prev=in_grad, recv_next=nxt is not None and not nxt[3])[1]
+    f_unit = lambda t: unit(t - r, False)  # noqa: E731
+    b_unit = lambda t: None if forward_only else unit(t - t0 - (pp - 1 - r), True)  # noqa: E731
+    saved = {}
+    inp, out_grad = None, None
+    for m in model:
+        set_last(m, False)
+    for t in range(ticks):
+        out = in_grad = None
+        cur = f_unit(t)
+        if cur is not None:
+            c, mb, first_virtual, last_virtual = cur
+            x = None if first_virtual else inp
+            out = _forward_one(forward_step_func, iters[c], model[c], x, reports, last_virtual)
+            if not forward_only:
+                saved[(c, mb)] = (x, out)
+            if last_virtual:
+                out = None
+        cur = b_unit(t)
+        if cur is not None:
+            c, mb, first_virtual, last_virtual = cur
+            b_in, b_out = saved.pop((c, mb))
+            # gradient buckets of chunk c may start reducing only on its very last backward
+            set_last(model[c], mb == num_microbatches - 1)
+            in_grad = _backward_one(b_in, b_out, None if last_virtual else out_grad)
+            if first_virtual:
+                in_grad = None
+        nf, nb = f_unit(t + 1), b_unit(t + 1)
+        inp, out_grad = p2p._ops(send_next=out, recv_prev=nf is not None and not nf[2],
+                                 send_prev=in_grad, recv_next=nb is not None and not nb[3])
+    assert not saved, "every forward unit must have had its backward"
     for m in model:
         set_last(m, True)
     return reports

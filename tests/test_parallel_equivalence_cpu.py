@@ -110,6 +110,17 @@ def test_two_rows_per_microbatch_match_single_process(model, dims, ov, world):
     _check(ref, res, lambda r: True, tol=1e-3)
 
 
+@pytest.mark.parametrize("model,dims,ov,world,gbs", [
+    ("tiny-llama", {"pp": 2, "vpp": 2}, {"num_layers": 4}, 2, 8),      # two groups of micro-batches in one stream
+    ("tiny-llama", {"pp": 3, "vpp": 2}, {"num_layers": 6}, 3, 6),
+    ("tiny-minimax", {"pp": 2, "vpp": 2}, {"num_layers": 4, "untie_embeddings_and_output_weights": False}, 2, 4),
+])
+def test_interleaved_schedule_matches_single_process(model, dims, ov, world, gbs):
+    ref = _single(model, 2, ov, gbs)
+    res = run_distributed(_run, world, model, dict(dims), 2, ov, gbs)
+    _check(ref, res, lambda r: r == world - 1, tol=1e-3)
+
+
 def _run_cp(rank, world, comm):
     from loongforge_b200.parallel import context_parallel as CP
 
