@@ -77,7 +77,8 @@ def load_hf_checkpoint_online(trainer, hf_dir: str, family: str = "llama3") -> i
 _HF_ARCH = {"llama": ("llama", "LlamaForCausalLM"), "llama2": ("llama", "LlamaForCausalLM"),
             "llama3": ("llama", "LlamaForCausalLM"), "internlm": ("internlm2", "InternLM2ForCausalLM"),
             "qwen2": ("qwen2", "Qwen2ForCausalLM"), "qwen2.5": ("qwen2", "Qwen2ForCausalLM"),
-            "qwen3": ("qwen3", "Qwen3ForCausalLM"), "qwen3_moe": ("qwen3_moe", "Qwen3MoeForCausalLM")}
+            "qwen3": ("qwen3", "Qwen3ForCausalLM"), "qwen3_moe": ("qwen3_moe", "Qwen3MoeForCausalLM"),
+            "deepseek": ("deepseek_v3", "DeepseekV3ForCausalLM"), "glm": ("glm_moe_dsa", "GlmMoeDsaForCausalLM")}
 
 
 def hf_config_from_model(cfg, family: str) -> dict:
@@ -92,6 +93,14 @@ def hf_config_from_model(cfg, family: str) -> dict:
         "tie_word_embeddings": not cfg.untie_embeddings_and_output_weights, "hidden_act": "silu",
         "attention_bias": bool(cfg.add_qkv_bias), "torch_dtype": str(cfg.params_dtype).replace("torch.", ""),
     }
+    if cfg.multi_latent_attention:
+        out.update(q_lora_rank=cfg.q_lora_rank, kv_lora_rank=cfg.kv_lora_rank, qk_nope_head_dim=cfg.qk_head_dim,
+                   qk_rope_head_dim=cfg.qk_pos_emb_head_dim, v_head_dim=cfg.v_head_dim,
+                   num_nextn_predict_layers=cfg.mtp_num_layers, n_routed_experts=cfg.num_moe_experts,
+                   n_shared_experts=1 if cfg.moe_shared_expert_intermediate_size else 0)
+        if cfg.use_dsa:
+            out.update(index_n_heads=cfg.dsa_indexer_n_heads, index_head_dim=cfg.dsa_indexer_head_dim,
+                       index_topk=cfg.dsa_indexer_topk)
     if cfg.num_moe_experts:
         out.update(num_experts=cfg.num_moe_experts, num_experts_per_tok=cfg.moe_router_topk,
                    moe_intermediate_size=cfg.moe_ffn_hidden_size, norm_topk_prob=True)

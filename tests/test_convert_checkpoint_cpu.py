@@ -133,3 +133,72 @@ def test_preprocess_and_log_parser(tmp_path):
             "    32 | lm loss: 1.042075E+01 | loss scale: 1.0 | grad norm: 4.648900 |")
     rec = parse([line])[0]
     assert rec["iteration"] == 3 and rec["throughput"] == 3550.1 and abs(rec["lm_loss"] - 10.42075) < 1e-6
+
+
+def test_deepseek_name_map_roundtrip_with_mtp_and_indexer():
+    """MLA projections, lightning indexer, dense + MoE layers with shared expert and router bias, one MTP layer."""
+    import torch
+
+    from loongforge_b200.models.registry import build_model, get_model_config
+    from loongforge_b200.parallel import state as ps
+    from tools.convert_checkpoint import name_maps as nm
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(ps.ParallelDims())
+    cfg = get_model_config("tiny-deepseek", mtp_num_layers=1, moe_router_enable_expert_bias=True)
+    mc = {k: v for k, v in build_model(cfg).state_dict().items() if "local_tokens_per_expert" not in k}
+    kw = dict(num_layers=cfg.num_layers, num_heads=cfg.num_attention_heads, num_groups=cfg.num_query_groups,
+              num_experts=cfg.num_moe_experts)
+    hf = nm.mcore_to_hf(mc, nm.FAMILIES["deepseek"], vocab_size=cfg.vocab_size, **kw)
+    for name in ("model.layers.0.self_attn.q_a_proj.weight", "model.layers.0.self_attn.kv_a_proj_with_mqa.weight",
+                 "model.layers.0.self_attn.kv_b_proj.weight", "model.layers.0.self_attn.indexer.wq_b.weight",
+                 "model.layers.0.mlp.gate_proj.weight", "model.layers.1.mlp.gate.e_score_correction_bias",
+                 "model.layers.1.mlp.experts.7.down_proj.weight", "model.layers.1.mlp.shared_experts.up_proj.weight",
+                 "model.layers.2.eh_proj.weight", "model.layers.2.shared_head.norm.weight",
+                 "model.layers.2.shared_head.head.weight", "model.layers.2.self_attn.q_b_proj.weight", "lm_head.weight"):
+        assert name in hf, name
+    back = nm.hf_to_mcore(hf, nm.FAMILIES["deepseek"], padded_vocab=cfg.padded_vocab_size, **kw)
+    assert set(back) == set(mc)
+    assert all(torch.equal(back[k], mc[k]) for k in mc)
+    # tensor-parallel sharding rules of the MLA projections survive a split / merge
+    for key in ("decoder.layers.0.self_attention.linear_q_up_proj.weight",
+                "decoder.layers.0.self_attention.linear_kv_up_proj.weight", "mtp.layers.0.eh_proj.weight",
+                "decoder.layers.1.mlp.shared_experts.linear_fc1.weight"):
+        parts = [nm.shard_tp(key, mc[key], r, 2) for r in range(2)]
+        assert parts[0].shape[0] * 2 == mc[key].shape[0] and torch.equal(nm.merge_tp(key, parts), mc[key])
+
+
+def _ds_bridge(rank, world, tmp, dims_kw, mode):
+    import os
+
+    from loongforge_b200.ckpt.hf_bridge import load_hf_checkpoint_online, save_hf_checkpoint
+    from loongforge_b200.data.synthetic import synthetic_batch_iterator
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel.state import ParallelDims
+    from loongforge_b200.runtime.trainer import TrainConfig, Trainer
+
+    cfg = get_model_config("tiny-deepseek", mtp_num_layers=1, moe_aux_loss_coeff=0.0)
+    cfg.sequence_parallel = dims_kw.get("tp", 1) > 1
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=4, seq_length=64, train_iters=4, lr=1e-3, clip_grad=1.0,
+                     log_interval=1000)
+    tr = Trainer(cfg, tc, ParallelDims(**dims_kw))
+    st = tr.st
+    it = synthetic_batch_iterator(cfg.vocab_size, 64, 1, dp_rank=st.dp_rank, dp_size=st.dp_size, seed=3, pin_memory=False)
+    if mode == "save":
+        for _ in range(2):
+            tr.train_step(it)
+        save_hf_checkpoint(tr, os.path.join(tmp, "hf"), family="deepseek")
+    else:
+        load_hf_checkpoint_online(tr, os.path.join(tmp, "hf"), family="deepseek")
+        for _ in range(2 * 4 // st.dp_size):
+            next(it)
+    m = tr.train_step(it)
+    return m.get("lm loss"), m["grad_norm"]
+
+
+def test_deepseek_online_bridge_across_layouts(tmp_path):
+    from dist_utils import run_distributed
+
+    a = run_distributed(_ds_bridge, 2, str(tmp_path), {"tp": 2}, "save")
+    b = run_distributed(_ds_bridge, 2, str(tmp_path), {"ep": 2}, "load")
+    assert abs(a[0][0] - b[0][0]) < 1e-4 * a[0][0] and abs(a[0][1] - b[0][1]) < 1e-3 * max(1, a[0][1]), (a, b)

@@ -145,7 +145,8 @@ def save_mcore(mc: Dict[str, torch.Tensor], path: str, *, tp: int, pp: int, ep: 
                         key = f"decoder.layers.{local_of[g]}.{m.group(2)}"
                     else:
                         first = k.startswith("embedding.")
-                        last = k.startswith(("decoder.final_layernorm", "output_layer"))
+                        # multi-token-prediction layers live on the stage that computes the loss
+                        last = k.startswith(("decoder.final_layernorm", "output_layer", "mtp."))
                         if (first and p_rank != 0) or (last and p_rank != pp - 1):
                             continue
                         key = k

@@ -29,6 +29,7 @@ class FamilyMap:
     expert_tpl: str = "mlp.experts.{e}."
     router: str = "mlp.gate.weight"
     shared_expert: Optional[str] = None  # e.g. "mlp.shared_experts."
+    mla: bool = False  # DeepSeek-style multi-latent attention (+ optional DSA indexer, router bias, MTP layers)
 
 
 FAMILIES: Dict[str, FamilyMap] = {
@@ -40,6 +41,10 @@ FAMILIES: Dict[str, FamilyMap] = {
     "qwen2.5": FamilyMap("qwen2.5", qkv_bias=True),
     "qwen3": FamilyMap("qwen3", qk_norm=True),
     "qwen3_moe": FamilyMap("qwen3_moe", qk_norm=True, moe=True),
+    # DeepSeek-V2 / V3 / V3.2 and GLM-5.x share one layout: MLA projections, optional lightning indexer, dense-then-MoE
+    # layers with a shared expert and a router bias, multi-token-prediction layers appended after the last layer
+    "deepseek": FamilyMap("deepseek", moe=True, mla=True, shared_expert="mlp.shared_experts."),
+    "glm": FamilyMap("glm", moe=True, mla=True, shared_expert="mlp.shared_experts."),
 }
 
 
@@ -72,9 +77,120 @@ def pad_vocab(w: torch.Tensor, padded: int) -> torch.Tensor:
     return torch.cat([w, w[-1:].expand(padded - w.shape[0], -1)], 0).contiguous()
 
 
+# (Megatron suffix, Hugging Face suffix) inside one MLA layer; entries absent from a checkpoint are skipped
+_MLA_LAYER = [
+    ("input_layernorm.weight", "input_layernorm.weight"),
+    ("self_attention.linear_q_proj.weight", "self_attn.q_proj.weight"),
+    ("self_attention.linear_q_down_proj.weight", "self_attn.q_a_proj.weight"),
+    ("self_attention.q_layernorm.weight", "self_attn.q_a_layernorm.weight"),
+    ("self_attention.linear_q_up_proj.weight", "self_attn.q_b_proj.weight"),
+    ("self_attention.linear_kv_down_proj.weight", "self_attn.kv_a_proj_with_mqa.weight"),
+    ("self_attention.kv_layernorm.weight", "self_attn.kv_a_layernorm.weight"),
+    ("self_attention.linear_kv_up_proj.weight", "self_attn.kv_b_proj.weight"),
+    ("self_attention.linear_proj.weight", "self_attn.o_proj.weight"),
+    ("self_attention.core_attention.indexer.linear_wq_b.weight", "self_attn.indexer.wq_b.weight"),
+    ("self_attention.core_attention.indexer.linear_wk.weight", "self_attn.indexer.wk.weight"),
+    ("self_attention.core_attention.indexer.k_norm.weight", "self_attn.indexer.k_norm.weight"),
+    ("self_attention.core_attention.indexer.k_norm.bias", "self_attn.indexer.k_norm.bias"),
+    ("self_attention.core_attention.indexer.linear_weights_proj.weight", "self_attn.indexer.weights_proj.weight"),
+    ("pre_mlp_layernorm.weight", "post_attention_layernorm.weight"),
+    ("mlp.router.weight", "mlp.gate.weight"),
+    ("mlp.router.expert_bias", "mlp.gate.e_score_correction_bias"),
+]
+_MTP_EXTRA = [("enorm.weight", "enorm.weight"), ("hnorm.weight", "hnorm.weight"), ("eh_proj.weight", "eh_proj.weight"),
+              ("final_layernorm.weight", "shared_head.norm.weight")]
+
+
+def _mla_layer_to_mcore(hf, h: str, m: str, out, fam: FamilyMap, num_experts) -> None:
+    for mk, hk in _MLA_LAYER:
+        if h + hk in hf:
+            out[m + mk] = hf[h + hk]
+    glu = lambda p: torch.cat([hf[p + "gate_proj.weight"], hf[p + "up_proj.weight"]], 0)  # noqa: E731
+    if h + "mlp.gate.weight" in hf:
+        for e in range(num_experts):
+            p = h + fam.expert_tpl.format(e=e)
+            out[m + f"mlp.experts.linear_fc1.weight{e}"] = glu(p)
+            out[m + f"mlp.experts.linear_fc2.weight{e}"] = hf[p + "down_proj.weight"]
+        if fam.shared_expert and h + fam.shared_expert + "gate_proj.weight" in hf:
+            out[m + "mlp.shared_experts.linear_fc1.weight"] = glu(h + fam.shared_expert)
+            out[m + "mlp.shared_experts.linear_fc2.weight"] = hf[h + fam.shared_expert + "down_proj.weight"]
+    else:
+        out[m + "mlp.linear_fc1.weight"] = glu(h + "mlp.")
+        out[m + "mlp.linear_fc2.weight"] = hf[h + "mlp.down_proj.weight"]
+
+
+def _mla_layer_to_hf(mc, m: str, h: str, out, fam: FamilyMap, num_experts) -> None:
+    for mk, hk in _MLA_LAYER:
+        if m + mk in mc:
+            out[h + hk] = mc[m + mk]
+
+    def unglu(w, p):
+        g, u = w.chunk(2, 0)
+        out[p + "gate_proj.weight"], out[p + "up_proj.weight"] = g.contiguous(), u.contiguous()
+
+    if m + "mlp.router.weight" in mc:
+        for e in range(num_experts):
+            p = h + fam.expert_tpl.format(e=e)
+            unglu(mc[m + f"mlp.experts.linear_fc1.weight{e}"], p)
+            out[p + "down_proj.weight"] = mc[m + f"mlp.experts.linear_fc2.weight{e}"]
+        if m + "mlp.shared_experts.linear_fc1.weight" in mc:
+            unglu(mc[m + "mlp.shared_experts.linear_fc1.weight"], h + fam.shared_expert)
+            out[h + fam.shared_expert + "down_proj.weight"] = mc[m + "mlp.shared_experts.linear_fc2.weight"]
+    else:
+        unglu(mc[m + "mlp.linear_fc1.weight"], h + "mlp.")
+        out[h + "mlp.down_proj.weight"] = mc[m + "mlp.linear_fc2.weight"]
+
+
+def _mla_to_mcore(hf, fam, num_layers, padded_vocab, num_experts, tie_embeddings):
+    """Multi-token-prediction layers follow the decoder in the Hugging Face file as layers L, L+1, ... (with their own
+    copies of the embedding and the head, which the Megatron side shares with the main model)."""
+    out: Dict[str, torch.Tensor] = {}
+    emb = hf[fam.hf_prefix + "embed_tokens.weight"]
+    out["embedding.word_embeddings.weight"] = pad_vocab(emb, padded_vocab or emb.shape[0])
+    for i in range(num_layers):
+        _mla_layer_to_mcore(hf, fam.hf_layers.format(i=i), f"decoder.layers.{i}.", out, fam, num_experts)
+    k = 0
+    while fam.hf_layers.format(i=num_layers + k) + "eh_proj.weight" in hf:
+        h, m = fam.hf_layers.format(i=num_layers + k), f"mtp.layers.{k}."
+        for mk, hk in _MTP_EXTRA:
+            out[m + mk] = hf[h + hk]
+        _mla_layer_to_mcore(hf, h, m + "transformer_layer.", out, fam, num_experts)
+        k += 1
+    out["decoder.final_layernorm.weight"] = hf[fam.hf_prefix + "norm.weight"]
+    if not tie_embeddings:
+        head = hf.get("lm_head.weight", emb)
+        out["output_layer.weight"] = pad_vocab(head, padded_vocab or head.shape[0])
+    return out
+
+
+def _mla_to_hf(mc, fam, num_layers, vocab_size, num_experts, tie_embeddings):
+    out: Dict[str, torch.Tensor] = {}
+    strip = lambda w: w[:vocab_size].contiguous() if vocab_size else w  # noqa: E731
+    emb = strip(mc["embedding.word_embeddings.weight"])
+    out[fam.hf_prefix + "embed_tokens.weight"] = emb
+    for i in range(num_layers):
+        _mla_layer_to_hf(mc, f"decoder.layers.{i}.", fam.hf_layers.format(i=i), out, fam, num_experts)
+    head = strip(mc["output_layer.weight"]) if (not tie_embeddings and "output_layer.weight" in mc) else emb
+    k = 0
+    while f"mtp.layers.{k}.eh_proj.weight" in mc:
+        m, h = f"mtp.layers.{k}.", fam.hf_layers.format(i=num_layers + k)
+        for mk, hk in _MTP_EXTRA:
+            out[h + hk] = mc[m + mk]
+        _mla_layer_to_hf(mc, m + "transformer_layer.", h, out, fam, num_experts)
+        # separate copies: the Hugging Face file stores the MTP layer's embedding and head as tensors of their own
+        out[h + "embed_tokens.weight"], out[h + "shared_head.head.weight"] = emb.clone(), head.clone()
+        k += 1
+    out[fam.hf_prefix + "norm.weight"] = mc["decoder.final_layernorm.weight"]
+    if not tie_embeddings and "output_layer.weight" in mc:
+        out["lm_head.weight"] = head
+    return out
+
+
 def hf_to_mcore(hf: Dict[str, torch.Tensor], fam: FamilyMap, *, num_layers: int, num_heads: int, num_groups: int,
                 padded_vocab: Optional[int] = None, num_experts: Optional[int] = None,
                 tie_embeddings: bool = False) -> Dict[str, torch.Tensor]:
+    if fam.mla:
+        return _mla_to_mcore(hf, fam, num_layers, padded_vocab, num_experts, tie_embeddings)
     out: Dict[str, torch.Tensor] = {}
     emb = hf[fam.hf_prefix + "embed_tokens.weight"]
     out["embedding.word_embeddings.weight"] = pad_vocab(emb, padded_vocab or emb.shape[0])
@@ -116,6 +232,8 @@ def hf_to_mcore(hf: Dict[str, torch.Tensor], fam: FamilyMap, *, num_layers: int,
 def mcore_to_hf(mc: Dict[str, torch.Tensor], fam: FamilyMap, *, num_layers: int, num_heads: int, num_groups: int,
                 vocab_size: Optional[int] = None, num_experts: Optional[int] = None,
                 tie_embeddings: bool = False) -> Dict[str, torch.Tensor]:
+    if fam.mla:
+        return _mla_to_hf(mc, fam, num_layers, vocab_size, num_experts, tie_embeddings)
     out: Dict[str, torch.Tensor] = {}
 
     def strip(w):
@@ -157,7 +275,9 @@ def mcore_to_hf(mc: Dict[str, torch.Tensor], fam: FamilyMap, *, num_layers: int,
 # ---- tensor / pipeline / expert sharding of the unsharded Megatron dict -----------------------
 def tp_rule(key: str):
     """(partition_dim, stride) of a Megatron key, or None when replicated."""
-    if key.endswith(("linear_qkv.weight", "linear_qkv.bias", "embedding.word_embeddings.weight", "output_layer.weight")):
+    if key.endswith(("linear_qkv.weight", "linear_qkv.bias", "embedding.word_embeddings.weight", "output_layer.weight",
+                     "self_attention.linear_q_proj.weight", "self_attention.linear_q_up_proj.weight",
+                     "self_attention.linear_kv_up_proj.weight", "eh_proj.weight")):
         return 0, 1
     if key.endswith(("linear_fc1.weight", "linear_fc1.bias")) and ".experts." not in key:
         return 0, 2
