@@ -202,3 +202,78 @@ def test_deepseek_online_bridge_across_layouts(tmp_path):
     a = run_distributed(_ds_bridge, 2, str(tmp_path), {"tp": 2}, "save")
     b = run_distributed(_ds_bridge, 2, str(tmp_path), {"ep": 2}, "load")
     assert abs(a[0][0] - b[0][0]) < 1e-4 * a[0][0] and abs(a[0][1] - b[0][1]) < 1e-3 * max(1, a[0][1]), (a, b)
+
+
+def test_qwen_vl_name_map_roundtrip_and_numerics():
+    """Vision tower + merger + language model of the Qwen2.5-VL layout: names round-trip, and the per-head QKV
+    packing reproduces the fused [q; k; v] projection."""
+    import torch
+
+    from loongforge_b200.models.omni import OmniCombinationModel
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel import state as ps
+    from tools.convert_checkpoint import name_maps as nm
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(ps.ParallelDims())
+    lm = get_model_config("tiny-llama", add_qkv_bias=True, position_embedding_type="mrope", mrope_section=[8, 12, 12])
+    vit = get_model_config("tiny-vit")
+    model = OmniCombinationModel(lm, vit, image_token_id=lm.vocab_size - 1)
+    mc = dict(model.state_dict())
+    kw = dict(vit_layers=vit.num_layers, vit_heads=vit.num_attention_heads, num_layers=lm.num_layers,
+              num_heads=lm.num_attention_heads, num_groups=lm.num_query_groups)
+    for nested in (False, True):
+        hf = nm.vlm_mcore_to_hf(mc, nm.FAMILIES["qwen2.5"], nested=nested, vocab_size=lm.vocab_size, **kw)
+        vp = "model.visual." if nested else "visual."
+        assert vp + "blocks.1.attn.qkv.bias" in hf and vp + "merger.mlp.2.weight" in hf
+        assert ("model.language_model.layers.0.self_attn.q_proj.bias" if nested else "model.layers.0.self_attn.q_proj.bias") in hf
+        back = nm.vlm_hf_to_mcore(hf, nm.FAMILIES["qwen2.5"], padded_vocab=lm.padded_vocab_size, **kw)
+        assert set(back) == set(mc) and all(torch.equal(back[k], mc[k]) for k in mc)
+    # fused HF projection == per-head packed Megatron projection, head by head
+    H, d = vit.num_attention_heads, vit.kv_channels
+    w = hf[vp + "blocks.0.attn.qkv.weight"]
+    x = torch.randn(5, w.shape[1])
+    q, k, v = (x @ w.t()).view(5, 3, H, d).unbind(1)
+    packed = (x @ mc["encoder_model.image_encoder.decoder.layers.0.self_attention.linear_qkv.weight"].t()).view(5, H, 3, d)
+    assert torch.allclose(packed[:, :, 0], q, atol=1e-6) and torch.allclose(packed[:, :, 2], v, atol=1e-6)
+
+
+def test_converter_cli_vlm_roundtrip_with_tp_pp(tmp_path):
+    """HF Qwen2.5-VL layout -> Megatron (TP 2, PP 2; encoder on the first stage) -> HF: bit-identical."""
+    import json
+
+    import torch
+
+    from loongforge_b200.models.omni import OmniCombinationModel
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel import state as ps
+    from tools.convert_checkpoint import convert as C
+    from tools.convert_checkpoint import name_maps as nm
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(ps.ParallelDims())
+    lm = get_model_config("tiny-llama", add_qkv_bias=True, position_embedding_type="mrope", mrope_section=[8, 12, 12])
+    vit = get_model_config("tiny-vit")
+    mc = dict(OmniCombinationModel(lm, vit, image_token_id=lm.vocab_size - 1).state_dict())
+    kw = dict(vit_layers=vit.num_layers, vit_heads=vit.num_attention_heads, num_layers=lm.num_layers,
+              num_heads=lm.num_attention_heads, num_groups=lm.num_query_groups)
+    hf = nm.vlm_mcore_to_hf(mc, nm.FAMILIES["qwen2.5"], vocab_size=lm.vocab_size, **kw)
+    cfg = {"model_type": "qwen2_5_vl", "text_config": {"num_hidden_layers": lm.num_layers, "vocab_size": lm.vocab_size,
+                                                        "num_attention_heads": lm.num_attention_heads,
+                                                        "num_key_value_heads": lm.num_query_groups},
+           "vision_config": {"depth": vit.num_layers, "num_heads": vit.num_attention_heads}}
+    C.save_hf(hf, str(tmp_path / "hf"), cfg)
+    common = ["--model_type_custom", "qwen2_5_vl", "--vit_num_heads", str(vit.num_attention_heads)]
+    C.main(["--load_platform", "huggingface", "--save_platform", "mcore", "--load_ckpt_path", str(tmp_path / "hf"),
+            "--save_ckpt_path", str(tmp_path / "mc"), "--tensor_model_parallel_size", "2",
+            "--pipeline_model_parallel_size", "2"] + common)
+    first = torch.load(tmp_path / "mc" / "release" / "mp_rank_00_000" / "model_optim_rng.pt", weights_only=False)["model"]
+    last = torch.load(tmp_path / "mc" / "release" / "mp_rank_01_001" / "model_optim_rng.pt", weights_only=False)["model"]
+    assert any(k.startswith("encoder_model.image_encoder") for k in first) and not any(k.startswith("encoder_model") for k in last)
+    assert "foundation_model.decoder.layers.0.mlp.linear_fc2.weight" in last and "foundation_model.output_layer.weight" in last
+    C.main(["--load_platform", "mcore", "--save_platform", "huggingface", "--load_ckpt_path", str(tmp_path / "mc"),
+            "--save_ckpt_path", str(tmp_path / "back"), "--num_layers", str(lm.num_layers), "--num_attention_heads",
+            str(lm.num_attention_heads), "--num_query_groups", str(lm.num_query_groups), "--vocab_size",
+            str(lm.vocab_size)] + common)
+    back = C.load_hf(str(tmp_path / "back"))
+    assert set(back) == set(hf) and all(torch.equal(back[k], hf[k]) for k in hf)

@@ -47,6 +47,8 @@ def parse_args(argv=None):
     p.add_argument("--num_attention_heads", type=int, default=None)
     p.add_argument("--num_query_groups", type=int, default=None)
     p.add_argument("--num_experts", type=int, default=None)
+    p.add_argument("--vit_num_layers", type=int, default=None, help="vision tower depth (else vision_config.depth)")
+    p.add_argument("--vit_num_heads", type=int, default=None, help="vision tower heads (else vision_config.num_heads)")
     p.add_argument("--no_load_optim", action="store_true")
     p.add_argument("--no_save_optim", action="store_true")
     p.add_argument("--load_lora_ckpt_path", default=None)
@@ -59,12 +61,13 @@ def _model_dims(args, hf_dir: Optional[str]):
     cfg = {}
     if hf_dir and os.path.isfile(os.path.join(hf_dir, "config.json")):
         cfg = json.load(open(os.path.join(hf_dir, "config.json")))
-    L = args.num_layers or cfg.get("num_hidden_layers")
-    H = args.num_attention_heads or cfg.get("num_attention_heads")
-    G = args.num_query_groups or cfg.get("num_key_value_heads") or H
-    V = args.vocab_size or cfg.get("vocab_size")
-    E = args.num_experts or cfg.get("num_experts") or cfg.get("n_routed_experts")
-    tie = bool(cfg.get("tie_word_embeddings", False))
+    tc = cfg.get("text_config") or cfg  # vision-language configs nest the language model's fields
+    L = args.num_layers or tc.get("num_hidden_layers")
+    H = args.num_attention_heads or tc.get("num_attention_heads")
+    G = args.num_query_groups or tc.get("num_key_value_heads") or H
+    V = args.vocab_size or tc.get("vocab_size")
+    E = args.num_experts or tc.get("num_experts") or tc.get("n_routed_experts")
+    tie = bool(tc.get("tie_word_embeddings", cfg.get("tie_word_embeddings", False)))
     assert L and H, "number of layers / heads unknown: pass --num_layers/--num_attention_heads or provide config.json"
     return L, H, G, V, E, tie, cfg
 
@@ -119,7 +122,9 @@ def layer_split(L: int, pp: int, custom: Optional[str]) -> List[List[int]]:
     return out
 
 
-_LAYER = re.compile(r"^decoder\.layers\.(\d+)\.(.*)$")
+# the language model's layers, optionally under the prefix of a vision-language composition (the encoder's own
+# "encoder_model...decoder.layers" are never pipelined and do not match)
+_LAYER = re.compile(r"^((?:foundation_model\.)?)decoder\.layers\.(\d+)\.(.*)$")
 _EXPERT = re.compile(r"\.experts\.linear_fc[12]\.weight(\d+)$")
 
 
@@ -139,14 +144,16 @@ def save_mcore(mc: Dict[str, torch.Tensor], path: str, *, tp: int, pp: int, ep: 
                 for k, w in mc.items():
                     m = _LAYER.match(k)
                     if m:
-                        g = int(m.group(1))
+                        g = int(m.group(2))
                         if g not in local_of:
                             continue
-                        key = f"decoder.layers.{local_of[g]}.{m.group(2)}"
+                        key = f"{m.group(1)}decoder.layers.{local_of[g]}.{m.group(3)}"
                     else:
-                        first = k.startswith("embedding.")
+                        bare = k[len("foundation_model."):] if k.startswith("foundation_model.") else k
+                        # the vision encoder and projector sit on the first stage with the embedding
+                        first = bare.startswith(("embedding.", "encoder_model."))
                         # multi-token-prediction layers live on the stage that computes the loss
-                        last = k.startswith(("decoder.final_layernorm", "output_layer", "mtp."))
+                        last = bare.startswith(("decoder.final_layernorm", "output_layer", "mtp."))
                         if (first and p_rank != 0) or (last and p_rank != pp - 1):
                             continue
                         key = k
@@ -192,7 +199,7 @@ def load_mcore(path: str, *, num_layers: int, custom_layers: Optional[str]) -> D
         e_local = None
         for k, w in sd.items():
             m = _LAYER.match(k)
-            key = f"decoder.layers.{split[p_rank][int(m.group(1))]}.{m.group(2)}" if m else k
+            key = f"{m.group(1)}decoder.layers.{split[p_rank][int(m.group(2))]}.{m.group(3)}" if m else k
             em = _EXPERT.search(key)
             if em:
                 if e_local is None:
@@ -213,17 +220,28 @@ def merge_lora_into(mc: Dict[str, torch.Tensor], lora_sd: Dict[str, torch.Tensor
 
 def main(argv=None):
     a = parse_args(argv)
-    fam = nm.FAMILIES[a.model_type_custom]
+    vlm = a.model_type_custom in nm.VLM_FAMILIES
+    fam = nm.FAMILIES[nm.VLM_FAMILIES[a.model_type_custom] if vlm else a.model_type_custom]
     dt = getattr(torch, a.torch_dtype) if a.torch_dtype else None
     hf_dir = a.load_ckpt_path if a.load_platform == "huggingface" else None
     L, H, G, V, E, tie, hf_cfg = _model_dims(a, hf_dir)
     if a.load_platform == "huggingface":
         hf = load_hf(a.load_ckpt_path)
         mult = a.make_vocab_size_divisible_by * a.tensor_model_parallel_size
-        V = V or hf[fam.hf_prefix + "embed_tokens.weight"].shape[0]
-        padded = -(-V // mult) * mult
-        mc = nm.hf_to_mcore(hf, fam, num_layers=L, num_heads=H, num_groups=G, padded_vocab=padded, num_experts=E,
-                            tie_embeddings=tie)
+        if not vlm:
+            V = V or hf[fam.hf_prefix + "embed_tokens.weight"].shape[0]
+            padded = -(-V // mult) * mult
+        if vlm:
+            vc = hf_cfg.get("vision_config", {})
+            vit = dict(vit_layers=a.vit_num_layers or vc.get("depth"), vit_heads=a.vit_num_heads or vc.get("num_heads"))
+            lp, _ = nm._vlm_prefixes(hf)
+            V = a.vocab_size or hf_cfg.get("vocab_size") or hf[lp + "embed_tokens.weight"].shape[0]
+            padded = -(-V // mult) * mult
+            mc = nm.vlm_hf_to_mcore(hf, fam, num_layers=L, num_heads=H, num_groups=G, padded_vocab=padded,
+                                    num_experts=E, tie_embeddings=tie, **vit)
+        else:
+            mc = nm.hf_to_mcore(hf, fam, num_layers=L, num_heads=H, num_groups=G, padded_vocab=padded, num_experts=E,
+                                tie_embeddings=tie)
     else:
         mc = load_mcore(a.load_ckpt_path, num_layers=L, custom_layers=a.custom_pipeline_layers)
     if a.load_lora_ckpt_path:
@@ -239,8 +257,15 @@ def main(argv=None):
                    ep=a.expert_parallel_size, num_layers=L, num_experts=E, custom_layers=a.custom_pipeline_layers,
                    args_dump=dump)
     else:
-        hf_out = nm.mcore_to_hf(mc, fam, num_layers=L, num_heads=H, num_groups=G, vocab_size=V, num_experts=E,
-                                tie_embeddings=tie)
+        if vlm:
+            n_vit = 1 + max(int(k.split("image_encoder.decoder.layers.")[1].split(".")[0]) for k in mc
+                            if "image_encoder.decoder.layers." in k)
+            hf_out = nm.vlm_mcore_to_hf(mc, fam, vit_layers=a.vit_num_layers or n_vit, vit_heads=a.vit_num_heads,
+                                        num_layers=L, num_heads=H, num_groups=G, vocab_size=V, num_experts=E,
+                                        tie_embeddings=tie)
+        else:
+            hf_out = nm.mcore_to_hf(mc, fam, num_layers=L, num_heads=H, num_groups=G, vocab_size=V, num_experts=E,
+                                    tie_embeddings=tie)
         save_hf(hf_out, a.save_ckpt_path, hf_cfg or None)
     print(f"converted {len(mc)} tensors: {a.load_platform} -> {a.save_platform} at {a.save_ckpt_path}")
     return 0

@@ -48,6 +48,10 @@ FAMILIES: Dict[str, FamilyMap] = {
 }
 
 
+# vision-language compositions: name -> family of their language model
+VLM_FAMILIES: Dict[str, str] = {"qwen2_vl": "qwen2", "qwen2_5_vl": "qwen2.5", "qwen2.5_vl": "qwen2.5"}
+
+
 def pack_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, num_groups: int) -> torch.Tensor:
     """[nq*d, ...], [ng*d, ...], [ng*d, ...] -> Megatron packed [(nq + 2 ng) * d, ...] per-group order."""
     tail = q.shape[1:]
@@ -280,7 +284,7 @@ def tp_rule(key: str):
                      "self_attention.linear_kv_up_proj.weight", "eh_proj.weight")):
         return 0, 1
     if key.endswith(("linear_fc1.weight", "linear_fc1.bias")) and ".experts." not in key:
-        return 0, 2
+        return 0, (1 if "image_projector." in key else 2)  # the projector's first linear is not gated
     if key.endswith(("linear_proj.weight", "linear_fc2.weight")) and ".experts." not in key:
         return 1, 1
     return None
@@ -305,3 +309,88 @@ def merge_tp(key: str, shards: List[torch.Tensor]) -> torch.Tensor:
         return torch.cat(shards, dim)
     blocks = [s.chunk(stride, dim) for s in shards]
     return torch.cat([torch.cat([b[j] for b in blocks], dim) for j in range(stride)], dim)
+
+
+# ---- vision-language models: Qwen2-VL / Qwen2.5-VL vision tower + merger ---------------------------------------------
+def _vit_pack_qkv(w: torch.Tensor, num_heads: int) -> torch.Tensor:
+    """HF fused ``[q_all; k_all; v_all]`` rows -> Megatron per-head ``[q_h, k_h, v_h]`` rows."""
+    tail = w.shape[1:]
+    d = w.shape[0] // (3 * num_heads)
+    return w.reshape(3, num_heads, d, *tail).transpose(0, 1).reshape(-1, *tail).contiguous()
+
+
+def _vit_unpack_qkv(w: torch.Tensor, num_heads: int) -> torch.Tensor:
+    tail = w.shape[1:]
+    d = w.shape[0] // (3 * num_heads)
+    return w.reshape(num_heads, 3, d, *tail).transpose(0, 1).reshape(-1, *tail).contiguous()
+
+
+_VIT_LAYER = [  # (Megatron suffix, HF suffix) inside one vision block
+    ("self_attention.linear_qkv.layer_norm_weight", "norm1.weight"),
+    ("self_attention.linear_proj.weight", "attn.proj.weight"), ("self_attention.linear_proj.bias", "attn.proj.bias"),
+    ("mlp.linear_fc1.layer_norm_weight", "norm2.weight"),
+    ("mlp.linear_fc2.weight", "mlp.down_proj.weight"), ("mlp.linear_fc2.bias", "mlp.down_proj.bias"),
+]
+_VIT_TOP = [("image_encoder.patch_embed.proj.weight", "patch_embed.proj.weight"),
+            ("image_projector.layernorm.weight", "merger.ln_q.weight"),
+            ("image_projector.linear_fc1.weight", "merger.mlp.0.weight"), ("image_projector.linear_fc1.bias", "merger.mlp.0.bias"),
+            ("image_projector.linear_fc2.weight", "merger.mlp.2.weight"), ("image_projector.linear_fc2.bias", "merger.mlp.2.bias")]
+
+
+def qwen_vision_to_mcore(hf: Dict[str, torch.Tensor], prefix: str, num_layers: int, num_heads: int) -> Dict[str, torch.Tensor]:
+    """``visual.*`` tensors -> ``image_encoder.* / image_projector.*`` (SwiGLU FC1 = [gate; up], packed QKV per head)."""
+    out = {mk: hf[prefix + hk] for mk, hk in _VIT_TOP}
+    for i in range(num_layers):
+        h, m = f"{prefix}blocks.{i}.", f"image_encoder.decoder.layers.{i}."
+        for mk, hk in _VIT_LAYER:
+            out[m + mk] = hf[h + hk]
+        out[m + "self_attention.linear_qkv.weight"] = _vit_pack_qkv(hf[h + "attn.qkv.weight"], num_heads)
+        out[m + "self_attention.linear_qkv.bias"] = _vit_pack_qkv(hf[h + "attn.qkv.bias"], num_heads)
+        out[m + "mlp.linear_fc1.weight"] = torch.cat([hf[h + "mlp.gate_proj.weight"], hf[h + "mlp.up_proj.weight"]], 0)
+        out[m + "mlp.linear_fc1.bias"] = torch.cat([hf[h + "mlp.gate_proj.bias"], hf[h + "mlp.up_proj.bias"]], 0)
+    return out
+
+
+def qwen_vision_to_hf(mc: Dict[str, torch.Tensor], prefix: str, num_layers: int, num_heads: int) -> Dict[str, torch.Tensor]:
+    out = {prefix + hk: mc[mk] for mk, hk in _VIT_TOP}
+    for i in range(num_layers):
+        h, m = f"{prefix}blocks.{i}.", f"image_encoder.decoder.layers.{i}."
+        for mk, hk in _VIT_LAYER:
+            out[h + hk] = mc[m + mk]
+        out[h + "attn.qkv.weight"] = _vit_unpack_qkv(mc[m + "self_attention.linear_qkv.weight"], num_heads)
+        out[h + "attn.qkv.bias"] = _vit_unpack_qkv(mc[m + "self_attention.linear_qkv.bias"], num_heads)
+        for name in ("weight", "bias"):
+            g, u = mc[m + f"mlp.linear_fc1.{name}"].chunk(2, 0)
+            out[h + f"mlp.gate_proj.{name}"], out[h + f"mlp.up_proj.{name}"] = g.contiguous(), u.contiguous()
+    return out
+
+
+def _vlm_prefixes(hf: Dict[str, torch.Tensor]):
+    """(language prefix, vision prefix) of the two Hugging Face layouts in circulation."""
+    if any(k.startswith("model.language_model.") for k in hf):
+        return "model.language_model.", "model.visual."
+    return "model.", "visual."
+
+
+def vlm_hf_to_mcore(hf: Dict[str, torch.Tensor], fam: FamilyMap, *, vit_layers: int, vit_heads: int,
+                    **lm_kw) -> Dict[str, torch.Tensor]:
+    """Whole vision-language checkpoint -> ``foundation_model.* / encoder_model.image_encoder.* /
+    encoder_model.image_projector.*`` (the composition of models/omni.py)."""
+    lp, vp = _vlm_prefixes(hf)
+    lm_fam = dataclasses.replace(fam, hf_prefix=lp, hf_layers=lp + "layers.{i}.")
+    lm = hf_to_mcore({k: v for k, v in hf.items() if not k.startswith(vp)}, lm_fam, **lm_kw)
+    vis = qwen_vision_to_mcore(hf, vp, vit_layers, vit_heads)
+    out = {"foundation_model." + k: v for k, v in lm.items()}
+    out.update({"encoder_model." + k: v for k, v in vis.items()})
+    return out
+
+
+def vlm_mcore_to_hf(mc: Dict[str, torch.Tensor], fam: FamilyMap, *, vit_layers: int, vit_heads: int,
+                    nested: bool = False, **lm_kw) -> Dict[str, torch.Tensor]:
+    lp, vp = ("model.language_model.", "model.visual.") if nested else ("model.", "visual.")
+    lm_fam = dataclasses.replace(fam, hf_prefix=lp, hf_layers=lp + "layers.{i}.")
+    out = mcore_to_hf({k[len("foundation_model."):]: v for k, v in mc.items() if k.startswith("foundation_model.")},
+                      lm_fam, **lm_kw)
+    out.update(qwen_vision_to_hf({k[len("encoder_model."):]: v for k, v in mc.items() if k.startswith("encoder_model.")},
+                                 vp, vit_layers, vit_heads))
+    return out
