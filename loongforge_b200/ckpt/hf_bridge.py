@@ -32,10 +32,19 @@ def load_hf_checkpoint_online(trainer, hf_dir: str, family: str = "llama3") -> i
     cfg = trainer.mcfg
     st = trainer.st
     hf = load_hf(hf_dir)
-    mc = nm.hf_to_mcore(hf, nm.FAMILIES[family], num_layers=cfg.num_layers, num_heads=cfg.num_attention_heads,
-                        num_groups=cfg.num_query_groups, padded_vocab=cfg.padded_vocab_size,
-                        num_experts=cfg.num_moe_experts,
-                        tie_embeddings=not cfg.untie_embeddings_and_output_weights)
+    lm_kw = dict(num_layers=cfg.num_layers, num_heads=cfg.num_attention_heads, num_groups=cfg.num_query_groups,
+                 padded_vocab=cfg.padded_vocab_size, num_experts=cfg.num_moe_experts,
+                 tie_embeddings=not cfg.untie_embeddings_and_output_weights)
+    enc_mc: Dict[str, torch.Tensor] = {}
+    if family in nm.VLM_FAMILIES:
+        # vision tower + merger + language model in one Hugging Face checkpoint
+        vit = trainer.vit_cfg
+        both = nm.vlm_hf_to_mcore(hf, nm.FAMILIES[nm.VLM_FAMILIES[family]], vit_layers=vit.num_layers,
+                                  vit_heads=vit.num_attention_heads, **lm_kw)
+        mc = {k[len("foundation_model."):]: v for k, v in both.items() if k.startswith("foundation_model.")}
+        enc_mc = {k[len("encoder_model."):]: v for k, v in both.items() if k.startswith("encoder_model.")}
+    else:
+        mc = nm.hf_to_mcore(hf, nm.FAMILIES[family], **lm_kw)
     e_local = (cfg.num_moe_experts // st.dims.ep) if cfg.num_moe_experts else 0
     n = 0
     for chunk in trainer.models:
@@ -70,6 +79,16 @@ def load_hf_checkpoint_online(trainer, hf_dir: str, family: str = "llama3") -> i
             for k, v in load.items():
                 own[k].copy_(v)
         n += len(load)
+        enc = getattr(mod, "encoder_model", None)
+        if enc is not None and enc_mc:
+            e_rank, e_tp = _encoder_tp(trainer)
+            params = dict(enc.named_parameters())
+            with torch.no_grad():
+                for k, t in enc.state_dict().items():
+                    if k not in enc_mc:
+                        raise KeyError(f"HF checkpoint does not provide the vision parameter {k}")
+                    t.copy_(_shard_like(params.get(k), enc_mc[k], e_rank, e_tp).to(t.dtype))
+                    n += 1
     trainer.optimizer.reload_model_params()
     return n
 
@@ -107,6 +126,29 @@ def hf_config_from_model(cfg, family: str) -> dict:
     return out
 
 
+def _shard_like(p, full: torch.Tensor, rank: int, tp: int) -> torch.Tensor:
+    """This rank's piece of `full` according to the sharding the parameter itself declares (partition dim and
+    stride set by the tensor-parallel layers); replicated parameters take the whole tensor."""
+    dim = getattr(p, "partition_dim", -1) if p is not None else -1
+    if tp == 1 or dim < 0 or not getattr(p, "tensor_model_parallel", False) or getattr(p, "tp_shards", tp) == 1:
+        return full
+    stride = getattr(p, "partition_stride", 1)
+    if stride == 1:
+        return full.chunk(tp, dim)[rank].contiguous()
+    return torch.cat([b.chunk(tp, dim)[rank] for b in full.chunk(stride, dim)], dim).contiguous()
+
+
+def _encoder_tp(trainer):
+    """(rank, size) of the vision encoder's own tensor-parallel group."""
+    from ..models.omni import ENCODER_STATE
+    from ..parallel import state as ps
+
+    if ENCODER_STATE in ps._STATES:
+        est = ps.get_state(ENCODER_STATE)
+        return est.tp_rank, est.dims.tp
+    return trainer.st.tp_rank, trainer.st.dims.tp
+
+
 def save_hf_checkpoint(trainer, out_dir: str, family: str = "llama3", hf_config: Optional[dict] = None) -> None:
     """Gather the model to rank 0 (TP shards merged, pipeline stages concatenated) and write safetensors."""
     from tools.convert_checkpoint.convert import save_hf
@@ -115,6 +157,7 @@ def save_hf_checkpoint(trainer, out_dir: str, family: str = "llama3", hf_config:
     cfg, st = trainer.mcfg, trainer.st
     e_local = (cfg.num_moe_experts // st.dims.ep) if cfg.num_moe_experts else 0
     local: Dict[str, torch.Tensor] = {}
+    enc_meta: Dict[str, tuple] = {}  # encoder tensors sharded over TP: key -> (dim, stride), from the parameters
     for chunk in trainer.models:
         lm = getattr(chunk.module, "foundation_model", chunk.module)
         numbers = lm.decoder.layer_numbers
@@ -125,6 +168,20 @@ def save_hf_checkpoint(trainer, out_dir: str, family: str = "llama3", hf_config:
             if em:
                 key = key[: em.start(1)] + str(int(em.group(1)) + st.ep_rank * e_local)
             local[key] = v.detach().cpu()
+        enc = getattr(chunk.module, "encoder_model", None)
+        if enc is not None and family in nm.VLM_FAMILIES and getattr(chunk.module, "pre_process", True):
+            e_rank, e_tp = _encoder_tp(trainer)
+            if e_tp not in (1, st.dims.tp):
+                raise NotImplementedError("the encoder's TP degree must be 1 or the decoder's for the HF export")
+            params = dict(enc.named_parameters())
+            for k, v in enc.state_dict().items():
+                p_ = params.get(k)
+                sharded = (e_tp > 1 and p_ is not None and getattr(p_, "tensor_model_parallel", False)
+                           and getattr(p_, "partition_dim", -1) >= 0 and getattr(p_, "tp_shards", e_tp) > 1)
+                if sharded:
+                    enc_meta["encoder_model." + k] = (p_.partition_dim, getattr(p_, "partition_stride", 1))
+                if sharded or st.tp_rank == 0:  # replicated tensors: one copy is enough
+                    local["encoder_model." + k] = v.detach().cpu()
     world = dist.get_world_size() if dist.is_initialized() else 1
     if world > 1:
         payload = (st.tp_rank, st.rank_in("dp_cp"), st.ep_rank, local) if st.rank_in("dp") == 0 or st.dims.ep > 1 else None
@@ -140,12 +197,38 @@ def save_hf_checkpoint(trainer, out_dir: str, family: str = "llama3", hf_config:
             t_rank, _, _, sd = item
             for k, v in sd.items():
                 pieces.setdefault(k, {}).setdefault(t_rank, v)
-        full = {k: nm.merge_tp(k, [v[t] for t in sorted(v)]) for k, v in pieces.items()}
+        def merge(k, shards):
+            if not k.startswith("encoder_model."):
+                return nm.merge_tp(k, shards)
+            if k not in enc_meta or len(shards) == 1:
+                return shards[0]
+            dim, stride = enc_meta[k]
+            if stride == 1:
+                return torch.cat(shards, dim)
+            blocks = [s_.chunk(stride, dim) for s_ in shards]
+            return torch.cat([torch.cat([b[j] for b in blocks], dim) for j in range(stride)], dim)
+
+        full = {k: merge(k, [v[t] for t in sorted(v)]) for k, v in pieces.items()}
     else:
         full = local
-    hf = nm.mcore_to_hf(full, nm.FAMILIES[family], num_layers=cfg.num_layers, num_heads=cfg.num_attention_heads,
-                        num_groups=cfg.num_query_groups, vocab_size=cfg.vocab_size, num_experts=cfg.num_moe_experts,
-                        tie_embeddings=not cfg.untie_embeddings_and_output_weights)
+    out_kw = dict(num_layers=cfg.num_layers, num_heads=cfg.num_attention_heads, num_groups=cfg.num_query_groups,
+                  vocab_size=cfg.vocab_size, num_experts=cfg.num_moe_experts,
+                  tie_embeddings=not cfg.untie_embeddings_and_output_weights)
+    if family in nm.VLM_FAMILIES:
+        vit = trainer.vit_cfg
+        lm_family = nm.VLM_FAMILIES[family]
+        both = {("foundation_model." + k if not k.startswith("encoder_model.") else k): v for k, v in full.items()}
+        hf = nm.vlm_mcore_to_hf(both, nm.FAMILIES[lm_family], vit_layers=vit.num_layers,
+                                vit_heads=vit.num_attention_heads, **out_kw)
+        if hf_config is None:
+            hf_config = {"model_type": family, "architectures": ["Qwen2_5_VLForConditionalGeneration"],
+                         "text_config": hf_config_from_model(cfg, lm_family),
+                         "vision_config": {"depth": vit.num_layers, "num_heads": vit.num_attention_heads,
+                                           "hidden_size": vit.hidden_size, "patch_size": vit.patch_size,
+                                           "spatial_merge_size": vit.spatial_merge_size,
+                                           "temporal_patch_size": vit.temporal_patch_size}}
+    else:
+        hf = nm.mcore_to_hf(full, nm.FAMILIES[family], **out_kw)
     save_hf(hf, out_dir, hf_config or hf_config_from_model(cfg, family))
     if world > 1:
         dist.barrier()

@@ -102,7 +102,9 @@ def _truthy(v) -> bool:
 
 def _hf_family(family: str, cfg) -> str:
     """Key of the Hugging Face name map (tools/convert_checkpoint/name_maps.py) for a model family."""
-    from tools.convert_checkpoint.name_maps import FAMILIES
+    from tools.convert_checkpoint.name_maps import FAMILIES, VLM_FAMILIES
+    if family in VLM_FAMILIES:
+        return family
     if family == "qwen3" and cfg.num_moe_experts:
         return "qwen3_moe"
     if family in FAMILIES:

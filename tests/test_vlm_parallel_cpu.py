@@ -87,3 +87,60 @@ def test_vlm_checkpoints_reshard(save, load, tmp_path):
     ga = [x for x in a if x[0] is not None][-1]
     gb = [x for x in b if x[0] is not None][-1]
     assert abs(ga[0] - gb[0]) < 1e-4 * abs(ga[0]) and abs(ga[1] - gb[1]) < 1e-3 * max(1, ga[1]), (ga, gb)
+
+
+def _hf_worker(rank, world, tmp, dims_kw, vlm_kw, mode):
+    import os
+
+    from loongforge_b200.ckpt.hf_bridge import load_hf_checkpoint_online, save_hf_checkpoint
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel.state import ParallelDims
+    from loongforge_b200.runtime.trainer import TrainConfig
+    from loongforge_b200.runtime.vlm import VLMTrainer, synthetic_vlm_iterator
+
+    lm = get_model_config("tiny-llama", add_qkv_bias=True, position_embedding_type="mrope", mrope_section=[8, 12, 12])
+    if dims_kw.get("tp", 1) > 1:
+        lm.sequence_parallel = True
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=4, seq_length=128, train_iters=4, lr=1e-3, clip_grad=1.0,
+                     log_interval=1000)
+    tr = VLMTrainer(lm, tc, ParallelDims(**dims_kw), vit_cfg=get_model_config("tiny-vit"), images_per_sample=2,
+                    image_size=112, **vlm_kw)
+    st = tr.st
+    it = synthetic_vlm_iterator(lm.vocab_size, 128, images_per_sample=2, image_size=112, pin_memory=False,
+                                dp_rank=st.dp_rank, dp_size=st.dp_size, seed=9)
+    if mode == "save":
+        for _ in range(2):
+            tr.train_step(it)
+        save_hf_checkpoint(tr, os.path.join(tmp, "hf"), family="qwen2_5_vl")
+    else:
+        load_hf_checkpoint_online(tr, os.path.join(tmp, "hf"), family="qwen2_5_vl")
+        for _ in range(2 * 4 // st.dp_size):
+            next(it)
+    m = tr.train_step(it)
+    return m.get("lm loss"), m["grad_norm"]
+
+
+def test_vlm_hugging_face_export_and_online_load_across_layouts(tmp_path):
+    """Trained VLM (decoder TP 2, encoder TP 1) -> Hugging Face Qwen2.5-VL layout -> loaded online under PP 2 and
+    under TP 2 with the encoder sharded as well: the next step is the one the exporting run takes."""
+    import os
+
+    a = run_distributed(_hf_worker, 2, str(tmp_path), {"tp": 2}, {}, "save")
+    assert os.path.isfile(tmp_path / "hf" / "config.json")
+    ga = [x for x in a if x[0] is not None][-1]
+    for dims, kw in (({"pp": 2}, {}), ({"tp": 2}, {"encoder_tp": 2})):
+        b = run_distributed(_hf_worker, 2, str(tmp_path), dims, kw, "load")
+        gb = [x for x in b if x[0] is not None][-1]
+        assert abs(ga[0] - gb[0]) < 1e-4 * abs(ga[0]) and abs(ga[1] - gb[1]) < 1e-3 * max(1, ga[1]), (ga, gb)
+    # export again from a run whose encoder is sharded too: the files must hold the same tensors
+    import shutil
+
+    from tools.convert_checkpoint.convert import load_hf
+    first = load_hf(str(tmp_path / "hf"))
+    shutil.rmtree(tmp_path / "hf")
+    c = run_distributed(_hf_worker, 2, str(tmp_path), {"tp": 2}, {"encoder_tp": 2}, "save")
+    second = load_hf(str(tmp_path / "hf"))
+    assert set(first) == set(second)
+    import torch
+    worst = max(float((first[k].float() - second[k].float()).abs().max()) for k in first)
+    assert worst < 2e-4, worst  # two independent training runs in different layouts: summation order differs
