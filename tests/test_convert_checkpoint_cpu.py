@@ -277,3 +277,49 @@ def test_converter_cli_vlm_roundtrip_with_tp_pp(tmp_path):
             str(lm.vocab_size)] + common)
     back = C.load_hf(str(tmp_path / "back"))
     assert set(back) == set(hf) and all(torch.equal(back[k], hf[k]) for k in hf)
+
+
+def _dist_ckpt_worker(rank, world, tmp, dims_kw, mode):
+    import os
+
+    from loongforge_b200.ckpt.hf_bridge import save_hf_checkpoint
+    from loongforge_b200.data.synthetic import synthetic_batch_iterator
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel.state import ParallelDims
+    from loongforge_b200.runtime.trainer import TrainConfig, Trainer
+
+    cfg = get_model_config("tiny-llama")
+    cfg.sequence_parallel = dims_kw.get("tp", 1) > 1
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=4, seq_length=64, train_iters=4, lr=1e-3, log_interval=1000)
+    tr = Trainer(cfg, tc, ParallelDims(**dims_kw))
+    it = synthetic_batch_iterator(cfg.vocab_size, 64, 1, seed=3, pin_memory=False)
+    if mode == "save":
+        for _ in range(2):
+            tr.train_step(it)
+        tr.save_checkpoint(os.path.join(tmp, "ck"))
+        save_hf_checkpoint(tr, os.path.join(tmp, "hf_online"), family="llama3")
+    else:
+        tr.load_checkpoint(os.path.join(tmp, "ck2"), load_optim=False, load_rng=False)
+        for _ in range(8):
+            next(it)
+    return tr.train_step(it).get("lm loss")
+
+
+def test_offline_dist_checkpoint_to_hf_and_back(tmp_path):
+    """torch_dist checkpoint written under TP 2 -> HF files offline (equal to the online export) -> weights-only
+    torch_dist checkpoint offline -> loaded under PP 2: the next loss is the one of the run that saved."""
+    import torch
+
+    from dist_utils import run_distributed
+    from tools.convert_checkpoint.convert import load_hf
+    from tools.dist_checkpoint import convert_dist_checkpoint as T
+
+    a = run_distributed(_dist_ckpt_worker, 2, str(tmp_path), {"tp": 2}, "save")
+    assert T.main(["--to", "hf", "--load", str(tmp_path / "ck"), "--save", str(tmp_path / "hf"), "--family", "llama3"]) == 0
+    off, on = load_hf(str(tmp_path / "hf")), load_hf(str(tmp_path / "hf_online"))
+    assert set(off) == set(on) and all(torch.equal(off[k], on[k]) for k in on)
+    assert (tmp_path / "hf" / "config.json").is_file()
+    assert T.main(["--to", "dist", "--load", str(tmp_path / "hf"), "--save", str(tmp_path / "ck2"), "--family", "llama3",
+                   "--model-name", "tiny-llama"]) == 0
+    b = run_distributed(_dist_ckpt_worker, 2, str(tmp_path), {"pp": 2}, "load")
+    assert abs(a[0] - b[1]) < 1e-5 * a[0], (a, b)
