@@ -1,0 +1,22 @@
+#!/bin/bash
+# Llama-2-7B pretraining, DP8 with the distributed optimizer
+set -euo pipefail
+REPO=$(cd "$(dirname "$0")/../.." && pwd)
+GPUS=${GPUS:-8}
+CKPT=${CKPT:-$REPO/outputs/llama2_7b}
+DATA_PATH=${DATA_PATH:-}
+export PYTORCH_CUDA_ALLOC_CONF=expandable_segments:True
+DATA_ARGS=(--mock-data)
+[ -n "$DATA_PATH" ] && DATA_ARGS=(--data-path "$DATA_PATH" --split 99,1,0)
+
+cd "$REPO"
+python -m torch.distributed.run --nnodes=1 --nproc-per-node "$GPUS" --master-addr 127.0.0.1 --master-port 29500 \
+  -m loongforge_b200.train \
+  --model-name llama2-7b \
+  --use-distributed-optimizer --overlap-grad-reduce \
+  --micro-batch-size 1 --global-batch-size 256 --seq-length 4096 \
+  --bf16 --lr 3e-4 --min-lr 3e-5 --lr-decay-style cosine --lr-warmup-fraction 0.01 --weight-decay 0.1 \
+  --adam-beta1 0.9 --adam-beta2 0.95 --clip-grad 1.0 \
+  --train-iters 5000 --log-interval 10 --log-throughput \
+  --save "$CKPT" --save-interval 500 --ckpt-format torch_dist \
+  "${DATA_ARGS[@]}"

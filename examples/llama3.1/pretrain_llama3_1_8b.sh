@@ -1,0 +1,24 @@
+#!/bin/bash
+# Llama-3.1-8B long-context pretraining, TP2 + SP, CP2 (ring attention)
+set -euo pipefail
+REPO=$(cd "$(dirname "$0")/../.." && pwd)
+GPUS=${GPUS:-8}
+CKPT=${CKPT:-$REPO/outputs/llama3_1_8b}
+DATA_PATH=${DATA_PATH:-}
+export PYTORCH_CUDA_ALLOC_CONF=expandable_segments:True
+DATA_ARGS=(--mock-data)
+[ -n "$DATA_PATH" ] && DATA_ARGS=(--data-path "$DATA_PATH" --split 99,1,0)
+
+cd "$REPO"
+python -m torch.distributed.run --nnodes=1 --nproc-per-node "$GPUS" --master-addr 127.0.0.1 --master-port 29500 \
+  -m loongforge_b200.train \
+  --model-name llama3.1-8b \
+  --tensor-model-parallel-size 2 --sequence-parallel \
+  --context-parallel-size 2 \
+  --use-distributed-optimizer --overlap-grad-reduce \
+  --micro-batch-size 1 --global-batch-size 32 --seq-length 32768 \
+  --bf16 --lr 3e-4 --min-lr 3e-5 --lr-decay-style cosine --lr-warmup-fraction 0.01 --weight-decay 0.1 \
+  --adam-beta1 0.9 --adam-beta2 0.95 --clip-grad 1.0 \
+  --train-iters 5000 --log-interval 10 --log-throughput \
+  --save "$CKPT" --save-interval 500 --ckpt-format torch_dist \
+  "${DATA_ARGS[@]}"
