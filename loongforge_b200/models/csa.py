@@ -142,9 +142,6 @@ class CompressedSparseAttention(nn.Module):
     def __init__(self, cfg: TransformerConfig, key: str, layer_number: int, *, device=None, parallel_state=None):
         super().__init__()
         st = ps.get_state(parallel_state)
-        if st.dims.cp > 1:
-            # window and compressed entries of a query reach into the previous rank's tokens
-            raise NotImplementedError("compressed sparse attention does not support context parallelism")
         tp = st.dims.tp
         self.cfg = cfg
         self.ratio = (cfg.csa_compress_ratios or [0] * (layer_number + 1))[layer_number]
@@ -198,6 +195,20 @@ class CompressedSparseAttention(nn.Module):
         if st.dims.tp > 1:
             x = M.gather_from_sequence_parallel_region(x, st.group("tp"), True) if cfg.sequence_parallel \
                 else M.copy_to_tensor_model_parallel_region(x, st.group("tp"))
+        own = None
+        if st.dims.cp > 1:
+            # The window and the compressed entries of a query reach into tokens of other context-parallel ranks: the
+            # layer runs on the gathered sequence (redundantly on every rank) and keeps this rank's outputs. Rotary
+            # angles follow the gathered positions.
+            from ..parallel.context_parallel import gather_full_sequence
+            extra = [rotary.pos_ids] if (rotary is not None and rotary.pos_ids is not None) else (
+                [rotary.freqs] if (rotary is not None and rotary.freqs.shape[0] == x.shape[0]) else [])
+            gathered, own = gather_full_sequence([x] + extra, packed.row_length if packed is not None else None)
+            x = gathered[0]
+            if extra and rotary.pos_ids is not None:
+                rotary = RotaryInputs(freqs=rotary.freqs, pos_ids=gathered[1], mscale=rotary.mscale)
+            elif extra:
+                rotary = RotaryInputs(freqs=gathered[1], pos_ids=None, mscale=rotary.mscale)
         T = x.shape[0]
         cu = packed.cu_seqlens if packed is not None else None
         ql = self.q_layernorm(F.linear(x, self.linear_q_down))
@@ -223,4 +234,7 @@ class CompressedSparseAttention(nn.Module):
         scale = self.scale
         o = blockwise_apply(lambda qb, ib, kvv, sk: sparse_mqa_attention_with_sink(qb, kvv, ib, sk, scale),
                             [q, idx], [kv_all, self.attn_sink], block=256)
-        return self.linear_proj(o.reshape(T, self.nq_l * self.d), residual)
+        o = o.reshape(T, self.nq_l * self.d)
+        if own is not None:
+            o = o.index_select(0, own)
+        return self.linear_proj(o, residual)

@@ -70,7 +70,8 @@ class GatedAttention(nn.Module):
                 f, kw = f[:, 0], {**kw, "pos_ids": None, "interleaved": False}
             q, k = OF.rope(q, f, **kw), OF.rope(k, f, **kw)
         cu = packed.cu_seqlens if packed is not None else None
-        o = core_attention(q, k, v, causal=True, scale=self.scale, cu_seqlens=cu, cfg=self.cfg)
+        o = core_attention(q, k, v, causal=True, scale=self.scale, cu_seqlens=cu, cfg=self.cfg,
+                           row_length=packed.row_length if packed is not None else None)
         o = o.reshape(T, self.nq_l * self.d) * torch.sigmoid(gate.float()).to(o.dtype)
         return self.linear_proj(o, residual)
 
@@ -93,10 +94,7 @@ class GatedDeltaNet(nn.Module):
     def __init__(self, cfg: TransformerConfig, key: str, *, device=None, parallel_state=None):
         super().__init__()
         st = ps.get_state(parallel_state)
-        if st.dims.cp > 1:
-            # the recurrent state of a sequence would have to travel from one context-parallel rank to the next
-            raise NotImplementedError("gated delta-net (linear attention) layers do not support context parallelism; "
-                                      "use tensor / sequence parallelism for long sequences")
+        self.cp = st.dims.cp  # > 1: convolution and recurrence run on the gathered sequence (see forward)
         tp = st.dims.tp
         self.cfg = cfg
         self.dk, self.dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
@@ -148,6 +146,14 @@ class GatedDeltaNet(nn.Module):
         cu = packed.cu_seqlens if packed is not None else None
         # conv over [q | k | v] channels, laid out type-major like the conv weight
         mixed = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=-1)
+        own = None
+        if self.cp > 1:
+            # The convolution window and the recurrent state cross the chunk boundaries of context parallelism: run
+            # both on the gathered sequence (token-wise projections stay local) and keep this rank's outputs.
+            from ..parallel.context_parallel import gather_full_sequence
+            (mixed, b, a), own = gather_full_sequence([mixed, b.reshape(T, -1), a.reshape(T, -1)],
+                                                      packed.row_length if packed is not None else None)
+            T_loc, T = T, mixed.shape[0]
         mixed = LA.causal_conv1d(mixed, self.conv_weight, cu_seqlens=cu, activation="silu")
         q, k, v = mixed.split([hk * dk, hk * dk, hk * r * dv], dim=-1)
         q = q.view(T, hk, dk).repeat_interleave(r, dim=1)
@@ -156,5 +162,7 @@ class GatedDeltaNet(nn.Module):
         beta = torch.sigmoid(b.reshape(T, hk * r).float())
         g = -self.A_log.float().exp() * F.softplus(a.reshape(T, hk * r).float() + self.dt_bias.float())
         o = LA.gated_delta_rule(q, k, v, g, beta, cu_seqlens=cu, qk_l2norm=True)
+        if own is not None:
+            o, T = o.index_select(0, own), T_loc
         o = self.out_norm(o, z.reshape(T, hk * r, dv))
         return self.out_proj(o.reshape(T, hk * r * dv), residual)

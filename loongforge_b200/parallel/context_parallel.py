@@ -101,6 +101,22 @@ def _positions(T_local: int, cp: int, rank: int, device, cu_seqlens=None, row_le
     return pos, seg
 
 
+def gather_full_sequence(tensors, row_length: Optional[int] = None):
+    """For layers whose mixing runs ALONG the sequence and cannot be cut into independent chunks (causal convolution,
+    recurrent / linear attention, window + compressed attention): every context-parallel rank gathers the tensors of
+    all ranks and puts the tokens into row order. Returns ``(full tensors, own)`` where ``own`` are the row positions
+    of this rank's tokens, i.e. ``full_out[own]`` is the local part of a result computed on the full sequence. The
+    mixing is computed redundantly on every rank; in backward the gather reduce-scatters, so each rank contributes the
+    gradient of its own tokens' outputs and receives the total for its own inputs."""
+    st = ps.get_state()
+    cp, rank, g = st.dims.cp, st.cp_rank, st.group("cp")
+    T = tensors[0].shape[0]
+    own, _ = _positions(T, cp, rank, tensors[0].device, None, row_length)
+    order = torch.argsort(M._all_gather_dim0(own, g))
+    full = [M.gather_from_sequence_parallel_region(t.contiguous(), g, True).index_select(0, order) for t in tensors]
+    return full, own
+
+
 def ring_attention(q, k, v, *, causal=True, scale=None, cu_seqlens=None, row_length: Optional[int] = None):
     """Attention for sequence-sharded q/k/v ``[T/cp, H, D]`` (load-balanced chunks)."""
     st = ps.get_state()

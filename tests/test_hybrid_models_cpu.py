@@ -161,21 +161,3 @@ def test_tiny_ernie_vl_routes_by_modality():
     g = moe.vision.experts.linear_fc1.weights()[0].grad
     assert g is None or float(g.abs().sum()) == 0.0
 
-
-def _cp_unsupported(rank, world, model_name):
-    import pytest as _pt
-
-    from loongforge_b200.models.registry import build_model, get_model_config
-    from loongforge_b200.parallel import state as ps
-
-    ps.initialize_model_parallel(ps.ParallelDims(cp=2))
-    with _pt.raises(NotImplementedError, match="context parallelism"):
-        build_model(get_model_config(model_name))
-    return True
-
-
-def test_recurrent_and_compressed_attention_reject_context_parallelism():
-    from dist_utils import run_distributed
-
-    for name in ("tiny-qwen3-next", "tiny-deepseek-v4"):
-        assert all(run_distributed(_cp_unsupported, 2, name))

@@ -102,6 +102,8 @@ def test_more_layouts_match_single_process(model, dims, ov, world):
     ("tiny-deepseek", {"cp": 2}, {"use_dsa": False}, 2),     # dense MLA through ring attention
     ("tiny-llama", {"tp": 2, "cp": 2}, {}, 4),
     ("tiny-ernie-vl", {"tp": 2}, {}, 2),                     # shared expert over the gathered sequence
+    ("tiny-qwen3-next", {"cp": 2}, {"moe_aux_loss_coeff": 0.0}, 2),   # convolution + delta rule on the gathered sequence
+    ("tiny-deepseek-v4", {"cp": 2, "tp": 2}, {}, 4),         # compressed sparse attention on the gathered sequence
 ])
 def test_two_rows_per_microbatch_match_single_process(model, dims, ov, world):
     """Micro-batches of two rows: context parallelism slices every row separately."""
