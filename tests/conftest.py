@@ -29,7 +29,7 @@ def pytest_cmdline_main(config):
     n = int(os.environ.get("LF_TEST_WORKERS", "0")) or max(1, min(4, (os.cpu_count() or 2) // 2))
     if n > 1:
         config.option.numprocesses = n
-        config.option.dist = "load"
+        config.option.dist = "loadfile"
     return None
 
 

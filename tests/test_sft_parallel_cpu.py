@@ -6,6 +6,9 @@ import torch
 from dist_utils import run_distributed
 
 
+_REF = {}
+
+
 def _run(rank, world, model_name, dims_kw, lora):
     from loongforge_b200.models.registry import get_model_config
     from loongforge_b200.parallel.state import ParallelDims
@@ -47,7 +50,9 @@ def _run(rank, world, model_name, dims_kw, lora):
     ("tiny-deepseek", {"cp": 2}, False, 2),
 ])
 def test_packed_sft_matches_single_process(model, dims, lora, world):
-    ref = run_distributed(_run, 1, model, {}, lora)[0]
+    if (model, lora) not in _REF:
+        _REF[(model, lora)] = run_distributed(_run, 1, model, {}, lora)[0]
+    ref = _REF[(model, lora)]
     res = run_distributed(_run, world, model, dict(dims), lora)
     got = [r for r in res if r[0][0] is not None][-1]
     for (l0, g0), (l1, g1) in zip(ref, got):

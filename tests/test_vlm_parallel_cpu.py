@@ -5,6 +5,9 @@ import pytest
 from dist_utils import run_distributed
 
 
+_REF = {}
+
+
 def _run(rank, world, dims_kw, vlm_kw, steps=2):
     from loongforge_b200.models.registry import get_model_config
     from loongforge_b200.parallel.state import ParallelDims
@@ -39,7 +42,9 @@ def _run(rank, world, dims_kw, vlm_kw, steps=2):
     ({"tp": 2, "pp": 2}, {"full_hetero_dp": True, "full_hetero_cpu_offload": True}, 4),
 ])
 def test_vlm_layouts_match_single_process(dims, vlm_kw, world):
-    ref = run_distributed(_run, 1, {}, {})[0]
+    if "ref" not in _REF:
+        _REF["ref"] = run_distributed(_run, 1, {}, {})[0]
+    ref = _REF["ref"]
     res = run_distributed(_run, world, dict(dims), dict(vlm_kw))
     got = [r for r in res if r[0][0] is not None][-1]
     for (l0, g0), (l1, g1) in zip(ref, got):
