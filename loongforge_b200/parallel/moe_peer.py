@@ -79,11 +79,13 @@ class PeerExchange:
         self.flags = self.block.peer_ptrs(self.off_flags)
 
     @classmethod
-    def get(cls, group, device, hidden: int, cap_rows: int) -> "PeerExchange":
+    def get(cls, group, device, hidden: int, cap_rows: int, headroom: float = 1.0) -> "PeerExchange":
+        """The group's exchange if it holds `cap_rows` rows, else a new one of ``cap_rows * headroom`` rows. Allocation
+        is collective: every rank of the group must reach this call with the SAME `cap_rows` and `headroom`."""
         key = (id(group), str(device), hidden)
         ex = cls._cache.get(key)
         if ex is None or ex.cap < cap_rows:
-            ex = cls(group, device, hidden, cap_rows)
+            ex = cls(group, device, hidden, int(cap_rows * max(headroom, 1.0)) + 128)
             cls._cache[key] = ex
         return ex
 
@@ -216,14 +218,12 @@ class PeerDispatcher:
         self.plan: Optional[RoutePlan] = None
 
     def dispatch(self, x: torch.Tensor, probs: torch.Tensor, topk_idx: torch.Tensor):
-        T, k = topk_idx.shape
-        cap = max(int(T * k * self.capacity_factor), 128)
-        self.ex = PeerExchange.get(self.group, x.device, self.H, cap)
-        self.plan = RoutePlan(topk_idx, self.E, self.ep, self.ep_rank, self.group, self.ex.cap)
-        if self.plan.max_rows > self.ex.cap:
-            # routing is more skewed than the capacity factor assumed: every rank sees the same maximum (it comes from
-            # the all-gathered counts), so all of them re-allocate the symmetric buffers at this same call
-            self.ex = PeerExchange.get(self.group, x.device, self.H, int(self.plan.max_rows * 1.25) + 128)
+        self.plan = RoutePlan(topk_idx, self.E, self.ep, self.ep_rank, self.group, 0)
+        # The buffers are sized from the most rows ANY rank receives: that number comes from the all-gathered counts
+        # and is the same on every rank, whatever each rank's own token count, so all ranks (re-)allocate the symmetric
+        # buffers at the same call. The capacity factor is the headroom kept above it when allocating.
+        self.ex = PeerExchange.get(self.group, x.device, self.H, max(self.plan.max_rows, 128),
+                                   headroom=max(self.capacity_factor, 1.25))
         pair_probs = probs[self.plan.pair_token.long(), self.plan.pair_expert]
         tokens, row_probs = _Dispatch.apply(x, pair_probs, self.ex, self.plan)
         return tokens, self.plan.tokens_per_expert, row_probs
