@@ -135,12 +135,16 @@ class WanSelfAttention(nn.Module):
         self.q, self.k, self.v, self.o = (_Linear(C, C, **kw) for _ in range(4))
         self.norm_q, self.norm_k = RMSNorm(C, cfg.eps, **kw), RMSNorm(C, cfg.eps, **kw)
 
-    def forward(self, x, angles, ulysses_group=None):
+    def forward(self, x, angles, ulysses_group=None, cu_seqlens=None):
         B, L, C = x.shape
         q = self.norm_q(self.q(x)).view(B, L, self.h, self.d)
         k = self.norm_k(self.k(x)).view(B, L, self.h, self.d)
         v = self.v(x).view(B, L, self.h, self.d)
         q, k = apply_rope_interleaved(q, angles), apply_rope_interleaved(k, angles)
+        if cu_seqlens is not None:
+            # several samples packed into one token row: attention stays inside each sample
+            o = OF.attention(q[0], k[0], v[0], causal=False, scale=self.d ** -0.5, cu_seqlens=cu_seqlens)
+            return self.o(o.reshape(1, L, C))
         return self.o(_attention(q, k, v, ulysses_group))
 
 
@@ -185,15 +189,27 @@ class WanBlock(nn.Module):
                                  _Linear(cfg.ffn_hidden_size, C, **kw))
         self.modulation = nn.Parameter(torch.randn(1, 6, C, **kw) / C ** 0.5)
 
-    def forward(self, x, e, angles, context, image_context=None, ulysses_group=None):
-        b1, s1, g1, b2, s2, g2 = (self.modulation.float() + e.float()).unbind(1)  # e [B, 6, C]
+    def forward(self, x, e, angles, context, image_context=None, ulysses_group=None, cu_seqlens=None):
+        """``e`` is ``[B, 6, C]`` (one modulation per sample) or, for packed rows, ``[1, L, 6, C]`` (per token; then
+        `context` / `image_context` are lists with one entry per packed sample and `cu_seqlens` their boundaries)."""
+        per_token = e.dim() == 4
+        b1, s1, g1, b2, s2, g2 = (self.modulation.float().unsqueeze(1) + e.float() if per_token
+                                  else self.modulation.float() + e.float()).unbind(-2)
+        up = (lambda t: t) if per_token else (lambda t: t[:, None])
 
         def mod(n, s, b):
-            return (n.float() * (1 + s[:, None]) + b[:, None]).to(x.dtype)
+            return (n.float() * (1 + up(s)) + up(b)).to(x.dtype)
 
-        x = x + (self.self_attn(mod(self.norm1(x), s1, b1), angles, ulysses_group).float() * g1[:, None]).to(x.dtype)
-        x = x + self.cross_attn(self.norm3(x), context, image_context)
-        return x + (self.ffn(mod(self.norm2(x), s2, b2)).float() * g2[:, None]).to(x.dtype)
+        x = x + (self.self_attn(mod(self.norm1(x), s1, b1), angles, ulysses_group, cu_seqlens).float() * up(g1)).to(x.dtype)
+        h = self.norm3(x)
+        if cu_seqlens is not None:
+            b = cu_seqlens.tolist()
+            parts = [self.cross_attn(h[:, s_:e_], context[i], image_context[i] if image_context is not None else None)
+                     for i, (s_, e_) in enumerate(zip(b, b[1:]))]
+            x = x + torch.cat(parts, dim=1)
+        else:
+            x = x + self.cross_attn(h, context, image_context)
+        return x + (self.ffn(mod(self.norm2(x), s2, b2)).float() * up(g2)).to(x.dtype)
 
 
 class WanModel(nn.Module):
@@ -258,6 +274,39 @@ class WanModel(nn.Module):
             from ..parallel.ulysses import gather_sequence
             x = gather_sequence(x, ulysses_group, dim=1)
         return self.unpatchify(x, grid)
+
+
+    def forward_packed(self, latents, timesteps, text_contexts, image_contexts=None):
+        """Samples of DIFFERENT sizes in one token row (the reference's WAN packing, wan_model.py:34-115): `latents` is
+        a list of ``[C, F_i, H_i, W_i]``, `timesteps` ``[n]``, `text_contexts` a list of ``[Lt_i, text_dim]``. Tokens of
+        all samples are concatenated; self-attention is confined to each sample through ``cu_seqlens``, rotary angles
+        restart per sample, the timestep modulation is looked up per token, cross-attention pairs each sample with its
+        own context. Returns the list of predictions."""
+        cfg = self.cfg
+        toks, grids, angs = [], [], []
+        for lat in latents:
+            t, g = self.patchify(lat[None])
+            toks.append(t[0])
+            grids.append(g)
+            angs.append(rope_3d_angles(g, cfg.head_dim, cfg.rope_theta, lat.device))
+        lens = [t.shape[0] for t in toks]
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=toks[0].device)
+        sample = torch.repeat_interleave(torch.arange(len(lens), device=cu.device), torch.tensor(lens, device=cu.device))
+        x = self.patch_embedding(torch.cat(toks)[None].to(cfg.params_dtype))
+        angles = torch.cat(angs)
+        e0 = self.time_embedding(timestep_embedding(timesteps, cfg.freq_dim).to(cfg.params_dtype))   # [n, C]
+        e = self.time_projection(e0).view(-1, 6, cfg.hidden_size)[sample][None]                       # [1, L, 6, C]
+        ctx = [self.text_embedding(c[None].to(cfg.params_dtype)) for c in text_contexts]
+        img = ([self.img_emb(c[None].to(cfg.params_dtype)) for c in image_contexts]
+               if image_contexts is not None else None)
+        for blk in self.blocks:
+            if self.recompute and torch.is_grad_enabled():
+                x = torch.utils.checkpoint.checkpoint(blk, x, e, angles, ctx, img, None, cu, use_reentrant=False)
+            else:
+                x = blk(x, e, angles, ctx, img, None, cu)
+        b, s_ = (self.head_modulation.float() + e0.float()[:, None]).unbind(1)                        # [n, C] each
+        x = self.head((self.head_norm(x).float() * (1 + s_[sample][None]) + b[sample][None]).to(x.dtype))
+        return [self.unpatchify(x[:, a:z], g)[0] for a, z, g in zip(cu.tolist(), cu.tolist()[1:], grids)]
 
 
 # ----------------------------------------------------------------------------- Qwen-Image MMDiT

@@ -90,7 +90,10 @@ def latent_file_iterator(paths: Sequence[str], micro_batch_size: int, *, dp_rank
         for j in range(micro_batch_size):
             idx = start_sample + (step * dp_size + dp_rank) * micro_batch_size + j
             items.append(torch.load(files[idx % len(files)], map_location="cpu", weights_only=True))
-        yield {k: torch.stack([it[k] for it in items]) for k in items[0]}
+        same = all(it["latents"].shape == items[0]["latents"].shape and it["text"].shape == items[0]["text"].shape
+                   for it in items)
+        # equal shapes: one batched tensor per field; different shapes: lists, which the trainer packs into one token row
+        yield {k: (torch.stack([it[k] for it in items]) if same else [it[k] for it in items]) for k in items[0]}
         step += 1
 
 
@@ -133,6 +136,8 @@ class DiffusionTrainer(Trainer):
         cp = st.dims.cp
         nmb = self.mb_calc.num_microbatches
         dt = self.dit_cfg.params_dtype
+        if isinstance(b["latents"], (list, tuple)):
+            return self._packed_forward_step(b, model, nmb)
         x0 = b["latents"].to(dt)
         B = x0.shape[0]
         ids = sched.sample_timestep_ids(B, self.gen).to(x0.device)
@@ -159,6 +164,30 @@ class DiffusionTrainer(Trainer):
             return loss * (float(cp) / nmb), {"loss": loss.detach()}
 
         return per_sample, loss_func
+
+    def _packed_forward_step(self, b, model, nmb):
+        """Samples of different sizes (variable resolution / length): packed into one token row by the model
+        (``WanModel.forward_packed``) instead of being padded to a common shape."""
+        if self.kind != "wan" or self.st.dims.cp > 1:
+            raise NotImplementedError("packed variable-size samples are supported for WAN without sequence parallelism")
+        sched, dt, dev = self.sched, self.dit_cfg.params_dtype, self.device
+        x0 = [x.to(dev, dt) for x in b["latents"]]
+        n = len(x0)
+        ids = sched.sample_timestep_ids(n, self.gen).to(dev)
+        noise = [torch.randn(x.shape, generator=self.gen).to(dev, dt) for x in x0]
+        xt = [sched.add_noise(x[None], z[None], ids[i:i + 1])[0] for i, (x, z) in enumerate(zip(x0, noise))]
+        if "condition" in b:
+            xt = [torch.cat([x, c.to(dev, dt)], dim=0) for x, c in zip(xt, b["condition"])]
+        img = [c.to(dev, dt) for c in b["image_context"]] if "image_context" in b else None
+        module = model.module if hasattr(model, "module") else model
+        pred = module.forward_packed(xt, sched.timesteps.to(dev)[ids], [c.to(dev, dt) for c in b["text"]], img)
+        loss = sum(sched.loss(p[None], x[None], z[None], ids[i:i + 1])
+                   for i, (p, x, z) in enumerate(zip(pred, x0, noise))) / n
+
+        def loss_func(l):
+            return l / nmb, {"loss": l.detach()}
+
+        return loss, loss_func
 
     def flops_per_step(self) -> float:
         n_params = sum(p.numel() for m in self.models for p in m.module.parameters())
