@@ -153,12 +153,18 @@ class OmniCombinationModel(nn.Module):
         n_img = grid_thw.shape[0]
         split = self.encoder_hetero_dp and tp > 1 and n_img >= tp
         if split:
-            per = [(n_img + tp - 1 - r) // tp for r in range(tp)]
-            starts = [sum(per[:r]) for r in range(tp)]
+            # images go to the ranks so that every rank encodes a similar number of PATCHES (longest first onto the
+            # least loaded rank), not a similar number of images (reference: data/dp_balance/vit_balance.py:27-155)
+            from ..data.dp_balance import balance_vit_images
             patches = (grid_thw[:, 0] * grid_thw[:, 1] * grid_thw[:, 2]).tolist()
-            i0, i1 = starts[st.tp_rank], starts[st.tp_rank] + per[st.tp_rank]
-            p0, p1 = sum(patches[:i0]), sum(patches[:i1])
-            pixels, my_grid = pixels[p0:p1], grid_thw[i0:i1]
+            plan = balance_vit_images([patches] + [[] for _ in range(tp - 1)])
+            by_rank = [sorted(i for (_, i) in plan[r]) for r in range(tp)]
+            offs = [0]
+            for n in patches:
+                offs.append(offs[-1] + n)
+            mine = by_rank[st.tp_rank]
+            pixels = torch.cat([pixels[offs[i]:offs[i + 1]] for i in mine])
+            my_grid = grid_thw[torch.tensor(mine, device=grid_thw.device)]
         else:
             my_grid = grid_thw
         self._deepstack = None
@@ -178,8 +184,17 @@ class OmniCombinationModel(nn.Module):
         if split:
             assert self.vision_family == "qwen2_vit", "encoder hetero-DP is implemented for the Qwen2-VL encoder"
             unit = self.encoder_model.image_projector.unit
-            counts = [sum(patches[starts[r]:starts[r] + per[r]]) // unit for r in range(tp)]
+            counts = [sum(patches[i] for i in by_rank[r]) // unit for r in range(tp)]
             emb = _GatherVarRows.apply(emb, counts, g)
+            # the gathered rows are rank-major: put the images' token blocks back into image order
+            toks = [p // unit for p in patches]
+            pos, start = {}, 0
+            for r in range(tp):
+                for i in by_rank[r]:
+                    pos[i] = start
+                    start += toks[i]
+            index = torch.cat([torch.arange(pos[i], pos[i] + toks[i], device=emb.device) for i in range(n_img)])
+            emb = emb.index_select(0, index)
         return emb
 
     def forward(self, tokens, position_ids, *, pixels=None, grid_thw=None, labels=None, loss_mask=None, packed=None,

@@ -149,3 +149,36 @@ def test_vlm_hugging_face_export_and_online_load_across_layouts(tmp_path):
     import torch
     worst = max(float((first[k].float() - second[k].float()).abs().max()) for k in first)
     assert worst < 2e-4, worst  # two independent training runs in different layouts: summation order differs
+
+
+def _hetero_balance(rank, world):
+    import torch
+
+    from loongforge_b200.models.omni import ENCODER_STATE, OmniCombinationModel
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel import state as ps
+
+    ps.initialize_model_parallel(ps.ParallelDims(tp=2))
+    ps.create_parallel_state(ENCODER_STATE, ps.ParallelDims(tp=1))
+    lm = get_model_config("tiny-llama")
+    vit = get_model_config("tiny-vit")
+    outs = {}
+    for hetero in (False, True):
+        model = OmniCombinationModel(lm, vit, image_token_id=lm.vocab_size - 1, encoder_hetero_dp=hetero)
+        g = torch.Generator().manual_seed(0)
+        grid = torch.tensor([[1, 8, 8], [1, 4, 4], [1, 4, 8], [1, 4, 4]])   # 64 + 16 + 32 + 16 patches
+        pixels = torch.randn(int((grid[:, 1] * grid[:, 2]).sum()), 3 * 2 * 14 * 14, generator=g)
+        emb = model.encode_images(pixels, grid)
+        emb.pow(2).sum().backward()
+        gsum = model.encoder_model.image_projector.linear_fc2.weight.grad.clone()
+        if hetero:
+            torch.distributed.all_reduce(gsum)   # partial per rank under hetero-DP (the trainer sums them)
+        outs[hetero] = (emb.detach(), gsum)
+    return float((outs[True][0] - outs[False][0]).abs().max()), float((outs[True][1] - outs[False][1]).abs().max())
+
+
+def test_encoder_hetero_dp_balances_images_by_patches():
+    """Four images of 64 / 16 / 32 / 16 patches over two ranks: 64 on one rank, 16 + 32 + 16 on the other; the
+    embeddings come back in image order and the encoder gradients add up to the unsplit ones."""
+    for err_emb, err_grad in run_distributed(_hetero_balance, 2):
+        assert err_emb < 1e-5 and err_grad < 1e-3, (err_emb, err_grad)
