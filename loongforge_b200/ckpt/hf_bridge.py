@@ -31,6 +31,7 @@ def load_hf_checkpoint_online(trainer, hf_dir: str, family: str = "llama3") -> i
     nm = _nm()
     cfg = trainer.mcfg
     st = trainer.st
+    _set_geometry(cfg)
     hf = load_hf(hf_dir)
     lm_kw = dict(num_layers=cfg.num_layers, num_heads=cfg.num_attention_heads, num_groups=cfg.num_query_groups,
                  padded_vocab=cfg.padded_vocab_size, num_experts=cfg.num_moe_experts,
@@ -93,11 +94,22 @@ def load_hf_checkpoint_online(trainer, hf_dir: str, family: str = "llama3") -> i
     return n
 
 
+def _set_geometry(cfg) -> None:
+    """The converter's TP rule for the GatedDeltaNet convolution needs the sizes of its q / k / v channel blocks."""
+    if getattr(cfg, "linear_num_key_heads", None):
+        _nm().set_linear_attention_geometry(cfg.linear_num_key_heads, cfg.linear_key_head_dim,
+                                            cfg.linear_num_value_heads, cfg.linear_value_head_dim)
+
+
+
 _HF_ARCH = {"llama": ("llama", "LlamaForCausalLM"), "llama2": ("llama", "LlamaForCausalLM"),
             "llama3": ("llama", "LlamaForCausalLM"), "internlm": ("internlm2", "InternLM2ForCausalLM"),
             "qwen2": ("qwen2", "Qwen2ForCausalLM"), "qwen2.5": ("qwen2", "Qwen2ForCausalLM"),
             "qwen3": ("qwen3", "Qwen3ForCausalLM"), "qwen3_moe": ("qwen3_moe", "Qwen3MoeForCausalLM"),
-            "deepseek": ("deepseek_v3", "DeepseekV3ForCausalLM"), "glm": ("glm_moe_dsa", "GlmMoeDsaForCausalLM")}
+            "deepseek": ("deepseek_v3", "DeepseekV3ForCausalLM"), "glm": ("glm_moe_dsa", "GlmMoeDsaForCausalLM"),
+            "internlm2": ("internlm2", "InternLM2ForCausalLM"), "kimi_k2": ("kimi_k2", "DeepseekV3ForCausalLM"),
+            "minimax": ("minimax_m2", "MiniMaxM2ForCausalLM"), "mimo": ("mimo", "MiMoForCausalLM"),
+            "qwen3_next": ("qwen3_next", "Qwen3NextForCausalLM"), "qwen3_5": ("qwen3_5_moe", "Qwen3_5MoeForCausalLM")}
 
 
 def hf_config_from_model(cfg, family: str) -> dict:
@@ -155,6 +167,7 @@ def save_hf_checkpoint(trainer, out_dir: str, family: str = "llama3", hf_config:
 
     nm = _nm()
     cfg, st = trainer.mcfg, trainer.st
+    _set_geometry(cfg)
     e_local = (cfg.num_moe_experts // st.dims.ep) if cfg.num_moe_experts else 0
     local: Dict[str, torch.Tensor] = {}
     enc_meta: Dict[str, tuple] = {}  # encoder tensors sharded over TP: key -> (dim, stride), from the parameters

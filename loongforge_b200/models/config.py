@@ -64,6 +64,7 @@ class TransformerConfig:
     moe_router_topk: int = 2
     moe_ffn_hidden_size: Optional[int] = None
     moe_shared_expert_intermediate_size: Optional[int] = None
+    moe_shared_expert_gate: bool = False  # sigmoid gate on the shared expert's output (Qwen3-Next, Qwen3.5)
     moe_layer_freq: Union[int, List[int]] = 1
     moe_router_score_function: str = "softmax"  # softmax | sigmoid
     moe_router_pre_softmax: bool = False

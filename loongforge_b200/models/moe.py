@@ -312,6 +312,15 @@ class MoELayer(nn.Module):
             self.shared_experts = MLP(cfg, key + ".shared_experts", ffn_hidden=cfg.moe_shared_expert_intermediate_size,
                                       fused_norm=False, device=device, parallel_state=parallel_state,
                                       sequence_parallel=False)
+            if cfg.moe_shared_expert_gate:
+                # y_shared * sigmoid(x . g): one gate logit per token (Qwen2-MoE / Qwen3-Next / Qwen3.5; stored as
+                # mlp.shared_experts.gate_weight, configs/models/qwen3_next/ckpt_convert/qwen3_next_moe_convert.yaml:132-134)
+                w = PL.init_full_then_slice(key + ".shared_experts.gate_weight", (1, cfg.hidden_size),
+                                            cfg.init_method_std, partition_dim=None, rank=0, world=1,
+                                            device=device or "cpu", dtype=cfg.params_dtype)
+                self.shared_experts.gate_weight = nn.Parameter(w)
+                # applied to this rank's token shard under sequence parallelism: partial gradient there
+                PL.mark_tp(self.shared_experts.gate_weight, None, sequence_parallel=cfg.sequence_parallel)
         else:
             self.shared_experts = None
         self.dispatcher = AlltoAllDispatcher(E, parallel_state)
@@ -360,12 +369,18 @@ class MoELayer(nn.Module):
         if local_shard:
             out = M.gather_from_sequence_parallel_region(out, st.group("tp"), False)
         if self.shared_experts is not None:
+            x_out = x_full  # the tokens that `out` holds on this rank
             if st.dims.tp > 1:
                 # shared expert is tensor parallel over the full token set of the TP group
                 g = st.group("tp")
                 xs = M.gather_from_sequence_parallel_region(x, g, False) if self.cfg.sequence_parallel else x_full
                 ys = self.shared_experts(xs)
-                out = out + (M.scatter_to_sequence_parallel_region(ys, g) if self.cfg.sequence_parallel else ys)
+                if self.cfg.sequence_parallel:
+                    ys, x_out = M.scatter_to_sequence_parallel_region(ys, g), x
             else:
-                out = out + self.shared_experts(x)
+                ys = self.shared_experts(x)
+            gate_w = getattr(self.shared_experts, "gate_weight", None)
+            if gate_w is not None:
+                ys = ys * torch.sigmoid(torch.nn.functional.linear(x_out, gate_w).float()).to(ys.dtype)
+            out = out + ys
         return out

@@ -323,3 +323,97 @@ def test_offline_dist_checkpoint_to_hf_and_back(tmp_path):
                    "--model-name", "tiny-llama"]) == 0
     b = run_distributed(_dist_ckpt_worker, 2, str(tmp_path), {"pp": 2}, "load")
     assert abs(a[0] - b[1]) < 1e-5 * a[0], (a, b)
+
+
+def test_family_spellings_internlm2_minimax_mimo_roundtrip():
+    """Families whose Hugging Face files name the same tensors differently: packed wqkv + w1/w3/w2 (InternLM2),
+    block_sparse_moe with a router bias (MiniMax), MTP layers under model.mtp_layers (MiMo)."""
+    from loongforge_b200.models.registry import build_model, get_model_config
+    from loongforge_b200.parallel import state as ps
+    from tools.convert_checkpoint import name_maps as nm
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(ps.ParallelDims())
+    cases = {
+        "internlm2": (get_model_config("tiny-llama"),
+                      ["model.tok_embeddings.weight", "output.weight", "model.layers.0.attention.wqkv.weight",
+                       "model.layers.0.attention.wo.weight", "model.layers.1.feed_forward.w3.weight",
+                       "model.layers.1.attention_norm.weight", "model.layers.1.ffn_norm.weight"]),
+        "minimax": (get_model_config("tiny-qwen3-moe", moe_router_enable_expert_bias=True),
+                    ["model.layers.0.block_sparse_moe.gate.weight", "model.layers.0.block_sparse_moe.experts.3.w1.weight",
+                     "model.layers.0.block_sparse_moe.experts.3.w2.weight",
+                     "model.layers.0.block_sparse_moe.e_score_correction_bias", "model.layers.0.self_attn.q_norm.weight"]),
+        "mimo": (get_model_config("tiny-llama", add_qkv_bias=True, mtp_num_layers=1),
+                 ["model.mtp_layers.0.token_layernorm.weight", "model.mtp_layers.0.hidden_layernorm.weight",
+                  "model.mtp_layers.0.input_proj.weight", "model.mtp_layers.0.final_layernorm.weight",
+                  "model.mtp_layers.0.self_attn.q_proj.bias", "model.mtp_layers.0.mlp.down_proj.weight"]),
+    }
+    for family, (cfg, expect) in cases.items():
+        fam = nm.FAMILIES[family]
+        mc = {k: v for k, v in build_model(cfg).state_dict().items()
+              if "local_tokens_per_expert" not in k and "_extra_state" not in k}
+        kw = dict(num_layers=cfg.num_layers, num_heads=cfg.num_attention_heads, num_groups=cfg.num_query_groups,
+                  num_experts=cfg.num_moe_experts)
+        hf = nm.mcore_to_hf(mc, fam, vocab_size=cfg.vocab_size, **kw)
+        for name in expect:
+            assert name in hf, (family, name, sorted(hf)[:12])
+        assert not any("self_attn.wqkv" in k or ".gate_proj." in k and family == "minimax" for k in hf), family
+        back = nm.hf_to_mcore(hf, fam, padded_vocab=cfg.padded_vocab_size, **kw)
+        assert set(back) == set(mc), (family, set(back) ^ set(mc))
+        assert all(torch.equal(back[k], mc[k]) for k in mc), family
+    ps.destroy_model_parallel()
+
+
+def _hybrid_shard_worker(rank, world, tmp):
+    """The TP shard that the converter cuts equals what a TP rank of the model itself holds."""
+    from loongforge_b200.models.registry import build_model, get_model_config
+    from loongforge_b200.parallel import state as ps
+    from tools.convert_checkpoint import name_maps as nm
+
+    cfg = get_model_config("tiny-qwen3-next")
+    nm.set_linear_attention_geometry(cfg.linear_num_key_heads, cfg.linear_key_head_dim, cfg.linear_num_value_heads,
+                                     cfg.linear_value_head_dim)
+    full = torch.load(os.path.join(tmp, "full.pt"))
+    ps.initialize_model_parallel(ps.ParallelDims(tp=2))
+    local = build_model(cfg).state_dict()
+    bad = [k for k, w in full.items() if k in local and not torch.equal(nm.shard_tp(k, w, rank, 2), local[k])]
+    return bad
+
+
+def test_qwen3_next_name_map_roundtrip_and_tp_shards(tmp_path):
+    """GatedDeltaNet + gated attention + gated shared expert: names, the per-head [q; gate] packing, TP rules."""
+    from loongforge_b200.models.registry import build_model, get_model_config
+    from loongforge_b200.parallel import state as ps
+    from tests.dist_utils import run_distributed
+    from tools.convert_checkpoint import name_maps as nm
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(ps.ParallelDims())
+    cfg = get_model_config("tiny-qwen3-next")
+    fam = nm.FAMILIES["qwen3_next"]
+    mc = {k: v for k, v in build_model(cfg).state_dict().items()
+          if "local_tokens_per_expert" not in k and "_extra_state" not in k and "expert_bias" not in k}
+    kw = dict(num_layers=cfg.num_layers, num_heads=cfg.num_attention_heads, num_groups=cfg.num_query_groups,
+              num_experts=cfg.num_moe_experts)
+    hf = nm.mcore_to_hf(mc, fam, vocab_size=cfg.vocab_size, **kw)
+    d, nh = cfg.kv_channels, cfg.num_attention_heads
+    assert hf["model.layers.3.self_attn.q_proj.weight"].shape == (2 * nh * d, cfg.hidden_size)
+    assert hf["model.layers.0.linear_attn.conv1d.weight"].dim() == 3
+    for name in ("model.layers.0.linear_attn.in_proj_qkvz.weight", "model.layers.0.linear_attn.A_log",
+                 "model.layers.0.linear_attn.norm.weight", "model.layers.0.mlp.shared_expert_gate.weight",
+                 "model.layers.0.mlp.shared_expert.down_proj.weight", "model.layers.3.self_attn.k_norm.weight"):
+        assert name in hf, name
+    # head 1's query rows sit at [2 d, 3 d) of the HF projection and in group 0's q block of the packed one
+    packed = mc["decoder.layers.3.self_attention.linear_qgkv.weight"]
+    assert torch.equal(hf["model.layers.3.self_attn.q_proj.weight"][2 * d:3 * d], packed[d:2 * d])
+    back = nm.hf_to_mcore(hf, fam, padded_vocab=cfg.padded_vocab_size, **kw)
+    assert set(back) == set(mc), set(back) ^ set(mc)
+    assert all(torch.equal(back[k], mc[k]) for k in mc)
+    nm.set_linear_attention_geometry(cfg.linear_num_key_heads, cfg.linear_key_head_dim, cfg.linear_num_value_heads,
+                                     cfg.linear_value_head_dim)
+    for k, w in mc.items():
+        assert torch.equal(nm.merge_tp(k, [nm.shard_tp(k, w, r, 2) for r in range(2)]), w), k
+    torch.save(mc, tmp_path / "full.pt")
+    ps.destroy_model_parallel()
+    for bad in run_distributed(_hybrid_shard_worker, 2, str(tmp_path)):
+        assert not bad, bad

@@ -49,6 +49,9 @@ def parse_args(argv=None):
     p.add_argument("--num_experts", type=int, default=None)
     p.add_argument("--vit_num_layers", type=int, default=None, help="vision tower depth (else vision_config.depth)")
     p.add_argument("--vit_num_heads", type=int, default=None, help="vision tower heads (else vision_config.num_heads)")
+    p.add_argument("--linear_attention_geometry", default=None,
+                   help="key heads,key dim,value heads,value dim of the GatedDeltaNet layers (Qwen3-Next / Qwen3.5 with "
+                        "tensor parallelism; else linear_* of config.json)")
     p.add_argument("--no_load_optim", action="store_true")
     p.add_argument("--no_save_optim", action="store_true")
     p.add_argument("--load_lora_ckpt_path", default=None)
@@ -225,6 +228,12 @@ def main(argv=None):
     dt = getattr(torch, a.torch_dtype) if a.torch_dtype else None
     hf_dir = a.load_ckpt_path if a.load_platform == "huggingface" else None
     L, H, G, V, E, tie, hf_cfg = _model_dims(a, hf_dir)
+    tc = hf_cfg.get("text_config") or hf_cfg
+    if a.linear_attention_geometry:
+        nm.set_linear_attention_geometry(*[int(x) for x in a.linear_attention_geometry.split(",")])
+    elif tc.get("linear_num_key_heads"):
+        nm.set_linear_attention_geometry(tc["linear_num_key_heads"], tc["linear_key_head_dim"],
+                                         tc["linear_num_value_heads"], tc["linear_value_head_dim"])
     if a.load_platform == "huggingface":
         hf = load_hf(a.load_ckpt_path)
         mult = a.make_vocab_size_divisible_by * a.tensor_model_parallel_size

@@ -30,13 +30,22 @@ class FamilyMap:
     router: str = "mlp.gate.weight"
     shared_expert: Optional[str] = None  # e.g. "mlp.shared_experts."
     mla: bool = False  # DeepSeek-style multi-latent attention (+ optional DSA indexer, router bias, MTP layers)
+    # families whose Hugging Face files spell the same tensors differently: (theirs, canonical) substring pairs applied
+    # to the part of a key after the layer prefix, and (theirs, canonical) prefixes for the keys outside the layers
+    layer_alias: tuple = ()
+    top_alias: tuple = ()
+    hybrid: bool = False  # Qwen3-Next / Qwen3.5: GatedDeltaNet layers + gated full attention, gated shared expert
+    packed_qkv: Optional[str] = None  # HF key suffix of an already packed per-group [q.., k, v] projection
+    # multi-token-prediction layers of the non-MLA families: HF prefix and the names of the four extra tensors
+    mtp_layers: Optional[str] = None  # e.g. "model.mtp_layers.{i}."
+    mtp_names: tuple = (("enorm.weight", "enorm.weight"), ("hnorm.weight", "hnorm.weight"),
+                        ("eh_proj.weight", "eh_proj.weight"), ("final_layernorm.weight", "shared_head.norm.weight"))
 
 
 FAMILIES: Dict[str, FamilyMap] = {
     "llama": FamilyMap("llama"),
     "llama2": FamilyMap("llama2"),
     "llama3": FamilyMap("llama3"),
-    "internlm": FamilyMap("internlm"),
     "qwen2": FamilyMap("qwen2", qkv_bias=True),
     "qwen2.5": FamilyMap("qwen2.5", qkv_bias=True),
     "qwen3": FamilyMap("qwen3", qk_norm=True),
@@ -45,10 +54,38 @@ FAMILIES: Dict[str, FamilyMap] = {
     # layers with a shared expert and a router bias, multi-token-prediction layers appended after the last layer
     "deepseek": FamilyMap("deepseek", moe=True, mla=True, shared_expert="mlp.shared_experts."),
     "glm": FamilyMap("glm", moe=True, mla=True, shared_expert="mlp.shared_experts."),
+    # (configs/models/qwen3_next/ckpt_convert/qwen3_next_moe_convert.yaml:17-100)
+    "qwen3_next": FamilyMap("qwen3_next", qk_norm=True, moe=True, hybrid=True, shared_expert="mlp.shared_expert."),
+    "qwen3_5": FamilyMap("qwen3_5", qk_norm=True, moe=True, hybrid=True, shared_expert="mlp.shared_expert."),
+    "kimi_k2": FamilyMap("kimi_k2", moe=True, mla=True, shared_expert="mlp.shared_experts."),
+    # InternLM2 / 2.5: packed wqkv, w1/w3/w2 feed-forward (configs/models/internlm2.5/ckpt_convert/internlm2_5_convert.yaml)
+    "internlm2": FamilyMap("internlm2", packed_qkv="self_attn.wqkv.weight",
+                           layer_alias=(("attention.wqkv.", "self_attn.wqkv."), ("attention.wo.", "self_attn.o_proj."),
+                                        ("feed_forward.w1.", "mlp.gate_proj."), ("feed_forward.w3.", "mlp.up_proj."),
+                                        ("feed_forward.w2.", "mlp.down_proj."), ("attention_norm.", "input_layernorm."),
+                                        ("ffn_norm.", "post_attention_layernorm.")),
+                           top_alias=(("model.tok_embeddings.", "model.embed_tokens."), ("output.", "lm_head."))),
+    # MiniMax-M2: block_sparse_moe with w1/w3/w2 experts, router bias, q/k norms
+    # (configs/models/minimax/ckpt_convert/minimax_convert.yaml)
+    "minimax": FamilyMap("minimax", qk_norm=True, moe=True,
+                         layer_alias=(("block_sparse_moe.experts.", "mlp.experts."), (".w1.", ".gate_proj."),
+                                      (".w3.", ".up_proj."), (".w2.", ".down_proj."),
+                                      ("block_sparse_moe.gate.", "mlp.gate."),
+                                      ("block_sparse_moe.e_score_correction_bias", "mlp.gate.e_score_correction_bias"))),
+    # MiMo: Qwen2-style layers plus multi-token-prediction layers under model.mtp_layers
+    # (configs/models/mimo/ckpt_convert/mimo_convert.yaml)
+    "mimo": FamilyMap("mimo", qkv_bias=True, mtp_layers="model.mtp_layers.{i}.",
+                      mtp_names=(("enorm.weight", "token_layernorm.weight"), ("hnorm.weight", "hidden_layernorm.weight"),
+                                 ("eh_proj.weight", "input_proj.weight"),
+                                 ("final_layernorm.weight", "final_layernorm.weight"))),
 }
 
 
 # vision-language compositions: name -> family of their language model
+# the InternLM presets of this package use family "internlm"; MiniMax / Kimi checkpoints share their families' maps
+FAMILIES["internlm"] = FAMILIES["internlm2.5"] = FAMILIES["internlm2"]
+FAMILIES["kimi"] = FAMILIES["kimi_k2"]
+
 VLM_FAMILIES: Dict[str, str] = {"qwen2_vl": "qwen2", "qwen2_5_vl": "qwen2.5", "qwen2.5_vl": "qwen2.5"}
 
 
@@ -190,42 +227,244 @@ def _mla_to_hf(mc, fam, num_layers, vocab_size, num_experts, tie_embeddings):
     return out
 
 
+def _layer_keys(fam: FamilyMap, num_layers: int, mtp: int = 8):
+    """Layer prefixes of a family (decoder layers, then whatever MTP prefixes it uses)."""
+    pre = [fam.hf_layers.format(i=i) for i in range(num_layers + (mtp if fam.mla else 0))]
+    if fam.mtp_layers:
+        pre += [fam.mtp_layers.format(i=i) for i in range(mtp)]
+    return pre
+
+
+def _rename(keys_in: Dict[str, torch.Tensor], fam: FamilyMap, num_layers: int, to_canonical: bool):
+    """Family spelling <-> canonical (Llama-style) spelling of the Hugging Face keys."""
+    if not fam.layer_alias and not fam.top_alias:
+        return keys_in
+    layer = [(a, b) if to_canonical else (b, a) for a, b in fam.layer_alias]
+    top = [(a, b) if to_canonical else (b, a) for a, b in fam.top_alias]
+    if not to_canonical:
+        layer.reverse()
+    prefixes = _layer_keys(fam, num_layers)
+    out = {}
+    for k, v in keys_in.items():
+        pre = next((p for p in prefixes if k.startswith(p)), None)
+        if pre is not None:
+            tail = k[len(pre):]
+            for a, b in layer:
+                tail = tail.replace(a, b)
+            out[pre + tail] = v
+            continue
+        for a, b in top:
+            if k.startswith(a):
+                k = b + k[len(a):]
+                break
+        out[k] = v
+    return out
+
+
+def _std_layer_to_mcore(hf, h: str, m: str, out, fam: FamilyMap, num_groups: int, num_experts) -> None:
+    out[m + "self_attention.linear_qkv.layer_norm_weight"] = hf[h + "input_layernorm.weight"]
+    if fam.packed_qkv:
+        out[m + "self_attention.linear_qkv.weight"] = hf[h + fam.packed_qkv]  # already [q.., k, v] per group
+    else:
+        out[m + "self_attention.linear_qkv.weight"] = pack_qkv(hf[h + "self_attn.q_proj.weight"],
+                                                               hf[h + "self_attn.k_proj.weight"],
+                                                               hf[h + "self_attn.v_proj.weight"], num_groups)
+    if fam.qkv_bias:
+        out[m + "self_attention.linear_qkv.bias"] = pack_qkv(hf[h + "self_attn.q_proj.bias"],
+                                                             hf[h + "self_attn.k_proj.bias"],
+                                                             hf[h + "self_attn.v_proj.bias"], num_groups)
+    if fam.qk_norm:
+        out[m + "self_attention.q_layernorm.weight"] = hf[h + "self_attn.q_norm.weight"]
+        out[m + "self_attention.k_layernorm.weight"] = hf[h + "self_attn.k_norm.weight"]
+    out[m + "self_attention.linear_proj.weight"] = hf[h + "self_attn.o_proj.weight"]
+    post = hf[h + "post_attention_layernorm.weight"]
+    if fam.moe and (h + fam.router) in hf:
+        out[m + "pre_mlp_layernorm.weight"] = post
+        out[m + "mlp.router.weight"] = hf[h + fam.router]
+        if h + "mlp.gate.e_score_correction_bias" in hf:
+            out[m + "mlp.router.expert_bias"] = hf[h + "mlp.gate.e_score_correction_bias"]
+        for e in range(num_experts):
+            p = h + fam.expert_tpl.format(e=e)
+            out[m + f"mlp.experts.linear_fc1.weight{e}"] = torch.cat([hf[p + "gate_proj.weight"],
+                                                                      hf[p + "up_proj.weight"]], 0)
+            out[m + f"mlp.experts.linear_fc2.weight{e}"] = hf[p + "down_proj.weight"]
+    else:
+        out[m + "mlp.linear_fc1.layer_norm_weight"] = post
+        out[m + "mlp.linear_fc1.weight"] = torch.cat([hf[h + "mlp.gate_proj.weight"], hf[h + "mlp.up_proj.weight"]], 0)
+        out[m + "mlp.linear_fc2.weight"] = hf[h + "mlp.down_proj.weight"]
+
+
+def _std_layer_to_hf(mc, m: str, h: str, out, fam: FamilyMap, num_heads: int, num_groups: int, num_experts) -> None:
+    out[h + "input_layernorm.weight"] = mc[m + "self_attention.linear_qkv.layer_norm_weight"]
+    if fam.packed_qkv:
+        out[h + fam.packed_qkv] = mc[m + "self_attention.linear_qkv.weight"]
+    else:
+        q, k, v = unpack_qkv(mc[m + "self_attention.linear_qkv.weight"], num_heads, num_groups)
+        out[h + "self_attn.q_proj.weight"], out[h + "self_attn.k_proj.weight"], out[h + "self_attn.v_proj.weight"] = q, k, v
+    if fam.qkv_bias:
+        qb, kb, vb = unpack_qkv(mc[m + "self_attention.linear_qkv.bias"], num_heads, num_groups)
+        out[h + "self_attn.q_proj.bias"], out[h + "self_attn.k_proj.bias"], out[h + "self_attn.v_proj.bias"] = qb, kb, vb
+    if fam.qk_norm:
+        out[h + "self_attn.q_norm.weight"] = mc[m + "self_attention.q_layernorm.weight"]
+        out[h + "self_attn.k_norm.weight"] = mc[m + "self_attention.k_layernorm.weight"]
+    out[h + "self_attn.o_proj.weight"] = mc[m + "self_attention.linear_proj.weight"]
+    if (m + "mlp.router.weight") in mc:
+        out[h + "post_attention_layernorm.weight"] = mc[m + "pre_mlp_layernorm.weight"]
+        out[h + fam.router] = mc[m + "mlp.router.weight"]
+        if m + "mlp.router.expert_bias" in mc:
+            out[h + "mlp.gate.e_score_correction_bias"] = mc[m + "mlp.router.expert_bias"]
+        for e in range(num_experts):
+            p = h + fam.expert_tpl.format(e=e)
+            g, u = mc[m + f"mlp.experts.linear_fc1.weight{e}"].chunk(2, 0)
+            out[p + "gate_proj.weight"], out[p + "up_proj.weight"] = g.contiguous(), u.contiguous()
+            out[p + "down_proj.weight"] = mc[m + f"mlp.experts.linear_fc2.weight{e}"]
+    else:
+        out[h + "post_attention_layernorm.weight"] = mc[m + "mlp.linear_fc1.layer_norm_weight"]
+        g, u = mc[m + "mlp.linear_fc1.weight"].chunk(2, 0)
+        out[h + "mlp.gate_proj.weight"], out[h + "mlp.up_proj.weight"] = g.contiguous(), u.contiguous()
+        out[h + "mlp.down_proj.weight"] = mc[m + "mlp.linear_fc2.weight"]
+
+
+# ---- Qwen3-Next / Qwen3.5 hybrid layers ----------------------------------------------------------
+_GDN = [("self_attention.in_proj_qkvz.weight", "linear_attn.in_proj_qkvz.weight"),
+        ("self_attention.in_proj_ba.weight", "linear_attn.in_proj_ba.weight"),
+        ("self_attention.dt_bias", "linear_attn.dt_bias"), ("self_attention.A_log", "linear_attn.A_log"),
+        ("self_attention.out_norm.weight", "linear_attn.norm.weight"),
+        ("self_attention.out_proj.weight", "linear_attn.out_proj.weight")]
+
+
+def _pack_qgkv(qg, k, v, num_heads: int, num_groups: int):
+    """HF ``q_proj`` rows are per head ``[q_h; gate_h]``; the packed projection holds per KV group
+    ``[q heads | gate heads | k | v]`` so that a tensor-parallel shard keeps whole groups."""
+    d = k.shape[0] // num_groups
+    r = num_heads // num_groups
+    tail = qg.shape[1:]
+    qg = qg.reshape(num_groups, r, 2, d, *tail)
+    q, g = qg[:, :, 0].reshape(num_groups, r * d, *tail), qg[:, :, 1].reshape(num_groups, r * d, *tail)
+    return torch.cat([q, g, k.reshape(num_groups, d, *tail), v.reshape(num_groups, d, *tail)], 1).reshape(-1, *tail)
+
+
+def _unpack_qgkv(w, num_heads: int, num_groups: int):
+    r = num_heads // num_groups
+    d = w.shape[0] // (num_groups * (2 * r + 2))
+    tail = w.shape[1:]
+    y = w.reshape(num_groups, 2 * r + 2, d, *tail)
+    q, g = y[:, :r], y[:, r:2 * r]
+    qg = torch.stack([q, g], 2).reshape(num_heads * 2 * d, *tail)
+    return qg.contiguous(), y[:, 2 * r].reshape(-1, *tail).contiguous(), y[:, 2 * r + 1].reshape(-1, *tail).contiguous()
+
+
+def _hybrid_mlp_to_mcore(hf, h, m, out, fam, num_experts):
+    glu = lambda p: torch.cat([hf[p + "gate_proj.weight"], hf[p + "up_proj.weight"]], 0)  # noqa: E731
+    out[m + "pre_mlp_layernorm.weight"] = hf[h + "post_attention_layernorm.weight"]
+    if h + fam.router in hf:
+        out[m + "mlp.router.weight"] = hf[h + fam.router]
+        for e in range(num_experts):
+            p = h + fam.expert_tpl.format(e=e)
+            out[m + f"mlp.experts.linear_fc1.weight{e}"] = glu(p)
+            out[m + f"mlp.experts.linear_fc2.weight{e}"] = hf[p + "down_proj.weight"]
+        if h + fam.shared_expert + "gate_proj.weight" in hf:
+            out[m + "mlp.shared_experts.linear_fc1.weight"] = glu(h + fam.shared_expert)
+            out[m + "mlp.shared_experts.linear_fc2.weight"] = hf[h + fam.shared_expert + "down_proj.weight"]
+        if h + "mlp.shared_expert_gate.weight" in hf:
+            out[m + "mlp.shared_experts.gate_weight"] = hf[h + "mlp.shared_expert_gate.weight"]
+    else:
+        out[m + "mlp.linear_fc1.weight"] = glu(h + "mlp.")
+        out[m + "mlp.linear_fc2.weight"] = hf[h + "mlp.down_proj.weight"]
+
+
+def _hybrid_mlp_to_hf(mc, m, h, out, fam, num_experts):
+    def unglu(w, p):
+        g, u = w.chunk(2, 0)
+        out[p + "gate_proj.weight"], out[p + "up_proj.weight"] = g.contiguous(), u.contiguous()
+
+    out[h + "post_attention_layernorm.weight"] = mc[m + "pre_mlp_layernorm.weight"]
+    if m + "mlp.router.weight" in mc:
+        out[h + fam.router] = mc[m + "mlp.router.weight"]
+        for e in range(num_experts):
+            p = h + fam.expert_tpl.format(e=e)
+            unglu(mc[m + f"mlp.experts.linear_fc1.weight{e}"], p)
+            out[p + "down_proj.weight"] = mc[m + f"mlp.experts.linear_fc2.weight{e}"]
+        if m + "mlp.shared_experts.linear_fc1.weight" in mc:
+            unglu(mc[m + "mlp.shared_experts.linear_fc1.weight"], h + fam.shared_expert)
+            out[h + fam.shared_expert + "down_proj.weight"] = mc[m + "mlp.shared_experts.linear_fc2.weight"]
+        if m + "mlp.shared_experts.gate_weight" in mc:
+            out[h + "mlp.shared_expert_gate.weight"] = mc[m + "mlp.shared_experts.gate_weight"]
+    else:
+        unglu(mc[m + "mlp.linear_fc1.weight"], h + "mlp.")
+        out[h + "mlp.down_proj.weight"] = mc[m + "mlp.linear_fc2.weight"]
+
+
+def _hybrid_to_mcore(hf, fam, num_layers, num_heads, num_groups, padded_vocab, num_experts, tie_embeddings):
+    out: Dict[str, torch.Tensor] = {}
+    emb = hf[fam.hf_prefix + "embed_tokens.weight"]
+    out["embedding.word_embeddings.weight"] = pad_vocab(emb, padded_vocab or emb.shape[0])
+    for i in range(num_layers):
+        h, m = fam.hf_layers.format(i=i), f"decoder.layers.{i}."
+        out[m + "input_layernorm.weight"] = hf[h + "input_layernorm.weight"]
+        if h + "linear_attn.A_log" in hf:
+            for mk, hk in _GDN:
+                out[m + mk] = hf[h + hk]
+            out[m + "self_attention.conv_weight"] = hf[h + "linear_attn.conv1d.weight"].squeeze(1)  # [C, 1, K] -> [C, K]
+        else:
+            out[m + "self_attention.linear_qgkv.weight"] = _pack_qgkv(
+                hf[h + "self_attn.q_proj.weight"], hf[h + "self_attn.k_proj.weight"], hf[h + "self_attn.v_proj.weight"],
+                num_heads, num_groups)
+            out[m + "self_attention.q_layernorm.weight"] = hf[h + "self_attn.q_norm.weight"]
+            out[m + "self_attention.k_layernorm.weight"] = hf[h + "self_attn.k_norm.weight"]
+            out[m + "self_attention.linear_proj.weight"] = hf[h + "self_attn.o_proj.weight"]
+        _hybrid_mlp_to_mcore(hf, h, m, out, fam, num_experts)
+    out["decoder.final_layernorm.weight"] = hf[fam.hf_prefix + "norm.weight"]
+    if not tie_embeddings:
+        head = hf.get("lm_head.weight", emb)
+        out["output_layer.weight"] = pad_vocab(head, padded_vocab or head.shape[0])
+    return out
+
+
+def _hybrid_to_hf(mc, fam, num_layers, num_heads, num_groups, vocab_size, num_experts, tie_embeddings):
+    out: Dict[str, torch.Tensor] = {}
+    strip = lambda w: w[:vocab_size].contiguous() if vocab_size else w  # noqa: E731
+    out[fam.hf_prefix + "embed_tokens.weight"] = strip(mc["embedding.word_embeddings.weight"])
+    for i in range(num_layers):
+        m, h = f"decoder.layers.{i}.", fam.hf_layers.format(i=i)
+        out[h + "input_layernorm.weight"] = mc[m + "input_layernorm.weight"]
+        if m + "self_attention.A_log" in mc:
+            for mk, hk in _GDN:
+                out[h + hk] = mc[m + mk]
+            out[h + "linear_attn.conv1d.weight"] = mc[m + "self_attention.conv_weight"].unsqueeze(1)
+        else:
+            qg, k, v = _unpack_qgkv(mc[m + "self_attention.linear_qgkv.weight"], num_heads, num_groups)
+            out[h + "self_attn.q_proj.weight"], out[h + "self_attn.k_proj.weight"], out[h + "self_attn.v_proj.weight"] = qg, k, v
+            out[h + "self_attn.q_norm.weight"] = mc[m + "self_attention.q_layernorm.weight"]
+            out[h + "self_attn.k_norm.weight"] = mc[m + "self_attention.k_layernorm.weight"]
+            out[h + "self_attn.o_proj.weight"] = mc[m + "self_attention.linear_proj.weight"]
+        _hybrid_mlp_to_hf(mc, m, h, out, fam, num_experts)
+    out[fam.hf_prefix + "norm.weight"] = mc["decoder.final_layernorm.weight"]
+    if not tie_embeddings and "output_layer.weight" in mc:
+        out["lm_head.weight"] = strip(mc["output_layer.weight"])
+    return out
+
+
 def hf_to_mcore(hf: Dict[str, torch.Tensor], fam: FamilyMap, *, num_layers: int, num_heads: int, num_groups: int,
                 padded_vocab: Optional[int] = None, num_experts: Optional[int] = None,
                 tie_embeddings: bool = False) -> Dict[str, torch.Tensor]:
+    hf = _rename(hf, fam, num_layers, True)
+    if fam.hybrid:
+        return _hybrid_to_mcore(hf, fam, num_layers, num_heads, num_groups, padded_vocab, num_experts, tie_embeddings)
     if fam.mla:
         return _mla_to_mcore(hf, fam, num_layers, padded_vocab, num_experts, tie_embeddings)
     out: Dict[str, torch.Tensor] = {}
     emb = hf[fam.hf_prefix + "embed_tokens.weight"]
     out["embedding.word_embeddings.weight"] = pad_vocab(emb, padded_vocab or emb.shape[0])
     for i in range(num_layers):
-        h = fam.hf_layers.format(i=i)
-        m = f"decoder.layers.{i}."
-        out[m + "self_attention.linear_qkv.layer_norm_weight"] = hf[h + "input_layernorm.weight"]
-        out[m + "self_attention.linear_qkv.weight"] = pack_qkv(hf[h + "self_attn.q_proj.weight"],
-                                                               hf[h + "self_attn.k_proj.weight"],
-                                                               hf[h + "self_attn.v_proj.weight"], num_groups)
-        if fam.qkv_bias:
-            out[m + "self_attention.linear_qkv.bias"] = pack_qkv(hf[h + "self_attn.q_proj.bias"],
-                                                                 hf[h + "self_attn.k_proj.bias"],
-                                                                 hf[h + "self_attn.v_proj.bias"], num_groups)
-        if fam.qk_norm:
-            out[m + "self_attention.q_layernorm.weight"] = hf[h + "self_attn.q_norm.weight"]
-            out[m + "self_attention.k_layernorm.weight"] = hf[h + "self_attn.k_norm.weight"]
-        out[m + "self_attention.linear_proj.weight"] = hf[h + "self_attn.o_proj.weight"]
-        post = hf[h + "post_attention_layernorm.weight"]
-        if fam.moe and (h + fam.router) in hf:
-            out[m + "pre_mlp_layernorm.weight"] = post
-            out[m + "mlp.router.weight"] = hf[h + fam.router]
-            for e in range(num_experts):
-                p = h + fam.expert_tpl.format(e=e)
-                out[m + f"mlp.experts.linear_fc1.weight{e}"] = torch.cat([hf[p + "gate_proj.weight"],
-                                                                          hf[p + "up_proj.weight"]], 0)
-                out[m + f"mlp.experts.linear_fc2.weight{e}"] = hf[p + "down_proj.weight"]
-        else:
-            out[m + "mlp.linear_fc1.layer_norm_weight"] = post
-            out[m + "mlp.linear_fc1.weight"] = torch.cat([hf[h + "mlp.gate_proj.weight"], hf[h + "mlp.up_proj.weight"]], 0)
-            out[m + "mlp.linear_fc2.weight"] = hf[h + "mlp.down_proj.weight"]
+        _std_layer_to_mcore(hf, fam.hf_layers.format(i=i), f"decoder.layers.{i}.", out, fam, num_groups, num_experts)
+    k = 0
+    while fam.mtp_layers and fam.mtp_layers.format(i=k) + fam.mtp_names[2][1] in hf:
+        h, m = fam.mtp_layers.format(i=k), f"mtp.layers.{k}."
+        for mk, hk in fam.mtp_names:
+            out[m + mk] = hf[h + hk]
+        _std_layer_to_mcore(hf, h, m + "transformer_layer.", out, fam, num_groups, num_experts)
+        k += 1
     out["decoder.final_layernorm.weight"] = hf[fam.hf_prefix + "norm.weight"]
     if not tie_embeddings:
         head = hf.get("lm_head.weight", emb)
@@ -236,8 +475,10 @@ def hf_to_mcore(hf: Dict[str, torch.Tensor], fam: FamilyMap, *, num_layers: int,
 def mcore_to_hf(mc: Dict[str, torch.Tensor], fam: FamilyMap, *, num_layers: int, num_heads: int, num_groups: int,
                 vocab_size: Optional[int] = None, num_experts: Optional[int] = None,
                 tie_embeddings: bool = False) -> Dict[str, torch.Tensor]:
+    if fam.hybrid:
+        return _hybrid_to_hf(mc, fam, num_layers, num_heads, num_groups, vocab_size, num_experts, tie_embeddings)
     if fam.mla:
-        return _mla_to_hf(mc, fam, num_layers, vocab_size, num_experts, tie_embeddings)
+        return _rename(_mla_to_hf(mc, fam, num_layers, vocab_size, num_experts, tie_embeddings), fam, num_layers, False)
     out: Dict[str, torch.Tensor] = {}
 
     def strip(w):
@@ -245,35 +486,19 @@ def mcore_to_hf(mc: Dict[str, torch.Tensor], fam: FamilyMap, *, num_layers: int,
 
     out[fam.hf_prefix + "embed_tokens.weight"] = strip(mc["embedding.word_embeddings.weight"])
     for i in range(num_layers):
-        h = fam.hf_layers.format(i=i)
-        m = f"decoder.layers.{i}."
-        out[h + "input_layernorm.weight"] = mc[m + "self_attention.linear_qkv.layer_norm_weight"]
-        q, k, v = unpack_qkv(mc[m + "self_attention.linear_qkv.weight"], num_heads, num_groups)
-        out[h + "self_attn.q_proj.weight"], out[h + "self_attn.k_proj.weight"], out[h + "self_attn.v_proj.weight"] = q, k, v
-        if fam.qkv_bias:
-            qb, kb, vb = unpack_qkv(mc[m + "self_attention.linear_qkv.bias"], num_heads, num_groups)
-            out[h + "self_attn.q_proj.bias"], out[h + "self_attn.k_proj.bias"], out[h + "self_attn.v_proj.bias"] = qb, kb, vb
-        if fam.qk_norm:
-            out[h + "self_attn.q_norm.weight"] = mc[m + "self_attention.q_layernorm.weight"]
-            out[h + "self_attn.k_norm.weight"] = mc[m + "self_attention.k_layernorm.weight"]
-        out[h + "self_attn.o_proj.weight"] = mc[m + "self_attention.linear_proj.weight"]
-        if (m + "mlp.router.weight") in mc:
-            out[h + "post_attention_layernorm.weight"] = mc[m + "pre_mlp_layernorm.weight"]
-            out[h + fam.router] = mc[m + "mlp.router.weight"]
-            for e in range(num_experts):
-                p = h + fam.expert_tpl.format(e=e)
-                g, u = mc[m + f"mlp.experts.linear_fc1.weight{e}"].chunk(2, 0)
-                out[p + "gate_proj.weight"], out[p + "up_proj.weight"] = g.contiguous(), u.contiguous()
-                out[p + "down_proj.weight"] = mc[m + f"mlp.experts.linear_fc2.weight{e}"]
-        else:
-            out[h + "post_attention_layernorm.weight"] = mc[m + "mlp.linear_fc1.layer_norm_weight"]
-            g, u = mc[m + "mlp.linear_fc1.weight"].chunk(2, 0)
-            out[h + "mlp.gate_proj.weight"], out[h + "mlp.up_proj.weight"] = g.contiguous(), u.contiguous()
-            out[h + "mlp.down_proj.weight"] = mc[m + "mlp.linear_fc2.weight"]
+        _std_layer_to_hf(mc, f"decoder.layers.{i}.", fam.hf_layers.format(i=i), out, fam, num_heads, num_groups,
+                         num_experts)
+    k = 0
+    while fam.mtp_layers and f"mtp.layers.{k}.eh_proj.weight" in mc:
+        m, h = f"mtp.layers.{k}.", fam.mtp_layers.format(i=k)
+        for mk, hk in fam.mtp_names:
+            out[h + hk] = mc[m + mk]
+        _std_layer_to_hf(mc, m + "transformer_layer.", h, out, fam, num_heads, num_groups, num_experts)
+        k += 1
     out[fam.hf_prefix + "norm.weight"] = mc["decoder.final_layernorm.weight"]
     if not tie_embeddings and "output_layer.weight" in mc:
         out["lm_head.weight"] = strip(mc["output_layer.weight"])
-    return out
+    return _rename(out, fam, num_layers, False)
 
 
 # ---- tensor / pipeline / expert sharding of the unsharded Megatron dict -----------------------
@@ -285,9 +510,26 @@ def tp_rule(key: str):
         return 0, 1
     if key.endswith(("linear_fc1.weight", "linear_fc1.bias")) and ".experts." not in key:
         return 0, (1 if "image_projector." in key else 2)  # the projector's first linear is not gated
-    if key.endswith(("linear_proj.weight", "linear_fc2.weight")) and ".experts." not in key:
+    if key.endswith(("linear_proj.weight", "linear_fc2.weight", "self_attention.out_proj.weight")) and ".experts." not in key:
         return 1, 1
+    # gated full attention packs whole KV groups, GatedDeltaNet projections whole key heads; per-value-head vectors
+    if key.endswith(("linear_qgkv.weight", "in_proj_qkvz.weight", "in_proj_ba.weight", "self_attention.dt_bias",
+                     "self_attention.A_log")):
+        return 0, 1
+    if key.endswith("self_attention.conv_weight"):
+        # channels are type-major [q heads | k heads | v heads]: three blocks of different sizes, each split by head
+        if _GDN_GEOMETRY["blocks"] is None:
+            raise ValueError("tensor-parallel conversion of GatedDeltaNet layers needs set_linear_attention_geometry()")
+        return 0, list(_GDN_GEOMETRY["blocks"])
     return None
+
+
+_GDN_GEOMETRY = {"blocks": None}
+
+
+def set_linear_attention_geometry(num_key_heads: int, key_dim: int, num_value_heads: int, value_dim: int) -> None:
+    """Sizes of the q / k / v channel blocks of the GatedDeltaNet convolution (needed to split it over TP ranks)."""
+    _GDN_GEOMETRY["blocks"] = (num_key_heads * key_dim, num_key_heads * key_dim, num_value_heads * value_dim)
 
 
 def shard_tp(key: str, w: torch.Tensor, rank: int, tp: int) -> torch.Tensor:
@@ -295,6 +537,8 @@ def shard_tp(key: str, w: torch.Tensor, rank: int, tp: int) -> torch.Tensor:
     if rule is None or tp == 1:
         return w
     dim, stride = rule
+    if isinstance(stride, list):
+        return torch.cat([b.chunk(tp, dim)[rank] for b in w.split(stride, dim)], dim).contiguous()
     if stride == 1:
         return w.chunk(tp, dim)[rank].contiguous()
     return torch.cat([b.chunk(tp, dim)[rank] for b in w.chunk(stride, dim)], dim).contiguous()
@@ -305,6 +549,10 @@ def merge_tp(key: str, shards: List[torch.Tensor]) -> torch.Tensor:
     if rule is None or len(shards) == 1:
         return shards[0]
     dim, stride = rule
+    if isinstance(stride, list):
+        tp = len(shards)
+        blocks = [s.split([n // tp for n in stride], dim) for s in shards]
+        return torch.cat([torch.cat([b[j] for b in blocks], dim) for j in range(len(stride))], dim)
     if stride == 1:
         return torch.cat(shards, dim)
     blocks = [s.chunk(stride, dim) for s in shards]
