@@ -95,7 +95,9 @@ def load_hf_checkpoint_online(trainer, hf_dir: str, family: str = "llama3") -> i
 
 
 def _set_geometry(cfg) -> None:
-    """The converter's TP rule for the GatedDeltaNet convolution needs the sizes of its q / k / v channel blocks."""
+    """Two of the converter's TP rules depend on the model: the GatedDeltaNet convolution needs the sizes of its
+    q / k / v channel blocks, and MiniMax's q / k norms over all heads are split with the heads."""
+    _nm().set_qk_norm_over_all_heads(getattr(cfg, "qk_layernorm_full", False))
     if getattr(cfg, "linear_num_key_heads", None):
         _nm().set_linear_attention_geometry(cfg.linear_num_key_heads, cfg.linear_key_head_dim,
                                             cfg.linear_num_value_heads, cfg.linear_value_head_dim)

@@ -56,6 +56,8 @@ def _add_moe_args(p):
     g.add_argument("--moe-router-topk", type=int, default=None)
     g.add_argument("--moe-ffn-hidden-size", type=int, default=None)
     g.add_argument("--moe-shared-expert-intermediate-size", type=int, default=None)
+    g.add_argument("--moe-shared-expert-gate", action="store_true", default=None,
+                   help="sigmoid gate on the shared expert's output (Qwen3-Next, Qwen3.5)")
     g.add_argument("--moe-layer-freq", type=str, default=None)
     g.add_argument("--moe-router-score-function", type=str, default=None, choices=[None, "softmax", "sigmoid"])
     g.add_argument("--moe-router-pre-softmax", action="store_true")

@@ -114,6 +114,7 @@ _ARG_TO_CFG = {
     "vocab_size": "vocab_size", "num_experts": "num_moe_experts", "moe_router_topk": "moe_router_topk",
     "moe_ffn_hidden_size": "moe_ffn_hidden_size",
     "moe_shared_expert_intermediate_size": "moe_shared_expert_intermediate_size",
+    "moe_shared_expert_gate": "moe_shared_expert_gate",
     "moe_router_score_function": "moe_router_score_function",
     "moe_router_bias_update_rate": "moe_router_bias_update_rate", "moe_router_num_groups": "moe_router_num_groups",
     "moe_router_group_topk": "moe_router_group_topk",

@@ -389,7 +389,7 @@ def test_qwen3_next_name_map_roundtrip_and_tp_shards(tmp_path):
 
     ps.destroy_model_parallel()
     ps.initialize_model_parallel(ps.ParallelDims())
-    cfg = get_model_config("tiny-qwen3-next")
+    cfg = get_model_config("tiny-qwen3-next", mtp_num_layers=1)
     fam = nm.FAMILIES["qwen3_next"]
     mc = {k: v for k, v in build_model(cfg).state_dict().items()
           if "local_tokens_per_expert" not in k and "_extra_state" not in k and "expert_bias" not in k}
@@ -401,7 +401,9 @@ def test_qwen3_next_name_map_roundtrip_and_tp_shards(tmp_path):
     assert hf["model.layers.0.linear_attn.conv1d.weight"].dim() == 3
     for name in ("model.layers.0.linear_attn.in_proj_qkvz.weight", "model.layers.0.linear_attn.A_log",
                  "model.layers.0.linear_attn.norm.weight", "model.layers.0.mlp.shared_expert_gate.weight",
-                 "model.layers.0.mlp.shared_expert.down_proj.weight", "model.layers.3.self_attn.k_norm.weight"):
+                 "model.layers.0.mlp.shared_expert.down_proj.weight", "model.layers.3.self_attn.k_norm.weight",
+                 "mtp.fc.weight", "mtp.pre_fc_norm_hidden.weight", "mtp.norm.weight",
+                 "mtp.layers.0.self_attn.q_proj.weight", "mtp.layers.0.mlp.shared_expert_gate.weight"):
         assert name in hf, name
     # head 1's query rows sit at [2 d, 3 d) of the HF projection and in group 0's q block of the packed one
     packed = mc["decoder.layers.3.self_attention.linear_qgkv.weight"]
@@ -416,4 +418,32 @@ def test_qwen3_next_name_map_roundtrip_and_tp_shards(tmp_path):
     torch.save(mc, tmp_path / "full.pt")
     ps.destroy_model_parallel()
     for bad in run_distributed(_hybrid_shard_worker, 2, str(tmp_path)):
+        assert not bad, bad
+
+
+def _minimax_shard_worker(rank, world, tmp):
+    from loongforge_b200.models.registry import build_model, get_model_config
+    from loongforge_b200.parallel import state as ps
+    from tools.convert_checkpoint import name_maps as nm
+
+    cfg = get_model_config("tiny-minimax")
+    nm.set_qk_norm_over_all_heads(cfg.qk_layernorm_full)
+    full = torch.load(os.path.join(tmp, "full.pt"))
+    ps.initialize_model_parallel(ps.ParallelDims(tp=2))
+    local = build_model(cfg).state_dict()
+    return [k for k, w in full.items() if k in local and ".experts." not in k
+            and nm.shard_tp(k, w, rank, 2).shape != local[k].shape]
+
+
+def test_minimax_full_head_qk_norm_is_split_with_the_heads(tmp_path):
+    from loongforge_b200.models.registry import build_model, get_model_config
+    from loongforge_b200.parallel import state as ps
+    from tests.dist_utils import run_distributed
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(ps.ParallelDims())
+    mc = {k: v for k, v in build_model(get_model_config("tiny-minimax")).state_dict().items() if "_extra_state" not in k}
+    torch.save(mc, tmp_path / "full.pt")
+    ps.destroy_model_parallel()
+    for bad in run_distributed(_minimax_shard_worker, 2, str(tmp_path)):
         assert not bad, bad

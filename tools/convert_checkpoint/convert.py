@@ -229,6 +229,7 @@ def main(argv=None):
     hf_dir = a.load_ckpt_path if a.load_platform == "huggingface" else None
     L, H, G, V, E, tie, hf_cfg = _model_dims(a, hf_dir)
     tc = hf_cfg.get("text_config") or hf_cfg
+    nm.set_qk_norm_over_all_heads(a.model_type_custom == "minimax")
     if a.linear_attention_geometry:
         nm.set_linear_attention_geometry(*[int(x) for x in a.linear_attention_geometry.split(",")])
     elif tc.get("linear_num_key_heads"):

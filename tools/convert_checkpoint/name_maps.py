@@ -395,25 +395,57 @@ def _hybrid_mlp_to_hf(mc, m, h, out, fam, num_experts):
         out[h + "mlp.down_proj.weight"] = mc[m + "mlp.linear_fc2.weight"]
 
 
+# Qwen3-Next keeps its multi-token-prediction block under ``mtp.``: four tensors without a layer index, then the layers
+# (qwen3_next_moe_convert.yaml:73-88)
+_HYBRID_MTP = [("enorm.weight", "mtp.pre_fc_norm_embedding.weight"), ("hnorm.weight", "mtp.pre_fc_norm_hidden.weight"),
+               ("eh_proj.weight", "mtp.fc.weight"), ("final_layernorm.weight", "mtp.norm.weight")]
+
+
+def _hybrid_layer_to_mcore(hf, h, m, out, fam, num_heads, num_groups, num_experts):
+    out[m + "input_layernorm.weight"] = hf[h + "input_layernorm.weight"]
+    if h + "linear_attn.A_log" in hf:
+        for mk, hk in _GDN:
+            out[m + mk] = hf[h + hk]
+        out[m + "self_attention.conv_weight"] = hf[h + "linear_attn.conv1d.weight"].squeeze(1)  # [C, 1, K] -> [C, K]
+    else:
+        out[m + "self_attention.linear_qgkv.weight"] = _pack_qgkv(
+            hf[h + "self_attn.q_proj.weight"], hf[h + "self_attn.k_proj.weight"], hf[h + "self_attn.v_proj.weight"],
+            num_heads, num_groups)
+        out[m + "self_attention.q_layernorm.weight"] = hf[h + "self_attn.q_norm.weight"]
+        out[m + "self_attention.k_layernorm.weight"] = hf[h + "self_attn.k_norm.weight"]
+        out[m + "self_attention.linear_proj.weight"] = hf[h + "self_attn.o_proj.weight"]
+    _hybrid_mlp_to_mcore(hf, h, m, out, fam, num_experts)
+
+
+def _hybrid_layer_to_hf(mc, m, h, out, fam, num_heads, num_groups, num_experts):
+    out[h + "input_layernorm.weight"] = mc[m + "input_layernorm.weight"]
+    if m + "self_attention.A_log" in mc:
+        for mk, hk in _GDN:
+            out[h + hk] = mc[m + mk]
+        out[h + "linear_attn.conv1d.weight"] = mc[m + "self_attention.conv_weight"].unsqueeze(1)
+    else:
+        qg, k, v = _unpack_qgkv(mc[m + "self_attention.linear_qgkv.weight"], num_heads, num_groups)
+        out[h + "self_attn.q_proj.weight"], out[h + "self_attn.k_proj.weight"], out[h + "self_attn.v_proj.weight"] = qg, k, v
+        out[h + "self_attn.q_norm.weight"] = mc[m + "self_attention.q_layernorm.weight"]
+        out[h + "self_attn.k_norm.weight"] = mc[m + "self_attention.k_layernorm.weight"]
+        out[h + "self_attn.o_proj.weight"] = mc[m + "self_attention.linear_proj.weight"]
+    _hybrid_mlp_to_hf(mc, m, h, out, fam, num_experts)
+
+
 def _hybrid_to_mcore(hf, fam, num_layers, num_heads, num_groups, padded_vocab, num_experts, tie_embeddings):
     out: Dict[str, torch.Tensor] = {}
     emb = hf[fam.hf_prefix + "embed_tokens.weight"]
     out["embedding.word_embeddings.weight"] = pad_vocab(emb, padded_vocab or emb.shape[0])
+    args = (fam, num_heads, num_groups, num_experts)
     for i in range(num_layers):
-        h, m = fam.hf_layers.format(i=i), f"decoder.layers.{i}."
-        out[m + "input_layernorm.weight"] = hf[h + "input_layernorm.weight"]
-        if h + "linear_attn.A_log" in hf:
-            for mk, hk in _GDN:
-                out[m + mk] = hf[h + hk]
-            out[m + "self_attention.conv_weight"] = hf[h + "linear_attn.conv1d.weight"].squeeze(1)  # [C, 1, K] -> [C, K]
-        else:
-            out[m + "self_attention.linear_qgkv.weight"] = _pack_qgkv(
-                hf[h + "self_attn.q_proj.weight"], hf[h + "self_attn.k_proj.weight"], hf[h + "self_attn.v_proj.weight"],
-                num_heads, num_groups)
-            out[m + "self_attention.q_layernorm.weight"] = hf[h + "self_attn.q_norm.weight"]
-            out[m + "self_attention.k_layernorm.weight"] = hf[h + "self_attn.k_norm.weight"]
-            out[m + "self_attention.linear_proj.weight"] = hf[h + "self_attn.o_proj.weight"]
-        _hybrid_mlp_to_mcore(hf, h, m, out, fam, num_experts)
+        _hybrid_layer_to_mcore(hf, fam.hf_layers.format(i=i), f"decoder.layers.{i}.", out, *args)
+    if "mtp.fc.weight" in hf:  # one set of the four extra tensors; the layers follow under mtp.layers.{k}.
+        for mk, hk in _HYBRID_MTP:
+            out["mtp.layers.0." + mk] = hf[hk]
+        k = 0
+        while f"mtp.layers.{k}.input_layernorm.weight" in hf:
+            _hybrid_layer_to_mcore(hf, f"mtp.layers.{k}.", f"mtp.layers.{k}.transformer_layer.", out, *args)
+            k += 1
     out["decoder.final_layernorm.weight"] = hf[fam.hf_prefix + "norm.weight"]
     if not tie_embeddings:
         head = hf.get("lm_head.weight", emb)
@@ -425,20 +457,15 @@ def _hybrid_to_hf(mc, fam, num_layers, num_heads, num_groups, vocab_size, num_ex
     out: Dict[str, torch.Tensor] = {}
     strip = lambda w: w[:vocab_size].contiguous() if vocab_size else w  # noqa: E731
     out[fam.hf_prefix + "embed_tokens.weight"] = strip(mc["embedding.word_embeddings.weight"])
+    args = (fam, num_heads, num_groups, num_experts)
     for i in range(num_layers):
-        m, h = f"decoder.layers.{i}.", fam.hf_layers.format(i=i)
-        out[h + "input_layernorm.weight"] = mc[m + "input_layernorm.weight"]
-        if m + "self_attention.A_log" in mc:
-            for mk, hk in _GDN:
-                out[h + hk] = mc[m + mk]
-            out[h + "linear_attn.conv1d.weight"] = mc[m + "self_attention.conv_weight"].unsqueeze(1)
-        else:
-            qg, k, v = _unpack_qgkv(mc[m + "self_attention.linear_qgkv.weight"], num_heads, num_groups)
-            out[h + "self_attn.q_proj.weight"], out[h + "self_attn.k_proj.weight"], out[h + "self_attn.v_proj.weight"] = qg, k, v
-            out[h + "self_attn.q_norm.weight"] = mc[m + "self_attention.q_layernorm.weight"]
-            out[h + "self_attn.k_norm.weight"] = mc[m + "self_attention.k_layernorm.weight"]
-            out[h + "self_attn.o_proj.weight"] = mc[m + "self_attention.linear_proj.weight"]
-        _hybrid_mlp_to_hf(mc, m, h, out, fam, num_experts)
+        _hybrid_layer_to_hf(mc, f"decoder.layers.{i}.", fam.hf_layers.format(i=i), out, *args)
+    if "mtp.layers.0.eh_proj.weight" in mc:
+        if "mtp.layers.1.eh_proj.weight" in mc:
+            raise NotImplementedError("the Hugging Face layout of this family holds one multi-token-prediction block")
+        for mk, hk in _HYBRID_MTP:
+            out[hk] = mc["mtp.layers.0." + mk]
+        _hybrid_layer_to_hf(mc, "mtp.layers.0.transformer_layer.", "mtp.layers.0.", out, *args)
     out[fam.hf_prefix + "norm.weight"] = mc["decoder.final_layernorm.weight"]
     if not tie_embeddings and "output_layer.weight" in mc:
         out["lm_head.weight"] = strip(mc["output_layer.weight"])
@@ -516,6 +543,8 @@ def tp_rule(key: str):
     if key.endswith(("linear_qgkv.weight", "in_proj_qkvz.weight", "in_proj_ba.weight", "self_attention.dt_bias",
                      "self_attention.A_log")):
         return 0, 1
+    if _QK_NORM_FULL["on"] and key.endswith(("self_attention.q_layernorm.weight", "self_attention.k_layernorm.weight")):
+        return 0, 1  # MiniMax: one norm over all heads, the weight is split with the heads
     if key.endswith("self_attention.conv_weight"):
         # channels are type-major [q heads | k heads | v heads]: three blocks of different sizes, each split by head
         if _GDN_GEOMETRY["blocks"] is None:
@@ -525,6 +554,12 @@ def tp_rule(key: str):
 
 
 _GDN_GEOMETRY = {"blocks": None}
+_QK_NORM_FULL = {"on": False}
+
+
+def set_qk_norm_over_all_heads(flag: bool) -> None:
+    """MiniMax normalises q (and k) over ALL heads at once; its norm weights are then sharded over TP ranks."""
+    _QK_NORM_FULL["on"] = bool(flag)
 
 
 def set_linear_attention_geometry(num_key_heads: int, key_dim: int, num_value_heads: int, value_dim: int) -> None:
