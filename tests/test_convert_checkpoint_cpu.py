@@ -447,3 +447,30 @@ def test_minimax_full_head_qk_norm_is_split_with_the_heads(tmp_path):
     ps.destroy_model_parallel()
     for bad in run_distributed(_minimax_shard_worker, 2, str(tmp_path)):
         assert not bad, bad
+
+
+def test_qwen3_vl_vision_tower_and_deepstack_name_map_roundtrip():
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.models.vision_zoo import DeepStackMergers, build_vision_encoder
+    from loongforge_b200.parallel import state as ps
+    from tools.convert_checkpoint import name_maps as nm
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(ps.ParallelDims())
+    cfg = get_model_config("tiny-vit")
+    vit = {k: v for k, v in build_vision_encoder("qwen3_vl_vit", cfg, deepstack_indexes=(0, 1)).state_dict().items()
+           if "_extra_state" not in k}
+    taps = dict(DeepStackMergers(cfg, 96, 2).state_dict())
+    hf = nm.qwen3_vision_to_hf(vit, taps, num_layers=cfg.num_layers, num_heads=cfg.num_attention_heads)
+    for name in ("model.visual.pos_embed.weight", "model.visual.blocks.0.attn.qkv.weight", "model.visual.blocks.1.norm2.weight",
+                 "model.visual.blocks.0.mlp.linear_fc1.bias", "model.visual.deepstack_merger_list.1.norm.bias",
+                 "model.visual.deepstack_merger_list.0.linear_fc2.weight"):
+        assert name in hf, name
+    d = cfg.hidden_size // cfg.num_attention_heads
+    # HF rows are [q of all heads; k of all heads; v of all heads]; ours are per head [q_h, k_h, v_h]
+    assert torch.equal(hf["model.visual.blocks.0.attn.qkv.weight"][d:2 * d],
+                       vit["decoder.layers.0.self_attention.linear_qkv.weight"][3 * d:4 * d])
+    vit2, taps2 = nm.qwen3_vision_to_mcore(hf, num_layers=cfg.num_layers, num_heads=cfg.num_attention_heads)
+    assert set(vit2) == set(vit) and all(torch.equal(vit2[k], vit[k]) for k in vit)
+    assert set(taps2) == set(taps) and all(torch.equal(taps2[k], taps[k]) for k in taps)
+    ps.destroy_model_parallel()

@@ -677,3 +677,71 @@ def vlm_mcore_to_hf(mc: Dict[str, torch.Tensor], fam: FamilyMap, *, vit_layers: 
     out.update(qwen_vision_to_hf({k[len("encoder_model."):]: v for k, v in mc.items() if k.startswith("encoder_model.")},
                                  vp, vit_layers, vit_heads))
     return out
+
+
+# ---- Qwen3-VL vision tower with DeepStack taps --------------------------------------------------------
+# (configs/models/image_encoder/ckpt_convert/qwen3_vit_convert.yaml:31-90)
+_Q3VIT_LAYER = [("self_attention.linear_qkv.layer_norm_weight", "norm1.weight"),
+                ("self_attention.linear_qkv.layer_norm_bias", "norm1.bias"),
+                ("self_attention.linear_proj.weight", "attn.proj.weight"), ("self_attention.linear_proj.bias", "attn.proj.bias"),
+                ("mlp.linear_fc1.layer_norm_weight", "norm2.weight"), ("mlp.linear_fc1.layer_norm_bias", "norm2.bias"),
+                ("mlp.linear_fc1.weight", "mlp.linear_fc1.weight"), ("mlp.linear_fc1.bias", "mlp.linear_fc1.bias"),
+                ("mlp.linear_fc2.weight", "mlp.linear_fc2.weight"), ("mlp.linear_fc2.bias", "mlp.linear_fc2.bias")]
+_Q3VIT_TOP = [("pos_embed", "pos_embed.weight"), ("patch_embed.proj.weight", "patch_embed.proj.weight"),
+              ("patch_embed.proj.bias", "patch_embed.proj.bias")]
+_Q3VIT_TAP = [("norms.{k}.weight", "deepstack_merger_list.{k}.norm.weight"),
+              ("norms.{k}.bias", "deepstack_merger_list.{k}.norm.bias"),
+              ("fc1.{k}.weight", "deepstack_merger_list.{k}.linear_fc1.weight"),
+              ("fc1.{k}.bias", "deepstack_merger_list.{k}.linear_fc1.bias"),
+              ("fc2.{k}.weight", "deepstack_merger_list.{k}.linear_fc2.weight"),
+              ("fc2.{k}.bias", "deepstack_merger_list.{k}.linear_fc2.bias")]
+
+
+def qwen3_vision_to_hf(vit: Dict[str, torch.Tensor], taps: Dict[str, torch.Tensor], *, num_layers: int, num_heads: int,
+                       prefix: str = "model.visual.") -> Dict[str, torch.Tensor]:
+    """State dicts of the vision tower and of its DeepStack mergers -> ``model.visual.*`` tensors. Entries that a
+    model does not have (norm biases, patch-embedding bias) are skipped."""
+    out: Dict[str, torch.Tensor] = {}
+    for mk, hk in _Q3VIT_TOP:
+        if mk in vit:
+            out[prefix + hk] = vit[mk]
+    for i in range(num_layers):
+        m, h = f"decoder.layers.{i}.", f"{prefix}blocks.{i}."
+        for mk, hk in _Q3VIT_LAYER:
+            if m + mk in vit:
+                out[h + hk] = vit[m + mk]
+        for suffix in ("weight", "bias"):
+            if m + f"self_attention.linear_qkv.{suffix}" in vit:
+                out[h + f"attn.qkv.{suffix}"] = _vit_unpack_qkv(vit[m + f"self_attention.linear_qkv.{suffix}"], num_heads)
+    k = 0
+    while f"fc1.{k}.weight" in taps:
+        for mk, hk in _Q3VIT_TAP:
+            if mk.format(k=k) in taps:
+                out[prefix + hk.format(k=k)] = taps[mk.format(k=k)]
+        k += 1
+    return out
+
+
+def qwen3_vision_to_mcore(hf: Dict[str, torch.Tensor], *, num_layers: int, num_heads: int,
+                          prefix: str = "model.visual."):
+    """Inverse of :func:`qwen3_vision_to_hf`: (vision tower state dict, DeepStack merger state dict)."""
+    vit: Dict[str, torch.Tensor] = {}
+    taps: Dict[str, torch.Tensor] = {}
+    for mk, hk in _Q3VIT_TOP:
+        if prefix + hk in hf:
+            vit[mk] = hf[prefix + hk]
+    for i in range(num_layers):
+        m, h = f"decoder.layers.{i}.", f"{prefix}blocks.{i}."
+        for mk, hk in _Q3VIT_LAYER:
+            if h + hk in hf:
+                vit[m + mk] = hf[h + hk]
+        for suffix in ("weight", "bias"):
+            if h + f"attn.qkv.{suffix}" in hf:
+                vit[m + f"self_attention.linear_qkv.{suffix}"] = _vit_pack_qkv(hf[h + f"attn.qkv.{suffix}"], num_heads)
+    k = 0
+    while f"{prefix}deepstack_merger_list.{k}.linear_fc1.weight" in hf:
+        for mk, hk in _Q3VIT_TAP:
+            if prefix + hk.format(k=k) in hf:
+                taps[mk.format(k=k)] = hf[prefix + hk.format(k=k)]
+        k += 1
+    return vit, taps
