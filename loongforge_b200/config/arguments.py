@@ -137,7 +137,10 @@ def _add_training_args(p):
     g.add_argument("--adam-beta2", type=float, default=0.999)
     g.add_argument("--adam-eps", type=float, default=1e-8)
     g.add_argument("--clip-grad", type=float, default=1.0)
-    g.add_argument("--optimizer", type=str, default="adam")
+    g.add_argument("--optimizer", type=str, default="adam", choices=["adam", "sgd"])
+    g.add_argument("--sgd-momentum", type=float, default=0.9)
+    g.add_argument("--optimizer-offload-fraction", type=float, default=1.0,
+                   help="with --optimizer-cpu-offload: part of the optimizer state kept on the host")
     g.add_argument("--use-precision-aware-optimizer", action="store_true")
     g.add_argument("--exp-avg-dtype", type=str, default="fp32", choices=["fp32", "bf16"])
     g.add_argument("--exp-avg-sq-dtype", type=str, default="fp32", choices=["fp32", "bf16"])

@@ -217,6 +217,8 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
         log_memory_stats=bool(getattr(args, "log_memory_stats", False)),
         dp_balance=bool(getattr(args, "use_vlm_dp_balance", False)),
         optimizer_cpu_offload=bool(getattr(args, "optimizer_cpu_offload", False)),
+        optimizer_offload_fraction=float(getattr(args, "optimizer_offload_fraction", 1.0) or 0.0),
+        optimizer=(getattr(args, "optimizer", None) or "adam").lower(), sgd_momentum=getattr(args, "sgd_momentum", 0.9),
         use_fsdp=bool(getattr(args, "use_torch_fsdp2", False) or getattr(args, "use_megatron_fsdp", False)),
         fsdp_sharding_strategy=getattr(args, "data_parallel_sharding_strategy", None) or "optim_grads_params",
         use_distributed_optimizer=args.use_distributed_optimizer, overlap_grad_reduce=args.overlap_grad_reduce,

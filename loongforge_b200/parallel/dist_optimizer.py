@@ -43,17 +43,23 @@ class OptimizerConfig:
     # fp32 masters and Adam moments in pinned host memory, updated by the native host AdamW; per step the gradient
     # shard goes device -> host and the refreshed weights host -> device on a side stream
     cpu_offload: bool = False
+    # part of the optimizer state (by elements, whole shards) that lives on the host when cpu_offload is on
+    # (reference: --optimizer-offload-fraction, docs/source/features/optimizer_support.md)
+    offload_fraction: float = 1.0
+    optimizer: str = "adam"  # "adam" (AdamW) or "sgd" (momentum in the first-moment buffer)
+    sgd_momentum: float = 0.9
     no_weight_decay_cond: Optional[object] = None  # callable(name, param) -> bool
 
 
 class _ShardState:
     """Optimizer state of one bucket shard, split into segments that share a weight decay."""
 
-    def __init__(self, buf: ParamAndGradBuffer, b: Bucket, s: int, e: int, cfg: OptimizerConfig, sharded: bool):
+    def __init__(self, buf: ParamAndGradBuffer, b: Bucket, s: int, e: int, cfg: OptimizerConfig, sharded: bool,
+                 offload: Optional[bool] = None):
         self.buf, self.bucket, self.start, self.end = buf, b, s, e
         dev = buf.param_data.device
         n = e - s
-        self.offload = cfg.cpu_offload
+        self.offload = cfg.cpu_offload if offload is None else offload
         self.remainder = cfg.master_as_remainder and buf.param_data.dtype == torch.bfloat16 and not self.offload
         if self.offload:
             pin = dev.type == "cuda"
@@ -109,15 +115,24 @@ class DistributedOptimizer:
         self.state = ps.get_state(parallel_state)
         self.sharded = ddp_models[0].cfg.use_distributed_optimizer
         self.shards: List[_ShardState] = []
+        if cfg.optimizer not in ("adam", "sgd"):
+            raise ValueError(f"unknown optimizer {cfg.optimizer!r}: adam or sgd")
+        if cfg.optimizer == "sgd" and (cfg.cpu_offload or cfg.master_as_remainder):
+            raise ValueError("sgd runs with device-resident fp32 master weights (no offload, no remainder masters)")
+        ranges = []
         for mi, m in enumerate(ddp_models):
             for buf in m._all_buffers:
                 for b in buf.buckets:
-                    if self.sharded:
-                        s, e = buf.shard_range(b)
-                    else:
-                        s, e = b.start, b.end
-                    self.shards.append(_ShardState(buf, b, s, e, cfg, self.sharded))
-                    self.shards[-1].chunk = mi
+                    s, e = buf.shard_range(b) if self.sharded else (b.start, b.end)
+                    ranges.append((mi, buf, b, s, e))
+        # shards go to the host in order until the requested fraction of the elements is reached
+        budget = cfg.offload_fraction * sum(e - s for *_, s, e in ranges) if cfg.cpu_offload else 0.0
+        moved = 0
+        for mi, buf, b, s, e in ranges:
+            off = cfg.cpu_offload and moved < budget
+            moved += (e - s) if off else 0
+            self.shards.append(_ShardState(buf, b, s, e, cfg, self.sharded, offload=off))
+            self.shards[-1].chunk = mi
         # callables run after the data-parallel gradient reduction and before the norm / update (for reductions over
         # other groups that need the final gradients, e.g. the embedding copies of the first and last pipeline stage)
         self.post_sync_hooks: List = []
@@ -253,6 +268,16 @@ class DistributedOptimizer:
                 else:
                     runs.append([lo, hi, use_wd])
             for lo, hi, use_wd in runs:
+                if cfg.optimizer == "sgd":
+                    # v = mu v + (g + wd w); w -= lr v   (momentum kept in the first-moment buffer)
+                    w, v = sh.master[lo:hi], sh.exp_avg[lo:hi]
+                    d = g[lo:hi].float() * clip
+                    if use_wd and wd:
+                        d = d + wd * w
+                    v.copy_((cfg.sgd_momentum * v.float() + d).to(v.dtype))
+                    w.add_(v.float(), alpha=-lr)
+                    out[lo:hi].copy_(w)
+                    continue
                 if self._peer_ok(sh):
                     self._peer_adam_and_gather(sh, lo, hi, lr, wd if use_wd else 0.0, clip)
                     continue
@@ -286,6 +311,8 @@ class DistributedOptimizer:
         if dev.is_cuda and self._offload_stream is None:
             self._offload_stream = torch.cuda.Stream()
         for sh in self.shards:
+            if not sh.offload:
+                continue
             g = sh.buf.grad_data[sh.start:sh.end]
             if g.is_cuda:
                 self._offload_stream.wait_stream(torch.cuda.current_stream())

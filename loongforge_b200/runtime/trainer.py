@@ -61,6 +61,9 @@ class TrainConfig:
     exp_avg_sq_dtype: torch.dtype = torch.float32
     master_as_remainder: bool = False
     optimizer_cpu_offload: bool = False  # masters + Adam moments on the host, native host AdamW
+    optimizer_offload_fraction: float = 1.0  # part of the optimizer state (whole shards) that goes to the host
+    optimizer: str = "adam"  # adam | sgd
+    sgd_momentum: float = 0.9
     fp8_policy_file: Optional[str] = None  # JSON rules: which linear kinds run FP8 (runtime/fp8_policy.py)
     log_memory_stats: bool = False  # memory fields in the log line also on the host (they are always there on GPUs)
     no_save_optim: bool = False  # checkpoints without optimizer state / RNG state
@@ -215,7 +218,9 @@ class Trainer:
                                adam_beta2=t.adam_beta2, adam_eps=t.adam_eps, clip_grad=t.clip_grad,
                                exp_avg_dtype=t.exp_avg_dtype, exp_avg_sq_dtype=t.exp_avg_sq_dtype,
                                overlap_param_gather=t.overlap_param_gather,
-                               master_as_remainder=t.master_as_remainder, cpu_offload=t.optimizer_cpu_offload)
+                               master_as_remainder=t.master_as_remainder and t.optimizer != "sgd",
+                               cpu_offload=t.optimizer_cpu_offload, offload_fraction=t.optimizer_offload_fraction,
+                               optimizer=t.optimizer, sgd_momentum=t.sgd_momentum)
         return DistributedOptimizer(self.models, ocfg)
 
     # ------------------------------------------------------------------ default LLM pretrain step

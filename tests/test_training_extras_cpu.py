@@ -129,21 +129,28 @@ def test_cli_hooks_end_to_end(tmp_path):
     assert recs and all(r["module"].endswith("decoder.layers.0.mlp") for r in recs)
 
 
-def _offload_traj(rank, world, offload):
+def _offload_traj(rank, world, offload, fraction=1.0):
     from loongforge_b200.data.synthetic import synthetic_batch_iterator
     from loongforge_b200.models.registry import get_model_config
     from loongforge_b200.runtime.trainer import TrainConfig, Trainer
 
     cfg = get_model_config("tiny-llama")
     tc = TrainConfig(micro_batch_size=1, global_batch_size=4, seq_length=64, train_iters=4, lr=1e-3, clip_grad=0.5,
-                     weight_decay=0.1, log_interval=1000, optimizer_cpu_offload=offload)
+                     weight_decay=0.1, log_interval=1000, optimizer_cpu_offload=offload,
+                     optimizer_offload_fraction=fraction, ddp_bucket_size=20000)
     tr = Trainer(cfg, tc)
     st = tr.st
     it = synthetic_batch_iterator(cfg.vocab_size, 64, 1, dp_rank=st.dp_rank, dp_size=st.dp_size, seed=11,
                                   pin_memory=False)
     out = [tr.train_step(it) for _ in range(4)]
-    if offload:
-        assert all(sh.offload and sh.exp_avg.device.type == "cpu" for sh in tr.optimizer.shards)
+    shards = tr.optimizer.shards
+    if offload and fraction >= 1.0:
+        assert all(sh.offload and sh.exp_avg.device.type == "cpu" for sh in shards)
+    elif offload:
+        total = sum(sh.end - sh.start for sh in shards)
+        on_host = sum(sh.end - sh.start for sh in shards if sh.offload)
+        assert len(shards) > 2 and 0 < on_host < total and on_host >= fraction * total - max(
+            sh.end - sh.start for sh in shards), (on_host, total)
     return [(m["lm loss"], m["grad_norm"]) for m in out]
 
 
@@ -155,6 +162,47 @@ def test_optimizer_cpu_offload_matches_device_optimizer():
     b = run_distributed(_offload_traj, 2, True)[0]
     for (l0, g0), (l1, g1) in zip(a, b):
         assert abs(l0 - l1) < 1e-5 * max(1, abs(l0)) and abs(g0 - g1) < 1e-4 * max(1, abs(g0)), (a, b)
+
+
+def test_optimizer_offload_fraction_keeps_part_of_the_state_on_the_device():
+    from dist_utils import run_distributed
+
+    a = run_distributed(_offload_traj, 2, False)[0]
+    b = run_distributed(_offload_traj, 2, True, 0.5)[0]
+    for (l0, g0), (l1, g1) in zip(a, b):
+        assert abs(l0 - l1) < 1e-5 * max(1, abs(l0)) and abs(g0 - g1) < 1e-4 * max(1, abs(g0)), (a, b)
+
+
+def test_sgd_with_momentum_follows_the_torch_update_rule():
+    """--optimizer sgd on the flat-buffer optimizer: with the gradients read back from the gradient buffer, the
+    parameters follow torch.optim.SGD (momentum, weight decay) step by step."""
+    import torch
+
+    from loongforge_b200.data.synthetic import synthetic_batch_iterator
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel import state as ps
+    from loongforge_b200.runtime.trainer import TrainConfig, Trainer
+
+    ps.destroy_model_parallel()
+    cfg = get_model_config("tiny-llama")
+    tc = TrainConfig(micro_batch_size=2, global_batch_size=2, seq_length=32, train_iters=3, lr=0.05, min_lr=0.05,
+                     lr_decay_style="constant", clip_grad=0.0, weight_decay=0.01, log_interval=1000, optimizer="sgd",
+                     sgd_momentum=0.8)
+    tr = Trainer(cfg, tc)
+    named = dict(tr.models[0].module.named_parameters())
+    ref = {n: torch.nn.Parameter(p.detach().clone().float()) for n, p in named.items()}
+    groups = [{"params": [ref[n] for n, p in named.items() if p.dim() > 1], "weight_decay": 0.01},
+              {"params": [ref[n] for n, p in named.items() if p.dim() <= 1], "weight_decay": 0.0}]
+    opt = torch.optim.SGD(groups, lr=0.05, momentum=0.8)
+    it = synthetic_batch_iterator(cfg.vocab_size, 32, 2, seed=3, pin_memory=False)
+    for step in range(3):
+        tr.train_step(it)
+        for n, p in named.items():   # the gradient buffer still holds this step's reduced gradients
+            ref[n].grad = p.main_grad.detach().clone().float()
+        opt.step()
+        worst = max(float((ref[n].detach() - p.detach().float()).abs().max()) for n, p in named.items())
+        assert worst < 1e-5, (step, worst)
+    ps.destroy_model_parallel()
 
 
 def _fsdp_traj(rank, world, use_fsdp, tmp):
