@@ -8,6 +8,7 @@ communication schemes.
 * ``cp_comm_type``:
     - ``"p2p"``      ring of KV blocks with online-softmax merging of partial results;
     - ``"allgather"`` K/V all-gathered once (backward reduce-scatters dK/dV);
+    - ``"a2a+p2p"``   two levels: Ulysses inside blocks of neighbouring ranks, the ring between the blocks
     - ``"a2a"``       Ulysses: all-to-all from sequence-sharded/all-heads to full-sequence/head-sharded,
                       the ordinary attention kernel, and the inverse all-to-all
                       (loongforge/train/validators.py:391-433 maps --context-parallel-ulysses-degree here).
@@ -30,9 +31,30 @@ from . import state as ps
 _CFG = {"comm_type": "auto"}
 
 
-def set_cp_comm_type(name: str):
-    assert name in ("auto", "p2p", "allgather", "a2a")
-    _CFG["comm_type"] = name
+def set_cp_comm_type(name: str, ulysses_degree: Optional[int] = None):
+    """``"a2a+p2p"`` is the two-level scheme: Ulysses all-to-all among `ulysses_degree` neighbouring ranks, the KV
+    ring between those blocks. Its process groups are created here, so every rank of the job must make this call."""
+    assert name in ("auto", "p2p", "allgather", "a2a", "a2a+p2p")
+    _CFG["comm_type"], _CFG["ulysses_degree"] = name, ulysses_degree
+    if name == "a2a+p2p" and ps.model_parallel_is_initialized():
+        ensure_cp_groups()
+
+
+def ensure_cp_groups() -> None:
+    """Create the process groups of the two-level scheme once the parallel state exists (the trainers call this right
+    after they initialise it; a no-op for the other communication types)."""
+    if _CFG["comm_type"] != "a2a+p2p":
+        return
+    st = ps.get_state()
+    u = _CFG.get("ulysses_degree")
+    if not u or st.dims.cp % u:
+        raise ValueError("a2a+p2p needs a Ulysses degree that divides the context parallel size")
+    if u == st.dims.cp:
+        _CFG["comm_type"] = "a2a"
+    elif u == 1:
+        _CFG["comm_type"] = "p2p"
+    elif "cp_inner" not in st.groups:
+        st.create_hierarchical_cp_groups(u)
 
 
 def cp_chunk_indices(seq_len: int, cp: int, rank: int, device=None) -> torch.Tensor:
@@ -129,6 +151,16 @@ def ring_attention(q, k, v, *, causal=True, scale=None, cu_seqlens=None, row_len
     if kind == "a2a":
         return _ulysses(q, k, v, causal, scale, cp, rank, g)
     pos, seg = _positions(q.shape[0], cp, rank, q.device, cu_seqlens, row_length)
+    if kind == "a2a+p2p":
+        # inner all-to-all: all tokens of the block's ranks, a slice of the heads; the ring then runs between the
+        # blocks with explicit positions (and segment ids), so the gathered token order needs no permutation
+        gi, go = st.group("cp_inner"), st.group("cp_outer")
+        n_outer = len(st.ranks("cp_outer"))
+        qh, kh, vh = (M.all_to_all_sp2hp(t, gi) for t in (q, k, v))
+        pos_h = M._all_gather_dim0(pos, gi)
+        seg_h = M._all_gather_dim0(seg, gi) if seg is not None else None
+        o = _RingP2P.apply(qh, kh, vh, pos_h, seg_h, scale, causal, n_outer, st.rank_in("cp_outer"), go)
+        return M.all_to_all_hp2sp(o, gi)
     if kind == "allgather":
         k_all = M.gather_from_sequence_parallel_region(k, g, True)
         v_all = M.gather_from_sequence_parallel_region(v, g, True)

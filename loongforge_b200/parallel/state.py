@@ -141,6 +141,23 @@ class ParallelState:
                         mine = g
                 self.gloo[kind] = mine
 
+    def create_hierarchical_cp_groups(self, inner: int, rank_offset: int = 0) -> None:
+        """Two-level context parallelism: every context-parallel group of size cp is cut into cp / inner blocks of
+        `inner` consecutive ranks ("cp_inner": Ulysses all-to-all, the ranks closest to one another) and `inner`
+        strided sets of cp / inner ranks ("cp_outer": the KV ring). Collective: every rank of the job calls it."""
+        cp = self.dims.cp
+        if inner < 1 or cp % inner:
+            raise ValueError(f"context parallel size {cp} must divide by the inner (Ulysses) degree {inner}")
+        backend = dist.get_backend() if dist.is_initialized() else None
+        for kind, make in (("cp_inner", lambda r: [r[b * inner:(b + 1) * inner] for b in range(cp // inner)]),
+                           ("cp_outer", lambda r: [r[i::inner] for i in range(inner)])):
+            self.groups[kind], self.group_ranks[kind] = None, [self.rank]
+            for ranks in self._all_rank_lists(rank_offset)["cp"]:
+                for sub in make(ranks):
+                    g = dist.new_group(sub, backend=backend) if (len(sub) > 1 and dist.is_initialized()) else None
+                    if self.rank in sub:
+                        self.groups[kind], self.group_ranks[kind] = g, sub
+
     # ------------------------------------------------------------------ accessors
     def group(self, kind: str):
         return self.groups.get(kind)

@@ -131,6 +131,8 @@ class Trainer:
         dims = dims or ParallelDims()
         if not ps.model_parallel_is_initialized():
             ps.initialize_model_parallel(dims, gloo_groups=False)
+            from ..parallel.context_parallel import ensure_cp_groups
+            ensure_cp_groups()
         self.st = ps.get_state()
         self.world = self.st.world_size
         self.dp = self.st.dp_size

@@ -84,6 +84,8 @@ class VLMTrainer(Trainer):
         dims = dims or ParallelDims()
         if not ps.model_parallel_is_initialized():
             ps.initialize_model_parallel(dims)
+            from ..parallel.context_parallel import ensure_cp_groups
+            ensure_cp_groups()
             # the encoder gets its own tensor-parallel degree (must divide the decoder's)
             ps.create_parallel_state(ENCODER_STATE, ParallelDims(tp=encoder_tp, pp=dims.pp, cp=dims.cp))
         if train_cfg.bf16:

@@ -32,7 +32,9 @@ def main(argv: Optional[List[str]] = None) -> int:
             print(f"WARNING: {note}", flush=True)
     if args.cp_comm_type not in ("auto", None):
         from .parallel.context_parallel import set_cp_comm_type
-        set_cp_comm_type(args.cp_comm_type if args.cp_comm_type in ("p2p", "allgather", "a2a") else "auto")
+        kinds = ("p2p", "allgather", "a2a", "a2a+p2p")
+        set_cp_comm_type(args.cp_comm_type if args.cp_comm_type in kinds else "auto",
+                         getattr(args, "context_parallel_ulysses_degree", None))
     if args.attention_backend in ("native", "sdpa"):
         from .ops.functional import set_attention_impl
         set_attention_impl(args.attention_backend)

@@ -102,3 +102,23 @@ def test_context_parallel_matches_single_process(comm):
     # the two cp ranks report the same (cp-summed, dp-averaged) loss
     for (l0, _), (l1, _) in zip(ref, res[0]):
         assert abs(l0 - l1) < 5e-4 * abs(l0), (l0, l1)
+
+
+def _run_cp_two_level(rank, world):
+    from loongforge_b200.parallel import context_parallel as CP
+    from loongforge_b200.parallel import state as ps
+
+    CP.set_cp_comm_type("a2a+p2p", 2)
+    out = _run(rank, world, "tiny-llama", {"cp": 4}, 3, {})
+    st = ps.get_state()
+    assert CP._CFG["comm_type"] == "a2a+p2p"
+    assert st.ranks("cp_inner") == [rank // 2 * 2, rank // 2 * 2 + 1] and st.ranks("cp_outer") == [rank % 2, rank % 2 + 2]
+    return out
+
+
+def test_two_level_context_parallel_matches_single_process():
+    """cp = 4 as Ulysses inside pairs of neighbouring ranks and a KV ring between the pairs."""
+    ref = _single("tiny-llama", 3, {})
+    res = run_distributed(_run_cp_two_level, 4)
+    for (l0, g0), (l1, g1) in zip(ref, res[0]):
+        assert abs(l0 - l1) < 5e-4 * abs(l0) and abs(g0 - g1) < 5e-4 * max(1.0, abs(g0)), (ref, res[0])
