@@ -24,8 +24,10 @@ def _nm():
     return name_maps
 
 
-def load_hf_checkpoint_online(trainer, hf_dir: str, family: str = "llama3") -> int:
-    """Returns the number of tensors loaded into this rank's model chunks."""
+def load_hf_checkpoint_online(trainer, hf_dir: str, family: str = "llama3", upcycle: bool = False) -> int:
+    """Returns the number of tensors loaded into this rank's model chunks. ``upcycle``: the directory holds the DENSE
+    model that this mixture-of-experts model grows from; every expert starts as (a slice of) the dense feed-forward
+    block and the routers are drawn from one seed on all ranks (``--moe-use-upcycling``)."""
     from tools.convert_checkpoint.convert import load_hf
 
     nm = _nm()
@@ -44,6 +46,19 @@ def load_hf_checkpoint_online(trainer, hf_dir: str, family: str = "llama3") -> i
                                   vit_heads=vit.num_attention_heads, **lm_kw)
         mc = {k[len("foundation_model."):]: v for k, v in both.items() if k.startswith("foundation_model.")}
         enc_mc = {k[len("encoder_model."):]: v for k, v in both.items() if k.startswith("encoder_model.")}
+    elif upcycle and cfg.num_moe_experts:
+        import dataclasses
+
+        from ..runtime.upcycling import upcycle_state_dict
+        dense_family = dataclasses.replace(nm.FAMILIES[family], moe=False)
+        mc = nm.hf_to_mcore(hf, dense_family, **{**lm_kw, "num_experts": None})
+        dense_ffn = mc["decoder.layers.0.mlp.linear_fc2.weight"].shape[1]
+        moe_ffn = cfg.moe_ffn_hidden_size or cfg.ffn_hidden_size
+        if dense_ffn % moe_ffn:
+            raise ValueError(f"dense FFN width {dense_ffn} must divide by the expert width {moe_ffn}")
+        mc = upcycle_state_dict(mc, cfg.num_moe_experts, granularity=dense_ffn // moe_ffn, glu=cfg.gated_linear_unit,
+                                router_std=cfg.init_method_std,
+                                moe_layers={i for i in range(cfg.num_layers) if cfg.is_moe_layer(i)})
     else:
         mc = nm.hf_to_mcore(hf, nm.FAMILIES[family], **lm_kw)
     e_local = (cfg.num_moe_experts // st.dims.ep) if cfg.num_moe_experts else 0

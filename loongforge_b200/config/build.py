@@ -217,6 +217,8 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
         log_memory_stats=bool(getattr(args, "log_memory_stats", False)),
         dp_balance=bool(getattr(args, "use_vlm_dp_balance", False)),
         optimizer_cpu_offload=bool(getattr(args, "optimizer_cpu_offload", False)),
+        timing_log_level=int(getattr(args, "timing_log_level", 0) or 0),
+        log_timers_to_tensorboard=bool(getattr(args, "log_timers_to_tensorboard", False)),
         optimizer_offload_fraction=float(getattr(args, "optimizer_offload_fraction", 1.0) or 0.0),
         optimizer=(getattr(args, "optimizer", None) or "adam").lower(), sgd_momentum=getattr(args, "sgd_momentum", 0.9),
         use_fsdp=bool(getattr(args, "use_torch_fsdp2", False) or getattr(args, "use_megatron_fsdp", False)),

@@ -80,14 +80,11 @@ _ACCEPTED = {
     "num_workers": "batches are assembled in the training process",
     "variable_seq_lengths": "pipeline stages exchange fixed-shape activations; packed rows are padded to --seq-length",
     "dist_ckpt_strictness": "unexpected or missing checkpoint keys raise",
-    "log_timers_to_tensorboard": "timers are logged to stdout",
-    "timing_log_level": "all timers are recorded",
     "detail_log_interval": "one log interval exists",
     "wandb_exp_name": "the run name is the output directory",
     "packing_batch_size": "the online packer's buffer holds 16 samples (64 for SFT text)",
     "frame_num": "video inputs are not decoded by the built-in loaders (image-text shards only)",
     "fps": "video inputs are not decoded by the built-in loaders (image-text shards only)",
-    "moe_use_upcycling": "dense checkpoints are upcycled offline with runtime.upcycling.upcycle_state_dict",
 }
 
 

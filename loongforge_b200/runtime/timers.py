@@ -65,7 +65,9 @@ class Timers:
         vals = torch.tensor([self.timers[n].elapsed(reset) * 1e3 / normalizer if n in self.timers else 0.0
                              for n in names], dtype=torch.float64)
         mn, mx = vals.clone(), vals.clone()
-        if dist.is_initialized() and dist.get_backend() == "gloo":
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            if dist.get_backend() != "gloo":  # NCCL reduces device tensors
+                mn, mx = mn.cuda(), mx.cuda()
             dist.all_reduce(mn, op=dist.ReduceOp.MIN)
             dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         return "(min, max) time across ranks (ms):" + "".join(

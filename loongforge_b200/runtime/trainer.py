@@ -60,6 +60,8 @@ class TrainConfig:
     exp_avg_dtype: torch.dtype = torch.float32
     exp_avg_sq_dtype: torch.dtype = torch.float32
     master_as_remainder: bool = False
+    timing_log_level: int = 0  # 0 | 1 | 2, see Trainer.timers
+    log_timers_to_tensorboard: bool = False  # phase times also go to the scalar writers
     optimizer_cpu_offload: bool = False  # masters + Adam moments on the host, native host AdamW
     optimizer_offload_fraction: float = 1.0  # part of the optimizer state (whole shards) that goes to the host
     optimizer: str = "adam"  # adam | sgd
@@ -136,7 +138,9 @@ class Trainer:
         self.st = ps.get_state()
         self.world = self.st.world_size
         self.dp = self.st.dp_size
-        self.timers = Timers()
+        # level 0: only the iteration time of the log line; 1: forward-backward and optimizer, timed with a device
+        # synchronisation on both sides; 2: also the smaller phases
+        self.timers = Timers(log_level=train_cfg.timing_log_level, device_sync=True)
         if train_cfg.bf16:
             model_cfg.params_dtype = torch.bfloat16
         torch.manual_seed(train_cfg.seed + 100 * self.st.pp_rank + 2718 * self.st.tp_rank)
@@ -303,18 +307,24 @@ class Trainer:
                       dtype=self.mcfg.params_dtype)
 
         skip_update = False
+        self.timers("forward-backward", 1).start()
         if self.rerun.mode == "disabled" and self.injector is None:
             reports = forward_backward(data_iterator)
         else:
             reports, skip_update = self._validated_forward_backward(forward_backward, data_iterator)
+        self.timers("forward-backward", 1).stop()
         if skip_update:
             self.optimizer.zero_grad()
             for m in self.models:
                 m.finish_grad_sync()  # nothing may stay in flight
             ok, grad_norm = False, float("nan")
         else:
+            self.timers("partial-grads-all-reduce", 2).start()
             self._allreduce_sequence_parallel_grads()
+            self.timers("partial-grads-all-reduce", 2).stop()
+            self.timers("optimizer", 1).start()
             ok, grad_norm, _ = self.optimizer.step()
+            self.timers("optimizer", 1).stop()
         if ok:
             self.scheduler.step(1)
             skipped = 0
@@ -324,6 +334,7 @@ class Trainer:
         self.consumed_samples += self.mb_calc.current_gbs
         metrics: Dict[str, float] = {"grad_norm": grad_norm, "skipped": skipped}
         # loss: average over micro-batches, then over the data-parallel group (last stage only)
+        self.timers("loss-reduce", 2).start()
         if reports:
             keys = [k for k in reports[0] if k != "num_tokens"]
             vals = torch.stack([torch.stack([r[k].float() for r in reports]).mean() for k in keys])
@@ -332,6 +343,7 @@ class Trainer:
                 vals /= self.st.size("dp_cp")
             for k, v in zip(keys, vals.tolist()):
                 metrics[k] = v
+        self.timers("loss-reduce", 2).stop()
         return metrics
 
     # ------------------------------------------------------------------ data and evaluation
@@ -598,6 +610,13 @@ class Trainer:
                 line = self.format_log(metrics, elapsed_ms)
                 if is_log_rank:
                     (on_log or print)(line)
+                if self.timers.timers:  # --timing-log-level >= 1: per-phase times, min and max over the ranks
+                    if t.log_timers_to_tensorboard:
+                        for name, tm in self.timers.timers.items():
+                            metrics[f"timers/{name}-ms"] = tm.elapsed(reset=False) * 1e3 / t.log_interval
+                    report = self.timers.report(normalizer=float(t.log_interval))
+                    if is_log_rank:
+                        (on_log or print)(report)
             if (t.eval_interval and t.eval_iters and self.iteration % t.eval_interval == 0
                     and getattr(self, "valid_iterator", None) is not None):
                 ev = self.evaluate(self.valid_iterator)

@@ -145,7 +145,8 @@ def _load_initial_state(trainer, args, train_cfg, family: str) -> str:
             how = "finetune"
     elif hf_dir:
         from .ckpt.hf_bridge import load_hf_checkpoint_online
-        load_hf_checkpoint_online(trainer, hf_dir, family=_hf_family(family, trainer.mcfg))
+        load_hf_checkpoint_online(trainer, hf_dir, family=_hf_family(family, trainer.mcfg),
+                                  upcycle=bool(getattr(args, "moe_use_upcycling", False)))
         trainer.optimizer.reload_model_params()
         how = "hf"
     elif getattr(args, "pretrained_checkpoint", None):

@@ -474,3 +474,34 @@ def test_qwen3_vl_vision_tower_and_deepstack_name_map_roundtrip():
     assert set(vit2) == set(vit) and all(torch.equal(vit2[k], vit[k]) for k in vit)
     assert set(taps2) == set(taps) and all(torch.equal(taps2[k], taps[k]) for k in taps)
     ps.destroy_model_parallel()
+
+
+def test_online_upcycling_from_a_dense_hf_checkpoint(tmp_path):
+    """--moe-use-upcycling: a dense HF checkpoint initialises an MoE model whose output equals the dense model's
+    (4 experts of half the dense width, top-2 over distinct slices is not guaranteed by a random router, so the
+    check is on the weights: every expert is a slice of the dense FFN, FC2 scaled by the granularity)."""
+    from loongforge_b200.ckpt.hf_bridge import load_hf_checkpoint_online
+    from loongforge_b200.models.config import TransformerConfig
+    from loongforge_b200.parallel import state as ps
+    from loongforge_b200.runtime.trainer import TrainConfig, Trainer
+
+    ps.destroy_model_parallel()
+    src = _fake_hf(str(tmp_path / "hf"), L=2, ffn=128)
+    cfg = TransformerConfig(num_layers=2, hidden_size=64, num_attention_heads=4, num_query_groups=2, ffn_hidden_size=128,
+                            vocab_size=1000, make_vocab_size_divisible_by=8, num_moe_experts=4, moe_router_topk=2,
+                            moe_ffn_hidden_size=64)
+    tr = Trainer(cfg, TrainConfig(micro_batch_size=1, global_batch_size=1, seq_length=16, train_iters=1))
+    assert load_hf_checkpoint_online(tr, str(tmp_path / "hf"), upcycle=True) > 0
+    sd = tr.models[0].module.state_dict()
+    gate, up = src["model.layers.1.mlp.gate_proj.weight"], src["model.layers.1.mlp.up_proj.weight"]
+    down = src["model.layers.1.mlp.down_proj.weight"]
+    for e in range(4):
+        s = e % 2
+        fc1 = sd[f"decoder.layers.1.mlp.experts.linear_fc1.weight{e}"].float()
+        fc2 = sd[f"decoder.layers.1.mlp.experts.linear_fc2.weight{e}"].float()
+        assert torch.allclose(fc1, torch.cat([gate[s * 64:(s + 1) * 64], up[s * 64:(s + 1) * 64]]), atol=1e-6)
+        assert torch.allclose(fc2, down[:, s * 64:(s + 1) * 64] * 2, atol=1e-6)
+    assert torch.allclose(sd["decoder.layers.1.pre_mlp_layernorm.weight"].float(),
+                          src["model.layers.1.post_attention_layernorm.weight"])
+    assert sd["decoder.layers.0.mlp.router.weight"].shape == (4, 64)
+    ps.destroy_model_parallel()

@@ -473,3 +473,27 @@ def test_batch_size_rampup_and_sample_based_flags(monkeypatch):
         sizes.append(tr.mb_calc.current_gbs)
     assert sizes == [2, 2, 2, 2, 4, 4] and tr.consumed_samples == 16
     assert "global batch size:     4" in tr.format_log({"lm loss": 1.0, "grad_norm": 1.0}, 10.0)
+
+
+def test_timing_log_level_reports_phase_times():
+    from loongforge_b200.data.synthetic import synthetic_batch_iterator
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel import state as ps
+    from loongforge_b200.runtime.trainer import TrainConfig, Trainer
+
+    ps.destroy_model_parallel()
+    cfg = get_model_config("tiny-llama")
+    seen = {}
+    for level in (0, 2):
+        tc = TrainConfig(micro_batch_size=1, global_batch_size=2, seq_length=32, train_iters=2, lr=1e-3, log_interval=2,
+                         timing_log_level=level, log_timers_to_tensorboard=True)
+        tr = Trainer(cfg, tc)
+        lines = []
+        hist = tr.train(synthetic_batch_iterator(cfg.vocab_size, 32, 1, seed=1, pin_memory=False), on_log=lines.append)
+        seen[level] = ("\n".join(lines), hist[-1])
+        ps.destroy_model_parallel()
+    assert "forward-backward" not in seen[0][0] and not any(k.startswith("timers/") for k in seen[0][1])
+    text, last = seen[2]
+    for name in ("forward-backward", "optimizer", "partial-grads-all-reduce", "loss-reduce"):
+        assert name in text, text
+    assert last["timers/forward-backward-ms"] > 0 and last["timers/optimizer-ms"] > 0
