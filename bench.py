@@ -136,11 +136,6 @@ def main():
     if args.impl == "reference":
         return reference_arm(args)
 
-    if os.environ.get("LF_DUMP_STACKS_AFTER_S"):
-        # diagnosis aid: print every thread's Python stack if the run is still going after this many seconds
-        import faulthandler
-        faulthandler.dump_traceback_later(float(os.environ["LF_DUMP_STACKS_AFTER_S"]), repeat=True, exit=False)
-
     import torch
     import torch.distributed as dist
 

@@ -94,6 +94,7 @@ def build(verbose: bool = False, force: bool = False):
             with_cuda=True,
         )
         _load_error = None
+        _apply_env_budget(_mod)
         return _mod
 
 
@@ -108,6 +109,7 @@ def _import_prebuilt():
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)
         sys.modules[_NAME] = mod
+        _apply_env_budget(mod)
         return mod
     except Exception as e:  # noqa: BLE001 - reported through require()
         _load_error = f"{type(e).__name__}: {e}"
@@ -174,6 +176,23 @@ def check_status(device=None) -> None:
     if code != 0:
         t.zero_()
         raise RuntimeError(f"loongforge_b200 kernel error {code}: {STATUS_NAMES.get(code, 'unknown')}")
+
+
+def set_peer_wait_budget_ms(ms: float) -> None:
+    """Budget of the device-side waits on flags that another GPU writes (fused tensor-parallel GEMMs, expert
+    exchange, peer-memory optimizer). Default two minutes, or ``LF_PEER_WAIT_MS`` from the environment; a wait
+    that runs out sets the status word (code 5) and the kernel returns."""
+    require().set_peer_wait_budget_ms(float(ms))
+
+
+def peer_wait_budget_ms() -> float:
+    return float(require().peer_wait_budget_ms())
+
+
+def _apply_env_budget(mod) -> None:
+    v = os.environ.get("LF_PEER_WAIT_MS")
+    if v:
+        mod.set_peer_wait_budget_ms(float(v))
 
 
 def launch_count() -> int:

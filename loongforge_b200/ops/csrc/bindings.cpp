@@ -10,6 +10,7 @@
 #include <cstdint>
 #include "elementwise.h"
 #include "gemm_sm100.h"
+#include "wait_budget.h"
 #ifdef LF_HAVE_ATTN
 #include "attention_sm100.h"
 #endif
@@ -124,6 +125,13 @@ std::vector<at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, c
   const int64_t H = x.size(-1);
   TORCH_CHECK(H % 8 == 0 && H <= 8192, "rmsnorm_bwd: H must be a multiple of 8 and <= 8192");
   const int64_t T = x.numel() / H;
+  TORCH_CHECK(T <= INT32_MAX, "rmsnorm_bwd: more than 2^31 - 1 rows");
+  check_bf16_cuda(w, "w");
+  TORCH_CHECK(w.numel() == H && w.device() == x.device(), "rmsnorm_bwd: w must hold H elements on x's device");
+  TORCH_CHECK(rstd.is_cuda() && rstd.scalar_type() == at::kFloat && rstd.is_contiguous() && rstd.numel() == T &&
+                  rstd.device() == x.device(),
+              "rmsnorm_bwd: rstd must be fp32 [T] on x's device");
+  TORCH_CHECK(dy.numel() == x.numel() && dy.device() == x.device(), "rmsnorm_bwd: dy must match x");
   at::Tensor dx = at::empty_like(x);
   const int grid = lf::rmsnorm_bwd_grid(T);
   at::Tensor partial = at::empty({grid, H}, x.options().dtype(at::kFloat));
@@ -806,6 +814,10 @@ void peer_wait(std::vector<int64_t> flags, int64_t rank, int64_t epoch, const at
 }
 #endif  // LF_HAVE_PEER_OPTIM
 
+// Budget of the device-side waits on flags written by other GPUs, in milliseconds (see wait_budget.h).
+void set_peer_wait_budget_ms(double ms) { lf::set_peer_wait_budget_ms(ms); }
+double peer_wait_budget_ms() { return lf::peer_wait_budget_ms(); }
+
 int64_t launch_count() { return g_launches; }
 void reset_launch_count() { g_launches = 0; }
 
@@ -855,6 +867,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 #endif
   m.def("router_fwd", &router_fwd);
   m.def("router_bwd", &router_bwd);
+  m.def("set_peer_wait_budget_ms", &set_peer_wait_budget_ms);
+  m.def("peer_wait_budget_ms", &peer_wait_budget_ms);
   m.def("launch_count", &launch_count);
   m.def("reset_launch_count", &reset_launch_count);
 }

@@ -727,6 +727,8 @@ float* g_scratch_dev_ptr[kMaxDevices] = {};  // device address of the array, per
 extern "C" int lf_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
                                       float* dw, long long T, int H, float w_offset, cudaStream_t stream) {
   if (H <= 0 || H > LF_RMSNORM_NOALLOC_MAX_H || (H % 8) != 0 || T < 0) return LF_NOALLOC_ERR_TOO_LARGE;
+  // the kernels count rows with a 32-bit int: a larger T would wrap, so it is refused, not narrowed
+  if (T > LF_RMSNORM_NOALLOC_MAX_T) return LF_NOALLOC_ERR_TOO_LARGE;
   if (T == 0) return LF_NOALLOC_OK;
   const void* ptrs[6] = {dy, x, w, rstd, dx, dw};
   for (const void* p : ptrs)
@@ -742,6 +744,8 @@ extern "C" int lf_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void*
     scratch = static_cast<float*>(p);
     g_scratch_dev_ptr[dev] = scratch;
   }
+  // An error left behind by earlier, unrelated work on this device must not be reported as this call's.
+  if (cudaPeekAtLastError() != cudaSuccess) return LF_NOALLOC_ERR_CUDA;
   const int grid = static_cast<int>(T < LF_RMSNORM_NOALLOC_MAX_CTAS ? T : LF_RMSNORM_NOALLOC_MAX_CTAS);
   // Every CTA writes its full row [0, H) of the scratch and the column sum reads exactly rows
   // [0, grid) x [0, H): stale contents of earlier calls are never read, so no clearing is needed.

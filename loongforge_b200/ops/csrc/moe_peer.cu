@@ -20,6 +20,7 @@
 #include <cstdint>
 
 #include "moe_peer.h"
+#include "wait_budget.h"
 #include "sm100_ptx.cuh"
 
 namespace lf {
@@ -119,7 +120,8 @@ __global__ void moe_signal_kernel(MoePeerPtrs pp, int rank, int world, int kind,
 }
 
 // One warp; lane r waits (bounded) for rank r's flag. On timeout the status word is set and the kernel returns.
-__global__ void moe_wait_kernel(const int* flags_local, int world, int kind, int epoch, int* status) {
+__global__ void moe_wait_kernel(const int* flags_local, int world, int kind, int epoch, int* status,
+                                long long budget) {
   const int r = threadIdx.x;
   if (r >= world) return;
   const int* p = flags_local + kind * kMoeMaxPeers + r;
@@ -127,7 +129,7 @@ __global__ void moe_wait_kernel(const int* flags_local, int world, int kind, int
   const long long t0 = clock64();
   while (mp_ld_acquire_sys(p) < epoch) {
     __nanosleep(100);
-    if (clock64() - t0 > LF_WAIT_BUDGET_CYCLES) {
+    if (clock64() - t0 > budget) {
       atomicCAS(status, 0, LF_ERR_WAIT_PEER);
       return;
     }
@@ -180,7 +182,7 @@ int moe_signal(const MoePeerBufs& b, int kind, int epoch, cudaStream_t st) {
 }
 
 int moe_wait(const MoePeerBufs& b, int kind, int epoch, int* status, cudaStream_t st) {
-  moe_wait_kernel<<<1, 32, 0, st>>>(b.flags[b.rank], b.world, kind, epoch, status);
+  moe_wait_kernel<<<1, 32, 0, st>>>(b.flags[b.rank], b.world, kind, epoch, status, g_peer_wait_cycles);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -23,7 +23,7 @@ int moe_push(const MoePeerBufs& b, const void* x, long long ldx, int H, const in
 int moe_pull(const MoePeerBufs& b, void* out, long long ldo, int H, int T, int k, const int* slot_pair,
              const int* pair_row, const int* pair_dst, float* slot_scal, int* status, cudaStream_t st);
 int moe_signal(const MoePeerBufs& b, int kind, int epoch, cudaStream_t st);
-// Waits (bounded, about a second) until every rank's flag of `kind` reached `epoch`; sets *status on timeout.
+// Waits (bounded by the run-time peer budget of wait_budget.h) until every rank's flag of `kind` reached `epoch`; sets *status on timeout.
 int moe_wait(const MoePeerBufs& b, int kind, int epoch, int* status, cudaStream_t st);
 
 }  // namespace lf

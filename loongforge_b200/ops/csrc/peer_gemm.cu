@@ -25,6 +25,7 @@
 #include "sm100_ptx.cuh"
 #include "gemm_sm100.h"
 #include "peer_gemm.h"
+#include "wait_budget.h"
 
 namespace lf {
 
@@ -57,6 +58,7 @@ struct PeerParams {
   int* peer_tile_flags[kMaxPeers];
   int parity;
   int expect;
+  long long wait_cycles;  // budget of every wait that depends on a peer GPU (wait_budget.h)
 };
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
@@ -82,13 +84,13 @@ __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.pr
 
 // Bounded spin on a global flag until it reaches `target`. Returns false on timeout.
 template <bool SYS>
-__device__ __forceinline__ bool wait_flag_ge(const int* p, int target) {
+__device__ __forceinline__ bool wait_flag_ge(const int* p, int target, long long budget) {
   if ((SYS ? ld_acquire_sys(p) : ld_acquire_gpu(p)) >= target) return true;
   const long long t0 = clock64();
   while (true) {
     if ((SYS ? ld_acquire_sys(p) : ld_acquire_gpu(p)) >= target) return true;
     __nanosleep(40);
-    if (clock64() - t0 > LF_WAIT_BUDGET_CYCLES) return false;
+    if (clock64() - t0 > budget) return false;
   }
 }
 
@@ -117,7 +119,7 @@ __device__ void ag_copy_cta(const PeerParams& p, uint8_t* smem, uint64_t* bars) 
   }
   bool ok = true;
   for (int r = 0; r < p.world && ok; ++r)
-    if (r != p.rank) ok = wait_flag_ge<true>(p.peer_sync[p.rank] + r, p.epoch);
+    if (r != p.rank) ok = wait_flag_ge<true>(p.peer_sync[p.rank] + r, p.epoch, p.wait_cycles);
   if (!ok) {
     atomicCAS(p.status, 0, LF_ERR_WAIT_PEER);
     return;
@@ -234,7 +236,7 @@ peer_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         pg_tile_coords(tile, p.tiles_m, p.tiles_n, vm, tn);
         const int tm = (vm + rot) % p.tiles_m;
         if (MODE == 0 && tm != ready_block) {
-          if (!wait_flag_ge<false>(p.chunk_flags + tm, p.epoch)) {
+          if (!wait_flag_ge<false>(p.chunk_flags + tm, p.epoch, p.wait_cycles)) {
             atomicCAS(p.status, 0, LF_ERR_WAIT_PEER);
             *abort_flag = 1;
             ok = false;
@@ -245,7 +247,7 @@ peer_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % PG_STAGES;
-          if (!mbar_wait(&empty_bar[s], ((it / PG_STAGES) & 1) ^ 1, abort_flag)) {
+          if (!mbar_wait(&empty_bar[s], ((it / PG_STAGES) & 1) ^ 1, abort_flag, p.wait_cycles)) {
             atomicCAS(p.status, 0, LF_ERR_WAIT_EMPTY);
             ok = false;
             break;
@@ -279,7 +281,7 @@ peer_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool ok = true;
       for (int tile = cta; tile < num_tiles && ok; tile += num_ctas, ++acc_it) {
         const uint32_t acc = acc_it & 1;
-        if (!mbar_wait(&tmem_empty[acc], ((acc_it >> 1) & 1) ^ 1, abort_flag)) {
+        if (!mbar_wait(&tmem_empty[acc], ((acc_it >> 1) & 1) ^ 1, abort_flag, p.wait_cycles)) {
           atomicCAS(p.status, 0, LF_ERR_WAIT_TMEM_EMPTY);
           break;
         }
@@ -287,7 +289,7 @@ peer_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const uint32_t tmem_d = tmem_base + acc * PG_BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % PG_STAGES;
-          if (!mbar_wait(&full_bar[s], (it / PG_STAGES) & 1, abort_flag)) {
+          if (!mbar_wait(&full_bar[s], (it / PG_STAGES) & 1, abort_flag, p.wait_cycles)) {
             atomicCAS(p.status, 0, LF_ERR_WAIT_FULL);
             ok = false;
             break;
@@ -316,7 +318,7 @@ peer_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       pg_tile_coords(tile, p.tiles_m, p.tiles_n, vm, tn);
       const int tm = (vm + rot) % p.tiles_m;
       const uint32_t acc = acc_it & 1;
-      if (!mbar_wait_warp(&tmem_full[acc], (acc_it >> 1) & 1, abort_flag)) {
+      if (!mbar_wait_warp(&tmem_full[acc], (acc_it >> 1) & 1, abort_flag, p.wait_cycles)) {
         if (lane == 0) atomicCAS(p.status, 0, LF_ERR_WAIT_TMEM_FULL);
         break;
       }
@@ -341,7 +343,7 @@ peer_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               got = wait_flag_ge<true>(
                   p.peer_tile_flags[p.rank] + (static_cast<long long>(p.parity) * p.world + src) * tiles_per_rank +
                       local_tile,
-                  p.expect);
+                  p.expect, p.wait_cycles);
         }
         got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
         if (!got) {
@@ -496,6 +498,7 @@ int ag_gemm(const AgGemmArgs& a, cudaStream_t stream) {
   p.x_full = static_cast<uint8_t*>(a.x_full);
   p.chunk_flags = a.chunk_flags;
   p.epoch = a.epoch;
+  p.wait_cycles = g_peer_wait_cycles;
   const int sms = pg_sms();
   int copy = a.copy_ctas;
   if (copy < 1) copy = 1;
@@ -539,6 +542,7 @@ int gemm_rs(const GemmRsArgs& a, cudaStream_t stream) {
     p.peer_tile_flags[r] = a.peer_tile_flags[r];
   }
   p.parity = a.call_index & 1;
+  p.wait_cycles = g_peer_wait_cycles;
   p.expect = 4 * (a.call_index / 2 + 1);
   const int tiles = p.tiles_m * p.tiles_n;
   int grid = pg_sms();

@@ -13,6 +13,7 @@
 #include <cuda_bf16.h>
 
 #include "peer_optim.h"
+#include "wait_budget.h"
 #include "sm100_ptx.cuh"
 
 namespace lf {
@@ -99,7 +100,7 @@ __global__ void peer_signal_kernel(PeerPtrs flags, int world, int rank, int epoc
                  : "memory");
 }
 
-__global__ void peer_wait_kernel(const int* flags_local, int world, int epoch, int* status) {
+__global__ void peer_wait_kernel(const int* flags_local, int world, int epoch, int* status, long long budget) {
   const int r = threadIdx.x;
   if (r >= world) return;
   const int* p = flags_local + r;
@@ -109,7 +110,7 @@ __global__ void peer_wait_kernel(const int* flags_local, int world, int epoch, i
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     if (v >= epoch) return;
     __nanosleep(100);
-    if (clock64() - t0 > LF_WAIT_BUDGET_CYCLES) {
+    if (clock64() - t0 > budget) {
       atomicCAS(status, 0, LF_ERR_WAIT_PEER);
       return;
     }
@@ -146,7 +147,8 @@ int peer_signal(const PeerTable& flags, int epoch, cudaStream_t st) {
 }
 
 int peer_wait(const PeerTable& flags, int epoch, int* status, cudaStream_t st) {
-  peer_wait_kernel<<<1, 32, 0, st>>>(static_cast<const int*>(flags.ptr[flags.rank]), flags.world, epoch, status);
+  peer_wait_kernel<<<1, 32, 0, st>>>(static_cast<const int*>(flags.ptr[flags.rank]), flags.world, epoch, status,
+                                    g_peer_wait_cycles);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

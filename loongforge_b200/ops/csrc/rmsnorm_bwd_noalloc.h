@@ -14,8 +14,11 @@
 // Contract
 //   * dy, x, dx: bf16 [T, H] contiguous; w: bf16 [H]; rstd: fp32 [T] (from the forward); dw: fp32 [H],
 //     overwritten. All pointers are device pointers on the CURRENT device, 16-byte aligned.
-//   * H must be a multiple of 8 and at most LF_RMSNORM_NOALLOC_MAX_H; T >= 0. Larger sizes are
-//     rejected with LF_NOALLOC_ERR_TOO_LARGE and nothing is launched.
+//   * H must be a multiple of 8 and at most LF_RMSNORM_NOALLOC_MAX_H; 0 <= T <= LF_RMSNORM_NOALLOC_MAX_T
+//     (the kernels index rows with a 32-bit int). Larger sizes are rejected with
+//     LF_NOALLOC_ERR_TOO_LARGE and nothing is launched.
+//   * If the device already carries an error from earlier work, LF_NOALLOC_ERR_CUDA is returned and nothing
+//     is launched (the pending error is left in place for its owner to read).
 //   * The first call on each device looks up the device address of the scratch array (a host-side
 //     symbol is not a device address). That first call should therefore be made before any stream
 //     capture is started on that device.
@@ -29,10 +32,11 @@
 
 #define LF_RMSNORM_NOALLOC_MAX_H 8192
 #define LF_RMSNORM_NOALLOC_MAX_CTAS 148
+#define LF_RMSNORM_NOALLOC_MAX_T 2147483647LL
 #define LF_RMSNORM_NOALLOC_SCRATCH_BYTES (LF_RMSNORM_NOALLOC_MAX_CTAS * LF_RMSNORM_NOALLOC_MAX_H * 4)
 
 #define LF_NOALLOC_OK 0
-#define LF_NOALLOC_ERR_TOO_LARGE 1   // H above the maximum, or not a multiple of 8
+#define LF_NOALLOC_ERR_TOO_LARGE 1   // H or T above the maximum, or H not a multiple of 8
 #define LF_NOALLOC_ERR_BAD_POINTER 2 // null or misaligned pointer
 #define LF_NOALLOC_ERR_CUDA 3        // a CUDA runtime call failed (symbol lookup or launch)
 

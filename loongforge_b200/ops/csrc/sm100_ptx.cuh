@@ -26,7 +26,8 @@ enum : int {
   LF_ERR_BAD_INDEX = 7,       // an index read from device memory was out of range; the access was skipped
 };
 
-// About one second at ~2 GHz. A healthy pipeline stage completes in microseconds.
+// About one second at ~2 GHz. A healthy pipeline stage completes in microseconds. Waits that depend on ANOTHER
+// GPU take their (much longer, run-time) budget from wait_budget.h through the `budget` arguments below.
 #ifndef LF_WAIT_BUDGET_CYCLES
 #define LF_WAIT_BUDGET_CYCLES (2000000000ll)
 #endif
@@ -74,7 +75,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait. Returns false when the clock budget ran out or another role of
 // this CTA already raised `*abort_flag` (a shared-memory int).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          long long budget = LF_WAIT_BUDGET_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
@@ -82,7 +84,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > LF_WAIT_BUDGET_CYCLES) {
+      if (clock64() - t0 > budget) {
         *abort_flag = 1;
         return false;
       }
@@ -104,7 +106,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 // Warp-collective bounded wait for warps that share an SM sub-partition with busy math warps:
 // only lane 0 polls, with the NON-blocking test_wait and a short sleep between polls, so that a
 // waiting warp neither floods shared memory nor sits inside a blocking instruction.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               long long budget = LF_WAIT_BUDGET_CYCLES) {
   int ok = 1;
   if (lane_id() == 0) {
     if (!mbar_test_wait(bar, parity)) {
@@ -113,7 +116,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, v
       while (!mbar_test_wait(bar, parity)) {
         __nanosleep(20);
         if ((++spins & 0xff) == 0) {
-          if (*abort_flag || clock64() - t0 > LF_WAIT_BUDGET_CYCLES) {
+          if (*abort_flag || clock64() - t0 > budget) {
             *abort_flag = 1;
             ok = 0;
             break;

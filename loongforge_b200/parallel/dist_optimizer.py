@@ -207,9 +207,12 @@ class DistributedOptimizer:
         """Gradient reduce-scatter by peer loads (csrc/peer_optim.cu): after a barrier (every rank finished its
         backward) each rank pulls and sums its shard of every bucket from all DP peers, scaled by 1/dp."""
         from ..ops import _ext
+        shards = list(self._peer_buffers())
+        if not shards:
+            return
         C = _ext.require()
         done = set()
-        for sh in self._peer_buffers():
+        for sh in shards:
             if id(sh.buf) not in done:
                 self._peer_barrier(sh.buf)
                 done.add(id(sh.buf))

@@ -174,6 +174,10 @@ class Trainer:
                     dist.broadcast(p.data, src=self.st.group_ranks["embd"][0], group=self.st.group("embd"))
             self.optimizer.reload_model_params()
             self.optimizer.post_sync_hooks.append(self._allreduce_embedding_grads)
+        # Gradients that are partial sums over the tensor-parallel group are completed AFTER the data-parallel
+        # reduction has finished: with an overlapped reduction the last buckets are still being reduced in place on
+        # the communication stream when backward returns, and touching them earlier would race with it.
+        self.optimizer.post_sync_hooks.insert(0, self._allreduce_sequence_parallel_grads)
         self.scheduler = OptimizerParamScheduler(
             self.optimizer, max_lr=train_cfg.lr, min_lr=train_cfg.min_lr, warmup_steps=train_cfg.lr_warmup_iters,
             decay_steps=train_cfg.lr_decay_iters or train_cfg.train_iters, decay_style=train_cfg.lr_decay_style)
@@ -314,17 +318,18 @@ class Trainer:
             reports, skip_update = self._validated_forward_backward(forward_backward, data_iterator)
         self.timers("forward-backward", 1).stop()
         if skip_update:
-            self.optimizer.zero_grad()
             for m in self.models:
-                m.finish_grad_sync()  # nothing may stay in flight
+                m.finish_grad_sync()  # nothing may stay in flight when the buffers are cleared
+            self.optimizer.zero_grad()
             ok, grad_norm = False, float("nan")
         else:
-            self.timers("partial-grads-all-reduce", 2).start()
-            self._allreduce_sequence_parallel_grads()
-            self.timers("partial-grads-all-reduce", 2).stop()
+            self._before_optimizer_step()
             self.timers("optimizer", 1).start()
+            # finishes the (possibly overlapped) data-parallel reduction first, then runs the post-sync hooks:
+            # tensor-parallel partial gradients, shared embeddings
             ok, grad_norm, _ = self.optimizer.step()
             self.timers("optimizer", 1).stop()
+        self._check_kernel_status()
         if ok:
             self.scheduler.step(1)
             skipped = 0
@@ -456,6 +461,8 @@ class Trainer:
             d = self.rerun.validate(loss)
             if d.action == "rerun":
                 replaying = True
+                for m in self.models:
+                    m.finish_grad_sync()  # an overlapped reduction must not be running while the buffers are cleared
                 self.optimizer.zero_grad()
                 replay.rewind()
                 set_rng_state(rng)
@@ -523,10 +530,36 @@ class Trainer:
         for p in self._shared_embeddings:
             dist.all_reduce(p.main_grad, group=g)
 
+    def _before_optimizer_step(self):
+        """Hook between the last backward and the optimizer step (subclasses: encoder backward of the
+        heterogeneous-DP schedule)."""
+
+    def _check_kernel_status(self):
+        """Read the native kernels' status word once per step and raise on the first wait that gave up, on every
+        rank of the job at the same step: a fused kernel whose peer wait ran out has returned partly written
+        outputs, so the step must not be trusted."""
+        if self.device.type != "cuda":
+            return
+        from ..ops import _ext
+        if not _ext.available():
+            return
+        word = _ext.status_tensor(self.device)
+        code = word.clone()
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(code, op=dist.ReduceOp.MAX)
+        c = int(code.item())
+        if c != 0:
+            word.zero_()
+            raise RuntimeError(f"iteration {self.iteration}: native kernel error {c} on some rank: "
+                               f"{_ext.STATUS_NAMES.get(c, 'unknown')}")
+
     def _allreduce_sequence_parallel_grads(self):
         """Replicated parameters whose gradient is only a PARTIAL sum on each TP rank are summed over the TP group:
         norm weights that see a sequence shard (sequence parallelism), and per-head norm weights applied to this
-        rank's heads only (``tp_partial_grad``: QK layernorm, gated-delta-net output norm)."""
+        rank's heads only (``tp_partial_grad``: QK layernorm, gated-delta-net output norm). Runs as the first
+        post-sync hook of the optimizer, i.e. after the data-parallel reduction. With the sharded optimizer only this
+        rank's shard of each gradient is valid by then; TP peers hold the same shard, so summing whole tensors is
+        still right where it matters."""
         st = self.st
         if st.dims.tp == 1:
             return

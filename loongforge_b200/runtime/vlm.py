@@ -208,10 +208,9 @@ class VLMTrainer(Trainer):
         finally:
             self._hetero_runner, self._already_balanced = None, False
 
-    def _allreduce_sequence_parallel_grads(self):
+    def _before_optimizer_step(self):
         # runs right after the pipeline's backward and before the optimizer: the point where the embedding gradients go
         # back to the ranks that encoded them (the first stage's first TP rank holds the complete gradient)
         runner = getattr(self, "_hetero_runner", None)
         if runner is not None:
             runner.backward(contributes=self.st.is_first_stage and self.st.tp_rank == 0)
-        super()._allreduce_sequence_parallel_grads()

@@ -1,6 +1,8 @@
 """Failure detection without touching a GPU: injected host faults, a rank that stops, store heartbeats."""
 import math
 
+import pytest
+
 import torch
 
 from dist_utils import run_distributed
@@ -78,3 +80,46 @@ def _straggler_worker(rank, world):
 
 def test_straggler_detector():
     assert run_distributed(_straggler_worker, 3)[0] == [2]
+
+
+def test_trainer_raises_on_kernel_status_word(monkeypatch):
+    """The trainer reads the native kernels' status word every step and raises on a wait that gave up."""
+    import types
+
+    import torch
+
+    from loongforge_b200.ops import _ext
+    from loongforge_b200.runtime.trainer import Trainer
+
+    word = torch.tensor([5], dtype=torch.int32)
+    monkeypatch.setattr(_ext, "available", lambda: True)
+    monkeypatch.setattr(_ext, "status_tensor", lambda device=None: word)
+    stub = types.SimpleNamespace(device=types.SimpleNamespace(type="cuda"), iteration=7)
+    with pytest.raises(RuntimeError, match="native kernel error 5"):
+        Trainer._check_kernel_status(stub)
+    assert int(word.item()) == 0
+    Trainer._check_kernel_status(stub)  # a clean word passes
+
+
+def test_tp_partial_grads_are_reduced_after_the_dp_sync():
+    """The tensor-parallel partial-gradient all-reduce is the optimizer's FIRST post-sync hook, i.e. it runs after
+    finish_grad_sync() and never while an overlapped data-parallel reduction is still in flight."""
+    import torch
+
+    from loongforge_b200.models.config import TransformerConfig
+    from loongforge_b200.runtime.trainer import TrainConfig, Trainer
+
+    cfg = TransformerConfig(num_layers=1, hidden_size=64, num_attention_heads=2, ffn_hidden_size=128, vocab_size=128)
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=1, seq_length=16, train_iters=1)
+    tr = Trainer(cfg, tc, device=torch.device("cpu"))
+    hooks = tr.optimizer.post_sync_hooks
+    assert hooks and hooks[0].__func__ is Trainer._allreduce_sequence_parallel_grads
+    order = []
+    m = tr.models[0]
+    orig_finish, orig_hook = m.finish_grad_sync, hooks[0]
+    m.finish_grad_sync = lambda: (order.append("dp_sync"), orig_finish())[1]
+    hooks[0] = lambda: (order.append("tp_partial"), orig_hook())[1]
+    from loongforge_b200.data.synthetic import synthetic_batch_iterator
+
+    tr.train_step(synthetic_batch_iterator(128, 16, 1))
+    assert order.index("dp_sync") < order.index("tp_partial")

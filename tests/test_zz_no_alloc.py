@@ -50,3 +50,12 @@ def test_noalloc_rmsnorm_bwd_matches_regular_entry_point():
               0.0, stream) == 1
     assert fn(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(), 4, 100,
               0.0, stream) == 1
+    # more rows than the kernels' 32-bit row counter can hold: refused, not narrowed
+    assert fn(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(), 2 ** 31, 64,
+              0.0, stream) == 1
+    # a null or misaligned pointer is refused before anything is launched
+    assert fn(None, x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(), 4, 64, 0.0,
+              stream) == 2
+    assert fn(dy.data_ptr() + 2, x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(), 4, 64,
+              0.0, stream) == 2
+    torch.cuda.synchronize()
