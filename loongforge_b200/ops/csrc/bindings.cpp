@@ -313,20 +313,24 @@ void sumsq_(const at::Tensor& x, at::Tensor out) {
 
 #ifdef LF_HAVE_ATTN
 // ------------------------------------------------------------------ attention
-// q: [T, G, R, 128] (any token/group/head strides, e.g. a view into a packed QKV buffer),
-// k, v: [T, G, 128] views. Returns o [T, G*R, 128] and lse [G*R, T].
+// q: [Tq, G, R, D] (any token/group/head strides, e.g. a view into a packed QKV buffer),
+// k, v: [Tk, G, D] views. Returns o [Tq, G*R, D] and lse [G*R, Tq].
 void fill_attn_common(lf::AttnArgs& a, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
-                      const c10::optional<at::Tensor>& cu_seqlens, double scale, bool causal,
-                      const at::Tensor& status) {
+                      const c10::optional<at::Tensor>& cu_q, const c10::optional<at::Tensor>& cu_k, double scale,
+                      bool causal, const at::Tensor& status) {
   check_bf16_cuda(q, "q");
   check_bf16_cuda(k, "k");
   check_bf16_cuda(v, "v");
-  TORCH_CHECK(q.dim() == 4 && k.dim() == 3 && v.dim() == 3, "q must be [T,G,R,128], k/v [T,G,128]");
-  TORCH_CHECK(q.size(3) == 128 && k.size(2) == 128 && v.size(2) == 128, "head dim must be 128");
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 3 && v.dim() == 3, "q must be [Tq,G,R,D], k/v [Tk,G,D]");
+  const int64_t D = q.size(3);
+  TORCH_CHECK(D >= 8 && D <= 128 && D % 8 == 0 && k.size(2) == D && v.size(2) == D,
+              "head dim must be a multiple of 8, at most 128, and the same for q, k and v");
   TORCH_CHECK(q.stride(3) == 1 && k.stride(2) == 1 && v.stride(2) == 1);
-  TORCH_CHECK(k.size(1) == q.size(1) && v.size(1) == q.size(1) && k.size(0) == q.size(0));
+  TORCH_CHECK(k.size(1) == q.size(1) && v.size(1) == q.size(1) && v.size(0) == k.size(0));
   a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr();
-  a.T = static_cast<int>(q.size(0));
+  a.Tq = static_cast<int>(q.size(0));
+  a.Tk = static_cast<int>(k.size(0));
+  a.D = static_cast<int>(D);
   a.Hkv = static_cast<int>(q.size(1));
   a.Hq = static_cast<int>(q.size(1) * q.size(2));
   a.q_ts = q.stride(0); a.q_gs = q.stride(1); a.q_hs = q.stride(2);
@@ -335,21 +339,30 @@ void fill_attn_common(lf::AttnArgs& a, const at::Tensor& q, const at::Tensor& k,
   a.scale = static_cast<float>(scale);
   a.causal = causal;
   a.status = status.data_ptr<int>();
-  if (cu_seqlens.has_value()) {
-    TORCH_CHECK(cu_seqlens->is_cuda() && cu_seqlens->scalar_type() == at::kInt && cu_seqlens->is_contiguous());
-    a.cu_seqlens = cu_seqlens->data_ptr<int>();
-    a.num_seqs = static_cast<int>(cu_seqlens->numel() - 1);
+  if (cu_q.has_value()) {
+    TORCH_CHECK(cu_q->is_cuda() && cu_q->scalar_type() == at::kInt && cu_q->is_contiguous() && cu_q->numel() >= 2);
+    a.cu_seqlens_q = cu_q->data_ptr<int>();
+    a.num_seqs = static_cast<int>(cu_q->numel() - 1);
+    if (cu_k.has_value()) {
+      TORCH_CHECK(cu_k->is_cuda() && cu_k->scalar_type() == at::kInt && cu_k->is_contiguous() &&
+                  cu_k->numel() == cu_q->numel());
+      a.cu_seqlens_k = cu_k->data_ptr<int>();
+    } else {
+      TORCH_CHECK(a.Tq == a.Tk, "different query and key lengths with sequence boundaries need both boundary lists");
+    }
+  } else {
+    TORCH_CHECK(!cu_k.has_value(), "key boundaries without query boundaries");
   }
 }
 
 std::vector<at::Tensor> attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
-                                 c10::optional<at::Tensor> cu_seqlens, double scale, bool causal,
-                                 const at::Tensor& status) {
+                                 c10::optional<at::Tensor> cu_q, c10::optional<at::Tensor> cu_k, double scale,
+                                 bool causal, const at::Tensor& status) {
   c10::cuda::CUDAGuard guard(q.device());
   lf::AttnArgs a;
-  fill_attn_common(a, q, k, v, cu_seqlens, scale, causal, status);
-  at::Tensor o = at::empty({a.T, a.Hq, 128}, q.options());
-  at::Tensor lse = at::empty({a.Hq, a.T}, q.options().dtype(at::kFloat));
+  fill_attn_common(a, q, k, v, cu_q, cu_k, scale, causal, status);
+  at::Tensor o = at::empty({a.Tq, a.Hq, a.D}, q.options());
+  at::Tensor lse = at::empty({a.Hq, a.Tq}, q.options().dtype(at::kFloat));
   a.o = o.data_ptr();
   a.o_ts = o.stride(0); a.o_hs = o.stride(1);
   a.lse = lse.data_ptr<float>();
@@ -362,17 +375,19 @@ std::vector<at::Tensor> attn_fwd(const at::Tensor& q, const at::Tensor& k, const
 // dq/dk/dv are OUTPUT views (same shapes as q/k/v), typically into one packed gradient buffer.
 void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
               const at::Tensor& o, const at::Tensor& lse, at::Tensor dq, at::Tensor dk, at::Tensor dv,
-              c10::optional<at::Tensor> cu_seqlens, double scale, bool causal, const at::Tensor& status) {
+              c10::optional<at::Tensor> cu_q, c10::optional<at::Tensor> cu_k, double scale, bool causal,
+              const at::Tensor& status) {
   c10::cuda::CUDAGuard guard(q.device());
   lf::AttnArgs a;
-  fill_attn_common(a, q, k, v, cu_seqlens, scale, causal, status);
+  fill_attn_common(a, q, k, v, cu_q, cu_k, scale, causal, status);
   check_bf16_cuda(dout, "dout");
   check_bf16_cuda(o, "o");
-  TORCH_CHECK(dout.dim() == 3 && dout.stride(2) == 1 && o.stride(2) == 1 && dout.size(1) == a.Hq);
+  TORCH_CHECK(dout.dim() == 3 && dout.stride(2) == 1 && o.stride(2) == 1 && dout.size(1) == a.Hq &&
+              dout.size(0) == a.Tq && dout.size(2) == a.D);
   TORCH_CHECK(dq.sizes() == q.sizes() && dk.sizes() == k.sizes() && dv.sizes() == v.sizes());
   TORCH_CHECK(dq.stride(3) == 1 && dk.stride(2) == 1 && dv.stride(2) == 1);
-  TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous());
-  at::Tensor delta = at::empty({a.Hq, a.T}, q.options().dtype(at::kFloat));
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.numel() == int64_t(a.Hq) * a.Tq);
+  at::Tensor delta = at::empty({a.Hq, a.Tq}, q.options().dtype(at::kFloat));
   a.o = const_cast<void*>(o.data_ptr());
   a.o_ts = o.stride(0); a.o_hs = o.stride(1);
   a.lse = const_cast<float*>(lse.data_ptr<float>());

@@ -29,8 +29,13 @@ __device__ __forceinline__ float warp_absmax(float v) {
 }
 
 __device__ __forceinline__ float block_scale(float amax, int pow2) {
-  float s = fmaxf(amax, 1e-12f) / kE4M3Max;
-  if (pow2) s = exp2f(ceilf(log2f(s)));
+  // exact arithmetic (the file is built with fast-math): IEEE division, and the next power of two from the bits
+  float s = __fdiv_rn(fmaxf(amax, 1e-12f), kE4M3Max);
+  if (pow2) {
+    const uint32_t bits = __float_as_uint(s);  // positive, normal
+    const uint32_t e = (bits >> 23) + ((bits & 0x7fffffu) ? 1u : 0u);
+    s = __uint_as_float(e << 23);
+  }
   return s;
 }
 

@@ -320,85 +320,111 @@ def swiglu(x: torch.Tensor) -> torch.Tensor:
 # ----------------------------------------------------------------------------- attention
 
 
-def attention_ref(q, k, v, causal=True, scale=None, cu_seqlens=None):
-    """Naive softmax attention. q [T, Hq, D], k/v [T, Hkv, D]; returns [T, Hq, D] (fp32 math)."""
-    T, Hq, D = q.shape
-    Dv = v.shape[-1]
-    Hkv = k.shape[1]
+def _seq_ids(T: int, cu, device):
+    """(sequence id, position inside the sequence, sequence length) of each of T packed tokens."""
+    idx = torch.arange(T, device=device)
+    if cu is None:
+        return torch.zeros_like(idx), idx, torch.full((1,), T, device=device, dtype=idx.dtype)
+    cu = cu.to(device=device, dtype=idx.dtype)
+    seg = torch.bucketize(idx, cu[1:], right=True).clamp_(max=cu.numel() - 2)
+    return seg, idx - cu[seg], cu[1:] - cu[:-1]
+
+
+def attention_ref(q, k, v, causal=True, scale=None, cu_seqlens=None, cu_seqlens_k=None, return_lse=False):
+    """Naive softmax attention in fp32. q [Tq, Hq, D], k/v [Tk, Hkv, D] -> [Tq, Hq, Dv]. Query and key sides may have
+    different lengths (per sequence when boundaries are given); the causal mask is aligned to the bottom right:
+    query i of a sequence sees keys j <= i + (k_len - q_len). Rows that see no key return 0 (lse = -inf)."""
+    Tq, Hq, D = q.shape
+    Tk, Hkv, Dv = k.shape[0], k.shape[1], v.shape[-1]
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     rep = Hq // Hkv
     qf = q.float().transpose(0, 1)
     kf = k.float().transpose(0, 1).repeat_interleave(rep, 0)
     vf = v.float().transpose(0, 1).repeat_interleave(rep, 0)
     s = torch.matmul(qf, kf.transpose(1, 2)) * scale
-    idx = torch.arange(T, device=q.device)
-    mask = torch.ones(T, T, dtype=torch.bool, device=q.device)
+    seg_q, pos_q, len_q = _seq_ids(Tq, cu_seqlens, q.device)
+    seg_k, pos_k, len_k = _seq_ids(Tk, cu_seqlens_k if cu_seqlens_k is not None else
+                                   (cu_seqlens if Tq == Tk else None), q.device)
+    mask = seg_q[:, None] == seg_k[None, :]
     if causal:
-        mask &= idx[None, :] <= idx[:, None]
-    if cu_seqlens is not None:
-        seg = torch.bucketize(idx, cu_seqlens[1:].to(idx.device), right=True)
-        mask &= seg[:, None] == seg[None, :]
+        off = (len_k - len_q)[seg_q]
+        mask &= pos_k[None, :] <= (pos_q + off)[:, None]
     s = s.masked_fill(~mask, float("-inf"))
-    p = torch.softmax(s, dim=-1)
-    return torch.matmul(p, vf).transpose(0, 1).to(q.dtype).reshape(T, Hq, Dv)
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse.masked_fill(torch.isinf(lse), 0.0).unsqueeze(-1))
+    o = torch.matmul(p, vf).transpose(0, 1).to(q.dtype).reshape(Tq, Hq, Dv)
+    return (o, lse) if return_lse else o
 
 
 class _AttnFn(torch.autograd.Function):
-    """q [T, Hq, 128], k/v [T, Hkv, 128] (strided views allowed) -> o [T, Hq, 128]."""
+    """q [Tq, Hq, D], k/v [Tk, Hkv, D] (strided views allowed, D <= 128) -> o [Tq, Hq, D]; also returns the
+    log-sum-exp [Hq, Tq] (not differentiable) so that partial results can be merged (context parallelism)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, cu_seqlens, scale, causal):
+    def forward(ctx, q, k, v, cu_q, cu_k, scale, causal):
         Hkv = k.shape[1]
         q4 = q.unflatten(1, (Hkv, q.shape[1] // Hkv))
-        o, lse = _C().attn_fwd(q4, k, v, cu_seqlens, scale, causal, _ext.status_tensor(q.device))
-        ctx.save_for_backward(q, k, v, o, lse, *([cu_seqlens] if cu_seqlens is not None else []))
-        ctx.scale, ctx.causal = scale, causal
-        return o
+        o, lse = _C().attn_fwd(q4, k, v, cu_q, cu_k, scale, causal, _ext.status_tensor(q.device))
+        ctx.save_for_backward(q, k, v, o, lse, *[c for c in (cu_q, cu_k) if c is not None])
+        ctx.cfg = (scale, causal, cu_q is not None, cu_k is not None)
+        ctx.mark_non_differentiable(lse)
+        return o, lse
 
     @staticmethod
-    def backward(ctx, do):
+    def backward(ctx, do, _dlse):
         q, k, v, o, lse, *rest = ctx.saved_tensors
-        cu = rest[0] if rest else None
-        if do.stride(2) != 1 or do.stride(1) % 8 or do.stride(0) % 8:
-            do = do.contiguous()
-        Hkv = k.shape[1]
-        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
-        dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
-        dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
-        R = q.shape[1] // Hkv
-        _C().attn_bwd(do, q.unflatten(1, (Hkv, R)), k, v, o, lse, dq.unflatten(1, (Hkv, R)), dk, dv, cu, ctx.scale,
-                      ctx.causal, _ext.status_tensor(q.device))
-        return dq, dk, dv, None, None, None
+        scale, causal, has_q, has_k = ctx.cfg
+        cu_q = rest[0] if has_q else None
+        cu_k = rest[1] if has_k else None
+        dq, dk, dv = attention_backward(do, q, k, v, o, lse, cu_q, cu_k, scale, causal)
+        return dq, dk, dv, None, None, None, None
+
+
+def attention_backward(do, q, k, v, o, lse, cu_q, cu_k, scale, causal):
+    """Gradients of the native attention from a saved output and log-sum-exp. `o` / `lse` may be the MERGED result of
+    several partial calls (ring / all-gather context parallelism): the probabilities are recomputed against the
+    given lse, so the returned dk / dv are this key block's share."""
+    if do.stride(2) != 1 or do.stride(1) % 8 or do.stride(0) % 8:
+        do = do.contiguous()
+    Hkv = k.shape[1]
+    R = q.shape[1] // Hkv
+    dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+    dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+    _C().attn_bwd(do, q.unflatten(1, (Hkv, R)), k, v, o, lse, dq.unflatten(1, (Hkv, R)), dk, dv, cu_q, cu_k, scale,
+                  causal, _ext.status_tensor(q.device))
+    return dq, dk, dv
 
 
 class _AttnPackedFn(torch.autograd.Function):
-    """Attention straight on the packed QKV GEMM output ``[T, G*(R+2)*128]`` (Megatron's per-group
+    """Attention straight on the packed QKV GEMM output ``[T, G*(R+2)*D]`` (Megatron's per-group
     ``[q_0..q_{R-1}, k, v]`` order): no split copies forward, and the backward kernels write dq,
     dk, dv into ONE packed gradient buffer that feeds the QKV dgrad/wgrad GEMMs directly."""
 
     @staticmethod
     def forward(ctx, qkv, G, R, cu_seqlens, scale, causal):
         T = qkv.shape[0]
-        pk = qkv.view(T, G, R + 2, 128)
-        o, lse = _C().attn_fwd(pk[:, :, :R], pk[:, :, R], pk[:, :, R + 1], cu_seqlens, scale, causal,
+        D = qkv.shape[1] // (G * (R + 2))
+        pk = qkv.view(T, G, R + 2, D)
+        o, lse = _C().attn_fwd(pk[:, :, :R], pk[:, :, R], pk[:, :, R + 1], cu_seqlens, None, scale, causal,
                                _ext.status_tensor(qkv.device))
         ctx.save_for_backward(qkv, o, lse, *([cu_seqlens] if cu_seqlens is not None else []))
-        ctx.cfg = (G, R, scale, causal)
+        ctx.cfg = (G, R, D, scale, causal)
         return o
 
     @staticmethod
     def backward(ctx, do):
         qkv, o, lse, *rest = ctx.saved_tensors
         cu = rest[0] if rest else None
-        G, R, scale, causal = ctx.cfg
+        G, R, D, scale, causal = ctx.cfg
         T = qkv.shape[0]
         if do.stride(2) != 1 or do.stride(1) % 8 or do.stride(0) % 8:
             do = do.contiguous()
-        pk = qkv.view(T, G, R + 2, 128)
+        pk = qkv.view(T, G, R + 2, D)
         dqkv = torch.empty_like(qkv)
-        dpk = dqkv.view(T, G, R + 2, 128)
+        dpk = dqkv.view(T, G, R + 2, D)
         _C().attn_bwd(do, pk[:, :, :R], pk[:, :, R], pk[:, :, R + 1], o, lse, dpk[:, :, :R], dpk[:, :, R],
-                      dpk[:, :, R + 1], cu, scale, causal, _ext.status_tensor(qkv.device))
+                      dpk[:, :, R + 1], cu, None, scale, causal, _ext.status_tensor(qkv.device))
         return dqkv, None, None, None, None, None
 
 
@@ -412,49 +438,69 @@ def set_attention_impl(name: str) -> None:
 
 
 def native_attention_supported(q, k, v) -> bool:
+    """The tcgen05 kernel covers bf16 with one head dim <= 128 (a multiple of 8) for q, k and v."""
     m = _ext.get()
+    D = q.shape[-1]
     return (m is not None and hasattr(m, "attn_fwd") and q.is_cuda and q.dtype == torch.bfloat16
-            and q.shape[-1] == 128 and v.shape[-1] == 128)
+            and D <= 128 and D % 8 == 0 and k.shape[-1] == D and v.shape[-1] == D)
 
 
 def attention_packed_supported(qkv: torch.Tensor, head_dim: int) -> bool:
     m = _ext.get()
     return (_ATTN_IMPL["impl"] != "sdpa" and m is not None and hasattr(m, "attn_fwd") and qkv.is_cuda
-            and qkv.dtype == torch.bfloat16 and head_dim == 128 and qkv.dim() == 2 and qkv.is_contiguous())
+            and qkv.dtype == torch.bfloat16 and head_dim <= 128 and head_dim % 8 == 0 and qkv.dim() == 2
+            and qkv.is_contiguous())
 
 
 def attention_packed(qkv: torch.Tensor, groups: int, q_per_group: int, *, causal: bool = True,
                      scale: Optional[float] = None, cu_seqlens: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Attention on a packed ``[T, G*(R+2)*128]`` QKV buffer -> ``[T, G*R, 128]``."""
-    scale = 1.0 / math.sqrt(128) if scale is None else scale
+    """Attention on a packed ``[T, G*(R+2)*D]`` QKV buffer -> ``[T, G*R, D]``."""
+    D = qkv.shape[1] // (groups * (q_per_group + 2))
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
     cu = cu_seqlens.to(torch.int32).contiguous() if cu_seqlens is not None else None
     return _AttnPackedFn.apply(qkv, groups, q_per_group, cu, scale, causal)
 
 
+def _strides_ok(t):
+    return t.stride(2) == 1 and t.stride(1) % 8 == 0 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
+
+
+def attention_with_lse(q, k, v, *, causal=True, scale=None, cu_seqlens=None, cu_seqlens_k=None):
+    """(output [Tq, Hq, D], log-sum-exp [Hq, Tq] fp32) of one attention call; the building block of the
+    context-parallel schemes, which merge partial results by their log-sum-exp. Native kernel on a GPU, the fp32
+    formulation elsewhere."""
+    D = q.shape[-1]
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    if q.is_cuda and _ATTN_IMPL["impl"] != "sdpa" and native_attention_supported(q, k, v):
+        cq = cu_seqlens.to(device=q.device, dtype=torch.int32).contiguous() if cu_seqlens is not None else None
+        ck = cu_seqlens_k.to(device=q.device, dtype=torch.int32).contiguous() if cu_seqlens_k is not None else None
+        q, k, v = (t if _strides_ok(t) else t.contiguous() for t in (q, k, v))
+        return _AttnFn.apply(q, k, v, cq, ck, scale, causal)
+    return attention_ref(q, k, v, causal, scale, cu_seqlens, cu_seqlens_k, return_lse=True)
+
+
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = True,
-              scale: Optional[float] = None, cu_seqlens: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Softmax attention over packed tokens. q [T, Hq, D], k/v [T, Hkv, D] -> [T, Hq, Dv]."""
+              scale: Optional[float] = None, cu_seqlens: Optional[torch.Tensor] = None,
+              cu_seqlens_k: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Softmax attention over packed tokens. q [Tq, Hq, D], k/v [Tk, Hkv, D] -> [Tq, Hq, Dv]. With Tq != Tk the causal
+    mask is aligned to the bottom right (per sequence when boundaries are given)."""
     D = q.shape[-1]
     scale = 1.0 / math.sqrt(D) if scale is None else scale
     impl = _ATTN_IMPL["impl"]
     if q.is_cuda and impl != "sdpa" and native_attention_supported(q, k, v):
-        cu = cu_seqlens.to(torch.int32).contiguous() if cu_seqlens is not None else None
-
-        def ok(t):
-            return t.stride(2) == 1 and t.stride(1) % 8 == 0 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
-
-        q, k, v = (t if ok(t) else t.contiguous() for t in (q, k, v))
-        return _AttnFn.apply(q, k, v, cu, scale, causal)
+        return attention_with_lse(q, k, v, causal=causal, scale=scale, cu_seqlens=cu_seqlens,
+                                  cu_seqlens_k=cu_seqlens_k)[0]
     if impl == "native" and q.is_cuda:
         raise RuntimeError("native attention requested but not available for this shape")
-    if q.is_cuda and cu_seqlens is None:
+    same = q.shape[0] == k.shape[0] and cu_seqlens_k is None
+    if q.is_cuda and cu_seqlens is None and same:
         Hq, Hkv = q.shape[1], k.shape[1]
         o = F.scaled_dot_product_attention(
             q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None],
             is_causal=causal, scale=scale, enable_gqa=Hq != Hkv)
         return o[0].transpose(0, 1).contiguous()
-    if q.is_cuda:
-        # library fallback for head dims the tcgen05 kernel does not cover (e.g. ViT d=80):
+    if q.is_cuda and same:
+        # library baseline for dtypes / head dims the tcgen05 kernel does not cover (fp32, head dim > 128):
         # block-diagonal (+ causal) mask from the sequence boundaries
         T = q.shape[0]
         idx = torch.arange(T, device=q.device)
@@ -467,7 +513,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
             q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None], attn_mask=mask[None, None],
             scale=scale, enable_gqa=Hq != Hkv)
         return o[0].transpose(0, 1).contiguous()
-    return attention_ref(q, k, v, causal, scale, cu_seqlens)
+    return attention_ref(q, k, v, causal, scale, cu_seqlens, cu_seqlens_k)
 
 
 # ----------------------------------------------------------------------------- fused linear + cross entropy

@@ -63,7 +63,9 @@ def set_recipe(r: Optional[BlockScalingRecipe]) -> None:
 def _scale(amax: torch.Tensor, pow2: bool, eps: float = 0.0) -> torch.Tensor:
     s = amax.clamp(min=max(eps, 1e-12)) / E4M3_MAX
     if pow2:
-        s = torch.exp2(torch.ceil(torch.log2(s)))
+        # smallest power of two >= s, exactly (log2 / ceil is off by one binade at exact powers on some back ends)
+        m, e = torch.frexp(s)  # s = m * 2^e, m in [0.5, 1)
+        s = torch.ldexp(torch.ones_like(s), torch.where(m == 0.5, e - 1, e))
     return s
 
 
