@@ -279,14 +279,12 @@ def core_attention(q, k, v, *, causal, scale, cu_seqlens, cfg: Optional[Transfor
     """Attention over packed tokens; context parallelism is applied here when enabled."""
     st = ps.get_state()
     if CHUNK_PREFIX["active"]:
-        from ..parallel.context_parallel import _masked_attention
         assert cu_seqlens is None and st.dims.cp == 1, "chunk pipelining runs one unpacked sequence per micro-batch"
-        past, T = CHUNK_PREFIX["past"], q.shape[0]
+        past = CHUNK_PREFIX["past"]
         CHUNK_PREFIX["out"] = (k, v)
         kk, vv = (torch.cat([past[0], k]), torch.cat([past[1], v])) if past is not None else (k, v)
-        P = kk.shape[0] - T
-        pos = torch.arange(P + T, device=q.device)
-        return _masked_attention(q, kk, vv, pos[P:], pos, scale, causal)
+        # fewer queries than keys: the causal mask is aligned to the bottom right, i.e. the chunk follows its prefix
+        return OF.attention(q, kk, vv, causal=causal, scale=scale)
     if st.dims.cp > 1:
         from ..parallel import context_parallel as CP
         return CP.ring_attention(q, k, v, causal=causal, scale=scale, cu_seqlens=cu_seqlens, row_length=row_length)

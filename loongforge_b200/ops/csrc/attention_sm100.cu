@@ -149,6 +149,12 @@ __device__ __forceinline__ int visible_keys(const Seq& s, int q_first, int rows,
   return max(lim, 0);
 }
 
+// Wait of a math warp. All lanes execute the blocking try_wait: its wake-up latency is far below that of a polled
+// test_wait + nanosleep, and the softmax / gradient math sits on the critical path between two tensor-core products.
+__device__ __forceinline__ bool math_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait(bar, parity, abort_flag);
+}
+
 struct SharedCtl {
   uint64_t bars[24];
   uint32_t tmem_slot;
@@ -304,7 +310,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     float l_sum = 0.f;
     bool ok = true;
     for (int j = 0; j < my_n && ok; ++j) {
-      ok = mbar_wait_warp(&bars[F_S_FULL + t], j & 1, abort_flag);
+      ok = math_wait(&bars[F_S_FULL + t], j & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
       const int kv0 = j * 128;
@@ -345,7 +351,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
       if (any) {
         // O must be complete (O += P[j-1] V[j-1] retired) before its rows are rescaled
-        ok = mbar_wait_warp(&bars[F_O_DONE + t], (j - 1) & 1, abort_flag);
+        ok = math_wait(&bars[F_O_DONE + t], (j - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
 #pragma unroll 1
@@ -405,7 +411,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       if (lane == 0) mbar_arrive(&bars[F_P_FULL + t]);
     }
     // ---------------------------------------------------------------- epilogue
-    if (ok && my_n > 0) ok = mbar_wait_warp(&bars[F_O_DONE + t], (my_n - 1) & 1, abort_flag);
+    if (ok && my_n > 0) ok = math_wait(&bars[F_O_DONE + t], (my_n - 1) & 1, abort_flag);
     if (!ok) {
       if (lane == 0) atomicCAS(p.status, 0, LF_ERR_WAIT_TMEM_FULL);
     } else {
@@ -631,8 +637,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       const int b = it & 1, s = it % ST;
       const int qb = qb_first + it / p.R;
       const int qc0 = qb * 64 + half * 32;  // first query row of this warp's columns
-      ok = mbar_wait_warp(&bars[B_QDO_FULL + s], (it / ST) & 1, abort_flag);  // statistics visible
-      if (ok) ok = mbar_wait_warp(&bars[B_S_FULL + b], (it >> 1) & 1, abort_flag);
+      ok = math_wait(&bars[B_QDO_FULL + s], (it / ST) & 1, abort_flag);  // statistics visible
+      if (ok) ok = math_wait(&bars[B_S_FULL + b], (it >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
       uint32_t rs[32], rd[32];
@@ -670,7 +676,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars[B_PDS_FULL + b]);
     }
-    if (ok && n_iter > 0) ok = mbar_wait_warp(&bars[B_ACC_DONE], 0, abort_flag);
+    if (ok && n_iter > 0) ok = math_wait(&bars[B_ACC_DONE], 0, abort_flag);
     if (!ok) {
       if (lane == 0) atomicCAS(p.status, 0, LF_ERR_WAIT_TMEM_FULL);
     } else {
@@ -864,7 +870,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int kv0 = j * 128;
-      ok = mbar_wait_warp(&bars[Q_S_FULL], j & 1, abort_flag);
+      ok = math_wait(&bars[Q_S_FULL], j & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
       const int lim = row_lim - kv0;  // score columns [0, lim) of this row are kept
@@ -898,7 +904,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars[Q_DS_FULL]);
     }
-    if (ok && n_kv > 0) ok = mbar_wait_warp(&bars[Q_ACC_DONE], (n_kv - 1) & 1, abort_flag);
+    if (ok && n_kv > 0) ok = math_wait(&bars[Q_ACC_DONE], (n_kv - 1) & 1, abort_flag);
     if (!ok) {
       if (lane == 0) atomicCAS(p.status, 0, LF_ERR_WAIT_TMEM_FULL);
     } else {
