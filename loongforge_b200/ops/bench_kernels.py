@@ -3,6 +3,8 @@
     python -m loongforge_b200.ops.bench_kernels gemm [--m 8192 --n 4096 --k 4096] [--iters 20]
     python -m loongforge_b200.ops.bench_kernels attention [--t 8192 --groups 8 --rep 4]
     python -m loongforge_b200.ops.bench_kernels norm [--t 8192 --h 4096]
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29511 \
+        -m loongforge_b200.ops.bench_kernels tp [--t 8192]     (fused TP GEMMs against NCCL + GEMM, Llama-3-8B shapes)
 
 Each sub-command prints one JSON line; `--once` runs a single un-timed invocation (for profilers).
 """
@@ -31,9 +33,82 @@ def _time(fn, iters, warm=5):
     return s.elapsed_time(e) / iters
 
 
+def tp_bench(a):
+    """All-gather->GEMM and GEMM->reduce-scatter of one tensor-parallel Llama-3-8B layer (hidden 4096, FFN 14336,
+    32 q / 8 kv heads) on `world` GPUs: the fused peer-memory kernels against NCCL collective + plain GEMM, forward
+    shapes. Times are CUDA-event times, max over ranks; the roofline is the slower of the FLOPs at the measured
+    sustained bf16 peak and the bytes that must cross NVLink at the measured 770 GB/s per direction."""
+    import os
+
+    import torch.distributed as dist
+
+    from ..parallel import fused_tp, state as ps
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    ps.initialize_model_parallel(ps.ParallelDims(tp=world))
+    g = ps.get_state().group("tp")
+    T, H, F = a.t, 4096, 14336
+    rows = T // world
+    peak = 1376.9e12
+    try:
+        peak = json.load(open(os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")))[
+            "bf16_tflops_sustained"] * 1e12
+    except Exception:  # noqa: BLE001
+        pass
+    torch.manual_seed(0)
+    res = {"what": "tp", "world": world, "t": T, "rows": []}
+
+    def timed(fn):
+        ms = torch.tensor([_time(fn, a.iters)], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms)
+
+    # (name, kind, K, N_local)
+    shapes = [("qkv", "ag", H, (32 + 16) * 128 // world), ("fc1", "ag", H, 2 * F // world),
+              ("proj", "rs", H // world, H), ("fc2", "rs", F // world, H)]
+    for name, kind, K, N in shapes:
+        w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+        if kind == "ag":
+            xs = torch.randn(rows, K, device=dev).bfloat16()
+            xf = torch.empty(T, K, device=dev, dtype=torch.bfloat16)
+
+            def nccl():
+                dist.all_gather_into_tensor(xf, xs, group=g)
+                return OF.gemm(xf, w)
+
+            fused = lambda: fused_tp._ag_gemm(xs, w, False, None, None)[0]  # noqa: E731
+            link_bytes = (world - 1) * rows * K * 2  # received per GPU
+        else:
+            x = torch.randn(T, K, device=dev).bfloat16()
+            out = torch.empty(rows, N, device=dev, dtype=torch.bfloat16)
+
+            def nccl():
+                y = OF.gemm(x, w)
+                dist.reduce_scatter_tensor(out, y, group=g)
+                return out
+
+            fused = lambda: fused_tp._gemm_rs(x, w, False, None, None)  # noqa: E731
+            link_bytes = (world - 1) * rows * N * 2  # partial sums sent per GPU
+        flops = 2.0 * T * K * N
+        t_n, t_f = timed(nccl), timed(fused)
+        t_gemm = timed((lambda: OF.gemm(xf, w)) if kind == "ag" else (lambda: OF.gemm(x, w)))
+        ideal = max(flops / peak, link_bytes / 770e9) * 1e3
+        res["rows"].append({"layer": name, "kind": kind, "K": K, "N": N, "nccl_plus_gemm_ms": t_n, "fused_ms": t_f,
+                            "gemm_only_ms": t_gemm, "roofline_ms": ideal, "fused_fraction_of_roofline": ideal / t_f})
+    torch.cuda.synchronize()
+    _ext.check_status()
+    if rank == 0:
+        print(json.dumps(res))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "norm", "grouped", "router", "fp8"])
+    ap.add_argument("what", choices=["gemm", "attention", "norm", "grouped", "router", "fp8", "tp"])
     ap.add_argument("--experts", type=int, default=16)
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--m", type=int, default=8192)
@@ -47,6 +122,8 @@ def main():
     ap.add_argument("--once", action="store_true")
     a = ap.parse_args()
     _ext.require()
+    if a.what == "tp":
+        return tp_bench(a)
     dev = "cuda"
     torch.manual_seed(0)
     out = {"what": a.what}

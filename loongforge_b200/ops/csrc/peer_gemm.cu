@@ -4,13 +4,14 @@
 //           GEMM, and the reference's closest analogue, TE userbuffers overlap,
 //           loongforge/train/initialize.py:349-351):
 //   One launch = a few COPY CTAs + the persistent tcgen05 GEMM CTAs.
-//   Copy CTAs pull the peers' activation shards through NVLink with SM-issued bulk copies
-//   (peer global -> shared -> local global, several 32 KB copies in flight per CTA) into a local
-//   [T, K] buffer, one 128-row block at a time, and publish `chunk_flags[block] = epoch`. The GEMM
-//   CTAs visit the row blocks in the same order (own rows first) and their TMA producer waits
-//   (bounded) on the flag of the block it is about to load, so the transfer of block i+1 overlaps
-//   the math of block i. Every remote byte crosses NVLink exactly once and is then re-read by the
-//   N/256 column tiles from local memory / L2.
+//   Every rank keeps a symmetric [T, K] gather buffer and has written its OWN rows into it before the
+//   launch. Copy CTAs pull the peers' rows through NVLink with SM-issued bulk copies (peer global ->
+//   shared -> local global, several 32 KB copies in flight per CTA) into the same rows of the local
+//   buffer, one 128-row block at a time, and publish `chunk_flags[block] = epoch`. The GEMM CTAs start
+//   on their own rows at once (nothing to wait for) and their TMA producer waits (bounded) on the flag
+//   of a remote block only when it reaches it, so the transfer overlaps the math of the own rows. Every
+//   remote byte crosses NVLink exactly once and is then re-read by the N/256 column tiles from local
+//   memory / L2.
 //
 // gemm_rs  (GEMM -> reduce-scatter (+ residual); replaces TE RowParallelLinear + reduce_scatter):
 //   Tiles whose rows belong to a peer are computed FIRST and their bf16 partial sums are stored
@@ -33,7 +34,9 @@ static constexpr int PG_BM = 128, PG_BN = 256, PG_BK = 64, PG_UMMA_K = 16, PG_ST
 static constexpr int PG_THREADS = 192;
 static constexpr int PG_A_BYTES = PG_BM * PG_BK * 2, PG_B_BYTES = PG_BN * PG_BK * 2;
 static constexpr int PG_STAGE_BYTES = PG_A_BYTES + PG_B_BYTES;
-static constexpr int PG_SMEM_BYTES = PG_STAGES * PG_STAGE_BYTES + 1024 + 256;
+static constexpr int PG_STG_ROW = 144;  // bytes per staged row: 64 bf16 + 16 bytes of padding (conflict-free 16-byte stores)
+static constexpr int PG_STG_BYTES = 4 * 32 * PG_STG_ROW;  // one [32 rows x 64 columns] patch per epilogue warp
+static constexpr int PG_SMEM_BYTES = PG_STAGES * PG_STAGE_BYTES + PG_STG_BYTES + 1024 + 256;
 static constexpr int CP_PIECE = 32 * 1024;  // bytes per bulk copy
 static constexpr int CP_STAGES = 5;         // 160 KB of the same dynamic shared memory
 
@@ -127,11 +130,14 @@ __device__ void ag_copy_cta(const PeerParams& p, uint8_t* smem, uint64_t* bars) 
   const long long block_bytes = static_cast<long long>(PG_BM) * p.K * 2;
   const int pieces = static_cast<int>((block_bytes + CP_PIECE - 1) / CP_PIECE);
   uint32_t issued = 0;  // pieces whose load has been issued (stage = issued % CP_STAGES)
-  for (int vb = c; vb < p.tiles_m; vb += p.copy_ctas) {
-    // visiting order: own shard first, then rank+1, rank+2, ...
-    const int b = (vb + p.rank * p.tiles_per_rank_m) % p.tiles_m;
+  // only the peers' rows move: this rank's own rows were written into the buffer before the launch
+  const int remote_blocks = p.tiles_m - p.tiles_per_rank_m;
+  for (int vb = c; vb < remote_blocks; vb += p.copy_ctas) {
+    // visiting order: rank+1's shard first, then rank+2, ... (the order in which the GEMM CTAs reach them)
+    const int b = ((p.rank + 1) * p.tiles_per_rank_m + vb) % p.tiles_m;
     const int src_rank = b / p.tiles_per_rank_m;
-    const uint8_t* src = p.peer_x[src_rank] + static_cast<long long>(b - src_rank * p.tiles_per_rank_m) * block_bytes;
+    // every rank's buffer has the same layout: block b sits at the same offset on its owner
+    const uint8_t* src = p.peer_x[src_rank] + static_cast<long long>(b) * block_bytes;
     uint8_t* dst = p.x_full + static_cast<long long>(b) * block_bytes;
     int loaded = 0, stored = 0;
     const uint32_t base = issued;
@@ -182,7 +188,8 @@ peer_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PG_STAGES * PG_STAGE_BYTES);
+  uint8_t* stage_base = smem + PG_STAGES * PG_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_base + PG_STG_BYTES);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + PG_STAGES;
   uint64_t* tmem_full = bars + 2 * PG_STAGES;
@@ -235,7 +242,7 @@ peer_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int vm, tn;
         pg_tile_coords(tile, p.tiles_m, p.tiles_n, vm, tn);
         const int tm = (vm + rot) % p.tiles_m;
-        if (MODE == 0 && tm != ready_block) {
+        if (MODE == 0 && tm != ready_block && tm / p.tiles_per_rank_m != p.rank) {
           if (!wait_flag_ge<false>(p.chunk_flags + tm, p.epoch, p.wait_cycles)) {
             atomicCAS(p.status, 0, LF_ERR_WAIT_PEER);
             *abort_flag = 1;
@@ -355,19 +362,27 @@ peer_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         drow = p.out + static_cast<long long>(row) * p.ldo;
       }
       if (ok) {
+        uint8_t* stg = stage_base + (warp & 3) * (32 * PG_STG_ROW);
+        // first row of this warp's 32-row patch in the destination, and the destination's row pitch
+        __nv_bfloat16* dwarp = drow - static_cast<long long>(lane) * ((MODE == 1) ? (owner != p.rank ? p.N : p.ldo) : p.ldo);
+        const long long dpitch = (MODE == 1) ? (owner != p.rank ? p.N : p.ldo) : p.ldo;
 #pragma unroll 1
-        for (int c0 = 0; c0 < PG_BN; c0 += 32) {
+        for (int c0 = 0; c0 < PG_BN; c0 += 64) {
           const int col = tn * PG_BN + c0;
           if (col >= p.N) break;
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(taddr + c0, r);
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32b_x32(taddr + c0, r0);
+          tmem_ld_32x32b_x32(taddr + c0 + 32, r1);
           tmem_ld_wait();
-          float v[32];
+          float v[64];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          for (int j = 0; j < 32; ++j) {
+            v[j] = __uint_as_float(r0[j]);
+            v[32 + j] = __uint_as_float(r1[j]);
+          }
           if (p.bias != nullptr && (MODE == 0)) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
+            for (int j = 0; j < 64; ++j)
               if (col + j < p.N) v[j] += __bfloat162float(p.bias[col + j]);
           }
           if (MODE == 1 && owner == p.rank) {
@@ -378,7 +393,7 @@ peer_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                   p.peer_recv[p.rank] +
                   ((static_cast<long long>(p.parity) * p.world + src) * p.rows_per_rank + lrow) * p.N + col;
 #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
+              for (int j = 0; j < 64; j += 8) {
                 if (col + j + 8 <= p.N) {
                   const uint4 q = __ldcv(reinterpret_cast<const uint4*>(rr + j));
                   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
@@ -394,7 +409,7 @@ peer_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (p.residual != nullptr) {
               const __nv_bfloat16* rs = p.residual + static_cast<long long>(lrow) * p.ldr + col;
 #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
+              for (int j = 0; j < 64; j += 8) {
                 if (col + j + 8 <= p.N) {
                   const uint4 q = *reinterpret_cast<const uint4*>(rs + j);
                   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
@@ -408,15 +423,26 @@ peer_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               }
             }
           }
+          // transpose through shared memory: each thread parks its row's 128 bytes, then the warp writes four rows
+          // per instruction as full 128-byte segments (efficient NVLink packets for the remote tiles)
+          __syncwarp();
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            if (col + j + 8 <= p.N) {
-              uint4 o;
-              o.x = pack_bf16x2(v[j], v[j + 1]);
-              o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-              o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-              o.w = pack_bf16x2(v[j + 6], v[j + 7]);
-              *reinterpret_cast<uint4*>(drow + col + j) = o;
+          for (int j = 0; j < 64; j += 8) {
+            uint4 o;
+            o.x = pack_bf16x2(v[j], v[j + 1]);
+            o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+            o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+            o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+            *reinterpret_cast<uint4*>(stg + lane * PG_STG_ROW + j * 2) = o;
+          }
+          __syncwarp();
+          const int piece = lane & 7;
+          if (col + piece * 8 + 8 <= p.N) {
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int rr = it * 4 + (lane >> 3);
+              const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * PG_STG_ROW + piece * 16);
+              *reinterpret_cast<uint4*>(dwarp + rr * dpitch + col + piece * 8) = o;
             }
           }
         }

@@ -58,20 +58,23 @@ class _AgContext:
     """Buffers of the all-gather->GEMM kernel for one (rows_per_rank, K) shape."""
 
     def __init__(self, rows: int, K: int, group, device):
-        shard = rows * K * 2
-        self.sync_off = 2 * shard
-        self.block = _SymmetricBlock(2 * shard + 256, group, device)
+        world = dist.get_world_size(group)
+        full = rows * world * K * 2
+        self.sync_off = 2 * full
+        # two (call parity) symmetric [T, K] gather buffers: every rank writes its own rows in place and pulls the
+        # peers' rows from the same offsets of their buffers
+        self.block = _SymmetricBlock(2 * full + 256, group, device)
         self.rows, self.K = rows, K
         self.world, self.rank = self.block.world, self.block.rank
-        self.shard_bytes = shard
-        self.x_sym = [self.block.local_view(i * shard, shard, torch.bfloat16, (rows, K)) for i in range(2)]
+        self.full_bytes = full
+        self.x_sym = [self.block.local_view(i * full, full, torch.bfloat16, (rows * world, K)) for i in range(2)]
         self.chunk_flags = torch.zeros(rows * self.world // 128, dtype=torch.int32, device=device)
         self.epoch = 0
 
     def next(self):
         self.epoch += 1
         par = self.epoch & 1
-        return self.epoch, self.x_sym[par], self.block.peer_ptrs(par * self.shard_bytes), \
+        return self.epoch, self.x_sym[par], self.block.peer_ptrs(par * self.full_bytes), \
             self.block.peer_ptrs(self.sync_off)
 
 
@@ -126,12 +129,12 @@ def supported(x: torch.Tensor, weight: torch.Tensor, rows_per_rank: int) -> bool
 
 
 def _ag_gemm(x_shard: torch.Tensor, B: torch.Tensor, b_mn: bool, bias, state_name):
-    """Returns (all_gather(x_shard) @ op(B), gathered x)."""
+    """Returns (all_gather(x_shard) @ op(B), gathered x). The gathered tensor is a view of the symmetric gather buffer:
+    it stays valid until the second-next call for the same shape, so consumers use it right away (same stream)."""
     rows, K = x_shard.shape
     ctx = _get_ag(rows, K, state_name, x_shard.device)
-    epoch, x_sym, peer_x, peer_sync = ctx.next()
-    x_sym.copy_(x_shard)
-    x_full = torch.empty(rows * ctx.world, K, dtype=x_shard.dtype, device=x_shard.device)
+    epoch, x_full, peer_x, peer_sync = ctx.next()
+    x_full[ctx.rank * rows:(ctx.rank + 1) * rows].copy_(x_shard)
     y = _ext.require().ag_gemm(peer_x, peer_sync, x_full, ctx.chunk_flags, B, b_mn, bias, ctx.rank, rows, epoch,
                                _COPY_CTAS, _ext.status_tensor(x_shard.device))
     return y, x_full
@@ -146,23 +149,46 @@ def _gemm_rs(a: torch.Tensor, B: torch.Tensor, b_mn: bool, residual, state_name)
                                   _ext.status_tensor(a.device))
 
 
+_side_stream: Dict[int, torch.cuda.Stream] = {}
+
+
+def _side(device) -> torch.cuda.Stream:
+    s = _side_stream.get(device.index)
+    if s is None:
+        s = _side_stream[device.index] = torch.cuda.Stream(device=device)
+    return s
+
+
 class _AllGatherLinearFn(torch.autograd.Function):
+    """Forward keeps only this rank's sequence shard (as Megatron's sequence parallelism does); backward gathers it
+    again on a side stream while the input-gradient GEMM -> reduce-scatter kernel runs."""
+
     @staticmethod
     def forward(ctx, x, weight, bias, state_name):
-        y, x_full = _ag_gemm(x, weight, False, bias, state_name)
-        ctx.save_for_backward(x_full, weight)
+        y, _ = _ag_gemm(x, weight, False, bias, state_name)
+        ctx.save_for_backward(x, weight)
         ctx.state_name = state_name
         ctx.has_bias = bias is not None
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x_full, weight = ctx.saved_tensors
+        x, weight = ctx.saved_tensors
         dy = dy.contiguous()
         dx = dw = db = None
+        x_full = None
+        if ctx.needs_input_grad[1]:
+            _, g = _group(ctx.state_name)
+            cur, side = torch.cuda.current_stream(), _side(x.device)
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                x_full = torch.empty(x.shape[0] * dist.get_world_size(g), x.shape[1], dtype=x.dtype, device=x.device)
+                dist.all_gather_into_tensor(x_full, x.contiguous(), group=g)
+            x_full.record_stream(cur)
         if ctx.needs_input_grad[0]:
             dx = _gemm_rs(dy, weight, True, None, ctx.state_name)
         if ctx.needs_input_grad[1]:
+            torch.cuda.current_stream().wait_stream(_side(x.device))
             dw = OF._wgrad(dy, x_full, weight)
         if ctx.has_bias:
             db = dy.float().sum(0).to(dy.dtype)

@@ -17,7 +17,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, queue):
     import torch.distributed as dist
 
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
@@ -61,11 +61,11 @@ def _worker(rank, world, port, q):
             out[comm] = (rel(o, ref[idx]), rel(ql.grad, qr.grad[idx]), rel(kl.grad, kr.grad[idx]),
                          rel(vl.grad, vr.grad[idx]), peak)
         CP.set_cp_comm_type("auto")
-        q.put((rank, "ok", out))
+        queue.put((rank, "ok", out))
     except Exception:  # noqa: BLE001
         import traceback
 
-        q.put((rank, "err", traceback.format_exc()))
+        queue.put((rank, "err", traceback.format_exc()))
     finally:
         try:
             dist.destroy_process_group()
@@ -87,7 +87,7 @@ def test_context_parallel_matches_single_gpu_kernel(world):
         p.start()
     try:
         for _ in range(world):
-            rank, status, payload = q.get(timeout=600)
+            rank, status, payload = q.get(timeout=240)
             assert status == "ok", f"rank {rank}:\n{payload}"
             for comm, (eo, eq, ek, ev, peak) in payload.items():
                 assert eo < 2e-2 and eq < 3e-2 and ek < 3e-2 and ev < 3e-2, (comm, payload[comm])

@@ -1,4 +1,4 @@
-"""Fused all-gather->GEMM and GEMM->reduce-scatter kernels against the NCCL + GEMM reference
+"""Fused all-gather->GEMM and GEMM->reduce-scatter kernels against plain fp32 products and the NCCL + GEMM path
 (needs >= 2 GPUs; spawned as one process per GPU)."""
 import os
 import socket
@@ -52,6 +52,14 @@ def _worker(rank, world, port, q):
             yr = OF.linear(M.gather_from_sequence_parallel_region(xs2, g, True), w2)
             yr.backward(gy)
             errs[f"ag{trial}_y"] = rel(y, yr)
+            # also against a plain fp32 product of the full operands (not only against the library path)
+            y32 = x_full.float() @ w_full.float().t()
+            errs[f"ag{trial}_y_fp32"] = rel(y, y32.chunk(world, 1)[rank])
+            errs[f"ag{trial}_dw_fp32"] = rel(w.grad, gy.float().t() @ x_full.float())
+            gy_all = [torch.empty_like(gy) for _ in range(world)]
+            dist.all_gather(gy_all, gy)
+            dx32 = sum(gy_all[r].float() @ w_full.chunk(world, 0)[r].float() for r in range(world))
+            errs[f"ag{trial}_dx_fp32"] = rel(xs.grad, dx32.chunk(world, 0)[rank])
             errs[f"ag{trial}_dx"] = rel(xs.grad, xs2.grad)
             errs[f"ag{trial}_dw"] = rel(w.grad, w2.grad)
             # ---- GEMM -> reduce-scatter (row parallel: W sharded on K), with residual
@@ -66,6 +74,13 @@ def _worker(rank, world, port, q):
             zr = M.reduce_scatter_to_sequence_parallel_region(OF.linear(xr2, wr2), g) + res.detach()
             zr.backward(gz)
             errs[f"rs{trial}_z"] = rel(z, zr)
+            z32 = (x_full.float() @ w_full.float().t()).chunk(world, 0)[rank] + res.detach().float()
+            errs[f"rs{trial}_z_fp32"] = rel(z, z32)
+            gz_all = [torch.empty_like(gz) for _ in range(world)]
+            dist.all_gather(gz_all, gz)
+            gz_full = torch.cat(gz_all).float()
+            errs[f"rs{trial}_dx_fp32"] = rel(xr.grad, gz_full @ w_full.chunk(world, 1)[rank].float())
+            errs[f"rs{trial}_dw_fp32"] = rel(wr.grad, gz_full.t() @ x_full.chunk(world, 1)[rank].float())
             errs[f"rs{trial}_dx"] = rel(xr.grad, xr2.grad)
             errs[f"rs{trial}_dw"] = rel(wr.grad, wr2.grad)
             errs[f"rs{trial}_dres"] = rel(res.grad, gz)
