@@ -35,8 +35,12 @@ struct GemmCfg {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulators
+  // epilogue transpose patches: one [32 rows x 32 fp32 columns] patch per epilogue warp, rows padded by 16 bytes so
+  // that the 16-byte stores of a warp spread over all banks
+  static constexpr int STG_ROW = 144;
+  static constexpr int STG_BYTES = NUM_EPI_WARPS * 32 * STG_ROW;
   // +1024 for manual 1024-byte alignment of the swizzled tiles, +256 for barriers
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STG_BYTES + 1024 + 256;
 };
 
 struct GemmParams {
@@ -74,7 +78,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   // 128B-swizzled tiles need 1024-byte alignment.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint8_t* stage_base = smem + STAGES * Cfg::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_base + Cfg::STG_BYTES);
   uint64_t* full_bar = bars;                 // [STAGES]
   uint64_t* empty_bar = bars + STAGES;       // [STAGES]
   uint64_t* tmem_full = bars + 2 * STAGES;   // [2]
@@ -212,9 +217,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         break;
       }
       tc_fence_after_sync();
-      const int row = tm * BM + quarter * 32 + lane;
-      const bool row_ok = row < p.M;
+      // Drain: every thread reads 32 accumulator columns of ITS row from TMEM and parks them in a shared-memory patch;
+      // the warp then walks the patch transposed, four rows per instruction with eight lanes per row, so that bias,
+      // residual, the fp32 read-modify-write of accumulate mode and the stores all touch full contiguous row segments.
+      const int row0 = tm * BM + quarter * 32;  // first row of this warp's patch
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      uint8_t* stg = stage_base + quarter * (32 * Cfg::STG_ROW);
+      const int piece = lane & 7;   // four consecutive columns of a row
+      const int rsub = lane >> 3;   // row inside a group of four
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         const int col = tn * BN + c0;
@@ -222,63 +232,62 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c0, r);
         tmem_ld_wait();
-        if (row_ok) {
-          float v[32];
+        __syncwarp();  // the previous chunk's readers are done with the patch
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-          if (p.bias != nullptr) {
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<uint4*>(stg + lane * Cfg::STG_ROW + j * 4) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+        __syncwarp();
+        const int c = col + piece * 4;  // first of this lane's four columns
+        const bool full4 = c + 4 <= p.N;
+        float bias4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (p.bias != nullptr) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col + j < p.N) v[j] += __bfloat162float(p.bias[col + j]);
-          }
+          for (int t = 0; t < 4; ++t)
+            if (c + t < p.N) bias4[t] = __bfloat162float(p.bias[c + t]);
+        }
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int rr = it * 4 + rsub;
+          const int row = row0 + rr;
+          if (row >= p.M || c >= p.N) continue;
+          const float4 a4 = *reinterpret_cast<const float4*>(stg + rr * Cfg::STG_ROW + piece * 16);
+          float v[4] = {a4.x * p.alpha + bias4[0], a4.y * p.alpha + bias4[1], a4.z * p.alpha + bias4[2],
+                        a4.w * p.alpha + bias4[3]};
           if (p.out_mode == 0) {
-            __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + col;
-            const __nv_bfloat16* rs =
-                p.residual ? p.residual + static_cast<long long>(row) * p.ldr + col : nullptr;
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col + j + 8 <= p.N) {
-                if (rs) {
-                  const uint4 q = *reinterpret_cast<const uint4*>(rs + j);
-                  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
-#pragma unroll
-                  for (int t = 0; t < 4; ++t) {
-                    const float2 f = __bfloat1622float2(h[t]);
-                    v[j + 2 * t] += f.x;
-                    v[j + 2 * t + 1] += f.y;
-                  }
-                }
-                uint4 o;
-                o.x = pack_bf16x2(v[j], v[j + 1]);
-                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
-                *reinterpret_cast<uint4*>(d + j) = o;
-              } else {
-                for (int t = 0; t < 8; ++t)
-                  if (col + j + t < p.N) {
-                    float x = v[j + t];
-                    if (rs) x += __bfloat162float(rs[j + t]);
-                    d[j + t] = __float2bfloat16(x);
-                  }
+            __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + c;
+            const __nv_bfloat16* rs = p.residual ? p.residual + static_cast<long long>(row) * p.ldr + c : nullptr;
+            if (full4) {
+              if (rs) {
+                const uint2 q = *reinterpret_cast<const uint2*>(rs);
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+                const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]);
+                v[0] += f0.x; v[1] += f0.y; v[2] += f1.x; v[3] += f1.y;
               }
+              uint2 o;
+              o.x = pack_bf16x2(v[0], v[1]);
+              o.y = pack_bf16x2(v[2], v[3]);
+              *reinterpret_cast<uint2*>(d) = o;
+            } else {
+              for (int t = 0; t < 4; ++t)
+                if (c + t < p.N) {
+                  float x = v[t];
+                  if (rs) x += __bfloat162float(rs[t]);
+                  d[t] = __float2bfloat16(x);
+                }
             }
           } else {
-            float* d = reinterpret_cast<float*>(p.D) + static_cast<long long>(row) * p.ldd + col;
+            float* d = reinterpret_cast<float*>(p.D) + static_cast<long long>(row) * p.ldd + c;
             const bool accumulate = p.out_mode == 2;
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              if (col + j + 4 <= p.N) {
-                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                if (accumulate) {
-                  const float4 old = *reinterpret_cast<const float4*>(d + j);
-                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                *reinterpret_cast<float4*>(d + j) = o;
-              } else {
-                for (int t = 0; t < 4; ++t)
-                  if (col + j + t < p.N) d[j + t] = accumulate ? d[j + t] + v[j + t] : v[j + t];
+            if (full4) {
+              float4 o = make_float4(v[0], v[1], v[2], v[3]);
+              if (accumulate) {
+                const float4 old = *reinterpret_cast<const float4*>(d);
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
               }
+              *reinterpret_cast<float4*>(d) = o;
+            } else {
+              for (int t = 0; t < 4; ++t)
+                if (c + t < p.N) d[t] = accumulate ? d[t] + v[t] : v[t];
             }
           }
         }
@@ -353,7 +362,6 @@ int make_tmap_u8_2d(CUtensorMap* map, const void* ptr, long long rows, long long
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
-static int g_num_sms = 0;
 
 template <int BN, bool A_MN, bool B_MN>
 static int launch_cfg(const GemmArgs& a, cudaStream_t stream) {
@@ -382,18 +390,20 @@ static int launch_cfg(const GemmArgs& a, cudaStream_t stream) {
   p.alpha = a.alpha;
   p.status = a.status;
   auto kern = gemm_bf16_tcgen05_kernel<BN, A_MN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  // per device: the shared-memory opt-in of this instantiation and the SM count (a process may drive several GPUs)
+  constexpr int kMaxDev = 64;
+  static bool attr_set[kMaxDev] = {};
+  static int num_sms[kMaxDev] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return -4;
+  if (!attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return -4;
-    attr_set = true;
+    cudaDeviceGetAttribute(&num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    attr_set[dev] = true;
   }
-  if (g_num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-  }
-  int sms = a.max_ctas > 0 ? (a.max_ctas < g_num_sms ? a.max_ctas : g_num_sms) : g_num_sms;
+  const int dev_sms = num_sms[dev];
+  int sms = a.max_ctas > 0 ? (a.max_ctas < dev_sms ? a.max_ctas : dev_sms) : dev_sms;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sms ? tiles : sms;
   if (grid <= 0) return 0;
