@@ -281,6 +281,10 @@ def get_rng_state() -> dict:
          "torch_rng_state": torch.get_rng_state()}
     if torch.cuda.is_available():
         s["cuda_rng_state"] = torch.cuda.get_rng_state()
+    # named streams of the model-parallel tracker (dropout inside tensor- / expert-parallel regions); reference:
+    # loongforge/train/checkpointing.py:511-552 saves them as `rng_tracker_states`
+    from ..parallel.random import get_rng_tracker
+    s["rng_tracker_states"] = get_rng_tracker().get_states()
     return s
 
 
@@ -290,6 +294,9 @@ def set_rng_state(s: dict) -> None:
     torch.set_rng_state(s["torch_rng_state"])
     if torch.cuda.is_available() and "cuda_rng_state" in s:
         torch.cuda.set_rng_state(s["cuda_rng_state"])
+    if s.get("rng_tracker_states"):
+        from ..parallel.random import get_rng_tracker
+        get_rng_tracker().set_states(s["rng_tracker_states"])
 
 
 def common_state(trainer) -> dict:

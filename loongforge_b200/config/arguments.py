@@ -255,10 +255,114 @@ def _add_peft_args(p):
     g.add_argument("--lora-target-modules", nargs="*", default=["linear_qkv", "linear_proj", "linear_fc1", "linear_fc2"])
 
 
+# (flag, kind, default) with kind: "flag" store_true, "noflag" store_false, int / float / str, "list" nargs="*".
+# The reference's own flags (loongforge/train/arguments.py:95-1439) that no group above defines, plus the Megatron
+# flags its example launchers pass. They are accepted so that those launchers run unchanged; `COMPAT_WIRED` lists the
+# ones the trainers act on, the rest describe code paths this framework covers differently (noted by the validators).
+_COMPAT_FLAGS = [
+    # tensor inspection / debugging
+    ("--log-tensor-stage", str, "forward"), ("--log-tensor-iter-pattern", str, None),
+    ("--log-tensor-mbs-pattern", str, None), ("--log-tensor-layer-pattern", str, None), ("--log-tensor-rank", str, "0"),
+    ("--save-tensor", "flag", False), ("--save-tensor-dir", str, ""), ("--random-fallback-cpu", "flag", False),
+    ("--no-detail-log", "noflag", True),
+    # low precision
+    ("--fp8-force-no-requant", "flag", False), ("--force-pow-2-scales", "flag", False), ("--amax-epsilon", float, 0.0),
+    ("--hf-dequantize-int4", "flag", False), ("--hf-dequantize-mxfp4", "flag", False),
+    ("--hf-dequantize-dtype", str, "bfloat16"), ("--hf-quant-config-file", str, None), ("--quant-method", str, "te"),
+    ("--pretrain-as-fp8", "flag", False), ("--enable-fp8-comm", "flag", False),
+    # model / attention
+    ("--enable-fa-within-mla", "flag", False), ("--language-model-type", str, None),
+    ("--should-get-embedding-weights-for-mtp", "flag", False), ("--cuda-graph-pad-length", int, None),
+    ("--rotary-seq-len-interpolation-factor", float, None), ("--no-position-embedding", "flag", False),
+    ("--attention-softmax-in-fp32", "flag", False), ("--no-masked-softmax-fusion", "flag", False),
+    ("--no-bias-gelu-fusion", "flag", False), ("--no-bias-dropout-fusion", "flag", False), ("--no-rope-fusion", "flag", False),
+    ("--mscale", float, None), ("--mscale-all-dim", float, None), ("--original-max-position-embeddings", int, None),
+    ("--moe-router-dtype", str, None), ("--moe-shared-expert-overlap", "flag", False),
+    # freezing / adapters
+    ("--freeze-parameters", "list", []), ("--freeze-parameters-regex", str, None), ("--trainable-modules", "list", ["all"]),
+    ("--allow-missing-adapter-checkpoint", "flag", False), ("--lora-dim", int, None),
+    # tokenizer
+    ("--hf-processor-path", str, None), ("--split-special-tokens", "flag", False), ("--padding-side", str, "right"),
+    ("--additional-special-tokens", str, None), ("--vocab-size-in-config-file", int, None), ("--padded-vocab-size", int, None),
+    # SFT data
+    ("--task-encoder", str, None), ("--chat-template-kwargs", str, None), ("--sft-train-dataset", "list", None),
+    ("--sft-valid-dataset", "list", None), ("--sft-test-dataset", "list", None), ("--sft-sort-batch", "flag", False),
+    ("--streaming-buffer-size", int, 16384), ("--sft-data-mix-strategy", str, "concat"),
+    ("--sft-num-preprocess-workers", int, None), ("--history-mask-loss", "flag", False), ("--is-tokenized-data", "flag", False),
+    ("--enable-discard-sample", "flag", False), ("--packing-buffer-size", int, 10000), ("--use-fixed-seq-lengths", "flag", False),
+    ("--sample-type", str, None), ("--packing-pretrain-data", "flag", False), ("--add-question-in-pretrain", "flag", False),
+    ("--data-shuffle-buffer-size", int, 0), ("--data-max-samples-per-sequence", int, 0), ("--dataloader-save", str, None),
+    ("--save-dataset-state", "flag", False), ("--dataloader-prefetch-factor", int, 2), ("--data-cache-path", str, None),
+    ("--no-create-attention-mask-in-dataloader", "flag", False),
+    # loss
+    ("--loss-reduction", str, "square"), ("--loss-reduction-all-gather", "flag", False),
+    ("--legacy-reporting-loss-reduction", "flag", False), ("--force-all-weight-decay", "flag", False),
+    # video / latent (diffusion) data
+    ("--latent-in-channels", int, None), ("--latent-out-channels", int, None), ("--caption-channels", int, None),
+    ("--latent-patch-size", str, None), ("--latent-space-scale", float, 1.0), ("--latent-time-scale", float, 1.0),
+    ("--num-latent-frames", int, None), ("--max-latent-height", int, None), ("--max-latent-width", int, None),
+    ("--max-text-length", int, None), ("--max-video-length", int, 32760), ("--max-image-length", int, None),
+    ("--max-timestep-boundary", float, 1.0), ("--min-timestep-boundary", float, 0.0), ("--dataset-metadata-path", str, None),
+    # multimodal (InternVL / Qwen-VL / RICE) data
+    ("--training-rice-vl-max-answer-length", int, 4096), ("--conv-style", str, "internvl2_5"), ("--force-image-size", int, 448),
+    ("--num-images-expected", int, 48), ("--pad2square", "flag", False), ("--down-sample-ratio", float, 0.5),
+    ("--max-buffer-size", int, 20), ("--max-packed-tokens", int, 8192), ("--strict-mode", "flag", False),
+    ("--replacement", "flag", False), ("--patch-size", int, 14), ("--group-by-length", "flag", False),
+    ("--min-num-frame", int, 8), ("--max-num-frame", int, 32), ("--dynamic-image-size", "flag", False),
+    ("--min-dynamic-patch", int, 1), ("--max-dynamic-patch", int, 12), ("--use_thumbnail", "flag", False),
+    ("--normalize_type", str, "imagenet"), ("--use-packed-ds", "flag", False), ("--frame-min-pixels", int, 128 * 28 * 28),
+    ("--frame-max-pixels", int, 768 * 28 * 28), ("--video-max-pixels", int, 65536 * 28 * 28), ("--fps-min-frames", int, 4),
+    ("--fps-max-frames", int, 768), ("--energon-pack-algo", str, "balanced"),
+    # data-parallel balancing of VLM batches
+    ("--use-vit-dp-balance", "flag", False), ("--vlm-dp-balance-warmup-iters", "list", [2, 5]),
+    ("--dp-balance-verbose", "flag", False), ("--dp-balance-max-len-ratio-vlm", float, 1.2),
+    ("--dp-balance-max-len-ratio-vit", float, None), ("--dp-balance-trigger-threshold-vlm", float, 0.2),
+    ("--dp-balance-trigger-threshold-vit", float, 0.2),
+    # EMA
+    ("--enable-ema", "flag", False), ("--save-ema", str, None), ("--load-ema", str, None),
+    # Megatron flags of the example launchers
+    ("--initial-loss-scale", float, 65536.0), ("--no-check-for-nan-in-loss-and-grad", "flag", False),
+    ("--empty-unused-memory-level", int, 0), ("--log-memory-to-tensorboard", "flag", False),
+    ("--log-validation-ppl-to-tensorboard", "flag", False), ("--tp-comm-overlap-bootstrap-backend", str, "nccl"),
+    ("--use-fp32-dtype-for-param-pattern", "list", None), ("--use-cpu-initialization", "flag", False),
+    ("--no-initialization", "flag", False), ("--reduce-variable-seq-shape-p2p-comm", "flag", False),
+    ("--offload-optimizer", str, None), ("--offload-optimizer-percent", float, None),
+    ("--overlap-cpu-optimizer-d2h-h2d", "flag", False), ("--ckpt-fully-parallel-load", "flag", False),
+    ("--no-strict-fsdp-dtensor-load", "flag", False), ("--suggested-communication-unit-size", int, None),
+    ("--timing-log-option", str, "minmax"), ("--disable-turn-off-bucketing", "flag", False),
+    ("--enable-experimental", "flag", False), ("--rope-scaling-factor", float, None),
+    ("--disable-rotate-activation", "flag", False),
+]
+
+# compat flags that change what the trainers do (the others are accepted and recorded in the argument dump)
+COMPAT_WIRED = {"--freeze-parameters", "--freeze-parameters-regex", "--trainable-modules", "--force-pow-2-scales",
+                "--amax-epsilon", "--enable-ema", "--no-check-for-nan-in-loss-and-grad", "--padded-vocab-size",
+                "--offload-optimizer", "--offload-optimizer-percent", "--no-position-embedding"}
+
+
+def _add_compat_args(p):
+    g = p.add_argument_group("reference compatibility")
+    have = {o for a in p._actions for o in a.option_strings}
+    for name, kind, default in _COMPAT_FLAGS:
+        if name in have:
+            continue
+        if kind == "flag":
+            # some launchers spell these with underscores
+            names = [name] + ([name.replace("-", "_").replace("__", "--", 1)] if name in (
+                "--fp8-force-no-requant", "--force-pow-2-scales") else [])
+            g.add_argument(*names, action="store_true", default=default)
+        elif kind == "noflag":
+            g.add_argument(name, action="store_false", default=default)
+        elif kind == "list":
+            g.add_argument(name, nargs="*", default=default)
+        else:
+            g.add_argument(name, type=kind, default=default)
+
+
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser("loongforge_b200 training", allow_abbrev=False)
     for add in (_add_model_args, _add_moe_args, _add_parallel_args, _add_training_args, _add_data_args,
-                _add_ckpt_logging_args, _add_peft_args):
+                _add_ckpt_logging_args, _add_peft_args, _add_compat_args):
         add(p)
     return p
 

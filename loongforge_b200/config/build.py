@@ -227,6 +227,10 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
         overlap_param_gather=args.overlap_param_gather, exp_avg_dtype=dt[args.exp_avg_dtype],
         exp_avg_sq_dtype=dt[args.exp_avg_sq_dtype], calculate_per_token_loss=args.calculate_per_token_loss,
         custom_pipeline_layers=custom_layers, custom_pipeline_recompute_layers=recompute_layers, training_phase=args.training_phase,
+        freeze_parameters=list(getattr(args, "freeze_parameters", None) or []),
+        freeze_parameters_regex=getattr(args, "freeze_parameters_regex", None),
+        trainable_modules=list(getattr(args, "trainable_modules", None) or []),
+        check_for_nan_in_loss=not bool(getattr(args, "no_check_for_nan_in_loss_and_grad", False)),
         log_throughput=True)  # --log-throughput: the TFLOP/s field is always part of the log line
     from .validators import validate
     validate(args, cfg, tc, dims)

@@ -165,7 +165,8 @@ class MLASelfAttention(nn.Module):
             qq = torch.cat([q_nope, q_pe], dim=-1)
             from .transformer import core_attention  # ring / all-gather attention under context parallelism
             o = core_attention(qq.contiguous(), k.contiguous(), v.contiguous(), causal=True, scale=scale, cu_seqlens=cu,
-                               cfg=cfg, row_length=packed.row_length if packed is not None else None)
+                               cfg=cfg, row_length=packed.row_length if packed is not None else None,
+                               training=self.training)
         else:
             o = self._dsa(x, q_c, q_nope, q_pe, kv_c, k_pe, w_up, rotary, cu, scale)
         return self.linear_proj(o.reshape(T, H * self.dv), residual)

@@ -227,7 +227,8 @@ class SelfAttention(nn.Module):
         if self.q_layernorm is None:
             if rotary is not None:
                 qkv = self._rope_packed(qkv, rotary)
-            if ps.get_state().dims.cp == 1 and not CHUNK_PREFIX["active"] and OF.attention_packed_supported(qkv, d):
+            if (ps.get_state().dims.cp == 1 and not CHUNK_PREFIX["active"] and OF.attention_packed_supported(qkv, d)
+                    and not (self.training and cfg.attention_dropout > 0)):
                 # tcgen05 attention reads q/k/v straight out of the packed GEMM output
                 o = OF.attention_packed(qkv, g, r, causal=cfg.causal, scale=self.scale, cu_seqlens=cu)
                 return self.linear_proj(o.view(T, g * r * d), residual)
@@ -248,7 +249,7 @@ class SelfAttention(nn.Module):
                 q = self._rope(q, rotary)
                 k = self._rope(k, rotary)
         o = core_attention(q, k, v, causal=cfg.causal, scale=self.scale, cu_seqlens=cu, cfg=cfg,
-                           row_length=packed.row_length if packed is not None else None)
+                           row_length=packed.row_length if packed is not None else None, training=self.training)
         return self.linear_proj(o.reshape(T, g * r * d), residual)
 
     def _rope_kw(self, rotary):
@@ -275,7 +276,7 @@ CHUNK_PREFIX = {"active": False, "past": None, "out": None}
 
 
 def core_attention(q, k, v, *, causal, scale, cu_seqlens, cfg: Optional[TransformerConfig] = None,
-                   row_length: Optional[int] = None):
+                   row_length: Optional[int] = None, training: bool = False):
     """Attention over packed tokens; context parallelism is applied here when enabled."""
     st = ps.get_state()
     if CHUNK_PREFIX["active"]:
@@ -285,10 +286,50 @@ def core_attention(q, k, v, *, causal, scale, cu_seqlens, cfg: Optional[Transfor
         kk, vv = (torch.cat([past[0], k]), torch.cat([past[1], v])) if past is not None else (k, v)
         # fewer queries than keys: the causal mask is aligned to the bottom right, i.e. the chunk follows its prefix
         return OF.attention(q, kk, vv, causal=causal, scale=scale)
+    p_drop = cfg.attention_dropout if (cfg is not None and training) else 0.0
+    if p_drop > 0:
+        return _attention_with_dropout(q, k, v, causal, scale, cu_seqlens, p_drop, st)
     if st.dims.cp > 1:
         from ..parallel import context_parallel as CP
         return CP.ring_attention(q, k, v, causal=causal, scale=scale, cu_seqlens=cu_seqlens, row_length=row_length)
     return OF.attention(q, k, v, causal=causal, scale=scale, cu_seqlens=cu_seqlens)
+
+
+def _attention_with_dropout(q, k, v, causal, scale, cu_seqlens, p_drop, st):
+    """Attention-probability dropout (``--attention-dropout`` > 0). The flash kernels carry no dropout, so this path
+    computes the probabilities in PyTorch; heads are sharded over the TP group, hence the masks come from the
+    tracker's model-parallel stream. Context parallelism and this path exclude each other."""
+    if st.dims.cp > 1:
+        raise ValueError("attention dropout is not available together with context parallelism")
+    from ..parallel import random as PR
+    import contextlib
+
+    Tq, Hq, _ = q.shape
+    Hkv = k.shape[1]
+    rep = Hq // Hkv
+    s = torch.einsum("qhd,khd->hqk", q.float(), k.float().repeat_interleave(rep, 1)) * scale
+    seg, pos, _ = OF._seq_ids(Tq, cu_seqlens, q.device)
+    mask = seg[:, None] == seg[None, :]
+    if causal:
+        mask &= pos[None, :] <= pos[:, None]
+    pr = torch.softmax(s.masked_fill(~mask, float("-inf")), dim=-1)
+    ctx = PR.get_rng_tracker().fork() if st.dims.tp > 1 else contextlib.nullcontext()
+    with ctx:
+        pr = torch.nn.functional.dropout(pr, p_drop, training=True)
+    return torch.einsum("hqk,khd->qhd", pr, v.float().repeat_interleave(rep, 1)).to(q.dtype)
+
+
+def hidden_dropout(t: torch.Tensor, p: float, cfg: TransformerConfig) -> torch.Tensor:
+    """Dropout on a sub-layer output. With sequence parallelism every tensor-parallel rank holds different tokens, so
+    the masks come from the tracker's model-parallel stream (different per TP rank); otherwise the activations are
+    replicated over the TP group and the default stream, seeded alike on its ranks, keeps the masks identical
+    (reference: loongforge/models/foundation/language_transformer_block.py:199-202, Megatron's bias-dropout-add)."""
+    from ..parallel import random as PR
+
+    if cfg.sequence_parallel and ps.get_state().dims.tp > 1:
+        with PR.get_rng_tracker().fork():
+            return torch.nn.functional.dropout(t, p, training=True)
+    return torch.nn.functional.dropout(t, p, training=True)
 
 
 class TransformerLayer(nn.Module):
@@ -357,9 +398,16 @@ class TransformerLayer(nn.Module):
     def forward(self, x, rotary=None, packed=None):
         if self.cfg.enable_hyper_connections:
             return self._forward_hyper(x, rotary, packed)
+        drop = self.cfg.hidden_dropout if self.training else 0.0
         h = self.input_layernorm(x) if self.input_layernorm is not None else x
-        x = self.self_attention(h, rotary, packed, residual=x)
+        if drop > 0:
+            # dropout sits between the sub-layer and the residual add, so the add leaves the GEMM epilogue
+            x = x + hidden_dropout(self.self_attention(h, rotary, packed, residual=None), drop, self.cfg)
+        else:
+            x = self.self_attention(h, rotary, packed, residual=x)
         h = self.pre_mlp_layernorm(x) if self.pre_mlp_layernorm is not None else x
+        if drop > 0:
+            return x + hidden_dropout(self.mlp(h), drop, self.cfg)
         if self.is_moe:
             return x + self.mlp(h)
         return self.mlp(h, residual=x)
@@ -413,7 +461,11 @@ class TransformerBlock(nn.Module):
         shared_idx = None
         for i, layer in enumerate(self.layers):
             do_rec = rec and ((method == "block" and i < rec_n) or method == "uniform")
-            if do_rec:
+            if do_rec and self.training and (cfg.hidden_dropout > 0 or cfg.attention_dropout > 0):
+                # dropout inside: the recomputation must replay the default AND the tracked random streams
+                from ..parallel import random as PR
+                x = PR.checkpoint(lambda t, _l=layer, _s=shared_idx: self._run(_l, t, rotary, packed, _s), x)
+            elif do_rec:
                 # the shared top-k indices are an explicit input, so a recomputed layer sees those of ITS forward
                 x = torch.utils.checkpoint.checkpoint(self._run, layer, x, rotary, packed, shared_idx, use_reentrant=False)
             else:

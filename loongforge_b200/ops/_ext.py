@@ -48,6 +48,8 @@ def _sources() -> tuple[list[str], list[str]]:
         defs.append("-DLF_HAVE_MOE_PEER")
     if os.path.exists(os.path.join(_CSRC, "grouped_gemm_sm100.cu")):
         defs.append("-DLF_HAVE_GROUPED")
+    if os.path.exists(os.path.join(_CSRC, "dsa_sm100.cu")):
+        defs.append("-DLF_HAVE_DSA")
     return srcs, defs
 
 

@@ -29,6 +29,9 @@
 #ifdef LF_HAVE_PEER_OPTIM
 #include "peer_optim.h"
 #endif
+#ifdef LF_HAVE_DSA
+#include "dsa_sm100.h"
+#endif
 
 namespace {
 
@@ -829,6 +832,41 @@ void peer_wait(std::vector<int64_t> flags, int64_t rank, int64_t epoch, const at
 }
 #endif  // LF_HAVE_PEER_OPTIM
 
+#ifdef LF_HAVE_DSA
+// ------------------------------------------------------------------ DeepSeek sparse attention
+// q [m, H, 576] bf16 (unit inner stride), kv [n, 576] bf16, idx [m, topk] int32 -> (o [m, H, 512] bf16, lse [m, H]).
+std::vector<at::Tensor> sparse_mla_fwd(const at::Tensor& q, const at::Tensor& kv, const at::Tensor& idx, double scale,
+                                       const at::Tensor& status) {
+  check_bf16_cuda(q, "q");
+  check_bf16_cuda(kv, "kv");
+  TORCH_CHECK(q.dim() == 3 && q.size(2) == 576 && q.stride(2) == 1 && q.size(1) >= 1 && q.size(1) <= 128,
+              "q must be [m, H <= 128, 576]");
+  TORCH_CHECK(kv.dim() == 2 && kv.size(1) == 576 && kv.stride(1) == 1, "kv must be [n, 576]");
+  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kInt && idx.dim() == 2 && idx.is_contiguous() &&
+                  idx.size(0) == q.size(0),
+              "idx must be int32 [m, topk]");
+  c10::cuda::CUDAGuard guard(q.device());
+  at::Tensor o = at::empty({q.size(0), q.size(1), 512}, q.options());
+  at::Tensor lse = at::empty({q.size(0), q.size(1)}, q.options().dtype(at::kFloat));
+  lf::SparseMlaArgs a;
+  a.q = q.data_ptr(); a.q_ts = q.stride(0); a.q_hs = q.stride(1);
+  a.kv = kv.data_ptr(); a.kv_ts = kv.stride(0);
+  a.idx = idx.data_ptr<int>();
+  a.topk = static_cast<int>(idx.size(1));
+  a.m = static_cast<int>(q.size(0));
+  a.H = static_cast<int>(q.size(1));
+  a.n_kv = static_cast<int>(kv.size(0));
+  a.scale = static_cast<float>(scale);
+  a.o = o.data_ptr(); a.o_ts = o.stride(0); a.o_hs = o.stride(1);
+  a.lse = lse.data_ptr<float>();
+  a.status = status.data_ptr<int>();
+  const int rc = lf::sparse_mla_fwd(a, cur_stream());
+  TORCH_CHECK(rc == 0, "lf::sparse_mla_fwd failed with code ", rc);
+  ++g_launches;
+  return {o, lse};
+}
+#endif  // LF_HAVE_DSA
+
 // Budget of the device-side waits on flags written by other GPUs, in milliseconds (see wait_budget.h).
 void set_peer_wait_budget_ms(double ms) { lf::set_peer_wait_budget_ms(ms); }
 double peer_wait_budget_ms() { return lf::peer_wait_budget_ms(); }
@@ -879,6 +917,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adam_push", &adam_push);
   m.def("peer_signal", &peer_signal);
   m.def("peer_wait", &peer_wait);
+#endif
+#ifdef LF_HAVE_DSA
+  m.def("sparse_mla_fwd", &sparse_mla_fwd);
 #endif
   m.def("router_fwd", &router_fwd);
   m.def("router_bwd", &router_bwd);

@@ -1,0 +1,339 @@
+// DeepSeek sparse attention (DSA) on the absorbed multi-latent form, forward, for sm_100a.
+//
+//   o[t, h, :512] = softmax_k( q[t, h, :576] . kv[idx[t, k], :576] * scale ) @ kv[idx[t, k], :512]
+//
+// q [m, H <= 128, 576] bf16 (latent 512 + rope 64), kv [n, 576] bf16 shared by all heads, idx [m, topk] int32 with -1
+// for empty slots. For one query token the H heads share the same gathered rows, so the heads are the M = 128 rows of
+// the tensor-core tile:
+//   S[128 heads x 32 keys]  = Q_t K_blk^T        (A = Q_t in shared memory, 36 k-steps over the 576 dims)
+//   O[128 heads x 256]     += P K_blk[:, half]   (A = P packed bf16 in TMEM over the columns of S, B = the gathered
+//                                                 block read MN-major)
+// The fp32 accumulator of all 512 value dims would fill the 512 TMEM columns by itself, so one CTA owns ONE HALF of the
+// value dims of one query token (grid = tokens x 2) and recomputes the scores. Rows are gathered by 128 producer
+// threads with 16-byte cp.async copies straight into the 128-byte-swizzled tile layout (two stages), the MMA thread
+// runs the scores one block ahead of the softmax warps, and the softmax uses the lazily rescaled running maximum of the
+// dense attention kernel. Every wait is bounded.
+//
+// Replaces the TileLang kernel of the reference (ops/tilelang_ops/sparse_mla_fwd.py:11-181; oracle :218-265).
+#include "sm100_ptx.cuh"
+#include "dsa_sm100.h"
+
+namespace lf {
+
+static constexpr int SM_DK = 576, SM_DV = 512, SM_NB = 32;        // key dims, value dims, gathered rows per block
+static constexpr int SM_QBOX = 128 * 64 * 2;                       // one [128 heads x 64 dims] box of Q: 16 KB
+static constexpr int SM_Q_BYTES = 9 * SM_QBOX;                     // 144 KB
+static constexpr int SM_KBOX = SM_NB * 64 * 2;                     // one [32 rows x 64 dims] box: 4 KB
+static constexpr int SM_KV_BYTES = 9 * SM_KBOX;                    // 36 KB per stage
+static constexpr int SM_STAGES = 2;
+static constexpr int SM_CTL = SM_Q_BYTES + SM_STAGES * SM_KV_BYTES;
+static constexpr int SM_SMEM = SM_CTL + 256 + 1024;
+static constexpr int SM_THREADS = 288;  // 4 gather warps, 1 MMA warp, 4 softmax warps
+static constexpr float SM_LOG2E = 1.4426950408889634f;
+
+struct SmlaParams {
+  const __nv_bfloat16* kv;
+  long long kv_ts;
+  const int* idx;
+  int topk, m, H, n_kv;
+  float scale_log2;
+  __nv_bfloat16* o;
+  long long o_ts, o_hs;
+  float* lse;  // [m, H]
+  int* status;
+};
+
+enum { S_Q = 0, S_KV_FULL = 1, S_KV_EMPTY = 3, S_S_FULL = 5, S_P_FULL = 7, S_O_DONE = 9 };
+
+struct SmlaCtl {
+  uint64_t bars[12];
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(SM_THREADS, 1)
+sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  SmlaCtl* ctl = reinterpret_cast<SmlaCtl*>(smem + SM_CTL);
+  uint64_t* bars = ctl->bars;
+  volatile int* abort_flag = &ctl->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tok = blockIdx.x >> 1, half = blockIdx.x & 1;
+  const int nb = (p.topk + SM_NB - 1) / SM_NB;
+  const int* my_idx = p.idx + static_cast<long long>(tok) * p.topk;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars[S_Q], 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars[S_KV_FULL + s], 128);
+      mbar_init(&bars[S_KV_EMPTY + s], 1);
+      mbar_init(&bars[S_S_FULL + s], 1);
+      mbar_init(&bars[S_P_FULL + s], 4);
+    }
+    mbar_init(&bars[S_O_DONE], 1);
+    ctl->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 4) tmem_alloc(&ctl->tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = ctl->tmem_slot;
+  const uint32_t t_o = tmem, t_s = tmem + 256;  // O: 256 columns, S[2]: 32 columns each
+
+  if (warp < 4) {
+    // ------------------------------------------------------------ gather producers
+    if (threadIdx.x == 0) {
+      mbar_arrive_expect_tx(&bars[S_Q], SM_Q_BYTES);
+      for (int b = 0; b < 9; ++b) tma_load_3d(smem + b * SM_QBOX, &tq, &bars[S_Q], b * 64, 0, tok);
+    }
+    const int t = threadIdx.x;  // 0..127
+    bool ok = true;
+    for (int j = 0; j < nb && ok; ++j) {
+      const int s = j & 1;
+      ok = mbar_wait(&bars[S_KV_EMPTY + s], ((j >> 1) & 1) ^ 1, abort_flag);
+      if (!ok) break;
+      uint8_t* stage = smem + SM_Q_BYTES + s * SM_KV_BYTES;
+      // 32 rows x 72 chunks of 16 bytes; chunk c -> (row, 16-byte column) -> swizzled place in its 64-dim box
+#pragma unroll 2
+      for (int c = t; c < SM_NB * 72; c += 128) {
+        const int row = c / 72, col16 = c - row * 72;
+        const int box = col16 >> 3, ch = col16 & 7;
+        const int slot = j * SM_NB + row;
+        const int id = slot < p.topk ? my_idx[slot] : -1;
+        uint8_t* dst = stage + box * SM_KBOX + (row >> 3) * 1024 + (row & 7) * 128 + ((ch ^ (row & 7)) << 4);
+        if (id >= 0 && id < p.n_kv) {
+          cp_async16(smem_u32(dst), p.kv + static_cast<long long>(id) * p.kv_ts + col16 * 8);
+        } else {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+          if (id >= p.n_kv) atomicCAS(p.status, 0, LF_ERR_BAD_INDEX);
+        }
+      }
+      cp_async_wait_all();
+      fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
+      mbar_arrive(&bars[S_KV_FULL + s]);
+    }
+    if (!ok && lane == 0) atomicCAS(p.status, 0, LF_ERR_WAIT_EMPTY);
+  } else if (warp == 4) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t sq = smem_u32(smem), skv = smem_u32(smem + SM_Q_BYTES);
+      constexpr uint32_t idesc_s = make_idesc(1, 1, false, false, 128, SM_NB);
+      constexpr uint32_t idesc_o = make_idesc(1, 1, false, true, 128, 256);
+      auto issue_s = [&](int j) {
+        const int s = j & 1;
+        const uint32_t kb = skv + s * SM_KV_BYTES;
+#pragma unroll 4
+        for (int kk = 0; kk < 36; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(sq + (kk >> 2) * SM_QBOX + (kk & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(kb + (kk >> 2) * SM_KBOX + (kk & 3) * 32, 16, 1024);
+          tc_mma_f16_ss(t_s + s * SM_NB, da, db, idesc_s, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(&bars[S_S_FULL + s]);
+      };
+      bool ok = mbar_wait(&bars[S_Q], 0, abort_flag);
+      if (ok) ok = mbar_wait(&bars[S_KV_FULL + 0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_s(0);
+      }
+      for (int j = 0; j < nb && ok; ++j) {
+        const int s = j & 1;
+        if (j + 1 < nb) {
+          ok = mbar_wait(&bars[S_KV_FULL + (s ^ 1)], ((j + 1) >> 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_s(j + 1);  // overwrites P[j-1], which O += P[j-1] V[j-1] (issued earlier) has read by then
+        }
+        ok = mbar_wait(&bars[S_P_FULL + s], (j >> 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        // O += P[j] V[j]: 32 gathered rows = 2 k-steps; B = this half's four 64-dim boxes read MN-major
+        const uint32_t vb = skv + s * SM_KV_BYTES + half * 4 * SM_KBOX;
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          const uint64_t db = make_smem_desc_sw128(vb + kk * 2048, SM_KBOX, 1024);
+          tc_mma_f16_ts(t_o, t_s + s * SM_NB + kk * 8, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(&bars[S_KV_EMPTY + s]);
+        tc_commit(&bars[S_O_DONE]);
+      }
+      if (!ok) atomicCAS(p.status, 0, LF_ERR_WAIT_FULL);
+    }
+  } else {
+    // ------------------------------------------------------------ softmax warps: one thread per head
+    const int quarter = warp & 3;
+    const int h = quarter * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nb && ok; ++j) {
+      const int s = j & 1;
+      ok = mbar_wait(&bars[S_S_FULL + s], (j >> 1) & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(t_s + s * SM_NB + lane_off, r);
+      tmem_ld_wait();
+      // empty slots (-1) are masked; the slot list is the same for every head: broadcast loads
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int slot = j * SM_NB + i;
+        const bool live = slot < p.topk && my_idx[slot] >= 0;
+        if (!live) r[i] = 0xff800000u;
+        mx = fmaxf(mx, __uint_as_float(r[i]));
+      }
+      mx *= p.scale_log2;
+      float m_new = m_ref;
+      if (mx > m_ref + 8.f || m_ref == -INFINITY) m_new = fmaxf(mx, m_ref);
+      const bool rescale = (m_new != m_ref) && (j > 0);
+      const unsigned any = __ballot_sync(0xffffffffu, rescale);
+      const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
+      if (any) {
+        ok = mbar_wait(&bars[S_O_DONE], (j - 1) & 1, abort_flag);  // O += P[j-1] V[j-1] retired
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll 1
+        for (int c0 = 0; c0 < 256; c0 += 16) {
+          uint32_t q[16];
+          tmem_ld_32x32b_x16(t_o + lane_off + c0, q);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) q[i] = __float_as_uint(__uint_as_float(q[i]) * alpha);
+          tmem_st_32x32b_x16(t_o + lane_off + c0, q);
+        }
+      }
+      l_sum *= alpha;
+      m_ref = m_new;
+      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float a = exp2f(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, neg_m));
+        const float b = exp2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, neg_m));
+        l_sum += a + b;
+        pk[i] = pack_bf16x2(a, b);
+      }
+      tmem_st_32x32b_x16(t_s + s * SM_NB + lane_off, pk);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[S_P_FULL + s]);
+    }
+    if (ok && nb > 0) ok = mbar_wait(&bars[S_O_DONE], (nb - 1) & 1, abort_flag);
+    if (!ok) {
+      if (lane == 0) atomicCAS(p.status, 0, LF_ERR_WAIT_TMEM_FULL);
+    } else {
+      tc_fence_after_sync();
+      const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      // every lane takes part in the warp-collective TMEM loads; only lanes that map to a head store
+      const bool live = h < p.H;
+      __nv_bfloat16* orow = p.o + static_cast<long long>(tok) * p.o_ts + static_cast<long long>(live ? h : 0) * p.o_hs +
+                            half * 256;
+#pragma unroll 1
+      for (int c0 = 0; c0 < 256; c0 += 32) {
+        uint32_t q[32];
+        if (nb > 0) {
+          tmem_ld_32x32b_x32(t_o + lane_off + c0, q);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) q[i] = 0u;
+        }
+        if (live) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(q[i]) * inv, __uint_as_float(q[i + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(q[i + 2]) * inv, __uint_as_float(q[i + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(q[i + 4]) * inv, __uint_as_float(q[i + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(q[i + 6]) * inv, __uint_as_float(q[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c0 + i) = w;
+          }
+        }
+      }
+      if (live && half == 0)
+        p.lse[static_cast<long long>(tok) * p.H + h] = l_sum > 0.f ? (m_ref + log2f(l_sum)) * (1.f / SM_LOG2E) : -INFINITY;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ---------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn dsa_encode_fn() {
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+int sparse_mla_fwd(const SparseMlaArgs& a, cudaStream_t stream) {
+  if (a.m <= 0) return 0;
+  if (a.H < 1 || a.H > 128 || a.topk < 1) return -2;
+  if ((a.q_ts % 8) || (a.q_hs % 8) || (a.kv_ts % 8) || (a.o_ts % 8) || (a.o_hs % 8)) return -2;
+  if ((reinterpret_cast<uintptr_t>(a.q) & 15) || (reinterpret_cast<uintptr_t>(a.kv) & 15) ||
+      (reinterpret_cast<uintptr_t>(a.o) & 15))
+    return -2;
+  EncodeTiledFn fn = dsa_encode_fn();
+  if (!fn) return -1;
+  // (dim, head, token) map of q with box (64, 128, 1); heads past H are zero-filled
+  CUtensorMap tq;
+  cuuint64_t dims[3] = {SM_DK, static_cast<cuuint64_t>(a.H), static_cast<cuuint64_t>(a.m)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(a.q_hs) * 2, static_cast<cuuint64_t>(a.q_ts) * 2};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  if (fn(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(a.q), dims, strides, box, es,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return -3;
+  constexpr int kMaxDev = 64;
+  static bool attr[kMaxDev] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return -4;
+  if (!attr[dev]) {
+    if (cudaFuncSetAttribute(sparse_mla_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_SMEM) != cudaSuccess)
+      return -4;
+    attr[dev] = true;
+  }
+  SmlaParams p;
+  p.kv = static_cast<const __nv_bfloat16*>(a.kv);
+  p.kv_ts = a.kv_ts;
+  p.idx = a.idx;
+  p.topk = a.topk; p.m = a.m; p.H = a.H; p.n_kv = a.n_kv;
+  p.scale_log2 = a.scale * SM_LOG2E;
+  p.o = static_cast<__nv_bfloat16*>(a.o);
+  p.o_ts = a.o_ts; p.o_hs = a.o_hs;
+  p.lse = a.lse;
+  p.status = a.status;
+  sparse_mla_fwd_kernel<<<2 * a.m, SM_THREADS, SM_SMEM, stream>>>(tq, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+}  // namespace lf

@@ -1,0 +1,28 @@
+// Host interface of the DeepSeek sparse attention kernels (dsa_sm100.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace lf {
+
+// Top-k sparse attention on the absorbed multi-latent form (key dims 576 = 512 latent + 64 rope, value = the first
+// 512 key dims). q [m, H <= 128, 576] bf16 with element strides (q_ts, q_hs); kv [n_kv, 576] bf16 with row stride
+// kv_ts; idx [m, topk] int32, -1 = empty slot; o [m, H, 512] bf16 with strides (o_ts, o_hs); lse [m, H] fp32 (natural
+// log-sum-exp of the scaled scores over the selected keys, -inf when a token selected nothing).
+struct SparseMlaArgs {
+  const void* q = nullptr;
+  long long q_ts = 0, q_hs = 0;
+  const void* kv = nullptr;
+  long long kv_ts = 0;
+  const int* idx = nullptr;
+  int topk = 0, m = 0, H = 0, n_kv = 0;
+  float scale = 1.f;
+  void* o = nullptr;
+  long long o_ts = 0, o_hs = 0;
+  float* lse = nullptr;
+  int* status = nullptr;
+};
+
+// 0 on success, negative on invalid arguments (alignment: strides multiples of 8 elements, bases 16-byte aligned).
+int sparse_mla_fwd(const SparseMlaArgs& a, cudaStream_t stream);
+
+}  // namespace lf

@@ -83,13 +83,54 @@ def _sparse_mla_block(q, idx, kv, scale: float, d_v: int, with_probs: bool):
     return torch.cat([o, p.mean(1).to(o.dtype)], dim=-1) if with_probs else o
 
 
+def _native_sparse_mla(q, kv, d_v) -> bool:
+    from . import _ext
+    mod = _ext.get()
+    return (mod is not None and hasattr(mod, "sparse_mla_fwd") and q.is_cuda and q.dtype == torch.bfloat16
+            and kv.dtype == torch.bfloat16 and q.shape[-1] == 576 and d_v == 512 and q.shape[1] <= 128)
+
+
+class _SparseMlaFn(torch.autograd.Function):
+    """Forward on the tcgen05 kernel (csrc/dsa_sm100.cu): no gathered [rows, K, 576] tensor ever exists. Backward
+    recomputes one query block at a time with the PyTorch formulation below and back-propagates through it."""
+
+    @staticmethod
+    def forward(ctx, q, kv, indices, scale, block):
+        from . import _ext
+        qc = q if (q.stride(2) == 1 and q.stride(1) % 8 == 0 and q.stride(0) % 8 == 0) else q.contiguous()
+        kc = kv if (kv.stride(1) == 1 and kv.stride(0) % 8 == 0) else kv.contiguous()
+        o, lse = _ext.require().sparse_mla_fwd(qc, kc, indices.to(torch.int32).contiguous(), float(scale),
+                                               _ext.status_tensor(q.device))
+        ctx.save_for_backward(q, kv, indices)
+        ctx.cfg = (scale, block)
+        ctx.mark_non_differentiable(lse)
+        return o, lse
+
+    @staticmethod
+    def backward(ctx, do, _dlse):
+        q, kv, indices = ctx.saved_tensors
+        scale, block = ctx.cfg
+        dq = torch.zeros_like(q)
+        kvl = kv.detach().requires_grad_(True)
+        for s in range(0, q.shape[0], block):
+            qb = q[s:s + block].detach().requires_grad_(True)
+            with torch.enable_grad():
+                ob = _sparse_mla_block(qb, indices[s:s + block].long(), kvl, scale, 512, False)
+            torch.autograd.backward(ob, do[s:s + block].flatten(1))
+            dq[s:s + block] = qb.grad
+        return dq, kvl.grad, None, None, None
+
+
 def sparse_mla_attention(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, scale: float, d_v: int = 512,
                          block: int = 256, return_head_mean_probs: bool = False):
     """q [m, H, Dk], kv [n, Dk] (shared by all heads), indices [m, K] (-1 = empty).
     Returns o [m, H, d_v] (and the head-averaged attention distribution over the K slots, a constant target).
-    Query blocks are recomputed in backward (``ops/blockwise.py``), so the gathered keys of only one block are alive."""
+    On a GPU the forward runs on the tcgen05 kernel when only the output is wanted; query blocks are recomputed in
+    backward (``ops/blockwise.py``), so the gathered keys of only one block are alive."""
     from .blockwise import blockwise_apply
 
+    if not return_head_mean_probs and _native_sparse_mla(q, kv, d_v):
+        return _SparseMlaFn.apply(q, kv, indices, scale, block)[0]
     m, H, _ = q.shape
     K = indices.shape[1]
     fn = lambda qb, ib, kvv: _sparse_mla_block(qb, ib, kvv, scale, d_v, return_head_mean_probs)  # noqa: E731

@@ -159,8 +159,9 @@ def build_hooks(args, trainer) -> List[TrainHook]:
     world = dist.get_world_size() if dist.is_initialized() else 1
     out = getattr(args, "tensorboard_dir", None) or (trainer.tcfg.save or ".")
     hooks: List[TrainHook] = []
-    if getattr(args, "ema_decay", None):
-        hooks.append(EMAHook(trainer, args.ema_decay))
+    if getattr(args, "ema_decay", None) or getattr(args, "enable_ema", False):
+        # --enable-ema without a decay uses the reference's default of 0.9999
+        hooks.append(EMAHook(trainer, getattr(args, "ema_decay", None) or 0.9999))
     if getattr(args, "profile", False) or getattr(args, "use_pytorch_profiler", False):
         hooks.append(ProfilerHook(out, args.profile_step_start, args.profile_step_end, args.profile_ranks, rank))
     if getattr(args, "record_memory_history", False):

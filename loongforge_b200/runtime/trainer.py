@@ -91,6 +91,9 @@ class TrainConfig:
     exit_on_nan: bool = False
     async_save: bool = False
     peer_optimizer: bool = False  # grad reduce-scatter / param all-gather inside the optimizer kernels (peer memory)
+    freeze_parameters: Optional[List[str]] = None  # parameter-name prefixes that do not train (--freeze-parameters)
+    freeze_parameters_regex: Optional[str] = None  # ... or a regular expression over the full parameter name
+    trainable_modules: Optional[List[str]] = None  # if given (and not ["all"]): only names containing one of these train
 
 
 def _device_for_rank() -> torch.device:
@@ -143,7 +146,10 @@ class Trainer:
         self.timers = Timers(log_level=train_cfg.timing_log_level, device_sync=True)
         if train_cfg.bf16:
             model_cfg.params_dtype = torch.bfloat16
-        torch.manual_seed(train_cfg.seed + 100 * self.st.pp_rank + 2718 * self.st.tp_rank)
+        # default stream alike on the TP ranks of a stage (dropout on replicated activations), tracked streams that
+        # differ per TP / expert rank (dropout on sharded activations)
+        from ..parallel.random import model_parallel_manual_seed
+        model_parallel_manual_seed(train_cfg.seed, self.st.tp_rank, self.st.pp_rank, self.st.ep_rank)
         from ..parallel.layers import set_init_seed
         set_init_seed(train_cfg.seed)
         self.mb_calc = MicrobatchCalculator(train_cfg.global_batch_size, train_cfg.micro_batch_size, self.dp,
@@ -211,6 +217,7 @@ class Trainer:
         for v in range(vpp):
             virt = v * pp + st.pp_rank
             module = self.model_provider(virt == 0, virt == pp * vpp - 1, splits[virt])
+            self._apply_freezing(module)
             ddp_cfg = DDPConfig(grad_reduce_in_fp32=self.tcfg.grad_reduce_in_fp32,
                                 overlap_grad_reduce=self.tcfg.overlap_grad_reduce,
                                 use_distributed_optimizer=self.tcfg.use_distributed_optimizer,
@@ -221,6 +228,26 @@ class Trainer:
         for c in chunks:
             c.broadcast_params()
         return chunks
+
+    def _apply_freezing(self, module) -> int:
+        """``--freeze-parameters`` (name prefixes), ``--freeze-parameters-regex`` and ``--trainable-modules``: the
+        selected parameters get ``requires_grad = False`` before gradient buffers and optimizer shards are laid out, so
+        they cost neither gradient memory nor optimizer state (reference: loongforge/train/arguments.py:309-330)."""
+        import re
+
+        t = self.tcfg
+        prefixes = [p for p in (t.freeze_parameters or []) if p]
+        rx = re.compile(t.freeze_parameters_regex) if t.freeze_parameters_regex else None
+        only = [m for m in (t.trainable_modules or []) if m and m != "all"]
+        n = 0
+        for name, p in module.named_parameters():
+            frozen = any(name.startswith(pre) for pre in prefixes) or bool(rx and rx.search(name))
+            if only and not any(m in name for m in only):
+                frozen = True
+            if frozen and p.requires_grad:
+                p.requires_grad_(False)
+                n += 1
+        return n
 
     def _build_optimizer(self) -> DistributedOptimizer:
         t = self.tcfg
@@ -606,7 +633,7 @@ class Trainer:
         s += " loss scale: %.1f |" % 1.0
         s += " grad norm: %.6f |" % metrics.get("grad_norm", float("nan"))
         s += " number of skipped iterations: %3d |" % metrics.get("skipped", 0)
-        s += " number of nan iterations: %3d |" % 0
+        s += " number of nan iterations: %3d |" % self._nan
         if self.device.type == "cuda":
             s += " mem-allocated-bytes-avg(MB): %.1f |" % (torch.cuda.memory_allocated() / 2 ** 20)
             s += " mem-max-allocated-bytes-avg(MB): %.1f |" % (torch.cuda.max_memory_allocated() / 2 ** 20)

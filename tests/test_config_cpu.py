@@ -83,3 +83,46 @@ def test_every_model_yaml_builds_the_registered_preset():
         checked += 1
     assert checked >= 20
 
+
+
+def test_reference_flags_and_entry_point_are_accepted():
+    """Every flag the reference defines itself (147) parses, the `loongforge.train` entry objects exist, and the
+    freezing flags reach the trainer."""
+    import re
+
+    from loongforge_b200.config.arguments import build_parser, parse_args
+
+    known = {o for a in build_parser()._actions for o in a.option_strings}
+    for f in ("--loss-reduction", "--freeze-parameters-regex", "--log-tensor-stage", "--dp-balance-verbose",
+              "--hf-dequantize-int4", "--max-latent-height", "--energon-pack-algo", "--initial-loss-scale"):
+        assert f in known, f
+    args, _ = parse_args(["--model-name", "tiny-llama", "--freeze-parameters", "embedding", "output_layer",
+                          "--freeze-parameters-regex", r"layers\\.0\\.", "--force_pow_2_scales", "--enable-ema"])
+    assert args.freeze_parameters == ["embedding", "output_layer"] and args.force_pow_2_scales and args.enable_ema
+    assert re.compile(args.freeze_parameters_regex)
+    import loongforge.train as entry
+
+    assert callable(entry.main) and callable(entry.parse_train_args) and callable(entry.build_model_trainer)
+
+
+def test_freeze_parameters_flags_freeze_before_the_optimizer_is_built():
+    import torch
+
+    from loongforge_b200.models.config import TransformerConfig
+    from loongforge_b200.runtime.trainer import TrainConfig, Trainer
+
+    cfg = TransformerConfig(num_layers=2, hidden_size=64, num_attention_heads=2, ffn_hidden_size=128, vocab_size=128)
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=1, seq_length=16, train_iters=1,
+                     freeze_parameters=["embedding"], freeze_parameters_regex=r"layers\.0\.")
+    tr = Trainer(cfg, tc, device=torch.device("cpu"))
+    named = dict(tr.models[0].module.named_parameters())
+    frozen = [n for n, p in named.items() if not p.requires_grad]
+    assert frozen and all(n.startswith("embedding") or "layers.0." in n for n in frozen)
+    assert any("layers.1." in n and p.requires_grad for n, p in named.items())
+    from loongforge_b200.data.synthetic import synthetic_batch_iterator
+
+    before = {n: p.detach().clone() for n, p in named.items()}
+    tr.train_step(synthetic_batch_iterator(128, 16, 1))
+    for n, p in named.items():
+        changed = not torch.equal(before[n], p.detach())
+        assert changed == p.requires_grad or not p.requires_grad and not changed, n
