@@ -205,7 +205,20 @@ class MLASelfAttention(nn.Module):
             with torch.no_grad():
                 qq, _ = dsa_ops.quant_fp8_rowwise_pow2(qi) if cfg.fp8 else (qi, None)
                 kq, _ = dsa_ops.quant_fp8_rowwise_pow2(ki_all) if cfg.fp8 else (ki_all, None)
-                indices, _ = dsa_ops.indexer_topk(qq, kq, wi, cfg.dsa_indexer_topk, pos, pos_k, seg, seg_k)
+                if st.dims.cp > 1:
+                    # gathered keys arrive rank-major: put them into row order so that every query's candidates are
+                    # one contiguous index range (what the native kernels want), and map the selection back
+                    order = torch.argsort(pos_k)
+                    sel, _ = dsa_ops.indexer_topk(qq, kq.index_select(0, order), wi, cfg.dsa_indexer_topk, pos,
+                                                  pos_k.index_select(0, order), seg,
+                                                  seg_k.index_select(0, order) if seg_k is not None else None,
+                                                  keys_in_order=True)
+                    indices = torch.where(sel >= 0, order[sel.clamp_min(0)], sel)
+                else:
+                    # one rank holds the row(s) in order: causal order is index order inside every sequence
+                    ar = torch.arange(T, device=x.device)
+                    indices, _ = dsa_ops.indexer_topk(qq, kq, wi, cfg.dsa_indexer_topk, ar, ar, seg, seg_k,
+                                                      keys_in_order=True)
         else:
             indices = self.shared_topk_indices
             if indices is None:

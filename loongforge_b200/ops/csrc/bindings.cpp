@@ -865,6 +865,37 @@ std::vector<at::Tensor> sparse_mla_fwd(const at::Tensor& q, const at::Tensor& kv
   ++g_launches;
   return {o, lse};
 }
+
+// Lightning-indexer logits for query rows [q0, q0 + rows) into `logits` [rows, ld] fp32 (entries outside each row's
+// key range stay unwritten), then the top-k selection over those ranges into `out` [rows, topk] int32.
+void indexer_topk(const at::Tensor& q, const at::Tensor& k, const at::Tensor& w, const at::Tensor& k_start,
+                  const at::Tensor& k_end, at::Tensor logits, at::Tensor out, int64_t max_len, const at::Tensor& status) {
+  check_bf16_cuda(q, "q");
+  check_bf16_cuda(k, "k");
+  TORCH_CHECK(q.dim() == 3 && q.size(2) == 128 && q.is_contiguous(), "q must be contiguous [m, Hi, 128]");
+  TORCH_CHECK(k.dim() == 2 && k.size(1) == 128 && k.stride(1) == 1, "k must be [n, 128]");
+  const int64_t m = q.size(0), Hi = q.size(1), n = k.size(0);
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kFloat && w.is_contiguous() && w.numel() == m * Hi);
+  TORCH_CHECK(k_start.scalar_type() == at::kInt && k_end.scalar_type() == at::kInt && k_start.numel() == m &&
+              k_end.numel() == m && k_start.is_contiguous() && k_end.is_contiguous());
+  TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.size(0) >= m && logits.size(1) >= n &&
+              logits.stride(1) == 1);
+  TORCH_CHECK(out.scalar_type() == at::kInt && out.dim() == 2 && out.size(0) == m && out.is_contiguous());
+  c10::cuda::CUDAGuard guard(q.device());
+  lf::IndexerArgs a;
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.k_ld = k.stride(0);
+  a.w = w.data_ptr<float>();
+  a.k_start = k_start.data_ptr<int>(); a.k_end = k_end.data_ptr<int>();
+  a.logits = logits.data_ptr<float>(); a.ld = logits.stride(0);
+  a.m = static_cast<int>(m); a.n = static_cast<int>(n); a.Hi = static_cast<int>(Hi);
+  a.status = status.data_ptr<int>();
+  int rc = lf::indexer_logits(a, cur_stream());
+  TORCH_CHECK(rc == 0, "lf::indexer_logits failed with code ", rc);
+  rc = lf::topk_range(a.logits, a.ld, a.k_start, a.k_end, out.data_ptr<int>(), a.m, static_cast<int>(out.size(1)),
+                      static_cast<int>(max_len), cur_stream());
+  TORCH_CHECK(rc == 0, "lf::topk_range failed with code ", rc);
+  g_launches += 2;
+}
 #endif  // LF_HAVE_DSA
 
 // Budget of the device-side waits on flags written by other GPUs, in milliseconds (see wait_budget.h).
@@ -920,6 +951,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 #endif
 #ifdef LF_HAVE_DSA
   m.def("sparse_mla_fwd", &sparse_mla_fwd);
+  m.def("indexer_topk", &indexer_topk);
 #endif
   m.def("router_fwd", &router_fwd);
   m.def("router_bwd", &router_bwd);

@@ -30,6 +30,7 @@ static constexpr int SM_CTL = SM_Q_BYTES + SM_STAGES * SM_KV_BYTES;
 static constexpr int SM_SMEM = SM_CTL + 256 + 1024;
 static constexpr int SM_THREADS = 288;  // 4 gather warps, 1 MMA warp, 4 softmax warps
 static constexpr float SM_LOG2E = 1.4426950408889634f;
+static constexpr int BOXK = 128 * 64 * 2;  // one [128 rows x 64 dims] box of the indexer's key tile
 
 struct SmlaParams {
   const __nv_bfloat16* kv;
@@ -333,6 +334,315 @@ int sparse_mla_fwd(const SparseMlaArgs& a, cudaStream_t stream) {
   p.lse = a.lse;
   p.status = a.status;
   sparse_mla_fwd_kernel<<<2 * a.m, SM_THREADS, SM_SMEM, stream>>>(tq, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+
+// =========================================================================== lightning indexer: logits
+//   logits[m, n] = sum_h w[m, h] * relu(q[m, h, :] . k[n, :])        (Hi index heads of 128 dims, k shared by the heads)
+// computed TRANSPOSED so that the key row is the TMEM lane and the head sum stays inside one thread:
+//   S^T[128 keys x 256] = K_blk (A, shared memory) x Q_grp^T (B: the 256 / Hi query tokens of this CTA, all heads)
+// One CTA owns a group of 256 / Hi consecutive query tokens, keeps their Q tile resident and streams the key blocks
+// its tokens may see (a contiguous range per token, [k_start, k_end)); the epilogue warps apply relu and the per-head
+// weights from shared memory and write one fp32 logit per (token, key). Entries outside a token's range are left
+// unwritten: the selection kernel below reads ranges only. Two S^T accumulators (2 x 256 TMEM columns) let the
+// tensor core run one key block ahead of the epilogue.
+// Replaces the TileLang indexer kernel of the reference (ops/tilelang_ops/lightning_indexer.py:82-139; oracle :12-32).
+static constexpr int IX_KSTAGES = 4;
+static constexpr int IX_Q_BYTES = 256 * 128 * 2;  // 64 KB: two [256 x 64] boxes
+static constexpr int IX_K_BYTES = 128 * 128 * 2;  // 32 KB: two [128 x 64] boxes
+static constexpr int IX_W = IX_Q_BYTES + IX_KSTAGES * IX_K_BYTES;  // 256 fp32 head weights
+static constexpr int IX_CTL = IX_W + 1024;
+static constexpr int IX_SMEM = IX_CTL + 256 + 1024;
+static constexpr int IX_THREADS = 192;
+enum { I_Q = 0, I_K_FULL = 1, I_K_EMPTY = 5, I_S_FULL = 9, I_S_EMPTY = 11 };
+
+struct IndexerParams {
+  const float* w;       // [m, Hi]
+  const int* k_start;   // [m]
+  const int* k_end;     // [m] exclusive
+  float* logits;        // [m, ld]
+  long long ld;
+  int m, n, Hi;
+  int* status;
+};
+
+struct IxCtl {
+  uint64_t bars[16];
+  uint32_t tmem_slot;
+  int abort_flag;
+  int blk_lo, blk_hi;
+};
+
+__global__ void __launch_bounds__(IX_THREADS, 1)
+indexer_logits_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                      const IndexerParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  IxCtl* ctl = reinterpret_cast<IxCtl*>(smem + IX_CTL);
+  uint64_t* bars = ctl->bars;
+  volatile int* abort_flag = &ctl->abort_flag;
+  float* ws = reinterpret_cast<float*>(smem + IX_W);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tpc = 256 / p.Hi;               // query tokens per CTA
+  const int t0 = blockIdx.x * tpc;          // first token of the group
+  // head weights of the group (zero for tokens past the end) and the union of the tokens' key ranges
+  for (int i = threadIdx.x; i < 256; i += IX_THREADS) {
+    const int t = t0 + i / p.Hi;
+    ws[i] = t < p.m ? p.w[static_cast<long long>(t) * p.Hi + (i % p.Hi)] : 0.f;
+  }
+  if (threadIdx.x == 0) {
+    int lo = 0x7fffffff, hi = 0;
+    for (int t = t0; t < min(t0 + tpc, p.m); ++t) {
+      if (p.k_end[t] > p.k_start[t]) {
+        lo = min(lo, p.k_start[t]);
+        hi = max(hi, p.k_end[t]);
+      }
+    }
+    ctl->blk_lo = hi > 0 ? lo / 128 : 0;
+    ctl->blk_hi = hi > 0 ? (min(hi, p.n) + 127) / 128 : 0;
+    mbar_init(&bars[I_Q], 1);
+    for (int s = 0; s < IX_KSTAGES; ++s) {
+      mbar_init(&bars[I_K_FULL + s], 1);
+      mbar_init(&bars[I_K_EMPTY + s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars[I_S_FULL + b], 1);
+      mbar_init(&bars[I_S_EMPTY + b], 4);
+    }
+    ctl->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) tmem_alloc(&ctl->tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = ctl->tmem_slot;
+  const int blk_lo = ctl->blk_lo, nblk = ctl->blk_hi - ctl->blk_lo;
+
+  if (warp == 0) {
+    if (lane == 0 && nblk > 0) {
+      mbar_arrive_expect_tx(&bars[I_Q], IX_Q_BYTES);
+      for (int b = 0; b < 2; ++b) tma_load_2d(smem + b * (256 * 128), &tq, &bars[I_Q], b * 64, t0 * p.Hi);
+      for (int j = 0; j < nblk; ++j) {
+        const int s = j % IX_KSTAGES;
+        if (!mbar_wait(&bars[I_K_EMPTY + s], ((j / IX_KSTAGES) & 1) ^ 1, abort_flag)) {
+          atomicCAS(p.status, 0, LF_ERR_WAIT_EMPTY);
+          break;
+        }
+        uint8_t* dst = smem + IX_Q_BYTES + s * IX_K_BYTES;
+        mbar_arrive_expect_tx(&bars[I_K_FULL + s], IX_K_BYTES);
+        for (int b = 0; b < 2; ++b) tma_load_2d(dst + b * BOXK, &tk, &bars[I_K_FULL + s], b * 64, (blk_lo + j) * 128);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && nblk > 0) {
+      constexpr uint32_t idesc = make_idesc(1, 1, false, false, 128, 256);
+      const uint32_t sq = smem_u32(smem), sk = smem_u32(smem + IX_Q_BYTES);
+      bool ok = mbar_wait(&bars[I_Q], 0, abort_flag);
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int s = j % IX_KSTAGES, b = j & 1;
+        ok = mbar_wait(&bars[I_K_FULL + s], (j / IX_KSTAGES) & 1, abort_flag);
+        if (ok) ok = mbar_wait(&bars[I_S_EMPTY + b], ((j >> 1) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t ka = sk + s * IX_K_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(ka + (kk >> 2) * BOXK + (kk & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(sq + (kk >> 2) * (256 * 128) + (kk & 3) * 32, 16, 1024);
+          tc_mma_f16_ss(tmem + b * 256, da, db, idesc, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(&bars[I_K_EMPTY + s]);
+        tc_commit(&bars[I_S_FULL + b]);
+      }
+      if (!ok) atomicCAS(p.status, 0, LF_ERR_WAIT_FULL);
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // key row inside the block
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const float4* w4 = reinterpret_cast<const float4*>(ws);
+    bool ok = true;
+    for (int j = 0; j < nblk && ok; ++j) {
+      const int b = j & 1;
+      ok = mbar_wait(&bars[I_S_FULL + b], (j >> 1) & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int key = (blk_lo + j) * 128 + row;
+      float acc = 0.f;
+      int col = 0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < 256; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem + b * 256 + lane_off + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float4 w = w4[(c0 + i) >> 2];
+          acc = fmaf(fmaxf(__uint_as_float(r[i]), 0.f), w.x, acc);
+          acc = fmaf(fmaxf(__uint_as_float(r[i + 1]), 0.f), w.y, acc);
+          acc = fmaf(fmaxf(__uint_as_float(r[i + 2]), 0.f), w.z, acc);
+          acc = fmaf(fmaxf(__uint_as_float(r[i + 3]), 0.f), w.w, acc);
+        }
+        col += 32;
+        if (col % p.Hi == 0) {  // a token's heads are complete (Hi is 32, 64, 128 or 256)
+          const int t = t0 + (c0 + 32) / p.Hi - 1;
+          if (t < p.m && key < p.n) p.logits[static_cast<long long>(t) * p.ld + key] = acc;
+          acc = 0.f;
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[I_S_EMPTY + b]);
+    }
+    if (!ok && lane == 0) atomicCAS(p.status, 0, LF_ERR_WAIT_TMEM_FULL);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// =========================================================================== top-k selection over a range of a row
+// One CTA per query row: the fp32 logits of the row's key range are loaded into shared memory once as order-preserving
+// unsigned keys, an MSB-first radix select (four 8-bit passes over shared memory) finds the k-th largest key exactly,
+// and a last pass writes the indices above it plus as many ties as are needed. The output order is unspecified
+// (a set), -1 pads rows with fewer than k candidates. Rows longer than TK_MAX_ROW are refused on the host.
+static constexpr int TK_THREADS = 512;
+static constexpr int TK_MAX_ROW = 49152;  // 192 KB of keys
+
+__device__ __forceinline__ uint32_t order_key(float x) {
+  const uint32_t b = __float_as_uint(x);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(TK_THREADS) topk_range_kernel(const float* __restrict__ logits, long long ld,
+                                                                const int* __restrict__ k_start,
+                                                                const int* __restrict__ k_end, int* __restrict__ out,
+                                                                int topk) {
+  extern __shared__ uint32_t keys[];
+  __shared__ int hist[256];
+  __shared__ uint32_t s_prefix, s_mask;
+  __shared__ int s_need, s_above, s_ties;
+  const int rowi = blockIdx.x;
+  const int ks = k_start[rowi];
+  const int len = max(k_end[rowi] - ks, 0);
+  int* o = out + static_cast<long long>(rowi) * topk;
+  if (len <= topk) {  // everything is selected
+    for (int i = threadIdx.x; i < topk; i += TK_THREADS) o[i] = i < len ? ks + i : -1;
+    return;
+  }
+  const float* src = logits + static_cast<long long>(rowi) * ld + ks;
+  for (int i = threadIdx.x; i < len; i += TK_THREADS) keys[i] = order_key(src[i]);
+  if (threadIdx.x == 0) {
+    s_prefix = 0u;
+    s_mask = 0u;
+    s_need = topk;
+  }
+  __syncthreads();
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += TK_THREADS) hist[i] = 0;
+    __syncthreads();
+    const uint32_t prefix = s_prefix, mask = s_mask;
+    for (int i = threadIdx.x; i < len; i += TK_THREADS) {
+      const uint32_t kx = keys[i];
+      if ((kx & mask) == prefix) atomicAdd(&hist[(kx >> shift) & 255], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int need = s_need, b = 255;
+      for (; b > 0; --b) {  // walk down from the largest digit
+        if (hist[b] >= need) break;
+        need -= hist[b];
+      }
+      s_need = need;  // how many of the chosen digit's keys are still wanted
+      s_prefix = prefix | (static_cast<uint32_t>(b) << shift);
+      s_mask = mask | (255u << shift);
+    }
+    __syncthreads();
+  }
+  // s_prefix is now the exact k-th largest key; s_need of the keys equal to it are taken
+  if (threadIdx.x == 0) {
+    s_above = 0;
+    s_ties = 0;
+  }
+  __syncthreads();
+  const uint32_t thr = s_prefix;
+  const int need = s_need, n_above = topk - need;
+  for (int i = threadIdx.x; i < len; i += TK_THREADS) {
+    const uint32_t kx = keys[i];
+    if (kx > thr) {
+      const int pos = atomicAdd(&s_above, 1);
+      if (pos < n_above) o[pos] = ks + i;
+    } else if (kx == thr) {
+      const int pos = atomicAdd(&s_ties, 1);
+      if (pos < need) o[n_above + pos] = ks + i;
+    }
+  }
+}
+
+static int make_map_2d(CUtensorMap* m, const void* ptr, long long rows, long long ld, int box_rows) {
+  EncodeTiledFn fn = dsa_encode_fn();
+  if (!fn) return -1;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (ld % 8)) return -2;
+  cuuint64_t dims[2] = {128, static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t es[2] = {1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -3;
+}
+
+int indexer_logits(const IndexerArgs& a, cudaStream_t stream) {
+  if (a.m <= 0 || a.n <= 0) return 0;
+  if (!(a.Hi == 32 || a.Hi == 64 || a.Hi == 128 || a.Hi == 256) || (a.ld % 4)) return -2;
+  CUtensorMap tq, tk;
+  int rc;
+  // q viewed as [m * Hi, 128] rows; rows past the end are zero-filled by TMA
+  if ((rc = make_map_2d(&tq, a.q, static_cast<long long>(a.m) * a.Hi, 128, 256))) return rc;
+  if ((rc = make_map_2d(&tk, a.k, a.n, a.k_ld, 128))) return rc;
+  constexpr int kMaxDev = 64;
+  static bool attr[kMaxDev] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return -4;
+  if (!attr[dev]) {
+    if (cudaFuncSetAttribute(indexer_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, IX_SMEM) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(topk_range_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_MAX_ROW * 4) !=
+            cudaSuccess)
+      return -4;
+    attr[dev] = true;
+  }
+  IndexerParams p;
+  p.w = a.w; p.k_start = a.k_start; p.k_end = a.k_end;
+  p.logits = a.logits; p.ld = a.ld;
+  p.m = a.m; p.n = a.n; p.Hi = a.Hi;
+  p.status = a.status;
+  const int tpc = 256 / a.Hi;
+  indexer_logits_kernel<<<(a.m + tpc - 1) / tpc, IX_THREADS, IX_SMEM, stream>>>(tq, tk, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+int topk_range(const float* logits, long long ld, const int* k_start, const int* k_end, int* out, int m, int topk,
+               int max_len, cudaStream_t stream) {
+  if (m <= 0) return 0;
+  if (max_len > TK_MAX_ROW || topk < 1) return -2;
+  constexpr int kMaxDev = 64;
+  static bool attr[kMaxDev] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return -4;
+  if (!attr[dev]) {
+    if (cudaFuncSetAttribute(topk_range_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_MAX_ROW * 4) !=
+        cudaSuccess)
+      return -4;
+    attr[dev] = true;
+  }
+  const size_t smem = static_cast<size_t>(max_len > 0 ? max_len : 1) * 4;
+  topk_range_kernel<<<m, TK_THREADS, smem, stream>>>(logits, ld, k_start, k_end, out, topk);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -25,4 +25,26 @@ struct SparseMlaArgs {
 // 0 on success, negative on invalid arguments (alignment: strides multiples of 8 elements, bases 16-byte aligned).
 int sparse_mla_fwd(const SparseMlaArgs& a, cudaStream_t stream);
 
+// Lightning-indexer logits logits[t, j] = sum_h w[t, h] * relu(q[t, h, :] . k[j, :]) for the keys j in
+// [k_start[t], k_end[t]) of every query t (entries outside that range are left unwritten). q [m, Hi, 128] bf16
+// contiguous, Hi in {32, 64, 128, 256}; k [n, 128] bf16 with row stride k_ld; w [m, Hi] fp32; logits [m, ld] fp32.
+struct IndexerArgs {
+  const void* q = nullptr;
+  const void* k = nullptr;
+  long long k_ld = 128;
+  const float* w = nullptr;
+  const int* k_start = nullptr;
+  const int* k_end = nullptr;
+  float* logits = nullptr;
+  long long ld = 0;
+  int m = 0, n = 0, Hi = 64;
+  int* status = nullptr;
+};
+int indexer_logits(const IndexerArgs& a, cudaStream_t stream);
+
+// Indices of the `topk` largest logits of every row inside [k_start, k_end) (unordered; -1 pads short rows) -> out
+// [m, topk] int32. `max_len` bounds k_end - k_start over all rows and must not exceed 49152.
+int topk_range(const float* logits, long long ld, const int* k_start, const int* k_end, int* out, int m, int topk,
+               int max_len, cudaStream_t stream);
+
 }  // namespace lf

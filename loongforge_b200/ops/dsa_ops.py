@@ -48,13 +48,54 @@ def indexer_logits_block(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor) -> t
     return (torch.relu(s) * w.float().unsqueeze(-1)).sum(1)
 
 
+_TK_MAX_ROW = 49152  # longest key range the selection kernel holds in shared memory
+
+
+def _native_indexer(q, k) -> bool:
+    from . import _ext
+    mod = _ext.get()
+    return (mod is not None and hasattr(mod, "indexer_topk") and q.is_cuda and q.dtype == torch.bfloat16
+            and k.dtype == torch.bfloat16 and q.shape[-1] == 128 and q.shape[1] in (32, 64, 128, 256))
+
+
+def indexer_topk_native(q, k, w, topk: int, k_start: torch.Tensor, k_end: torch.Tensor, max_len: int,
+                        chunk: int = 4096) -> torch.Tensor:
+    """Top-k key indices (int32 [m, topk], unordered, -1 padded) of every query over its key range [k_start, k_end):
+    the tcgen05 logits kernel fills a [chunk, n] fp32 buffer for `chunk` queries at a time (never [m, n]) and the
+    radix-select kernel picks from each row's range (csrc/dsa_sm100.cu)."""
+    from . import _ext
+    C = _ext.require()
+    m, n = q.shape[0], k.shape[0]
+    ld = (n + 3) // 4 * 4
+    logits = torch.empty(min(chunk, m), ld, dtype=torch.float32, device=q.device)
+    out = torch.empty(m, topk, dtype=torch.int32, device=q.device)
+    st = _ext.status_tensor(q.device)
+    qc, kc, wc = q.contiguous(), k.contiguous(), w.float().contiguous()
+    ks, ke = k_start.to(torch.int32).contiguous(), k_end.to(torch.int32).contiguous()
+    for s in range(0, m, chunk):
+        e = min(m, s + chunk)
+        C.indexer_topk(qc[s:e], kc, wc[s:e], ks[s:e], ke[s:e], logits, out[s:e], int(max_len), st)
+    return out
+
+
 def indexer_topk(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, topk: int, q_pos: torch.Tensor,
                  k_pos: torch.Tensor, seg_q: Optional[torch.Tensor] = None, seg_k: Optional[torch.Tensor] = None,
-                 block: int = 1024) -> Tuple[torch.Tensor, torch.Tensor]:
+                 block: int = 1024, keys_in_order: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """Causal top-k key indices per query. Returns (indices [m, topk] int64 with -1 padding,
     scores [m, topk] fp32 with -inf padding). `q_pos` / `k_pos` are global positions; `seg_*`
-    optional packed-sequence ids."""
+    optional packed-sequence ids. With ``keys_in_order`` (keys sorted by position, sequences contiguous) every
+    query's candidates are one index range and a GPU runs the native kernels; the scores are then not returned
+    (None): callers that need them evaluate `indexer_scores_at` on the selection."""
     m, n = q.shape[0], k.shape[0]
+    if keys_in_order and n <= _TK_MAX_ROW and _native_indexer(q, k):
+        kp = k_pos.contiguous()
+        k_end = torch.searchsorted(kp, q_pos.contiguous(), right=True)
+        if seg_q is not None:
+            # keys of one sequence are contiguous: the range starts at the sequence's first key
+            k_start = torch.searchsorted(seg_k.contiguous(), seg_q.contiguous(), right=False)
+        else:
+            k_start = torch.zeros_like(k_end)
+        return indexer_topk_native(q, k, w, topk, k_start, k_end, n).long(), None
     kk = min(topk, n)
     idx_out = torch.full((m, topk), -1, dtype=torch.int64, device=q.device)
     sc_out = torch.full((m, topk), float("-inf"), dtype=torch.float32, device=q.device)

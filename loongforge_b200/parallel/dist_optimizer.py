@@ -136,6 +136,10 @@ class DistributedOptimizer:
         # callables run after the data-parallel gradient reduction and before the norm / update (for reductions over
         # other groups that need the final gradients, e.g. the embedding copies of the first and last pipeline stage)
         self.post_sync_hooks: List = []
+        self._gather_stream = None          # --overlap-param-gather: stream, events per (buffer, bucket), hook state
+        self._gather_events: Dict[tuple, object] = {}
+        self._param_bucket: Dict[int, tuple] = {}
+        self._gather_hooks_installed = False
         self.step_count = 0
         self.lr = cfg.lr
         self.weight_decay = cfg.weight_decay
@@ -350,12 +354,33 @@ class DistributedOptimizer:
                 out[lo:hi].copy_(src[lo:hi])
 
     def _gather_params(self):
+        """Refresh every rank's copy of the parameters from the owners' shards. With ``overlap_param_gather`` on a GPU
+        the bucket all-gathers are only QUEUED here, on a communication stream and in the order the next forward pass
+        needs them (the buffers hold the parameters in roughly backward order, so the last bucket goes first); each
+        module waits for the buckets of its own parameters right before its forward (``_install_gather_waits``), so
+        the transfer of the later layers hides under the compute of the earlier ones
+        (reference: loongforge/train/training_utils.py:943-991,1319-1339)."""
         if not self.sharded:
             return
-        for sh in self.shards:
+        todo = [sh for sh in self.shards if sh.buf.dp_size > 1 and not self._peer_ok(sh)]
+        overlap = self.cfg.overlap_param_gather and todo and todo[0].buf.param_data.is_cuda
+        if overlap:
+            self._install_gather_waits()
+            if self._gather_stream is None:
+                self._gather_stream = torch.cuda.Stream()
+            cur = torch.cuda.current_stream()
+            self._gather_stream.wait_stream(cur)  # the updated shards are written by kernels of this stream
+            with torch.cuda.stream(self._gather_stream):
+                for sh in reversed(todo):
+                    buf, b = sh.buf, sh.bucket
+                    dist.all_gather_into_tensor(buf.param_data[b.start:b.end], buf.param_data[sh.start:sh.end],
+                                                group=buf.dp_group)
+                    ev = torch.cuda.Event()
+                    ev.record(self._gather_stream)
+                    self._gather_events[(id(buf), b.index)] = ev
+            return
+        for sh in todo:
             buf, b = sh.buf, sh.bucket
-            if buf.dp_size == 1 or self._peer_ok(sh):
-                continue
             full = buf.param_data[b.start:b.end]
             mine = buf.param_data[sh.start:sh.end]
             if full.is_cuda:
@@ -363,6 +388,45 @@ class DistributedOptimizer:
             else:
                 parts = list(full.chunk(buf.dp_size))
                 dist.all_gather(parts, mine.clone(), group=buf.dp_group)
+
+    def wait_param_gather(self, params=None) -> None:
+        """Make the current stream wait for the queued all-gathers of the buckets that hold `params` (all pending
+        buckets when None): called by the forward pre-hooks, and by anything that reads parameters outside a forward
+        pass (checkpoint save, evaluation of parameter norms, weight hashing)."""
+        if not self._gather_events:
+            return
+        if params is None:
+            keys = list(self._gather_events)
+        else:
+            keys = {self._param_bucket.get(id(p)) for p in params}
+        cur = torch.cuda.current_stream()
+        for k in keys:
+            ev = self._gather_events.pop(k, None) if k is not None else None
+            if ev is not None:
+                cur.wait_event(ev)
+
+    def _install_gather_waits(self) -> None:
+        if self._gather_hooks_installed:
+            return
+        self._gather_hooks_installed = True
+        for m in self.models:
+            for buf in m._all_buffers:
+                for p, (_, _, bi) in buf.param_index.items():
+                    self._param_bucket[id(p)] = (id(buf), bi)
+            # Granularity: the members of every nn.ModuleList (transformer layers, experts) wait for the parameters of
+            # their whole subtree right before they run; everything else (embedding, final norm, output layer, heads
+            # whose weights the model reads without calling the sub-module) is awaited when the model's forward starts.
+            layered = set()
+            for mod in m.module.modules():
+                if isinstance(mod, torch.nn.ModuleList):
+                    for child in mod:
+                        sub = list(child.parameters())
+                        if sub:
+                            layered.update(id(p) for p in sub)
+                            child.register_forward_pre_hook(
+                                lambda _m, _a, _sub=sub: self.wait_param_gather(_sub))
+            rest = [p for p in m.module.parameters() if id(p) not in layered]
+            m.module.register_forward_pre_hook(lambda _m, _a, _rest=rest: self.wait_param_gather(_rest))
 
     def zero_grad(self):
         for m in self.models:

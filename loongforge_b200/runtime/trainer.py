@@ -218,8 +218,15 @@ class Trainer:
             virt = v * pp + st.pp_rank
             module = self.model_provider(virt == 0, virt == pp * vpp - 1, splits[virt])
             self._apply_freezing(module)
+            # The NCCL all-to-all dispatcher puts expert-parallel collectives on the compute stream during backward;
+            # an overlapped gradient reduce-scatter would run a SECOND communicator (the data-parallel one) next to
+            # them on another stream, in an order that differs between ranks. That combination stopped making progress
+            # at 8 expert-parallel ranks, so with that dispatcher the reduction waits for the end of backward. The
+            # peer-memory dispatcher issues no NCCL call in backward and keeps the overlap.
+            serial_nccl = (bool(self.mcfg.num_moe_experts) and st.dims.ep > 1 and self.device.type == "cuda"
+                           and self.mcfg.moe_token_dispatcher_type != "peer")
             ddp_cfg = DDPConfig(grad_reduce_in_fp32=self.tcfg.grad_reduce_in_fp32,
-                                overlap_grad_reduce=self.tcfg.overlap_grad_reduce,
+                                overlap_grad_reduce=self.tcfg.overlap_grad_reduce and not serial_nccl,
                                 use_distributed_optimizer=self.tcfg.use_distributed_optimizer,
                                 peer_optimizer=self.tcfg.peer_optimizer,
                                 bucket_size=self.tcfg.ddp_bucket_size or max(40_000_000, 1_000_000 * self.dp))
@@ -501,6 +508,8 @@ class Trainer:
     def check_weight_hash_across_dp_replicas(self) -> bool:
         """Data-parallel replicas must hold bit-identical parameters: compares a checksum of every replica's parameter
         buffers over the data-parallel group (reference: loongforge/train/training_utils.py:2640-2645)."""
+        if hasattr(self.optimizer, "wait_param_gather"):
+            self.optimizer.wait_param_gather()  # queued (overlapped) parameter all-gathers must have landed
         acc = torch.zeros(1, dtype=torch.int64, device=self.device)
         for m in self.models:
             for buf in m._all_buffers:
@@ -708,6 +717,8 @@ class Trainer:
     # ------------------------------------------------------------------ checkpoints
     def save_checkpoint(self, path: str):
         from ..ckpt import checkpointing
+        if hasattr(self.optimizer, "wait_param_gather"):
+            self.optimizer.wait_param_gather()  # parameters are read outside a forward pass
         checkpointing.save_checkpoint(path, self)
 
     def load_checkpoint(self, path: str, **kw):

@@ -69,3 +69,46 @@ def test_sparse_mla_autograd_wrapper():
     assert _rel(o, ref) < 2e-2
     assert _rel(qg.grad, qr.grad) < 3e-2
     assert _rel(kg.grad, kr.grad) < 3e-2
+
+
+@pytest.mark.parametrize("m,n,Hi,topk,packed", [(300, 300, 64, 64, False), (1000, 1000, 32, 128, True),
+                                                (4200, 4200, 64, 2048, False), (513, 2000, 64, 256, False)])
+def test_indexer_logits_and_topk_match_fp32(m, n, Hi, topk, packed):
+    """Selected sets of the native indexer (tcgen05 logits + radix select) against the fp32 formulation: the k-th
+    largest logit of every row agrees and every selected key lies inside the row's causal range and scores at least
+    that threshold (ties may be broken differently)."""
+    from loongforge_b200.ops import _ext, dsa_ops
+
+    torch.manual_seed(m + Hi)
+    dev = "cuda"
+    q = torch.randn(m, Hi, 128, device=dev).bfloat16()
+    k = torch.randn(n, 128, device=dev).bfloat16()
+    w = torch.randn(m, Hi, device=dev) * 0.1
+    # query i sits at key position i + (n - m): it sees keys [seg start, i + n - m]
+    q_pos = torch.arange(m, device=dev) + (n - m)
+    k_pos = torch.arange(n, device=dev)
+    seg_q = seg_k = None
+    if packed:
+        bounds = torch.tensor([0, 130, 131, 600, n], device=dev)
+        seg_k = torch.bucketize(k_pos, bounds[1:], right=True)
+        seg_q = torch.bucketize(q_pos, bounds[1:], right=True)
+    idx, _ = dsa_ops.indexer_topk(q, k, w, topk, q_pos, k_pos, seg_q, seg_k, keys_in_order=True)
+    _ext.check_status()
+    ref_idx, ref_sc = dsa_ops.indexer_topk(q, k, w, topk, q_pos, k_pos, seg_q, seg_k, keys_in_order=False)
+    logits = dsa_ops.indexer_logits_block(q, k, w)
+    mask = k_pos[None, :] <= q_pos[:, None]
+    if packed:
+        mask &= seg_q[:, None] == seg_k[None, :]
+    n_valid = mask.sum(1)
+    # same number of selected keys, all of them inside the mask
+    assert torch.equal((idx >= 0).sum(1), torch.minimum(n_valid, torch.tensor(topk, device=dev)))
+    sel_ok = torch.gather(mask, 1, idx.clamp_min(0)) | (idx < 0)
+    assert bool(sel_ok.all())
+    # no duplicates
+    srt = torch.sort(torch.where(idx >= 0, idx, torch.arange(-topk, 0, device=dev)[None, :].expand_as(idx)), 1).values
+    assert bool((srt[:, 1:] != srt[:, :-1]).all())
+    # threshold agreement: the smallest selected logit equals the reference's k-th largest (bf16 products, fp32 sums)
+    got = torch.gather(logits, 1, idx.clamp_min(0)).masked_fill(idx < 0, float("inf")).min(1).values
+    ref = ref_sc.masked_fill(torch.isinf(ref_sc), float("inf")).min(1).values
+    rows = n_valid > 0
+    assert (got[rows] - ref[rows]).abs().max().item() < 2e-2 * max(1.0, ref[rows].abs().max().item())

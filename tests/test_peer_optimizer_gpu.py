@@ -1,5 +1,6 @@
 """Distributed optimizer with the peer-memory kernels (gradient reduce-scatter by pull, AdamW + all-gather by push)
-against the NCCL path: identical loss curves and parameters on 2 GPUs."""
+against the NCCL path: identical loss curves and parameters on 2 GPUs; and the overlapped parameter all-gather
+(``overlap_param_gather``) against the synchronous one, bit for bit."""
 import os
 import socket
 
@@ -31,12 +32,13 @@ def _worker(rank, world, port, q):
         from loongforge_b200.parallel import state as ps
         from loongforge_b200.runtime.trainer import TrainConfig, Trainer
 
-        def run(peer):
+        def run(peer, overlap_gather=False):
             ps.destroy_model_parallel()
             cfg = TransformerConfig(num_layers=2, hidden_size=512, num_attention_heads=4, num_query_groups=2,
                                     kv_channels=128, ffn_hidden_size=1024, vocab_size=2048)
             tc = TrainConfig(micro_batch_size=1, global_batch_size=4, seq_length=256, train_iters=4, lr=1e-3, bf16=True,
-                             master_as_remainder=True, peer_optimizer=peer, log_interval=1000)
+                             master_as_remainder=True, peer_optimizer=peer, log_interval=1000,
+                             overlap_param_gather=overlap_gather)
             tr = Trainer(cfg, tc, device=torch.device("cuda", rank))
             it = synthetic_batch_iterator(2048, 256, 1, dp_rank=tr.st.dp_rank, dp_size=tr.st.dp_size, seed=5)
             losses = [tr.train_step(it)["lm loss"] for _ in range(4)]
@@ -45,6 +47,8 @@ def _worker(rank, world, port, q):
 
         la, pa = run(False)
         lb, pb = run(True)
+        lc, pc = run(False, overlap_gather=True)  # parameter all-gathers queued behind the step, awaited per layer
+        assert lc == la and torch.equal(pa, pc), "overlapped parameter gather must not change a single bit"
         q.put((rank, "ok", (la, lb, float((pa - pb).abs().max()))))
     except Exception:  # noqa: BLE001
         import traceback
