@@ -58,6 +58,7 @@ at::Tensor gemm(const at::Tensor& A, const at::Tensor& B, c10::optional<at::Tens
   const int64_t N = b_mn_major ? B.size(1) : B.size(0);
   const int64_t Kb = b_mn_major ? B.size(0) : B.size(1);
   TORCH_CHECK(K == Kb, "gemm contraction mismatch: ", K, " vs ", Kb);
+  TORCH_CHECK(N % 8 == 0, "gemm: the output width N = ", N, " must be a multiple of 8 (16-byte rows)");
   at::Tensor D;
   if (D_.has_value()) {
     D = *D_;

@@ -56,9 +56,11 @@ def gemm(
     K-major A is ``[M, K]``, MN-major A is ``[K, M]``; K-major B is ``[N, K]``, MN-major B is
     ``[K, N]``. ``out_mode``: 0 bf16 store, 1 fp32 store, 2 fp32 accumulate into ``out``.
     """
-    if a.is_cuda:
+    if a.is_cuda and _gemm_native_ok(a, b, a_mn_major, b_mn_major, out, bias, residual):
         return _C().gemm(a, b, out, a_mn_major, b_mn_major, out_mode, bias, residual, alpha,
                          _ext.status_tensor(a.device), max_ctas)
+    # CPU, or a shape / dtype the tcgen05 GEMM does not take (an output narrower than 8 columns, fp32 operands):
+    # the same contract in PyTorch math
     am = a.t() if a_mn_major else a
     bm = b if b_mn_major else b.t()
     d = (am.float() @ bm.float()) * alpha
@@ -79,6 +81,20 @@ def gemm(
         out.copy_(d)
         return out
     return d
+
+
+def _gemm_native_ok(a, b, a_mn, b_mn, out, bias, residual) -> bool:
+    """Operands the tcgen05 GEMM accepts: bf16, unit inner stride, leading dimensions that are multiples of 8
+    elements (16-byte rows for TMA and the vectorised epilogue), 16-byte aligned bases."""
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or a.dim() != 2 or b.dim() != 2:
+        return False
+    n = b.shape[1] if b_mn else b.shape[0]
+    if n % 8 != 0:
+        return False  # the output's leading dimension
+    for t in (a, b, out, residual):
+        if t is not None and (t.stride(-1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0):
+            return False
+    return bias is None or (bias.dtype == torch.bfloat16 and bias.is_contiguous())
 
 
 def grouped_gemm(a: torch.Tensor, x: Optional[torch.Tensor], weights, outs, tokens_per_expert, *, mode: int,
