@@ -3,6 +3,7 @@
     python -m loongforge_b200.ops.bench_kernels gemm [--m 8192 --n 4096 --k 4096] [--iters 20]
     python -m loongforge_b200.ops.bench_kernels attention [--t 8192 --groups 8 --rep 4]
     python -m loongforge_b200.ops.bench_kernels norm [--t 8192 --h 4096]
+    python -m loongforge_b200.ops.bench_kernels dsa [--t 4096 --skv 8192 --topk 2048 --impl ours|torch|reference]
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29511 \
         -m loongforge_b200.ops.bench_kernels tp [--t 8192]     (fused TP GEMMs against NCCL + GEMM, Llama-3-8B shapes)
 
@@ -31,6 +32,77 @@ def _time(fn, iters, warm=5):
     e.record()
     torch.cuda.synchronize()
     return s.elapsed_time(e) / iters
+
+
+def dsa_bench(a):
+    """DeepSeek sparse attention kernels on the reference's own test shape (ops/tilelang_ops/sparse_mla_fwd.py:
+    S queries x 128 heads x 576 dims against SKV keys, top-k 2048; indexer 64 heads x 128 dims): `ours` = the tcgen05
+    kernels of csrc/dsa_sm100.cu, `torch` = the blocked PyTorch formulation, `reference` = the reference's TileLang
+    kernels imported unmodified from a copy of its ops/ directory under baseline/_ref."""
+    import os
+    import sys
+
+    from . import dsa_ops
+
+    S, SKV, K, H = a.t, a.skv, a.topk if a.topk > 8 else 2048, 128
+    dev = "cuda"
+    torch.manual_seed(0)
+    q = (torch.randn(S, H, 576, device=dev) * 0.3).bfloat16()
+    kv = (torch.randn(SKV, 576, device=dev) * 0.3).bfloat16()
+    # causal selection: query i sits at key position i + SKV - S and picks K of the keys it may see
+    lim = torch.arange(S, device=dev) + (SKV - S) + 1
+    idx = (torch.rand(S, K, device=dev) * lim[:, None]).int().clamp_(max=SKV - 1)
+    idx = torch.where(torch.arange(K, device=dev)[None, :] < lim[:, None], idx, torch.full_like(idx, -1))
+    scale = 576 ** -0.5
+    qi = torch.randn(S, 64, 128, device=dev).bfloat16()
+    ki = torch.randn(SKV, 128, device=dev).bfloat16()
+    wi = torch.randn(S, 64, device=dev) * 0.1
+    pos_q, pos_k = torch.arange(S, device=dev) + (SKV - S), torch.arange(SKV, device=dev)
+    out = {"what": "dsa", "impl": a.impl, "s": S, "skv": SKV, "topk": K, "heads": H}
+    fl_attn = 2.0 * S * K * H * (576 + 512) / 1e9          # useful FLOPs (one score pass)
+    fl_idx = 2.0 * 64 * 128 * float((lim.clamp(max=SKV)).sum()) / 1e9
+    if a.impl == "ours":
+        C, st = _ext.require(), _ext.status_tensor(q.device)
+        f_attn = lambda: C.sparse_mla_fwd(q, kv, idx, scale, st)  # noqa: E731
+        f_idx = lambda: dsa_ops.indexer_topk(qi, ki, wi, K, pos_q, pos_k, keys_in_order=True)  # noqa: E731
+    elif a.impl == "torch":
+        f_attn = lambda: dsa_ops._sparse_mla_block(q[:256], idx[:256].long(), kv, scale, 512, False)  # noqa: E731
+        f_idx = lambda: dsa_ops.indexer_topk(qi, ki, wi, K, pos_q, pos_k, keys_in_order=False)  # noqa: E731
+        fl_attn *= 256.0 / S  # one 256-query block (what fits without the blockwise wrapper)
+    else:
+        ref = os.path.join(os.path.dirname(__file__), "..", "..", "baseline", "_ref", "ops", "tilelang_ops")
+        if not os.path.isdir(ref):
+            print(json.dumps({"what": "dsa", "impl": "reference", "unavailable": "baseline/_ref/ops/tilelang_ops missing"}))
+            return
+        sys.path.insert(0, os.path.abspath(ref))
+        try:
+            import sparse_mla_fwd as R  # the reference's file, unmodified
+            offsets = torch.tensor([0, S], dtype=torch.int32, device=dev)  # query-token boundaries, as in its own test
+            idx_r = idx.clone()
+            idx_r[idx_r < 0] = SKV  # the reference marks unused slots with an index past the keys
+            kv3, idx3 = kv.view(SKV, 1, 576).contiguous(), idx_r.view(S, 1, K).contiguous()
+            f_attn = lambda: R.sparse_mla_fwd_interface(q, kv3, idx3, offsets, chunk_offset=SKV - S, sm_scale=scale,  # noqa: E731
+                                                        block_I=64, num_stages=2, threads=256)
+            f_attn()
+            torch.cuda.synchronize()
+        except Exception as e:  # noqa: BLE001 - the TileLang kernels may not build for this architecture
+            print(json.dumps({"what": "dsa", "impl": "reference",
+                              "unavailable": f"{type(e).__name__}: {str(e)[:300]}"}))
+            return
+        f_idx = None
+    if a.once:
+        f_attn()
+        if f_idx:
+            f_idx()
+    else:
+        ms = _time(f_attn, a.iters, warm=2)
+        out.update(sparse_mla_fwd_ms=ms, sparse_mla_fwd_tflops=fl_attn / ms)
+        if f_idx:
+            ms = _time(f_idx, max(2, a.iters // 4), warm=1)
+            out.update(indexer_topk_ms=ms, indexer_logits_tflops=fl_idx / ms)
+    torch.cuda.synchronize()
+    _ext.check_status()
+    print(json.dumps(out))
 
 
 def tp_bench(a):
@@ -108,7 +180,9 @@ def tp_bench(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "norm", "grouped", "router", "fp8", "tp"])
+    ap.add_argument("what", choices=["gemm", "attention", "norm", "grouped", "router", "fp8", "tp", "dsa"])
+    ap.add_argument("--skv", type=int, default=8192)
+    ap.add_argument("--impl", default="ours", choices=["ours", "torch", "reference"])
     ap.add_argument("--experts", type=int, default=16)
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--m", type=int, default=8192)
@@ -124,6 +198,8 @@ def main():
     _ext.require()
     if a.what == "tp":
         return tp_bench(a)
+    if a.what == "dsa":
+        return dsa_bench(a)
     dev = "cuda"
     torch.manual_seed(0)
     out = {"what": a.what}

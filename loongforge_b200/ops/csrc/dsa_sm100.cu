@@ -5,14 +5,20 @@
 // q [m, H <= 128, 576] bf16 (latent 512 + rope 64), kv [n, 576] bf16 shared by all heads, idx [m, topk] int32 with -1
 // for empty slots. For one query token the H heads share the same gathered rows, so the heads are the M = 128 rows of
 // the tensor-core tile:
-//   S[128 heads x 32 keys]  = Q_t K_blk^T        (A = Q_t in shared memory, 36 k-steps over the 576 dims)
+//   S[128 heads x 32 keys]  = Q_t K_blk^T        (36 k-steps over the 576 dims)
 //   O[128 heads x 256]     += P K_blk[:, half]   (A = P packed bf16 in TMEM over the columns of S, B = the gathered
 //                                                 block read MN-major)
 // The fp32 accumulator of all 512 value dims would fill the 512 TMEM columns by itself, so one CTA owns ONE HALF of the
-// value dims of one query token (grid = tokens x 2) and recomputes the scores. Rows are gathered by 128 producer
-// threads with 16-byte cp.async copies straight into the 128-byte-swizzled tile layout (two stages), the MMA thread
-// runs the scores one block ahead of the softmax warps, and the softmax uses the lazily rescaled running maximum of the
-// dense attention kernel. Every wait is bounded.
+// value dims of one query token (grid = tokens x 2) and recomputes the scores.
+//
+// Where the operands live. The kernel is bound by the latency of the row gather, so shared memory goes to gather
+// stages, not to Q: the first 384 dims of the Q tile sit in TMEM (192 columns, written once per CTA by the softmax
+// warps from a TMA-staged copy) and feed the score product as a TMEM A operand; only the last 192 dims stay in shared
+// memory (48 KB). That leaves four 36 KB stages for gathered key blocks, filled by 128 producer threads with 16-byte
+// cp.async copies straight into the 128-byte-swizzled tile layout. TMEM: O 256 | S[2] 2 x 32 | Q 192 = 512 columns.
+// The MMA thread keeps the scores two blocks ahead of the softmax warps; the softmax uses the lazily rescaled
+// running maximum of the dense attention kernel; a per-block bit mask of live slots comes from the producers.
+// Every wait is bounded.
 //
 // Replaces the TileLang kernel of the reference (ops/tilelang_ops/sparse_mla_fwd.py:11-181; oracle :218-265).
 #include "sm100_ptx.cuh"
@@ -20,13 +26,15 @@
 
 namespace lf {
 
-static constexpr int SM_DK = 576, SM_DV = 512, SM_NB = 32;        // key dims, value dims, gathered rows per block
+static constexpr int SM_DK = 576, SM_NB = 32;                      // key dims, gathered rows per block
 static constexpr int SM_QBOX = 128 * 64 * 2;                       // one [128 heads x 64 dims] box of Q: 16 KB
-static constexpr int SM_Q_BYTES = 9 * SM_QBOX;                     // 144 KB
+static constexpr int SM_QT_BOXES = 6;                              // Q boxes that move to TMEM (384 dims = 192 columns)
+static constexpr int SM_QS_BYTES = 3 * SM_QBOX;                    // Q boxes that stay in shared memory: 48 KB
 static constexpr int SM_KBOX = SM_NB * 64 * 2;                     // one [32 rows x 64 dims] box: 4 KB
 static constexpr int SM_KV_BYTES = 9 * SM_KBOX;                    // 36 KB per stage
-static constexpr int SM_STAGES = 2;
-static constexpr int SM_CTL = SM_Q_BYTES + SM_STAGES * SM_KV_BYTES;
+static constexpr int SM_STAGES = 4;
+static constexpr int SM_KV0 = SM_QS_BYTES;                         // gather stages (first used to stage Q for TMEM)
+static constexpr int SM_CTL = SM_KV0 + SM_STAGES * SM_KV_BYTES;
 static constexpr int SM_SMEM = SM_CTL + 256 + 1024;
 static constexpr int SM_THREADS = 288;  // 4 gather warps, 1 MMA warp, 4 softmax warps
 static constexpr float SM_LOG2E = 1.4426950408889634f;
@@ -44,12 +52,13 @@ struct SmlaParams {
   int* status;
 };
 
-enum { S_Q = 0, S_KV_FULL = 1, S_KV_EMPTY = 3, S_S_FULL = 5, S_P_FULL = 7, S_O_DONE = 9 };
+enum { S_Q = 0, S_QT = 1, S_KV_FULL = 2, S_KV_EMPTY = 6, S_S_FULL = 10, S_P_FULL = 12, S_O_DONE = 14 };
 
 struct SmlaCtl {
-  uint64_t bars[12];
+  uint64_t bars[16];
   uint32_t tmem_slot;
   int abort_flag;
+  uint32_t live[SM_STAGES];  // bit i: slot i of the stage's block holds a key
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -73,11 +82,14 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
 
   if (threadIdx.x == 0) {
     mbar_init(&bars[S_Q], 1);
-    for (int s = 0; s < 2; ++s) {
+    mbar_init(&bars[S_QT], 4);
+    for (int s = 0; s < SM_STAGES; ++s) {
       mbar_init(&bars[S_KV_FULL + s], 128);
       mbar_init(&bars[S_KV_EMPTY + s], 1);
-      mbar_init(&bars[S_S_FULL + s], 1);
-      mbar_init(&bars[S_P_FULL + s], 4);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars[S_S_FULL + b], 1);
+      mbar_init(&bars[S_P_FULL + b], 4);
     }
     mbar_init(&bars[S_O_DONE], 1);
     ctl->abort_flag = 0;
@@ -88,23 +100,33 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = ctl->tmem_slot;
-  const uint32_t t_o = tmem, t_s = tmem + 256;  // O: 256 columns, S[2]: 32 columns each
+  const uint32_t t_o = tmem, t_s = tmem + 256, t_q = tmem + 320;  // O 256 | S[2] 2 x 32 | Q 192
 
   if (warp < 4) {
     // ------------------------------------------------------------ gather producers
     if (threadIdx.x == 0) {
-      mbar_arrive_expect_tx(&bars[S_Q], SM_Q_BYTES);
-      for (int b = 0; b < 9; ++b) tma_load_3d(smem + b * SM_QBOX, &tq, &bars[S_Q], b * 64, 0, tok);
+      // Q: boxes 0..5 are staged in the (still unused) gather area for the copy into TMEM, boxes 6..8 stay resident
+      mbar_arrive_expect_tx(&bars[S_Q], 9 * SM_QBOX);
+      for (int b = 0; b < SM_QT_BOXES; ++b) tma_load_3d(smem + SM_KV0 + b * SM_QBOX, &tq, &bars[S_Q], b * 64, 0, tok);
+      for (int b = SM_QT_BOXES; b < 9; ++b)
+        tma_load_3d(smem + (b - SM_QT_BOXES) * SM_QBOX, &tq, &bars[S_Q], b * 64, 0, tok);
     }
     const int t = threadIdx.x;  // 0..127
-    bool ok = true;
+    // the gather area is free once the softmax warps have moved the staged part of Q into TMEM
+    bool ok = mbar_wait(&bars[S_QT], 0, abort_flag);
     for (int j = 0; j < nb && ok; ++j) {
-      const int s = j & 1;
-      ok = mbar_wait(&bars[S_KV_EMPTY + s], ((j >> 1) & 1) ^ 1, abort_flag);
+      const int s = j % SM_STAGES;
+      ok = mbar_wait(&bars[S_KV_EMPTY + s], ((j / SM_STAGES) & 1) ^ 1, abort_flag);
       if (!ok) break;
-      uint8_t* stage = smem + SM_Q_BYTES + s * SM_KV_BYTES;
+      uint8_t* stage = smem + SM_KV0 + s * SM_KV_BYTES;
+      if (warp == 0) {
+        const int slot = j * SM_NB + lane;
+        const int id = slot < p.topk ? my_idx[slot] : -1;
+        const unsigned m = __ballot_sync(0xffffffffu, id >= 0 && id < p.n_kv);
+        if (lane == 0) ctl->live[s] = m;
+      }
       // 32 rows x 72 chunks of 16 bytes; chunk c -> (row, 16-byte column) -> swizzled place in its 64-dim box
-#pragma unroll 2
+#pragma unroll 3
       for (int c = t; c < SM_NB * 72; c += 128) {
         const int row = c / 72, col16 = c - row * 72;
         const int box = col16 >> 3, ch = col16 & 7;
@@ -126,35 +148,38 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
   } else if (warp == 4) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t sq = smem_u32(smem), skv = smem_u32(smem + SM_Q_BYTES);
+      const uint32_t sq = smem_u32(smem), skv = smem_u32(smem + SM_KV0);
       constexpr uint32_t idesc_s = make_idesc(1, 1, false, false, 128, SM_NB);
       constexpr uint32_t idesc_o = make_idesc(1, 1, false, true, 128, 256);
       auto issue_s = [&](int j) {
-        const int s = j & 1;
+        const int s = j % SM_STAGES, b = j & 1;
         const uint32_t kb = skv + s * SM_KV_BYTES;
+        // dims 0..383: Q from TMEM (8 columns per k-step); dims 384..575: Q from shared memory
 #pragma unroll 4
-        for (int kk = 0; kk < 36; ++kk) {
-          const uint64_t da = make_smem_desc_sw128(sq + (kk >> 2) * SM_QBOX + (kk & 3) * 32, 16, 1024);
+        for (int kk = 0; kk < 24; ++kk) {
           const uint64_t db = make_smem_desc_sw128(kb + (kk >> 2) * SM_KBOX + (kk & 3) * 32, 16, 1024);
-          tc_mma_f16_ss(t_s + s * SM_NB, da, db, idesc_s, kk > 0 ? 1u : 0u);
+          tc_mma_f16_ts(t_s + b * SM_NB, t_q + kk * 8, db, idesc_s, kk > 0 ? 1u : 0u);
         }
-        tc_commit(&bars[S_S_FULL + s]);
+#pragma unroll 4
+        for (int kk = 24; kk < 36; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(sq + ((kk >> 2) - SM_QT_BOXES) * SM_QBOX + (kk & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(kb + (kk >> 2) * SM_KBOX + (kk & 3) * 32, 16, 1024);
+          tc_mma_f16_ss(t_s + b * SM_NB, da, db, idesc_s, 1u);
+        }
+        tc_commit(&bars[S_S_FULL + b]);
       };
       bool ok = mbar_wait(&bars[S_Q], 0, abort_flag);
-      if (ok) ok = mbar_wait(&bars[S_KV_FULL + 0], 0, abort_flag);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_s(0);
+      if (ok) ok = mbar_wait(&bars[S_QT], 0, abort_flag);
+      for (int j = 0; j < 2 && j < nb && ok; ++j) {  // scores of the first two blocks
+        ok = mbar_wait(&bars[S_KV_FULL + j], 0, abort_flag);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_s(j);
+        }
       }
       for (int j = 0; j < nb && ok; ++j) {
-        const int s = j & 1;
-        if (j + 1 < nb) {
-          ok = mbar_wait(&bars[S_KV_FULL + (s ^ 1)], ((j + 1) >> 1) & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after_sync();
-          issue_s(j + 1);  // overwrites P[j-1], which O += P[j-1] V[j-1] (issued earlier) has read by then
-        }
-        ok = mbar_wait(&bars[S_P_FULL + s], (j >> 1) & 1, abort_flag);
+        const int s = j % SM_STAGES, b = j & 1;
+        ok = mbar_wait(&bars[S_P_FULL + b], (j >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
         // O += P[j] V[j]: 32 gathered rows = 2 k-steps; B = this half's four 64-dim boxes read MN-major
@@ -162,10 +187,17 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk) {
           const uint64_t db = make_smem_desc_sw128(vb + kk * 2048, SM_KBOX, 1024);
-          tc_mma_f16_ts(t_o, t_s + s * SM_NB + kk * 8, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          tc_mma_f16_ts(t_o, t_s + b * SM_NB + kk * 8, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         }
         tc_commit(&bars[S_KV_EMPTY + s]);
         tc_commit(&bars[S_O_DONE]);
+        if (j + 2 < nb) {  // scores two blocks ahead, into the buffer P[j] has just been read from
+          const int s2 = (j + 2) % SM_STAGES;
+          ok = mbar_wait(&bars[S_KV_FULL + s2], ((j + 2) / SM_STAGES) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_s(j + 2);
+        }
       }
       if (!ok) atomicCAS(p.status, 0, LF_ERR_WAIT_FULL);
     }
@@ -175,22 +207,43 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
     const int h = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     float m_ref = -INFINITY, l_sum = 0.f;
-    bool ok = true;
+    bool ok = mbar_wait(&bars[S_Q], 0, abort_flag);
+    if (ok) {
+      // move dims 0..383 of this head's Q row from the staged (swizzled) boxes into TMEM: two bf16 per column
+      const uint8_t* qst = smem + SM_KV0;
+#pragma unroll 1
+      for (int b = 0; b < SM_QT_BOXES; ++b) {
+        const uint8_t* rowp = qst + b * SM_QBOX + (h >> 3) * 1024 + (h & 7) * 128;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {  // 16 columns = 32 dims = four 16-byte chunks
+          uint32_t r[16];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint4 v = *reinterpret_cast<const uint4*>(rowp + (((hh * 4 + c) ^ (h & 7)) << 4));
+            r[c * 4] = v.x; r[c * 4 + 1] = v.y; r[c * 4 + 2] = v.z; r[c * 4 + 3] = v.w;
+          }
+          tmem_st_32x32b_x16(t_q + lane_off + b * 32 + hh * 16, r);
+        }
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[S_QT]);
+    }
     for (int j = 0; j < nb && ok; ++j) {
-      const int s = j & 1;
-      ok = mbar_wait(&bars[S_S_FULL + s], (j >> 1) & 1, abort_flag);
+      const int s = j % SM_STAGES, b = j & 1;
+      ok = mbar_wait(&bars[S_KV_FULL + s], (j / SM_STAGES) & 1, abort_flag);  // the producers' mask is visible
+      if (ok) ok = mbar_wait(&bars[S_S_FULL + b], (j >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
+      const uint32_t live = ctl->live[s];
       uint32_t r[32];
-      tmem_ld_32x32b_x32(t_s + s * SM_NB + lane_off, r);
+      tmem_ld_32x32b_x32(t_s + b * SM_NB + lane_off, r);
       tmem_ld_wait();
-      // empty slots (-1) are masked; the slot list is the same for every head: broadcast loads
       float mx = -INFINITY;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const int slot = j * SM_NB + i;
-        const bool live = slot < p.topk && my_idx[slot] >= 0;
-        if (!live) r[i] = 0xff800000u;
+        if (!((live >> i) & 1u)) r[i] = 0xff800000u;  // empty slots (-1) are masked
         mx = fmaxf(mx, __uint_as_float(r[i]));
       }
       mx *= p.scale_log2;
@@ -220,15 +273,15 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const float a = exp2f(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, neg_m));
-        const float b = exp2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, neg_m));
-        l_sum += a + b;
-        pk[i] = pack_bf16x2(a, b);
+        const float b2 = exp2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, neg_m));
+        l_sum += a + b2;
+        pk[i] = pack_bf16x2(a, b2);
       }
-      tmem_st_32x32b_x16(t_s + s * SM_NB + lane_off, pk);
+      tmem_st_32x32b_x16(t_s + b * SM_NB + lane_off, pk);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[S_P_FULL + s]);
+      if (lane == 0) mbar_arrive(&bars[S_P_FULL + b]);
     }
     if (ok && nb > 0) ok = mbar_wait(&bars[S_O_DONE], (nb - 1) & 1, abort_flag);
     if (!ok) {
