@@ -111,38 +111,61 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
       for (int b = SM_QT_BOXES; b < 9; ++b)
         tma_load_3d(smem + (b - SM_QT_BOXES) * SM_QBOX, &tq, &bars[S_Q], b * 64, 0, tok);
     }
-    const int t = threadIdx.x;  // 0..127
+    // Thread t copies row t / 4 of every block: the 16-byte chunks 4 i + (t % 4), so four neighbouring lanes read 64
+    // contiguous bytes. Copies of up to three blocks are in flight per thread: the arrival for block j - 2 is made
+    // (after a proxy fence) once its cp.async group has landed, while the copies of blocks j - 1 and j are under way.
+    const int row = threadIdx.x >> 2, qd = threadIdx.x & 3;
     // the gather area is free once the softmax warps have moved the staged part of Q into TMEM
     bool ok = mbar_wait(&bars[S_QT], 0, abort_flag);
+    int issued = 0;
     for (int j = 0; j < nb && ok; ++j) {
       const int s = j % SM_STAGES;
       ok = mbar_wait(&bars[S_KV_EMPTY + s], ((j / SM_STAGES) & 1) ^ 1, abort_flag);
       if (!ok) break;
       uint8_t* stage = smem + SM_KV0 + s * SM_KV_BYTES;
       if (warp == 0) {
-        const int slot = j * SM_NB + lane;
-        const int id = slot < p.topk ? my_idx[slot] : -1;
-        const unsigned m = __ballot_sync(0xffffffffu, id >= 0 && id < p.n_kv);
+        const int sl = j * SM_NB + lane;
+        const int idl = sl < p.topk ? my_idx[sl] : -1;
+        const unsigned m = __ballot_sync(0xffffffffu, idl >= 0 && idl < p.n_kv);
         if (lane == 0) ctl->live[s] = m;
       }
-      // 32 rows x 72 chunks of 16 bytes; chunk c -> (row, 16-byte column) -> swizzled place in its 64-dim box
-#pragma unroll 3
-      for (int c = t; c < SM_NB * 72; c += 128) {
-        const int row = c / 72, col16 = c - row * 72;
-        const int box = col16 >> 3, ch = col16 & 7;
-        const int slot = j * SM_NB + row;
-        const int id = slot < p.topk ? my_idx[slot] : -1;
-        uint8_t* dst = stage + box * SM_KBOX + (row >> 3) * 1024 + (row & 7) * 128 + ((ch ^ (row & 7)) << 4);
-        if (id >= 0 && id < p.n_kv) {
-          cp_async16(smem_u32(dst), p.kv + static_cast<long long>(id) * p.kv_ts + col16 * 8);
-        } else {
-          *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
-          if (id >= p.n_kv) atomicCAS(p.status, 0, LF_ERR_BAD_INDEX);
+      const int slot = j * SM_NB + row;
+      const int id = slot < p.topk ? my_idx[slot] : -1;
+      uint8_t* drow = stage + (row >> 3) * 1024 + (row & 7) * 128;
+      if (id >= 0 && id < p.n_kv) {
+        const __nv_bfloat16* src = p.kv + static_cast<long long>(id) * p.kv_ts;
+#pragma unroll
+        for (int i = 0; i < 18; ++i) {
+          const int col16 = i * 4 + qd;
+          cp_async16(smem_u32(drow + (col16 >> 3) * SM_KBOX + (((col16 & 7) ^ (row & 7)) << 4)), src + col16 * 8);
         }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 18; ++i) {
+          const int col16 = i * 4 + qd;
+          *reinterpret_cast<uint4*>(drow + (col16 >> 3) * SM_KBOX + (((col16 & 7) ^ (row & 7)) << 4)) =
+              make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (id >= p.n_kv) atomicCAS(p.status, 0, LF_ERR_BAD_INDEX);
       }
-      cp_async_wait_all();
-      fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
-      mbar_arrive(&bars[S_KV_FULL + s]);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      ++issued;
+      if (j >= 2) {
+        asm volatile("cp.async.wait_group 2;" ::: "memory");  // block j - 2 has landed
+        fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
+        mbar_arrive(&bars[S_KV_FULL + (j - 2) % SM_STAGES]);
+      }
+    }
+    // drain: the last (up to) two blocks
+    if (issued >= 2) {
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+      fence_proxy_async_smem();
+      mbar_arrive(&bars[S_KV_FULL + (issued - 2) % SM_STAGES]);
+    }
+    if (issued >= 1) {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      fence_proxy_async_smem();
+      mbar_arrive(&bars[S_KV_FULL + (issued - 1) % SM_STAGES]);
     }
     if (!ok && lane == 0) atomicCAS(p.status, 0, LF_ERR_WAIT_EMPTY);
   } else if (warp == 4) {
