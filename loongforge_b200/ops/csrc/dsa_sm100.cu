@@ -5,20 +5,22 @@
 // q [m, H <= 128, 576] bf16 (latent 512 + rope 64), kv [n, 576] bf16 shared by all heads, idx [m, topk] int32 with -1
 // for empty slots. For one query token the H heads share the same gathered rows, so the heads are the M = 128 rows of
 // the tensor-core tile:
-//   S[128 heads x 32 keys]  = Q_t K_blk^T        (36 k-steps over the 576 dims)
+//   S[128 heads x 64 keys]  = Q_t K_blk^T        (36 k-steps over the 576 dims)
 //   O[128 heads x 256]     += P K_blk[:, half]   (A = P packed bf16 in TMEM over the columns of S, B = the gathered
 //                                                 block read MN-major)
 // The fp32 accumulator of all 512 value dims would fill the 512 TMEM columns by itself, so one CTA owns ONE HALF of the
 // value dims of one query token (grid = tokens x 2) and recomputes the scores.
 //
-// Where the operands live. The kernel is bound by the latency of the row gather, so shared memory goes to gather
-// stages, not to Q: the first 384 dims of the Q tile sit in TMEM (192 columns, written once per CTA by the softmax
-// warps from a TMA-staged copy) and feed the score product as a TMEM A operand; only the last 192 dims stay in shared
-// memory (48 KB). That leaves four 36 KB stages for gathered key blocks, filled by 128 producer threads with 16-byte
-// cp.async copies straight into the 128-byte-swizzled tile layout. TMEM: O 256 | S[2] 2 x 32 | Q 192 = 512 columns.
-// The MMA thread keeps the scores two blocks ahead of the softmax warps; the softmax uses the lazily rescaled
-// running maximum of the dense attention kernel; a per-block bit mask of live slots comes from the producers.
-// Every wait is bounded.
+// Where the operands live. Score MMAs narrower than 64 keys run far below the tensor core's rate (a cycle probe
+// showed ~75 cycles for a 128 x 32 x 16 MMA against 64 for 128 x 128 x 16), so a block is 64 gathered keys, and
+// shared memory goes to two 72 KB gather stages rather than to Q: the first 256 dims of the Q tile sit in TMEM (128
+// columns, written once per CTA by the softmax warps from a TMA-staged copy) and feed the score product as a TMEM A
+// operand; the other 320 dims stay in shared memory (80 KB). The stages are filled by 128 producer threads with
+// 16-byte cp.async copies straight into the 128-byte-swizzled tile layout. TMEM: O 256 | S[2] 2 x 64 | Q 128 = 512
+// columns. Issue order of the MMA thread per block: O += P[j] V[j], then S[j+1]: the gather of block j + 2 (into the
+// stage that product has just released) then has a whole block of tensor work and softmax to land in. The softmax
+// uses the lazily rescaled running maximum of the dense attention kernel; a per-block bit mask of live slots comes
+// from the producers. Every wait is bounded.
 //
 // Replaces the TileLang kernel of the reference (ops/tilelang_ops/sparse_mla_fwd.py:11-181; oracle :218-265).
 #include "sm100_ptx.cuh"
@@ -26,13 +28,13 @@
 
 namespace lf {
 
-static constexpr int SM_DK = 576, SM_NB = 32;                      // key dims, gathered rows per block
+static constexpr int SM_DK = 576, SM_NB = 64;                      // key dims, gathered rows per block
 static constexpr int SM_QBOX = 128 * 64 * 2;                       // one [128 heads x 64 dims] box of Q: 16 KB
-static constexpr int SM_QT_BOXES = 6;                              // Q boxes that move to TMEM (384 dims = 192 columns)
-static constexpr int SM_QS_BYTES = 3 * SM_QBOX;                    // Q boxes that stay in shared memory: 48 KB
-static constexpr int SM_KBOX = SM_NB * 64 * 2;                     // one [32 rows x 64 dims] box: 4 KB
-static constexpr int SM_KV_BYTES = 9 * SM_KBOX;                    // 36 KB per stage
-static constexpr int SM_STAGES = 4;
+static constexpr int SM_QT_BOXES = 4;                              // Q boxes that move to TMEM (256 dims = 128 columns)
+static constexpr int SM_QS_BYTES = 5 * SM_QBOX;                    // Q boxes that stay in shared memory: 80 KB
+static constexpr int SM_KBOX = SM_NB * 64 * 2;                     // one [64 rows x 64 dims] box: 8 KB
+static constexpr int SM_KV_BYTES = 9 * SM_KBOX;                    // 72 KB per stage
+static constexpr int SM_STAGES = 2;
 static constexpr int SM_KV0 = SM_QS_BYTES;                         // gather stages (first used to stage Q for TMEM)
 static constexpr int SM_CTL = SM_KV0 + SM_STAGES * SM_KV_BYTES;
 static constexpr int SM_SMEM = SM_CTL + 256 + 1024;
@@ -52,13 +54,13 @@ struct SmlaParams {
   int* status;
 };
 
-enum { S_Q = 0, S_QT = 1, S_KV_FULL = 2, S_KV_EMPTY = 6, S_S_FULL = 10, S_P_FULL = 12, S_O_DONE = 14 };
+enum { S_Q = 0, S_QT = 1, S_KV_FULL = 2, S_KV_EMPTY = 4, S_S_FULL = 6, S_P_FULL = 8, S_O_DONE = 10 };
 
 struct SmlaCtl {
   uint64_t bars[16];
   uint32_t tmem_slot;
   int abort_flag;
-  uint32_t live[SM_STAGES];  // bit i: slot i of the stage's block holds a key
+  uint32_t live[SM_STAGES][2];  // bit i of word w: slot 32 w + i of the stage's block holds a key
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -100,34 +102,34 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = ctl->tmem_slot;
-  const uint32_t t_o = tmem, t_s = tmem + 256, t_q = tmem + 320;  // O 256 | S[2] 2 x 32 | Q 192
+  const uint32_t t_o = tmem, t_s = tmem + 256, t_q = tmem + 384;  // O 256 | S[2] 2 x 64 | Q 128
 
   if (warp < 4) {
     // ------------------------------------------------------------ gather producers
     if (threadIdx.x == 0) {
-      // Q: boxes 0..5 are staged in the (still unused) gather area for the copy into TMEM, boxes 6..8 stay resident
+      // Q: boxes 0..3 are staged in the (still unused) gather area for the copy into TMEM, boxes 4..8 stay resident
       mbar_arrive_expect_tx(&bars[S_Q], 9 * SM_QBOX);
       for (int b = 0; b < SM_QT_BOXES; ++b) tma_load_3d(smem + SM_KV0 + b * SM_QBOX, &tq, &bars[S_Q], b * 64, 0, tok);
       for (int b = SM_QT_BOXES; b < 9; ++b)
         tma_load_3d(smem + (b - SM_QT_BOXES) * SM_QBOX, &tq, &bars[S_Q], b * 64, 0, tok);
     }
-    // Thread t copies row t / 4 of every block: the 16-byte chunks 4 i + (t % 4), so four neighbouring lanes read 64
-    // contiguous bytes. Copies of up to three blocks are in flight per thread: the arrival for block j - 2 is made
-    // (after a proxy fence) once its cp.async group has landed, while the copies of blocks j - 1 and j are under way.
-    const int row = threadIdx.x >> 2, qd = threadIdx.x & 3;
+    // Thread t copies row t / 2 of every block: the 16-byte chunks 2 i + (t % 2), so two neighbouring lanes read 32
+    // contiguous bytes. Only one stage is ever free at a time (the other holds the block whose scores are running),
+    // so a producer issues a block, waits for it to land, publishes it (after a proxy fence) and then waits for the
+    // next stage to be released.
+    const int row = threadIdx.x >> 1, hd = threadIdx.x & 1;
     // the gather area is free once the softmax warps have moved the staged part of Q into TMEM
     bool ok = mbar_wait(&bars[S_QT], 0, abort_flag);
-    int issued = 0;
     for (int j = 0; j < nb && ok; ++j) {
       const int s = j % SM_STAGES;
       ok = mbar_wait(&bars[S_KV_EMPTY + s], ((j / SM_STAGES) & 1) ^ 1, abort_flag);
       if (!ok) break;
       uint8_t* stage = smem + SM_KV0 + s * SM_KV_BYTES;
-      if (warp == 0) {
-        const int sl = j * SM_NB + lane;
+      if (warp < 2) {  // warp w publishes the live bits of slots 32 w .. 32 w + 31
+        const int sl = j * SM_NB + warp * 32 + lane;
         const int idl = sl < p.topk ? my_idx[sl] : -1;
         const unsigned m = __ballot_sync(0xffffffffu, idl >= 0 && idl < p.n_kv);
-        if (lane == 0) ctl->live[s] = m;
+        if (lane == 0) ctl->live[s][warp] = m;
       }
       const int slot = j * SM_NB + row;
       const int id = slot < p.topk ? my_idx[slot] : -1;
@@ -135,37 +137,22 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
       if (id >= 0 && id < p.n_kv) {
         const __nv_bfloat16* src = p.kv + static_cast<long long>(id) * p.kv_ts;
 #pragma unroll
-        for (int i = 0; i < 18; ++i) {
-          const int col16 = i * 4 + qd;
+        for (int i = 0; i < 36; ++i) {
+          const int col16 = i * 2 + hd;
           cp_async16(smem_u32(drow + (col16 >> 3) * SM_KBOX + (((col16 & 7) ^ (row & 7)) << 4)), src + col16 * 8);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 18; ++i) {
-          const int col16 = i * 4 + qd;
+        for (int i = 0; i < 36; ++i) {
+          const int col16 = i * 2 + hd;
           *reinterpret_cast<uint4*>(drow + (col16 >> 3) * SM_KBOX + (((col16 & 7) ^ (row & 7)) << 4)) =
               make_uint4(0u, 0u, 0u, 0u);
         }
         if (id >= p.n_kv) atomicCAS(p.status, 0, LF_ERR_BAD_INDEX);
       }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      ++issued;
-      if (j >= 2) {
-        asm volatile("cp.async.wait_group 2;" ::: "memory");  // block j - 2 has landed
-        fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
-        mbar_arrive(&bars[S_KV_FULL + (j - 2) % SM_STAGES]);
-      }
-    }
-    // drain: the last (up to) two blocks
-    if (issued >= 2) {
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-      fence_proxy_async_smem();
-      mbar_arrive(&bars[S_KV_FULL + (issued - 2) % SM_STAGES]);
-    }
-    if (issued >= 1) {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-      fence_proxy_async_smem();
-      mbar_arrive(&bars[S_KV_FULL + (issued - 1) % SM_STAGES]);
+      cp_async_wait_all();
+      fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
+      mbar_arrive(&bars[S_KV_FULL + s]);
     }
     if (!ok && lane == 0) atomicCAS(p.status, 0, LF_ERR_WAIT_EMPTY);
   } else if (warp == 4) {
@@ -177,14 +164,14 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
       auto issue_s = [&](int j) {
         const int s = j % SM_STAGES, b = j & 1;
         const uint32_t kb = skv + s * SM_KV_BYTES;
-        // dims 0..383: Q from TMEM (8 columns per k-step); dims 384..575: Q from shared memory
+        // dims 0..255: Q from TMEM (8 columns per k-step); dims 256..575: Q from shared memory
 #pragma unroll 4
-        for (int kk = 0; kk < 24; ++kk) {
+        for (int kk = 0; kk < 4 * SM_QT_BOXES; ++kk) {
           const uint64_t db = make_smem_desc_sw128(kb + (kk >> 2) * SM_KBOX + (kk & 3) * 32, 16, 1024);
           tc_mma_f16_ts(t_s + b * SM_NB, t_q + kk * 8, db, idesc_s, kk > 0 ? 1u : 0u);
         }
 #pragma unroll 4
-        for (int kk = 24; kk < 36; ++kk) {
+        for (int kk = 4 * SM_QT_BOXES; kk < 36; ++kk) {
           const uint64_t da = make_smem_desc_sw128(sq + ((kk >> 2) - SM_QT_BOXES) * SM_QBOX + (kk & 3) * 32, 16, 1024);
           const uint64_t db = make_smem_desc_sw128(kb + (kk >> 2) * SM_KBOX + (kk & 3) * 32, 16, 1024);
           tc_mma_f16_ss(t_s + b * SM_NB, da, db, idesc_s, 1u);
@@ -193,11 +180,11 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
       };
       bool ok = mbar_wait(&bars[S_Q], 0, abort_flag);
       if (ok) ok = mbar_wait(&bars[S_QT], 0, abort_flag);
-      for (int j = 0; j < 2 && j < nb && ok; ++j) {  // scores of the first two blocks
-        ok = mbar_wait(&bars[S_KV_FULL + j], 0, abort_flag);
+      if (ok && nb > 0) {
+        ok = mbar_wait(&bars[S_KV_FULL + 0], 0, abort_flag);
         if (ok) {
           tc_fence_after_sync();
-          issue_s(j);
+          issue_s(0);
         }
       }
       for (int j = 0; j < nb && ok; ++j) {
@@ -205,21 +192,20 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
         ok = mbar_wait(&bars[S_P_FULL + b], (j >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
-        // O += P[j] V[j]: 32 gathered rows = 2 k-steps; B = this half's four 64-dim boxes read MN-major
+        // O += P[j] V[j]: 64 gathered rows = 4 k-steps; B = this half's four 64-dim boxes read MN-major
         const uint32_t vb = skv + s * SM_KV_BYTES + half * 4 * SM_KBOX;
 #pragma unroll
-        for (int kk = 0; kk < 2; ++kk) {
+        for (int kk = 0; kk < 4; ++kk) {
           const uint64_t db = make_smem_desc_sw128(vb + kk * 2048, SM_KBOX, 1024);
           tc_mma_f16_ts(t_o, t_s + b * SM_NB + kk * 8, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        tc_commit(&bars[S_KV_EMPTY + s]);
+        tc_commit(&bars[S_KV_EMPTY + s]);  // the producers refill this stage with block j + 2 ...
         tc_commit(&bars[S_O_DONE]);
-        if (j + 2 < nb) {  // scores two blocks ahead, into the buffer P[j] has just been read from
-          const int s2 = (j + 2) % SM_STAGES;
-          ok = mbar_wait(&bars[S_KV_FULL + s2], ((j + 2) / SM_STAGES) & 1, abort_flag);
+        if (j + 1 < nb) {  // ... while the scores of block j + 1 (other stage, other S buffer) run
+          ok = mbar_wait(&bars[S_KV_FULL + ((j + 1) % SM_STAGES)], ((j + 1) / SM_STAGES) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_s(j + 2);
+          issue_s(j + 1);
         }
       }
       if (!ok) atomicCAS(p.status, 0, LF_ERR_WAIT_FULL);
@@ -232,7 +218,7 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
     float m_ref = -INFINITY, l_sum = 0.f;
     bool ok = mbar_wait(&bars[S_Q], 0, abort_flag);
     if (ok) {
-      // move dims 0..383 of this head's Q row from the staged (swizzled) boxes into TMEM: two bf16 per column
+      // move dims 0..255 of this head's Q row from the staged (swizzled) boxes into TMEM: two bf16 per column
       const uint8_t* qst = smem + SM_KV0;
 #pragma unroll 1
       for (int b = 0; b < SM_QT_BOXES; ++b) {
@@ -259,17 +245,20 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
       if (ok) ok = mbar_wait(&bars[S_S_FULL + b], (j >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t live = ctl->live[s];
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(t_s + b * SM_NB + lane_off, r);
+      const uint32_t live0 = ctl->live[s][0], live1 = ctl->live[s][1];
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32b_x32(t_s + b * SM_NB + lane_off, r0);
+      tmem_ld_32x32b_x32(t_s + b * SM_NB + lane_off + 32, r1);
       tmem_ld_wait();
-      float mx = -INFINITY;
+      float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        if (!((live >> i) & 1u)) r[i] = 0xff800000u;  // empty slots (-1) are masked
-        mx = fmaxf(mx, __uint_as_float(r[i]));
+        if (!((live0 >> i) & 1u)) r0[i] = 0xff800000u;  // empty slots (-1) are masked
+        if (!((live1 >> i) & 1u)) r1[i] = 0xff800000u;
+        mx0 = fmaxf(mx0, __uint_as_float(r0[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(r1[i]));
       }
-      mx *= p.scale_log2;
+      const float mx = fmaxf(mx0, mx1) * p.scale_log2;
       float m_new = m_ref;
       if (mx > m_ref + 8.f || m_ref == -INFINITY) m_new = fmaxf(mx, m_ref);
       const bool rescale = (m_new != m_ref) && (j > 0);
@@ -292,15 +281,25 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
       l_sum *= alpha;
       m_ref = m_new;
       const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+      float la = 0.f, lb = 0.f;
       uint32_t pk[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float a = exp2f(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, neg_m));
-        const float b2 = exp2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, neg_m));
-        l_sum += a + b2;
+        const float a = exp2f(fmaf(__uint_as_float(r0[2 * i]), p.scale_log2, neg_m));
+        const float b2 = exp2f(fmaf(__uint_as_float(r0[2 * i + 1]), p.scale_log2, neg_m));
+        la += a; lb += b2;
         pk[i] = pack_bf16x2(a, b2);
       }
       tmem_st_32x32b_x16(t_s + b * SM_NB + lane_off, pk);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float a = exp2f(fmaf(__uint_as_float(r1[2 * i]), p.scale_log2, neg_m));
+        const float b2 = exp2f(fmaf(__uint_as_float(r1[2 * i + 1]), p.scale_log2, neg_m));
+        la += a; lb += b2;
+        pk[i] = pack_bf16x2(a, b2);
+      }
+      tmem_st_32x32b_x16(t_s + b * SM_NB + lane_off + 16, pk);
+      l_sum += la + lb;
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
