@@ -50,6 +50,8 @@ def parse():
     ap.add_argument("--tp", type=int, default=None)
     ap.add_argument("--ep", type=int, default=1)
     ap.add_argument("--moe-dispatcher", default="alltoall", choices=["peer", "alltoall"])
+    ap.add_argument("--overlap-moe-a2a", action="store_true",
+                    help="MoE side benchmark: 1F1B interleave of expert-parallel exchanges with compute")
     ap.add_argument("--peer-optimizer", action="store_true",
                     help="gradient reduce-scatter / parameter all-gather inside the optimizer kernels over peer memory")
     ap.add_argument("--attention", default="auto", choices=["auto", "native", "sdpa"])
@@ -179,7 +181,8 @@ def main():
     tc = TrainConfig(micro_batch_size=1, global_batch_size=gbs, seq_length=args.seq_len,
                      train_iters=10 ** 9, lr=3e-4, weight_decay=0.1, adam_beta2=0.95, clip_grad=1.0, bf16=True,
                      use_distributed_optimizer=True, overlap_grad_reduce=True,
-                     master_as_remainder=not args.fp32_master_copy, peer_optimizer=args.peer_optimizer)
+                     master_as_remainder=not args.fp32_master_copy, peer_optimizer=args.peer_optimizer,
+                     overlap_moe_expert_parallel_comm=args.overlap_moe_a2a)
     trainer = Trainer(cfg, tc, ParallelDims(tp=tp, ep=args.ep), device=dev)
     st = trainer.st
     host_iter = synthetic_batch_iterator(cfg.vocab_size, tc.seq_length, 1, dp_rank=st.dp_rank, dp_size=st.dp_size,

@@ -207,6 +207,7 @@ def build_configs(args, overrides: Optional[List[str]] = None) -> Tuple[Transfor
         fp8_policy_file=getattr(args, "fp8_dynamic_policy_path", None),
         chunkpipe_chunks=(max(1, args.seq_length // int(args.chunksize))
                           if getattr(args, "enable_chunkpipe", False) and getattr(args, "chunksize", None) else 0),
+        overlap_moe_expert_parallel_comm=bool(getattr(args, "overlap_moe_expert_parallel_comm", False)),
         rerun_mode=getattr(args, "rerun_mode", "disabled") or "disabled",
         error_injection_rate=int(getattr(args, "error_injection_rate", 0) or 0),
         error_injection_type=getattr(args, "error_injection_type", "transient_error"),

@@ -56,7 +56,6 @@ def validate(args, cfg, tc, dims) -> None:
 # rather than the training CLI today. Nothing is ignored silently: `unwired_flag_notes` lists what was requested.
 _LIBRARY_ONLY = {
     "enable_cuda_graph": "CUDA graphs: runtime.cuda_graphs.GraphedCallable / embodied.cuda_graph.MicrobatchGraphRunner",
-    "overlap_moe_expert_parallel_comm": "A2A overlap plan: runtime.a2a_overlap.interleave / OverlapExecutor",
 }
 
 

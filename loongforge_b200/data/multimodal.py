@@ -98,11 +98,6 @@ class VLMTaskEncoder:
                 "grid_thw": torch.tensor(grids, dtype=torch.long).view(-1, 3)}
 
 
-TASK_ENCODERS = {"qwen2_vl": VLMTaskEncoder, "qwen3_vl": VLMTaskEncoder, "internvl": VLMTaskEncoder,
-                 "llava_ov": VLMTaskEncoder, "ernie_vl": VLMTaskEncoder, "kimi_vl": VLMTaskEncoder,
-                 "minicpm_v": VLMTaskEncoder}
-
-
 def pad_to_multiple(n: int, tp: int = 1, cp: int = 1, sequence_parallel: bool = False, fp8: bool = False) -> int:
     """Sequence lengths must divide by 2*cp (load-balanced CP chunks), by tp under sequence parallelism and by 16 for
     FP8 GEMM rows."""
@@ -252,6 +247,9 @@ def vlm_batch_iterator(samples, encoder: VLMTaskEncoder, seq_len: int, *, merge_
 
     for raw in samples:
         enc = encoder.encode(raw)
-        enc["mrope"] = mrope_ids(enc["tokens"], enc["grid_thw"], encoder.img_id, merge_size)
+        if enc is None:
+            continue  # gated by the task encoder (over-long sample)
+        if "mrope" not in enc:  # family encoders (data/task_encoders.py) bring their own position ids
+            enc["mrope"] = mrope_ids(enc["tokens"], enc["grid_thw"], encoder.img_id, merge_size)
         yield from batches(packer.add(enc))
     yield from batches(packer.flush())

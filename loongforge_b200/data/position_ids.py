@@ -55,3 +55,80 @@ def mrope_ids(input_ids: torch.Tensor, image_grid_thw: Optional[torch.Tensor], i
         nxt = int(pos[:, i:i + n].max()) + 1
         i += n
     return pos.to(input_ids.device)
+
+
+def qwen2_5_vl_ids(input_ids: torch.Tensor, image_grid_thw: Optional[torch.Tensor], image_token_id: int,
+                   spatial_merge_size: int = 2, video_grid_thw: Optional[torch.Tensor] = None,
+                   video_token_id: Optional[int] = None, second_per_grid_ts: Optional[List[float]] = None,
+                   tokens_per_second: float = 2.0) -> torch.Tensor:
+    """Qwen2.5-VL: like `mrope_ids`, but the temporal index of video frame group g is
+    ``floor(g * second_per_grid_t * tokens_per_second)``: frames further apart in time sit further apart in the t stream
+    (reference: loongforge/train/get_position_idx_func.py:181-338)."""
+    pos = mrope_ids(input_ids, image_grid_thw, image_token_id, spatial_merge_size, video_grid_thw, video_token_id)
+    if video_grid_thw is None or video_token_id is None or not second_per_grid_ts:
+        return pos
+    ids = input_ids.tolist()
+    T, i, vi, shift = len(ids), 0, 0, 0
+    pos = pos.clone()
+    vg = video_grid_thw.tolist()
+    while i < T:
+        if ids[i] != video_token_id:
+            pos[:, i] += shift
+            i += 1
+            continue
+        t, h, w = vg[vi]
+        per = (h // spatial_merge_size) * (w // spatial_merge_size)
+        n = min(t * per, T - i)
+        base = int(pos[0, i]) + shift
+        sec = float(second_per_grid_ts[vi]) if vi < len(second_per_grid_ts) else 1.0
+        tt = (torch.arange(t, dtype=torch.float64) * sec * tokens_per_second).floor().long().repeat_interleave(per)[:n]
+        old_max = int(pos[:, i:i + n].max()) + shift
+        pos[1:, i:i + n] += shift
+        pos[0, i:i + n] = base + tt
+        shift += max(int(pos[:, i:i + n].max()) - old_max, 0)
+        vi += 1
+        i += n
+    return pos
+
+
+def qwen3_vl_ids(input_ids: torch.Tensor, image_grid_thw: Optional[torch.Tensor], image_token_id: int,
+                 spatial_merge_size: int = 2, video_grid_thw: Optional[torch.Tensor] = None,
+                 video_token_id: Optional[int] = None) -> torch.Tensor:
+    """Qwen3-VL / Qwen3.5: videos are written frame by frame with a text time stamp before each frame
+    (``<t1> <vision_start> frame <vision_end> <t2> ...``), so a video grid (t, h, w) is t grids (1, h, w) and time is
+    carried by the stamps, not by the t stream (reference: loongforge/train/get_position_idx_func.py:10-148)."""
+    if video_grid_thw is not None and video_grid_thw.numel():
+        v = torch.repeat_interleave(video_grid_thw, video_grid_thw[:, 0], dim=0).clone()
+        v[:, 0] = 1
+        video_grid_thw = v
+    return mrope_ids(input_ids, image_grid_thw, image_token_id, spatial_merge_size, video_grid_thw, video_token_id)
+
+
+def internvl_ids(token_types: torch.Tensor, vision_type: int = 1, language_type: int = 0) -> torch.Tensor:
+    """InternVL: `token_types` [T] marks vision tokens. The first and last token of every vision run (begin / end of
+    image) count as language; language tokens and the first inner vision token after language advance the position,
+    the other inner vision tokens share it (reference: loongforge/train/get_position_idx_func.py:151-178)."""
+    x = token_types.clone()
+    vis = x == vision_type
+    lang = x == language_type
+    edge = torch.zeros_like(vis)
+    edge[1:] |= vis[1:] & lang[:-1]
+    edge[0] |= vis[0]
+    edge[:-1] |= vis[:-1] & lang[1:]
+    edge[-1] |= vis[-1]
+    x[edge] = language_type
+    lang, vis = x == language_type, x == vision_type
+    step = torch.zeros_like(x, dtype=torch.long)
+    step[1:] = (lang[1:] | (vis[1:] & lang[:-1])).long()
+    return step.cumsum(0)
+
+
+POSITION_ID_FUNCS = {"text": text_position_ids, "packed": packed_position_ids, "qwen2_vl": mrope_ids,
+                     "qwen2_5_vl": qwen2_5_vl_ids, "qwen3_vl": qwen3_vl_ids, "internvl": internvl_ids}
+
+
+def get_position_id_func(name: str):
+    """Position-id function by the name the model configuration selects (YAML resolver ``${position_func:...}``)."""
+    if name not in POSITION_ID_FUNCS:
+        raise KeyError(f"unknown position-id function {name!r}; known: {sorted(POSITION_ID_FUNCS)}")
+    return POSITION_ID_FUNCS[name]

@@ -278,7 +278,10 @@ class AlltoAllDispatcher:
         self.tpe = rc.sum(0).tolist()
         return sorted_tokens, self.tpe
 
-    def combine(self, y):
+    def combine(self, y, sel_probs=None):
+        """`sel_probs`: the probabilities `dispatch` left in ``self.sel_probs`` (passed explicitly by callers that cut
+        the autograd graph between the two calls)."""
+        sel_probs = self.sel_probs if sel_probs is None else sel_probs
         if self.ep > 1:
             sizes_sorted = [self.chunk_sizes[i] for i in self.order]
             chunks = y.split(sizes_sorted, 0)
@@ -287,7 +290,7 @@ class AlltoAllDispatcher:
                 inv[i] = pos
             y = torch.cat([chunks[inv[i]] for i in range(len(self.order))], 0) if len(chunks) > 1 else y
             y = M.all_to_all(y, self.group, self.in_splits, self.out_splits)
-        y = y * self.sel_probs.to(y.dtype).unsqueeze(-1)
+        y = y * sel_probs.to(y.dtype).unsqueeze(-1)
         out = torch.zeros(self.T, y.shape[1], dtype=y.dtype, device=y.device)
         return out.index_add(0, self.token_idx, y)
 
@@ -330,57 +333,93 @@ class MoELayer(nn.Module):
             self.peer_dispatcher = PeerDispatcher(E, cfg.hidden_size, ep, st.ep_rank, st.group("ep") if ep > 1 else None,
                                                   cfg.moe_peer_capacity_factor)
 
-    def _forward_etp(self, x, probs, routing_map):
-        """Expert tensor parallelism: the ranks of an ETP group hold slices of every expert's FFN width. They first
-        share their tokens (all-gather), run the same dispatch, compute partial FC2 sums with their slices, and
-        reduce-scatter the combined output back to each rank's own tokens."""
-        g = ps.get_state(self.state_name).group("etp")
-        # each rank back-propagates only through ITS slices of the expert weights, so the gradients of the gathered
-        # tokens and probabilities are partial sums: reduce-scatter them in backward
-        xf = M.gather_from_sequence_parallel_region(x, g, True)
-        pf = M.gather_from_sequence_parallel_region(probs, g, True)
-        mf = M.gather_from_sequence_parallel_region(routing_map.to(torch.uint8), g, False).bool()
-        tokens, tpe = self.dispatcher.dispatch(xf, pf, mf)
-        out = self.dispatcher.combine(self.experts(tokens, tpe))
-        return M.reduce_scatter_to_sequence_parallel_region(out, g)
+    # The layer is five stages with explicit tensor interfaces: route (compute) -> dispatch_tokens (communication)
+    # -> run_experts (compute) -> combine_tokens (communication) -> finish (compute). ``forward`` runs them back to
+    # back; the all-to-all overlap schedule (runtime/a2a_overlap.py) runs the same five methods as separate autograd
+    # segments so that one micro-batch's exchange sits under another's compute (reference:
+    # loongforge/models/omni_models/model_chunk_schedule_plan.py:203-305, node split
+    # loongforge/models/omni_models/fine_grained_callables.py:704-1060).
 
-    def forward(self, x: torch.Tensor, seq_lens=None) -> torch.Tensor:
+    def route(self, x: torch.Tensor, seq_lens=None):
+        """-> (x_loc, probs, routing_map): the tokens this rank routes, their probabilities [T, E] and the map.
+        Experts are replicated over the TP ranks (or sliced over them, ETP) and their gradients are summed over those
+        ranks, so every rank must route a DIFFERENT part of the tokens. Sequence parallelism delivers shards already;
+        without it the layer shards its input here and gathers its output."""
         st = ps.get_state(self.state_name)
-        # Experts are replicated over the TP ranks (or sliced over them, ETP) and their gradients are summed over those
-        # ranks, so every rank must route a DIFFERENT part of the tokens. Sequence parallelism delivers shards already;
-        # without it the layer shards its input here and gathers its output.
-        local_shard = st.dims.tp > 1 and not self.cfg.sequence_parallel
-        x_full = x
-        if local_shard:
+        if st.dims.tp > 1 and not self.cfg.sequence_parallel:
             self.router.tokens_sharded_over_tp = True
             x = M.scatter_to_sequence_parallel_region(x, st.group("tp"))
         probs, routing_map = self.router(x, seq_lens)
+        return x, probs, routing_map
+
+    def _use_peer(self, x) -> bool:
+        return self.etp == 1 and self.peer_dispatcher is not None and x.is_cuda and x.dtype == torch.bfloat16
+
+    def dispatch_tokens(self, x_loc, probs, routing_map):
+        """-> (tokens sorted by local expert, aux, tokens_per_expert). `aux` are the probabilities the later stages
+        need: per received row with the peer dispatcher (applied on the expert side), per sent (token, expert) pair
+        with the all-to-all dispatcher (applied in the combine)."""
         if self.etp > 1:
-            out = self._forward_etp(x, probs, routing_map)
-        elif self.peer_dispatcher is not None and x.is_cuda and x.dtype == torch.bfloat16:
+            # Expert tensor parallelism: the ranks of an ETP group hold slices of every expert's FFN width. They first
+            # share their tokens (all-gather) and run the same dispatch. Each rank back-propagates only through ITS
+            # slices of the expert weights, so the gradients of the gathered tokens and probabilities are partial
+            # sums: reduce-scatter them in backward.
+            g = ps.get_state(self.state_name).group("etp")
+            x_loc = M.gather_from_sequence_parallel_region(x_loc, g, True)
+            probs = M.gather_from_sequence_parallel_region(probs, g, True)
+            routing_map = M.gather_from_sequence_parallel_region(routing_map.to(torch.uint8), g, False).bool()
+        if self._use_peer(x_loc):
             # indices of the k selected experts of every token (order within a token is irrelevant)
             topk_idx = routing_map.to(torch.float16).topk(self.cfg.moe_router_topk, dim=1).indices
-            tokens, tpe, row_probs = self.peer_dispatcher.dispatch(x, probs, topk_idx)
-            out = self.peer_dispatcher.combine(self.experts(tokens, tpe, row_probs))
-        else:
-            tokens, tpe = self.dispatcher.dispatch(x, probs, routing_map)
-            y = self.experts(tokens, tpe)
-            out = self.dispatcher.combine(y)
-        if local_shard:
-            out = M.gather_from_sequence_parallel_region(out, st.group("tp"), False)
+            tokens, tpe, row_probs = self.peer_dispatcher.dispatch(x_loc, probs, topk_idx)
+            return tokens, row_probs, tpe
+        tokens, tpe = self.dispatcher.dispatch(x_loc, probs, routing_map)
+        return tokens, self.dispatcher.sel_probs, tpe
+
+    def run_experts(self, tokens, aux, tpe, x_loc, x_full):
+        """-> (y, y_shared or None). The shared expert belongs to this compute stage: it only needs the layer input,
+        so in the overlap schedule it also covers the exchange of the routed tokens."""
+        y = self.experts(tokens, tpe, aux) if self._use_peer(x_loc) else self.experts(tokens, tpe)
+        ys = None
         if self.shared_experts is not None:
-            x_out = x_full  # the tokens that `out` holds on this rank
+            st = ps.get_state(self.state_name)
             if st.dims.tp > 1:
                 # shared expert is tensor parallel over the full token set of the TP group
                 g = st.group("tp")
-                xs = M.gather_from_sequence_parallel_region(x, g, False) if self.cfg.sequence_parallel else x_full
+                xs = M.gather_from_sequence_parallel_region(x_loc, g, False) if self.cfg.sequence_parallel else x_full
                 ys = self.shared_experts(xs)
                 if self.cfg.sequence_parallel:
-                    ys, x_out = M.scatter_to_sequence_parallel_region(ys, g), x
+                    ys = M.scatter_to_sequence_parallel_region(ys, g)
             else:
-                ys = self.shared_experts(x)
+                ys = self.shared_experts(x_loc)
+        return y, ys
+
+    def combine_tokens(self, y, aux, x_loc):
+        if self._use_peer(x_loc):
+            return self.peer_dispatcher.combine(y)
+        out = self.dispatcher.combine(y, aux)
+        if self.etp > 1:
+            # partial FC2 sums of the slices: reduce-scatter back to each rank's own tokens
+            out = M.reduce_scatter_to_sequence_parallel_region(out, ps.get_state(self.state_name).group("etp"))
+        return out
+
+    def finish(self, out, ys, x_loc, x_full):
+        st = ps.get_state(self.state_name)
+        local_shard = st.dims.tp > 1 and not self.cfg.sequence_parallel
+        if local_shard:
+            out = M.gather_from_sequence_parallel_region(out, st.group("tp"), False)
+        if ys is not None:
+            # the tokens that `out` holds on this rank
+            x_out = x_loc if (st.dims.tp > 1 and self.cfg.sequence_parallel) or st.dims.tp == 1 else x_full
             gate_w = getattr(self.shared_experts, "gate_weight", None)
             if gate_w is not None:
                 ys = ys * torch.sigmoid(torch.nn.functional.linear(x_out, gate_w).float()).to(ys.dtype)
             out = out + ys
         return out
+
+    def forward(self, x: torch.Tensor, seq_lens=None) -> torch.Tensor:
+        x_loc, probs, routing_map = self.route(x, seq_lens)
+        tokens, aux, tpe = self.dispatch_tokens(x_loc, probs, routing_map)
+        y, ys = self.run_experts(tokens, aux, tpe, x_loc, x)
+        out = self.combine_tokens(y, aux, x_loc)
+        return self.finish(out, ys, x_loc, x)

@@ -244,6 +244,7 @@ class DistributedOptimizer:
         Returns (update_successful, grad_norm, num_zeros)."""
         for m in self.models:
             m.finish_grad_sync()
+        self.wait_param_gather()  # a bucket no forward waited for (unused parameters) must land before it is rewritten
         self._peer_reduce_grads()
         for hook in self.post_sync_hooks:
             hook()

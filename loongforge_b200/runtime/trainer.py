@@ -79,6 +79,7 @@ class TrainConfig:
     check_weight_hash_interval: int = 0  # > 0: compare parameter checksums across data-parallel replicas every N steps
     dp_balance: bool = False  # trade whole micro-batches between DP ranks by modelled cost (data/dp_balance.py)
     chunkpipe_chunks: int = 0  # > 1: every sequence runs as that many chunks (runtime/chunkpipe.py)
+    overlap_moe_expert_parallel_comm: bool = False  # 1F1B interleave of MoE exchanges and compute (runtime/a2a_overlap.py)
     use_fsdp: bool = False  # FSDP2 units instead of DDP + distributed optimizer (runtime/fsdp_trainer.py)
     fsdp_sharding_strategy: str = "optim_grads_params"  # or optim_grads
     ddp_bucket_size: Optional[int] = None
@@ -277,9 +278,8 @@ class Trainer:
             out[k] = v.to(self.device, non_blocking=True) if isinstance(v, torch.Tensor) else v
         return out
 
-    def _default_forward_step(self, data_iterator, model):
-        t = self.tcfg
-        b = self.get_batch(data_iterator)
+    def _microbatch_inputs(self, b: Dict[str, torch.Tensor]):
+        """Batch dict -> (keyword arguments of ``GPTModel.forward``, loss function of the per-token losses)."""
         cp = self.st.dims.cp
         extra = {}
         if cp > 1:
@@ -309,13 +309,49 @@ class Trainer:
         # each context-parallel rank sums its own tokens; gradients are averaged over dp x cp, so the
         # factor cp turns that average into (sum over cp, mean over dp)
         scale = float(cp) / (max(n_valid, 1) * nmb)
-        out = model(tokens, pos, labels=labels, loss_mask=mask, packed=packed, loss_scale=scale, **extra)
 
         def loss_func(losses):
             loss = (losses * mask.float()).sum() * scale
             return loss, {"lm loss": loss.detach() * nmb, "num_tokens": n_valid}
 
-        return out, loss_func
+        kw = dict(tokens=tokens, position_ids=pos, labels=labels, loss_mask=mask, packed=packed, loss_scale=scale,
+                  **extra)
+        return kw, loss_func
+
+    def _default_forward_step(self, data_iterator, model):
+        kw, loss_func = self._microbatch_inputs(self.get_batch(data_iterator))
+        tokens, pos = kw.pop("tokens"), kw.pop("position_ids")
+        return model(tokens, pos, **kw), loss_func
+
+    def _a2a_overlap_microbatches(self, data_iterator) -> List[dict]:
+        """The step's micro-batches under the MoE all-to-all overlap schedule (``runtime/a2a_overlap.py``): forward of
+        micro-batch i is issued node by node between the backward nodes of micro-batch i - 1, expert-parallel
+        exchanges on a side stream."""
+        from .a2a_overlap import OverlapExecutor, gpt_overlapped_forward_backward
+
+        if self.st.dims.pp > 1 or len(self.models) != 1:
+            raise ValueError("--overlap-moe-expert-parallel-comm needs pipeline size 1")
+        if self.forward_step != self._default_forward_step:
+            raise ValueError("--overlap-moe-expert-parallel-comm covers the language-model forward step")
+        model = self.models[0]
+        nmb = self.mb_calc.num_microbatches
+        if not hasattr(self, "_a2a_executor"):
+            self._a2a_executor = OverlapExecutor()
+        self._a2a_executor.trace.clear()
+        ctx = model.no_sync()
+        ctx.__enter__()
+        state = {"open": True}
+
+        def leave_no_sync():
+            if state["open"]:
+                state["open"] = False
+                ctx.__exit__(None, None, None)
+
+        try:
+            batches = (self._microbatch_inputs(self.get_batch(data_iterator)) for _ in range(nmb))
+            return gpt_overlapped_forward_backward(model.module, batches, leave_no_sync, self._a2a_executor)
+        finally:
+            leave_no_sync()
 
     # ------------------------------------------------------------------ step
     def train_step(self, data_iterator) -> Dict[str, float]:
@@ -337,6 +373,8 @@ class Trainer:
         def forward_backward(it):
             if t.chunkpipe_chunks and t.chunkpipe_chunks > 1:
                 return self._chunkpipe_microbatches(it)
+            if t.overlap_moe_expert_parallel_comm:
+                return self._a2a_overlap_microbatches(it)
             return fb(forward_step_func=self.forward_step, data_iterator=it,
                       model=self.models if len(self.models) > 1 else self.models[0],
                       num_microbatches=self.mb_calc.num_microbatches,
@@ -596,25 +634,29 @@ class Trainer:
         post-sync hook of the optimizer, i.e. after the data-parallel reduction. With the sharded optimizer only this
         rank's shard of each gradient is valid by then; TP peers hold the same shard, so summing whole tensors is
         still right where it matters."""
-        st = self.st
-        if st.dims.tp == 1:
-            return
-        sp = self.mcfg.sequence_parallel
-        grads = []
-        for m in self.models:
-            for p in m.module.parameters():
-                if p.requires_grad and ((sp and getattr(p, "sequence_parallel", False))
-                                        or getattr(p, "tp_partial_grad", False)):
-                    grads.append(p.main_grad)
-        if not grads:
-            return
-        flat = torch.cat([g.reshape(-1) for g in grads])
-        dist.all_reduce(flat, group=st.group("tp"))
-        off = 0
-        for g in grads:
-            n = g.numel()
-            g.copy_(flat[off:off + n].view_as(g))
-            off += n
+        self.timers("partial-grads-all-reduce", 2).start()
+        try:
+            st = self.st
+            if st.dims.tp == 1:
+                return
+            sp = self.mcfg.sequence_parallel
+            grads = []
+            for m in self.models:
+                for p in m.module.parameters():
+                    if p.requires_grad and ((sp and getattr(p, "sequence_parallel", False))
+                                            or getattr(p, "tp_partial_grad", False)):
+                        grads.append(p.main_grad)
+            if not grads:
+                return
+            flat = torch.cat([g.reshape(-1) for g in grads])
+            dist.all_reduce(flat, group=st.group("tp"))
+            off = 0
+            for g in grads:
+                n = g.numel()
+                g.copy_(flat[off:off + n].view_as(g))
+                off += n
+        finally:
+            self.timers("partial-grads-all-reduce", 2).stop()
 
     # ------------------------------------------------------------------ logging
     def flops_per_step(self) -> float:
@@ -702,6 +744,8 @@ class Trainer:
                 if t.save:
                     self.save_checkpoint(t.save)
                 break
+        if hasattr(self.optimizer, "wait_param_gather"):
+            self.optimizer.wait_param_gather()  # whoever reads the parameters next (export, evaluation code) sees them whole
         for h in getattr(self, "hooks", ()):
             h.on_train_end(self)
         if getattr(self, "_pending_save", None) is not None:

@@ -130,7 +130,21 @@ class VLMTrainer(Trainer):
                                       merge_size=v.spatial_merge_size,
                                       **{k: getattr(args, k) for k in ("min_pixels", "max_pixels")
                                          if getattr(args, k, None) is not None})
-            enc = VLMTaskEncoder(lambda text: tok.tokenize(text), self.image_token_id, vision, eos_id=tok.eod)
+            # the family of the vision tower decides how an image becomes tokens (data/task_encoders.py)
+            from ..data.task_encoders import TASK_ENCODERS, SpecialTokens, build_task_encoder
+            if self.vision_family in TASK_ENCODERS:
+                def special(name):
+                    try:
+                        ids = tok.tokenize(name)
+                    except Exception:  # noqa: BLE001
+                        return None
+                    return ids[0] if len(ids) == 1 else None
+                enc = build_task_encoder(self.vision_family, lambda text: tok.tokenize(text),
+                                         SpecialTokens(image=self.image_token_id, vision_start=special("<|vision_start|>"),
+                                                       vision_end=special("<|vision_end|>"), eos=tok.eod),
+                                         vision, max_length=self.tcfg.seq_length)
+            else:
+                enc = VLMTaskEncoder(lambda text: tok.tokenize(text), self.image_token_id, vision, eos_id=tok.eod)
             samples = webdataset_samples(paths[-1], dp_rank=st.dp_rank, dp_size=st.dp_size, seed=self.tcfg.seed,
                                          start_sample=self.consumed_samples // max(st.dp_size, 1))
             return vlm_batch_iterator(samples, enc, self.tcfg.seq_length, merge_size=v.spatial_merge_size,

@@ -42,13 +42,16 @@ def _worker(rank, world, port, q):
             tr = Trainer(cfg, tc, device=torch.device("cuda", rank))
             it = synthetic_batch_iterator(2048, 256, 1, dp_rank=tr.st.dp_rank, dp_size=tr.st.dp_size, seed=5)
             losses = [tr.train_step(it)["lm loss"] for _ in range(4)]
+            tr.optimizer.wait_param_gather()  # parameters are read below, outside a forward pass
+            torch.cuda.synchronize()
             _ext.check_status()
             return losses, torch.cat([p.detach().float().reshape(-1) for p in tr.models[0].parameters()])
 
         la, pa = run(False)
         lb, pb = run(True)
         lc, pc = run(False, overlap_gather=True)  # parameter all-gathers queued behind the step, awaited per layer
-        assert lc == la and torch.equal(pa, pc), "overlapped parameter gather must not change a single bit"
+        assert lc == la, f"overlapped parameter gather changed the losses: {la} vs {lc}"
+        assert torch.equal(pa, pc), "overlapped parameter gather must not change a single bit of the parameters"
         q.put((rank, "ok", (la, lb, float((pa - pb).abs().max()))))
     except Exception:  # noqa: BLE001
         import traceback

@@ -1,0 +1,115 @@
+"""Family task encoders: token counts per medium, label masking, position ids, packing compatibility."""
+import numpy as np
+import pytest
+import torch
+
+from loongforge_b200.data import position_ids as P
+from loongforge_b200.data import task_encoders as TE
+from loongforge_b200.data.multimodal import OnlinePacker, VisionPreprocess
+
+IMG, VID, VS, VE, EOS = 900, 901, 902, 903, 2
+
+
+def _tok(text):
+    return [10 + (ord(c) % 50) for c in text]
+
+
+def _img(h, w, seed=0):
+    return np.random.RandomState(seed).randint(0, 255, (h, w, 3), dtype=np.uint8)
+
+
+def _sp(**kw):
+    return TE.SpecialTokens(image=IMG, video=VID, vision_start=VS, vision_end=VE, eos=EOS, **kw)
+
+
+def _vision():
+    return VisionPreprocess(patch_size=14, temporal_patch_size=2, merge_size=2, min_pixels=28 * 28, max_pixels=28 * 28 * 64)
+
+
+CHAT = {"images": [_img(56, 84)], "conversation": [{"role": "user", "content": "look <image> what?"},
+                                                  {"role": "assistant", "content": "a cat"}]}
+
+
+def test_qwen_encoder_counts_masks_and_positions():
+    enc = TE.build_task_encoder("qwen2_vl", _tok, _sp(), _vision())
+    out = enc.encode(CHAT)
+    gh, gw = out["grid_thw"][0, 1:].tolist()
+    n_img = (gh // 2) * (gw // 2)
+    ids = out["tokens"].tolist()
+    assert ids.count(IMG) == n_img and out["pixels"].shape == (gh * gw, 3 * 2 * 14 * 14)
+    i0 = ids.index(VS)
+    assert ids[i0 + 1] == IMG and ids[i0 + n_img + 1] == VE
+    # loss only on the assistant turn (its text + eos), shifted by one; never on placeholders
+    n_ans = len(_tok("a cat")) + 1
+    assert int(out["loss_mask"].sum()) == n_ans
+    assert out["loss_mask"][-n_ans - 1:-1].all() and out["loss_mask"][-1] == 0
+    assert out["mrope"].shape == (3, len(ids))
+    assert torch.equal(out["mrope"], P.mrope_ids(out["tokens"], out["grid_thw"], IMG, 2))
+    # the three kinds of raw samples normalise to the same walker
+    cap = enc.encode({"image": _img(56, 56), "caption": "a dog"})
+    vqa = enc.encode({"image": _img(56, 56), "context": "what is it?", "answer": "a dog"})
+    assert cap["tokens"].tolist().count(IMG) == vqa["tokens"].tolist().count(IMG) == 4
+
+
+def test_video_encoding_families():
+    frames = [_img(56, 56, s) for s in range(3)]  # padded to 4 frames = 2 temporal groups
+    sample = {"videos": [frames], "conversation": [{"role": "user", "content": "<video> describe"},
+                                                   {"role": "assistant", "content": "ok"}]}
+    q2 = TE.build_task_encoder("qwen2_5_vl", _tok, _sp(), _vision(), fps=1.0, tokens_per_second=2.0).encode(sample)
+    assert q2["video_grid_thw"].tolist() == [[2, 4, 4]] and q2["tokens"].tolist().count(VID) == 2 * 2 * 2
+    assert q2["video_pixels"].shape == (2 * 16, 3 * 2 * 14 * 14)
+    # second frame group sits second_per_grid_t * tokens_per_second = 2 * 2 = 4 steps later in the t stream
+    t_pos = q2["mrope"][0][q2["tokens"] == VID]
+    assert (t_pos[4:] - t_pos[:4]).unique().tolist() == [4]
+    q3 = TE.build_task_encoder("qwen3_vl", _tok, _sp(), _vision(), fps=2.0).encode(sample)
+    ids = q3["tokens"].tolist()
+    assert ids.count(VID) == 8 and ids.count(VS) == 2  # one wrapped block per frame group, time stamps between
+    kimi = TE.build_task_encoder("kimi_vl", _tok, _sp(), _vision()).encode(sample)
+    assert kimi["tokens"].tolist().count(VID) == 2 * 2  # time pooled away
+    mini = TE.build_task_encoder("minicpm_v", _tok, _sp(), _vision()).encode(sample)
+    assert mini["tokens"].tolist().count(VID) == 2 * 1 * 1  # (4 / (2 * 2))^2 per group
+
+
+def test_internvl_tiles_and_positions():
+    enc = TE.build_task_encoder("internvl", _tok, _sp(), max_tiles=6, tokens_per_tile=16)
+    out = enc.encode({"images": [_img(300, 900)], "conversation": [{"role": "user", "content": "<image> hi"},
+                                                                   {"role": "assistant", "content": "yo"}]})
+    n_tiles = out["pixel_tiles"].shape[0]
+    assert n_tiles == 3 + 1 and out["pixel_tiles"].shape[1:] == (3, 448, 448)  # 3 x 1 grid + thumbnail
+    assert out["tokens"].tolist().count(IMG) == n_tiles * 16
+    pos = out["mrope"][0]
+    inner = (out["tokens"] == IMG).nonzero().flatten()
+    assert pos[inner[1]] == pos[inner[-1]]  # inner vision tokens share a position
+    assert pos[-1] == pos.max() and (pos[1:] >= pos[:-1]).all()
+
+
+def test_ernie_types_llava_wrappers_and_overlong_gating():
+    ern = TE.build_task_encoder("ernie_vl", _tok, _sp(), _vision()).encode(CHAT)
+    assert torch.equal(ern["token_type"], (ern["tokens"] == IMG).long())
+    img_pos = ern["mrope"][:, ern["tokens"] == IMG]
+    assert img_pos[0].unique().numel() == 1  # an image is one time step
+    lla = TE.build_task_encoder("llava_ov", _tok, _sp(), _vision()).encode(CHAT)
+    assert VS not in lla["tokens"].tolist()
+    assert TE.build_task_encoder("qwen2_vl", _tok, _sp(), _vision(), max_length=8).encode(CHAT) is None
+    long = {"images": [], "conversation": [{"role": "user", "content": "x" * 40}, {"role": "assistant", "content": "y" * 40}]}
+    cut = TE.build_task_encoder("kimi_vl", _tok, _sp(), _vision(), max_length=50).encode(long)
+    assert cut["tokens"].numel() == 50
+    with pytest.raises(ValueError):
+        TE.build_task_encoder("qwen2_vl", _tok, _sp(), _vision()).encode({"images": [], "conversation": CHAT["conversation"]})
+
+
+def test_encoded_samples_pack():
+    enc = TE.build_task_encoder("qwen3_vl", _tok, _sp(), _vision())
+    packer = OnlinePacker(256, buffer_size=4, pad_to_seq_len=True)
+    packs = []
+    for s in range(5):
+        packs += packer.add(enc.encode({"image": _img(56, 56 + 28 * (s % 2), s), "caption": "c" * (5 + s)}))
+    packs += packer.flush()
+    assert packs and all(p["tokens"].numel() == 256 and p["position_ids"].shape == (3, 256) for p in packs)
+    assert sum(p["grid_thw"].shape[0] for p in packs) == 5
+
+
+def test_position_id_registry():
+    assert P.get_position_id_func("qwen3_vl") is P.qwen3_vl_ids
+    with pytest.raises(KeyError):
+        P.get_position_id_func("nope")
