@@ -1,8 +1,11 @@
 """Chat templates for supervised fine-tuning: turn a list of {role, content} messages into token
 ids with a loss mask that covers assistant replies only (the reference's template registry,
-loongforge/data/chat_template.py, with 18 Jinja templates). Templates here are declarative:
-a prefix/suffix per role plus a system default, which covers the ChatML (Qwen), Llama-3,
-Llama-2, DeepSeek, InternLM2, Mistral and plain "alpaca" families."""
+loongforge/data/chat_template.py, with 18 Jinja templates). Two kinds of templates live here:
+declarative ones (a prefix/suffix per role plus a system default: ChatML, Llama-3, Llama-2, DeepSeek,
+InternLM2, Mistral, "alpaca"), and Jinja templates under ``data/chat_templates/*.jinja`` (tool calls, reasoning
+blocks, multimodal content parts) in which ``{% generation %} ... {% endgeneration %}`` blocks mark the spans the
+model is trained on; `JinjaChatTemplate` turns those marks into the loss mask. ``--chat-template`` takes the name of
+either kind or the path of a ``.jinja`` file."""
 from __future__ import annotations
 
 import dataclasses
@@ -70,10 +73,88 @@ register_template(ChatTemplate("alpaca", ("### Instruction:\n", "\n\n"), ("### R
 register_template(ChatTemplate("empty", ("", ""), ("", "")))
 
 
-def get_template(name: str) -> ChatTemplate:
-    if name not in _TEMPLATES:
-        raise KeyError(f"unknown chat template {name!r}; known: {sorted(_TEMPLATES)}")
-    return _TEMPLATES[name]
+_GEN_OPEN, _GEN_CLOSE = "\x00<gen>\x00", "\x00</gen>\x00"
+
+
+def _jinja_env(search_dir: str):
+    import jinja2
+    from jinja2 import nodes
+    from jinja2.ext import Extension
+
+    class Generation(Extension):
+        """``{% generation %}body{% endgeneration %}``: the body is emitted between two sentinel strings."""
+        tags = {"generation"}
+
+        def parse(self, parser):
+            lineno = next(parser.stream).lineno
+            body = parser.parse_statements(["name:endgeneration"], drop_needle=True)
+            return nodes.CallBlock(self.call_method("_mark"), [], [], body).set_lineno(lineno)
+
+        def _mark(self, caller):
+            return _GEN_OPEN + caller() + _GEN_CLOSE
+
+    import json
+    env = jinja2.Environment(loader=jinja2.FileSystemLoader(search_dir), extensions=[Generation],
+                             trim_blocks=True, lstrip_blocks=True, keep_trailing_newline=False)
+    env.filters["tojson"] = lambda v, **kw: json.dumps(v, ensure_ascii=False, **kw)
+    return env
+
+
+class JinjaChatTemplate:
+    """A ``.jinja`` chat template with generation blocks. ``render`` returns the same ``[(text, is_target)]`` segments
+    as the declarative templates: text inside a generation block is a target."""
+
+    def __init__(self, path: str):
+        import os
+        self.path = path
+        self.name = os.path.splitext(os.path.basename(path))[0]
+        self._tpl = _jinja_env(os.path.dirname(os.path.abspath(path))).get_template(os.path.basename(path))
+
+    def render(self, messages: Sequence[Dict], tools: Optional[List[Dict]] = None,
+               add_generation_prompt: bool = False, **kw) -> List[Tuple[str, bool]]:
+        text = self._tpl.render(messages=list(messages), tools=tools, add_generation_prompt=add_generation_prompt, **kw)
+        segs: List[Tuple[str, bool]] = []
+        rest, inside = text, False
+        while rest:
+            mark = _GEN_CLOSE if inside else _GEN_OPEN
+            i = rest.find(mark)
+            if i < 0:
+                if inside:
+                    raise ValueError(f"template {self.name}: generation block not closed")
+                segs.append((rest, False))
+                break
+            if i:
+                segs.append((rest[:i], inside))
+            rest = rest[i + len(mark):]
+            inside = not inside
+        return segs
+
+
+def jinja_template_dir() -> str:
+    import os
+    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "chat_templates")
+
+
+def list_templates() -> List[str]:
+    import os
+    jin = [f[:-6] for f in os.listdir(jinja_template_dir()) if f.endswith(".jinja") and not f.startswith("_")]
+    return sorted(_TEMPLATES) + sorted(jin)
+
+
+_JINJA_CACHE: Dict[str, JinjaChatTemplate] = {}
+
+
+def get_template(name: str):
+    """Declarative template by name, Jinja template by file stem (``qwen3_hf_training``) or by path."""
+    import os
+    if name in _TEMPLATES:
+        return _TEMPLATES[name]
+    path = name if name.endswith(".jinja") and os.path.isfile(name) else os.path.join(jinja_template_dir(), name + ".jinja")
+    if os.path.isfile(path):
+        if path not in _JINJA_CACHE:
+            _JINJA_CACHE[path] = JinjaChatTemplate(path)
+        return _JINJA_CACHE[path]
+    raise KeyError(f"unknown chat template {name!r}; known: {list_templates()}")
 
 
 def to_messages(example: Dict, fmt: str = "auto") -> List[Dict[str, str]]:
@@ -82,7 +163,8 @@ def to_messages(example: Dict, fmt: str = "auto") -> List[Dict[str, str]]:
     if fmt == "auto":
         fmt = "openai" if "messages" in example else "sharegpt" if "conversations" in example else "alpaca"
     if fmt == "openai":
-        return [{"role": m["role"], "content": m["content"]} for m in example["messages"]]
+        # tool calls, reasoning and multimodal content parts travel with the message (the Jinja templates read them)
+        return [dict(m) for m in example["messages"]]
     if fmt == "sharegpt":
         role = {"human": "user", "gpt": "assistant", "system": "system", "user": "user", "assistant": "assistant"}
         return [{"role": role[c["from"]], "content": c["value"]} for c in example["conversations"]]
@@ -97,11 +179,15 @@ def to_messages(example: Dict, fmt: str = "auto") -> List[Dict[str, str]]:
     return msgs
 
 
-def encode_chat(tokenizer, messages, template: str = "chatml", train_on_prompt: bool = False, max_len: Optional[int] = None):
-    """-> (input_ids, labels) with labels = -100 on non-target tokens (before the causal shift)."""
+def encode_chat(tokenizer, messages, template: str = "chatml", train_on_prompt: bool = False, max_len: Optional[int] = None,
+                tools: Optional[List[Dict]] = None):
+    """-> (input_ids, labels) with labels = -100 on non-target tokens (before the causal shift). Segments are tokenised
+    one by one, so the mask boundary is exact whatever the tokenizer merges inside a segment."""
     ids: List[int] = []
     labels: List[int] = []
-    for text, tgt in get_template(template).render(messages):
+    tpl = get_template(template)
+    segs = tpl.render(messages, tools=tools) if isinstance(tpl, JinjaChatTemplate) else tpl.render(messages)
+    for text, tgt in segs:
         t = tokenizer.tokenize(text)
         ids.extend(t)
         labels.extend(t if (tgt or train_on_prompt) else [-100] * len(t))

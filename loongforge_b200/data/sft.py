@@ -45,8 +45,9 @@ class SFTDataset:
         return len(self.records)
 
     def __getitem__(self, i):
-        return encode_chat(self.tokenizer, to_messages(self.records[i], self.fmt), self.template,
-                           self.train_on_prompt, self.max_len)
+        rec = self.records[i]
+        return encode_chat(self.tokenizer, to_messages(rec, self.fmt), self.template, self.train_on_prompt,
+                           self.max_len, tools=rec.get("tools"))
 
 
 def sft_batch_iterator(ds: SFTDataset, seq_length: int, *, packing: bool = True, dp_rank: int = 0, dp_size: int = 1,

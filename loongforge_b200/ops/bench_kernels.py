@@ -3,6 +3,7 @@
     python -m loongforge_b200.ops.bench_kernels gemm [--m 8192 --n 4096 --k 4096] [--iters 20]
     python -m loongforge_b200.ops.bench_kernels attention [--t 8192 --groups 8 --rep 4]
     python -m loongforge_b200.ops.bench_kernels norm [--t 8192 --h 4096]
+    python -m loongforge_b200.ops.bench_kernels elementwise [--t 8192 --h 4096]   (RoPE, SwiGLU, linear + CE, AdamW)
     python -m loongforge_b200.ops.bench_kernels dsa [--t 4096 --skv 8192 --topk 2048 --impl ours|torch|reference]
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29511 \
         -m loongforge_b200.ops.bench_kernels tp [--t 8192]     (fused TP GEMMs against NCCL + GEMM, Llama-3-8B shapes)
@@ -180,7 +181,7 @@ def tp_bench(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "norm", "grouped", "router", "fp8", "tp", "dsa"])
+    ap.add_argument("what", choices=["gemm", "attention", "norm", "grouped", "router", "fp8", "tp", "dsa", "elementwise"])
     ap.add_argument("--skv", type=int, default=8192)
     ap.add_argument("--impl", default="ours", choices=["ours", "torch", "reference"])
     ap.add_argument("--experts", type=int, default=16)
@@ -271,6 +272,54 @@ def main():
             ms = _time(f, a.iters)
             out.update(ms=ms, gbytes_per_s=a.t * a.experts * (4 + 4 + 4 + 1) / ms / 1e6)
         out.update(t=a.t, experts=a.experts, topk=a.topk)
+    elif a.what == "elementwise":
+        # memory-bound ops of one Llama-3-8B layer / step at `t` tokens: achieved bytes per second against the copy peak
+        T, H, F, V = a.t, a.h, 14336, 32064
+        qkv = torch.randn(T, 48 * 128, device=dev).bfloat16()  # packed QKV: 8 groups of (4 q + k + v) heads
+        freqs = OF.rope_freqs(torch.arange(T, device=dev), 128, 500000.0)
+        hf = torch.randn(T, 2 * F, device=dev).bfloat16().requires_grad_()
+        gf = torch.randn(T, F, device=dev).bfloat16()
+        hid = torch.randn(T, H, device=dev).bfloat16().requires_grad_()
+        wv = (torch.randn(V, H, device=dev) * 0.02).bfloat16().requires_grad_()
+        labels = torch.randint(0, V, (T,), device=dev)
+        mask = torch.ones(T, device=dev)
+        n = 64 * 1024 * 1024  # one optimizer shard of 64 Mi parameters
+        w16, lo = torch.randn(n, device=dev).bfloat16(), torch.zeros(n, dtype=torch.int16, device=dev)
+        grad, m1, m2 = torch.randn(n, device=dev) * 1e-3, torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+
+        def f_rope():
+            OF.rope(qkv, freqs, group=6, rope_in_group=5, inplace=True, head_dim=128)
+
+        def f_swiglu():
+            y = OF.swiglu(hf)
+            y.backward(gf)
+            hf.grad = None
+
+        def f_ce():
+            los = OF.linear_cross_entropy(hid, wv, labels, mask)
+            ((los * mask).sum() / T).backward()
+            hid.grad = None
+            wv.grad = None
+
+        def f_adam():
+            OF.adam_step_remainder(w16, lo, grad, m1, m2, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
+                                   step=3)
+
+        fns = {"rope": (f_rope, T * 48 * 128 * 2 * 2 * 5 / 6), "swiglu_fwd_bwd": (f_swiglu, T * F * 2 * (3 + 5)),
+               "adamw_remainder": (f_adam, n * (2 + 2 + 4 + 4 + 4) * 1.0 + n * (2 + 2 + 4 + 4))}
+        if a.once:
+            for f, _ in fns.values():
+                f()
+            f_ce()
+        else:
+            for k_, (f, nbytes) in fns.items():
+                ms = _time(f, a.iters)
+                out[k_ + "_ms"] = ms
+                out[k_ + "_gbytes_per_s"] = nbytes / ms / 1e6
+            ms = _time(f_ce, max(2, a.iters // 4), warm=2)
+            out["linear_ce_fwd_bwd_ms"] = ms
+            out["linear_ce_tflops"] = 3 * 2.0 * T * H * V / ms / 1e9  # logits, dgrad, wgrad
+        out.update(t=T, h=H, ffn=F, vocab=V, adam_params=n)
     elif a.what == "fp8":
         from . import quant as Q
         Q.enable_native(True)
