@@ -50,6 +50,12 @@ def parse():
     ap.add_argument("--tp", type=int, default=None)
     ap.add_argument("--ep", type=int, default=1)
     ap.add_argument("--moe-dispatcher", default="alltoall", choices=["peer", "alltoall"])
+    ap.add_argument("--pp", type=int, default=1, help="side benchmark: pipeline-parallel size")
+    ap.add_argument("--images-per-sample", type=int, default=4, help="vision-language side benchmark")
+    ap.add_argument("--experts", type=int, default=None,
+                    help="side benchmark: number of routed experts (e.g. the 32 a rank holds of DeepSeek's 256 at EP8)")
+    ap.add_argument("--cp", type=int, default=1, help="side benchmark: context-parallel size")
+    ap.add_argument("--no-fp8", action="store_true", help="side benchmark: run a preset that names fp8 in bf16")
     ap.add_argument("--overlap-moe-a2a", action="store_true",
                     help="MoE side benchmark: 1F1B interleave of expert-parallel exchanges with compute")
     ap.add_argument("--peer-optimizer", action="store_true",
@@ -158,12 +164,25 @@ def main():
 
     flagship = args.model == "llama3-8b"
     tp = args.tp if args.tp is not None else (2 if world >= 2 and flagship else 1)
-    dp = world // tp
-    cfg = get_model_config(args.model)
-    if flagship or args.layers != 32:
+    dp = world // (tp * args.cp * args.pp)
+    vlm = args.model in ("qwen2.5-vl-7b", "qwen2_5_vl_7b")
+    if vlm:
+        # Qwen2.5-VL-7B: Qwen2.5-7B language model with multimodal rotary positions + the 32-layer window-attention ViT
+        cfg = get_model_config("qwen2.5-7b", position_embedding_type="mrope", mrope_section=[16, 24, 24])
+    else:
+        cfg = get_model_config(args.model)
+    if vlm:
+        pass
+    elif flagship or args.layers != 32:
         cfg.num_layers = args.layers
     if cfg.num_moe_experts:
         cfg.moe_token_dispatcher_type = args.moe_dispatcher
+        if args.experts:
+            cfg.num_moe_experts = args.experts
+            if cfg.moe_router_num_groups and args.experts % cfg.moe_router_num_groups:
+                cfg.moe_router_num_groups = cfg.moe_router_group_topk = None
+    if args.no_fp8:
+        cfg.fp8 = None
     cfg.sequence_parallel = tp > 1
     cfg.tp_comm_overlap = tp > 1 and not args.no_tp_overlap
     # One GPU holds all 8 B parameters with exact fp32 master weights (bf16 + int16 remainder), fp32
@@ -183,10 +202,19 @@ def main():
                      use_distributed_optimizer=True, overlap_grad_reduce=True,
                      master_as_remainder=not args.fp32_master_copy, peer_optimizer=args.peer_optimizer,
                      overlap_moe_expert_parallel_comm=args.overlap_moe_a2a)
-    trainer = Trainer(cfg, tc, ParallelDims(tp=tp, ep=args.ep), device=dev)
-    st = trainer.st
-    host_iter = synthetic_batch_iterator(cfg.vocab_size, tc.seq_length, 1, dp_rank=st.dp_rank, dp_size=st.dp_size,
-                                         pin_memory=True)
+    dims = ParallelDims(tp=tp, ep=args.ep, cp=args.cp, pp=args.pp)
+    if vlm:
+        from loongforge_b200.runtime.vlm import VLMTrainer, synthetic_vlm_iterator
+        trainer = VLMTrainer(cfg, tc, dims, vit_cfg=get_model_config("qwen2.5-vit"), encoder_tp=1, encoder_recompute=True,
+                             images_per_sample=args.images_per_sample, image_size=448, device=dev)
+        st = trainer.st
+        host_iter = synthetic_vlm_iterator(cfg.vocab_size, tc.seq_length, images_per_sample=args.images_per_sample,
+                                           image_size=448, dp_rank=st.dp_rank, dp_size=st.dp_size, pin_memory=True)
+    else:
+        trainer = Trainer(cfg, tc, dims, device=dev)
+        st = trainer.st
+        host_iter = synthetic_batch_iterator(cfg.vocab_size, tc.seq_length, 1, dp_rank=st.dp_rank, dp_size=st.dp_size,
+                                             pin_memory=True)
 
     def device_iter():
         # the same synthetic stream, staged on the device ahead of time (device-timed region)
@@ -267,7 +295,8 @@ def main():
                 "model": (f"llama3-8b ({cfg.num_layers} layers, h4096, 32q/8kv, ffn14336, vocab128256)" if flagship else
                           f"{args.model} ({cfg.num_layers} layers, ep{args.ep}, dispatcher {args.moe_dispatcher})"),
                 "global_batch": gbs, "seq_len": tc.seq_length, "micro_batch": 1,
-                "parallelism": (f"tp{tp}+sp" if tp > 1 else "tp1") + f" dp{dp} distributed-optimizer",
+                "parallelism": (f"tp{tp}+sp" if tp > 1 else "tp1") + (f" pp{args.pp}" if args.pp > 1 else "")
+                + (f" cp{args.cp}" if args.cp > 1 else "") + f" dp{dp} distributed-optimizer",
                 "recompute": recompute, "attention_impl": args.attention,
                 "tp_comm_overlap": bool(cfg.tp_comm_overlap),
                 "tokens_per_sec_per_gpu": value / world, "model_tflops_per_gpu": tflops_gpu,

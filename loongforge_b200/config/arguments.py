@@ -337,7 +337,8 @@ _COMPAT_FLAGS = [
 # compat flags that change what the trainers do (the others are accepted and recorded in the argument dump)
 COMPAT_WIRED = {"--freeze-parameters", "--freeze-parameters-regex", "--trainable-modules", "--force-pow-2-scales",
                 "--amax-epsilon", "--enable-ema", "--no-check-for-nan-in-loss-and-grad", "--padded-vocab-size",
-                "--offload-optimizer", "--offload-optimizer-percent", "--no-position-embedding"}
+                "--offload-optimizer", "--offload-optimizer-percent", "--no-position-embedding", "--group-by-length",
+                "--sft-sort-batch"}
 
 
 def _add_compat_args(p):

@@ -52,11 +52,25 @@ class SFTDataset:
 
 def sft_batch_iterator(ds: SFTDataset, seq_length: int, *, packing: bool = True, dp_rank: int = 0, dp_size: int = 1,
                        seed: int = 1234, pad_id: int = 0, start_sample: int = 0,
-                       pad_to_multiple: int = 1) -> Iterator[Dict[str, torch.Tensor]]:
+                       pad_to_multiple: int = 1, balance_group: int = 0) -> Iterator[Dict[str, torch.Tensor]]:
     """Infinite iterator of micro-batches of ONE packed row of `seq_length` tokens (or one padded
     sample when packing is off). Epochs are reshuffled deterministically; rank r takes every
-    dp_size-th bin."""
+    dp_size-th bin. With ``balance_group`` = G > 0 (``--group-by-length`` / ``--sft-sort-batch``) every G consecutive
+    samples of the shuffled order are split over the data-parallel ranks by cost (length squared) before packing, so
+    that ranks finish their share of a step together (data/samplers.py::BalancedGroupSampler)."""
     epoch, consumed = 0, start_sample
+    if balance_group > 0:
+        from .samplers import BalancedGroupSampler
+        samples = [ds[i] for i in range(len(ds))]
+        sampler = BalancedGroupSampler([len(s[0]) for s in samples], min(balance_group, len(samples)), dp_size, dp_rank,
+                                       seq_length, seed=seed)
+        for packs in sampler:
+            for pack in packs:
+                if consumed > 0:
+                    consumed -= 1
+                    continue
+                yield collate_packed([(samples[i][0][:seq_length], samples[i][1][:seq_length]) for i in pack],
+                                     seq_length, pad_id, pad_to_multiple)
     while True:
         rng = random.Random(seed + epoch)
         order = list(range(len(ds)))

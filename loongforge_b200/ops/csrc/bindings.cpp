@@ -867,6 +867,40 @@ std::vector<at::Tensor> sparse_mla_fwd(const at::Tensor& q, const at::Tensor& kv
   return {o, lse};
 }
 
+// Head-averaged attention probabilities of the selected slots, given the forward's lse [m, H] -> pmean [m, topk] fp32.
+at::Tensor sparse_mla_probs(const at::Tensor& q, const at::Tensor& kv, const at::Tensor& idx, const at::Tensor& lse,
+                            double scale, const at::Tensor& status) {
+  check_bf16_cuda(q, "q");
+  check_bf16_cuda(kv, "kv");
+  TORCH_CHECK(q.dim() == 3 && q.size(2) == 576 && q.stride(2) == 1 && q.size(1) >= 1 && q.size(1) <= 128,
+              "q must be [m, H <= 128, 576]");
+  TORCH_CHECK(kv.dim() == 2 && kv.size(1) == 576 && kv.stride(1) == 1, "kv must be [n, 576]");
+  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kInt && idx.dim() == 2 && idx.is_contiguous() &&
+                  idx.size(0) == q.size(0),
+              "idx must be int32 [m, topk]");
+  TORCH_CHECK(lse.is_cuda() && lse.scalar_type() == at::kFloat && lse.is_contiguous() &&
+                  lse.numel() == q.size(0) * q.size(1),
+              "lse must be fp32 [m, H]");
+  c10::cuda::CUDAGuard guard(q.device());
+  at::Tensor pmean = at::zeros({q.size(0), idx.size(1)}, q.options().dtype(at::kFloat));
+  lf::SparseMlaArgs a;
+  a.q = q.data_ptr(); a.q_ts = q.stride(0); a.q_hs = q.stride(1);
+  a.kv = kv.data_ptr(); a.kv_ts = kv.stride(0);
+  a.idx = idx.data_ptr<int>();
+  a.topk = static_cast<int>(idx.size(1));
+  a.m = static_cast<int>(q.size(0));
+  a.H = static_cast<int>(q.size(1));
+  a.n_kv = static_cast<int>(kv.size(0));
+  a.scale = static_cast<float>(scale);
+  a.lse = lse.data_ptr<float>();
+  a.pmean = pmean.data_ptr<float>();
+  a.status = status.data_ptr<int>();
+  const int rc = lf::sparse_mla_probs(a, cur_stream());
+  TORCH_CHECK(rc == 0, "lf::sparse_mla_probs failed with code ", rc);
+  ++g_launches;
+  return pmean;
+}
+
 // Lightning-indexer logits for query rows [q0, q0 + rows) into `logits` [rows, ld] fp32 (entries outside each row's
 // key range stay unwritten), then the top-k selection over those ranges into `out` [rows, topk] int32.
 void indexer_topk(const at::Tensor& q, const at::Tensor& k, const at::Tensor& w, const at::Tensor& k_start,
@@ -952,6 +986,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 #endif
 #ifdef LF_HAVE_DSA
   m.def("sparse_mla_fwd", &sparse_mla_fwd);
+  m.def("sparse_mla_probs", &sparse_mla_probs);
   m.def("indexer_topk", &indexer_topk);
 #endif
   m.def("router_fwd", &router_fwd);

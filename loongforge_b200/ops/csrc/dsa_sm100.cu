@@ -37,7 +37,7 @@ static constexpr int SM_KV_BYTES = 9 * SM_KBOX;                    // 72 KB per 
 static constexpr int SM_STAGES = 2;
 static constexpr int SM_KV0 = SM_QS_BYTES;                         // gather stages (first used to stage Q for TMEM)
 static constexpr int SM_CTL = SM_KV0 + SM_STAGES * SM_KV_BYTES;
-static constexpr int SM_SMEM = SM_CTL + 256 + 1024;
+static constexpr int SM_SMEM = SM_CTL + 1280 + 1024;  // control block (barriers, masks, head-sum scratch) + alignment slack
 static constexpr int SM_THREADS = 288;  // 4 gather warps, 1 MMA warp, 4 softmax warps
 static constexpr float SM_LOG2E = 1.4426950408889634f;
 static constexpr int BOXK = 128 * 64 * 2;  // one [128 rows x 64 dims] box of the indexer's key tile
@@ -51,16 +51,20 @@ struct SmlaParams {
   __nv_bfloat16* o;
   long long o_ts, o_hs;
   float* lse;  // [m, H]
+  float* pmean;  // PROBS pass: [m, topk] head-mean attention probabilities (lse is an input there)
   int* status;
 };
 
-enum { S_Q = 0, S_QT = 1, S_KV_FULL = 2, S_KV_EMPTY = 4, S_S_FULL = 6, S_P_FULL = 8, S_O_DONE = 10 };
+enum { S_Q = 0, S_QT = 1, S_KV_FULL = 2, S_KV_EMPTY = 4, S_S_FULL = 6, S_P_FULL = 8, S_O_DONE = 10, S_PART_FULL = 11,
+       S_PART_EMPTY = 12 };
 
 struct SmlaCtl {
   uint64_t bars[16];
   uint32_t tmem_slot;
   int abort_flag;
-  uint32_t live[SM_STAGES][2];  // bit i of word w: slot 32 w + i of the stage's block holds a key
+  uint32_t live[4][2];  // [block & 3]: bit i of word w: slot 32 w + i of the block holds a key (four entries: a stage is
+                        // refilled before the softmax warps are done with the mask of its previous block)
+  float part[4][SM_NB];         // PROBS pass: per-warp head sums of one block
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -70,6 +74,13 @@ __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
 
+// PROBS = false: the attention forward above. PROBS = true: a second pass that, given the forward's log-sum-exp, writes
+// the head-averaged attention probability of every selected slot, pmean[m, s] = (1 / H) sum_h exp(scale s_h - lse_h)
+// (the target distribution of the indexer loss, reference dsa_fused_kernels.py:1844-1955). Same gather, same score
+// MMAs, no value product: one CTA per token; the softmax warps turn scores into probabilities, sum over their 32
+// heads with a transposing butterfly of warp shuffles (62 shuffles for 64 columns) and over the four warps through
+// shared memory in a fixed order.
+template <bool PROBS>
 __global__ void __launch_bounds__(SM_THREADS, 1)
 sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -78,7 +89,7 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
   uint64_t* bars = ctl->bars;
   volatile int* abort_flag = &ctl->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tok = blockIdx.x >> 1, half = blockIdx.x & 1;
+  const int tok = PROBS ? blockIdx.x : (blockIdx.x >> 1), half = PROBS ? 0 : (blockIdx.x & 1);
   const int nb = (p.topk + SM_NB - 1) / SM_NB;
   const int* my_idx = p.idx + static_cast<long long>(tok) * p.topk;
 
@@ -94,6 +105,8 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
       mbar_init(&bars[S_P_FULL + b], 4);
     }
     mbar_init(&bars[S_O_DONE], 1);
+    mbar_init(&bars[S_PART_FULL], 4);
+    mbar_init(&bars[S_PART_EMPTY], 4);
     ctl->abort_flag = 0;
     fence_mbar_init();
   }
@@ -129,7 +142,7 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
         const int sl = j * SM_NB + warp * 32 + lane;
         const int idl = sl < p.topk ? my_idx[sl] : -1;
         const unsigned m = __ballot_sync(0xffffffffu, idl >= 0 && idl < p.n_kv);
-        if (lane == 0) ctl->live[s][warp] = m;
+        if (lane == 0) ctl->live[j & 3][warp] = m;
       }
       const int slot = j * SM_NB + row;
       const int id = slot < p.topk ? my_idx[slot] : -1;
@@ -180,6 +193,20 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
       };
       bool ok = mbar_wait(&bars[S_Q], 0, abort_flag);
       if (ok) ok = mbar_wait(&bars[S_QT], 0, abort_flag);
+      if constexpr (PROBS) {
+        for (int j = 0; j < nb && ok; ++j) {
+          const int s = j % SM_STAGES, b = j & 1;
+          ok = mbar_wait(&bars[S_KV_FULL + s], (j / SM_STAGES) & 1, abort_flag);
+          // the softmax warps have read the scores of block j - 2 out of this buffer
+          if (ok && j >= 2) ok = mbar_wait(&bars[S_P_FULL + b], ((j - 2) >> 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_s(j);
+          tc_commit(&bars[S_KV_EMPTY + s]);
+        }
+        if (!ok) atomicCAS(p.status, 0, LF_ERR_WAIT_FULL);
+        ok = false;  // nothing of the forward's loop below runs
+      }
       if (ok && nb > 0) {
         ok = mbar_wait(&bars[S_KV_FULL + 0], 0, abort_flag);
         if (ok) {
@@ -208,7 +235,7 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
           issue_s(j + 1);
         }
       }
-      if (!ok) atomicCAS(p.status, 0, LF_ERR_WAIT_FULL);
+      if (!PROBS && !ok) atomicCAS(p.status, 0, LF_ERR_WAIT_FULL);
     }
   } else {
     // ------------------------------------------------------------ softmax warps: one thread per head
@@ -239,13 +266,73 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars[S_QT]);
     }
+    if constexpr (PROBS) {
+      const float lse_n = h < p.H ? p.lse[static_cast<long long>(tok) * p.H + h] : -INFINITY;
+      const float neg_lse2 = lse_n == -INFINITY ? -INFINITY : -lse_n * SM_LOG2E;
+      const float inv_h = 1.f / static_cast<float>(p.H);
+      const int st_tid = threadIdx.x - 5 * 32;  // 0..127 over the softmax warps
+      for (int j = 0; j < nb && ok; ++j) {
+        const int s = j % SM_STAGES, b = j & 1;
+        ok = mbar_wait(&bars[S_KV_FULL + s], (j / SM_STAGES) & 1, abort_flag);
+        if (ok) ok = mbar_wait(&bars[S_S_FULL + b], (j >> 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t live0 = ctl->live[j & 3][0], live1 = ctl->live[j & 3][1];
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32b_x32(t_s + b * SM_NB + lane_off, r0);
+        tmem_ld_32x32b_x32(t_s + b * SM_NB + lane_off + 32, r1);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[S_P_FULL + b]);  // the score buffer may be overwritten
+        float v[64];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          v[i] = ((live0 >> i) & 1u) && neg_lse2 != -INFINITY
+                     ? exp2f(fmaf(__uint_as_float(r0[i]), p.scale_log2, neg_lse2)) : 0.f;
+          v[32 + i] = ((live1 >> i) & 1u) && neg_lse2 != -INFINITY
+                          ? exp2f(fmaf(__uint_as_float(r1[i]), p.scale_log2, neg_lse2)) : 0.f;
+        }
+        // transposing butterfly: after the step with distance d a lane keeps the half of its columns that its bit d
+        // selects, summed with the partner's; at the end lane L holds the 32-head sums of columns 2 L and 2 L + 1
+#pragma unroll
+        for (int d = 16, n = 32; d >= 1; d >>= 1, n >>= 1) {
+          const bool up = (lane & d) != 0;
+#pragma unroll
+          for (int i = 0; i < n; ++i) {
+            const float send = up ? v[i] : v[i + n];
+            const float recv = __shfl_xor_sync(0xffffffffu, send, d);
+            v[i] = (up ? v[i + n] : v[i]) + recv;
+          }
+        }
+        // the four warps meet through two mbarriers (bounded waits, like every other wait of this kernel)
+        if (j >= 1) ok = mbar_wait(&bars[S_PART_EMPTY], (j - 1) & 1, abort_flag);  // previous block's sums were read
+        if (!ok) break;
+        ctl->part[quarter][2 * lane] = v[0];
+        ctl->part[quarter][2 * lane + 1] = v[1];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[S_PART_FULL]);
+        ok = mbar_wait(&bars[S_PART_FULL], j & 1, abort_flag);
+        if (!ok) break;
+        if (st_tid < SM_NB) {
+          const int slot = j * SM_NB + st_tid;
+          if (slot < p.topk)
+            p.pmean[static_cast<long long>(tok) * p.topk + slot] =
+                (ctl->part[0][st_tid] + ctl->part[1][st_tid] + ctl->part[2][st_tid] + ctl->part[3][st_tid]) * inv_h;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[S_PART_EMPTY]);
+      }
+      if (!ok && lane == 0) atomicCAS(p.status, 0, LF_ERR_WAIT_TMEM_FULL);
+      ok = false;  // skip the forward's loop and epilogue below
+    }
     for (int j = 0; j < nb && ok; ++j) {
       const int s = j % SM_STAGES, b = j & 1;
       ok = mbar_wait(&bars[S_KV_FULL + s], (j / SM_STAGES) & 1, abort_flag);  // the producers' mask is visible
       if (ok) ok = mbar_wait(&bars[S_S_FULL + b], (j >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t live0 = ctl->live[s][0], live1 = ctl->live[s][1];
+      const uint32_t live0 = ctl->live[j & 3][0], live1 = ctl->live[j & 3][1];
       uint32_t r0[32], r1[32];
       tmem_ld_32x32b_x32(t_s + b * SM_NB + lane_off, r0);
       tmem_ld_32x32b_x32(t_s + b * SM_NB + lane_off + 32, r1);
@@ -306,7 +393,9 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
       if (lane == 0) mbar_arrive(&bars[S_P_FULL + b]);
     }
     if (ok && nb > 0) ok = mbar_wait(&bars[S_O_DONE], (nb - 1) & 1, abort_flag);
-    if (!ok) {
+    if (PROBS) {
+      // nothing more to do in the probabilities pass
+    } else if (!ok) {
       if (lane == 0) atomicCAS(p.status, 0, LF_ERR_WAIT_TMEM_FULL);
     } else {
       tc_fence_after_sync();
@@ -370,12 +459,17 @@ static EncodeTiledFn dsa_encode_fn() {
   return fn;
 }
 
-int sparse_mla_fwd(const SparseMlaArgs& a, cudaStream_t stream) {
+static int sparse_mla_launch(const SparseMlaArgs& a, bool probs, cudaStream_t stream);
+int sparse_mla_fwd(const SparseMlaArgs& a, cudaStream_t stream) { return sparse_mla_launch(a, false, stream); }
+int sparse_mla_probs(const SparseMlaArgs& a, cudaStream_t stream) { return sparse_mla_launch(a, true, stream); }
+
+static int sparse_mla_launch(const SparseMlaArgs& a, bool probs, cudaStream_t stream) {
   if (a.m <= 0) return 0;
+  if (probs && (a.pmean == nullptr || a.lse == nullptr)) return -2;
   if (a.H < 1 || a.H > 128 || a.topk < 1) return -2;
-  if ((a.q_ts % 8) || (a.q_hs % 8) || (a.kv_ts % 8) || (a.o_ts % 8) || (a.o_hs % 8)) return -2;
+  if ((a.q_ts % 8) || (a.q_hs % 8) || (a.kv_ts % 8) || (!probs && ((a.o_ts % 8) || (a.o_hs % 8)))) return -2;
   if ((reinterpret_cast<uintptr_t>(a.q) & 15) || (reinterpret_cast<uintptr_t>(a.kv) & 15) ||
-      (reinterpret_cast<uintptr_t>(a.o) & 15))
+      (!probs && (reinterpret_cast<uintptr_t>(a.o) & 15)))
     return -2;
   EncodeTiledFn fn = dsa_encode_fn();
   if (!fn) return -1;
@@ -394,7 +488,10 @@ int sparse_mla_fwd(const SparseMlaArgs& a, cudaStream_t stream) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return -4;
   if (!attr[dev]) {
-    if (cudaFuncSetAttribute(sparse_mla_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(sparse_mla_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_SMEM) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(sparse_mla_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_SMEM) !=
+            cudaSuccess)
       return -4;
     attr[dev] = true;
   }
@@ -407,8 +504,12 @@ int sparse_mla_fwd(const SparseMlaArgs& a, cudaStream_t stream) {
   p.o = static_cast<__nv_bfloat16*>(a.o);
   p.o_ts = a.o_ts; p.o_hs = a.o_hs;
   p.lse = a.lse;
+  p.pmean = a.pmean;
   p.status = a.status;
-  sparse_mla_fwd_kernel<<<2 * a.m, SM_THREADS, SM_SMEM, stream>>>(tq, p);
+  if (probs)
+    sparse_mla_fwd_kernel<true><<<a.m, SM_THREADS, SM_SMEM, stream>>>(tq, p);
+  else
+    sparse_mla_fwd_kernel<false><<<2 * a.m, SM_THREADS, SM_SMEM, stream>>>(tq, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -19,11 +19,16 @@ struct SparseMlaArgs {
   void* o = nullptr;
   long long o_ts = 0, o_hs = 0;
   float* lse = nullptr;
+  float* pmean = nullptr;  // sparse_mla_probs only: [m, topk] fp32
   int* status = nullptr;
 };
 
 // 0 on success, negative on invalid arguments (alignment: strides multiples of 8 elements, bases 16-byte aligned).
 int sparse_mla_fwd(const SparseMlaArgs& a, cudaStream_t stream);
+
+// Second pass for the indexer loss: with `lse` of the forward as INPUT, writes pmean[m, s] = mean over heads of the
+// attention probability of selected slot s (0 for empty slots). `o` is not used.
+int sparse_mla_probs(const SparseMlaArgs& a, cudaStream_t stream);
 
 // Lightning-indexer logits logits[t, j] = sum_h w[t, h] * relu(q[t, h, :] . k[j, :]) for the keys j in
 // [k_start[t], k_end[t]) of every query t (entries outside that range are left unwritten). q [m, Hi, 128] bf16

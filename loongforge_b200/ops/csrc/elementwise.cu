@@ -132,36 +132,58 @@ rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
 // Persistent grid: CTA b handles rows b, b+grid, ...; keeps its partial dw in
 // registers and writes one fp32 row of `dw_partial[grid, H]` (scratch); a second
 // kernel sums the partials. dx = rstd*(w*dy) - x*rstd^3*mean(w*dy*x) (+ dx_residual).
-__global__ void __launch_bounds__(NORM_THREADS)
+// VPT = uint4 chunks per thread (H <= VPT * 8 * NORM_THREADS). The loads of the NEXT row are issued before the block
+// reduction of the current one, so the reduction's two barriers do not leave the memory system idle.
+template <int VPT>
+__global__ void __launch_bounds__(NORM_THREADS, VPT <= 2 ? 3 : 1)
 rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
                    const float* __restrict__ rstd, const bf16* __restrict__ dres, bf16* __restrict__ dx,
                    float* __restrict__ dw_partial, int T, int H, float w_offset) {
   __shared__ float sh[32];
   const int nvec = H >> 3;
-  float dwacc[NORM_VPT][8];
+  float dwacc[VPT][8];
+  uint4 cw[VPT], nx[VPT], ng[VPT];
 #pragma unroll
-  for (int i = 0; i < NORM_VPT; ++i)
+  for (int i = 0; i < VPT; ++i) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
-  const uint4* wr = reinterpret_cast<const uint4*>(w);
-  for (long long row = blockIdx.x; row < T; row += gridDim.x) {
+    const int v = threadIdx.x + i * NORM_THREADS;
+    cw[i] = v < nvec ? reinterpret_cast<const uint4*>(w)[v] : make_uint4(0u, 0u, 0u, 0u);
+    nx[i] = ng[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  auto load_row = [&](long long row) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
     const uint4* gr = reinterpret_cast<const uint4*>(dy + row * H);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
+      if (v < nvec) {
+        nx[i] = xr[v];
+        ng[i] = gr[v];
+      }
+    }
+  };
+  if (blockIdx.x < T) load_row(blockIdx.x);
+  for (long long row = blockIdx.x; row < T; row += gridDim.x) {
     const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + row * H) : nullptr;
     uint4* or_ = reinterpret_cast<uint4*>(dx + row * H);
     const float r = rstd[row];
-    uint4 cx[NORM_VPT], cg[NORM_VPT];
+    uint4 cx[VPT], cg[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      cx[i] = nx[i];
+      cg[i] = ng[i];
+    }
+    if (row + gridDim.x < T) load_row(row + gridDim.x);
     float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < NORM_VPT; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int v = threadIdx.x + i * NORM_THREADS;
       if (v < nvec) {
-        cx[i] = xr[v];
-        cg[i] = gr[v];
         float fx[8], fg[8], fw[8];
         unpack8(cx[i], fx);
         unpack8(cg[i], fg);
-        unpack8(wr[v], fw);
+        unpack8(cw[i], fw);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           dot += fg[j] * (fw[j] + w_offset) * fx[j];
@@ -172,13 +194,13 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
     dot = block_sum<NORM_THREADS>(dot, sh);
     const float c = dot * r * r * r / static_cast<float>(H);
 #pragma unroll
-    for (int i = 0; i < NORM_VPT; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int v = threadIdx.x + i * NORM_THREADS;
       if (v < nvec) {
         float fx[8], fg[8], fw[8], o[8];
         unpack8(cx[i], fx);
         unpack8(cg[i], fg);
-        unpack8(wr[v], fw);
+        unpack8(cw[i], fw);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = r * fg[j] * (fw[j] + w_offset) - c * fx[j];
         if (rr) {
@@ -192,7 +214,7 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
     }
   }
 #pragma unroll
-  for (int i = 0; i < NORM_VPT; ++i) {
+  for (int i = 0; i < VPT; ++i) {
     const int v = threadIdx.x + i * NORM_THREADS;
     if (v < nvec) {
       float4* d = reinterpret_cast<float4*>(dw_partial + static_cast<long long>(blockIdx.x) * H + v * 8);
@@ -220,24 +242,82 @@ __global__ void colsum_partials_kernel(const float* __restrict__ partial, int P,
 // head rotate, the v head does not). freqs[T, rot_dim/2] fp32 angles; cos/sin are
 // scaled by `mscale` (YaRN). interleaved=0: pairs (i, i+rot/2); 1: pairs (2i, 2i+1).
 // `sign` = +1 forward, -1 backward (inverse rotation). In place.
+// One CTA per token: the rot_dim / 2 (cos, sin) pairs of the token are computed once into shared memory and reused by
+// all heads; rotating heads are processed eight bf16 at a time when the layout allows 16-byte accesses.
+constexpr int ROPE_MAX_HALF = 256;
 __global__ void rope_kernel(bf16* __restrict__ x, const float* __restrict__ freqs, int T, int heads, int D,
                             int rot_dim, int rot_offset, long long t_stride, long long h_stride, int group,
                             int rope_in_group, int interleaved, float mscale, float sign,
-                            const int* __restrict__ pos_ids) {
+                            const int* __restrict__ pos_ids, int vec_ok) {
+  __shared__ float cs[ROPE_MAX_HALF], sn[ROPE_MAX_HALF];
   const int t = blockIdx.x;
   const int half = rot_dim >> 1;
   const long long frow = pos_ids ? pos_ids[t] : t;
   const float* fr = freqs + frow * half;
   bf16* xt = x + static_cast<long long>(t) * t_stride;
+  const bool cached = half <= ROPE_MAX_HALF;
+  if (cached) {
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      float s, c;
+      sincosf(fr[i], &s, &c);
+      sn[i] = s * mscale * sign;
+      cs[i] = c * mscale;
+    }
+    __syncthreads();
+  }
+  if (cached && vec_ok) {
+    if (!interleaved) {
+      const int hv = half >> 3;  // 16-byte chunks per half
+      for (int idx = threadIdx.x; idx < heads * hv; idx += blockDim.x) {
+        const int h = idx / hv, v = idx - h * hv;
+        if ((h % group) >= rope_in_group) continue;
+        uint4* p0 = reinterpret_cast<uint4*>(xt + h * h_stride + rot_offset) + v;
+        uint4* p1 = reinterpret_cast<uint4*>(xt + h * h_stride + rot_offset + half) + v;
+        float a[8], b[8], o0[8], o1[8];
+        unpack8(*p0, a);
+        unpack8(*p1, b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float c = cs[v * 8 + j], s = sn[v * 8 + j];
+          o0[j] = a[j] * c - b[j] * s;
+          o1[j] = b[j] * c + a[j] * s;
+        }
+        *p0 = pack8(o0);
+        *p1 = pack8(o1);
+      }
+    } else {
+      const int rv = rot_dim >> 3;  // 16-byte chunks of the rotated span: four (even, odd) pairs each
+      for (int idx = threadIdx.x; idx < heads * rv; idx += blockDim.x) {
+        const int h = idx / rv, v = idx - h * rv;
+        if ((h % group) >= rope_in_group) continue;
+        uint4* p = reinterpret_cast<uint4*>(xt + h * h_stride + rot_offset) + v;
+        float e[8], o[8];
+        unpack8(*p, e);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float c = cs[v * 4 + j], s = sn[v * 4 + j];
+          o[2 * j] = e[2 * j] * c - e[2 * j + 1] * s;
+          o[2 * j + 1] = e[2 * j + 1] * c + e[2 * j] * s;
+        }
+        *p = pack8(o);
+      }
+    }
+    return;
+  }
   const int total = heads * half;
   for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
     const int h = idx / half;
     const int i = idx - h * half;
     if ((h % group) >= rope_in_group) continue;
     float s, c;
-    sincosf(fr[i], &s, &c);
-    s *= mscale * sign;
-    c *= mscale;
+    if (cached) {
+      s = sn[i];
+      c = cs[i];
+    } else {
+      sincosf(fr[i], &s, &c);
+      s *= mscale * sign;
+      c *= mscale;
+    }
     bf16* xh = xt + h * h_stride + rot_offset;
     const int i0 = interleaved ? 2 * i : i;
     const int i1 = interleaved ? 2 * i + 1 : i + half;
@@ -593,10 +673,16 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
                                                            accumulate);
     return;
   }
-  rmsnorm_bwd_kernel<<<grid, NORM_THREADS, 0, s>>>(static_cast<const bf16*>(dy), static_cast<const bf16*>(x),
-                                                   static_cast<const bf16*>(w), rstd, static_cast<const bf16*>(dres),
-                                                   static_cast<bf16*>(dx), dw_partial, static_cast<int>(T), H,
-                                                   w_offset);
+  const bf16 *gp = static_cast<const bf16*>(dy), *xp = static_cast<const bf16*>(x), *wp = static_cast<const bf16*>(w);
+  const bf16* rp = static_cast<const bf16*>(dres);
+  bf16* op = static_cast<bf16*>(dx);
+  const int nvec = H >> 3, Ti = static_cast<int>(T);
+  if (nvec <= NORM_THREADS)
+    rmsnorm_bwd_kernel<1><<<grid, NORM_THREADS, 0, s>>>(gp, xp, wp, rstd, rp, op, dw_partial, Ti, H, w_offset);
+  else if (nvec <= 2 * NORM_THREADS)
+    rmsnorm_bwd_kernel<2><<<grid, NORM_THREADS, 0, s>>>(gp, xp, wp, rstd, rp, op, dw_partial, Ti, H, w_offset);
+  else
+    rmsnorm_bwd_kernel<NORM_VPT><<<grid, NORM_THREADS, 0, s>>>(gp, xp, wp, rstd, rp, op, dw_partial, Ti, H, w_offset);
   colsum_partials_kernel<<<(H + 255) / 256, 256, 0, s>>>(dw_partial, grid, H, dw_f32, static_cast<bf16*>(dw_bf16),
                                                          accumulate);
 }
@@ -605,10 +691,13 @@ void rope_inplace(void* x, const float* freqs, const int* pos_ids, int T, int he
                   int rot_offset, long long t_stride, long long h_stride, int group, int rope_in_group,
                   int interleaved, float mscale, float sign, cudaStream_t s) {
   if (T == 0) return;
-  const int work = heads * (rot_dim / 2);
+  // 16-byte accesses need aligned rows, heads, rotated span and halves
+  const int vec_ok = (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (t_stride % 8 == 0) && (h_stride % 8 == 0) &&
+                     (rot_offset % 8 == 0) && (rot_dim % 16 == 0);
+  const int work = vec_ok ? heads * (rot_dim / 16) : heads * (rot_dim / 2);
   const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
   rope_kernel<<<T, threads, 0, s>>>(static_cast<bf16*>(x), freqs, T, heads, D, rot_dim, rot_offset, t_stride,
-                                    h_stride, group, rope_in_group, interleaved, mscale, sign, pos_ids);
+                                    h_stride, group, rope_in_group, interleaved, mscale, sign, pos_ids, vec_ok);
 }
 
 void swiglu_fwd(const void* in, void* out, long long T, int F, cudaStream_t s) {
@@ -749,7 +838,7 @@ extern "C" int lf_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void*
   const int grid = static_cast<int>(T < LF_RMSNORM_NOALLOC_MAX_CTAS ? T : LF_RMSNORM_NOALLOC_MAX_CTAS);
   // Every CTA writes its full row [0, H) of the scratch and the column sum reads exactly rows
   // [0, grid) x [0, H): stale contents of earlier calls are never read, so no clearing is needed.
-  lf::rmsnorm_bwd_kernel<<<grid, lf::NORM_THREADS, 0, stream>>>(
+  lf::rmsnorm_bwd_kernel<lf::NORM_VPT><<<grid, lf::NORM_THREADS, 0, stream>>>(
       static_cast<const lf::bf16*>(dy), static_cast<const lf::bf16*>(x), static_cast<const lf::bf16*>(w), rstd,
       nullptr, static_cast<lf::bf16*>(dx), scratch, static_cast<int>(T), H, w_offset);
   lf::colsum_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(scratch, grid, H, dw, nullptr, 0);

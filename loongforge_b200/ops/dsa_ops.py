@@ -162,16 +162,30 @@ class _SparseMlaFn(torch.autograd.Function):
         return dq, kvl.grad, None, None, None
 
 
+def sparse_mla_head_mean_probs(q, kv, indices, lse, scale: float) -> torch.Tensor:
+    """Head-averaged attention probabilities of the selected slots [m, K] fp32 (a constant: no gradient), from a second
+    pass of the sparse attention kernel that takes the forward's log-sum-exp as input (csrc/dsa_sm100.cu)."""
+    from . import _ext
+    qd, kd = q.detach(), kv.detach()
+    qc = qd if (qd.stride(2) == 1 and qd.stride(1) % 8 == 0 and qd.stride(0) % 8 == 0) else qd.contiguous()
+    kc = kd if (kd.stride(1) == 1 and kd.stride(0) % 8 == 0) else kd.contiguous()
+    return _ext.require().sparse_mla_probs(qc, kc, indices.to(torch.int32).contiguous(), lse.detach().contiguous(),
+                                           float(scale), _ext.status_tensor(q.device))
+
+
 def sparse_mla_attention(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, scale: float, d_v: int = 512,
                          block: int = 256, return_head_mean_probs: bool = False):
     """q [m, H, Dk], kv [n, Dk] (shared by all heads), indices [m, K] (-1 = empty).
     Returns o [m, H, d_v] (and the head-averaged attention distribution over the K slots, a constant target).
-    On a GPU the forward runs on the tcgen05 kernel when only the output is wanted; query blocks are recomputed in
-    backward (``ops/blockwise.py``), so the gathered keys of only one block are alive."""
+    On a GPU the forward (and, when asked for, the head-mean distribution) run on the tcgen05 kernels; query blocks are
+    recomputed in backward (``ops/blockwise.py``), so the gathered keys of only one block are alive."""
     from .blockwise import blockwise_apply
 
-    if not return_head_mean_probs and _native_sparse_mla(q, kv, d_v):
-        return _SparseMlaFn.apply(q, kv, indices, scale, block)[0]
+    if _native_sparse_mla(q, kv, d_v):
+        o, lse = _SparseMlaFn.apply(q, kv, indices, scale, block)
+        if not return_head_mean_probs:
+            return o
+        return o, sparse_mla_head_mean_probs(q, kv, indices, lse, scale)
     m, H, _ = q.shape
     K = indices.shape[1]
     fn = lambda qb, ib, kvv: _sparse_mla_block(qb, ib, kvv, scale, d_v, return_head_mean_probs)  # noqa: E731

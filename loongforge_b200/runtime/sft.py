@@ -33,4 +33,7 @@ class SFTTrainer(Trainer):
         return sft_batch_iterator(ds, self.tcfg.seq_length, packing=args.packing_sft_data, dp_rank=self.st.dp_rank,
                                   dp_size=self.st.dp_size, seed=self.tcfg.seed, pad_id=tok.pad,
                                   start_sample=self.consumed_samples // max(self.st.dp_size, 1),
-                                  pad_to_multiple=1)  # rows are padded to seq_length, which the parallel sizes divide
+                                  pad_to_multiple=1,  # rows are padded to seq_length, which the parallel sizes divide
+                                  balance_group=(self.tcfg.global_batch_size
+                                                 if (getattr(args, "group_by_length", False)
+                                                     or getattr(args, "sft_sort_batch", False)) else 0))

@@ -4,9 +4,12 @@ from __future__ import annotations
 
 from typing import Callable, Dict, Tuple
 
+from ..config.constants import LANGUAGE_FAMILIES, VISION_LANGUAGE_FAMILIES
+
 _REGISTRY: Dict[Tuple[str, str], Callable] = {}
-LLM_FAMILIES = ("llama", "qwen2", "qwen3", "deepseek", "glm", "internlm", "minimax", "mimo", "qwen")
-VLM_FAMILIES = ("qwen2_5_vl", "qwen2_vl", "qwen3_vl", "internvl", "llava_ov", "ernie4_5_vl")
+# the family groupings of config/constants.py, plus the spellings model YAMLs use for the same families
+LLM_FAMILIES = tuple(sorted({f.value for f in LANGUAGE_FAMILIES} | {"qwen"}))
+VLM_FAMILIES = tuple(sorted({f.value for f in VISION_LANGUAGE_FAMILIES} | {"qwen2_5_vl"}))
 
 
 def register_model_trainer(families, phase: str):

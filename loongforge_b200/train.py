@@ -22,6 +22,12 @@ def main(argv: Optional[List[str]] = None) -> int:
     device = init_distributed(backend=args.distributed_backend if args.distributed_backend == "gloo" else None,
                               timeout_s=args.distributed_timeout_minutes * 60)
     model_cfg, train_cfg, dims, raw = build_configs(args, overrides)
+    # process-wide handles: library code far from the trainer (tokenizer / template helpers, position-id functions,
+    # user hooks) reads the parsed arguments, the composed YAML and the model configuration from here
+    from .config import global_vars
+    global_vars.set_args(args)
+    global_vars.set_yaml_config(raw)
+    global_vars.set_model_config(model_cfg)
     rank = dist.get_rank() if dist.is_initialized() else 0
     if rank == 0:
         print("------------------------ arguments ------------------------", flush=True)

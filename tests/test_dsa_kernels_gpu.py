@@ -53,6 +53,29 @@ def test_sparse_mla_forward_matches_fp32(m, H, n, topk):
     assert o[0].abs().max().item() == 0  # nothing selected -> zero output
 
 
+@pytest.mark.parametrize("m,H,n,topk", [(5, 128, 300, 64), (3, 16, 1000, 200), (4, 64, 4096, 2048), (2, 128, 77, 33)])
+def test_sparse_mla_head_mean_probabilities_match_fp32(m, H, n, topk):
+    """Second pass of the kernel: mean over heads of the attention probabilities of the selected slots."""
+    from loongforge_b200.ops import _ext, dsa_ops
+
+    q, kv, idx = _case(m, H, n, topk, seed=m + H + 1)
+    scale = 1.0 / math.sqrt(192)
+    o, pm = dsa_ops.sparse_mla_attention(q, kv, idx.long(), scale, return_head_mean_probs=True)
+    _ext.check_status()
+    valid = idx >= 0
+    g = kv.float()[idx.clamp_min(0).long()]
+    sc = torch.einsum("mhd,mkd->mhk", q.float(), g) * scale
+    sc = sc.masked_fill(~valid[:, None, :], float("-inf"))
+    ref = torch.nan_to_num(torch.softmax(sc, dim=-1)).mean(1)
+    assert pm.shape == ref.shape and pm.dtype == torch.float32
+    assert (pm - ref).abs().max().item() < 2e-3 * max(ref.max().item(), 1e-3) + 1e-6, (pm - ref).abs().max().item()
+    assert pm[~valid].abs().max().item() == 0 if (~valid).any() else True
+    rows = valid.any(1)
+    assert (pm.sum(1)[rows] - 1).abs().max().item() < 5e-3  # a distribution over the selected slots
+    ref_o, _ = _ref(q, kv, idx, scale)
+    assert _rel(o, ref_o) < 2e-2
+
+
 def test_sparse_mla_autograd_wrapper():
     from loongforge_b200.ops import _ext, dsa_ops
 
