@@ -52,6 +52,10 @@ def parse():
     ap.add_argument("--moe-dispatcher", default="alltoall", choices=["peer", "alltoall"])
     ap.add_argument("--pp", type=int, default=1, help="side benchmark: pipeline-parallel size")
     ap.add_argument("--images-per-sample", type=int, default=4, help="vision-language side benchmark")
+    ap.add_argument("--encoder-hetero-dp", action="store_true",
+                    help="vision-language side benchmark: images of a micro-batch split over the decoder's TP ranks")
+    ap.add_argument("--full-hetero-dp", action="store_true",
+                    help="vision-language side benchmark: all encoder rounds before the pipeline, one owner rank per micro-batch")
     ap.add_argument("--experts", type=int, default=None,
                     help="side benchmark: number of routed experts (e.g. the 32 a rank holds of DeepSeek's 256 at EP8)")
     ap.add_argument("--cp", type=int, default=1, help="side benchmark: context-parallel size")
@@ -206,6 +210,7 @@ def main():
     if vlm:
         from loongforge_b200.runtime.vlm import VLMTrainer, synthetic_vlm_iterator
         trainer = VLMTrainer(cfg, tc, dims, vit_cfg=get_model_config("qwen2.5-vit"), encoder_tp=1, encoder_recompute=True,
+                             encoder_hetero_dp=args.encoder_hetero_dp, full_hetero_dp=args.full_hetero_dp,
                              images_per_sample=args.images_per_sample, image_size=448, device=dev)
         st = trainer.st
         host_iter = synthetic_vlm_iterator(cfg.vocab_size, tc.seq_length, images_per_sample=args.images_per_sample,

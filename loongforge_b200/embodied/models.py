@@ -4,9 +4,10 @@ All eight reference policies share one skeleton — observation encoders -> a to
 with flow matching — and differ in which parts they use; ``POLICY_PRESETS`` records the differences:
 
 =============  =======================================================================================
-pi05           VLM prefix (SigLIP-style ViT + Gemma-style LM) with a separate, narrower action-expert
-               transformer attending to the prefix (reference model/pi05/modeling_pi05.py)
-groot_n1_6     Eagle VL backbone features -> DiT action head with AdaLN timestep conditioning
+pi05           own architecture in ``embodied/pi05.py`` (PaliGemma-style prefix + Gemma action expert with
+               shared attention and adaptive RMSNorm); the skeleton below only with ``architecture: skeleton``
+groot_n1_6     own architecture in ``embodied/groot.py`` (Eagle backbone + alternating vision / language DiT
+               action head with embodiment-specific encoders)
 groot_n1_7     Qwen3 backbone + DiT action head
 xvla           Florence-2 style encoder-decoder features + soft-prompted action transformer
 lingbot_va     WAN video-DiT backbone streaming latents, action tokens decoded jointly
@@ -208,13 +209,75 @@ class FlowMatchingPolicy(nn.Module):
         return x
 
 
-def build_policy(name: str, args=None, **overrides) -> FlowMatchingPolicy:
+class _BatchAdapter(nn.Module):
+    """Lets the dedicated architectures (embodied/pi05.py, embodied/groot.py) take the trainer's batch layout:
+    ``text`` is their ``tokens``; the padded part of the instruction (token id 0) is masked."""
+
+    def __init__(self, policy: nn.Module):
+        super().__init__()
+        self.policy = policy
+        self.c = policy.c
+
+    @staticmethod
+    def _adapt(batch):
+        b = dict(batch)
+        if "tokens" not in b:
+            b["tokens"] = b["text"]
+            b.setdefault("token_mask", b["text"] != 0)
+        return b
+
+    def forward(self, batch, noise=None, t=None):
+        return self.policy(self._adapt(batch), noise=noise, t=t)
+
+    @torch.no_grad()
+    def predict_action(self, obs, steps=None, generator=None):
+        return self.policy.predict_action(self._adapt(obs), steps=steps)
+
+
+def _dedicated_policy(name: str, args, overrides: dict) -> Optional[nn.Module]:
+    """Pi0.5 and GR00T N1.6 have architectures of their own. ``model_overrides: {size: tiny}`` selects the small test
+    geometry, any other key overrides a field of the architecture's configuration."""
+    if name not in ("pi05", "groot_n1_6"):
+        return None
+    kw = dict(getattr(args, "model_overrides", None) or {}) if args is not None else {}
+    kw.update(overrides)
+    size = kw.pop("size", "full")
+    if size == "tiny":
+        kw.setdefault("vocab_size", 32000)  # the hash tokenizer of the synthetic / npz data sets
+    if args is not None:
+        kw.setdefault("action_dim", args.action_dim)
+        kw.setdefault("action_horizon", args.action_horizon)
+        kw.setdefault("image_size", args.image_size)
+    if name == "pi05":
+        from .pi05 import Pi05Config, Pi05Policy
+        if args is not None:
+            kw.setdefault("num_cameras", args.num_cameras)
+        fields = {f.name for f in dataclasses.fields(Pi05Config)}
+        kw = {k: v for k, v in kw.items() if k in fields}
+        cfg = Pi05Config.tiny(**kw) if size == "tiny" else Pi05Config(**kw)
+        return _BatchAdapter(Pi05Policy(cfg))
+    from .groot import GrootConfig, GrootPolicy
+    if args is not None:
+        kw.setdefault("state_dim", args.state_dim)
+    fields = {f.name for f in dataclasses.fields(GrootConfig)}
+    kw = {k: v for k, v in kw.items() if k in fields}
+    cfg = GrootConfig.tiny(**kw) if size == "tiny" else GrootConfig(**kw)
+    return _BatchAdapter(GrootPolicy(cfg))
+
+
+def build_policy(name: str, args=None, **overrides) -> nn.Module:
     if name not in POLICY_PRESETS:
         raise KeyError(f"unknown policy {name!r}; known: {sorted(POLICY_PRESETS)}")
+    if (getattr(args, "model_overrides", None) or {}).get("architecture", overrides.get("architecture")) != "skeleton":
+        dedicated = _dedicated_policy(name, args, {k: v for k, v in overrides.items() if k != "architecture"})
+        if dedicated is not None:
+            return dedicated
+    overrides = {k: v for k, v in overrides.items() if k != "architecture"}
+    skeleton_fields = {f.name for f in dataclasses.fields(PolicyConfig)}
     kw = dict(POLICY_PRESETS[name], name=name)
     if args is not None:
         kw.update(action_dim=args.action_dim, state_dim=args.state_dim, action_horizon=args.action_horizon,
                   image_size=args.image_size, num_cameras=args.num_cameras)
-        kw.update(args.model_overrides or {})
-    kw.update(overrides)
+        kw.update({k: v for k, v in (args.model_overrides or {}).items() if k in skeleton_fields})
+    kw.update({k: v for k, v in overrides.items() if k in skeleton_fields})
     return FlowMatchingPolicy(PolicyConfig(**kw))

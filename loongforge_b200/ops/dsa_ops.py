@@ -131,9 +131,43 @@ def _native_sparse_mla(q, kv, d_v) -> bool:
             and kv.dtype == torch.bfloat16 and q.shape[-1] == 576 and d_v == 512 and q.shape[1] <= 128)
 
 
+def _bmm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Batched product of bf16 operands on the tensor cores with an fp32 result (plain fp32 product elsewhere)."""
+    if a.is_cuda and a.dtype == torch.bfloat16:
+        try:
+            return torch.bmm(a, b, out_dtype=torch.float32)
+        except (TypeError, NotImplementedError, RuntimeError):  # a PyTorch without the out_dtype overload
+            pass
+    return torch.bmm(a.float(), b.float())
+
+
+def sparse_mla_backward_block(q, kv, idx, o, lse, do, scale: float, dkv: torch.Tensor, d_v: int = 512):
+    """Backward of one query block given the forward's output and log-sum-exp: five batched GEMMs over the gathered
+    rows, no autograd graph. q [b, H, Dk], idx [b, K] (-1 = empty), o / do [b, H, d_v], lse [b, H] (natural log);
+    returns dq and ADDS the block's key / value gradient into `dkv` [n, Dk] fp32 (``index_add_``: on a GPU the order of
+    the additions, hence the last bits, can differ between runs)."""
+    valid = idx >= 0
+    gi = idx.clamp_min(0)
+    g = kv[gi]                                                      # [b, K, Dk]
+    s = _bmm_f32(q, g.transpose(1, 2)) * scale                      # [b, H, K] fp32
+    fin = torch.isfinite(lse)
+    p = torch.exp(s - torch.where(fin, lse, torch.zeros_like(lse)).unsqueeze(-1))
+    p = p * (valid.unsqueeze(1) & fin.unsqueeze(-1))
+    dp = _bmm_f32(do, g[..., :d_v].transpose(1, 2))                 # [b, H, K]
+    delta = (do.float() * o.float()).sum(-1, keepdim=True)          # [b, H, 1]
+    ds = (p * (dp - delta) * scale).to(q.dtype)
+    pb = p.to(q.dtype)
+    dq = _bmm_f32(ds, g)                                            # [b, H, Dk]
+    dg = _bmm_f32(ds.transpose(1, 2), q)                            # [b, K, Dk]
+    dg[..., :d_v] += _bmm_f32(pb.transpose(1, 2), do)
+    dkv.index_add_(0, gi.reshape(-1), dg.reshape(-1, dg.shape[-1]))  # empty slots carry p = ds = 0
+    return dq.to(q.dtype)
+
+
 class _SparseMlaFn(torch.autograd.Function):
-    """Forward on the tcgen05 kernel (csrc/dsa_sm100.cu): no gathered [rows, K, 576] tensor ever exists. Backward
-    recomputes one query block at a time with the PyTorch formulation below and back-propagates through it."""
+    """Forward on the tcgen05 kernel (csrc/dsa_sm100.cu): no gathered [rows, K, 576] tensor ever exists. Backward works
+    one query block at a time from the saved output and log-sum-exp (`sparse_mla_backward_block`: batched tensor-core
+    GEMMs over the block's gathered rows), so only one block's gathered keys are alive."""
 
     @staticmethod
     def forward(ctx, q, kv, indices, scale, block):
@@ -142,24 +176,23 @@ class _SparseMlaFn(torch.autograd.Function):
         kc = kv if (kv.stride(1) == 1 and kv.stride(0) % 8 == 0) else kv.contiguous()
         o, lse = _ext.require().sparse_mla_fwd(qc, kc, indices.to(torch.int32).contiguous(), float(scale),
                                                _ext.status_tensor(q.device))
-        ctx.save_for_backward(q, kv, indices)
+        ctx.save_for_backward(q, kv, indices, o, lse)
         ctx.cfg = (scale, block)
         ctx.mark_non_differentiable(lse)
         return o, lse
 
     @staticmethod
     def backward(ctx, do, _dlse):
-        q, kv, indices = ctx.saved_tensors
+        q, kv, indices, o, lse = ctx.saved_tensors
         scale, block = ctx.cfg
-        dq = torch.zeros_like(q)
-        kvl = kv.detach().requires_grad_(True)
+        dq = torch.empty_like(q)
+        dkv = torch.zeros(kv.shape, dtype=torch.float32, device=kv.device)
+        kvd = kv.detach()
         for s in range(0, q.shape[0], block):
-            qb = q[s:s + block].detach().requires_grad_(True)
-            with torch.enable_grad():
-                ob = _sparse_mla_block(qb, indices[s:s + block].long(), kvl, scale, 512, False)
-            torch.autograd.backward(ob, do[s:s + block].flatten(1))
-            dq[s:s + block] = qb.grad
-        return dq, kvl.grad, None, None, None
+            e = min(q.shape[0], s + block)
+            dq[s:e] = sparse_mla_backward_block(q[s:e].detach(), kvd, indices[s:e].long(), o[s:e], lse[s:e],
+                                                do[s:e].contiguous(), scale, dkv)
+        return dq, dkv.to(kv.dtype), None, None, None
 
 
 def sparse_mla_head_mean_probs(q, kv, indices, lse, scale: float) -> torch.Tensor:

@@ -12,7 +12,8 @@ from loongforge_b200.embodied.config import EmbodiedArgs, parse_args, validate
 from loongforge_b200.embodied.models import POLICY_PRESETS, build_policy
 from tests.dist_utils import run_distributed
 
-SMALL = dict(hidden=32, layers=1, heads=2, expert_hidden=32, expert_layers=1)
+# skeleton fields for the shared skeleton, `size` for the policies with an architecture of their own (Pi0.5, GR00T)
+SMALL = dict(hidden=32, layers=1, heads=2, expert_hidden=32, expert_layers=1, size="tiny")
 
 
 def _args(tmp, **kw):
@@ -43,7 +44,15 @@ def test_policies_loss_and_sampling(name, tmp_path):
     batch = collate([SyntheticEpisodes(a)[i] for i in range(2)])
     loss = p(batch)
     loss.backward()
-    assert torch.isfinite(loss) and all(q.grad is not None for q in p.parameters() if q.requires_grad)
+    assert torch.isfinite(loss)
+    no_grad = [n for n, q in p.named_parameters() if q.requires_grad and q.grad is None]
+    if name == "pi05":
+        # the loss reads the action tokens only: what the LAST language layer computes after its attention (output
+        # projection, MLP, final norm) feeds nothing and gets no gradient; its keys / values do
+        assert no_grad and all(".lang_norm." in n or ".lang.1." in n for n in no_grad), no_grad
+        assert not any(".qkv." in n or ".input_norm." in n for n in no_grad), no_grad
+    else:
+        assert not no_grad, no_grad
     act = p.predict_action(batch, steps=2)
     assert act.shape == (2, a.action_horizon, a.action_dim)
 
@@ -52,7 +61,7 @@ def test_trainer_learns_and_resumes(tmp_path):
     from loongforge_b200.embodied.trainer import build_trainer
 
     a = _args(tmp_path, train_steps=6, save_interval=3, gradient_accumulation_steps=2, warmup_steps=2,
-              activation_checkpoint_patterns=["backbone.blocks.*"])
+              activation_checkpoint_patterns=["policy.decoder.lang.*"])
     t = build_trainer(a)
     t.train()
     lines = [json.loads(x) for x in open(os.path.join(tmp_path, "metrics.jsonl"))]
@@ -167,3 +176,95 @@ def test_orchestrator_with_mock_and_real_policy(tmp_path):
     assert "success_rate" in compare_reports(rep, rep2)
     with pytest.raises(RuntimeError, match="unavailable on this box"):
         ENV_ADAPTERS["libero"]()
+
+
+def test_pi05_cached_sampling_and_checkpoint_names():
+    """Pi0.5: the expert-only pass over cached prefix keys / values gives the velocity of the joint pass; the
+    public-checkpoint name map round-trips every tensor (fused q, k, v and gate, up included)."""
+    from loongforge_b200.embodied.pi05 import Pi05Config, Pi05Policy, convert_pi05_state_dict
+
+    torch.manual_seed(0)
+    c = Pi05Config.tiny()
+    m = Pi05Policy(c).eval()
+    B = 2
+    obs = {"images": torch.randn(B, 2, 3, 28, 28), "image_masks": torch.tensor([[1, 1], [1, 0]]).bool(),
+           "tokens": torch.randint(0, 512, (B, 12)), "token_mask": torch.arange(12)[None, :] < torch.tensor([[12], [7]])}
+    noise, t = torch.randn(B, 6, 7), torch.full((B,), 0.7)
+    with torch.no_grad():
+        prefix, valid = m.embed_prefix(obs)
+        suffix, cond = m.embed_suffix(noise, t)
+        mask, pos = m._masks(valid, 6)
+        P = valid.shape[1]
+        _, joint, _ = m.decoder(prefix, suffix, mask, pos, cond)
+        _, _, cache = m.decoder(prefix, None, mask[:, :P, :P], pos[:, :P], fill_cache=True)
+        _, cached, _ = m.decoder(None, suffix, mask[:, P:], pos[:, P:], cond, cache=cache)
+    assert torch.allclose(joint, cached, atol=1e-5)
+    # a padded camera / padded instruction tokens do not change the result
+    obs2 = dict(obs, tokens=obs["tokens"].clone())
+    obs2["tokens"][1, 7:] = 3
+    a1, a2 = m.predict_action(obs, steps=2, noise=noise), m.predict_action(obs2, steps=2, noise=noise)
+    assert torch.allclose(a1, a2, atol=1e-5)
+    sd = m.state_dict()
+    pub = convert_pi05_state_dict(sd, c, to_public=True)
+    assert "paligemma_with_expert.gemma_expert.model.layers.0.self_attn.q_proj.weight" in pub
+    assert "paligemma_with_expert.paligemma.model.vision_tower.vision_model.encoder.layers.1.self_attn.k_proj.bias" in pub
+    back = convert_pi05_state_dict({"model." + k: v for k, v in pub.items()}, c)
+    assert set(back) == set(sd) and all(torch.equal(sd[k], back[k]) for k in sd)
+    with pytest.raises(KeyError):
+        convert_pi05_state_dict({**pub, "stray.weight": torch.zeros(1)}, c)
+
+
+def test_groot_embodiment_specific_weights_and_alternating_context():
+    """GR00T N1.6: another embodiment id selects other encoder / decoder weights; cross-attention blocks alternate
+    between text and image tokens; the action-head name map round-trips."""
+    from loongforge_b200.embodied.groot import GrootConfig, GrootPolicy, convert_groot_state_dict
+
+    torch.manual_seed(0)
+    c = GrootConfig.tiny()
+    m = GrootPolicy(c).eval()
+    B = 2
+    obs = {"images": torch.randn(B, 1, 3, 28, 28), "tokens": torch.randint(0, 256, (B, 9)), "state": torch.randn(B, 7),
+           "embodiment_id": torch.tensor([1, 1])}
+    noise = torch.randn(B, 5, 7)
+    a1 = m.predict_action(obs, noise=noise)
+    a2 = m.predict_action(dict(obs, embodiment_id=torch.tensor([1, 2])), noise=noise)
+    assert torch.allclose(a1[0], a2[0], atol=1e-6) and not torch.allclose(a1[1], a2[1], atol=1e-4)
+    # block 0 reads text only, block 2 images only: changing the instruction leaves block-2 inputs' context mask alone
+    seen = []
+    for i, blk in enumerate(m.action_head.model.blocks):
+        blk.register_forward_hook(lambda _m, args, _o, i=i: seen.append((i, None if len(args) < 4 else args[3])))
+    m.predict_action(obs, steps=1, noise=noise)
+    masks = {i: mk for i, mk in seen}
+    n_img = (28 // 7 // 2) ** 2
+    assert masks[1] is None and masks[3] is None
+    assert masks[0][:, :n_img].sum() == 0 and masks[0][:, n_img:].all()
+    assert masks[2][:, :n_img].all() and masks[2][:, n_img:].sum() == 0
+    sd = {k: v for k, v in m.state_dict().items() if k.startswith("action_head.")}
+    pub = convert_groot_state_dict(sd, c, to_public=True, head_only=False)
+    assert "action_head.model.transformer_blocks.3.attn1.to_out.0.weight" in pub
+    back = convert_groot_state_dict({**pub, "backbone.anything": torch.zeros(1)}, c)
+    assert set(back) == set(sd) and all(torch.equal(sd[k], back[k]) for k in sd)
+
+
+def test_eval_command_line_serves_a_trained_checkpoint_and_runs_episodes(tmp_path, capsys):
+    """``python -m loongforge_b200.embodied.eval``: serve the newest checkpoint of a run, evaluate against a server."""
+    from loongforge_b200.embodied.eval import __main__ as cli
+    from loongforge_b200.embodied.eval.policy_server import MockPolicyService, serve
+    from loongforge_b200.embodied.trainer import build_trainer
+
+    a = _args(tmp_path, train_steps=2, save_interval=2, action_dim=3, state_dim=6, model_name="groot_n1_6")
+    build_trainer(a).train()
+    over = ["model_name=groot_n1_6", "model_overrides={size: tiny}", "action_dim=3", "state_dim=6", "image_size=28",
+            "action_horizon=4"]
+    assert cli.main(["serve", "--checkpoint", str(tmp_path), "--once"] + over) == 0
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["model"] == "groot_n1_6"
+    with pytest.raises(FileNotFoundError):
+        cli.main(["serve", "--checkpoint", str(tmp_path / "none"), "--once"] + over)
+    srv = serve(MockPolicyService(horizon=4, action_dim=3))
+    try:
+        assert cli.main(["run", "--port", str(srv.port), "--episodes", "2", "--max-steps", "3",
+                         "--output-dir", str(tmp_path / "ev")]) == 0
+    finally:
+        srv.stop()
+    rep = json.load(open(tmp_path / "ev" / "report.json"))
+    assert len(rep["episodes"]) == 2

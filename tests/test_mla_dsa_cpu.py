@@ -105,3 +105,30 @@ def test_index_share_layers_reuse_topk_and_train():
     import pytest
     with pytest.raises(ValueError, match="IndexShare"):
         GPTModel(cfg, pre_process=False, post_process=True, layer_numbers=[3, 4, 5])
+
+
+def test_sparse_mla_block_backward_from_saved_lse_matches_autograd():
+    """The GEMM formulation of the sparse attention backward (from output + log-sum-exp, no autograd graph) against
+    autograd through the gather formulation: ragged selections, an empty row, repeated keys across queries."""
+    import torch
+
+    from loongforge_b200.ops import dsa_ops as D
+
+    torch.manual_seed(0)
+    m, H, n, K, scale = 12, 8, 50, 16, 0.07
+    q = torch.randn(m, H, 576, requires_grad=True)
+    kv = torch.randn(n, 576, requires_grad=True)
+    idx = torch.stack([torch.randperm(n)[:K] for _ in range(m)])
+    idx[0] = -1
+    idx[3, 5:] = -1
+    do = torch.randn(m, H, 512)
+    o = D._sparse_mla_block(q, idx, kv, scale, 512, False).view(m, H, 512)
+    o.backward(do)
+    g = kv.detach()[idx.clamp_min(0)]
+    sc = torch.einsum("bhd,bkd->bhk", q.detach(), g) * scale
+    lse = torch.logsumexp(sc.masked_fill(~(idx >= 0)[:, None, :], float("-inf")), -1)
+    dkv = torch.zeros(n, 576)
+    dq = torch.cat([D.sparse_mla_backward_block(q.detach()[s:s + 5], kv.detach(), idx[s:s + 5], o.detach()[s:s + 5],
+                                                lse[s:s + 5], do[s:s + 5], scale, dkv) for s in range(0, m, 5)])
+    assert torch.allclose(dq, q.grad, atol=2e-5) and torch.allclose(dkv, kv.grad, atol=2e-5)
+    assert dq[0].abs().max() == 0

@@ -3,6 +3,7 @@ WebDataset shards."""
 import json
 import os
 
+import pytest
 import torch
 
 
@@ -109,3 +110,48 @@ def test_layer_benchmark_exports_policy(tmp_path):
     out = tmp_path / "policy.json"
     B.main(["--model-name", "tiny-llama", "--tokens", "16", "--out", str(out)])
     FP8Policy.from_json(str(out))
+
+
+def test_convert_file_descriptors_exist_and_select_the_family():
+    """Every `convert_file:` key of a model YAML points at a descriptor in the tree, and the converter reads it."""
+    import glob
+    import re
+
+    from tools.convert_checkpoint import convert as C
+    from tools.convert_checkpoint.name_maps import FAMILIES
+
+    root = os.path.join(os.path.dirname(__file__), "..")
+    seen = 0
+    for y in glob.glob(os.path.join(root, "configs", "models", "**", "*.yaml"), recursive=True):
+        for line in open(y):
+            m = re.match(r"\s*convert_file:\s*\$\{oc\.env:LOONGFORGE_PATH\}/(\S+)", line)
+            if m:
+                path = os.path.join(root, m.group(1))
+                assert os.path.isfile(path), f"{y} names {m.group(1)}, which does not exist"
+                a = C.parse_args(["--load_platform", "huggingface", "--save_platform", "mcore", "--load_ckpt_path", "x",
+                                  "--save_ckpt_path", "y", "--convert_file", path])
+                assert a.model_type_custom in FAMILIES and a.safetensors
+                seen += 1
+    assert seen >= 4
+
+
+@pytest.mark.parametrize("family,model", [("llama3", "tiny-llama"), ("qwen3_moe", "tiny-qwen3-moe")])
+def test_hf_roundtrip_tool(tmp_path, family, model):
+    from loongforge_b200.parallel import state as ps
+    from tools.dist_checkpoint import hf_roundtrip as R
+
+    ps.destroy_model_parallel()
+    try:
+        rep_path = tmp_path / "rep.json"
+        assert R.main(["--synthetic", "--family", family, "--model-name", model, "--work-dir", str(tmp_path / "w"),
+                       "--report", str(rep_path)]) == 0
+        rep = json.load(open(rep_path))
+        assert rep["ok"] and rep["compared"] > 5 and rep["tensors_exported"] == rep["compared"]
+        # a corrupted tensor is reported
+        import torch
+        a = {"x": torch.ones(2), "y": torch.zeros(3)}
+        bad = R.compare_state_dicts(a, {"x": torch.ones(2) * 2, "z": torch.zeros(1)})
+        assert not bad["ok"] and bad["missing_in_result"] == ["y"] and bad["extra_in_result"] == ["z"]
+        assert bad["value_mismatch"][0]["max_abs_diff"] == 1.0
+    finally:
+        ps.destroy_model_parallel()

@@ -35,6 +35,9 @@ def parse_args(argv=None):
     p.add_argument("--save_ckpt_path", required=True)
     p.add_argument("--model_type_custom", default="llama3")
     p.add_argument("--config_file", default=None, help="model YAML; otherwise config.json of the HF directory is read")
+    p.add_argument("--convert_file", default=None,
+                   help="conversion descriptor (configs/models/*/ckpt_convert/*.yaml, the `convert_file` key of a model "
+                        "YAML): selects the name-map family and side defaults")
     p.add_argument("--safetensors", action="store_true")
     p.add_argument("--torch_dtype", default=None, choices=[None, "float16", "float32", "bfloat16"])
     p.add_argument("--tensor_model_parallel_size", type=int, default=1)
@@ -57,7 +60,26 @@ def parse_args(argv=None):
     p.add_argument("--load_lora_ckpt_path", default=None)
     p.add_argument("--lora_alpha", type=int, default=None)
     p.add_argument("--lora_dim", type=int, default=None)
-    return p.parse_args(argv)
+    args = p.parse_args(argv)
+    if args.convert_file:
+        apply_convert_file(args, args.convert_file)
+    return args
+
+
+def apply_convert_file(args, path: str) -> None:
+    """Descriptor keys: ``family`` (name-map family, replaces --model_type_custom), ``huggingface.safetensors``,
+    ``mcore.make_vocab_size_divisible_by``. Explicit command-line values win over the descriptor."""
+    import yaml
+
+    with open(os.path.expandvars(path)) as f:
+        d = yaml.safe_load(f) or {}
+    if d.get("family") and args.model_type_custom == "llama3":
+        args.model_type_custom = d["family"]
+    if (d.get("huggingface") or {}).get("safetensors") and not args.safetensors:
+        args.safetensors = True
+    div = (d.get("mcore") or {}).get("make_vocab_size_divisible_by")
+    if div and args.make_vocab_size_divisible_by == 128:
+        args.make_vocab_size_divisible_by = int(div)
 
 
 def _model_dims(args, hf_dir: Optional[str]):
