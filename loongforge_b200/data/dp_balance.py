@@ -112,6 +112,7 @@ class BalancedMicrobatchIterator:
         self.length_key = length_key
         self.buffer: List[dict] = []
         self.last_imbalance = (1.0, 1.0)  # (before, after) of the latest step
+        self.last_lengths: List[int] = []  # token counts of the micro-batches this rank ran in the latest step
 
     def __iter__(self):
         return self
@@ -119,6 +120,7 @@ class BalancedMicrobatchIterator:
     def __next__(self):
         if not self.buffer:
             self.buffer = self._exchange([next(self.it) for _ in range(self.nmb)])
+            self.last_lengths = [int(b[self.length_key].numel()) for b in self.buffer]
         return self.buffer.pop(0)
 
     # -- (de)serialisation of one micro-batch
@@ -190,3 +192,14 @@ def _comm_device(group) -> torch.device:
     """Tensors of a collective must live where the group's backend works: the GPU for NCCL, the host for gloo."""
     backend = dist.get_backend(group)
     return torch.device("cuda", torch.cuda.current_device()) if "nccl" in str(backend) else torch.device("cpu")
+
+
+def fit_cost_model_across_ranks(model: CostModel, group=None) -> np.ndarray:
+    """Warm-up fit (reference: loongforge/data/dp_balance/rebalance/warmup.py:55-139): every rank has observed
+    (lengths of the micro-batches it ran, its forward + backward time) for a few steps; the observations of all ranks
+    are pooled so that every rank fits, and from then on plans with, the same coefficients."""
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        pooled: List[list] = [None] * dist.get_world_size(group)
+        dist.all_gather_object(pooled, model.obs, group=group)
+        model.obs = [o for part in pooled for o in part]
+    return model.fit()

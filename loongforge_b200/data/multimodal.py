@@ -184,46 +184,69 @@ def decode_image(data: bytes, ext: str) -> np.ndarray:
     return np.asarray(Image.open(io.BytesIO(data)).convert("RGB"))
 
 
+def is_packed_dataset(root: str) -> bool:
+    """True for shards written by tools/data_preprocess/vlm_offline_packing.py (packs decided offline)."""
+    import json
+    import os
+    with open(os.path.join(root, "index.json")) as f:
+        return bool(json.load(f).get("packed"))
+
+
 def webdataset_samples(root: str, *, dp_rank: int = 0, dp_size: int = 1, seed: int = 0, start_sample: int = 0,
                        epochs: Optional[int] = None):
     """Raw samples (``{"images": [...], "conversation": [...]}``) from the tar shards under `root` (the layout written
     by tools/data_preprocess/vlm_to_webdataset.py: ``index.json`` + ``shard-*.tar`` with ``{key}.json`` and
     ``{key}[.n].{ext}`` members). Shards are visited in a per-epoch shuffled order that all ranks share; rank r keeps
-    every dp_size-th sample. ``start_sample`` skips what an earlier run of this rank consumed."""
+    every dp_size-th sample (every dp_size-th PACK of shards packed offline, whose members stay together).
+    ``start_sample`` skips what an earlier run of this rank consumed."""
     import json
     import os
     import tarfile
 
     with open(os.path.join(root, "index.json")) as f:
-        shards = [os.path.join(root, sh["name"]) for sh in json.load(f)["shards"]]
+        idx = json.load(f)
+    shards = [os.path.join(root, sh["name"]) for sh in idx["shards"]]
+    packed = bool(idx.get("packed"))  # packs decided offline: the unit handed to a rank is a whole pack
     n, epoch = 0, 0
     while epochs is None or epoch < epochs:
         order = np.random.RandomState(seed + epoch).permutation(len(shards))
         for si in order:
-            cur, group = None, {}
+            cur, group, last_pack = None, {}, None
 
-            def emit(group):
-                meta = json.loads(group["json"])
+            def emit(group, meta):
                 imgs = sorted((k for k in group if k != "json"), key=lambda k: (len(k), k))
+                pack = {"pack_id": meta["pack_id"], "pack_size": meta["pack_size"]} if "pack_id" in meta else {}
                 conv = meta.get("conversation") or [
                     {"role": "user" if c.get("from", c.get("role")) in ("human", "user") else "assistant",
                      "content": c.get("value", c.get("content", ""))} for c in meta.get("conversations", [])]
-                return {"images": [decode_image(group[k], k) for k in imgs], "conversation": conv}
+                return {"images": [decode_image(group[k], k) for k in imgs], "conversation": conv, **pack}
+
+            def take(group):
+                """Counts the sample (or, for packed shards, its pack) and says whether this rank keeps it."""
+                nonlocal n, last_pack
+                meta = json.loads(group["json"])
+                if packed and meta.get("pack_id") == last_pack:
+                    unit = n - 1  # another member of the pack counted last
+                else:
+                    unit, n = n, n + 1
+                    last_pack = meta.get("pack_id") if packed else None
+                keep = unit % dp_size == dp_rank and unit // dp_size >= start_sample
+                return emit(group, meta) if keep else None
 
             with tarfile.open(shards[si]) as tar:
                 for m in tar:
                     key, _, ext = m.name.partition(".")
                     if key != cur and cur is not None:
-                        if n % dp_size == dp_rank and n // dp_size >= start_sample:
-                            yield emit(group)
-                        n += 1
+                        out = take(group)
+                        if out is not None:
+                            yield out
                         group = {}
                     cur = key
                     group[ext] = tar.extractfile(m).read()
                 if cur is not None:
-                    if n % dp_size == dp_rank and n // dp_size >= start_sample:
-                        yield emit(group)
-                    n += 1
+                    out = take(group)
+                    if out is not None:
+                        yield out
         epoch += 1
 
 
@@ -234,6 +257,7 @@ def vlm_batch_iterator(samples, encoder: VLMTaskEncoder, seq_len: int, *, merge_
     from .position_ids import mrope_ids
 
     packer = OnlinePacker(seq_len, buffer_size=buffer_size if packing else 1, pad_id=pad_id, pad_to_seq_len=True)
+    offline: List[Dict] = []  # members of the offline pack being collected (samples carrying pack_id / pack_size)
 
     def batches(packs):
         for p in packs:
@@ -251,5 +275,16 @@ def vlm_batch_iterator(samples, encoder: VLMTaskEncoder, seq_len: int, *, merge_
             continue  # gated by the task encoder (over-long sample)
         if "mrope" not in enc:  # family encoders (data/task_encoders.py) bring their own position ids
             enc["mrope"] = mrope_ids(enc["tokens"], enc["grid_thw"], encoder.img_id, merge_size)
+        if "pack_id" in raw:
+            # packs were decided offline: the members of a pack arrive consecutively and form one row as they are
+            # (the offline lengths are estimates: a pack that comes out too long sheds its last members)
+            offline.append(enc)
+            if len(offline) >= int(raw["pack_size"]):
+                while sum(e["tokens"].numel() for e in offline) > seq_len and len(offline) > 1:
+                    offline.pop()
+                if offline[0]["tokens"].numel() <= seq_len:
+                    yield from batches([packer._pack(offline)])
+                offline = []
+            continue
         yield from batches(packer.add(enc))
     yield from batches(packer.flush())

@@ -272,12 +272,16 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tq, const SmlaParams p
       const float inv_h = 1.f / static_cast<float>(p.H);
       const int st_tid = threadIdx.x - 5 * 32;  // 0..127 over the softmax warps
       for (int j = 0; j < nb && ok; ++j) {
-        const int s = j % SM_STAGES, b = j & 1;
-        ok = mbar_wait(&bars[S_KV_FULL + s], (j / SM_STAGES) & 1, abort_flag);
-        if (ok) ok = mbar_wait(&bars[S_S_FULL + b], (j >> 1) & 1, abort_flag);
+        const int b = j & 1;
+        // No wait on the stage's "full" barrier here: in this pass a stage is released as soon as its scores are
+        // done, so that barrier can complete the phase of block j + 2 before these warps have looked at it for block
+        // j, and a parity wait two phases late would never return. The scores' barrier orders the mask as well: the
+        // MMA thread saw the stage full before it issued the scores.
+        ok = mbar_wait(&bars[S_S_FULL + b], (j >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t live0 = ctl->live[j & 3][0], live1 = ctl->live[j & 3][1];
+        const uint32_t live0 = *reinterpret_cast<volatile uint32_t*>(&ctl->live[j & 3][0]);
+        const uint32_t live1 = *reinterpret_cast<volatile uint32_t*>(&ctl->live[j & 3][1]);
         uint32_t r0[32], r1[32];
         tmem_ld_32x32b_x32(t_s + b * SM_NB + lane_off, r0);
         tmem_ld_32x32b_x32(t_s + b * SM_NB + lane_off + 32, r1);

@@ -229,17 +229,51 @@ def sparse_mla_attention(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tenso
     return o
 
 
+class _IndexerScoresFn(torch.autograd.Function):
+    """Index scores at the selected slots, one query block at a time, without an autograd graph over the gathered keys:
+    forward keeps only the [m, K] result; backward recomputes a block's scores and forms the three gradients with
+    batched GEMMs (reference kernels: ops/tilelang_ops/lightning_indexer.py:170-347, restricted to the selection)."""
+
+    @staticmethod
+    def _block(qb, kk, ib):
+        kg = kk[ib.clamp_min(0)]                                     # [b, K, D]
+        return kg, _bmm_f32(qb, kg.transpose(1, 2))                  # [b, Hi, K] fp32
+
+    @staticmethod
+    def forward(ctx, qi, wi, ki, indices, block):
+        out = torch.empty(indices.shape, dtype=torch.float32, device=qi.device)
+        for s in range(0, qi.shape[0], block):
+            e = min(qi.shape[0], s + block)
+            _, sc = _IndexerScoresFn._block(qi[s:e], ki, indices[s:e])
+            out[s:e] = (torch.relu(sc) * wi[s:e].float().unsqueeze(-1)).sum(1)
+        ctx.save_for_backward(qi, wi, ki, indices)
+        ctx.block = block
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        qi, wi, ki, indices = ctx.saved_tensors
+        dq = torch.empty_like(qi)
+        dw = torch.empty(wi.shape, dtype=torch.float32, device=wi.device)
+        dk = torch.zeros(ki.shape, dtype=torch.float32, device=ki.device)
+        for s in range(0, qi.shape[0], ctx.block):
+            e = min(qi.shape[0], s + ctx.block)
+            ib = indices[s:e]
+            kg, sc = _IndexerScoresFn._block(qi[s:e], ki, ib)
+            g = (d_out[s:e].float() * (ib >= 0)).unsqueeze(1)        # [b, 1, K]; empty slots carry no gradient
+            dw[s:e] = (torch.relu(sc) * g).sum(-1)
+            ds = (g * wi[s:e].float().unsqueeze(-1) * (sc > 0)).to(qi.dtype)   # [b, Hi, K]
+            dq[s:e] = _bmm_f32(ds, kg).to(qi.dtype)
+            dk.index_add_(0, ib.clamp_min(0).reshape(-1), _bmm_f32(ds.transpose(1, 2), qi[s:e]).reshape(-1, ki.shape[-1]))
+        return dq, dw.to(wi.dtype), dk.to(ki.dtype), None, None
+
+
 def indexer_scores_at(qi: torch.Tensor, wi: torch.Tensor, ki: torch.Tensor, indices: torch.Tensor,
                       block: int = 256) -> torch.Tensor:
     """Index scores ``sum_h w * relu(q_h . k)`` at the selected slots only: [m, K] fp32, differentiable w.r.t. the
-    indexer projections, evaluated in recomputed query blocks."""
-    from .blockwise import blockwise_apply
-
-    def fn(qb, wb, ib, kk):
-        kg = kk[ib.clamp_min(0)]
-        return (torch.relu(torch.einsum("mhd,mkd->mhk", qb.float(), kg.float())) * wb.float().unsqueeze(-1)).sum(1)
-
-    return blockwise_apply(fn, [qi, wi, indices], [ki], block)
+    indexer projections, evaluated (and differentiated) in query blocks so that only one block's gathered keys are
+    alive."""
+    return _IndexerScoresFn.apply(qi, wi, ki, indices, block)
 
 
 def indexer_kl_loss(index_scores: torch.Tensor, attn_probs_head_mean: torch.Tensor, indices: torch.Tensor,

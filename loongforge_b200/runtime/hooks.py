@@ -96,6 +96,31 @@ class ManualGCHook(TrainHook):
         gc.enable()
 
 
+class DPBalanceWarmupHook(TrainHook):
+    """Fits the cost model of the data-parallel load balancer from measured step times: during iterations
+    [first, last] (``--vlm-dp-balance-warmup-iters first last``) every rank records the token counts of the micro-batches
+    it ran with the step's forward + backward time; after `last` the observations of all ranks are pooled and the
+    coefficients of ``a s^2 + b s + c`` replace the defaults."""
+
+    def __init__(self, trainer, first: int, last: int):
+        self.first, self.last, self.done = int(first), int(last), False
+
+    def on_step_end(self, trainer, metrics, elapsed_ms):
+        if self.done:
+            return None
+        it = next(iter(getattr(trainer, "_balanced_iterators", {}).values()), None)
+        if it is None:
+            return None
+        if self.first <= trainer.iteration <= self.last and it.last_lengths:
+            it.model.observe(it.last_lengths, elapsed_ms)
+        if trainer.iteration >= self.last:
+            from ..data.dp_balance import fit_cost_model_across_ranks
+            coef = fit_cost_model_across_ranks(it.model, trainer.st.group("dp"))
+            self.done = True
+            metrics["dp_balance_cost_coefficients"] = [float(c) for c in coef]
+        return None
+
+
 class ExitHook(TrainHook):
     def __init__(self, duration_min, interval, signals: bool):
         from ..ckpt.async_save import ExitDecider
@@ -176,6 +201,9 @@ def build_hooks(args, trainer) -> List[TrainHook]:
         hooks.append(ManualGCHook(getattr(args, "manual_gc_interval", 0) or 1))
     if getattr(args, "log_straggler", False):
         hooks.append(StragglerHook(trainer))
+    if trainer.tcfg.dp_balance:
+        w = list(getattr(args, "vlm_dp_balance_warmup_iters", None) or [2, 5])
+        hooks.append(DPBalanceWarmupHook(trainer, int(w[0]), int(w[-1])))
     if getattr(args, "heartbeat_timeout_s", None) and dist.is_initialized() and world > 1:
         store = dist.distributed_c10d._get_default_store()
         hooks.append(HeartbeatHook(store, rank, world, float(args.heartbeat_timeout_s)))

@@ -105,11 +105,21 @@ def test_layer_benchmark_exports_policy(tmp_path):
     shapes = B.layer_shapes(__import__("loongforge_b200.models.registry", fromlist=["x"]).get_model_config("llama3-8b"), 2)
     assert shapes["linear_qkv"] == (4096, 3072) and shapes["linear_fc1"] == (4096, 14336) and shapes["linear_fc2"] == (7168, 4096)
     rows = B.run("tiny-llama", 1, [16, 32], warmup=1, iters=1)
-    assert {r["kind"] for r in rows} == {"linear_qkv", "linear_proj", "linear_fc1", "linear_fc2"} and len(rows) == 8
-    assert all(r["bf16_ms"] > 0 for r in rows)
+    assert {r["kind"] for r in rows} == {"linear_qkv", "linear_proj", "linear_fc1", "linear_fc2", "output_layer"}
+    assert len(rows) == 10 and all(r["bf16_ms"] >= r["bf16_fwd_ms"] * 0.5 > 0 for r in rows)
+    # multi-latent attention, routed (grouped) and shared experts, several tensor-parallel sizes in one sweep
+    ds = B.layer_shapes(__import__("loongforge_b200.models.registry", fromlist=["x"]).get_model_config("deepseek-v3"), 2, ep=8)
+    assert ds["linear_q_up_proj"] == (1536, 128 * 192 // 2) and ds["linear_kv_down_proj"] == (7168, 576)
+    assert ds["experts.linear_fc1"] == (7168, 4096, 32) and ds["shared_experts.linear_fc2"] == (1024, 7168)
+    rows = B.run("tiny-deepseek", [1, 2], [32], warmup=1, iters=1, kinds=["experts.linear_fc1", "linear_kv_up_proj"])
+    assert {(r["kind"], r["tp"]) for r in rows} == {("experts.linear_fc1", 1), ("experts.linear_fc1", 2),
+                                                    ("linear_kv_up_proj", 1), ("linear_kv_up_proj", 2)}
+    assert all(r["experts"] == 8 for r in rows if r["kind"].startswith("experts"))
     out = tmp_path / "policy.json"
-    B.main(["--model-name", "tiny-llama", "--tokens", "16", "--out", str(out)])
+    B.main(["--model-name", "tiny-llama", "--tokens", "16", "--out", str(out), "--csv", str(tmp_path / "r.csv"),
+            "--markdown", str(tmp_path / "r.md"), "--iters", "1", "--warmup", "1"])
     FP8Policy.from_json(str(out))
+    assert open(tmp_path / "r.md").read().count("\n") == 2 + 5 and open(tmp_path / "r.csv").readline().startswith("kind,tp")
 
 
 def test_convert_file_descriptors_exist_and_select_the_family():
@@ -155,3 +165,46 @@ def test_hf_roundtrip_tool(tmp_path, family, model):
         assert bad["value_mismatch"][0]["max_abs_diff"] == 1.0
     finally:
         ps.destroy_model_parallel()
+
+
+def test_vlm_offline_packing_pipeline_and_loader(tmp_path):
+    """scan -> plan -> write over image-text shards, then the loader keeps every offline pack together."""
+    import numpy as np
+
+    from loongforge_b200.data.multimodal import VisionPreprocess, is_packed_dataset, vlm_batch_iterator, webdataset_samples
+    from loongforge_b200.data.task_encoders import SpecialTokens, build_task_encoder
+    from tools.data_preprocess import vlm_offline_packing as P
+    from tools.data_preprocess.vlm_to_webdataset import write_shards
+
+    rng = np.random.RandomState(0)
+    img_dir = tmp_path / "img"
+    img_dir.mkdir()
+    recs = []
+    for i in range(12):
+        h, w = int(rng.choice([28, 56, 84])), int(rng.choice([28, 56]))
+        np.save(img_dir / f"{i}.npy", rng.randint(0, 255, (h, w, 3), dtype=np.uint8))
+        recs.append({"image": f"{i}.npy", "conversations": [{"from": "human", "value": "<image> " + "word " * int(rng.randint(2, 30))},
+                                                            {"from": "gpt", "value": "ok " * int(rng.randint(1, 10))}]})
+    write_shards(recs, str(tmp_path / "src"), str(img_dir), samples_per_shard=5)
+    out = P.main(["all", "--shards", str(tmp_path / "src"), "--output-dir", str(tmp_path / "dst"), "--seq-length", "128",
+                  "--packs-per-shard", "2", "--min-pixels", "784", "--max-pixels", "50176"])
+    assert out["scanned"] == 12 and out["plan"]["dropped"] == 0 and 0.3 < out["plan"]["fill_rate"] <= 1.0
+    assert P.scan(str(tmp_path / "src"), str(tmp_path / "dst" / "manifest.sqlite")) == 0  # resumable: nothing left
+    assert is_packed_dataset(str(tmp_path / "dst")) and not is_packed_dataset(str(tmp_path / "src"))
+    idx = json.load(open(tmp_path / "dst" / "index.json"))
+    assert idx["total"] == 12 and idx["packs"] == out["plan"]["packs"] and len(idx["shards"]) == -(-idx["packs"] // 2)
+    # every rank sees whole packs; together the ranks see every sample once
+    seen = []
+    for r in range(2):
+        got = list(webdataset_samples(str(tmp_path / "dst"), dp_rank=r, dp_size=2, epochs=1))
+        by_pack = {}
+        for s in got:
+            by_pack.setdefault(s["pack_id"], []).append(s)
+        assert all(len(v) == v[0]["pack_size"] for v in by_pack.values())
+        seen += got
+    assert len(seen) == 12
+    enc = build_task_encoder("qwen2_vl", lambda t: [10 + (ord(c) % 50) for c in t], SpecialTokens(image=900, eos=2),
+                             VisionPreprocess(min_pixels=784, max_pixels=50176))
+    rows = list(vlm_batch_iterator(webdataset_samples(str(tmp_path / "dst"), epochs=1), enc, 512))
+    assert len(rows) == idx["packs"] and all(b["tokens"].shape == (1, 512) for b in rows)
+    assert sum(b["grid_thw"].shape[0] for b in rows) == 12

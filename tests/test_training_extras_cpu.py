@@ -497,3 +497,25 @@ def test_timing_log_level_reports_phase_times():
     for name in ("forward-backward", "optimizer", "partial-grads-all-reduce", "loss-reduce"):
         assert name in text, text
     assert last["timers/forward-backward-ms"] > 0 and last["timers/optimizer-ms"] > 0
+
+
+def _dp_balance_fit(rank, world):
+    import numpy as np
+
+    from loongforge_b200.data.dp_balance import CostModel, fit_cost_model_across_ranks
+
+    m = CostModel()
+    rng = np.random.RandomState(rank)
+    for _ in range(4):  # each rank alone has too few distinct observations for a 3-parameter fit to be trusted
+        ls = [int(x) for x in rng.randint(50, 400, size=3)]
+        m.observe(ls, sum(2e-5 * s * s + 3e-3 * s + 0.5 for s in ls))
+    return [float(c) for c in fit_cost_model_across_ranks(m)], len(m.obs)
+
+
+def test_dp_balance_warmup_fit_pools_observations_of_all_ranks():
+    from dist_utils import run_distributed
+
+    res = run_distributed(_dp_balance_fit, 2)
+    (c0, n0), (c1, n1) = res
+    assert n0 == n1 == 8 and c0 == c1  # same pooled observations -> same plan on every rank
+    assert abs(c0[0] - 2e-5) < 1e-7 and abs(c0[1] - 3e-3) < 1e-4 and abs(c0[2] - 0.5) < 5e-2
