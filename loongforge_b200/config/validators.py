@@ -50,6 +50,93 @@ def validate(args, cfg, tc, dims) -> None:
         raise ValueError("SFT needs --sft-dataset (or --mock-data)")
     if dims.vpp and dims.vpp > 1 and cfg.num_layers % (dims.pp * dims.vpp) and not tc.custom_pipeline_layers:
         raise ValueError("num_layers must divide by pp x virtual stages")
+    _validate_sft(args, tc)
+    _validate_attention_variants(args, cfg, tc, dims)
+    _validate_moe(args, cfg, tc, dims)
+    _validate_multimodal(args, cfg, tc, dims)
+
+
+def _validate_sft(args, tc) -> None:
+    """Supervised fine-tuning rules (reference: loongforge/train/validators.py:140-312)."""
+    if tc.training_phase != "sft":
+        return
+    if getattr(args, "train_on_prompt", False) and getattr(args, "history_mask_loss", False):
+        raise ValueError("--train-on-prompt and --history-mask-loss cannot both be set")
+    if getattr(args, "sft_data_streaming", False) and getattr(args, "sft_sort_batch", False):
+        raise ValueError("--sft-sort-batch cannot be used together with --sft-data-streaming")
+    if getattr(args, "packing_sft_data", False) and tc.micro_batch_size > 1:
+        raise ValueError("--packing-sft-data packs one row per micro-batch: use --micro-batch-size 1")
+    tmpl = getattr(args, "chat_template", None)
+    if tmpl:
+        from ..data.chat_template import get_template
+        get_template(tmpl)  # unknown names fail here, not after the model is built
+    if getattr(args, "sft_dataset", None) and getattr(args, "tokenizer_type", None) not in (None, "HFTokenizer", "NullTokenizer"):
+        raise ValueError("--tokenizer-type should be HFTokenizer when the training phase is sft")
+
+
+def _validate_attention_variants(args, cfg, tc, dims) -> None:
+    """Sparse attention / chunk pipelining / overlap-schedule combinations (reference: validators.py:314-366)."""
+    if getattr(args, "use_dsa_sp_first", False) and not cfg.sequence_parallel:
+        raise ValueError("--use-dsa-sp-first requires --sequence-parallel")
+    share = getattr(cfg, "dsa_indexer_topk_freq", 1) or 1
+    if share > 1 and not getattr(cfg, "use_dsa", False):
+        raise ValueError("--dsa-indexer-topk-freq > 1 (IndexShare) requires the sparse attention variant")
+    if tc.overlap_moe_expert_parallel_comm:
+        if dims.pp > 1:
+            raise ValueError("--overlap-moe-expert-parallel-comm needs pipeline size 1")
+        if not cfg.num_moe_experts:
+            raise ValueError("--overlap-moe-expert-parallel-comm needs an MoE model")
+        if cfg.recompute_granularity == "full":
+            raise ValueError("--overlap-moe-expert-parallel-comm does not cover full activation recomputation")
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        dp = world // (dims.tp * dims.pp * dims.cp)
+        if tc.global_batch_size // (tc.micro_batch_size * max(dp, 1)) < 2:
+            raise ValueError("--overlap-moe-expert-parallel-comm interleaves micro-batches: at least two per step are needed")
+    if tc.chunkpipe_chunks and tc.chunkpipe_chunks > 1:
+        if dims.pp > 1 or dims.cp > 1 or tc.micro_batch_size != 1:
+            raise ValueError("chunk pipelining needs pp = cp = 1 and micro batch size 1")
+        if tc.seq_length % tc.chunkpipe_chunks:
+            raise ValueError("--seq-length must divide by the number of chunks (seq-length / chunksize)")
+
+
+def _validate_moe(args, cfg, tc, dims) -> None:
+    if not cfg.num_moe_experts:
+        # dispatcher types that only exist for MoE models fall back, as the reference does (validators.py:359-365)
+        if getattr(args, "moe_token_dispatcher_type", None) in ("allgather", "alltoall_seq"):
+            args.moe_token_dispatcher_type = "alltoall"
+        return
+    if cfg.moe_router_topk > cfg.num_moe_experts:
+        raise ValueError("--moe-router-topk exceeds the number of experts")
+    g, gk = cfg.moe_router_num_groups, cfg.moe_router_group_topk
+    if g:
+        if cfg.num_moe_experts % g:
+            raise ValueError("number of experts must divide by --moe-router-num-groups")
+        if gk and (gk > g or cfg.moe_router_topk > gk * (cfg.num_moe_experts // g)):
+            raise ValueError("--moe-router-group-topk groups cannot hold --moe-router-topk experts")
+    if cfg.moe_token_dispatcher_type == "peer" and dims.etp > 1:
+        raise ValueError("the peer-memory dispatcher does not cover expert tensor parallelism; use alltoall")
+
+
+def _validate_multimodal(args, cfg, tc, dims) -> None:
+    """Vision-language and diffusion rules (reference: validators.py:370-420 and the WAN trainers' shape checks)."""
+    mtl = getattr(args, "max_text_length", None)
+    if mtl and dims.cp > 1 and mtl % dims.cp:
+        args.max_text_length = (mtl + dims.cp - 1) // dims.cp * dims.cp  # text length divisible by the CP size
+    enc_tp = getattr(args, "encoder_tensor_model_parallel_size", None)
+    if enc_tp and dims.tp % enc_tp:
+        raise ValueError("the decoder's tensor parallel size must divide by the encoder's")
+    if getattr(args, "enable_full_hetero_dp", False) and getattr(args, "enable_encoder_hetero_dp", False):
+        raise ValueError("--enable-full-hetero-dp replaces --enable-encoder-hetero-dp: give one of them")
+    name = str(getattr(args, "model_name", "") or "")
+    if name.startswith("wan"):
+        # WAN latents: 4x temporal / 8x spatial VAE compression, then (1, 2, 2) patches; Ulysses splits the token axis
+        frames = getattr(args, "num_frames", None) or getattr(args, "frame_num", None)
+        if frames and (int(frames) - 1) % 4:
+            raise ValueError("WAN video lengths must be 4 k + 1 frames")
+        for side in ("height", "width"):
+            v = getattr(args, side, None)
+            if v and int(v) % 16:
+                raise ValueError(f"WAN {side} must be a multiple of 16 (8x VAE, 2x patch)")
 
 
 # Flags that are accepted for command-line compatibility but whose feature is reached through a library entry point

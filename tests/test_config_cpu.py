@@ -126,3 +126,57 @@ def test_freeze_parameters_flags_freeze_before_the_optimizer_is_built():
     for n, p in named.items():
         changed = not torch.equal(before[n], p.detach())
         assert changed == p.requires_grad or not p.requires_grad and not changed, n
+
+
+def test_validator_rule_families():
+    """SFT, MoE, overlap-schedule and multimodal rules raise on inconsistent flags and fix up derived ones."""
+    import types
+
+    import pytest
+
+    from loongforge_b200.config import validators as V
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel.state import ParallelDims
+    from loongforge_b200.runtime.trainer import TrainConfig
+
+    def ns(**kw):
+        return types.SimpleNamespace(**kw)
+
+    tc = TrainConfig(micro_batch_size=2, global_batch_size=4, seq_length=64, training_phase="sft")
+    with pytest.raises(ValueError, match="packs one row"):
+        V._validate_sft(ns(packing_sft_data=True), tc)
+    with pytest.raises(ValueError, match="cannot both"):
+        V._validate_sft(ns(train_on_prompt=True, history_mask_loss=True), tc)
+    with pytest.raises(KeyError):
+        V._validate_sft(ns(chat_template="no_such_template"), TrainConfig(training_phase="sft"))
+    V._validate_sft(ns(chat_template="qwen3_hf_training"), TrainConfig(training_phase="sft"))
+
+    moe = get_model_config("tiny-qwen3-moe")
+    dense = get_model_config("tiny-llama")
+    over = TrainConfig(micro_batch_size=1, global_batch_size=1, seq_length=64, overlap_moe_expert_parallel_comm=True)
+    with pytest.raises(ValueError, match="at least two"):
+        V._validate_attention_variants(ns(), moe, over, ParallelDims())
+    over.global_batch_size = 4
+    V._validate_attention_variants(ns(), moe, over, ParallelDims())
+    with pytest.raises(ValueError, match="MoE model"):
+        V._validate_attention_variants(ns(), dense, over, ParallelDims())
+    with pytest.raises(ValueError, match="pipeline size 1"):
+        V._validate_attention_variants(ns(), moe, over, ParallelDims(pp=2))
+
+    a = ns(moe_token_dispatcher_type="allgather")
+    V._validate_moe(a, dense, tc, ParallelDims())
+    assert a.moe_token_dispatcher_type == "alltoall"
+    bad = get_model_config("tiny-qwen3-moe", moe_router_topk=9)
+    with pytest.raises(ValueError, match="exceeds"):
+        V._validate_moe(ns(), bad, tc, ParallelDims())
+    grp = get_model_config("tiny-qwen3-moe", moe_router_num_groups=4, moe_router_group_topk=1, moe_router_topk=3)
+    with pytest.raises(ValueError, match="cannot hold"):
+        V._validate_moe(ns(), grp, tc, ParallelDims())
+
+    a = ns(max_text_length=510, encoder_tensor_model_parallel_size=1, model_name="wan2-1-i2v", num_frames=81, height=480, width=832)
+    V._validate_multimodal(a, dense, tc, ParallelDims(cp=4))
+    assert a.max_text_length == 512
+    with pytest.raises(ValueError, match="4 k \\+ 1"):
+        V._validate_multimodal(ns(model_name="wan2-1-i2v", num_frames=80), dense, tc, ParallelDims())
+    with pytest.raises(ValueError, match="divide by the encoder"):
+        V._validate_multimodal(ns(encoder_tensor_model_parallel_size=3), dense, tc, ParallelDims(tp=4))
