@@ -176,6 +176,16 @@ void rope_(at::Tensor x, const at::Tensor& freqs, c10::optional<at::Tensor> pos_
   ++g_launches;
 }
 
+at::Tensor hadamard128(const at::Tensor& x) {
+  check_bf16_cuda(x, "x");
+  TORCH_CHECK(x.is_contiguous() && x.dim() >= 1 && x.size(-1) == 128, "hadamard128 wants contiguous rows of 128");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor y = at::empty_like(x);
+  lf::hadamard128(x.data_ptr(), y.data_ptr(), x.numel() / 128, cur_stream());
+  ++g_launches;
+  return y;
+}
+
 at::Tensor swiglu_fwd(const at::Tensor& in) {
   check_bf16_cuda(in, "in");
   TORCH_CHECK(in.is_contiguous());
@@ -947,6 +957,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("rope_", &rope_);
+  m.def("hadamard128", &hadamard128);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("ce_stats", &ce_stats);

@@ -328,6 +328,39 @@ __global__ void rope_kernel(bf16* __restrict__ x, const float* __restrict__ freq
   }
 }
 
+// ============================================================== Hadamard (n = 128)
+// y = x H_128 / sqrt(128) on rows of 128 bf16 (the rotation of the lightning indexer's q / k). One warp per row, four
+// consecutive elements per lane: two butterfly stages inside the lane, five across lanes by shuffles. H is symmetric
+// and orthogonal, so the same kernel is its own backward.
+__global__ void hadamard128_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long rows) {
+  const int lane = threadIdx.x & 31;
+  const long long row = blockIdx.x * static_cast<long long>(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const uint2 raw = reinterpret_cast<const uint2*>(x + row * 128)[lane];
+  const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  float v0 = __bfloat162float(p0.x), v1 = __bfloat162float(p0.y), v2 = __bfloat162float(p1.x), v3 = __bfloat162float(p1.y);
+  // strides 1 and 2: inside the lane
+  float a = v0 + v1, b = v0 - v1, c = v2 + v3, d = v2 - v3;
+  v0 = a + c; v1 = b + d; v2 = a - c; v3 = b - d;
+  // strides 4 .. 64: lane distance 1 .. 16
+#pragma unroll
+  for (int m = 1; m < 32; m <<= 1) {
+    const bool up = (lane & m) != 0;
+    const float o0 = __shfl_xor_sync(0xffffffffu, v0, m), o1 = __shfl_xor_sync(0xffffffffu, v1, m);
+    const float o2 = __shfl_xor_sync(0xffffffffu, v2, m), o3 = __shfl_xor_sync(0xffffffffu, v3, m);
+    v0 = up ? o0 - v0 : v0 + o0;
+    v1 = up ? o1 - v1 : v1 + o1;
+    v2 = up ? o2 - v2 : v2 + o2;
+    v3 = up ? o3 - v3 : v3 + o3;
+  }
+  const float sc = 0.08838834764831845f;  // 1 / sqrt(128)
+  uint2 out;
+  *reinterpret_cast<__nv_bfloat162*>(&out.x) = __floats2bfloat162_rn(v0 * sc, v1 * sc);
+  *reinterpret_cast<__nv_bfloat162*>(&out.y) = __floats2bfloat162_rn(v2 * sc, v3 * sc);
+  reinterpret_cast<uint2*>(y + row * 128)[lane] = out;
+}
+
 // ============================================================== SwiGLU
 // in [T, 2F] = [gate | up]; out[T, F] = silu(gate) * up.
 __global__ void swiglu_fwd_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, long long T, int F) {
@@ -698,6 +731,12 @@ void rope_inplace(void* x, const float* freqs, const int* pos_ids, int T, int he
   const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
   rope_kernel<<<T, threads, 0, s>>>(static_cast<bf16*>(x), freqs, T, heads, D, rot_dim, rot_offset, t_stride,
                                     h_stride, group, rope_in_group, interleaved, mscale, sign, pos_ids, vec_ok);
+}
+
+void hadamard128(const void* x, void* y, long long rows, cudaStream_t s) {
+  if (rows == 0) return;
+  hadamard128_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, s>>>(static_cast<const bf16*>(x),
+                                                                          static_cast<bf16*>(y), rows);
 }
 
 void swiglu_fwd(const void* in, void* out, long long T, int F, cudaStream_t s) {

@@ -14,6 +14,8 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
 void rope_inplace(void* x, const float* freqs, const int* pos_ids, int T, int heads, int D, int rot_dim,
                   int rot_offset, long long t_stride, long long h_stride, int group, int rope_in_group,
                   int interleaved, float mscale, float sign, cudaStream_t s);
+// y = x H_128 / sqrt(128) on `rows` contiguous rows of 128 bf16 (x and y may alias).
+void hadamard128(const void* x, void* y, long long rows, cudaStream_t s);
 void swiglu_fwd(const void* in, void* out, long long T, int F, cudaStream_t s);
 void swiglu_bwd(const void* dout, const void* in, void* din, long long T, int F, cudaStream_t s);
 void ce_stats(const void* logits, const long long* labels, float* row_max, float* row_sum, float* tgt, long long T,

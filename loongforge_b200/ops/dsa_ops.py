@@ -17,10 +17,30 @@ from typing import Optional, Tuple
 import torch
 
 
+class _Hadamard128Fn(torch.autograd.Function):
+    """H_128 / sqrt(128) is symmetric and orthogonal: the backward is the same kernel on the gradient."""
+
+    @staticmethod
+    def forward(ctx, x):
+        from . import _ext
+        return _ext.require().hadamard128(x.contiguous())
+
+    @staticmethod
+    def backward(ctx, g):
+        from . import _ext
+        return _ext.require().hadamard128(g.contiguous())
+
+
 def hadamard_transform(x: torch.Tensor) -> torch.Tensor:
-    """x @ H_n / sqrt(n) on the last dim (n a power of two), fast Walsh-Hadamard butterflies."""
+    """x @ H_n / sqrt(n) on the last dim (n a power of two), fast Walsh-Hadamard butterflies; rows of 128 bf16 on a
+    GPU run on the warp-shuffle kernel (csrc/elementwise.cu), as the indexer's rotation does."""
     n = x.shape[-1]
     assert n & (n - 1) == 0
+    if n == 128 and x.is_cuda and x.dtype == torch.bfloat16:
+        from . import _ext
+        mod = _ext.get()
+        if mod is not None and hasattr(mod, "hadamard128"):
+            return _Hadamard128Fn.apply(x)
     y = x.float().reshape(-1, n)
     h = 1
     while h < n:

@@ -180,3 +180,69 @@ def test_validator_rule_families():
         V._validate_multimodal(ns(model_name="wan2-1-i2v", num_frames=80), dense, tc, ParallelDims())
     with pytest.raises(ValueError, match="divide by the encoder"):
         V._validate_multimodal(ns(encoder_tensor_model_parallel_size=3), dense, tc, ParallelDims(tp=4))
+
+
+def test_flags_of_the_reference_training_launchers_are_all_accepted():
+    """Every ``--flag`` that a training launcher of the reference passes to its entry point is an option of this
+    parser (the launchers are read as text; skipped when no reference tree sits beside the repository)."""
+    import glob
+    import os
+    import re
+
+    import pytest
+
+    from loongforge_b200.config.arguments import build_parser
+
+    ref = os.environ.get("LOONGFORGE_REFERENCE_DIR") or os.path.join(os.path.dirname(__file__), "..", "..", "reference")
+    scripts = [f for f in glob.glob(os.path.join(ref, "examples", "**", "*.sh"), recursive=True)
+               if "loongforge/train.py" in open(f, errors="ignore").read()]
+    if not scripts:
+        pytest.skip("no reference tree beside the repository")
+    known = {o for a in build_parser()._actions for o in a.option_strings}
+    not_ours = {"--nproc_per_node", "--nnodes", "--node_rank", "--master_addr", "--master_port", "--rdzv_backend",
+                "--rdzv_endpoint", "--rdzv_id", "--max_restarts",
+                # flags of the profiler some launchers wrap the command in
+                "--version", "--force-overwrite", "--capture-range", "--capture-range-end"}
+    unknown = {}
+    for f in scripts:
+        text = "\n".join(l for l in open(f, errors="ignore").read().splitlines() if not l.strip().startswith("#"))
+        for m in re.finditer(r"(?<![\w-])(--[a-z][a-z0-9_-]+)", text):
+            flag = m.group(1)
+            if flag in not_ours or flag in known or flag.replace("_", "-") in known:
+                continue
+            unknown.setdefault(flag, []).append(os.path.relpath(f, ref))
+    assert len(scripts) > 100 and not unknown, {k: v[:2] for k, v in unknown.items()}
+
+
+def test_model_yamls_of_the_reference_compose_unchanged(monkeypatch):
+    """The reference's own ``configs/models/**/*.yaml`` (Hydra ``_target_`` keys, defaults lists, custom resolvers) go
+    through this composer and the model-config builder as they are (skipped without a reference tree)."""
+    import glob
+    import os
+
+    import pytest
+
+    from loongforge_b200.config import yaml_compose as Y
+    from loongforge_b200.config.build import transformer_config_from_yaml
+
+    ref = os.environ.get("LOONGFORGE_REFERENCE_DIR") or os.path.join(os.path.dirname(__file__), "..", "..", "reference")
+    files = [f for f in glob.glob(os.path.join(ref, "configs", "models", "**", "*.yaml"), recursive=True)
+             if "ckpt_convert" not in f]
+    if not files:
+        pytest.skip("no reference tree beside the repository")
+    monkeypatch.setenv("LOONGFORGE_PATH", os.path.abspath(ref))
+    built = {}
+    for f in files:
+        try:
+            raw = Y.compose(f)
+        except KeyError as e:
+            if "environment variable" in str(e):
+                continue  # embodied recipes interpolate checkpoint locations from the environment
+            raise
+        node = raw.get("model", raw)
+        node = node["foundation"] if isinstance(node, dict) and "foundation" in node else node
+        built[os.path.relpath(f, ref)] = transformer_config_from_yaml({k: v for k, v in node.items() if not isinstance(v, dict)})
+    assert len(built) > 100
+    ll = built[os.path.join("configs", "models", "llama3", "llama3_8b.yaml")]
+    assert (ll.num_layers, ll.hidden_size, ll.ffn_hidden_size, ll.num_query_groups) == (32, 4096, 14336, 8)
+    assert ll.gated_linear_unit and ll.model_family == "llama"

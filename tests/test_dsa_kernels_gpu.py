@@ -135,3 +135,19 @@ def test_indexer_logits_and_topk_match_fp32(m, n, Hi, topk, packed):
     ref = ref_sc.masked_fill(torch.isinf(ref_sc), float("inf")).min(1).values
     rows = n_valid > 0
     assert (got[rows] - ref[rows]).abs().max().item() < 2e-2 * max(1.0, ref[rows].abs().max().item())
+
+
+def test_hadamard128_kernel_matches_butterflies_and_is_its_own_inverse():
+    from loongforge_b200.ops import dsa_ops
+
+    torch.manual_seed(0)
+    x = torch.randn(1000, 64, 128, device="cuda").bfloat16().requires_grad_()
+    y = dsa_ops.hadamard_transform(x)
+    n = 128
+    h = torch.tensor([[(-1) ** bin(i & j).count("1") for j in range(n)] for i in range(n)], dtype=torch.float32, device="cuda")
+    ref = x.detach().float() @ h / math.sqrt(n)
+    assert _rel(y, ref) < 5e-3
+    assert _rel(dsa_ops.hadamard_transform(y.detach()), x.detach()) < 1e-2  # H H = n I
+    g = torch.randn_like(y)
+    y.backward(g)
+    assert _rel(x.grad, g.float() @ h / math.sqrt(n)) < 5e-3
