@@ -93,8 +93,8 @@ def _validate_attention_variants(args, cfg, tc, dims) -> None:
         if tc.global_batch_size // (tc.micro_batch_size * max(dp, 1)) < 2:
             raise ValueError("--overlap-moe-expert-parallel-comm interleaves micro-batches: at least two per step are needed")
     if tc.chunkpipe_chunks and tc.chunkpipe_chunks > 1:
-        if dims.pp > 1 or dims.cp > 1 or tc.micro_batch_size != 1:
-            raise ValueError("chunk pipelining needs pp = cp = 1 and micro batch size 1")
+        if dims.cp > 1 or tc.micro_batch_size != 1 or (dims.vpp or 1) > 1:
+            raise ValueError("chunk pipelining needs cp = 1, micro batch size 1 and no virtual pipeline stages")
         if tc.seq_length % tc.chunkpipe_chunks:
             raise ValueError("--seq-length must divide by the number of chunks (seq-length / chunksize)")
 
@@ -176,9 +176,11 @@ _ACCEPTED = {
 
 def unwired_flag_notes(args) -> list:
     notes = []
+    from .arguments import build_parser
+    parser = build_parser()
     for flag, what in _ACCEPTED.items():
         v = getattr(args, flag, None)
-        if v not in (None, False, 0, "", []):
+        if v not in (None, False, 0, "", []) and v != parser.get_default(flag):  # only what the user actually set
             notes.append(f"--{flag.replace('_', '-')} was given: {what}")
     for flag, where in _LIBRARY_ONLY.items():
         v = getattr(args, flag, None)

@@ -61,28 +61,51 @@ def chunk_bounds(seq_len: int, num_chunks: int) -> List[Tuple[int, int]]:
     return [(s, min(s + size, seq_len)) for s in range(0, seq_len, size)]
 
 
-def chunkpipe_forward_backward(layers: Sequence[nn.Module], embed: Callable[[torch.Tensor], torch.Tensor],
-                               loss_fn: Callable[[torch.Tensor, int, int], torch.Tensor], tokens: torch.Tensor,
-                               num_chunks: int) -> float:
+def chunkpipe_forward_backward(layers: Sequence[nn.Module], embed: Optional[Callable[[torch.Tensor], torch.Tensor]],
+                               loss_fn: Optional[Callable[[torch.Tensor, int, int], torch.Tensor]], tokens: torch.Tensor,
+                               num_chunks: int, p2p=None) -> float:
     """Accumulates parameter gradients of ``sum_c loss_fn(hidden_c, start_c, end_c)`` and returns the loss value.
-    Peak activation memory is that of one chunk plus the K/V caches."""
+    Peak activation memory is that of one chunk plus the K/V caches.
+
+    With pipeline parallelism (`p2p`: the stage-to-stage send / receive helper of ``runtime/schedules.py``) `layers`
+    are THIS stage's layers and the chunks flow through the stages like micro-batches: in the forward phase stage s
+    works on chunk c while stage s + 1 works on chunk c - 1, in the backward phase the same in reverse chunk order.
+    Every stage keeps the K/V caches of its own layers and the chunk inputs it received (one sequence of activations
+    in total); `embed` is used on the first stage only, `loss_fn` on the last (other stages return 0)."""
+    first = p2p is None or p2p.st.is_first_stage
+    last = p2p is None or p2p.st.is_last_stage
     bounds = chunk_bounds(tokens.shape[0], num_chunks)
+    if p2p is not None and len({e - s for s, e in bounds}) != 1:
+        raise ValueError("with pipeline parallelism all chunks must have the same length")
     L = len(layers)
     caches: List[List[KV]] = [[] for _ in range(L)]  # caches[l][c] = (k, v) of chunk c at layer l
+    received: List[Optional[torch.Tensor]] = []      # chunk inputs of a later stage, kept for the recomputation
     total = 0.0
     with torch.no_grad():
         for (s, e) in bounds:
-            x = embed(tokens[s:e])
+            if first:
+                x = embed(tokens[s:e])
+            else:
+                x = p2p.recv_forward().detach()
+                received.append(x)
             for l, layer in enumerate(layers):
                 past = (torch.cat([kv[0] for kv in caches[l]]), torch.cat([kv[1] for kv in caches[l]])) if caches[l] else None
                 x, kv = layer(x, past, s)
                 caches[l].append(kv)
-            total += float(loss_fn(x, s, e))
+            if last:
+                total += float(loss_fn(x, s, e))
+            else:
+                p2p.send_forward(x)
     grads: List[List[Optional[KV]]] = [[None] * len(bounds) for _ in range(L)]  # gradient deposited on chunk c's K/V
     for c in range(len(bounds) - 1, -1, -1):
         s, e = bounds[c]
         leaves: List[Optional[KV]] = []
-        x = embed(tokens[s:e])
+        if first:
+            x_in = None
+            x = embed(tokens[s:e])
+        else:
+            x_in = received[c].detach().requires_grad_(True)
+            x = x_in
         own: List[KV] = []
         for l, layer in enumerate(layers):
             if c > 0:
@@ -94,12 +117,18 @@ def chunkpipe_forward_backward(layers: Sequence[nn.Module], embed: Callable[[tor
                 leaves.append(None)
                 x, kv = layer(x, None, s)
             own.append(kv)
-        outs, outg = [loss_fn(x, s, e)], [None]
+        if last:
+            outs, outg = [loss_fn(x, s, e)], [None]
+        else:
+            outs, outg = [x], [p2p.recv_backward()]
         for l in range(L):
             if grads[l][c] is not None:  # what later chunks want from this chunk's keys / values
                 outs += [own[l][0], own[l][1]]
                 outg += [grads[l][c][0], grads[l][c][1]]
         torch.autograd.backward(outs, outg)
+        if not first:
+            p2p.send_backward(x_in.grad)
+            received[c] = None
         for l in range(L):
             if leaves[l] is None:
                 continue
@@ -124,7 +153,8 @@ def num_microbatches_with_chunks(num_microbatches: int, num_chunks: int) -> int:
 # ----------------------------------------------------------------------------- GPT models
 def gpt_chunkpipe_step(model: nn.Module, tokens: torch.Tensor, position_ids: torch.Tensor, labels: torch.Tensor,
                        loss_mask: torch.Tensor, num_chunks: int, loss_scale: float) -> torch.Tensor:
-    """One micro-batch (ONE sequence, flat ``[T]`` tensors) of a single-stage GPT model through the chunk pipeline:
+    """One micro-batch (ONE sequence, flat ``[T]`` tensors) of a GPT model (one pipeline stage of it, when the model is
+    pipeline parallel: chunks then flow through the stages like micro-batches) through the chunk pipeline:
     accumulates the gradients of ``loss_scale * sum(loss * mask)`` and returns that loss value. Attention layers
     take the earlier chunks' keys / values through ``models.transformer.CHUNK_PREFIX``; every other sub-layer (norms,
     dense and MoE MLPs, the fused linear + cross-entropy head) is token-local and runs on the chunk alone. Tensor
@@ -133,7 +163,6 @@ def gpt_chunkpipe_step(model: nn.Module, tokens: torch.Tensor, position_ids: tor
     from ..models import transformer as TF
 
     cfg = model.cfg
-    assert model.pre_process and model.post_process, "chunk pipelining needs the whole model on this rank"
     assert not (cfg.multi_latent_attention or cfg.enable_hyper_connections or cfg.csa_compress_ratios
                 or cfg.layer_types or cfg.full_attention_interval or cfg.mtp_num_layers), \
         "chunk pipelining covers softmax-attention GPT layers"
@@ -166,6 +195,12 @@ def gpt_chunkpipe_step(model: nn.Module, tokens: torch.Tensor, position_ids: tor
         losses = model.postprocess(hidden, labels[s:e], loss_mask[s:e], loss_scale)
         return (losses * mask_f[s:e]).sum() * loss_scale
 
-    total = chunkpipe_forward_backward([_Layer(l) for l in model.decoder.layers], model.embed, loss_fn, tokens,
-                                       num_chunks)
+    p2p = None
+    if st.dims.pp > 1:
+        from .schedules import P2P
+        width = cfg.hidden_size * (cfg.num_residual_streams if cfg.enable_hyper_connections else 1)
+        p2p = P2P(((bounds[0][1] - bounds[0][0]) // sp_factor, width), cfg.params_dtype, dev)
+    total = chunkpipe_forward_backward([_Layer(l) for l in model.decoder.layers],
+                                       model.embed if model.pre_process else None,
+                                       loss_fn if model.post_process else None, tokens, num_chunks, p2p=p2p)
     return torch.tensor(total, device=dev)

@@ -580,8 +580,8 @@ class Trainer:
         from .chunkpipe import gpt_chunkpipe_step
 
         t, st = self.tcfg, self.st
-        if st.dims.pp > 1 or st.dims.cp > 1 or t.micro_batch_size != 1:
-            raise ValueError("chunk pipelining needs pp = cp = 1 and micro batch size 1")
+        if st.dims.cp > 1 or t.micro_batch_size != 1 or len(self.models) != 1:
+            raise ValueError("chunk pipelining needs cp = 1, micro batch size 1 and no virtual pipeline stages")
         model = self.models[0]
         nmb = self.mb_calc.num_microbatches
         reports = []
@@ -593,7 +593,8 @@ class Trainer:
                 scale = 1.0 / (max(n_valid, 1) * nmb)
                 loss = gpt_chunkpipe_step(model.module, b["tokens"].reshape(-1), b["position_ids"].reshape(-1),
                                           b["labels"].reshape(-1), mask, t.chunkpipe_chunks, scale)
-                reports.append({"lm loss": loss * nmb, "num_tokens": n_valid})
+                if st.is_last_stage:
+                    reports.append({"lm loss": loss * nmb, "num_tokens": n_valid})
         return reports
 
     def _allreduce_embedding_grads(self):

@@ -111,3 +111,33 @@ def test_chunk_pipelining_under_tensor_parallelism(sp):
     got = run_distributed(_chunk_tp, 2, 4, {"tp": 2}, sp)[0]
     for (l0, g0), (l1, g1) in zip(ref, got):
         assert abs(l0 - l1) < 1e-4 * abs(l0) and abs(g0 - g1) < 1e-3 * max(1, g0), (ref, got)
+
+
+def _chunk_pp(rank, world, chunks, dims_kw):
+    from loongforge_b200.data.synthetic import synthetic_batch_iterator
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel.state import ParallelDims
+    from loongforge_b200.runtime.trainer import TrainConfig, Trainer
+
+    cfg = get_model_config("tiny-llama", num_layers=4)
+    cfg.sequence_parallel = dims_kw.get("tp", 1) > 1
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=2, seq_length=64, train_iters=2, lr=1e-3, log_interval=1000,
+                     chunkpipe_chunks=chunks, clip_grad=1.0)
+    tr = Trainer(cfg, tc, ParallelDims(**dims_kw))
+    it = synthetic_batch_iterator(cfg.vocab_size, 64, 1, seed=4, pin_memory=False)
+    return [(m.get("lm loss"), m["grad_norm"]) for m in (tr.train_step(it) for _ in range(2))]
+
+
+@pytest.mark.parametrize("dims,world", [({"pp": 2}, 2), ({"pp": 2, "tp": 2}, 4)])
+def test_chunks_flow_through_pipeline_stages(dims, world):
+    """Chunk pipelining with pipeline parallelism: every stage keeps the K/V caches of its layers, chunks travel between
+    stages like micro-batches (forward in order, backward in reverse); same trajectory as whole sequences on one rank."""
+    from dist_utils import run_distributed
+
+    ref = run_distributed(_chunk_pp, 1, 0, {})[0]
+    got = run_distributed(_chunk_pp, world, 4, dict(dims))
+    last = got[world - 1]  # a rank of the last stage reports the loss
+    for (l0, g0), (l1, g1) in zip(ref, last):
+        assert l1 is not None and abs(l0 - l1) < 1e-4 * abs(l0) and abs(g0 - g1) < 1e-3 * max(1, g0), (ref, got)
+    for (_, g0), (_, g1) in zip(ref, got[0]):
+        assert abs(g0 - g1) < 1e-3 * max(1, g0)  # the global gradient norm is the same on every stage
