@@ -187,7 +187,10 @@ class GPTModel(nn.Module):
                                    self.cfg.rope_3d_freq_allocation)
         if self.cfg.position_embedding_type == "mrope" or position_ids.dim() == 2 and position_ids.shape[0] == 3:
             return self.rotary.mrope(position_ids)
-        n_pos = max(self.cfg.max_position_embeddings, n_tokens)
+        # position ids index the table: under context parallelism a rank holds n_tokens of a row that is cp times as
+        # long, so its ids run up to cp * n_tokens - 1 (an index past the table would be read as garbage on a GPU)
+        cp = max(ps.get_state(self.state_name).dims.cp, 1) if ps.model_parallel_is_initialized() else 1
+        n_pos = max(self.cfg.max_position_embeddings, n_tokens * cp)
         r = self.rotary.table(n_pos, device)
         return RotaryInputs(freqs=r.freqs, pos_ids=position_ids.to(torch.int32), mscale=r.mscale)
 

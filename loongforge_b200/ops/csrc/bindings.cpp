@@ -321,8 +321,10 @@ void sumsq_(const at::Tensor& x, at::Tensor out) {
   c10::cuda::CUDAGuard guard(x.device());
   const bool b = x.scalar_type() == at::kBFloat16;
   TORCH_CHECK(b || x.scalar_type() == at::kFloat);
-  lf::sumsq(x.data_ptr(), b, x.numel(), out.data_ptr<float>(), cur_stream());
-  ++g_launches;
+  if (x.numel() == 0) return;
+  at::Tensor partial = at::empty({lf::sumsq_partials(x.numel())}, out.options());
+  lf::sumsq(x.data_ptr(), b, x.numel(), out.data_ptr<float>(), partial.data_ptr<float>(), cur_stream());
+  g_launches += 2;
 }
 
 #ifdef LF_HAVE_ATTN

@@ -644,7 +644,7 @@ rmsnorm_bwd_warp_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
 }
 
 template <typename T>
-__global__ void sumsq_kernel(const T* __restrict__ x, long long n, float* __restrict__ out) {
+__global__ void sumsq_kernel(const T* __restrict__ x, long long n, float* __restrict__ partial) {
   __shared__ float sh[32];
   float s = 0.f;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
@@ -653,7 +653,16 @@ __global__ void sumsq_kernel(const T* __restrict__ x, long long n, float* __rest
     s += f * f;
   }
   s = block_sum<256>(s, sh);
-  if (threadIdx.x == 0) atomicAdd(out, s);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+// out[0] += sum of the per-CTA partials, added up in a fixed order: the result does not depend on which CTA finished
+// first, so the gradient norm (and with it the clipping factor) is the same bit pattern on every run.
+__global__ void sumsq_final_kernel(const float* __restrict__ partial, int count, float* __restrict__ out) {
+  __shared__ float sh[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < count; i += 256) s += partial[i];
+  s = block_sum<256>(s, sh);
+  if (threadIdx.x == 0) out[0] += s;
 }
 
 // ---------------------------------------------------------------------------- launchers
@@ -829,13 +838,16 @@ void master_join(const void* w, const void* lo, float* master, long long n, cuda
                                                                 static_cast<const short*>(lo), master, n);
 }
 
-void sumsq(const void* x, int is_bf16, long long n, float* out, cudaStream_t s) {
+int sumsq_partials(long long n) { return grid_for(n, 256, 148 * 8); }
+
+void sumsq(const void* x, int is_bf16, long long n, float* out, float* partial, cudaStream_t s) {
   if (n == 0) return;
-  const int grid = grid_for(n, 256, 148 * 8);
+  const int grid = sumsq_partials(n);
   if (is_bf16)
-    sumsq_kernel<bf16><<<grid, 256, 0, s>>>(static_cast<const bf16*>(x), n, out);
+    sumsq_kernel<bf16><<<grid, 256, 0, s>>>(static_cast<const bf16*>(x), n, partial);
   else
-    sumsq_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), n, out);
+    sumsq_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), n, partial);
+  sumsq_final_kernel<<<1, 256, 0, s>>>(partial, grid, out);
 }
 
 }  // namespace lf

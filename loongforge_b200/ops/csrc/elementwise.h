@@ -30,7 +30,10 @@ void adam_step_remainder(void* w, void* lo, const void* grad, int grad_is_bf16, 
                          float grad_scale, cudaStream_t s);
 void master_split(const float* master, void* w, void* lo, long long n, int write_w, cudaStream_t s);
 void master_join(const void* w, const void* lo, float* master, long long n, cudaStream_t s);
-void sumsq(const void* x, int is_bf16, long long n, float* out, cudaStream_t s);
+// out[0] += sum x^2, deterministic: per-CTA partial sums go to `partial` (at least sumsq_partials(n) floats of
+// scratch) and are added in a fixed order.
+int sumsq_partials(long long n);
+void sumsq(const void* x, int is_bf16, long long n, float* out, float* partial, cudaStream_t s);
 
 // MoE router (router.cu). score: 0 softmax over the selected k, 1 softmax over all experts then top-k, 2 sigmoid.
 struct RouterArgs {

@@ -122,3 +122,16 @@ def test_two_level_context_parallel_matches_single_process():
     res = run_distributed(_run_cp_two_level, 4)
     for (l0, g0), (l1, g1) in zip(ref, res[0]):
         assert abs(l0 - l1) < 5e-4 * abs(l0) and abs(g0 - g1) < 5e-4 * max(1.0, abs(g0)), (ref, res[0])
+
+
+def _run_cp_short_table(rank, world):
+    return _run(rank, world, "tiny-llama", {"cp": 2}, 2, {"max_position_embeddings": 16})
+
+
+def test_context_parallel_rows_longer_than_the_trained_context():
+    """The rotary table must cover the positions of the whole row (cp x the rank's tokens), not only as many rows as the
+    rank holds tokens: 64-token rows, 32 tokens per rank, a configured context of 16."""
+    ref = _single("tiny-llama", 2, {"max_position_embeddings": 16})
+    res = run_distributed(_run_cp_short_table, 2)
+    for (l0, _), (l1, _) in zip(ref, res[0]):
+        assert abs(l0 - l1) < 5e-4 * abs(l0), (l0, l1)
