@@ -1,4 +1,4 @@
-"""GR00T N1.6 vision-language-action policy (reference: loongforge/embodied/model/groot_n1_6/modeling_groot_n1_6.py
+"""GR00T N1.6 / N1.7 vision-language-action policy (reference: loongforge/embodied/model/groot_n1_6/modeling_groot_n1_6.py
 :74-896, modules/dit.py:35-420, modules/embodiment_mlp.py:67-250, eagle3_model/).
 
 Two parts.
@@ -16,6 +16,10 @@ Two parts.
 Flow matching (note the direction, opposite to Pi0.5): ``x_t = (1 - t) * noise + t * actions``, target
 ``actions - noise``, ``t = (1 - Beta(1.5, 1)) * 0.999`` discretised into 1000 buckets for the time embedding; sampling
 integrates from noise (t = 0) with `num_inference_timesteps` Euler steps.
+
+N1.7 (``GrootConfig.n1_7``; reference loongforge/embodied/model/groot_n1_7/modeling_groot_n1_7.py:45-290) adds a 4-layer
+self-attention transformer over the backbone features before the DiT reads them, state dropout with a learned mask
+token, and larger state / action paddings (132) with a 40-step horizon.
 
 `GROOT_HEAD_NAME_MAP` / `convert_groot_state_dict` translate the public GR00T checkpoints' parameter names
 (``action_head.model.transformer_blocks.N.attn1.to_q`` ...) to the names used here."""
@@ -69,6 +73,19 @@ class GrootConfig:
     num_timestep_buckets: int = 1000
     tune_llm: bool = False
     tune_visual: bool = False
+    # GR00T N1.7 additions: a small self-attention transformer over the backbone features before the DiT reads them,
+    # and state dropout (the state token is replaced by a learned mask token with this probability while training)
+    vl_self_attention_layers: int = 0
+    vl_self_attention_heads: int = 32
+    state_dropout_prob: float = 0.0
+
+    @staticmethod
+    def n1_7(**kw) -> "GrootConfig":
+        """GR00T N1.7 geometry (reference: loongforge/embodied/model/groot_n1_7/model_configuration_groot_n1_7.py:30-95)."""
+        base = dict(max_state_dim=132, max_action_dim=132, action_horizon=40, vl_self_attention_layers=4,
+                    vl_self_attention_heads=32, state_dropout_prob=0.2)
+        base.update(kw)
+        return GrootConfig(**base)
 
     @staticmethod
     def tiny(**kw) -> "GrootConfig":
@@ -303,12 +320,38 @@ class AlternateVLDiT(nn.Module):
         return self.proj_out_2(self.norm_out(x) * (1 + scale[:, None]) + shift[:, None])
 
 
+class VLSelfAttention(nn.Module):
+    """Pre-norm self-attention + feed-forward blocks over the backbone features (padded positions masked as keys)."""
+
+    def __init__(self, c: GrootConfig):
+        super().__init__()
+        d, self.h = c.llm_width, c.vl_self_attention_heads
+        self.blocks = nn.ModuleList([nn.ModuleDict(dict(
+            norm1=nn.LayerNorm(d), to_q=nn.Linear(d, d), to_k=nn.Linear(d, d), to_v=nn.Linear(d, d), to_out=nn.Linear(d, d),
+            norm3=nn.LayerNorm(d), ff_in=nn.Linear(d, 4 * d), ff_out=nn.Linear(4 * d, d)))
+            for _ in range(c.vl_self_attention_layers)])
+        self.drop = nn.Dropout(c.dropout)
+
+    def forward(self, x, valid):
+        B, L, D = x.shape
+        sp = lambda t: t.view(B, L, self.h, D // self.h).transpose(1, 2)  # noqa: E731
+        m = valid[:, None, None, :]
+        for b in self.blocks:
+            h = b["norm1"](x)
+            o = F.scaled_dot_product_attention(sp(b["to_q"](h)), sp(b["to_k"](h)), sp(b["to_v"](h)), attn_mask=m)
+            x = x + self.drop(b["to_out"](o.transpose(1, 2).reshape(B, L, D)))
+            x = x + self.drop(b["ff_out"](F.gelu(b["ff_in"](b["norm3"](x)), approximate="tanh")))
+        return x
+
+
 class GrootActionHead(nn.Module):
     def __init__(self, c: GrootConfig):
         super().__init__()
         self.c = c
         n = c.max_num_embodiments
         self.model = AlternateVLDiT(c)
+        self.vl_self_attention = VLSelfAttention(c) if c.vl_self_attention_layers > 0 else None
+        self.mask_token = nn.Parameter(0.02 * torch.randn(1, 1, c.input_embedding_dim)) if c.state_dropout_prob > 0 else None
         self.state_encoder = CategoryMLP(n, c.max_state_dim, c.hidden_size, c.input_embedding_dim)
         self.action_encoder = ActionEncoder(n, c.max_action_dim, c.input_embedding_dim)
         self.action_decoder = CategoryMLP(n, c.hidden_size, c.hidden_size, c.max_action_dim)
@@ -319,9 +362,15 @@ class GrootActionHead(nn.Module):
     def velocity(self, feats, valid, is_image, state, x_t, t_bucket, ids):
         c = self.c
         s = self.state_encoder(F.pad(state, (0, c.max_state_dim - state.shape[-1])).unsqueeze(1), ids)
+        if self.mask_token is not None and self.training:
+            drop = torch.rand(s.shape[0], 1, 1, device=s.device) < c.state_dropout_prob
+            s = torch.where(drop, self.mask_token.to(s.dtype), s)
+        feats = self.vlln(feats)
+        if self.vl_self_attention is not None:
+            feats = self.vl_self_attention(feats, valid)
         a = self.action_encoder(F.pad(x_t, (0, c.max_action_dim - x_t.shape[-1])), t_bucket, ids)
         a = a + self.position_embedding.weight[: a.shape[1]].to(a.dtype)
-        out = self.model(torch.cat([s, a], dim=1), self.vlln(feats), t_bucket, valid, is_image)
+        out = self.model(torch.cat([s, a], dim=1), feats, t_bucket, valid, is_image)
         return self.action_decoder(out, ids)[:, -x_t.shape[1]:, : x_t.shape[-1]]
 
 
@@ -395,6 +444,10 @@ GROOT_HEAD_NAME_MAP: List[Tuple[str, str]] = [
     (_AH + "model.proj_out_2.{wb}", "action_head.model.proj_out_2.{wb}"),
     (_AH + "vlln.{wb}", "action_head.vlln.{wb}"),
     (_AH + "position_embedding.weight", "action_head.position_embedding.weight"),
+    (_AH + "mask_token", "action_head.mask_token"),
+] + [(_AH + f"vl_self_attention.transformer_blocks.{{i}}.{there}.{{wb}}", f"action_head.vl_self_attention.blocks.{{i}}.{here}.{{wb}}")
+     for there, here in (("norm1", "norm1"), ("attn1.to_q", "to_q"), ("attn1.to_k", "to_k"), ("attn1.to_v", "to_v"),
+                         ("attn1.to_out.0", "to_out"), ("norm3", "norm3"), ("ff.net.0.proj", "ff_in"), ("ff.net.2", "ff_out"))
 ] + [(_AH + f"{m}.{l}.{p}", f"action_head.{m}.{l}.{p}") for m, ls in (("state_encoder", ("layer1", "layer2")),
                                                                      ("action_decoder", ("layer1", "layer2")),
                                                                      ("action_encoder", ("W1", "W2", "W3")))
@@ -408,10 +461,11 @@ def convert_groot_state_dict(sd: Dict[str, torch.Tensor], cfg: GrootConfig, to_p
     out, used = {}, set()
     for there, here in GROOT_HEAD_NAME_MAP:
         a, b = (here, there) if to_public else (there, here)
-        for i in (range(cfg.dit_layers) if "{i}" in there else [None]):
+        depth = cfg.vl_self_attention_layers if "vl_self_attention" in there else cfg.dit_layers
+        for i in (range(depth) if "{i}" in there else [None]):
             for wb in (("weight", "bias") if "{wb}" in there else (None,)):
                 ka = a.replace("{i}", str(i)).replace("{wb}", wb or "")
-                if ka in sd:
+                if ka in sd and ka not in used:
                     out[b.replace("{i}", str(i)).replace("{wb}", wb or "")] = sd[ka]
                     used.add(ka)
     left = [k for k in sd if k not in used and not (head_only and k.startswith("backbone."))]

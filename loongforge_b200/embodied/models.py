@@ -8,8 +8,9 @@ pi05           own architecture in ``embodied/pi05.py`` (PaliGemma-style prefix 
                shared attention and adaptive RMSNorm); the skeleton below only with ``architecture: skeleton``
 groot_n1_6     own architecture in ``embodied/groot.py`` (Eagle backbone + alternating vision / language DiT
                action head with embodiment-specific encoders)
-groot_n1_7     Qwen3 backbone + DiT action head
-xvla           Florence-2 style encoder-decoder features + soft-prompted action transformer
+groot_n1_7     ``embodied/groot.py`` with the N1.7 additions (self-attention over the backbone features, state dropout)
+xvla           own architecture in ``embodied/xvla.py`` (DaViT-style tower + BART-style fusion encoder, domain-aware
+               soft-prompted transformer, action spaces with regressed and gripper-logit channels)
 lingbot_va     WAN video-DiT backbone streaming latents, action tokens decoded jointly
 fastwam        WAN DiT + VAE latents, mixture-of-transformers action branch
 dreamzero      causal WAN world model with an action head on the denoised latents
@@ -237,7 +238,7 @@ class _BatchAdapter(nn.Module):
 def _dedicated_policy(name: str, args, overrides: dict) -> Optional[nn.Module]:
     """Pi0.5 and GR00T N1.6 have architectures of their own. ``model_overrides: {size: tiny}`` selects the small test
     geometry, any other key overrides a field of the architecture's configuration."""
-    if name not in ("pi05", "groot_n1_6"):
+    if name not in ("pi05", "groot_n1_6", "groot_n1_7", "xvla"):
         return None
     kw = dict(getattr(args, "model_overrides", None) or {}) if args is not None else {}
     kw.update(overrides)
@@ -256,12 +257,28 @@ def _dedicated_policy(name: str, args, overrides: dict) -> Optional[nn.Module]:
         kw = {k: v for k, v in kw.items() if k in fields}
         cfg = Pi05Config.tiny(**kw) if size == "tiny" else Pi05Config(**kw)
         return _BatchAdapter(Pi05Policy(cfg))
+    if name == "xvla":
+        from .xvla import XVLAConfig, XVLAPolicy
+        kw["num_actions"] = kw.pop("action_horizon", kw.get("num_actions", 30))
+        if args is not None:
+            kw.setdefault("num_views", args.num_cameras)
+        if "action_space" not in kw:  # any robot: regress the real channels, pad to the model's width
+            kw["action_space"] = "auto"
+            kw["max_action_dim"] = max(kw.get("max_action_dim", 20 if size != "tiny" else 8), kw.get("action_dim", 7))
+        fields = {f.name for f in dataclasses.fields(XVLAConfig)}
+        kw = {k: v for k, v in kw.items() if k in fields}
+        cfg = XVLAConfig.tiny(**kw) if size == "tiny" else XVLAConfig(**kw)
+        return _BatchAdapter(XVLAPolicy(cfg))
     from .groot import GrootConfig, GrootPolicy
     if args is not None:
         kw.setdefault("state_dim", args.state_dim)
     fields = {f.name for f in dataclasses.fields(GrootConfig)}
     kw = {k: v for k, v in kw.items() if k in fields}
-    cfg = GrootConfig.tiny(**kw) if size == "tiny" else GrootConfig(**kw)
+    if name == "groot_n1_7":
+        extra = dict(vl_self_attention_layers=2, vl_self_attention_heads=4, state_dropout_prob=0.2) if size == "tiny" else {}
+        cfg = GrootConfig.tiny(**{**extra, **kw}) if size == "tiny" else GrootConfig.n1_7(**kw)
+    else:
+        cfg = GrootConfig.tiny(**kw) if size == "tiny" else GrootConfig(**kw)
     return _BatchAdapter(GrootPolicy(cfg))
 
 

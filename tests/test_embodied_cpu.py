@@ -1,6 +1,7 @@
 """Embodied stack on CPU: config layers, policies, trainer (single process, DDP / ZeRO-1 / FSDP over gloo), resume,
 LoRA, optimizer pieces, eval transport + decoders + orchestrator."""
 import json
+import math
 import os
 
 import numpy as np
@@ -268,3 +269,32 @@ def test_eval_command_line_serves_a_trained_checkpoint_and_runs_episodes(tmp_pat
         srv.stop()
     rep = json.load(open(tmp_path / "ev" / "report.json"))
     assert len(rep["episodes"]) == 2
+
+
+def test_xvla_domains_action_spaces_and_sampler():
+    """X-VLA: another domain id selects other encoder / decoder matrices and soft prompts; gripper channels are logits
+    (zeroed in the inputs, sigmoid in the sampler's output); a padded view contributes nothing."""
+    from loongforge_b200.embodied.xvla import EE6DSpace, XVLAConfig, XVLAPolicy
+
+    torch.manual_seed(0)
+    c = XVLAConfig.tiny(action_space="ee6d", action_dim=20, max_action_dim=20)
+    m = XVLAPolicy(c).eval()
+    B = 2
+    obs = {"images": torch.randn(B, 2, 3, 32, 32), "tokens": torch.randint(0, 100, (B, 9)), "state": torch.randn(B, 20),
+           "domain_id": torch.tensor([1, 1])}
+    noise = torch.randn(B, 4, 20)
+    a1 = m.predict_action(obs, steps=2, noise=noise)
+    a2 = m.predict_action(dict(obs, domain_id=torch.tensor([1, 2])), steps=2, noise=noise)
+    assert torch.allclose(a1[0], a2[0], atol=1e-6) and not torch.allclose(a1[1], a2[1], atol=1e-4)
+    assert ((a1[..., [9, 19]] >= 0) & (a1[..., [9, 19]] <= 1)).all()  # gripper probabilities
+    # the second view masked out == the second view replaced by anything
+    masked = dict(obs, image_masks=torch.tensor([[1, 0], [1, 0]]).bool())
+    other = dict(masked, images=torch.cat([obs["images"][:, :1], torch.randn(B, 1, 3, 32, 32)], 1))
+    assert torch.allclose(m.predict_action(masked, steps=1, noise=noise), m.predict_action(other, steps=1, noise=noise), atol=1e-6)
+    sp = EE6DSpace()
+    pred, tgt = torch.zeros(2, 3, 20), torch.zeros(2, 3, 20)
+    tgt[..., 0] = 0.1
+    l = sp.compute_loss(pred, tgt)
+    assert abs(float(l["regress_0"]) - 500.0 * 0.01 / 3) < 1e-5 and abs(float(l["gripper"]) - math.log(2.0)) < 1e-6
+    l2 = sp.compute_loss(pred, tgt, valid=torch.tensor([True, False]))
+    assert abs(float(l2["regress_0"]) - float(l["regress_0"])) < 1e-6  # padded rows leave the mean over valid rows unchanged
