@@ -253,6 +253,11 @@ def _add_peft_args(p):
     g.add_argument("--lora-alpha", type=int, default=32)
     g.add_argument("--lora-dropout", type=float, default=0.0)
     g.add_argument("--lora-target-modules", nargs="*", default=["linear_qkv", "linear_proj", "linear_fc1", "linear_fc2"])
+    g.add_argument("--lora-apply-to-image-encoder", action="store_true",
+                   help="vision-language models: adapters on the vision tower's linears as well")
+    g.add_argument("--lora-apply-to-image-projector", action="store_true")
+    g.add_argument("--lora-skip-foundation", action="store_true",
+                   help="vision-language models: no adapters on the language model (it keeps training or stays frozen)")
 
 
 # (flag, kind, default) with kind: "flag" store_true, "noflag" store_false, int / float / str, "list" nargs="*".

@@ -121,11 +121,12 @@ def _canonical_splits(name: str, mod) -> Optional[List[int]]:
 
 def apply_lora(model: nn.Module, rank: int = 16, alpha: float = 32, dropout: float = 0.0,
                targets: Iterable[str] = ("linear_qkv", "linear_proj", "linear_fc1", "linear_fc2"),
-               canonical: bool = False) -> List[str]:
-    """Wrap target linears in place; returns the wrapped module names. Everything else is frozen."""
+               canonical: bool = False, freeze_rest: bool = True) -> List[str]:
+    """Wrap target linears in place; returns the wrapped module names. Everything else is frozen (``freeze_rest``)."""
     targets = tuple(targets)
-    for p in model.parameters():
-        p.requires_grad_(False)
+    if freeze_rest:
+        for p in model.parameters():
+            p.requires_grad_(False)
     wrapped = []
     for name, mod in list(model.named_modules()):
         if not isinstance(mod, (PL.ColumnParallelLinear, PL.RowParallelLinear)):
@@ -136,6 +137,38 @@ def apply_lora(model: nn.Module, rank: int = 16, alpha: float = 32, dropout: flo
         splits = _canonical_splits(name, mod) if canonical else None
         setattr(parent, name.split(".")[-1], LoRALinear(mod, rank, alpha, dropout, key=name, splits=splits))
         wrapped.append(name)
+    return wrapped
+
+
+VLM_COMPONENTS = ("foundation", "image_encoder", "image_projector")
+
+
+def apply_vlm_lora(omni: nn.Module, *, apply_to_foundation: bool = True, apply_to_image_encoder: bool = False,
+                   apply_to_image_projector: bool = False, frozen: Iterable[str] = (), **lora_kw) -> Dict[str, List[str]]:
+    """Adapters per component of a vision-language model (reference: the component prefixes of
+    loongforge/train/training_utils.py:645-700). A component that gets adapters has its base weights frozen and its
+    adapters trained; a component without adapters keeps its own training state (trainable, or frozen when it is listed
+    in `frozen`). Asking for adapters on a component that is also listed as frozen is an error, as in the reference."""
+    want = {"foundation": apply_to_foundation, "image_encoder": apply_to_image_encoder,
+            "image_projector": apply_to_image_projector}
+    frozen = set(frozen)
+    for comp in VLM_COMPONENTS:
+        if want[comp] and comp in frozen:
+            raise ValueError(f"cannot freeze the {comp.replace('_', ' ')} when adapters are applied to it")
+    enc = getattr(omni, "encoder_model", None)
+    mods = {"foundation": getattr(omni, "foundation_model", None),
+            "image_encoder": getattr(enc, "image_encoder", None) if enc is not None else None,
+            "image_projector": getattr(enc, "image_projector", None) if enc is not None else None}
+    wrapped: Dict[str, List[str]] = {}
+    for comp in VLM_COMPONENTS:
+        m = mods[comp]
+        if m is None:
+            continue
+        if want[comp]:
+            wrapped[comp] = apply_lora(m, **lora_kw)
+        elif comp in frozen:
+            for p in m.parameters():
+                p.requires_grad_(False)
     return wrapped
 
 

@@ -105,8 +105,9 @@ class VLMTrainer(Trainer):
     def _default_model_provider(self, pre_process, post_process, layer_numbers):
         model = self._build_omni(pre_process, post_process, layer_numbers)
         if self._lora:
-            from ..models.peft import apply_lora
-            apply_lora(model.foundation_model, **self._lora)
+            # adapters per component: {"apply_to_image_encoder": True, ...} next to the usual rank / alpha / targets
+            from ..models.peft import apply_vlm_lora
+            apply_vlm_lora(model, frozen=("image_encoder",) if self.freeze_encoder else (), **self._lora)
         return model
 
     def _build_omni(self, pre_process, post_process, layer_numbers):

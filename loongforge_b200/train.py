@@ -67,6 +67,10 @@ def main(argv: Optional[List[str]] = None) -> int:
     if getattr(args, "peft_type", None) and train_cfg.training_phase == "sft" and "lora" not in extra:
         extra["lora"] = dict(rank=args.lora_rank, alpha=args.lora_alpha, dropout=args.lora_dropout,
                              targets=tuple(args.lora_target_modules), canonical=args.peft_type == "canonical_lora")
+        if isinstance(enc, dict):  # vision-language model: which components get adapters
+            extra["lora"].update(apply_to_foundation=not getattr(args, "lora_skip_foundation", False),
+                                 apply_to_image_encoder=bool(getattr(args, "lora_apply_to_image_encoder", False)),
+                                 apply_to_image_projector=bool(getattr(args, "lora_apply_to_image_projector", False)))
     from .runtime.diffusion_trainer import build_diffusion_trainer, is_diffusion_model
     if is_diffusion_model(args.model_name):
         # diffusion transformers (WAN, Qwen-Image): their own model configuration, the common loop around it

@@ -169,3 +169,48 @@ def test_pretrain_data_path_split_blend_and_evaluation(tmp_path):
     evals = re.findall(r"validation loss at iteration (\d+) \| lm loss value: ([0-9.E+-]+) \| lm loss PPL: ([0-9.E+-]+)",
                        p.stdout)
     assert [int(e[0]) for e in evals] == [2, 4] and all(float(e[1]) < 8.0 for e in evals)
+
+
+def test_vlm_lora_per_component():
+    """Adapters on chosen components of a vision-language model: the language model alone (default), the vision tower
+    and projector as well; a component that is frozen cannot also get adapters."""
+    import pytest
+    import torch
+
+    from loongforge_b200.models.omni import OmniCombinationModel
+    from loongforge_b200.models.peft import apply_vlm_lora
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(ps.ParallelDims())
+    try:
+        def build():
+            lm = get_model_config("tiny-llama", position_embedding_type="mrope", mrope_section=[8, 12, 12])
+            return OmniCombinationModel(lm, get_model_config("tiny-vit"), image_token_id=lm.vocab_size - 1)
+
+        def trainable(m):
+            return {n for n, p in m.named_parameters() if p.requires_grad}
+
+        m = build()
+        w = apply_vlm_lora(m, rank=2, alpha=4)
+        t = trainable(m)
+        assert set(w) == {"foundation"} and w["foundation"]
+        assert all("lora_" in n for n in t if n.startswith("foundation_model."))
+        assert any(n.startswith("encoder_model.image_encoder.") for n in t)  # untouched component keeps training
+
+        m = build()
+        w = apply_vlm_lora(m, rank=2, alpha=4, apply_to_image_encoder=True, apply_to_image_projector=True)
+        t = trainable(m)
+        assert set(w) == {"foundation", "image_encoder", "image_projector"} and w["image_encoder"]
+        assert all("lora_" in n for n in t), sorted(t)[:5]
+
+        m = build()
+        apply_vlm_lora(m, rank=2, alpha=4, apply_to_foundation=False, apply_to_image_encoder=True, frozen=("image_projector",))
+        t = trainable(m)
+        assert not any(n.startswith("encoder_model.image_projector.") for n in t)
+        assert any(n.startswith("foundation_model.") and "lora_" not in n for n in t)
+        with pytest.raises(ValueError, match="cannot freeze"):
+            apply_vlm_lora(build(), rank=2, apply_to_image_encoder=True, frozen=("image_encoder",))
+    finally:
+        ps.destroy_model_parallel()
