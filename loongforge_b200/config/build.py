@@ -132,6 +132,7 @@ _FLAG_TO_CFG = {"swiglu": ("activation", "swiglu"), "add_qkv_bias": ("add_qkv_bi
                 "moe_router_pre_softmax": ("moe_router_pre_softmax", True),
                 "moe_router_enable_expert_bias": ("moe_router_enable_expert_bias", True),
                 "multi_latent_attention": ("multi_latent_attention", True), "use_dsa_fused": ("use_dsa", True),
+                "use_dsa_sp_first": ("dsa_sp_first", True),
                 "sequence_parallel": ("sequence_parallel", True), "tp_comm_overlap": ("tp_comm_overlap", True),
                 "no_gradient_accumulation_fusion": ("gradient_accumulation_fusion", False),
                 "moe_grouped_gemm": ("moe_grouped_gemm", True),

@@ -76,8 +76,13 @@ def _validate_sft(args, tc) -> None:
 
 def _validate_attention_variants(args, cfg, tc, dims) -> None:
     """Sparse attention / chunk pipelining / overlap-schedule combinations (reference: validators.py:314-366)."""
-    if getattr(args, "use_dsa_sp_first", False) and not cfg.sequence_parallel:
-        raise ValueError("--use-dsa-sp-first requires --sequence-parallel")
+    if getattr(args, "use_dsa_sp_first", False) or getattr(cfg, "dsa_sp_first", False):
+        if not cfg.sequence_parallel:
+            raise ValueError("--use-dsa-sp-first requires --sequence-parallel")
+        if not getattr(cfg, "use_dsa", False):
+            raise ValueError("--use-dsa-sp-first requires the sparse attention variant (--use-dsa-fused)")
+        if dims.cp > 1:
+            raise ValueError("--use-dsa-sp-first does not combine with context parallelism")
     share = getattr(cfg, "dsa_indexer_topk_freq", 1) or 1
     if share > 1 and not getattr(cfg, "use_dsa", False):
         raise ValueError("--dsa-indexer-topk-freq > 1 (IndexShare) requires the sparse attention variant")
@@ -150,7 +155,6 @@ _LIBRARY_ONLY = {
 # which only one exists here. They are accepted so that the reference's launch scripts run unchanged; when one is given,
 # the note says what happens instead.
 _ACCEPTED = {
-    "use_dsa_sp_first": "sparse attention runs head-parallel under TP with a replicated indexer; there is no separate sequence-first mode",
     "absorb_backend": "the MLA absorb products use one einsum formulation",
     "moe_permute_fusion": "token permutation is always fused into the dispatch path",
     "delay_wgrad_compute": "weight gradients are computed with their data gradients",

@@ -97,6 +97,9 @@ class TransformerConfig:
     # IndexShare (GLM-5.2): only some layers own an indexer; the others reuse the latest computed top-k indices.
     # Layers below the offset and every `freq`-th layer from (offset + freq - 1) on compute their own.
     dsa_indexer_topk_freq: int = 1
+    # sequence-first sparse attention under TP + SP: every rank attends from ITS tokens with ALL heads (up projections
+    # and the output projection replicated); only the 576-value compressed keys and the indexer keys are gathered
+    dsa_sp_first: bool = False
     dsa_indexer_skip_topk_offset: int = 0
     dsa_indexer_rope_interleaved: bool = False  # GLM-5.x rotates the indexer's rotary part in interleaved pairs
     dsa_indexer_rotate_activation: bool = True  # Hadamard transform of the indexer q / k (DeepSeek-V3.2: on, GLM-5.x: off)

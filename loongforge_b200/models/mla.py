@@ -14,6 +14,13 @@ against the shared ``[kv_c | k_pe]`` (576-dim) rows selected by the indexer, and
 is projected with W_uv. Down projections are replicated across TP ranks; heads are TP-sharded.
 Under context parallelism the compressed KV (576 values per token) is all-gathered, which is cheap
 for MLA, and each rank attends from its own query chunk.
+
+Sequence-first mode (``cfg.dsa_sp_first``, ``--use-dsa-sp-first``; reference multi_latent_attention.py:260-368): under
+TP + SP the sparse attention does not split heads. Every rank keeps its T / tp tokens, the up projections and the
+output projection are replicated (full heads), and only the compressed keys and the indexer keys are gathered over
+the TP group, exactly as under context parallelism. The absorbed query tile then has all 128 heads (a full 128-row
+tensor-core tile) instead of 128 / tp, the hidden states are never gathered, and the output needs no reduce-scatter.
+All parameters of the block see a token shard, so their gradients are partial sums over the TP group.
 """
 from __future__ import annotations
 
@@ -94,29 +101,41 @@ class MLASelfAttention(nn.Module):
         tp = st.dims.tp
         nh = cfg.num_attention_heads
         assert nh % tp == 0
-        self.nh_local = nh // tp
+        self.sp_first = bool(cfg.use_dsa and getattr(cfg, "dsa_sp_first", False) and tp > 1 and cfg.sequence_parallel)
+        if self.sp_first and st.dims.cp > 1:
+            raise ValueError("sequence-first sparse attention does not combine with context parallelism")
+        self.nh_local = nh if self.sp_first else nh // tp
         self.dn, self.dr, self.dv, self.dc = cfg.qk_head_dim, cfg.qk_pos_emb_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
         qd = self.dn + self.dr
         common = dict(init_std=cfg.init_method_std, params_dtype=cfg.params_dtype, device=device,
                       parallel_state=parallel_state)
+
+        def column(in_f, out_f, name):
+            if self.sp_first:  # replicated, full heads; its gradient is a partial sum over the ranks' token shards
+                return _ReplicatedLinear(in_f, out_f, key + "." + name, cfg, device)
+            return PL.ColumnParallelLinear(in_f, out_f, key=key + "." + name, **common)
+
         if cfg.q_lora_rank:
             self.linear_q_down_proj = _ReplicatedLinear(cfg.hidden_size, cfg.q_lora_rank, key + ".linear_q_down_proj",
                                                         cfg, device)
             from .transformer import Norm
             self.q_layernorm = Norm(cfg.q_lora_rank, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
-            self.linear_q_up_proj = PL.ColumnParallelLinear(cfg.q_lora_rank, nh * qd, key=key + ".linear_q_up_proj",
-                                                            **common)
+            self.linear_q_up_proj = column(cfg.q_lora_rank, nh * qd, "linear_q_up_proj")
         else:
-            self.linear_q_proj = PL.ColumnParallelLinear(cfg.hidden_size, nh * qd, key=key + ".linear_q_proj", **common)
+            self.linear_q_proj = column(cfg.hidden_size, nh * qd, "linear_q_proj")
         self.linear_kv_down_proj = _ReplicatedLinear(cfg.hidden_size, self.dc + self.dr, key + ".linear_kv_down_proj",
                                                      cfg, device)
         from .transformer import Norm
         self.kv_layernorm = Norm(self.dc, cfg, device=device, sequence_parallel=cfg.sequence_parallel)
-        self.linear_kv_up_proj = PL.ColumnParallelLinear(self.dc, nh * (self.dn + self.dv),
-                                                         key=key + ".linear_kv_up_proj", **common)
+        self.linear_kv_up_proj = column(self.dc, nh * (self.dn + self.dv), "linear_kv_up_proj")
         common["init_std"] = cfg.init_method_std / math.sqrt(2.0 * cfg.num_layers)
-        self.linear_proj = PL.RowParallelLinear(nh * self.dv, cfg.hidden_size, key=key + ".linear_proj",
-                                                sequence_parallel=cfg.sequence_parallel, **common)
+        if self.sp_first:
+            import dataclasses
+            self.linear_proj = _ReplicatedLinear(nh * self.dv, cfg.hidden_size, key + ".linear_proj",
+                                                 dataclasses.replace(cfg, init_method_std=common["init_std"]), device)
+        else:
+            self.linear_proj = PL.RowParallelLinear(nh * self.dv, cfg.hidden_size, key=key + ".linear_proj",
+                                                    sequence_parallel=cfg.sequence_parallel, **common)
         if cfg.use_dsa:
             self.core_attention = nn.Module()
             # IndexShare: a layer without an indexer receives the top-k indices of its source layer
@@ -125,6 +144,9 @@ class MLASelfAttention(nn.Module):
                 self.core_attention.indexer = DSAIndexer(cfg, key + ".core_attention.indexer", device)
             self.last_topk_indices = None  # what this layer selected (or was given) in its latest forward
             self.shared_topk_indices = None  # set by the layer loop before calling a layer that reuses indices
+            if self.sp_first and self.computes_topk:
+                for p in self.core_attention.indexer.k_norm.parameters():
+                    p.sequence_parallel = True  # sees a token shard here: partial gradient
         self.mscale = 1.0  # set from the rotary inputs (YaRN)
 
     def _softmax_scale(self, rotary) -> float:
@@ -135,7 +157,16 @@ class MLASelfAttention(nn.Module):
         cfg = self.cfg
         st = ps.get_state(self.state_name)
         g_tp = st.group("tp")
-        if cfg.sequence_parallel and st.dims.tp > 1:
+        if self.sp_first:
+            # this rank's tokens are rows [r T, (r + 1) T) of the micro-batch: rotary angles of exactly those rows
+            T = x.shape[0]
+            lo = st.tp_rank * T
+            if rotary is not None:
+                from .transformer import RotaryInputs
+                ids = rotary.pos_ids[lo:lo + T] if rotary.pos_ids is not None else \
+                    torch.arange(lo, lo + T, device=x.device, dtype=torch.int32)
+                rotary = RotaryInputs(freqs=rotary.freqs, pos_ids=ids, mscale=rotary.mscale)
+        elif cfg.sequence_parallel and st.dims.tp > 1:
             x = M.gather_from_sequence_parallel_region(x, g_tp, True)
         T = x.shape[0]
         H = self.nh_local
@@ -169,6 +200,9 @@ class MLASelfAttention(nn.Module):
                                training=self.training)
         else:
             o = self._dsa(x, q_c, q_nope, q_pe, kv_c, k_pe, w_up, rotary, cu, scale)
+        if self.sp_first:
+            out = self.linear_proj(o.reshape(T, H * self.dv))  # already this rank's sequence shard: nothing to reduce
+            return out if residual is None else out + residual
         return self.linear_proj(o.reshape(T, H * self.dv), residual)
 
     # ------------------------------------------------------------------ sparse path
@@ -181,10 +215,19 @@ class MLASelfAttention(nn.Module):
         q_abs = torch.einsum("thd,hdc->thc", q_nope, w_uk.to(q_nope.dtype))
         query = torch.cat([q_abs, q_pe], dim=-1)  # [T, H, dc + dr]
         key = torch.cat([kv_c, k_pe.view(T, self.dr)], dim=-1)  # [T, dc + dr]
+        seq_group = st.group("cp") if st.dims.cp > 1 else (st.group("tp") if self.sp_first else None)
         if st.dims.cp > 1:
             # this rank holds two chunks of the packed row: causal order and sequence membership follow the ROW position
             from ..parallel.context_parallel import _positions
             pos, seg = _positions(T, st.dims.cp, st.cp_rank, x.device, cu, self._row_length)
+        elif self.sp_first:
+            # this rank holds rows [r T, (r + 1) T) of a micro-batch of tp * T tokens
+            lo = st.tp_rank * T
+            pos = torch.arange(lo, lo + T, device=x.device)
+            seg = None
+            if cu is not None:
+                seg = torch.bucketize(pos, cu[1:].long().to(x.device), right=True)
+                # causal order inside a packed sequence is the row order, so row positions serve as positions
         else:
             pos = rotary.pos_ids.long() if (rotary is not None and rotary.pos_ids is not None) \
                 else torch.arange(T, device=x.device)
@@ -192,8 +235,8 @@ class MLASelfAttention(nn.Module):
             if cu is not None:
                 seg = torch.bucketize(torch.arange(T, device=x.device), cu[1:].long().to(x.device), right=True)
         key_all, pos_k, seg_k = key, pos, seg
-        if st.dims.cp > 1:
-            g = st.group("cp")
+        if seq_group is not None:
+            g = seq_group
             key_all = M.gather_from_sequence_parallel_region(key, g, True)
             pos_k = M._all_gather_dim0(pos, g)
             seg_k = M._all_gather_dim0(seg, g) if seg is not None else None
@@ -201,11 +244,15 @@ class MLASelfAttention(nn.Module):
             idxr = self.core_attention.indexer
             qi, ki, wi = idxr.project(x.detach(), q_c.detach(), rotary)
             # index keys of the other context-parallel ranks; their gradient (indexer loss) flows back by reduce-scatter
-            ki_all = M.gather_from_sequence_parallel_region(ki, st.group("cp"), True) if st.dims.cp > 1 else ki
+            ki_all = M.gather_from_sequence_parallel_region(ki, seq_group, True) if seq_group is not None else ki
             with torch.no_grad():
                 qq, _ = dsa_ops.quant_fp8_rowwise_pow2(qi) if cfg.fp8 else (qi, None)
                 kq, _ = dsa_ops.quant_fp8_rowwise_pow2(ki_all) if cfg.fp8 else (ki_all, None)
-                if st.dims.cp > 1:
+                if self.sp_first:
+                    # rank-major order IS row order here (contiguous shards): candidates are one index range per query
+                    indices, _ = dsa_ops.indexer_topk(qq, kq, wi, cfg.dsa_indexer_topk, pos, pos_k, seg, seg_k,
+                                                      keys_in_order=True)
+                elif st.dims.cp > 1:
                     # gathered keys arrive rank-major: put them into row order so that every query's candidates are
                     # one contiguous index range (what the native kernels want), and map the selection back
                     order = torch.argsort(pos_k)

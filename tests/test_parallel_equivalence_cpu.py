@@ -135,3 +135,13 @@ def test_context_parallel_rows_longer_than_the_trained_context():
     res = run_distributed(_run_cp_short_table, 2)
     for (l0, _), (l1, _) in zip(ref, res[0]):
         assert abs(l0 - l1) < 5e-4 * abs(l0), (l0, l1)
+
+
+def test_sparse_attention_sequence_first_matches_single_process():
+    """Sequence-first sparse attention under TP + SP: every rank attends from its own tokens with all heads against the
+    gathered compressed keys (replicated up / output projections); same trajectory as one process, incl. the indexer
+    loss and packed position handling."""
+    ov = {"dsa_sp_first": True}
+    ref = _single("tiny-deepseek", 3, {})
+    res = run_distributed(_run, 2, "tiny-deepseek", {"tp": 2}, 3, ov)
+    _check(ref, res, lambda r: True, tol=5e-4)
