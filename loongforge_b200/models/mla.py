@@ -235,6 +235,17 @@ class MLASelfAttention(nn.Module):
             if cu is not None:
                 seg = torch.bucketize(torch.arange(T, device=x.device), cu[1:].long().to(x.device), right=True)
         key_all, pos_k, seg_k = key, pos, seg
+        from .transformer import CHUNK_PREFIX
+        chunked = CHUNK_PREFIX["active"]
+        if chunked:
+            # sequence-chunk pipelining: the compressed keys (and the indexer keys) of the sequence's earlier chunks are
+            # the prefix; this chunk's tokens sit behind them
+            assert cu is None and seq_group is None, "chunk pipelining runs one unpacked sequence, without cp / sp-first"
+            past = CHUNK_PREFIX["past"]
+            n_past = past[0].shape[0] if past is not None else 0
+            pos = torch.arange(n_past, n_past + T, device=x.device)
+            key_all = torch.cat([past[0], key]) if past is not None else key
+            pos_k = torch.arange(n_past + T, device=x.device)
         if seq_group is not None:
             g = seq_group
             key_all = M.gather_from_sequence_parallel_region(key, g, True)
@@ -245,11 +256,14 @@ class MLASelfAttention(nn.Module):
             qi, ki, wi = idxr.project(x.detach(), q_c.detach(), rotary)
             # index keys of the other context-parallel ranks; their gradient (indexer loss) flows back by reduce-scatter
             ki_all = M.gather_from_sequence_parallel_region(ki, seq_group, True) if seq_group is not None else ki
+            if chunked:
+                CHUNK_PREFIX["out"] = (key, ki)
+                ki_all = torch.cat([past[1], ki]) if past is not None else ki
             with torch.no_grad():
                 qq, _ = dsa_ops.quant_fp8_rowwise_pow2(qi) if cfg.fp8 else (qi, None)
                 kq, _ = dsa_ops.quant_fp8_rowwise_pow2(ki_all) if cfg.fp8 else (ki_all, None)
-                if self.sp_first:
-                    # rank-major order IS row order here (contiguous shards): candidates are one index range per query
+                if self.sp_first or chunked:
+                    # keys are in row order (contiguous shards / prefix then chunk): one index range per query
                     indices, _ = dsa_ops.indexer_topk(qq, kq, wi, cfg.dsa_indexer_topk, pos, pos_k, seg, seg_k,
                                                       keys_in_order=True)
                 elif st.dims.cp > 1:
@@ -267,6 +281,8 @@ class MLASelfAttention(nn.Module):
                     indices, _ = dsa_ops.indexer_topk(qq, kq, wi, cfg.dsa_indexer_topk, ar, ar, seg, seg_k,
                                                       keys_in_order=True)
         else:
+            if chunked:
+                CHUNK_PREFIX["out"] = (key, key.new_zeros(T, 0))  # no indexer here: nothing but the keys to cache
             indices = self.shared_topk_indices
             if indices is None:
                 raise RuntimeError(f"layer {self.layer_number} reuses top-k indices (IndexShare) but received none; "

@@ -156,16 +156,20 @@ def gpt_chunkpipe_step(model: nn.Module, tokens: torch.Tensor, position_ids: tor
     """One micro-batch (ONE sequence, flat ``[T]`` tensors) of a GPT model (one pipeline stage of it, when the model is
     pipeline parallel: chunks then flow through the stages like micro-batches) through the chunk pipeline:
     accumulates the gradients of ``loss_scale * sum(loss * mask)`` and returns that loss value. Attention layers
-    take the earlier chunks' keys / values through ``models.transformer.CHUNK_PREFIX``; every other sub-layer (norms,
+    take the earlier chunks' keys / values through ``models.transformer.CHUNK_PREFIX`` (multi-latent attention: the
+    materialised per-head keys / values in its dense form, the 576-value compressed keys and the indexer keys in its
+    sparse form, as the reference caches them: dsa_fused.py:240-421); every other sub-layer (norms,
     dense and MoE MLPs, the fused linear + cross-entropy head) is token-local and runs on the chunk alone. Tensor
     parallelism (with or without sequence parallelism) needs nothing extra: every rank caches the keys / values of its
     own heads."""
     from ..models import transformer as TF
 
     cfg = model.cfg
-    assert not (cfg.multi_latent_attention or cfg.enable_hyper_connections or cfg.csa_compress_ratios
-                or cfg.layer_types or cfg.full_attention_interval or cfg.mtp_num_layers), \
-        "chunk pipelining covers softmax-attention GPT layers"
+    assert not (cfg.enable_hyper_connections or cfg.csa_compress_ratios or cfg.layer_types
+                or cfg.full_attention_interval or cfg.mtp_num_layers), \
+        "chunk pipelining covers softmax-attention and multi-latent (dense or sparse) attention GPT layers"
+    assert not (cfg.use_dsa and (cfg.dsa_indexer_topk_freq or 1) > 1), \
+        "chunk pipelining does not carry shared top-k indices (IndexShare) from layer to layer"
     dev = tokens.device
     mask_f = loss_mask.float()
     from ..parallel import state as ps

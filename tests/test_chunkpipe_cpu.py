@@ -141,3 +141,27 @@ def test_chunks_flow_through_pipeline_stages(dims, world):
         assert l1 is not None and abs(l0 - l1) < 1e-4 * abs(l0) and abs(g0 - g1) < 1e-3 * max(1, g0), (ref, got)
     for (_, g0), (_, g1) in zip(ref, got[0]):
         assert abs(g0 - g1) < 1e-3 * max(1, g0)  # the global gradient norm is the same on every stage
+
+
+@pytest.mark.parametrize("use_dsa", [True, False])
+def test_chunk_pipelining_with_multi_latent_attention(use_dsa):
+    """MLA under chunk pipelining: the sparse form caches compressed keys and indexer keys per chunk (top-k selection over
+    prefix + chunk), the dense form the materialised keys / values; same trajectory as whole sequences."""
+    from loongforge_b200.data.synthetic import synthetic_batch_iterator
+    from loongforge_b200.models.registry import get_model_config
+    from loongforge_b200.parallel import state as ps
+    from loongforge_b200.runtime.trainer import TrainConfig, Trainer
+
+    def run(chunks):
+        ps.destroy_model_parallel()
+        cfg = get_model_config("tiny-deepseek", moe_aux_loss_coeff=0.0, use_dsa=use_dsa)
+        tc = TrainConfig(micro_batch_size=1, global_batch_size=2, seq_length=64, train_iters=2, lr=1e-3,
+                         log_interval=1000, chunkpipe_chunks=chunks)
+        tr = Trainer(cfg, tc)
+        it = synthetic_batch_iterator(cfg.vocab_size, 64, 1, seed=4, pin_memory=False)
+        return [(m["lm loss"], m["grad_norm"]) for m in (tr.train_step(it) for _ in range(2))]
+
+    ref, got = run(0), run(4)
+    ps.destroy_model_parallel()
+    for (l0, g0), (l1, g1) in zip(ref, got):
+        assert abs(l0 - l1) < 2e-4 * max(1, abs(l0)) and abs(g0 - g1) < 2e-3 * max(1, abs(g0)), (ref, got)
