@@ -24,6 +24,8 @@ class EmbodiedArgs:
     image_size: int = 56
     num_cameras: int = 1
     max_text_len: int = 16
+    video_frames: int = 0  # world-model policies: future frames per sample (1 + 4k; 0 = none), camera 0, one per `video_frame_stride` steps
+    video_frame_stride: int = 1
     # ---- optimisation
     train_steps: int = 100
     per_device_batch_size: int = 4

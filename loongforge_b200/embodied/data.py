@@ -1,7 +1,8 @@
 """Datasets and collators of the embodied stack.
 
 Every sample is one time step of an episode: camera images, a proprioceptive state, a language instruction and the
-chunk of the next ``action_horizon`` actions (padded at episode end, with a mask). Sources:
+chunk of the next ``action_horizon`` actions (padded at episode end, with a mask); with ``video_frames > 0`` also the
+camera-0 frames of the coming steps (``video [T, 3, H, W]``), which the world-model policies encode into latents. Sources:
 
 * ``SyntheticEpisodes``  — deterministic random episodes (benchmarks, tests);
 * ``NpzEpisodes``        — a directory of ``episode_*.npz`` files (arrays ``images [T, cams, C, H, W]``, ``state``,
@@ -34,6 +35,11 @@ def _chunk(actions: np.ndarray, t: int, horizon: int):
     return seg.astype(np.float32), mask
 
 
+def _future_frames(frames_at, t: int, length: int, n: int, stride: int) -> np.ndarray:
+    """``[n, 3, H, W]``: camera-0 frames at steps t, t + stride, ... (the last frame repeats past the episode's end)."""
+    return np.stack([frames_at(min(t + i * stride, length - 1)) for i in range(n)]).astype(np.float32)
+
+
 def hash_tokenize(text: str, max_len: int, vocab: int = 32000) -> np.ndarray:
     """Whitespace tokens hashed into a fixed vocabulary (stand-in for the model tokenizer in tests / synthetic runs)."""
     ids = [(zlib.crc32(w.encode()) % (vocab - 2)) + 2 for w in text.lower().split()][:max_len]
@@ -55,8 +61,13 @@ class SyntheticEpisodes(Dataset):
         state = rng.standard_normal((self.L, a.state_dim)).astype(np.float32)
         img = np.random.default_rng(i).random((a.num_cameras, 3, a.image_size, a.image_size), dtype=np.float32)
         chunk, mask = _chunk(actions, t, a.action_horizon)
-        return {"images": img, "state": state[t], "actions": chunk, "action_mask": mask,
-                "text": hash_tokenize(f"task {ep % 3} move the object", a.max_text_len)}
+        out = {"images": img, "state": state[t], "actions": chunk, "action_mask": mask,
+               "text": hash_tokenize(f"task {ep % 3} move the object", a.max_text_len)}
+        if getattr(a, "video_frames", 0):
+            # a smooth drift of the current image: frame k is the image rolled by k pixels (something a world model can learn)
+            out["video"] = _future_frames(lambda k: np.roll(img[0], k - t, axis=-1), t, self.L + a.video_frames * a.video_frame_stride,
+                                          a.video_frames, a.video_frame_stride)
+        return out
 
 
 class NpzEpisodes(Dataset):
@@ -85,8 +96,12 @@ class NpzEpisodes(Dataset):
         ep = self._episode(fi)
         chunk, mask = _chunk(ep["actions"], t, self.a.action_horizon)
         task = str(ep["task"]) if "task" in ep else "do the task"
-        return {"images": ep["images"][t].astype(np.float32), "state": ep["state"][t].astype(np.float32),
-                "actions": chunk, "action_mask": mask, "text": hash_tokenize(task, self.a.max_text_len)}
+        out = {"images": ep["images"][t].astype(np.float32), "state": ep["state"][t].astype(np.float32),
+               "actions": chunk, "action_mask": mask, "text": hash_tokenize(task, self.a.max_text_len)}
+        if getattr(self.a, "video_frames", 0):
+            out["video"] = _future_frames(lambda k: ep["images"][k][0], t, ep["images"].shape[0], self.a.video_frames,
+                                          self.a.video_frame_stride)
+        return out
 
 
 class LeRobotParquet(Dataset):

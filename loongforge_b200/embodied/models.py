@@ -11,14 +11,18 @@ groot_n1_6     own architecture in ``embodied/groot.py`` (Eagle backbone + alter
 groot_n1_7     ``embodied/groot.py`` with the N1.7 additions (self-attention over the backbone features, state dropout)
 xvla           own architecture in ``embodied/xvla.py`` (DaViT-style tower + BART-style fusion encoder, domain-aware
                soft-prompted transformer, action spaces with regressed and gripper-logit channels)
-lingbot_va     WAN video-DiT backbone streaming latents, action tokens decoded jointly
-fastwam        WAN DiT + VAE latents, mixture-of-transformers action branch
-dreamzero      causal WAN world model with an action head on the denoised latents
-cosmos3        video foundation network over packed sequences with a Qwen3-VL conditioner
+lingbot_va     ``embodied/lingbot_va.py``: one WAN transformer over noisy / clean video latents and action chunks
+               with a teacher-forcing mask, roll-out at test time
+fastwam        ``embodied/fastwam.py``: WAN video expert + narrow action expert with joint attention (variants
+               fastwam / joint / idm), action-only inference against the cached first frame
+dreamzero      ``embodied/dreamzero.py``: block-causal WAN image-to-video model with embodiment-specific action and
+               state registers in the sequence
+cosmos3        ``embodied/cosmos3.py``: Qwen3-VL-style decoder with understanding / generation pathways over
+               packed sequences, unified 3-D M-RoPE, domain-aware action projections
 =============  =======================================================================================
 
-The world-model policies (last four) use ``models/diffusion.py::WanModel`` as backbone; the VLA policies use the
-transformer blocks below. Sizes here are the configurable skeleton; published sizes are set through ``model_overrides``.
+Every policy has an architecture of its own; the skeleton below (one backbone + a flow-matching action head) remains
+for ``model_overrides: {architecture: skeleton}`` (quick experiments, tests of the trainer).
 """
 from __future__ import annotations
 
@@ -236,9 +240,9 @@ class _BatchAdapter(nn.Module):
 
 
 def _dedicated_policy(name: str, args, overrides: dict) -> Optional[nn.Module]:
-    """Pi0.5 and GR00T N1.6 have architectures of their own. ``model_overrides: {size: tiny}`` selects the small test
+    """Every named policy has an architecture of its own. ``model_overrides: {size: tiny}`` selects the small test
     geometry, any other key overrides a field of the architecture's configuration."""
-    if name not in ("pi05", "groot_n1_6", "groot_n1_7", "xvla"):
+    if name not in ("pi05", "groot_n1_6", "groot_n1_7", "xvla", "lingbot_va", "fastwam", "dreamzero", "cosmos3"):
         return None
     kw = dict(getattr(args, "model_overrides", None) or {}) if args is not None else {}
     kw.update(overrides)
@@ -249,6 +253,19 @@ def _dedicated_policy(name: str, args, overrides: dict) -> Optional[nn.Module]:
         kw.setdefault("action_dim", args.action_dim)
         kw.setdefault("action_horizon", args.action_horizon)
         kw.setdefault("image_size", args.image_size)
+    if name in ("lingbot_va", "fastwam", "dreamzero", "cosmos3"):
+        import importlib
+        mod = importlib.import_module(f".{name}", __package__)
+        cfg_cls, pol_cls = {"lingbot_va": ("LingBotVAConfig", "LingBotVAPolicy"), "fastwam": ("FastWAMConfig", "FastWAMPolicy"),
+                            "dreamzero": ("DreamZeroConfig", "DreamZeroPolicy"), "cosmos3": ("Cosmos3Config", "Cosmos3Policy")}[name]
+        cfg_cls, pol_cls = getattr(mod, cfg_cls), getattr(mod, pol_cls)
+        fields = {f.name for f in dataclasses.fields(cfg_cls)}
+        if args is not None:
+            kw.setdefault("state_dim", args.state_dim)
+            if getattr(args, "video_frames", 0):
+                kw.setdefault("video_frames", args.video_frames)
+        kw = {k: v for k, v in kw.items() if k in fields}
+        return _BatchAdapter(pol_cls(cfg_cls.tiny(**kw) if size == "tiny" else cfg_cls(**kw)))
     if name == "pi05":
         from .pi05 import Pi05Config, Pi05Policy
         if args is not None:
