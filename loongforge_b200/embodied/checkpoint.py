@@ -3,6 +3,7 @@ data-loader state, ZeRO optimizer consolidation, LoRA adapter metadata, ``latest
 single-file export (reference: loongforge/embodied/distributed/checkpoint.py:71-975, tools/dcp_to_safetensors.py)."""
 from __future__ import annotations
 
+import glob
 import json
 import os
 import random
@@ -58,10 +59,12 @@ def save_checkpoint(root: str, step: int, model: nn.Module, optimizer, scheduler
         msd, osd = get_state_dict(inner, optimizer)
         dcp.save({"model": msd, "optim": osd}, checkpoint_id=os.path.join(d, "dcp"))
     else:
-        if hasattr(optimizer, "consolidate_state_dict"):  # ZeRO-1: gather the shards on rank 0
-            optimizer.consolidate_state_dict(to=0)
+        sharded = hasattr(optimizer, "local_state_dict")  # ZeRO-1: every rank writes the shard it owns, keyed by name
+        if sharded:
+            torch.save(optimizer.local_state_dict(), os.path.join(d, f"optim_shard_{rank:05d}.pt"))
         if rank == 0:
-            torch.save({"model": inner.state_dict(), "optim": optimizer.state_dict()}, os.path.join(d, "model_optim.pt"))
+            torch.save({"model": inner.state_dict(), "optim": None if sharded else optimizer.state_dict()},
+                       os.path.join(d, "model_optim.pt"))
     # per-rank auxiliary state
     torch.save({"rng": rng_state(), "dataloader": dataloader_state}, os.path.join(d, f"aux_rank{rank:05d}.pt"))
     if rank == 0:
@@ -103,7 +106,17 @@ def load_checkpoint(root: str, model: nn.Module, optimizer=None, scheduler=None,
         blob = torch.load(os.path.join(d, "model_optim.pt"), map_location="cpu", weights_only=False)
         inner.load_state_dict(blob["model"])
         if optimizer is not None:
-            optimizer.load_state_dict(blob["optim"])
+            shards = sorted(glob.glob(os.path.join(d, "optim_shard_*.pt")))
+            if shards and hasattr(optimizer, "load_local_state_dicts"):
+                # any number of shard files (the world size at save time) into the present partition
+                optimizer.load_local_state_dicts([torch.load(f, map_location="cpu", weights_only=False) for f in shards])
+            elif shards:
+                merged = {}
+                for f in shards:
+                    merged.update(torch.load(f, map_location="cpu", weights_only=False)["state"])
+                raise ValueError(f"{d} holds a sharded (zero1) optimizer state of {len(merged)} tensors; resume with strategy=zero1")
+            elif blob["optim"] is not None:
+                optimizer.load_state_dict(blob["optim"])
     if scheduler is not None and meta.get("scheduler"):
         scheduler.load_state_dict(meta["scheduler"])
     aux_path = os.path.join(d, f"aux_rank{rank:05d}.pt")

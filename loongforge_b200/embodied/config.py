@@ -45,6 +45,12 @@ class EmbodiedArgs:
     strategy: str = "ddp"  # ddp | zero1 | fsdp | hsdp
     fsdp_wrap_patterns: List[str] = dataclasses.field(default_factory=lambda: ["blocks.*", "layers.*"])
     fsdp_prefetch: int = 1
+    fsdp_min_num_params: int = 1_000_000            # automatic plan ([auto]): smallest group of repeated layers
+    fsdp_leftover_min_num_params: int = 10_000_000  # ... and smallest single leaf that gets a unit of its own
+    fsdp_no_wrap_modules: List[str] = dataclasses.field(default_factory=list)  # class names never taken as one unit
+    fsdp_reshard_default: Any = True                # reshard_after_forward of the units (bool or int)
+    fsdp_reshard_root: Any = False
+    fsdp_reshard_module_overrides: Dict[str, Any] = dataclasses.field(default_factory=dict)  # glob -> bool | int
     hsdp_shard_size: Optional[int] = None
     ddp_bucket_mb: int = 25
     ddp_comm_hook: Optional[str] = None  # None | bf16_compress
@@ -54,7 +60,13 @@ class EmbodiedArgs:
     # ---- LoRA
     lora_rank: int = 0
     lora_alpha: float = 16.0
-    lora_targets: List[str] = dataclasses.field(default_factory=lambda: ["q", "k", "v", "o"])
+    lora_targets: List[str] = dataclasses.field(default_factory=lambda: ["q", "k", "v", "o"])  # names, globs, all-linear; [] = the policy's own
+    lora_dropout: float = 0.0
+    lora_use_rslora: bool = False
+    lora_init: str = "kaiming"  # kaiming | gaussian
+    lora_exclude: List[str] = dataclasses.field(default_factory=list)
+    lora_modules_to_save: List[str] = dataclasses.field(default_factory=list)
+    lora_adapter_path: Optional[str] = None  # start from a stored adapter (directory with adapter_model.pt + adapter_config.json)
     # ---- CUDA graphs
     per_microbatch_cuda_graph: bool = False
     # ---- checkpoint / logging

@@ -290,6 +290,11 @@ class Cosmos3Network(nn.Module):
 
 
 class Cosmos3Policy(nn.Module):
+
+    def default_lora_targets(self):
+        """Every projection of both pathways of the decoder layers."""
+        return ["*net.layers.*_proj"]
+
     def __init__(self, c: Cosmos3Config):
         super().__init__()
         self.c = c

@@ -278,6 +278,11 @@ class CausalWanModel(nn.Module):
 
 
 class DreamZeroPolicy(nn.Module):
+
+    def default_lora_targets(self):
+        """Attention and FFN projections of the transformer blocks; codec, text encoder and heads stay as they are."""
+        return [f"*model.blocks.*.{n}" for n in ("q", "k", "v", "o", "k_img", "v_img", "ffn.0", "ffn.2")]
+
     def __init__(self, c: DreamZeroConfig):
         super().__init__()
         self.c = c

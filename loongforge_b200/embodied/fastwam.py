@@ -125,6 +125,9 @@ class _Expert(nn.Module):
 
 
 class FastWAMModel(nn.Module):
+    # the joint attention reaches into both experts' blocks and their attention projections
+    FSDP_NO_WRAP = ("_Expert", "DiTBlock", "Attention", "FastWAMModel")
+
     def __init__(self, c: FastWAMConfig):
         super().__init__()
         self.c = c
@@ -215,6 +218,11 @@ class FastWAMModel(nn.Module):
 
 
 class FastWAMPolicy(nn.Module):
+
+    def default_lora_targets(self):
+        """Attention and FFN projections of the transformer blocks; codec, text encoder and heads stay as they are."""
+        return [f"*model.*.blocks.*.{n}" for n in ("q", "k", "v", "o", "k_img", "v_img", "ffn.0", "ffn.2")]
+
     def __init__(self, c: FastWAMConfig):
         super().__init__()
         assert c.variant in ("fastwam", "joint", "idm")

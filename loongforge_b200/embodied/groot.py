@@ -378,6 +378,11 @@ class GrootPolicy(nn.Module):
     """batch: ``images`` [B, cams, 3, H, W], ``image_masks``, ``tokens`` [B, L], ``token_mask``, ``state`` [B, state_dim],
     ``embodiment_id`` [B], ``actions`` [B, horizon, action_dim], ``action_mask`` (optional)."""
 
+    def default_lora_targets(self):
+        """Attention projections of the backbone's language layers and of the DiT head."""
+        return ["qkv", "o", "to_q", "to_k", "to_v", "to_out"]
+
+
     def __init__(self, c: GrootConfig):
         super().__init__()
         self.c = c

@@ -176,6 +176,11 @@ class LingBotVAModel(nn.Module):
 class LingBotVAPolicy(nn.Module):
     """Codec + text encoder + transformer, the training loss and the roll-out."""
 
+    def default_lora_targets(self):
+        """Attention and FFN projections of the transformer blocks; codec, text encoder and heads stay as they are."""
+        return [f"*model.blocks.*.{n}" for n in ("q", "k", "v", "o", "k_img", "v_img", "ffn.0", "ffn.2")]
+
+
     def __init__(self, c: LingBotVAConfig):
         super().__init__()
         self.c = c

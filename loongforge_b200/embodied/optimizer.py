@@ -4,7 +4,7 @@ loongforge/embodied/optimizer/optimizer.py:37-378, lr_scheduler.py, clip_gradien
 from __future__ import annotations
 
 import math
-from typing import Dict, Iterable, List
+from typing import Dict, Iterable, List, Optional
 
 import torch
 import torch.distributed as dist
@@ -69,16 +69,126 @@ class FP32MasterAdapter(torch.optim.Optimizer):
                 m.data.copy_(s)
 
 
+class ZeroAdamW(torch.optim.Optimizer):
+    """ZeRO stage 1 with fp32 masters, written against plain collectives. Every parameter has ONE owner rank (greedy
+    balancing by element count); the owner keeps the fp32 master and both Adam moments, applies decoupled AdamW to the
+    master from the (already data-parallel-reduced) gradient, writes the result into the model parameter and the owners'
+    updated parameters are broadcast, one flat buffer per owner and dtype. Memory per rank: masters + moments of 1 / world
+    of the model. Works for mixed dtypes (bf16 weights next to fp32 scalars).
+
+    The state is keyed by parameter NAME: ``local_state_dict()`` is this rank's shard, and
+    ``load_local_state_dicts(shards)`` takes the shards of ANY earlier world size and keeps what this rank owns now, so a
+    checkpoint survives a change of the number of ranks (reference: the ZeRO wrappers of
+    loongforge/embodied/optimizer/optimizer.py:37-104,221-250 and the shard files of distributed/checkpoint.py)."""
+
+    def __init__(self, groups: List[dict], names: Dict[int, str], lr: float, betas=(0.9, 0.95), eps: float = 1e-8,
+                 weight_decay: float = 0.0, group=None):
+        super().__init__(groups, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.names = names
+        params = [p for g in self.param_groups for p in g["params"]]
+        load = [0] * self.world
+        self.owner: Dict[int, int] = {}
+        for p in sorted(params, key=lambda q: -q.numel()):          # largest first onto the lightest rank
+            r = min(range(self.world), key=lambda i: load[i])
+            self.owner[id(p)] = r
+            load[r] += p.numel()
+        self._params = params
+        for p in params:
+            if self.owner[id(p)] == self.rank:
+                self.state[p] = {"step": 0, "master": p.detach().float().clone(),
+                                 "exp_avg": torch.zeros_like(p, dtype=torch.float32),
+                                 "exp_avg_sq": torch.zeros_like(p, dtype=torch.float32)}
+
+    def owned(self):
+        return [p for p in self._params if self.owner[id(p)] == self.rank]
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        for g in self.param_groups:
+            b1, b2 = g["betas"]
+            for p in g["params"]:
+                if self.owner[id(p)] != self.rank or p.grad is None:
+                    continue
+                st = self.state[p]
+                st["step"] += 1
+                grad = p.grad.float()
+                st["exp_avg"].mul_(b1).add_(grad, alpha=1 - b1)
+                st["exp_avg_sq"].mul_(b2).addcmul_(grad, grad, value=1 - b2)
+                bc1, bc2 = 1 - b1 ** st["step"], 1 - b2 ** st["step"]
+                m = st["master"]
+                m.mul_(1 - g["lr"] * g["weight_decay"])
+                m.addcdiv_(st["exp_avg"], (st["exp_avg_sq"] / bc2).sqrt_().add_(g["eps"]), value=-g["lr"] / bc1)
+                p.copy_(m)
+        self._broadcast_params()
+
+    def _broadcast_params(self):
+        if self.world == 1:
+            return
+        from torch._utils import _flatten_dense_tensors, _unflatten_dense_tensors
+        for r in range(self.world):
+            by_dtype: Dict[torch.dtype, List[torch.Tensor]] = {}
+            for p in self._params:
+                if self.owner[id(p)] == r:
+                    by_dtype.setdefault(p.dtype, []).append(p.data)
+            src = dist.get_global_rank(self.group, r) if self.group is not None else r
+            for ts in by_dtype.values():
+                flat = _flatten_dense_tensors(ts)
+                dist.broadcast(flat, src=src, group=self.group)
+                if r != self.rank:
+                    for t, u in zip(ts, _unflatten_dense_tensors(flat, ts)):
+                        t.copy_(u)
+
+    # -- name-keyed shard state
+    def local_state_dict(self) -> dict:
+        return {"world": self.world, "rank": self.rank,
+                "state": {self.names[id(p)]: {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in self.state[p].items()}
+                          for p in self.owned()},
+                "param_groups": [{k: v for k, v in g.items() if k != "params"} for g in self.param_groups]}
+
+    def load_local_state_dicts(self, shards: List[dict]) -> None:
+        merged: Dict[str, dict] = {}
+        for sh in shards:
+            merged.update(sh["state"])
+        for p in self.owned():
+            src = merged[self.names[id(p)]]
+            st = self.state[p]
+            st["step"] = int(src["step"])
+            for k in ("master", "exp_avg", "exp_avg_sq"):
+                st[k].copy_(src[k])
+            p.data.copy_(st["master"])
+        for g, sg in zip(self.param_groups, shards[0]["param_groups"]):
+            g.update({k: v for k, v in sg.items() if k in ("lr", "betas", "eps", "weight_decay")})
+        self._broadcast_params()
+
+    def consolidated_state_dict(self, to: int = 0) -> Optional[dict]:
+        """All shards merged on rank ``to`` (one file for export); None elsewhere."""
+        local = self.local_state_dict()
+        if self.world == 1:
+            return local
+        out = [None] * self.world if self.rank == to else None
+        dist.gather_object(local, out, dst=dist.get_global_rank(self.group, to) if self.group is not None else to, group=self.group)
+        if self.rank != to:
+            return None
+        merged = dict(out[0])
+        merged["state"] = {k: v for sh in out for k, v in sh["state"].items()}
+        return merged
+
+    def state_dict(self):
+        return self.local_state_dict()
+
+    def load_state_dict(self, sd):
+        self.load_local_state_dicts([sd])
+
+
 def build_optimizer(model: nn.Module, args, world: int = 1):
     groups = build_param_groups(model, args.weight_decay, args.lr)
     kw = dict(lr=args.lr, betas=(args.adam_beta1, args.adam_beta2), eps=1e-8)
-    if args.strategy == "zero1" and world > 1:
-        from torch.distributed.optim import ZeroRedundancyOptimizer
-
-        # ZeRO partitions whole parameters; groups with different dtypes are handled by one instance per dtype
-        opt = ZeroRedundancyOptimizer([p for g in groups for p in g["params"]], optimizer_class=torch.optim.AdamW,
-                                      weight_decay=args.weight_decay, **kw)
-        return opt
+    if args.strategy == "zero1":
+        names = {id(p): n[len("module."):] if n.startswith("module.") else n for n, p in model.named_parameters()}
+        return ZeroAdamW(groups, names, weight_decay=args.weight_decay, **kw)
     if args.fp32_master_weights:
         return FP32MasterAdapter(groups, torch.optim.AdamW, **kw)
     return torch.optim.AdamW(groups, **kw)

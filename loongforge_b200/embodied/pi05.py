@@ -151,6 +151,8 @@ class JointDecoder(nn.Module):
     """Language stack + action expert with shared attention. ``forward`` takes one or both streams; a cache of the
     prefix keys / values lets the expert run alone during sampling."""
 
+    FSDP_NO_WRAP = ("GemmaLayer",)  # the decoder calls the layers' projection / finish methods, not their forward
+
     def __init__(self, c: Pi05Config):
         super().__init__()
         self.c = c
@@ -246,6 +248,12 @@ def sincos_time_embedding(t: torch.Tensor, dim: int, min_period: float, max_peri
 class Pi05Policy(nn.Module):
     """batch: ``images`` [B, cams, 3, H, W], ``image_masks`` [B, cams] (False = camera absent), ``tokens`` [B, L],
     ``token_mask`` [B, L], ``actions`` [B, horizon, action_dim] (training)."""
+
+    def default_lora_targets(self):
+        """Attention and MLP projections of the language stack and the action expert (the vision tower stays exact)."""
+        return ["policy.decoder.*.qkv", "policy.decoder.*.o", "policy.decoder.*.gate_up", "policy.decoder.*.down",
+                "decoder.*.qkv", "decoder.*.o", "decoder.*.gate_up", "decoder.*.down"]
+
 
     def __init__(self, c: Pi05Config):
         super().__init__()

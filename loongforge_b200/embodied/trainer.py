@@ -41,8 +41,14 @@ class BaseTrainer:
         torch.manual_seed(a.seed)  # identical initial weights on every rank
         model = self.build_model()
         if a.lora_rank > 0:
-            from .lora import inject_lora
-            self.lora_meta = inject_lora(model, a.lora_rank, a.lora_alpha, a.lora_targets)
+            from .lora import inject_lora, load_adapter
+            self.lora_meta = inject_lora(model, a.lora_rank, a.lora_alpha, a.lora_targets, dropout=a.lora_dropout,
+                                         use_rslora=a.lora_use_rslora, init=a.lora_init, exclude=a.lora_exclude,
+                                         modules_to_save=a.lora_modules_to_save)
+            if a.lora_adapter_path:
+                load_adapter(model, a.lora_adapter_path, trainable=True)
+                for n, p in model.named_parameters():  # adapters and fully-trained modules train on, the base stays frozen
+                    p.requires_grad_(".lora_a." in n or ".lora_b." in n or any(n.startswith(m + ".") for m in self.lora_meta["saved_modules"]))
         else:
             self.lora_meta = None
         if a.bf16:
@@ -113,6 +119,10 @@ class BaseTrainer:
         ckpt.save_checkpoint(self.args.output_dir, self.step, self.model, self.optimizer, self.scheduler,
                              fmt=self.args.checkpoint_format, dataloader_state=self.loader.state_dict(),
                              lora_meta=self.lora_meta, rank=self.ctx.rank, world=self.ctx.world)
+        if self.lora_meta is not None and self.ctx.is_main and self.args.strategy in ("ddp", "zero1"):
+            from .lora import save_adapter
+            save_adapter(ckpt._unwrap(self.model), os.path.join(self.args.output_dir, f"step_{self.step:08d}", "adapter"),
+                         self.lora_meta, {"model_name": self.args.model_name, "step": self.step})
 
     def train(self):
         if self.args.manual_gc_interval:

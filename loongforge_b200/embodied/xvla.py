@@ -355,6 +355,10 @@ class XVLAPolicy(nn.Module):
     """batch: ``images`` [B, views, 3, S, S], ``image_masks`` [B, views], ``tokens`` [B, L], ``token_mask``, ``state``
     [B, d], ``domain_id`` [B], ``actions`` [B, num_actions, action_dim]."""
 
+    def default_lora_targets(self):
+        return ["qkv", "o", "qkv1", "qkv2", "o1", "o2"]
+
+
     def __init__(self, c: XVLAConfig):
         super().__init__()
         self.c = c

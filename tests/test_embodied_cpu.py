@@ -113,7 +113,11 @@ def _dist_train(rank, world, strategy, out):
 
     ctx = DistContext()
     ctx.rank, ctx.world, ctx.local_rank = rank, world, rank
-    a = _args(out, strategy=strategy, train_steps=3, fsdp_wrap_patterns=["backbone.blocks.*", "head.blocks.*"],
+    auto = strategy == "fsdp-auto"
+    strategy = "fsdp" if auto else strategy
+    a = _args(out, strategy=strategy, train_steps=3,
+              fsdp_wrap_patterns=["auto"] if auto else ["backbone.blocks.*", "head.blocks.*"], fsdp_min_num_params=20000,
+              fsdp_reshard_module_overrides={"*expert*": False},
               checkpoint_format="dcp" if strategy == "fsdp" else "pt", save_interval=3)
     t = build_trainer(a, ctx)
     m = t.train()
@@ -122,7 +126,7 @@ def _dist_train(rank, world, strategy, out):
     return m["loss"], full
 
 
-@pytest.mark.parametrize("strategy", ["ddp", "zero1", "fsdp"])
+@pytest.mark.parametrize("strategy", ["ddp", "zero1", "fsdp", "fsdp-auto"])
 def test_distributed_strategies_agree_across_ranks(strategy, tmp_path):
     res = run_distributed(_dist_train, 2, strategy, str(tmp_path))
     assert abs(res[0][1] - res[1][1]) < 1e-3 * max(1.0, abs(res[0][1]))  # replicas hold identical weights
@@ -298,3 +302,194 @@ def test_xvla_domains_action_spaces_and_sampler():
     assert abs(float(l["regress_0"]) - 500.0 * 0.01 / 3) < 1e-5 and abs(float(l["gripper"]) - math.log(2.0)) < 1e-6
     l2 = sp.compute_loss(pred, tgt, valid=torch.tensor([True, False]))
     assert abs(float(l2["regress_0"]) - float(l["regress_0"])) < 1e-6  # padded rows leave the mean over valid rows unchanged
+
+
+def _zero_worker(rank, world, tmp, steps, resume_from):
+    """Identical 'reduced' gradients on every rank: the sharded optimizer must reproduce plain AdamW on all of them."""
+    from loongforge_b200.embodied.optimizer import ZeroAdamW, build_param_groups
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.LayerNorm(5), torch.nn.Linear(5, 3))
+    names = {id(p): n for n, p in model.named_parameters()}
+    opt = ZeroAdamW(build_param_groups(model, 0.1, 1e-2), names, lr=1e-2, weight_decay=0.1)
+    if resume_from:
+        import glob
+        opt.load_local_state_dicts([torch.load(f, weights_only=False) for f in sorted(glob.glob(os.path.join(resume_from, "shard_*.pt")))])
+    g = torch.Generator().manual_seed(5 + (100 if resume_from else 0))
+    for _ in range(steps):
+        for p in model.parameters():
+            p.grad = torch.randn(p.shape, generator=g)
+        opt.step()
+    torch.save(opt.local_state_dict(), os.path.join(tmp, f"shard_{rank}.pt"))
+    owned = sum(p.numel() for p in opt.owned())
+    return [p.detach().flatten().tolist() for p in model.parameters()], owned, len(opt.state)
+
+
+def test_zero_adamw_matches_adamw_and_reshards(tmp_path):
+    from tests.dist_utils import run_distributed as rd
+
+    def reference(steps_a, steps_b):
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.LayerNorm(5), torch.nn.Linear(5, 3))
+        from loongforge_b200.embodied.optimizer import build_param_groups
+        opt = torch.optim.AdamW(build_param_groups(model, 0.1, 1e-2), lr=1e-2, betas=(0.9, 0.95), eps=1e-8)
+        for seed, n in ((5, steps_a), (105, steps_b)):
+            g = torch.Generator().manual_seed(seed)
+            for _ in range(n):
+                for p in model.parameters():
+                    p.grad = torch.randn(p.shape, generator=g)
+                opt.step()
+        return [p.detach().clone() for p in model.parameters()]
+
+    d2 = tmp_path / "w2"
+    d2.mkdir()
+    res = rd(_zero_worker, 2, str(d2), 4, None)
+    ref = reference(4, 0)
+    for r in res:
+        assert all(torch.allclose(torch.tensor(a), b.flatten(), atol=1e-6) for a, b in zip(r[0], ref))
+    total = sum(p.numel() for p in ref)
+    assert res[0][1] + res[1][1] == total and 0.3 * total < res[0][1] < 0.7 * total   # balanced partition
+    assert res[0][2] + res[1][2] == len(ref)                                          # every parameter has one owner
+    # the two shards resume on THREE ranks and on one
+    ref2 = reference(4, 3)
+    for world in (3, 1):
+        dn = tmp_path / f"w{world}"
+        dn.mkdir()
+        res = rd(_zero_worker, world, str(dn), 3, str(d2))
+        for r in res:
+            assert all(torch.allclose(torch.tensor(a), b.flatten(), atol=1e-6) for a, b in zip(r[0], ref2))
+
+
+def _zero_resume_worker(rank, world, out, steps, resume):
+    from loongforge_b200.embodied.distributed import DistContext
+    from loongforge_b200.embodied.trainer import build_trainer
+
+    ctx = DistContext()
+    ctx.rank, ctx.world, ctx.local_rank = rank, world, rank
+    a = _args(out, strategy="zero1", train_steps=steps, save_interval=2, resume=resume, lr_scheduler="constant")
+    t = build_trainer(a, ctx)
+    t.train()
+    return float(sum(p.float().sum() for p in t.model.parameters())), sorted(os.listdir(os.path.join(out, f"step_{steps:08d}")) if os.path.isdir(os.path.join(out, f"step_{steps:08d}")) else [])
+
+
+def test_zero1_trainer_writes_shards_and_resumes(tmp_path):
+    out = str(tmp_path)
+    res = run_distributed(_zero_resume_worker, 2, out, 2, False)
+    step_dir = [d for d in os.listdir(out) if d.startswith("step")][0]
+    files = os.listdir(os.path.join(out, step_dir))
+    assert "optim_shard_00000.pt" in files and "optim_shard_00001.pt" in files and "model_optim.pt" in files
+    res2 = run_distributed(_zero_resume_worker, 2, out, 4, True)           # continues from step 2
+    assert ckpt.latest_step(out) == 4 and abs(res2[0][0] - res2[1][0]) < 1e-3 * max(1.0, abs(res2[0][0]))
+    assert res2[0][0] != res[0][0]
+
+
+def test_fsdp_auto_planner_units():
+    import torch.nn as nn
+    from loongforge_b200.embodied.distributed import FSDPAutoPlanner
+
+    class Block(nn.Module):
+        def __init__(self, d):
+            super().__init__()
+            self.a, self.b = nn.Linear(d, d), nn.Linear(d, d)
+
+        def forward(self, x):
+            return self.b(self.a(x))
+
+    class Odd(nn.Module):  # parameters of two dtypes: never one unit
+        def __init__(self, d):
+            super().__init__()
+            self.w = nn.Linear(d, d)
+            self.s = nn.Linear(d, d).to(torch.bfloat16)
+
+        def forward(self, x):
+            return self.s(self.w(x).bfloat16())
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.embed = nn.Embedding(1000, 16)                      # 16,000 parameters: a leftover leaf
+            self.blocks = nn.ModuleList([Block(16) for _ in range(5)])   # 544 each
+            self.odd = nn.ModuleList([Odd(16), Odd(16)])
+            self.head = nn.Linear(16, 4)
+
+    net = Net()
+    p = FSDPAutoPlanner(net, min_num_params=1000, leftover_min_num_params=10000,
+                        reshard_overrides={"blocks.2": 4}, reshard_default=True, reshard_root=False)
+    layer_units = [u for u in p.units if u["kind"] == "layers"]
+    # five blocks of 544 -> groups of two (>= 1000); the single tail block joins the last group
+    assert [u["names"] for u in layer_units if u["names"][0].startswith("blocks")] == [["blocks.0", "blocks.1"], ["blocks.2", "blocks.3", "blocks.4"]]
+    assert [u["reshard"] for u in layer_units if u["names"][0].startswith("blocks")] == [True, 4]
+    # mixed-dtype modules are descended into: their fp32 / bf16 linears group by parent and class (272 each: below the
+    # threshold even together within one parent, so they stay with the root)
+    assert not any(n.startswith("odd") for u in p.units for n in u["names"])
+    assert [u["names"] for u in p.units if u["kind"] == "leaf"] == [["embed"]]
+    planned = sum(u["params"] for u in p.units)
+    assert planned + p.root_params == sum(q.numel() for q in net.parameters())
+    assert "root" in p.describe() and "blocks.0, blocks.1" in p.describe()
+    q = FSDPAutoPlanner(net, min_num_params=1000, leftover_min_num_params=10000, no_wrap=["Block"])
+    # blocks may not be units: the walk reaches their linears (class Linear, parent blocks.i: 2 x 272 < 1000 per parent)
+    assert not any(n.startswith("blocks") for u in q.units for n in u["names"])
+
+    class Reached(Block):
+        forward = nn.Module.forward            # no forward of its own: other code calls its parts
+
+    net2 = nn.ModuleList([Reached(16) for _ in range(4)])
+    assert not FSDPAutoPlanner(net2, min_num_params=100, leftover_min_num_params=10000).units[0]["names"][0].count(".") == 0
+
+
+def test_lora_selection_adapter_files_and_merge(tmp_path):
+    import torch.nn as nn
+    from loongforge_b200.embodied import lora as L
+
+    class Attn(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q, self.k, self.o = nn.Linear(8, 8), nn.Linear(8, 8), nn.Linear(8, 8)
+
+        def forward(self, x):
+            return self.o(self.q(x) * self.k(x))
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.blocks = nn.ModuleList([Attn(), Attn()])
+            self.head = nn.Linear(8, 3)
+
+        def default_lora_targets(self):
+            return ["q", "k"]
+
+        def forward(self, x):
+            for b in self.blocks:
+                x = x + b(x)
+            return self.head(x)
+
+    torch.manual_seed(0)
+    net, x = Net(), torch.randn(4, 8)
+    y0 = net(x)
+    meta = L.inject_lora(net, 2, 4.0, [], use_rslora=True, exclude=["blocks.1.k"], modules_to_save=["head"])
+    assert meta["modules"] == ["blocks.0.q", "blocks.0.k", "blocks.1.q"] and meta["saved_modules"] == ["head"]
+    assert net.blocks[0].q.scale == 4.0 / 2 ** 0.5
+    assert torch.allclose(net(x), y0)                                        # B = 0: nothing changes yet
+    train = {n for n, p in net.named_parameters() if p.requires_grad}
+    assert train == {n for n in dict(net.named_parameters()) if "lora_" in n or n.startswith("head.")}
+    opt = torch.optim.SGD([p for p in net.parameters() if p.requires_grad], lr=0.01)
+    for _ in range(3):
+        opt.zero_grad()
+        net(x).pow(2).sum().backward()
+        opt.step()
+    y1 = net(x)
+    L.save_adapter(net, str(tmp_path / "ad"), meta, {"model_name": "toy"})
+    sd = torch.load(tmp_path / "ad" / L.ADAPTER_WEIGHTS)
+    assert set(sd) == {n if "lora_" in n else n for n in train} and not any(".base." in k for k in sd)
+    torch.manual_seed(0)
+    fresh = Net()                                                            # base weights as before training
+    got = L.load_adapter(fresh, str(tmp_path / "ad"))
+    assert got["model_name"] == "toy" and torch.allclose(fresh(x), y1, atol=1e-6)
+    assert L.merge_lora(fresh) == 3 and not any(isinstance(m, L.LoRALinear) for m in fresh.modules())
+    assert torch.allclose(fresh(x), y1, atol=1e-5)
+    with pytest.raises(ValueError):
+        L.inject_lora(Net(), 2, 4.0, ["nothing_matches"])
+    all_lin = L.inject_lora(Net(), 2, 4.0, ["all-linear"], exclude=["head"])
+    assert len(all_lin["modules"]) == 6
+    g = L.inject_lora(Net(), 2, 4.0, ["blocks.*.o"], dropout=0.1, init="gaussian")
+    assert g["modules"] == ["blocks.0.o", "blocks.1.o"]
