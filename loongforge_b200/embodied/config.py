@@ -75,6 +75,10 @@ class EmbodiedArgs:
     checkpoint_format: str = "pt"  # pt | dcp
     resume: bool = False
     log_interval: int = 1
+    log_stage_times: bool = False      # data / forward-backward / optimizer time per step, slowest rank
+    tensorboard: bool = False
+    wandb_project: Optional[str] = None  # written offline unless WANDB_MODE says otherwise
+    run_name: Optional[str] = None
     manual_gc_interval: int = 0
 
 

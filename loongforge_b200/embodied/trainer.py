@@ -16,7 +16,7 @@ from .config import EmbodiedArgs, set_global_args
 from .cuda_graph import MicrobatchGraphRunner
 from .data import ResumableLoader, build_dataset
 from .distributed import DistContext, apply_activation_checkpointing, grad_sync_context, wrap_model
-from .logging import MetricLogger
+from .logging import MetricLogger, StageTimers
 from .models import build_policy
 from .optimizer import LRScheduler, build_optimizer, clip_gradients
 
@@ -59,10 +59,21 @@ class BaseTrainer:
         self.optimizer = build_optimizer(self.model, a, ctx.world)
         self.scheduler = LRScheduler(self.optimizer, a.lr_scheduler, a.lr, a.min_lr, a.warmup_steps, a.train_steps)
         self.loader = ResumableLoader(build_dataset(a), a.per_device_batch_size, ctx.rank, ctx.world, a.seed)
-        self.logger = MetricLogger(a.output_dir, ctx.is_main, a.train_steps)
+        self.logger = MetricLogger(a.output_dir, ctx.is_main, a.train_steps, tensorboard=a.tensorboard,
+                                   wandb_project=a.wandb_project, run_name=a.run_name)
+        self.timers = StageTimers(a.log_stage_times)
+        self.logger.log_config(a)
+        self.logger.log_param_stats(self.model)
+        if self.lora_meta is not None:
+            self.logger.note(f"LoRA rank {self.lora_meta['rank']} on {len(self.lora_meta['modules'])} linear layers"
+                             + (f", fully trained: {self.lora_meta['saved_modules']}" if self.lora_meta["saved_modules"] else ""))
         self.graph_runner = MicrobatchGraphRunner(self.model, self.compute_loss) if a.per_microbatch_cuda_graph else None
         if a.resume:
             st = ckpt.load_checkpoint(a.output_dir, self.model, self.optimizer, self.scheduler, rank=ctx.rank)
+            if st is None:
+                self.logger.note(f"resume requested but no checkpoint under {a.output_dir}: starting from step 0")
+            else:
+                self.logger.note(f"resumed from step {st['step']}")
             if st is not None:
                 self.step = st["step"]
                 if st.get("dataloader"):
@@ -80,18 +91,23 @@ class BaseTrainer:
         a = self.args
         n = a.gradient_accumulation_steps
         total = 0.0
+        parts: Dict[str, float] = {}
         for i in range(n):
-            batch = self._to_device(next(it))
-            with grad_sync_context(self.model, sync=(i == n - 1)):
+            with self.timers("data"):
+                batch = self._to_device(next(it))
+            with self.timers("forward-backward"), grad_sync_context(self.model, sync=(i == n - 1)):
                 if self.graph_runner is not None:
                     loss = self.graph_runner.run(batch, 1.0 / n)
                 else:
                     loss = self.compute_loss(self.model, batch)
                     (loss / n).backward()
             total += float(loss.detach()) / n
-        norm = clip_gradients(self.model.parameters(), a.max_grad_norm, nan_clean=a.nan_clean,
-                              sharded=a.strategy in ("fsdp", "hsdp"))
-        self.optimizer.step()
+            for k, v in self._loss_parts().items():  # what the policy reports beside the total (video / action loss ...)
+                parts[k] = parts.get(k, 0.0) + float(v) / n
+        with self.timers("optimizer"):
+            norm = clip_gradients(self.model.parameters(), a.max_grad_norm, nan_clean=a.nan_clean,
+                                  sharded=a.strategy in ("fsdp", "hsdp"))
+            self.optimizer.step()
         if self.graph_runner is not None and self.graph_runner.graph is not None:
             for p in self.model.parameters():  # captured graphs accumulate into fixed .grad storage
                 if p.grad is not None:
@@ -99,7 +115,14 @@ class BaseTrainer:
         else:
             self.optimizer.zero_grad(set_to_none=True)
         self.scheduler.step()
-        return {"loss": total, "grad_norm": norm, "lr": self.optimizer.param_groups[0]["lr"]}
+        return {"loss": total, **parts, "grad_norm": norm, "lr": self.optimizer.param_groups[0]["lr"]}
+
+    def _loss_parts(self) -> Dict[str, torch.Tensor]:
+        for m in self.model.modules():
+            d = getattr(m, "last_losses", None)
+            if isinstance(d, dict) and d:
+                return d
+        return {}
 
     def _training_loop(self):
         a = self.args
@@ -108,7 +131,8 @@ class BaseTrainer:
             metrics = self._train_step(it)
             self.step += 1
             if a.log_interval and self.step % a.log_interval == 0:
-                self.logger.log(self.step, metrics, a.per_device_batch_size * a.gradient_accumulation_steps * self.ctx.world)
+                self.logger.log(self.step, metrics, a.per_device_batch_size * a.gradient_accumulation_steps * self.ctx.world,
+                                self.timers.summary(a.log_interval) if a.log_stage_times else None)
             if a.manual_gc_interval and self.step % a.manual_gc_interval == 0:
                 gc.collect()
             if a.save_interval and self.step % a.save_interval == 0:
@@ -131,6 +155,8 @@ class BaseTrainer:
             self._setup()
             self._training_loop()
         finally:
+            if hasattr(self, "logger"):
+                self.logger.finish()
             if self.args.manual_gc_interval:
                 gc.enable()
         return self.last_metrics if hasattr(self, "last_metrics") else {}

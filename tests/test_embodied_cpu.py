@@ -493,3 +493,38 @@ def test_lora_selection_adapter_files_and_merge(tmp_path):
     assert len(all_lin["modules"]) == 6
     g = L.inject_lora(Net(), 2, 4.0, ["blocks.*.o"], dropout=0.1, init="gaussian")
     assert g["modules"] == ["blocks.0.o", "blocks.1.o"]
+
+
+def test_metric_logger_and_stage_timers(tmp_path, capsys):
+    import time as _t
+    from loongforge_b200.embodied.logging import MetricLogger, StageTimers, flatten_config, format_block
+
+    a = _args(tmp_path, model_overrides={"size": "tiny", "nested": {"x": 1}})
+    flat = flatten_config(a)
+    assert flat["model_overrides.nested.x"] == 1 and flat["model_name"] == "pi05"
+    assert "model_name ..." in format_block("t", flat) and format_block("t", flat).startswith("-" * 24 + " t ")
+    lg = MetricLogger(str(tmp_path), True, total_steps=30, tensorboard=True, smoothing=5, spike_factor=3.0)
+    lg.log_config(a)
+    stats = lg.log_param_stats(torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.Linear(4, 2)))
+    assert stats["total"] == 30 and stats["trainable"] == 30
+    timers = StageTimers(True)
+    for step in range(1, 9):
+        with timers("data"):
+            _t.sleep(0.002)
+        with timers("optimizer"):
+            pass
+        loss = 10.0 if step == 8 else 1.0
+        lg.log(step, {"loss": loss, "video loss": 0.5, "lr": 1e-4}, samples=4, stage_times=timers.summary(1))
+    lg.finish()
+    recs = [json.loads(x) for x in open(tmp_path / "metrics.jsonl")]
+    assert len(recs) == 8 and recs[-1].get("loss_spike") is True and lg.spikes == 1
+    assert abs(recs[4]["loss_smoothed"] - 1.0) < 1e-9 and recs[-1]["time/data"] >= 2.0 and "eta_s" in recs[-1]
+    assert recs[3]["video loss"] == 0.5
+    out = capsys.readouterr().out
+    assert "loss spike at step 8" in out and "time (ms) | data:" in out and "end of embodied training arguments" in out
+    assert os.path.isdir(tmp_path / "tensorboard") and os.listdir(tmp_path / "tensorboard")
+    assert json.load(open(tmp_path / "config.json"))["model_name"] == "pi05"
+    off = StageTimers(False)
+    with off("x"):
+        pass
+    assert off.summary() == {}
