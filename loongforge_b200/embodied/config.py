@@ -24,6 +24,15 @@ class EmbodiedArgs:
     image_size: int = 56
     num_cameras: int = 1
     max_text_len: int = 16
+    use_transforms: bool = False       # per-policy sample pipeline of embodied/transforms.py (resize, augment, normalise, prompt / ids)
+    stats_path: Optional[str] = None   # stats.json (or a data-set directory with meta/stats.json); else computed and stored in output_dir
+    stats_samples: int = 2048          # samples read when the statistics are computed here
+    normalization_mode: Optional[str] = None  # mean_std | min_max | q99 | scale | identity; default by policy
+    image_augmentation: bool = False
+    image_resize_mode: str = "pad"     # pad | crop | stretch
+    relative_action_mask: List[bool] = dataclasses.field(default_factory=list)  # channels trained as offsets from the state
+    embodiment_tags: Dict[str, int] = dataclasses.field(default_factory=dict)   # tag / domain name -> id
+    robot_description: Optional[str] = None
     video_frames: int = 0  # world-model policies: future frames per sample (1 + 4k; 0 = none), camera 0, one per `video_frame_stride` steps
     video_frame_stride: int = 1
     # ---- optimisation

@@ -47,6 +47,8 @@ def hash_tokenize(text: str, max_len: int, vocab: int = 32000) -> np.ndarray:
 
 
 class SyntheticEpisodes(Dataset):
+    raw = False  # True: samples also carry the task string (and other non-tensor fields) for the transforms
+
     def __init__(self, args, num_episodes: int = 8, episode_len: int = 32, seed: int = 0):
         self.a, self.n, self.L, self.seed = args, num_episodes, episode_len, seed
 
@@ -61,8 +63,11 @@ class SyntheticEpisodes(Dataset):
         state = rng.standard_normal((self.L, a.state_dim)).astype(np.float32)
         img = np.random.default_rng(i).random((a.num_cameras, 3, a.image_size, a.image_size), dtype=np.float32)
         chunk, mask = _chunk(actions, t, a.action_horizon)
+        task = f"task {ep % 3} move the object"
         out = {"images": img, "state": state[t], "actions": chunk, "action_mask": mask,
-               "text": hash_tokenize(f"task {ep % 3} move the object", a.max_text_len)}
+               "text": hash_tokenize(task, a.max_text_len)}
+        if self.raw:
+            out["task"] = task
         if getattr(a, "video_frames", 0):
             # a smooth drift of the current image: frame k is the image rolled by k pixels (something a world model can learn)
             out["video"] = _future_frames(lambda k: np.roll(img[0], k - t, axis=-1), t, self.L + a.video_frames * a.video_frame_stride,
@@ -71,6 +76,8 @@ class SyntheticEpisodes(Dataset):
 
 
 class NpzEpisodes(Dataset):
+    raw = False
+
     def __init__(self, args, path: str):
         self.a = args
         self.files = sorted(glob.glob(os.path.join(path, "episode_*.npz")))
@@ -98,6 +105,10 @@ class NpzEpisodes(Dataset):
         task = str(ep["task"]) if "task" in ep else "do the task"
         out = {"images": ep["images"][t].astype(np.float32), "state": ep["state"][t].astype(np.float32),
                "actions": chunk, "action_mask": mask, "text": hash_tokenize(task, self.a.max_text_len)}
+        if self.raw:
+            out["task"] = task
+            if "embodiment_tag" in ep:
+                out["embodiment_tag"] = out["domain"] = str(ep["embodiment_tag"])
         if getattr(self.a, "video_frames", 0):
             out["video"] = _future_frames(lambda k: ep["images"][k][0], t, ep["images"].shape[0], self.a.video_frames,
                                           self.a.video_frame_stride)
@@ -105,6 +116,8 @@ class NpzEpisodes(Dataset):
 
 
 class LeRobotParquet(Dataset):
+    raw = False
+
     def __init__(self, args, path: str):
         import pyarrow.parquet as pq
 
@@ -137,15 +150,32 @@ class LeRobotParquet(Dataset):
         ep, a = self.episodes[e], self.a
         chunk, mask = _chunk(ep["actions"], t, a.action_horizon)
         img = np.zeros((a.num_cameras, 3, a.image_size, a.image_size), dtype=np.float32)  # videos are decoded offline
-        return {"images": img, "state": ep["state"][t], "actions": chunk, "action_mask": mask,
-                "text": hash_tokenize(ep["task"], a.max_text_len)}
+        out = {"images": img, "state": ep["state"][t], "actions": chunk, "action_mask": mask,
+               "text": hash_tokenize(ep["task"], a.max_text_len)}
+        if self.raw:
+            out["task"] = ep["task"]
+        return out
 
 
 def collate(samples: List[dict]) -> Dict[str, torch.Tensor]:
     return {k: torch.from_numpy(np.stack([s[k] for s in samples])) for k in samples[0]}
 
 
-def build_dataset(args) -> Dataset:
+class TransformedDataset(Dataset):
+    """A data set whose samples go through a ``transforms.Compose`` pipeline (in the worker that loads them)."""
+
+    def __init__(self, base: Dataset, transform):
+        base.raw = True
+        self.base, self.transform = base, transform
+
+    def __len__(self):
+        return len(self.base)
+
+    def __getitem__(self, i):
+        return self.transform(self.base[i])
+
+
+def _base_dataset(args) -> Dataset:
     if args.dataset_type == "synthetic":
         return SyntheticEpisodes(args)
     if args.dataset_type in ("npz_episodes", "hdf5"):
@@ -153,6 +183,27 @@ def build_dataset(args) -> Dataset:
     if args.dataset_type == "lerobot":
         return LeRobotParquet(args, args.dataset_path)
     raise ValueError(args.dataset_type)
+
+
+def build_dataset(args, training: bool = True) -> Dataset:
+    """The data set of ``args.dataset_type``; with ``use_transforms`` wrapped in the policy's pipeline, with statistics from
+    ``stats_path`` or, failing that, computed over the first ``stats_samples`` samples and kept as ``output_dir/stats.json``
+    (the file an evaluation server reads to turn predictions back into robot units)."""
+    ds = _base_dataset(args)
+    if not getattr(args, "use_transforms", False):
+        return ds
+    from . import transforms as T
+    own = os.path.join(args.output_dir, "stats.json")
+    if args.stats_path:
+        stats = T.load_stats(args.stats_path)
+    elif os.path.isfile(own):
+        stats = T.load_stats(own)
+    else:
+        stats = T.dataset_stats(ds, limit=args.stats_samples, relative_mask=list(args.relative_action_mask) or None)
+        if int(os.environ.get("RANK", "0")) == 0:
+            T.save_stats(stats, own)
+    stats = {"state": stats.get("state", stats.get("observation.state")), "actions": stats.get("actions", stats.get("action"))}
+    return TransformedDataset(ds, T.build_transforms(args, {k: v for k, v in stats.items() if v}, training))
 
 
 class ResumableLoader:

@@ -77,7 +77,7 @@ def main(argv=None) -> int:
         policy.eval()
         if torch.cuda.is_available():
             policy.cuda()
-        srv = serve(PolicyService(policy, args, action_space=a.action_space, denoise_steps=a.denoise_steps), a.host, a.port)
+        srv = serve(PolicyService.from_output_dir(policy, args, action_space=a.action_space, denoise_steps=a.denoise_steps), a.host, a.port)
         if a.once:
             print(json.dumps({"serving": True, "port": srv.port, "model": args.model_name}), flush=True)
             srv.stop()

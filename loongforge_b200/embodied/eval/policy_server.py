@@ -38,23 +38,76 @@ PAYLOAD_BUILDERS: Dict[str, Callable] = {n: build_payload for n in
                                           "dreamzero", "cosmos3")}
 
 
-class PolicyService:
-    """``predict_action(observation) -> action chunk`` around a FlowMatchingPolicy."""
+def transformed_payload(obs: Observation, transform, args, device="cpu", dtype=torch.float32):
+    """The observation through the policy's TRAINING pipeline in inference mode (same resize mode, state normalisation,
+    Pi0.5 prompt with the discretised state, embodiment / domain ids); returns the batch and the raw state (needed to turn
+    relative actions back into absolute targets)."""
+    cams = [obs.images[n].transpose(2, 0, 1).astype(np.float32) / 255.0 for n in sorted(obs.images)[:args.num_cameras]]
+    while len(cams) < args.num_cameras:
+        cams.append(np.zeros_like(cams[0]))
+    hw = cams[0].shape[1:]
+    cams = [c if c.shape[1:] == hw else np.zeros_like(cams[0]) for c in cams]
+    raw_state = np.zeros(args.state_dim, np.float32)
+    raw_state[:min(args.state_dim, obs.state.shape[0])] = obs.state[:args.state_dim]
+    sample = {"images": np.stack(cams), "state": raw_state.copy(), "task": obs.instruction,
+              "actions": np.zeros((args.action_horizon, args.action_dim), np.float32),
+              "action_mask": np.ones(args.action_horizon, np.float32)}
+    if getattr(obs, "embodiment_tag", None):
+        sample["embodiment_tag"] = sample["domain"] = obs.embodiment_tag
+    out = transform(sample)
+    if "text" not in out:
+        out["text"] = hash_tokenize(obs.instruction, args.max_text_len)
+    batch = {}
+    for k, v in out.items():
+        if k in ("actions", "action_mask"):
+            continue
+        t = torch.from_numpy(np.asarray(v))[None]
+        batch[k] = t.to(device, dtype) if t.is_floating_point() else t.to(device)
+    return batch, raw_state
 
-    def __init__(self, policy, args, action_space: str = "joint", denoise_steps: int = 10):
+
+class PolicyService:
+    """``predict_action(observation) -> action chunk`` around a policy. With ``transform`` (the training pipeline built by
+    ``embodied.transforms.build_transforms(args, stats, training=False)``) observations are prepared exactly as in training
+    and predictions are returned in robot units."""
+
+    def __init__(self, policy, args, action_space: str = "joint", denoise_steps: int = 10, transform=None):
         self.policy, self.args, self.space, self.steps = policy.eval(), args, action_space, denoise_steps
         self.device = next(policy.parameters()).device
         self.dtype = next(policy.parameters()).dtype
         self.calls = 0
+        self.transform = transform
+
+    @classmethod
+    def from_output_dir(cls, policy, args, **kw):
+        """Picks up ``stats.json`` written next to the checkpoints when the run used transforms."""
+        import os
+        transform = None
+        path = os.path.join(args.output_dir, "stats.json")
+        if getattr(args, "use_transforms", False) and os.path.isfile(path):
+            from .. import transforms as T
+            st = T.load_stats(path)
+            st = {"state": st.get("state"), "actions": st.get("actions")}
+            transform = T.build_transforms(args, {k: v for k, v in st.items() if v}, training=False)
+        return cls(policy, args, transform=transform, **kw)
 
     def predict_action(self, observation: dict) -> dict:
         t0 = time.perf_counter()
         obs = Observation.from_wire(observation)
         a = self.args
-        batch = PAYLOAD_BUILDERS.get(a.model_name, build_payload)(
-            obs, image_size=a.image_size, num_cameras=a.num_cameras, max_text_len=a.max_text_len,
-            state_dim=a.state_dim, device=self.device, dtype=self.dtype)
+        raw_state = None
+        if self.transform is not None:
+            batch, raw_state = transformed_payload(obs, self.transform, a, self.device, self.dtype)
+        else:
+            batch = PAYLOAD_BUILDERS.get(a.model_name, build_payload)(
+                obs, image_size=a.image_size, num_cameras=a.num_cameras, max_text_len=a.max_text_len,
+                state_dim=a.state_dim, device=self.device, dtype=self.dtype)
         actions = self.policy.predict_action(batch, steps=self.steps)[0].float().cpu().numpy()
+        if self.transform is not None:
+            from ..transforms import NormalizeStateAction
+            nsa = self.transform.find(NormalizeStateAction)
+            if nsa is not None:
+                actions = nsa.unnormalize_actions(actions[:, :a.action_dim], raw_state)
         self.calls += 1
         return ActionChunk(actions, self.space, (time.perf_counter() - t0) * 1e3).to_wire()
 

@@ -528,3 +528,113 @@ def test_metric_logger_and_stage_timers(tmp_path, capsys):
     with off("x"):
         pass
     assert off.summary() == {}
+
+
+def test_transforms_normalizer_images_rotations_and_prompts(tmp_path):
+    from loongforge_b200.embodied import transforms as T
+    from loongforge_b200.embodied.data import hash_tokenize
+
+    rng = np.random.default_rng(0)
+    data = rng.normal(2.0, 3.0, size=(500, 4)).astype(np.float32)
+    data[:, 3] = 7.0                                                    # a constant channel
+    st = T.compute_stats([data[:250], data[250:]])
+    assert abs(st["mean"][0] - data[:, 0].mean()) < 1e-4 and st["count"] == [500]
+    for mode in ("mean_std", "min_max", "q99", "scale"):
+        nz = T.Normalizer(mode, st)
+        y = nz.forward(data)
+        if mode in ("min_max", "q99"):
+            assert y[:, :3].min() >= -1 - 1e-6 and y[:, :3].max() <= 1 + 1e-6
+        inside = np.abs(y[:, :3]) < 1 if mode == "q99" else np.ones_like(y[:, :3], dtype=bool)
+        back = nz.inverse(y)
+        assert np.allclose(back[:, :3][inside], data[:, :3][inside], atol=1e-3), mode
+    assert np.allclose(T.Normalizer("mean_std", st).forward(data)[:, 3], 7.0)            # constant channel passes through
+    assert np.allclose(T.Normalizer("min_max", st).forward(data)[:, 3], 0.0)
+    masked = T.Normalizer("mean_std", st, mask=[True, True, False, False]).forward(data)
+    assert np.allclose(masked[:, 2], data[:, 2]) and not np.allclose(masked[:, 0], data[:, 0])
+    with pytest.raises(KeyError):
+        T.Normalizer("q99", {"mean": [0], "std": [1]})
+    T.save_stats({"state": st}, str(tmp_path / "meta" / "stats.json"))
+    assert T.load_stats(str(tmp_path))["state"]["q99"] == st["q99"]
+
+    img = np.zeros((3, 20, 40), np.float32)
+    img[:, :, 20:] = 1.0
+    padded = T.resize_with_pad(img, 32, 32)
+    assert padded.shape == (3, 32, 32) and padded[:, :8].max() == 0 and padded[:, 8:24, 28:].min() == 1.0
+    assert T.center_crop_resize(img, 16, 16).shape == (3, 16, 16)
+    aug = T.ImageAugment(seed=0)
+    s = aug({"images": rng.random((2, 3, 16, 16)).astype(np.float32)})
+    assert s["images"].shape == (2, 3, 16, 16) and 0 <= s["images"].min() and s["images"].max() <= 1
+
+    eul = rng.uniform(-1, 1, size=(5, 3))
+    r6 = T.RotationTransform("euler", "rot6d")
+    assert r6.forward(eul).shape == (5, 6) and np.allclose(r6.inverse(r6.forward(eul)), eul, atol=1e-5)
+    q = T.RotationTransform("euler", "quat")
+    assert np.allclose(q.inverse(q.forward(eul)), eul, atol=1e-5)
+    a, state = rng.normal(size=(4, 3)).astype(np.float32), rng.normal(size=(5,)).astype(np.float32)
+    rel = T.to_relative(a, state, [True, True, False])
+    assert np.allclose(rel[:, 2], a[:, 2]) and np.allclose(T.to_absolute(rel, state, [True, True, False]), a, atol=1e-6)
+
+    p = T.Pi05Prompt(lambda t, n: hash_tokenize(t, n), 48, num_bins=256, max_state_dim=4)
+    text = p.prompt("pick_up the\ncube ", np.array([-1.0, 0.0, 0.999]))
+    assert text == "Task: pick up the cube, State: 0 128 255 128;\nAction: "
+    assert p.prompt("x", None) == "Task: x;\nAction: "
+    g = T.GrootEmbodiment({"gr1": 3})({"embodiment_tag": "gr1", "state": {"arm": [1, 2], "hand": [3]}, "actions": np.zeros((2, 2))})
+    assert g["embodiment_id"] == 3
+    g2 = T.GrootEmbodiment({"gr1": 3}, state_keys=["hand", "arm"])({"state": {"arm": [1, 2], "hand": [3]}, "actions": np.zeros((2, 2))})
+    assert g2["embodiment_id"] == 4 and g2["state"].tolist() == [3, 1, 2]
+    assert T.Cosmos3Meta.append_sentence("Pick the cube", "Robot: arm.") == "Pick the cube. Robot: arm."
+    d = T.DreamZeroFlags()({"actions": np.array([[2.0, -3.0]]), "state": np.array([0.5]), "action_mask": np.zeros(1)})
+    assert d["actions"].tolist() == [[1.0, -1.0]] and d["has_real_action"] == 0.0
+
+
+@pytest.mark.parametrize("name", ["pi05", "dreamzero", "cosmos3"])
+def test_transformed_dataset_feeds_the_trainer(name, tmp_path):
+    from loongforge_b200.embodied.data import build_dataset, collate
+    from loongforge_b200.embodied.trainer import build_trainer
+
+    a = _args(tmp_path, model_name=name, model_overrides={"size": "tiny"}, use_transforms=True, image_augmentation=True,
+              image_size=32, stats_samples=64, train_steps=2, video_frames=9 if name == "dreamzero" else 5 if name == "cosmos3" else 0,
+              robot_description="A single-arm robot." if name == "cosmos3" else None, relative_action_mask=[True] * 7)
+    ds = build_dataset(a)
+    assert os.path.isfile(tmp_path / "stats.json")
+    b = collate([ds[i] for i in range(2)])
+    assert b["images"].shape == (2, 1, 3, 32, 32)
+    assert name == "cosmos3" or b["actions"].abs().max() <= 1 + 1e-6       # q99 / min-max are bounded, mean-std is not
+    if name == "dreamzero":
+        assert b["has_real_action"].tolist() == [1.0, 1.0] and b["embodiment_id"].tolist() == [0, 0]
+    if name == "cosmos3":
+        assert b["domain_id"].tolist() == [0, 0] and b["raw_action_dim"].tolist() == [7, 7]
+    nsa = ds.transform.find(__import__("loongforge_b200.embodied.transforms", fromlist=["x"]).NormalizeStateAction)
+    raw = ds.base[0]
+    norm = ds[0]["actions"]
+    inside = (np.abs(norm) < 1) | (name == "cosmos3")           # q99 / min-max clip the tails: those do not come back
+    assert inside.mean() > 0.8
+    assert np.allclose(nsa.unnormalize_actions(norm, raw["state"])[inside], raw["actions"][inside], atol=1e-3)
+    m = build_trainer(a).train()
+    assert np.isfinite(m["loss"])
+
+
+def test_policy_service_uses_training_transforms(tmp_path):
+    """A server started from a run's output directory prepares observations like the training pipeline and answers in
+    robot units (the statistics written during training bring the normalised prediction back)."""
+    from loongforge_b200.embodied.data import build_dataset
+    from loongforge_b200.embodied.eval.policy_server import PolicyService
+    from loongforge_b200.embodied.eval.protocol import ActionChunk, Observation
+    from loongforge_b200.embodied import transforms as T
+
+    a = _args(tmp_path, model_name="pi05", model_overrides={"size": "tiny"}, use_transforms=True, image_size=32, stats_samples=64)
+    build_dataset(a)                                            # writes stats.json
+    torch.manual_seed(0)
+    policy = build_policy("pi05", a)
+    svc = PolicyService.from_output_dir(policy, a, denoise_steps=2)
+    assert svc.transform is not None and svc.transform.find(T.Pi05Prompt) is not None
+    obs = Observation({"front": np.random.default_rng(0).integers(0, 255, (48, 64, 3), dtype=np.uint8)},
+                      np.linspace(-1, 1, 8).astype(np.float32), "pick up the cube")
+    out = ActionChunk.from_wire(svc.predict_action(obs.to_wire()))
+    assert out.actions.shape == (a.action_horizon, a.action_dim) and np.isfinite(out.actions).all()
+    plain = PolicyService(policy, a, denoise_steps=2)
+    nsa = svc.transform.find(T.NormalizeStateAction)
+    lo, hi = np.asarray(nsa.action.s["q01"]), np.asarray(nsa.action.s["q99"])
+    # the transformed service answers inside the data's action range (inverse of a [-1, 1] normalisation, up to overshoot)
+    assert (out.actions > lo - 3 * (hi - lo)).all() and (out.actions < hi + 3 * (hi - lo)).all()
+    assert plain.transform is None
