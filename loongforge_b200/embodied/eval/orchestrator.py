@@ -63,11 +63,17 @@ ENV_ADAPTERS: Dict[str, Callable] = {"reach": ReachEnv, **{n: _unavailable(n) fo
 class EvalConfig:
     env: str = "reach"
     env_kwargs: dict = dataclasses.field(default_factory=dict)
-    episodes: int = 5
-    replan_every: int = 4  # execute this many actions of a chunk before asking the policy again
+    episodes: int = 5                 # per task and seed
+    replan_every: int = 4             # execute this many actions of a chunk before asking the policy again
     host: str = "127.0.0.1"
     port: int = 0
     output_dir: Optional[str] = None
+    suite: str = "default"
+    tasks: List[dict] = dataclasses.field(default_factory=list)   # [{"name": ..., "env_kwargs": {...}}]; empty: one task
+    seeds: List[int] = dataclasses.field(default_factory=lambda: [0])
+    resume: bool = True               # skip the episodes already in output_dir/results.jsonl
+    min_episodes: int = 1             # floor checked in the report
+    name: str = "run"
 
 
 class ResourceMonitor:
@@ -88,40 +94,65 @@ class ResourceMonitor:
 
 
 def run_evaluation(cfg: EvalConfig, action_adapter: Optional[Callable[[np.ndarray, Observation], np.ndarray]] = None) -> dict:
-    """Rolls out `cfg.episodes` episodes against the policy server at (host, port). `action_adapter` maps a policy
+    """Rolls out ``cfg.episodes`` episodes of every task and seed against the policy server at (host, port). Every finished
+    episode is appended to ``output_dir/results.jsonl``; with ``resume`` the episodes found there are not run again. The
+    report (``report.json`` / ``report.md`` / CSV summaries) covers old and new episodes. `action_adapter` maps a policy
     action and the current observation to the environment's command (identity by default)."""
+    from . import metrics as M
+
     client = RPCClient(cfg.host, cfg.port)
     info = client.call("info")
-    env = ENV_ADAPTERS[cfg.env](**cfg.env_kwargs)
+    results = os.path.join(cfg.output_dir, "results.jsonl") if cfg.output_dir else None
+    records = M.load_jsonl(results) if (results and cfg.resume) else []
+    if results and not cfg.resume and os.path.isfile(results):
+        os.remove(results)
+    done = M.completed_keys(records)
+    tasks = cfg.tasks or [{"name": cfg.env, "env_kwargs": cfg.env_kwargs}]
     mon = ResourceMonitor()
-    episodes, lat = [], []
-    for _ in range(cfg.episodes):
-        obs, done, success, steps = env.reset(), False, False, 0
-        while not done:
-            t0 = time.perf_counter()
-            chunk = ActionChunk.from_wire(client.call("predict_action", observation=obs.to_wire()))
-            lat.append({"round_trip_ms": (time.perf_counter() - t0) * 1e3, "server_ms": client.last_server_ms})
-            for a in chunk.actions[:cfg.replan_every]:
-                cmd = action_adapter(a, obs) if action_adapter is not None else a
-                obs, done, success = env.step(cmd)
-                steps += 1
-                if done:
-                    break
-            mon.sample()
-        episodes.append({"success": success, "steps": steps})
+    for task_id, task in enumerate(tasks):
+        for seed in cfg.seeds:
+            kw = {**cfg.env_kwargs, **task.get("env_kwargs", {})}
+            if "seed" not in kw:
+                kw["seed"] = seed
+            env = None
+            for ep in range(cfg.episodes):
+                key = (cfg.suite, task["name"], ep, seed)
+                if env is None:
+                    env = ENV_ADAPTERS[task.get("env", cfg.env)](**kw)
+                obs = env.reset()              # also for finished episodes: the environment's random stream stays aligned
+                if key in done:
+                    continue
+                finished, success, steps, rt, sv = False, False, 0, [], []
+                while not finished:
+                    t0 = time.perf_counter()
+                    chunk = ActionChunk.from_wire(client.call("predict_action", observation=obs.to_wire()))
+                    rt.append((time.perf_counter() - t0) * 1e3)
+                    sv.append(client.last_server_ms)
+                    for a in chunk.actions[:cfg.replan_every]:
+                        cmd = action_adapter(a, obs) if action_adapter is not None else a
+                        obs, finished, success = env.step(cmd)
+                        steps += 1
+                        if finished:
+                            break
+                    mon.sample()
+                rec = {"suite": cfg.suite, "task": task["name"], "task_id": task_id, "episode": ep, "seed": seed,
+                       "success": bool(success), "steps": steps, "failure_reason": None if success else "timeout",
+                       "round_trip_ms": rt, "server_ms": sv}
+                records.append(rec)
+                if results:
+                    M.append_jsonl(results, rec)
     client.close()
-    rt = np.array([x["round_trip_ms"] for x in lat])
-    report = {"policy": info, "env": cfg.env, "episodes": episodes,
-              "success_rate": float(np.mean([e["success"] for e in episodes])),
-              "mean_steps": float(np.mean([e["steps"] for e in episodes])),
-              "latency_ms": {"mean": float(rt.mean()), "p50": float(np.percentile(rt, 50)),
-                             "p95": float(np.percentile(rt, 95)),
-                             "server_mean": float(np.mean([x["server_ms"] for x in lat]))},
-              "resources": mon.summary()}
+    cfg_dict = {k: v for k, v in dataclasses.asdict(cfg).items()}
     if cfg.output_dir:
-        os.makedirs(cfg.output_dir, exist_ok=True)
-        with open(os.path.join(cfg.output_dir, "report.json"), "w") as f:
-            json.dump(report, f, indent=1)
+        report = M.write_report(cfg.output_dir, records, name=cfg.name, policy=info, config=cfg_dict,
+                                min_episodes=cfg.min_episodes, resources=mon.summary())
+    else:
+        import tempfile
+        with tempfile.TemporaryDirectory() as tmp:
+            report = M.write_report(tmp, records, name=cfg.name, policy=info, config=cfg_dict, min_episodes=cfg.min_episodes,
+                                    resources=mon.summary())
+    report["env"] = cfg.env
+    report["episodes"] = [{"success": r["success"], "steps": r["steps"]} for r in records if "success" in r]
     return report
 
 

@@ -638,3 +638,44 @@ def test_policy_service_uses_training_transforms(tmp_path):
     # the transformed service answers inside the data's action range (inverse of a [-1, 1] normalisation, up to overshoot)
     assert (out.actions > lo - 3 * (hi - lo)).all() and (out.actions < hi + 3 * (hi - lo)).all()
     assert plain.transform is None
+
+
+def test_eval_metrics_resume_and_report(tmp_path):
+    from loongforge_b200.embodied.eval import metrics as M
+    from loongforge_b200.embodied.eval.orchestrator import EvalConfig, run_evaluation
+    from loongforge_b200.embodied.eval.policy_server import MockPolicyService, serve
+
+    lo, hi = M.wilson_interval(8, 10)
+    assert abs(lo - 0.4902) < 1e-3 and abs(hi - 0.9433) < 1e-3 and M.wilson_interval(0, 0) == (0.0, 1.0)
+    recs = [{"suite": "s", "task": "a", "episode": i, "seed": 0, "success": i < 3, "steps": 10 + i, "failure_reason": None if i < 3 else "timeout"}
+            for i in range(4)] + [{"suite": "s", "task": "b", "episode": 0, "seed": 0, "success": False, "steps": 5, "failure_reason": "collision"}]
+    tasks = M.summarize_tasks(recs)
+    assert [t["task"] for t in tasks] == ["a", "b"] and tasks[0]["success_rate"] == 0.75 and tasks[0]["failure_reasons"] == {"timeout": 1}
+    suite = M.summarize_suites(recs, min_episodes=2)[0]
+    assert suite["episodes"] == 5 and suite["success_rate"] == 0.6 and suite["task_mean_success_rate"] == 0.75 and suite["short_tasks"] == ["b"]
+    assert M.validate_episode_floor(recs, 2) == [{"suite": "s", "task": "b", "episodes": 1, "required": 2}]
+    p = str(tmp_path / "r.jsonl")
+    for r in recs[:2]:
+        M.append_jsonl(p, r)
+    with open(p, "a") as f:
+        f.write('{"suite": "s", "task": "a", "epis')                      # a record cut off by an interruption
+    assert len(M.load_jsonl(p)) == 2 and M.completed_keys(M.load_jsonl(p)) == {("s", "a", 0, 0), ("s", "a", 1, 0)}
+
+    srv = serve(MockPolicyService(horizon=4, action_dim=3))
+    to_goal = lambda a, obs: obs.state[3:6] + 0 * a  # noqa: E731
+    out = str(tmp_path / "eval")
+    cfg = EvalConfig(episodes=2, port=srv.port, output_dir=out, suite="reach", seeds=[0, 1], min_episodes=3,
+                     tasks=[{"name": "easy", "env_kwargs": {"tol": 0.2}}, {"name": "never", "env_kwargs": {"tol": 0.2, "max_steps": 3}}])
+    rep = run_evaluation(cfg, action_adapter=to_goal)
+    assert len(M.load_jsonl(os.path.join(out, "results.jsonl"))) == 8 and rep["success_rate"] == 1.0 and len(rep["tasks"]) == 2 and rep["suites"][0]["episodes"] == 8
+    assert rep["latency_ms"]["calls"] >= 8 and not rep["floor_violations"]          # 2 episodes x 2 seeds = 4 per task
+    # resume: nothing runs again, one more episode per task and seed is added
+    cfg.episodes = 3
+    rep2 = run_evaluation(cfg, action_adapter=lambda a, obs: np.ones(3) * 5)        # the new episodes fail
+    srv.stop()
+    assert len(M.load_jsonl(os.path.join(out, "results.jsonl"))) == 12
+    assert abs(rep2["success_rate"] - 8 / 12) < 1e-9 and len(rep2["failures"]) == 4 and rep2["failures"][0]["failure_reason"] == "timeout"
+    md = open(os.path.join(out, "report.md")).read()
+    assert "## Suites" in md and "| reach | easy | 6 | 4 |" in md and "## Failed episodes" in md and "## Reproduction" in md
+    rows = list(__import__("csv").DictReader(open(os.path.join(out, "summary_tasks.csv"))))
+    assert len(rows) == 2 and rows[0]["task"] == "easy" and float(rows[0]["ci95_high"]) <= 1.0
