@@ -48,7 +48,10 @@ def latest_step(root: str) -> Optional[int]:
 
 def save_checkpoint(root: str, step: int, model: nn.Module, optimizer, scheduler=None, *, fmt: str = "pt",
                     dataloader_state: Optional[dict] = None, lora_meta: Optional[dict] = None, rank: int = 0,
-                    world: int = 1) -> str:
+                    world: int = 1, async_save: bool = False) -> str:
+    """``optimizer=None`` stores the weights only. ``async_save`` (pt format): tensors are copied to the host here and the
+    file is written by a background thread (``wait_async_saves`` joins them; the ``latest`` marker moves only when the
+    file is complete)."""
     d = _step_dir(root, step)
     os.makedirs(d, exist_ok=True)
     inner = _unwrap(model)
@@ -56,15 +59,27 @@ def save_checkpoint(root: str, step: int, model: nn.Module, optimizer, scheduler
         import torch.distributed.checkpoint as dcp
         from torch.distributed.checkpoint.state_dict import get_state_dict
 
-        msd, osd = get_state_dict(inner, optimizer)
-        dcp.save({"model": msd, "optim": osd}, checkpoint_id=os.path.join(d, "dcp"))
+        if optimizer is None:
+            from torch.distributed.checkpoint.state_dict import get_model_state_dict
+            dcp.save({"model": get_model_state_dict(inner)}, checkpoint_id=os.path.join(d, "dcp"))
+        else:
+            msd, osd = get_state_dict(inner, optimizer)
+            dcp.save({"model": msd, "optim": osd}, checkpoint_id=os.path.join(d, "dcp"))
     else:
         sharded = hasattr(optimizer, "local_state_dict")  # ZeRO-1: every rank writes the shard it owns, keyed by name
         if sharded:
             torch.save(optimizer.local_state_dict(), os.path.join(d, f"optim_shard_{rank:05d}.pt"))
         if rank == 0:
-            torch.save({"model": inner.state_dict(), "optim": None if sharded else optimizer.state_dict()},
-                       os.path.join(d, "model_optim.pt"))
+            blob = {"model": inner.state_dict(), "optim": None if (sharded or optimizer is None) else optimizer.state_dict()}
+            target = os.path.join(d, "model_optim.pt")
+            if async_save:
+                blob = _to_host(blob)
+                import threading
+                th = threading.Thread(target=_write_then_mark, args=(blob, target, root, step), daemon=False)
+                th.start()
+                _PENDING.append(th)
+            else:
+                torch.save(blob, target)
     # per-rank auxiliary state
     torch.save({"rng": rng_state(), "dataloader": dataloader_state}, os.path.join(d, f"aux_rank{rank:05d}.pt"))
     if rank == 0:
@@ -74,12 +89,40 @@ def save_checkpoint(root: str, step: int, model: nn.Module, optimizer, scheduler
             json.dump(meta, f)
     if world > 1 and dist.is_initialized():
         dist.barrier()
-    if rank == 0:
-        tmp = os.path.join(root, "latest.tmp")
-        with open(tmp, "w") as f:
-            f.write(str(step))
-        os.replace(tmp, os.path.join(root, "latest"))
+    if rank == 0 and not (async_save and fmt != "dcp"):
+        _mark_latest(root, step)
     return d
+
+
+_PENDING: list = []
+
+
+def _mark_latest(root: str, step: int) -> None:
+    tmp = os.path.join(root, "latest.tmp")
+    with open(tmp, "w") as f:
+        f.write(str(step))
+    os.replace(tmp, os.path.join(root, "latest"))
+
+
+def _to_host(obj):
+    if torch.is_tensor(obj):
+        return obj.detach().to("cpu", copy=True)
+    if isinstance(obj, dict):
+        return {k: _to_host(v) for k, v in obj.items()}
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_to_host(v) for v in obj)
+    return obj
+
+
+def _write_then_mark(blob, target: str, root: str, step: int) -> None:
+    torch.save(blob, target + ".tmp")
+    os.replace(target + ".tmp", target)
+    _mark_latest(root, step)
+
+
+def wait_async_saves() -> None:
+    while _PENDING:
+        _PENDING.pop().join()
 
 
 def load_checkpoint(root: str, model: nn.Module, optimizer=None, scheduler=None, *, step: Optional[int] = None,

@@ -43,13 +43,34 @@ class EmbodiedArgs:
     min_lr: float = 0.0
     weight_decay: float = 0.01
     warmup_steps: int = 0
-    lr_scheduler: str = "cosine"  # constant | linear | cosine | wsd
+    lr_scheduler: str = "cosine"  # constant | linear | cosine | cosine_restarts | polynomial | wsd
+    lr_decay_steps: Optional[int] = None   # where the decay ends (default: train_steps)
+    lr_num_cycles: int = 1
+    lr_power: float = 1.0
+    lr_mults: Dict[str, float] = dataclasses.field(default_factory=dict)  # parameter-name prefix -> lr multiplier
+    optimizer: str = "adamw"      # adamw | adam | sgd | lion
+    adam_eps: float = 1e-8
     adam_beta1: float = 0.9
     adam_beta2: float = 0.95
     max_grad_norm: float = 1.0
     nan_clean: bool = True
     bf16: bool = False
     seed: int = 1234
+    deterministic_mode: bool = False   # deterministic algorithms + no cuDNN autotuning
+    disable_tf32: bool = False
+    check_for_nan_in_loss: bool = True  # stop with an error when the loss is not finite
+    pretrained_checkpoint: Optional[str] = None  # .pt / .safetensors file or a directory of them: weights loaded before training
+    pretrained_strict: bool = False
+    freeze_modules: List[str] = dataclasses.field(default_factory=list)  # dot paths or globs of sub-modules kept frozen
+    num_workers: int = 0
+    save_training_state: bool = True   # False: checkpoints hold the weights only
+    async_save: bool = False           # pt format: the file is written by a background thread from a CPU copy
+    profile_step_start: int = -1       # torch profiler over [start, end) on rank 0, trace in output_dir/profile
+    profile_step_end: int = -1
+    fsdp_param_dtype: Optional[str] = None    # FSDP mixed precision: dtype of the gathered parameters (bf16)
+    fsdp_reduce_dtype: Optional[str] = None   # ... and of the gradient reduce-scatter (fp32)
+    ddp_find_unused_parameters: bool = False
+    ddp_broadcast_buffers: bool = True
     # ---- distribution
     strategy: str = "ddp"  # ddp | zero1 | fsdp | hsdp
     fsdp_wrap_patterns: List[str] = dataclasses.field(default_factory=lambda: ["blocks.*", "layers.*"])
@@ -106,6 +127,14 @@ def validate(a: EmbodiedArgs) -> EmbodiedArgs:
         raise ValueError(f"unknown checkpoint format {a.checkpoint_format}")
     if a.per_microbatch_cuda_graph and a.strategy in ("fsdp", "hsdp"):
         raise ValueError("per-microbatch CUDA graphs need parameters resident on the device (ddp / zero1)")
+    if a.lr_scheduler not in ("constant", "linear", "cosine", "cosine_restarts", "polynomial", "wsd"):
+        raise ValueError(f"unknown lr_scheduler {a.lr_scheduler}")
+    if a.optimizer not in ("adamw", "adam", "sgd", "lion"):
+        raise ValueError(f"unknown optimizer {a.optimizer}")
+    if a.async_save and a.checkpoint_format != "pt":
+        raise ValueError("async_save writes the single-file format (checkpoint_format: pt)")
+    if a.ddp_find_unused_parameters and a.ddp_static_graph:
+        a.ddp_static_graph = False  # a static graph cannot have parameters that come and go
     if a.lora_rank < 0:
         raise ValueError("lora_rank must be >= 0")
     return a

@@ -213,7 +213,9 @@ def wrap_model(model: nn.Module, args, ctx: DistContext) -> nn.Module:
     if args.strategy in ("ddp", "zero1"):
         ddp = nn.parallel.DistributedDataParallel(
             model, device_ids=[ctx.local_rank] if ctx.device.type == "cuda" else None,
-            bucket_cap_mb=args.ddp_bucket_mb, gradient_as_bucket_view=True, static_graph=args.ddp_static_graph)
+            bucket_cap_mb=args.ddp_bucket_mb, gradient_as_bucket_view=True, static_graph=args.ddp_static_graph,
+            find_unused_parameters=getattr(args, "ddp_find_unused_parameters", False),
+            broadcast_buffers=getattr(args, "ddp_broadcast_buffers", True))
         if args.ddp_comm_hook == "bf16_compress":
             ddp.register_comm_hook(None, bf16_compress_hook)
         return ddp

@@ -194,6 +194,7 @@ def write_report(output_dir: str, records: List[Record], *, name: str = "run", p
               "floor_violations": validate_episode_floor(records, min_episodes), "latency_ms": latency_summary(done),
               "failures": [{k: r.get(k) for k in ("suite", "task", "episode", "seed", "steps", "failure_reason")}
                            for r in done if not r["success"]],
+              "episodes": [{k: r.get(k) for k in ("suite", "task", "episode", "seed", "success", "steps")} for r in done],
               "resources": resources or {},
               "reproduction": {"config": config or {}, "host": resource_snapshot(), "source": source_revision()}}
     os.makedirs(output_dir, exist_ok=True)

@@ -152,7 +152,6 @@ def run_evaluation(cfg: EvalConfig, action_adapter: Optional[Callable[[np.ndarra
             report = M.write_report(tmp, records, name=cfg.name, policy=info, config=cfg_dict, min_episodes=cfg.min_episodes,
                                     resources=mon.summary())
     report["env"] = cfg.env
-    report["episodes"] = [{"success": r["success"], "steps": r["steps"]} for r in records if "success" in r]
     return report
 
 

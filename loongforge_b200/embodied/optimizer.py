@@ -184,23 +184,65 @@ class ZeroAdamW(torch.optim.Optimizer):
 
 
 def build_optimizer(model: nn.Module, args, world: int = 1):
-    groups = build_param_groups(model, args.weight_decay, args.lr)
-    kw = dict(lr=args.lr, betas=(args.adam_beta1, args.adam_beta2), eps=1e-8)
+    """``optimizer``: adamw (default) | adam | sgd | lion; ``strategy: zero1`` always uses the sharded AdamW; ``lr_mults``
+    maps parameter-name prefixes to learning-rate multipliers (a slower backbone next to a fresh head)."""
+    mults = dict(getattr(args, "lr_mults", None) or {})
+    groups = build_param_groups(model, args.weight_decay, args.lr, {("module." + k if hasattr(model, "module") else k): v
+                                                                     for k, v in mults.items()})
+    eps = getattr(args, "adam_eps", 1e-8)
+    kw = dict(lr=args.lr, betas=(args.adam_beta1, args.adam_beta2), eps=eps)
     if args.strategy == "zero1":
         names = {id(p): n[len("module."):] if n.startswith("module.") else n for n, p in model.named_parameters()}
         return ZeroAdamW(groups, names, weight_decay=args.weight_decay, **kw)
+    kind = getattr(args, "optimizer", "adamw")
+    if kind == "adamw":
+        cls, ckw = torch.optim.AdamW, kw
+    elif kind == "adam":
+        cls, ckw = torch.optim.Adam, kw
+    elif kind == "sgd":
+        cls, ckw = torch.optim.SGD, dict(lr=args.lr, momentum=args.adam_beta1)
+    elif kind == "lion":
+        cls, ckw = Lion, dict(lr=args.lr, betas=(args.adam_beta1, args.adam_beta2))
+    else:
+        raise ValueError(f"unknown optimizer {kind!r} (adamw | adam | sgd | lion)")
     if args.fp32_master_weights:
-        return FP32MasterAdapter(groups, torch.optim.AdamW, **kw)
-    return torch.optim.AdamW(groups, **kw)
+        return FP32MasterAdapter(groups, cls, **ckw)
+    return cls(groups, **ckw)
+
+
+class Lion(torch.optim.Optimizer):
+    """Sign-of-interpolated-momentum update with decoupled weight decay: ``u = sign(b1 m + (1 - b1) g)``,
+    ``p -= lr (u + wd p)``, ``m = b2 m + (1 - b2) g``."""
+
+    def __init__(self, params, lr: float = 1e-4, betas=(0.9, 0.99), weight_decay: float = 0.0):
+        super().__init__(params, dict(lr=lr, betas=betas, weight_decay=weight_decay))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        for g in self.param_groups:
+            b1, b2 = g["betas"]
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if not st:
+                    st["exp_avg"] = torch.zeros_like(p)
+                m = st["exp_avg"]
+                p.mul_(1 - g["lr"] * g["weight_decay"])
+                p.add_(torch.sign(m * b1 + p.grad * (1 - b1)), alpha=-g["lr"])
+                m.mul_(b2).add_(p.grad, alpha=1 - b2)
 
 
 class LRScheduler:
-    """constant | linear | cosine | wsd (warmup - stable - decay), all with linear warm-up; per-group multipliers kept."""
+    """constant | linear | cosine | cosine_restarts | polynomial | wsd (warmup - stable - decay), all with linear warm-up;
+    per-group multipliers kept. ``total`` is the step at which the decay ends (the learning rate stays at ``min_lr`` after
+    it); ``num_cycles`` cosine periods for ``cosine_restarts``; ``power`` for ``polynomial``."""
 
     def __init__(self, optimizer, kind: str, max_lr: float, min_lr: float, warmup: int, total: int,
-                 decay_fraction: float = 0.1):
+                 decay_fraction: float = 0.1, num_cycles: int = 1, power: float = 1.0):
         self.opt, self.kind, self.max_lr, self.min_lr = optimizer, kind, max_lr, min_lr
         self.warmup, self.total, self.decay_fraction = warmup, max(total, 1), decay_fraction
+        self.num_cycles, self.power = max(int(num_cycles), 1), power
         self.step_count = 0
         self._apply()
 
@@ -215,6 +257,13 @@ class LRScheduler:
             return self.max_lr + (self.min_lr - self.max_lr) * frac
         if self.kind == "cosine":
             return self.min_lr + 0.5 * (self.max_lr - self.min_lr) * (1 + math.cos(math.pi * frac))
+        if self.kind == "cosine_restarts":
+            if frac >= 1.0:
+                return self.min_lr
+            within = (frac * self.num_cycles) % 1.0
+            return self.min_lr + 0.5 * (self.max_lr - self.min_lr) * (1 + math.cos(math.pi * within))
+        if self.kind == "polynomial":
+            return self.min_lr + (self.max_lr - self.min_lr) * (1 - frac) ** self.power
         if self.kind == "wsd":
             start = 1.0 - self.decay_fraction
             if frac < start:

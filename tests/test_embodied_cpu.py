@@ -679,3 +679,48 @@ def test_eval_metrics_resume_and_report(tmp_path):
     assert "## Suites" in md and "| reach | easy | 6 | 4 |" in md and "## Failed episodes" in md and "## Reproduction" in md
     rows = list(__import__("csv").DictReader(open(os.path.join(out, "summary_tasks.csv"))))
     assert len(rows) == 2 and rows[0]["task"] == "easy" and float(rows[0]["ci95_high"]) <= 1.0
+
+
+def test_trainer_options_pretrained_freeze_schedules_async_save(tmp_path):
+    from loongforge_b200.embodied.optimizer import Lion, LRScheduler, build_optimizer
+    from loongforge_b200.embodied.trainer import build_trainer, freeze_modules, load_pretrained
+
+    a = _args(tmp_path / "a", train_steps=2, save_interval=2, async_save=True, save_training_state=False, num_workers=0,
+              deterministic_mode=True, lr_scheduler="cosine_restarts", lr_num_cycles=2, lr_decay_steps=8, optimizer="lion",
+              lr_mults={"policy.decoder.expert": 0.1}, profile_step_start=0, profile_step_end=1)
+    t = build_trainer(a)
+    t.train()
+    assert isinstance(t.optimizer, Lion) and {round(g["lr_mult"], 3) for g in t.optimizer.param_groups} == {0.1, 1.0}
+    assert ckpt.latest_step(str(tmp_path / "a")) == 2                       # the background writer finished and marked it
+    blob = torch.load(tmp_path / "a" / "step_00000002" / "model_optim.pt", weights_only=False)
+    assert blob["optim"] is None and os.listdir(tmp_path / "a" / "profile")
+    sd = blob["model"]
+    # a second run starts from those weights with part of the model frozen
+    b = _args(tmp_path / "b", train_steps=1, pretrained_checkpoint=str(tmp_path / "a" / "step_00000002" / "model_optim.pt"),
+              freeze_modules=["policy.decoder.lang.*"])
+    t2 = build_trainer(b)
+    t2._setup()
+    got = ckpt._unwrap(t2.model).state_dict()
+    assert all(torch.equal(got[k], v) for k, v in sd.items())
+    frozen = [n for n, p in t2.model.named_parameters() if not p.requires_grad]
+    assert frozen and all(".decoder.lang." in n for n in frozen)
+    with pytest.raises(KeyError):
+        freeze_modules(t2.model, ["no.such.module"])
+    rep = load_pretrained(t2.model, str(tmp_path / "a" / "step_00000002"))           # a directory of weight files
+    assert rep["loaded"] == len(sd) and not rep["missing"]
+    with pytest.raises(KeyError):
+        load_pretrained(t2.model, _save_partial(tmp_path, sd), strict=True)
+    s = LRScheduler(torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=1.0), "cosine_restarts", 1.0, 0.0, 0, 8, num_cycles=2)
+    assert s.lr_at(0) == 1.0 and abs(s.lr_at(2) - 0.5) < 1e-9 and s.lr_at(4) == 1.0 and s.lr_at(8) == 0.0 and s.lr_at(20) == 0.0
+    pl = LRScheduler(torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=1.0), "polynomial", 1.0, 0.1, 0, 10, power=2.0)
+    assert abs(pl.lr_at(5) - (0.1 + 0.9 * 0.25)) < 1e-9
+    with pytest.raises(ValueError):
+        validate(EmbodiedArgs(optimizer="adagrad"))
+    with pytest.raises(ValueError):
+        validate(EmbodiedArgs(async_save=True, checkpoint_format="dcp"))
+
+
+def _save_partial(tmp_path, sd):
+    p = str(tmp_path / "partial.pt")
+    torch.save({k: v for i, (k, v) in enumerate(sd.items()) if i % 2 == 0}, p)
+    return p
