@@ -193,13 +193,13 @@ class FSDPAutoPlanner:
         lines = [f"{u['kind']:6s} {u['params']:>12,d}  reshard={u['reshard']}  {', '.join(u['names'])}" for u in self.units]
         return "\n".join(lines + [f"root   {self.root_params:>12,d}  reshard={self.reshard_root}"])
 
-    def apply(self, mesh) -> List[nn.Module]:
+    def apply(self, mesh, **fsdp_kw) -> List[nn.Module]:
         from torch.distributed.fsdp import fully_shard
         handles = []
         for u in self.units:
             mods = [self.model.get_submodule(n) for n in u["names"]]
-            handles.append(fully_shard(mods if len(mods) > 1 else mods[0], mesh=mesh, reshard_after_forward=u["reshard"]))
-        fully_shard(self.model, mesh=mesh, reshard_after_forward=self.reshard_root)
+            handles.append(fully_shard(mods if len(mods) > 1 else mods[0], mesh=mesh, reshard_after_forward=u["reshard"], **fsdp_kw))
+        fully_shard(self.model, mesh=mesh, reshard_after_forward=self.reshard_root, **fsdp_kw)
         return [h[0] if isinstance(h, (list, tuple)) else h for h in handles]
 
 
@@ -228,18 +228,23 @@ def wrap_model(model: nn.Module, args, ctx: DistContext) -> nn.Module:
         mesh = init_device_mesh(dev_type, (ctx.world // shard, shard), mesh_dim_names=("replicate", "shard"))
     else:
         mesh = init_device_mesh(dev_type, (ctx.world,), mesh_dim_names=("shard",))
+    fsdp_kw = {}
+    if getattr(args, "fsdp_param_dtype", None) or getattr(args, "fsdp_reduce_dtype", None):
+        from torch.distributed.fsdp import MixedPrecisionPolicy
+        to = {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32, "float32": torch.float32, None: None}
+        fsdp_kw["mp_policy"] = MixedPrecisionPolicy(param_dtype=to[args.fsdp_param_dtype], reduce_dtype=to[args.fsdp_reduce_dtype])
     if list(args.fsdp_wrap_patterns) == ["auto"]:
         planner = FSDPAutoPlanner(model, args.fsdp_min_num_params, args.fsdp_leftover_min_num_params, args.fsdp_no_wrap_modules,
                                   args.fsdp_reshard_default, args.fsdp_reshard_root, args.fsdp_reshard_module_overrides)
         if ctx.is_main:
             print("FSDP units (automatic plan):\n" + planner.describe(), flush=True)
-        units = planner.apply(mesh)
+        units = planner.apply(mesh, **fsdp_kw)
     else:
         units = []
         for name in FSDPWrapPlan(model, args.fsdp_wrap_patterns):
             units.append(fully_shard(model.get_submodule(name), mesh=mesh,
-                                     reshard_after_forward=FSDPAutoPlanner._reshard_for(_ReshardOnly(args), name)))
-        fully_shard(model, mesh=mesh, reshard_after_forward=args.fsdp_reshard_root)
+                                     reshard_after_forward=FSDPAutoPlanner._reshard_for(_ReshardOnly(args), name), **fsdp_kw))
+        fully_shard(model, mesh=mesh, reshard_after_forward=args.fsdp_reshard_root, **fsdp_kw)
     n = max(int(args.fsdp_prefetch), 0)
     for i, u in enumerate(units):  # ordered forward prefetch of the next `n` units
         nxt = units[i + 1:i + 1 + n]

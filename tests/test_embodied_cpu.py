@@ -117,7 +117,7 @@ def _dist_train(rank, world, strategy, out):
     strategy = "fsdp" if auto else strategy
     a = _args(out, strategy=strategy, train_steps=3,
               fsdp_wrap_patterns=["auto"] if auto else ["backbone.blocks.*", "head.blocks.*"], fsdp_min_num_params=20000,
-              fsdp_reshard_module_overrides={"*expert*": False},
+              fsdp_reshard_module_overrides={"*expert*": False}, fsdp_reduce_dtype="fp32" if auto else None,
               checkpoint_format="dcp" if strategy == "fsdp" else "pt", save_interval=3)
     t = build_trainer(a, ctx)
     m = t.train()
