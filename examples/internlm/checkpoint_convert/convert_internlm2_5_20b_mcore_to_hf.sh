@@ -1,0 +1,9 @@
+#!/bin/bash
+# Training checkpoint of internlm2.5-20b -> Hugging Face safetensors (shards of any TP / PP / EP layout are merged).
+set -euo pipefail
+REPO=$(cd "$(dirname "$0")/../../.." && pwd)
+IN=${1:?path to the training checkpoint}
+OUT=${2:-$REPO/outputs/internlm2_5_20b_hf}
+cd "$REPO"
+python -m tools.convert_checkpoint.convert --load_platform mcore --save_platform huggingface \
+  --model_type_custom internlm2.5 --load_ckpt_path "$IN" --save_ckpt_path "$OUT" --safetensors --torch_dtype bfloat16

@@ -1,0 +1,9 @@
+#!/bin/bash
+# Training checkpoint of qwen2.5-3b -> Hugging Face safetensors (shards of any TP / PP / EP layout are merged).
+set -euo pipefail
+REPO=$(cd "$(dirname "$0")/../../.." && pwd)
+IN=${1:?path to the training checkpoint}
+OUT=${2:-$REPO/outputs/qwen2_5_3b_hf}
+cd "$REPO"
+python -m tools.convert_checkpoint.convert --load_platform mcore --save_platform huggingface \
+  --model_type_custom qwen2.5 --load_ckpt_path "$IN" --save_ckpt_path "$OUT" --safetensors --torch_dtype bfloat16

@@ -22,6 +22,7 @@ def _train_args(text: str):
     body = re.sub(r'"\$\{DATA_ARGS\[@\]\}"', "--mock-data", body)
     defaults = dict(re.findall(r"^([A-Z_]+)=\$\{\1:-([^}$]*)\}", text, re.M))  # VAR=${VAR:-default} lines
     defaults["GPUS"] = "8"
+    _train_args.nnodes = int(defaults.get("NNODES", "1") or 1)
     body = re.sub(r'"?\$\{?([A-Z_]+)(:-[^}]*)?\}?"?', lambda m: defaults.get(m.group(1)) or "/tmp/x", body)
     return [a for a in shlex.split(body.strip().splitlines()[0] if "\n" in body else body) if a]
 
@@ -35,7 +36,32 @@ def test_example_script(path, monkeypatch):
     from loongforge_b200.config.arguments import parse_args
     from loongforge_b200.config.build import build_configs
 
-    monkeypatch.setenv("WORLD_SIZE", "8")
+    world = 8 * _train_args.nnodes                      # multi-node scripts carry NNODES=${NNODES:-n}
+    monkeypatch.setenv("WORLD_SIZE", str(world))
     a, ov = parse_args(args)
     cfg, tc, dims, _ = build_configs(a, ov)
-    assert tc.train_iters > 0 and 8 % (dims.tp * dims.pp * dims.cp) == 0
+    assert tc.train_iters > 0 and world % (dims.tp * dims.pp * dims.cp) == 0
+    stage = world // dims.pp
+    assert stage % (dims.ep * dims.etp) == 0            # the expert mesh tiles the ranks of a pipeline stage
+
+
+def test_launcher_planner_layouts():
+    from loongforge_b200.models.registry import get_model_config
+    from tools.generate_launchers import family_of, generate, plan, presets, stage_layers
+
+    small = plan("llama3-8b")
+    assert (small.tp, small.pp, small.nodes, small.recompute) == (1, 1, 1, "none") and small.est_gb < 126
+    big = plan("llama3.1-405b")
+    assert big.nodes > 1 and big.tp == 8 and big.pp > 1 and big.est_gb <= 126
+    moe = plan("qwen3-235b-a22b")
+    cfg = get_model_config("qwen3-235b-a22b")
+    assert cfg.num_query_groups % moe.tp == 0 and moe.ep >= 8 and (moe.world // moe.pp) % moe.ep == 0
+    assert sum(stage_layers(94, 4)) == 94 and stage_layers(94, 4) == [24, 24, 23, 23] and stage_layers(61, 2) == [31, 30]
+    assert plan("qwen3-8b", "sft").seq_length == 8192
+    assert family_of("qwen3-next-80b-a3b")[0] == "qwen3_next" and family_of("llama3.1-8b")[1] == "llama3"
+    files = generate(write=False)
+    on_disk = {os.path.relpath(p, ROOT) for p in SCRIPTS}
+    assert set(files) <= on_disk, sorted(set(files) - on_disk)[:5]           # the committed scripts are the generator's output
+    for rel in ("examples/qwen3/pretrain/pretrain_qwen3_8b.sh", "examples/llama3/finetuning/sft_llama3_8b_lora.sh"):
+        assert open(os.path.join(ROOT, rel)).read() == files[rel]
+    assert len(presets()) >= 55
