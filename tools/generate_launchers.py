@@ -31,7 +31,8 @@ GPU_GB, BUDGET, GPUS_PER_NODE = 180.0, 0.70, 8
 FAMILY_OF = [
     ("deepseek-v2", ("deepseek_v2", "deepseek", "deepseek")), ("deepseek-v3", ("deepseek_v3", "deepseek", "deepseek")),
     ("deepseek-v4", ("deepseek_v4", None, "deepseek")), ("ernie4.5", ("ernie4.5", None, "chatml")),
-    ("glm5", ("glm5.2", "glm", "chatml")), ("internlm2.5", ("internlm", "internlm2.5", "internlm2")),
+    ("glm5.2", ("glm5.2", "glm", "chatml")), ("glm5", ("glm5", "glm", "chatml")), ("kimi-k2", ("kimi_k2.x", "kimi_k2", "chatml")),
+    ("minicpm-v", ("minicpm_v_4_6", None, "chatml")), ("qwen3.6", ("qwen3.6", "qwen3_5", "chatml")), ("internlm2.5", ("internlm", "internlm2.5", "internlm2")),
     ("llama2", ("llama2", "llama2", "llama2")), ("llama3.1", ("llama3.1", "llama3", "llama3")),
     ("llama3", ("llama3", "llama3", "llama3")), ("mimo", ("mimo", "mimo", "chatml")),
     ("minimax", ("minimax", "minimax", "chatml")), ("qwen-", ("qwen", "qwen2", "chatml")),
@@ -234,9 +235,56 @@ def convert_script(p: Plan, direction: str, family: str) -> str:
             f"  --model_type_custom {fam} --load_ckpt_path \"$IN\" --save_ckpt_path \"$OUT\" --safetensors --torch_dtype bfloat16\n")
 
 
+# VLM name (first line of its YAML) -> (examples directory, language-model preset)
+def vlm_presets() -> Dict[str, Tuple[str, str]]:
+    """Vision-language models registered by the YAML files under configs/models, with the language preset they compose."""
+    import yaml as _yaml
+    from loongforge_b200.config import build as B
+    from loongforge_b200.models.registry import list_models
+    llms = {m.replace("-", "_").replace(".", "_"): m for m in list_models()}
+    dirs = {"qwen2.5vl": "qwen2.5_vl", "qwen3vl": "qwen3_vl", "internvl": "internvl", "llavaov": "llava_onevision_1.5",
+            "ernie4.5vl": "ernie4.5", "kimi_k2": "kimi_k2.x", "glm": "glm5.2_vit", "custom": "custom"}
+    out: Dict[str, Tuple[str, str]] = {}
+    for name, rel in sorted(B._scan_model_yaml().items()):
+        with open(os.path.join(B.CONFIG_DIR, rel)) as f:
+            node = _yaml.safe_load(f.read().replace("${", "$("))     # resolvers are not needed here
+        if not isinstance(node, dict) or "defaults" not in node:
+            continue
+        llm = None
+        for d in node["defaults"]:
+            if isinstance(d, dict):
+                for k, v in d.items():
+                    if k.endswith("@model.foundation"):
+                        llm = llms.get(str(v).replace("_llm", "")) or llms.get(str(v))
+        if llm:
+            out[name] = (dirs.get(rel.split("/")[0], rel.split("/")[0]), llm)
+    return out
+
+
+def vlm_sft_script(name: str, llm: str) -> str:
+    p = plan(llm, "sft", 4096)
+    slug = "sft_" + name.replace("-", "_").replace(".", "_")
+    gbs = max(p.world // (p.tp * p.pp), 1) * 4
+    head = HEADER.format(title=f"{name} supervised fine-tuning on image-text conversations (language model: {llm}); the vision encoder keeps\n"
+                               f"# tensor-parallel size 1 and is spread over the TP ranks by encoder heterogeneous DP", nodes=p.nodes,
+                         label=p.label(), est=p.est_gb, slug=slug)
+    head += ('DATA_PATH=${DATA_PATH:-}        # WebDataset shards written by tools/data_preprocess/vlm_to_webdataset.py\n'
+             'TOKENIZER=${TOKENIZER:-}\nexport PYTORCH_CUDA_ALLOC_CONF=expandable_segments:True\nDATA_ARGS=(--mock-data)\n'
+             '[ -n "$DATA_PATH" ] && DATA_ARGS=(--data-path "$DATA_PATH" --tokenizer-type HFTokenizer --hf-tokenizer-path "$TOKENIZER")\n\ncd "$REPO"\n').replace("\\n", "\n")
+    par = _parallel_flags(p)
+    if p.tp > 1:
+        par[0] += " --encoder-tensor-model-parallel-size 1"
+    body = [f"--model-name {name} --training-phase sft"] + par + [
+        f"--micro-batch-size 1 --global-batch-size {gbs} --seq-length 4096 --packing-sft-data --variable-seq-lengths",
+        "--bf16 --lr 1e-5 --min-lr 1e-6 --lr-decay-style cosine --lr-warmup-fraction 0.03 --weight-decay 0.1 --clip-grad 1.0",
+        "--train-iters 1000 --log-interval 5 --log-throughput", '--save "$CKPT" --save-interval 250 --ckpt-format torch_dist',
+        '"${DATA_ARGS[@]}"', "+model.image_encoder.freeze=True"]
+    return head + _launch(p, body)
+
+
 def presets() -> List[str]:
     from loongforge_b200.models.registry import list_models
-    skip = ("tiny-", "qwen2.5-vit")
+    skip = ("tiny-", "qwen2.5-vit", "minicpm-v-4.6-llm")
     return [m for m in list_models() if not m.startswith(skip) and not m.endswith(("-slice", "-warmup", "-sparse"))]
 
 
@@ -254,6 +302,8 @@ def generate(write: bool) -> Dict[str, str]:
         if conv:
             files[f"examples/{d}/checkpoint_convert/convert_{slug}_hf_to_mcore.sh"] = convert_script(pp, "hf_to_mcore", conv)
             files[f"examples/{d}/checkpoint_convert/convert_{slug}_mcore_to_hf.sh"] = convert_script(pp, "mcore_to_hf", conv)
+    for name, (d, llm) in vlm_presets().items():
+        files[f"examples/{d}/finetuning/sft_{name.replace('-', '_').replace('.', '_')}.sh"] = vlm_sft_script(name, llm)
     if write:
         for rel, text in files.items():
             path = os.path.join(ROOT, rel)
