@@ -200,3 +200,73 @@ def test_vlm_cli_trains_from_image_text_shards(tmp_path):
                        env=dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=root))
     assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
     assert "iteration        3/" in p.stdout and "lm loss" in p.stdout
+
+
+def _vlm_names():
+    from loongforge_b200.config import build as B
+    import os
+    out = []
+    for name, rel in sorted(B._scan_model_yaml().items()):
+        with open(os.path.join(B.CONFIG_DIR, rel)) as f:
+            if "@model.image_encoder" in f.read():
+                out.append(name)
+    return out
+
+
+@pytest.mark.parametrize("name", _vlm_names())
+def test_every_vlm_yaml_builds_and_trains_at_reduced_size(name):
+    """Every vision-language YAML under configs/models: composed, both towers shrunk to two layers of width 64 (all other
+    architecture switches kept: norms, biases, position tables, MLA / MoE / hybrid layers of the language model), then one
+    forward / backward through the composed model."""
+    import dataclasses
+    import os
+    from loongforge_b200.config import build as B
+    from loongforge_b200.config import yaml_compose
+    from loongforge_b200.models.omni import OmniCombinationModel
+
+    os.environ.setdefault("LOONGFORGE_PATH", B.REPO_ROOT)
+    raw = yaml_compose.compose(os.path.join(B.CONFIG_DIR, B._scan_model_yaml()[name]))
+    node = raw["model"]
+    enc = node["image_encoder"]
+    vit = B.transformer_config_from_yaml({k: v for k, v in enc.items() if not isinstance(v, dict) and k != "freeze"})
+    vit = dataclasses.replace(vit, num_layers=2, hidden_size=64, num_attention_heads=4, num_query_groups=4, kv_channels=16,
+                              ffn_hidden_size=128)
+    lm = B.transformer_config_from_yaml({k: v for k, v in node["foundation"].items() if not isinstance(v, dict)})
+    small = dict(num_layers=2, hidden_size=64, num_attention_heads=4, num_query_groups=2, kv_channels=16, ffn_hidden_size=128,
+                 vocab_size=300, make_vocab_size_divisible_by=1, mtp_num_layers=0)
+    if lm.num_moe_experts:
+        small.update(num_moe_experts=4, moe_router_topk=2, moe_ffn_hidden_size=32, moe_layer_freq=[0, 1] if isinstance(lm.moe_layer_freq, list) else 1,
+                     moe_router_num_groups=None, moe_router_group_topk=None)
+        if lm.moe_shared_expert_intermediate_size:
+            small["moe_shared_expert_intermediate_size"] = 32
+    if lm.multi_latent_attention:
+        small.update(q_lora_rank=24, kv_lora_rank=16, qk_head_dim=16, qk_pos_emb_head_dim=8, v_head_dim=16, kv_channels=None)
+        if lm.use_dsa:
+            small.update(dsa_indexer_n_heads=2, dsa_indexer_head_dim=16, dsa_indexer_topk=8, dsa_indexer_topk_freq=1,
+                         dsa_indexer_skip_topk_offset=0)
+    if lm.full_attention_interval:
+        small.update(full_attention_interval=2, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=16,
+                     linear_value_head_dim=16, kv_channels=16)
+    if lm.position_embedding_type == "mrope":
+        full = not lm.rotary_percent or lm.rotary_percent == 1.0
+        small["mrope_section"] = [4, 2, 2] if full else [1, 1, 0]          # sums to (head channels x rotary share) / 2
+        small["rotary_percent"] = 1.0 if full else 0.25
+    lm = dataclasses.replace(lm, **small)
+    family = str(enc.get("model_type", "qwen2_5_vit"))
+    family = family if family in VZ.VISION_FAMILIES else "qwen2_vit"
+    opts = dict(enc.get("vision_options") or {})
+    if "pos_table_side" in opts:
+        opts["pos_table_side"] = 8
+    if "deepstack_indexes" in opts:
+        opts["deepstack_indexes"] = (0, 1)
+    torch.manual_seed(0)
+    m = OmniCombinationModel(lm, vit, image_token_id=299, vision_family=family, vision_options=opts or None)
+    merge = vit.spatial_merge_size
+    n_img_tok = sum(int(t * (h // merge) * (w // merge)) for t, h, w in GRID.tolist())
+    tokens = torch.cat([torch.randint(0, 298, (5,)), torch.full((n_img_tok,), 299), torch.randint(0, 298, (7,))])
+    T = tokens.numel()
+    pos = torch.arange(T) if lm.position_embedding_type != "mrope" else torch.arange(T)[None].expand(3, -1)
+    loss = m(tokens, pos, pixels=_pixels(vit), grid_thw=GRID, labels=torch.roll(tokens, -1), loss_mask=torch.ones(T)).mean()
+    loss.backward()
+    assert torch.isfinite(loss), name
+    assert any(p.grad is not None and p.grad.abs().sum() > 0 for p in m.parameters())
