@@ -29,6 +29,29 @@ class IndexedDatasetWriter:
         self.sizes.append(len(arr))
         self.doc_idx.append(len(self.sizes))
 
+    def add_sentences(self, sentences: Sequence[Sequence[int]]):
+        """One document made of several sequences (sentence-split corpora): every sentence is an item of its own, the
+        document index marks where the document ends."""
+        for sent in sentences:
+            arr = np.asarray(sent, dtype=self.dtype)
+            self._bin.write(arr.tobytes(order="C"))
+            self.sizes.append(len(arr))
+        self.doc_idx.append(len(self.sizes))
+
+    def merge(self, prefix: str):
+        """Appends another data set of the same dtype (partition files of a parallel pre-processing run)."""
+        other = IndexedDataset(prefix)
+        assert other.dtype == self.dtype, f"{prefix}: dtype {other.dtype} != {self.dtype}"
+        base = len(self.sizes)
+        with open(prefix + ".bin", "rb") as f:
+            while True:
+                chunk = f.read(1 << 24)
+                if not chunk:
+                    break
+                self._bin.write(chunk)
+        self.sizes.extend(int(x) for x in other.sizes)
+        self.doc_idx.extend(int(d) + base for d in other.doc_idx[1:])
+
     def finalize(self):
         self._bin.close()
         with open(self.prefix + ".idx", "wb") as f:

@@ -46,6 +46,9 @@ class SFTDataset:
 
     def __getitem__(self, i):
         rec = self.records[i]
+        if "input_ids" in rec:  # tokenised offline (tools/data_preprocess/preprocess_sft_data.py): used as it is
+            ids, labels = list(rec["input_ids"]), list(rec.get("labels") or rec["input_ids"])
+            return ids[:self.max_len], labels[:self.max_len]
         return encode_chat(self.tokenizer, to_messages(rec, self.fmt), self.template, self.train_on_prompt,
                            self.max_len, tools=rec.get("tools"))
 

@@ -175,6 +175,46 @@ class TransformedDataset(Dataset):
         return self.transform(self.base[i])
 
 
+class PrecomputedFeatures(Dataset):
+    """A data set whose samples take ``latents`` / ``text_emb`` / ``text_emb_mask`` / ``image_tokens`` from a cache written by
+    ``tools/data_preprocess/embodied_precompute.py`` (same sample order) instead of carrying the raw video; the policies use
+    these arrays in place of their codec, text encoder and image tower."""
+
+    def __init__(self, base: Dataset, cache_dir: str):
+        with open(os.path.join(cache_dir, "manifest.json")) as f:
+            self.m = json.load(f)
+        if not self.m.get("complete"):
+            raise ValueError(f"{cache_dir}: the feature cache is not complete")
+        if self.m["num_samples"] != len(base):
+            raise ValueError(f"{cache_dir}: cache of {self.m['num_samples']} samples, data set of {len(base)}")
+        self.base, self.dir = base, cache_dir
+        self.firsts = np.array([s["first"] for s in self.m["shards"]])
+        self._open = (None, None)
+
+    @property
+    def raw(self):
+        return getattr(self.base, "raw", False)
+
+    @raw.setter
+    def raw(self, v):
+        self.base.raw = v
+
+    def __len__(self):
+        return len(self.base)
+
+    def __getitem__(self, i):
+        s = int(np.searchsorted(self.firsts, i, side="right") - 1)
+        if self._open[0] != s:
+            with np.load(os.path.join(self.dir, self.m["shards"][s]["file"])) as z:
+                self._open = (s, {k: z[k] for k in z.files})
+        out = dict(self.base[i])
+        out.pop("video", None)
+        j = i - int(self.firsts[s])
+        for k, arr in self._open[1].items():
+            out[k] = arr[j].astype(np.float32) if arr.dtype.kind == "f" else arr[j]
+        return out
+
+
 def _base_dataset(args) -> Dataset:
     if args.dataset_type == "synthetic":
         return SyntheticEpisodes(args)
@@ -190,6 +230,8 @@ def build_dataset(args, training: bool = True) -> Dataset:
     ``stats_path`` or, failing that, computed over the first ``stats_samples`` samples and kept as ``output_dir/stats.json``
     (the file an evaluation server reads to turn predictions back into robot units)."""
     ds = _base_dataset(args)
+    if getattr(args, "precomputed_cache", None):
+        ds = PrecomputedFeatures(ds, args.precomputed_cache)
     if not getattr(args, "use_transforms", False):
         return ds
     from . import transforms as T

@@ -335,10 +335,10 @@ class DreamZeroPolicy(nn.Module):
 
     def forward(self, batch: Dict[str, torch.Tensor], noise=None, t=None):
         c, m, sch = self.c, self.model, self.schedule
-        video = video_from_batch(batch, c.video_frames)
         with torch.no_grad():
+            video = video_from_batch(batch, c.video_frames) if not ("latents" in batch and "image_tokens" in batch) else None
             lat = batch["latents"] if "latents" in batch else self.vae.encode(video)
-            img = self.image_tower(video[:, :, 0])
+            img = batch["image_tokens"] if "image_tokens" in batch else self.image_tower(video[:, :, 0])
         B, _, Fr, _, _ = lat.shape
         nfb = c.num_frame_per_block
         assert (Fr - 1) % nfb == 0, "latent frames after the observation must fill whole blocks"

@@ -65,14 +65,14 @@ def test_sft_pretokenise_then_offline_packing(tmp_path):
     recs = [{"instruction": "say " + "x" * n, "output": "ok"} for n in (5, 50, 500, 20, 200, 3000)]
     src = tmp_path / "sft.jsonl"
     src.write_text("\n".join(json.dumps(r) for r in recs))
-    kept, dropped = preprocess_sft_data.main(["--input", str(src), "--output-prefix", str(tmp_path / "tok"),
-                                              "--max-length", "1000", "--shard-size", "3"])
+    kept, dropped = preprocess_sft_data.main(["--input", str(src), "--output-path", str(tmp_path / "tok"),
+                                              "--seq-length", "1000", "--shard-size", "3", "--enable-discard-sample"])
     assert (kept, dropped) == (5, 1)
-    idx = json.load(open(tmp_path / "tok_index.json"))
-    assert idx["shards"] == 2 and len(idx["lengths"]) == 5
-    first = json.loads(open(tmp_path / "tok_00000.jsonl").readline())
+    idx = json.load(open(tmp_path / "tok" / "index.json"))["splits"]["train"]
+    assert len(idx["shards"]) == 2 and len(idx["lengths"]) == 5
+    first = json.loads(open(tmp_path / "tok" / "train_00000.jsonl").readline())
     assert len(first["input_ids"]) == len(first["labels"]) and -100 in first["labels"]
-    packs = offline_packing.main(["--index", str(tmp_path / "tok_index.json"), "--seq-length", "1000", "--output",
+    packs = offline_packing.main(["--index", str(tmp_path / "tok" / "index.json"), "--seq-length", "1000", "--output",
                                   str(tmp_path / "packs.json")])
     flat = sorted(i for p in packs for i in p)
     assert flat == [0, 1, 2, 3, 4]
@@ -208,3 +208,75 @@ def test_vlm_offline_packing_pipeline_and_loader(tmp_path):
     rows = list(vlm_batch_iterator(webdataset_samples(str(tmp_path / "dst"), epochs=1), enc, 512))
     assert len(rows) == idx["packs"] and all(b["tokens"].shape == (1, 512) for b in rows)
     assert sum(b["grid_thw"].shape[0] for b in rows) == 12
+
+
+def test_pretrain_preprocessing_partitions_sentences_and_resume(tmp_path):
+    """Partitioned runs merge to the same data set as one pass (round-robin and sequential dealing); sentence splitting
+    keeps document boundaries; gzip input and globs; a finished partition is not redone."""
+    import gzip
+    import json as js
+    import numpy as np
+    from loongforge_b200.data.indexed_dataset import IndexedDataset
+    from tools.data_preprocess import preprocess_pretrain_data as pp
+
+    docs = [{"text": f"Document {i} starts here. It has a second sentence! And a third one?\nNew line {i}.", "title": f"t{i}"}
+            for i in range(11)]
+    (tmp_path / "a.jsonl").write_text("\n".join(js.dumps(d) for d in docs[:6]) + "\n")
+    with gzip.open(tmp_path / "b.jsonl.gz", "wt") as f:
+        f.write("\n".join(js.dumps(d) for d in docs[6:]) + "\n")
+    glob_in = str(tmp_path / "*.jsonl*")
+    pp.main(["--input", glob_in, "--output-prefix", str(tmp_path / "one" / "c"), "--append-eod", "--json-keys", "text", "title"])
+    one = IndexedDataset(str(tmp_path / "one" / "c_text_document"))
+    assert len(one) == 11 and len(IndexedDataset(str(tmp_path / "one" / "c_title_document"))) == 11
+    pp.main(["--input", glob_in, "--output-prefix", str(tmp_path / "seq" / "c"), "--append-eod", "--partitions", "3",
+             "--keep-sequential-samples", "--workers", "2"])
+    seq = IndexedDataset(str(tmp_path / "seq" / "c_text_document"))
+    assert len(seq) == 11 and all(np.array_equal(seq[i], one[i]) for i in range(11))          # contiguous ranges: same order
+    assert list(seq.doc_idx) == list(range(12)) and not any("part" in f for f in os.listdir(tmp_path / "seq"))
+    pp.main(["--input", glob_in, "--output-prefix", str(tmp_path / "rr" / "c"), "--append-eod", "--partitions", "3"])
+    rr = IndexedDataset(str(tmp_path / "rr" / "c_text_document"))
+    assert sorted(bytes(rr[i]) for i in range(11)) == sorted(bytes(one[i]) for i in range(11))  # round-robin: same documents
+    pp.main(["--input", glob_in, "--output-prefix", str(tmp_path / "sent" / "c"), "--append-eod", "--split-sentences", "--keep-newlines"])
+    sent = IndexedDataset(str(tmp_path / "sent" / "c_text_sentence"))
+    assert len(sent) == 44 and list(sent.doc_idx) == list(range(0, 45, 4))                     # four sentences per document
+    assert sent[3][-1] == 257 and sent[2][-1] != 257                                          # end-of-document on the last one
+    assert sent.num_tokens == one.num_tokens - 11 * 3            # separators (3 per document) are not tokens of any sentence
+    assert pp.split_sentences("A b. C d! E\nF", keep_newlines=False) == ["A b.", "C d!", "E F"]
+
+
+def test_sft_preprocessing_masks_splits_packing_and_trainer_reads_shards(tmp_path):
+    from loongforge_b200.data.sft import SFTDataset
+    from loongforge_b200.tokenizer.tokenizer import build_tokenizer
+    from tools.data_preprocess import preprocess_sft_data as P
+
+    assert P.mask_history([-100, 5, 6, -100, -100, 7, 8, -100]) == [-100, -100, -100, -100, -100, 7, 8, -100]
+    assert P.mask_run_ends([-100, 5, 6, -100, 7]) == [-100, 5, -100, -100, -100]
+    recs = [{"messages": [{"role": "user", "content": f"q{i} " + "a" * (7 * i)}, {"role": "assistant", "content": "first"},
+                          {"role": "user", "content": "again"}, {"role": "assistant", "content": "second answer"}]} for i in range(20)]
+    src = tmp_path / "chat.jsonl"
+    src.write_text("\n".join(json.dumps(r) for r in recs))
+    out = tmp_path / "o"
+    P.main(["--input", str(src), "--output-path", str(out), "--seq-length", "4096", "--split", "80,10,10", "--history-mask-loss",
+            "--context-parallel-size", "2", "--sft-sort-batch", "--workers", "2"])
+    idx = json.load(open(out / "index.json"))
+    assert {k: v["num_samples"] for k, v in idx["splits"].items()} == {"train": 16, "valid": 2, "test": 2}
+    rows = [json.loads(l) for l in open(out / "train_00000.jsonl")]
+    lens = [len(r["input_ids"]) for r in rows]
+    assert lens == sorted(lens) and all(n % 4 == 0 for n in lens)                  # sorted, padded to 2 x cp
+    tok = build_tokenizer("ByteTokenizer")
+    tgt = bytes(t for t in rows[0]["labels"] if t != -100 and t < 256).decode()
+    assert "second answer" in tgt and "first" not in tgt                             # only the last turn is trained
+    plain = tmp_path / "p"
+    P.main(["--input", str(src), "--output-path", str(plain), "--seq-length", "4096"])
+    both = bytes(t for t in json.loads(open(plain / "train_00000.jsonl").readline())["labels"] if t != -100 and t < 256).decode()
+    assert "first" in both and "second answer" in both
+    packed = tmp_path / "k"
+    P.main(["--input", str(src), "--output-path", str(packed), "--seq-length", "600", "--packing-sft-data", "--packing-buffer-size", "4"])
+    prow = [json.loads(l) for l in open(packed / "train_00000.jsonl")]
+    assert len(prow) < 20 and all(len(r["input_ids"]) <= 600 and sum(r["seq_lens"]) == len(r["input_ids"]) for r in prow)
+    assert sum(len(r["seq_lens"]) for r in prow) == 20
+    # the trainer's data set takes the shard as it is
+    ds = SFTDataset([str(plain / "train_00000.jsonl")], tok, max_len=4096)
+    ids, labels = ds[3]
+    ref = json.loads(open(plain / "train_00000.jsonl").readlines()[3])
+    assert ids == ref["input_ids"] and labels == ref["labels"]

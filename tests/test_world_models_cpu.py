@@ -230,3 +230,51 @@ def test_world_model_policies_train_on_future_frames(name, extra, tmp_path):
     act = p.predict_action(batch, steps=2)
     assert act.shape == (2, a.action_horizon, a.action_dim) and torch.isfinite(act).all()
     assert p.policy.last_losses
+
+
+@pytest.mark.parametrize("name", ["dreamzero", "lingbot_va"])
+def test_precomputed_feature_cache_matches_online_encoding(name, tmp_path):
+    """Build -> validate -> train from the cache: the loss equals the loss with the codec / encoders in the loop; a stale
+    or damaged cache is reported."""
+    import json
+    import os
+    import numpy as np
+    from loongforge_b200.embodied.data import PrecomputedFeatures, SyntheticEpisodes, build_dataset, collate
+    from loongforge_b200.embodied.models import build_policy
+    from tools.data_preprocess import embodied_precompute as E
+
+    a = validate(EmbodiedArgs(model_name=name, model_overrides={"size": "tiny"}, image_size=32, action_horizon=4,
+                              video_frames=9 if name == "dreamzero" else 5, output_dir=str(tmp_path / "run")))
+    torch.manual_seed(a.seed)
+    policy = build_policy(name, a)
+    small = SyntheticEpisodes(a, num_episodes=1, episode_len=10)
+    cache = str(tmp_path / "cache")
+    m = E.build(a, cache, shard_size=4, batch_size=3, dtype="float32", policy=policy, dataset=small)
+    assert m["complete"] and [s["count"] for s in m["shards"]] == [4, 4, 2] and "latents" in m["arrays"] and "text_emb" in m["arrays"]
+    assert ("image_tokens" in m["arrays"]) == (name == "dreamzero")
+    assert E.validate(cache, deep=True, expected_fingerprint=E.fingerprint(policy, a)) == []
+    ds = PrecomputedFeatures(small, cache)
+    assert "video" not in ds[5] and ds[5]["latents"].shape == tuple(m["arrays"]["latents"]["shape"])
+    batch_cached, batch_raw = collate([ds[i] for i in (3, 4)]), collate([small[i] for i in (3, 4)])
+    torch.manual_seed(11)
+    l_cached = policy(batch_cached)
+    torch.manual_seed(11)
+    l_raw = policy(batch_raw)
+    assert abs(float(l_cached) - float(l_raw)) < 1e-5 * max(1.0, abs(float(l_raw)))
+    # resume: a build over the finished cache does nothing and keeps the manifest
+    before = os.path.getmtime(os.path.join(cache, "features_00001.npz"))
+    E.build(a, cache, shard_size=4, batch_size=3, dtype="float32", policy=policy, dataset=small)
+    assert os.path.getmtime(os.path.join(cache, "features_00001.npz")) == before
+    # other frozen weights -> another fingerprint; a missing shard and a wrong shape are found
+    with torch.no_grad():
+        next(policy.policy.vae.parameters()).add_(1.0)
+    assert any("fingerprint" in p for p in E.validate(cache, expected_fingerprint=E.fingerprint(policy, a)))
+    os.remove(os.path.join(cache, "features_00002.npz"))
+    assert any("features_00002.npz is missing" in p for p in E.validate(cache))
+    with np.load(os.path.join(cache, "features_00000.npz")) as z:
+        arrays = {k: z[k] for k in z.files}
+    arrays["latents"] = arrays["latents"][:, :, :1]
+    np.savez(os.path.join(cache, "features_00000.npz"), **arrays)
+    assert any("latents has shape" in p for p in E.validate(cache))
+    with pytest.raises(ValueError):
+        PrecomputedFeatures(SyntheticEpisodes(a, num_episodes=2, episode_len=10), cache)

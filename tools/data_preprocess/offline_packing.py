@@ -2,7 +2,7 @@
 in memory needs only the length index; each bucket is filled first-fit from the longest bucket down (reference:
 tools/data_preprocess offline packing, hash-bucket variant).
 
-Input: the ``*_index.json`` written by ``preprocess_sft_data.py`` (or any JSON with a ``lengths`` list).
+Input: the ``index.json`` written by ``preprocess_sft_data.py`` (``--split`` picks the split) or any JSON with a ``lengths`` list.
 Output: ``packs.json`` — a list of packs, each a list of sample ids whose lengths sum to at most ``--seq-length``."""
 from __future__ import annotations
 
@@ -54,9 +54,11 @@ def main(argv=None):
     ap.add_argument("--seq-length", type=int, required=True)
     ap.add_argument("--bucket-width", type=int, default=64)
     ap.add_argument("--output", required=True)
+    ap.add_argument("--split", default="train", help="split of an index written by preprocess_sft_data.py")
     args = ap.parse_args(argv)
     with open(args.index) as f:
-        lengths = json.load(f)["lengths"]
+        node = json.load(f)
+    lengths = node["lengths"] if "lengths" in node else node["splits"][args.split]["lengths"]
     packs = pack_with_buckets(lengths, args.seq_length, args.bucket_width)
     used = sum(lengths[i] for p in packs for i in p)
     with open(args.output, "w") as f:
