@@ -164,7 +164,6 @@ _ACCEPTED = {
     "use_flash_attn": "attention always runs on the in-tree flash kernel on GPUs",
     "cuda_graph_scope": "graph capture is offered by runtime.cuda_graphs for callables, not selected by scope",
     "tokenizer_model": "tokenizers load from --hf-tokenizer-path",
-    "sft_dataset_config": "dataset options are given as flags",
     "sft_data_streaming": "SFT datasets are read eagerly",
     "dataloader_type": "one cyclic, resumable sampler is used",
     "num_workers": "batches are assembled in the training process",

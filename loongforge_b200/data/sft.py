@@ -25,10 +25,15 @@ def load_records(path: str) -> List[dict]:
 class SFTDataset:
     def __init__(self, paths: Sequence[str], tokenizer, template: str = "chatml", max_len: int = 2048,
                  weights: Optional[Sequence[float]] = None, fmt: str = "auto", train_on_prompt: bool = False,
-                 seed: int = 1234):
+                 seed: int = 1234, formats: Optional[Sequence] = None):
+        """``formats``: one ``sft_formats.DatasetFormat`` per path (named layouts of ``--sft-dataset``); without it the
+        layout is guessed from the record's keys (``fmt``)."""
         self.tokenizer, self.template, self.max_len = tokenizer, template, max_len
         self.train_on_prompt, self.fmt = train_on_prompt, fmt
         sets = [load_records(p) for p in paths]
+        if formats is not None:
+            assert len(formats) == len(sets)
+            sets = [[dict(r, __format__=f) for r in s] for s, f in zip(sets, formats)]
         if weights is None:
             self.records = [r for s in sets for r in s]
         else:  # blend: sample each source proportionally to its weight
@@ -49,6 +54,10 @@ class SFTDataset:
         if "input_ids" in rec:  # tokenised offline (tools/data_preprocess/preprocess_sft_data.py): used as it is
             ids, labels = list(rec["input_ids"]), list(rec.get("labels") or rec["input_ids"])
             return ids[:self.max_len], labels[:self.max_len]
+        if "__format__" in rec:
+            from .sft_formats import convert
+            msgs, tools, _ = convert(rec, rec["__format__"])
+            return encode_chat(self.tokenizer, msgs, self.template, self.train_on_prompt, self.max_len, tools=tools)
         return encode_chat(self.tokenizer, to_messages(rec, self.fmt), self.template, self.train_on_prompt,
                            self.max_len, tools=rec.get("tools"))
 

@@ -12,6 +12,22 @@ from ..tokenizer.tokenizer import build_tokenizer
 from .trainer import Trainer
 
 
+def sft_paths_and_formats(args):
+    """``--sft-dataset`` holds either data files (then the layout is read off the records) or, as in the reference's
+    launchers, NAMES of layouts defined in ``--sft-dataset-config`` that describe the files of ``--train-data-path`` /
+    ``--data-path``."""
+    import os
+    entries = list(args.sft_dataset)
+    if all(os.path.exists(e) for e in entries):
+        return entries, None
+    paths = list(getattr(args, "train_data_path", None) or getattr(args, "data_path", None) or [])
+    if not paths:
+        raise ValueError(f"--sft-dataset {entries}: not files, and no --data-path / --train-data-path names the files they describe")
+    from ..data.sft_formats import resolve_formats
+    names = list(getattr(args, "sft_train_dataset", None) or entries)
+    return paths, resolve_formats(names, len(paths), getattr(args, "sft_dataset_config", None))
+
+
 class SFTTrainer(Trainer):
     def __init__(self, model_cfg, train_cfg, dims=None, *, lora: Optional[dict] = None, **kw):
         self._lora = lora
@@ -28,8 +44,9 @@ class SFTTrainer(Trainer):
         if getattr(args, "mock_data", False) or not getattr(args, "sft_dataset", None):
             return None
         tok = build_tokenizer(args.tokenizer_type, args.hf_tokenizer_path, use_fast=args.use_fast_tokenizer)
-        ds = SFTDataset(args.sft_dataset, tok, template=args.chat_template or "chatml", max_len=self.tcfg.seq_length,
-                        train_on_prompt=args.train_on_prompt, seed=self.tcfg.seed)
+        paths, formats = sft_paths_and_formats(args)
+        ds = SFTDataset(paths, tok, template=args.chat_template or "chatml", max_len=self.tcfg.seq_length,
+                        train_on_prompt=args.train_on_prompt, seed=self.tcfg.seed, formats=formats)
         return sft_batch_iterator(ds, self.tcfg.seq_length, packing=args.packing_sft_data, dp_rank=self.st.dp_rank,
                                   dp_size=self.st.dp_size, seed=self.tcfg.seed, pad_id=tok.pad,
                                   start_sample=self.consumed_samples // max(self.st.dp_size, 1),

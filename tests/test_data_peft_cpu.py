@@ -214,3 +214,49 @@ def test_vlm_lora_per_component():
             apply_vlm_lora(build(), rank=2, apply_to_image_encoder=True, frozen=("image_encoder",))
     finally:
         ps.destroy_model_parallel()
+
+
+def test_named_sft_dataset_layouts(tmp_path):
+    """--sft-dataset as layout names (the reference's launchers): columns and tags of configs/data/sft_dataset_config.yaml
+    map alpaca records with history, renamed sharegpt keys, openai tools and function calls to chat messages."""
+    import json
+    from types import SimpleNamespace as NS
+    from loongforge_b200.data import sft_formats as F
+    from loongforge_b200.data.sft import SFTDataset
+    from loongforge_b200.runtime.sft import sft_paths_and_formats
+    from loongforge_b200.tokenizer.tokenizer import build_tokenizer
+
+    table = F.load_dataset_config()
+    assert {"default", "alpaca", "extended_alpaca", "sharegpt", "openai", "multimodal", "multimodal_sharegpt"} <= set(table)
+    m, tools, _ = F.convert({"instruction": "Add", "input": "1 2", "output": "3", "system": "calc", "history": [["hi", "hello"]]},
+                            table["extended_alpaca"])
+    assert [x["role"] for x in m] == ["system", "user", "assistant", "user", "assistant"] and m[3]["content"] == "Add\n1 2"
+    m, _, imgs = F.convert({"messages": [{"from": "human", "value": "<image> what"}, {"from": "gpt", "value": "a cat"}], "images": ["a.jpg"]},
+                           table["multimodal_sharegpt"])
+    assert [x["role"] for x in m] == ["user", "assistant"] and imgs == ["a.jpg"]
+    rec = {"conversations": [{"from": "human", "value": "weather?"}, {"from": "function_call", "value": json.dumps({"name": "get", "arguments": {"c": "x"}})},
+                             {"from": "observation", "value": "sunny"}, {"from": "gpt", "value": "It is sunny."}],
+           "tools": json.dumps([{"name": "get"}]), "system": "be brief"}
+    m, tools, _ = F.convert(rec, table["sharegpt_conversations"])
+    assert [x["role"] for x in m] == ["system", "user", "assistant", "tool", "assistant"]
+    assert m[2]["tool_calls"][0]["function"]["name"] == "get" and tools == [{"name": "get"}]
+    with pytest.raises(ValueError):
+        F.convert({"messages": [{"role": "narrator", "content": "x"}]}, table["openai"])
+    with pytest.raises(KeyError):
+        F.resolve_formats(["nope"], 1)
+    a, b = tmp_path / "a.jsonl", tmp_path / "b.jsonl"
+    a.write_text(json.dumps({"instruction": "say hi", "input": "", "output": "hi"}) + "\n")
+    b.write_text(json.dumps({"messages": [{"role": "user", "content": "q"}, {"role": "assistant", "content": "ans"}]}) + "\n")
+    args = NS(sft_dataset=["alpaca", "openai"], data_path=[str(a), str(b)], train_data_path=None, sft_train_dataset=None, sft_dataset_config=None)
+    paths, fmts = sft_paths_and_formats(args)
+    assert paths == [str(a), str(b)] and [f.name for f in fmts] == ["alpaca", "openai"]
+    ds = SFTDataset(paths, build_tokenizer("ByteTokenizer"), formats=fmts)
+    texts = [bytes(t for t in ds[i][1] if t != -100 and t < 256).decode() for i in range(2)]
+    assert any("hi" in t for t in texts) and any("ans" in t for t in texts)
+    assert sft_paths_and_formats(NS(sft_dataset=[str(a)], data_path=None, train_data_path=None))[1] is None   # files as before
+    with pytest.raises(ValueError):
+        sft_paths_and_formats(NS(sft_dataset=["alpaca"], data_path=None, train_data_path=None, sft_train_dataset=None, sft_dataset_config=None))
+    custom = tmp_path / "cfg.yaml"
+    custom.write_text("mine:\n  format: alpaca\n  columns: {prompt: q, response: a}\n")
+    m, _, _ = F.convert({"q": "Q?", "a": "A."}, F.load_dataset_config(str(custom))["mine"])
+    assert m[0]["content"] == "Q?" and m[1]["content"] == "A."
