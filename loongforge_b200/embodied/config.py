@@ -33,6 +33,8 @@ class EmbodiedArgs:
     relative_action_mask: List[bool] = dataclasses.field(default_factory=list)  # channels trained as offsets from the state
     embodiment_tags: Dict[str, int] = dataclasses.field(default_factory=dict)   # tag / domain name -> id
     robot_description: Optional[str] = None
+    dataset_mixture: List[Dict[str, Any]] = dataclasses.field(default_factory=list)  # [{type, path, weight}]: several data sets in fixed proportions
+    mixture_epoch_length: Optional[int] = None
     precomputed_cache: Optional[str] = None  # features written by tools/data_preprocess/embodied_precompute.py
     video_frames: int = 0  # world-model policies: future frames per sample (1 + 4k; 0 = none), camera 0, one per `video_frame_stride` steps
     video_frame_stride: int = 1

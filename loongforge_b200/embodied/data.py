@@ -116,12 +116,26 @@ class NpzEpisodes(Dataset):
 
 
 class LeRobotParquet(Dataset):
+    """LeRobot v2 layout:
+
+    * ``meta/info.json``      fps, robot type, ``data_path`` / ``video_path`` templates, ``features`` (which keys are videos);
+    * ``meta/tasks.jsonl``    task index -> instruction; ``meta/episodes.jsonl`` episode lengths; ``meta/stats.json`` statistics;
+    * ``data/chunk-XXX/episode_XXXXXX.parquet``  one row per step: ``observation.state``, ``action``, ``task_index``, ...
+      (image columns holding encoded bytes are decoded when present);
+    * ``videos/chunk-XXX/<camera key>/episode_XXXXXX.mp4``  one video per camera and episode, decoded by frame index with
+      OpenCV (a few captures stay open per worker).
+
+    ``cameras`` picks / orders the camera keys (default: the first ``num_cameras`` video features); ``episodes`` restricts
+    the episode indices; without videos and image columns the images are zeros (state-only data sets)."""
+
     raw = False
 
-    def __init__(self, args, path: str):
+    def __init__(self, args, path: str, cameras: Optional[List[str]] = None, episodes: Optional[List[int]] = None):
         import pyarrow.parquet as pq
 
-        self.a = args
+        self.a, self.root = args, path
+        info_p = os.path.join(path, "meta", "info.json")
+        self.info = json.load(open(info_p)) if os.path.isfile(info_p) else {}
         files = sorted(glob.glob(os.path.join(path, "data", "chunk-*", "episode_*.parquet")))
         if not files:
             raise FileNotFoundError(f"no LeRobot parquet episodes under {path}")
@@ -130,31 +144,90 @@ class LeRobotParquet(Dataset):
         if os.path.isfile(tp):
             with open(tp) as f:
                 for line in f:
-                    r = json.loads(line)
-                    self.tasks[int(r["task_index"])] = r["task"]
-        self.episodes = []
-        self.index = []
+                    if line.strip():
+                        r = json.loads(line)
+                        self.tasks[int(r["task_index"])] = r["task"]
+        feats = self.info.get("features", {})
+        video_keys = [k for k, v in feats.items() if v.get("dtype") == "video"]
+        image_keys = [k for k, v in feats.items() if v.get("dtype") == "image"]
+        self.cameras = list(cameras or (video_keys + image_keys))[:args.num_cameras]
+        self.video_keys = set(video_keys)
+        self.robot = self.info.get("robot_type")
+        self.episodes, self.index = [], []
         for f in files:
+            ep_idx = int(os.path.basename(f).split("_")[1].split(".")[0])
+            if episodes is not None and ep_idx not in episodes:
+                continue
             t = pq.read_table(f).to_pydict()
-            ep = {"state": np.asarray(t["observation.state"], dtype=np.float32),
+            ep = {"index": ep_idx, "chunk": os.path.basename(os.path.dirname(f)),
+                  "state": np.asarray(t["observation.state"], dtype=np.float32),
                   "actions": np.asarray(t["action"], dtype=np.float32),
-                  "task": self.tasks.get(int(t["task_index"][0]), "") if "task_index" in t else ""}
+                  "task": self.tasks.get(int(t["task_index"][0]), "") if "task_index" in t else "",
+                  "frames": {k: t[k] for k in self.cameras if k in t and k not in self.video_keys}}
             self.index += [(len(self.episodes), i) for i in range(ep["actions"].shape[0])]
             self.episodes.append(ep)
+        self._caps: Dict[str, object] = {}
 
     def __len__(self):
         return len(self.index)
+
+    def stats(self) -> Optional[dict]:
+        p = os.path.join(self.root, "meta", "stats.json")
+        return json.load(open(p)) if os.path.isfile(p) else None
+
+    def _video_file(self, ep: dict, key: str) -> str:
+        tpl = self.info.get("video_path", "videos/{episode_chunk_dir}/{video_key}/episode_{episode_index:06d}.mp4")
+        rel = tpl.format(episode_chunk=int(ep["chunk"].split("-")[1]), episode_chunk_dir=ep["chunk"], video_key=key,
+                         episode_index=ep["index"])
+        return os.path.join(self.root, rel)
+
+    def _frame(self, ep: dict, key: str, t: int) -> np.ndarray:
+        """``[3, H, W]`` in [0, 1] at the model's image size (nearest resize; the transforms resize properly when used)."""
+        S = self.a.image_size
+        img = None
+        if key in ep["frames"]:
+            cell = ep["frames"][key][t]
+            data = cell.get("bytes") if isinstance(cell, dict) else cell
+            import cv2
+            img = cv2.imdecode(np.frombuffer(data, np.uint8), cv2.IMREAD_COLOR)[:, :, ::-1]
+        elif key in self.video_keys:
+            import cv2
+            f = self._video_file(ep, key)
+            cap = self._caps.get(f)
+            if cap is None and os.path.isfile(f):
+                if len(self._caps) >= 8:
+                    self._caps.pop(next(iter(self._caps))).release()
+                cap = self._caps[f] = cv2.VideoCapture(f)
+            if cap is not None:
+                cap.set(cv2.CAP_PROP_POS_FRAMES, t)
+                ok, fr = cap.read()
+                img = fr[:, :, ::-1] if ok else None
+        if img is None:
+            return np.zeros((3, S, S), dtype=np.float32)
+        ys = (np.arange(S) * img.shape[0] / S).astype(int)
+        xs = (np.arange(S) * img.shape[1] / S).astype(int)
+        return np.ascontiguousarray(img[ys][:, xs].transpose(2, 0, 1)).astype(np.float32) / 255.0
 
     def __getitem__(self, i):
         e, t = self.index[i]
         ep, a = self.episodes[e], self.a
         chunk, mask = _chunk(ep["actions"], t, a.action_horizon)
-        img = np.zeros((a.num_cameras, 3, a.image_size, a.image_size), dtype=np.float32)  # videos are decoded offline
-        out = {"images": img, "state": ep["state"][t], "actions": chunk, "action_mask": mask,
+        cams = [self._frame(ep, k, t) for k in self.cameras]
+        while len(cams) < a.num_cameras:
+            cams.append(np.zeros((3, a.image_size, a.image_size), dtype=np.float32))
+        out = {"images": np.stack(cams), "state": ep["state"][t], "actions": chunk, "action_mask": mask,
                "text": hash_tokenize(ep["task"], a.max_text_len)}
+        if getattr(a, "video_frames", 0) and self.cameras:
+            out["video"] = _future_frames(lambda k: self._frame(ep, self.cameras[0], k), t, ep["actions"].shape[0], a.video_frames,
+                                          a.video_frame_stride)
         if self.raw:
             out["task"] = ep["task"]
+            if self.robot:
+                out["embodiment_tag"] = out["domain"] = str(self.robot)
         return out
+
+
+LeRobotDataset = LeRobotParquet
 
 
 def collate(samples: List[dict]) -> Dict[str, torch.Tensor]:
@@ -215,7 +288,55 @@ class PrecomputedFeatures(Dataset):
         return out
 
 
+class MixtureDataset(Dataset):
+    """Several data sets (other robots, other tasks) sampled in fixed proportions: an epoch has ``length`` samples, sample
+    i comes from data set ``schedule[i]`` (drawn once from the weights with the seed), walking each data set in its own order
+    and wrapping around the small ones. Every sample carries ``dataset_id``."""
+
+    def __init__(self, datasets: List[Dataset], weights: Optional[List[float]] = None, seed: int = 0, length: Optional[int] = None):
+        assert datasets
+        self.sets = datasets
+        w = np.asarray(weights or [len(d) for d in datasets], dtype=np.float64)
+        self.weights = w / w.sum()
+        self.n = int(length or sum(len(d) for d in datasets))
+        rng = np.random.default_rng(seed)
+        self.schedule = rng.choice(len(datasets), size=self.n, p=self.weights)
+        self.local = np.zeros(self.n, dtype=np.int64)
+        for k in range(len(datasets)):
+            pos = np.nonzero(self.schedule == k)[0]
+            self.local[pos] = np.arange(len(pos)) % max(len(datasets[k]), 1)
+
+    @property
+    def raw(self):
+        return all(getattr(d, "raw", False) for d in self.sets)
+
+    @raw.setter
+    def raw(self, v):
+        for d in self.sets:
+            d.raw = v
+
+    def __len__(self):
+        return self.n
+
+    def __getitem__(self, i):
+        k = int(self.schedule[i])
+        out = dict(self.sets[k][int(self.local[i])])
+        out["dataset_id"] = np.int64(k)
+        return out
+
+
 def _base_dataset(args) -> Dataset:
+    mix = getattr(args, "dataset_mixture", None)
+    if mix:
+        import copy
+        sets, weights = [], []
+        for entry in mix:
+            sub = copy.copy(args)
+            sub.dataset_mixture = None
+            sub.dataset_type, sub.dataset_path = entry.get("type", args.dataset_type), entry.get("path")
+            sets.append(_base_dataset(sub))
+            weights.append(float(entry.get("weight", len(sets[-1]))))
+        return MixtureDataset(sets, weights, seed=args.seed, length=getattr(args, "mixture_epoch_length", None))
     if args.dataset_type == "synthetic":
         return SyntheticEpisodes(args)
     if args.dataset_type in ("npz_episodes", "hdf5"):

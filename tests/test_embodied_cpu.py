@@ -724,3 +724,85 @@ def _save_partial(tmp_path, sd):
     p = str(tmp_path / "partial.pt")
     torch.save({k: v for i, (k, v) in enumerate(sd.items()) if i % 2 == 0}, p)
     return p
+
+
+def _write_lerobot(root, episodes=2, steps=6, size=(24, 32)):
+    """A tiny LeRobot v2 data set: parquet episodes, one mp4 per camera and episode, meta files."""
+    import cv2
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+
+    os.makedirs(root / "meta", exist_ok=True)
+    feats = {"observation.images.front": {"dtype": "video"}, "observation.images.wrist": {"dtype": "video"},
+             "observation.state": {"dtype": "float32", "shape": [4]}, "action": {"dtype": "float32", "shape": [3]}}
+    (root / "meta" / "info.json").write_text(json.dumps({"fps": 10, "robot_type": "toy_arm", "features": feats,
+                                                        "video_path": "videos/{episode_chunk_dir}/{video_key}/episode_{episode_index:06d}.mp4"}))
+    (root / "meta" / "tasks.jsonl").write_text(json.dumps({"task_index": 0, "task": "stack the blocks"}) + "\n")
+    (root / "meta" / "stats.json").write_text(json.dumps({"observation.state": {"mean": [0] * 4, "std": [1] * 4, "min": [-1] * 4, "max": [1] * 4,
+                                                                                  "q01": [-1] * 4, "q99": [1] * 4},
+                                                          "action": {"mean": [0] * 3, "std": [1] * 3, "min": [-1] * 3, "max": [1] * 3,
+                                                                     "q01": [-1] * 3, "q99": [1] * 3}}))
+    for e in range(episodes):
+        d = root / "data" / "chunk-000"
+        os.makedirs(d, exist_ok=True)
+        pq.write_table(pa.table({"observation.state": [[float(e), float(t), 0.0, 1.0] for t in range(steps)],
+                                 "action": [[0.1 * t, 0.0, float(e)] for t in range(steps)],
+                                 "task_index": [0] * steps, "episode_index": [e] * steps}), d / f"episode_{e:06d}.parquet")
+        for cam, base in (("observation.images.front", 40), ("observation.images.wrist", 160)):
+            vd = root / "videos" / "chunk-000" / cam
+            os.makedirs(vd, exist_ok=True)
+            w = cv2.VideoWriter(str(vd / f"episode_{e:06d}.mp4"), cv2.VideoWriter_fourcc(*"mp4v"), 10, (size[1], size[0]))
+            for t in range(steps):
+                w.write(np.full((size[0], size[1], 3), base + 10 * t, np.uint8))
+            w.release()
+
+
+def test_lerobot_v2_dataset_reads_videos_and_meta(tmp_path):
+    from loongforge_b200.embodied.data import LeRobotDataset, build_dataset, collate
+
+    root = tmp_path / "ds"
+    _write_lerobot(root)
+    a = _args(tmp_path / "o", dataset_type="lerobot", dataset_path=str(root), num_cameras=2, image_size=16, action_dim=3, state_dim=4,
+              action_horizon=3, video_frames=5, video_frame_stride=1)
+    ds = build_dataset(a)
+    assert isinstance(ds, LeRobotDataset) and len(ds) == 12 and ds.cameras == ["observation.images.front", "observation.images.wrist"]
+    s = ds[8]                                                     # episode 1, step 2
+    assert s["images"].shape == (2, 3, 16, 16) and s["state"].tolist() == [1.0, 2.0, 0.0, 1.0]
+    front, wrist = s["images"][0].mean() * 255, s["images"][1].mean() * 255
+    assert abs(front - 60) < 6 and abs(wrist - 180) < 6            # frame 2 of each camera (lossy codec)
+    assert s["actions"].shape == (3, 3) and abs(s["actions"][1, 0] - 0.3) < 1e-6 and s["action_mask"].tolist() == [1, 1, 1]
+    assert ds[11]["action_mask"].tolist() == [1, 0, 0]            # last step of the episode: padded chunk
+    v = s["video"]
+    assert v.shape == (5, 3, 16, 16) and v[1].mean() > v[0].mean() and abs(v[4].mean() - v[3].mean()) < 1e-6   # clamps at the end
+    assert ds.stats()["action"]["q99"] == [1, 1, 1]
+    only = LeRobotDataset(a, str(root), cameras=["observation.images.wrist"], episodes=[1])
+    assert len(only) == 6 and abs(only[0]["images"][0].mean() * 255 - 160) < 6 and only[0]["images"][1].max() == 0
+    ds.raw = True
+    assert ds[0]["task"] == "stack the blocks" and ds[0]["embodiment_tag"] == "toy_arm"
+    b = collate([build_dataset(a)[i] for i in range(2)])
+    assert b["video"].shape == (2, 5, 3, 16, 16)
+    # statistics of the data set itself feed the transforms
+    a2 = _args(tmp_path / "o2", dataset_type="lerobot", dataset_path=str(root), num_cameras=2, image_size=16, action_dim=3, state_dim=4,
+               action_horizon=3, use_transforms=True, stats_path=str(root), model_name="groot_n1_6", embodiment_tags={"toy_arm": 5})
+    t = build_dataset(a2)[3]
+    assert t["embodiment_id"] == 5 and t["images"].shape == (2, 3, 16, 16)
+
+
+def test_dataset_mixture_proportions(tmp_path):
+    from loongforge_b200.embodied.data import MixtureDataset, SyntheticEpisodes, build_dataset, collate
+
+    root = tmp_path / "ds"
+    _write_lerobot(root)
+    a = _args(tmp_path / "o", num_cameras=2, image_size=16, action_dim=3, state_dim=4, action_horizon=3,
+              dataset_mixture=[{"type": "lerobot", "path": str(root), "weight": 3}, {"type": "synthetic", "weight": 1}],
+              mixture_epoch_length=400)
+    ds = build_dataset(a)
+    assert isinstance(ds, MixtureDataset) and len(ds) == 400
+    ids = np.array([int(ds[i]["dataset_id"]) for i in range(400)])
+    assert 0.68 < (ids == 0).mean() < 0.82                        # 3 : 1
+    again = build_dataset(a)
+    assert [int(again[i]["dataset_id"]) for i in range(50)] == ids[:50].tolist()      # same seed, same schedule
+    firsts = [ds[i]["state"].tolist() for i in np.nonzero(ids == 0)[0][:13]]
+    assert firsts[12] == firsts[0]                                # the 12-sample robot set wraps around
+    b = collate([ds[i] for i in range(4)])
+    assert b["images"].shape == (4, 2, 3, 16, 16) and b["dataset_id"].shape == (4,)
