@@ -102,6 +102,9 @@ class EmbodiedArgs:
     lora_adapter_path: Optional[str] = None  # start from a stored adapter (directory with adapter_model.pt + adapter_config.json)
     # ---- CUDA graphs
     per_microbatch_cuda_graph: bool = False
+    cuda_graph_warmup_steps: int = 3       # eager micro-batches per input signature before capture
+    cuda_graph_pad_length: int = 1         # token fields are padded to a multiple of this (fewer distinct signatures)
+    cuda_graph_max_graphs: int = 4
     # ---- checkpoint / logging
     output_dir: str = "./outputs"
     save_interval: int = 0

@@ -127,7 +127,8 @@ class BaseTrainer:
         if self.lora_meta is not None:
             self.logger.note(f"LoRA rank {self.lora_meta['rank']} on {len(self.lora_meta['modules'])} linear layers"
                              + (f", fully trained: {self.lora_meta['saved_modules']}" if self.lora_meta["saved_modules"] else ""))
-        self.graph_runner = MicrobatchGraphRunner(self.model, self.compute_loss) if a.per_microbatch_cuda_graph else None
+        self.graph_runner = (MicrobatchGraphRunner(self.model, self.compute_loss, a.cuda_graph_warmup_steps, a.cuda_graph_pad_length,
+                                                   a.cuda_graph_max_graphs) if a.per_microbatch_cuda_graph else None)
         if a.resume:
             st = ckpt.load_checkpoint(a.output_dir, self.model, self.optimizer, self.scheduler, rank=ctx.rank)
             if st is None:

@@ -806,3 +806,30 @@ def test_dataset_mixture_proportions(tmp_path):
     assert firsts[12] == firsts[0]                                # the 12-sample robot set wraps around
     b = collate([ds[i] for i in range(4)])
     assert b["images"].shape == (4, 2, 3, 16, 16) and b["dataset_id"].shape == (4,)
+
+
+def test_microbatch_graph_runner_signatures_and_padding():
+    """On CPU the runner is eager, but its bookkeeping is the same: token fields padded to the configured multiple, one slot
+    per input signature, least recently used slot dropped, gradients accumulated with the given scale."""
+    from loongforge_b200.embodied.cuda_graph import MicrobatchGraphRunner, pad_batch, shape_key
+
+    b = {"text": torch.ones(2, 5, dtype=torch.long), "state": torch.zeros(2, 3)}
+    p = pad_batch(b, 8)
+    assert p["text"].shape == (2, 8) and p["text"][:, 5:].sum() == 0 and p["state"] is b["state"]
+    assert shape_key(p) != shape_key(b) and shape_key(pad_batch({"text": torch.ones(2, 7, dtype=torch.long), "state": torch.zeros(2, 3)}, 8)) == shape_key(p)
+    lin = torch.nn.Linear(3, 1)
+    loss_fn = lambda m, batch: m(batch["state"]).pow(2).mean() + 0 * batch["text"].float().mean()  # noqa: E731
+    r = MicrobatchGraphRunner(lin, loss_fn, warmup=1, pad_to=8, max_graphs=2)
+    x = torch.randn(2, 3)
+    l1 = r.run({"text": torch.ones(2, 5, dtype=torch.long), "state": x}, scale=0.5)
+    g1 = lin.weight.grad.clone()
+    ref = torch.nn.Linear(3, 1)
+    ref.load_state_dict(lin.state_dict())
+    (0.5 * ref(x).pow(2).mean()).backward()
+    assert torch.allclose(g1, ref.weight.grad) and torch.allclose(l1, ref(x).pow(2).mean())
+    r.run({"text": torch.ones(2, 7, dtype=torch.long), "state": x}, scale=0.5)          # same signature after padding
+    assert len(r.captured) == 1 and next(iter(r.captured.values())).calls == 2
+    assert torch.allclose(lin.weight.grad, 2 * g1)                                        # accumulated
+    r.run({"text": torch.ones(2, 9, dtype=torch.long), "state": x})
+    r.run({"text": torch.ones(2, 17, dtype=torch.long), "state": x})
+    assert len(r.captured) == 2 and r.calls == 4 and r.graph is None                      # oldest signature dropped; no GPU: eager
