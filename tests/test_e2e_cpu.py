@@ -9,7 +9,7 @@ from tests.e2e import harness
 SCEN = os.path.join(os.path.dirname(__file__), "e2e", "scenarios")
 
 
-@pytest.mark.parametrize("name", ["tiny_llama_pretrain.yaml", "tiny_llama_tp2_dp1.yaml", "embodied_pi05.yaml",
+@pytest.mark.parametrize("name", ["tiny_llama_pretrain.yaml", "tiny_llama_tp2_dp1.yaml", "embodied_pi05.yaml", "embodied_dreamzero.yaml",
                                   "tiny_llama_cp2.yaml", "tiny_llama_4l_pretrain.yaml", "tiny_llama_4l_pp2_vpp2.yaml",
                                   "tiny_qwen3_moe_pretrain.yaml", "tiny_qwen3_moe_tp2_ep2.yaml"])
 def test_scenario_matches_baseline(name):
