@@ -65,3 +65,26 @@ def test_launcher_planner_layouts():
     for rel in ("examples/qwen3/pretrain/pretrain_qwen3_8b.sh", "examples/llama3/finetuning/sft_llama3_8b_lora.sh"):
         assert open(os.path.join(ROOT, rel)).read() == files[rel]
     assert len(presets()) >= 55
+
+
+EMBODIED = [p for p in SCRIPTS if "-m loongforge_b200.embodied.train" in open(p).read()]
+
+
+@pytest.mark.parametrize("path", EMBODIED, ids=[os.path.relpath(p, ROOT) for p in EMBODIED])
+def test_embodied_script_overrides_parse(path, monkeypatch):
+    """The recipe and the key=value overrides of every embodied launcher are accepted by the embodied argument parser."""
+    from loongforge_b200.embodied.config import parse_args
+
+    text = open(path).read()
+    m = re.search(r"-m loongforge_b200\.embodied\.train(.*)", text, re.S)
+    body = m.group(1).replace("\\\n", " ")
+    body = re.sub(r'"\$\{DATA_ARGS\[@\]\}"', "dataset_type=synthetic", body)
+    body = re.sub(r"\$\{[A-Z]+:\+[^}]*\}", "", body)                      # ${VAR:+...}: absent by default
+    body = body.replace('"$@"', "")
+    body = re.sub(r'"?\$\{?OUT[^"\s]*"?', "/tmp/x", body)
+    body = re.sub(r'"?\$\{?[A-Z_]+(:-[^}]*)?\}?"?', "/tmp/x", body)
+    monkeypatch.chdir(ROOT)
+    a = parse_args(shlex.split(body))
+    assert a.model_name in path and a.train_steps > 0
+    if "lora" in os.path.basename(path):
+        assert a.lora_rank > 0 and a.lora_targets == []

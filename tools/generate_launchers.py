@@ -282,6 +282,62 @@ def vlm_sft_script(name: str, llm: str) -> str:
     return head + _launch(p, body)
 
 
+EMBODIED = {  # policy -> (strategy, extra overrides, world model?)
+    "pi05": ("ddp", "ddp_comm_hook=bf16_compress per_device_batch_size=16", False),
+    "groot_n1_6": ("ddp", "per_device_batch_size=16", False),
+    "groot_n1_7": ("ddp", "per_device_batch_size=16", False),
+    "xvla": ("ddp", "per_device_batch_size=16", False),
+    "lingbot_va": ("fsdp", "'fsdp_wrap_patterns=[auto]' fsdp_reduce_dtype=fp32 per_device_batch_size=2", True),
+    "fastwam": ("zero1", "per_device_batch_size=2", True),
+    "dreamzero": ("fsdp", "'fsdp_wrap_patterns=[auto]' fsdp_reduce_dtype=fp32 per_device_batch_size=1", True),
+    "cosmos3": ("fsdp", "'fsdp_wrap_patterns=[auto]' fsdp_reduce_dtype=fp32 per_device_batch_size=2", True),
+}
+
+_EMB_HEAD = """#!/bin/bash
+# {title}
+set -euo pipefail
+REPO=$(cd "$(dirname "$0")/../../.." && pwd)
+GPUS=${{GPUS:-8}}
+OUT=${{OUT:-$REPO/outputs/{slug}}}
+DATA=${{DATA:-}}            # LeRobot v2 data set directory (empty: synthetic episodes)
+DATA_ARGS=(dataset_type=synthetic)
+[ -n "$DATA" ] && DATA_ARGS=(dataset_type=lerobot dataset_path="$DATA" use_transforms=true stats_path="$DATA")
+cd "$REPO"
+"""
+
+
+def embodied_scripts() -> Dict[str, str]:
+    out: Dict[str, str] = {}
+    for name, (strategy, extra, world) in EMBODIED.items():
+        run = ('python -m torch.distributed.run --nnodes=1 --nproc-per-node "$GPUS" --master-addr 127.0.0.1 --master-port 29500 \\\n'
+               f"  -m loongforge_b200.embodied.train --config configs/embodied/{name}.yaml \\\n")
+        cache = ' ${CACHE:+precomputed_cache="$CACHE"}' if world else ""
+        out[f"examples/embodied/{name}/finetune_{name}.sh"] = (
+            _EMB_HEAD.format(title=f"Fine-tune the {name} policy ({strategy}); key=value tokens after the script name override the recipe."
+                             + ("\n# CACHE=<dir> trains from features written by precompute_" + name + ".sh." if world else ""), slug=name)
+            + run + f"  strategy={strategy} {extra} train_steps=2000 save_interval=500 log_stage_times=true \\\n"
+            + f'  output_dir="$OUT" "${{DATA_ARGS[@]}}"{cache} "$@"\n')
+        out[f"examples/embodied/{name}/finetune_{name}_lora.sh"] = (
+            _EMB_HEAD.format(title=f"LoRA fine-tuning of {name}: adapters on the policy's default projections, base weights from PRETRAINED.", slug=name + "_lora")
+            + 'PRETRAINED=${PRETRAINED:-}\n' + run
+            + "  strategy=ddp lora_rank=16 lora_alpha=32 'lora_targets=[]' per_device_batch_size=4 lr=2e-4 train_steps=2000 save_interval=500 \\\n"
+            + '  output_dir="$OUT" "${DATA_ARGS[@]}" ${PRETRAINED:+pretrained_checkpoint="$PRETRAINED"} "$@"\n')
+        out[f"examples/embodied/{name}/eval_{name}.sh"] = (
+            f"#!/bin/bash\n# Serve the newest checkpoint of a {name} run and roll out evaluation episodes against it.\nset -euo pipefail\n"
+            'REPO=$(cd "$(dirname "$0")/../../.." && pwd)\nRUN=${1:?run directory (output_dir of the training)}\nPORT=${PORT:-18600}\ncd "$REPO"\n'
+            f'python -m loongforge_b200.embodied.eval serve --checkpoint "$RUN" --port "$PORT" model_name={name} output_dir="$RUN" &\n'
+            'SERVER=$!\ntrap \'kill "$SERVER"\' EXIT\nsleep 20\n'
+            'python -m loongforge_b200.embodied.eval run --port "$PORT" --episodes "${EPISODES:-20}" --output-dir "$RUN/eval"\n')
+        if world:
+            out[f"examples/embodied/{name}/precompute_{name}.sh"] = (
+                f"#!/bin/bash\n# Cache the codec latents / text embeddings of a data set for {name} (train afterwards with CACHE=<dir>).\nset -euo pipefail\n"
+                'REPO=$(cd "$(dirname "$0")/../../.." && pwd)\nDATA=${1:?LeRobot v2 data set directory}\nCACHE=${2:?output directory}\ncd "$REPO"\n'
+                f'python -m tools.data_preprocess.embodied_precompute build --output "$CACHE" --config configs/embodied/{name}.yaml \\\n'
+                '  dataset_type=lerobot dataset_path="$DATA" ${PRETRAINED:+pretrained_checkpoint="$PRETRAINED"}\n'
+                f'python -m tools.data_preprocess.embodied_precompute validate --cache "$CACHE" --deep\n')
+    return out
+
+
 def presets() -> List[str]:
     from loongforge_b200.models.registry import list_models
     skip = ("tiny-", "qwen2.5-vit", "minicpm-v-4.6-llm")
@@ -304,6 +360,7 @@ def generate(write: bool) -> Dict[str, str]:
             files[f"examples/{d}/checkpoint_convert/convert_{slug}_mcore_to_hf.sh"] = convert_script(pp, "mcore_to_hf", conv)
     for name, (d, llm) in vlm_presets().items():
         files[f"examples/{d}/finetuning/sft_{name.replace('-', '_').replace('.', '_')}.sh"] = vlm_sft_script(name, llm)
+    files.update(embodied_scripts())
     if write:
         for rel, text in files.items():
             path = os.path.join(ROOT, rel)
