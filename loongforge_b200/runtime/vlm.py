@@ -107,7 +107,11 @@ class VLMTrainer(Trainer):
         if self._lora:
             # adapters per component: {"apply_to_image_encoder": True, ...} next to the usual rank / alpha / targets
             from ..models.peft import apply_vlm_lora
-            apply_vlm_lora(model, frozen=("image_encoder",) if self.freeze_encoder else (), **self._lora)
+            done = apply_vlm_lora(model, frozen=("image_encoder",) if self.freeze_encoder else (), **self._lora)
+            if self.st.rank == 0:
+                n_train = sum(p.numel() for p in model.parameters() if p.requires_grad)
+                print(" > LoRA adapters: " + ", ".join(f"{k}: {len(v)} linears" for k, v in done.items())
+                      + f"; {n_train:,d} trainable parameters of {sum(p.numel() for p in model.parameters()):,d}", flush=True)
         return model
 
     def _build_omni(self, pre_process, post_process, layer_numbers):

@@ -64,6 +64,17 @@ def main(argv: Optional[List[str]] = None) -> int:
         extra["full_hetero_cpu_offload"] = bool(getattr(args, "full_hetero_dp_cpu_offload", False))
         if getattr(args, "image_resolution", None):
             extra["image_size"] = int(args.image_resolution)
+    peft = node.get("peft_config") if isinstance(node, dict) else None
+    if isinstance(peft, dict) and train_cfg.training_phase == "sft":
+        # adapters described in the model YAML (configs/models/lora/*.yaml composed as `model.peft_config`)
+        extra["lora"] = dict(rank=int(peft.get("dim", peft.get("rank", 16))), alpha=float(peft.get("alpha", 32)),
+                             dropout=float(peft.get("dropout", 0.0)),
+                             targets=tuple(peft.get("target_modules") or ("linear_qkv", "linear_proj", "linear_fc1", "linear_fc2")),
+                             canonical=bool(peft.get("canonical", False)))
+        if isinstance(enc, dict):
+            extra["lora"].update(apply_to_foundation=bool(peft.get("apply_to_foundation", True)),
+                                 apply_to_image_encoder=bool(peft.get("apply_to_image_encoder", False)),
+                                 apply_to_image_projector=bool(peft.get("apply_to_image_projector", False)))
     if getattr(args, "peft_type", None) and train_cfg.training_phase == "sft" and "lora" not in extra:
         extra["lora"] = dict(rank=args.lora_rank, alpha=args.lora_alpha, dropout=args.lora_dropout,
                              targets=tuple(args.lora_target_modules), canonical=args.peft_type == "canonical_lora")

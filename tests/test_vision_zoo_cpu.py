@@ -270,3 +270,60 @@ def test_every_vlm_yaml_builds_and_trains_at_reduced_size(name):
     loss.backward()
     assert torch.isfinite(loss), name
     assert any(p.grad is not None and p.grad.abs().sum() > 0 for p in m.parameters())
+
+
+def test_vlm_cli_with_lora_described_in_the_model_yaml(tmp_path):
+    """`model.peft_config` of a composed VLM YAML (configs/models/lora/vlm_lora.yaml) gives the language model adapters
+    and leaves the frozen encoder alone; the run trains through the CLI."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    y = tmp_path / "tiny_vl_lora.yaml"
+    y.write_text(f"""
+defaults:
+  - {root}/configs/models/lora@model.peft_config: vlm_lora
+  - _self_
+model:
+  model_type: qwen2_5_vl
+  image_encoder:
+    model_type: qwen2_5_vit
+    freeze: true
+    num_layers: 2
+    hidden_size: 64
+    kv_channels: 16
+    ffn_hidden_size: 128
+    num_attention_heads: 4
+    num_query_groups: 4
+    patch_size: 14
+    temporal_patch_size: 2
+    spatial_merge_size: 2
+    normalization: RMSNorm
+    add_qkv_bias: true
+    causal: false
+    vocab_size: 0
+  foundation:
+    model_type: llama
+    num_layers: 2
+    hidden_size: 64
+    num_attention_heads: 4
+    num_query_groups: 2
+    ffn_hidden_size: 128
+    vocab_size: 512
+  peft_config:
+    apply_to_foundation: true
+    dim: 4
+""")
+    cmd = [sys.executable, "-m", "loongforge_b200.train", "--config-file", str(y), "--training-phase", "sft", "--mock-data",
+           "--seq-length", "64", "--micro-batch-size", "1", "--global-batch-size", "2", "--train-iters", "2", "--lr", "1e-3",
+           "--image-resolution", "56", "--log-interval", "1"]
+    p = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=600,
+                       env=dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=root))
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
+    assert "iteration        2/" in p.stdout
+    line = next(l for l in p.stdout.splitlines() if "LoRA adapters" in l)
+    assert "foundation: 8 linears" in line and "image_encoder" not in line        # 2 layers x (qkv, proj, fc1, fc2)
+    m = __import__("re").search(r"([\d,]+) trainable parameters of ([\d,]+)", line)
+    trainable, total = (int(x.replace(",", "")) for x in m.groups())
+    assert 0 < trainable < 0.6 * total            # adapters + the (unfrozen) projector; base language model and encoder are fixed
