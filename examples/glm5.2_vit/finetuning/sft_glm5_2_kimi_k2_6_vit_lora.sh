@@ -1,0 +1,34 @@
+#!/bin/bash
+# glm5.2-kimi-k2.6-vit-lora supervised fine-tuning on image-text conversations (language model: glm5.2); the vision encoder keeps
+# tensor-parallel size 1 and is spread over the TP ranks by encoder heterogeneous DP
+# Layout for 16 node(s) of 8 B200 (TP4 + SP, PP2, EP64, DP16); estimated 125 GB of 180 GB per GPU. Written by
+# tools/generate_launchers.py; run it on every node with NODE_RANK set (one node: no variables needed).
+set -euo pipefail
+REPO=$(cd "$(dirname "$0")/../../.." && pwd)
+GPUS=${GPUS:-8}
+NNODES=${NNODES:-16}
+NODE_RANK=${NODE_RANK:-0}
+MASTER_ADDR=${MASTER_ADDR:-127.0.0.1}
+MASTER_PORT=${MASTER_PORT:-29500}
+CKPT=${CKPT:-$REPO/outputs/sft_glm5_2_kimi_k2_6_vit_lora}
+DATA_PATH=${DATA_PATH:-}        # WebDataset shards written by tools/data_preprocess/vlm_to_webdataset.py
+TOKENIZER=${TOKENIZER:-}
+export PYTORCH_CUDA_ALLOC_CONF=expandable_segments:True
+DATA_ARGS=(--mock-data)
+[ -n "$DATA_PATH" ] && DATA_ARGS=(--data-path "$DATA_PATH" --tokenizer-type HFTokenizer --hf-tokenizer-path "$TOKENIZER")
+
+cd "$REPO"
+python -m torch.distributed.run --nnodes "$NNODES" --node-rank "$NODE_RANK" --nproc-per-node "$GPUS" \
+  --master-addr "$MASTER_ADDR" --master-port "$MASTER_PORT" \
+  -m loongforge_b200.train \
+  --model-name glm5.2-kimi-k2.6-vit-lora --training-phase sft \
+  --tensor-model-parallel-size 4 --sequence-parallel --encoder-tensor-model-parallel-size 1 \
+  --pipeline-model-parallel-size 2 \
+  --expert-model-parallel-size 64 --moe-token-dispatcher-type alltoall --moe-grouped-gemm \
+  --use-distributed-optimizer --overlap-grad-reduce --overlap-param-gather \
+  --micro-batch-size 1 --global-batch-size 64 --seq-length 4096 --packing-sft-data --variable-seq-lengths \
+  --bf16 --lr 1e-5 --min-lr 1e-6 --lr-decay-style cosine --lr-warmup-fraction 0.03 --weight-decay 0.1 --clip-grad 1.0 \
+  --train-iters 1000 --log-interval 5 --log-throughput \
+  --save "$CKPT" --save-interval 250 --ckpt-format torch_dist \
+  "${DATA_ARGS[@]}" \
+  +model.image_encoder.freeze=True

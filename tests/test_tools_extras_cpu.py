@@ -280,3 +280,22 @@ def test_sft_preprocessing_masks_splits_packing_and_trainer_reads_shards(tmp_pat
     ids, labels = ds[3]
     ref = json.loads(open(plain / "train_00000.jsonl").readlines()[3])
     assert ids == ref["input_ids"] and labels == ref["labels"]
+
+
+def test_every_conversion_descriptor_names_a_known_family():
+    import glob
+    from types import SimpleNamespace as NS
+    from tools.convert_checkpoint import convert as C
+    from tools.convert_checkpoint.name_maps import FAMILIES
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    files = sorted(glob.glob(os.path.join(root, "configs", "models", "*", "ckpt_convert", "*.yaml")))
+    assert len(files) >= 18
+    for f in files:
+        a = NS(model_type_custom="llama3", safetensors=False, make_vocab_size_divisible_by=128)
+        C.apply_convert_file(a, f)
+        assert a.model_type_custom in FAMILIES, (f, a.model_type_custom)
+        assert a.safetensors is True
+    a = NS(model_type_custom="llama3", safetensors=False, make_vocab_size_divisible_by=128)
+    C.apply_convert_file(a, os.path.join(root, "configs/models/kimi_k2/ckpt_convert/kimi_k2_convert.yaml"))
+    assert a.model_type_custom == "kimi_k2" and a.make_vocab_size_divisible_by == 1280
