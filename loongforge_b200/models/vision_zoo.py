@@ -73,11 +73,15 @@ class LayerScaleLayer(TransformerLayer):
 class GenericViT(nn.Module):
     def __init__(self, cfg: TransformerConfig, *, pos_table_side: Optional[int] = None, rope_2d: bool = True,
                  cls_token: bool = False, layer_scale: bool = False, deepstack_indexes: Sequence[int] = (),
-                 pre_norm: bool = False, post_norm: bool = False, device=None, parallel_state: Optional[str] = None):
+                 pre_norm: bool = False, post_norm: bool = False, patch_bias: bool = False, device=None,
+                 parallel_state: Optional[str] = None):
         super().__init__()
         self.cfg, self.rope_2d, self.side = cfg, rope_2d, pos_table_side
         self.patch_embed = PatchEmbed(cfg, device)
         dt, dev = cfg.params_dtype, device or "cpu"
+        if patch_bias:  # the patch convolution of InternViT / MoonViT / SigLIP-style towers has a bias
+            self.patch_embed.proj.bias = nn.Parameter(torch.zeros(cfg.hidden_size, device=device, dtype=dt))
+            PL.mark_tp(self.patch_embed.proj.bias, None)
         if pos_table_side:
             n = pos_table_side * pos_table_side + (1 if cls_token else 0)
             self.pos_embed = nn.Parameter(PL.init_full_then_slice("vision.pos_embed", (n, cfg.hidden_size), 0.02,
@@ -104,6 +108,8 @@ class GenericViT(nn.Module):
         image/frame is prepended to that image's patches."""
         cfg, dev = self.cfg, pixels.device
         x = self.patch_embed(pixels)
+        if getattr(self.patch_embed.proj, "bias", None) is not None:
+            x = x + self.patch_embed.proj.bias.to(x.dtype)
         g = grid_thw.cpu()
         if self.pos_embed is not None:
             table = self.pos_embed[1:] if self.cls_token is not None else self.pos_embed
@@ -288,11 +294,11 @@ VISION_FAMILIES = {
     # name: (GenericViT options, adapter class)
     "qwen3_vl_vit": (dict(pos_table_side=48, rope_2d=True, deepstack_indexes=(8, 16, 24)), None),
     "qwen3_5_vit": (dict(pos_table_side=48, rope_2d=True), None),
-    "intern_vit": (dict(pos_table_side=32, rope_2d=False, cls_token=True, layer_scale=True), PixelShuffleAdapter),
+    "intern_vit": (dict(pos_table_side=32, rope_2d=False, cls_token=True, layer_scale=True, patch_bias=True), PixelShuffleAdapter),
     "rice_vit": (dict(rope_2d=True, pre_norm=True), None),
-    "moon_vit": (dict(pos_table_side=64, rope_2d=True, post_norm=True), PatchMergerAdapter),
+    "moon_vit": (dict(pos_table_side=64, rope_2d=True, post_norm=True, patch_bias=True), PatchMergerAdapter),
     "ernie_vit": (dict(rope_2d=True, post_norm=True), ResamplerAdapter),
-    "minicpm_v_vit": (dict(pos_table_side=70, rope_2d=False, post_norm=True), DownsampleMLPAdapter),
+    "minicpm_v_vit": (dict(pos_table_side=70, rope_2d=False, post_norm=True, patch_bias=True), DownsampleMLPAdapter),
 }
 
 

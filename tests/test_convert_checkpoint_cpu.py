@@ -1,4 +1,5 @@
 """HF -> mcore (TP2 x PP2 / EP2) -> HF round trip is exact; the converted shards load into the model."""
+import pytest
 import json
 import os
 
@@ -505,3 +506,92 @@ def test_online_upcycling_from_a_dense_hf_checkpoint(tmp_path):
                           src["model.layers.1.post_attention_layernorm.weight"])
     assert sd["decoder.layers.0.mlp.router.weight"].shape == (4, 64)
     ps.destroy_model_parallel()
+
+
+@pytest.mark.parametrize("family", ["intern_vit", "moon_vit"])
+def test_generic_vision_tower_name_maps_round_trip(family):
+    """InternViT / MoonViT towers with their projectors: every tensor of the built modules has a public name, the shapes on
+    the public side are the published ones (Conv2d patch weight, [1, 1 + N, C] or [H, W, C] position table), and loading
+    the converted tensors back reproduces the module's output."""
+    import torch
+    from loongforge_b200.models import vision_zoo as VZ
+    from loongforge_b200.models.config import TransformerConfig
+    from loongforge_b200.parallel import state as ps
+    from tools.convert_checkpoint import name_maps as nm
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(ps.ParallelDims())
+    cfg = TransformerConfig(num_layers=2, hidden_size=64, num_attention_heads=4, kv_channels=16, ffn_hidden_size=128, vocab_size=0,
+                            normalization="LayerNorm", activation="gelu", gated_linear_unit=False, add_bias_linear=True, add_qkv_bias=True,
+                            causal=False, patch_size=14, temporal_patch_size=1, spatial_merge_size=2, position_embedding_type="none",
+                            qk_layernorm_full=(family == "intern_vit"))
+    torch.manual_seed(0)
+    vit = VZ.build_vision_encoder(family, cfg, pos_table_side=4)
+    adapter = VZ.VISION_FAMILIES[family][1](cfg, 96)
+    for p in list(vit.parameters()) + list(adapter.parameters()):
+        torch.nn.init.normal_(p, std=0.05)
+    mc = {"image_encoder." + k: v.detach().clone() for k, v in vit.state_dict().items()}
+    mc.update({"image_projector." + k: v.detach().clone() for k, v in adapter.state_dict().items()})
+    hf = nm.generic_vision_to_hf(mc, family, 2, 4)
+    assert len(hf) == len(mc), sorted(set(mc) - {("image_encoder." + a) for a, _ in nm._GENERIC_VIT[family]["top"]})[:3]
+    if family == "intern_vit":
+        assert hf["vision_model.embeddings.patch_embedding.weight"].shape == (64, 3, 14, 14)
+        assert hf["vision_model.embeddings.position_embedding"].shape == (1, 17, 64)
+        assert hf["vision_model.embeddings.class_embedding"].shape == (1, 1, 64) and "mlp1.3.weight" in hf
+        assert "vision_model.encoder.layers.1.attn.q_norm.weight" in hf and "vision_model.encoder.layers.0.ls2" in hf
+    else:
+        assert hf["vision_tower.patch_embed.pos_emb.weight"].shape == (4, 4, 64)
+        assert "vision_tower.encoder.blocks.1.wqkv.bias" in hf and "multi_modal_projector.linear_2.weight" in hf
+    # q rows of head 0 come first on the public side, per-head interleaved on ours
+    w_pub = hf[("vision_model.encoder.layers.0.attn.qkv.weight" if family == "intern_vit" else "vision_tower.encoder.blocks.0.wqkv.weight")]
+    w_own = mc["image_encoder.decoder.layers.0.self_attention.linear_qkv.weight"]
+    assert torch.equal(w_pub[:16], w_own[:16]) and torch.equal(w_pub[64:80], w_own[16:32])
+    back = nm.generic_vision_to_mcore(hf, family, 2, 4)
+    assert set(back) == set(mc) and all(torch.equal(back[k], mc[k]) for k in mc)
+    vit2 = VZ.build_vision_encoder(family, cfg, pos_table_side=4)
+    vit2.load_state_dict({k[len("image_encoder."):]: v for k, v in back.items() if k.startswith("image_encoder.")})
+    grid = torch.tensor([[1, 4, 4]])
+    px = torch.randn(16, 3 * 14 * 14)
+    assert torch.allclose(vit(px, grid)[0], vit2(px, grid)[0])
+
+
+def test_internvl_style_checkpoint_converts_both_ways(tmp_path):
+    """``language_model.*`` + ``vision_model.*`` + ``mlp1.*`` (InternVL layout, Qwen3 language model) -> TP2 training shards
+    -> back: every tensor returns bit-exact."""
+    from safetensors.torch import load_file, save_file
+    from tools.convert_checkpoint import convert as C
+
+    src = tmp_path / "lm"
+    _fake_hf(str(src), L=2, V=512, qk_norm=True)
+    lm = load_file(str(src / "model.safetensors"))
+    torch.manual_seed(1)
+    sd = {"language_model." + k: v for k, v in lm.items()}
+    C_, nh = 64, 4
+    sd.update({"vision_model.embeddings.class_embedding": torch.randn(1, 1, C_), "vision_model.embeddings.position_embedding": torch.randn(1, 17, C_),
+               "vision_model.embeddings.patch_embedding.weight": torch.randn(C_, 3, 14, 14), "vision_model.embeddings.patch_embedding.bias": torch.randn(C_),
+               "mlp1.0.weight": torch.randn(4 * C_), "mlp1.0.bias": torch.randn(4 * C_), "mlp1.1.weight": torch.randn(64, 4 * C_),
+               "mlp1.1.bias": torch.randn(64), "mlp1.3.weight": torch.randn(64, 64), "mlp1.3.bias": torch.randn(64)})
+    for i in range(2):
+        p = f"vision_model.encoder.layers.{i}."
+        sd.update({p + "norm1.weight": torch.randn(C_), p + "norm1.bias": torch.randn(C_), p + "norm2.weight": torch.randn(C_), p + "norm2.bias": torch.randn(C_),
+                   p + "attn.qkv.weight": torch.randn(3 * C_, C_), p + "attn.qkv.bias": torch.randn(3 * C_), p + "attn.proj.weight": torch.randn(C_, C_),
+                   p + "attn.proj.bias": torch.randn(C_), p + "ls1": torch.randn(C_), p + "ls2": torch.randn(C_), p + "mlp.fc1.weight": torch.randn(128, C_),
+                   p + "mlp.fc1.bias": torch.randn(128), p + "mlp.fc2.weight": torch.randn(C_, 128), p + "mlp.fc2.bias": torch.randn(C_)})
+    hf_dir = tmp_path / "internvl"
+    os.makedirs(hf_dir)
+    save_file(sd, str(hf_dir / "model.safetensors"))
+    (hf_dir / "config.json").write_text(json.dumps({"llm_config": {"num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "vocab_size": 512},
+                                                    "vision_config": {"num_hidden_layers": 2, "num_attention_heads": nh}}))
+    mc_dir, back_dir = tmp_path / "mc", tmp_path / "back"
+    common = ["--model_type_custom", "internvl3.5", "--language_family", "qwen3", "--vit_num_heads", "4", "--num_layers", "2",
+              "--num_attention_heads", "4", "--num_query_groups", "2", "--vocab_size", "512"]
+    C.main(["--load_platform", "huggingface", "--save_platform", "mcore", "--load_ckpt_path", str(hf_dir), "--save_ckpt_path", str(mc_dir),
+            "--tensor_model_parallel_size", "2", "--safetensors"] + common)
+    C.main(["--load_platform", "mcore", "--save_platform", "huggingface", "--load_ckpt_path", str(mc_dir), "--save_ckpt_path", str(back_dir),
+            "--safetensors"] + common)
+    out = load_file(str(back_dir / "model.safetensors"))
+    assert set(out) == set(sd), (sorted(set(sd) - set(out))[:4], sorted(set(out) - set(sd))[:4])
+    assert all(torch.equal(out[k], sd[k]) for k in sd)
+    with pytest.raises(SystemExit):
+        C.main(["--load_platform", "huggingface", "--save_platform", "mcore", "--load_ckpt_path", str(hf_dir), "--save_ckpt_path", str(mc_dir),
+                "--model_type_custom", "internvl"])

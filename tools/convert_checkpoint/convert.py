@@ -50,6 +50,9 @@ def parse_args(argv=None):
     p.add_argument("--num_attention_heads", type=int, default=None)
     p.add_argument("--num_query_groups", type=int, default=None)
     p.add_argument("--num_experts", type=int, default=None)
+    p.add_argument("--language_family", default=None,
+                   help="name-map family of the language model inside an InternVL / Kimi-VL composition "
+                        "(--model_type_custom internvl | kimi_vl ...), e.g. qwen3, qwen2.5, internlm2.5, deepseek")
     p.add_argument("--vit_num_layers", type=int, default=None, help="vision tower depth (else vision_config.depth)")
     p.add_argument("--vit_num_heads", type=int, default=None, help="vision tower heads (else vision_config.num_heads)")
     p.add_argument("--linear_attention_geometry", default=None,
@@ -86,7 +89,7 @@ def _model_dims(args, hf_dir: Optional[str]):
     cfg = {}
     if hf_dir and os.path.isfile(os.path.join(hf_dir, "config.json")):
         cfg = json.load(open(os.path.join(hf_dir, "config.json")))
-    tc = cfg.get("text_config") or cfg  # vision-language configs nest the language model's fields
+    tc = cfg.get("text_config") or cfg.get("llm_config") or cfg  # vision-language configs nest the language model's fields
     L = args.num_layers or tc.get("num_hidden_layers")
     H = args.num_attention_heads or tc.get("num_attention_heads")
     G = args.num_query_groups or tc.get("num_key_value_heads") or H
@@ -245,12 +248,15 @@ def merge_lora_into(mc: Dict[str, torch.Tensor], lora_sd: Dict[str, torch.Tensor
 
 def main(argv=None):
     a = parse_args(argv)
+    composite = nm.COMPOSITE_VLM.get(a.model_type_custom)
+    if composite and not a.language_family:
+        raise SystemExit(f"--model_type_custom {a.model_type_custom} needs --language_family (the language model's name-map family)")
     vlm = a.model_type_custom in nm.VLM_FAMILIES
-    fam = nm.FAMILIES[nm.VLM_FAMILIES[a.model_type_custom] if vlm else a.model_type_custom]
+    fam = nm.FAMILIES[a.language_family if composite else nm.VLM_FAMILIES[a.model_type_custom] if vlm else a.model_type_custom]
     dt = getattr(torch, a.torch_dtype) if a.torch_dtype else None
     hf_dir = a.load_ckpt_path if a.load_platform == "huggingface" else None
     L, H, G, V, E, tie, hf_cfg = _model_dims(a, hf_dir)
-    tc = hf_cfg.get("text_config") or hf_cfg
+    tc = hf_cfg.get("text_config") or hf_cfg.get("llm_config") or hf_cfg
     nm.set_qk_norm_over_all_heads(a.model_type_custom == "minimax")
     if a.linear_attention_geometry:
         nm.set_linear_attention_geometry(*[int(x) for x in a.linear_attention_geometry.split(",")])
@@ -260,10 +266,18 @@ def main(argv=None):
     if a.load_platform == "huggingface":
         hf = load_hf(a.load_ckpt_path)
         mult = a.make_vocab_size_divisible_by * a.tensor_model_parallel_size
-        if not vlm:
+        if composite:
+            vc = hf_cfg.get("vision_config", {})
+            vit = dict(vit_layers=a.vit_num_layers or vc.get("num_hidden_layers") or vc.get("depth"),
+                       vit_heads=a.vit_num_heads or vc.get("num_attention_heads") or vc.get("num_heads"))
+            V = a.vocab_size or tc.get("vocab_size") or hf["language_model." + fam.hf_prefix + "embed_tokens.weight"].shape[0]
+            padded = -(-V // mult) * mult
+            mc = nm.composite_vlm_hf_to_mcore(hf, fam, composite, num_layers=L, num_heads=H, num_groups=G, padded_vocab=padded,
+                                              num_experts=E, tie_embeddings=tie, **vit)
+        elif not vlm:
             V = V or hf[fam.hf_prefix + "embed_tokens.weight"].shape[0]
             padded = -(-V // mult) * mult
-        if vlm:
+        if vlm and not composite:
             vc = hf_cfg.get("vision_config", {})
             vit = dict(vit_layers=a.vit_num_layers or vc.get("depth"), vit_heads=a.vit_num_heads or vc.get("num_heads"))
             lp, _ = nm._vlm_prefixes(hf)
@@ -271,7 +285,7 @@ def main(argv=None):
             padded = -(-V // mult) * mult
             mc = nm.vlm_hf_to_mcore(hf, fam, num_layers=L, num_heads=H, num_groups=G, padded_vocab=padded,
                                     num_experts=E, tie_embeddings=tie, **vit)
-        else:
+        elif not composite:
             mc = nm.hf_to_mcore(hf, fam, num_layers=L, num_heads=H, num_groups=G, padded_vocab=padded, num_experts=E,
                                 tie_embeddings=tie)
     else:
@@ -289,7 +303,13 @@ def main(argv=None):
                    ep=a.expert_parallel_size, num_layers=L, num_experts=E, custom_layers=a.custom_pipeline_layers,
                    args_dump=dump)
     else:
-        if vlm:
+        if composite:
+            n_vit = 1 + max(int(k.split("image_encoder.decoder.layers.")[1].split(".")[0]) for k in mc
+                            if "image_encoder.decoder.layers." in k)
+            hf_out = nm.composite_vlm_mcore_to_hf(mc, fam, composite, vit_layers=a.vit_num_layers or n_vit, vit_heads=a.vit_num_heads,
+                                                  num_layers=L, num_heads=H, num_groups=G, vocab_size=V, num_experts=E,
+                                                  tie_embeddings=tie)
+        elif vlm:
             n_vit = 1 + max(int(k.split("image_encoder.decoder.layers.")[1].split(".")[0]) for k in mc
                             if "image_encoder.decoder.layers." in k)
             hf_out = nm.vlm_mcore_to_hf(mc, fam, vit_layers=a.vit_num_layers or n_vit, vit_heads=a.vit_num_heads,

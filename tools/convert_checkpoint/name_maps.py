@@ -745,3 +745,126 @@ def qwen3_vision_to_mcore(hf: Dict[str, torch.Tensor], *, num_layers: int, num_h
                 taps[mk.format(k=k)] = hf[prefix + hk.format(k=k)]
         k += 1
     return vit, taps
+
+
+# ---- InternViT (InternVL2.5 / 3.5) and MoonViT (Kimi-VL / K2.5 / K2.6) towers with their projectors --------------------
+# (configs/models/image_encoder/ckpt_convert/{internvl_vit_*,moon_vit_3d}_convert.yaml,
+#  configs/models/image_projector/ckpt_convert/{intern_mlp_adapter,patch_merger_adapter}_convert.yaml)
+_GENERIC_VIT = {
+    "intern_vit": dict(
+        prefix="vision_model.", proj_prefix="mlp1.",
+        top=[("patch_embed.proj.weight", "embeddings.patch_embedding.weight"), ("patch_embed.proj.bias", "embeddings.patch_embedding.bias"),
+             ("pos_embed", "embeddings.position_embedding"), ("cls_token", "embeddings.class_embedding")],
+        layer_prefix="encoder.layers.",
+        layer=[("self_attention.linear_qkv.layer_norm_weight", "norm1.weight"), ("self_attention.linear_qkv.layer_norm_bias", "norm1.bias"),
+               ("self_attention.linear_qkv.weight", "attn.qkv.weight"), ("self_attention.linear_qkv.bias", "attn.qkv.bias"),
+               ("self_attention.q_layernorm.weight", "attn.q_norm.weight"), ("self_attention.k_layernorm.weight", "attn.k_norm.weight"),
+               ("self_attention.linear_proj.weight", "attn.proj.weight"), ("self_attention.linear_proj.bias", "attn.proj.bias"),
+               ("ls1", "ls1"), ("ls2", "ls2"),
+               ("mlp.linear_fc1.layer_norm_weight", "norm2.weight"), ("mlp.linear_fc1.layer_norm_bias", "norm2.bias"),
+               ("mlp.linear_fc1.weight", "mlp.fc1.weight"), ("mlp.linear_fc1.bias", "mlp.fc1.bias"),
+               ("mlp.linear_fc2.weight", "mlp.fc2.weight"), ("mlp.linear_fc2.bias", "mlp.fc2.bias")],
+        projector=[("norm.weight", "0.weight"), ("norm.bias", "0.bias"), ("fc1.weight", "1.weight"), ("fc1.bias", "1.bias"),
+                   ("fc2.weight", "3.weight"), ("fc2.bias", "3.bias")]),
+    "moon_vit": dict(
+        prefix="vision_tower.", proj_prefix="multi_modal_projector.",
+        top=[("patch_embed.proj.weight", "patch_embed.proj.weight"), ("patch_embed.proj.bias", "patch_embed.proj.bias"),
+             ("pos_embed", "patch_embed.pos_emb.weight"), ("post_layernorm.weight", "encoder.final_layernorm.weight"),
+             ("post_layernorm.bias", "encoder.final_layernorm.bias")],
+        layer_prefix="encoder.blocks.",
+        layer=[("self_attention.linear_qkv.layer_norm_weight", "norm0.weight"), ("self_attention.linear_qkv.layer_norm_bias", "norm0.bias"),
+               ("self_attention.linear_qkv.weight", "wqkv.weight"), ("self_attention.linear_qkv.bias", "wqkv.bias"),
+               ("self_attention.linear_proj.weight", "wo.weight"), ("self_attention.linear_proj.bias", "wo.bias"),
+               ("mlp.linear_fc1.layer_norm_weight", "norm1.weight"), ("mlp.linear_fc1.layer_norm_bias", "norm1.bias"),
+               ("mlp.linear_fc1.weight", "mlp.fc0.weight"), ("mlp.linear_fc1.bias", "mlp.fc0.bias"),
+               ("mlp.linear_fc2.weight", "mlp.fc1.weight"), ("mlp.linear_fc2.bias", "mlp.fc1.bias")],
+        projector=[("pre_norm.weight", "pre_norm.weight"), ("pre_norm.bias", "pre_norm.bias"), ("fc1.weight", "linear_1.weight"),
+                   ("fc1.bias", "linear_1.bias"), ("fc2.weight", "linear_2.weight"), ("fc2.bias", "linear_2.bias")]),
+}
+
+
+def _vit_shape_to_mcore(family: str, key: str, t: torch.Tensor, num_heads: int) -> torch.Tensor:
+    if key.endswith("linear_qkv.weight") or key.endswith("linear_qkv.bias"):
+        return _vit_pack_qkv(t, num_heads)
+    if key == "patch_embed.proj.weight" and t.dim() == 4:
+        return t.unsqueeze(2)                                       # Conv2d -> the Conv3d shape with one frame per patch
+    if key == "pos_embed":
+        return t.reshape(-1, t.shape[-1])                           # [1, 1 + N, C] (InternViT) or [H, W, C] (MoonViT) -> rows
+    if key == "cls_token":
+        return t.reshape(1, -1)
+    return t
+
+
+def _vit_shape_to_hf(family: str, key: str, t: torch.Tensor, num_heads: int) -> torch.Tensor:
+    if key.endswith("linear_qkv.weight") or key.endswith("linear_qkv.bias"):
+        return _vit_unpack_qkv(t, num_heads)
+    if key == "patch_embed.proj.weight" and t.dim() == 5:
+        return t.squeeze(2)
+    if key == "pos_embed":
+        if family == "intern_vit":
+            return t.unsqueeze(0)
+        side = int(round(t.shape[0] ** 0.5))
+        return t.reshape(side, side, t.shape[-1])
+    if key == "cls_token":
+        return t.reshape(1, 1, -1)
+    return t
+
+
+def generic_vision_to_mcore(hf: Dict[str, torch.Tensor], family: str, num_layers: int, num_heads: int) -> Dict[str, torch.Tensor]:
+    """Vision tower and projector tensors of an InternVL / Kimi-VL checkpoint -> ``image_encoder.* / image_projector.*``
+    (entries the checkpoint does not have, like q / k norms of the small InternViT, are skipped)."""
+    spec = _GENERIC_VIT[family]
+    out: Dict[str, torch.Tensor] = {}
+    for mk, hk in spec["top"]:
+        if spec["prefix"] + hk in hf:
+            out["image_encoder." + mk] = _vit_shape_to_mcore(family, mk, hf[spec["prefix"] + hk], num_heads)
+    for i in range(num_layers):
+        for mk, hk in spec["layer"]:
+            src = f"{spec['prefix']}{spec['layer_prefix']}{i}.{hk}"
+            if src in hf:
+                out[f"image_encoder.decoder.layers.{i}.{mk}"] = _vit_shape_to_mcore(family, mk, hf[src], num_heads)
+    for mk, hk in spec["projector"]:
+        if spec["proj_prefix"] + hk in hf:
+            out["image_projector." + mk] = hf[spec["proj_prefix"] + hk]
+    return out
+
+
+def generic_vision_to_hf(mc: Dict[str, torch.Tensor], family: str, num_layers: int, num_heads: int) -> Dict[str, torch.Tensor]:
+    spec = _GENERIC_VIT[family]
+    out: Dict[str, torch.Tensor] = {}
+    for mk, hk in spec["top"]:
+        if "image_encoder." + mk in mc:
+            out[spec["prefix"] + hk] = _vit_shape_to_hf(family, mk, mc["image_encoder." + mk], num_heads)
+    for i in range(num_layers):
+        for mk, hk in spec["layer"]:
+            src = f"image_encoder.decoder.layers.{i}.{mk}"
+            if src in mc:
+                out[f"{spec['prefix']}{spec['layer_prefix']}{i}.{hk}"] = _vit_shape_to_hf(family, mk, mc[src], num_heads)
+    for mk, hk in spec["projector"]:
+        if "image_projector." + mk in mc:
+            out[spec["proj_prefix"] + hk] = mc["image_projector." + mk]
+    return out
+
+
+# vision-language checkpoints that keep the language model under ``language_model.`` next to a tower of its own:
+# composition name -> vision family of ``_GENERIC_VIT``
+COMPOSITE_VLM = {"internvl": "intern_vit", "internvl2.5": "intern_vit", "internvl3.5": "intern_vit",
+                 "kimi_vl": "moon_vit", "kimi_k2.5": "moon_vit", "kimi_k2.6": "moon_vit"}
+
+
+def composite_vlm_hf_to_mcore(hf: Dict[str, torch.Tensor], lm_fam: FamilyMap, vision_family: str, *, vit_layers: int,
+                              vit_heads: int, **lm_kw) -> Dict[str, torch.Tensor]:
+    """InternVL / Kimi-VL checkpoint -> ``foundation_model.* / encoder_model.image_encoder.* / image_projector.*``."""
+    lang = {k[len("language_model."):]: v for k, v in hf.items() if k.startswith("language_model.")}
+    out = {"foundation_model." + k: v for k, v in hf_to_mcore(lang, lm_fam, **lm_kw).items()}
+    out.update({"encoder_model." + k: v for k, v in generic_vision_to_mcore(hf, vision_family, vit_layers, vit_heads).items()})
+    return out
+
+
+def composite_vlm_mcore_to_hf(mc: Dict[str, torch.Tensor], lm_fam: FamilyMap, vision_family: str, *, vit_layers: int,
+                              vit_heads: int, **lm_kw) -> Dict[str, torch.Tensor]:
+    lang = mcore_to_hf({k[len("foundation_model."):]: v for k, v in mc.items() if k.startswith("foundation_model.")}, lm_fam, **lm_kw)
+    out = {"language_model." + k: v for k, v in lang.items()}
+    out.update(generic_vision_to_hf({k[len("encoder_model."):]: v for k, v in mc.items() if k.startswith("encoder_model.")},
+                                    vision_family, vit_layers, vit_heads))
+    return out
