@@ -299,3 +299,24 @@ def test_every_conversion_descriptor_names_a_known_family():
     a = NS(model_type_custom="llama3", safetensors=False, make_vocab_size_divisible_by=128)
     C.apply_convert_file(a, os.path.join(root, "configs/models/kimi_k2/ckpt_convert/kimi_k2_convert.yaml"))
     assert a.model_type_custom == "kimi_k2" and a.make_vocab_size_divisible_by == 1280
+
+
+def test_compare_checkpoints_tool(tmp_path, capsys):
+    from safetensors.torch import save_file
+    from tools.dist_checkpoint import compare_checkpoints as CC
+
+    torch.manual_seed(0)
+    a = {"w": torch.randn(4, 4), "b": torch.randn(4), "only_a": torch.zeros(1), "s": torch.randn(2, 3)}
+    b = {"w": a["w"].clone(), "b": a["b"] + 1e-3, "only_b": torch.zeros(1), "s": torch.randn(3, 2)}
+    os.makedirs(tmp_path / "A")
+    os.makedirs(tmp_path / "B")
+    save_file(a, str(tmp_path / "A" / "model.safetensors"))
+    torch.save(b, tmp_path / "B" / "pytorch_model.bin")
+    rc = CC.main([str(tmp_path / "A"), str(tmp_path / "B"), "--report", str(tmp_path / "r.json")])
+    rep = json.load(open(tmp_path / "r.json"))
+    assert rc == 1 and rep["only_in_a"] == ["only_a"] and rep["only_in_b"] == ["only_b"] and rep["matched"] == 1
+    assert rep["shape_mismatch"][0]["key"] == "s" and rep["value_mismatch"][0]["key"] == "b" and abs(rep["max_abs_diff"] - 1e-3) < 1e-5
+    out = capsys.readouterr().out
+    assert "DIFFERENT" in out and "only in A: 1 (only_a)" in out and "value  b:" in out
+    assert CC.main([str(tmp_path / "A"), str(tmp_path / "B"), "--atol", "1e-2", "--ignore", "^only_", "^s$"]) == 0
+    assert CC.main([str(tmp_path / "A" / "model.safetensors"), str(tmp_path / "A")]) == 0
