@@ -254,8 +254,8 @@ class Cosmos3Network(nn.Module):
         in [0, 1]; ``noisy_vision`` / ``noisy_action``: boolean per vision / action token (False = conditioning, clean).
         Returns per-sample velocity predictions for the latents and the actions, and the final hidden states."""
         c = self.c
-        x = self.embed_tokens.weight.new_zeros(seq.length, c.hidden_size)
-        x = x.index_copy(0, seq.text_index, self.embed_tokens(seq.text_ids))
+        t_emb = self.embed_tokens(seq.text_ids)   # (through the module's forward: its weight may be a shard outside it)
+        x = t_emb.new_zeros(seq.length, c.hidden_size).index_copy(0, seq.text_index, t_emb)
         temb = self.time_embed(timesteps)                                             # [B, C]
         v_tok = self.vae2llm(torch.cat([self.patchify(l) for l in latents]).to(x.dtype)) + self.vision_modality_embed
         v_tok = v_tok + temb[seq.sample[seq.vision_index]] * noisy_vision[:, None].to(x.dtype)

@@ -278,3 +278,32 @@ def test_precomputed_feature_cache_matches_online_encoding(name, tmp_path):
     assert any("latents has shape" in p for p in E.validate(cache))
     with pytest.raises(ValueError):
         PrecomputedFeatures(SyntheticEpisodes(a, num_episodes=2, episode_len=10), cache)
+
+
+def _wm_dist(rank, world, name, strategy, out):
+    from loongforge_b200.embodied.distributed import DistContext
+    from loongforge_b200.embodied.trainer import build_trainer
+
+    ctx = DistContext()
+    ctx.rank, ctx.world, ctx.local_rank = rank, world, rank
+    a = validate(EmbodiedArgs(model_name=name, model_overrides={"size": "tiny"}, image_size=32, action_horizon=4,
+                              video_frames=9 if name == "dreamzero" else 5, train_steps=2, per_device_batch_size=2, output_dir=out,
+                              strategy=strategy, fsdp_wrap_patterns=["auto"], fsdp_min_num_params=5000, fsdp_leftover_min_num_params=20000,
+                              hsdp_shard_size=2 if strategy == "hsdp" else None, log_interval=1))
+    t = build_trainer(a, ctx)
+    m = t.train()
+    full = sum(float(p.full_tensor().float().sum()) if hasattr(p, "full_tensor") else float(p.float().sum()) for p in t.model.parameters())
+    return m["loss"], full
+
+
+@pytest.mark.parametrize("name,strategy,world", [("lingbot_va", "fsdp", 2), ("fastwam", "fsdp", 2), ("dreamzero", "fsdp", 2),
+                                                 ("cosmos3", "fsdp", 2), ("dreamzero", "zero1", 2), ("lingbot_va", "hsdp", 4)])
+def test_world_models_train_sharded(name, strategy, world, tmp_path):
+    """The automatic FSDP plan (and ZeRO-1 / HSDP) on the world-model policies: two steps on gloo ranks, finite loss, equal
+    weights on all ranks — the policies that run joint attention over several experts name their no-wrap classes."""
+    import math
+    from tests.dist_utils import run_distributed
+
+    res = run_distributed(_wm_dist, world, name, strategy, str(tmp_path))
+    assert all(math.isfinite(r[0]) for r in res)
+    assert max(abs(r[1] - res[0][1]) for r in res) < 1e-3 * max(1.0, abs(res[0][1]))
