@@ -369,7 +369,7 @@ class GrootActionHead(nn.Module):
         if self.vl_self_attention is not None:
             feats = self.vl_self_attention(feats, valid)
         a = self.action_encoder(F.pad(x_t, (0, c.max_action_dim - x_t.shape[-1])), t_bucket, ids)
-        a = a + self.position_embedding.weight[: a.shape[1]].to(a.dtype)
+        a = a + self.position_embedding(torch.arange(a.shape[1], device=a.device)).to(a.dtype)
         out = self.model(torch.cat([s, a], dim=1), feats, t_bucket, valid, is_image)
         return self.action_decoder(out, ids)[:, -x_t.shape[1]:, : x_t.shape[-1]]
 

@@ -180,8 +180,9 @@ class FlorenceEncoder(nn.Module):
 
     def image_features(self, images):
         t, (h, w) = self.tower(images)
-        pos = torch.cat([self.col_embed.weight[:w].unsqueeze(0).expand(h, -1, -1),
-                         self.row_embed.weight[:h].unsqueeze(1).expand(-1, w, -1)], dim=-1).reshape(1, h * w, -1)
+        # tables are read through the modules' forward (under FSDP their weights are shards outside it)
+        col, row = self.col_embed(torch.arange(w, device=t.device)), self.row_embed(torch.arange(h, device=t.device))
+        pos = torch.cat([col.unsqueeze(0).expand(h, -1, -1), row.unsqueeze(1).expand(-1, w, -1)], dim=-1).reshape(1, h * w, -1)
         f = self.image_proj(t)
         f = self.image_proj_norm(f + pos.to(f.dtype))
         return f + self.temporal_embed.to(f.dtype)
@@ -195,7 +196,7 @@ class FlorenceEncoder(nn.Module):
         text = self.embed_tokens(tokens) * math.sqrt(self.c.d_model)
         x = torch.cat([feats[:, 0], text.to(feats.dtype)], dim=1)
         valid = torch.cat([torch.ones(B, n, dtype=torch.bool, device=x.device), token_mask.bool()], dim=1)
-        x = self.embed_norm(x + self.embed_positions.weight[: x.shape[1]].to(x.dtype))
+        x = self.embed_norm(x + self.embed_positions(torch.arange(x.shape[1], device=x.device)).to(x.dtype))
         for layer in self.layers:
             x = layer(x, valid)
         aux = feats[:, 1:].reshape(B, (V - 1) * n, feats.shape[-1])  # one camera: no auxiliary tokens

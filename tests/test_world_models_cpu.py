@@ -287,7 +287,7 @@ def _wm_dist(rank, world, name, strategy, out):
     ctx = DistContext()
     ctx.rank, ctx.world, ctx.local_rank = rank, world, rank
     a = validate(EmbodiedArgs(model_name=name, model_overrides={"size": "tiny"}, image_size=32, action_horizon=4,
-                              video_frames=9 if name == "dreamzero" else 5, train_steps=2, per_device_batch_size=2, output_dir=out,
+                              video_frames=9 if name == "dreamzero" else 0 if name.startswith(("groot", "xvla")) else 5, train_steps=2, per_device_batch_size=2, output_dir=out,
                               strategy=strategy, fsdp_wrap_patterns=["auto"], fsdp_min_num_params=5000, fsdp_leftover_min_num_params=20000,
                               hsdp_shard_size=2 if strategy == "hsdp" else None, log_interval=1))
     t = build_trainer(a, ctx)
@@ -297,7 +297,8 @@ def _wm_dist(rank, world, name, strategy, out):
 
 
 @pytest.mark.parametrize("name,strategy,world", [("lingbot_va", "fsdp", 2), ("fastwam", "fsdp", 2), ("dreamzero", "fsdp", 2),
-                                                 ("cosmos3", "fsdp", 2), ("dreamzero", "zero1", 2), ("lingbot_va", "hsdp", 4)])
+                                                 ("cosmos3", "fsdp", 2), ("dreamzero", "zero1", 2), ("lingbot_va", "hsdp", 4),
+                                                 ("groot_n1_6", "fsdp", 2), ("groot_n1_7", "fsdp", 2), ("xvla", "fsdp", 2)])
 def test_world_models_train_sharded(name, strategy, world, tmp_path):
     """The automatic FSDP plan (and ZeRO-1 / HSDP) on the world-model policies: two steps on gloo ranks, finite loss, equal
     weights on all ranks — the policies that run joint attention over several experts name their no-wrap classes."""
