@@ -178,6 +178,9 @@ def _add_training_args(p):
 def _add_data_args(p):
     g = p.add_argument_group("data")
     g.add_argument("--data-path", nargs="*", default=None)
+    g.add_argument("--train-data-path", nargs="*", default=None, help="separate training data (then --split is not used)")
+    g.add_argument("--valid-data-path", nargs="*", default=None)
+    g.add_argument("--test-data-path", nargs="*", default=None)
     g.add_argument("--split", type=str, default="949,50,1")
     g.add_argument("--mock-data", action="store_true")
     g.add_argument("--num-workers", type=int, default=2)

@@ -47,6 +47,17 @@ class SFTTrainer(Trainer):
         paths, formats = sft_paths_and_formats(args)
         ds = SFTDataset(paths, tok, template=args.chat_template or "chatml", max_len=self.tcfg.seq_length,
                         train_on_prompt=args.train_on_prompt, seed=self.tcfg.seed, formats=formats)
+        vpaths = list(getattr(args, "valid_data_path", None) or [])
+        if vpaths and self.tcfg.eval_interval and self.tcfg.eval_iters:
+            vformats = None
+            if formats is not None:
+                from ..data.sft_formats import resolve_formats
+                vformats = resolve_formats(list(getattr(args, "sft_valid_dataset", None) or [f.name for f in formats][:1]),
+                                           len(vpaths), getattr(args, "sft_dataset_config", None))
+            vds = SFTDataset(vpaths, tok, template=args.chat_template or "chatml", max_len=self.tcfg.seq_length,
+                             train_on_prompt=args.train_on_prompt, seed=self.tcfg.seed, formats=vformats)
+            self.valid_iterator = sft_batch_iterator(vds, self.tcfg.seq_length, packing=args.packing_sft_data, dp_rank=self.st.dp_rank,
+                                                     dp_size=self.st.dp_size, seed=self.tcfg.seed + 1, pad_id=tok.pad, pad_to_multiple=1)
         return sft_batch_iterator(ds, self.tcfg.seq_length, packing=args.packing_sft_data, dp_rank=self.st.dp_rank,
                                   dp_size=self.st.dp_size, seed=self.tcfg.seed, pad_id=tok.pad,
                                   start_sample=self.consumed_samples // max(self.st.dp_size, 1),

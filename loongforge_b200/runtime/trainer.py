@@ -426,9 +426,10 @@ class Trainer:
     # ------------------------------------------------------------------ data and evaluation
     def build_data_iterator(self, args):
         """Training stream from ``--data-path`` (one ``.bin/.idx`` prefix or weight / prefix pairs, split by
-        ``--split``); also prepares ``self.valid_iterator`` when evaluation is requested. None = no data path
+        ``--split``) or from ``--train-data-path`` with ``--valid-data-path`` beside it; also prepares ``self.valid_iterator`` when evaluation is requested. None = no data path
         (the caller falls back to synthetic data)."""
-        if not getattr(args, "data_path", None):
+        separate = getattr(args, "train_data_path", None)
+        if not (getattr(args, "data_path", None) or separate):
             return None
         from ..data.indexed_dataset import build_gpt_datasets, gpt_batch_iterator
 
@@ -436,9 +437,15 @@ class Trainer:
         n_train = t.train_iters * t.global_batch_size
         n_eval = (t.train_iters // t.eval_interval + 1) * t.eval_iters * t.global_batch_size if t.eval_interval else 0
         eod = getattr(args, "eod_token_id", None)
-        train, valid, _ = build_gpt_datasets(args.data_path, getattr(args, "split", "949,50,1") or "949,50,1",
-                                              t.seq_length, (n_train, n_eval, 0), t.seed, eod,
-                                              bool(getattr(args, "eod_mask_loss", False)))
+        mask_eod = bool(getattr(args, "eod_mask_loss", False))
+        if separate:  # --train-data-path / --valid-data-path: every split has data of its own, used whole
+            train, _, _ = build_gpt_datasets(separate, "100,0,0", t.seq_length, (n_train, 0, 0), t.seed, eod, mask_eod)
+            valid = None
+            if getattr(args, "valid_data_path", None) and n_eval:
+                valid, _, _ = build_gpt_datasets(args.valid_data_path, "100,0,0", t.seq_length, (n_eval, 0, 0), t.seed + 1, eod, mask_eod)
+        else:
+            train, valid, _ = build_gpt_datasets(args.data_path, getattr(args, "split", "949,50,1") or "949,50,1",
+                                                  t.seq_length, (n_train, n_eval, 0), t.seed, eod, mask_eod)
         if train is None:
             raise ValueError("the training split of --data-path holds no documents")
         pin = self.device.type == "cuda"

@@ -519,3 +519,31 @@ def test_dp_balance_warmup_fit_pools_observations_of_all_ranks():
     (c0, n0), (c1, n1) = res
     assert n0 == n1 == 8 and c0 == c1  # same pooled observations -> same plan on every rank
     assert abs(c0[0] - 2e-5) < 1e-7 and abs(c0[1] - 3e-3) < 1e-4 and abs(c0[2] - 0.5) < 5e-2
+
+
+def test_cli_separate_train_and_validation_data(tmp_path):
+    """--train-data-path / --valid-data-path for pretraining (.bin / .idx prefixes) and for SFT (named layouts), with
+    periodic evaluation on the validation stream."""
+    import json
+    import subprocess
+    import sys
+    from tools.data_preprocess import preprocess_pretrain_data as pp
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for name, n in (("train", 60), ("valid", 12)):
+        (tmp_path / f"{name}.jsonl").write_text("\n".join(json.dumps({"text": f"{name} document {i} " + "word " * 40}) for i in range(n)))
+        pp.main(["--input", str(tmp_path / f"{name}.jsonl"), "--output-prefix", str(tmp_path / name), "--append-eod"])
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=root)
+    base = [sys.executable, "-m", "loongforge_b200.train", "--model-name", "tiny-llama", "--seq-length", "64", "--micro-batch-size", "1",
+            "--global-batch-size", "2", "--train-iters", "4", "--lr", "1e-3", "--log-interval", "1", "--eval-interval", "2", "--eval-iters", "2"]
+    p = subprocess.run(base + ["--train-data-path", str(tmp_path / "train_text_document"), "--valid-data-path", str(tmp_path / "valid_text_document"),
+                               "--tokenizer-type", "NullTokenizer", "--vocab-size", "512"], cwd=root, capture_output=True, text=True, timeout=600, env=env)
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
+    assert p.stdout.count("validation loss at iteration") >= 2 or p.stdout.count("validation") >= 2, p.stdout[-1500:]
+    (tmp_path / "sft_train.jsonl").write_text("\n".join(json.dumps({"instruction": f"say {i}", "input": "", "output": f"{i} " * 5}) for i in range(16)))
+    (tmp_path / "sft_valid.jsonl").write_text("\n".join(json.dumps({"instruction": f"tell {i}", "input": "", "output": f"{i}"}) for i in range(6)))
+    q = subprocess.run(base + ["--training-phase", "sft", "--sft-dataset", "alpaca", "--train-data-path", str(tmp_path / "sft_train.jsonl"),
+                               "--valid-data-path", str(tmp_path / "sft_valid.jsonl"), "--chat-template", "chatml", "--packing-sft-data",
+                               "--tokenizer-type", "NullTokenizer", "--vocab-size", "512"], cwd=root, capture_output=True, text=True, timeout=600, env=env)
+    assert q.returncode == 0, q.stdout[-1500:] + q.stderr[-3000:]
+    assert q.stdout.count("validation") >= 2, q.stdout[-1500:]
