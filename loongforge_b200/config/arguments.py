@@ -346,7 +346,8 @@ _COMPAT_FLAGS = [
 COMPAT_WIRED = {"--freeze-parameters", "--freeze-parameters-regex", "--trainable-modules", "--force-pow-2-scales",
                 "--amax-epsilon", "--enable-ema", "--no-check-for-nan-in-loss-and-grad", "--padded-vocab-size",
                 "--offload-optimizer", "--offload-optimizer-percent", "--no-position-embedding", "--group-by-length",
-                "--sft-sort-batch", "--vlm-dp-balance-warmup-iters", "--sft-train-dataset"}
+                "--sft-sort-batch", "--vlm-dp-balance-warmup-iters", "--sft-train-dataset",
+                "--streaming-buffer-size", "--sft-data-mix-strategy", "--sft-valid-dataset"}
 
 
 def _add_compat_args(p):

@@ -164,7 +164,6 @@ _ACCEPTED = {
     "use_flash_attn": "attention always runs on the in-tree flash kernel on GPUs",
     "cuda_graph_scope": "graph capture is offered by runtime.cuda_graphs for callables, not selected by scope",
     "tokenizer_model": "tokenizers load from --hf-tokenizer-path",
-    "sft_data_streaming": "SFT datasets are read eagerly",
     "dataloader_type": "one cyclic, resumable sampler is used",
     "num_workers": "batches are assembled in the training process",
     "variable_seq_lengths": "pipeline stages exchange fixed-shape activations; packed rows are padded to --seq-length",

@@ -45,6 +45,15 @@ class SFTTrainer(Trainer):
             return None
         tok = build_tokenizer(args.tokenizer_type, args.hf_tokenizer_path, use_fast=args.use_fast_tokenizer)
         paths, formats = sft_paths_and_formats(args)
+        if getattr(args, "sft_data_streaming", False):
+            from ..data.sft import streaming_sft_batch_iterator
+            return streaming_sft_batch_iterator(
+                paths, tok, self.tcfg.seq_length, template=args.chat_template or "chatml",
+                buffer_size=int(getattr(args, "streaming_buffer_size", 16384) or 16384),
+                strategy=getattr(args, "sft_data_mix_strategy", "concat") or "concat", formats=formats,
+                train_on_prompt=args.train_on_prompt, packing=args.packing_sft_data, dp_rank=self.st.dp_rank,
+                dp_size=self.st.dp_size, seed=self.tcfg.seed, pad_id=tok.pad,
+                start_sample=self.consumed_samples // max(self.st.dp_size, 1))
         ds = SFTDataset(paths, tok, template=args.chat_template or "chatml", max_len=self.tcfg.seq_length,
                         train_on_prompt=args.train_on_prompt, seed=self.tcfg.seed, formats=formats)
         vpaths = list(getattr(args, "valid_data_path", None) or [])

@@ -260,3 +260,36 @@ def test_named_sft_dataset_layouts(tmp_path):
     custom.write_text("mine:\n  format: alpaca\n  columns: {prompt: q, response: a}\n")
     m, _, _ = F.convert({"q": "Q?", "a": "A."}, F.load_dataset_config(str(custom))["mine"])
     assert m[0]["content"] == "Q?" and m[1]["content"] == "A."
+
+
+def test_streaming_sft_iterator_and_mix_strategies(tmp_path):
+    import json
+    from loongforge_b200.data.sft import mixed_record_stream, streaming_sft_batch_iterator
+    from loongforge_b200.tokenizer.tokenizer import build_tokenizer
+
+    a, b = tmp_path / "a.jsonl", tmp_path / "b.jsonl"
+    a.write_text("\n".join(json.dumps({"instruction": f"a{i}", "output": "x" * 10}) for i in range(5)) + "\n")
+    b.write_text("\n".join(json.dumps({"instruction": f"b{i}", "output": "y" * 10}) for i in range(2)) + "\n")
+    tag = lambda it: [r["instruction"] for r in it]  # noqa: E731
+    assert tag(mixed_record_stream([str(a), str(b)], "concat")) == ["a0", "a1", "a2", "a3", "a4", "b0", "b1"]
+    assert tag(mixed_record_stream([str(a), str(b)], "interleave_under")) == ["a0", "b0", "a1", "b1", "a2"]
+    over = tag(mixed_record_stream([str(a), str(b)], "interleave_over"))
+    assert over[:6] == ["a0", "b0", "a1", "b1", "a2", "b0"] and over.count("a4") == 1 and sum(x.startswith("a") for x in over) == 5
+    tok = build_tokenizer("ByteTokenizer")
+    seen = []
+    for rank in range(2):
+        it = streaming_sft_batch_iterator([str(a), str(b)], tok, 128, buffer_size=3, strategy="concat", dp_rank=rank, dp_size=2, seed=3)
+        rows = []
+        for _ in range(40):
+            batch = next(it)
+            rows.append(batch)
+            text = bytes(t for t in batch["tokens"].flatten().tolist() if 0 < t < 256).decode()
+            seen += [w for w in ("a0", "a1", "a2", "a3", "a4", "b0", "b1") if w in text]
+            if len(set(seen)) == 7 and rank == 1:
+                break
+        assert rows[0]["tokens"].shape == (1, 128)
+    assert set(seen) == {"a0", "a1", "a2", "a3", "a4", "b0", "b1"}            # every record reaches some rank
+    it1 = streaming_sft_batch_iterator([str(a)], tok, 64, buffer_size=2, seed=5)
+    it2 = streaming_sft_batch_iterator([str(a)], tok, 64, buffer_size=2, seed=5, start_sample=2)
+    first = [next(it1) for _ in range(4)]
+    assert torch.equal(next(it2)["tokens"], first[2]["tokens"])               # resuming skips what was consumed
