@@ -171,8 +171,6 @@ _ACCEPTED = {
     "detail_log_interval": "one log interval exists",
     "wandb_exp_name": "the run name is the output directory",
     "packing_batch_size": "the online packer's buffer holds 16 samples (64 for SFT text)",
-    "frame_num": "video inputs are not decoded by the built-in loaders (image-text shards only)",
-    "fps": "video inputs are not decoded by the built-in loaders (image-text shards only)",
 }
 
 

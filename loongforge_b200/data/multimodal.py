@@ -192,13 +192,54 @@ def is_packed_dataset(root: str) -> bool:
         return bool(json.load(f).get("packed"))
 
 
+VIDEO_EXTENSIONS = ("mp4", "avi", "mov", "mkv", "webm")
+
+
+def decode_video(data: bytes, ext: str = "mp4", frame_num: Optional[int] = None, fps: Optional[float] = None) -> List[np.ndarray]:
+    """Frames ``[H, W, 3]`` uint8 of an encoded video: every frame, or frames sampled at ``fps`` (of the video's own clock),
+    thinned evenly to at most ``frame_num`` (``--frame-num`` / ``--fps``). OpenCV reads files, so the bytes pass through
+    a temporary file."""
+    import os
+    import tempfile
+
+    import cv2
+    fd, path = tempfile.mkstemp(suffix="." + ext.split(".")[-1])
+    try:
+        with os.fdopen(fd, "wb") as f:
+            f.write(data)
+        cap = cv2.VideoCapture(path)
+        total = int(cap.get(cv2.CAP_PROP_FRAME_COUNT))
+        native = cap.get(cv2.CAP_PROP_FPS) or 0.0
+        if total <= 0:
+            raise ValueError("video has no frames")
+        step = max(native / fps, 1.0) if (fps and native > 0) else 1.0
+        want = [min(int(round(i * step)), total - 1) for i in range(int((total - 1) // step) + 1)]
+        if frame_num and len(want) > frame_num:
+            want = [want[int(round(i * (len(want) - 1) / max(frame_num - 1, 1)))] for i in range(frame_num)]
+        frames, nxt = [], 0
+        for idx in sorted(set(want)):
+            if idx != nxt:
+                cap.set(cv2.CAP_PROP_POS_FRAMES, idx)
+            ok, fr = cap.read()
+            nxt = idx + 1
+            if ok:
+                frames.append(np.ascontiguousarray(fr[:, :, ::-1]))
+        cap.release()
+        if not frames:
+            raise ValueError("no frame could be decoded")
+        return frames
+    finally:
+        os.remove(path)
+
+
 def webdataset_samples(root: str, *, dp_rank: int = 0, dp_size: int = 1, seed: int = 0, start_sample: int = 0,
-                       epochs: Optional[int] = None):
+                       epochs: Optional[int] = None, frame_num: Optional[int] = None, fps: Optional[float] = None):
     """Raw samples (``{"images": [...], "conversation": [...]}``) from the tar shards under `root` (the layout written
     by tools/data_preprocess/vlm_to_webdataset.py: ``index.json`` + ``shard-*.tar`` with ``{key}.json`` and
     ``{key}[.n].{ext}`` members). Shards are visited in a per-epoch shuffled order that all ranks share; rank r keeps
     every dp_size-th sample (every dp_size-th PACK of shards packed offline, whose members stay together).
-    ``start_sample`` skips what an earlier run of this rank consumed."""
+    ``start_sample`` skips what an earlier run of this rank consumed. Members with a video extension are decoded into
+    frame lists (``videos``), sampled with ``frame_num`` / ``fps``."""
     import json
     import os
     import tarfile
@@ -214,12 +255,17 @@ def webdataset_samples(root: str, *, dp_rank: int = 0, dp_size: int = 1, seed: i
             cur, group, last_pack = None, {}, None
 
             def emit(group, meta):
-                imgs = sorted((k for k in group if k != "json"), key=lambda k: (len(k), k))
+                members = sorted((k for k in group if k != "json"), key=lambda k: (len(k), k))
+                vids = [k for k in members if k.split(".")[-1].lower() in VIDEO_EXTENSIONS]
+                imgs = [k for k in members if k not in vids]
                 pack = {"pack_id": meta["pack_id"], "pack_size": meta["pack_size"]} if "pack_id" in meta else {}
                 conv = meta.get("conversation") or [
                     {"role": "user" if c.get("from", c.get("role")) in ("human", "user") else "assistant",
                      "content": c.get("value", c.get("content", ""))} for c in meta.get("conversations", [])]
-                return {"images": [decode_image(group[k], k) for k in imgs], "conversation": conv, **pack}
+                out = {"images": [decode_image(group[k], k) for k in imgs], "conversation": conv, **pack}
+                if vids:  # video members become frame lists for the <video> markers of the conversation
+                    out["videos"] = [decode_video(group[k], k, frame_num, fps) for k in vids]
+                return out
 
             def take(group):
                 """Counts the sample (or, for packed shards, its pack) and says whether this rank keeps it."""

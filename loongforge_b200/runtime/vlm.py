@@ -151,7 +151,8 @@ class VLMTrainer(Trainer):
             else:
                 enc = VLMTaskEncoder(lambda text: tok.tokenize(text), self.image_token_id, vision, eos_id=tok.eod)
             samples = webdataset_samples(paths[-1], dp_rank=st.dp_rank, dp_size=st.dp_size, seed=self.tcfg.seed,
-                                         start_sample=self.consumed_samples // max(st.dp_size, 1))
+                                         start_sample=self.consumed_samples // max(st.dp_size, 1),
+                                         frame_num=getattr(args, "frame_num", None), fps=getattr(args, "fps", None))
             return vlm_batch_iterator(samples, enc, self.tcfg.seq_length, merge_size=v.spatial_merge_size,
                                       pad_id=tok.pad, packing=bool(getattr(args, "packing_sft_data", True)),
                                       pin_memory=self.device.type == "cuda")

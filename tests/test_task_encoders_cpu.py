@@ -113,3 +113,36 @@ def test_position_id_registry():
     assert P.get_position_id_func("qwen3_vl") is P.qwen3_vl_ids
     with pytest.raises(KeyError):
         P.get_position_id_func("nope")
+
+
+def test_video_members_of_shards_are_decoded_and_encoded(tmp_path):
+    """An .mp4 next to the conversation in a shard -> frames sampled by --fps / --frame-num -> the <video> marker's
+    placeholder tokens and video patches of the Qwen2.5-VL task encoder."""
+    import json
+    import cv2
+    from loongforge_b200.data.multimodal import decode_video, webdataset_samples
+    from loongforge_b200.data.task_encoders import build_task_encoder
+    from tools.data_preprocess import vlm_to_webdataset as W
+
+    src = tmp_path / "raw"
+    src.mkdir()
+    w = cv2.VideoWriter(str(src / "clip.mp4"), cv2.VideoWriter_fourcc(*"mp4v"), 10, (56, 56))
+    for t in range(20):
+        w.write(np.full((56, 56, 3), 10 * t, np.uint8))
+    w.release()
+    data = (src / "clip.mp4").read_bytes()
+    assert len(decode_video(data)) == 20
+    half = decode_video(data, fps=5)                                    # every second frame of a 10 fps clip
+    assert len(half) == 10 and half[1].mean() > half[0].mean()
+    four = decode_video(data, frame_num=4)
+    assert len(four) == 4 and abs(float(four[-1].mean()) - 190) < 12     # first and last frame kept
+    recs = [{"video": "clip.mp4", "conversations": [{"from": "human", "value": "<video> what happens?"}, {"from": "gpt", "value": "it brightens"}]}]
+    W.write_shards(recs, str(tmp_path / "shards"), image_root=str(src))
+    sample = next(webdataset_samples(str(tmp_path / "shards"), epochs=1, frame_num=4))
+    assert len(sample["videos"]) == 1 and len(sample["videos"][0]) == 4 and sample["images"] == []
+    enc = build_task_encoder("qwen2_5_vl", _tok, _sp(), _vision(), max_length=512)
+    out = enc.encode(sample)
+    assert "video_pixels" in out and out["video_grid_thw"][0][0] == 2    # 4 frames, temporal patch 2
+    n_tok = int((out["tokens"] == enc.sp.video).sum()) if enc.sp.video is not None else int((out["tokens"] == enc.sp.image).sum())
+    t, gh, gw = (int(x) for x in out["video_grid_thw"][0])
+    assert n_tok == t * (gh // 2) * (gw // 2)

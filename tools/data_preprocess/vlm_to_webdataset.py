@@ -18,7 +18,8 @@ def _add(tar: tarfile.TarFile, name: str, data: bytes) -> None:
 
 
 def write_shards(records: Iterable[dict], out_dir: str, image_root: str = "", samples_per_shard: int = 1000) -> dict:
-    """records: ``{"image": path or [paths], "conversations": [...]}``. Returns the shard index."""
+    """records: ``{"image": path or [paths], "video": path or [paths], "conversations": [...]}`` (videos keep their
+    container, e.g. ``.mp4``; the loader decodes frames). Returns the shard index."""
     os.makedirs(out_dir, exist_ok=True)
     index, shard, n, tar = {"shards": []}, -1, 0, None
     for i, rec in enumerate(records):
@@ -37,8 +38,14 @@ def write_shards(records: Iterable[dict], out_dir: str, image_root: str = "", sa
             with open(os.path.join(image_root, p), "rb") as f:
                 ext = os.path.splitext(p)[1].lstrip(".").lower() or "jpg"
                 _add(tar, f"{key}.{j}.{ext}" if len(images) > 1 else f"{key}.{ext}", f.read())
-        meta = {k: v for k, v in rec.items() if k != "image"}
-        meta["num_images"] = len(images)
+        videos = rec.get("video") or rec.get("videos") or []
+        videos = [videos] if isinstance(videos, str) else list(videos)
+        for j, p in enumerate(videos):
+            with open(os.path.join(image_root, p), "rb") as f:
+                ext = os.path.splitext(p)[1].lstrip(".").lower() or "mp4"
+                _add(tar, f"{key}.v{j}.{ext}", f.read())
+        meta = {k: v for k, v in rec.items() if k not in ("image", "video", "videos")}
+        meta["num_images"], meta["num_videos"] = len(images), len(videos)
         _add(tar, f"{key}.json", json.dumps(meta).encode())
         n += 1
     if tar is not None:
