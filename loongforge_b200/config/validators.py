@@ -46,8 +46,9 @@ def validate(args, cfg, tc, dims) -> None:
         raise ValueError("encoder hetero-DP needs encoder tensor parallel size 1")
     if getattr(args, "enable_chunkpipe", False) and not getattr(args, "chunksize", None):
         raise ValueError("--enable-chunkpipe needs --chunksize")
-    if tc.training_phase == "sft" and not (getattr(args, "sft_dataset", None) or getattr(args, "mock_data", False)):
-        raise ValueError("SFT needs --sft-dataset (or --mock-data)")
+    if tc.training_phase == "sft" and not (getattr(args, "sft_dataset", None) or getattr(args, "mock_data", False)
+                                           or getattr(args, "data_path", None) or getattr(args, "train_data_path", None)):
+        raise ValueError("SFT needs --sft-dataset / --data-path (or --mock-data)")
     if dims.vpp and dims.vpp > 1 and cfg.num_layers % (dims.pp * dims.vpp) and not tc.custom_pipeline_layers:
         raise ValueError("num_layers must divide by pp x virtual stages")
     _validate_sft(args, tc)

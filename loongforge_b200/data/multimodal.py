@@ -296,6 +296,35 @@ def webdataset_samples(root: str, *, dp_rank: int = 0, dp_size: int = 1, seed: i
         epoch += 1
 
 
+def merge_video_into_image_stream(enc: Dict, image_id: int, video_id: Optional[int]) -> Dict:
+    """The model scatters vision-tower features into the image placeholders in order. A sample with videos therefore gets
+    ONE patch stream and ONE grid list in the order the media appear in its tokens (``media_order``), and its video
+    placeholders are renamed to the image placeholder — after the position ids were computed from the original ids."""
+    if "video_pixels" not in enc:
+        return enc
+    pix, grids = enc["pixels"], enc["grid_thw"]
+    vpix, vgrids = enc["video_pixels"], enc["video_grid_thw"]
+    i_off = [0] + torch.cumsum(grids.prod(-1), 0).tolist() if len(grids) else [0]
+    v_off = [0] + torch.cumsum(vgrids.prod(-1), 0).tolist()
+    parts, out_grids, ki, kv = [], [], 0, 0
+    for kind in enc["media_order"].tolist():
+        if kind == 0:
+            parts.append(pix[i_off[ki]:i_off[ki + 1]])
+            out_grids.append(grids[ki])
+            ki += 1
+        else:
+            parts.append(vpix[v_off[kv]:v_off[kv + 1]].to(pix.dtype if pix.numel() else vpix.dtype))
+            out_grids.append(vgrids[kv])
+            kv += 1
+    enc = dict(enc)
+    enc["pixels"], enc["grid_thw"] = torch.cat(parts), torch.stack(out_grids)
+    if video_id is not None and video_id != image_id:
+        enc["tokens"] = torch.where(enc["tokens"] == video_id, torch.full_like(enc["tokens"], image_id), enc["tokens"])
+    for k in ("video_pixels", "video_grid_thw", "media_order"):
+        enc.pop(k)
+    return enc
+
+
 def vlm_batch_iterator(samples, encoder: VLMTaskEncoder, seq_len: int, *, merge_size: int = 2, pad_id: int = 0,
                        packing: bool = True, buffer_size: int = 16, pin_memory: bool = False):
     """Raw samples -> micro-batches of the vision-language trainer: one packed row of exactly `seq_len` tokens with
@@ -321,6 +350,7 @@ def vlm_batch_iterator(samples, encoder: VLMTaskEncoder, seq_len: int, *, merge_
             continue  # gated by the task encoder (over-long sample)
         if "mrope" not in enc:  # family encoders (data/task_encoders.py) bring their own position ids
             enc["mrope"] = mrope_ids(enc["tokens"], enc["grid_thw"], encoder.img_id, merge_size)
+        enc = merge_video_into_image_stream(enc, encoder.img_id, getattr(getattr(encoder, "sp", None), "video", None))
         if "pack_id" in raw:
             # packs were decided offline: the members of a pack arrive consecutively and form one row as they are
             # (the offline lengths are estimates: a pack that comes out too long sheds its last members)

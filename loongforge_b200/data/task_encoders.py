@@ -110,7 +110,7 @@ class TaskEncoder:
     # ---- the walker
     def encode(self, sample: Dict) -> Optional[Dict[str, torch.Tensor]]:
         conv, images, videos = to_conversation(sample)
-        acc = {"pixels": [], "grids": [], "vpixels": [], "vgrids": [], "tiles": []}
+        acc = {"pixels": [], "grids": [], "vpixels": [], "vgrids": [], "tiles": [], "order": []}
         ids: List[int] = []
         labels: List[int] = []
         ki = kv = 0
@@ -131,11 +131,13 @@ class TaskEncoder:
                     if ki >= len(images):
                         raise ValueError("more <image> markers than images")
                     t_ids += self.encode_image(images[ki], acc)
+                    acc["order"].append(0)
                     ki += 1
                 else:
                     if kv >= len(videos):
                         raise ValueError("more <video> markers than videos")
                     t_ids += self.encode_video(videos[kv], acc)
+                    acc["order"].append(1)
                     kv += 1
                 rest = rest[i + len(m):]
             if turn["role"] == self.roles[1]:
@@ -170,7 +172,15 @@ class TaskEncoder:
         if acc["vpixels"]:
             out["video_pixels"] = torch.from_numpy(np.concatenate(acc["vpixels"]))
             out["video_grid_thw"] = vgrids
-        out["mrope"] = self.positions(tokens, grids if len(grids) else None, vgrids if len(vgrids) else None)
+            out["media_order"] = torch.tensor(acc["order"], dtype=torch.long)   # 0 image / 1 video, in token order
+        if len(vgrids) and self.sp.video is None:
+            # no video placeholder of its own: videos are written with the image placeholder, so the position function
+            # walks ONE grid list in token order
+            ig, vg = iter(grids), iter(vgrids)
+            merged = torch.stack([next(ig) if kind == 0 else next(vg) for kind in acc["order"]])
+            out["mrope"] = self.positions(tokens, merged, None)
+        else:
+            out["mrope"] = self.positions(tokens, grids if len(grids) else None, vgrids if len(vgrids) else None)
         return self.finish(out, acc)
 
 

@@ -145,7 +145,8 @@ class VLMTrainer(Trainer):
                         return None
                     return ids[0] if len(ids) == 1 else None
                 enc = build_task_encoder(self.vision_family, lambda text: tok.tokenize(text),
-                                         SpecialTokens(image=self.image_token_id, vision_start=special("<|vision_start|>"),
+                                         SpecialTokens(image=self.image_token_id, video=special("<|video_pad|>"),
+                                                       vision_start=special("<|vision_start|>"),
                                                        vision_end=special("<|vision_end|>"), eos=tok.eod),
                                          vision, max_length=self.tcfg.seq_length)
             else:

@@ -146,3 +146,24 @@ def test_video_members_of_shards_are_decoded_and_encoded(tmp_path):
     n_tok = int((out["tokens"] == enc.sp.video).sum()) if enc.sp.video is not None else int((out["tokens"] == enc.sp.image).sum())
     t, gh, gw = (int(x) for x in out["video_grid_thw"][0])
     assert n_tok == t * (gh // 2) * (gw // 2)
+
+
+def test_videos_and_images_share_one_patch_stream_in_token_order():
+    from loongforge_b200.data.multimodal import merge_video_into_image_stream, vlm_batch_iterator
+
+    frames = [_img(56, 56, seed=s) for s in range(4)]
+    sample = {"images": [_img(56, 84, seed=9), _img(28, 56, seed=8)], "videos": [frames],
+              "conversation": [{"role": "user", "content": "first <image> then <video> and <image> ?"}, {"role": "assistant", "content": "ok"}]}
+    enc_obj = TE.build_task_encoder("qwen2_5_vl", _tok, _sp(), _vision())
+    enc = enc_obj.encode(sample)
+    assert enc["media_order"].tolist() == [0, 1, 0]
+    merged = merge_video_into_image_stream(enc, IMG, VID)
+    g = merged["grid_thw"]
+    assert g.shape == (3, 3) and torch.equal(g[0], enc["grid_thw"][0]) and torch.equal(g[1], enc["video_grid_thw"][0]) and torch.equal(g[2], enc["grid_thw"][1])
+    assert merged["pixels"].shape[0] == int(g.prod(-1).sum()) and (merged["tokens"] == VID).sum() == 0
+    n0, nv = int(g[0].prod()), int(g[1].prod())
+    assert torch.equal(merged["pixels"][n0:n0 + nv].float(), enc["video_pixels"].float())        # the video sits between the images
+    assert int((merged["tokens"] == IMG).sum()) == int((g.prod(-1) // 4).sum())                 # one placeholder per merged 2 x 2 patch
+    assert torch.equal(merged["mrope"], enc["mrope"])                                             # positions come from the original ids
+    batch = next(vlm_batch_iterator(iter([sample]), enc_obj, 512))
+    assert batch["grid_thw"].shape == (3, 3) and batch["pixels"].shape[0] == int(batch["grid_thw"].prod(-1).sum())

@@ -327,3 +327,45 @@ model:
     m = __import__("re").search(r"([\d,]+) trainable parameters of ([\d,]+)", line)
     trainable, total = (int(x.replace(",", "")) for x in m.groups())
     assert 0 < trainable < 0.6 * total            # adapters + the (unfrozen) projector; base language model and encoder are fixed
+
+
+def test_vlm_cli_trains_on_shards_with_videos(tmp_path):
+    """Shards that mix image samples and video samples (.mp4 members): the loader decodes --frame-num frames, the task
+    encoder writes <video> placeholders, the trainer runs the vision tower over both kinds in one patch stream."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import cv2
+    import numpy as np
+    from tools.data_preprocess.vlm_to_webdataset import write_shards
+
+    raw = tmp_path / "raw"
+    raw.mkdir()
+    rng = np.random.RandomState(0)
+    recs = []
+    for i in range(4):
+        np.save(raw / f"{i}.npy", rng.randint(0, 255, size=(56, 56, 3), dtype=np.uint8))
+        recs.append({"image": f"{i}.npy", "conversations": [{"from": "human", "value": "<image>what?"}, {"from": "gpt", "value": f"item {i}"}]})
+        w = cv2.VideoWriter(str(raw / f"{i}.mp4"), cv2.VideoWriter_fourcc(*"mp4v"), 10, (56, 56))
+        for t in range(8):
+            w.write(rng.randint(0, 255, size=(56, 56, 3), dtype=np.uint8))
+        w.release()
+        recs.append({"video": f"{i}.mp4", "conversations": [{"from": "human", "value": "<video>what moves?"}, {"from": "gpt", "value": f"clip {i}"}]})
+    write_shards(recs, str(tmp_path / "wds"), image_root=str(raw), samples_per_shard=4)
+    y = tmp_path / "tiny_vl.yaml"
+    y.write_text(json.dumps({"model": {
+        "model_type": "qwen2_5_vl",
+        "image_encoder": {"model_type": "qwen2_5_vit", "num_layers": 2, "hidden_size": 64, "kv_channels": 16, "ffn_hidden_size": 128,
+                          "num_attention_heads": 4, "num_query_groups": 4, "patch_size": 14, "temporal_patch_size": 2,
+                          "spatial_merge_size": 2, "causal": False, "vocab_size": 0, "fullatt_block_indexes": [1], "vision_window_size": 56},
+        "foundation": {"model_type": "qwen2", "num_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_query_groups": 2,
+                       "ffn_hidden_size": 128, "vocab_size": 512, "position_embedding_type": "mrope", "mrope_section": [2, 3, 3]}}}))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "loongforge_b200.train", "--config-file", str(y), "--seq-length", "192", "--micro-batch-size", "1",
+           "--global-batch-size", "2", "--train-iters", "3", "--lr", "1e-3", "--log-interval", "1", "--data-path", str(tmp_path / "wds"),
+           "--training-phase", "sft", "--frame-num", "4"]
+    p = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=600, env=dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=root))
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
+    assert "iteration        3/" in p.stdout and "lm loss" in p.stdout
