@@ -170,8 +170,6 @@ _ACCEPTED = {
     "variable_seq_lengths": "pipeline stages exchange fixed-shape activations; packed rows are padded to --seq-length",
     "dist_ckpt_strictness": "unexpected or missing checkpoint keys raise",
     "detail_log_interval": "one log interval exists",
-    "wandb_exp_name": "the run name is the output directory",
-    "packing_batch_size": "the online packer's buffer holds 16 samples (64 for SFT text)",
 }
 
 

@@ -70,9 +70,9 @@ class TensorInspectorHook(TrainHook):
 
 
 class ScalarHook(TrainHook):
-    def __init__(self, out_dir, wandb_project, enabled):
+    def __init__(self, out_dir, wandb_project, enabled, run_name=None):
         from .metrics_writers import ScalarWriter
-        self.w = ScalarWriter(out_dir, wandb_project=wandb_project, enabled=enabled)
+        self.w = ScalarWriter(out_dir, wandb_project=wandb_project, enabled=enabled, run_name=run_name)
 
     def on_step_end(self, trainer, metrics, elapsed_ms):
         sc = {k: v for k, v in metrics.items() if isinstance(v, (int, float))}
@@ -196,7 +196,8 @@ def build_hooks(args, trainer) -> List[TrainHook]:
         pats = [pats] if isinstance(pats, str) else list(pats)
         hooks.append(TensorInspectorHook(trainer, pats, f"{out}/tensors_rank{rank}.jsonl", rank))
     if getattr(args, "tensorboard_dir", None) or getattr(args, "wandb_project", None):
-        hooks.append(ScalarHook(out, getattr(args, "wandb_project", None), enabled=(rank == world - 1)))
+        hooks.append(ScalarHook(out, getattr(args, "wandb_project", None), enabled=(rank == world - 1),
+                                run_name=getattr(args, "wandb_exp_name", None)))
     if getattr(args, "manual_gc", False):
         hooks.append(ManualGCHook(getattr(args, "manual_gc_interval", 0) or 1))
     if getattr(args, "log_straggler", False):

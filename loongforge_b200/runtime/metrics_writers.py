@@ -12,7 +12,8 @@ import torch
 
 
 class ScalarWriter:
-    def __init__(self, out_dir: str, *, tensorboard: bool = True, wandb_project: Optional[str] = None, enabled: bool = True):
+    def __init__(self, out_dir: str, *, tensorboard: bool = True, wandb_project: Optional[str] = None, enabled: bool = True,
+                 run_name: Optional[str] = None):
         self.enabled = enabled
         self.tb = self.wandb = None
         if not enabled:
@@ -28,7 +29,9 @@ class ScalarWriter:
         if wandb_project:
             try:
                 import wandb
-                self.wandb = wandb.init(project=wandb_project, dir=out_dir)
+                # no network is assumed: runs are written to disk unless WANDB_MODE says otherwise
+                self.wandb = wandb.init(project=wandb_project, name=run_name, dir=out_dir,
+                                        mode=os.environ.get("WANDB_MODE", "offline"))
             except Exception:  # noqa: BLE001
                 self.wandb = None
 

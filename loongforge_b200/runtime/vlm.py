@@ -156,6 +156,7 @@ class VLMTrainer(Trainer):
                                          frame_num=getattr(args, "frame_num", None), fps=getattr(args, "fps", None))
             return vlm_batch_iterator(samples, enc, self.tcfg.seq_length, merge_size=v.spatial_merge_size,
                                       pad_id=tok.pad, packing=bool(getattr(args, "packing_sft_data", True)),
+                                      buffer_size=int(getattr(args, "packing_batch_size", None) or 16),
                                       pin_memory=self.device.type == "cuda")
         return synthetic_vlm_iterator(self.mcfg.vocab_size, self.tcfg.seq_length, patch=v.patch_size,
                                       temporal_patch=v.temporal_patch_size, merge=v.spatial_merge_size,
