@@ -166,7 +166,6 @@ _ACCEPTED = {
     "cuda_graph_scope": "graph capture is offered by runtime.cuda_graphs for callables, not selected by scope",
     "tokenizer_model": "tokenizers load from --hf-tokenizer-path",
     "dataloader_type": "one cyclic, resumable sampler is used",
-    "num_workers": "batches are assembled in the training process",
     "variable_seq_lengths": "pipeline stages exchange fixed-shape activations; packed rows are padded to --seq-length",
     "dist_ckpt_strictness": "unexpected or missing checkpoint keys raise",
     "detail_log_interval": "one log interval exists",

@@ -75,3 +75,57 @@ class SavableCyclicIterator:
     def load_state_dict(self, sd):
         self.epoch, self.pos = sd["epoch"], sd["pos"]
         self._perm = self._order()
+
+
+class PrefetchIterator:
+    """Runs a batch iterator in a background thread and keeps up to ``depth`` batches ready, so that tokenisation, image
+    decoding and packing overlap the training step (``--num-workers``: depth = 2 x workers; one producer thread, since the
+    iterators are stateful generators). An exception in the producer is raised in the consumer at the same position.
+    ``close()`` stops the thread; batches prepared ahead are dropped — resuming goes by the trainer's sample counter."""
+
+    _END = object()
+
+    def __init__(self, iterator, depth: int = 4):
+        import queue
+        import threading
+        self.q: "queue.Queue" = queue.Queue(maxsize=max(depth, 1))
+        self._stop = threading.Event()
+        self._it = iterator
+
+        def work():
+            try:
+                for item in self._it:
+                    while not self._stop.is_set():
+                        try:
+                            self.q.put(item, timeout=0.1)
+                            break
+                        except queue.Full:
+                            continue
+                    if self._stop.is_set():
+                        return
+                self.q.put(self._END)
+            except BaseException as e:  # noqa: BLE001 - handed to the consumer
+                self.q.put(e)
+
+        self.thread = threading.Thread(target=work, daemon=True, name="data-prefetch")
+        self.thread.start()
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        item = self.q.get()
+        if item is self._END:
+            raise StopIteration
+        if isinstance(item, BaseException):
+            raise item
+        return item
+
+    def close(self):
+        self._stop.set()
+        try:
+            while True:
+                self.q.get_nowait()
+        except Exception:  # noqa: BLE001 - queue.Empty
+            pass
+        self.thread.join(timeout=2.0)

@@ -96,6 +96,13 @@ def main(argv: Optional[List[str]] = None) -> int:
                                       dims=dims, device=device, **extra)
     _load_initial_state(trainer, args, train_cfg, family)
     data_iter = trainer.build_data_iterator(args) if hasattr(trainer, "build_data_iterator") else None
+    prefetch = None
+    collective_in_data_path = bool(getattr(args, "use_vlm_dp_balance", False) or getattr(args, "enable_full_hetero_dp", False))
+    if data_iter is not None and int(getattr(args, "num_workers", 0) or 0) > 0 and not collective_in_data_path:
+        # (data paths that exchange samples between ranks stay in the training thread: their collectives must keep
+        # their order relative to the step's)
+        from .data.samplers import PrefetchIterator
+        data_iter = prefetch = PrefetchIterator(data_iter, depth=2 * int(args.num_workers))   # host work overlaps the step
     if data_iter is None:
         st = trainer.st
         data_iter = synthetic_batch_iterator(model_cfg.vocab_size, train_cfg.seq_length, train_cfg.micro_batch_size,
@@ -104,6 +111,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     from .runtime.hooks import build_hooks
     trainer.hooks = build_hooks(args, trainer)
     trainer.train(data_iter)
+    if prefetch is not None:
+        prefetch.close()
     if train_cfg.save:
         trainer.save_checkpoint(train_cfg.save)
     if _truthy(getattr(args, "save_hf", False)) and trainer.iteration >= train_cfg.train_iters:

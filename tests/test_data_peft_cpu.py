@@ -293,3 +293,33 @@ def test_streaming_sft_iterator_and_mix_strategies(tmp_path):
     it2 = streaming_sft_batch_iterator([str(a)], tok, 64, buffer_size=2, seed=5, start_sample=2)
     first = [next(it1) for _ in range(4)]
     assert torch.equal(next(it2)["tokens"], first[2]["tokens"])               # resuming skips what was consumed
+
+
+def test_prefetch_iterator_order_errors_and_close():
+    import time
+    from loongforge_b200.data.samplers import PrefetchIterator
+
+    def gen(n, fail_at=None):
+        for i in range(n):
+            if i == fail_at:
+                raise RuntimeError("boom")
+            time.sleep(0.002)
+            yield i
+
+    assert list(PrefetchIterator(gen(20), depth=3)) == list(range(20))
+    it = PrefetchIterator(gen(10, fail_at=4), depth=2)
+    got = []
+    with pytest.raises(RuntimeError, match="boom"):
+        for x in it:
+            got.append(x)
+    assert got == [0, 1, 2, 3]                                      # the error arrives at its position
+    slow = PrefetchIterator(gen(10 ** 6), depth=2)
+    assert next(slow) == 0
+    t0 = time.perf_counter()
+    slow.close()
+    assert time.perf_counter() - t0 < 3 and not slow.thread.is_alive()
+    # work overlaps: while the consumer sleeps the producer fills the queue
+    p = PrefetchIterator(gen(8), depth=8)
+    time.sleep(0.1)
+    t0 = time.perf_counter()
+    assert [next(p) for _ in range(8)] == list(range(8)) and time.perf_counter() - t0 < 0.01
