@@ -88,3 +88,16 @@ def test_embodied_script_overrides_parse(path, monkeypatch):
     assert a.model_name in path and a.train_steps > 0
     if "lora" in os.path.basename(path):
         assert a.lora_rank > 0 and a.lora_targets == []
+
+
+def test_packaging_entry_points_resolve():
+    import importlib
+    import tomllib
+
+    with open(os.path.join(ROOT, "pyproject.toml"), "rb") as f:
+        meta = tomllib.load(f)
+    scripts = meta["project"]["scripts"]
+    assert scripts["LoongForge"] == "loongforge.train:main"               # the reference's console script
+    for target in scripts.values():
+        mod, fn = target.split(":")
+        assert callable(getattr(importlib.import_module(mod), fn)), target
