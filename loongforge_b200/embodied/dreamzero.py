@@ -138,7 +138,7 @@ class ImageTower(nn.Module):
                                      for _ in range(c.image_tower_layers)])
 
     def forward(self, image):
-        x = self.patch(image).flatten(2).transpose(1, 2)
+        x = self.patch(image.to(self.patch.weight.dtype)).flatten(2).transpose(1, 2)
         x = torch.cat([self.cls.expand(x.shape[0], -1, -1), x], dim=1)
         x = x + F.interpolate(self.pos.transpose(1, 2), size=x.shape[1], mode="linear").transpose(1, 2) \
             if x.shape[1] != self.pos.shape[1] else x + self.pos

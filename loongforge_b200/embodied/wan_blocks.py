@@ -302,12 +302,12 @@ class CausalVideoVAE(nn.Module):
 
     def encode(self, video: torch.Tensor, sample: bool = False) -> torch.Tensor:
         assert (video.shape[2] - 1) % self.temporal_factor == 0, "the codec takes 1 + 4k frames"
-        mu, logvar = self.encoder(video).chunk(2, dim=1)
+        mu, logvar = self.encoder(video.to(self.mean.dtype)).chunk(2, dim=1)   # (the buffers follow the module's dtype)
         z = mu + torch.randn_like(mu) * (0.5 * logvar.clamp(-30, 20)).exp() if sample else mu
         return (z - self.mean.view(1, -1, 1, 1, 1)) / self.std.view(1, -1, 1, 1, 1)
 
     def decode(self, z: torch.Tensor) -> torch.Tensor:
-        x = self.dec_in(z * self.std.view(1, -1, 1, 1, 1) + self.mean.view(1, -1, 1, 1, 1))
+        x = self.dec_in(z.to(self.mean.dtype) * self.std.view(1, -1, 1, 1, 1) + self.mean.view(1, -1, 1, 1, 1))
         for j, (res, up) in enumerate(zip(self.dec_res, self.dec_up)):
             i = self.ss - 1 - j
             x = up(res(x))

@@ -308,3 +308,26 @@ def test_world_models_train_sharded(name, strategy, world, tmp_path):
     res = run_distributed(_wm_dist, world, name, strategy, str(tmp_path))
     assert all(math.isfinite(r[0]) for r in res)
     assert max(abs(r[1] - res[0][1]) for r in res) < 1e-3 * max(1.0, abs(res[0][1]))
+
+
+@pytest.mark.parametrize("name", ["lingbot_va", "fastwam", "dreamzero", "cosmos3", "pi05", "groot_n1_6", "groot_n1_7", "xvla"])
+def test_policies_run_in_bf16(name):
+    """`bf16: true` casts the whole policy (codec and towers included) and the floating-point inputs: loss, gradients and
+    sampled actions stay finite."""
+    from loongforge_b200.embodied.data import SyntheticEpisodes, collate
+    from loongforge_b200.embodied.models import build_policy
+
+    world = name in ("lingbot_va", "fastwam", "dreamzero", "cosmos3")
+    a = validate(EmbodiedArgs(model_name=name, model_overrides={"size": "tiny"}, image_size=32, action_horizon=4,
+                              video_frames=(9 if name == "dreamzero" else 5) if world else 0))
+    torch.manual_seed(0)
+    p = build_policy(name, a).to(torch.bfloat16)
+    b = collate([SyntheticEpisodes(a)[i] for i in range(2)])
+    b = {k: (v.to(torch.bfloat16) if v.is_floating_point() else v) for k, v in b.items()}
+    loss = p(b)
+    loss.backward()
+    assert torch.isfinite(loss.detach().float())
+    grads = [q.grad for q in p.parameters() if q.grad is not None]
+    assert grads and all(torch.isfinite(g.float()).all() for g in grads)
+    act = p.predict_action(b, steps=2)
+    assert act.shape == (2, 4, a.action_dim) and torch.isfinite(act.float()).all()
