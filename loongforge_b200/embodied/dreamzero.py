@@ -33,8 +33,8 @@ import torch.nn.functional as F
 
 from ..models.diffusion import RMSNorm, _Linear
 from .groot import CategoryLinear, CategoryMLP, _sincos
-from .wan_blocks import (Attention, CausalVideoVAE, DiTBlock, FlowSchedule, Head, TextEncoder, TimeEmbedder, grid_positions,
-                         masked_attention, rope_angles, video_from_batch)
+from .wan_blocks import (Attention, CausalVideoVAE, DiTBlock, FlowSchedule, Head, SegmentMask, TextEncoder, TimeEmbedder,
+                         contiguous_runs, grid_positions, masked_attention, rope_angles, video_from_batch)
 
 
 @dataclasses.dataclass
@@ -75,6 +75,7 @@ class DreamZeroConfig:
     tune_diffusion_model: bool = True
     tune_projector: bool = True
     recompute: bool = False
+    segment_attention: bool = True        # run-by-run evaluation of the block-causal mask (no [L, L] mask)
 
     @classmethod
     def tiny(cls, **kw) -> "DreamZeroConfig":
@@ -90,11 +91,11 @@ class DreamZeroConfig:
 CLEAN, NOISY, ACT, STATE = 0, 1, 2, 3
 
 
-def block_causal_mask(frames: int, per_frame: int, nfb: int, n_act: int, apb: int, n_state: int, spb: int,
-                      teacher_forcing: bool, local_blocks: int = -1, device=None, register_block_offset: int = 0) -> torch.Tensor:
-    """``[L, L]`` boolean mask for ``[clean video (teacher forcing only) | video | actions | states]``. The registers
-    belong to blocks ``register_block_offset, register_block_offset + 1, ...`` (roll-out: only the block being denoised
-    has registers in the sequence)."""
+def block_token_attributes(frames: int, per_frame: int, nfb: int, n_act: int, apb: int, n_state: int, spb: int,
+                           teacher_forcing: bool, device=None, register_block_offset: int = 0):
+    """Per token of ``[clean video (teacher forcing only) | video | actions | states]``: kind, block (frame 0 = -1; the
+    registers belong to blocks ``register_block_offset, ...``) and, for state tokens, a number of their own (they attend
+    themselves only)."""
     fb = (torch.arange(frames, device=device) - 1).div(nfb, rounding_mode="floor")   # frame 0 -> block -1
     vb = fb.repeat_interleave(per_frame)
     kinds, blocks = [], []
@@ -106,19 +107,38 @@ def block_causal_mask(frames: int, per_frame: int, nfb: int, n_act: int, apb: in
     kinds += [torch.full_like(ab, ACT), torch.full_like(sb, STATE)]
     blocks += [ab, sb]
     kind, blk = torch.cat(kinds), torch.cat(blocks)
+    own = torch.where(kind == STATE, torch.arange(kind.numel(), device=device), torch.full_like(kind, -1))
+    return kind, blk, own
+
+
+def block_causal_rule(kind, blk, own, teacher_forcing: bool, local_blocks: int = -1) -> torch.Tensor:
+    """The attention rule on token attributes (or on one representative per run of equal attributes)."""
     kq, kk, bq, bk = kind[:, None], kind[None, :], blk[:, None], blk[None, :]
     hist = CLEAN if teacher_forcing else NOISY                    # where a block's history lives
     in_window = (bk == -1) | (bq - bk <= local_blocks) if local_blocks > 0 else torch.ones_like(bq == bk)
     history = (kk == hist) & (bk < bq) & in_window
     same = bk == bq
-    m = torch.eye(kind.numel(), dtype=torch.bool, device=device)
+    m = (own[:, None] == own[None, :]) & (own[:, None] >= 0)      # a state token sees itself
     if teacher_forcing:
-        m |= (kq == CLEAN) & (kk == CLEAN) & (bk <= bq) & in_window
-    m |= (kq == NOISY) & (kk == NOISY) & same                     # a frame / block sees all of itself (observation too)
+        m = m | ((kq == CLEAN) & (kk == CLEAN) & (bk <= bq) & in_window)
+    m = m | ((kq == NOISY) & (kk == NOISY) & same)                # a frame / block sees all of itself (observation too)
     generated = (kq == NOISY) & (bq >= 0)
-    m |= generated & (history | (same & ((kk == NOISY) | (kk == ACT) | (kk == STATE))))
-    m |= (kq == ACT) & (history | (same & ((kk == NOISY) | (kk == ACT) | (kk == STATE))))
+    m = m | (generated & (history | (same & ((kk == NOISY) | (kk == ACT) | (kk == STATE)))))
+    m = m | ((kq == ACT) & (history | (same & ((kk == NOISY) | (kk == ACT) | (kk == STATE)))))
     return m
+
+
+def block_causal_mask(frames: int, per_frame: int, nfb: int, n_act: int, apb: int, n_state: int, spb: int,
+                      teacher_forcing: bool, local_blocks: int = -1, device=None, register_block_offset: int = 0,
+                      segments: bool = False):
+    """``[L, L]`` boolean mask, or with ``segments`` the same mask in run form (``wan_blocks.SegmentMask``): it is constant on
+    runs of equal (kind, block), so attention can be evaluated run by run without the dense mask."""
+    kind, blk, own = block_token_attributes(frames, per_frame, nfb, n_act, apb, n_state, spb, teacher_forcing, device,
+                                            register_block_offset)
+    if not segments:
+        return block_causal_rule(kind, blk, own, teacher_forcing, local_blocks)
+    starts, ends, rep = contiguous_runs(kind, blk, own)
+    return SegmentMask(starts, ends, block_causal_rule(kind[rep], blk[rep], own[rep], teacher_forcing, local_blocks))
 
 
 class ImageTower(nn.Module):
@@ -263,7 +283,8 @@ class CausalWanModel(nn.Module):
         angles = rope_angles(torch.cat(poss), c.hidden_size // c.num_heads)
         temb, mod = self.time(t_all)
         mask = block_causal_mask(f, per_frame, c.num_frame_per_block, na, c.num_action_per_block, ns,
-                                 c.num_state_per_block, tf, c.local_attn_blocks, dev, register_block_offset)
+                                 c.num_state_per_block, tf, c.local_attn_blocks, dev, register_block_offset,
+                                 segments=c.segment_attention)
         ctx = (self.text_embedding(text_emb.to(x.dtype)), self.img_emb(image_tokens.to(x.dtype)) if image_tokens is not None else None)
         for blk in self.blocks:
             if c.recompute and torch.is_grad_enabled():

@@ -31,7 +31,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..models.diffusion import _Linear
-from .wan_blocks import (CausalVideoVAE, DiTBlock, Head, TextEncoder, TimeEmbedder, grid_positions, masked_attention,
+from .wan_blocks import (CausalVideoVAE, DiTBlock, Head, SegmentMask, TextEncoder, TimeEmbedder, grid_positions, masked_attention,
                          rope_angles, video_from_batch)
 
 
@@ -69,6 +69,7 @@ class FastWAMConfig:
     vae_base: int = 32
     freeze_text_encoder: bool = True
     recompute: bool = False
+    segment_attention: bool = True        # evaluate the joint mask run by run (no [L, L] mask)
 
     @classmethod
     def tiny(cls, **kw) -> "FastWAMConfig":
@@ -111,6 +112,15 @@ def mot_mask(variant: str, frames: int, per_frame: int, n_action: int, mode: str
     m[Lv:, Lv:] = True
     m[Lv:, :(Lv if variant == "joint" else per_frame)] = True
     return m
+
+
+def mot_segment_mask(variant: str, frames: int, per_frame: int, n_action: int, mode: str, device=None) -> SegmentMask:
+    """``mot_mask`` in run form: the mask is constant on frames and on the action block, so the rule evaluated with one token
+    per frame and one action token is the run-level mask."""
+    n_video = (2 if variant == "idm" else 1) * frames
+    starts = [f * per_frame for f in range(n_video)] + [n_video * per_frame]
+    ends = starts[1:] + [n_video * per_frame + n_action]
+    return SegmentMask(starts, ends, mot_mask(variant, frames, 1, 1, mode, device))
 
 
 class _Expert(nn.Module):
@@ -300,7 +310,8 @@ class FastWAMPolicy(nn.Module):
             xc, modc, _, angc, _ = m.embed_video(cond, t_c)
             video_parts.append((xc, modc, angc))
         streams = self._streams(text, text_mask, batch.get("state"), video_parts, m.embed_action(noisy_a, t_a))
-        mask = mot_mask(c.variant, grid[0], grid[1] * grid[2], act.shape[1], c.video_mask_mode, dev)
+        mask = (mot_segment_mask if c.segment_attention else mot_mask)(
+            c.variant, grid[0], grid[1] * grid[2], act.shape[1], c.video_mask_mode, dev)
         out = m.layers(streams, mask)
         pred_v = m.unpatchify(m.video_head(out[0], tembv), grid)[:, :, 1:]
         tgt_v = (noise_v - lat)[:, :, 1:]
@@ -365,7 +376,8 @@ class FastWAMPolicy(nn.Module):
             xv, modv, tembv, angv, grid = m.embed_video(lat, (sig_v[i] * n).expand(B))
             parts = [(xv, modv, angv)] * (2 if c.variant == "idm" else 1)  # idm: the evolving video is its own condition
             streams = self._streams(text, text_mask, state, parts, m.embed_action(a, (sig_a[i] * n).expand(B)))
-            mask = mot_mask(c.variant, grid[0], grid[1] * grid[2], c.action_horizon, c.video_mask_mode, dev)
+            mask = (mot_segment_mask if c.segment_attention else mot_mask)(
+                c.variant, grid[0], grid[1] * grid[2], c.action_horizon, c.video_mask_mode, dev)
             out = m.layers(streams, mask)
             v = m.unpatchify(m.video_head(out[0], tembv), grid)
             lat = lat + v * (sig_v[i + 1] - sig_v[i])

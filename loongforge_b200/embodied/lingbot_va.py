@@ -30,8 +30,8 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..models.diffusion import _Linear
-from .wan_blocks import (CausalVideoVAE, DiTBlock, FlowSchedule, TextEncoder, TimeEmbedder, action_positions,
-                         grid_positions, rope_angles, video_from_batch)
+from .wan_blocks import (CausalVideoVAE, DiTBlock, FlowSchedule, SegmentMask, TextEncoder, TimeEmbedder, action_positions,
+                         contiguous_runs, grid_positions, rope_angles, video_from_batch)
 
 
 @dataclasses.dataclass
@@ -65,6 +65,7 @@ class LingBotVAConfig:
     vae_base: int = 32
     freeze_text_encoder: bool = True
     recompute: bool = False
+    segment_attention: bool = True  # evaluate the block-constant mask run by run (no [L, L] mask); False: dense boolean mask
 
     @classmethod
     def tiny(cls, **kw) -> "LingBotVAConfig":
@@ -150,7 +151,11 @@ class LingBotVAModel(nn.Module):
         angles = rope_angles(torch.cat([p.pos for p in parts]), c.hidden_size // c.num_heads)
         order = torch.cat([p.order for p in parts])
         noisy = torch.cat([torch.full_like(p.order, p.noisy, dtype=torch.bool) for p in parts])
-        mask = teacher_forcing_mask(order, noisy, window)
+        if c.segment_attention:  # the mask is constant on (part, order) runs: one un-masked attention per run
+            starts, ends, rep = contiguous_runs(order, noisy.long())
+            mask = SegmentMask(starts, ends, teacher_forcing_mask(order[rep], noisy[rep], window))
+        else:
+            mask = teacher_forcing_mask(order, noisy, window)
         temb, mod = [], []
         for p in parts:
             e, m = (self.time_action if p.action else self.time)(p.t)

@@ -68,6 +68,8 @@ def apply_rope(x: torch.Tensor, angles: Optional[torch.Tensor]) -> torch.Tensor:
 def masked_attention(q, k, v, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q ``[B, Lq, H, d]``, k / v ``[B, Lk, Hk, d]`` (Hk divides H) -> ``[B, Lq, H*d]``. ``mask`` is boolean (True = may
     attend), ``[Lq, Lk]``, ``[B, Lk]`` (key padding) or ``[B, 1|H, Lq, Lk]``."""
+    if isinstance(mask, SegmentMask):
+        return segment_attention(q, k, v, mask.starts, mask.ends, mask.seg_mask)
     B, Lq, H, d = q.shape
     if k.shape[2] != H:
         rep = H // k.shape[2]
@@ -79,6 +81,67 @@ def masked_attention(q, k, v, mask: Optional[torch.Tensor] = None) -> torch.Tens
             mask = mask[None, None]
     o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=mask)
     return o.transpose(1, 2).reshape(B, Lq, H * d)
+
+
+def contiguous_runs(*attrs: torch.Tensor):
+    """Tokens with equal attributes in a row form a run. Returns (starts, ends, representative token of each run)."""
+    a = torch.stack([x.reshape(-1).to(torch.float64) for x in attrs], dim=-1)
+    change = torch.ones(a.shape[0], dtype=torch.bool, device=a.device)
+    change[1:] = (a[1:] != a[:-1]).any(-1)
+    starts = torch.nonzero(change).flatten()
+    ends = torch.cat([starts[1:], torch.tensor([a.shape[0]], device=a.device)])
+    return starts.tolist(), ends.tolist(), starts
+
+
+def segment_attention(q, k, v, starts, ends, seg_mask: torch.Tensor) -> torch.Tensor:
+    """Attention under a mask that is constant on blocks: query run i attends ALL tokens of the key runs j with
+    ``seg_mask[i, j]`` and nothing else. Every query run is one un-masked attention call over the concatenation of its
+    key runs (adjacent ones are taken as one slice), so no ``[L, L]`` mask or score matrix exists and cost follows the
+    allowed area only. q ``[B, L, H, d]``, k / v ``[B, L, Hk, d]`` -> ``[B, L, H*d]``. Query runs with the same key set are
+    batched into one call."""
+    B, L, H, d = q.shape
+    if k.shape[2] != H:
+        rep = H // k.shape[2]
+        k, v = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
+    out = q.new_empty(B, L, H * d)
+    rows = seg_mask.tolist()
+    groups: dict = {}
+    for i, row in enumerate(rows):                      # runs that see the same keys share one call
+        groups.setdefault(tuple(j for j, ok in enumerate(row) if ok), []).append(i)
+    for keys, qs in groups.items():
+        assert keys, "a run of queries attends nothing"
+        spans, cur = [], None                            # merge adjacent key runs into slices
+        for j in keys:
+            if cur is not None and starts[j] == cur[1]:
+                cur[1] = ends[j]
+            else:
+                cur = [starts[j], ends[j]]
+                spans.append(cur)
+        kk = k[:, spans[0][0]:spans[0][1]] if len(spans) == 1 else torch.cat([k[:, a:b] for a, b in spans], dim=1)
+        vv = v[:, spans[0][0]:spans[0][1]] if len(spans) == 1 else torch.cat([v[:, a:b] for a, b in spans], dim=1)
+        qq = torch.cat([q[:, starts[i]:ends[i]] for i in qs], dim=1) if len(qs) > 1 else q[:, starts[qs[0]]:ends[qs[0]]]
+        o = F.scaled_dot_product_attention(qq.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2)).transpose(1, 2)
+        o = o.reshape(B, -1, H * d)
+        at = 0
+        for i in qs:
+            n = ends[i] - starts[i]
+            out[:, starts[i]:ends[i]] = o[:, at:at + n]
+            at += n
+    return out
+
+
+class SegmentMask:
+    """A block-constant mask in run form; ``Attention`` / ``masked_attention`` callers pass it instead of a dense mask."""
+
+    def __init__(self, starts, ends, seg_mask: torch.Tensor):
+        self.starts, self.ends, self.seg_mask = starts, ends, seg_mask
+
+    def dense(self, device=None) -> torch.Tensor:
+        L = self.ends[-1]
+        owner = torch.zeros(L, dtype=torch.long)
+        for i, (a, b) in enumerate(zip(self.starts, self.ends)):
+            owner[a:b] = i
+        return self.seg_mask.cpu()[owner][:, owner].to(device)
 
 
 class Attention(nn.Module):

@@ -331,3 +331,51 @@ def test_policies_run_in_bf16(name):
     assert grads and all(torch.isfinite(g.float()).all() for g in grads)
     act = p.predict_action(b, steps=2)
     assert act.shape == (2, 4, a.action_dim) and torch.isfinite(act.float()).all()
+
+
+def test_segment_attention_equals_dense_mask():
+    """Block-constant masks in run form: same mask, same attention output (grouped-query heads included)."""
+    from loongforge_b200.embodied.dreamzero import block_causal_mask
+    from loongforge_b200.embodied.fastwam import mot_mask, mot_segment_mask
+    from loongforge_b200.embodied.lingbot_va import teacher_forcing_mask
+    from loongforge_b200.embodied.wan_blocks import SegmentMask, contiguous_runs, masked_attention
+
+    torch.manual_seed(0)
+    order = torch.tensor([0, 0, 0, 2, 2, 2, 1, 1, 3, 3, 0, 0, 0, 2, 2, 2, 1, 1, 3, 3])
+    noisy = torch.tensor([1] * 10 + [0] * 10, dtype=torch.bool)
+    st, en, rep = contiguous_runs(order, noisy.long())
+    assert st == [0, 3, 6, 8, 10, 13, 16, 18] and en[-1] == 20
+    cases = [(SegmentMask(st, en, teacher_forcing_mask(order[rep], noisy[rep], 2)), teacher_forcing_mask(order, noisy, 2))]
+    for tf in (True, False):
+        for off in (0, 1):
+            a = (5, 3, 2, 4, 2, 2, 1, tf, 1 if tf else -1, None, off)
+            cases.append((block_causal_mask(*a, segments=True), block_causal_mask(*a)))
+    for variant, mode in (("fastwam", "first_frame_causal"), ("joint", "per_frame_causal"), ("idm", "bidirectional"),
+                          ("idm", "per_frame_causal")):
+        cases.append((mot_segment_mask(variant, 3, 4, 5, mode), mot_mask(variant, 3, 4, 5, mode)))
+    for seg, dense in cases:
+        assert isinstance(seg, SegmentMask) and torch.equal(seg.dense(), dense)
+        L = dense.shape[0]
+        q, k, v = torch.randn(2, L, 4, 8), torch.randn(2, L, 2, 8), torch.randn(2, L, 2, 8)
+        assert torch.allclose(masked_attention(q, k, v, seg), masked_attention(q, k, v, dense), atol=1e-5)
+    q = torch.randn(1, 20, 2, 8, requires_grad=True)
+    masked_attention(q, q, q, cases[0][0]).sum().backward()
+    g = q.grad.clone()
+    q.grad = None
+    masked_attention(q, q, q, cases[0][1]).sum().backward()
+    assert torch.allclose(g, q.grad, atol=1e-5)
+
+
+@pytest.mark.parametrize("name", ["lingbot_va", "fastwam", "dreamzero"])
+def test_policies_give_the_same_loss_with_segment_attention(name):
+    import importlib
+    mod = importlib.import_module(f"loongforge_b200.embodied.{name}")
+    cfg_cls = {"lingbot_va": "LingBotVAConfig", "fastwam": "FastWAMConfig", "dreamzero": "DreamZeroConfig"}[name]
+    pol_cls = {"lingbot_va": "LingBotVAPolicy", "fastwam": "FastWAMPolicy", "dreamzero": "DreamZeroPolicy"}[name]
+    losses = []
+    for seg in (True, False):
+        torch.manual_seed(0)
+        p = getattr(mod, pol_cls)(getattr(mod, cfg_cls).tiny(action_dim=7, segment_attention=seg))
+        torch.manual_seed(1)
+        losses.append(float(p(_batch())))
+    assert abs(losses[0] - losses[1]) < 1e-5 * max(1.0, abs(losses[1])), losses
