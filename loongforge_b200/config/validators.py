@@ -51,6 +51,9 @@ def validate(args, cfg, tc, dims) -> None:
         raise ValueError("SFT needs --sft-dataset / --data-path (or --mock-data)")
     if dims.vpp and dims.vpp > 1 and cfg.num_layers % (dims.pp * dims.vpp) and not tc.custom_pipeline_layers:
         raise ValueError("num_layers must divide by pp x virtual stages")
+    if dims.pp > 1 and cfg.num_layers % dims.pp and not tc.custom_pipeline_layers \
+            and not getattr(args, "pipeline_model_parallel_layout", None):
+        raise ValueError(f"{cfg.num_layers} layers do not divide by pipeline size {dims.pp}: give --custom-pipeline-layers")
     _validate_sft(args, tc)
     _validate_attention_variants(args, cfg, tc, dims)
     _validate_moe(args, cfg, tc, dims)
