@@ -29,7 +29,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..models.diffusion import RMSNorm, _Linear, timestep_embedding
-from .wan_blocks import CausalVideoVAE, masked_attention, video_from_batch
+from .wan_blocks import CausalVideoVAE, SegmentMask, contiguous_runs, masked_attention, video_from_batch
 from .xvla import DomainAwareLinear
 
 
@@ -67,6 +67,7 @@ class Cosmos3Config:
     vae_base: int = 32
     vae_spatial_stages: int = 3
     recompute: bool = False
+    segment_attention: bool = True       # evaluate the packed mask run by run (no [L, L] mask)
 
     @classmethod
     def tiny(cls, **kw) -> "Cosmos3Config":
@@ -146,6 +147,20 @@ def packed_attention_mask(seq: PackedSequence, temporal_causal: bool) -> torch.T
     if temporal_causal:
         gen = gen & (k_und | (seq.frame[None, :] <= seq.frame[:, None]))
     return m | gen
+
+
+def packed_segment_mask(seq: PackedSequence, temporal_causal: bool) -> SegmentMask:
+    """``packed_attention_mask`` in run form: runs of equal (sample, pathway, frame); a text run attends itself causally,
+    everything else is constant on runs, so attention is evaluated run by run without the ``[L, L]`` mask."""
+    path = seq.pathway
+    starts, ends, rep = contiguous_runs(seq.sample, path, seq.frame)
+    sample, und, frame = seq.sample[rep], path[rep] == UND, seq.frame[rep]
+    same = sample[:, None] == sample[None, :]
+    m = same & und[:, None] & und[None, :] & (rep[None, :] <= rep[:, None])
+    gen = same & ~und[:, None]
+    if temporal_causal:
+        gen = gen & (und[None, :] | (frame[None, :] <= frame[:, None]))
+    return SegmentMask(starts, ends, m | gen, causal=und.tolist())
 
 
 def mrope_angles(pos: torch.Tensor, head_dim: int, theta: float, section: Tuple[int, int, int]) -> torch.Tensor:
@@ -268,7 +283,7 @@ class Cosmos3Network(nn.Module):
         gen_idx = torch.cat([seq.vision_index, seq.action_index]).sort().values
         und_idx = seq.text_index
         angles = mrope_angles(seq.position, c.head_dim, c.rope_theta, c.mrope_section)
-        mask = packed_attention_mask(seq, c.video_temporal_causal)
+        mask = (packed_segment_mask if c.segment_attention else packed_attention_mask)(seq, c.video_temporal_causal)
         for layer in self.layers:
             if c.recompute and torch.is_grad_enabled():
                 x = torch.utils.checkpoint.checkpoint(layer, x, und_idx, gen_idx, angles, mask, use_reentrant=False)

@@ -69,7 +69,7 @@ def masked_attention(q, k, v, mask: Optional[torch.Tensor] = None) -> torch.Tens
     """q ``[B, Lq, H, d]``, k / v ``[B, Lk, Hk, d]`` (Hk divides H) -> ``[B, Lq, H*d]``. ``mask`` is boolean (True = may
     attend), ``[Lq, Lk]``, ``[B, Lk]`` (key padding) or ``[B, 1|H, Lq, Lk]``."""
     if isinstance(mask, SegmentMask):
-        return segment_attention(q, k, v, mask.starts, mask.ends, mask.seg_mask)
+        return segment_attention(q, k, v, mask.starts, mask.ends, mask.seg_mask, mask.causal)
     B, Lq, H, d = q.shape
     if k.shape[2] != H:
         rep = H // k.shape[2]
@@ -93,12 +93,13 @@ def contiguous_runs(*attrs: torch.Tensor):
     return starts.tolist(), ends.tolist(), starts
 
 
-def segment_attention(q, k, v, starts, ends, seg_mask: torch.Tensor) -> torch.Tensor:
+def segment_attention(q, k, v, starts, ends, seg_mask: torch.Tensor, causal=None) -> torch.Tensor:
     """Attention under a mask that is constant on blocks: query run i attends ALL tokens of the key runs j with
     ``seg_mask[i, j]`` and nothing else. Every query run is one un-masked attention call over the concatenation of its
     key runs (adjacent ones are taken as one slice), so no ``[L, L]`` mask or score matrix exists and cost follows the
     allowed area only. q ``[B, L, H, d]``, k / v ``[B, L, Hk, d]`` -> ``[B, L, H*d]``. Query runs with the same key set are
-    batched into one call."""
+    batched into one call. A run i with ``causal[i]`` attends its own tokens causally (text inside a packed row): it is one
+    call of its own with a ``[run, keys]`` mask."""
     B, L, H, d = q.shape
     if k.shape[2] != H:
         rep = H // k.shape[2]
@@ -107,8 +108,10 @@ def segment_attention(q, k, v, starts, ends, seg_mask: torch.Tensor) -> torch.Te
     rows = seg_mask.tolist()
     groups: dict = {}
     for i, row in enumerate(rows):                      # runs that see the same keys share one call
-        groups.setdefault(tuple(j for j, ok in enumerate(row) if ok), []).append(i)
-    for keys, qs in groups.items():
+        keys = tuple(j for j, ok in enumerate(row) if ok)
+        own_causal = bool(causal is not None and causal[i] and row[i])
+        groups.setdefault((keys, i if own_causal else -1), []).append(i)
+    for (keys, own), qs in groups.items():
         assert keys, "a run of queries attends nothing"
         spans, cur = [], None                            # merge adjacent key runs into slices
         for j in keys:
@@ -120,7 +123,12 @@ def segment_attention(q, k, v, starts, ends, seg_mask: torch.Tensor) -> torch.Te
         kk = k[:, spans[0][0]:spans[0][1]] if len(spans) == 1 else torch.cat([k[:, a:b] for a, b in spans], dim=1)
         vv = v[:, spans[0][0]:spans[0][1]] if len(spans) == 1 else torch.cat([v[:, a:b] for a, b in spans], dim=1)
         qq = torch.cat([q[:, starts[i]:ends[i]] for i in qs], dim=1) if len(qs) > 1 else q[:, starts[qs[0]]:ends[qs[0]]]
-        o = F.scaled_dot_product_attention(qq.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2)).transpose(1, 2)
+        am = None
+        if own >= 0:                                     # all of the other runs, the lower triangle of its own
+            n = ends[own] - starts[own]
+            am = torch.cat([torch.ones(n, ends[j] - starts[j], dtype=torch.bool, device=q.device) if j != own else
+                            torch.ones(n, n, dtype=torch.bool, device=q.device).tril() for j in keys], dim=1)
+        o = F.scaled_dot_product_attention(qq.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), attn_mask=am).transpose(1, 2)
         o = o.reshape(B, -1, H * d)
         at = 0
         for i in qs:
@@ -133,15 +141,20 @@ def segment_attention(q, k, v, starts, ends, seg_mask: torch.Tensor) -> torch.Te
 class SegmentMask:
     """A block-constant mask in run form; ``Attention`` / ``masked_attention`` callers pass it instead of a dense mask."""
 
-    def __init__(self, starts, ends, seg_mask: torch.Tensor):
-        self.starts, self.ends, self.seg_mask = starts, ends, seg_mask
+    def __init__(self, starts, ends, seg_mask: torch.Tensor, causal=None):
+        self.starts, self.ends, self.seg_mask, self.causal = starts, ends, seg_mask, causal
 
     def dense(self, device=None) -> torch.Tensor:
         L = self.ends[-1]
         owner = torch.zeros(L, dtype=torch.long)
         for i, (a, b) in enumerate(zip(self.starts, self.ends)):
             owner[a:b] = i
-        return self.seg_mask.cpu()[owner][:, owner].to(device)
+        m = self.seg_mask.cpu()[owner][:, owner]
+        if self.causal is not None:
+            idx = torch.arange(L)
+            own_causal = torch.tensor([bool(c) for c in self.causal])[owner]
+            m = m & ~(own_causal[:, None] & (owner[:, None] == owner[None, :]) & (idx[None, :] > idx[:, None]))
+        return m.to(device)
 
 
 class Attention(nn.Module):

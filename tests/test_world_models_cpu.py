@@ -353,6 +353,10 @@ def test_segment_attention_equals_dense_mask():
     for variant, mode in (("fastwam", "first_frame_causal"), ("joint", "per_frame_causal"), ("idm", "bidirectional"),
                           ("idm", "per_frame_causal")):
         cases.append((mot_segment_mask(variant, 3, 4, 5, mode), mot_mask(variant, 3, 4, 5, mode)))
+    from loongforge_b200.embodied.cosmos3 import pack_samples, packed_attention_mask, packed_segment_mask
+    seq = pack_samples([torch.arange(1, 6), torch.arange(1, 4)], [(3, 2, 2), (2, 2, 2)], [4, 2])
+    for tc in (True, False):
+        cases.append((packed_segment_mask(seq, tc), packed_attention_mask(seq, tc)))
     for seg, dense in cases:
         assert isinstance(seg, SegmentMask) and torch.equal(seg.dense(), dense)
         L = dense.shape[0]
@@ -366,12 +370,14 @@ def test_segment_attention_equals_dense_mask():
     assert torch.allclose(g, q.grad, atol=1e-5)
 
 
-@pytest.mark.parametrize("name", ["lingbot_va", "fastwam", "dreamzero"])
+@pytest.mark.parametrize("name", ["lingbot_va", "fastwam", "dreamzero", "cosmos3"])
 def test_policies_give_the_same_loss_with_segment_attention(name):
     import importlib
     mod = importlib.import_module(f"loongforge_b200.embodied.{name}")
-    cfg_cls = {"lingbot_va": "LingBotVAConfig", "fastwam": "FastWAMConfig", "dreamzero": "DreamZeroConfig"}[name]
-    pol_cls = {"lingbot_va": "LingBotVAPolicy", "fastwam": "FastWAMPolicy", "dreamzero": "DreamZeroPolicy"}[name]
+    cfg_cls = {"lingbot_va": "LingBotVAConfig", "fastwam": "FastWAMConfig", "dreamzero": "DreamZeroConfig",
+               "cosmos3": "Cosmos3Config"}[name]
+    pol_cls = {"lingbot_va": "LingBotVAPolicy", "fastwam": "FastWAMPolicy", "dreamzero": "DreamZeroPolicy",
+               "cosmos3": "Cosmos3Policy"}[name]
     losses = []
     for seg in (True, False):
         torch.manual_seed(0)
