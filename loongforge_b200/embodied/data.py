@@ -6,7 +6,9 @@ camera-0 frames of the coming steps (``video [T, 3, H, W]``), which the world-mo
 
 * ``SyntheticEpisodes``  — deterministic random episodes (benchmarks, tests);
 * ``NpzEpisodes``        — a directory of ``episode_*.npz`` files (arrays ``images [T, cams, C, H, W]``, ``state``,
-  ``actions``, optional ``task``), the layout HDF5 exports convert to (reference: hdf5_dataset.py);
+  ``actions``, optional ``task``);
+* ``hdf5_data.HDF5Episodes`` — bimanual end-effector episodes in HDF5 files, re-sampled into two-second action windows
+  (reference: hdf5_dataset.py);
 * ``LeRobotParquet``     — LeRobot-style ``data/chunk-*/episode_*.parquet`` tables with ``observation.state``,
   ``action``, ``episode_index``, ``task_index`` columns plus ``meta/tasks.jsonl`` (reference: lerobot_dataset.py).
 
@@ -339,8 +341,11 @@ def _base_dataset(args) -> Dataset:
         return MixtureDataset(sets, weights, seed=args.seed, length=getattr(args, "mixture_epoch_length", None))
     if args.dataset_type == "synthetic":
         return SyntheticEpisodes(args)
-    if args.dataset_type in ("npz_episodes", "hdf5"):
+    if args.dataset_type == "npz_episodes":
         return NpzEpisodes(args, args.dataset_path)
+    if args.dataset_type == "hdf5":
+        from .hdf5_data import HDF5Episodes
+        return HDF5Episodes(args, args.dataset_path)
     if args.dataset_type == "lerobot":
         return LeRobotParquet(args, args.dataset_path)
     raise ValueError(args.dataset_type)
@@ -369,11 +374,41 @@ def build_dataset(args, training: bool = True) -> Dataset:
     return TransformedDataset(ds, T.build_transforms(args, {k: v for k, v in stats.items() if v}, training))
 
 
-class ResumableLoader:
-    """DataLoader + DistributedSampler whose position (epoch, batches consumed) can be saved and restored."""
+class BlockShardSampler(torch.utils.data.Sampler):
+    """The epoch's (shuffled) order is cut into batches first and whole batches go to the ranks in turn: the ranks' k-th
+    batches together are ``world`` consecutive batches of the one-process order, so a run on N ranks with batch B sees the
+    batches a one-process run with batch B sees, N at a time (``DistributedSampler`` deals single samples instead).
+    (reference: loongforge/embodied/data/datasets/sampler_builder.py:47-112)"""
 
-    def __init__(self, dataset: Dataset, batch_size: int, rank: int, world: int, seed: int, num_workers: int = 0):
-        self.sampler = DistributedSampler(dataset, num_replicas=world, rank=rank, shuffle=True, seed=seed, drop_last=True)
+    def __init__(self, dataset, batch_size: int, num_replicas: int, rank: int, shuffle: bool = True, seed: int = 0):
+        self.n, self.b, self.world, self.rank, self.shuffle, self.seed, self.epoch = len(dataset), batch_size, num_replicas, rank, shuffle, seed, 0
+
+    def set_epoch(self, epoch: int) -> None:
+        self.epoch = epoch
+
+    def __len__(self) -> int:                                 # only rounds in which every rank gets a whole batch
+        return self.n // (self.b * self.world) * self.b
+
+    def __iter__(self):
+        order = (torch.randperm(self.n, generator=torch.Generator().manual_seed(self.seed + self.epoch)).tolist()
+                 if self.shuffle else list(range(self.n)))
+        for r in range(self.n // (self.b * self.world)):
+            at = (r * self.world + self.rank) * self.b
+            yield from order[at:at + self.b]
+
+
+class ResumableLoader:
+    """DataLoader + sampler whose position (epoch, batches consumed) can be saved and restored. ``sampler``:
+    ``distributed`` (samples dealt to ranks one by one) or ``block_shard`` (whole batches dealt to ranks)."""
+
+    def __init__(self, dataset: Dataset, batch_size: int, rank: int, world: int, seed: int, num_workers: int = 0,
+                 sampler: str = "distributed"):
+        if sampler == "block_shard":
+            self.sampler = BlockShardSampler(dataset, batch_size, world, rank, shuffle=True, seed=seed)
+        elif sampler == "distributed":
+            self.sampler = DistributedSampler(dataset, num_replicas=world, rank=rank, shuffle=True, seed=seed, drop_last=True)
+        else:
+            raise ValueError(f"unknown sampler {sampler!r} (distributed | block_shard)")
         self.loader = DataLoader(dataset, batch_size=batch_size, sampler=self.sampler, collate_fn=collate,
                                  num_workers=num_workers, drop_last=True, pin_memory=torch.cuda.is_available())
         self.epoch, self.consumed = 0, 0

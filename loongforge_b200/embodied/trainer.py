@@ -118,7 +118,8 @@ class BaseTrainer:
         self.optimizer = build_optimizer(self.model, a, ctx.world)
         self.scheduler = LRScheduler(self.optimizer, a.lr_scheduler, a.lr, a.min_lr, a.warmup_steps,
                                      a.lr_decay_steps or a.train_steps, num_cycles=a.lr_num_cycles, power=a.lr_power)
-        self.loader = ResumableLoader(build_dataset(a), a.per_device_batch_size, ctx.rank, ctx.world, a.seed, a.num_workers)
+        self.loader = ResumableLoader(build_dataset(a), a.per_device_batch_size, ctx.rank, ctx.world, a.seed, a.num_workers,
+                                      sampler=a.sampler)
         self.logger = MetricLogger(a.output_dir, ctx.is_main, a.train_steps, tensorboard=a.tensorboard,
                                    wandb_project=a.wandb_project, run_name=a.run_name)
         self.timers = StageTimers(a.log_stage_times)

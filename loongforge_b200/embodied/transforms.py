@@ -113,10 +113,40 @@ def save_stats(stats: dict, path: str) -> None:
         json.dump(stats, f)
 
 
+def merge_stats(parts: Sequence[dict]) -> dict:
+    """Statistics of the union from statistics of the parts (per episode, per data set): for every feature the pooled mean
+    and standard deviation (weighted by ``count``; the variance of a union is the weighted mean of the parts' variances
+    plus the spread of their means), the overall min / max, and for the quantiles the outermost of the parts' values (an
+    upper bound of the spread: exact quantiles cannot be merged). (reference: loongforge/embodied/data/datasets/
+    compute_stats.py:32-92)"""
+    out = {}
+    for key in sorted({k for p in parts for k in p}):
+        have = [p[key] for p in parts if key in p]
+        n = np.array([float(np.asarray(h.get("count", [1])).reshape(-1)[0]) for h in have])
+        mean = np.stack([np.asarray(h["mean"], dtype=np.float64) for h in have])
+        var = np.stack([np.asarray(h["std"], dtype=np.float64) ** 2 for h in have])
+        w = n.reshape(-1, *([1] * (mean.ndim - 1))) / n.sum()
+        pooled = (mean * w).sum(0)
+        merged = {"mean": pooled.tolist(), "std": np.sqrt(((var + (mean - pooled) ** 2) * w).sum(0)).tolist(),
+                  "min": np.min(np.stack([np.asarray(h["min"], dtype=np.float64) for h in have]), 0).tolist(),
+                  "max": np.max(np.stack([np.asarray(h["max"], dtype=np.float64) for h in have]), 0).tolist(),
+                  "count": [int(n.sum())]}
+        if all("q01" in h and "q99" in h for h in have):
+            merged["q01"] = np.min(np.stack([np.asarray(h["q01"], dtype=np.float64) for h in have]), 0).tolist()
+            merged["q99"] = np.max(np.stack([np.asarray(h["q99"], dtype=np.float64) for h in have]), 0).tolist()
+        out[key] = merged
+    return out
+
+
 def load_stats(path: str) -> dict:
-    """``stats.json`` of a data set (or the directory holding ``meta/stats.json``)."""
+    """``stats.json`` of a data set, or the directory holding ``meta/stats.json``; a LeRobot v2.1 directory that only has
+    per-episode statistics (``meta/episodes_stats.jsonl``, one ``{"episode_index", "stats"}`` record per line) is merged."""
     if os.path.isdir(path):
-        path = os.path.join(path, "meta", "stats.json")
+        whole, per_episode = os.path.join(path, "meta", "stats.json"), os.path.join(path, "meta", "episodes_stats.jsonl")
+        if not os.path.isfile(whole) and os.path.isfile(per_episode):
+            with open(per_episode) as f:
+                return merge_stats([json.loads(line)["stats"] for line in f if line.strip()])
+        path = whole
     with open(path) as f:
         return json.load(f)
 

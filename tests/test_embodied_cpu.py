@@ -833,3 +833,77 @@ def test_microbatch_graph_runner_signatures_and_padding():
     r.run({"text": torch.ones(2, 9, dtype=torch.long), "state": x})
     r.run({"text": torch.ones(2, 17, dtype=torch.long), "state": x})
     assert len(r.captured) == 2 and r.calls == 4 and r.graph is None                      # oldest signature dropped; no GPU: eager
+
+
+def test_hdf5_bimanual_episodes(tmp_path):
+    """Trajectory logic of the HDF5 data set on a dictionary-backed episode (no HDF5 library needed): rotation layout
+    against SciPy, two-second windows on the common clock, static windows dropped, first point = state."""
+    import json
+    import numpy as np
+    from scipy.spatial.transform import Rotation
+
+    from loongforge_b200.embodied.config import EmbodiedArgs
+    from loongforge_b200.embodied.hdf5_data import HDF5Episodes, arm_trajectories, quat_xyzw_to_rot6d
+
+    rng = np.random.default_rng(0)
+    q = rng.normal(size=(5, 4))
+    want = Rotation.from_quat(q / np.linalg.norm(q, axis=-1, keepdims=True)).as_matrix()[..., :, :2].reshape(5, 6)
+    assert np.allclose(quat_xyzw_to_rot6d(q), want, atol=1e-9)
+
+    T = 120
+    eef = np.zeros((T, 16), dtype=np.float32)
+    eef[:, 6] = eef[:, 14] = 1.0                                   # identity rotations
+    t = np.arange(T) / 30.0
+    eef[60:, 0] = t[60:] - t[60]                                   # the left arm rests for two seconds, then moves
+    eef[:, 7], eef[:, 15] = 0.01, 0.05                             # left gripper closed (0.5 < 1), right open
+    left, right = arm_trajectories(eef)
+    assert left.shape == (T, 10) and left[0, 9] == 1.0 and right[0, 9] == 0.0 and np.allclose(left[0, 3:9], [1, 0, 0, 1, 0, 0])
+    store = {"observations/eef_quaternion": eef, "language_instruction": b"fold the towel",
+             "observations/images/cam_high": rng.integers(0, 255, size=(T, 12, 16, 3), dtype=np.uint8)}
+    (tmp_path / "metadata.json").write_text(json.dumps({"dataset_name": "agilex", "datalist": ["episode_0.hdf5"],
+                                                        "observation_key": ["observations/images/cam_high"]}))
+    a = EmbodiedArgs(model_name="xvla", action_horizon=8, image_size=8, num_cameras=2, max_text_len=8)
+    ds = HDF5Episodes(a, str(tmp_path), opener=lambda path: store)
+    starts = [s for _, s in ds.index]
+    assert starts and all(s % 2 == 0 and s < T - 30 for s in starts)
+    assert min(starts) > 0 and min(starts) <= 60                   # the windows before any motion are dropped
+    s = ds[0]
+    assert s["images"].shape == (2, 3, 8, 8) and s["images"][1].max() == 0 and 0 <= s["images"][0].min() and s["images"][0].max() <= 1
+    assert s["state"].shape == (20,) and s["actions"].shape == (8, 20) and s["action_mask"].sum() == 8
+    i = starts.index(60)
+    w = ds[i]
+    assert np.allclose(w["state"][0], 0.0) and np.allclose(w["actions"][-1][0], 59 / 30, atol=1e-5)   # held at the episode's end
+    assert np.allclose(np.diff(w["actions"][:, 0])[:3], (59 / 30) / 8, atol=1e-4)
+    ds.raw = True
+    assert ds[0]["task"] == "fold the towel" and ds[0]["embodiment_tag"] == "agilex"
+    assert ds.__getstate__()["_open"] == {} and ds._open        # open files stay out of what loader workers receive
+
+
+def test_merge_stats_and_block_shard_sampler(tmp_path):
+    import json
+    import numpy as np
+    from loongforge_b200.embodied.data import BlockShardSampler
+    from loongforge_b200.embodied.transforms import compute_stats, load_stats, merge_stats
+
+    rng = np.random.default_rng(0)
+    parts = [rng.normal(i, 1 + i, size=(50 + 20 * i, 3)) for i in range(3)]
+    merged = merge_stats([{"action": compute_stats([p])} for p in parts])["action"]
+    whole = compute_stats([np.concatenate(parts)])
+    for k in ("mean", "std", "min", "max"):
+        assert np.allclose(merged[k], whole[k], atol=1e-9), k
+    assert merged["count"] == [210] and np.all(np.asarray(merged["q99"]) >= np.asarray(whole["q99"]))
+    (tmp_path / "meta").mkdir()
+    with open(tmp_path / "meta" / "episodes_stats.jsonl", "w") as f:
+        for i, p in enumerate(parts):
+            f.write(json.dumps({"episode_index": i, "stats": {"action": compute_stats([p])}}) + "\n")
+    assert np.allclose(load_stats(str(tmp_path))["action"]["std"], whole["std"], atol=1e-9)
+
+    data = list(range(23))
+    one = list(BlockShardSampler(data, 2, 1, 0, seed=5))
+    ranks = [list(BlockShardSampler(data, 2, 2, r, seed=5)) for r in range(2)]
+    assert len(ranks[0]) == len(ranks[1]) == 10 == len(BlockShardSampler(data, 2, 2, 0))
+    for k in range(5):                                            # round k on two ranks = batches 2k, 2k+1 of one process
+        assert ranks[0][2 * k:2 * k + 2] == one[4 * k:4 * k + 2] and ranks[1][2 * k:2 * k + 2] == one[4 * k + 2:4 * k + 4]
+    s = BlockShardSampler(data, 2, 2, 0, seed=5)
+    s.set_epoch(1)
+    assert list(s) != ranks[0]
