@@ -74,16 +74,29 @@ def test_trainer_learns_and_resumes(tmp_path):
     assert t2.step == 8 and t2.scheduler.step_count == 8
 
 
+def _open_gates(model):
+    """A freshly initialised Pi0.5 gates every action-expert sub-layer with zero (adaptive norms start at zero), so nothing
+    inside them receives a gradient until the gates move; pretrained weights have them open. Open them as a checkpoint would."""
+    torch.manual_seed(11)
+    with torch.no_grad():
+        for m in model.modules():
+            if getattr(m, "dense", None) is not None and hasattr(m, "eps"):
+                m.dense.weight.normal_(std=0.05)
+                m.dense.bias.normal_(std=0.5)
+
+
 def test_lora_freezes_base_and_trains_adapters(tmp_path):
     from loongforge_b200.embodied.trainer import build_trainer
 
-    a = _args(tmp_path, lora_rank=2, lora_targets=["qkv", "o"], train_steps=2)
+    a = _args(tmp_path, lora_rank=2, lora_targets=["qkv", "o"], train_steps=2, weight_decay=0.0)
     t = build_trainer(a)
     t._setup()
+    _open_gates(t.model)
     before = {n: p.detach().clone() for n, p in t.model.named_parameters()}
     t._training_loop()
     changed = [n for n, p in t.model.named_parameters() if not torch.equal(p, before[n])]
-    assert changed and all("lora_" in n for n in changed)
+    assert changed and all("lora_" in n for n in changed)       # no weight decay: these moved by their gradients
+    assert any(".expert." in n and ".lora_b." in n for n in changed)
     assert t.lora_meta["modules"]
 
 
@@ -907,3 +920,40 @@ def test_merge_stats_and_block_shard_sampler(tmp_path):
     s = BlockShardSampler(data, 2, 2, 0, seed=5)
     s.set_epoch(1)
     assert list(s) != ranks[0]
+
+
+def test_export_checkpoint_folds_lora_into_one_file(tmp_path):
+    """A LoRA run's checkpoint exported to one safetensors file loads into a plain model and gives the same loss."""
+    from safetensors.torch import load_file
+
+    from loongforge_b200.embodied import export_checkpoint as ex
+    from loongforge_b200.embodied.models import build_policy
+    from loongforge_b200.embodied.trainer import build_trainer
+
+    a = _args(tmp_path, lora_rank=2, lora_targets=["qkv", "o"], train_steps=2, save_interval=2, lr=1e-2)
+    t = build_trainer(a)
+    t._setup()
+    _open_gates(t.model)
+    t._training_loop()
+    assert any(float(p.abs().max()) > 0 for n, p in t.model.named_parameters() if ".lora_b." in n)   # something to fold
+    root = os.path.join(a.output_dir, "checkpoints")
+    root = root if os.path.isdir(root) else a.output_dir
+    out = str(tmp_path / "release" / "policy.safetensors")
+    assert ex.main(["--ckpt", root, "--out", out]) == 0
+    sd = load_file(out)
+    assert sd and not any("lora_" in k or ".base." in k for k in sd)
+    plain = build_policy(a.model_name, a)
+    missing, unexpected = plain.load_state_dict(sd, strict=False)
+    assert not unexpected and not missing
+    batch = next(iter(t.loader))
+    t.model.eval(), plain.eval()
+    with torch.no_grad():
+        torch.manual_seed(3)
+        want = float(t.model(batch))
+        torch.manual_seed(3)
+        got = float(plain(batch))
+    assert abs(want - got) < 1e-5 * max(1.0, abs(want))
+    kept = ex.export(root, str(tmp_path / "kept.pt"), fmt="pt", keep_lora=True, dtype="bf16")
+    blob = torch.load(str(tmp_path / "kept.pt"))
+    assert kept["lora_folded"] == 0 and any(".lora_a." in k for k in blob) and all(
+        v.dtype == torch.bfloat16 for v in blob.values() if v.is_floating_point())
