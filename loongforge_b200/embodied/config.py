@@ -66,6 +66,7 @@ class EmbodiedArgs:
     pretrained_strict: bool = False
     freeze_modules: List[str] = dataclasses.field(default_factory=list)  # dot paths or globs of sub-modules kept frozen
     num_workers: int = 0
+    video_backend: str = "opencv"  # opencv | pyav | decord | torchcodec (the last three when installed)
     sampler: str = "distributed"  # distributed (samples dealt to ranks) | block_shard (whole batches dealt to ranks)
     save_training_state: bool = True   # False: checkpoints hold the weights only
     async_save: bool = False           # pt format: the file is written by a background thread from a CPU copy

@@ -192,6 +192,10 @@ class LeRobotParquet(Dataset):
             data = cell.get("bytes") if isinstance(cell, dict) else cell
             import cv2
             img = cv2.imdecode(np.frombuffer(data, np.uint8), cv2.IMREAD_COLOR)[:, :, ::-1]
+        elif key in self.video_keys and getattr(self.a, "video_backend", "opencv") != "opencv":
+            from .video_backends import decode_frames
+            f = self._video_file(ep, key)
+            img = decode_frames(f, indices=[t], backend=self.a.video_backend)[0] if os.path.isfile(f) else None
         elif key in self.video_keys:
             import cv2
             f = self._video_file(ep, key)

@@ -957,3 +957,26 @@ def test_export_checkpoint_folds_lora_into_one_file(tmp_path):
     blob = torch.load(str(tmp_path / "kept.pt"))
     assert kept["lora_folded"] == 0 and any(".lora_a." in k for k in blob) and all(
         v.dtype == torch.bfloat16 for v in blob.values() if v.is_floating_point())
+
+
+def test_video_backends_decode_by_index_and_time(tmp_path):
+    import cv2
+    from loongforge_b200.embodied.video_backends import decode_frames
+
+    path = str(tmp_path / "clip.mp4")
+    w = cv2.VideoWriter(path, cv2.VideoWriter_fourcc(*"mp4v"), 10.0, (32, 32))
+    for i in range(10):
+        w.write(np.full((32, 32, 3), i * 25, dtype=np.uint8))
+    w.release()
+    got = decode_frames(path, indices=[7, 2, 2, 9, 30])
+    assert got.shape == (5, 32, 32, 3) and got.dtype == np.uint8
+    level = got.reshape(5, -1).mean(1)
+    assert np.allclose(level, [175, 50, 50, 225, 225], atol=6)        # request order kept, past the end = last frame
+    by_time = decode_frames(path, timestamps=[0.0, 0.31, 0.7]).reshape(3, -1).mean(1)
+    assert np.allclose(by_time, [0, 75, 175], atol=6)
+    with pytest.raises(ValueError):
+        decode_frames(path)
+    with pytest.raises(ValueError):
+        decode_frames(path, indices=[0], backend="vhs")
+    with pytest.raises(ImportError, match="not installed"):
+        decode_frames(path, indices=[0], backend="decord")
